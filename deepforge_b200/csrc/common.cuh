@@ -1,0 +1,187 @@
+// Shared device/host helpers of the dfgpu kernel library (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "dfgpu.h"
+
+namespace dfgpu {
+
+// DeepForge Status codes the launchers return.
+constexpr int kOk = 0;
+constexpr int kInvalidArgument = 1;
+constexpr int kInvalidLayout = 14;
+constexpr int kInvalidShape = 15;
+constexpr int kExecutionFailed = 19;
+constexpr int kUnsupported = 20;
+
+int fail(int code, const char* format, ...);
+int check_launch(const char* what);
+
+inline cudaStream_t as_stream(void* stream) { return static_cast<cudaStream_t>(stream); }
+
+inline int64_t element_count(const dfgpu_tensor& t) {
+    int64_t count = 1;
+    for (int i = 0; i < t.rank; ++i) count *= t.dim[i];
+    return count;
+}
+
+inline bool is_packed_row_major(const dfgpu_tensor& t) {
+    int64_t expected = 1;
+    for (int i = t.rank - 1; i >= 0; --i) {
+        if (t.dim[i] != 1 && t.stride[i] != expected) return false;
+        expected *= t.dim[i];
+    }
+    return true;
+}
+
+inline int dtype_bytes(int dtype) {
+    switch (dtype) {
+        case DFGPU_F32: case DFGPU_I32: return 4;
+        case DFGPU_F16: case DFGPU_BF16: return 2;
+        default: return 1;
+    }
+}
+
+inline bool valid_tensor(const dfgpu_tensor& t) {
+    if (t.rank < 1 || t.rank > DFGPU_MAX_RANK) return false;
+    for (int i = 0; i < t.rank; ++i)
+        if (t.dim[i] <= 0 || t.stride[i] < 0) return false;
+    return true;
+}
+
+int sm_count();
+
+// ---- device-side element access -------------------------------------------------
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16) {
+    return __uint_as_float(bits16 << 16);
+}
+
+// Round-to-nearest-even f32 -> bf16 with NaN kept quiet (arith.truncf semantics).
+__device__ __forceinline__ uint16_t f32_to_bf16_bits(float value) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(value));
+}
+
+// E4M3 decode: exponent 0 -> m * 2^-9, 0x7f/0xff -> NaN, else (1+m/8) * 2^(e-7).
+__device__ __forceinline__ float decode_e4m3(uint32_t code) {
+    uint32_t magnitude = code & 0x7fu;
+    float value;
+    if (magnitude == 0x7fu) {
+        value = __int_as_float(0x7fc00000);
+    } else if ((magnitude >> 3) == 0) {
+        value = static_cast<float>(magnitude) * 0.001953125f;
+    } else {
+        // place exponent/mantissa into an f32: bias 7 -> 127 adds 120 to the exponent
+        value = __uint_as_float((magnitude << 20) + (120u << 23));
+    }
+    return (code & 0x80u) ? -value : value;
+}
+
+// E8M0 decode: 2^(code-127); 0xff -> NaN. Code 0 is the f32 subnormal 2^-127.
+__device__ __forceinline__ float decode_e8m0(uint32_t code) {
+    if (code == 0xffu) return __int_as_float(0x7fc00000);
+    if (code == 0u) return __uint_as_float(0x00400000u);
+    return __uint_as_float(code << 23);
+}
+
+// Exact reciprocal of an E8M0 scale as f32 (2^(127-code)); multiplying by it is
+// bit-identical to the IEEE division by the scale because both are the correctly
+// rounded value of the same real number. code 254 -> 2^-127 (subnormal), NaN kept.
+__device__ __forceinline__ float reciprocal_e8m0(uint32_t code) {
+    if (code == 0xffu) return __int_as_float(0x7fc00000);
+    if (code == 254u) return __uint_as_float(0x00400000u);
+    return __uint_as_float((254u - code) << 23);
+}
+
+__device__ __forceinline__ float load_as_f32(const void* data, int dtype, int64_t offset) {
+    switch (dtype) {
+        case DFGPU_F32: return static_cast<const float*>(data)[offset];
+        case DFGPU_F16: return __half2float(static_cast<const __half*>(data)[offset]);
+        case DFGPU_BF16: return bf16_bits_to_f32(static_cast<const uint16_t*>(data)[offset]);
+        case DFGPU_E4M3: return decode_e4m3(static_cast<const uint8_t*>(data)[offset]);
+        case DFGPU_E8M0: return decode_e8m0(static_cast<const uint8_t*>(data)[offset]);
+        case DFGPU_I32: return static_cast<float>(static_cast<const int32_t*>(data)[offset]);
+        default: return 0.0f;
+    }
+}
+
+__device__ __forceinline__ void store_from_f32(void* data, int dtype, int64_t offset, float value) {
+    switch (dtype) {
+        case DFGPU_F32: static_cast<float*>(data)[offset] = value; break;
+        case DFGPU_F16: static_cast<__half*>(data)[offset] = __float2half_rn(value); break;
+        case DFGPU_BF16: static_cast<uint16_t*>(data)[offset] = f32_to_bf16_bits(value); break;
+        default: break;
+    }
+}
+
+// arith.maximumf / minimumf: NaN if either side is NaN (CUDA's fmaxf drops NaN).
+__device__ __forceinline__ float maximum_nan(float a, float b) {
+    float m = fmaxf(a, b);
+    return (a != a || b != b) ? __int_as_float(0x7fc00000) : m;
+}
+__device__ __forceinline__ float minimum_nan(float a, float b) {
+    float m = fminf(a, b);
+    return (a != a || b != b) ? __int_as_float(0x7fc00000) : m;
+}
+
+// RELU_FWD with clips and lower slope:
+//   x < lower ? lower + slope * (x - lower) : min(max(x, lower), upper), NaN propagating.
+__device__ __forceinline__ float relu_forward(float x, float lower, float upper, float slope) {
+    float clipped = minimum_nan(maximum_nan(x, lower), upper);
+    float lower_branch = __fadd_rn(lower, __fmul_rn(slope, __fsub_rn(x, lower)));
+    return x < lower ? lower_branch : clipped;
+}
+
+// Tensor view passed by value to the generic kernels.
+struct View {
+    int32_t dtype;
+    int32_t rank;
+    int64_t dim[DFGPU_MAX_RANK];
+    int64_t stride[DFGPU_MAX_RANK];
+};
+
+inline View make_view(const dfgpu_tensor& t) {
+    View v{};
+    v.dtype = t.dtype;
+    v.rank = t.rank;
+    for (int i = 0; i < DFGPU_MAX_RANK; ++i) {
+        v.dim[i] = i < t.rank ? t.dim[i] : 1;
+        v.stride[i] = i < t.rank ? t.stride[i] : 0;
+    }
+    return v;
+}
+
+// The fused epilogue carried by value into contraction kernels.
+struct Epilogue {
+    int32_t count;
+    int32_t op[DFGPU_MAX_EPILOGUE];
+    int32_t operand[DFGPU_MAX_EPILOGUE];
+    float lower[DFGPU_MAX_EPILOGUE];
+    float upper[DFGPU_MAX_EPILOGUE];
+    float slope[DFGPU_MAX_EPILOGUE];
+};
+
+inline Epilogue make_epilogue(int count, const dfgpu_epilogue_step* steps) {
+    Epilogue e{};
+    e.count = count;
+    for (int i = 0; i < count && i < DFGPU_MAX_EPILOGUE; ++i) {
+        e.op[i] = steps[i].op;
+        e.operand[i] = steps[i].operand;
+        e.lower[i] = steps[i].relu_lower;
+        e.upper[i] = steps[i].relu_upper;
+        e.slope[i] = steps[i].relu_slope;
+    }
+    return e;
+}
+
+int validate_epilogue(int count, const dfgpu_epilogue_step* steps, const dfgpu_tensor* extra,
+                      void* const* extra_pointers, const dfgpu_tensor& out, const char* what);
+
+}  // namespace dfgpu

@@ -1,0 +1,303 @@
+// CONV_FPROP on CUDA cores: a direct kernel that covers every rank-4 convolution
+// the generic path accepts (groups, stride, dilation, asymmetric padding, filter
+// reversal, any strides, f32/f16/bf16 storage) and an f32-accumulate implicit-GEMM
+// kernel for groups == 1. The tcgen05 implicit GEMM for bf16 NHWC lives in
+// umma_gemm.cu; this file owns the launcher and the kernel choice.
+//
+// Padding: out-of-range taps read as 0 and are still multiplied, which is what the
+// reference's single-node path does with its materialised zero padding; for finite
+// data this equals the generic path's "skip the tap" rule.
+#include "common.cuh"
+#include "umma.cuh"
+
+namespace dfgpu {
+namespace {
+
+struct ConvArgs {
+    View x, w, y;
+    View extra[2];
+    const void* extra_data[2];
+    Epilogue epilogue;
+    int32_t pad_h, pad_w, stride_h, stride_w, dilation_h, dilation_w;
+    int32_t reverse;
+    int32_t groups;
+    int64_t c_per_group, k_per_group;
+};
+
+__device__ __forceinline__ float apply_epilogue(float value, const ConvArgs& a, int64_t n, int64_t k, int64_t p, int64_t q) {
+    for (int step = 0; step < a.epilogue.count; ++step) {
+        if (a.epilogue.op[step] == DFGPU_EPI_ADD) {
+            const View& t = a.extra[a.epilogue.operand[step]];
+            int64_t index[4] = {n, k, p, q};
+            int shift = 4 - t.rank;
+            int64_t offset = 0;
+            for (int i = 0; i < t.rank; ++i) offset += (t.dim[i] == 1 ? 0 : index[i + shift]) * t.stride[i];
+            value = __fadd_rn(value, load_as_f32(a.extra_data[a.epilogue.operand[step]], t.dtype, offset));
+        } else {
+            value = relu_forward(value, a.epilogue.lower[step], a.epilogue.upper[step], a.epilogue.slope[step]);
+        }
+    }
+    return value;
+}
+
+__global__ void conv_direct_kernel(const void* x, const void* w, void* y, ConvArgs a, int64_t total) {
+    int64_t flat = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (flat >= total) return;
+    int64_t q = flat % a.y.dim[3];
+    int64_t rest = flat / a.y.dim[3];
+    int64_t p = rest % a.y.dim[2];
+    rest /= a.y.dim[2];
+    int64_t k = rest % a.y.dim[1];
+    int64_t n = rest / a.y.dim[1];
+    int64_t group = k / a.k_per_group;
+    int64_t R = a.w.dim[2], S = a.w.dim[3];
+    float sum = 0.0f;
+    for (int64_t c = 0; c < a.c_per_group; ++c) {
+        int64_t xc = group * a.c_per_group + c;
+        for (int64_t r = 0; r < R; ++r) {
+            int64_t ih = p * a.stride_h + r * a.dilation_h - a.pad_h;
+            if (ih < 0 || ih >= a.x.dim[2]) continue;
+            for (int64_t s = 0; s < S; ++s) {
+                int64_t iw = q * a.stride_w + s * a.dilation_w - a.pad_w;
+                if (iw < 0 || iw >= a.x.dim[3]) continue;
+                int64_t wr = a.reverse ? R - 1 - r : r, ws = a.reverse ? S - 1 - s : s;
+                float xv = load_as_f32(x, a.x.dtype, n * a.x.stride[0] + xc * a.x.stride[1] + ih * a.x.stride[2] + iw * a.x.stride[3]);
+                float wv = load_as_f32(w, a.w.dtype, k * a.w.stride[0] + c * a.w.stride[1] + wr * a.w.stride[2] + ws * a.w.stride[3]);
+                sum = __fadd_rn(sum, __fmul_rn(xv, wv));
+            }
+        }
+    }
+    sum = apply_epilogue(sum, a, n, k, p, q);
+    store_from_f32(y, a.y.dtype, n * a.y.stride[0] + k * a.y.stride[1] + p * a.y.stride[2] + q * a.y.stride[3], sum);
+}
+
+// Implicit GEMM: M = N*P*Q output pixels, N = K output channels, K = C*R*S.
+// BM x 64 tile, 16-deep K slices through shared memory, 256 threads with a
+// (BM/16) x 4 register tile each. CHANNELS_LAST picks the K ordering (r,s,c with c
+// fastest, or c,r,s with s fastest) and the thread->element map of the X loads so
+// that consecutive lanes read consecutive addresses in either layout.
+template <int BM, bool CHANNELS_LAST>
+__global__ void __launch_bounds__(256)
+conv_igemm_ffma_kernel(const void* __restrict__ x, const void* __restrict__ w, void* __restrict__ y, ConvArgs a,
+                       int64_t m_total, int64_t k_total) {
+    constexpr int BN = 64, BK = 16, TM = BM / 16, TN = 4;
+    constexpr int A_PER_THREAD = BM * BK / 256;
+    constexpr int B_PER_THREAD = BN * BK / 256;
+    __shared__ float as[BK][BM + 4];
+    __shared__ float bs[BK][BN + 4];
+
+    const int tid = threadIdx.x;
+    const int64_t m0 = static_cast<int64_t>(blockIdx.x) * BM;
+    const int64_t n0 = static_cast<int64_t>(blockIdx.y) * BN;
+    const int64_t P = a.y.dim[2], Q = a.y.dim[3];
+    const int64_t C = a.x.dim[1], R = a.w.dim[2], S = a.w.dim[3];
+    const int64_t K = a.y.dim[1];
+
+    // element -> (m, k) map of this thread's A loads
+    int a_m[A_PER_THREAD], a_k[A_PER_THREAD];
+    int64_t a_base[A_PER_THREAD];
+    int32_t a_ih0[A_PER_THREAD], a_iw0[A_PER_THREAD];
+    bool a_ok[A_PER_THREAD];
+#pragma unroll
+    for (int i = 0; i < A_PER_THREAD; ++i) {
+        int e = tid + i * 256;
+        if (CHANNELS_LAST) { a_k[i] = e % BK; a_m[i] = e / BK; }
+        else { a_m[i] = e % BM; a_k[i] = e / BM; }
+        int64_t m = m0 + a_m[i];
+        a_ok[i] = m < m_total;
+        int64_t mm = a_ok[i] ? m : 0;
+        int64_t q = mm % Q, p = (mm / Q) % P, n = mm / (P * Q);
+        a_base[i] = n * a.x.stride[0];
+        a_ih0[i] = static_cast<int32_t>(p * a.stride_h - a.pad_h);
+        a_iw0[i] = static_cast<int32_t>(q * a.stride_w - a.pad_w);
+    }
+    int b_n[B_PER_THREAD], b_k[B_PER_THREAD];
+#pragma unroll
+    for (int i = 0; i < B_PER_THREAD; ++i) {
+        int e = tid + i * 256;
+        b_k[i] = e % BK;
+        b_n[i] = e / BK;
+    }
+
+    const int ty = tid / 16, tx = tid % 16;
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+
+    for (int64_t k0 = 0; k0 < k_total; k0 += BK) {
+#pragma unroll
+        for (int i = 0; i < A_PER_THREAD; ++i) {
+            int64_t kk = k0 + a_k[i];
+            float value = 0.0f;
+            if (a_ok[i] && kk < k_total) {
+                int64_t c, r, s;
+                if (CHANNELS_LAST) { c = kk % C; s = (kk / C) % S; r = kk / (C * S); }
+                else { s = kk % S; r = (kk / S) % R; c = kk / (R * S); }
+                int64_t ih = a_ih0[i] + r * a.dilation_h, iw = a_iw0[i] + s * a.dilation_w;
+                if (ih >= 0 && ih < a.x.dim[2] && iw >= 0 && iw < a.x.dim[3])
+                    value = load_as_f32(x, a.x.dtype, a_base[i] + c * a.x.stride[1] + ih * a.x.stride[2] + iw * a.x.stride[3]);
+            }
+            as[a_k[i]][a_m[i]] = value;
+        }
+#pragma unroll
+        for (int i = 0; i < B_PER_THREAD; ++i) {
+            int64_t kk = k0 + b_k[i];
+            int64_t n = n0 + b_n[i];
+            float value = 0.0f;
+            if (n < K && kk < k_total) {
+                int64_t c, r, s;
+                if (CHANNELS_LAST) { c = kk % C; s = (kk / C) % S; r = kk / (C * S); }
+                else { s = kk % S; r = (kk / S) % R; c = kk / (R * S); }
+                if (a.reverse) { r = R - 1 - r; s = S - 1 - s; }
+                value = load_as_f32(w, a.w.dtype, n * a.w.stride[0] + c * a.w.stride[1] + r * a.w.stride[2] + s * a.w.stride[3]);
+            }
+            bs[b_k[i]][b_n[i]] = value;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float av[TM], bv[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) av[i] = as[kk][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) bv[j] = bs[kk][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        int64_t m = m0 + ty * TM + i;
+        if (m >= m_total) continue;
+        int64_t q = m % Q, p = (m / Q) % P, n = m / (P * Q);
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            int64_t k = n0 + tx * TN + j;
+            if (k >= K) continue;
+            float value = apply_epilogue(acc[i][j], a, n, k, p, q);
+            store_from_f32(y, a.y.dtype, n * a.y.stride[0] + k * a.y.stride[1] + p * a.y.stride[2] + q * a.y.stride[3], value);
+        }
+    }
+}
+
+int build_args(const dfgpu_conv_params& p, void* const* tensors, ConvArgs& a) {
+    if (!valid_tensor(p.x) || !valid_tensor(p.w) || !valid_tensor(p.y))
+        return fail(kInvalidShape, "CONV_FPROP: tensor rank or extent out of range");
+    if (p.x.rank != 4 || p.w.rank != 4 || p.y.rank != 4)
+        return fail(kUnsupported, "CONV_FPROP: only rank-4 (2-D spatial) convolutions are executable on this backend");
+    auto float_type = [](int t) { return t == DFGPU_F32 || t == DFGPU_F16 || t == DFGPU_BF16; };
+    if (!float_type(p.x.dtype) || !float_type(p.w.dtype) || !float_type(p.y.dtype))
+        return fail(kUnsupported, "CONV_FPROP: tensors must be FLOAT, HALF or BFLOAT16");
+    if (p.x.dim[0] != p.y.dim[0] || p.w.dim[0] != p.y.dim[1] || p.w.dim[1] <= 0 || p.x.dim[1] % p.w.dim[1] != 0)
+        return fail(kInvalidShape, "CONV_FPROP: convolution N/K/C dimensions are inconsistent");
+    int64_t groups = p.x.dim[1] / p.w.dim[1];
+    if (groups <= 0 || p.y.dim[1] % groups != 0)
+        return fail(kInvalidShape, "CONV_FPROP: convolution output channels are not divisible by groups");
+    for (int axis = 0; axis < 2; ++axis) {
+        if (p.pre_pad[axis] < 0 || p.post_pad[axis] < 0 || p.stride[axis] <= 0 || p.dilation[axis] <= 0)
+            return fail(kInvalidArgument, "CONV_FPROP: padding must be non-negative and stride/dilation positive");
+        int64_t dilated = p.dilation[axis] * (p.w.dim[axis + 2] - 1) + 1;
+        int64_t padded = p.x.dim[axis + 2] + p.pre_pad[axis] + p.post_pad[axis];
+        if (padded < dilated) return fail(kInvalidShape, "CONV_FPROP: effective filter exceeds padded input");
+        if (p.y.dim[axis + 2] != 1 + (padded - dilated) / p.stride[axis])
+            return fail(kInvalidShape, "CONV_FPROP: output spatial dimensions do not match attributes");
+    }
+    int status = validate_epilogue(p.epilogue_count, p.epilogue, p.extra, tensors ? tensors + 3 : nullptr, p.y, "CONV_FPROP");
+    if (status) return status;
+    a.x = make_view(p.x);
+    a.w = make_view(p.w);
+    a.y = make_view(p.y);
+    a.extra[0] = make_view(p.extra[0]);
+    a.extra[1] = make_view(p.extra[1]);
+    a.extra_data[0] = tensors ? tensors[3] : nullptr;
+    a.extra_data[1] = tensors ? tensors[4] : nullptr;
+    a.epilogue = make_epilogue(p.epilogue_count, p.epilogue);
+    a.pad_h = static_cast<int32_t>(p.pre_pad[0]);
+    a.pad_w = static_cast<int32_t>(p.pre_pad[1]);
+    a.stride_h = static_cast<int32_t>(p.stride[0]);
+    a.stride_w = static_cast<int32_t>(p.stride[1]);
+    a.dilation_h = static_cast<int32_t>(p.dilation[0]);
+    a.dilation_w = static_cast<int32_t>(p.dilation[1]);
+    a.reverse = p.reverse_filter;
+    a.groups = static_cast<int32_t>(groups);
+    a.c_per_group = p.w.dim[1];
+    a.k_per_group = p.y.dim[1] / groups;
+    return kOk;
+}
+
+int choose_kernel(const dfgpu_conv_params& p, const ConvArgs& a, int& kernel) {
+    int automatic = a.groups == 1 ? DFGPU_CONV_IGEMM_FFMA : DFGPU_CONV_DIRECT;
+    if (conv_umma_supported(p)) automatic = DFGPU_CONV_UMMA_BF16;
+    kernel = p.kernel == DFGPU_CONV_AUTO ? automatic : p.kernel;
+    if (kernel == DFGPU_CONV_IGEMM_FFMA && a.groups != 1)
+        return fail(kUnsupported, "CONV_FPROP: the implicit-GEMM kernel needs groups == 1");
+    if (kernel == DFGPU_CONV_UMMA_BF16 && !conv_umma_supported(p))
+        return fail(kUnsupported, "CONV_FPROP: the tcgen05 kernel needs bf16 NHWC/KRSC, C and K multiples of 64, stride 1, dilation 1");
+    if (kernel < DFGPU_CONV_DIRECT || kernel > DFGPU_CONV_UMMA_BF16)
+        return fail(kInvalidArgument, "CONV_FPROP: unknown kernel id %d", kernel);
+    return kOk;
+}
+
+}  // namespace
+}  // namespace dfgpu
+
+using namespace dfgpu;
+
+extern "C" int dfgpu_query_conv_fprop(const dfgpu_conv_params* p, dfgpu_plan_info* info) {
+    if (!p || !info) return fail(kInvalidArgument, "CONV_FPROP: null params");
+    ConvArgs a;
+    dfgpu_conv_params copy = *p;
+    int saved = copy.epilogue_count;
+    copy.epilogue_count = 0;  // pointers are not available at query time
+    int status = build_args(copy, nullptr, a);
+    if (status) return status;
+    copy.epilogue_count = saved;
+    int kernel;
+    status = choose_kernel(copy, a, kernel);
+    if (status) return status;
+    info->kernel = kernel;
+    info->launches = 1;
+    info->scratch_bytes = 0;
+    return kOk;
+}
+
+extern "C" int dfgpu_conv_fprop(const dfgpu_conv_params* p, void* const* tensors, void* scratch, void* stream_handle) {
+    (void)scratch;
+    if (!p || !tensors) return fail(kInvalidArgument, "CONV_FPROP: null params");
+    if (!tensors[0] || !tensors[1] || !tensors[2]) return fail(kInvalidArgument, "CONV_FPROP: null tensor pointer");
+    ConvArgs a;
+    int status = build_args(*p, tensors, a);
+    if (status) return status;
+    int kernel;
+    status = choose_kernel(*p, a, kernel);
+    if (status) return status;
+    cudaStream_t stream = as_stream(stream_handle);
+    if (kernel == DFGPU_CONV_UMMA_BF16) return launch_conv_umma(*p, tensors, stream);
+    int64_t m_total = p->y.dim[0] * p->y.dim[2] * p->y.dim[3];
+    if (kernel == DFGPU_CONV_DIRECT) {
+        int64_t total = element_count(p->y);
+        conv_direct_kernel<<<static_cast<unsigned>((total + 127) / 128), 128, 0, stream>>>(tensors[0], tensors[1], tensors[2], a, total);
+    } else {
+        int64_t k_total = p->x.dim[1] * p->w.dim[2] * p->w.dim[3];
+        bool channels_last = p->x.stride[1] == 1;
+        unsigned grid_n = static_cast<unsigned>((p->y.dim[1] + 63) / 64);
+        int64_t tiles64 = (m_total + 63) / 64 * grid_n;
+        bool small = tiles64 < 2 * sm_count();
+        if (small) {
+            dim3 grid(static_cast<unsigned>((m_total + 31) / 32), grid_n);
+            if (channels_last) conv_igemm_ffma_kernel<32, true><<<grid, 256, 0, stream>>>(tensors[0], tensors[1], tensors[2], a, m_total, k_total);
+            else conv_igemm_ffma_kernel<32, false><<<grid, 256, 0, stream>>>(tensors[0], tensors[1], tensors[2], a, m_total, k_total);
+        } else {
+            dim3 grid(static_cast<unsigned>((m_total + 63) / 64), grid_n);
+            if (channels_last) conv_igemm_ffma_kernel<64, true><<<grid, 256, 0, stream>>>(tensors[0], tensors[1], tensors[2], a, m_total, k_total);
+            else conv_igemm_ffma_kernel<64, false><<<grid, 256, 0, stream>>>(tensors[0], tensors[1], tensors[2], a, m_total, k_total);
+        }
+    }
+    return check_launch("CONV_FPROP");
+}

@@ -1,0 +1,20 @@
+// Entry points of the tcgen05 (UMMA) kernels, used by the per-op launchers.
+#pragma once
+
+#include "common.cuh"
+
+namespace dfgpu {
+
+// bf16 NHWC/KRSC convolution as an implicit GEMM on tcgen05 (1x1 and 3x3, stride 1).
+bool conv_umma_supported(const dfgpu_conv_params& p);
+int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStream_t stream);
+
+// MATMUL on tcgen05: kernel is DFGPU_MATMUL_UMMA_BF16 or DFGPU_MATMUL_UMMA_MXF8.
+bool matmul_umma_supported(const dfgpu_matmul_params& p, int kernel);
+int launch_matmul_umma(const dfgpu_matmul_params& p, void* const* tensors, int kernel, cudaStream_t stream);
+
+// SDPA forward on tcgen05 (bf16, head dim 128, contiguous K/V).
+bool sdpa_umma_supported(const dfgpu_sdpa_params& p);
+int launch_sdpa_umma(const dfgpu_sdpa_params& p, void* const* tensors, void* scratch, cudaStream_t stream);
+
+}  // namespace dfgpu

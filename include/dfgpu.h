@@ -1,0 +1,208 @@
+/*
+ * dfgpu -- C ABI of the sm_100a kernel library behind DeepForge's op hot path.
+ *
+ * This is the boundary the runtime's execute() binds device buffers to: plain
+ * C structs, plain device pointers, no allocation and no synchronisation
+ * inside any launcher. Every launcher has the shape
+ *
+ *     int dfgpu_<op>(const dfgpu_<op>_params*, void* const* tensors,
+ *                    void* scratch, void* stream);
+ *
+ * `tensors` holds DEVICE pointers in the port order documented per op (a null
+ * entry for an absent optional port), `scratch` is caller-owned device memory
+ * of at least the size dfgpu_query_<op>() reports (may be null when that size
+ * is 0), `stream` is a cudaStream_t (null = the legacy default stream). The
+ * return value is 0 or one of DeepForge's numeric Status codes
+ * (include/DeepForge/Import/Status.h:10-32 in the reference): 1 invalid
+ * argument, 14 invalid layout, 15 invalid shape, 19 graph execution failed
+ * (a CUDA launch error), 20 unsupported operation (no kernel covers the
+ * request). dfgpu_last_error() gives the detail for the calling thread.
+ *
+ * Each entry point replaces the x86 object code the reference emits for one
+ * operation tag; the citation beside it names the emitter it stands in for.
+ */
+#ifndef DFGPU_H
+#define DFGPU_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DFGPU_MAX_RANK 8
+#define DFGPU_MAX_EPILOGUE 4
+
+/* storage types (subset of the reference's DataType the path executes) */
+enum {
+    DFGPU_F32 = 0,
+    DFGPU_F16 = 1,
+    DFGPU_BF16 = 2,
+    DFGPU_E4M3 = 3,
+    DFGPU_E8M0 = 4,
+    DFGPU_I32 = 5
+};
+
+enum { DFGPU_REORDER_NONE = 0, DFGPU_REORDER_F8_128x4 = 1 };
+
+/* Logical dims with strides in ELEMENTS, exactly as the serialized graph's
+   tensor entry gives them. rank == 0 marks an absent optional tensor. */
+typedef struct dfgpu_tensor {
+    int32_t dtype;
+    int32_t rank;
+    int32_t reorder;
+    int32_t reserved;
+    int64_t dim[DFGPU_MAX_RANK];
+    int64_t stride[DFGPU_MAX_RANK];
+} dfgpu_tensor;
+
+/* What dfgpu_query_<op>() reports: the kernel the launcher will use for these
+   params (after resolving kernel == 0 "auto"), the scratch it needs and the
+   number of kernel launches one call makes. */
+typedef struct dfgpu_plan_info {
+    int32_t kernel;
+    int32_t launches;
+    int64_t scratch_bytes;
+} dfgpu_plan_info;
+
+const char* dfgpu_last_error(void);
+int dfgpu_abi_version(void);
+
+/* Fused trailing pointwise work, applied to the f32 accumulator in order
+   before the output store. Stands in for POINTWISE nodes that consume a
+   contraction's virtual output (lib/Compiler/FoundationalGraph.cpp:2599 ADD,
+   :2731-2758 RELU_FWD). */
+enum { DFGPU_EPI_ADD = 1, DFGPU_EPI_RELU = 2 };
+typedef struct dfgpu_epilogue_step {
+    int32_t op;       /* DFGPU_EPI_* */
+    int32_t operand;  /* ADD: index into `extra` (0 or 1) */
+    float relu_lower;
+    float relu_upper;
+    float relu_slope;
+    int32_t reserved;
+} dfgpu_epilogue_step;
+
+/* ---- BLOCK_SCALE_QUANTIZE -------------------------------------------------
+   Replaces emit_block_quantize (lib/Compiler/SpecializedGraph.cpp:840-935)
+   with encode_low_precision (lib/Compiler/Numeric.cpp:504-632).
+   tensors: {X, Y, scale}. X f32/f16/bf16, Y E4M3, scale E8M0 (NONE or
+   F8_128x4). Codes and scales are bit-exact with the reference. */
+enum { DFGPU_BSQ_AUTO = 0, DFGPU_BSQ_GENERIC = 1, DFGPU_BSQ_ROW32 = 2, DFGPU_BSQ_COL32 = 3 };
+typedef struct dfgpu_bsq_params {
+    dfgpu_tensor x, y, scale;
+    int64_t block_size;
+    int32_t axis; /* < 0: last axis */
+    int32_t kernel;
+} dfgpu_bsq_params;
+int dfgpu_query_block_scale_quantize(const dfgpu_bsq_params*, dfgpu_plan_info*);
+int dfgpu_block_scale_quantize(const dfgpu_bsq_params*, void* const* tensors, void* scratch, void* stream);
+
+/* ---- BLOCK_SCALE_DEQUANTIZE -----------------------------------------------
+   Replaces emit_block_dequantize (lib/Compiler/SpecializedGraph.cpp:752-795).
+   tensors: {X, scale, Y}. X E4M3, scale E8M0, Y f32/f16/bf16. block[] covers
+   the trailing block_count axes. */
+enum { DFGPU_BSD_AUTO = 0, DFGPU_BSD_GENERIC = 1, DFGPU_BSD_PACKED = 2 };
+typedef struct dfgpu_bsd_params {
+    dfgpu_tensor x, scale, y;
+    int64_t block[DFGPU_MAX_RANK];
+    int32_t block_count;
+    int32_t kernel;
+} dfgpu_bsd_params;
+int dfgpu_query_block_scale_dequantize(const dfgpu_bsd_params*, dfgpu_plan_info*);
+int dfgpu_block_scale_dequantize(const dfgpu_bsd_params*, void* const* tensors, void* scratch, void* stream);
+
+/* ---- POINTWISE --------------------------------------------------------------
+   Replaces emit_pointwise (lib/Compiler/FoundationalGraph.cpp:2957-3004) for
+   the modes the path uses. tensors: {IN_0, IN_1 or null, OUT_0}. */
+enum { DFGPU_PW_ADD = 0, DFGPU_PW_RELU_FWD = 1, DFGPU_PW_IDENTITY = 2, DFGPU_PW_MUL = 3, DFGPU_PW_SUB = 4 };
+typedef struct dfgpu_pointwise_params {
+    dfgpu_tensor in0, in1, out;
+    int32_t mode;
+    float relu_lower, relu_upper, relu_slope;
+} dfgpu_pointwise_params;
+int dfgpu_query_pointwise(const dfgpu_pointwise_params*, dfgpu_plan_info*);
+int dfgpu_pointwise(const dfgpu_pointwise_params*, void* const* tensors, void* scratch, void* stream);
+
+/* ---- CONV_FPROP -------------------------------------------------------------
+   Replaces lower_scalar_conv / lower_vector_conv for the single-node graph
+   (lib/Compiler/ScalarLowering.cpp:92-465) and emit_fprop for DAGs
+   (lib/Compiler/TrainingGraph.cpp:436-542). Logical NCHW dims with arbitrary
+   strides. tensors: {X, W, Y, extra0 or null, extra1 or null}. */
+enum {
+    DFGPU_CONV_AUTO = 0,
+    DFGPU_CONV_DIRECT = 1,      /* any rank-4 conv, one thread per output */
+    DFGPU_CONV_IGEMM_FFMA = 2,  /* f32-accumulate implicit GEMM on CUDA cores */
+    DFGPU_CONV_UMMA_BF16 = 3    /* bf16 NHWC implicit GEMM on tcgen05 */
+};
+typedef struct dfgpu_conv_params {
+    dfgpu_tensor x, w, y;
+    dfgpu_tensor extra[2]; /* ADD operands of the fused epilogue */
+    int64_t pre_pad[2], post_pad[2], stride[2], dilation[2];
+    int32_t reverse_filter; /* math_mode CONVOLUTION */
+    int32_t epilogue_count;
+    dfgpu_epilogue_step epilogue[DFGPU_MAX_EPILOGUE];
+    int32_t kernel;
+    int32_t reserved;
+} dfgpu_conv_params;
+int dfgpu_query_conv_fprop(const dfgpu_conv_params*, dfgpu_plan_info*);
+int dfgpu_conv_fprop(const dfgpu_conv_params*, void* const* tensors, void* scratch, void* stream);
+
+/* ---- MATMUL -----------------------------------------------------------------
+   Replaces emit_matmul (lib/Compiler/FoundationalGraph.cpp:3167-3295); with
+   a_scale/b_scale present it also absorbs the BLOCK_SCALE_DEQUANTIZE nodes
+   that feed A and B (SpecializedGraph.cpp:752-795), reading E4M3 codes and
+   E8M0 scales directly. tensors: {A, B, C, A_scale or null, B_scale or null,
+   extra0 or null, extra1 or null}. */
+enum { DFGPU_MATMUL_AUTO = 0, DFGPU_MATMUL_FFMA = 1, DFGPU_MATMUL_UMMA_BF16 = 2, DFGPU_MATMUL_UMMA_MXF8 = 3 };
+typedef struct dfgpu_matmul_params {
+    dfgpu_tensor a, b, c;
+    dfgpu_tensor a_scale, b_scale;
+    int64_t a_block[2], b_block[2]; /* block sizes over the two trailing axes */
+    dfgpu_tensor extra[2];
+    int32_t epilogue_count;
+    int32_t kernel;
+    dfgpu_epilogue_step epilogue[DFGPU_MAX_EPILOGUE];
+} dfgpu_matmul_params;
+int dfgpu_query_matmul(const dfgpu_matmul_params*, dfgpu_plan_info*);
+int dfgpu_matmul(const dfgpu_matmul_params*, void* const* tensors, void* scratch, void* stream);
+
+/* ---- SDPA forward -----------------------------------------------------------
+   Replaces emit_sdpa_forward with its helpers (lib/Compiler/SequenceGraph.cpp
+   :1839-1889 paged loads, :1988-2091 validity, :2135-2341 scores and softmax
+   row, :2416-2582 outputs). tensors: {Q, K, V, O, Stats, Max, Sum_exp,
+   SEQ_LEN_Q, SEQ_LEN_KV, Page_table_K, Page_table_V} (null when absent). */
+enum { DFGPU_SDPA_AUTO = 0, DFGPU_SDPA_ROWWISE = 1, DFGPU_SDPA_PAGED_DECODE = 2, DFGPU_SDPA_UMMA = 3 };
+typedef struct dfgpu_sdpa_params {
+    dfgpu_tensor q, k, v, o;
+    dfgpu_tensor stats, max, sum_exp;
+    dfgpu_tensor seq_q, seq_kv;
+    dfgpu_tensor page_table_k, page_table_v;
+    float attn_scale;
+    int32_t padding_mask;
+    int32_t has_left_bound;
+    int32_t has_right_bound;
+    int64_t left_bound;
+    int64_t right_bound;
+    int32_t bottom_right;
+    int32_t kernel;
+    int64_t s_kv; /* logical key/value length */
+} dfgpu_sdpa_params;
+int dfgpu_query_sdpa_forward(const dfgpu_sdpa_params*, dfgpu_plan_info*);
+int dfgpu_sdpa_forward(const dfgpu_sdpa_params*, void* const* tensors, void* scratch, void* stream);
+
+/* ---- self-check of the E4M3 encoder ------------------------------------------
+   Encodes `count` consecutive f32 bit patterns starting at `first_bits` with
+   the production encoder and with a literal candidate search, on the device.
+   result (device, 2 x uint64): [0] += number of disagreements, [1] = one
+   disagreeing bit pattern + 1 (0 if none). Used by the exhaustive 2^32 sweep. */
+int dfgpu_selfcheck_e4m3(uint32_t first_bits, uint64_t count, void* result, void* stream);
+/* Same for the E8M0 block-scale rule: amax patterns -> scale code, compared
+   with a search over the 255 powers of two using exact integer log2. */
+int dfgpu_debug_scale_codes(const void* amax_f32, void* codes_u8, int64_t count, void* stream);
+int dfgpu_debug_encode_e4m3(const void* values_f32, void* codes_u8, int64_t count, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

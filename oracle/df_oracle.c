@@ -1,0 +1,687 @@
+/*
+ * CPU oracle for the DeepForge data-parallel op hot path -- TEST INFRASTRUCTURE ONLY.
+ * See df_oracle.h for the role and the parity status of this file.
+ *
+ * Build: gcc -O2 -ffp-contract=off -fno-fast-math -fPIC -shared (see Makefile).
+ * -ffp-contract=off matters: the reference's scalar variant issues a separate
+ * multiply and add, never a fused one.
+ */
+#include "df_oracle.h"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+/* ------------------------------------------------------------------------ */
+/* codecs (reference: lib/Compiler/Numeric.cpp)                              */
+/* ------------------------------------------------------------------------ */
+
+/* Numeric.cpp:111-126 */
+float dfo_decode_e4m3(uint8_t code) {
+    int sign = (code & 0x80u) != 0;
+    unsigned exponent = (code >> 3) & 0x0fu;
+    unsigned mantissa = code & 0x07u;
+    float value;
+    if (exponent == 0) {
+        value = ldexpf((float)mantissa, -9);
+    } else if (exponent == 15 && mantissa == 7) {
+        return NAN;
+    } else {
+        value = ldexpf(1.0f + (float)mantissa / 8.0f, (int)exponent - 7);
+    }
+    return sign ? -value : value;
+}
+
+/* Numeric.cpp:148-153 */
+float dfo_decode_e8m0(uint8_t code) {
+    if (code == 0xffu) return NAN;
+    return ldexpf(1.0f, (int)code - 127);
+}
+
+/* Numeric.cpp:504-632, E4M3 branch. A linear search over all 256 codes:
+   candidates whose low 7 bits are >= 127 (the NaN codes) are skipped; a
+   candidate wins when strictly closer, or equally close with an even code
+   while the current best is odd. Exact zero keeps its sign, |v| > 448
+   saturates to 0x7e|sign, NaN is always 0x7f. */
+uint8_t dfo_encode_e4m3(float value) {
+    uint8_t best = 0;
+    float best_difference = fabsf(value - dfo_decode_e4m3(0));
+    for (unsigned candidate = 0; candidate < 256; ++candidate) {
+        float decoded = dfo_decode_e4m3((uint8_t)candidate);
+        float difference = fabsf(value - decoded);
+        int better = difference < best_difference;
+        int equal = difference == best_difference;
+        int candidate_even = (candidate & 1u) == 0;
+        int best_odd = (best & 1u) != 0;
+        int valid = (candidate % 128u) < 127u;
+        if (valid && (better || (equal && candidate_even && best_odd))) {
+            best = (uint8_t)candidate;
+            best_difference = difference;
+        }
+    }
+    uint32_t bits;
+    memcpy(&bits, &value, 4);
+    int negative = (bits & 0x80000000u) != 0;
+    float absolute = fabsf(value);
+    uint8_t result = best;
+    if (absolute == 0.0f) result = negative ? 0x80 : 0x00;
+    if (absolute > 448.0f) result = (uint8_t)(0x7e | (negative ? 0x80 : 0x00));
+    if (value != value) result = 0x7f;
+    return result;
+}
+
+/* Numeric.cpp:504-591, E8M0 branch: 255 candidates 2^(code-127); v > 2^127
+   -> 0xfe; v <= 0 -> 0x00; NaN -> 0xff. */
+uint8_t dfo_encode_e8m0(float value) {
+    uint8_t best = 0;
+    float best_difference = fabsf(value - dfo_decode_e8m0(0));
+    for (unsigned candidate = 0; candidate < 255; ++candidate) {
+        float difference = fabsf(value - dfo_decode_e8m0((uint8_t)candidate));
+        int better = difference < best_difference;
+        int equal = difference == best_difference;
+        int candidate_even = (candidate & 1u) == 0;
+        int best_odd = (best & 1u) != 0;
+        if (better || (equal && candidate_even && best_odd)) {
+            best = (uint8_t)candidate;
+            best_difference = difference;
+        }
+    }
+    uint8_t result = best;
+    if (value > ldexpf(1.0f, 127)) result = 0xfe;
+    if (value <= 0.0f) result = 0x00;
+    if (value != value) result = 0xff;
+    return result;
+}
+
+/* arith.truncf / arith.extf semantics (Numeric.cpp:766-770): RNE, NaN kept. */
+uint16_t dfo_f32_to_bf16(float value) {
+    uint32_t bits;
+    memcpy(&bits, &value, 4);
+    if ((bits & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((bits >> 16) | 0x0040u);
+    uint32_t rounding = 0x7fffu + ((bits >> 16) & 1u);
+    return (uint16_t)((bits + rounding) >> 16);
+}
+
+float dfo_bf16_to_f32(uint16_t half) {
+    uint32_t bits = (uint32_t)half << 16;
+    float value;
+    memcpy(&value, &bits, 4);
+    return value;
+}
+
+float dfo_f16_to_f32(uint16_t half) {
+    uint32_t sign = (uint32_t)(half & 0x8000u) << 16;
+    uint32_t exponent = (half >> 10) & 0x1fu;
+    uint32_t mantissa = half & 0x3ffu;
+    uint32_t bits;
+    if (exponent == 0) {
+        if (mantissa == 0) {
+            bits = sign;
+        } else {
+            float v = ldexpf((float)mantissa, -24);
+            memcpy(&bits, &v, 4);
+            bits |= sign;
+        }
+    } else if (exponent == 31) {
+        bits = sign | 0x7f800000u | (mantissa << 13);
+    } else {
+        bits = sign | ((exponent + 112u) << 23) | (mantissa << 13);
+    }
+    float value;
+    memcpy(&value, &bits, 4);
+    return value;
+}
+
+uint16_t dfo_f32_to_f16(float value) {
+    uint32_t bits;
+    memcpy(&bits, &value, 4);
+    uint32_t sign = (bits >> 16) & 0x8000u;
+    uint32_t absolute = bits & 0x7fffffffu;
+    if (absolute > 0x7f800000u) return (uint16_t)(sign | 0x7e00u);
+    if (absolute >= 0x477ff000u) { /* >= 65520 rounds to inf */
+        return (uint16_t)(sign | 0x7c00u);
+    }
+    if (absolute < 0x33000001u) return (uint16_t)sign; /* <= 2^-25 -> 0 */
+    int exponent = (int)(absolute >> 23) - 127;
+    uint32_t mantissa = (absolute & 0x7fffffu) | 0x800000u;
+    int shift;
+    uint32_t base;
+    if (exponent < -14) {
+        shift = 13 + (-14 - exponent);
+        base = 0;
+    } else {
+        shift = 13;
+        base = (uint32_t)(exponent + 15) << 10;
+        mantissa &= 0x7fffffu;
+    }
+    uint32_t truncated = mantissa >> shift;
+    uint32_t remainder = mantissa & ((1u << shift) - 1u);
+    uint32_t halfway = 1u << (shift - 1);
+    uint32_t result = base + truncated;
+    if (remainder > halfway || (remainder == halfway && (result & 1u))) result += 1;
+    return (uint16_t)(sign | result);
+}
+
+/* Numeric.cpp:240-308 */
+int64_t dfo_f8_128x4_offset(int64_t leading, int64_t m, int64_t k,
+                            int64_t m_extent, int64_t k_extent) {
+    int64_t m_blocks = m_extent / 128;
+    int64_t k_blocks = k_extent / 4;
+    return (((leading * m_blocks + m / 128) * k_blocks + k / 4) * 512) +
+           (m % 32) * 16 + ((m / 32) % 4) * 4 + k % 4;
+}
+
+void dfo_encode_e4m3_many(const float* values, uint8_t* codes, int64_t count) {
+    for (int64_t i = 0; i < count; ++i) codes[i] = dfo_encode_e4m3(values[i]);
+}
+
+/* ------------------------------------------------------------------------ */
+/* element access                                                            */
+/* ------------------------------------------------------------------------ */
+
+static int64_t element_count(const dfo_tensor* t) {
+    int64_t count = 1;
+    for (int i = 0; i < t->rank; ++i) count *= t->dim[i];
+    return count;
+}
+
+static void unflatten(const dfo_tensor* t, int64_t flat, int64_t* index) {
+    for (int i = t->rank - 1; i >= 0; --i) {
+        index[i] = flat % t->dim[i];
+        flat /= t->dim[i];
+    }
+}
+
+/* F8_128x4 layout selection, Numeric.cpp:38-87: the M axis is the first of the
+   two trailing axes whose stride equals the other's extent (K stride 1). */
+static int reorder_axes(const dfo_tensor* t, int* m_axis, int* k_axis) {
+    int first = t->rank - 2;
+    for (int attempt = 0; attempt < 2; ++attempt) {
+        int ma = first + attempt;
+        int ka = attempt == 0 ? first + 1 : first;
+        int64_t m = t->dim[ma], k = t->dim[ka];
+        if (m <= 0 || k <= 0 || m % 128 != 0 || k % 4 != 0) continue;
+        if (t->stride[ka] != 1 || t->stride[ma] != k) continue;
+        int64_t expected = m * k;
+        int packed = 1;
+        for (int axis = first; axis > 0; --axis) {
+            if (t->stride[axis - 1] != expected) { packed = 0; break; }
+            expected *= t->dim[axis - 1];
+        }
+        if (packed) { *m_axis = ma; *k_axis = ka; return 1; }
+    }
+    return 0;
+}
+
+static int64_t element_offset(const dfo_tensor* t, const int64_t* index) {
+    if (t->reorder == DFO_REORDER_F8_128x4) {
+        int ma = 0, ka = 0;
+        if (reorder_axes(t, &ma, &ka)) {
+            int64_t leading = 0;
+            for (int axis = 0; axis + 2 < t->rank; ++axis)
+                leading = leading * t->dim[axis] + index[axis];
+            return dfo_f8_128x4_offset(leading, index[ma], index[ka], t->dim[ma], t->dim[ka]);
+        }
+    }
+    int64_t offset = 0;
+    for (int i = 0; i < t->rank; ++i) offset += index[i] * t->stride[i];
+    return offset;
+}
+
+/* numeric::load_as_f32 */
+static float load_f32(const dfo_tensor* t, const void* data, int64_t offset) {
+    switch (t->dtype) {
+        case DFO_F32: return ((const float*)data)[offset];
+        case DFO_F16: return dfo_f16_to_f32(((const uint16_t*)data)[offset]);
+        case DFO_BF16: return dfo_bf16_to_f32(((const uint16_t*)data)[offset]);
+        case DFO_E4M3: return dfo_decode_e4m3(((const uint8_t*)data)[offset]);
+        case DFO_E8M0: return dfo_decode_e8m0(((const uint8_t*)data)[offset]);
+        case DFO_I32: return (float)((const int32_t*)data)[offset];
+        default: return NAN;
+    }
+}
+
+/* numeric::store_from_f32 */
+static void store_f32(const dfo_tensor* t, void* data, int64_t offset, float value) {
+    switch (t->dtype) {
+        case DFO_F32: ((float*)data)[offset] = value; break;
+        case DFO_F16: ((uint16_t*)data)[offset] = dfo_f32_to_f16(value); break;
+        case DFO_BF16: ((uint16_t*)data)[offset] = dfo_f32_to_bf16(value); break;
+        case DFO_E4M3: ((uint8_t*)data)[offset] = dfo_encode_e4m3(value); break;
+        case DFO_E8M0: ((uint8_t*)data)[offset] = dfo_encode_e8m0(value); break;
+        default: break;
+    }
+}
+
+/* ------------------------------------------------------------------------ */
+/* block scale (reference: lib/Compiler/SpecializedGraph.cpp)                */
+/* ------------------------------------------------------------------------ */
+
+/* arith.maximumf: NaN if either operand is NaN. */
+static float maximumf_nan(float a, float b) {
+    if (a != a) return a;
+    if (b != b) return b;
+    return a > b ? a : b;
+}
+static float minimumf_nan(float a, float b) {
+    if (a != a) return a;
+    if (b != b) return b;
+    return a < b ? a : b;
+}
+
+/* SpecializedGraph.cpp:810-838 for Y = E4M3, scale = E8M0, then the E8M0
+   encode of the stored value. */
+uint8_t dfo_block_scale_code(float amax) {
+    float desired = amax / 448.0f;
+    float guarded = desired > 0.0f ? desired : 1.0f;
+    if (desired != desired) guarded = desired;
+    guarded = powf(2.0f, ceilf(log2f(guarded)));
+    return dfo_encode_e8m0(guarded);
+}
+
+void dfo_block_scale_code_many(const float* amax, uint8_t* codes, int64_t count) {
+    for (int64_t i = 0; i < count; ++i) codes[i] = dfo_block_scale_code(amax[i]);
+}
+
+/* SpecializedGraph.cpp:840-935: (1) every scale slot <- encode(1.0);
+   (2) per block amax -> scale; (3) Y = encode(x / decode(stored scale)). */
+int dfo_block_scale_quantize(const dfo_tensor* x, const void* x_data,
+                             const dfo_tensor* y, void* y_data,
+                             const dfo_tensor* scale, void* scale_data,
+                             int64_t block, int32_t axis) {
+    if (y->dtype != DFO_E4M3 || scale->dtype != DFO_E8M0) return 20;
+    if (axis < 0) axis = x->rank - 1;
+    if (axis >= x->rank || block <= 0 || x->dim[axis] % block != 0) return 15;
+    int64_t index[DFO_MAX_RANK];
+
+    int64_t scale_count = element_count(scale);
+    for (int64_t flat = 0; flat < scale_count; ++flat) {
+        unflatten(scale, flat, index);
+        store_f32(scale, scale_data, element_offset(scale, index), 1.0f);
+    }
+
+    dfo_tensor logical = *x;
+    logical.dim[axis] /= block;
+    int64_t logical_count = element_count(&logical);
+    for (int64_t flat = 0; flat < logical_count; ++flat) {
+        unflatten(&logical, flat, index);
+        int64_t input_index[DFO_MAX_RANK];
+        memcpy(input_index, index, sizeof(index));
+        float amax = 0.0f;
+        for (int64_t within = 0; within < block; ++within) {
+            input_index[axis] = index[axis] * block + within;
+            float value = load_f32(x, x_data, element_offset(x, input_index));
+            amax = maximumf_nan(amax, fabsf(value));
+        }
+        float desired = amax / 448.0f;
+        float guarded = desired > 0.0f ? desired : 1.0f;
+        if (desired != desired) guarded = desired;
+        guarded = powf(2.0f, ceilf(log2f(guarded)));
+        store_f32(scale, scale_data, element_offset(scale, index), guarded);
+    }
+
+    int64_t y_count = element_count(y);
+    for (int64_t flat = 0; flat < y_count; ++flat) {
+        unflatten(y, flat, index);
+        int64_t scale_index[DFO_MAX_RANK];
+        memcpy(scale_index, index, sizeof(index));
+        scale_index[axis] = index[axis] / block;
+        float input = load_f32(x, x_data, element_offset(x, index));
+        float scale_value = load_f32(scale, scale_data, element_offset(scale, scale_index));
+        store_f32(y, y_data, element_offset(y, index), input / scale_value);
+    }
+    return 0;
+}
+
+/* SpecializedGraph.cpp:752-795 */
+int dfo_block_scale_dequantize(const dfo_tensor* x, const void* x_data,
+                               const dfo_tensor* scale, const void* scale_data,
+                               const dfo_tensor* y, void* y_data,
+                               const int64_t* block, int32_t block_count) {
+    if (block_count > y->rank) return 15;
+    int64_t index[DFO_MAX_RANK];
+    int64_t count = element_count(y);
+    int first = y->rank - block_count;
+    for (int64_t flat = 0; flat < count; ++flat) {
+        unflatten(y, flat, index);
+        int64_t scale_index[DFO_MAX_RANK];
+        memcpy(scale_index, index, sizeof(index));
+        for (int b = 0; b < block_count; ++b) scale_index[first + b] = index[first + b] / block[b];
+        float xv = load_f32(x, x_data, element_offset(x, index));
+        float sv = load_f32(scale, scale_data, element_offset(scale, scale_index));
+        store_f32(y, y_data, element_offset(y, index), xv * sv);
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------------ */
+/* pointwise (reference: lib/Compiler/FoundationalGraph.cpp:2552-2567 for   */
+/* trailing-axis broadcast, :2599 ADD, :2731-2758 RELU_FWD)                  */
+/* ------------------------------------------------------------------------ */
+
+static int64_t broadcast_offset(const dfo_tensor* t, const dfo_tensor* out, const int64_t* index) {
+    int64_t offset = 0;
+    int shift = out->rank - t->rank;
+    for (int i = 0; i < t->rank; ++i) {
+        int64_t position = t->dim[i] == 1 ? 0 : index[i + shift];
+        offset += position * t->stride[i];
+    }
+    return offset;
+}
+
+int dfo_pointwise(int32_t mode, const dfo_tensor* a, const void* a_data,
+                  const dfo_tensor* b, const void* b_data,
+                  const dfo_tensor* out, void* out_data,
+                  float relu_lower, float relu_upper, float relu_slope) {
+    int64_t index[DFO_MAX_RANK];
+    int64_t count = element_count(out);
+    for (int64_t flat = 0; flat < count; ++flat) {
+        unflatten(out, flat, index);
+        float x = load_f32(a, a_data, broadcast_offset(a, out, index));
+        float result;
+        switch (mode) {
+            case DFO_PW_ADD:
+                result = x + load_f32(b, b_data, broadcast_offset(b, out, index));
+                break;
+            case DFO_PW_MUL:
+                result = x * load_f32(b, b_data, broadcast_offset(b, out, index));
+                break;
+            case DFO_PW_SUB:
+                result = x - load_f32(b, b_data, broadcast_offset(b, out, index));
+                break;
+            case DFO_PW_RELU_FWD: {
+                float clipped = minimumf_nan(maximumf_nan(x, relu_lower), relu_upper);
+                float lower_branch = relu_lower + relu_slope * (x - relu_lower);
+                result = x < relu_lower ? lower_branch : clipped;
+                break;
+            }
+            case DFO_PW_IDENTITY:
+                result = x;
+                break;
+            default:
+                return 20;
+        }
+        int64_t offset = 0;
+        for (int i = 0; i < out->rank; ++i) offset += index[i] * out->stride[i];
+        store_f32(out, out_data, offset, result);
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------------ */
+/* convolution                                                               */
+/* ------------------------------------------------------------------------ */
+
+/* lib/Compiler/ScalarLowering.cpp:161-205: loop nest n,oh,ow,k / r,s,c over a
+   zero-padded copy of X (lib/Transforms/BufferizationPipeline.cpp pads into
+   the workspace), separate mulf and addf. */
+int dfo_conv_mvp_scalar(const float* x, const float* w, float* y,
+                        int64_t n, int64_t h, int64_t wd, int64_t c, int64_t k,
+                        int64_t r, int64_t s, int64_t pad_top, int64_t pad_left,
+                        int64_t pad_bottom, int64_t pad_right) {
+    int64_t ph = h + pad_top + pad_bottom, pw = wd + pad_left + pad_right;
+    int64_t oh = ph - r + 1, ow = pw - s + 1;
+    if (oh <= 0 || ow <= 0) return 15;
+    float* padded = (float*)calloc((size_t)(n * ph * pw * c), sizeof(float));
+    if (!padded) return 19;
+    for (int64_t in = 0; in < n; ++in)
+        for (int64_t ih = 0; ih < h; ++ih)
+            memcpy(padded + ((in * ph + ih + pad_top) * pw + pad_left) * c,
+                   x + (in * h + ih) * wd * c, (size_t)(wd * c) * sizeof(float));
+    for (int64_t in = 0; in < n; ++in)
+        for (int64_t io = 0; io < oh; ++io)
+            for (int64_t jo = 0; jo < ow; ++jo)
+                for (int64_t ik = 0; ik < k; ++ik) {
+                    float sum = 0.0f;
+                    for (int64_t ir = 0; ir < r; ++ir)
+                        for (int64_t is = 0; is < s; ++is) {
+                            const float* xp = padded + ((in * ph + io + ir) * pw + jo + is) * c;
+                            const float* wp = w + ((ik * r + ir) * s + is) * c;
+                            for (int64_t ic = 0; ic < c; ++ic) {
+                                float product = xp[ic] * wp[ic];
+                                sum = sum + product;
+                            }
+                        }
+                    y[((in * oh + io) * ow + jo) * k + ik] = sum;
+                }
+    free(padded);
+    return 0;
+}
+
+/* lib/Compiler/ScalarLowering.cpp:275-461: per output element `vf` lane
+   accumulators updated with fused multiply-add over channel vectors, a scalar
+   channel tail accumulated separately (mul then add), and a final horizontal
+   add seeded with the tail sum. The K-unroll only shares X loads and does not
+   change any per-element arithmetic, so it is not modelled. */
+int dfo_conv_mvp_vector(const float* x, const float* w, float* y,
+                        int64_t n, int64_t h, int64_t wd, int64_t c, int64_t k,
+                        int64_t r, int64_t s, int64_t pad_top, int64_t pad_left,
+                        int64_t pad_bottom, int64_t pad_right, int32_t vf) {
+    if (vf != 8 && vf != 16) return 1;
+    int64_t ph = h + pad_top + pad_bottom, pw = wd + pad_left + pad_right;
+    int64_t oh = ph - r + 1, ow = pw - s + 1;
+    if (oh <= 0 || ow <= 0) return 15;
+    float* padded = (float*)calloc((size_t)(n * ph * pw * c), sizeof(float));
+    if (!padded) return 19;
+    for (int64_t in = 0; in < n; ++in)
+        for (int64_t ih = 0; ih < h; ++ih)
+            memcpy(padded + ((in * ph + ih + pad_top) * pw + pad_left) * c,
+                   x + (in * h + ih) * wd * c, (size_t)(wd * c) * sizeof(float));
+    int64_t c_main = (c / vf) * vf;
+    for (int64_t in = 0; in < n; ++in)
+        for (int64_t io = 0; io < oh; ++io)
+            for (int64_t jo = 0; jo < ow; ++jo)
+                for (int64_t ik = 0; ik < k; ++ik) {
+                    float lanes[16];
+                    for (int l = 0; l < vf; ++l) lanes[l] = 0.0f;
+                    float tail = 0.0f;
+                    for (int64_t ir = 0; ir < r; ++ir)
+                        for (int64_t is = 0; is < s; ++is) {
+                            const float* xp = padded + ((in * ph + io + ir) * pw + jo + is) * c;
+                            const float* wp = w + ((ik * r + ir) * s + is) * c;
+                            for (int64_t ic = 0; ic < c_main; ic += vf)
+                                for (int l = 0; l < vf; ++l)
+                                    lanes[l] = fmaf(xp[ic + l], wp[ic + l], lanes[l]);
+                            for (int64_t ic = c_main; ic < c; ++ic) {
+                                float product = xp[ic] * wp[ic];
+                                tail = tail + product;
+                            }
+                        }
+                    float sum = tail;
+                    for (int l = 0; l < vf; ++l) sum = sum + lanes[l];
+                    y[((in * oh + io) * ow + jo) * k + ik] = sum;
+                }
+    free(padded);
+    return 0;
+}
+
+/* lib/Compiler/TrainingGraph.cpp:165-296 (decode) and :380-542 (emit_fprop):
+   flat loop over logical Y; reduction over c (within the group), then filter
+   axes; a tap whose input coordinate falls in the padding contributes +0.0
+   without touching memory; CONVOLUTION math mode reverses the filter. */
+int dfo_conv_generic(const dfo_tensor* x, const void* x_data,
+                     const dfo_tensor* w, const void* w_data,
+                     const dfo_tensor* y, void* y_data,
+                     const dfo_conv_attrs* attrs) {
+    int rank = x->rank;
+    int spatial = rank - 2;
+    if (rank < 3 || rank > 5 || w->rank != rank || y->rank != rank || spatial != attrs->spatial_rank) return 15;
+    if (w->dim[1] <= 0 || x->dim[1] % w->dim[1] != 0) return 15;
+    int64_t groups = x->dim[1] / w->dim[1];
+    if (groups <= 0 || y->dim[1] % groups != 0) return 15;
+    int64_t k_per_group = y->dim[1] / groups;
+    int64_t c_per_group = w->dim[1];
+    int64_t taps = 1;
+    for (int a = 0; a < spatial; ++a) taps *= w->dim[a + 2];
+    int64_t count = element_count(y);
+    int64_t yi[DFO_MAX_RANK], xi[DFO_MAX_RANK], wi[DFO_MAX_RANK];
+    for (int64_t flat = 0; flat < count; ++flat) {
+        unflatten(y, flat, yi);
+        int64_t group = yi[1] / k_per_group;
+        float sum = 0.0f;
+        xi[0] = yi[0];
+        wi[0] = yi[1];
+        for (int64_t ic = 0; ic < c_per_group; ++ic) {
+            xi[1] = group * c_per_group + ic;
+            wi[1] = ic;
+            for (int64_t tap = 0; tap < taps; ++tap) {
+                int64_t rest = tap;
+                int valid = 1;
+                for (int a = spatial - 1; a >= 0; --a) {
+                    int64_t f = rest % w->dim[a + 2];
+                    rest /= w->dim[a + 2];
+                    int64_t coordinate = yi[a + 2] * attrs->stride[a] + f * attrs->dilation[a] - attrs->pre_pad[a];
+                    if (coordinate < 0 || coordinate >= x->dim[a + 2]) valid = 0;
+                    xi[a + 2] = coordinate;
+                    wi[a + 2] = attrs->reverse_filter ? w->dim[a + 2] - 1 - f : f;
+                }
+                float product = 0.0f;
+                if (valid) {
+                    int64_t xo = 0, wo = 0;
+                    for (int i = 0; i < rank; ++i) { xo += xi[i] * x->stride[i]; wo += wi[i] * w->stride[i]; }
+                    product = load_f32(x, x_data, xo) * load_f32(w, w_data, wo);
+                }
+                sum = sum + product;
+            }
+        }
+        int64_t yo = 0;
+        for (int i = 0; i < rank; ++i) yo += yi[i] * y->stride[i];
+        store_f32(y, y_data, yo, sum);
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------------ */
+/* matmul (reference: lib/Compiler/FoundationalGraph.cpp:865-928, 3167-3295) */
+/* ------------------------------------------------------------------------ */
+int dfo_matmul(const dfo_tensor* a, const void* a_data,
+               const dfo_tensor* b, const void* b_data,
+               const dfo_tensor* c, void* c_data,
+               int64_t row_begin, int64_t row_end) {
+    int rank = c->rank;
+    if (rank < 2 || a->rank != rank || b->rank != rank) return 15;
+    int64_t m = c->dim[rank - 2], n = c->dim[rank - 1], kk = a->dim[rank - 1];
+    if (row_begin < 0) row_begin = 0;
+    if (row_end < 0 || row_end > m) row_end = m;
+    int64_t batches = 1;
+    for (int i = 0; i < rank - 2; ++i) batches *= c->dim[i];
+    int64_t bi[DFO_MAX_RANK];
+    for (int64_t batch = 0; batch < batches; ++batch) {
+        int64_t rest = batch;
+        for (int i = rank - 3; i >= 0; --i) { bi[i] = rest % c->dim[i]; rest /= c->dim[i]; }
+        int64_t a_base = 0, b_base = 0, c_base = 0;
+        for (int i = 0; i < rank - 2; ++i) {
+            a_base += (a->dim[i] == 1 ? 0 : bi[i]) * a->stride[i];
+            b_base += (b->dim[i] == 1 ? 0 : bi[i]) * b->stride[i];
+            c_base += bi[i] * c->stride[i];
+        }
+        for (int64_t im = row_begin; im < row_end; ++im)
+            for (int64_t in = 0; in < n; ++in) {
+                float sum = 0.0f;
+                for (int64_t ik = 0; ik < kk; ++ik) {
+                    float av = load_f32(a, a_data, a_base + im * a->stride[rank - 2] + ik * a->stride[rank - 1]);
+                    float bv = load_f32(b, b_data, b_base + ik * b->stride[rank - 2] + in * b->stride[rank - 1]);
+                    float product = av * bv;
+                    sum = sum + product;
+                }
+                store_f32(c, c_data, c_base + im * c->stride[rank - 2] + in * c->stride[rank - 1], sum);
+            }
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------------ */
+/* SDPA forward (reference: lib/Compiler/SequenceGraph.cpp)                  */
+/* ------------------------------------------------------------------------ */
+
+static int64_t offset4(const dfo_tensor* t, int64_t i0, int64_t i1, int64_t i2, int64_t i3) {
+    return i0 * t->stride[0] + i1 * t->stride[1] + i2 * t->stride[2] + i3 * t->stride[3];
+}
+
+/* SequenceGraph.cpp:1839-1889: slot = kv / block, page = table[b,0,slot,0];
+   an id outside [0, num_blocks) reads as 0.0 and never touches memory. */
+static float load_kv(const dfo_tensor* t, const void* data, const dfo_tensor* table,
+                     const int32_t* table_data, int64_t b, int64_t head, int64_t kv, int64_t d) {
+    if (table->rank == 0) return load_f32(t, data, offset4(t, b, head, kv, d));
+    int64_t block = t->dim[2];
+    int64_t slot = kv / block, within = kv % block;
+    int64_t page = table_data[offset4(table, b, 0, slot, 0)];
+    if (page < 0 || page >= t->dim[0]) return 0.0f;
+    return load_f32(t, data, offset4(t, page, head, within, d));
+}
+
+/* SequenceGraph.cpp:1988-2091 (validity), :2135-2195 (score = scale * dot),
+   :2248-2314 (row max and sum of exp over valid scores), :2316-2341
+   (probability), :2416-2582 (outputs; Stats = max + ln(sum)). */
+int dfo_sdpa_forward(const dfo_sdpa_params* p, void* const* data,
+                     int64_t bh_begin, int64_t bh_end, int64_t q_step) {
+    const dfo_tensor *q = &p->q, *k = &p->k, *v = &p->v, *o = &p->o;
+    if (q->rank != 4 || k->rank != 4 || v->rank != 4 || o->rank != 4) return 15;
+    int64_t batch = q->dim[0], hq = q->dim[1], sq = q->dim[2], dqk = q->dim[3];
+    int64_t hk = k->dim[1], hv = v->dim[1], dv = v->dim[3];
+    int64_t skv = p->s_kv;
+    if (hk <= 0 || hv <= 0 || hq % hk != 0 || hq % hv != 0) return 15;
+    const int32_t* seq_q = (const int32_t*)data[7];
+    const int32_t* seq_kv = (const int32_t*)data[8];
+    const int32_t* table_k = (const int32_t*)data[9];
+    const int32_t* table_v = (const int32_t*)data[10];
+    if (q_step <= 0) q_step = 1;
+    float* scores = (float*)malloc((size_t)(skv > 0 ? skv : 1) * sizeof(float));
+    unsigned char* valid = (unsigned char*)malloc((size_t)(skv > 0 ? skv : 1));
+    float* out_row = (float*)malloc((size_t)dv * sizeof(float));
+    if (!scores || !valid || !out_row) return 19;
+    for (int64_t bh = bh_begin; bh < bh_end && bh < batch * hq; ++bh) {
+        int64_t ib = bh / hq, ih = bh % hq;
+        int64_t kh = ih / (hq / hk), vh = ih / (hq / hv);
+        int64_t len_q = 0, len_kv = 0;
+        if (p->padding_mask) {
+            len_q = seq_q[ib * p->seq_q.stride[0]];
+            len_kv = seq_kv[ib * p->seq_kv.stride[0]];
+        }
+        int64_t shift = 0;
+        if (p->bottom_right) shift = p->padding_mask ? len_kv - len_q : skv - sq;
+        for (int64_t iq = 0; iq < sq; iq += q_step) {
+            float maximum = -INFINITY;
+            for (int64_t ikv = 0; ikv < skv; ++ikv) {
+                int ok = 1;
+                if (p->padding_mask && !(iq < len_q && ikv < len_kv && iq >= 0 && ikv >= 0)) ok = 0;
+                int64_t difference = ikv - iq;
+                if (p->has_right_bound && !(difference <= shift + p->right_bound)) ok = 0;
+                if (p->has_left_bound && !(difference > shift - p->left_bound)) ok = 0;
+                valid[ikv] = (unsigned char)ok;
+                if (!ok) { scores[ikv] = -INFINITY; continue; }
+                float dot = 0.0f;
+                for (int64_t d = 0; d < dqk; ++d) {
+                    float qv = load_f32(q, data[0], offset4(q, ib, ih, iq, d));
+                    float kv = load_kv(k, data[1], &p->page_table_k, table_k, ib, kh, ikv, d);
+                    float product = qv * kv;
+                    dot = dot + product;
+                }
+                scores[ikv] = p->attn_scale * dot;
+                if (scores[ikv] > maximum) maximum = scores[ikv];
+                if (scores[ikv] != scores[ikv]) maximum = scores[ikv];
+            }
+            float sum = 0.0f;
+            for (int64_t ikv = 0; ikv < skv; ++ikv)
+                if (valid[ikv]) sum = sum + expf(scores[ikv] - maximum);
+            for (int64_t d = 0; d < dv; ++d) out_row[d] = 0.0f;
+            for (int64_t ikv = 0; ikv < skv; ++ikv) {
+                if (!valid[ikv] || !(sum > 0.0f)) continue;
+                float probability = expf(scores[ikv] - maximum) / sum;
+                for (int64_t d = 0; d < dv; ++d) {
+                    float vv = load_kv(v, data[2], &p->page_table_v, table_v, ib, vh, ikv, d);
+                    float product = probability * vv;
+                    out_row[d] = out_row[d] + product;
+                }
+            }
+            for (int64_t d = 0; d < dv; ++d) store_f32(o, data[3], offset4(o, ib, ih, iq, d), out_row[d]);
+            if (p->stats.rank) store_f32(&p->stats, data[4], offset4(&p->stats, ib, ih, iq, 0), maximum + logf(sum));
+            if (p->max.rank) store_f32(&p->max, data[5], offset4(&p->max, ib, ih, iq, 0), maximum);
+            if (p->sum_exp.rank) store_f32(&p->sum_exp, data[6], offset4(&p->sum_exp, ib, ih, iq, 0), sum);
+        }
+    }
+    free(scores);
+    free(valid);
+    free(out_row);
+    return 0;
+}

@@ -1,0 +1,141 @@
+/*
+ * CPU oracle for the DeepForge data-parallel op hot path.
+ *
+ * TEST INFRASTRUCTURE ONLY. This is a plain-C restatement of the reference's
+ * arithmetic (file:line cited per function in df_oracle.c). It is the checker
+ * the GPU kernels are compared against and the timed "port" CPU baseline; it
+ * is never linked into, imported by or called from the product libraries.
+ *
+ * Parity status: pinned. Every known-answer vector the reference's own tests
+ * hold for this path is replayed against these functions by the CPU test
+ * suite (block-scale codes/scales, F8_128x4 offsets, conv fixtures, conv+ReLU
+ * exact case, matmul+bias, SDPA feature case, paged tables, invalid pages).
+ * bf16 graphs have no reference execution at all (the reference accepts only
+ * FLOAT tensors outside the block-scale tags): for them the oracle is the f32
+ * restatement on bf16-representable inputs, i.e. "parity unpinned" there.
+ */
+#ifndef DF_ORACLE_H
+#define DF_ORACLE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DFO_MAX_RANK 8
+
+enum {
+    DFO_F32 = 0,
+    DFO_F16 = 1,
+    DFO_BF16 = 2,
+    DFO_E4M3 = 3,
+    DFO_E8M0 = 4,
+    DFO_I32 = 5
+};
+
+enum { DFO_REORDER_NONE = 0, DFO_REORDER_F8_128x4 = 1 };
+
+/* Same field layout as dfgpu_tensor so one ctypes struct serves both. */
+typedef struct dfo_tensor {
+    int32_t dtype;
+    int32_t rank;
+    int32_t reorder;
+    int32_t reserved;
+    int64_t dim[DFO_MAX_RANK];
+    int64_t stride[DFO_MAX_RANK]; /* in elements */
+} dfo_tensor;
+
+/* codecs */
+float dfo_decode_e4m3(uint8_t code);
+float dfo_decode_e8m0(uint8_t code);
+uint8_t dfo_encode_e4m3(float value);
+uint8_t dfo_encode_e8m0(float value);
+uint16_t dfo_f32_to_bf16(float value);
+float dfo_bf16_to_f32(uint16_t bits);
+uint16_t dfo_f32_to_f16(float value);
+float dfo_f16_to_f32(uint16_t bits);
+int64_t dfo_f8_128x4_offset(int64_t leading, int64_t m, int64_t k,
+                            int64_t m_extent, int64_t k_extent);
+uint8_t dfo_block_scale_code(float amax);
+/* bulk helpers used by exhaustive sweeps */
+void dfo_encode_e4m3_many(const float* values, uint8_t* codes, int64_t count);
+void dfo_block_scale_code_many(const float* amax, uint8_t* codes, int64_t count);
+
+/* block scale */
+int dfo_block_scale_quantize(const dfo_tensor* x, const void* x_data,
+                             const dfo_tensor* y, void* y_data,
+                             const dfo_tensor* scale, void* scale_data,
+                             int64_t block, int32_t axis);
+int dfo_block_scale_dequantize(const dfo_tensor* x, const void* x_data,
+                               const dfo_tensor* scale, const void* scale_data,
+                               const dfo_tensor* y, void* y_data,
+                               const int64_t* block, int32_t block_count);
+
+/* pointwise */
+enum { DFO_PW_ADD = 0, DFO_PW_RELU_FWD = 1, DFO_PW_IDENTITY = 2, DFO_PW_MUL = 3, DFO_PW_SUB = 4 };
+int dfo_pointwise(int32_t mode, const dfo_tensor* a, const void* a_data,
+                  const dfo_tensor* b, const void* b_data,
+                  const dfo_tensor* out, void* out_data,
+                  float relu_lower, float relu_upper, float relu_slope);
+
+/* convolution */
+typedef struct dfo_conv_attrs {
+    int32_t spatial_rank;
+    int32_t reverse_filter;
+    int64_t pre_pad[3];
+    int64_t post_pad[3];
+    int64_t stride[3];
+    int64_t dilation[3];
+} dfo_conv_attrs;
+/* single-node "MVP" path: NHWC/KRSC physical, materialised zero padding,
+   reduction order r,s,c with separate multiply and add. */
+int dfo_conv_mvp_scalar(const float* x, const float* w, float* y,
+                        int64_t n, int64_t h, int64_t wd, int64_t c, int64_t k,
+                        int64_t r, int64_t s, int64_t pad_top, int64_t pad_left,
+                        int64_t pad_bottom, int64_t pad_right);
+/* the AVX-style schedule of the MVP path: FMA over `vf` channel lanes, scalar
+   channel tail, horizontal add seeded with the tail sum. */
+int dfo_conv_mvp_vector(const float* x, const float* w, float* y,
+                        int64_t n, int64_t h, int64_t wd, int64_t c, int64_t k,
+                        int64_t r, int64_t s, int64_t pad_top, int64_t pad_left,
+                        int64_t pad_bottom, int64_t pad_right, int32_t vf);
+/* generic DAG path: logical NC[D]HW dims with arbitrary strides, groups,
+   stride, dilation; padded taps are skipped; order c then filter axes. */
+int dfo_conv_generic(const dfo_tensor* x, const void* x_data,
+                     const dfo_tensor* w, const void* w_data,
+                     const dfo_tensor* y, void* y_data,
+                     const dfo_conv_attrs* attrs);
+
+/* matmul; row_begin/row_end restrict the M range computed (sampling) */
+int dfo_matmul(const dfo_tensor* a, const void* a_data,
+               const dfo_tensor* b, const void* b_data,
+               const dfo_tensor* c, void* c_data,
+               int64_t row_begin, int64_t row_end);
+
+/* SDPA forward */
+typedef struct dfo_sdpa_params {
+    dfo_tensor q, k, v, o;
+    dfo_tensor stats, max, sum_exp;         /* rank 0 => absent */
+    dfo_tensor seq_q, seq_kv;               /* rank 0 => absent */
+    dfo_tensor page_table_k, page_table_v;  /* rank 0 => absent */
+    float attn_scale;
+    int32_t padding_mask;
+    int32_t has_left_bound;
+    int32_t has_right_bound;
+    int64_t left_bound;
+    int64_t right_bound;
+    int32_t bottom_right;
+    int32_t reserved;
+    int64_t s_kv; /* logical kv length */
+} dfo_sdpa_params;
+/* pointer order: Q,K,V,O,Stats,Max,Sum_exp,SEQ_LEN_Q,SEQ_LEN_KV,Page_table_K,Page_table_V.
+   Only (b,h) pairs with flat index bh_begin <= b*Hq+h < bh_end and rows with
+   q % q_step == 0 are computed; others are left untouched. */
+int dfo_sdpa_forward(const dfo_sdpa_params* p, void* const* data,
+                     int64_t bh_begin, int64_t bh_end, int64_t q_step);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
