@@ -1,0 +1,302 @@
+"""Bit-exact parity of the block-scale kernels with the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+import oracle
+from deepforge_b200 import dfgpu, synthetic
+from deepforge_b200.dfgpu import BF16, E4M3, E8M0, F16, F32, REORDER_F8_128x4, tensor
+
+pytestmark = pytest.mark.gpu
+
+NP_OF = {F32: np.float32, F16: np.float16, BF16: np.uint16}
+
+
+def _make_x(dtype, shape, seed, special=False):
+    count = int(np.prod(shape))
+    values = synthetic.normal(seed, 1, count)
+    mask = synthetic.outlier_mask(seed, 1, count)
+    values = np.where(mask, values * 64.0, values).astype(np.float32)
+    if special:
+        values[::97] = 0.0
+        values[5::101] = -0.0
+        values[7::211] = -1e-7          # negative that rounds to zero
+        values[11::257] = np.float32(448.0)
+        values[13::509] = np.inf
+        values[17::1021] = np.nan
+        values[19::127] = 1e-30
+        values[23::131] = -3.0e38
+    if dtype == F32:
+        return values.reshape(shape)
+    if dtype == F16:
+        with np.errstate(over="ignore"):
+            return values.astype(np.float16).reshape(shape)
+    return synthetic.to_bf16_bits(values).reshape(shape)
+
+
+def _quantize_both(dtype, shape, block, axis, kernel, scale_dims=None, scale_strides=None, reorder=0, seed=3, special=False,
+                   x_strides=None):
+    import gpu_util as g
+    x = _make_x(dtype, shape, seed, special)
+    logical = list(shape)
+    logical[axis] //= block
+    scale_dims = scale_dims or logical
+    xd = tensor(dtype, shape, x_strides)
+    yd = tensor(E4M3, shape)
+    sd = tensor(E8M0, scale_dims, scale_strides, reorder)
+    scale_bytes = int(np.prod(scale_dims))
+    y_ref = np.zeros(int(np.prod(shape)), dtype=np.uint8)
+    s_ref = np.full(scale_bytes, 0xAA, dtype=np.uint8)
+    oracle.block_scale_quantize(xd, x, yd, y_ref, sd, s_ref, block, axis)
+
+    p = dfgpu.BsqParams()
+    p.x, p.y, p.scale, p.block_size, p.axis, p.kernel = xd, yd, sd, block, axis, kernel
+    info = dfgpu.query("block_scale_quantize", p)
+    dx = g.to_device(x)
+    dy = g.device_zeros(y_ref.size, 0x55)
+    ds = g.device_zeros(scale_bytes, 0xAA)
+    dfgpu.block_scale_quantize(p, g.ptr(dx), g.ptr(dy), g.ptr(ds))
+    y = g.to_host(dy, np.uint8)
+    s = g.to_host(ds, np.uint8)
+    return info, x, y, s, y_ref, s_ref
+
+
+def test_known_answers_through_the_abi():
+    import gpu_util as g
+    p = dfgpu.BsqParams()
+    p.x, p.y, p.scale = tensor(F32, [1, 4]), tensor(E4M3, [1, 4]), tensor(E8M0, [1, 2])
+    p.block_size, p.axis = 2, 1
+    for values, scales, codes in (
+        ([1.0, 2.0, -4.0, 8.0], [120, 122], [0x70, 0x78, 0xf0, 0x78]),
+        ([np.inf, 0.0, np.nan, 0.0], [0xfe, 0xff], [0x7e, 0x00, 0x7f, 0x7f]),
+    ):
+        dx = g.to_device(np.array(values, dtype=np.float32))
+        dy, ds = g.device_zeros(4), g.device_zeros(2)
+        dfgpu.block_scale_quantize(p, g.ptr(dx), g.ptr(dy), g.ptr(ds))
+        assert g.to_host(ds, np.uint8).tolist() == scales
+        assert g.to_host(dy, np.uint8).tolist() == codes
+    q = dfgpu.BsdParams()
+    q.x, q.scale, q.y = tensor(E4M3, [1, 4]), tensor(E8M0, [1, 2]), tensor(F32, [1, 4])
+    q.block[0], q.block_count = 2, 1
+    dx = g.to_device(np.array([0x38, 0x40, 0xb8, 0x30], dtype=np.uint8))
+    ds = g.to_device(np.array([127, 128], dtype=np.uint8))
+    dy = g.device_zeros(16)
+    dfgpu.block_scale_dequantize(q, g.ptr(dx), g.ptr(ds), g.ptr(dy))
+    assert g.to_host(dy, np.float32).tolist() == [1.0, 2.0, -2.0, 1.0]
+
+
+@pytest.mark.parametrize("dtype", [F32, F16, BF16])
+@pytest.mark.parametrize("kernel", [dfgpu.BSQ_GENERIC, dfgpu.BSQ_ROW32])
+def test_row_blocks_match_oracle(dtype, kernel):
+    info, x, y, s, y_ref, s_ref = _quantize_both(dtype, [96, 256], 32, 1, kernel, special=True)
+    assert info.kernel == kernel
+    assert np.array_equal(s, s_ref)
+    assert np.array_equal(y, y_ref)
+
+
+@pytest.mark.parametrize("dtype", [F32, F16, BF16])
+@pytest.mark.parametrize("kernel", [dfgpu.BSQ_GENERIC, dfgpu.BSQ_COL32])
+def test_column_blocks_match_oracle(dtype, kernel):
+    info, x, y, s, y_ref, s_ref = _quantize_both(dtype, [3, 128, 72], 32, 1, kernel, special=True, seed=9)
+    assert info.kernel == kernel
+    assert np.array_equal(s, s_ref)
+    assert np.array_equal(y, y_ref)
+
+
+@pytest.mark.parametrize("block,axis,shape", [(2, 1, [5, 6]), (16, 0, [32, 7]), (64, 2, [2, 3, 128]), (8, 1, [4, 24, 5])])
+def test_generic_blocks_match_oracle(block, axis, shape):
+    info, x, y, s, y_ref, s_ref = _quantize_both(F32, shape, block, axis, dfgpu.BSQ_AUTO, special=True, seed=21)
+    assert np.array_equal(s, s_ref)
+    assert np.array_equal(y, y_ref)
+
+
+def test_strided_input_uses_generic_kernel():
+    # X is a [64, 64] window of a [64, 80] buffer
+    info, x, y, s, y_ref, s_ref = _quantize_both(BF16, [64, 64], 32, 1, dfgpu.BSQ_AUTO, seed=4)
+    assert info.kernel == dfgpu.BSQ_ROW32
+    import gpu_util as g
+    full = _make_x(BF16, [64, 80], 4)
+    xd = tensor(BF16, [64, 64], [80, 1])
+    yd, sd = tensor(E4M3, [64, 64]), tensor(E8M0, [64, 2])
+    y_ref = np.zeros(64 * 64, dtype=np.uint8)
+    s_ref = np.zeros(128, dtype=np.uint8)
+    oracle.block_scale_quantize(xd, full, yd, y_ref, sd, s_ref, 32, 1)
+    p = dfgpu.BsqParams()
+    p.x, p.y, p.scale, p.block_size, p.axis = xd, yd, sd, 32, 1
+    assert dfgpu.query("block_scale_quantize", p).kernel == dfgpu.BSQ_GENERIC
+    dx, dy, ds = g.to_device(full), g.device_zeros(64 * 64), g.device_zeros(128)
+    dfgpu.block_scale_quantize(p, g.ptr(dx), g.ptr(dy), g.ptr(ds))
+    assert np.array_equal(g.to_host(dy, np.uint8), y_ref) and np.array_equal(g.to_host(ds, np.uint8), s_ref)
+
+
+@pytest.mark.parametrize("kernel", [dfgpu.BSQ_GENERIC, dfgpu.BSQ_ROW32])
+def test_reordered_scale_with_padding_slots(kernel):
+    # the reference's 128x32 case: logical scale [128,1] inside an F8_128x4 [128,4] tensor
+    info, x, y, s, y_ref, s_ref = _quantize_both(F32, [128, 32], 32, 1, kernel, scale_dims=[128, 4], scale_strides=[4, 1],
+                                                 reorder=REORDER_F8_128x4, seed=8)
+    assert info.launches == 2  # fill + quantize
+    assert np.array_equal(s, s_ref) and np.array_equal(y, y_ref)
+    assert np.count_nonzero(s == 0x7f) >= 128 * 3
+
+
+@pytest.mark.parametrize("kernel", [dfgpu.BSQ_GENERIC, dfgpu.BSQ_ROW32])
+def test_reordered_scale_full_grid(kernel):
+    info, x, y, s, y_ref, s_ref = _quantize_both(BF16, [256, 256], 32, 1, kernel, scale_dims=[256, 8], scale_strides=[8, 1],
+                                                 reorder=REORDER_F8_128x4, seed=12, special=True)
+    assert np.array_equal(s, s_ref) and np.array_equal(y, y_ref)
+
+
+@pytest.mark.parametrize("kernel", [dfgpu.BSQ_GENERIC, dfgpu.BSQ_COL32])
+def test_transposed_reordered_scale(kernel):
+    # B-style operand [K, N], blocks along K, scale [K/32, N] stored with N as the 128-row axis
+    info, x, y, s, y_ref, s_ref = _quantize_both(BF16, [128, 256], 32, 0, kernel, scale_dims=[4, 256], scale_strides=[1, 4],
+                                                 reorder=REORDER_F8_128x4, seed=14, special=True)
+    assert np.array_equal(s, s_ref) and np.array_equal(y, y_ref)
+
+
+def test_reference_reordered_known_answer():
+    import gpu_util as g
+    x = np.full((128, 32), 448.0, dtype=np.float32)
+    x[32] = 224.0
+    x[127] = 112.0
+    p = dfgpu.BsqParams()
+    p.x, p.y = tensor(F32, [128, 32]), tensor(E4M3, [128, 32])
+    p.scale = tensor(E8M0, [128, 4], [4, 1], REORDER_F8_128x4)
+    p.block_size, p.axis = 32, 1
+    dx, dy, ds = g.to_device(x), g.device_zeros(128 * 32), g.device_zeros(512)
+    dfgpu.block_scale_quantize(p, g.ptr(dx), g.ptr(dy), g.ptr(ds))
+    y, s = g.to_host(dy, np.uint8), g.to_host(ds, np.uint8)
+    assert np.all(y == 0x7e)
+    off = oracle.lib().dfo_f8_128x4_offset
+    for m in range(128):
+        for k in range(4):
+            expected = 126 if (k == 0 and m == 32) else 125 if (k == 0 and m == 127) else 127
+            assert s[off(0, m, k, 128, 4)] == expected
+
+
+def test_exhaustive_e4m3_encoder_sweep():
+    """All 2^32 f32 bit patterns: the production encoder equals the literal candidate search."""
+    import torch
+    result = torch.zeros(2, dtype=torch.int64, device="cuda")
+    for chunk in range(16):
+        dfgpu.selfcheck_e4m3(chunk << 28, 1 << 28, result.data_ptr())
+    torch.cuda.synchronize()
+    bad, witness = result.cpu().tolist()
+    assert bad == 0, f"{bad} disagreements, e.g. bits {witness - 1:#010x}"
+
+
+def test_encoder_matches_oracle_on_boundaries_and_samples():
+    import gpu_util as g
+    codes = np.arange(256, dtype=np.uint8)
+    lib = oracle.lib()
+    decoded = np.array([lib.dfo_decode_e4m3(int(c)) for c in codes if (c & 0x7f) != 0x7f], dtype=np.float32)
+    mids = ((decoded[:-1].astype(np.float64) + decoded[1:].astype(np.float64)) / 2).astype(np.float32)
+    around = np.concatenate([decoded, mids, np.nextafter(mids, np.float32(np.inf)), np.nextafter(mids, np.float32(-np.inf)),
+                             np.nextafter(decoded, np.float32(np.inf)), np.nextafter(decoded, np.float32(-np.inf))])
+    bits = synthetic.raw_u64(77, 1, 1 << 20).astype(np.uint32)
+    samples = np.concatenate([around, bits.view(np.float32),
+                              np.array([0.0, -0.0, np.inf, -np.inf, np.nan, -np.nan, 1e-45, -1e-45, 2.0 ** -10, -(2.0 ** -10)], dtype=np.float32)])
+    expected = oracle.encode_e4m3_many(samples)
+    dv, dc = g.to_device(samples), g.device_zeros(samples.size)
+    dfgpu.debug_encode_e4m3(g.ptr(dv), g.ptr(dc), samples.size)
+    assert np.array_equal(g.to_host(dc, np.uint8), expected)
+
+
+def test_scale_rule_for_every_16bit_amax():
+    """All 65,536 bf16 and f16 patterns as block amax go through the E8M0 rule bit-exactly."""
+    import gpu_util as g
+    patterns = np.arange(1 << 16, dtype=np.uint16)
+    bf = synthetic.bf16_bits_to_f32(patterns)
+    with np.errstate(invalid="ignore"):
+        half = patterns.view(np.float16).astype(np.float32)
+    amax = np.abs(np.concatenate([bf, half])).astype(np.float32)
+    expected = oracle.block_scale_code_many(amax)
+    da, dc = g.to_device(amax), g.device_zeros(amax.size)
+    dfgpu.debug_scale_codes(g.ptr(da), g.ptr(dc), amax.size)
+    assert np.array_equal(g.to_host(dc, np.uint8), expected)
+
+
+@pytest.mark.parametrize("ydtype", [F32, F16, BF16])
+@pytest.mark.parametrize("blocks,shape,kernel", [([1, 32], [64, 128], dfgpu.BSD_PACKED), ([32, 1], [64, 128], dfgpu.BSD_PACKED),
+                                                 ([1, 32], [64, 128], dfgpu.BSD_GENERIC), ([2], [3, 4], dfgpu.BSD_GENERIC),
+                                                 ([4, 2], [2, 8, 6], dfgpu.BSD_GENERIC)])
+def test_dequantize_matches_oracle(ydtype, blocks, shape, kernel):
+    import gpu_util as g
+    count = int(np.prod(shape))
+    codes = (synthetic.raw_u64(5, 2, count) & np.uint64(0xff)).astype(np.uint8)
+    scale_dims = list(shape)
+    for i, b in enumerate(blocks):
+        axis = len(shape) - len(blocks) + i
+        scale_dims[axis] = shape[axis] // b
+    scount = int(np.prod(scale_dims))
+    scales = (100 + synthetic.raw_u64(5, 3, scount) % np.uint64(60)).astype(np.uint8)
+    scales[::17] = 0xff
+    scales[1::19] = 0
+    scales[2::23] = 254
+    xd, sd, yd = tensor(E4M3, shape), tensor(E8M0, scale_dims), tensor(ydtype, shape)
+    width = dfgpu.DTYPE_BYTES[ydtype]
+    ref = np.zeros(count * width, dtype=np.uint8)
+    oracle.block_scale_dequantize(xd, codes, sd, scales, yd, ref, blocks)
+    p = dfgpu.BsdParams()
+    p.x, p.scale, p.y = xd, sd, yd
+    for i, b in enumerate(blocks):
+        p.block[i] = b
+    p.block_count, p.kernel = len(blocks), kernel
+    assert dfgpu.query("block_scale_dequantize", p).kernel == kernel
+    dx, ds, dy = g.to_device(codes), g.to_device(scales), g.device_zeros(count * width)
+    dfgpu.block_scale_dequantize(p, g.ptr(dx), g.ptr(ds), g.ptr(dy))
+    out = g.to_host(dy, np.uint8)
+    if ydtype == F32:
+        a, b = out.view(np.uint32), ref.view(np.uint32)
+    else:
+        a, b = out.view(np.uint16), ref.view(np.uint16)
+    nan_a = np.isnan(out.view(NP_OF[ydtype])) if ydtype != BF16 else np.isnan(synthetic.bf16_bits_to_f32(a))
+    nan_b = np.isnan(ref.view(NP_OF[ydtype])) if ydtype != BF16 else np.isnan(synthetic.bf16_bits_to_f32(b))
+    assert np.array_equal(nan_a, nan_b)
+    assert np.array_equal(a[~nan_a], b[~nan_b])
+
+
+def test_full_size_quantize_properties():
+    """The benchmark's 4096x4096 bf16 operands: A-style and B-style. Checked against the
+    oracle on a slab, and through size-independent properties on the whole matrix:
+    every |x / scale| <= 448 unless saturated, scale code == rule(amax), decode(code)*scale
+    within half an E4M3 step of x."""
+    import gpu_util as g
+    n = 4096
+    seed = 20261125 + 3
+    values = synthetic.normal(seed, 1, n * n)
+    values = np.where(synthetic.outlier_mask(seed, 1, n * n), values * 64.0, values).astype(np.float32)
+    bits = synthetic.to_bf16_bits(values).reshape(n, n)
+    x32 = synthetic.bf16_bits_to_f32(bits)
+    dx = g.to_device(bits)
+    for axis, kernel in ((1, dfgpu.BSQ_ROW32), (0, dfgpu.BSQ_COL32)):
+        sdims = [n, n // 32] if axis == 1 else [n // 32, n]
+        p = dfgpu.BsqParams()
+        p.x, p.y, p.scale, p.block_size, p.axis = tensor(BF16, [n, n]), tensor(E4M3, [n, n]), tensor(E8M0, sdims), 32, axis
+        assert dfgpu.query("block_scale_quantize", p).kernel == kernel
+        dy, ds = g.device_zeros(n * n), g.device_zeros(n * n // 32)
+        dfgpu.block_scale_quantize(p, g.ptr(dx), g.ptr(dy), g.ptr(ds))
+        y = g.to_host(dy, np.uint8, (n, n))
+        s = g.to_host(ds, np.uint8, sdims)
+        blocks = np.abs(x32).reshape(n, n // 32, 32).max(axis=2) if axis == 1 else np.abs(x32).reshape(n // 32, 32, n).max(axis=1)
+        assert np.array_equal(s, oracle.block_scale_code_many(blocks))
+        # oracle slab: 64 rows (A) or 64 columns' worth of blocks via the first 64 K-rows (B)
+        rows = 64
+        sub = np.ascontiguousarray(bits[:rows])
+        y_ref = np.zeros(rows * n, dtype=np.uint8)
+        s_rows = rows if axis == 1 else rows // 32
+        s_ref = np.zeros(s_rows * (n // 32 if axis == 1 else n), dtype=np.uint8)
+        oracle.block_scale_quantize(tensor(BF16, [rows, n]), sub, tensor(E4M3, [rows, n]), y_ref,
+                                    tensor(E8M0, [rows, n // 32] if axis == 1 else [rows // 32, n]), s_ref, 32, axis)
+        assert np.array_equal(y[:rows].reshape(-1), y_ref)
+        assert np.array_equal(s[:s_rows].reshape(-1), s_ref)
+        # round trip through the dequantize kernel
+        q = dfgpu.BsdParams()
+        q.x, q.scale, q.y = tensor(E4M3, [n, n]), tensor(E8M0, sdims), tensor(F32, [n, n])
+        q.block[0], q.block[1], q.block_count = (1, 32, 2) if axis == 1 else (32, 1, 2)
+        dz = g.device_zeros(n * n * 4)
+        dfgpu.block_scale_dequantize(q, g.ptr(dy), g.ptr(ds), g.ptr(dz))
+        z = g.to_host(dz, np.float32, (n, n))
+        scale_full = np.repeat(np.ldexp(1.0, s.astype(np.int32) - 127), 32, axis=1 if axis == 1 else 0)
+        assert np.all(np.abs(z - x32) <= scale_full * 16.0 + 0)  # coarse: half a top-binade step (32/2)
+        rel = np.abs(z - x32) <= np.maximum(np.abs(x32) * 0.0625, scale_full * 2.0 ** -10)
+        assert np.all(rel)

@@ -1,0 +1,257 @@
+"""POINTWISE, CONV_FPROP and MATMUL kernels against the CPU oracle, through the C ABI.
+
+Tolerances: f32 graphs max|d| <= 1e-4 * max|ref| (and the reference's own
+1e-4 + 1e-3*|ref| per element); bf16 storage |d| <= 1e-2 + 2e-2*|ref|."""
+import numpy as np
+import pytest
+
+import gpu_util as g
+import oracle
+from deepforge_b200 import dfgpu, synthetic
+from deepforge_b200.dfgpu import BF16, E4M3, E8M0, F32, tensor
+
+pytestmark = pytest.mark.gpu
+FLT_MAX = 3.4028234663852886e38
+
+
+def check_f32(actual, reference):
+    scale = max(float(np.max(np.abs(reference))), 1e-30)
+    assert float(np.max(np.abs(actual - reference))) <= 1e-4 * scale
+    assert np.all(np.abs(actual - reference) <= 1e-4 + 1e-3 * np.abs(reference))
+
+
+def check_bf16(actual, reference):
+    assert np.all(np.abs(actual - reference) <= 1e-2 + 2e-2 * np.abs(reference))
+
+
+def host_array(values, dtype):
+    return synthetic.to_bf16_bits(values) if dtype == BF16 else np.ascontiguousarray(values, dtype=np.float32)
+
+
+def read_back(buffer, dtype, shape):
+    if dtype == BF16:
+        return synthetic.bf16_bits_to_f32(g.to_host(buffer, np.uint16)).reshape(shape)
+    return g.to_host(buffer, np.float32, shape)
+
+
+def nhwc_strides(dims):
+    n, c, h, w = dims
+    return [h * w * c, 1, w * c, c]
+
+
+def step(op, operand=0, lower=0.0, upper=FLT_MAX, slope=0.0):
+    s = dfgpu.EpilogueStep()
+    s.op, s.operand, s.relu_lower, s.relu_upper, s.relu_slope = op, operand, lower, upper, slope
+    return s
+
+
+@pytest.mark.parametrize("mode", [dfgpu.PW_ADD, dfgpu.PW_MUL, dfgpu.PW_SUB, dfgpu.PW_RELU_FWD, dfgpu.PW_IDENTITY])
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_pointwise_broadcast(mode, dtype):
+    shape = [2, 6, 5, 4]
+    a = synthetic.normal(1, 1, int(np.prod(shape)))
+    a[3] = np.nan
+    a[5] = np.inf
+    b = synthetic.normal(1, 2, 6)
+    ad, bd, od = tensor(dtype, shape), tensor(dtype, [1, 6, 1, 1]), tensor(dtype, shape)
+    ha, hb = host_array(a, dtype), host_array(b, dtype)
+    width = dfgpu.DTYPE_BYTES[dtype]
+    ref = np.zeros(a.size * width, dtype=np.uint8)
+    oracle.pointwise(mode, ad, ha, bd, hb, od, ref, 0.25, 1.5, 0.1)
+    p = dfgpu.PointwiseParams()
+    p.in0, p.in1, p.out, p.mode = ad, bd, od, mode
+    p.relu_lower, p.relu_upper, p.relu_slope = 0.25, 1.5, 0.1
+    da, db, do = g.to_device(ha), g.to_device(hb), g.device_zeros(ref.size)
+    dfgpu.pointwise(p, g.ptr(da), g.ptr(db), g.ptr(do))
+    out = g.to_host(do, np.uint8)
+    view = np.uint32 if dtype == F32 else np.uint16
+    a_bits, r_bits = out.view(view), ref.view(view)
+    nan = np.isnan(read_back(do, dtype, shape)).reshape(-1)
+    assert np.array_equal(a_bits[~nan], r_bits[~nan])
+
+
+def test_relu_default_clips_inf_to_flt_max_and_keeps_nan():
+    x = np.array([-1.0, 0.5, np.inf, np.nan, -np.inf], dtype=np.float32)
+    d = tensor(F32, [5])
+    p = dfgpu.PointwiseParams()
+    p.in0, p.out, p.mode, p.relu_lower, p.relu_upper, p.relu_slope = d, d, dfgpu.PW_RELU_FWD, 0.0, FLT_MAX, 0.0
+    dx, do = g.to_device(x), g.device_zeros(20)
+    dfgpu.pointwise(p, g.ptr(dx), 0, g.ptr(do))
+    out = g.to_host(do, np.float32)
+    assert out[0] == 0.0 and out[1] == 0.5 and out[2] == np.float32(FLT_MAX) and np.isnan(out[3]) and out[4] == 0.0
+
+
+def run_conv(dtype, x_dims, w_dims, pre, post, stride, dilation, kernel, x_strides=None, w_strides=None, y_strides=None,
+             reverse=False, epilogue=(), extras=(), seed=1):
+    n, c, h, w = x_dims
+    k, cg, r, s = w_dims
+    oh = (h + pre[0] + post[0] - (dilation[0] * (r - 1) + 1)) // stride[0] + 1
+    ow = (w + pre[1] + post[1] - (dilation[1] * (s - 1) + 1)) // stride[1] + 1
+    y_dims = [n, k, oh, ow]
+    xd, wd, yd = tensor(dtype, x_dims, x_strides), tensor(dtype, w_dims, w_strides), tensor(dtype, y_dims, y_strides)
+    x = synthetic.normal(seed, 1, int(np.prod(x_dims)))
+    wv = synthetic.normal(seed, 2, int(np.prod(w_dims)), std=(2.0 / (cg * r * s)) ** 0.5)
+    hx, hw = host_array(x, dtype), host_array(wv, dtype)
+    # oracle: f32 restatement on the (possibly bf16-rounded) values
+    fx = synthetic.round_to_bf16(x) if dtype == BF16 else x
+    fw = synthetic.round_to_bf16(wv) if dtype == BF16 else wv
+    fxd, fwd, fyd = tensor(F32, x_dims, x_strides), tensor(F32, w_dims, w_strides), tensor(F32, y_dims, y_strides)
+    ref = np.zeros(int(np.prod(y_dims)), dtype=np.float32)
+    oracle.conv_generic(fxd, fx, fwd, fw, fyd, ref, oracle.conv_attrs(pre, post, stride, dilation, reverse))
+    p = dfgpu.ConvParams()
+    p.x, p.w, p.y = xd, wd, yd
+    for i in range(2):
+        p.pre_pad[i], p.post_pad[i], p.stride[i], p.dilation[i] = pre[i], post[i], stride[i], dilation[i]
+    p.reverse_filter, p.kernel = int(reverse), kernel
+    extra_dev = [None, None]
+    for i, (dims, strides, values) in enumerate(extras):
+        p.extra[i] = tensor(dtype, dims, strides)
+        extra_dev[i] = g.to_device(host_array(values, dtype))
+    p.epilogue_count = len(epilogue)
+    for i, e in enumerate(epilogue):
+        p.epilogue[i] = e
+        tmp = np.zeros_like(ref)
+        if e.op == dfgpu.EPI_ADD:
+            dims, strides, values = extras[e.operand]
+            ev = synthetic.round_to_bf16(values) if dtype == BF16 else values
+            oracle.pointwise(dfgpu.PW_ADD, fyd, ref, tensor(F32, dims, strides), np.ascontiguousarray(ev, dtype=np.float32), fyd, tmp)
+        else:
+            oracle.pointwise(dfgpu.PW_RELU_FWD, fyd, ref, None, None, fyd, tmp, e.relu_lower, e.relu_upper, e.relu_slope)
+        ref = tmp
+    dx, dw = g.to_device(hx), g.to_device(hw)
+    dy = g.device_zeros(ref.size * dfgpu.DTYPE_BYTES[dtype])
+    info = dfgpu.query("conv_fprop", p)
+    dfgpu.conv_fprop(p, g.ptr(dx), g.ptr(dw), g.ptr(dy), g.ptr(extra_dev[0]), g.ptr(extra_dev[1]))
+    out = read_back(dy, dtype, -1)
+    return info, out, ref
+
+
+@pytest.mark.parametrize("kernel", [dfgpu.CONV_DIRECT, dfgpu.CONV_IGEMM_FFMA])
+@pytest.mark.parametrize("c,k,h,w", [(1, 1, 5, 5), (7, 8, 6, 9), (17, 33, 29, 30), (64, 64, 14, 14), (31, 15, 8, 8)])
+def test_conv_f32_nhwc_tails(kernel, c, k, h, w):
+    x_dims, w_dims = [2, c, h, w], [k, c, 3, 3]
+    info, out, ref = run_conv(F32, x_dims, w_dims, [1, 1], [1, 1], [1, 1], [1, 1], kernel,
+                              nhwc_strides(x_dims), nhwc_strides(w_dims), nhwc_strides([2, k, h, w]))
+    assert info.kernel == kernel
+    check_f32(out, ref)
+
+
+@pytest.mark.parametrize("kernel", [dfgpu.CONV_DIRECT, dfgpu.CONV_IGEMM_FFMA])
+def test_conv_f32_nchw_asymmetric_strided_dilated(kernel):
+    info, out, ref = run_conv(F32, [2, 6, 11, 9], [10, 6, 3, 2], [1, 0], [2, 1], [2, 1], [1, 2], kernel, reverse=True)
+    check_f32(out, ref)
+
+
+def test_conv_grouped_direct():
+    info, out, ref = run_conv(F32, [2, 8, 9, 8], [6, 4, 3, 2], [1, 2], [2, 0], [2, 1], [1, 2], dfgpu.CONV_AUTO)
+    assert info.kernel == dfgpu.CONV_DIRECT
+    check_f32(out, ref)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_conv_fused_bias_relu_residual(dtype):
+    x_dims, w_dims = [2, 16, 7, 7], [16, 16, 3, 3]
+    bias = synthetic.uniform(3, 5, 16, -0.1, 0.1)
+    residual = synthetic.normal(3, 6, 2 * 16 * 7 * 7)
+    y_strides = nhwc_strides([2, 16, 7, 7])
+    info, out, ref = run_conv(dtype, x_dims, w_dims, [1, 1], [1, 1], [1, 1], [1, 1], dfgpu.CONV_IGEMM_FFMA,
+                              nhwc_strides(x_dims), nhwc_strides(w_dims), y_strides,
+                              epilogue=[step(dfgpu.EPI_ADD, 0), step(dfgpu.EPI_RELU), step(dfgpu.EPI_ADD, 1)],
+                              extras=[([1, 16, 1, 1], [16, 1, 16, 16], bias), ([2, 16, 7, 7], y_strides, residual)])
+    (check_f32 if dtype == F32 else check_bf16)(out, ref)
+
+
+def test_conv_benchmark_shape_c1_both_layouts():
+    """1x64x56x56 (*) 64x64x3x3, pad 1: the reference's 'large' profile (NHWC) and the NCHW-strided form."""
+    x_dims, w_dims, y_dims = [1, 64, 56, 56], [64, 64, 3, 3], [1, 64, 56, 56]
+    info, out, ref = run_conv(F32, x_dims, w_dims, [1, 1], [1, 1], [1, 1], [1, 1], dfgpu.CONV_AUTO,
+                              nhwc_strides(x_dims), nhwc_strides(w_dims), nhwc_strides(y_dims), seed=20261126)
+    check_f32(out, ref)
+    info, out, ref = run_conv(F32, x_dims, w_dims, [1, 1], [1, 1], [1, 1], [1, 1], dfgpu.CONV_AUTO, seed=20261126)
+    check_f32(out, ref)
+
+
+def test_conv_special_values_single_node_rule():
+    # zero -> 0, NaN -> NaN, +Inf -> +Inf
+    xd = tensor(F32, [1, 1, 3, 3])
+    p = dfgpu.ConvParams()
+    p.x, p.w, p.y = xd, xd, xd
+    for i in range(2):
+        p.pre_pad[i], p.post_pad[i], p.stride[i], p.dilation[i] = 1, 1, 1, 1
+    w = np.ones(9, dtype=np.float32)
+    for centre, check in ((0.0, lambda y: np.all(y == 0)), (np.nan, lambda y: np.all(np.isnan(y))), (np.inf, lambda y: np.all(y == np.inf))):
+        x = np.zeros(9, dtype=np.float32)
+        x[4] = centre
+        dx, dw, dy = g.to_device(x), g.to_device(w), g.device_zeros(36)
+        for kernel in (dfgpu.CONV_DIRECT, dfgpu.CONV_IGEMM_FFMA):
+            p.kernel = kernel
+            dfgpu.conv_fprop(p, g.ptr(dx), g.ptr(dw), g.ptr(dy))
+            assert check(g.to_host(dy, np.float32)), (centre, kernel)
+
+
+def run_matmul(dtype, a_dims, b_dims, kernel=dfgpu.MATMUL_FFMA, a_strides=None, b_strides=None, seed=2):
+    rank = len(a_dims)
+    c_dims = [max(x, y) for x, y in zip(a_dims[:-2], b_dims[:-2])] + [a_dims[-2], b_dims[-1]]
+    a = synthetic.normal(seed, 1, int(np.prod(a_dims)))
+    b = synthetic.normal(seed, 2, int(np.prod(b_dims)))
+    fa = synthetic.round_to_bf16(a) if dtype == BF16 else a
+    fb = synthetic.round_to_bf16(b) if dtype == BF16 else b
+    ref = np.zeros(int(np.prod(c_dims)), dtype=np.float32)
+    oracle.matmul(tensor(F32, a_dims, a_strides), fa, tensor(F32, b_dims, b_strides), fb, tensor(F32, c_dims), ref)
+    p = dfgpu.MatmulParams()
+    p.a, p.b, p.c, p.kernel = tensor(dtype, a_dims, a_strides), tensor(dtype, b_dims, b_strides), tensor(dtype, c_dims), kernel
+    da, db = g.to_device(host_array(a, dtype)), g.to_device(host_array(b, dtype))
+    dc = g.device_zeros(ref.size * dfgpu.DTYPE_BYTES[dtype])
+    dfgpu.matmul(p, g.ptr(da), g.ptr(db), g.ptr(dc))
+    return read_back(dc, dtype, -1), ref
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("a_dims,b_dims", [([2, 2, 3], [1, 3, 2]), ([70, 45], [45, 33]), ([3, 1, 65, 129], [1, 2, 129, 64])])
+def test_matmul_ffma(dtype, a_dims, b_dims):
+    out, ref = run_matmul(dtype, a_dims, b_dims)
+    (check_f32 if dtype == F32 else check_bf16)(out, ref)
+
+
+def test_matmul_transposed_strides():
+    out, ref = run_matmul(F32, [40, 24], [24, 56], a_strides=[1, 40], b_strides=[1, 24])
+    check_f32(out, ref)
+
+
+def test_matmul_known_answer_with_bias_epilogue():
+    a = np.array([1, 2, 3, 4, 5, 6, -1, 0, 1, 2, -2, 1], dtype=np.float32)
+    b = np.array([1, 2, 0, 1, 1, 0], dtype=np.float32)
+    bias = np.array([0.5, -1.0], dtype=np.float32)
+    p = dfgpu.MatmulParams()
+    p.a, p.b, p.c = tensor(F32, [2, 2, 3]), tensor(F32, [1, 3, 2]), tensor(F32, [2, 2, 2])
+    p.extra[0] = tensor(F32, [2])
+    p.epilogue_count = 1
+    p.epilogue[0] = step(dfgpu.EPI_ADD, 0)
+    da, db, dbias, dc = g.to_device(a), g.to_device(b), g.to_device(bias), g.device_zeros(32)
+    dfgpu.matmul(p, g.ptr(da), g.ptr(db), g.ptr(dc), extra0=g.ptr(dbias))
+    assert g.to_host(dc, np.float32).tolist() == [4.5, 3.0, 10.5, 12.0, 0.5, -3.0, 3.5, 1.0]
+
+
+def test_matmul_with_fused_block_dequantize():
+    """quantize -> (dequantize -> matmul fused): equals the oracle's dequantize + f32 matmul."""
+    m, k, n = 96, 128, 80
+    a = synthetic.normal(7, 1, m * k)
+    b = synthetic.normal(7, 2, k * n)
+    aq, sa = np.zeros(m * k, dtype=np.uint8), np.zeros(m * k // 32, dtype=np.uint8)
+    bq, sb = np.zeros(k * n, dtype=np.uint8), np.zeros(k * n // 32, dtype=np.uint8)
+    oracle.block_scale_quantize(tensor(F32, [m, k]), a, tensor(E4M3, [m, k]), aq, tensor(E8M0, [m, k // 32]), sa, 32, 1)
+    oracle.block_scale_quantize(tensor(F32, [k, n]), b, tensor(E4M3, [k, n]), bq, tensor(E8M0, [k // 32, n]), sb, 32, 0)
+    af, bf = np.zeros(m * k, dtype=np.float32), np.zeros(k * n, dtype=np.float32)
+    oracle.block_scale_dequantize(tensor(E4M3, [m, k]), aq, tensor(E8M0, [m, k // 32]), sa, tensor(F32, [m, k]), af, [1, 32])
+    oracle.block_scale_dequantize(tensor(E4M3, [k, n]), bq, tensor(E8M0, [k // 32, n]), sb, tensor(F32, [k, n]), bf, [32, 1])
+    ref = np.zeros(m * n, dtype=np.float32)
+    oracle.matmul(tensor(F32, [m, k]), af, tensor(F32, [k, n]), bf, tensor(F32, [m, n]), ref)
+    p = dfgpu.MatmulParams()
+    p.a, p.b, p.c = tensor(E4M3, [m, k]), tensor(E4M3, [k, n]), tensor(F32, [m, n])
+    p.a_scale, p.b_scale = tensor(E8M0, [m, k // 32]), tensor(E8M0, [k // 32, n])
+    p.a_block[0], p.a_block[1], p.b_block[0], p.b_block[1] = 1, 32, 32, 1
+    p.kernel = dfgpu.MATMUL_FFMA
+    d = [g.to_device(v) for v in (aq, bq, sa, sb)]
+    dc = g.device_zeros(m * n * 4)
+    dfgpu.matmul(p, g.ptr(d[0]), g.ptr(d[1]), g.ptr(dc), g.ptr(d[2]), g.ptr(d[3]))
+    check_f32(g.to_host(dc, np.float32), ref)

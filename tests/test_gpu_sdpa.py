@@ -1,0 +1,178 @@
+"""SDPA forward kernels (row-wise general kernel, paged decode) against the CPU oracle."""
+import numpy as np
+import pytest
+
+import gpu_util as g
+import oracle
+from deepforge_b200 import dfgpu, synthetic
+from deepforge_b200.dfgpu import BF16, F32, I32, tensor
+
+pytestmark = pytest.mark.gpu
+INF = float("inf")
+
+
+def close_f32(actual, expected, tol=8e-5):
+    finite = np.isfinite(expected)
+    assert np.array_equal(actual[~finite], expected[~finite])
+    assert np.all(np.abs(actual[finite] - expected[finite]) <= tol * (1 + np.abs(expected[finite])))
+
+
+def close_bf16(actual, expected):
+    assert np.all(np.abs(actual - expected) <= 1e-2 + 2e-2 * np.abs(expected))
+
+
+def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=None, stats=True, seed=5, q_step=1, bh_range=None, **flags):
+    """Run oracle (f32 restatement on dtype-rounded inputs) and the GPU kernel on the same data."""
+    b, hq, sq, _ = q_dims
+    o_dims = [b, hq, sq, v_dims[3]]
+    row_dims = [b, hq, sq, 1]
+    raw = [synthetic.normal(seed, i + 1, int(np.prod(d))) for i, d in enumerate((q_dims, k_dims, v_dims))]
+    rounded = [synthetic.round_to_bf16(a) if dtype == BF16 else a for a in raw]
+    host = [synthetic.to_bf16_bits(a) if dtype == BF16 else a for a in raw]
+
+    def fill(params, t):
+        params.q, params.k, params.v, params.o = (tensor(t, d) for d in (q_dims, k_dims, v_dims, o_dims))
+        if stats:
+            params.stats = params.max = params.sum_exp = tensor(F32, row_dims)
+        params.attn_scale, params.s_kv = scale, s_kv
+        if seq is not None:
+            params.padding_mask = 1
+            params.seq_q = params.seq_kv = tensor(I32, [b, 1, 1, 1])
+        if tables is not None:
+            params.page_table_k = tensor(I32, [b, 1, tables[0].shape[1], 1])
+            params.page_table_v = tensor(I32, [b, 1, tables[1].shape[1], 1])
+        for key, value in flags.items():
+            setattr(params, key, value)
+
+    op = oracle.SdpaParams()
+    fill(op, F32)
+    o_ref = np.full(int(np.prod(o_dims)), -99.0, dtype=np.float32)
+    rows_ref = [np.full(int(np.prod(row_dims)), -99.0, dtype=np.float32) for _ in range(3)]
+    seq_arrays = [None, None] if seq is None else [np.asarray(s, dtype=np.int32) for s in seq]
+    table_arrays = [None, None] if tables is None else [np.ascontiguousarray(t, dtype=np.int32) for t in tables]
+    lo, hi = bh_range if bh_range else (0, b * hq)
+    oracle.sdpa_forward(op, rounded + [o_ref] + (rows_ref if stats else [None] * 3) + seq_arrays + table_arrays, lo, hi, q_step)
+
+    gp = dfgpu.SdpaParams()
+    fill(gp, dtype)
+    gp.kernel = kernel
+    info = dfgpu.query("sdpa_forward", gp)
+    dev = [g.to_device(a) for a in host]
+    do = g.device_zeros(o_ref.size * dfgpu.DTYPE_BYTES[dtype])
+    drows = [g.device_zeros(rows_ref[0].size * 4) for _ in range(3)] if stats else [None] * 3
+    dseq = [g.to_device(a) if a is not None else None for a in seq_arrays]
+    dtab = [g.to_device(a) if a is not None else None for a in table_arrays]
+    scratch = g.device_zeros(info.scratch_bytes) if info.scratch_bytes else None
+    dfgpu.sdpa_forward(gp, [g.ptr(t) for t in dev + [do] + drows + dseq + dtab], scratch=g.ptr(scratch))
+    if dtype == BF16:
+        o = synthetic.bf16_bits_to_f32(g.to_host(do, np.uint16))
+    else:
+        o = g.to_host(do, np.float32)
+    rows = [g.to_host(d, np.float32) for d in drows] if stats else None
+    return info, o.reshape(o_dims), o_ref.reshape(o_dims), rows, rows_ref
+
+
+def test_rowwise_gqa_padding_windows_stats_f32():
+    for bottom_right in (0, 1):
+        info, o, o_ref, rows, rows_ref = both(F32, [2, 4, 5, 8], [2, 2, 7, 8], [2, 1, 7, 6], 7, 0.3, dfgpu.SDPA_ROWWISE,
+                                              seq=([5, 3], [7, 4]), has_right_bound=1, right_bound=1, has_left_bound=1,
+                                              left_bound=3, bottom_right=bottom_right)
+        close_f32(o, o_ref)
+        for a, r in zip(rows, rows_ref):
+            close_f32(a, r)
+        assert np.all(o[1, :, 3:] == 0.0) and np.all(rows[0].reshape(2, 4, 5)[1, :, 3:] == -INF)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_rowwise_causal_medium(dtype):
+    info, o, o_ref, rows, rows_ref = both(dtype, [2, 4, 96, 128], [2, 4, 96, 128], [2, 4, 96, 128], 96, 128 ** -0.5,
+                                          dfgpu.SDPA_ROWWISE, has_right_bound=1, right_bound=0)
+    if dtype == F32:
+        close_f32(o, o_ref)
+        close_f32(rows[0], rows_ref[0])
+    else:
+        close_bf16(o, o_ref)
+        close_f32(rows[0], rows_ref[0], 2e-3)
+
+
+def _reference_paged_case():
+    q = np.array([0.2, -0.3, -0.5, 0.4], dtype=np.float32)
+    k = np.array([0.6, -0.2, -0.4, 0.9, 0.1, 0.5, -0.3, 0.8, 0.7, -0.6, 0.2, 0.4], dtype=np.float32).reshape(2, 1, 3, 2)
+    v = np.array([0.3, -0.7, 0.8, 0.2, -0.6, 0.4, 0.5, -0.1, -0.2, 0.9, 0.6, -0.8], dtype=np.float32).reshape(2, 1, 3, 2)
+    page_k = np.array([2, 0, 3, 1], dtype=np.int32)
+    page_v = np.array([1, 3, 0, 2], dtype=np.int32)
+
+    def container(logical, table):
+        c = np.full((4, 1, 2, 2), -17.0, dtype=np.float32)
+        for b in range(2):
+            for s in range(3):
+                c[table[b * 2 + s // 2], 0, s % 2] = logical[b, 0, s]
+        return c
+    return q, k, v, page_k, page_v, container(k, page_k), container(v, page_v)
+
+
+def test_reference_paged_case_and_invalid_pages():
+    q, k, v, page_k, page_v, kc, vc = _reference_paged_case()
+    p = dfgpu.SdpaParams()
+    p.q, p.o = tensor(F32, [2, 1, 1, 2]), tensor(F32, [2, 1, 1, 2])
+    p.k = p.v = tensor(F32, [4, 1, 2, 2])
+    p.seq_q = p.seq_kv = tensor(I32, [2, 1, 1, 1])
+    p.page_table_k = p.page_table_v = tensor(I32, [2, 1, 2, 1])
+    p.attn_scale, p.padding_mask, p.s_kv = 0.5, 1, 3
+    seq_q, seq_kv = np.array([1, 1], dtype=np.int32), np.array([3, 3], dtype=np.int32)
+    # contiguous reference through the oracle
+    op = oracle.SdpaParams()
+    op.q, op.o = tensor(F32, [2, 1, 1, 2]), tensor(F32, [2, 1, 1, 2])
+    op.k = op.v = tensor(F32, [2, 1, 3, 2])
+    op.attn_scale, op.s_kv = 0.5, 3
+    ref = np.zeros(4, dtype=np.float32)
+    oracle.sdpa_forward(op, [q, k, v, ref] + [None] * 7)
+    dev = [g.to_device(a) for a in (q, kc, vc)]
+    do = g.device_zeros(16)
+    dsq, dskv = g.to_device(seq_q), g.to_device(seq_kv)
+    for tables, check in (((page_k, page_v), lambda o: close_f32(o, ref)),
+                          ((np.array([-1, 99, 3, 1], dtype=np.int32), np.array([-1, 99, 0, 2], dtype=np.int32)),
+                           lambda o: (o[0] == 0.0 and o[1] == 0.0) or pytest.fail("invalid pages must read as zero"))):
+        dt = [g.to_device(t) for t in tables]
+        dfgpu.sdpa_forward(p, [g.ptr(t) for t in dev + [do]] + [0, 0, 0, g.ptr(dsq), g.ptr(dskv), g.ptr(dt[0]), g.ptr(dt[1])])
+        check(g.to_host(do, np.float32))
+
+
+def _paged_inputs(batch, hq, hkv, pages, block, max_len, seed, lengths=None):
+    table_len = (max_len + block - 1) // block
+    if lengths is None:
+        lengths = synthetic.integers(seed, 50, batch, max(1, max_len // 16), max_len)
+    tk = np.stack([synthetic.permutation_prefix(seed, 100 + i, pages, table_len) for i in range(batch)])
+    tv = np.stack([synthetic.permutation_prefix(seed, 200 + i, pages, table_len) for i in range(batch)])
+    return np.asarray(lengths, dtype=np.int32), tk.astype(np.int32), tv.astype(np.int32)
+
+
+@pytest.mark.parametrize("group,block", [(4, 64), (1, 16), (8, 128), (2, 256)])
+def test_paged_decode_matches_oracle(group, block):
+    batch, hkv, pages, max_len = 5, 2, 40, 700
+    hq = hkv * group
+    lengths, tk, tv = _paged_inputs(batch, hq, hkv, pages, block, max_len, seed=31 + group)
+    lengths[0] = max_len
+    lengths[1] = 1
+    tk[2, 1] = -1          # invalid page ids read as zeros
+    tv[2, 0] = pages + 7
+    info, o, o_ref, rows, rows_ref = both(BF16, [batch, hq, 1, 128], [pages, hkv, block, 128], [pages, hkv, block, 128], max_len,
+                                          128 ** -0.5, dfgpu.SDPA_PAGED_DECODE, seq=([1] * batch, lengths), tables=(tk, tv))
+    assert info.kernel == dfgpu.SDPA_PAGED_DECODE and info.scratch_bytes > 0 and info.launches == 2
+    close_bf16(o, o_ref)
+    for a, r in zip(rows, rows_ref):
+        close_f32(a, r, 1e-3)
+    # and the general kernel agrees on the same paged inputs
+    info2, o2, _, _, _ = both(BF16, [batch, hq, 1, 128], [pages, hkv, block, 128], [pages, hkv, block, 128], max_len,
+                              128 ** -0.5, dfgpu.SDPA_ROWWISE, seq=([1] * batch, lengths), tables=(tk, tv))
+    close_bf16(o2, o_ref)
+
+
+def test_paged_decode_zero_length_sequence_gives_zero_output():
+    batch, hkv, pages, block, max_len = 3, 2, 16, 64, 256
+    lengths, tk, tv = _paged_inputs(batch, 8, hkv, pages, block, max_len, seed=3, lengths=[0, 256, 100])
+    info, o, o_ref, rows, rows_ref = both(BF16, [batch, 8, 1, 128], [pages, hkv, block, 128], [pages, hkv, block, 128], max_len,
+                                          0.1, dfgpu.SDPA_AUTO, seq=([1] * batch, lengths), tables=(tk, tv))
+    assert info.kernel == dfgpu.SDPA_PAGED_DECODE
+    assert np.all(o[0] == 0.0) and np.all(rows[0].reshape(batch, 8)[0] == -INF)
+    close_bf16(o, o_ref)
