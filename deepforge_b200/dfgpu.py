@@ -104,7 +104,7 @@ EXPORTS = [
     "dfgpu_query_conv_fprop", "dfgpu_conv_fprop",
     "dfgpu_query_matmul", "dfgpu_matmul",
     "dfgpu_query_sdpa_forward", "dfgpu_sdpa_forward",
-    "dfgpu_selfcheck_e4m3", "dfgpu_debug_scale_codes", "dfgpu_debug_encode_e4m3",
+    "dfgpu_selfcheck_e4m3", "dfgpu_debug_scale_codes", "dfgpu_debug_encode_e4m3", "dfgpu_device_status",
 ]
 
 
@@ -201,3 +201,12 @@ def debug_encode_e4m3(values_ptr: int, codes_ptr: int, count: int, stream=None) 
     fn = load().dfgpu_debug_encode_e4m3
     fn.restype = C.c_int
     _check(fn(C.c_void_p(values_ptr), C.c_void_p(codes_ptr), C.c_int64(count), C.c_void_p(stream or None)))
+
+
+def device_status() -> int:
+    """Synchronise, then read and clear the device-side status word (0 = healthy)."""
+    value = C.c_int(0)
+    fn = load().dfgpu_device_status
+    fn.restype = C.c_int
+    _check(fn(C.byref(value)))
+    return value.value

@@ -202,6 +202,13 @@ int dfgpu_selfcheck_e4m3(uint32_t first_bits, uint64_t count, void* result, void
 int dfgpu_debug_scale_codes(const void* amax_f32, void* codes_u8, int64_t count, void* stream);
 int dfgpu_debug_encode_e4m3(const void* values_f32, void* codes_u8, int64_t count, void* stream);
 
+/* ---- device status ---------------------------------------------------------------
+   Kernels that wait on hardware barriers (TMA / tcgen05 pipelines) bound every wait;
+   a wait that expires leaves a non-zero code in a device-side status word and the
+   kernel returns early. This call synchronises the device, reads the word into
+   *status and clears it. 0 = no kernel gave up since the last call. */
+int dfgpu_device_status(int* status);
+
 #ifdef __cplusplus
 }
 #endif

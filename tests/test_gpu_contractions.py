@@ -78,7 +78,8 @@ def test_relu_default_clips_inf_to_flt_max_and_keeps_nan():
     dx, do = g.to_device(x), g.device_zeros(20)
     dfgpu.pointwise(p, g.ptr(dx), 0, g.ptr(do))
     out = g.to_host(do, np.float32)
-    assert out[0] == 0.0 and out[1] == 0.5 and out[2] == np.float32(FLT_MAX) and np.isnan(out[3]) and out[4] == 0.0
+    # -inf takes the lower branch: 0 + 0 * (-inf - 0) = NaN, exactly as the reference's formula gives
+    assert out[0] == 0.0 and out[1] == 0.5 and out[2] == np.float32(FLT_MAX) and np.isnan(out[3]) and np.isnan(out[4])
 
 
 def run_conv(dtype, x_dims, w_dims, pre, post, stride, dilation, kernel, x_strides=None, w_strides=None, y_strides=None,
