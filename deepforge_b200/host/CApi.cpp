@@ -1,0 +1,159 @@
+// Flat C API (include/deepforge_b200.h) over the C++ host side.
+#include "deepforge_b200.h"
+
+#include "DeepForge/Compiler/Codegen.h"
+
+#include <algorithm>
+#include <cstring>
+#include <span>
+
+using namespace deepforge;
+
+struct df_executable {
+    compiler::CompilationResult result;
+};
+
+namespace {
+thread_local std::string g_error;
+
+int report(import::Status const& status) {
+    if (status.is_bad()) g_error = status.message();
+    return static_cast<int>(status.code());
+}
+
+import::InputFormat to_format(int format) {
+    return format == DF_FORMAT_JSON ? import::InputFormat::kJson : format == DF_FORMAT_UBJSON ? import::InputFormat::kUbjson : import::InputFormat::kAuto;
+}
+}  // namespace
+
+extern "C" const char* df_last_error(void) { return g_error.c_str(); }
+
+extern "C" int df_parse(const uint8_t* document, size_t size, int format, int64_t* tensor_count, int64_t* node_count) {
+    import::SerializedGraph graph;
+    import::SerializedGraphImporter importer;
+    auto status = importer.parse(std::span<const uint8_t>(document, size), to_format(format), graph);
+    if (status.is_good()) {
+        if (tensor_count) *tensor_count = static_cast<int64_t>(graph.tensor_count());
+        if (node_count) *node_count = static_cast<int64_t>(graph.nodes.size());
+    }
+    return report(status);
+}
+
+extern "C" int df_compile(const uint8_t* document, size_t size, int format, uint32_t options, df_executable** out) {
+    if (!out) return report(import::Status::failure(import::ErrorCode::kInvalidArgument, "out", "null output pointer"));
+    *out = nullptr;
+    import::SerializedGraph graph;
+    import::SerializedGraphImporter importer;
+    auto status = importer.parse(std::span<const uint8_t>(document, size), to_format(format), graph);
+    if (status.is_bad()) return report(status);
+    compiler::CompileOptions compile_options;
+    compile_options.fuse = !(options & DF_OPTION_NO_FUSION);
+    compile_options.narrow_virtual_tensors = !(options & DF_OPTION_NO_NARROWING);
+    compile_options.disable_tensor_cores = (options & DF_OPTION_NO_TENSOR_CORES) != 0;
+    auto holder = std::make_unique<df_executable>();
+    status = compiler::compile_graph(graph, compile_options, holder->result);
+    if (status.is_bad()) return report(status);
+    *out = holder.release();
+    return 0;
+}
+
+extern "C" void df_destroy(df_executable* executable) { delete executable; }
+
+extern "C" int64_t df_workspace_size(const df_executable* executable) { return executable->result.executable->get_workspace_size(); }
+extern "C" int64_t df_launch_count(const df_executable* executable) { return executable->result.executable->launch_count(); }
+
+extern "C" size_t df_plan_text(const df_executable* executable, char* buffer, size_t capacity) {
+    auto text = executable->result.executable->plan_text();
+    if (buffer && capacity) {
+        size_t n = std::min(capacity - 1, text.size());
+        std::memcpy(buffer, text.data(), n);
+        buffer[n] = '\0';
+    }
+    return text.size();
+}
+
+extern "C" int64_t df_argument_count(const df_executable* executable) { return static_cast<int64_t>(executable->result.metadata.arguments.size()); }
+
+extern "C" int df_argument_info(const df_executable* executable, int64_t index, int64_t* uid, uint64_t* size_bytes, uint64_t* alignment, int32_t* access) {
+    auto const& arguments = executable->result.metadata.arguments;
+    if (index < 0 || index >= static_cast<int64_t>(arguments.size()))
+        return report(import::Status::failure(import::ErrorCode::kInvalidArgument, "index", "argument index out of range"));
+    auto const& argument = arguments[static_cast<size_t>(index)];
+    if (uid) *uid = argument.uid;
+    if (size_bytes) *size_bytes = argument.size_bytes;
+    if (alignment) *alignment = argument.alignment;
+    if (access) *access = static_cast<int32_t>(argument.access);
+    return 0;
+}
+
+extern "C" void df_set_stream(df_executable* executable, void* stream) { executable->result.executable->set_stream(stream); }
+
+extern "C" int df_execute(const df_executable* executable, void* handle, const int64_t* uids, void* const* pointers, size_t count, void* workspace) {
+    runtime::VariantPack pack;
+    pack.reserve(count);
+    for (size_t i = 0; i < count; ++i) pack[uids[i]] = pointers[i];
+    return report(executable->result.executable->execute(handle, pack, workspace));
+}
+
+extern "C" int64_t df_step_count(const df_executable* executable) { return static_cast<int64_t>(executable->result.plan.steps.size()); }
+
+extern "C" int df_step_info(const df_executable* executable, int64_t step, char* label, size_t label_capacity, int32_t* op, int32_t* kernel,
+                            int32_t* launches, uint64_t* bound_bytes) {
+    auto const& steps = executable->result.plan.steps;
+    if (step < 0 || step >= static_cast<int64_t>(steps.size()))
+        return report(import::Status::failure(import::ErrorCode::kInvalidArgument, "step", "step index out of range"));
+    auto const& s = steps[static_cast<size_t>(step)];
+    if (label && label_capacity) {
+        size_t n = std::min(label_capacity - 1, s.label.size());
+        std::memcpy(label, s.label.data(), n);
+        label[n] = '\0';
+    }
+    if (op) *op = static_cast<int32_t>(s.op);
+    if (kernel) *kernel = s.kernel;
+    if (launches) *launches = s.launches;
+    if (bound_bytes) {
+        // bytes of every tensor bound to this launch, each counted once
+        uint64_t total = 0;
+        std::vector<std::pair<int, int64_t>> seen;
+        for (auto const& binding : s.tensors) {
+            if (binding.kind == compiler::TensorBinding::Kind::kAbsent) continue;
+            std::pair<int, int64_t> key{static_cast<int>(binding.kind), binding.uid};
+            if (std::find(seen.begin(), seen.end(), key) != seen.end()) continue;
+            seen.push_back(key);
+            if (binding.kind == compiler::TensorBinding::Kind::kArgument) {
+                for (auto const& argument : executable->result.metadata.arguments)
+                    if (argument.uid == binding.uid) total += argument.size_bytes;
+            } else {
+                for (auto const& allocation : executable->result.workspace.allocations)
+                    if (allocation.offset == binding.offset && allocation.name.rfind("scratch.", 0) != 0) { total += allocation.size_bytes; break; }
+            }
+        }
+        *bound_bytes = total;
+    }
+    return 0;
+}
+
+extern "C" int df_execute_steps(const df_executable* executable, int64_t first, int64_t last, const int64_t* uids, void* const* pointers,
+                                size_t count, void* workspace) {
+    runtime::VariantPack pack;
+    pack.reserve(count);
+    for (size_t i = 0; i < count; ++i) pack[uids[i]] = pointers[i];
+    return report(executable->result.executable->execute_steps(first, last, pack, workspace));
+}
+
+extern "C" int df_plan_workspace(size_t count, const char* const* names, const uint64_t* sizes, const uint64_t* alignments, const uint64_t* live_starts,
+                                 const uint64_t* live_ends, uint64_t* offsets, int64_t* placement_order, uint64_t* total_bytes) {
+    std::vector<compiler::WorkspaceRequest> requests(count);
+    for (size_t i = 0; i < count; ++i) requests[i] = {names[i], sizes[i], alignments[i], live_starts[i], live_ends[i]};
+    compiler::WorkspacePlan plan;
+    auto status = compiler::plan_workspace(requests, plan);
+    if (status.is_bad()) return report(status);
+    for (size_t order = 0; order < plan.allocations.size(); ++order)
+        for (size_t i = 0; i < count; ++i)
+            if (plan.allocations[order].name == names[i]) {
+                offsets[i] = plan.allocations[order].offset;
+                if (placement_order) placement_order[i] = static_cast<int64_t>(order);
+            }
+    if (total_bytes) *total_bytes = plan.size_bytes;
+    return 0;
+}

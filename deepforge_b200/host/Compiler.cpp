@@ -1,0 +1,751 @@
+// compile_graph: graph analysis, GPU kernel selection and workspace planning.
+//
+// Takes the place of the reference's compile_graph (lib/Compiler/Compiler.cpp:367) for
+// the hot-path tags: where the reference builds an MLIR module and emits x86 objects,
+// this lowers each node (or fused group of nodes) to one launch through the dfgpu C
+// ABI. The analysis keeps the reference's contract (lib/Compiler/FoundationalGraph.cpp
+// :1705-2136): argument table in ascending UID order, alignment = clamp(element bytes,
+// 1, 8), size_bytes = storage span, one workspace request per materialised virtual
+// tensor with lifetime [producer, last consumer].
+#include "DeepForge/Compiler/Codegen.h"
+
+#include "Internal.h"
+
+#include <algorithm>
+#include <cfloat>
+#include <cmath>
+#include <map>
+#include <optional>
+#include <set>
+#include <sstream>
+
+namespace deepforge::compiler {
+namespace {
+
+using import::AttributeValue;
+using import::DataType;
+using import::ErrorCode;
+using import::OperationDesc;
+using import::OperationTag;
+using import::SerializedGraph;
+using import::Status;
+using import::TensorDesc;
+
+Status fail(ErrorCode code, std::string_view subject, std::string_view detail) { return Status::failure(code, subject, detail); }
+
+// ---- attribute access ------------------------------------------------------------------
+
+AttributeValue const* attribute(OperationDesc const& node, char const* key) {
+    auto it = node.attributes.find(key);
+    return it == node.attributes.end() ? nullptr : &it->second;
+}
+bool is_null(OperationDesc const& node, char const* key) {
+    auto const* value = attribute(node, key);
+    return value == nullptr || std::holds_alternative<std::monostate>(*value);
+}
+std::optional<std::int64_t> get_int(OperationDesc const& node, char const* key) {
+    auto const* value = attribute(node, key);
+    if (value && std::holds_alternative<std::int64_t>(*value)) return std::get<std::int64_t>(*value);
+    return std::nullopt;
+}
+std::optional<double> get_number(OperationDesc const& node, char const* key) {
+    auto const* value = attribute(node, key);
+    if (!value) return std::nullopt;
+    if (std::holds_alternative<std::int64_t>(*value)) return static_cast<double>(std::get<std::int64_t>(*value));
+    if (std::holds_alternative<double>(*value)) return std::get<double>(*value);
+    return std::nullopt;
+}
+std::optional<bool> get_bool(OperationDesc const& node, char const* key) {
+    auto const* value = attribute(node, key);
+    if (value && std::holds_alternative<bool>(*value)) return std::get<bool>(*value);
+    return std::nullopt;
+}
+std::optional<std::string> get_string(OperationDesc const& node, char const* key) {
+    auto const* value = attribute(node, key);
+    if (value && std::holds_alternative<std::string>(*value)) return std::get<std::string>(*value);
+    return std::nullopt;
+}
+std::optional<std::vector<std::int64_t>> get_int_array(OperationDesc const& node, char const* key) {
+    auto const* value = attribute(node, key);
+    if (value && std::holds_alternative<std::vector<std::int64_t>>(*value)) return std::get<std::vector<std::int64_t>>(*value);
+    return std::nullopt;
+}
+
+std::optional<std::int64_t> port(std::map<std::string, std::int64_t> const& ports, char const* name) {
+    auto it = ports.find(name);
+    if (it == ports.end()) return std::nullopt;
+    return it->second;
+}
+
+// ---- tensors -----------------------------------------------------------------------------
+
+std::optional<int> to_dfgpu_dtype(DataType type) {
+    switch (type) {
+        case DataType::kFloat32: return DFGPU_F32;
+        case DataType::kFloat16: return DFGPU_F16;
+        case DataType::kBFloat16: return DFGPU_BF16;
+        case DataType::kFp8E4M3: return DFGPU_E4M3;
+        case DataType::kFp8E8M0: return DFGPU_E8M0;
+        case DataType::kInt32: return DFGPU_I32;
+        default: return std::nullopt;
+    }
+}
+
+struct Lowering {
+    SerializedGraph const& graph;
+    CompileOptions const& options;
+    std::map<std::int64_t, int> producer;                       // uid -> node index
+    std::map<std::int64_t, std::vector<std::size_t>> consumers;  // uid -> node indices
+    std::map<std::int64_t, int> storage_override;                // virtual uid -> dfgpu dtype
+    std::vector<int> absorbed_into;                              // node -> anchor node, or -1
+    KernelPlan plan;
+
+    explicit Lowering(SerializedGraph const& g, CompileOptions const& o) : graph(g), options(o), absorbed_into(g.nodes.size(), -1) {}
+
+    TensorDesc const& tensor(std::int64_t uid) const { return graph.tensors.at(uid); }
+
+    Status describe(std::int64_t uid, dfgpu_tensor& out, std::string const& where) const {
+        auto const& t = tensor(uid);
+        auto dtype = to_dfgpu_dtype(t.data_type);
+        if (!dtype) return fail(ErrorCode::kUnsupportedDataType, where, "tensor '" + t.name + "' has data type " + std::string(import::data_type_name(t.data_type)) + ", which this backend does not execute");
+        if (t.dim.size() > DFGPU_MAX_RANK) return fail(ErrorCode::kInvalidShape, where, "tensor rank above 8");
+        out = dfgpu_tensor{};
+        auto narrowed = storage_override.find(uid);
+        out.dtype = narrowed != storage_override.end() ? narrowed->second : *dtype;
+        out.rank = static_cast<std::int32_t>(t.dim.size());
+        out.reorder = t.reordering_type == "F8_128x4" ? DFGPU_REORDER_F8_128x4 : DFGPU_REORDER_NONE;
+        for (std::size_t i = 0; i < t.dim.size(); ++i) {
+            out.dim[i] = t.dim[i];
+            out.stride[i] = t.stride[i];
+        }
+        return Status::ok();
+    }
+
+    TensorBinding bind(std::int64_t uid) const {
+        TensorBinding binding;
+        binding.kind = tensor(uid).is_virtual ? TensorBinding::Kind::kWorkspace : TensorBinding::Kind::kArgument;
+        binding.uid = uid;
+        return binding;
+    }
+
+    bool single_consumer(std::int64_t uid, std::size_t& node) const {
+        auto it = consumers.find(uid);
+        if (it == consumers.end() || it->second.size() != 1) return false;
+        node = it->second.front();
+        return true;
+    }
+
+    // Is `uid` ready before node `anchor` runs (a graph input, or written by an earlier node)?
+    bool available_before(std::int64_t uid, std::size_t anchor) const {
+        auto it = producer.find(uid);
+        return it == producer.end() || static_cast<std::size_t>(it->second) < anchor;
+    }
+};
+
+std::string node_path(std::size_t index, OperationDesc const& node) {
+    return "nodes[" + std::to_string(index) + "] " + std::string(import::operation_tag_name(node.tag)) + " '" + node.name + "'";
+}
+
+Status require_float_compute(OperationDesc const& node, std::string const& where) {
+    auto compute = get_string(node, "compute_data_type");
+    if (!compute || *compute != "FLOAT") return fail(ErrorCode::kUnsupportedOperation, where, "compute_data_type must be FLOAT");
+    return Status::ok();
+}
+
+// POINTWISE node -> (mode, relu parameters)
+Status pointwise_mode(OperationDesc const& node, std::string const& where, int& mode, float& lower, float& upper, float& slope) {
+    auto name = get_string(node, "mode");
+    if (!name) return fail(ErrorCode::kInvalidValue, where, "mode must be a string");
+    if (*name == "ADD") mode = DFGPU_PW_ADD;
+    else if (*name == "MUL") mode = DFGPU_PW_MUL;
+    else if (*name == "SUB") mode = DFGPU_PW_SUB;
+    else if (*name == "RELU_FWD") mode = DFGPU_PW_RELU_FWD;
+    else if (*name == "IDENTITY") mode = DFGPU_PW_IDENTITY;
+    else return fail(ErrorCode::kUnsupportedOperation, where, "pointwise mode " + *name + " is outside the GPU hot path");
+    lower = static_cast<float>(get_number(node, "relu_lower_clip").value_or(0.0));
+    upper = static_cast<float>(get_number(node, "relu_upper_clip").value_or(static_cast<double>(FLT_MAX)));
+    slope = static_cast<float>(get_number(node, "relu_lower_clip_slope").value_or(0.0));
+    for (auto key : {"swish_beta", "elu_alpha", "softplus_beta"})
+        if (!is_null(node, key)) return fail(ErrorCode::kUnsupportedOperation, where, std::string(key) + " is not used by any executable mode");
+    return Status::ok();
+}
+
+bool broadcasts_onto(TensorDesc const& small, TensorDesc const& big) {
+    if (small.dim.size() > big.dim.size()) return false;
+    std::size_t shift = big.dim.size() - small.dim.size();
+    for (std::size_t i = 0; i < small.dim.size(); ++i)
+        if (small.dim[i] != 1 && small.dim[i] != big.dim[i + shift]) return false;
+    return true;
+}
+
+// Walk the chain of single-consumer POINTWISE nodes hanging off `value` and absorb ADD /
+// RELU_FWD steps into the contraction at `anchor`. Returns the UID finally written.
+Status absorb_epilogue(Lowering& low, std::size_t anchor, std::int64_t value, dfgpu_epilogue_step* steps, std::int32_t& count,
+                       dfgpu_tensor* extra, std::vector<std::int64_t>& extra_uids, std::vector<std::size_t>& nodes, std::string& label,
+                       std::int64_t& final_uid) {
+    final_uid = value;
+    count = 0;
+    if (!low.options.fuse) return Status::ok();
+    for (;;) {
+        auto const& current = low.tensor(final_uid);
+        std::size_t next = 0;
+        if (!current.is_virtual || !low.single_consumer(final_uid, next) || count >= DFGPU_MAX_EPILOGUE) break;
+        auto const& node = low.graph.nodes[next];
+        if (node.tag != OperationTag::kPointwise || low.absorbed_into[next] >= 0) break;
+        int mode = 0;
+        float lower = 0, upper = 0, slope = 0;
+        if (pointwise_mode(node, "", mode, lower, upper, slope).is_bad()) break;
+        auto in0 = port(node.inputs, "IN_0"), in1 = port(node.inputs, "IN_1"), out = port(node.outputs, "OUT_0");
+        if (!in0 || !out || port(node.inputs, "IN_2")) break;
+        auto const& out_tensor = low.tensor(*out);
+        if (out_tensor.dim != current.dim) break;
+        dfgpu_epilogue_step step{};
+        if (mode == DFGPU_PW_RELU_FWD) {
+            if (*in0 != final_uid || in1) break;
+            step.op = DFGPU_EPI_RELU;
+            step.relu_lower = lower;
+            step.relu_upper = upper;
+            step.relu_slope = slope;
+        } else if (mode == DFGPU_PW_ADD) {
+            if (!in1 || (*in0 != final_uid && *in1 != final_uid) || *in0 == *in1) break;
+            std::int64_t other = *in0 == final_uid ? *in1 : *in0;
+            if (extra_uids.size() >= 2 || !low.available_before(other, anchor) || !broadcasts_onto(low.tensor(other), out_tensor)) break;
+            auto other_type = low.tensor(other).data_type;
+            if (other_type != DataType::kFloat32 && other_type != DataType::kBFloat16 && other_type != DataType::kFloat16) break;
+            dfgpu_tensor described;
+            if (low.describe(other, described, "").is_bad()) break;
+            step.op = DFGPU_EPI_ADD;
+            step.operand = static_cast<std::int32_t>(extra_uids.size());
+            extra[extra_uids.size()] = described;
+            extra_uids.push_back(other);
+        } else {
+            break;
+        }
+        steps[count++] = step;
+        low.absorbed_into[next] = static_cast<int>(anchor);
+        nodes.push_back(next);
+        label += "+" + node.name;
+        final_uid = *out;
+    }
+    return Status::ok();
+}
+
+Status lower_conv(Lowering& low, std::size_t index) {
+    auto const& node = low.graph.nodes[index];
+    auto const where = node_path(index, node);
+    auto status = require_float_compute(node, where);
+    if (status.is_bad()) return status;
+    auto x = port(node.inputs, "X"), w = port(node.inputs, "W"), y = port(node.outputs, "Y");
+    if (!x || !w || !y || node.inputs.size() != 2 || node.outputs.size() != 1)
+        return fail(ErrorCode::kInvalidValue, where, "convolution ports are incomplete");
+    auto mode = get_string(node, "math_mode");
+    if (!mode || (*mode != "CROSS_CORRELATION" && *mode != "CONVOLUTION")) return fail(ErrorCode::kInvalidValue, where, "math_mode must be CROSS_CORRELATION or CONVOLUTION");
+    auto pre = get_int_array(node, "pre_padding"), post = get_int_array(node, "post_padding"), stride = get_int_array(node, "stride"),
+         dilation = get_int_array(node, "dilation");
+    if (!pre || !post || !stride || !dilation) return fail(ErrorCode::kInvalidValue, where, "padding, stride and dilation must be integer arrays");
+    auto const rank = low.tensor(*x).dim.size();
+    if (rank < 3 || rank > 5 || low.tensor(*w).dim.size() != rank || low.tensor(*y).dim.size() != rank || pre->size() != rank - 2 ||
+        post->size() != rank - 2 || stride->size() != rank - 2 || dilation->size() != rank - 2)
+        return fail(ErrorCode::kInvalidShape, where, "convolution requires matching rank 3-5 tensors and spatial attributes");
+    if (rank != 4) return fail(ErrorCode::kUnsupportedOperation, where, "only 2-D (rank-4) convolutions are executable on this backend");
+
+    KernelStep step;
+    step.op = KernelOp::kConvFprop;
+    step.label = node.name;
+    step.nodes = {index};
+    dfgpu_conv_params params{};
+    for (int i = 0; i < 2; ++i) {
+        params.pre_pad[i] = (*pre)[i];
+        params.post_pad[i] = (*post)[i];
+        params.stride[i] = (*stride)[i];
+        params.dilation[i] = (*dilation)[i];
+    }
+    params.reverse_filter = *mode == "CONVOLUTION";
+    std::vector<std::int64_t> extras;
+    std::int64_t final_uid = *y;
+    status = absorb_epilogue(low, index, *y, params.epilogue, params.epilogue_count, params.extra, extras, step.nodes, step.label, final_uid);
+    if (status.is_bad()) return status;
+    if ((status = low.describe(*x, params.x, where)).is_bad()) return status;
+    if ((status = low.describe(*w, params.w, where)).is_bad()) return status;
+    if ((status = low.describe(final_uid, params.y, where)).is_bad()) return status;
+    if (low.tensor(final_uid).dim != low.tensor(*y).dim) return fail(ErrorCode::kInvalidShape, where, "fused output shape differs from the convolution output");
+    if (low.options.disable_tensor_cores) params.kernel = low.tensor(*x).dim[1] == low.tensor(*w).dim[1] ? DFGPU_CONV_IGEMM_FFMA : DFGPU_CONV_DIRECT;
+    step.tensors = {low.bind(*x), low.bind(*w), low.bind(final_uid), TensorBinding{}, TensorBinding{}};
+    for (std::size_t i = 0; i < extras.size(); ++i) step.tensors[3 + i] = low.bind(extras[i]);
+    step.params = params;
+    low.plan.steps.push_back(std::move(step));
+    return Status::ok();
+}
+
+// BLOCK_SCALE_DEQUANTIZE feeding only this MATMUL operand -> read codes and scales directly.
+bool try_absorb_dequantize(Lowering& low, std::size_t matmul_index, std::int64_t operand_uid, dfgpu_tensor& operand, dfgpu_tensor& scale,
+                           std::int64_t* block, std::int64_t& codes_uid, std::int64_t& scale_uid, std::size_t& dequant_index) {
+    if (!low.options.fuse) return false;
+    auto const& t = low.tensor(operand_uid);
+    auto producer = low.producer.find(operand_uid);
+    std::size_t only = 0;
+    if (!t.is_virtual || producer == low.producer.end() || !low.single_consumer(operand_uid, only) || only != matmul_index) return false;
+    auto const& node = low.graph.nodes[producer->second];
+    if (node.tag != OperationTag::kBlockScaleDequantize) return false;
+    auto x = port(node.inputs, "X"), s = port(node.inputs, "scale");
+    auto blocks = get_int_array(node, "block_size");
+    if (!x || !s || !blocks || blocks->empty() || blocks->size() > 2) return false;
+    auto const& codes = low.tensor(*x);
+    auto const& scales = low.tensor(*s);
+    if (codes.data_type != DataType::kFp8E4M3 || scales.data_type != DataType::kFp8E8M0 || scales.reordering_type != "NONE") return false;
+    if (codes.dim != t.dim || scales.dim.size() != t.dim.size() || t.dim.size() < 2) return false;
+    if (low.describe(*x, operand, "").is_bad() || low.describe(*s, scale, "").is_bad()) return false;
+    block[0] = blocks->size() == 2 ? (*blocks)[0] : 1;
+    block[1] = blocks->back();
+    if (block[0] <= 0 || block[1] <= 0) return false;
+    codes_uid = *x;
+    scale_uid = *s;
+    dequant_index = static_cast<std::size_t>(producer->second);
+    return true;
+}
+
+Status lower_matmul(Lowering& low, std::size_t index) {
+    auto const& node = low.graph.nodes[index];
+    auto const where = node_path(index, node);
+    auto status = require_float_compute(node, where);
+    if (status.is_bad()) return status;
+    auto a = port(node.inputs, "A"), b = port(node.inputs, "B"), c = port(node.outputs, "C");
+    if (!a || !b || !c) return fail(ErrorCode::kInvalidValue, where, "matmul ports are incomplete");
+    for (auto name : {"M_override", "N_override", "K_override"})
+        if (port(node.inputs, name)) return fail(ErrorCode::kUnsupportedOperation, where, "extent override tensors are not executable on this backend");
+    KernelStep step;
+    step.op = KernelOp::kMatmul;
+    step.label = node.name;
+    step.nodes = {index};
+    dfgpu_matmul_params params{};
+    std::int64_t a_uid = *a, b_uid = *b, a_scale_uid = 0, b_scale_uid = 0;
+    bool a_fused = false, b_fused = false;
+    std::size_t dequant = 0;
+    if (try_absorb_dequantize(low, index, *a, params.a, params.a_scale, params.a_block, a_uid, a_scale_uid, dequant)) {
+        a_fused = true;
+        low.absorbed_into[dequant] = static_cast<int>(index);
+        step.nodes.push_back(dequant);
+        step.label = low.graph.nodes[dequant].name + "+" + step.label;
+    } else if ((status = low.describe(*a, params.a, where)).is_bad()) {
+        return status;
+    }
+    if (try_absorb_dequantize(low, index, *b, params.b, params.b_scale, params.b_block, b_uid, b_scale_uid, dequant)) {
+        b_fused = true;
+        low.absorbed_into[dequant] = static_cast<int>(index);
+        step.nodes.push_back(dequant);
+        step.label = low.graph.nodes[dequant].name + "+" + step.label;
+    } else if ((status = low.describe(*b, params.b, where)).is_bad()) {
+        return status;
+    }
+    std::vector<std::int64_t> extras;
+    std::int64_t final_uid = *c;
+    status = absorb_epilogue(low, index, *c, params.epilogue, params.epilogue_count, params.extra, extras, step.nodes, step.label, final_uid);
+    if (status.is_bad()) return status;
+    if ((status = low.describe(final_uid, params.c, where)).is_bad()) return status;
+    if (low.options.disable_tensor_cores) params.kernel = DFGPU_MATMUL_FFMA;
+    step.tensors = {low.bind(a_uid), low.bind(b_uid), low.bind(final_uid), TensorBinding{}, TensorBinding{}, TensorBinding{}, TensorBinding{}};
+    if (a_fused) step.tensors[3] = low.bind(a_scale_uid);
+    if (b_fused) step.tensors[4] = low.bind(b_scale_uid);
+    for (std::size_t i = 0; i < extras.size(); ++i) step.tensors[5 + i] = low.bind(extras[i]);
+    step.params = params;
+    low.plan.steps.push_back(std::move(step));
+    return Status::ok();
+}
+
+Status lower_pointwise(Lowering& low, std::size_t index) {
+    auto const& node = low.graph.nodes[index];
+    auto const where = node_path(index, node);
+    auto status = require_float_compute(node, where);
+    if (status.is_bad()) return status;
+    dfgpu_pointwise_params params{};
+    if ((status = pointwise_mode(node, where, params.mode, params.relu_lower, params.relu_upper, params.relu_slope)).is_bad()) return status;
+    auto in0 = port(node.inputs, "IN_0"), in1 = port(node.inputs, "IN_1"), out = port(node.outputs, "OUT_0");
+    bool binary = params.mode == DFGPU_PW_ADD || params.mode == DFGPU_PW_MUL || params.mode == DFGPU_PW_SUB;
+    if (!in0 || !out || binary != in1.has_value() || port(node.inputs, "IN_2"))
+        return fail(ErrorCode::kInvalidValue, where, "pointwise input count does not match the mode");
+    if ((status = low.describe(*in0, params.in0, where)).is_bad()) return status;
+    if (binary && (status = low.describe(*in1, params.in1, where)).is_bad()) return status;
+    if ((status = low.describe(*out, params.out, where)).is_bad()) return status;
+    KernelStep step;
+    step.op = KernelOp::kPointwise;
+    step.label = node.name;
+    step.nodes = {index};
+    step.tensors = {low.bind(*in0), binary ? low.bind(*in1) : TensorBinding{}, low.bind(*out)};
+    step.params = params;
+    low.plan.steps.push_back(std::move(step));
+    return Status::ok();
+}
+
+Status lower_quantize(Lowering& low, std::size_t index) {
+    auto const& node = low.graph.nodes[index];
+    auto const where = node_path(index, node);
+    auto status = require_float_compute(node, where);
+    if (status.is_bad()) return status;
+    auto x = port(node.inputs, "X"), y = port(node.outputs, "Y"), scale = port(node.outputs, "scale");
+    if (!x || !y || !scale) return fail(ErrorCode::kInvalidValue, where, "block-scale quantize ports are incomplete");
+    auto block = get_int(node, "block_size");
+    if (!block || *block <= 0) return fail(ErrorCode::kInvalidValue, where, "block_size must be a positive integer");
+    dfgpu_bsq_params params{};
+    params.block_size = *block;
+    auto axis = get_int(node, "axis");
+    if (!axis && !is_null(node, "axis")) return fail(ErrorCode::kInvalidValue, where, "axis must be an integer or null");
+    params.axis = axis ? static_cast<std::int32_t>(*axis) : -1;
+    if (axis && (*axis < 0 || *axis >= static_cast<std::int64_t>(low.tensor(*x).dim.size()))) return fail(ErrorCode::kInvalidValue, where, "axis is out of range");
+    if ((status = low.describe(*x, params.x, where)).is_bad()) return status;
+    if ((status = low.describe(*y, params.y, where)).is_bad()) return status;
+    if ((status = low.describe(*scale, params.scale, where)).is_bad()) return status;
+    KernelStep step;
+    step.op = KernelOp::kBlockScaleQuantize;
+    step.label = node.name;
+    step.nodes = {index};
+    step.tensors = {low.bind(*x), low.bind(*y), low.bind(*scale)};
+    step.params = params;
+    low.plan.steps.push_back(std::move(step));
+    return Status::ok();
+}
+
+Status lower_dequantize(Lowering& low, std::size_t index) {
+    auto const& node = low.graph.nodes[index];
+    auto const where = node_path(index, node);
+    auto status = require_float_compute(node, where);
+    if (status.is_bad()) return status;
+    auto x = port(node.inputs, "X"), scale = port(node.inputs, "scale"), y = port(node.outputs, "Y");
+    if (!x || !y || !scale) return fail(ErrorCode::kInvalidValue, where, "block-scale dequantize ports are incomplete");
+    auto blocks = get_int_array(node, "block_size");
+    if (!blocks || blocks->empty() || blocks->size() > DFGPU_MAX_RANK) return fail(ErrorCode::kInvalidValue, where, "block_size must be a non-empty integer array");
+    if (!get_bool(node, "is_negative_scale")) return fail(ErrorCode::kInvalidValue, where, "is_negative_scale must be a boolean");
+    dfgpu_bsd_params params{};
+    params.block_count = static_cast<std::int32_t>(blocks->size());
+    for (std::size_t i = 0; i < blocks->size(); ++i) params.block[i] = (*blocks)[i];
+    if ((status = low.describe(*x, params.x, where)).is_bad()) return status;
+    if ((status = low.describe(*scale, params.scale, where)).is_bad()) return status;
+    if ((status = low.describe(*y, params.y, where)).is_bad()) return status;
+    KernelStep step;
+    step.op = KernelOp::kBlockScaleDequantize;
+    step.label = node.name;
+    step.nodes = {index};
+    step.tensors = {low.bind(*x), low.bind(*scale), low.bind(*y)};
+    step.params = params;
+    low.plan.steps.push_back(std::move(step));
+    return Status::ok();
+}
+
+Status lower_sdpa(Lowering& low, std::size_t index) {
+    auto const& node = low.graph.nodes[index];
+    auto const where = node_path(index, node);
+    for (auto name : {"Attn_scale", "Bias", "Seed", "Offset", "Dropout_mask", "Dropout_scale", "Block_mask", "Descale_Q", "Descale_K", "Descale_V",
+                      "Descale_S", "Scale_S", "Scale_O", "SINK_TOKEN"})
+        if (port(node.inputs, name)) return fail(ErrorCode::kUnsupportedOperation, where, std::string("input port ") + name + " is outside the GPU hot path");
+    for (auto name : {"RNG_DUMP", "Amax_S", "Amax_O"})
+        if (port(node.outputs, name)) return fail(ErrorCode::kUnsupportedOperation, where, std::string("output port ") + name + " is outside the GPU hot path");
+    auto q = port(node.inputs, "Q"), k = port(node.inputs, "K"), v = port(node.inputs, "V"), o = port(node.outputs, "O");
+    if (!q || !k || !v || !o) return fail(ErrorCode::kInvalidValue, where, "SDPA ports are incomplete");
+    if (get_bool(node, "alibi_mask").value_or(true)) return fail(ErrorCode::kUnsupportedOperation, where, "alibi_mask is outside the GPU hot path");
+    if (!is_null(node, "dropout_probability")) return fail(ErrorCode::kUnsupportedOperation, where, "dropout is outside the GPU hot path");
+    if (get_bool(node, "is_mxfp8").value_or(true)) return fail(ErrorCode::kUnsupportedOperation, where, "is_mxfp8 must be false");
+    auto padding = get_bool(node, "padding_mask"), stats_flag = get_bool(node, "generate_stats");
+    if (!padding || !stats_flag) return fail(ErrorCode::kInvalidValue, where, "padding_mask and generate_stats must be booleans");
+    auto stats = port(node.outputs, "Stats"), max = port(node.outputs, "Max"), sum_exp = port(node.outputs, "Sum_exp");
+    if (*stats_flag != stats.has_value()) return fail(ErrorCode::kInvalidValue, where, "generate_stats must be set exactly when the Stats output is present");
+    auto alignment = get_string(node, "diagonal_alignment");
+    if (!alignment || (*alignment != "TOP_LEFT" && *alignment != "BOTTOM_RIGHT")) return fail(ErrorCode::kInvalidValue, where, "diagonal_alignment must be TOP_LEFT or BOTTOM_RIGHT");
+
+    dfgpu_sdpa_params params{};
+    Status status = Status::ok();
+    if ((status = low.describe(*q, params.q, where)).is_bad()) return status;
+    if ((status = low.describe(*k, params.k, where)).is_bad()) return status;
+    if ((status = low.describe(*v, params.v, where)).is_bad()) return status;
+    if ((status = low.describe(*o, params.o, where)).is_bad()) return status;
+    if (stats && (status = low.describe(*stats, params.stats, where)).is_bad()) return status;
+    if (max && (status = low.describe(*max, params.max, where)).is_bad()) return status;
+    if (sum_exp && (status = low.describe(*sum_exp, params.sum_exp, where)).is_bad()) return status;
+    auto seq_q = port(node.inputs, "SEQ_LEN_Q"), seq_kv = port(node.inputs, "SEQ_LEN_KV");
+    auto table_k = port(node.inputs, "Page_table_K"), table_v = port(node.inputs, "Page_table_V");
+    if (*padding != (seq_q.has_value() && seq_kv.has_value()) || seq_q.has_value() != seq_kv.has_value())
+        return fail(ErrorCode::kInvalidValue, where, "padding_mask requires both SEQ_LEN_Q and SEQ_LEN_KV, and only then");
+    if ((table_k || table_v) && !*padding) return fail(ErrorCode::kInvalidValue, where, "paged K/V requires padding_mask with sequence lengths");
+    if (seq_q && (status = low.describe(*seq_q, params.seq_q, where)).is_bad()) return status;
+    if (seq_kv && (status = low.describe(*seq_kv, params.seq_kv, where)).is_bad()) return status;
+    if (table_k && (status = low.describe(*table_k, params.page_table_k, where)).is_bad()) return status;
+    if (table_v && (status = low.describe(*table_v, params.page_table_v, where)).is_bad()) return status;
+    if (params.q.rank != 4 || params.k.rank != 4 || params.v.rank != 4) return fail(ErrorCode::kInvalidShape, where, "Q, K and V must have rank 4");
+    params.attn_scale = static_cast<float>(get_number(node, "attn_scale_value").value_or(1.0));
+    params.padding_mask = *padding;
+    if (auto bound = get_int(node, "left_bound")) {
+        params.has_left_bound = 1;
+        params.left_bound = *bound;
+    } else if (!is_null(node, "left_bound")) {
+        return fail(ErrorCode::kInvalidValue, where, "left_bound must be an integer or null");
+    }
+    if (auto bound = get_int(node, "right_bound")) {
+        params.has_right_bound = 1;
+        params.right_bound = *bound;
+    } else if (!is_null(node, "right_bound")) {
+        return fail(ErrorCode::kInvalidValue, where, "right_bound must be an integer or null");
+    }
+    params.bottom_right = *alignment == "BOTTOM_RIGHT";
+    // logical key/value length: max_seq_len_kv when given, else the container/table capacity
+    auto max_len = get_int(node, "max_seq_len_kv");
+    std::int64_t capacity_k = table_k ? params.page_table_k.dim[2] * params.k.dim[2] : params.k.dim[2];
+    std::int64_t capacity_v = table_v ? params.page_table_v.dim[2] * params.v.dim[2] : params.v.dim[2];
+    params.s_kv = max_len ? *max_len : std::min(capacity_k, capacity_v);
+    if (params.s_kv <= 0 || params.s_kv > capacity_k || params.s_kv > capacity_v)
+        return fail(ErrorCode::kInvalidShape, where, "key/value capacity is below the logical sequence length");
+    KernelStep step;
+    step.op = KernelOp::kSdpaForward;
+    step.label = node.name;
+    step.nodes = {index};
+    auto optional_binding = [&](std::optional<std::int64_t> uid) { return uid ? low.bind(*uid) : TensorBinding{}; };
+    step.tensors = {low.bind(*q), low.bind(*k), low.bind(*v), low.bind(*o), optional_binding(stats), optional_binding(max), optional_binding(sum_exp),
+                    optional_binding(seq_q), optional_binding(seq_kv), optional_binding(table_k), optional_binding(table_v)};
+    step.params = params;
+    low.plan.steps.push_back(std::move(step));
+    return Status::ok();
+}
+
+bool is_contraction(KernelOp op) { return op == KernelOp::kConvFprop || op == KernelOp::kMatmul; }
+
+dfgpu_tensor* step_output(KernelStep& step) {
+    if (auto* conv = std::get_if<dfgpu_conv_params>(&step.params)) return &conv->y;
+    if (auto* matmul = std::get_if<dfgpu_matmul_params>(&step.params)) return &matmul->c;
+    return nullptr;
+}
+
+// A virtual f32 tensor written by a bf16 contraction and read only by contractions is
+// stored as bf16: the consuming tensor-core kernel would round it to bf16 anyway, and
+// the narrower store halves the traffic of the intermediate.
+void narrow_virtual_tensors(Lowering& low) {
+    if (!low.options.narrow_virtual_tensors || low.options.disable_tensor_cores) return;
+    std::map<std::int64_t, std::vector<std::size_t>> readers;
+    std::map<std::int64_t, std::size_t> writer;
+    for (std::size_t s = 0; s < low.plan.steps.size(); ++s) {
+        auto const& step = low.plan.steps[s];
+        for (std::size_t slot = 0; slot < step.tensors.size(); ++slot) {
+            auto const& binding = step.tensors[slot];
+            if (binding.kind != TensorBinding::Kind::kWorkspace) continue;
+            bool is_output = is_contraction(step.op) ? slot == 2 : false;
+            if (step.op == KernelOp::kPointwise) is_output = slot == 2;
+            if (step.op == KernelOp::kBlockScaleQuantize) is_output = slot >= 1;
+            if (step.op == KernelOp::kBlockScaleDequantize) is_output = slot == 2;
+            if (step.op == KernelOp::kSdpaForward) is_output = slot >= 3 && slot <= 6;
+            if (is_output) writer[binding.uid] = s;
+            else readers[binding.uid].push_back(s);
+        }
+    }
+    for (auto const& [uid, step_index] : writer) {
+        auto& step = low.plan.steps[step_index];
+        if (!is_contraction(step.op) || low.tensor(uid).data_type != DataType::kFloat32) continue;
+        bool bf16_inputs = false;
+        if (auto* conv = std::get_if<dfgpu_conv_params>(&step.params)) bf16_inputs = conv->x.dtype == DFGPU_BF16 && conv->w.dtype == DFGPU_BF16;
+        if (auto* matmul = std::get_if<dfgpu_matmul_params>(&step.params)) bf16_inputs = matmul->a.dtype == DFGPU_BF16 && matmul->b.dtype == DFGPU_BF16;
+        if (!bf16_inputs) continue;
+        bool only_contractions = !readers[uid].empty();
+        for (auto reader : readers[uid]) only_contractions = only_contractions && is_contraction(low.plan.steps[reader].op);
+        if (!only_contractions) continue;
+        low.storage_override[uid] = DFGPU_BF16;
+        step_output(step)->dtype = DFGPU_BF16;
+        for (auto reader : readers[uid]) {
+            auto& consumer = low.plan.steps[reader];
+            for (std::size_t slot = 0; slot < consumer.tensors.size(); ++slot) {
+                if (consumer.tensors[slot].kind != TensorBinding::Kind::kWorkspace || consumer.tensors[slot].uid != uid) continue;
+                if (auto* conv = std::get_if<dfgpu_conv_params>(&consumer.params)) {
+                    if (slot == 0) conv->x.dtype = DFGPU_BF16;
+                    if (slot == 1) conv->w.dtype = DFGPU_BF16;
+                    if (slot >= 3) conv->extra[slot - 3].dtype = DFGPU_BF16;
+                }
+                if (auto* matmul = std::get_if<dfgpu_matmul_params>(&consumer.params)) {
+                    if (slot == 0) matmul->a.dtype = DFGPU_BF16;
+                    if (slot == 1) matmul->b.dtype = DFGPU_BF16;
+                    if (slot >= 5) matmul->extra[slot - 5].dtype = DFGPU_BF16;
+                }
+            }
+        }
+    }
+}
+
+Status query_step(KernelStep& step, std::int64_t& scratch_bytes) {
+    dfgpu_plan_info info{};
+    int code = 0;
+    switch (step.op) {
+        case KernelOp::kBlockScaleQuantize: code = dfgpu_query_block_scale_quantize(&std::get<dfgpu_bsq_params>(step.params), &info); break;
+        case KernelOp::kBlockScaleDequantize: code = dfgpu_query_block_scale_dequantize(&std::get<dfgpu_bsd_params>(step.params), &info); break;
+        case KernelOp::kPointwise: code = dfgpu_query_pointwise(&std::get<dfgpu_pointwise_params>(step.params), &info); break;
+        case KernelOp::kConvFprop: code = dfgpu_query_conv_fprop(&std::get<dfgpu_conv_params>(step.params), &info); break;
+        case KernelOp::kMatmul: code = dfgpu_query_matmul(&std::get<dfgpu_matmul_params>(step.params), &info); break;
+        case KernelOp::kSdpaForward: code = dfgpu_query_sdpa_forward(&std::get<dfgpu_sdpa_params>(step.params), &info); break;
+    }
+    if (code != 0) return Status::failure(static_cast<ErrorCode>(code), step.label, dfgpu_last_error());
+    step.kernel = info.kernel;
+    step.launches = info.launches;
+    scratch_bytes = info.scratch_bytes;
+    return Status::ok();
+}
+
+}  // namespace
+
+char const* kernel_op_name(KernelOp op) {
+    switch (op) {
+        case KernelOp::kBlockScaleQuantize: return "block_scale_quantize";
+        case KernelOp::kBlockScaleDequantize: return "block_scale_dequantize";
+        case KernelOp::kPointwise: return "pointwise";
+        case KernelOp::kConvFprop: return "conv_fprop";
+        case KernelOp::kMatmul: return "matmul";
+        case KernelOp::kSdpaForward: return "sdpa_forward";
+    }
+    return "?";
+}
+
+std::string KernelPlan::to_text() const {
+    std::ostringstream out;
+    for (std::size_t i = 0; i < steps.size(); ++i) {
+        auto const& step = steps[i];
+        out << i << ": " << kernel_op_name(step.op) << " kernel=" << step.kernel << " launches=" << step.launches << " [" << step.label << "]";
+        for (auto const& binding : step.tensors) {
+            if (binding.kind == TensorBinding::Kind::kAbsent) out << " -";
+            else if (binding.kind == TensorBinding::Kind::kArgument) out << " uid" << binding.uid;
+            else out << " ws+" << binding.offset << "(uid" << binding.uid << ")";
+        }
+        if (step.scratch.kind == TensorBinding::Kind::kWorkspace) out << " scratch=ws+" << step.scratch.offset;
+        out << "\n";
+    }
+    return out.str();
+}
+
+Status compile_graph(SerializedGraph const& graph, CompileOptions const& options, CompilationResult& output) {
+    if (graph.nodes.empty()) return fail(ErrorCode::kInvalidValue, "graph", "graph has no nodes");
+    Lowering low(graph, options);
+    for (std::size_t index = 0; index < graph.nodes.size(); ++index) {
+        for (auto const& [name, uid] : graph.nodes[index].inputs) {
+            if (!graph.tensors.count(uid)) return fail(ErrorCode::kMissingUid, node_path(index, graph.nodes[index]), "tensor reference is unresolved");
+            low.consumers[uid].push_back(index);
+        }
+        for (auto const& [name, uid] : graph.nodes[index].outputs) {
+            if (!graph.tensors.count(uid)) return fail(ErrorCode::kMissingUid, node_path(index, graph.nodes[index]), "tensor reference is unresolved");
+            if (low.producer.count(uid)) return fail(ErrorCode::kInvalidValue, node_path(index, graph.nodes[index]), "tensor is produced twice");
+            low.producer[uid] = static_cast<int>(index);
+        }
+    }
+    for (auto const& [uid, tensor] : graph.tensors)
+        if (tensor.is_virtual && !low.producer.count(uid)) return fail(ErrorCode::kInvalidValue, "tensors." + std::to_string(uid), "virtual tensor has no producer");
+
+    // dequantize nodes that a later MATMUL will absorb must not be emitted on their own:
+    // decide that first, by lowering MATMULs' operand fusion lazily in node order.
+    std::vector<std::size_t> order;
+    for (std::size_t index = 0; index < graph.nodes.size(); ++index) order.push_back(index);
+    // First pass: find absorbable dequantize producers.
+    if (options.fuse) {
+        for (std::size_t index = 0; index < graph.nodes.size(); ++index) {
+            if (graph.nodes[index].tag != OperationTag::kMatmul) continue;
+            for (auto name : {"A", "B"}) {
+                auto uid = port(graph.nodes[index].inputs, name);
+                if (!uid) continue;
+                dfgpu_tensor operand{}, scale{};
+                std::int64_t block[2] = {1, 1}, codes = 0, scales = 0;
+                std::size_t dequant = 0;
+                if (try_absorb_dequantize(low, index, *uid, operand, scale, block, codes, scales, dequant)) low.absorbed_into[dequant] = static_cast<int>(index);
+            }
+        }
+    }
+    for (std::size_t index : order) {
+        if (low.absorbed_into[index] >= 0) continue;
+        Status status = Status::ok();
+        switch (graph.nodes[index].tag) {
+            case OperationTag::kConvFprop: status = lower_conv(low, index); break;
+            case OperationTag::kMatmul: status = lower_matmul(low, index); break;
+            case OperationTag::kPointwise: status = lower_pointwise(low, index); break;
+            case OperationTag::kBlockScaleQuantize: status = lower_quantize(low, index); break;
+            case OperationTag::kBlockScaleDequantize: status = lower_dequantize(low, index); break;
+            case OperationTag::kSdpa: status = lower_sdpa(low, index); break;
+        }
+        if (status.is_bad()) return status;
+    }
+    narrow_virtual_tensors(low);
+
+    // argument table: ascending UID, non-virtual tensors only
+    GraphCompileMetadata metadata;
+    metadata.function_name = options.foundational_function_name;
+    for (auto const& [uid, tensor] : graph.tensors) {
+        if (tensor.is_virtual) continue;
+        TensorArgumentMetadata argument;
+        argument.uid = uid;
+        argument.name = tensor.name;
+        argument.data_type = tensor.data_type;
+        argument.dimensions = tensor.dim;
+        argument.strides = tensor.stride;
+        if (!import::tensor_storage_bytes(tensor, argument.size_bytes)) return fail(ErrorCode::kDimensionOverflow, tensor.name, "storage span overflows int64");
+        std::uint64_t element_bytes = std::max<std::uint64_t>(1, import::data_type_storage_bits(tensor.data_type) / 8);
+        argument.alignment = std::clamp<std::uint64_t>(element_bytes, 1, 8);
+        bool read = low.consumers.count(uid) != 0, written = low.producer.count(uid) != 0;
+        argument.access = read && written ? TensorAccess::kReadWrite : (written ? TensorAccess::kWrite : TensorAccess::kRead);
+        metadata.arguments.push_back(std::move(argument));
+    }
+    auto status = validate_graph_compile_metadata(metadata);
+    if (status.is_bad()) return status;
+
+    // kernel queries + workspace requests (lifetimes in plan-step indices)
+    std::vector<WorkspaceRequest> requests;
+    std::map<std::int64_t, std::pair<std::size_t, std::size_t>> lifetime;
+    for (std::size_t s = 0; s < low.plan.steps.size(); ++s) {
+        auto& step = low.plan.steps[s];
+        std::int64_t scratch = 0;
+        if ((status = query_step(step, scratch)).is_bad()) return status;
+        for (auto const& binding : step.tensors) {
+            if (binding.kind != TensorBinding::Kind::kWorkspace) continue;
+            auto it = lifetime.find(binding.uid);
+            if (it == lifetime.end()) lifetime[binding.uid] = {s, s};
+            else it->second.second = s;
+        }
+        if (scratch > 0) {
+            requests.push_back({"scratch." + std::to_string(s), static_cast<std::uint64_t>(scratch), kWorkspaceAlignment, s, s});
+            step.scratch.kind = TensorBinding::Kind::kWorkspace;
+        }
+    }
+    for (auto const& [uid, range] : lifetime) {
+        auto tensor = graph.tensors.at(uid);
+        auto narrowed = low.storage_override.find(uid);
+        if (narrowed != low.storage_override.end()) tensor.data_type = DataType::kBFloat16;
+        std::uint64_t bytes = 0;
+        if (!import::tensor_storage_bytes(tensor, bytes)) return fail(ErrorCode::kDimensionOverflow, tensor.name, "storage span overflows int64");
+        requests.push_back({tensor.name, bytes, kWorkspaceAlignment, range.first, range.second});
+    }
+    WorkspacePlan workspace;
+    if ((status = plan_workspace(requests, workspace)).is_bad()) return status;
+    std::map<std::string, std::uint64_t> offsets;
+    for (auto const& allocation : workspace.allocations) offsets[allocation.name] = allocation.offset;
+    for (std::size_t s = 0; s < low.plan.steps.size(); ++s) {
+        auto& step = low.plan.steps[s];
+        for (auto& binding : step.tensors)
+            if (binding.kind == TensorBinding::Kind::kWorkspace) binding.offset = offsets.at(graph.tensors.at(binding.uid).name);
+        if (step.scratch.kind == TensorBinding::Kind::kWorkspace) step.scratch.offset = offsets.at("scratch." + std::to_string(s));
+    }
+
+    output.metadata = metadata;
+    output.workspace = workspace;
+    output.plan = low.plan;
+    output.executable = runtime::ExecutableFactory::create(metadata, workspace, low.plan);
+    return Status::ok();
+}
+
+Status compile_file(std::filesystem::path const& path, CompileOptions const& options, CompilationResult& output) {
+    import::SerializedGraph graph;
+    import::SerializedGraphImporter importer;
+    auto status = importer.parse_file(path, options.input_format, graph);
+    if (status.is_bad()) return status;
+    return compile_graph(graph, options, output);
+}
+
+Status validate_graph_compile_metadata(GraphCompileMetadata const& metadata) {
+    if (metadata.arguments.empty() || metadata.arguments.size() > 4096) return fail(ErrorCode::kInvalidValue, "metadata", "argument count must be between 1 and 4096");
+    std::set<std::int64_t> uids;
+    for (auto const& argument : metadata.arguments) {
+        if (!uids.insert(argument.uid).second) return fail(ErrorCode::kDuplicateUid, argument.name, "argument UID is used twice");
+        if (argument.name.empty() || argument.name.find('\0') != std::string::npos) return fail(ErrorCode::kInvalidValue, "metadata", "argument names must be non-empty and NUL-free");
+        if (argument.dimensions.empty() || argument.dimensions.size() > 64 || argument.dimensions.size() != argument.strides.size())
+            return fail(ErrorCode::kInvalidShape, argument.name, "rank must be between 1 and 64 with matching strides");
+        if (argument.alignment == 0 || (argument.alignment & (argument.alignment - 1)) != 0 || argument.alignment > 4096)
+            return fail(ErrorCode::kInvalidValue, argument.name, "alignment must be a power of two no greater than 4096");
+    }
+    return Status::ok();
+}
+
+}  // namespace deepforge::compiler

@@ -1,0 +1,42 @@
+// compile_graph / compile_file: serialized graph -> validated metadata, workspace plan,
+// kernel plan and an Executable. Same entry points as the reference's
+// include/DeepForge/Compiler/Codegen.h:52-60; the result carries a kernel plan where
+// the reference carries three x86 objects.
+#pragma once
+
+#include "DeepForge/Compiler/Bufferization.h"
+#include "DeepForge/Compiler/GraphMetadata.h"
+#include "DeepForge/Compiler/KernelPlan.h"
+#include "DeepForge/Import/SerializedGraphImporter.h"
+#include "DeepForge/Runtime/Executable.h"
+
+#include <filesystem>
+#include <memory>
+#include <string>
+
+namespace deepforge::compiler {
+
+struct CompileOptions {
+    std::string foundational_function_name = "deepforge_graph";
+    import::InputFormat input_format = import::InputFormat::kAuto;
+    // Fuse POINTWISE consumers into contraction epilogues and BLOCK_SCALE_DEQUANTIZE
+    // producers into MATMUL operand loads.
+    bool fuse = true;
+    // Store virtual tensors that only feed bf16 tensor-core contractions as bf16.
+    bool narrow_virtual_tensors = true;
+    // Force the CUDA-core kernels (used by tests to cross-check the tcgen05 paths).
+    bool disable_tensor_cores = false;
+};
+
+struct CompilationResult {
+    std::unique_ptr<runtime::Executable> executable;
+    GraphCompileMetadata metadata;
+    WorkspacePlan workspace;
+    KernelPlan plan;
+    std::string target = "sm_100a";
+};
+
+[[nodiscard]] import::Status compile_graph(import::SerializedGraph const& graph, CompileOptions const& options, CompilationResult& output);
+[[nodiscard]] import::Status compile_file(std::filesystem::path const& path, CompileOptions const& options, CompilationResult& output);
+
+}  // namespace deepforge::compiler

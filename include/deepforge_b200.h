@@ -1,0 +1,69 @@
+/*
+ * Flat C API over the C++ host side (importer -> compile_graph -> Executable), for
+ * callers that bind through an FFI (ctypes, cgo, JNI) instead of including the C++
+ * headers. Each function stands for one call of the reference's C++ interface:
+ *   df_compile        SerializedGraphImporter::parse + compiler::compile_graph
+ *                     (include/DeepForge/Import/SerializedGraphImporter.h:22-41,
+ *                      include/DeepForge/Compiler/Codegen.h:52-60)
+ *   df_execute        runtime::Executable::execute (include/DeepForge/Runtime/Executable.h:75-78)
+ *   df_workspace_size runtime::Executable::get_workspace_size (Executable.h:64)
+ * Return values are DeepForge Status codes (0 = DFE_OK); the message of the last
+ * failure on the calling thread is available from df_last_error().
+ */
+#ifndef DEEPFORGE_B200_H
+#define DEEPFORGE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct df_executable df_executable;
+
+enum { DF_FORMAT_AUTO = 0, DF_FORMAT_JSON = 1, DF_FORMAT_UBJSON = 2 };
+enum { DF_OPTION_NO_FUSION = 1, DF_OPTION_NO_NARROWING = 2, DF_OPTION_NO_TENSOR_CORES = 4 };
+
+const char* df_last_error(void);
+
+/* Parse only: validates a serialized graph and reports the tensor and node counts. */
+int df_parse(const uint8_t* document, size_t size, int format, int64_t* tensor_count, int64_t* node_count);
+
+int df_compile(const uint8_t* document, size_t size, int format, uint32_t options, df_executable** out);
+void df_destroy(df_executable* executable);
+
+int64_t df_workspace_size(const df_executable* executable);
+int64_t df_launch_count(const df_executable* executable);
+/* Copies the kernel plan dump (one line per launch) into buffer; returns the full length. */
+size_t df_plan_text(const df_executable* executable, char* buffer, size_t capacity);
+
+/* Argument table (ascending UID). access: 0 read, 1 write, 2 read-write. */
+int64_t df_argument_count(const df_executable* executable);
+int df_argument_info(const df_executable* executable, int64_t index, int64_t* uid, uint64_t* size_bytes,
+                     uint64_t* alignment, int32_t* access);
+
+/* stream: a cudaStream_t (NULL = legacy default stream). */
+void df_set_stream(df_executable* executable, void* stream);
+
+/* uids[i] -> pointers[i] is the variant pack; pointers and workspace are device pointers. */
+int df_execute(const df_executable* executable, void* handle, const int64_t* uids, void* const* pointers, size_t count,
+               void* workspace);
+
+/* Kernel plan introspection and partial execution (used for per-kernel timing): the plan has
+   df_step_count() launches groups; df_execute_steps runs steps [first, last) only. */
+int64_t df_step_count(const df_executable* executable);
+int df_step_info(const df_executable* executable, int64_t step, char* label, size_t label_capacity, int32_t* op, int32_t* kernel,
+                 int32_t* launches, uint64_t* bound_bytes);
+int df_execute_steps(const df_executable* executable, int64_t first, int64_t last, const int64_t* uids, void* const* pointers,
+                     size_t count, void* workspace);
+
+/* Workspace planner on its own: sizes/alignments/live ranges in, offsets + total out. */
+int df_plan_workspace(size_t count, const char* const* names, const uint64_t* sizes, const uint64_t* alignments,
+                      const uint64_t* live_starts, const uint64_t* live_ends, uint64_t* offsets, int64_t* placement_order,
+                      uint64_t* total_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,216 @@
+"""Host side without a GPU: importer protocol rules and error codes, the workspace planner's
+known answers, kernel-selection plans, the argument table and the runtime's variant-pack
+checks (all of which fail before any CUDA call).
+
+Reference behaviour being mirrored:
+  test/Import/SerializedGraphImporterTest.cpp:393-605,806-848  stable error codes per mutation
+  test/Transforms/BufferizationTest.cpp:95-136                placement a@0, c@64, b@0, total 192
+  test/Compiler/CompilerTest.cpp:318-403                      runtime negatives (code 17)
+"""
+import copy
+import json
+
+import pytest
+
+from deepforge_b200 import graphs, runtime
+from deepforge_b200.runtime import DeepForgeError
+
+OK_DOC = graphs.c1_conv(n=1, c=3, h=5, w=5, k=5)
+
+
+def code_of(document, fmt=runtime.FORMAT_AUTO):
+    try:
+        runtime.parse(document, fmt)
+    except DeepForgeError as error:
+        return error.code
+    return 0
+
+
+def mutated(fn):
+    doc = copy.deepcopy(OK_DOC)
+    fn(doc)
+    return doc
+
+
+def test_exports_of_the_host_library():
+    lib = runtime.load()
+    import re
+    from pathlib import Path
+    header = (Path(__file__).resolve().parent.parent / "include" / "deepforge_b200.h").read_text()
+    declared = sorted(set(re.findall(r"\b(df_[a-z_]+)\s*\(", header)))
+    assert declared == sorted(runtime.EXPORTS)
+    for name in declared:
+        assert hasattr(lib, name)
+
+
+def test_accepts_reference_fixture_shape_and_all_five_configs():
+    assert runtime.parse(OK_DOC) == (3, 1)
+    assert runtime.parse(json.dumps(OK_DOC), runtime.FORMAT_JSON) == (3, 1)
+    for doc in (graphs.c2_bottleneck(n=1, h=8, w=8), graphs.c3_quantize_matmul(128, 128, 128), graphs.c4_sdpa(1, 2, 16, 8), graphs.c5_paged_decode(2, 4, 2, 16, 8, 4, 16)):
+        runtime.parse(doc)
+
+
+@pytest.mark.parametrize("mutation,expected", [
+    (lambda d: d.update(json_version="1.1"), 4),
+    (lambda d: d.update(cudnn_frontend_version=12300), 5),
+    (lambda d: d.pop("context"), 6),
+    (lambda d: d["context"].pop("sm_count"), 6),
+    (lambda d: d["context"].update(extra=1), 8),
+    (lambda d: d.update(unknown_top_level=1), 8),
+    (lambda d: d["tensors"]["1"].update(bogus=1), 8),
+    (lambda d: d["tensors"]["1"].pop("stride"), 6),
+    (lambda d: d["tensors"]["1"].update(dim="x"), 7),
+    (lambda d: d["tensors"]["1"].update(data_type="COMPLEX"), 10),
+    (lambda d: d["tensors"]["1"].update(uid=9), 8),                      # key/UID mismatch
+    (lambda d: d["tensors"]["1"].update(uid_assigned=False), 13),
+    (lambda d: d["tensors"]["1"].update(dim=[1, 3, 0, 5]), 15),
+    (lambda d: d["tensors"]["1"].update(dim=[2 ** 40, 2 ** 40, 5, 5]), 16),
+    (lambda d: d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value=1.0), 11),
+    (lambda d: d["tensors"]["1"].update(reordering_type="F16x16"), 8),
+    (lambda d: d["nodes"][0].update(tag="LAYER_NORM"), 9),
+    (lambda d: d["nodes"][0].update(tag="NOT_A_TAG"), 9),
+    (lambda d: d["nodes"][0].pop("math_mode"), 6),
+    (lambda d: d["nodes"][0].update(surprise=True), 8),
+    (lambda d: d["nodes"][0]["inputs"].update(Z=1), 8),
+    (lambda d: d["nodes"][0]["inputs"].update(X=42), 13),
+    (lambda d: d["nodes"][0]["inputs"].update(X="X"), 7),
+    (lambda d: d["nodes"][0]["outputs"].update(Y=1), 8),                 # writes a tensor it reads
+    (lambda d: d["context"].update(is_dynamic_shape_enabled=True), 11),
+    (lambda d: d.update(fe_workspace_size=64), 11),
+    (lambda d: d.update(workspace_modifications={"1": [0, 1, 2]}), 11),
+    (lambda d: d.update(variant_pack_replacements=[[1, 2]]), 11),
+    (lambda d: d.update(variant_pack_uids=[1, 2]), 11),
+    (lambda d: d["tensors"].update({"4": graphs.tensor(4, "Unused", [1])}), 8),
+])
+def test_importer_error_codes(mutation, expected):
+    assert code_of(mutated(mutation)) == expected
+
+
+def test_importer_rejects_broken_encodings_and_sizes():
+    assert code_of(b"") == 1
+    assert code_of(b"{not json", runtime.FORMAT_JSON) == 3
+    assert code_of(json.dumps(OK_DOC) + " trailing", runtime.FORMAT_JSON) == 3
+    assert code_of(b"\x00" * 16, runtime.FORMAT_UBJSON) == 3
+    assert code_of(b" " * (16 * 1024 * 1024 + 1)) == 1
+    assert code_of(b"\xff\xfe\x00garbage") == 3
+
+
+def test_virtual_tensor_consumed_before_produced_is_rejected():
+    doc = graphs.c2_bottleneck(n=1, h=8, w=8)
+    doc["nodes"][0], doc["nodes"][1] = doc["nodes"][1], doc["nodes"][0]
+    assert code_of(doc) == 8
+
+
+def test_workspace_planner_known_answer():
+    plan = runtime.plan_workspace([
+        {"name": "a", "size_bytes": 64, "alignment": 64, "live_start": 0, "live_end": 3},
+        {"name": "b", "size_bytes": 64, "alignment": 64, "live_start": 4, "live_end": 7},
+        {"name": "c", "size_bytes": 96, "alignment": 32, "live_start": 2, "live_end": 5},
+    ])
+    assert plan["order"] == ["a", "c", "b"]
+    assert plan["offsets"] == {"a": 0, "c": 64, "b": 0}
+    assert plan["total"] == 192
+    assert runtime.plan_workspace([{"name": "pad", "size_bytes": 588, "alignment": 64, "live_start": 0, "live_end": 0}])["total"] == 640
+
+
+@pytest.mark.parametrize("requests,expected", [
+    ([{"name": "a", "size_bytes": 8, "alignment": 3, "live_start": 0, "live_end": 1}], 1),
+    ([{"name": "a", "size_bytes": 8, "alignment": 128, "live_start": 0, "live_end": 1}], 1),
+    ([{"name": "a", "size_bytes": 0, "alignment": 8, "live_start": 0, "live_end": 1}], 1),
+    ([{"name": "a", "size_bytes": 8, "alignment": 8, "live_start": 2, "live_end": 1}], 1),
+    ([{"name": "a", "size_bytes": 8, "alignment": 8, "live_start": 0, "live_end": 1}] * 2, 8),
+    ([{"name": "a", "size_bytes": 2 ** 63 - 1, "alignment": 64, "live_start": 0, "live_end": 1}], 16),
+])
+def test_workspace_planner_rejections(requests, expected):
+    with pytest.raises(DeepForgeError) as error:
+        runtime.plan_workspace(requests)
+    assert error.value.code == expected
+
+
+def test_bottleneck_plan_fuses_to_three_launches_and_shares_workspace():
+    exe = runtime.compile_graph(graphs.c2_bottleneck(n=2, h=8, w=8))
+    text = exe.plan_text()
+    assert exe.launch_count == 3
+    assert "[conv1+bias1+relu1]" in text and "[conv2+bias2+relu2]" in text and "[conv3+residual]" in text
+    assert text.count("kernel=3") == 3  # tcgen05 implicit GEMM for all three
+    # two bf16 intermediates of 2*8*8*64 elements, alive at the same time
+    assert exe.workspace_size == 2 * (2 * 8 * 8 * 64 * 2)
+    unfused = runtime.compile_graph(graphs.c2_bottleneck(n=2, h=8, w=8), options=runtime.NO_FUSION)
+    assert unfused.launch_count == 8
+    f32 = runtime.compile_graph(graphs.c2_bottleneck(n=2, h=8, w=8, io="FLOAT"))
+    assert f32.plan_text().count("kernel=2") == 3 and f32.workspace_size == 2 * (2 * 8 * 8 * 64 * 4)
+
+
+def test_quantize_matmul_plan_absorbs_the_dequantize_nodes():
+    exe = runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 128))
+    assert exe.launch_count == 3 and exe.workspace_size == 0
+    assert "dequantize_a" in exe.plan_text() and "dequantize_b" in exe.plan_text()
+    unfused = runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 128), options=runtime.NO_FUSION)
+    assert unfused.launch_count == 5 and unfused.workspace_size == 2 * 128 * 128 * 4
+
+
+def test_argument_table_is_sorted_with_clamped_alignment():
+    exe = runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 128))
+    arguments = exe.arguments()
+    assert [a["uid"] for a in arguments] == [1, 2, 3, 4, 5, 6, 9]
+    by_uid = {a["uid"]: a for a in arguments}
+    assert by_uid[1]["alignment"] == 2 and by_uid[3]["alignment"] == 1 and by_uid[9]["alignment"] == 2
+    assert by_uid[1]["access"] == "read" and by_uid[3]["access"] == "readwrite" and by_uid[9]["access"] == "write"
+    assert by_uid[4]["size_bytes"] == 128 * 4
+    decode = runtime.compile_graph(graphs.c5_paged_decode(2, 4, 2, 128, 8, 64, 256))
+    assert {a["uid"]: a["alignment"] for a in decode.arguments()}[5] == 4
+
+
+@pytest.mark.parametrize("doc_fn,expected", [
+    (lambda: graphs.c4_sdpa(1, 2, 16, 8, io="HALF"), 0),
+    (lambda: _with(graphs.c4_sdpa(1, 2, 16, 8), lambda d: d["nodes"][0].update(alibi_mask=True)), 20),
+    (lambda: _with(graphs.c4_sdpa(1, 2, 16, 8), lambda d: d["nodes"][0].update(dropout_probability=0.1)), 20),
+    (lambda: _with(graphs.c4_sdpa(1, 2, 16, 8), lambda d: d["nodes"][0].update(generate_stats=False)), 8),
+    (lambda: _with(graphs.c2_bottleneck(n=1, h=8, w=8), lambda d: d["nodes"][2].update(mode="GELU_FWD")), 20),
+    (lambda: _with(graphs.c1_conv(n=1, c=3, h=5, w=5, k=5), lambda d: d["tensors"]["3"].update(dim=[1, 5, 4, 5], stride=[100, 1, 25, 5])), 15),
+    (lambda: _with(graphs.c3_quantize_matmul(128, 128, 128), lambda d: d["tensors"]["3"].update(data_type="FP8_E5M2")), 10),
+    (lambda: _with(graphs.c3_quantize_matmul(128, 128, 128), lambda d: d["nodes"][0].update(block_size=24)), 15),
+])
+def test_compile_time_rejections(doc_fn, expected):
+    try:
+        runtime.compile_graph(doc_fn())
+        code = 0
+    except DeepForgeError as error:
+        code = error.code
+    assert code == expected
+
+
+def _with(doc, fn):
+    fn(doc)
+    return doc
+
+
+def test_runtime_rejects_bad_variant_packs_before_any_launch():
+    """Missing UID, null, misaligned, write aliasing, workspace problems: all DFE_INVALID_VARIANT_PACK (17)."""
+    exe = runtime.compile_graph(graphs.c2_bottleneck(n=1, h=8, w=8))
+    sizes = {a["uid"]: a["size_bytes"] for a in exe.arguments()}
+    base = 0x10000000
+    good, cursor = {}, base
+    for uid, size in sizes.items():
+        good[uid] = cursor
+        cursor += (size + 255) // 256 * 256
+    workspace = cursor + 4096
+
+    def code(pack, ws):
+        try:
+            exe.execute(pack, ws)
+        except DeepForgeError as error:
+            assert str(error).startswith("DFE_")
+            return error.code
+        return 0
+
+    missing = dict(good)
+    del missing[7]
+    assert code(missing, workspace) == 17
+    assert code({**good, 1: 0}, workspace) == 17
+    assert code({**good, 1: good[1] + 1}, workspace) == 17           # bf16 needs 2-byte alignment
+    assert code({**good, 7: good[1]}, workspace) == 17               # output aliases an input
+    assert code({**good, 7: good[1] + 64}, workspace) == 17          # partial overlap with a written tensor
+    assert code(good, 0) == 17                                       # workspace required but null
+    assert code(good, workspace + 8) == 17                           # workspace misaligned
+    assert code(good, good[7]) == 17                                 # workspace overlaps an argument
