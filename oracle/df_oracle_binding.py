@@ -1,0 +1,156 @@
+"""ctypes face of the CPU oracle (df_oracle.c) -- TEST INFRASTRUCTURE ONLY.
+
+Imported by the tests, by the smoke check and by the benchmark's CPU-baseline leg; never by
+the product package. use_native() switches to the -O3 -march=native build used for timing (it
+is built on the machine that runs it)."""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+_LIB = None
+
+from deepforge_b200 import dfgpu  # noqa: E402  (struct layout shared with dfo_tensor)
+
+Tensor = dfgpu.Tensor  # the oracle's dfo_tensor has the same field layout
+tensor = dfgpu.tensor
+
+
+class ConvAttrs(C.Structure):
+    _fields_ = [("spatial_rank", C.c_int32), ("reverse_filter", C.c_int32), ("pre_pad", C.c_int64 * 3),
+                ("post_pad", C.c_int64 * 3), ("stride", C.c_int64 * 3), ("dilation", C.c_int64 * 3)]
+
+
+class SdpaParams(C.Structure):
+    _fields_ = [("q", Tensor), ("k", Tensor), ("v", Tensor), ("o", Tensor), ("stats", Tensor), ("max", Tensor),
+                ("sum_exp", Tensor), ("seq_q", Tensor), ("seq_kv", Tensor), ("page_table_k", Tensor),
+                ("page_table_v", Tensor), ("attn_scale", C.c_float), ("padding_mask", C.c_int32),
+                ("has_left_bound", C.c_int32), ("has_right_bound", C.c_int32), ("left_bound", C.c_int64),
+                ("right_bound", C.c_int64), ("bottom_right", C.c_int32), ("reserved", C.c_int32), ("s_kv", C.c_int64)]
+
+
+def _declare(l: C.CDLL) -> C.CDLL:
+    l.dfo_decode_e4m3.restype = C.c_float
+    l.dfo_decode_e4m3.argtypes = [C.c_uint8]
+    l.dfo_decode_e8m0.restype = C.c_float
+    l.dfo_decode_e8m0.argtypes = [C.c_uint8]
+    l.dfo_encode_e4m3.restype = C.c_uint8
+    l.dfo_encode_e4m3.argtypes = [C.c_float]
+    l.dfo_encode_e8m0.restype = C.c_uint8
+    l.dfo_encode_e8m0.argtypes = [C.c_float]
+    l.dfo_block_scale_code.restype = C.c_uint8
+    l.dfo_block_scale_code.argtypes = [C.c_float]
+    l.dfo_f32_to_bf16.restype = C.c_uint16
+    l.dfo_f32_to_bf16.argtypes = [C.c_float]
+    l.dfo_f32_to_f16.restype = C.c_uint16
+    l.dfo_f32_to_f16.argtypes = [C.c_float]
+    l.dfo_f16_to_f32.restype = C.c_float
+    l.dfo_f16_to_f32.argtypes = [C.c_uint16]
+    l.dfo_f8_128x4_offset.restype = C.c_int64
+    l.dfo_f8_128x4_offset.argtypes = [C.c_int64] * 5
+    return l
+
+
+def use_native() -> None:
+    """Switch every wrapper in this module to the -O3 -march=native build (compiled on this
+    machine by `make native`); used only for timing the CPU baseline."""
+    global _LIB
+    subprocess.run(["make", "-C", str(ROOT / "oracle"), "-B", "native"], check=True, capture_output=True)
+    _LIB = _declare(C.CDLL(str(ROOT / "oracle" / "_build" / "libdf_oracle_native.so")))
+
+
+def lib() -> C.CDLL:
+    global _LIB
+    if _LIB is None:
+        path = ROOT / "oracle" / "_build" / "libdf_oracle.so"
+        source = ROOT / "oracle" / "df_oracle.c"
+        if not path.exists() or path.stat().st_mtime < source.stat().st_mtime:
+            subprocess.run(["make", "-C", str(ROOT / "oracle")], check=True, capture_output=True)
+        _LIB = _declare(C.CDLL(str(path)))
+    return _LIB
+
+
+def ptr(array: np.ndarray) -> C.c_void_p:
+    return C.c_void_p(array.ctypes.data)
+
+
+def encode_e4m3_many(values: np.ndarray) -> np.ndarray:
+    values = np.ascontiguousarray(values, dtype=np.float32)
+    out = np.empty(values.size, dtype=np.uint8)
+    lib().dfo_encode_e4m3_many(ptr(values), ptr(out), C.c_int64(values.size))
+    return out.reshape(values.shape)
+
+
+def block_scale_code_many(amax: np.ndarray) -> np.ndarray:
+    amax = np.ascontiguousarray(amax, dtype=np.float32)
+    out = np.empty(amax.size, dtype=np.uint8)
+    lib().dfo_block_scale_code_many(ptr(amax), ptr(out), C.c_int64(amax.size))
+    return out.reshape(amax.shape)
+
+
+def block_scale_quantize(xd: Tensor, x: np.ndarray, yd: Tensor, y: np.ndarray, sd: Tensor, scale: np.ndarray,
+                         block: int, axis: int) -> None:
+    code = lib().dfo_block_scale_quantize(C.byref(xd), ptr(x), C.byref(yd), ptr(y), C.byref(sd), ptr(scale),
+                                          C.c_int64(block), C.c_int32(axis))
+    assert code == 0, code
+
+
+def block_scale_dequantize(xd, x, sd, scale, yd, y, blocks) -> None:
+    arr = (C.c_int64 * len(blocks))(*blocks)
+    code = lib().dfo_block_scale_dequantize(C.byref(xd), ptr(x), C.byref(sd), ptr(scale), C.byref(yd), ptr(y), arr,
+                                            C.c_int32(len(blocks)))
+    assert code == 0, code
+
+
+def pointwise(mode, ad, a, bd, b, od, out, lower=0.0, upper=3.4028234663852886e38, slope=0.0) -> None:
+    code = lib().dfo_pointwise(C.c_int32(mode), C.byref(ad), ptr(a), C.byref(bd) if bd is not None else None,
+                               ptr(b) if b is not None else None, C.byref(od), ptr(out), C.c_float(lower),
+                               C.c_float(upper), C.c_float(slope))
+    assert code == 0, code
+
+
+def conv_attrs(pre, post, stride, dilation, reverse=False) -> ConvAttrs:
+    a = ConvAttrs()
+    a.spatial_rank = len(pre)
+    a.reverse_filter = int(reverse)
+    for i in range(len(pre)):
+        a.pre_pad[i], a.post_pad[i], a.stride[i], a.dilation[i] = pre[i], post[i], stride[i], dilation[i]
+    return a
+
+
+def conv_generic(xd, x, wd, w, yd, y, attrs) -> None:
+    code = lib().dfo_conv_generic(C.byref(xd), ptr(x), C.byref(wd), ptr(w), C.byref(yd), ptr(y), C.byref(attrs))
+    assert code == 0, code
+
+
+def conv_mvp(x, w, n, h, wd, c, k, r, s, pads, vector_width=0) -> np.ndarray:
+    top, left, bottom, right = pads
+    oh, ow = h + top + bottom - r + 1, wd + left + right - s + 1
+    y = np.empty((n, oh, ow, k), dtype=np.float32)
+    args = [ptr(x), ptr(w), ptr(y)] + [C.c_int64(v) for v in (n, h, wd, c, k, r, s, top, left, bottom, right)]
+    if vector_width:
+        code = lib().dfo_conv_mvp_vector(*args, C.c_int32(vector_width))
+    else:
+        code = lib().dfo_conv_mvp_scalar(*args)
+    assert code == 0, code
+    return y
+
+
+def matmul(ad, a, bd, b, cd, c, row_begin=0, row_end=-1) -> None:
+    code = lib().dfo_matmul(C.byref(ad), ptr(a), C.byref(bd), ptr(b), C.byref(cd), ptr(c), C.c_int64(row_begin),
+                            C.c_int64(row_end))
+    assert code == 0, code
+
+
+def sdpa_forward(params: SdpaParams, arrays, bh_begin=0, bh_end=1 << 62, q_step=1) -> None:
+    assert len(arrays) == 11
+    pointers = (C.c_void_p * 11)(*[C.c_void_p(a.ctypes.data) if a is not None else C.c_void_p(None) for a in arrays])
+    code = lib().dfo_sdpa_forward(C.byref(params), pointers, C.c_int64(bh_begin), C.c_int64(bh_end), C.c_int64(q_step))
+    assert code == 0, code

@@ -1,0 +1,147 @@
+"""Evaluate a serialized graph document on the CPU with the oracle, node by node --
+TEST INFRASTRUCTURE ONLY (parity checker and timed CPU baseline; never the product path).
+
+Every floating tensor is held as f32: a BFLOAT16/HALF graph input is widened exactly and
+the graph is run as its all-FLOAT twin, which is the reference's own semantics (it accepts
+only FLOAT tensors outside the block-scale tags). Block-scale quantize reads its input in
+the tensor's real storage type, so codes and scales are bit-exact checks.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import numpy as np
+
+import df_oracle_binding as oracle
+from deepforge_b200 import dfgpu, synthetic
+
+FLT_MAX = 3.4028234663852886e38
+_FLOATING = {"FLOAT", "BFLOAT16", "HALF"}
+_CODE = {"FP8_E4M3": dfgpu.E4M3, "FP8_E8M0": dfgpu.E8M0, "INT32": dfgpu.I32}
+_STORAGE = {"FLOAT": dfgpu.F32, "BFLOAT16": dfgpu.BF16, "HALF": dfgpu.F16}
+
+
+def widen(array: np.ndarray, data_type: str) -> np.ndarray:
+    """Host array in storage dtype -> what the oracle holds (f32 for floating tensors)."""
+    if data_type == "BFLOAT16":
+        return synthetic.bf16_bits_to_f32(np.ascontiguousarray(array).view(np.uint16).reshape(-1))
+    if data_type == "HALF":
+        return np.ascontiguousarray(array).view(np.float16).reshape(-1).astype(np.float32)
+    if data_type == "FLOAT":
+        return np.ascontiguousarray(array).view(np.float32).reshape(-1).copy()
+    if data_type == "INT32":
+        return np.ascontiguousarray(array).view(np.int32).reshape(-1).copy()
+    return np.ascontiguousarray(array).view(np.uint8).reshape(-1).copy()
+
+
+def _span(t: dict) -> int:
+    if t["reordering_type"] != "NONE":
+        return int(np.prod(t["dim"]))
+    return sum((d - 1) * s for d, s in zip(t["dim"], t["stride"])) + 1
+
+
+def _desc(t: dict, as_storage: bool = False):
+    if t["data_type"] in _FLOATING:
+        dtype = _STORAGE[t["data_type"]] if as_storage else dfgpu.F32
+    else:
+        dtype = _CODE[t["data_type"]]
+    reorder = dfgpu.REORDER_F8_128x4 if t["reordering_type"] == "F8_128x4" else dfgpu.REORDER_NONE
+    return dfgpu.tensor(dtype, t["dim"], t["stride"], reorder)
+
+
+def _alloc(t: dict) -> np.ndarray:
+    if t["data_type"] in _FLOATING:
+        return np.zeros(_span(t), dtype=np.float32)
+    return np.zeros(_span(t), dtype=np.int32 if t["data_type"] == "INT32" else np.uint8)
+
+
+def run(document: dict, inputs: Dict[int, np.ndarray], matmul_rows: Optional[Tuple[int, int]] = None,
+        sdpa_bh: Optional[Tuple[int, int]] = None, sdpa_q_step: int = 1, storage_inputs: Optional[Dict[int, np.ndarray]] = None) -> Dict[int, np.ndarray]:
+    """inputs: uid -> widened arrays (see widen()). storage_inputs: uid -> raw storage-dtype arrays
+    for tensors a BLOCK_SCALE_QUANTIZE reads (so bf16/f16 inputs are decoded by the oracle itself)."""
+    tensors = {int(k): v for k, v in document["tensors"].items()}
+    values: Dict[int, np.ndarray] = dict(inputs)
+    for node in document["nodes"]:
+        tag = node["tag"]
+        ins, outs = node["inputs"], node["outputs"]
+        if tag == "CONV_FPROP":
+            x, w, y = ins["X"], ins["W"], outs["Y"]
+            values[y] = _alloc(tensors[y])
+            attrs = oracle.conv_attrs(node["pre_padding"], node["post_padding"], node["stride"], node["dilation"], node["math_mode"] == "CONVOLUTION")
+            oracle.conv_generic(_desc(tensors[x]), values[x], _desc(tensors[w]), values[w], _desc(tensors[y]), values[y], attrs)
+        elif tag == "POINTWISE":
+            out = outs["OUT_0"]
+            values[out] = _alloc(tensors[out])
+            mode = {"ADD": dfgpu.PW_ADD, "MUL": dfgpu.PW_MUL, "SUB": dfgpu.PW_SUB, "RELU_FWD": dfgpu.PW_RELU_FWD, "IDENTITY": dfgpu.PW_IDENTITY}[node["mode"]]
+            a = ins["IN_0"]
+            b = ins.get("IN_1")
+            lower = node.get("relu_lower_clip")
+            upper = node.get("relu_upper_clip")
+            slope = node.get("relu_lower_clip_slope")
+            oracle.pointwise(mode, _desc(tensors[a]), values[a], _desc(tensors[b]) if b is not None else None, values[b] if b is not None else None,
+                             _desc(tensors[out]), values[out], 0.0 if lower is None else lower, FLT_MAX if upper is None else upper,
+                             0.0 if slope is None else slope)
+        elif tag == "MATMUL":
+            a, b, c = ins["A"], ins["B"], outs["C"]
+            values[c] = _alloc(tensors[c])
+            lo, hi = matmul_rows if matmul_rows else (0, -1)
+            oracle.matmul(_desc(tensors[a]), values[a], _desc(tensors[b]), values[b], _desc(tensors[c]), values[c], lo, hi)
+        elif tag == "BLOCK_SCALE_QUANTIZE":
+            x, y, scale = ins["X"], outs["Y"], outs["scale"]
+            values[y], values[scale] = _alloc(tensors[y]), _alloc(tensors[scale])
+            axis = node["axis"] if node["axis"] is not None else -1
+            if storage_inputs and x in storage_inputs:
+                oracle.block_scale_quantize(_desc(tensors[x], True), storage_inputs[x], _desc(tensors[y]), values[y], _desc(tensors[scale]), values[scale], node["block_size"], axis)
+            else:
+                oracle.block_scale_quantize(_desc(tensors[x]), values[x], _desc(tensors[y]), values[y], _desc(tensors[scale]), values[scale], node["block_size"], axis)
+        elif tag == "BLOCK_SCALE_DEQUANTIZE":
+            x, scale, y = ins["X"], ins["scale"], outs["Y"]
+            values[y] = _alloc(tensors[y])
+            oracle.block_scale_dequantize(_desc(tensors[x]), values[x], _desc(tensors[scale]), values[scale], _desc(tensors[y]), values[y], node["block_size"])
+        elif tag == "SDPA":
+            p = oracle.SdpaParams()
+            arrays = []
+            for name, field in (("Q", "q"), ("K", "k"), ("V", "v")):
+                uid = ins[name]
+                if storage_inputs and uid in storage_inputs and uid not in values:
+                    # large K/V pools stay in their storage type; the oracle widens per element
+                    setattr(p, field, _desc(tensors[uid], True))
+                    arrays.append(storage_inputs[uid])
+                else:
+                    setattr(p, field, _desc(tensors[uid]))
+                    arrays.append(values[uid])
+            p.o = _desc(tensors[outs["O"]])
+            values[outs["O"]] = _alloc(tensors[outs["O"]])
+            arrays.append(values[outs["O"]])
+            for name, field in (("Stats", "stats"), ("Max", "max"), ("Sum_exp", "sum_exp")):
+                if name in outs:
+                    setattr(p, field, _desc(tensors[outs[name]]))
+                    values[outs[name]] = _alloc(tensors[outs[name]])
+                    arrays.append(values[outs[name]])
+                else:
+                    arrays.append(None)
+            for name, field in (("SEQ_LEN_Q", "seq_q"), ("SEQ_LEN_KV", "seq_kv"), ("Page_table_K", "page_table_k"), ("Page_table_V", "page_table_v")):
+                if name in ins:
+                    setattr(p, field, _desc(tensors[ins[name]]))
+                    arrays.append(values[ins[name]])
+                else:
+                    arrays.append(None)
+            p.attn_scale = node["attn_scale_value"] if node["attn_scale_value"] is not None else 1.0
+            p.padding_mask = int(node["padding_mask"])
+            if node["left_bound"] is not None:
+                p.has_left_bound, p.left_bound = 1, node["left_bound"]
+            if node["right_bound"] is not None:
+                p.has_right_bound, p.right_bound = 1, node["right_bound"]
+            p.bottom_right = int(node["diagonal_alignment"] == "BOTTOM_RIGHT")
+            k_t = tensors[ins["K"]]
+            if node["max_seq_len_kv"] is not None:
+                p.s_kv = node["max_seq_len_kv"]
+            elif "Page_table_K" in ins:
+                p.s_kv = tensors[ins["Page_table_K"]]["dim"][2] * k_t["dim"][2]
+            else:
+                p.s_kv = k_t["dim"][2]
+            lo, hi = sdpa_bh if sdpa_bh else (0, 1 << 62)
+            oracle.sdpa_forward(p, arrays, lo, hi, sdpa_q_step)
+        else:
+            raise NotImplementedError(tag)
+    return values
