@@ -56,9 +56,12 @@ def _alloc(t: dict) -> np.ndarray:
 
 
 def run(document: dict, inputs: Dict[int, np.ndarray], matmul_rows: Optional[Tuple[int, int]] = None,
-        sdpa_bh: Optional[Tuple[int, int]] = None, sdpa_q_step: int = 1, storage_inputs: Optional[Dict[int, np.ndarray]] = None) -> Dict[int, np.ndarray]:
+        sdpa_bh: Optional[Tuple[int, int]] = None, sdpa_q_step: int = 1, storage_inputs: Optional[Dict[int, np.ndarray]] = None,
+        round_to_bf16: Tuple[int, ...] = ()) -> Dict[int, np.ndarray]:
     """inputs: uid -> widened arrays (see widen()). storage_inputs: uid -> raw storage-dtype arrays
-    for tensors a BLOCK_SCALE_QUANTIZE reads (so bf16/f16 inputs are decoded by the oracle itself)."""
+    for tensors a BLOCK_SCALE_QUANTIZE reads (so bf16/f16 inputs are decoded by the oracle itself).
+    round_to_bf16: UIDs of intermediate tensors to round to bf16 once produced -- the "staged"
+    oracle for a chain of bf16 tensor-core contractions, each of which reads bf16 operands."""
     tensors = {int(k): v for k, v in document["tensors"].items()}
     values: Dict[int, np.ndarray] = dict(inputs)
     for node in document["nodes"]:
@@ -144,4 +147,7 @@ def run(document: dict, inputs: Dict[int, np.ndarray], matmul_rows: Optional[Tup
             oracle.sdpa_forward(p, arrays, lo, hi, sdpa_q_step)
         else:
             raise NotImplementedError(tag)
+        for uid in outs.values():
+            if uid in round_to_bf16:
+                values[uid] = synthetic.round_to_bf16(values[uid])
     return values

@@ -54,6 +54,15 @@ def test_c1_single_conv(layout, shape):
     assert np.all(np.abs(s.output(3) - ref[3]) <= 1e-4 + 1e-3 * np.abs(ref[3]))  # the reference's own acceptance rule
 
 
+def check_chain(actual, staged, pure):
+    """A chain of three bf16 contractions: each contraction is held to the bf16 gate against the
+    oracle that feeds it the same bf16-rounded operands (the tensor core reads bf16); against
+    the all-f32 twin the rounding of the two intermediates compounds, so that comparison gets
+    twice the gate."""
+    check_bf16(actual, staged)
+    assert np.all(np.abs(actual - pure) <= 2e-2 + 4e-2 * np.abs(pure))
+
+
 @pytest.mark.parametrize("io,options", [("FLOAT", 0), ("BFLOAT16", 0), ("BFLOAT16", runtime.NO_TENSOR_CORES), ("BFLOAT16", runtime.NO_FUSION)])
 def test_c2_bottleneck_small(io, options):
     wl = workloads.c2(n=2, h=14, w=14, io=io)
@@ -61,7 +70,31 @@ def test_c2_bottleneck_small(io, options):
     s.run()
     ins, _ = oracle_inputs(wl, s)
     ref = graph_oracle.run(wl.document, ins)
-    (check_f32 if io == "FLOAT" else check_bf16)(s.output(7), ref[7])
+    if io == "FLOAT":
+        check_f32(s.output(7), ref[7])
+    elif options == 0:
+        # intermediates 13 and 16 live in the workspace as bf16 (they only feed tensor-core convolutions)
+        check_chain(s.output(7), graph_oracle.run(wl.document, ins, round_to_bf16=(13, 16))[7], ref[7])
+    else:
+        check_bf16(s.output(7), ref[7])  # f32 intermediates: the plain gate holds end to end
+
+
+def test_c2_each_contraction_within_the_gate_given_its_own_inputs():
+    """Same DAG with the two intermediates made real bf16 outputs, so every convolution can be
+    checked on its own against the oracle fed with the operands the GPU actually read."""
+    wl = workloads.c2(n=2, h=14, w=14)
+    doc = wl.document
+    for uid in ("13", "16"):
+        doc["tensors"][uid].update(is_virtual=False, data_type="BFLOAT16")
+    s = harness.Session(wl)
+    assert s.exe.launch_count == 3
+    s.run()
+    ins, _ = oracle_inputs(wl, s)
+    t1, t2, y = s.output(13), s.output(16), s.output(7)
+    stage = lambda nodes, values: graph_oracle.run({**doc, "nodes": nodes}, values)
+    check_bf16(t1, stage(doc["nodes"][:3], ins)[13])
+    check_bf16(t2, stage(doc["nodes"][3:6], {**ins, 13: t1})[16])
+    check_bf16(y, stage(doc["nodes"][6:], {**ins, 16: t2})[7])
 
 
 def test_c2_bottleneck_full_geometry_two_images():
@@ -70,8 +103,7 @@ def test_c2_bottleneck_full_geometry_two_images():
     assert s.exe.launch_count == 3 and s.exe.plan_text().count("kernel=3") == 3
     s.run()
     ins, _ = oracle_inputs(wl, s)
-    ref = graph_oracle.run(wl.document, ins)
-    check_bf16(s.output(7), ref[7])
+    check_chain(s.output(7), graph_oracle.run(wl.document, ins, round_to_bf16=(13, 16))[7], graph_oracle.run(wl.document, ins)[7])
 
 
 @pytest.mark.parametrize("io,c_type,options", [("FLOAT", "FLOAT", 0), ("BFLOAT16", "BFLOAT16", 0), ("BFLOAT16", "FLOAT", runtime.NO_FUSION)])
