@@ -149,7 +149,7 @@ def _paged_inputs(batch, hq, hkv, pages, block, max_len, seed, lengths=None):
 
 @pytest.mark.parametrize("group,block", [(4, 64), (1, 16), (8, 128), (2, 256)])
 def test_paged_decode_matches_oracle(group, block):
-    batch, hkv, pages, max_len = 5, 2, 40, 700
+    batch, hkv, pages, max_len = 5, 2, 64, 700
     hq = hkv * group
     lengths, tk, tv = _paged_inputs(batch, hq, hkv, pages, block, max_len, seed=31 + group)
     lengths[0] = max_len
