@@ -558,3 +558,81 @@ extern "C" int dfgpu_sdpa_forward(const dfgpu_sdpa_params* p, void* const* tenso
     sdpa_rowwise_kernel<<<static_cast<unsigned>((rows + 3) / 4), 128, 0, stream>>>(a, rows);
     return check_launch("SDPA");
 }
+
+// ---- paged decode for callers that cannot allocate ---------------------------------------
+//
+// Some hosts of this library are not allowed to call cudaMalloc on the path that runs the
+// decode step: a serving loop that pre-reserved all device memory at start-up and runs with
+// allocation disabled, a plugin called while the framework above it holds its allocator
+// lock, a real-time thread that must not enter the driver's allocator. For those callers the
+// split-KV partial results live in the fixed device array below instead of a caller-provided
+// scratch buffer. The price is a size limit and shared state:
+//   * the partials of one call must fit kStaticDecodeScratchBytes (8 MiB): batch * query
+//     heads * ceil(s_kv / 256) chunks * 520 bytes; larger requests are refused with a message,
+//   * every GPU that loads this library keeps the 8 MiB resident until the process exits,
+//   * all calls on one device share the array: it still holds the previous call's partials
+//     when the next call starts. Nothing in it has to be zero beforehand, because a call
+//     rewrites every slot it later reads (chunks without valid tokens are marked empty by
+//     the first kernel), but two calls whose kernels overlap on the GPU (different streams
+//     or threads) race on it; callers must serialise them.
+// The array's device address is looked up with cudaGetSymbolAddress the first time the entry
+// point runs on a device (with that device current) and remembered per device; make that
+// first call before any stream capture begins.
+constexpr size_t kStaticDecodeScratchBytes = 8u << 20;
+static __device__ __align__(256) unsigned char g_static_decode_scratch[kStaticDecodeScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_static_decode_scratch_address[kMaxDevices] = {};
+
+int static_decode_scratch(void** address) {
+    int device = 0;
+    cudaError_t error = cudaGetDevice(&device);
+    if (error != cudaSuccess) return dfgpu::fail(dfgpu::kExecutionFailed, "SDPA static decode: cudaGetDevice failed: %s", cudaGetErrorString(error));
+    if (device < 0 || device >= kMaxDevices) return dfgpu::fail(dfgpu::kUnsupported, "SDPA static decode: device ordinal %d is above %d", device, kMaxDevices - 1);
+    if (g_static_decode_scratch_address[device] == nullptr) {
+        // In host code the array's name is only a handle for the runtime, not a device pointer:
+        // the address a kernel can use has to come from the runtime, for the current device.
+        void* resolved = nullptr;
+        error = cudaGetSymbolAddress(&resolved, g_static_decode_scratch);
+        if (error != cudaSuccess || resolved == nullptr)
+            return dfgpu::fail(dfgpu::kExecutionFailed, "SDPA static decode: cudaGetSymbolAddress failed: %s", cudaGetErrorString(error));
+        g_static_decode_scratch_address[device] = resolved;
+    }
+    *address = g_static_decode_scratch_address[device];
+    return dfgpu::kOk;
+}
+}  // namespace
+
+extern "C" int dfgpu_sdpa_paged_decode_static(const dfgpu_sdpa_params* p, void* const* tensors, void* stream_handle) {
+    if (!p || !tensors) return fail(kInvalidArgument, "SDPA static decode: null params");
+    SdpaArgs a;
+    int status = build_args(*p, tensors, a);
+    if (status) return status;
+    if (!decode_supported(*p))
+        return fail(kUnsupported, "SDPA static decode: needs Sq=1, bf16, D=128, paged K and V, group size 1/2/4/8");
+    if (!aligned16(a.q_data) || !aligned16(a.k_data) || !aligned16(a.v_data))
+        return fail(kInvalidArgument, "SDPA static decode: needs 16-byte aligned Q, K and V");
+    const int chunks = decode_chunks(*p);
+    const size_t needed = static_cast<size_t>(p->q.dim[0]) * static_cast<size_t>(p->q.dim[1]) * static_cast<size_t>(chunks) * kPartialStride * sizeof(float);
+    if (needed > kStaticDecodeScratchBytes)
+        return fail(kInvalidShape, "SDPA static decode: this call needs %zu bytes of split-KV partials, the built-in scratch holds %zu (batch * query heads * ceil(s_kv/256) * 520 must not exceed it)",
+                    needed, kStaticDecodeScratchBytes);
+    void* scratch = nullptr;
+    status = static_decode_scratch(&scratch);
+    if (status) return status;
+    cudaStream_t stream = as_stream(stream_handle);
+    const int group = static_cast<int>(p->q.dim[1] / p->k.dim[1]);
+    dim3 grid(static_cast<unsigned>(chunks), static_cast<unsigned>(p->k.dim[1]), static_cast<unsigned>(p->q.dim[0]));
+    float* partial = static_cast<float*>(scratch);
+    switch (group) {
+        case 1: sdpa_paged_decode_kernel<1><<<grid, 256, 0, stream>>>(a, partial, chunks); break;
+        case 2: sdpa_paged_decode_kernel<2><<<grid, 256, 0, stream>>>(a, partial, chunks); break;
+        case 4: sdpa_paged_decode_kernel<4><<<grid, 256, 0, stream>>>(a, partial, chunks); break;
+        default: sdpa_paged_decode_kernel<8><<<grid, 256, 0, stream>>>(a, partial, chunks); break;
+    }
+    status = check_launch("SDPA static decode");
+    if (status) return status;
+    sdpa_decode_merge_kernel<<<static_cast<unsigned>(p->q.dim[0] * p->q.dim[1]), kDecodeD, 0, stream>>>(a, partial, chunks);
+    return check_launch("SDPA static decode merge");
+}

@@ -103,7 +103,7 @@ EXPORTS = [
     "dfgpu_query_pointwise", "dfgpu_pointwise",
     "dfgpu_query_conv_fprop", "dfgpu_conv_fprop",
     "dfgpu_query_matmul", "dfgpu_matmul",
-    "dfgpu_query_sdpa_forward", "dfgpu_sdpa_forward",
+    "dfgpu_query_sdpa_forward", "dfgpu_sdpa_forward", "dfgpu_sdpa_paged_decode_static",
     "dfgpu_selfcheck_e4m3", "dfgpu_debug_scale_codes", "dfgpu_debug_encode_e4m3", "dfgpu_device_status",
 ]
 
@@ -183,6 +183,14 @@ def matmul(params, a, b, c, a_scale=None, b_scale=None, extra0=None, extra1=None
 def sdpa_forward(params, pointers: Sequence[Optional[int]], scratch=None, stream=None):
     assert len(pointers) == 11
     _call("dfgpu_sdpa_forward", params, pointers, scratch, stream)
+
+
+def sdpa_paged_decode_static(params, pointers: Sequence[Optional[int]], stream=None):
+    """Paged decode with the library's built-in 8 MiB scratch: no caller buffer, no allocation."""
+    assert len(pointers) == 11
+    fn = load().dfgpu_sdpa_paged_decode_static
+    fn.restype = C.c_int
+    _check(fn(C.byref(params), _pointers(pointers), C.c_void_p(stream or None)))
 
 
 def selfcheck_e4m3(first_bits: int, count: int, result_ptr: int, stream=None) -> None:

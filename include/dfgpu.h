@@ -191,6 +191,20 @@ typedef struct dfgpu_sdpa_params {
 int dfgpu_query_sdpa_forward(const dfgpu_sdpa_params*, dfgpu_plan_info*);
 int dfgpu_sdpa_forward(const dfgpu_sdpa_params*, void* const* tensors, void* scratch, void* stream);
 
+/* ---- paged decode without caller scratch ------------------------------------------
+   No counterpart in the reference (it has no device memory to manage). Same computation
+   and tensor order as dfgpu_sdpa_forward's paged-decode kernel, for hosts that may not
+   allocate device memory around the call (allocation frozen after start-up, allocator lock
+   held by the framework above, real-time threads): the split-KV partials go to an 8 MiB
+   array built into the library instead of a caller buffer. Limits: batch * query heads *
+   ceil(s_kv / 256) * 520 bytes must fit 8 MiB, else the call returns 15 with a message; the
+   array is shared by every call on a device and keeps the previous call's contents (each
+   call rewrites all it reads, so nothing needs clearing), so calls that overlap on the GPU
+   race and must be serialised by the caller; each GPU that loads the library holds the
+   8 MiB until exit. The first call on a device resolves the array's address (with that
+   device current): make it before any stream capture. Makes no allocation of any kind. */
+int dfgpu_sdpa_paged_decode_static(const dfgpu_sdpa_params*, void* const* tensors, void* stream);
+
 /* ---- self-check of the E4M3 encoder ------------------------------------------
    Encodes `count` consecutive f32 bit patterns starting at `first_bits` with
    the production encoder and with a literal candidate search, on the device.
