@@ -167,7 +167,7 @@ struct SmemLayout {
 };
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs args) {
     using L = SmemLayout<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
@@ -392,11 +392,22 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& a
     return check_launch("tcgen05 GEMM");
 }
 
+// Ring depth: shallow K loops (the 1x1 convolutions) get short rings so that several CTAs fit on
+// one SM and overlap each other's load / MMA / epilogue phases; deep K loops (matmul) get 4 stages.
 int dispatch(int bn, int k_blocks, const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& args, dim3 grid, cudaStream_t stream) {
-    const bool shallow = k_blocks <= 2;
-    if (bn == 64) return shallow ? launch<64, 2>(map_a, map_b, args, grid, stream) : launch<64, 4>(map_a, map_b, args, grid, stream);
-    if (bn == 128) return shallow ? launch<128, 2>(map_a, map_b, args, grid, stream) : launch<128, 4>(map_a, map_b, args, grid, stream);
-    return shallow ? launch<256, 2>(map_a, map_b, args, grid, stream) : launch<256, 4>(map_a, map_b, args, grid, stream);
+    const int stages = k_blocks <= 1 ? 1 : (k_blocks <= 12 ? 2 : 4);
+    if (bn == 64) {
+        if (stages == 1) return launch<64, 1>(map_a, map_b, args, grid, stream);
+        if (stages == 2) return launch<64, 2>(map_a, map_b, args, grid, stream);
+        return launch<64, 4>(map_a, map_b, args, grid, stream);
+    }
+    if (bn == 128) {
+        if (stages == 1) return launch<128, 1>(map_a, map_b, args, grid, stream);
+        if (stages == 2) return launch<128, 2>(map_a, map_b, args, grid, stream);
+        return launch<128, 4>(map_a, map_b, args, grid, stream);
+    }
+    if (stages <= 2) return launch<256, 2>(map_a, map_b, args, grid, stream);
+    return launch<256, 4>(map_a, map_b, args, grid, stream);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -451,7 +462,12 @@ bool translate_epilogue(int count, const dfgpu_epilogue_step* steps, const dfgpu
     return true;
 }
 
-int pick_bn(int64_t n) { return n % 256 == 0 ? 256 : (n % 128 == 0 ? 128 : 64); }
+// Wide N tiles pay off when the K loop is long (matmul); with a short K loop a narrower tile keeps
+// more CTAs resident per SM (less shared memory and TMEM each).
+int pick_bn(int64_t n, int64_t k_blocks) {
+    if (k_blocks > 12 && n % 256 == 0) return 256;
+    return n % 128 == 0 ? 128 : 64;
+}
 
 }  // namespace
 
@@ -474,7 +490,7 @@ int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStrea
         return fail(kInvalidArgument, "CONV_FPROP: the tcgen05 kernel needs 16-byte aligned X, W and Y");
     GemmArgs args{};
     const bool pointwise = R == 1 && S == 1 && p.pre_pad[0] == 0 && p.pre_pad[1] == 0 && p.post_pad[0] == 0 && p.post_pad[1] == 0;
-    const int bn = pick_bn(K);
+    const int bn = pick_bn(K, R * S * (C / kBlockK));
     CUtensorMap map_a, map_b;
     int status;
     int64_t m_tiles;
@@ -549,7 +565,7 @@ int launch_matmul_umma(const dfgpu_matmul_params& p, void* const* tensors, int k
     const int64_t M = p.c.dim[rank - 2], N = p.c.dim[rank - 1], K = p.a.dim[rank - 1];
     if (!aligned16(tensors[0]) || !aligned16(tensors[1]) || !aligned16(tensors[2]))
         return fail(kInvalidArgument, "MATMUL: the tcgen05 kernel needs 16-byte aligned A, B and C");
-    const int bn = pick_bn(N);
+    const int bn = pick_bn(N, K / kBlockK);
     const bool b_k_major = p.b.stride[rank - 2] == 1 && p.b.stride[rank - 1] % 8 == 0 && p.b.stride[rank - 1] >= K;
     const bool b_n_major = !b_k_major;
     GemmArgs args{};

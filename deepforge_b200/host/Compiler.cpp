@@ -277,10 +277,31 @@ Status lower_conv(Lowering& low, std::size_t index) {
     return Status::ok();
 }
 
+// Would the tcgen05 bf16 kernel cover this MATMUL if its floating operands were bf16? Then
+// dequantize nodes in front of it are kept as separate launches whose outputs are stored as
+// bf16 (exact: an E4M3 code times a power of two has four significant bits), instead of being
+// folded into the CUDA-core matmul's operand loads.
+bool matmul_fits_tensor_cores(Lowering const& low, OperationDesc const& node) {
+    if (low.options.disable_tensor_cores || !low.options.narrow_virtual_tensors) return false;
+    auto a = port(node.inputs, "A"), b = port(node.inputs, "B"), c = port(node.outputs, "C");
+    if (!a || !b || !c) return false;
+    dfgpu_matmul_params trial{};
+    if (low.describe(*a, trial.a, "").is_bad() || low.describe(*b, trial.b, "").is_bad() || low.describe(*c, trial.c, "").is_bad()) return false;
+    auto floating = [](int t) { return t == DFGPU_F32 || t == DFGPU_BF16; };
+    if (!floating(trial.a.dtype) || !floating(trial.b.dtype)) return false;
+    if (trial.a.dtype == DFGPU_F32 && !low.tensor(*a).is_virtual) return false;  // a real f32 input cannot be narrowed
+    if (trial.b.dtype == DFGPU_F32 && !low.tensor(*b).is_virtual) return false;
+    trial.a.dtype = trial.b.dtype = DFGPU_BF16;
+    if (trial.c.dtype == DFGPU_F32 && low.tensor(*c).is_virtual) trial.c.dtype = DFGPU_BF16;
+    trial.kernel = DFGPU_MATMUL_UMMA_BF16;
+    dfgpu_plan_info info{};
+    return dfgpu_query_matmul(&trial, &info) == 0;
+}
+
 // BLOCK_SCALE_DEQUANTIZE feeding only this MATMUL operand -> read codes and scales directly.
 bool try_absorb_dequantize(Lowering& low, std::size_t matmul_index, std::int64_t operand_uid, dfgpu_tensor& operand, dfgpu_tensor& scale,
                            std::int64_t* block, std::int64_t& codes_uid, std::int64_t& scale_uid, std::size_t& dequant_index) {
-    if (!low.options.fuse) return false;
+    if (!low.options.fuse || matmul_fits_tensor_cores(low, low.graph.nodes[matmul_index])) return false;
     auto const& t = low.tensor(operand_uid);
     auto producer = low.producer.find(operand_uid);
     std::size_t only = 0;
@@ -532,18 +553,34 @@ void narrow_virtual_tensors(Lowering& low) {
             else readers[binding.uid].push_back(s);
         }
     }
+    // pass 1: dequantize outputs (exactly representable in bf16) that only feed contractions which
+    // would then run on the tensor cores; pass 2: contraction outputs with bf16 inputs.
+    for (int pass = 0; pass < 2; ++pass)
     for (auto const& [uid, step_index] : writer) {
         auto& step = low.plan.steps[step_index];
-        if (!is_contraction(step.op) || low.tensor(uid).data_type != DataType::kFloat32) continue;
-        bool bf16_inputs = false;
-        if (auto* conv = std::get_if<dfgpu_conv_params>(&step.params)) bf16_inputs = conv->x.dtype == DFGPU_BF16 && conv->w.dtype == DFGPU_BF16;
-        if (auto* matmul = std::get_if<dfgpu_matmul_params>(&step.params)) bf16_inputs = matmul->a.dtype == DFGPU_BF16 && matmul->b.dtype == DFGPU_BF16;
-        if (!bf16_inputs) continue;
+        if (low.tensor(uid).data_type != DataType::kFloat32 || low.storage_override.count(uid)) continue;
         bool only_contractions = !readers[uid].empty();
         for (auto reader : readers[uid]) only_contractions = only_contractions && is_contraction(low.plan.steps[reader].op);
         if (!only_contractions) continue;
+        if (pass == 0) {
+            auto* dequantize = std::get_if<dfgpu_bsd_params>(&step.params);
+            if (!dequantize || dequantize->x.dtype != DFGPU_E4M3 || dequantize->scale.dtype != DFGPU_E8M0) continue;
+            bool wanted = true;
+            for (auto reader : readers[uid]) {
+                auto const& consumer = low.plan.steps[reader];
+                wanted = wanted && consumer.op == KernelOp::kMatmul && matmul_fits_tensor_cores(low, low.graph.nodes[consumer.nodes.front()]);
+            }
+            if (!wanted) continue;
+            dequantize->y.dtype = DFGPU_BF16;
+        } else {
+            if (!is_contraction(step.op)) continue;
+            bool bf16_inputs = false;
+            if (auto* conv = std::get_if<dfgpu_conv_params>(&step.params)) bf16_inputs = conv->x.dtype == DFGPU_BF16 && conv->w.dtype == DFGPU_BF16;
+            if (auto* matmul = std::get_if<dfgpu_matmul_params>(&step.params)) bf16_inputs = matmul->a.dtype == DFGPU_BF16 && matmul->b.dtype == DFGPU_BF16;
+            if (!bf16_inputs) continue;
+            step_output(step)->dtype = DFGPU_BF16;
+        }
         low.storage_override[uid] = DFGPU_BF16;
-        step_output(step)->dtype = DFGPU_BF16;
         for (auto reader : readers[uid]) {
             auto& consumer = low.plan.steps[reader];
             for (std::size_t slot = 0; slot < consumer.tensors.size(); ++slot) {

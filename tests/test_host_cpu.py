@@ -141,12 +141,18 @@ def test_bottleneck_plan_fuses_to_three_launches_and_shares_workspace():
     assert f32.plan_text().count("kernel=2") == 3 and f32.workspace_size == 2 * (2 * 8 * 8 * 64 * 4)
 
 
-def test_quantize_matmul_plan_absorbs_the_dequantize_nodes():
+def test_quantize_matmul_plans():
+    # tensor-core shape: dequantize stays a launch whose output is stored as bf16 (exact), matmul on tcgen05
     exe = runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 128))
-    assert exe.launch_count == 3 and exe.workspace_size == 0
-    assert "dequantize_a" in exe.plan_text() and "dequantize_b" in exe.plan_text()
-    unfused = runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 128), options=runtime.NO_FUSION)
-    assert unfused.launch_count == 5 and unfused.workspace_size == 2 * 128 * 128 * 4
+    assert exe.launch_count == 5 and exe.workspace_size == 2 * 128 * 128 * 2
+    assert "matmul kernel=2" in exe.plan_text()
+    # shapes the tcgen05 kernel does not cover: the dequantize nodes are absorbed into the CUDA-core matmul
+    for doc, options in ((graphs.c3_quantize_matmul(128, 128, 96), 0), (graphs.c3_quantize_matmul(128, 128, 128), runtime.NO_TENSOR_CORES)):
+        absorbed = runtime.compile_graph(doc, options=options)
+        assert absorbed.launch_count == 3 and absorbed.workspace_size == 0
+        assert "[dequantize_b+dequantize_a+matmul]" in absorbed.plan_text()
+    unfused = runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 96), options=runtime.NO_FUSION)
+    assert unfused.launch_count == 5 and unfused.workspace_size == 128 * 128 * 4 + 128 * 96 * 4
 
 
 def test_argument_table_is_sorted_with_clamped_alignment():
