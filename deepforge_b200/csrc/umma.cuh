@@ -16,5 +16,6 @@ int launch_matmul_umma(const dfgpu_matmul_params& p, void* const* tensors, int k
 // SDPA forward on tcgen05 (bf16, head dim 128, contiguous K/V).
 bool sdpa_umma_supported(const dfgpu_sdpa_params& p);
 int launch_sdpa_umma(const dfgpu_sdpa_params& p, void* const* tensors, void* scratch, cudaStream_t stream);
+int sdpa_umma_device_status(int* status);  // reads and clears that unit's status word
 
 }  // namespace dfgpu

@@ -18,109 +18,10 @@
 // Every wait is bounded (wall-clock, ~2 s): on expiry the waiter records a code in
 // g_device_status and all roles fall through to the common exit, so TMEM is always
 // freed and the kernel always returns.
-#include <cuda.h>
-
-#include "umma.cuh"
+#include "umma_ptx.cuh"
 
 namespace dfgpu {
-
-__device__ int g_device_status = 0;
-
 namespace {
-
-// ---- PTX wrappers -------------------------------------------------------------------
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    return done != 0;
-}
-__device__ __forceinline__ uint64_t global_timer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// Bounded wait: false after ~2 s, with `code` left in g_device_status.
-__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t start = global_timer_ns();
-    for (;;) {
-        for (int spin = 0; spin < 128; ++spin)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (global_timer_ns() - start > 2000000000ull) {
-            atomicCAS(&g_device_status, 0, code);
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
-                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t columns) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(columns) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t columns) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, 128-byte swizzle, Blackwell version bit set.
-// K-major operand: rows of 64 bf16 (128 B), 8-row groups 1024 B apart (SBO); LBO unused (1).
-// MN-major operand: 64-element chunks along MN are `lbo_bytes` apart, 8-row K groups 1024 B apart.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t address, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t desc = 0;
-    desc |= static_cast<uint64_t>((address & 0x3FFFFu) >> 4);
-    desc |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
-    desc |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
-    desc |= 1ull << 46;
-    desc |= 2ull << 61;
-    return desc;
-}
 
 // ---- kernel ---------------------------------------------------------------------------
 
@@ -347,37 +248,304 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
 }
 
+// ---- persistent variant for the bandwidth-bound convolutions ------------------------------
+//
+// One CTA per SM walks a static list of output tiles. These convolutions have tiny K loops and
+// almost no math per byte, so what matters is bytes in flight per SM:
+//   * the whole filter (all taps, all output-channel tiles) is loaded into shared memory ONCE per
+//     CTA and stays there; the ring then carries only 16 KiB activation tiles, as many stages as
+//     the remaining shared memory allows (8-10), filled by the TMA producer across tile borders;
+//   * the MMA lane alternates between two TMEM accumulators, so tile i+1 is multiplied while the
+//     four epilogue warps drain tile i: tcgen05.ld -> bias / ReLU / residual -> bf16 -> swizzled
+//     shared-memory tile -> one TMA store per 64 output channels;
+//   * a residual operand is prefetched by TMA into one of three epilogue buffers and the result
+//     is written over it in place, so the same buffer is the source of the TMA store.
+// Every global access is a full-line TMA transfer; nothing is read from HBM twice.
+
+constexpr int kMaxRingStages = 12;
+constexpr int kPersistentThreads = 320;  // producer warp, MMA warp, two epilogue warpgroups
+constexpr int kAccumulators = 4;          // TMEM accumulators in flight: hides the commit -> epilogue -> release round trip
+constexpr int kMaxBiasFloats = 2048;    // per-channel ADD operands staged in shared memory as f32
+
+struct PersistentArgs {
+    GemmArgs gemm;
+    int32_t n_tiles;       // tiles along the output-channel axis
+    int32_t total_tiles;
+    int32_t box_rows;      // rows of the output / residual TMA boxes (valid rows of a tile)
+    int32_t stages;        // activation ring depth (slots)
+    int32_t group_k;       // 64-deep K slices per ring slot: one full/empty handshake moves group_k * 16 KiB
+    int32_t filter_bytes;  // resident filter: n_tiles * k_blocks * BN * 128
+    int32_t w_offset, epi_offset, ring_offset, bias_offset, barrier_offset;  // shared-memory layout (bytes from the aligned base)
+    int32_t bias_stride;   // output channels (floats per staged bias vector)
+};
+
+template <int BN, bool HAS_RES>
+__global__ void __launch_bounds__(kPersistentThreads, 1)
+umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                            const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_res,
+                            PersistentArgs pargs) {
+    constexpr int kABytes = kTileM * kBlockK * 2;
+    constexpr int kBTileBytes = BN * 128;                 // one 64-deep slice of the filter for this N tile
+    constexpr int kEpiBytes = (BN / 64) * kTileM * 128;   // one epilogue buffer
+    const GemmArgs& args = pargs.gemm;
+    const int STAGES = pargs.stages;
+    const int G = pargs.group_k;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t w_base = smem_base + pargs.w_offset;
+    const uint32_t epi_base = smem_base + pargs.epi_offset;
+    const uint32_t ring_base = smem_base + pargs.ring_offset;
+    const uint32_t bar_base = smem_base + pargs.barrier_offset;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxRingStages + s); };
+    auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * kMaxRingStages + a); };
+    auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * kMaxRingStages + 4 + a); };
+    auto res_full_bar = [&](int b) { return bar_base + 8u * (2 * kMaxRingStages + 8 + b); };
+    auto res_empty_bar = [&](int b) { return bar_base + 8u * (2 * kMaxRingStages + 12 + b); };
+    const uint32_t w_full_bar = bar_base + 8u * (2 * kMaxRingStages + 16);
+    const uint32_t tmem_slot = bar_base + 8u * (2 * kMaxRingStages + 17);
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + pargs.barrier_offset + 8 * (2 * kMaxRingStages + 17));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < kAccumulators; ++a) {
+            mbar_init(acc_full_bar(a), 1);
+            mbar_init(acc_empty_bar(a), 4);  // one arrival per warp of the group that drained it
+        }
+        for (int b = 0; b < 4; ++b) {
+            mbar_init(res_full_bar(b), 1);
+            mbar_init(res_empty_bar(b), 1);  // the thread that issues that group's TMA stores
+        }
+        mbar_init(w_full_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kAccumulators * BN);
+        tmem_relinquish();
+        tc_fence_before();
+    }
+    {
+        // per-channel ADD operands -> f32 in shared memory, once per CTA
+        float* bias_stage = reinterpret_cast<float*>(generic_base + pargs.bias_offset);
+        int slot = 0;
+        for (int e = 0; e < args.epi_count; ++e) {
+            if (args.epi_kind[e] != kEpiBias) continue;
+            for (int c = threadIdx.x; c < pargs.bias_stride; c += blockDim.x)
+                bias_stage[slot * pargs.bias_stride + c] = load_as_f32(args.epi_data[e], args.epi_dtype[e], c);
+            ++slot;
+        }
+    }
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    auto tile_geometry = [&](int tile, int& m_tile, int& n_tile, int& image, int& h0, int64_t& out_row0) {
+        m_tile = tile / pargs.n_tiles;
+        n_tile = tile - m_tile * pargs.n_tiles;
+        image = 0;
+        h0 = 0;
+        if (args.is_conv) {
+            image = m_tile / args.tiles_per_image;
+            h0 = (m_tile - image * args.tiles_per_image) * args.rows_per_tile;
+            out_row0 = (static_cast<int64_t>(image) * args.out_p + h0) * args.out_q;
+        } else {
+            out_row0 = static_cast<int64_t>(m_tile) * kTileM;
+        }
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // the filter, once: [n_tile][k_block] slices of BN x 64
+            mbar_expect_tx(w_full_bar, static_cast<uint32_t>(pargs.filter_bytes));
+            for (int nt = 0; nt < pargs.n_tiles; ++nt)
+                for (int kb = 0; kb < args.k_blocks; ++kb)
+                    tma_load_2d(w_base + (nt * args.k_blocks + kb) * kBTileBytes, &map_b, kb * kBlockK, nt * BN, w_full_bar);
+            const uint32_t a_bytes = args.is_conv ? static_cast<uint32_t>(args.rows_per_tile * args.out_q * kBlockK * 2) : kABytes;
+            const uint32_t res_bytes = static_cast<uint32_t>(pargs.box_rows) * 128u * (BN / 64);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x, i = 0; tile < pargs.total_tiles && ok; tile += gridDim.x, ++i) {
+                int m_tile, n_tile, image, h0;
+                int64_t out_row0;
+                tile_geometry(tile, m_tile, n_tile, image, h0, out_row0);
+                if (HAS_RES) {
+                    const int b = (i & 1) * 2 + ((i >> 1) & 1);  // the owning epilogue group's next buffer
+                    ok = mbar_wait(res_empty_bar(b), ((i >> 2) & 1) ^ 1, 111);
+                    if (!ok) break;
+                    mbar_expect_tx(res_full_bar(b), res_bytes);
+#pragma unroll
+                    for (int j = 0; j < BN / 64; ++j)
+                        tma_load_2d(epi_base + b * kEpiBytes + j * (kTileM * 128), &map_res, n_tile * BN + 64 * j, static_cast<int>(out_row0), res_full_bar(b));
+                }
+                for (int kb0 = 0; kb0 < args.k_blocks; kb0 += G, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, 112);
+                    if (!ok) break;
+                    mbar_expect_tx(full_bar(s), a_bytes * G);
+                    for (int g = 0; g < G; ++g) {
+                        const int kb = kb0 + g;
+                        const uint32_t a_dst = ring_base + (s * G + g) * kABytes;
+                        const int tap = kb / args.k_blocks_per_tap;
+                        const int c0 = (kb - tap * args.k_blocks_per_tap) * kBlockK;
+                        if (args.is_conv) {
+                            const int r = tap / args.filter_s, sx = tap - r * args.filter_s;
+                            tma_load_4d(a_dst, &map_a, c0, sx - args.pad_w, h0 + r - args.pad_h, image, full_bar(s));
+                        } else {
+                            tma_load_2d(a_dst, &map_a, kb * kBlockK, m_tile * kTileM, full_bar(s));
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                                   (static_cast<uint32_t>(kTileM >> 4) << 24);
+            uint32_t it = 0;
+            bool ok = mbar_wait(w_full_bar, 0, 117);
+            for (int tile = blockIdx.x, i = 0; tile < pargs.total_tiles; tile += gridDim.x, ++i) {
+                const int acc = i % kAccumulators;
+                const int n_tile = tile % pargs.n_tiles;
+                if (ok) ok = mbar_wait(acc_empty_bar(acc), ((i / kAccumulators) & 1) ^ 1, 113);
+                tc_fence_after();
+                const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * BN);
+                for (int kb0 = 0; kb0 < args.k_blocks && ok; kb0 += G, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(full_bar(s), (it / STAGES) & 1, 114);
+                    if (!ok) break;
+                    tc_fence_after();
+                    {
+                        for (int g = 0; g < G; ++g) {
+                            const uint32_t a_src = ring_base + (s * G + g) * kABytes;
+                            const uint32_t b_src = w_base + (n_tile * args.k_blocks + kb0 + g) * kBTileBytes;
+#pragma unroll
+                            for (int k = 0; k < kBlockK / 16; ++k)
+                                umma_bf16(tmem_acc, smem_desc(a_src + k * 32, 16, 1024), smem_desc(b_src + k * 32, 16, 1024), idesc, (kb0 | g | k) != 0 ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(empty_bar(s));
+                }
+                umma_commit(acc_full_bar(acc));  // arrives even after a failed wait so the epilogue never hangs
+            }
+        }
+    } else {
+        // two epilogue warpgroups: group g drains accumulator g, i.e. every other tile
+        const int group = (warp - 2) >> 2;
+        const int quadrant = warp & 3;
+        const int row = quadrant * 32 + lane;
+        const bool store_thread = ((warp - 2) & 3) == 0 && lane == 0;
+        const float* bias_smem = reinterpret_cast<const float*>(generic_base + pargs.bias_offset);
+        bool ok = true;
+        for (int tile = blockIdx.x + group * gridDim.x, j = 0; tile < pargs.total_tiles; tile += 2 * gridDim.x, ++j) {
+            int m_tile, n_tile, image, h0;
+            int64_t out_row0;
+            tile_geometry(tile, m_tile, n_tile, image, h0, out_row0);
+            const int n0 = n_tile * BN;
+            const int i = group + 2 * j;  // position of this tile in the CTA's tile list
+            const int acc = i % kAccumulators;
+            const int buf = HAS_RES ? group * 2 + (j & 1) : group;
+            if (ok) ok = mbar_wait(acc_full_bar(acc), (i / kAccumulators) & 1, 115);
+            if (HAS_RES) {
+                if (ok) ok = mbar_wait(res_full_bar(buf), (j >> 1) & 1, 116);
+            } else {
+                // this group's staging buffer was last read by the TMA store of its previous tile
+                if (store_thread) tma_store_wait_read<0>();
+                epilogue_barrier(1 + group);
+            }
+            tc_fence_after();
+            const bool healthy = ok && g_device_status == 0;
+            uint8_t* tile_smem = generic_base + pargs.epi_offset + buf * kEpiBytes;
+#pragma unroll 1
+            for (int chunk = 0; chunk < BN / 32; ++chunk) {
+                uint32_t raw[32];
+                tmem_load_32(tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) + acc * BN + chunk * 32, raw);
+                tmem_load_wait();
+                float v[32];
+#pragma unroll
+                for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[e]);
+                const int region = chunk >> 1;        // which 64-channel box
+                const int chunk16 = (chunk & 1) * 4;  // first 16-byte unit inside the 128-byte row
+                uint8_t* row_smem = tile_smem + region * (kTileM * 128) + row * 128;
+                int bias_slot = 0;
+                for (int e = 0; e < args.epi_count; ++e) {
+                    const int kind = args.epi_kind[e];
+                    if (kind == kEpiRelu) {
+                        const float lower = args.epi_lower[e], upper = args.epi_upper[e], slope = args.epi_slope[e];
+#pragma unroll
+                        for (int t = 0; t < 32; ++t) v[t] = relu_fast(v[t], lower, upper, slope);
+                    } else if (kind == kEpiBias) {
+                        const float4* p = reinterpret_cast<const float4*>(bias_smem + bias_slot * pargs.bias_stride + n0 + chunk * 32);
+                        ++bias_slot;
+#pragma unroll
+                        for (int q4 = 0; q4 < 8; ++q4) {
+                            const float4 q = p[q4];
+                            v[4 * q4] = __fadd_rn(v[4 * q4], q.x);
+                            v[4 * q4 + 1] = __fadd_rn(v[4 * q4 + 1], q.y);
+                            v[4 * q4 + 2] = __fadd_rn(v[4 * q4 + 2], q.z);
+                            v[4 * q4 + 3] = __fadd_rn(v[4 * q4 + 3], q.w);
+                        }
+                    } else if (HAS_RES) {  // the residual tile the producer staged in this buffer
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            const uint4 q = *reinterpret_cast<const uint4*>(row_smem + (((chunk16 + q4) ^ (row & 7)) << 4));
+                            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                v[8 * q4 + 2 * t] = __fadd_rn(v[8 * q4 + 2 * t], __uint_as_float(w[t] << 16));
+                                v[8 * q4 + 2 * t + 1] = __fadd_rn(v[8 * q4 + 2 * t + 1], __uint_as_float(w[t] & 0xffff0000u));
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        __nv_bfloat162 pair = __floats2bfloat162_rn(v[8 * q4 + 2 * t], v[8 * q4 + 2 * t + 1]);
+                        w[t] = *reinterpret_cast<uint32_t*>(&pair);
+                    }
+                    *reinterpret_cast<uint4*>(row_smem + (((chunk16 + q4) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+            // release the accumulator, then publish the finished tile
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+            fence_async_shared();
+            epilogue_barrier(1 + group);
+            if (store_thread) {
+                if (healthy) {
+#pragma unroll
+                    for (int q = 0; q < BN / 64; ++q)
+                        tma_store_2d(&map_out, epi_base + buf * kEpiBytes + q * (kTileM * 128), n0 + 64 * q, static_cast<int>(out_row0));
+                }
+                tma_store_commit();
+                if (HAS_RES && j >= 1) {
+                    // this group's previous store has finished reading its buffer: hand it back for a residual prefetch
+                    tma_store_wait_read<1>();
+                    mbar_arrive(res_empty_bar(group * 2 + ((j - 1) & 1)));
+                }
+            }
+        }
+        if (store_thread) tma_store_wait_all();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kAccumulators * BN);
+    }
+}
+
 // ---- host side ----------------------------------------------------------------------------
-
-using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_tiled() {
-    static EncodeTiled fn = [] {
-        void* entry = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result) != cudaSuccess ||
-            result != cudaDriverEntryPointSuccess)
-            entry = nullptr;
-        return reinterpret_cast<EncodeTiled>(entry);
-    }();
-    return fn;
-}
-
-// bf16 tensor map with a 64-element (128-byte) swizzled inner box.
-int make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
-             const uint32_t* box, const char* what) {
-    EncodeTiled encode = encode_tiled();
-    if (!encode) return fail(kExecutionFailed, "%s: cuTensorMapEncodeTiled is unavailable", what);
-    cuuint32_t element_strides[5] = {1, 1, 1, 1, 1};
-    CUresult result = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base),
-                             reinterpret_cast<const cuuint64_t*>(dims), reinterpret_cast<const cuuint64_t*>(strides_bytes),
-                             reinterpret_cast<const cuuint32_t*>(box), element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (result != CUDA_SUCCESS) return fail(kExecutionFailed, "%s: tensor map encode failed (CUresult %d)", what, static_cast<int>(result));
-    return kOk;
-}
 
 template <int BN, int STAGES>
 int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& args, dim3 grid, cudaStream_t stream) {
@@ -408,6 +576,47 @@ int dispatch(int bn, int k_blocks, const CUtensorMap& map_a, const CUtensorMap& 
     }
     if (stages <= 2) return launch<256, 2>(map_a, map_b, args, grid, stream);
     return launch<256, 4>(map_a, map_b, args, grid, stream);
+}
+
+constexpr int kSmemBudget = 227 * 1024;
+
+template <int BN, bool HAS_RES>
+int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_out, const CUtensorMap& map_res,
+                      PersistentArgs args, cudaStream_t stream) {
+    constexpr int kEpiBytes = (BN / 64) * kTileM * 128;
+    constexpr int kEpiBuffers = HAS_RES ? 4 : 2;
+    constexpr int kBarrierBytes = (2 * kMaxRingStages + 18) * 8;
+    int bias_vectors = 0;
+    for (int e = 0; e < args.gemm.epi_count; ++e) bias_vectors += args.gemm.epi_kind[e] == kEpiBias;
+    const int bias_bytes = (bias_vectors * args.bias_stride * 4 + 1023) & ~1023;
+    args.w_offset = 0;
+    args.epi_offset = (args.filter_bytes + 1023) & ~1023;
+    args.ring_offset = args.epi_offset + kEpiBuffers * kEpiBytes;
+    int room = kSmemBudget - 1024 - kBarrierBytes - bias_bytes - args.ring_offset;
+    // K slices per handshake: the largest divisor of the K loop (<= 4) that still leaves >= 2 ring slots
+    int group = 1;
+    for (int candidate = 4; candidate >= 2; --candidate)
+        if (args.gemm.k_blocks % candidate == 0 && room / (candidate * kTileM * kBlockK * 2) >= 2) {
+            group = candidate;
+            break;
+        }
+    int stages = room / (group * kTileM * kBlockK * 2);
+    if (stages > kMaxRingStages) stages = kMaxRingStages;
+    if (stages < 2) return fail(kUnsupported, "tcgen05 conv: the filter does not leave room for an activation ring");
+    args.stages = stages;
+    args.group_k = group;
+    args.bias_offset = args.ring_offset + stages * group * kTileM * kBlockK * 2;
+    args.barrier_offset = args.bias_offset + bias_bytes;
+    const int dynamic = args.barrier_offset + kBarrierBytes + 1024;
+    static int configured = 0;
+    if (configured < dynamic) {
+        cudaError_t error = cudaFuncSetAttribute(umma_conv_persistent_kernel<BN, HAS_RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+        if (error != cudaSuccess) return fail(kExecutionFailed, "tcgen05 conv: cannot reserve %d bytes of shared memory: %s", kSmemBudget, cudaGetErrorString(error));
+        configured = kSmemBudget;
+    }
+    const int grid = args.total_tiles < sm_count() ? args.total_tiles : sm_count();
+    umma_conv_persistent_kernel<BN, HAS_RES><<<grid, kPersistentThreads, dynamic, stream>>>(map_a, map_b, map_out, map_res, args);
+    return check_launch("tcgen05 conv (persistent)");
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -537,6 +746,46 @@ int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStrea
     args.out_dtype = p.y.dtype;
     if (!translate_epilogue(p.epilogue_count, p.epilogue, p.extra, p.y, 1, true, K, tensors + 3, &args))
         return fail(kUnsupported, "CONV_FPROP: the fused epilogue is not one the tcgen05 kernel applies");
+    // Persistent kernel (TMA-store epilogue) when its preconditions hold; else one tile per CTA.
+    int residual_step = -1, full_steps = 0;
+    for (int e = 0; e < args.epi_count; ++e)
+        if (args.epi_kind[e] == kEpiFull) {
+            residual_step = e;
+            ++full_steps;
+        }
+    const int box_rows = pointwise ? kTileM : args.rows_per_tile * static_cast<int>(Q);
+    const bool whole_tiles = pointwise || P % args.rows_per_tile == 0;
+    const bool residual_ok = full_steps == 0 || (full_steps == 1 && args.epi_dtype[residual_step] == DFGPU_BF16);
+    const int64_t filter_bytes = K * R * S * C * 2;
+    const int epilogue_bytes = (full_steps ? 4 : 2) * (bn / 64) * kTileM * 128;
+    int bias_steps = 0;
+    for (int e = 0; e < args.epi_count; ++e) bias_steps += args.epi_kind[e] == kEpiBias;
+    const bool filter_fits = bias_steps * K <= kMaxBiasFloats &&
+                             filter_bytes + epilogue_bytes + 3 * kTileM * kBlockK * 2 + bias_steps * K * 4 + 6144 <= kSmemBudget;
+    if (p.reserved != 1 && p.y.dtype == DFGPU_BF16 && whole_tiles && residual_ok && filter_fits && N * P * Q < (1ll << 31) && bn <= 128) {
+        PersistentArgs pargs{};
+        pargs.gemm = args;
+        pargs.n_tiles = static_cast<int>(K / bn);
+        pargs.total_tiles = static_cast<int>(m_tiles) * pargs.n_tiles;
+        pargs.box_rows = box_rows;
+        pargs.filter_bytes = static_cast<int>(filter_bytes);
+        pargs.bias_stride = static_cast<int>(K);
+        CUtensorMap map_out, map_res;
+        uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N * P * Q)};
+        uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
+        uint32_t box[2] = {64, static_cast<uint32_t>(box_rows)};
+        status = make_map(&map_out, tensors[2], 2, dims, strides, box, "CONV_FPROP Y");
+        if (status) return status;
+        const void* residual = full_steps ? args.epi_data[residual_step] : tensors[2];
+        status = make_map(&map_res, residual, 2, dims, strides, box, "CONV_FPROP residual");
+        if (status) return status;
+        if (bn == 64) {
+            if (full_steps) return launch_persistent<64, true>(map_a, map_b, map_out, map_res, pargs, stream);
+            return launch_persistent<64, false>(map_a, map_b, map_out, map_res, pargs, stream);
+        }
+        if (full_steps) return launch_persistent<128, true>(map_a, map_b, map_out, map_res, pargs, stream);
+        return launch_persistent<128, false>(map_a, map_b, map_out, map_res, pargs, stream);
+    }
     dim3 grid(static_cast<unsigned>(m_tiles), static_cast<unsigned>(K / bn));
     return dispatch(bn, args.k_blocks, map_a, map_b, args, grid, stream);
 }
@@ -606,21 +855,18 @@ int launch_matmul_umma(const dfgpu_matmul_params& p, void* const* tensors, int k
     return dispatch(bn, args.k_blocks, map_a, map_b, args, grid, stream);
 }
 
-bool sdpa_umma_supported(const dfgpu_sdpa_params&) { return false; }
-int launch_sdpa_umma(const dfgpu_sdpa_params&, void* const*, void*, cudaStream_t) {
-    return fail(kUnsupported, "SDPA: the tcgen05 kernel is not built");
-}
-
 }  // namespace dfgpu
 
-// Reads and clears the device-side status word the bounded waits write (0 = none).
+// Reads and clears the device-side status words the bounded waits write (0 = none).
 // Synchronises the device; meant for tests and for the runtime's post-mortem path.
 extern "C" int dfgpu_device_status(int* status) {
     using namespace dfgpu;
     if (!status) return fail(kInvalidArgument, "device_status: null pointer");
-    int zero = 0;
-    cudaError_t error = cudaMemcpyFromSymbol(status, g_device_status, sizeof(int));
-    if (error == cudaSuccess) error = cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
-    if (error != cudaSuccess) return fail(kExecutionFailed, "device_status: %s", cudaGetErrorString(error));
+    int gemm = 0, sdpa = 0;
+    int code = read_and_clear_device_status(&gemm);
+    if (code) return code;
+    code = sdpa_umma_device_status(&sdpa);
+    if (code) return code;
+    *status = gemm ? gemm : sdpa;
     return kOk;
 }

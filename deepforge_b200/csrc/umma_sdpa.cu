@@ -1,0 +1,371 @@
+// SDPA forward on the 5th-generation tensor cores (bf16, head dim 128, contiguous K/V).
+//
+// One CTA owns a 128-row query tile of one (batch, head) and walks the key/value tiles of 128:
+//   warp 0     TMA producer: Q once, then K_0, V_0, K_1, V_1, ... into a ring of 32 KiB slots
+//   warp 1     one lane issues S_j = Q K_j^T into one of two TMEM score buffers (so S_{j+1} is
+//              multiplied while the softmax warps work on S_j) and O += P_j V_j into the TMEM
+//              output accumulator
+//   warps 2-5  softmax, one query row per thread: tcgen05.ld the scores, running max / sum in the
+//              exp2 domain, P_j as bf16 into a swizzled shared-memory tile (the A operand of the
+//              second product), final 1/sum, O and Stats stores.
+// The running maximum is only raised when it grows by more than 2^8 (the accumulator is rescaled
+// in TMEM then, which is rare); Stats = ln2 * (m + log2(l)) is exact whichever reference m is
+// in use. Causal graphs skip tiles above the diagonal and mask inside the diagonal tile.
+// Scores are scaled after the f32 dot product, invalid positions are -inf, as in the reference's
+// emit_sdpa_forward (lib/Compiler/SequenceGraph.cpp:2135-2341).
+#include "umma_ptx.cuh"
+
+namespace dfgpu {
+namespace {
+
+constexpr int kRows = 128;      // query rows per CTA
+constexpr int kKeys = 128;      // keys per tile
+constexpr int kHeadDim = 128;
+constexpr int kTileBytes = kRows * kHeadDim * 2;  // 32 KiB: one Q / K / V / P tile (two 64-column halves)
+constexpr int kHalfBytes = kTileBytes / 2;
+constexpr int kSlots = 3;       // K/V ring
+constexpr int kSdpaThreads = 192;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct SdpaUmmaArgs {
+    int32_t heads_q, heads_kv, seq_q, seq_kv;
+    int32_t q_tiles;
+    int32_t causal;
+    float scale_log2;  // attn_scale * log2(e)
+    float* stats;      // [B, Hq, Sq] or null
+    int64_t stats_batch_stride, stats_head_stride, stats_row_stride;
+};
+
+struct Smem {
+    static constexpr int kQ = 0;
+    static constexpr int kRing = kTileBytes;
+    static constexpr int kP = kRing + kSlots * kTileBytes;
+    static constexpr int kBarriers = kP + 2 * kTileBytes;
+    // q_full, kv_full[3], kv_empty[3], s_full[2], s_empty[2], p_full[2], pv_done[2]
+    static constexpr int kBarrierCount = 1 + 2 * kSlots + 8;
+    static constexpr int kTotal = kBarriers + kBarrierCount * 8 + 16;
+    static constexpr int kDynamic = kTotal + 1024;
+};
+
+__device__ __forceinline__ void tmem_store_32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+          "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+          "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__global__ void __launch_bounds__(kSdpaThreads, 1)
+sdpa_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o, SdpaUmmaArgs args) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + Smem::kBarriers;
+    const uint32_t q_full = bar_base;
+    auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
+    auto kv_empty = [&](int s) { return bar_base + 8u * (1 + kSlots + s); };
+    auto s_full = [&](int b) { return bar_base + 8u * (1 + 2 * kSlots + b); };
+    auto s_empty = [&](int b) { return bar_base + 8u * (3 + 2 * kSlots + b); };
+    auto p_full = [&](int b) { return bar_base + 8u * (5 + 2 * kSlots + b); };
+    auto pv_done = [&](int b) { return bar_base + 8u * (7 + 2 * kSlots + b); };
+    const uint32_t tmem_slot = bar_base + 8u * Smem::kBarrierCount;
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + Smem::kBarriers + 8 * Smem::kBarrierCount);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // heavy (late) causal tiles first
+    const int q_tile = args.q_tiles - 1 - static_cast<int>(blockIdx.x);
+    const int bh = blockIdx.y;
+    const int batch = bh / args.heads_q, head = bh - batch * args.heads_q;
+    const int kv_head = head / (args.heads_q / args.heads_kv);
+    const int q_row0 = (batch * args.heads_q + head) * args.seq_q + q_tile * kRows;
+    const int kv_row0 = (batch * args.heads_kv + kv_head) * args.seq_kv;
+    const int total_kv_tiles = args.seq_kv / kKeys;
+    const int kv_tiles = args.causal ? min(total_kv_tiles, q_tile + 1) : total_kv_tiles;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < kSlots; ++s) {
+            mbar_init(kv_full(s), 1);
+            mbar_init(kv_empty(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(s_full(b), 1);
+            mbar_init(s_empty(b), 4);
+            mbar_init(p_full(b), 4);
+            mbar_init(pv_done(b), 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+        tc_fence_before();
+    }
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+    const uint32_t tmem_o = tmem_base + 256;  // S0 at +0, S1 at +128, O at +256
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(q_full, kTileBytes);
+            tma_load_2d(smem_base + Smem::kQ, &map_q, 0, q_row0, q_full);
+            tma_load_2d(smem_base + Smem::kQ + kHalfBytes, &map_q, 64, q_row0, q_full);
+            for (int t = 0; t < 2 * kv_tiles; ++t) {
+                const int slot = t % kSlots;
+                if (!mbar_wait(kv_empty(slot), ((t / kSlots) & 1) ^ 1, 201)) break;
+                const CUtensorMap* map = (t & 1) ? &map_v : &map_k;
+                const int row = kv_row0 + (t >> 1) * kKeys;
+                const uint32_t dst = smem_base + Smem::kRing + slot * kTileBytes;
+                mbar_expect_tx(kv_full(slot), kTileBytes);
+                tma_load_2d(dst, map, 0, row, kv_full(slot));
+                tma_load_2d(dst + kHalfBytes, map, 64, row, kv_full(slot));
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // D f32, A/B bf16, M = 128, N = 128; the second product reads V as an MN-major B operand
+            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kKeys >> 3) << 17) | (static_cast<uint32_t>(kRows >> 4) << 24);
+            const uint32_t idesc_pv = idesc_qk | (1u << 16);
+            const uint32_t q_smem = smem_base + Smem::kQ;
+            bool ok = mbar_wait(q_full, 0, 202);
+            auto issue_scores = [&](int j) {
+                const int t = 2 * j, slot = t % kSlots, b = j & 1;
+                if (ok) ok = mbar_wait(kv_full(slot), (t / kSlots) & 1, 203);
+                if (ok) ok = mbar_wait(s_empty(b), ((j >> 1) & 1) ^ 1, 204);
+                tc_fence_after();
+                if (ok) {
+                    const uint32_t k_smem = smem_base + Smem::kRing + slot * kTileBytes;
+#pragma unroll
+                    for (int k = 0; k < kHeadDim / 16; ++k) {
+                        const uint32_t offset = (k >> 2) * kHalfBytes + (k & 3) * 32;
+                        umma_bf16(tmem_base + b * 128, smem_desc(q_smem + offset, 16, 1024), smem_desc(k_smem + offset, 16, 1024), idesc_qk, k != 0 ? 1u : 0u);
+                    }
+                }
+                umma_commit(kv_empty(slot));
+                umma_commit(s_full(b));
+            };
+            issue_scores(0);
+            for (int j = 0; j < kv_tiles; ++j) {
+                if (j + 1 < kv_tiles) issue_scores(j + 1);
+                const int t = 2 * j + 1, slot = t % kSlots, b = j & 1;
+                if (ok) ok = mbar_wait(p_full(b), (j >> 1) & 1, 205);
+                if (ok) ok = mbar_wait(kv_full(slot), (t / kSlots) & 1, 206);
+                tc_fence_after();
+                if (ok) {
+                    const uint32_t p_smem = smem_base + Smem::kP + b * kTileBytes;
+                    const uint32_t v_smem = smem_base + Smem::kRing + slot * kTileBytes;
+#pragma unroll
+                    for (int k = 0; k < kKeys / 16; ++k) {
+                        const uint64_t desc_p = smem_desc(p_smem + (k >> 2) * kHalfBytes + (k & 3) * 32, 16, 1024);
+                        const uint64_t desc_v = smem_desc(v_smem + k * 2048, kHalfBytes, 1024);
+                        umma_bf16(tmem_o, desc_p, desc_v, idesc_pv, (j | k) != 0 ? 1u : 0u);
+                    }
+                }
+                umma_commit(kv_empty(slot));
+                umma_commit(pv_done(b));
+            }
+        }
+    } else {
+        const int quadrant = warp & 3;
+        const int row = quadrant * 32 + lane;
+        const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
+        const int q_index = q_tile * kRows + row;  // query position inside the sequence
+        float m_ref = -INFINITY;  // reference maximum (scaled, log2 domain)
+        float l_sum = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < kv_tiles; ++j) {
+            const int b = j & 1;
+            if (ok) ok = mbar_wait(s_full(b), (j >> 1) & 1, 207);
+            tc_fence_after();
+            float s[128];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t raw[32];
+                tmem_load_32(tmem_base + lane_base + b * 128 + c * 32, raw);
+                tmem_load_wait();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(raw[e]) * args.scale_log2;
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_empty(b));
+            if (args.causal && j == q_tile) {
+                const int limit = q_index - j * kKeys;  // keys 0..limit of this tile are visible
+#pragma unroll
+                for (int e = 0; e < 128; ++e)
+                    if (e > limit) s[e] = -INFINITY;
+            }
+            float tile_max = s[0];
+#pragma unroll
+            for (int e = 1; e < 128; ++e) tile_max = fmaxf(tile_max, s[e]);
+            // raise the reference only when it would grow by more than the threshold (or on the first tile)
+            const bool raise = tile_max > m_ref + kRescaleThreshold;
+            const bool any_raise = __any_sync(0xffffffffu, raise) != 0;
+            if (any_raise) {
+                const float m_new = fmaxf(m_ref, tile_max);
+                const float alpha = m_ref == -INFINITY ? 0.0f : exp2f(m_ref - m_new);
+                l_sum *= alpha;
+                m_ref = m_new;
+                if (j > 0) {
+                    // the accumulator holds P V up to tile j-1: wait for that product, then rescale it in TMEM
+                    if (ok) ok = mbar_wait(pv_done((j - 1) & 1), ((j - 1) >> 1) & 1, 208);
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t raw[32];
+                        tmem_load_32(tmem_o + lane_base + c * 32, raw);
+                        tmem_load_wait();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) raw[e] = __float_as_uint(__uint_as_float(raw[e]) * alpha);
+                        tmem_store_32(tmem_o + lane_base + c * 32, raw);
+                    }
+                    tmem_store_wait();
+                    tc_fence_before();
+                }
+            }
+            // P buffer b was last read by the product of tile j-2
+            if (ok) ok = mbar_wait(pv_done(b), ((j >> 1) & 1) ^ 1, 209);
+            uint8_t* p_row = generic_base + Smem::kP + b * kTileBytes + row * 128;
+            float tile_sum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {  // 16-byte units: 8 keys each
+                uint32_t w[4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const float p0 = exp2f(s[c * 8 + 2 * t] - m_ref);
+                    const float p1 = exp2f(s[c * 8 + 2 * t + 1] - m_ref);
+                    tile_sum += p0 + p1;
+                    __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+                    w[t] = *reinterpret_cast<uint32_t*>(&pair);
+                }
+                const int half = c >> 3, unit = c & 7;
+                *reinterpret_cast<uint4*>(p_row + half * kHalfBytes + ((unit ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            l_sum += tile_sum;
+            fence_async_shared();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full(b));
+        }
+        // last product done -> normalise, store O through shared memory and the TMA unit
+        const int last = kv_tiles - 1;
+        if (ok) ok = mbar_wait(pv_done(last & 1), (last >> 1) & 1, 210);
+        tc_fence_after();
+        const float inverse = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
+        uint8_t* o_row = generic_base + Smem::kP + row * 128;  // P buffer 0 doubles as the output staging tile
+        // P buffer 0 may still be the operand of the last product only if last is even: that product is done (waited above)
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            uint32_t raw[32];
+            tmem_load_32(tmem_o + lane_base + c * 32, raw);
+            tmem_load_wait();
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                uint32_t w[4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(raw[u * 8 + 2 * t]) * inverse, __uint_as_float(raw[u * 8 + 2 * t + 1]) * inverse);
+                    w[t] = *reinterpret_cast<uint32_t*>(&pair);
+                }
+                const int unit16 = c * 4 + u;  // 16-byte unit inside the 256-byte output row
+                const int half = unit16 >> 3, unit = unit16 & 7;
+                *reinterpret_cast<uint4*>(o_row + half * kHalfBytes + ((unit ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+        if (args.stats != nullptr && ok)
+            args.stats[batch * args.stats_batch_stride + head * args.stats_head_stride + static_cast<int64_t>(q_index) * args.stats_row_stride] =
+                l_sum > 0.0f ? 0.6931471805599453f * (m_ref + log2f(l_sum)) : -INFINITY;
+        tc_fence_before();
+        fence_async_shared();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+            if (ok && g_device_status == 0) {
+                tma_store_2d(&map_o, smem_base + Smem::kP, 0, q_row0);
+                tma_store_2d(&map_o, smem_base + Smem::kP + kHalfBytes, 64, q_row0);
+            }
+            tma_store_commit();
+            tma_store_wait_all();
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+bool packed_bhsd(const dfgpu_tensor& t) {
+    return t.rank == 4 && t.stride[3] == 1 && t.stride[2] == t.dim[3] && t.stride[1] == t.dim[2] * t.dim[3] &&
+           t.stride[0] == t.dim[1] * t.dim[2] * t.dim[3];
+}
+
+}  // namespace
+
+bool sdpa_umma_supported(const dfgpu_sdpa_params& p) {
+    if (p.q.dtype != DFGPU_BF16 || p.k.dtype != DFGPU_BF16 || p.v.dtype != DFGPU_BF16 || p.o.dtype != DFGPU_BF16) return false;
+    if (p.q.rank != 4 || p.k.rank != 4 || p.v.rank != 4 || p.o.rank != 4) return false;
+    if (p.q.dim[3] != kHeadDim || p.v.dim[3] != kHeadDim || p.k.dim[3] != kHeadDim) return false;
+    if (p.page_table_k.rank || p.page_table_v.rank || p.padding_mask || p.has_left_bound || p.bottom_right) return false;
+    if (p.max.rank || p.sum_exp.rank) return false;
+    if (!packed_bhsd(p.q) || !packed_bhsd(p.k) || !packed_bhsd(p.v) || !packed_bhsd(p.o)) return false;
+    const int64_t sq = p.q.dim[2], skv = p.k.dim[2];
+    if (p.s_kv != skv || p.v.dim[2] != skv || p.k.dim[1] != p.v.dim[1]) return false;
+    if (sq % kRows != 0 || skv % kKeys != 0 || sq < kRows || skv < kKeys) return false;
+    if (p.has_right_bound && (p.right_bound != 0 || sq != skv)) return false;  // causal, top-left aligned, square
+    if (p.stats.rank && p.stats.dtype != DFGPU_F32) return false;
+    const int64_t rows_q = p.q.dim[0] * p.q.dim[1] * sq, rows_kv = p.k.dim[0] * p.k.dim[1] * skv;
+    if (rows_q >= (1ll << 31) || rows_kv >= (1ll << 31) || p.q.dim[0] * p.q.dim[1] > 65535) return false;
+    return true;
+}
+
+int launch_sdpa_umma(const dfgpu_sdpa_params& p, void* const* tensors, void* scratch, cudaStream_t stream) {
+    (void)scratch;
+    for (int i = 0; i < 4; ++i)
+        if ((reinterpret_cast<uintptr_t>(tensors[i]) & 15u) != 0) return fail(kInvalidArgument, "SDPA: the tcgen05 kernel needs 16-byte aligned Q, K, V and O");
+    const int64_t batch = p.q.dim[0], hq = p.q.dim[1], hkv = p.k.dim[1], sq = p.q.dim[2], skv = p.k.dim[2];
+    CUtensorMap map_q, map_k, map_v, map_o;
+    uint32_t box[2] = {64, kRows};
+    uint64_t strides[1] = {kHeadDim * 2};
+    uint64_t dims_q[2] = {kHeadDim, static_cast<uint64_t>(batch * hq * sq)};
+    uint64_t dims_kv[2] = {kHeadDim, static_cast<uint64_t>(batch * hkv * skv)};
+    int status = make_map(&map_q, tensors[0], 2, dims_q, strides, box, "SDPA Q");
+    if (!status) status = make_map(&map_k, tensors[1], 2, dims_kv, strides, box, "SDPA K");
+    if (!status) status = make_map(&map_v, tensors[2], 2, dims_kv, strides, box, "SDPA V");
+    if (!status) status = make_map(&map_o, tensors[3], 2, dims_q, strides, box, "SDPA O");
+    if (status) return status;
+    SdpaUmmaArgs args{};
+    args.heads_q = static_cast<int>(hq);
+    args.heads_kv = static_cast<int>(hkv);
+    args.seq_q = static_cast<int>(sq);
+    args.seq_kv = static_cast<int>(skv);
+    args.q_tiles = static_cast<int>(sq / kRows);
+    args.causal = p.has_right_bound ? 1 : 0;
+    args.scale_log2 = p.attn_scale * 1.4426950408889634f;
+    args.stats = p.stats.rank ? static_cast<float*>(tensors[4]) : nullptr;
+    if (p.stats.rank) {
+        args.stats_batch_stride = p.stats.stride[0];
+        args.stats_head_stride = p.stats.stride[1];
+        args.stats_row_stride = p.stats.stride[2];
+    }
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t error = cudaFuncSetAttribute(sdpa_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kDynamic);
+        if (error != cudaSuccess) return fail(kExecutionFailed, "SDPA: cannot reserve %d bytes of shared memory: %s", Smem::kDynamic, cudaGetErrorString(error));
+        configured = true;
+    }
+    dim3 grid(static_cast<unsigned>(args.q_tiles), static_cast<unsigned>(batch * hq));
+    sdpa_umma_kernel<<<grid, kSdpaThreads, Smem::kDynamic, stream>>>(map_q, map_k, map_v, map_o, args);
+    return check_launch("SDPA (tcgen05)");
+}
+
+int sdpa_umma_device_status(int* status) { return read_and_clear_device_status(status); }
+
+}  // namespace dfgpu

@@ -143,7 +143,7 @@ typedef struct dfgpu_conv_params {
     int32_t epilogue_count;
     dfgpu_epilogue_step epilogue[DFGPU_MAX_EPILOGUE];
     int32_t kernel;
-    int32_t reserved;
+    int32_t reserved; /* 0; 1 selects the one-tile-per-CTA form of the tcgen05 kernel (cross-check) */
 } dfgpu_conv_params;
 int dfgpu_query_conv_fprop(const dfgpu_conv_params*, dfgpu_plan_info*);
 int dfgpu_conv_fprop(const dfgpu_conv_params*, void* const* tensors, void* scratch, void* stream);

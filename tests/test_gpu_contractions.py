@@ -83,7 +83,7 @@ def test_relu_default_clips_inf_to_flt_max_and_keeps_nan():
 
 
 def run_conv(dtype, x_dims, w_dims, pre, post, stride, dilation, kernel, x_strides=None, w_strides=None, y_strides=None,
-             reverse=False, epilogue=(), extras=(), seed=1):
+             reverse=False, epilogue=(), extras=(), seed=1, reserved=0):
     n, c, h, w = x_dims
     k, cg, r, s = w_dims
     oh = (h + pre[0] + post[0] - (dilation[0] * (r - 1) + 1)) // stride[0] + 1
@@ -104,6 +104,7 @@ def run_conv(dtype, x_dims, w_dims, pre, post, stride, dilation, kernel, x_strid
     for i in range(2):
         p.pre_pad[i], p.post_pad[i], p.stride[i], p.dilation[i] = pre[i], post[i], stride[i], dilation[i]
     p.reverse_filter, p.kernel = int(reverse), kernel
+    p.reserved = reserved
     extra_dev = [None, None]
     for i, (dims, strides, values) in enumerate(extras):
         p.extra[i] = tensor(dtype, dims, strides)

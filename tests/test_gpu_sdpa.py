@@ -176,3 +176,49 @@ def test_paged_decode_zero_length_sequence_gives_zero_output():
     assert info.kernel == dfgpu.SDPA_PAGED_DECODE
     assert np.all(o[0] == 0.0) and np.all(rows[0].reshape(batch, 8)[0] == -INF)
     close_bf16(o, o_ref)
+
+
+@pytest.fixture(autouse=True)
+def _device_healthy():
+    yield
+    assert dfgpu.device_status() == 0, "a bounded wait expired inside a kernel"
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("batch,hq,hkv,seq", [(1, 2, 2, 128), (2, 4, 2, 384), (1, 8, 1, 640)])
+def test_umma_sdpa_matches_oracle(causal, batch, hq, hkv, seq):
+    flags = dict(has_right_bound=1, right_bound=0) if causal else {}
+    info, o, o_ref, rows, rows_ref = both(BF16, [batch, hq, seq, 128], [batch, hkv, seq, 128], [batch, hkv, seq, 128], seq,
+                                          128 ** -0.5, dfgpu.SDPA_UMMA, stats=False, seed=17, **flags)
+    assert info.kernel == dfgpu.SDPA_UMMA
+    close_bf16(o, o_ref)
+
+
+def test_umma_sdpa_stats_and_large_scores():
+    """Stats = max + ln(sum) in natural log; a 4x larger scale makes the running maximum jump between
+    tiles, which exercises the in-TMEM rescale of the output accumulator."""
+    import gpu_util as g
+    batch, heads, seq = 1, 2, 512
+    p = dfgpu.SdpaParams()
+    dims = [batch, heads, seq, 128]
+    p.q = p.k = p.v = p.o = tensor(BF16, dims)
+    p.stats = tensor(F32, [batch, heads, seq, 1])
+    p.attn_scale, p.s_kv, p.has_right_bound, p.right_bound = 4 * 128 ** -0.5, seq, 1, 0
+    raw = [synthetic.normal(23, i + 1, batch * heads * seq * 128) for i in range(3)]
+    dev = [g.to_device(synthetic.to_bf16_bits(a)) for a in raw]
+    outs = {}
+    for kernel in (dfgpu.SDPA_UMMA, dfgpu.SDPA_ROWWISE):
+        p.kernel = kernel
+        do, ds = g.device_zeros(batch * heads * seq * 128 * 2), g.device_zeros(batch * heads * seq * 4)
+        dfgpu.sdpa_forward(p, [g.ptr(dev[0]), g.ptr(dev[1]), g.ptr(dev[2]), g.ptr(do), g.ptr(ds), 0, 0, 0, 0, 0, 0])
+        outs[kernel] = (synthetic.bf16_bits_to_f32(g.to_host(do, np.uint16)), g.to_host(ds, np.float32).copy())
+    op = oracle.SdpaParams()
+    op.q = op.k = op.v = op.o = tensor(F32, dims)
+    op.stats = tensor(F32, [batch, heads, seq, 1])
+    op.attn_scale, op.s_kv, op.has_right_bound, op.right_bound = p.attn_scale, seq, 1, 0
+    rounded = [synthetic.round_to_bf16(a) for a in raw]
+    o_ref, s_ref = np.zeros(batch * heads * seq * 128, dtype=np.float32), np.zeros(batch * heads * seq, dtype=np.float32)
+    oracle.sdpa_forward(op, rounded + [o_ref, s_ref] + [None] * 6)
+    for kernel in outs:
+        close_bf16(outs[kernel][0], o_ref)
+        close_f32(outs[kernel][1], s_ref, 2e-3)

@@ -71,14 +71,14 @@ def test_matmul_umma_bf16_out_bias_relu():
     check_bf16(out, ref)
 
 
-def conv_case(n, c, h, w, k, r, pad, epilogue=(), extras=(), ydtype=BF16, seed=6):
+def conv_case(n, c, h, w, k, r, pad, epilogue=(), extras=(), ydtype=BF16, seed=6, one_tile_per_cta=False):
     x_dims, w_dims = [n, c, h, w], [k, c, r, r]
     p_out = h + 2 * pad - r + 1
     q_out = w + 2 * pad - r + 1
     y_dims = [n, k, p_out, q_out]
     return run_conv(BF16, x_dims, w_dims, [pad, pad], [pad, pad], [1, 1], [1, 1], dfgpu.CONV_UMMA_BF16,
                     nhwc_strides(x_dims), nhwc_strides(w_dims), nhwc_strides(y_dims), epilogue=epilogue,
-                    extras=extras, seed=seed)
+                    extras=extras, seed=seed, reserved=int(one_tile_per_cta))
 
 
 @pytest.mark.parametrize("n,c,h,w,k,r,pad", [
@@ -89,19 +89,29 @@ def conv_case(n, c, h, w, k, r, pad, epilogue=(), extras=(), ydtype=BF16, seed=6
     (2, 128, 10, 12, 128, 3, 0),  # no padding, two K slices per tap
     (1, 64, 6, 5, 256, 3, 2),     # wide padding, BN = 256
 ])
-def test_conv_umma_matches_oracle(n, c, h, w, k, r, pad):
-    info, out, ref = conv_case(n, c, h, w, k, r, pad)
+@pytest.mark.parametrize("one_tile_per_cta", [False, True])
+def test_conv_umma_matches_oracle(n, c, h, w, k, r, pad, one_tile_per_cta):
+    # both forms of the kernel: the persistent one (TMA-store epilogue) and one tile per CTA
+    info, out, ref = conv_case(n, c, h, w, k, r, pad, one_tile_per_cta=one_tile_per_cta)
     assert info.kernel == dfgpu.CONV_UMMA_BF16
     check_bf16(out, ref)
 
 
-def test_conv_umma_fused_bias_relu_and_residual():
-    n, c, h, w, k = 2, 64, 12, 12, 256
+@pytest.mark.parametrize("one_tile_per_cta", [False, True])
+@pytest.mark.parametrize("n,c,h,w,k,r,pad", [(2, 64, 12, 12, 256, 1, 0), (3, 64, 16, 16, 64, 3, 1), (40, 64, 28, 28, 128, 1, 0)])
+def test_conv_umma_fused_bias_relu_and_residual(n, c, h, w, k, r, pad, one_tile_per_cta):
     bias = synthetic.uniform(3, 5, k, -0.1, 0.1)
     residual = synthetic.normal(3, 6, n * k * h * w)
     y_strides = nhwc_strides([n, k, h, w])
-    info, out, ref = conv_case(n, c, h, w, k, 1, 0,
+    info, out, ref = conv_case(n, c, h, w, k, r, pad,
                                epilogue=[step(dfgpu.EPI_ADD, 0), step(dfgpu.EPI_RELU), step(dfgpu.EPI_ADD, 1)],
-                               extras=[([1, k, 1, 1], [k, 1, k, k], bias), ([n, k, h, w], y_strides, residual)])
+                               extras=[([1, k, 1, 1], [k, 1, k, k], bias), ([n, k, h, w], y_strides, residual)],
+                               one_tile_per_cta=one_tile_per_cta)
     assert info.kernel == dfgpu.CONV_UMMA_BF16
+    check_bf16(out, ref)
+
+
+def test_conv_umma_many_tiles_per_cta():
+    # 1568 tiles on 148 SMs: every CTA of the persistent kernel walks ~10 tiles through both accumulators
+    info, out, ref = conv_case(16, 64, 112, 112, 64, 1, 0, epilogue=[step(dfgpu.EPI_RELU)], seed=9)
     check_bf16(out, ref)
