@@ -363,14 +363,14 @@ sdpa_paged_decode_kernel(SdpaArgs a, float* __restrict__ partial, int max_chunks
 
 // One CTA of 128 threads per (batch, query head): combine the chunk partials.
 __global__ void __launch_bounds__(128)
-sdpa_decode_merge_kernel(SdpaArgs a, const float* __restrict__ partial, int max_chunks) {
+sdpa_decode_merge_kernel(SdpaArgs a, const float* __restrict__ partial, int max_chunks, int chunk_keys) {
     const int64_t row = blockIdx.x;  // b * Hq + h
     const int64_t hq = a.q.dim[1];
     const int64_t ib = row / hq, ih = row % hq;
     const int d = threadIdx.x;
     int64_t lo, hi;
     valid_range(a, ib, 0, lo, hi);
-    int chunks = hi > 0 ? static_cast<int>((hi + kDecodeChunk - 1) / kDecodeChunk) : 0;
+    int chunks = hi > 0 ? static_cast<int>((hi + chunk_keys - 1) / chunk_keys) : 0;
     if (chunks > max_chunks) chunks = max_chunks;
     const float* base = partial + row * max_chunks * kPartialStride;
     float total_max = -INFINITY;
@@ -484,7 +484,8 @@ int decode_chunks(const dfgpu_sdpa_params& p) { return static_cast<int>((p.s_kv 
 
 int choose_kernel(const dfgpu_sdpa_params& p, int& kernel) {
     int automatic = DFGPU_SDPA_ROWWISE;
-    if (decode_supported(p)) automatic = DFGPU_SDPA_PAGED_DECODE;
+    if (decode_umma_supported(p)) automatic = DFGPU_SDPA_PAGED_DECODE_UMMA;
+    else if (decode_supported(p)) automatic = DFGPU_SDPA_PAGED_DECODE;
     else if (sdpa_umma_supported(p)) automatic = DFGPU_SDPA_UMMA;
     kernel = p.kernel == DFGPU_SDPA_AUTO ? automatic : p.kernel;
     if (kernel == DFGPU_SDPA_ROWWISE) {
@@ -497,6 +498,10 @@ int choose_kernel(const dfgpu_sdpa_params& p, int& kernel) {
     }
     if (kernel == DFGPU_SDPA_UMMA) {
         if (!sdpa_umma_supported(p)) return fail(kUnsupported, "SDPA: the tcgen05 kernel does not cover this shape, layout or mask");
+        return kOk;
+    }
+    if (kernel == DFGPU_SDPA_PAGED_DECODE_UMMA) {
+        if (!decode_umma_supported(p)) return fail(kUnsupported, "SDPA: the TMA paged decode kernel needs Sq=1, bf16, D=128, packed paged K and V, page size 16..128, group size 1/2/4/8");
         return kOk;
     }
     return fail(kInvalidArgument, "SDPA: unknown kernel id %d", kernel);
@@ -522,6 +527,10 @@ extern "C" int dfgpu_query_sdpa_forward(const dfgpu_sdpa_params* p, dfgpu_plan_i
         info->launches = 2;
         info->scratch_bytes = p->q.dim[0] * p->q.dim[1] * decode_chunks(*p) * kPartialStride * static_cast<int64_t>(sizeof(float));
     }
+    if (kernel == DFGPU_SDPA_PAGED_DECODE_UMMA) {
+        info->launches = 2;
+        info->scratch_bytes = decode_umma_scratch_bytes(*p);
+    }
     return kOk;
 }
 
@@ -535,6 +544,14 @@ extern "C" int dfgpu_sdpa_forward(const dfgpu_sdpa_params* p, void* const* tenso
     if (status) return status;
     cudaStream_t stream = as_stream(stream_handle);
     if (kernel == DFGPU_SDPA_UMMA) return launch_sdpa_umma(*p, tensors, scratch, stream);
+    if (kernel == DFGPU_SDPA_PAGED_DECODE_UMMA) {
+        if (!scratch || !aligned16(scratch)) return fail(kInvalidArgument, "SDPA: the paged decode kernel needs its 16-byte aligned scratch buffer");
+        status = launch_decode_umma(*p, tensors, scratch, stream);
+        if (status) return status;
+        const int chunks = decode_umma_chunks(*p);
+        sdpa_decode_merge_kernel<<<static_cast<unsigned>(p->q.dim[0] * p->q.dim[1]), kDecodeD, 0, stream>>>(a, static_cast<const float*>(scratch), chunks, 1024);
+        return check_launch("SDPA decode merge");
+    }
     if (kernel == DFGPU_SDPA_PAGED_DECODE) {
         if (!scratch) return fail(kInvalidArgument, "SDPA: the paged decode kernel needs its scratch buffer");
         if (!aligned16(a.q_data) || !aligned16(a.k_data) || !aligned16(a.v_data) || !aligned16(scratch))
@@ -551,7 +568,7 @@ extern "C" int dfgpu_sdpa_forward(const dfgpu_sdpa_params* p, void* const* tenso
         }
         status = check_launch("SDPA paged decode");
         if (status) return status;
-        sdpa_decode_merge_kernel<<<static_cast<unsigned>(p->q.dim[0] * p->q.dim[1]), kDecodeD, 0, stream>>>(a, partial, chunks);
+        sdpa_decode_merge_kernel<<<static_cast<unsigned>(p->q.dim[0] * p->q.dim[1]), kDecodeD, 0, stream>>>(a, partial, chunks, kDecodeChunk);
         return check_launch("SDPA decode merge");
     }
     int64_t rows = p->q.dim[0] * p->q.dim[1] * p->q.dim[2];
@@ -633,6 +650,6 @@ extern "C" int dfgpu_sdpa_paged_decode_static(const dfgpu_sdpa_params* p, void* 
     }
     status = check_launch("SDPA static decode");
     if (status) return status;
-    sdpa_decode_merge_kernel<<<static_cast<unsigned>(p->q.dim[0] * p->q.dim[1]), kDecodeD, 0, stream>>>(a, partial, chunks);
+    sdpa_decode_merge_kernel<<<static_cast<unsigned>(p->q.dim[0] * p->q.dim[1]), kDecodeD, 0, stream>>>(a, partial, chunks, kDecodeChunk);
     return check_launch("SDPA static decode merge");
 }

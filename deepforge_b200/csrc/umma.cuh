@@ -18,4 +18,12 @@ bool sdpa_umma_supported(const dfgpu_sdpa_params& p);
 int launch_sdpa_umma(const dfgpu_sdpa_params& p, void* const* tensors, void* scratch, cudaStream_t stream);
 int sdpa_umma_device_status(int* status);  // reads and clears that unit's status word
 
+// Paged-KV decode on TMA + tcgen05 (bf16, head dim 128, Sq = 1); partials go to `scratch`, the
+// CUDA-core merge kernel in sdpa.cu finishes the job.
+bool decode_umma_supported(const dfgpu_sdpa_params& p);
+int decode_umma_chunks(const dfgpu_sdpa_params& p);
+int64_t decode_umma_scratch_bytes(const dfgpu_sdpa_params& p);
+int launch_decode_umma(const dfgpu_sdpa_params& p, void* const* tensors, void* scratch, cudaStream_t stream);
+int decode_umma_device_status(int* status);
+
 }  // namespace dfgpu

@@ -862,11 +862,13 @@ int launch_matmul_umma(const dfgpu_matmul_params& p, void* const* tensors, int k
 extern "C" int dfgpu_device_status(int* status) {
     using namespace dfgpu;
     if (!status) return fail(kInvalidArgument, "device_status: null pointer");
-    int gemm = 0, sdpa = 0;
+    int gemm = 0, sdpa = 0, decode = 0;
     int code = read_and_clear_device_status(&gemm);
     if (code) return code;
     code = sdpa_umma_device_status(&sdpa);
     if (code) return code;
-    *status = gemm ? gemm : sdpa;
+    code = decode_umma_device_status(&decode);
+    if (code) return code;
+    *status = gemm ? gemm : (sdpa ? sdpa : decode);
     return kOk;
 }

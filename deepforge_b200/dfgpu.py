@@ -23,7 +23,7 @@ BSQ_AUTO, BSQ_GENERIC, BSQ_ROW32, BSQ_COL32 = range(4)
 BSD_AUTO, BSD_GENERIC, BSD_PACKED = range(3)
 CONV_AUTO, CONV_DIRECT, CONV_IGEMM_FFMA, CONV_UMMA_BF16 = range(4)
 MATMUL_AUTO, MATMUL_FFMA, MATMUL_UMMA_BF16, MATMUL_UMMA_MXF8 = range(4)
-SDPA_AUTO, SDPA_ROWWISE, SDPA_PAGED_DECODE, SDPA_UMMA = range(4)
+SDPA_AUTO, SDPA_ROWWISE, SDPA_PAGED_DECODE, SDPA_UMMA, SDPA_PAGED_DECODE_UMMA = range(5)
 
 
 class Tensor(C.Structure):

@@ -172,7 +172,13 @@ int dfgpu_matmul(const dfgpu_matmul_params*, void* const* tensors, void* scratch
    :1839-1889 paged loads, :1988-2091 validity, :2135-2341 scores and softmax
    row, :2416-2582 outputs). tensors: {Q, K, V, O, Stats, Max, Sum_exp,
    SEQ_LEN_Q, SEQ_LEN_KV, Page_table_K, Page_table_V} (null when absent). */
-enum { DFGPU_SDPA_AUTO = 0, DFGPU_SDPA_ROWWISE = 1, DFGPU_SDPA_PAGED_DECODE = 2, DFGPU_SDPA_UMMA = 3 };
+enum {
+    DFGPU_SDPA_AUTO = 0,
+    DFGPU_SDPA_ROWWISE = 1,           /* general kernel on CUDA cores */
+    DFGPU_SDPA_PAGED_DECODE = 2,      /* split-KV paged decode on CUDA cores */
+    DFGPU_SDPA_UMMA = 3,              /* tcgen05 forward, bf16, D = 128, contiguous K/V */
+    DFGPU_SDPA_PAGED_DECODE_UMMA = 4  /* paged decode streamed by TMA, products on tcgen05 */
+};
 typedef struct dfgpu_sdpa_params {
     dfgpu_tensor q, k, v, o;
     dfgpu_tensor stats, max, sum_exp;

@@ -185,7 +185,7 @@ def test_c5_paged_decode_small_and_generic_agree():
     wl = workloads.c5(batch=6, hq=8, hkv=2, pages=64, block=64, max_len=1024, min_len=64)
     for options in (0,):
         s = harness.Session(wl, options=options)
-        assert "kernel=2" in s.exe.plan_text()
+        assert "kernel=4" in s.exe.plan_text()  # the TMA-streamed paged decode kernel
         s.run()
         ins, _ = oracle_inputs(wl, s)
         ref = graph_oracle.run(wl.document, ins)

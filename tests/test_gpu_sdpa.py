@@ -147,8 +147,11 @@ def _paged_inputs(batch, hq, hkv, pages, block, max_len, seed, lengths=None):
     return np.asarray(lengths, dtype=np.int32), tk.astype(np.int32), tv.astype(np.int32)
 
 
+@pytest.mark.parametrize("kernel", [dfgpu.SDPA_PAGED_DECODE, dfgpu.SDPA_PAGED_DECODE_UMMA])
 @pytest.mark.parametrize("group,block", [(4, 64), (1, 16), (8, 128), (2, 256)])
-def test_paged_decode_matches_oracle(group, block):
+def test_paged_decode_matches_oracle(group, block, kernel):
+    if kernel == dfgpu.SDPA_PAGED_DECODE_UMMA and block > 128:
+        pytest.skip("the TMA kernel takes pages of at most 128 tokens")
     batch, hkv, pages, max_len = 5, 2, 64, 700
     hq = hkv * group
     lengths, tk, tv = _paged_inputs(batch, hq, hkv, pages, block, max_len, seed=31 + group)
@@ -157,8 +160,8 @@ def test_paged_decode_matches_oracle(group, block):
     tk[2, 1] = -1          # invalid page ids read as zeros
     tv[2, 0] = pages + 7
     info, o, o_ref, rows, rows_ref = both(BF16, [batch, hq, 1, 128], [pages, hkv, block, 128], [pages, hkv, block, 128], max_len,
-                                          128 ** -0.5, dfgpu.SDPA_PAGED_DECODE, seq=([1] * batch, lengths), tables=(tk, tv))
-    assert info.kernel == dfgpu.SDPA_PAGED_DECODE and info.scratch_bytes > 0 and info.launches == 2
+                                          128 ** -0.5, kernel, seq=([1] * batch, lengths), tables=(tk, tv))
+    assert info.kernel == kernel and info.scratch_bytes > 0 and info.launches == 2
     close_bf16(o, o_ref)
     for a, r in zip(rows, rows_ref):
         close_f32(a, r, 1e-3)
@@ -173,7 +176,7 @@ def test_paged_decode_zero_length_sequence_gives_zero_output():
     lengths, tk, tv = _paged_inputs(batch, 8, hkv, pages, block, max_len, seed=3, lengths=[0, 256, 100])
     info, o, o_ref, rows, rows_ref = both(BF16, [batch, 8, 1, 128], [pages, hkv, block, 128], [pages, hkv, block, 128], max_len,
                                           0.1, dfgpu.SDPA_AUTO, seq=([1] * batch, lengths), tables=(tk, tv))
-    assert info.kernel == dfgpu.SDPA_PAGED_DECODE
+    assert info.kernel == dfgpu.SDPA_PAGED_DECODE_UMMA
     assert np.all(o[0] == 0.0) and np.all(rows[0].reshape(batch, 8)[0] == -INF)
     close_bf16(o, o_ref)
 
@@ -222,3 +225,17 @@ def test_umma_sdpa_stats_and_large_scores():
     for kernel in outs:
         close_bf16(outs[kernel][0], o_ref)
         close_f32(outs[kernel][1], s_ref, 2e-3)
+
+
+def test_tma_paged_decode_long_sequences_and_windows():
+    """Several CTAs per sequence (chunks of 1024 keys), a left bound that skips whole leading tiles,
+    and a bottom-right aligned right bound."""
+    batch, hq, hkv, pages, block, max_len = 3, 8, 2, 160, 64, 3000
+    lengths, tk, tv = _paged_inputs(batch, hq, hkv, pages, block, max_len, seed=77, lengths=[3000, 1025, 2048])
+    for flags in ({}, dict(has_left_bound=1, left_bound=1500, bottom_right=1), dict(has_right_bound=1, right_bound=-10, bottom_right=1)):
+        outs = []
+        for kernel in (dfgpu.SDPA_PAGED_DECODE_UMMA, dfgpu.SDPA_ROWWISE):
+            info, o, o_ref, rows, rows_ref = both(BF16, [batch, hq, 1, 128], [pages, hkv, block, 128], [pages, hkv, block, 128], max_len,
+                                                  128 ** -0.5, kernel, seq=([1] * batch, lengths), tables=(tk, tv), **flags)
+            close_bf16(o, o_ref)
+            close_f32(rows[0], rows_ref[0], 1e-3)
