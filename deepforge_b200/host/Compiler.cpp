@@ -650,6 +650,8 @@ std::string KernelPlan::to_text() const {
 
 Status compile_graph(SerializedGraph const& graph, CompileOptions const& options, CompilationResult& output) {
     if (graph.nodes.empty()) return fail(ErrorCode::kInvalidValue, "graph", "graph has no nodes");
+    if (graph.context.is_override_shape_enabled.value_or(false))
+        return fail(ErrorCode::kUnsupportedOperation, "context.is_override_shape_enabled", "shape overrides are not executable on this backend");
     Lowering low(graph, options);
     for (std::size_t index = 0; index < graph.nodes.size(); ++index) {
         for (auto const& [name, uid] : graph.nodes[index].inputs) {

@@ -61,14 +61,15 @@ def _store(values: np.ndarray, data_type: str) -> np.ndarray:
     return np.ascontiguousarray(values, dtype=np.float32)
 
 
-def _normal(seed: int, uid: int, count: int, data_type: str, std: float = 1.0) -> Callable[[], np.ndarray]:
+def _normal(seed: int, uid: int, count: int, data_type: str, std: float = 1.0, first: int = 0) -> Callable[[], np.ndarray]:
+    """Elements [first, first + count) of the tensor's N(0, std) stream (first must be even)."""
     def make():
         out = np.empty(count, dtype=NP_DTYPE[data_type])
         chunk = 1 << 23
         for start in range(0, count, chunk):
             n = min(chunk, count - start)
             # Box-Muller pairs are indexed from the chunk start (chunks are even-sized)
-            u = synthetic.unit(seed, uid, n + (n & 1), start)
+            u = synthetic.unit(seed, uid, n + (n & 1), first + start)
             u1 = np.maximum(u[0::2], 2.0 ** -53)
             radius = np.sqrt(-2.0 * np.log(u1))
             values = np.empty(n + (n & 1), dtype=np.float64)
@@ -100,7 +101,8 @@ def c1(layout: str = "nhwc", **shape) -> Workload:
         outputs=[3], notes="231 MFLOP over 1.75 MB: latency-bound, neither roof binds")
 
 
-def c2(n=32, h=56, w=56, c_in=256, c_mid=64, io="BFLOAT16") -> Workload:
+def c2(n=32, h=56, w=56, c_in=256, c_mid=64, io="BFLOAT16", first_image=0) -> Workload:
+    """first_image: index of this shard's first image inside the full batch (its X slice of the stream)."""
     doc = graphs.c2_bottleneck(n, h, w, c_in, c_mid, io)
     seed = BASE_SEED + 2
     pixels = n * h * w
@@ -108,7 +110,7 @@ def c2(n=32, h=56, w=56, c_in=256, c_mid=64, io="BFLOAT16") -> Workload:
     width = DTYPE_BYTES[io]
     nbytes = width * (2.0 * pixels * c_in + c_in * c_mid * 2 + 9 * c_mid * c_mid + 2 * c_mid)
     inputs = {
-        1: _normal(seed, 1, pixels * c_in, io),
+        1: _normal(seed, 1, pixels * c_in, io, first=first_image * h * w * c_in),
         2: _normal(seed, 2, c_mid * c_in, io, math.sqrt(2.0 / c_in)),
         3: _uniform(seed, 3, c_mid, io, -0.1, 0.1),
         4: _normal(seed, 4, c_mid * c_mid * 9, io, math.sqrt(2.0 / (9 * c_mid))),
@@ -122,14 +124,15 @@ def c2(n=32, h=56, w=56, c_in=256, c_mid=64, io="BFLOAT16") -> Workload:
         notes="fused end to end the DAG is HBM-bound (arithmetic intensity 136 < ridge ~212)")
 
 
-def c3(m=4096, k=4096, n=4096, io="BFLOAT16", c_type="BFLOAT16") -> Workload:
+def c3(m=4096, k=4096, n=4096, io="BFLOAT16", c_type="BFLOAT16", first_row=0) -> Workload:
+    """first_row: index of this shard's first row of A (and of C) inside the full matrix."""
     doc = graphs.c3_quantize_matmul(m, k, n, io, c_type)
     seed = BASE_SEED + 3
 
-    def operand(uid: int, count: int):
+    def operand(uid: int, count: int, first: int = 0):
         def make():
-            values = _normal(seed, uid, count, "FLOAT")()
-            mask = synthetic.outlier_mask(seed, uid, count)
+            values = _normal(seed, uid, count, "FLOAT", first=first)()
+            mask = synthetic.raw_u64(seed, uid + 0x5151, count, first) % np.uint64(100) == 0
             values[mask] *= np.float32(64.0)
             return _store(values, io)
         return make
@@ -141,33 +144,36 @@ def c3(m=4096, k=4096, n=4096, io="BFLOAT16", c_type="BFLOAT16") -> Workload:
         name="c3_mxfp8_quantize_matmul", config=3, document=doc,
         description={"workload": f"block-scale quantize (MXFP8 E4M3, 32-element blocks, E8M0 scales) -> MATMUL M={m} K={k} N={n} {io}"},
         metric="quantize_matmul_throughput", unit="TFLOP/s", flops=2.0 * m * n * k, bytes=quant_bytes + matmul_bytes, bound="tensor",
-        inputs={1: operand(1, m * k), 2: operand(2, k * n)}, outputs=[3, 4, 5, 6, 9])
+        inputs={1: operand(1, m * k, first_row * k), 2: operand(2, k * n)}, outputs=[3, 4, 5, 6, 9])
 
 
-def c4(b=8, h=32, s=2048, d=128, io="BFLOAT16", causal=True) -> Workload:
+def c4(b=8, h=32, s=2048, d=128, io="BFLOAT16", causal=True, first_batch=0) -> Workload:
     doc = graphs.c4_sdpa(b, h, s, d, io, causal)
     seed = BASE_SEED + 4
     pairs = s * (s + 1) / 2 if causal else s * s
     count = b * h * s * d
+    first = first_batch * h * s * d
     return Workload(
         name="c4_sdpa_forward", config=4, document=doc,
         description={"workload": f"SDPA forward {io} BHSD [{b},{h},{s},{d}] causal={causal} scale=1/sqrt({d}) with f32 Stats"},
         metric="sdpa_forward_throughput", unit="TFLOP/s", flops=4.0 * b * h * d * pairs, bytes=4.0 * count * DTYPE_BYTES[io] + 4.0 * b * h * s,
-        bound="tensor", inputs={1: _normal(seed, 1, count, io), 2: _normal(seed, 2, count, io), 3: _normal(seed, 3, count, io)}, outputs=[4, 5])
+        bound="tensor", inputs={1: _normal(seed, 1, count, io, first=first), 2: _normal(seed, 2, count, io, first=first), 3: _normal(seed, 3, count, io, first=first)},
+        outputs=[4, 5])
 
 
-def c5(batch=64, hq=32, hkv=8, d=128, pages=16384, block=64, max_len=8192, min_len=512, io="BFLOAT16") -> Workload:
+def c5(batch=64, hq=32, hkv=8, d=128, pages=16384, block=64, max_len=8192, min_len=512, io="BFLOAT16", first_sequence=0) -> Workload:
+    """first_sequence: index of this shard's first sequence inside the full batch (the KV pool is replicated)."""
     doc = graphs.c5_paged_decode(batch, hq, hkv, d, pages, block, max_len, io)
     seed = BASE_SEED + 5
     table = max_len // block
-    lengths = synthetic.integers(seed, 6, batch, min_len, max_len).astype(np.int32)
+    lengths = synthetic.integers(seed, 6, first_sequence + batch, min_len, max_len).astype(np.int32)[first_sequence:]
     total = int(lengths.sum())
     pool = pages * hkv * block * d
 
     def tables(stream: int):
-        return lambda: np.stack([synthetic.permutation_prefix(seed, stream * 1000 + i, pages, table) for i in range(batch)]).astype(np.int32).reshape(-1)
+        return lambda: np.stack([synthetic.permutation_prefix(seed, stream * 1000 + first_sequence + i, pages, table) for i in range(batch)]).astype(np.int32).reshape(-1)
 
-    inputs = {1: _normal(seed, 1, batch * hq * d, io), 5: lambda: np.ones(batch, dtype=np.int32), 6: lambda: lengths.copy(), 7: tables(7), 8: tables(8)}
+    inputs = {1: _normal(seed, 1, batch * hq * d, io, first=first_sequence * hq * d), 5: lambda: np.ones(batch, dtype=np.int32), 6: lambda: lengths.copy(), 7: tables(7), 8: tables(8)}
     device_inputs = {}
     if pool <= (1 << 27):
         inputs[2] = _normal(seed, 2, pool, io)
@@ -194,18 +200,32 @@ def c5(batch=64, hq=32, hkv=8, d=128, pages=16384, block=64, max_len=8192, min_l
 BUILDERS = {"c1": c1, "c1_nchw": lambda **kw: c1("nchw", **kw), "c2": c2, "c3": c3, "c4": c4, "c5": c5}
 
 
-def shard(name: str, rank: int, world: int) -> Workload:
-    """The rank's share of a configuration that splits naturally (batch for the convolutions,
-    rows of A/C for the matmul, batch for SDPA, sequences for paged decode). C1 has N=1 and
-    does not shard: every rank runs a replica."""
+# which axis of which output tensor the shards concatenate along when gathered
+GATHER_AXIS = {"c2": {7: 0}, "c3": {3: 0, 4: 0, 9: 0}, "c4": {4: 0, 5: 0}, "c5": {4: 0}}
+
+
+def shard(name: str, rank: int, world: int, **size) -> Workload:
+    """The rank's share of a configuration that splits naturally: images for the bottleneck, rows of A
+    and C for the quantize->matmul (B is quantized on every rank), batch entries for SDPA, sequences
+    for paged decode (the KV pool is replicated). Each shard draws exactly its slice of the full
+    problem's input streams, so gathering the shards' outputs along GATHER_AXIS reproduces the
+    unsharded result. C1 has N = 1 and does not shard: every rank runs a replica."""
     if world == 1 or name in ("c1", "c1_nchw"):
-        return BUILDERS[name]()
+        return BUILDERS[name](**size)
     if name == "c2":
-        return c2(n=32 // world)
+        n = size.pop("n", 32)
+        assert n % world == 0
+        return c2(n=n // world, first_image=rank * (n // world), **size)
     if name == "c3":
-        return c3(m=4096 // world)
+        m = size.pop("m", 4096)
+        assert m % world == 0
+        return c3(m=m // world, first_row=rank * (m // world), **size)
     if name == "c4":
-        return c4(b=8 // world)
+        b = size.pop("b", 8)
+        assert b % world == 0
+        return c4(b=b // world, first_batch=rank * (b // world), **size)
     if name == "c5":
-        return c5(batch=64 // world)
+        batch = size.pop("batch", 64)
+        assert batch % world == 0
+        return c5(batch=batch // world, first_sequence=rank * (batch // world), **size)
     raise KeyError(name)

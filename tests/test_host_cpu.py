@@ -56,7 +56,7 @@ def test_accepts_reference_fixture_shape_and_all_five_configs():
     (lambda d: d.pop("context"), 6),
     (lambda d: d["context"].pop("sm_count"), 6),
     (lambda d: d["context"].update(extra=1), 8),
-    (lambda d: d.update(unknown_top_level=1), 8),
+    (lambda d: d.update(unknown_top_level=1), 0),                        # tolerated, as in the reference
     (lambda d: d["tensors"]["1"].update(bogus=1), 8),
     (lambda d: d["tensors"]["1"].pop("stride"), 6),
     (lambda d: d["tensors"]["1"].update(dim="x"), 7),
