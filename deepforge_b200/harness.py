@@ -41,6 +41,51 @@ class Session:
     def run(self) -> None:
         self.exe.execute(self.pack, self.workspace_ptr)
 
+    # ---- replicas: independent copies of every buffer, so that back-to-back steps touch cold data ----
+
+    def footprint_bytes(self) -> int:
+        return sum(t.numel() for t in self.dev.values()) + (self.workspace.numel() if self.workspace is not None else 0)
+
+    def make_replicas(self, count: int) -> None:
+        """Replica 0 is the session's own buffers; replicas 1.. are device-side copies (inputs copied,
+        outputs and workspace fresh). Read-only tensors above 256 MiB (the paged KV pool) are shared:
+        one pass over them already exceeds the L2 several times."""
+        self.replicas = [(self.pack, self.workspace_ptr)]
+        self._replica_buffers = []
+        written = {a["uid"] for a in self.exe.arguments() if a["access"] != "read"}
+        for _ in range(1, count):
+            buffers = {}
+            for uid, tensor in self.dev.items():
+                if uid not in written and tensor.numel() > (256 << 20):
+                    buffers[uid] = tensor
+                else:
+                    buffers[uid] = tensor.clone()
+            workspace = torch.empty_like(self.workspace) if self.workspace is not None else None
+            self._replica_buffers.append((buffers, workspace))
+            self.replicas.append(({uid: t.data_ptr() for uid, t in buffers.items()}, workspace.data_ptr() if workspace is not None else 0))
+
+    def capture(self, first: Optional[int] = None, last: Optional[int] = None):
+        """One CUDA graph per replica holding plan steps [first, last) (default: the whole plan)."""
+        if not hasattr(self, "replicas"):
+            self.make_replicas(1)
+        stream = torch.cuda.Stream(self.device)
+        graphs = []
+        lo = 0 if first is None else first
+        hi = len(self.exe.steps()) if last is None else last
+        with torch.cuda.stream(stream):
+            self.exe.set_stream(stream.cuda_stream)
+            for pack, workspace in self.replicas:  # warm-up outside capture (one-time kernel attribute calls)
+                self.exe.execute_steps(lo, hi, pack, workspace)
+            torch.cuda.synchronize(self.device)
+            for pack, workspace in self.replicas:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    self.exe.execute_steps(lo, hi, pack, workspace)
+                graphs.append(graph)
+        self.exe.set_stream(None)
+        torch.cuda.synchronize(self.device)
+        return graphs
+
     def run_steps(self, first: int, last: int) -> None:
         self.exe.execute_steps(first, last, self.pack, self.workspace_ptr)
 
