@@ -309,6 +309,43 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    auto tile_geometry = [&](int tile, int& m_tile, int& n_tile, int& image, int& h0, int64_t& out_row0) {
+        m_tile = tile / pargs.n_tiles;
+        n_tile = tile - m_tile * pargs.n_tiles;
+        image = 0;
+        h0 = 0;
+        if (args.is_conv) {
+            image = m_tile / args.tiles_per_image;
+            h0 = (m_tile - image * args.tiles_per_image) * args.rows_per_tile;
+            out_row0 = (static_cast<int64_t>(image) * args.out_p + h0) * args.out_q;
+        } else {
+            out_row0 = static_cast<int64_t>(m_tile) * kTileM;
+        }
+    };
+    const uint32_t a_bytes = args.is_conv ? static_cast<uint32_t>(args.rows_per_tile * args.out_q * kBlockK * 2) : kABytes;
+    // One ring slot = G consecutive K slices of one tile; `it` numbers the slots this CTA fills.
+    auto issue_group = [&](uint32_t it, int tile, int kb0) {
+        int m_tile, n_tile, image, h0;
+        int64_t out_row0;
+        tile_geometry(tile, m_tile, n_tile, image, h0, out_row0);
+        const int s = it % STAGES;
+        mbar_expect_tx(full_bar(s), a_bytes * G);
+        for (int g = 0; g < G; ++g) {
+            const int kb = kb0 + g;
+            const uint32_t a_dst = ring_base + (s * G + g) * kABytes;
+            const int tap = kb / args.k_blocks_per_tap;
+            const int c0 = (kb - tap * args.k_blocks_per_tap) * kBlockK;
+            if (args.is_conv) {
+                const int r = tap / args.filter_s, sx = tap - r * args.filter_s;
+                tma_load_4d(a_dst, &map_a, c0, sx - args.pad_w, h0 + r - args.pad_h, image, full_bar(s));
+            } else {
+                tma_load_2d(a_dst, &map_a, kb * kBlockK, m_tile * kTileM, full_bar(s));
+            }
+        }
+    };
+    const int groups_per_tile = args.k_blocks / G;
+    uint32_t prefetched = 0;  // ring slots already filled by the prologue (thread 0 only)
+
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar(s), 1);
@@ -324,6 +361,15 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         }
         mbar_init(w_full_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // Start streaming right away: the filter and the first ring-full of activations are in flight
+        // while the other warps allocate tensor memory and stage the bias vectors.
+        mbar_expect_tx(w_full_bar, static_cast<uint32_t>(pargs.filter_bytes));
+        for (int nt = 0; nt < pargs.n_tiles; ++nt)
+            for (int kb = 0; kb < args.k_blocks; ++kb)
+                tma_load_2d(w_base + (nt * args.k_blocks + kb) * kBTileBytes, &map_b, kb * kBlockK, nt * BN, w_full_bar);
+        for (int tile = blockIdx.x; tile < pargs.total_tiles && prefetched < static_cast<uint32_t>(STAGES); tile += gridDim.x)
+            for (int grp = 0; grp < groups_per_tile && prefetched < static_cast<uint32_t>(STAGES); ++grp, ++prefetched)
+                issue_group(prefetched, tile, grp * G);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, kAccumulators * BN);
@@ -345,28 +391,8 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
 
-    auto tile_geometry = [&](int tile, int& m_tile, int& n_tile, int& image, int& h0, int64_t& out_row0) {
-        m_tile = tile / pargs.n_tiles;
-        n_tile = tile - m_tile * pargs.n_tiles;
-        image = 0;
-        h0 = 0;
-        if (args.is_conv) {
-            image = m_tile / args.tiles_per_image;
-            h0 = (m_tile - image * args.tiles_per_image) * args.rows_per_tile;
-            out_row0 = (static_cast<int64_t>(image) * args.out_p + h0) * args.out_q;
-        } else {
-            out_row0 = static_cast<int64_t>(m_tile) * kTileM;
-        }
-    };
-
     if (warp == 0) {
         if (lane == 0) {
-            // the filter, once: [n_tile][k_block] slices of BN x 64
-            mbar_expect_tx(w_full_bar, static_cast<uint32_t>(pargs.filter_bytes));
-            for (int nt = 0; nt < pargs.n_tiles; ++nt)
-                for (int kb = 0; kb < args.k_blocks; ++kb)
-                    tma_load_2d(w_base + (nt * args.k_blocks + kb) * kBTileBytes, &map_b, kb * kBlockK, nt * BN, w_full_bar);
-            const uint32_t a_bytes = args.is_conv ? static_cast<uint32_t>(args.rows_per_tile * args.out_q * kBlockK * 2) : kABytes;
             const uint32_t res_bytes = static_cast<uint32_t>(pargs.box_rows) * 128u * (BN / 64);
             uint32_t it = 0;
             bool ok = true;
@@ -384,22 +410,11 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                         tma_load_2d(epi_base + b * kEpiBytes + j * (kTileM * 128), &map_res, n_tile * BN + 64 * j, static_cast<int>(out_row0), res_full_bar(b));
                 }
                 for (int kb0 = 0; kb0 < args.k_blocks; kb0 += G, ++it) {
+                    if (it < prefetched) continue;  // already issued by the prologue
                     const int s = it % STAGES;
                     ok = mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, 112);
                     if (!ok) break;
-                    mbar_expect_tx(full_bar(s), a_bytes * G);
-                    for (int g = 0; g < G; ++g) {
-                        const int kb = kb0 + g;
-                        const uint32_t a_dst = ring_base + (s * G + g) * kABytes;
-                        const int tap = kb / args.k_blocks_per_tap;
-                        const int c0 = (kb - tap * args.k_blocks_per_tap) * kBlockK;
-                        if (args.is_conv) {
-                            const int r = tap / args.filter_s, sx = tap - r * args.filter_s;
-                            tma_load_4d(a_dst, &map_a, c0, sx - args.pad_w, h0 + r - args.pad_h, image, full_bar(s));
-                        } else {
-                            tma_load_2d(a_dst, &map_a, kb * kBlockK, m_tile * kTileM, full_bar(s));
-                        }
-                    }
+                    issue_group(it, tile, kb0);
                 }
             }
         }
