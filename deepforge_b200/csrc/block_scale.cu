@@ -279,39 +279,52 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 bsq_row32_kernel(const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* __restrict__ scale,
                  int64_t rows, int64_t cols, int reordered, int64_t scale_k_extent) {
-    int64_t thread = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    int64_t element = thread * 8;
-    if (element >= rows * cols) return;  // blocks are 4 whole lanes, so a block never straddles this exit
-    float v[8];
-    Load8<T>::load(x, element, v);
-    uint32_t amax_bits = 0;
+    // A thread owns kChunks groups of 8 consecutive elements, kChunks * 2048 elements apart, so that each
+    // load instruction of a warp is one contiguous 512-byte (16-bit input) segment and all of a thread's
+    // loads are in flight before the first amax. 4 neighbouring lanes form one 32-element block.
+    constexpr int kChunks = 4;
+    const int64_t total = rows * cols;
+    const int64_t tile0 = static_cast<int64_t>(blockIdx.x) * (256 * 8 * kChunks);
+    float v[kChunks][8];
+    bool live[kChunks];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        uint32_t bits = __float_as_uint(v[i]) & 0x7fffffffu;
-        amax_bits = bits > amax_bits ? bits : amax_bits;
+    for (int c = 0; c < kChunks; ++c) {
+        const int64_t element = tile0 + (static_cast<int64_t>(c) * 256 + threadIdx.x) * 8;
+        live[c] = element < total;
+        Load8<T>::load(x, live[c] ? element : 0, v[c]);  // a dead chunk re-reads element 0 and is discarded
     }
-    unsigned mask = __activemask();
-    uint32_t other = __shfl_xor_sync(mask, amax_bits, 1);
-    amax_bits = other > amax_bits ? other : amax_bits;
-    other = __shfl_xor_sync(mask, amax_bits, 2);
-    amax_bits = other > amax_bits ? other : amax_bits;
-    uint32_t code = scale_code_from_amax_bits(amax_bits);
-    uint2 packed = quantize8(v, code);
-    *reinterpret_cast<uint2*>(y + element) = packed;
-    if ((threadIdx.x & 3) == 0) {
-        int64_t block_index = thread >> 2;
-        int64_t k_blocks = cols >> 5;
-        if (reordered) {
-            int64_t row = block_index / k_blocks, kb = block_index - row * k_blocks;
-            scale[f8_128x4_offset(0, row, kb, rows, scale_k_extent)] = static_cast<uint8_t>(code);
-        } else {
-            scale[block_index] = static_cast<uint8_t>(code);
+    const int64_t k_blocks = cols >> 5;
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+        const int64_t element = tile0 + (static_cast<int64_t>(c) * 256 + threadIdx.x) * 8;
+        uint32_t amax_bits = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            uint32_t bits = __float_as_uint(v[c][i]) & 0x7fffffffu;
+            amax_bits = bits > amax_bits ? bits : amax_bits;
+        }
+        // blocks are 4 whole lanes and the element count is a multiple of 32, so the 4 lanes of a block are live together
+        uint32_t other = __shfl_xor_sync(0xffffffffu, amax_bits, 1);
+        amax_bits = other > amax_bits ? other : amax_bits;
+        other = __shfl_xor_sync(0xffffffffu, amax_bits, 2);
+        amax_bits = other > amax_bits ? other : amax_bits;
+        const uint32_t code = scale_code_from_amax_bits(amax_bits);
+        const uint2 packed = quantize8(v[c], code);
+        if (live[c]) *reinterpret_cast<uint2*>(y + element) = packed;
+        if (live[c] && (threadIdx.x & 3) == 0) {
+            const int64_t block_index = element >> 5;
+            if (reordered) {
+                const int64_t row = block_index / k_blocks, kb = block_index - row * k_blocks;
+                scale[f8_128x4_offset(0, row, kb, rows, scale_k_extent)] = static_cast<uint8_t>(code);
+            } else {
+                scale[block_index] = static_cast<uint8_t>(code);
+            }
         }
     }
 }
 
 // ---- column kernel: block of 32 along the second-to-last axis -------------------
-// X is [batch, K, N] packed; a thread owns 32 rows x VEC columns and keeps the raw
+// X is [batch, K, N] packed; a thread owns 8 rows x VEC columns and keeps the raw
 // 16-byte loads in registers (VEC = 8 for 16-bit inputs, 4 for f32), so X is read
 // from HBM exactly once and the amax runs on the raw bit patterns.
 
@@ -377,47 +390,59 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 bsq_col32_kernel(const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* __restrict__ scale,
                  int64_t k_extent, int64_t n_extent, int reordered, int64_t scale_k_extent) {
+    // One CTA = one 32-row block over 32 * VEC columns: warp g holds rows 8g..8g+7 (8 raw 16-byte loads per
+    // thread, 512 contiguous bytes per warp instruction) and the four partial column maxima meet in shared memory.
     using Traits = ColumnTraits<T>;
     constexpr int VEC = Traits::VEC;
-    int64_t column = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * VEC;
-    if (column >= n_extent) return;
-    int64_t kb = blockIdx.y;
-    int64_t batch = blockIdx.z;
-    int64_t base = (batch * k_extent + kb * 32) * n_extent + column;
+    constexpr int kRows = 8;
+    __shared__ uint32_t partial[4][VEC][32];
+    const int lane = threadIdx.x & 31, group = threadIdx.x >> 5;
+    const int64_t column = (static_cast<int64_t>(blockIdx.x) * 32 + lane) * VEC;
+    const bool live = column < n_extent;
+    const int64_t kb = blockIdx.y;
+    const int64_t batch = blockIdx.z;
+    const int64_t base = (batch * k_extent + kb * 32 + group * kRows) * n_extent + (live ? column : 0);
     const T* xp = static_cast<const T*>(x) + base;
-    uint4 raw[32];
+    uint4 raw[kRows];
 #pragma unroll
-    for (int r = 0; r < 32; ++r) raw[r] = __ldg(reinterpret_cast<const uint4*>(xp + r * n_extent));
+    for (int r = 0; r < kRows; ++r) raw[r] = __ldg(reinterpret_cast<const uint4*>(xp + r * n_extent));
     uint32_t pattern[VEC];
 #pragma unroll
     for (int c = 0; c < VEC; ++c) pattern[c] = 0;
 #pragma unroll
-    for (int r = 0; r < 32; ++r) Traits::amax(raw[r], pattern);
+    for (int r = 0; r < kRows; ++r) Traits::amax(raw[r], pattern);
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) partial[group][c][lane] = pattern[c];
+    __syncthreads();
+    if (!live) return;
     uint32_t code[VEC];
     float reciprocal[VEC];
-    int64_t k_blocks = k_extent >> 5;
+    const int64_t k_blocks = k_extent >> 5;
 #pragma unroll
     for (int c = 0; c < VEC; ++c) {
-        code[c] = scale_code_from_amax_bits(Traits::amax_f32_bits(pattern[c]));
+        uint32_t m = max(max(partial[0][c][lane], partial[1][c][lane]), max(partial[2][c][lane], partial[3][c][lane]));
+        code[c] = scale_code_from_amax_bits(Traits::amax_f32_bits(m));
         reciprocal[c] = reciprocal_e8m0(code[c]);
     }
-    if (reordered) {
-        // scale dims [batch, K/32, N] with N as the 128-row axis of the tile
+    if (group == 0) {
+        if (reordered) {
+            // scale dims [batch, K/32, N] with N as the 128-row axis of the tile
 #pragma unroll
-        for (int c = 0; c < VEC; ++c)
-            scale[f8_128x4_offset(batch, column + c, kb, n_extent, scale_k_extent)] = static_cast<uint8_t>(code[c]);
-    } else {
-        uint8_t* out = scale + (batch * k_blocks + kb) * n_extent + column;
-        if constexpr (VEC == 8) {
-            *reinterpret_cast<uint2*>(out) =
-                make_uint2(code[0] | (code[1] << 8) | (code[2] << 16) | (code[3] << 24),
-                           code[4] | (code[5] << 8) | (code[6] << 16) | (code[7] << 24));
+            for (int c = 0; c < VEC; ++c)
+                scale[f8_128x4_offset(batch, column + c, kb, n_extent, scale_k_extent)] = static_cast<uint8_t>(code[c]);
         } else {
-            *reinterpret_cast<uint32_t*>(out) = code[0] | (code[1] << 8) | (code[2] << 16) | (code[3] << 24);
+            uint8_t* out = scale + (batch * k_blocks + kb) * n_extent + column;
+            if constexpr (VEC == 8) {
+                *reinterpret_cast<uint2*>(out) =
+                    make_uint2(code[0] | (code[1] << 8) | (code[2] << 16) | (code[3] << 24),
+                               code[4] | (code[5] << 8) | (code[6] << 16) | (code[7] << 24));
+            } else {
+                *reinterpret_cast<uint32_t*>(out) = code[0] | (code[1] << 8) | (code[2] << 16) | (code[3] << 24);
+            }
         }
     }
 #pragma unroll
-    for (int r = 0; r < 32; ++r) {
+    for (int r = 0; r < kRows; ++r) {
         float v[VEC];
         Traits::values(raw[r], v);
         uint32_t bytes[VEC];
@@ -482,6 +507,13 @@ bsd_packed_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ sca
         float s = decode_e8m0(__ldg(scale_row + col / block_cols));
 #pragma unroll
         for (int i = 0; i < 16; ++i) out[i] = __fmul_rn(decode_e4m3((w[i >> 2] >> ((i & 3) * 8)) & 0xffu), s);
+    } else if (block_cols == 1 && ((reinterpret_cast<uintptr_t>(scale_row + col)) & 15u) == 0) {
+        // one scale per column (blocks run down the rows): 16 scale bytes in one load
+        uint4 sraw = __ldg(reinterpret_cast<const uint4*>(scale_row + col));
+        uint32_t sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w};
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            out[i] = __fmul_rn(decode_e4m3((w[i >> 2] >> ((i & 3) * 8)) & 0xffu), decode_e8m0((sw[i >> 2] >> ((i & 3) * 8)) & 0xffu));
     } else {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -630,7 +662,7 @@ extern "C" int dfgpu_block_scale_quantize(const dfgpu_bsq_params* p, void* const
     if (kernel == DFGPU_BSQ_COL32 && !(aligned(x, 16) && aligned(y, 8) && aligned(scale, 8))) kernel = DFGPU_BSQ_GENERIC;
 
     if (kernel == DFGPU_BSQ_ROW32) {
-        int64_t threads = plan.rows * plan.cols / 8;
+        int64_t threads = (plan.rows * plan.cols / 8 + 3) / 4;  // 4 chunks of 8 elements per thread
         unsigned grid = static_cast<unsigned>((threads + 255) / 256);
         int reordered = plan.layout.reordered;
         if (p->x.dtype == DFGPU_F32) bsq_row32_kernel<float><<<grid, 256, 0, stream>>>(x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
@@ -638,8 +670,8 @@ extern "C" int dfgpu_block_scale_quantize(const dfgpu_bsq_params* p, void* const
         else bsq_row32_kernel<__half><<<grid, 256, 0, stream>>>(x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
     } else if (kernel == DFGPU_BSQ_COL32) {
         int vec = p->x.dtype == DFGPU_F32 ? 4 : 8;
-        int64_t threads = plan.cols / vec;
-        dim3 grid(static_cast<unsigned>((threads + 127) / 128), static_cast<unsigned>(plan.rows / 32),
+        int64_t lanes = plan.cols / vec;  // one lane per group of vec columns, 32 lanes (x 4 row groups) per CTA
+        dim3 grid(static_cast<unsigned>((lanes + 31) / 32), static_cast<unsigned>(plan.rows / 32),
                   static_cast<unsigned>(plan.batch));
         int reordered = plan.layout.reordered;
         if (p->x.dtype == DFGPU_F32) bsq_col32_kernel<float><<<grid, 128, 0, stream>>>(x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);

@@ -22,7 +22,6 @@ constexpr int kHeadsPadded = 16;              // N of both products (GQA group p
 constexpr int kTilesPerCta = 8;               // 1024 keys per CTA
 constexpr int kKvTileBytes = kTileKeys * kDim * 2;  // 32 KiB
 constexpr int kKvHalfBytes = kKvTileBytes / 2;
-constexpr int kRingSlots = 5;
 constexpr int kDecodeThreads = 192;
 constexpr int kPartialStride = kDim + 2;      // o[128], max, sum  (layout shared with the merge kernel)
 constexpr float kRaiseThreshold = 8.0f;
@@ -45,11 +44,13 @@ struct DecodeArgs {
     float* partial;
 };
 
-struct DecodeSmem {
+template <int kRingSlots>
+struct DecodeSmemT {
     static constexpr int kQ = 0;                                  // [16 heads x 128 d] as two swizzled halves (2 x 2 KiB), padded to 4 KiB
     static constexpr int kP = 4096;                               // two buffers of [16 heads x 128 keys] (2 x 4 KiB)
     static constexpr int kRing = 4096 + 8192;
     static constexpr int kReduce = kRing + kRingSlots * kKvTileBytes;  // cross-warp max exchange: 2 x [4 warps][8 heads] floats
+    static constexpr int kPages = kReduce + 512;                  // page ids of this CTA's keys: [K | V][64] int32, -1 = reads as zeros
     static constexpr int kBarriers = kReduce + 1024;
     // q_full, kv_full[S], kv_empty[S], s_full[2], s_empty[2], p_full[2], pv_done[2]
     static constexpr int kBarrierCount = 1 + 2 * kRingSlots + 8;
@@ -70,6 +71,17 @@ __device__ __forceinline__ void tmem_store_16(uint32_t taddr, const uint32_t (&r
         ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
+}
+
+// Maximum of a float over the warp in one reduction instruction: floats compare like the signed
+// integers obtained by flipping the magnitude bits of negative values (a NaN score ends as a NaN output either way).
+__device__ __forceinline__ float warp_max_f32(float v) {
+    int32_t bits = __float_as_int(v);
+    bits ^= (bits >> 31) & 0x7fffffff;
+    int32_t top;
+    asm volatile("redux.sync.max.s32 %0, %1, 0xffffffff;" : "=r"(top) : "r"(bits));
+    top ^= (top >> 31) & 0x7fffffff;
+    return __int_as_float(top);
 }
 
 // Valid key window [lo, hi) of a sequence for its single query row (q index 0).
@@ -96,10 +108,11 @@ __device__ __forceinline__ void key_window(const DecodeArgs& a, int64_t batch, i
     if (hi < 0) hi = 0;
 }
 
-template <int G>
-__global__ void __launch_bounds__(kDecodeThreads, 1)
+template <int G, int kRingSlots>
+__global__ void __launch_bounds__(kDecodeThreads, kRingSlots <= 3 ? 2 : 1)
 sdpa_decode_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, DecodeArgs args) {
+    using DecodeSmem = DecodeSmemT<kRingSlots>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -151,6 +164,21 @@ sdpa_decode_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // Page ids of the (at most 64 + 64) table slots this CTA's 1024 keys map to, fetched once and side by side:
+    // the loader and the softmax threads then read them from shared memory instead of paying a dependent
+    // global load per tile. An id outside the container is stored as -1 (its rows read as zeros).
+    int32_t* page_ids = reinterpret_cast<int32_t*>(generic_base + DecodeSmem::kPages);
+    if (threadIdx.x < 128) {
+        const bool is_v = threadIdx.x >= 64;
+        const int entry = threadIdx.x & 63;
+        const int64_t table_slot = chunk_begin / args.block + entry;
+        int64_t page = -1;
+        if (entry < kTilesPerCta * args.pages_per_tile && table_slot < (is_v ? args.table_len_v : args.table_len_k)) {
+            page = is_v ? args.table_v[batch * args.table_v_stride + table_slot * args.table_v_slot_stride]
+                        : args.table_k[batch * args.table_k_stride + table_slot * args.table_k_slot_stride];
+        }
+        page_ids[threadIdx.x] = (page >= 0 && page < args.num_pages) ? static_cast<int32_t>(page) : -1;
+    }
     if (warp == 1) {
         tmem_alloc(tmem_slot, 64);
         tmem_relinquish();
@@ -174,26 +202,16 @@ sdpa_decode_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 if (!mbar_wait(kv_empty(slot), ((t / kRingSlots) & 1) ^ 1, 301)) break;
                 const bool is_v = (t & 1) != 0;
                 const CUtensorMap* map = is_v ? &map_v : &map_k;
-                const int32_t* table = is_v ? args.table_v : args.table_k;
-                const int64_t table_base = batch * (is_v ? args.table_v_stride : args.table_k_stride);
-                const int64_t slot_stride = is_v ? args.table_v_slot_stride : args.table_k_slot_stride;
-                const int table_len = is_v ? args.table_len_v : args.table_len_k;
-                const int64_t key0 = chunk_begin + static_cast<int64_t>(first_tile + (t >> 1)) * kTileKeys;
+                const int32_t* ids = page_ids + (is_v ? 64 : 0) + (first_tile + (t >> 1)) * args.pages_per_tile;
                 const uint32_t dst = smem_base + DecodeSmem::kRing + slot * kKvTileBytes;
                 uint32_t expected = 0;
-                for (int pg = 0; pg < args.pages_per_tile; ++pg) {
-                    const int64_t table_slot = key0 / args.block + pg;
-                    int64_t page = -1;
-                    if (table_slot < table_len) page = table[table_base + table_slot * slot_stride];
-                    if (page >= 0 && page < args.num_pages) expected += 2 * page_bytes;
-                }
+                for (int pg = 0; pg < args.pages_per_tile; ++pg)
+                    if (ids[pg] >= 0) expected += 2 * page_bytes;
                 mbar_expect_tx(kv_full(slot), expected);  // also the arrival; 0 bytes when every page is invalid
                 for (int pg = 0; pg < args.pages_per_tile; ++pg) {
-                    const int64_t table_slot = key0 / args.block + pg;
-                    int64_t page = -1;
-                    if (table_slot < table_len) page = table[table_base + table_slot * slot_stride];
+                    const int64_t page = ids[pg];
                     const uint32_t page_dst = dst + pg * page_bytes;
-                    if (page >= 0 && page < args.num_pages) {
+                    if (page >= 0) {
                         const int row = static_cast<int>((page * args.heads_kv + kv_head) * args.block);
                         tma_load_2d(page_dst, map, 0, row, kv_full(slot));
                         tma_load_2d(page_dst + kKvHalfBytes, map, 64, row, kv_full(slot));
@@ -257,20 +275,23 @@ sdpa_decode_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
         for (int h = 0; h < G; ++h) { m_ref[h] = -INFINITY; m_true[h] = -INFINITY; l_part[h] = 0.0f; }
         bool ok = true;
+        {
+            // rows of the padded heads (G..15) of both P buffers stay zero for the whole kernel
+            const int half = key_lane >> 6, within = key_lane & 63;
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+                for (int h = G; h < kHeadsPadded; ++h) {
+                    const uint32_t offset = half * (kHeadsPadded * 128) + h * 128 + (((within >> 3) ^ (h & 7)) << 4) + (within & 7) * 2;
+                    *reinterpret_cast<uint16_t*>(generic_base + DecodeSmem::kP + b * 4096 + offset) = 0;
+                }
+        }
         for (int j = 0; j < tiles; ++j) {
             const int b = j & 1;
             const int64_t key = chunk_begin + static_cast<int64_t>(first_tile + j) * kTileKeys + key_lane;
             // page validity of this key (an invalid page reads as zeros: score 0, no contribution to O)
-            const int64_t table_slot = key / args.block;
-            bool k_page_ok = false, v_page_ok = false;
-            if (table_slot < args.table_len_k) {
-                const int64_t page = args.table_k[batch * args.table_k_stride + table_slot * args.table_k_slot_stride];
-                k_page_ok = page >= 0 && page < args.num_pages;
-            }
-            if (table_slot < args.table_len_v) {
-                const int64_t page = args.table_v[batch * args.table_v_stride + table_slot * args.table_v_slot_stride];
-                v_page_ok = page >= 0 && page < args.num_pages;
-            }
+            const int entry = ((first_tile + j) * kTileKeys + key_lane) / args.block;
+            const bool k_page_ok = page_ids[entry] >= 0, v_page_ok = page_ids[64 + entry] >= 0;
             const bool in_window = key >= lo && key < hi;
             if (!v_page_ok) {
                 // No TMA transfer targets this key's value row (its page id is out of range): the row must
@@ -303,10 +324,7 @@ sdpa_decode_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             float warp_max[G];
 #pragma unroll
             for (int h = 0; h < G; ++h) {
-                float v = s[h];
-#pragma unroll
-                for (int step = 16; step > 0; step >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, step));
-                warp_max[h] = v;
+                warp_max[h] = warp_max_f32(s[h]);
             }
             float* slot_reduce = reduce + b * 32;
             if (lane == 0) {
@@ -349,13 +367,10 @@ sdpa_decode_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             uint8_t* p_tile = generic_base + DecodeSmem::kP + b * 4096;
             const int half = key_lane >> 6, within = key_lane & 63;
 #pragma unroll
-            for (int h = 0; h < kHeadsPadded; ++h) {
-                float p = 0.0f;
-                if (h < G) {
-                    p = (s[h < G ? h : 0] == -INFINITY || m_ref[h < G ? h : 0] == -INFINITY) ? 0.0f : exp2f(s[h < G ? h : 0] - m_ref[h < G ? h : 0]);
-                    l_part[h < G ? h : 0] += p;
-                    if (!v_page_ok) p = 0.0f;  // the value row reads as zeros
-                }
+            for (int h = 0; h < G; ++h) {
+                float p = (s[h] == -INFINITY || m_ref[h] == -INFINITY) ? 0.0f : exp2f(s[h] - m_ref[h]);
+                l_part[h] += p;
+                if (!v_page_ok) p = 0.0f;  // the value row reads as zeros
                 const uint32_t offset = half * (kHeadsPadded * 128) + h * 128 + (((within >> 3) ^ (h & 7)) << 4) + (within & 7) * 2;
                 *reinterpret_cast<__nv_bfloat16*>(p_tile + offset) = __float2bfloat16_rn(p);
             }
@@ -478,18 +493,21 @@ int launch_decode_umma(const dfgpu_sdpa_params& p, void* const* tensors, void* s
     args.table_v_slot_stride = p.page_table_v.stride[2];
     args.partial = static_cast<float*>(scratch);
     dim3 grid(static_cast<unsigned>(args.max_chunks), static_cast<unsigned>(hkv), static_cast<unsigned>(batch));
-    auto run = [&](auto kernel) -> int {
-        cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeSmem::kDynamic);
-        if (error != cudaSuccess) return fail(kExecutionFailed, "SDPA decode: cannot reserve %d bytes of shared memory: %s", DecodeSmem::kDynamic, cudaGetErrorString(error));
-        kernel<<<grid, kDecodeThreads, DecodeSmem::kDynamic, stream>>>(map_q, map_k, map_v, args);
+    auto run = [&](auto kernel, int dynamic) -> int {
+        cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dynamic);
+        if (error != cudaSuccess) return fail(kExecutionFailed, "SDPA decode: cannot reserve %d bytes of shared memory: %s", dynamic, cudaGetErrorString(error));
+        kernel<<<grid, kDecodeThreads, dynamic, stream>>>(map_q, map_k, map_v, args);
         return check_launch("SDPA paged decode (tcgen05)");
     };
+    // three ring slots: two CTAs per SM (about 219 KiB of shared memory together) hide each other's softmax latency
+#define DFGPU_DECODE_CASE(G_) return run(sdpa_decode_umma_kernel<G_, 3>, DecodeSmemT<3>::kDynamic)
     switch (args.group) {
-        case 1: return run(sdpa_decode_umma_kernel<1>);
-        case 2: return run(sdpa_decode_umma_kernel<2>);
-        case 4: return run(sdpa_decode_umma_kernel<4>);
-        default: return run(sdpa_decode_umma_kernel<8>);
+        case 1: DFGPU_DECODE_CASE(1);
+        case 2: DFGPU_DECODE_CASE(2);
+        case 4: DFGPU_DECODE_CASE(4);
+        default: DFGPU_DECODE_CASE(8);
     }
+#undef DFGPU_DECODE_CASE
 }
 
 int decode_umma_device_status(int* status) { return read_and_clear_device_status(status); }

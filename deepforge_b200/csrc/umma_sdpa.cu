@@ -302,6 +302,298 @@ sdpa_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
 }
 
+// ---- two query tiles per CTA ------------------------------------------------------
+// The softmax of one tile costs about as many cycles as its two products, so a CTA that owns two
+// 128-row query tiles (A and B) lets the tensor pipe work on one while the other is in its softmax:
+//   warp 0      TMA: Q_A, Q_B once, then K_0, V_0, K_1, ... into a ring of 32 KiB slots
+//   warp 1      one lane issues, per key tile j:  O_A += P_A(j) V_j ; S_A(j+1) = Q_A K_{j+1}^T ;
+//                                                 O_B += P_B(j) V_j ; S_B(j+1) = Q_B K_{j+1}^T
+//   warps 2-5   softmax of tile A, warps 6-9 softmax of tile B, one query row per thread
+// TMEM: S_A at +0, S_B at +128, O_A at +256, O_B at +384. P never goes through shared memory: each
+// thread overwrites the front of its own score row with the bf16 probabilities (two per 32-bit
+// column) and the second product takes its A operand from tensor memory. The tensor pipe runs the
+// products of one CTA in issue order, so S_X(j+1) may be issued right behind the product that reads P_X(j).
+// Under a causal mask tile A (the earlier rows) has one key tile fewer than tile B.
+
+constexpr int kPairSlots = 5;
+constexpr int kPairThreads = 320;
+
+struct PairSmem {
+    static constexpr int kQ = 0;                       // Q_A, Q_B; later the output staging tiles
+    static constexpr int kRing = 2 * kTileBytes;
+    static constexpr int kBarriers = kRing + kPairSlots * kTileBytes;
+    // q_full, kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2]
+    static constexpr int kBarrierCount = 1 + 2 * kPairSlots + 6;
+    static constexpr int kTotal = kBarriers + kBarrierCount * 8 + 16;
+    static constexpr int kDynamic = kTotal + 1024;
+};
+
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (bf16 pairs, one row per lane) is read from tensor memory.
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(kPairThreads, 1)
+sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o, SdpaUmmaArgs args) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + PairSmem::kBarriers;
+    const uint32_t q_full = bar_base;
+    auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
+    auto kv_empty = [&](int s) { return bar_base + 8u * (1 + kPairSlots + s); };
+    auto s_full = [&](int x) { return bar_base + 8u * (1 + 2 * kPairSlots + x); };
+    auto p_full = [&](int x) { return bar_base + 8u * (3 + 2 * kPairSlots + x); };
+    auto o_full = [&](int x) { return bar_base + 8u * (5 + 2 * kPairSlots + x); };
+    const uint32_t tmem_slot = bar_base + 8u * PairSmem::kBarrierCount;
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + PairSmem::kBarriers + 8 * PairSmem::kBarrierCount);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pairs = args.q_tiles >> 1;
+    const int pair = pairs - 1 - static_cast<int>(blockIdx.x);  // heavy (late) causal pairs first
+    const int bh = blockIdx.y;
+    const int batch = bh / args.heads_q, head = bh - batch * args.heads_q;
+    const int kv_head = head / (args.heads_q / args.heads_kv);
+    const int q_tile_a = 2 * pair;
+    const int q_row_a = (batch * args.heads_q + head) * args.seq_q + q_tile_a * kRows;
+    const int kv_row0 = (batch * args.heads_kv + kv_head) * args.seq_kv;
+    const int total_kv_tiles = args.seq_kv / kKeys;
+    const int tiles_a = args.causal ? min(total_kv_tiles, q_tile_a + 1) : total_kv_tiles;
+    const int tiles_b = args.causal ? min(total_kv_tiles, q_tile_a + 2) : total_kv_tiles;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < kPairSlots; ++s) {
+            mbar_init(kv_full(s), 1);
+            mbar_init(kv_empty(s), 1);
+        }
+        for (int x = 0; x < 2; ++x) {
+            mbar_init(s_full(x), 1);
+            mbar_init(p_full(x), 4);
+            mbar_init(o_full(x), 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+        tc_fence_before();
+    }
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(q_full, 2 * kTileBytes);
+            for (int x = 0; x < 2; ++x) {
+                tma_load_2d(smem_base + PairSmem::kQ + x * kTileBytes, &map_q, 0, q_row_a + x * kRows, q_full);
+                tma_load_2d(smem_base + PairSmem::kQ + x * kTileBytes + kHalfBytes, &map_q, 64, q_row_a + x * kRows, q_full);
+            }
+            for (int t = 0; t < 2 * tiles_b; ++t) {
+                const int slot = t % kPairSlots;
+                if (!mbar_wait(kv_empty(slot), ((t / kPairSlots) & 1) ^ 1, 221)) break;
+                const CUtensorMap* map = (t & 1) ? &map_v : &map_k;
+                const int row = kv_row0 + (t >> 1) * kKeys;
+                const uint32_t dst = smem_base + PairSmem::kRing + slot * kTileBytes;
+                mbar_expect_tx(kv_full(slot), kTileBytes);
+                tma_load_2d(dst, map, 0, row, kv_full(slot));
+                tma_load_2d(dst + kHalfBytes, map, 64, row, kv_full(slot));
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kKeys >> 3) << 17) | (static_cast<uint32_t>(kRows >> 4) << 24);
+            const uint32_t idesc_pv = idesc_qk | (1u << 16);  // B = V read MN-major
+            bool ok = mbar_wait(q_full, 0, 222);
+            auto wait_slot = [&](int t, int code) {
+                if (ok) ok = mbar_wait(kv_full(t % kPairSlots), (t / kPairSlots) & 1, code);
+                tc_fence_after();
+            };
+            auto scores = [&](int x, int j) {  // S_x = Q_x K_j^T
+                if (!ok) return;
+                const uint32_t q_smem = smem_base + PairSmem::kQ + x * kTileBytes;
+                const uint32_t k_smem = smem_base + PairSmem::kRing + ((2 * j) % kPairSlots) * kTileBytes;
+#pragma unroll
+                for (int k = 0; k < kHeadDim / 16; ++k) {
+                    const uint32_t offset = (k >> 2) * kHalfBytes + (k & 3) * 32;
+                    umma_bf16(tmem_base + x * 128, smem_desc(q_smem + offset, 16, 1024), smem_desc(k_smem + offset, 16, 1024), idesc_qk, k != 0 ? 1u : 0u);
+                }
+            };
+            auto product = [&](int x, int j) {  // O_x += P_x V_j, P_x as bf16 pairs in the front 64 columns of S_x
+                if (ok) ok = mbar_wait(p_full(x), j & 1, 223 + x);
+                tc_fence_after();
+                if (!ok) return;
+                const uint32_t v_smem = smem_base + PairSmem::kRing + ((2 * j + 1) % kPairSlots) * kTileBytes;
+#pragma unroll
+                for (int k = 0; k < kKeys / 16; ++k)
+                    umma_bf16_a_tmem(tmem_base + 256 + x * 128, tmem_base + x * 128 + k * 8, smem_desc(v_smem + k * 2048, kHalfBytes, 1024), idesc_pv, (j | k) != 0 ? 1u : 0u);
+            };
+            wait_slot(0, 225);
+            scores(0, 0);
+            umma_commit(s_full(0));
+            scores(1, 0);
+            umma_commit(s_full(1));
+            umma_commit(kv_empty(0));
+            for (int j = 0; j < tiles_b; ++j) {
+                const int tv = 2 * j + 1, tk = 2 * j + 2;
+                wait_slot(tv, 226);
+                if (j < tiles_a) {
+                    product(0, j);
+                    if (j == tiles_a - 1) umma_commit(o_full(0));
+                }
+                if (j + 1 < tiles_b) wait_slot(tk, 227);
+                if (j + 1 < tiles_a) {
+                    scores(0, j + 1);
+                    umma_commit(s_full(0));
+                }
+                product(1, j);
+                umma_commit(kv_empty(tv % kPairSlots));
+                if (j + 1 < tiles_b) {
+                    scores(1, j + 1);
+                    umma_commit(s_full(1));
+                    umma_commit(kv_empty(tk % kPairSlots));
+                }
+            }
+            umma_commit(o_full(1));
+        }
+    } else {
+        const int x = (warp - 2) >> 2;  // 0: tile A, 1: tile B
+        const int quadrant = warp & 3;
+        const int row = quadrant * 32 + lane;
+        const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
+        const uint32_t tmem_s = tmem_base + lane_base + x * 128;
+        const uint32_t tmem_o = tmem_base + lane_base + 256 + x * 128;
+        const int q_tile = q_tile_a + x;
+        const int q_index = q_tile * kRows + row;
+        const int my_tiles = x ? tiles_b : tiles_a;
+        const float scale = args.scale_log2;
+        float m_ref = -INFINITY;  // reference maximum, scaled, log2 domain
+        float l_sum = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < my_tiles; ++j) {
+            if (ok) ok = mbar_wait(s_full(x), j & 1, 228 + x);
+            tc_fence_after();
+            uint32_t raw[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_load_32(tmem_s + c * 32, raw[c]);
+            tmem_load_wait();
+            if (args.causal && j == q_tile) {
+                const int limit = q_index - j * kKeys;  // keys 0..limit of this tile are visible
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        if (c * 32 + e > limit) raw[c][e] = 0xff800000u;  // -inf
+            }
+            float lane_max[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                lane_max[c] = __uint_as_float(raw[c][0]);
+#pragma unroll
+                for (int e = 1; e < 32; ++e) lane_max[c] = fmaxf(lane_max[c], __uint_as_float(raw[c][e]));
+            }
+            const float tile_max = fmaxf(fmaxf(lane_max[0], lane_max[1]), fmaxf(lane_max[2], lane_max[3])) * scale;
+            // raise the reference only when it would grow by more than the threshold (or on the first tile)
+            const bool raise = tile_max > m_ref + kRescaleThreshold;
+            if (__any_sync(0xffffffffu, raise)) {
+                const float m_new = fmaxf(m_ref, tile_max);
+                const float alpha = m_ref == -INFINITY ? 0.0f : ex2_fast(m_ref - m_new);
+                l_sum *= alpha;
+                m_ref = m_new;
+                if (j > 0) {
+                    // O_x holds P V up to tile j-1; that product was issued ahead of S_x(j), which has completed
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t acc[32];
+                        tmem_load_32(tmem_o + c * 32, acc);
+                        tmem_load_wait();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
+                        tmem_store_32(tmem_o + c * 32, acc);
+                    }
+                }
+            }
+            const float bias = -m_ref;
+            float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t packed[32];  // 64 keys as bf16 pairs
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const int key = half * 64 + 2 * e;
+                    const float p0 = ex2_fast(fmaf(__uint_as_float(raw[key >> 5][key & 31]), scale, bias));
+                    const float p1 = ex2_fast(fmaf(__uint_as_float(raw[(key + 1) >> 5][(key + 1) & 31]), scale, bias));
+                    sums[e & 3] += p0 + p1;
+                    __nv_bfloat162 two = __floats2bfloat162_rn(p0, p1);
+                    packed[e] = *reinterpret_cast<uint32_t*>(&two);
+                }
+                tmem_store_32(tmem_s + half * 32, packed);
+            }
+            l_sum += (sums[0] + sums[1]) + (sums[2] + sums[3]);
+            tmem_store_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full(x));
+        }
+        // last product done -> normalise, stage O in this tile's Q buffer (no product reads it any more), TMA store
+        if (ok) ok = mbar_wait(o_full(x), 0, 230 + x);
+        tc_fence_after();
+        const float inverse = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
+        uint8_t* o_row = generic_base + PairSmem::kQ + x * kTileBytes + row * 128;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            uint32_t acc[32];
+            tmem_load_32(tmem_o + c * 32, acc);
+            tmem_load_wait();
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                uint32_t w[4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    __nv_bfloat162 two = __floats2bfloat162_rn(__uint_as_float(acc[u * 8 + 2 * t]) * inverse, __uint_as_float(acc[u * 8 + 2 * t + 1]) * inverse);
+                    w[t] = *reinterpret_cast<uint32_t*>(&two);
+                }
+                const int unit16 = c * 4 + u;  // 16-byte unit inside the 256-byte output row
+                const int half = unit16 >> 3, unit = unit16 & 7;
+                *reinterpret_cast<uint4*>(o_row + half * kHalfBytes + ((unit ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+        if (args.stats != nullptr && ok)
+            args.stats[batch * args.stats_batch_stride + head * args.stats_head_stride + static_cast<int64_t>(q_index) * args.stats_row_stride] =
+                l_sum > 0.0f ? 0.6931471805599453f * (m_ref + log2f(l_sum)) : -INFINITY;
+        tc_fence_before();
+        fence_async_shared();
+        if (x == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+        else asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (quadrant == 0 && lane == 0) {
+            if (ok && g_device_status == 0) {
+                tma_store_2d(&map_o, smem_base + PairSmem::kQ + x * kTileBytes, 0, q_row_a + x * kRows);
+                tma_store_2d(&map_o, smem_base + PairSmem::kQ + x * kTileBytes + kHalfBytes, 64, q_row_a + x * kRows);
+            }
+            tma_store_commit();
+            tma_store_wait_all();
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
 bool packed_bhsd(const dfgpu_tensor& t) {
     return t.rank == 4 && t.stride[3] == 1 && t.stride[2] == t.dim[3] && t.stride[1] == t.dim[2] * t.dim[3] &&
            t.stride[0] == t.dim[1] * t.dim[2] * t.dim[3];
@@ -355,11 +647,18 @@ int launch_sdpa_umma(const dfgpu_sdpa_params& p, void* const* tensors, void* scr
         args.stats_head_stride = p.stats.stride[1];
         args.stats_row_stride = p.stats.stride[2];
     }
+    const bool pair_form = sq % (2 * kRows) == 0 && p.attn_scale > 0.0f && p.attn_scale < INFINITY;
     static bool configured = false;
     if (!configured) {
         cudaError_t error = cudaFuncSetAttribute(sdpa_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kDynamic);
-        if (error != cudaSuccess) return fail(kExecutionFailed, "SDPA: cannot reserve %d bytes of shared memory: %s", Smem::kDynamic, cudaGetErrorString(error));
+        if (error == cudaSuccess) error = cudaFuncSetAttribute(sdpa_umma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::kDynamic);
+        if (error != cudaSuccess) return fail(kExecutionFailed, "SDPA: cannot reserve %d bytes of shared memory: %s", PairSmem::kDynamic, cudaGetErrorString(error));
         configured = true;
+    }
+    if (pair_form) {
+        dim3 grid(static_cast<unsigned>(args.q_tiles / 2), static_cast<unsigned>(batch * hq));
+        sdpa_umma_pair_kernel<<<grid, kPairThreads, PairSmem::kDynamic, stream>>>(map_q, map_k, map_v, map_o, args);
+        return check_launch("SDPA (tcgen05, two query tiles per CTA)");
     }
     dim3 grid(static_cast<unsigned>(args.q_tiles), static_cast<unsigned>(batch * hq));
     sdpa_umma_kernel<<<grid, kSdpaThreads, Smem::kDynamic, stream>>>(map_q, map_k, map_v, map_o, args);

@@ -188,8 +188,10 @@ def _device_healthy():
 
 
 @pytest.mark.parametrize("causal", [True, False])
-@pytest.mark.parametrize("batch,hq,hkv,seq", [(1, 2, 2, 128), (2, 4, 2, 384), (1, 8, 1, 640)])
+@pytest.mark.parametrize("batch,hq,hkv,seq", [(1, 2, 2, 128), (2, 4, 2, 384), (1, 8, 1, 640), (1, 4, 2, 256), (2, 2, 1, 768)])
 def test_umma_sdpa_matches_oracle(causal, batch, hq, hkv, seq):
+    """Sequence lengths that are a multiple of 256 take the form with two query tiles per CTA
+    (probabilities kept in tensor memory), the others one tile per CTA."""
     flags = dict(has_right_bound=1, right_bound=0) if causal else {}
     info, o, o_ref, rows, rows_ref = both(BF16, [batch, hq, seq, 128], [batch, hkv, seq, 128], [batch, hkv, seq, 128], seq,
                                           128 ** -0.5, dfgpu.SDPA_UMMA, stats=False, seed=17, **flags)
