@@ -315,6 +315,14 @@ sdpa_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 // products of one CTA in issue order, so S_X(j+1) may be issued right behind the product that reads P_X(j).
 // Under a causal mask tile A (the earlier rows) has one key tile fewer than tile B.
 
+// Cycle stamps of the first CTA's three roles (softmax A, softmax B, issuing lane), for tuning builds only.
+#ifdef DFGPU_SDPA_TRACE
+__device__ long long g_sdpa_trace[3][64][10];
+#define SDPA_TRACE(role, j, k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (j) < 64) g_sdpa_trace[role][j][k] = clock64(); } while (0)
+#else
+#define SDPA_TRACE(role, j, k) do {} while (0)
+#endif
+
 constexpr int kPairSlots = 5;
 constexpr int kPairThreads = 320;
 
@@ -447,23 +455,30 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             umma_commit(kv_empty(0));
             for (int j = 0; j < tiles_b; ++j) {
                 const int tv = 2 * j + 1, tk = 2 * j + 2;
+                SDPA_TRACE(2, j, 0);
                 wait_slot(tv, 226);
+                SDPA_TRACE(2, j, 1);
                 if (j < tiles_a) {
                     product(0, j);
                     if (j == tiles_a - 1) umma_commit(o_full(0));
                 }
+                SDPA_TRACE(2, j, 2);
                 if (j + 1 < tiles_b) wait_slot(tk, 227);
+                SDPA_TRACE(2, j, 3);
                 if (j + 1 < tiles_a) {
                     scores(0, j + 1);
                     umma_commit(s_full(0));
                 }
+                SDPA_TRACE(2, j, 4);
                 product(1, j);
+                SDPA_TRACE(2, j, 5);
                 umma_commit(kv_empty(tv % kPairSlots));
                 if (j + 1 < tiles_b) {
                     scores(1, j + 1);
                     umma_commit(s_full(1));
                     umma_commit(kv_empty(tk % kPairSlots));
                 }
+                SDPA_TRACE(2, j, 6);
             }
             umma_commit(o_full(1));
         }
@@ -482,12 +497,15 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         float l_sum = 0.0f;
         bool ok = true;
         for (int j = 0; j < my_tiles; ++j) {
+            if (threadIdx.x == 64 + x * 128) SDPA_TRACE(x, j, 0);
             if (ok) ok = mbar_wait(s_full(x), j & 1, 228 + x);
             tc_fence_after();
+            if (threadIdx.x == 64 + x * 128) SDPA_TRACE(x, j, 1);
             uint32_t raw[4][32];
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_load_32(tmem_s + c * 32, raw[c]);
             tmem_load_wait();
+            if (threadIdx.x == 64 + x * 128) SDPA_TRACE(x, j, 2);
             if (args.causal && j == q_tile) {
                 const int limit = q_index - j * kKeys;  // keys 0..limit of this tile are visible
 #pragma unroll
@@ -524,6 +542,7 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     }
                 }
             }
+            if (threadIdx.x == 64 + x * 128) SDPA_TRACE(x, j, 3);
             const float bias = -m_ref;
             float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
@@ -541,10 +560,12 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 tmem_store_32(tmem_s + half * 32, packed);
             }
             l_sum += (sums[0] + sums[1]) + (sums[2] + sums[3]);
+            if (threadIdx.x == 64 + x * 128) SDPA_TRACE(x, j, 4);
             tmem_store_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full(x));
+            if (threadIdx.x == 64 + x * 128) SDPA_TRACE(x, j, 5);
         }
         // last product done -> normalise, stage O in this tile's Q buffer (no product reads it any more), TMA store
         if (ok) ok = mbar_wait(o_full(x), 0, 230 + x);
