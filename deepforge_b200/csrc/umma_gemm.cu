@@ -279,6 +279,14 @@ struct PersistentArgs {
     int32_t bias_stride;   // output channels (floats per staged bias vector)
 };
 
+// Cycle stamps of the first CTA's roles (loader, issuing lane, two epilogue groups), for tuning builds only.
+#ifdef DFGPU_CONV_TRACE
+__device__ long long g_conv_trace[4][128][4];
+#define CONV_TRACE(role, n, k) do { if (blockIdx.x == 0 && (n) < 128) g_conv_trace[role][n][k] = clock64(); } while (0)
+#else
+#define CONV_TRACE(role, n, k) do {} while (0)
+#endif
+
 template <int BN, bool HAS_RES>
 __global__ void __launch_bounds__(kPersistentThreads, 1)
 umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -307,7 +315,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     const uint32_t tmem_slot = bar_base + 8u * (2 * kMaxRingStages + 17);
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + pargs.barrier_offset + 8 * (2 * kMaxRingStages + 17));
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
 
     auto tile_geometry = [&](int tile, int& m_tile, int& n_tile, int& image, int& h0, int64_t& out_row0) {
         m_tile = tile / pargs.n_tiles;
@@ -323,53 +331,106 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         }
     };
     const uint32_t a_bytes = args.is_conv ? static_cast<uint32_t>(args.rows_per_tile * args.out_q * kBlockK * 2) : kABytes;
-    // One ring slot = G consecutive K slices of one tile; `it` numbers the slots this CTA fills.
-    auto issue_group = [&](uint32_t it, int tile, int kb0) {
+
+    // ---- loader state (warp 0). The loop below runs on all 32 lanes with warp-uniform control flow and
+    // only the TMA instructions are predicated on one elected lane: a loop that runs inside a single-lane
+    // branch pays hundreds of cycles per copy for address arithmetic on the vector pipe. No divisions per
+    // copy either: the filter tap and channel block advance as counters.
+    struct Loader {
+        int tile, index;          // current tile and its position in this CTA's list
+        int kb0;                  // next K slice of the tile
+        int tap_r, tap_s, cblk;   // filter tap and 64-channel block of that slice
+        int stage;                // ring slot to fill next
+        uint32_t phase;           // parity of that slot's "free" wait
+        uint32_t filled;          // slots filled so far
         int m_tile, n_tile, image, h0;
         int64_t out_row0;
-        tile_geometry(tile, m_tile, n_tile, image, h0, out_row0);
-        const int s = it % STAGES;
-        mbar_expect_tx(full_bar(s), a_bytes * G);
-        for (int g = 0; g < G; ++g) {
-            const int kb = kb0 + g;
-            const uint32_t a_dst = ring_base + (s * G + g) * kABytes;
-            const int tap = kb / args.k_blocks_per_tap;
-            const int c0 = (kb - tap * args.k_blocks_per_tap) * kBlockK;
-            if (args.is_conv) {
-                const int r = tap / args.filter_s, sx = tap - r * args.filter_s;
-                tma_load_4d(a_dst, &map_a, c0, sx - args.pad_w, h0 + r - args.pad_h, image, full_bar(s));
-            } else {
-                tma_load_2d(a_dst, &map_a, kb * kBlockK, m_tile * kTileM, full_bar(s));
+        bool open;                // geometry computed (and residual requested) for `tile`
+        bool ok;
+    } ld{};
+    const bool leader = elect_one();  // per warp: the lane that issues this warp's asynchronous instructions
+    // Fills ring slots until the tile list ends or, with `bounded`, until the first ring-full is in flight
+    // (nothing in that part can wait on another warp, so it runs ahead of the CTA-wide barrier).
+    auto run_loader = [&](bool bounded) {
+        const uint32_t res_bytes = static_cast<uint32_t>(pargs.box_rows) * 128u * (BN / 64);
+        while (ld.ok && ld.tile < pargs.total_tiles) {
+            if (!ld.open) {
+                if (bounded && HAS_RES && ld.index >= 4) return;
+                tile_geometry(ld.tile, ld.m_tile, ld.n_tile, ld.image, ld.h0, ld.out_row0);
+                if (HAS_RES) {
+                    const int i = ld.index;
+                    const int b = (i & 1) * 2 + ((i >> 1) & 1);  // the owning epilogue group's next buffer
+                    ld.ok = mbar_wait_warp(res_empty_bar(b), ((i >> 2) & 1) ^ 1, 111);
+                    if (!ld.ok) return;
+                    if (leader) {
+                        mbar_expect_tx(res_full_bar(b), res_bytes);
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_2d(epi_base + b * kEpiBytes + j * (kTileM * 128), &map_res, ld.n_tile * BN + 64 * j, static_cast<int>(ld.out_row0), res_full_bar(b));
+                    }
+                }
+                ld.open = true;
+            }
+            if (bounded && ld.filled >= static_cast<uint32_t>(STAGES)) return;
+            if (leader) CONV_TRACE(0, ld.filled, 0);
+            ld.ok = mbar_wait_warp(empty_bar(ld.stage), ld.phase, 112);
+            if (!ld.ok) return;
+            if (leader) CONV_TRACE(0, ld.filled, 1);
+            if (leader) mbar_expect_tx(full_bar(ld.stage), a_bytes * G);
+            for (int g = 0; g < G; ++g) {
+                const uint32_t a_dst = ring_base + (ld.stage * G + g) * kABytes;
+                if (args.is_conv) {
+                    if (leader) tma_load_4d(a_dst, &map_a, ld.cblk * kBlockK, ld.tap_s - args.pad_w, ld.h0 + ld.tap_r - args.pad_h, ld.image, full_bar(ld.stage));
+                } else {
+                    if (leader) tma_load_2d(a_dst, &map_a, (ld.kb0 + g) * kBlockK, ld.m_tile * kTileM, full_bar(ld.stage));
+                }
+                if (++ld.cblk == args.k_blocks_per_tap) {
+                    ld.cblk = 0;
+                    if (++ld.tap_s == args.filter_s) { ld.tap_s = 0; ++ld.tap_r; }
+                }
+            }
+            if (leader) CONV_TRACE(0, ld.filled, 2);
+            ++ld.filled;
+            if (++ld.stage == STAGES) { ld.stage = 0; ld.phase ^= 1; }
+            ld.kb0 += G;
+            if (ld.kb0 >= args.k_blocks) {
+                ld.tile += gridDim.x;
+                ++ld.index;
+                ld.kb0 = 0;
+                ld.tap_r = ld.tap_s = ld.cblk = 0;
+                ld.open = false;
             }
         }
     };
-    const int groups_per_tile = args.k_blocks / G;
-    uint32_t prefetched = 0;  // ring slots already filled by the prologue (thread 0 only)
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), 1);
+    if (warp == 0) {
+        if (leader) {
+            for (int s = 0; s < STAGES; ++s) {
+                mbar_init(full_bar(s), 1);
+                mbar_init(empty_bar(s), 1);
+            }
+            for (int a = 0; a < kAccumulators; ++a) {
+                mbar_init(acc_full_bar(a), 1);
+                mbar_init(acc_empty_bar(a), 4);  // one arrival per warp of the group that drained it
+            }
+            for (int b = 0; b < 4; ++b) {
+                mbar_init(res_full_bar(b), 1);
+                mbar_init(res_empty_bar(b), 1);  // the thread that issues that group's TMA stores
+            }
+            mbar_init(w_full_bar, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            mbar_expect_tx(w_full_bar, static_cast<uint32_t>(pargs.filter_bytes));
         }
-        for (int a = 0; a < kAccumulators; ++a) {
-            mbar_init(acc_full_bar(a), 1);
-            mbar_init(acc_empty_bar(a), 4);  // one arrival per warp of the group that drained it
-        }
-        for (int b = 0; b < 4; ++b) {
-            mbar_init(res_full_bar(b), 1);
-            mbar_init(res_empty_bar(b), 1);  // the thread that issues that group's TMA stores
-        }
-        mbar_init(w_full_bar, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        __syncwarp();
         // Start streaming right away: the filter and the first ring-full of activations are in flight
         // while the other warps allocate tensor memory and stage the bias vectors.
-        mbar_expect_tx(w_full_bar, static_cast<uint32_t>(pargs.filter_bytes));
         for (int nt = 0; nt < pargs.n_tiles; ++nt)
             for (int kb = 0; kb < args.k_blocks; ++kb)
-                tma_load_2d(w_base + (nt * args.k_blocks + kb) * kBTileBytes, &map_b, kb * kBlockK, nt * BN, w_full_bar);
-        for (int tile = blockIdx.x; tile < pargs.total_tiles && prefetched < static_cast<uint32_t>(STAGES); tile += gridDim.x)
-            for (int grp = 0; grp < groups_per_tile && prefetched < static_cast<uint32_t>(STAGES); ++grp, ++prefetched)
-                issue_group(prefetched, tile, grp * G);
+                if (leader) tma_load_2d(w_base + (nt * args.k_blocks + kb) * kBTileBytes, &map_b, kb * kBlockK, nt * BN, w_full_bar);
+        ld.tile = blockIdx.x;
+        ld.phase = 1;
+        ld.ok = true;
+        run_loader(true);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, kAccumulators * BN);
@@ -392,62 +453,41 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     const uint32_t tmem_base = *tmem_slot_ptr;
 
     if (warp == 0) {
-        if (lane == 0) {
-            const uint32_t res_bytes = static_cast<uint32_t>(pargs.box_rows) * 128u * (BN / 64);
-            uint32_t it = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x, i = 0; tile < pargs.total_tiles && ok; tile += gridDim.x, ++i) {
-                int m_tile, n_tile, image, h0;
-                int64_t out_row0;
-                tile_geometry(tile, m_tile, n_tile, image, h0, out_row0);
-                if (HAS_RES) {
-                    const int b = (i & 1) * 2 + ((i >> 1) & 1);  // the owning epilogue group's next buffer
-                    ok = mbar_wait(res_empty_bar(b), ((i >> 2) & 1) ^ 1, 111);
-                    if (!ok) break;
-                    mbar_expect_tx(res_full_bar(b), res_bytes);
-#pragma unroll
-                    for (int j = 0; j < BN / 64; ++j)
-                        tma_load_2d(epi_base + b * kEpiBytes + j * (kTileM * 128), &map_res, n_tile * BN + 64 * j, static_cast<int>(out_row0), res_full_bar(b));
-                }
-                for (int kb0 = 0; kb0 < args.k_blocks; kb0 += G, ++it) {
-                    if (it < prefetched) continue;  // already issued by the prologue
-                    const int s = it % STAGES;
-                    ok = mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, 112);
-                    if (!ok) break;
-                    issue_group(it, tile, kb0);
-                }
-            }
-        }
+        run_loader(false);
     } else if (warp == 1) {
-        if (lane == 0) {
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
-                                   (static_cast<uint32_t>(kTileM >> 4) << 24);
-            uint32_t it = 0;
-            bool ok = mbar_wait(w_full_bar, 0, 117);
-            for (int tile = blockIdx.x, i = 0; tile < pargs.total_tiles; tile += gridDim.x, ++i) {
-                const int acc = i % kAccumulators;
-                const int n_tile = tile % pargs.n_tiles;
-                if (ok) ok = mbar_wait(acc_empty_bar(acc), ((i / kAccumulators) & 1) ^ 1, 113);
+        // All 32 lanes walk the schedule; the elected lane issues the products and their commits.
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                               (static_cast<uint32_t>(kTileM >> 4) << 24);
+        const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+        int stage = 0;
+        uint32_t phase = 0, it = 0;
+        bool ok = mbar_wait_warp(w_full_bar, 0, 117);
+        for (int tile = blockIdx.x, i = 0; tile < pargs.total_tiles; tile += gridDim.x, ++i) {
+            const int acc = i % kAccumulators;
+            const int n_tile = tile % pargs.n_tiles;
+            if (ok) ok = mbar_wait_warp(acc_empty_bar(acc), ((i / kAccumulators) & 1) ^ 1, 113);
+            tc_fence_after();
+            const uint32_t tmem_acc = tmem_u + static_cast<uint32_t>(acc * BN);
+            for (int kb0 = 0; kb0 < args.k_blocks && ok; kb0 += G, ++it) {
+                if (leader) CONV_TRACE(1, it, 0);
+                ok = mbar_wait_warp(full_bar(stage), phase, 114);
+                if (!ok) break;
                 tc_fence_after();
-                const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * BN);
-                for (int kb0 = 0; kb0 < args.k_blocks && ok; kb0 += G, ++it) {
-                    const int s = it % STAGES;
-                    ok = mbar_wait(full_bar(s), (it / STAGES) & 1, 114);
-                    if (!ok) break;
-                    tc_fence_after();
-                    {
-                        for (int g = 0; g < G; ++g) {
-                            const uint32_t a_src = ring_base + (s * G + g) * kABytes;
-                            const uint32_t b_src = w_base + (n_tile * args.k_blocks + kb0 + g) * kBTileBytes;
+                if (leader) CONV_TRACE(1, it, 1);
+                for (int g = 0; g < G; ++g) {
+                    const uint32_t a_src = ring_base + (stage * G + g) * kABytes;
+                    const uint32_t b_src = w_base + (n_tile * args.k_blocks + kb0 + g) * kBTileBytes;
 #pragma unroll
-                            for (int k = 0; k < kBlockK / 16; ++k)
-                                umma_bf16(tmem_acc, smem_desc(a_src + k * 32, 16, 1024), smem_desc(b_src + k * 32, 16, 1024), idesc, (kb0 | g | k) != 0 ? 1u : 0u);
-                        }
+                    for (int k = 0; k < kBlockK / 16; ++k) {
+                        const uint64_t desc_a = smem_desc(a_src + k * 32, 16, 1024), desc_b = smem_desc(b_src + k * 32, 16, 1024);
+                        if (leader) umma_bf16(tmem_acc, desc_a, desc_b, idesc, (kb0 | g | k) != 0 ? 1u : 0u);
                     }
-                    umma_commit(empty_bar(s));
                 }
-                umma_commit(acc_full_bar(acc));  // arrives even after a failed wait so the epilogue never hangs
+                if (leader) umma_commit(empty_bar(stage));
+                if (leader) CONV_TRACE(1, it, 2);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
+            if (leader) umma_commit(acc_full_bar(acc));  // arrives even after a failed wait so the epilogue never hangs
         }
     } else {
         // two epilogue warpgroups: group g drains accumulator g, i.e. every other tile
@@ -465,7 +505,9 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const int i = group + 2 * j;  // position of this tile in the CTA's tile list
             const int acc = i % kAccumulators;
             const int buf = HAS_RES ? group * 2 + (j & 1) : group;
+            if (store_thread) CONV_TRACE(2 + group, j, 0);
             if (ok) ok = mbar_wait(acc_full_bar(acc), (i / kAccumulators) & 1, 115);
+            if (store_thread) CONV_TRACE(2 + group, j, 1);
             if (HAS_RES) {
                 if (ok) ok = mbar_wait(res_full_bar(buf), (j >> 1) & 1, 116);
             } else {
@@ -530,6 +572,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 }
             }
             // release the accumulator, then publish the finished tile
+            if (store_thread) CONV_TRACE(2 + group, j, 2);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty_bar(acc));
@@ -547,6 +590,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     tma_store_wait_read<1>();
                     mbar_arrive(res_empty_bar(group * 2 + ((j - 1) & 1)));
                 }
+                CONV_TRACE(2 + group, j, 3);
             }
         }
         if (store_thread) tma_store_wait_all();

@@ -66,6 +66,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
     return mbar_wait_slow(bar, parity, code);
 }
 
+// Whole-warp forms for the loader and issuing warps. Their loops run on all 32 lanes with warp-uniform
+// control flow, so addresses, descriptors and counters live in uniform registers (the operands the TMA
+// and tcgen05 instructions take) and only the asynchronous instruction itself is predicated on one
+// elected lane; a loop that runs inside `if (lane == 0)` pays a vector-to-uniform move per operand.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int code) {
+#pragma unroll 1
+    for (int spin = 0; spin < 64; ++spin)
+        if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+    return __all_sync(0xffffffffu, mbar_wait_slow(bar, parity, code)) != 0;
+}
+__device__ __forceinline__ bool elect_one() {
+    uint32_t elected;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(elected));
+    return elected != 0;
+}
+__device__ __forceinline__ int uniform_warp_index() { return __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0); }
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");

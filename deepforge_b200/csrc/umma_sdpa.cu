@@ -366,7 +366,7 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const uint32_t tmem_slot = bar_base + 8u * PairSmem::kBarrierCount;
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + PairSmem::kBarriers + 8 * PairSmem::kBarrierCount);
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
     const int pairs = args.q_tiles >> 1;
     const int pair = pairs - 1 - static_cast<int>(blockIdx.x);  // heavy (late) causal pairs first
     const int bh = blockIdx.y;
@@ -402,86 +402,107 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const uint32_t tmem_base = *tmem_slot_ptr;
 
     if (warp == 0) {
-        if (lane == 0) {
+        const bool leader = elect_one();
+        if (leader) {
             mbar_expect_tx(q_full, 2 * kTileBytes);
             for (int x = 0; x < 2; ++x) {
                 tma_load_2d(smem_base + PairSmem::kQ + x * kTileBytes, &map_q, 0, q_row_a + x * kRows, q_full);
                 tma_load_2d(smem_base + PairSmem::kQ + x * kTileBytes + kHalfBytes, &map_q, 64, q_row_a + x * kRows, q_full);
             }
-            for (int t = 0; t < 2 * tiles_b; ++t) {
-                const int slot = t % kPairSlots;
-                if (!mbar_wait(kv_empty(slot), ((t / kPairSlots) & 1) ^ 1, 221)) break;
+        }
+        int slot = 0;
+        uint32_t phase = 1;  // parity of the "slot is free" wait
+        for (int t = 0; t < 2 * tiles_b; ++t) {
+            if (!mbar_wait_warp(kv_empty(slot), phase, 221)) break;
+            const int row = kv_row0 + (t >> 1) * kKeys;
+            const uint32_t dst = smem_base + PairSmem::kRing + slot * kTileBytes;
+            if (leader) {
                 const CUtensorMap* map = (t & 1) ? &map_v : &map_k;
-                const int row = kv_row0 + (t >> 1) * kKeys;
-                const uint32_t dst = smem_base + PairSmem::kRing + slot * kTileBytes;
                 mbar_expect_tx(kv_full(slot), kTileBytes);
                 tma_load_2d(dst, map, 0, row, kv_full(slot));
                 tma_load_2d(dst + kHalfBytes, map, 64, row, kv_full(slot));
             }
+            if (++slot == kPairSlots) { slot = 0; phase ^= 1; }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kKeys >> 3) << 17) | (static_cast<uint32_t>(kRows >> 4) << 24);
-            const uint32_t idesc_pv = idesc_qk | (1u << 16);  // B = V read MN-major
-            bool ok = mbar_wait(q_full, 0, 222);
-            auto wait_slot = [&](int t, int code) {
-                if (ok) ok = mbar_wait(kv_full(t % kPairSlots), (t / kPairSlots) & 1, code);
-                tc_fence_after();
-            };
-            auto scores = [&](int x, int j) {  // S_x = Q_x K_j^T
-                if (!ok) return;
-                const uint32_t q_smem = smem_base + PairSmem::kQ + x * kTileBytes;
-                const uint32_t k_smem = smem_base + PairSmem::kRing + ((2 * j) % kPairSlots) * kTileBytes;
+        // All 32 lanes walk the schedule; the elected lane issues the products and their commits.
+        const bool leader = elect_one();
+        const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kKeys >> 3) << 17) | (static_cast<uint32_t>(kRows >> 4) << 24);
+        const uint32_t idesc_pv = idesc_qk | (1u << 16);  // B = V read MN-major
+        const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+        bool ok = mbar_wait_warp(q_full, 0, 222);
+        int slot = 0;         // ring slot of the next K or V tile to consume
+        uint32_t phase = 0;
+        auto wait_slot = [&](int code) {
+            if (ok) ok = mbar_wait_warp(kv_full(slot), phase, code);
+            tc_fence_after();
+        };
+        auto next_slot = [&]() { if (++slot == kPairSlots) { slot = 0; phase ^= 1; } };
+        auto commit = [&](uint32_t bar) { if (leader) umma_commit(bar); };
+        auto scores = [&](int x, int k_slot) {  // S_x = Q_x K^T
+            if (!ok) return;
+            const uint32_t q_smem = smem_base + PairSmem::kQ + x * kTileBytes;
+            const uint32_t k_smem = smem_base + PairSmem::kRing + k_slot * kTileBytes;
 #pragma unroll
-                for (int k = 0; k < kHeadDim / 16; ++k) {
-                    const uint32_t offset = (k >> 2) * kHalfBytes + (k & 3) * 32;
-                    umma_bf16(tmem_base + x * 128, smem_desc(q_smem + offset, 16, 1024), smem_desc(k_smem + offset, 16, 1024), idesc_qk, k != 0 ? 1u : 0u);
-                }
-            };
-            auto product = [&](int x, int j) {  // O_x += P_x V_j, P_x as bf16 pairs in the front 64 columns of S_x
-                if (ok) ok = mbar_wait(p_full(x), j & 1, 223 + x);
-                tc_fence_after();
-                if (!ok) return;
-                const uint32_t v_smem = smem_base + PairSmem::kRing + ((2 * j + 1) % kPairSlots) * kTileBytes;
-#pragma unroll
-                for (int k = 0; k < kKeys / 16; ++k)
-                    umma_bf16_a_tmem(tmem_base + 256 + x * 128, tmem_base + x * 128 + k * 8, smem_desc(v_smem + k * 2048, kHalfBytes, 1024), idesc_pv, (j | k) != 0 ? 1u : 0u);
-            };
-            wait_slot(0, 225);
-            scores(0, 0);
-            umma_commit(s_full(0));
-            scores(1, 0);
-            umma_commit(s_full(1));
-            umma_commit(kv_empty(0));
-            for (int j = 0; j < tiles_b; ++j) {
-                const int tv = 2 * j + 1, tk = 2 * j + 2;
-                SDPA_TRACE(2, j, 0);
-                wait_slot(tv, 226);
-                SDPA_TRACE(2, j, 1);
-                if (j < tiles_a) {
-                    product(0, j);
-                    if (j == tiles_a - 1) umma_commit(o_full(0));
-                }
-                SDPA_TRACE(2, j, 2);
-                if (j + 1 < tiles_b) wait_slot(tk, 227);
-                SDPA_TRACE(2, j, 3);
-                if (j + 1 < tiles_a) {
-                    scores(0, j + 1);
-                    umma_commit(s_full(0));
-                }
-                SDPA_TRACE(2, j, 4);
-                product(1, j);
-                SDPA_TRACE(2, j, 5);
-                umma_commit(kv_empty(tv % kPairSlots));
-                if (j + 1 < tiles_b) {
-                    scores(1, j + 1);
-                    umma_commit(s_full(1));
-                    umma_commit(kv_empty(tk % kPairSlots));
-                }
-                SDPA_TRACE(2, j, 6);
+            for (int k = 0; k < kHeadDim / 16; ++k) {
+                const uint32_t offset = (k >> 2) * kHalfBytes + (k & 3) * 32;
+                const uint64_t desc_q = smem_desc(q_smem + offset, 16, 1024), desc_k = smem_desc(k_smem + offset, 16, 1024);
+                if (leader) umma_bf16(tmem_u + x * 128, desc_q, desc_k, idesc_qk, k != 0 ? 1u : 0u);
             }
-            umma_commit(o_full(1));
+        };
+        auto product = [&](int x, int j, int v_slot) {  // O_x += P_x V_j, P_x as bf16 pairs in the front 64 columns of S_x
+            if (ok) ok = mbar_wait_warp(p_full(x), j & 1, 223 + x);
+            tc_fence_after();
+            if (!ok) return;
+            const uint32_t v_smem = smem_base + PairSmem::kRing + v_slot * kTileBytes;
+#pragma unroll
+            for (int k = 0; k < kKeys / 16; ++k) {
+                const uint64_t desc_v = smem_desc(v_smem + k * 2048, kHalfBytes, 1024);
+                if (leader) umma_bf16_a_tmem(tmem_u + 256 + x * 128, tmem_u + x * 128 + k * 8, desc_v, idesc_pv, (j | k) != 0 ? 1u : 0u);
+            }
+        };
+        wait_slot(225);
+        scores(0, slot);
+        commit(s_full(0));
+        scores(1, slot);
+        commit(s_full(1));
+        commit(kv_empty(slot));
+        next_slot();
+        for (int j = 0; j < tiles_b; ++j) {
+            if (leader) SDPA_TRACE(2, j, 0);
+            wait_slot(226);
+            const int v_slot = slot;
+            next_slot();
+            if (leader) SDPA_TRACE(2, j, 1);
+            if (j < tiles_a) {
+                product(0, j, v_slot);
+                if (j == tiles_a - 1) commit(o_full(0));
+            }
+            if (leader) SDPA_TRACE(2, j, 2);
+            const bool more = j + 1 < tiles_b;
+            int k_slot = 0;
+            if (more) {
+                wait_slot(227);
+                k_slot = slot;
+                next_slot();
+            }
+            if (leader) SDPA_TRACE(2, j, 3);
+            if (j + 1 < tiles_a) {
+                scores(0, k_slot);
+                commit(s_full(0));
+            }
+            if (leader) SDPA_TRACE(2, j, 4);
+            product(1, j, v_slot);
+            if (leader) SDPA_TRACE(2, j, 5);
+            commit(kv_empty(v_slot));
+            if (more) {
+                scores(1, k_slot);
+                commit(s_full(1));
+                commit(kv_empty(k_slot));
+            }
+            if (leader) SDPA_TRACE(2, j, 6);
         }
+        commit(o_full(1));
     } else {
         const int x = (warp - 2) >> 2;  // 0: tile A, 1: tile B
         const int quadrant = warp & 3;
