@@ -13,6 +13,11 @@ int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStrea
 bool matmul_umma_supported(const dfgpu_matmul_params& p, int kernel);
 int launch_matmul_umma(const dfgpu_matmul_params& p, void* const* tensors, int kernel, cudaStream_t stream);
 
+// MATMUL on MXFP8 codes + E8M0 block scales (tcgen05 block-scaled kind), no dequantize pass.
+bool matmul_mxf8_supported(const dfgpu_matmul_params& p);
+int launch_matmul_mxf8(const dfgpu_matmul_params& p, void* const* tensors, cudaStream_t stream);
+int mxf8_device_status(int* status);
+
 // SDPA forward on tcgen05 (bf16, head dim 128, contiguous K/V).
 bool sdpa_umma_supported(const dfgpu_sdpa_params& p);
 int launch_sdpa_umma(const dfgpu_sdpa_params& p, void* const* tensors, void* scratch, cudaStream_t stream);

@@ -505,6 +505,12 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const int i = group + 2 * j;  // position of this tile in the CTA's tile list
             const int acc = i % kAccumulators;
             const int buf = HAS_RES ? group * 2 + (j & 1) : group;
+            if (HAS_RES && store_thread && j >= 1) {
+                // The store of this group's previous tile has had a whole wait to read its buffer: hand the
+                // buffer back now, so that its next residual tile streams in while this tile is worked on.
+                tma_store_wait_read<0>();
+                mbar_arrive(res_empty_bar(group * 2 + ((j - 1) & 1)));
+            }
             if (store_thread) CONV_TRACE(2 + group, j, 0);
             if (ok) ok = mbar_wait(acc_full_bar(acc), (i / kAccumulators) & 1, 115);
             if (store_thread) CONV_TRACE(2 + group, j, 1);
@@ -585,11 +591,6 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                         tma_store_2d(&map_out, epi_base + buf * kEpiBytes + q * (kTileM * 128), n0 + 64 * q, static_cast<int>(out_row0));
                 }
                 tma_store_commit();
-                if (HAS_RES && j >= 1) {
-                    // this group's previous store has finished reading its buffer: hand it back for a residual prefetch
-                    tma_store_wait_read<1>();
-                    mbar_arrive(res_empty_bar(group * 2 + ((j - 1) & 1)));
-                }
                 CONV_TRACE(2 + group, j, 3);
             }
         }
@@ -850,7 +851,8 @@ int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStrea
 }
 
 bool matmul_umma_supported(const dfgpu_matmul_params& p, int kernel) {
-    if (kernel != DFGPU_MATMUL_UMMA_BF16) return false;  // the MXFP8 variant is not built yet
+    if (kernel == DFGPU_MATMUL_UMMA_MXF8) return matmul_mxf8_supported(p);
+    if (kernel != DFGPU_MATMUL_UMMA_BF16) return false;
     if (p.a_scale.rank || p.b_scale.rank) return false;
     if (p.a.dtype != DFGPU_BF16 || p.b.dtype != DFGPU_BF16 || (p.c.dtype != DFGPU_BF16 && p.c.dtype != DFGPU_F32)) return false;
     const int rank = p.c.rank;
@@ -868,7 +870,7 @@ bool matmul_umma_supported(const dfgpu_matmul_params& p, int kernel) {
 }
 
 int launch_matmul_umma(const dfgpu_matmul_params& p, void* const* tensors, int kernel, cudaStream_t stream) {
-    (void)kernel;
+    if (kernel == DFGPU_MATMUL_UMMA_MXF8) return launch_matmul_mxf8(p, tensors, stream);
     const int rank = p.c.rank;
     const int64_t M = p.c.dim[rank - 2], N = p.c.dim[rank - 1], K = p.a.dim[rank - 1];
     if (!aligned16(tensors[0]) || !aligned16(tensors[1]) || !aligned16(tensors[2]))
@@ -921,9 +923,12 @@ int launch_matmul_umma(const dfgpu_matmul_params& p, void* const* tensors, int k
 extern "C" int dfgpu_device_status(int* status) {
     using namespace dfgpu;
     if (!status) return fail(kInvalidArgument, "device_status: null pointer");
-    int gemm = 0, sdpa = 0, decode = 0;
+    int gemm = 0, sdpa = 0, decode = 0, mxf8 = 0;
     int code = read_and_clear_device_status(&gemm);
     if (code) return code;
+    code = mxf8_device_status(&mxf8);
+    if (code) return code;
+    if (!gemm) gemm = mxf8;
     code = sdpa_umma_device_status(&sdpa);
     if (code) return code;
     code = decode_umma_device_status(&decode);

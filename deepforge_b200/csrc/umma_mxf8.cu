@@ -1,0 +1,432 @@
+// MATMUL on MXFP8 operands without a dequantize pass: C = (A_codes * 2^SFA) (B_codes * 2^SFB).
+//
+// The E4M3 codes and their E8M0 block scales (one per 32 elements along K) go straight into the
+// block-scaled tensor-core instruction (tcgen05.mma.kind::mxf8f6f4.block_scale): the products of two
+// E4M3 values are exact, the power-of-two scales are applied per 32-deep block, accumulation is f32 in
+// tensor memory. That is the arithmetic of BLOCK_SCALE_DEQUANTIZE -> MATMUL in the reference
+// (lib/Compiler/SpecializedGraph.cpp:752-795 feeding FoundationalGraph.cpp:3167-3295) up to the order
+// of the f32 additions, and it reads 1 byte per element instead of writing and re-reading bf16 copies.
+//
+// Persistent kernel, one CTA per SM, 128 x BN output tile, K in steps of 128 elements (one 128-byte
+// swizzled row):
+//   warp 0      TMA: A tile (128 rows x 128 B) and B tile (BN x 128 B, K-major or N-major) into a 4-slot ring
+//   warp 1      per slot: tcgen05.cp of the slot's scale factors into tensor memory, then 4 products of K = 32,
+//               each selecting its scale byte through the instruction descriptor
+//   warps 2-5   epilogue: tcgen05.ld -> fused steps -> bf16 / f32 -> global
+//   warps 6-9   scale loaders, one ring slot each: gather the slot's 128 + BN scale words from the plain
+//               [rows, K/32] / [K/32, cols] tensors and lay them out in shared memory the way the tensor core wants
+//               them: 512-byte chunks of 128 rows x 4 K-blocks at (row % 32) * 16 + (row / 32) * 4 + block.
+// Whole-warp uniform loops with one elected lane issuing, bounded waits, no spinning on other launches.
+#include "umma.cuh"
+#include "umma_ptx.cuh"
+
+namespace dfgpu {
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kBlockK = 128;   // fp8 elements = bytes per swizzled row
+constexpr int kStages = 4;
+constexpr int kABytes = kTileM * kBlockK;
+constexpr int kSfaBytes = 512;
+constexpr int kMxThreads = 320;
+constexpr int kMaxSteps = DFGPU_MAX_EPILOGUE;
+
+enum { kStepRelu = 1, kStepBias = 2, kStepFull = 3 };
+
+struct MxArgs {
+    const uint8_t* sfa;  // [M, K/32] plain
+    const uint8_t* sfb;  // [K/32, N] plain
+    int64_t sfa_ld, sfb_ld;
+    void* out;
+    int64_t out_ld;
+    int32_t out_dtype;
+    int32_t m_tiles, n_tiles, k_blocks;
+    int32_t b_mn_major;
+    int32_t step_count;
+    int32_t step_kind[kMaxSteps];
+    float relu_lower[kMaxSteps], relu_upper[kMaxSteps], relu_slope[kMaxSteps];
+    const void* step_data[kMaxSteps];
+    int32_t step_dtype[kMaxSteps];
+    int64_t step_ld[kMaxSteps];
+};
+
+template <int BN>
+struct MxSmem {
+    static constexpr int kBBytes = BN * kBlockK;
+    static constexpr int kSfbBytes = (BN / 128) * 512;
+    static constexpr int kSfaOffset = kABytes + kBBytes;
+    static constexpr int kSfbOffset = kSfaOffset + kSfaBytes;
+    static constexpr int kStageBytes = kSfbOffset + 1024;  // keeps every slot 1024-byte aligned
+    static constexpr int kBarriers = kStages * kStageBytes;
+    // full[4], empty[4], acc_full, acc_empty
+    static constexpr int kBarrierCount = 2 * kStages + 2;
+    static constexpr int kTotal = kBarriers + kBarrierCount * 8 + 16;
+    static constexpr int kDynamic = kTotal + 1024;
+};
+
+// 32 rows x 16 bytes of shared memory -> 4 columns of tensor memory, replicated to the four lane quarters.
+__device__ __forceinline__ void tmem_copy_scales(uint32_t tmem_dst, uint64_t smem_descriptor) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(smem_descriptor) : "memory");
+}
+// Descriptor of an unswizzled K-major block for tcgen05.cp: 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t scale_desc(uint32_t address) {
+    uint64_t desc = 0;
+    desc |= static_cast<uint64_t>((address & 0x3FFFFu) >> 4);
+    desc |= static_cast<uint64_t>(128u >> 4) << 32;
+    desc |= 1ull << 46;
+    return desc;
+}
+__device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate,
+                                          uint32_t tmem_sfa, uint32_t tmem_sfb) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
+}
+
+__device__ __forceinline__ float load_step_f32(const void* base, int dtype, int64_t index) {
+    if (dtype == DFGPU_F32) return static_cast<const float*>(base)[index];
+    return __uint_as_float(static_cast<uint32_t>(static_cast<const uint16_t*>(base)[index]) << 16);
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kMxThreads, 1)
+umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, MxArgs args) {
+    using L = MxSmem<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + L::kBarriers;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    const uint32_t acc_full_bar = bar_base + 8u * (2 * kStages);
+    const uint32_t acc_empty_bar = bar_base + 8u * (2 * kStages + 1);
+    const uint32_t tmem_slot = bar_base + 8u * L::kBarrierCount;
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + L::kBarriers + 8 * L::kBarrierCount);
+
+    const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
+    const bool leader = elect_one();
+    const int total_tiles = args.m_tiles * args.n_tiles;
+
+    if (warp == 0) {
+        if (leader) {
+            for (int s = 0; s < kStages; ++s) {
+                mbar_init(full_bar(s), 2);   // the loader's expect_tx arrival + the scale warp of that slot
+                mbar_init(empty_bar(s), 1);  // tcgen05.commit
+            }
+            mbar_init(acc_full_bar, 1);
+            mbar_init(acc_empty_bar, 4);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+        tc_fence_before();
+    }
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ---- TMA loader ----
+        int stage = 0;
+        uint32_t phase = 1;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
+            for (int kb = 0; kb < args.k_blocks; ++kb) {
+                ok = mbar_wait_warp(empty_bar(stage), phase, 401);
+                if (!ok) break;
+                const uint32_t a_dst = smem_base + stage * L::kStageBytes;
+                const uint32_t b_dst = a_dst + kABytes;
+                if (leader) {
+                    mbar_expect_tx(full_bar(stage), kABytes + L::kBBytes);
+                    tma_load_2d(a_dst, &map_a, kb * kBlockK, m_tile * kTileM, full_bar(stage));
+                    if (args.b_mn_major) {
+#pragma unroll
+                        for (int j = 0; j < BN / 128; ++j)
+                            tma_load_2d(b_dst + j * (kBlockK * 128), &map_b, n_tile * BN + 128 * j, kb * kBlockK, full_bar(stage));
+                    } else {
+                        tma_load_2d(b_dst, &map_b, kb * kBlockK, n_tile * BN, full_bar(stage));
+                    }
+                }
+                if (++stage == kStages) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- issuing warp ----
+        // instruction descriptor: E4M3 x E4M3, E8M0 scales, A K-major, B per flag, N = BN, M = 128; the two
+        // scale-id fields (bits 4-5 for B, 29-30 for A) pick the K block's byte inside the scale columns
+        const uint32_t idesc_base = (static_cast<uint32_t>(args.b_mn_major) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) | (1u << 23) |
+                                    (static_cast<uint32_t>(kTileM >> 4) << 24);
+        const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+            if (ok) ok = mbar_wait_warp(acc_empty_bar, (local & 1) ^ 1, 402);
+            tc_fence_after();
+            for (int kb = 0; kb < args.k_blocks && ok; ++kb) {
+                ok = mbar_wait_warp(full_bar(stage), phase, 403);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_src = smem_base + stage * L::kStageBytes;
+                const uint32_t b_src = a_src + kABytes;
+                const uint32_t sf_tmem = tmem_u + 256 + (stage & 1) * 16;  // SFA at +0..3, SFB at +4..
+                if (leader) {
+                    tmem_copy_scales(sf_tmem, scale_desc(a_src + L::kSfaOffset));
+#pragma unroll
+                    for (int c = 0; c < BN / 128; ++c) tmem_copy_scales(sf_tmem + 4 + 4 * c, scale_desc(a_src + L::kSfbOffset + 512 * c));
+                }
+#pragma unroll
+                for (int j = 0; j < kBlockK / 32; ++j) {
+                    const uint64_t desc_a = smem_desc(a_src + j * 32, 16, 1024);
+                    const uint64_t desc_b = args.b_mn_major ? smem_desc(b_src + j * 4096, kBlockK * 128, 1024) : smem_desc(b_src + j * 32, 16, 1024);
+                    const uint32_t idesc = idesc_base | (static_cast<uint32_t>(j) << 29) | (static_cast<uint32_t>(j) << 4);
+                    if (leader) umma_mxf8(tmem_u, desc_a, desc_b, idesc, (kb | j) != 0 ? 1u : 0u, sf_tmem, sf_tmem + 4);
+                }
+                if (leader) umma_commit(empty_bar(stage));
+                if (++stage == kStages) { stage = 0; phase ^= 1; }
+            }
+            if (leader) umma_commit(acc_full_bar);  // arrives even after a failed wait so the epilogue never hangs
+        }
+    } else if (warp < 6) {
+        // ---- epilogue ----
+        const int quadrant = warp & 3;
+        const int row = quadrant * 32 + lane;
+        bool ok = true;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+            const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
+            if (ok) ok = mbar_wait(acc_full_bar, local & 1, 404);
+            tc_fence_after();
+            const bool healthy = ok && g_device_status == 0;
+            const int64_t out_row = static_cast<int64_t>(m_tile) * kTileM + row;
+#pragma unroll 1
+            for (int chunk = 0; chunk < BN / 32; ++chunk) {
+                uint32_t raw[32];
+                tmem_load_32(tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) + chunk * 32, raw);
+                tmem_load_wait();
+                float v[32];
+#pragma unroll
+                for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[e]);
+                const int64_t col0 = static_cast<int64_t>(n_tile) * BN + chunk * 32;
+                for (int s = 0; s < args.step_count; ++s) {
+                    const int kind = args.step_kind[s];
+                    if (kind == kStepRelu) {
+                        const float lower = args.relu_lower[s], upper = args.relu_upper[s], slope = args.relu_slope[s];
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) v[e] = relu_fast(v[e], lower, upper, slope);
+                    } else if (kind == kStepBias) {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) v[e] = __fadd_rn(v[e], load_step_f32(args.step_data[s], args.step_dtype[s], col0 + e));
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) v[e] = __fadd_rn(v[e], load_step_f32(args.step_data[s], args.step_dtype[s], out_row * args.step_ld[s] + col0 + e));
+                    }
+                }
+                if (healthy) {
+                    if (args.out_dtype == DFGPU_BF16) {
+                        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(args.out) + out_row * args.out_ld + col0);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                __nv_bfloat162 pair = __floats2bfloat162_rn(v[8 * q + 2 * t], v[8 * q + 2 * t + 1]);
+                                w[t] = *reinterpret_cast<uint32_t*>(&pair);
+                            }
+                            dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+                        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(args.out) + out_row * args.out_ld + col0);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar);
+        }
+    } else {
+        // ---- scale loaders: warp 6 + q owns ring slot q ----
+        const int slot = warp - 6;
+        uint32_t phase = 1;
+        bool ok = true;
+        int it = 0;  // ring events of this CTA, in the loader's order
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
+            for (int kb = 0; kb < args.k_blocks; ++kb, ++it) {
+                if ((it & (kStages - 1)) != slot) continue;
+                // issue the global loads first: they do not depend on the slot being free
+                uint32_t a_words[4];
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+                    a_words[g] = __ldg(reinterpret_cast<const uint32_t*>(args.sfa + (static_cast<int64_t>(m_tile) * kTileM + g * 32 + lane) * args.sfa_ld + kb * 4));
+                uint32_t b_words[BN / 128][4];
+#pragma unroll
+                for (int c = 0; c < BN / 128; ++c)
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const uint8_t* p = args.sfb + static_cast<int64_t>(kb) * 4 * args.sfb_ld + static_cast<int64_t>(n_tile) * BN + c * 128 + g * 32 + lane;
+                        const uint32_t b0 = __ldg(p), b1 = __ldg(p + args.sfb_ld), b2 = __ldg(p + 2 * args.sfb_ld), b3 = __ldg(p + 3 * args.sfb_ld);
+                        b_words[c][g] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+                    }
+                ok = mbar_wait_warp(empty_bar(slot), phase, 405);
+                phase ^= 1;
+                if (!ok) break;
+                uint8_t* stage_base = generic_base + slot * L::kStageBytes;
+                *reinterpret_cast<uint4*>(stage_base + L::kSfaOffset + lane * 16) = make_uint4(a_words[0], a_words[1], a_words[2], a_words[3]);
+#pragma unroll
+                for (int c = 0; c < BN / 128; ++c)
+                    *reinterpret_cast<uint4*>(stage_base + L::kSfbOffset + c * 512 + lane * 16) = make_uint4(b_words[c][0], b_words[c][1], b_words[c][2], b_words[c][3]);
+                fence_async_shared();
+                __syncwarp();
+                if (leader) mbar_arrive(full_bar(slot));
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+inline int make_map_u8(CUtensorMap* map, const void* base, const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box, const char* what) {
+    EncodeTiled encode = encode_tiled();
+    if (!encode) return fail(kExecutionFailed, "%s: cuTensorMapEncodeTiled is unavailable", what);
+    cuuint32_t element_strides[2] = {1, 1};
+    CUresult result = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), reinterpret_cast<const cuuint64_t*>(dims),
+                             reinterpret_cast<const cuuint64_t*>(strides_bytes), reinterpret_cast<const cuuint32_t*>(box), element_strides,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (result != CUDA_SUCCESS) return fail(kExecutionFailed, "%s: tensor map encode failed (CUresult %d)", what, static_cast<int>(result));
+    return kOk;
+}
+
+bool aligned(const void* p, uintptr_t to) { return (reinterpret_cast<uintptr_t>(p) & (to - 1)) == 0; }
+
+// The fused steps this kernel applies: ReLU, a per-column ADD operand, a full [M, N] ADD operand.
+bool translate_steps(const dfgpu_matmul_params& p, void* const* tensors, MxArgs* args) {
+    if (p.epilogue_count < 0 || p.epilogue_count > kMaxSteps) return false;
+    const int rank = p.c.rank;
+    if (args) args->step_count = p.epilogue_count;
+    for (int i = 0; i < p.epilogue_count; ++i) {
+        const dfgpu_epilogue_step& step = p.epilogue[i];
+        if (step.op == DFGPU_EPI_RELU) {
+            if (args) {
+                args->step_kind[i] = kStepRelu;
+                args->relu_lower[i] = step.relu_lower;
+                args->relu_upper[i] = step.relu_upper;
+                args->relu_slope[i] = step.relu_slope;
+            }
+            continue;
+        }
+        if (step.op != DFGPU_EPI_ADD || step.operand < 0 || step.operand > 1) return false;
+        const dfgpu_tensor& t = p.extra[step.operand];
+        if (t.rank < 1 || t.rank > rank || (t.dtype != DFGPU_BF16 && t.dtype != DFGPU_F32)) return false;
+        // operand axes align with the trailing axes of C: [.., 1 or M, N]
+        for (int axis = 0; axis < t.rank - 2; ++axis)
+            if (t.dim[axis] != 1) return false;
+        if (t.dim[t.rank - 1] != p.c.dim[rank - 1] || t.stride[t.rank - 1] != 1) return false;
+        const bool per_column = t.rank == 1 || t.dim[t.rank - 2] == 1;
+        if (!per_column && t.dim[t.rank - 2] != p.c.dim[rank - 2]) return false;
+        if (args) {
+            args->step_kind[i] = per_column ? kStepBias : kStepFull;
+            args->step_data[i] = tensors[5 + step.operand];
+            args->step_dtype[i] = t.dtype;
+            args->step_ld[i] = per_column ? 0 : t.stride[t.rank - 2];
+        }
+    }
+    return true;
+}
+
+}  // namespace
+
+bool matmul_mxf8_supported(const dfgpu_matmul_params& p) {
+    if (p.a.dtype != DFGPU_E4M3 || p.b.dtype != DFGPU_E4M3 || p.a_scale.dtype != DFGPU_E8M0 || p.b_scale.dtype != DFGPU_E8M0) return false;
+    if (p.c.dtype != DFGPU_BF16 && p.c.dtype != DFGPU_F32) return false;
+    const int rank = p.c.rank;
+    if (rank < 2 || p.a.rank != rank || p.b.rank != rank || p.a_scale.rank != rank || p.b_scale.rank != rank) return false;
+    for (int i = 0; i < rank - 2; ++i)
+        if (p.c.dim[i] != 1 || p.a.dim[i] != 1 || p.b.dim[i] != 1 || p.a_scale.dim[i] != 1 || p.b_scale.dim[i] != 1) return false;
+    const int64_t M = p.c.dim[rank - 2], N = p.c.dim[rank - 1], K = p.a.dim[rank - 1];
+    if (M % kTileM != 0 || N % 128 != 0 || K % kBlockK != 0 || M < kTileM || N < 128 || K < kBlockK) return false;
+    if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30)) return false;
+    if (p.b.dim[rank - 2] != K || p.b.dim[rank - 1] != N || p.a.dim[rank - 2] != M) return false;
+    // scales: one per 32 elements along K, plain layout, densely indexed
+    if (p.a_block[0] != 1 || p.a_block[1] != 32 || p.b_block[0] != 32 || p.b_block[1] != 1) return false;
+    if (p.a_scale.reorder != DFGPU_REORDER_NONE || p.b_scale.reorder != DFGPU_REORDER_NONE) return false;
+    if (p.a_scale.dim[rank - 2] != M || p.a_scale.dim[rank - 1] != K / 32 || p.a_scale.stride[rank - 1] != 1 || p.a_scale.stride[rank - 2] % 4 != 0) return false;
+    if (p.b_scale.dim[rank - 2] != K / 32 || p.b_scale.dim[rank - 1] != N || p.b_scale.stride[rank - 1] != 1) return false;
+    if (p.a.stride[rank - 1] != 1 || p.a.stride[rank - 2] % 16 != 0 || p.a.stride[rank - 2] < K) return false;
+    const bool b_k_major = p.b.stride[rank - 2] == 1 && p.b.stride[rank - 1] % 16 == 0 && p.b.stride[rank - 1] >= K;
+    const bool b_n_major = p.b.stride[rank - 1] == 1 && p.b.stride[rank - 2] % 16 == 0 && p.b.stride[rank - 2] >= N;
+    if (!b_k_major && !b_n_major) return false;
+    if (p.c.stride[rank - 1] != 1 || p.c.stride[rank - 2] % 8 != 0 || p.c.stride[rank - 2] < N) return false;
+    return translate_steps(p, nullptr, nullptr);
+}
+
+int launch_matmul_mxf8(const dfgpu_matmul_params& p, void* const* tensors, cudaStream_t stream) {
+    const int rank = p.c.rank;
+    const int64_t M = p.c.dim[rank - 2], N = p.c.dim[rank - 1], K = p.a.dim[rank - 1];
+    if (!aligned(tensors[0], 16) || !aligned(tensors[1], 16) || !aligned(tensors[2], 16) || !aligned(tensors[3], 4))
+        return fail(kInvalidArgument, "MATMUL: the MXFP8 kernel needs 16-byte aligned A, B and C and a 4-byte aligned A scale");
+    const bool b_k_major = p.b.stride[rank - 2] == 1 && p.b.stride[rank - 1] % 16 == 0 && p.b.stride[rank - 1] >= K;
+    const int bn = N % 256 == 0 ? 256 : 128;
+    CUtensorMap map_a, map_b;
+    {
+        uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+        uint64_t strides[1] = {static_cast<uint64_t>(p.a.stride[rank - 2])};
+        uint32_t box[2] = {kBlockK, kTileM};
+        int status = make_map_u8(&map_a, tensors[0], dims, strides, box, "MATMUL A (E4M3)");
+        if (status) return status;
+    }
+    if (b_k_major) {
+        uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+        uint64_t strides[1] = {static_cast<uint64_t>(p.b.stride[rank - 1])};
+        uint32_t box[2] = {kBlockK, static_cast<uint32_t>(bn)};
+        int status = make_map_u8(&map_b, tensors[1], dims, strides, box, "MATMUL B (E4M3)");
+        if (status) return status;
+    } else {
+        uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
+        uint64_t strides[1] = {static_cast<uint64_t>(p.b.stride[rank - 2])};
+        uint32_t box[2] = {128, kBlockK};
+        int status = make_map_u8(&map_b, tensors[1], dims, strides, box, "MATMUL B (E4M3)");
+        if (status) return status;
+    }
+    MxArgs args{};
+    args.sfa = static_cast<const uint8_t*>(tensors[3]);
+    args.sfb = static_cast<const uint8_t*>(tensors[4]);
+    args.sfa_ld = p.a_scale.stride[rank - 2];
+    args.sfb_ld = p.b_scale.stride[rank - 2];
+    args.out = tensors[2];
+    args.out_ld = p.c.stride[rank - 2];
+    args.out_dtype = p.c.dtype;
+    args.m_tiles = static_cast<int>(M / kTileM);
+    args.n_tiles = static_cast<int>(N / bn);
+    args.k_blocks = static_cast<int>(K / kBlockK);
+    args.b_mn_major = b_k_major ? 0 : 1;
+    if (!translate_steps(p, tensors, &args)) return fail(kUnsupported, "MATMUL: the fused epilogue is not one the MXFP8 kernel applies");
+    const int64_t tiles = static_cast<int64_t>(args.m_tiles) * args.n_tiles;
+    const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
+    auto run = [&](auto kernel, int dynamic) -> int {
+        cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dynamic);
+        if (error != cudaSuccess) return fail(kExecutionFailed, "MATMUL: cannot reserve %d bytes of shared memory: %s", dynamic, cudaGetErrorString(error));
+        kernel<<<grid, kMxThreads, dynamic, stream>>>(map_a, map_b, args);
+        return check_launch("MATMUL (tcgen05, MXFP8 block scaled)");
+    };
+    if (bn == 256) return run(umma_mxf8_kernel<256>, MxSmem<256>::kDynamic);
+    return run(umma_mxf8_kernel<128>, MxSmem<128>::kDynamic);
+}
+
+int mxf8_device_status(int* status) { return read_and_clear_device_status(status); }
+
+}  // namespace dfgpu

@@ -298,10 +298,10 @@ bool matmul_fits_tensor_cores(Lowering const& low, OperationDesc const& node) {
     return dfgpu_query_matmul(&trial, &info) == 0;
 }
 
-// BLOCK_SCALE_DEQUANTIZE feeding only this MATMUL operand -> read codes and scales directly.
-bool try_absorb_dequantize(Lowering& low, std::size_t matmul_index, std::int64_t operand_uid, dfgpu_tensor& operand, dfgpu_tensor& scale,
-                           std::int64_t* block, std::int64_t& codes_uid, std::int64_t& scale_uid, std::size_t& dequant_index) {
-    if (!low.options.fuse || matmul_fits_tensor_cores(low, low.graph.nodes[matmul_index])) return false;
+// BLOCK_SCALE_DEQUANTIZE feeding only this MATMUL operand: describes the codes and scales the matmul
+// would read directly (no policy here).
+bool describe_dequantize(Lowering const& low, std::size_t matmul_index, std::int64_t operand_uid, dfgpu_tensor& operand, dfgpu_tensor& scale,
+                         std::int64_t* block, std::int64_t& codes_uid, std::int64_t& scale_uid, std::size_t& dequant_index) {
     auto const& t = low.tensor(operand_uid);
     auto producer = low.producer.find(operand_uid);
     std::size_t only = 0;
@@ -323,6 +323,35 @@ bool try_absorb_dequantize(Lowering& low, std::size_t matmul_index, std::int64_t
     scale_uid = *s;
     dequant_index = static_cast<std::size_t>(producer->second);
     return true;
+}
+
+// Both operands are MXFP8 (E4M3 codes, one E8M0 scale per 32 elements along K) and the shape fits the
+// block-scaled tensor-core kernel: the matmul then reads codes and scales itself and neither dequantize
+// runs (no bf16 copies of A and B are written or read).
+bool matmul_fits_mxf8(Lowering const& low, std::size_t matmul_index) {
+    if (low.options.disable_tensor_cores || !low.options.fuse) return false;
+    auto const& node = low.graph.nodes[matmul_index];
+    auto a = port(node.inputs, "A"), b = port(node.inputs, "B"), c = port(node.outputs, "C");
+    if (!a || !b || !c) return false;
+    dfgpu_matmul_params trial{};
+    std::int64_t codes = 0, scales = 0;
+    std::size_t dequant = 0;
+    if (!describe_dequantize(low, matmul_index, *a, trial.a, trial.a_scale, trial.a_block, codes, scales, dequant)) return false;
+    if (!describe_dequantize(low, matmul_index, *b, trial.b, trial.b_scale, trial.b_block, codes, scales, dequant)) return false;
+    if (low.describe(*c, trial.c, "").is_bad()) return false;
+    trial.kernel = DFGPU_MATMUL_UMMA_MXF8;
+    dfgpu_plan_info info{};
+    return dfgpu_query_matmul(&trial, &info) == 0;
+}
+
+// Policy: read through the dequantize when the block-scaled tensor-core kernel takes both operands, or
+// when no tensor-core kernel fits at all (the CUDA-core matmul decodes on the fly); when only the bf16
+// tensor-core kernel fits, the dequantize stays a launch of its own and stores bf16 (exact for E4M3 x 2^k).
+bool try_absorb_dequantize(Lowering& low, std::size_t matmul_index, std::int64_t operand_uid, dfgpu_tensor& operand, dfgpu_tensor& scale,
+                           std::int64_t* block, std::int64_t& codes_uid, std::int64_t& scale_uid, std::size_t& dequant_index) {
+    if (!low.options.fuse) return false;
+    if (!matmul_fits_mxf8(low, matmul_index) && matmul_fits_tensor_cores(low, low.graph.nodes[matmul_index])) return false;
+    return describe_dequantize(low, matmul_index, operand_uid, operand, scale, block, codes_uid, scale_uid, dequant_index);
 }
 
 Status lower_matmul(Lowering& low, std::size_t index) {

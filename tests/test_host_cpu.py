@@ -142,9 +142,14 @@ def test_bottleneck_plan_fuses_to_three_launches_and_shares_workspace():
 
 
 def test_quantize_matmul_plans():
-    # tensor-core shape: dequantize stays a launch whose output is stored as bf16 (exact), matmul on tcgen05
+    # MXFP8 shape: the block-scaled tensor-core matmul reads codes and scales itself, no dequantize launch, no workspace
     exe = runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 128))
-    assert exe.launch_count == 5 and exe.workspace_size == 2 * 128 * 128 * 2
+    assert exe.launch_count == 3 and exe.workspace_size == 0
+    assert "matmul kernel=3" in exe.plan_text() and "[dequantize_b+dequantize_a+matmul]" in exe.plan_text()
+    # only the bf16 tensor-core kernel fits (N is not a multiple of 128): dequantize stays a launch whose
+    # output is stored as bf16 (exact), matmul on tcgen05
+    exe = runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 64))
+    assert exe.launch_count == 5 and exe.workspace_size == 128 * 128 * 2 + 128 * 64 * 2
     assert "matmul kernel=2" in exe.plan_text()
     # shapes the tcgen05 kernel does not cover: the dequantize nodes are absorbed into the CUDA-core matmul
     for doc, options in ((graphs.c3_quantize_matmul(128, 128, 96), 0), (graphs.c3_quantize_matmul(128, 128, 128), runtime.NO_TENSOR_CORES)):
