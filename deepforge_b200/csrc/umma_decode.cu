@@ -233,12 +233,11 @@ sdpa_decode_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 tc_fence_after();
                 if (ok) {
                     const uint32_t k_smem = smem_base + DecodeSmem::kRing + slot * kKvTileBytes;
+                    const uint32_t k_lo = smem_desc_lo(k_smem, 16), q_lo = smem_desc_lo(q_smem, 16);
 #pragma unroll
-                    for (int k = 0; k < kDim / 16; ++k) {
-                        const uint64_t desc_k = smem_desc(k_smem + (k >> 2) * kKvHalfBytes + (k & 3) * 32, 16, 1024);
-                        const uint64_t desc_q = smem_desc(q_smem + (k >> 2) * (kHeadsPadded * 128) + (k & 3) * 32, 16, 1024);
-                        umma_bf16(tmem_base + b * 16, desc_k, desc_q, idesc_s, k != 0 ? 1u : 0u);
-                    }
+                    for (int k = 0; k < kDim / 16; ++k)
+                        umma_bf16(tmem_base + b * 16, desc_words(k_lo + (((k >> 2) * kKvHalfBytes + (k & 3) * 32) >> 4), smem_desc_hi(1024)),
+                                  desc_words(q_lo + (((k >> 2) * (kHeadsPadded * 128) + (k & 3) * 32) >> 4), smem_desc_hi(1024)), idesc_s, k != 0 ? 1u : 0u);
                 }
                 umma_commit(kv_empty(slot));
                 umma_commit(s_full(b));
@@ -253,12 +252,11 @@ sdpa_decode_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 if (ok) {
                     const uint32_t v_smem = smem_base + DecodeSmem::kRing + slot * kKvTileBytes;
                     const uint32_t p_smem = smem_base + DecodeSmem::kP + b * 4096;
+                    const uint32_t v_lo = smem_desc_lo(v_smem, kKvHalfBytes), p_lo = smem_desc_lo(p_smem, 16);
 #pragma unroll
-                    for (int k = 0; k < kTileKeys / 16; ++k) {
-                        const uint64_t desc_v = smem_desc(v_smem + k * 2048, kKvHalfBytes, 1024);
-                        const uint64_t desc_p = smem_desc(p_smem + (k >> 2) * (kHeadsPadded * 128) + (k & 3) * 32, 16, 1024);
-                        umma_bf16(tmem_o, desc_v, desc_p, idesc_o, (j | k) != 0 ? 1u : 0u);
-                    }
+                    for (int k = 0; k < kTileKeys / 16; ++k)
+                        umma_bf16(tmem_o, desc_words(v_lo + ((k * 2048) >> 4), smem_desc_hi(1024)),
+                                  desc_words(p_lo + (((k >> 2) * (kHeadsPadded * 128) + (k & 3) * 32) >> 4), smem_desc_hi(1024)), idesc_o, (j | k) != 0 ? 1u : 0u);
                 }
                 umma_commit(kv_empty(slot));
                 umma_commit(pv_done(b));

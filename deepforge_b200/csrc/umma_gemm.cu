@@ -159,13 +159,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 tc_fence_after();
                 const uint32_t a_src = smem_base + s * L::kStageBytes;
                 const uint32_t b_src = a_src + L::kABytes;
+                const uint32_t a_lo = smem_desc_lo(a_src, 16);
+                const uint32_t b_lo = args.b_mn_major ? smem_desc_lo(b_src, kBlockK * 128) : smem_desc_lo(b_src, 16);
+                const uint32_t b_step = args.b_mn_major ? (2048u >> 4) : (32u >> 4);
 #pragma unroll
-                for (int k = 0; k < kBlockK / 16; ++k) {
-                    const uint64_t desc_a = smem_desc(a_src + k * 32, 16, 1024);
-                    const uint64_t desc_b = args.b_mn_major ? smem_desc(b_src + k * 2048, kBlockK * 128, 1024)
-                                                            : smem_desc(b_src + k * 32, 16, 1024);
-                    umma_bf16(tmem_base, desc_a, desc_b, idesc, (kb | k) != 0 ? 1u : 0u);
-                }
+                for (int k = 0; k < kBlockK / 16; ++k)
+                    umma_bf16(tmem_base, desc_words(a_lo + ((k * 32) >> 4), smem_desc_hi(1024)), desc_words(b_lo + k * b_step, smem_desc_hi(1024)), idesc, (kb | k) != 0 ? 1u : 0u);
                 umma_commit(empty_bar(s));
             }
             // always arrive, so the epilogue's wait ends even after a failed wait above
@@ -474,13 +473,14 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 if (!ok) break;
                 tc_fence_after();
                 if (leader) CONV_TRACE(1, it, 1);
-                for (int g = 0; g < G; ++g) {
-                    const uint32_t a_src = ring_base + (stage * G + g) * kABytes;
-                    const uint32_t b_src = w_base + (n_tile * args.k_blocks + kb0 + g) * kBTileBytes;
+                const uint32_t a_lo = smem_desc_lo(ring_base + stage * G * kABytes, 16);
+                const uint32_t b_lo = smem_desc_lo(w_base + (n_tile * args.k_blocks + kb0) * kBTileBytes, 16);
+                if (leader) {
+                    for (int g = 0; g < G; ++g) {
 #pragma unroll
-                    for (int k = 0; k < kBlockK / 16; ++k) {
-                        const uint64_t desc_a = smem_desc(a_src + k * 32, 16, 1024), desc_b = smem_desc(b_src + k * 32, 16, 1024);
-                        if (leader) umma_bf16(tmem_acc, desc_a, desc_b, idesc, (kb0 | g | k) != 0 ? 1u : 0u);
+                        for (int k = 0; k < kBlockK / 16; ++k)
+                            umma_bf16(tmem_acc, desc_words(a_lo + ((g * kABytes + k * 32) >> 4), smem_desc_hi(1024)),
+                                      desc_words(b_lo + ((g * kBTileBytes + k * 32) >> 4), smem_desc_hi(1024)), idesc, (kb0 | g | k) != 0 ? 1u : 0u);
                     }
                 }
                 if (leader) umma_commit(empty_bar(stage));

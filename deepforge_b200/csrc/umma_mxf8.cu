@@ -181,12 +181,16 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
                     for (int c = 0; c < BN / 128; ++c) tmem_copy_scales(sf_tmem + 4 + 4 * c, scale_desc(a_src + L::kSfbOffset + 512 * c));
                 }
+                const uint32_t a_lo = smem_desc_lo(a_src, 16);
+                const uint32_t b_lo = args.b_mn_major ? smem_desc_lo(b_src, kBlockK * 128) : smem_desc_lo(b_src, 16);
+                const uint32_t b_step = args.b_mn_major ? (4096u >> 4) : (32u >> 4);
+                if (leader) {
 #pragma unroll
-                for (int j = 0; j < kBlockK / 32; ++j) {
-                    const uint64_t desc_a = smem_desc(a_src + j * 32, 16, 1024);
-                    const uint64_t desc_b = args.b_mn_major ? smem_desc(b_src + j * 4096, kBlockK * 128, 1024) : smem_desc(b_src + j * 32, 16, 1024);
-                    const uint32_t idesc = idesc_base | (static_cast<uint32_t>(j) << 29) | (static_cast<uint32_t>(j) << 4);
-                    if (leader) umma_mxf8(tmem_u, desc_a, desc_b, idesc, (kb | j) != 0 ? 1u : 0u, sf_tmem, sf_tmem + 4);
+                    for (int j = 0; j < kBlockK / 32; ++j) {
+                        const uint32_t idesc = idesc_base | (static_cast<uint32_t>(j) << 29) | (static_cast<uint32_t>(j) << 4);
+                        umma_mxf8(tmem_u, desc_words(a_lo + ((j * 32) >> 4), smem_desc_hi(1024)), desc_words(b_lo + j * b_step, smem_desc_hi(1024)), idesc,
+                                  (kb | j) != 0 ? 1u : 0u, sf_tmem, sf_tmem + 4);
+                    }
                 }
                 if (leader) umma_commit(empty_bar(stage));
                 if (++stage == kStages) { stage = 0; phase ^= 1; }

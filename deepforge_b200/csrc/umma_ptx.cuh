@@ -40,6 +40,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(done) : "r"(bar), "r"(parity) : "memory");
     return done != 0;
 }
+// Non-blocking probe: a completed phase is the common case in the steady state of a pipeline, and the
+// potentially-suspending try_wait form costs a few hundred cycles even then.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
 __device__ __forceinline__ uint64_t global_timer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -60,6 +71,7 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int c
     }
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
+    if (mbar_test_wait(bar, parity)) return true;
 #pragma unroll 1
     for (int spin = 0; spin < 64; ++spin)
         if (mbar_try_wait(bar, parity)) return true;
@@ -71,6 +83,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
 // and tcgen05 instructions take) and only the asynchronous instruction itself is predicated on one
 // elected lane; a loop that runs inside `if (lane == 0)` pays a vector-to-uniform move per operand.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int code) {
+    if (__all_sync(0xffffffffu, mbar_test_wait(bar, parity))) return true;
 #pragma unroll 1
     for (int spin = 0; spin < 64; ++spin)
         if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
@@ -160,6 +173,20 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t address, uint32_t lbo_byt
     return desc;
 }
 
+// The same descriptor as two 32-bit words. Issuing one product costs about as many cycles as the
+// instructions around it (a lone lane has nothing to hide latency with): building the 64-bit value with
+// shifts and ORs per product makes a 128 x 128 x 16 product issue in ~120 cycles, twice what the tensor pipe
+// needs to run it. The high word never changes and the low word advances by (bytes >> 4), so a K step is
+// one 32-bit add.
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t address, uint32_t lbo_bytes) {
+    return ((address & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ constexpr uint32_t smem_desc_hi(uint32_t sbo_bytes) { return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29); }
+__device__ __forceinline__ uint64_t desc_words(uint32_t lo, uint32_t hi) {
+    uint64_t desc;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(desc) : "r"(lo), "r"(hi));
+    return desc;
+}
 
 // ---- host: tensor maps ------------------------------------------------------------------------
 

@@ -141,11 +141,11 @@ sdpa_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 if (ok) ok = mbar_wait(s_empty(b), ((j >> 1) & 1) ^ 1, 204);
                 tc_fence_after();
                 if (ok) {
-                    const uint32_t k_smem = smem_base + Smem::kRing + slot * kTileBytes;
+                    const uint32_t q_lo = smem_desc_lo(q_smem, 16), k_lo = smem_desc_lo(smem_base + Smem::kRing + slot * kTileBytes, 16);
 #pragma unroll
                     for (int k = 0; k < kHeadDim / 16; ++k) {
-                        const uint32_t offset = (k >> 2) * kHalfBytes + (k & 3) * 32;
-                        umma_bf16(tmem_base + b * 128, smem_desc(q_smem + offset, 16, 1024), smem_desc(k_smem + offset, 16, 1024), idesc_qk, k != 0 ? 1u : 0u);
+                        const uint32_t offset = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
+                        umma_bf16(tmem_base + b * 128, desc_words(q_lo + offset, smem_desc_hi(1024)), desc_words(k_lo + offset, smem_desc_hi(1024)), idesc_qk, k != 0 ? 1u : 0u);
                     }
                 }
                 umma_commit(kv_empty(slot));
@@ -159,14 +159,12 @@ sdpa_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 if (ok) ok = mbar_wait(kv_full(slot), (t / kSlots) & 1, 206);
                 tc_fence_after();
                 if (ok) {
-                    const uint32_t p_smem = smem_base + Smem::kP + b * kTileBytes;
-                    const uint32_t v_smem = smem_base + Smem::kRing + slot * kTileBytes;
+                    const uint32_t p_lo = smem_desc_lo(smem_base + Smem::kP + b * kTileBytes, 16);
+                    const uint32_t v_lo = smem_desc_lo(smem_base + Smem::kRing + slot * kTileBytes, kHalfBytes);
 #pragma unroll
-                    for (int k = 0; k < kKeys / 16; ++k) {
-                        const uint64_t desc_p = smem_desc(p_smem + (k >> 2) * kHalfBytes + (k & 3) * 32, 16, 1024);
-                        const uint64_t desc_v = smem_desc(v_smem + k * 2048, kHalfBytes, 1024);
-                        umma_bf16(tmem_o, desc_p, desc_v, idesc_pv, (j | k) != 0 ? 1u : 0u);
-                    }
+                    for (int k = 0; k < kKeys / 16; ++k)
+                        umma_bf16(tmem_o, desc_words(p_lo + (((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4), smem_desc_hi(1024)),
+                                  desc_words(v_lo + ((k * 2048) >> 4), smem_desc_hi(1024)), idesc_pv, (j | k) != 0 ? 1u : 0u);
                 }
                 umma_commit(kv_empty(slot));
                 umma_commit(pv_done(b));
@@ -350,6 +348,25 @@ __device__ __forceinline__ float ex2_fast(float x) {
     return y;
 }
 
+// Packed pairs of f32 (one 64-bit register): Blackwell's FMA pipe takes two lanes per instruction, which
+// halves the instruction count of the scale-and-subtract and of the row sums in the softmax loop.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+    return v;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 __global__ void __launch_bounds__(kPairThreads, 1)
 sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o, SdpaUmmaArgs args) {
@@ -439,26 +456,30 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         };
         auto next_slot = [&]() { if (++slot == kPairSlots) { slot = 0; phase ^= 1; } };
         auto commit = [&](uint32_t bar) { if (leader) umma_commit(bar); };
+        constexpr uint32_t kDescHi = smem_desc_hi(1024);
         auto scores = [&](int x, int k_slot) {  // S_x = Q_x K^T
             if (!ok) return;
-            const uint32_t q_smem = smem_base + PairSmem::kQ + x * kTileBytes;
-            const uint32_t k_smem = smem_base + PairSmem::kRing + k_slot * kTileBytes;
+            const uint32_t q_lo = smem_desc_lo(smem_base + PairSmem::kQ + x * kTileBytes, 16);
+            const uint32_t k_lo = smem_desc_lo(smem_base + PairSmem::kRing + k_slot * kTileBytes, 16);
+            const uint32_t d_tmem = tmem_u + x * 128;
+            if (leader) {
 #pragma unroll
-            for (int k = 0; k < kHeadDim / 16; ++k) {
-                const uint32_t offset = (k >> 2) * kHalfBytes + (k & 3) * 32;
-                const uint64_t desc_q = smem_desc(q_smem + offset, 16, 1024), desc_k = smem_desc(k_smem + offset, 16, 1024);
-                if (leader) umma_bf16(tmem_u + x * 128, desc_q, desc_k, idesc_qk, k != 0 ? 1u : 0u);
+                for (int k = 0; k < kHeadDim / 16; ++k) {
+                    const uint32_t offset = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;  // in 16-byte units
+                    umma_bf16(d_tmem, desc_words(q_lo + offset, kDescHi), desc_words(k_lo + offset, kDescHi), idesc_qk, k != 0 ? 1u : 0u);
+                }
             }
         };
         auto product = [&](int x, int j, int v_slot) {  // O_x += P_x V_j, P_x as bf16 pairs in the front 64 columns of S_x
             if (ok) ok = mbar_wait_warp(p_full(x), j & 1, 223 + x);
             tc_fence_after();
             if (!ok) return;
-            const uint32_t v_smem = smem_base + PairSmem::kRing + v_slot * kTileBytes;
+            const uint32_t v_lo = smem_desc_lo(smem_base + PairSmem::kRing + v_slot * kTileBytes, kHalfBytes);
+            const uint32_t d_tmem = tmem_u + 256 + x * 128, p_tmem = tmem_u + x * 128;
+            if (leader) {
 #pragma unroll
-            for (int k = 0; k < kKeys / 16; ++k) {
-                const uint64_t desc_v = smem_desc(v_smem + k * 2048, kHalfBytes, 1024);
-                if (leader) umma_bf16_a_tmem(tmem_u + 256 + x * 128, tmem_u + x * 128 + k * 8, desc_v, idesc_pv, (j | k) != 0 ? 1u : 0u);
+                for (int k = 0; k < kKeys / 16; ++k)
+                    umma_bf16_a_tmem(d_tmem, p_tmem + k * 8, desc_words(v_lo + ((k * 2048) >> 4), kDescHi), idesc_pv, (j | k) != 0 ? 1u : 0u);
             }
         };
         wait_slot(225);
@@ -564,23 +585,29 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 }
             }
             if (threadIdx.x == 64 + x * 128) SDPA_TRACE(x, j, 3);
-            const float bias = -m_ref;
-            float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const uint64_t scale2 = pack2(scale, scale), bias2 = pack2(-m_ref, -m_ref);
+            uint64_t sums[4] = {0, 0, 0, 0};  // four independent chains of packed partial sums
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 uint32_t packed[32];  // 64 keys as bf16 pairs
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
                     const int key = half * 64 + 2 * e;
-                    const float p0 = ex2_fast(fmaf(__uint_as_float(raw[key >> 5][key & 31]), scale, bias));
-                    const float p1 = ex2_fast(fmaf(__uint_as_float(raw[(key + 1) >> 5][(key + 1) & 31]), scale, bias));
-                    sums[e & 3] += p0 + p1;
+                    const uint64_t x = fma2(pack2(__uint_as_float(raw[key >> 5][key & 31]), __uint_as_float(raw[(key + 1) >> 5][(key + 1) & 31])), scale2, bias2);
+                    float x0, x1;
+                    unpack2(x, x0, x1);
+                    const float p0 = ex2_fast(x0), p1 = ex2_fast(x1);
+                    sums[e & 3] = add2(sums[e & 3], pack2(p0, p1));
                     __nv_bfloat162 two = __floats2bfloat162_rn(p0, p1);
                     packed[e] = *reinterpret_cast<uint32_t*>(&two);
                 }
                 tmem_store_32(tmem_s + half * 32, packed);
             }
-            l_sum += (sums[0] + sums[1]) + (sums[2] + sums[3]);
+            {
+                float lo, hi;
+                unpack2(add2(add2(sums[0], sums[1]), add2(sums[2], sums[3])), lo, hi);
+                l_sum += lo + hi;
+            }
             if (threadIdx.x == 64 + x * 128) SDPA_TRACE(x, j, 4);
             tmem_store_wait();
             tc_fence_before();

@@ -86,6 +86,48 @@ class Session:
         torch.cuda.synchronize(self.device)
         return graphs
 
+    def replica_tensors(self, index: int) -> Dict[int, torch.Tensor]:
+        return self.dev if index == 0 else self._replica_buffers[index - 1][0]
+
+    def run_pipelined(self, steps: int, graphs, host_outputs) -> None:
+        """`steps` end-to-end passes: every pass copies all host-generated inputs from pinned memory to the
+        device, replays Executable.execute() and copies all outputs to pinned host memory. The three phases
+        run on three streams over the buffer replicas, so that the upload of pass i+1, the kernels of pass i
+        and the download of pass i-1 overlap (PCIe carries both directions at once). `graphs` come from
+        capture(); `host_outputs[r][uid]` is the pinned destination of replica r. The caller synchronises."""
+        count = len(self.replicas)
+        if not hasattr(self, "_pipeline"):
+            make = lambda: [torch.cuda.Event() for _ in range(count)]
+            self._pipeline = (torch.cuda.Stream(self.device), torch.cuda.Stream(self.device), torch.cuda.Stream(self.device), make(), make(), make())
+        up, compute, down, uploaded, computed, downloaded = self._pipeline
+        start = torch.cuda.Event()
+        start.record(torch.cuda.current_stream(self.device))
+        for stream in (up, compute, down):
+            stream.wait_event(start)
+        for i in range(steps):
+            r = i % count
+            tensors = self.replica_tensors(r)
+            with torch.cuda.stream(up):
+                if i >= count:
+                    up.wait_event(computed[r])  # the kernels of pass i - count have read this replica's inputs
+                for uid, host in self.host.items():
+                    tensors[uid].copy_(host, non_blocking=True)
+                uploaded[r].record(up)
+            with torch.cuda.stream(compute):
+                compute.wait_event(uploaded[r])
+                if i >= count:
+                    compute.wait_event(downloaded[r])  # its previous outputs are on the host
+                graphs[r].replay()
+                computed[r].record(compute)
+            with torch.cuda.stream(down):
+                down.wait_event(computed[r])
+                for uid, host in host_outputs[r].items():
+                    host.copy_(tensors[uid], non_blocking=True)
+                downloaded[r].record(down)
+        main = torch.cuda.current_stream(self.device)
+        for r in range(min(count, steps)):
+            main.wait_event(downloaded[r])
+
     def run_steps(self, first: int, last: int) -> None:
         self.exe.execute_steps(first, last, self.pack, self.workspace_ptr)
 
