@@ -283,6 +283,8 @@ bsq_row32_kernel(const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* _
     // load instruction of a warp is one contiguous 512-byte (16-bit input) segment and all of a thread's
     // loads are in flight before the first amax. 4 neighbouring lanes form one 32-element block.
     constexpr int kChunks = 4;
+    chain_release();
+    chain_wait();
     const int64_t total = rows * cols;
     const int64_t tile0 = static_cast<int64_t>(blockIdx.x) * (256 * 8 * kChunks);
     float v[kChunks][8];
@@ -396,6 +398,8 @@ bsq_col32_kernel(const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* _
     constexpr int VEC = Traits::VEC;
     constexpr int kRows = 8;
     __shared__ uint32_t partial[4][VEC][32];
+    chain_release();
+    chain_wait();
     const int lane = threadIdx.x & 31, group = threadIdx.x >> 5;
     const int64_t column = (static_cast<int64_t>(blockIdx.x) * 32 + lane) * VEC;
     const bool live = column < n_extent;
@@ -665,18 +669,18 @@ extern "C" int dfgpu_block_scale_quantize(const dfgpu_bsq_params* p, void* const
         int64_t threads = (plan.rows * plan.cols / 8 + 3) / 4;  // 4 chunks of 8 elements per thread
         unsigned grid = static_cast<unsigned>((threads + 255) / 256);
         int reordered = plan.layout.reordered;
-        if (p->x.dtype == DFGPU_F32) bsq_row32_kernel<float><<<grid, 256, 0, stream>>>(x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
-        else if (p->x.dtype == DFGPU_BF16) bsq_row32_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
-        else bsq_row32_kernel<__half><<<grid, 256, 0, stream>>>(x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
+        if (p->x.dtype == DFGPU_F32) launch_chained(bsq_row32_kernel<float>, dim3(grid), dim3(256), 0, stream, x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
+        else if (p->x.dtype == DFGPU_BF16) launch_chained(bsq_row32_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
+        else launch_chained(bsq_row32_kernel<__half>, dim3(grid), dim3(256), 0, stream, x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
     } else if (kernel == DFGPU_BSQ_COL32) {
         int vec = p->x.dtype == DFGPU_F32 ? 4 : 8;
         int64_t lanes = plan.cols / vec;  // one lane per group of vec columns, 32 lanes (x 4 row groups) per CTA
         dim3 grid(static_cast<unsigned>((lanes + 31) / 32), static_cast<unsigned>(plan.rows / 32),
                   static_cast<unsigned>(plan.batch));
         int reordered = plan.layout.reordered;
-        if (p->x.dtype == DFGPU_F32) bsq_col32_kernel<float><<<grid, 128, 0, stream>>>(x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
-        else if (p->x.dtype == DFGPU_BF16) bsq_col32_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
-        else bsq_col32_kernel<__half><<<grid, 128, 0, stream>>>(x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
+        if (p->x.dtype == DFGPU_F32) launch_chained(bsq_col32_kernel<float>, grid, dim3(128), 0, stream, x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
+        else if (p->x.dtype == DFGPU_BF16) launch_chained(bsq_col32_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
+        else launch_chained(bsq_col32_kernel<__half>, grid, dim3(128), 0, stream, x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
     } else {
         int64_t block_total = element_count(p->x) / p->block_size;
         unsigned grid = static_cast<unsigned>((block_total + 127) / 128);

@@ -58,6 +58,34 @@ inline bool valid_tensor(const dfgpu_tensor& t) {
 
 int sm_count();
 
+// ---- programmatic dependent launch ------------------------------------------------
+// A kernel launched with launch_chained() may start while the kernel before it in the stream is still
+// draining: its CTAs take SMs as the earlier kernel's CTAs leave, run their private prologue (barrier
+// setup, tensor-memory allocation) and then block in chain_wait() until the earlier kernel has completed
+// and its writes are visible. Every kernel launched this way must call chain_wait() before its first
+// global-memory access; chain_release() at its top lets the kernel after it do the same. Both are no-ops
+// when the kernel was launched the ordinary way. Captured into a CUDA graph the dependency becomes a
+// programmatic edge, so the gap between the kernels of one plan shrinks to the tail of the slowest CTA.
+#ifdef __CUDACC__
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... Params, typename... Args>
+cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t dynamic_smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t config{};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = dynamic_smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+#endif
+
 // ---- device-side element access -------------------------------------------------
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16) {

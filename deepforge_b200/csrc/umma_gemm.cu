@@ -315,6 +315,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + pargs.barrier_offset + 8 * (2 * kMaxRingStages + 17));
 
     const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
+    chain_release();  // the next kernel of the plan may start taking SMs as this one's CTAs leave
 
     auto tile_geometry = [&](int tile, int& m_tile, int& n_tile, int& image, int& h0, int64_t& out_row0) {
         m_tile = tile / pargs.n_tiles;
@@ -421,6 +422,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             mbar_expect_tx(w_full_bar, static_cast<uint32_t>(pargs.filter_bytes));
         }
         __syncwarp();
+        chain_wait();  // everything before this line is private to the CTA; the loads below read the previous kernel's output
         // Start streaming right away: the filter and the first ring-full of activations are in flight
         // while the other warps allocate tensor memory and stage the bias vectors.
         for (int nt = 0; nt < pargs.n_tiles; ++nt)
@@ -436,6 +438,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         tmem_relinquish();
         tc_fence_before();
     }
+    if (warp != 0) chain_wait();  // warp 0 waited before its first load
     {
         // per-channel ADD operands -> f32 in shared memory, once per CTA
         float* bias_stage = reinterpret_cast<float*>(generic_base + pargs.bias_offset);
@@ -675,7 +678,8 @@ int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const 
         configured = kSmemBudget;
     }
     const int grid = args.total_tiles < sm_count() ? args.total_tiles : sm_count();
-    umma_conv_persistent_kernel<BN, HAS_RES><<<grid, kPersistentThreads, dynamic, stream>>>(map_a, map_b, map_out, map_res, args);
+    cudaError_t launched = launch_chained(umma_conv_persistent_kernel<BN, HAS_RES>, dim3(grid), dim3(kPersistentThreads), dynamic, stream, map_a, map_b, map_out, map_res, args);
+    if (launched != cudaSuccess) return fail(kExecutionFailed, "tcgen05 conv (persistent): launch failed: %s", cudaGetErrorString(launched));
     return check_launch("tcgen05 conv (persistent)");
 }
 

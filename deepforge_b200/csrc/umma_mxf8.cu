@@ -108,6 +108,7 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
     const bool leader = elect_one();
     const int total_tiles = args.m_tiles * args.n_tiles;
+    chain_release();
 
     if (warp == 0) {
         if (leader) {
@@ -128,6 +129,7 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
+    chain_wait();  // barriers and tensor memory are set up; from here on the previous kernel's output is read
 
     if (warp == 0) {
         // ---- TMA loader ----
@@ -424,7 +426,8 @@ int launch_matmul_mxf8(const dfgpu_matmul_params& p, void* const* tensors, cudaS
     auto run = [&](auto kernel, int dynamic) -> int {
         cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dynamic);
         if (error != cudaSuccess) return fail(kExecutionFailed, "MATMUL: cannot reserve %d bytes of shared memory: %s", dynamic, cudaGetErrorString(error));
-        kernel<<<grid, kMxThreads, dynamic, stream>>>(map_a, map_b, args);
+        error = launch_chained(kernel, dim3(grid), dim3(kMxThreads), dynamic, stream, map_a, map_b, args);
+        if (error != cudaSuccess) return fail(kExecutionFailed, "MATMUL (tcgen05, MXFP8 block scaled): launch failed: %s", cudaGetErrorString(error));
         return check_launch("MATMUL (tcgen05, MXFP8 block scaled)");
     };
     if (bn == 256) return run(umma_mxf8_kernel<256>, MxSmem<256>::kDynamic);
