@@ -276,6 +276,14 @@ struct PersistentArgs {
     int32_t filter_bytes;  // resident filter: n_tiles * k_blocks * BN * 128
     int32_t w_offset, epi_offset, ring_offset, bias_offset, barrier_offset;  // shared-memory layout (bytes from the aligned base)
     int32_t bias_stride;   // output channels (floats per staged bias vector)
+    // Halo form (filters wider than one tap): one ring slot holds the input rows one FILTER ROW needs, padded
+    // columns included (pitch = Q + S - 1 pixels per row); the S taps of that filter row are the same slot
+    // read from S starting rows, so the activations cross L2 -> shared memory R times instead of R * S times.
+    // GEMM row m is then the padded position (m / pitch, m % pitch) and the positions with m % pitch >= Q are
+    // computed but never stored.
+    int32_t halo;          // 0 = one slot per tap (or plain GEMM rows)
+    int32_t pitch;         // Q + S - 1
+    int32_t slot_bytes;    // bytes between ring slots
 };
 
 // Cycle stamps of the first CTA's roles (loader, issuing lane, two epilogue groups), for tuning builds only.
@@ -376,9 +384,17 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             ld.ok = mbar_wait_warp(empty_bar(ld.stage), ld.phase, 112);
             if (!ld.ok) return;
             if (leader) CONV_TRACE(0, ld.filled, 1);
+            if (pargs.halo) {
+                // one slot = the rows of filter row tap_r for channel block cblk: box (64 ch, pitch, rows, 1)
+                if (leader) {
+                    mbar_expect_tx(full_bar(ld.stage), static_cast<uint32_t>(args.rows_per_tile * pargs.pitch * kBlockK * 2));
+                    tma_load_4d(ring_base + ld.stage * pargs.slot_bytes, &map_a, ld.cblk * kBlockK, -args.pad_w, ld.h0 + ld.tap_r - args.pad_h, ld.image, full_bar(ld.stage));
+                }
+                if (++ld.cblk == args.k_blocks_per_tap) { ld.cblk = 0; ++ld.tap_r; }
+            } else {
             if (leader) mbar_expect_tx(full_bar(ld.stage), a_bytes * G);
             for (int g = 0; g < G; ++g) {
-                const uint32_t a_dst = ring_base + (ld.stage * G + g) * kABytes;
+                const uint32_t a_dst = ring_base + ld.stage * pargs.slot_bytes + g * kABytes;
                 if (args.is_conv) {
                     if (leader) tma_load_4d(a_dst, &map_a, ld.cblk * kBlockK, ld.tap_s - args.pad_w, ld.h0 + ld.tap_r - args.pad_h, ld.image, full_bar(ld.stage));
                 } else {
@@ -389,10 +405,11 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     if (++ld.tap_s == args.filter_s) { ld.tap_s = 0; ++ld.tap_r; }
                 }
             }
+            }
             if (leader) CONV_TRACE(0, ld.filled, 2);
             ++ld.filled;
             if (++ld.stage == STAGES) { ld.stage = 0; ld.phase ^= 1; }
-            ld.kb0 += G;
+            ld.kb0 += pargs.halo ? args.filter_s : G;  // K slices this slot covers
             if (ld.kb0 >= args.k_blocks) {
                 ld.tile += gridDim.x;
                 ++ld.index;
@@ -470,15 +487,42 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             if (ok) ok = mbar_wait_warp(acc_empty_bar(acc), ((i / kAccumulators) & 1) ^ 1, 113);
             tc_fence_after();
             const uint32_t tmem_acc = tmem_u + static_cast<uint32_t>(acc * BN);
-            for (int kb0 = 0; kb0 < args.k_blocks && ok; kb0 += G, ++it) {
+            int halo_r = 0, halo_c = 0;  // filter row and channel block of the next slot (halo form)
+            for (int kb0 = 0; kb0 < args.k_blocks && ok; kb0 += (pargs.halo ? args.filter_s : G), ++it) {
                 if (leader) CONV_TRACE(1, it, 0);
                 ok = mbar_wait_warp(full_bar(stage), phase, 114);
                 if (!ok) break;
                 tc_fence_after();
                 if (leader) CONV_TRACE(1, it, 1);
-                const uint32_t a_lo = smem_desc_lo(ring_base + stage * G * kABytes, 16);
-                const uint32_t b_lo = smem_desc_lo(w_base + (n_tile * args.k_blocks + kb0) * kBTileBytes, 16);
-                if (leader) {
+                const uint32_t a_lo = smem_desc_lo(ring_base + stage * pargs.slot_bytes, 16);
+                if (pargs.halo) {
+                    // tap s of this filter row reads the slot from row s on: only the start address moves, by s * 128 bytes.
+                    // The 128-byte swizzle is a function of the absolute shared-memory address (TMA wrote the slot that
+                    // way), so a start in the middle of an 8-row swizzle atom needs no base offset in the descriptor.
+                    const uint32_t b_first = smem_desc_lo(w_base + ((n_tile * args.k_blocks + halo_r * args.filter_s * args.k_blocks_per_tap + halo_c) * kBTileBytes), 16);
+                    const uint32_t b_tap_step = static_cast<uint32_t>(args.k_blocks_per_tap * kBTileBytes) >> 4;
+                    if (leader) {
+                        const uint32_t first = kb0 != 0 ? 1u : 0u;
+                        if (args.filter_s == 3) {
+                            // straight-line code: a branch between products costs more than the product itself takes to run
+#pragma unroll
+                            for (int tap = 0; tap < 3; ++tap)
+#pragma unroll
+                                for (int k = 0; k < kBlockK / 16; ++k)
+                                    umma_bf16(tmem_acc, desc_words(a_lo + ((tap * 128 + k * 32) >> 4), smem_desc_hi(1024)),
+                                              desc_words(b_first + tap * b_tap_step + ((k * 32) >> 4), smem_desc_hi(1024)), idesc, (tap | k) != 0 ? 1u : first);
+                        } else {
+                            for (int tap = 0; tap < args.filter_s; ++tap) {
+#pragma unroll
+                                for (int k = 0; k < kBlockK / 16; ++k)
+                                    umma_bf16(tmem_acc, desc_words(a_lo + ((tap * 128 + k * 32) >> 4), smem_desc_hi(1024)),
+                                              desc_words(b_first + tap * b_tap_step + ((k * 32) >> 4), smem_desc_hi(1024)), idesc, (tap | k) != 0 ? 1u : first);
+                            }
+                        }
+                    }
+                    if (++halo_c == args.k_blocks_per_tap) { halo_c = 0; ++halo_r; }
+                } else if (leader) {
+                    const uint32_t b_lo = smem_desc_lo(w_base + (n_tile * args.k_blocks + kb0) * kBTileBytes, 16);
                     for (int g = 0; g < G; ++g) {
 #pragma unroll
                         for (int k = 0; k < kBlockK / 16; ++k)
@@ -496,7 +540,15 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         // two epilogue warpgroups: group g drains accumulator g, i.e. every other tile
         const int group = (warp - 2) >> 2;
         const int quadrant = warp & 3;
-        const int row = quadrant * 32 + lane;
+        const int gemm_row = quadrant * 32 + lane;
+        // halo form: GEMM row = padded position; only columns < Q of each row are outputs, compacted for the store
+        int row = gemm_row;
+        bool row_is_output = true;
+        if (pargs.halo) {
+            const int line = gemm_row / pargs.pitch, column = gemm_row - line * pargs.pitch;
+            row_is_output = column < args.out_q && line < args.rows_per_tile;
+            row = row_is_output ? line * args.out_q + column : 0;
+        }
         const bool store_thread = ((warp - 2) & 3) == 0 && lane == 0;
         const float* bias_smem = reinterpret_cast<const float*>(generic_base + pargs.bias_offset);
         bool ok = true;
@@ -577,7 +629,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                         __nv_bfloat162 pair = __floats2bfloat162_rn(v[8 * q4 + 2 * t], v[8 * q4 + 2 * t + 1]);
                         w[t] = *reinterpret_cast<uint32_t*>(&pair);
                     }
-                    *reinterpret_cast<uint4*>(row_smem + (((chunk16 + q4) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    if (row_is_output) *reinterpret_cast<uint4*>(row_smem + (((chunk16 + q4) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
             // release the accumulator, then publish the finished tile
@@ -658,17 +710,23 @@ int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const 
     int room = kSmemBudget - 1024 - kBarrierBytes - bias_bytes - args.ring_offset;
     // K slices per handshake: the largest divisor of the K loop (<= 4) that still leaves >= 2 ring slots
     int group = 1;
-    for (int candidate = 4; candidate >= 2; --candidate)
-        if (args.gemm.k_blocks % candidate == 0 && room / (candidate * kTileM * kBlockK * 2) >= 2) {
-            group = candidate;
-            break;
-        }
-    int stages = room / (group * kTileM * kBlockK * 2);
+    if (args.halo) {
+        // a slot holds 128 + S - 1 rows of 128 bytes: the last tap reads S - 1 rows past the 128th GEMM row
+        args.slot_bytes = ((kTileM + args.gemm.filter_s - 1) * 128 + 1023) & ~1023;
+    } else {
+        for (int candidate = 4; candidate >= 2; --candidate)
+            if (args.gemm.k_blocks % candidate == 0 && room / (candidate * kTileM * kBlockK * 2) >= 2) {
+                group = candidate;
+                break;
+            }
+        args.slot_bytes = group * kTileM * kBlockK * 2;
+    }
+    int stages = room / args.slot_bytes;
     if (stages > kMaxRingStages) stages = kMaxRingStages;
     if (stages < 2) return fail(kUnsupported, "tcgen05 conv: the filter does not leave room for an activation ring");
     args.stages = stages;
     args.group_k = group;
-    args.bias_offset = args.ring_offset + stages * group * kTileM * kBlockK * 2;
+    args.bias_offset = args.ring_offset + stages * args.slot_bytes;
     args.barrier_offset = args.bias_offset + bias_bytes;
     const int dynamic = args.barrier_offset + kBarrierBytes + 1024;
     static int configured = 0;
@@ -829,15 +887,33 @@ int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStrea
     if (p.reserved != 1 && p.y.dtype == DFGPU_BF16 && whole_tiles && residual_ok && filter_fits && N * P * Q < (1ll << 31) && bn <= 128) {
         PersistentArgs pargs{};
         pargs.gemm = args;
+        // filters wider than one tap: load each filter row's input rows once, padded columns included
+        const int64_t pitch = Q + S - 1;
+        if (!pointwise && S > 1 && S <= 8 && pitch <= kTileM) {
+            const int halo_rows = static_cast<int>(kTileM / pitch);
+            if (halo_rows >= 1 && P % halo_rows == 0) {
+                pargs.halo = 1;
+                pargs.pitch = static_cast<int>(pitch);
+                pargs.gemm.rows_per_tile = halo_rows;
+                pargs.gemm.tiles_per_image = static_cast<int>(P / halo_rows);
+                m_tiles = N * pargs.gemm.tiles_per_image;
+                uint64_t dims4[4] = {static_cast<uint64_t>(C), static_cast<uint64_t>(W), static_cast<uint64_t>(H), static_cast<uint64_t>(N)};
+                uint64_t strides3[3] = {static_cast<uint64_t>(C) * 2, static_cast<uint64_t>(W * C) * 2, static_cast<uint64_t>(H * W * C) * 2};
+                uint32_t box4[4] = {kBlockK, static_cast<uint32_t>(pitch), static_cast<uint32_t>(halo_rows), 1};
+                status = make_map(&map_a, tensors[0], 4, dims4, strides3, box4, "CONV_FPROP X (halo)");
+                if (status) return status;
+            }
+        }
+        const int out_box_rows = pargs.halo ? pargs.gemm.rows_per_tile * static_cast<int>(Q) : box_rows;
         pargs.n_tiles = static_cast<int>(K / bn);
         pargs.total_tiles = static_cast<int>(m_tiles) * pargs.n_tiles;
-        pargs.box_rows = box_rows;
+        pargs.box_rows = out_box_rows;
         pargs.filter_bytes = static_cast<int>(filter_bytes);
         pargs.bias_stride = static_cast<int>(K);
         CUtensorMap map_out, map_res;
         uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N * P * Q)};
         uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
-        uint32_t box[2] = {64, static_cast<uint32_t>(box_rows)};
+        uint32_t box[2] = {64, static_cast<uint32_t>(out_box_rows)};
         status = make_map(&map_out, tensors[2], 2, dims, strides, box, "CONV_FPROP Y");
         if (status) return status;
         const void* residual = full_steps ? args.epi_data[residual_step] : tensors[2];
