@@ -262,7 +262,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // Every global access is a full-line TMA transfer; nothing is read from HBM twice.
 
 constexpr int kMaxRingStages = 12;
-constexpr int kPersistentThreads = 320;  // producer warp, MMA warp, two epilogue warpgroups
+constexpr int kPersistentThreads = 352;  // loader warp, issuing warp, two epilogue warpgroups, second issuing warp
 constexpr int kAccumulators = 4;          // TMEM accumulators in flight: hides the commit -> epilogue -> release round trip
 constexpr int kMaxBiasFloats = 2048;    // per-channel ADD operands staged in shared memory as f32
 
@@ -284,14 +284,19 @@ struct PersistentArgs {
     int32_t halo;          // 0 = one slot per tap (or plain GEMM rows)
     int32_t pitch;         // Q + S - 1
     int32_t slot_bytes;    // bytes between ring slots
+    int32_t issuers;       // 1, or 2: warp 10 issues the odd tiles of this CTA (a lone lane issues ~60 cycles per product,
+                           // twice what a 128 x 64 x 16 product takes to run, so many-tap tiles are issue-bound with one)
 };
 
 // Cycle stamps of the first CTA's roles (loader, issuing lane, two epilogue groups), for tuning builds only.
 #ifdef DFGPU_CONV_TRACE
 __device__ long long g_conv_trace[4][128][4];
+__device__ unsigned long long g_conv_span[160][8];  // per CTA wall-clock ns: entry, after the prologue barrier, exit, loader prefetch done, tensor memory allocated, bias staged
 #define CONV_TRACE(role, n, k) do { if (blockIdx.x == 0 && (n) < 128) g_conv_trace[role][n][k] = clock64(); } while (0)
+#define CONV_SPAN_AT(thread, k) do { if (threadIdx.x == (thread) && blockIdx.x < 160) g_conv_span[blockIdx.x][k] = global_timer_ns(); } while (0)
 #else
 #define CONV_TRACE(role, n, k) do {} while (0)
+#define CONV_SPAN_AT(thread, k) do {} while (0)
 #endif
 
 template <int BN, bool HAS_RES>
@@ -324,6 +329,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 
     const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
     chain_release();  // the next kernel of the plan may start taking SMs as this one's CTAs leave
+    CONV_SPAN_AT(0, 0);
 
     auto tile_geometry = [&](int tile, int& m_tile, int& n_tile, int& image, int& h0, int64_t& out_row0) {
         m_tile = tile / pargs.n_tiles;
@@ -449,11 +455,13 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         ld.phase = 1;
         ld.ok = true;
         run_loader(true);
+        CONV_SPAN_AT(0, 3);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, kAccumulators * BN);
         tmem_relinquish();
         tc_fence_before();
+        CONV_SPAN_AT(32, 4);
     }
     if (warp != 0) chain_wait();  // warp 0 waited before its first load
     {
@@ -467,21 +475,31 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             ++slot;
         }
     }
+    CONV_SPAN_AT(64, 5);
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
+    CONV_SPAN_AT(0, 1);
 
     if (warp == 0) {
         run_loader(false);
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 10) {
         // All 32 lanes walk the schedule; the elected lane issues the products and their commits.
+        const int me = warp == 1 ? 0 : 1;
         const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
                                (static_cast<uint32_t>(kTileM >> 4) << 24);
         const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+        const int slots_per_tile = pargs.halo ? args.k_blocks / args.filter_s : args.k_blocks / G;
         int stage = 0;
         uint32_t phase = 0, it = 0;
-        bool ok = mbar_wait_warp(w_full_bar, 0, 117);
-        for (int tile = blockIdx.x, i = 0; tile < pargs.total_tiles; tile += gridDim.x, ++i) {
+        bool ok = me < pargs.issuers && mbar_wait_warp(w_full_bar, 0, 117);
+        for (int tile = blockIdx.x, i = 0; tile < pargs.total_tiles && me < pargs.issuers; tile += gridDim.x, ++i) {
+            if (pargs.issuers == 2 && (i & 1) != me) {
+                // the other issuing warp's tile: step over its ring slots
+                for (int n = 0; n < slots_per_tile; ++n, ++it)
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                continue;
+            }
             const int acc = i % kAccumulators;
             const int n_tile = tile % pargs.n_tiles;
             if (ok) ok = mbar_wait_warp(acc_empty_bar(acc), ((i / kAccumulators) & 1) ^ 1, 113);
@@ -489,11 +507,11 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const uint32_t tmem_acc = tmem_u + static_cast<uint32_t>(acc * BN);
             int halo_r = 0, halo_c = 0;  // filter row and channel block of the next slot (halo form)
             for (int kb0 = 0; kb0 < args.k_blocks && ok; kb0 += (pargs.halo ? args.filter_s : G), ++it) {
-                if (leader) CONV_TRACE(1, it, 0);
+                if (leader && me == 0) CONV_TRACE(1, it, 0);
                 ok = mbar_wait_warp(full_bar(stage), phase, 114);
                 if (!ok) break;
                 tc_fence_after();
-                if (leader) CONV_TRACE(1, it, 1);
+                if (leader && me == 0) CONV_TRACE(1, it, 1);
                 const uint32_t a_lo = smem_desc_lo(ring_base + stage * pargs.slot_bytes, 16);
                 if (pargs.halo) {
                     // tap s of this filter row reads the slot from row s on: only the start address moves, by s * 128 bytes.
@@ -531,7 +549,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     }
                 }
                 if (leader) umma_commit(empty_bar(stage));
-                if (leader) CONV_TRACE(1, it, 2);
+                if (leader && me == 0) CONV_TRACE(1, it, 2);
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
             if (leader) umma_commit(acc_full_bar(acc));  // arrives even after a failed wait so the epilogue never hangs
@@ -654,6 +672,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 
     tc_fence_before();
     __syncthreads();
+    CONV_SPAN_AT(0, 2);
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kAccumulators * BN);
@@ -729,6 +748,8 @@ int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const 
     args.bias_offset = args.ring_offset + stages * args.slot_bytes;
     args.barrier_offset = args.bias_offset + bias_bytes;
     const int dynamic = args.barrier_offset + kBarrierBytes + 1024;
+    // two issuing warps when a tile is many products (filters wider than one tap) and the ring holds two tiles
+    args.issuers = (args.halo && 2 * (args.gemm.k_blocks / args.gemm.filter_s) <= stages) ? 2 : 1;
     static int configured = 0;
     if (configured < dynamic) {
         cudaError_t error = cudaFuncSetAttribute(umma_conv_persistent_kernel<BN, HAS_RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
