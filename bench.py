@@ -296,6 +296,16 @@ def measure(name: str, steps: int, warmup: int, torch, device, distributed: bool
             "plan": plan, "per_step_ms": per_step, "device_status": status, "replicas": replicas, "footprint": footprint}
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of each configuration's dominant kernel, from the ncu
+# captures summarised under profiles/ (full-size workloads; keyed by configuration number and launch label).
+NCU_TRAFFIC_BYTES = {
+    (2, "conv3+residual"): 72.6e6,     # profiles/umma_conv_persistent_kernel_c2_bottleneck.md
+    (3, "dequantize_b+dequantize_a+matmul"): 34.8e6,  # profiles/umma_mxf8_and_bsq_kernels_c3_quantize_matmul.md
+    (4, "sdpa"): 518.9e6,              # profiles/sdpa_umma_pair_kernel_c4_sdpa.md
+    (5, "paged_decode"): 1313.0e6,     # profiles/sdpa_decode_umma_kernel_c5_paged_decode.md
+}
+
+
 def roofline_for(result: dict, peaks: dict) -> dict:
     wl, plan, per_step = result["workload"], result["plan"], result["per_step_ms"]
     dominant = int(np.argmax(per_step))
@@ -312,10 +322,10 @@ def roofline_for(result: dict, peaks: dict) -> dict:
             # The block-scaled MXFP8 tensor-core kind issues twice the bf16 rate (dense nominal 4.5 vs 2.25 PFLOP/s);
             # the measured peaks hold no fp8 figure, so the denominator is twice the measured bf16 burst.
             peak, note = 2.0 * peak, " (2 x bf16 burst: MXFP8 kind, no measured fp8 peak)"
-        return {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak, "traffic": None,
+        return {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak, "traffic": NCU_TRAFFIC_BYTES.get((wl.config, info["label"])),
                 "kernel": info["label"], "peak_source": peaks["source"] + note, "kernels": kernels}
     gbs = nbytes / 1e9 / duration_s
-    return {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+    return {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get((wl.config, info["label"])),
             "kernel": info["label"], "algorithmic_bytes": nbytes, "peak_source": peaks["source"], "kernels": kernels}
 
 
