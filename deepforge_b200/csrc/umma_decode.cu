@@ -8,6 +8,9 @@
 //     O^T[d,   head] += V_tile^T[d, key] . P[key, head]     M = 128 (d),   N = 16, K = 128 keys
 // One CTA handles one (sequence, KV head) and up to kTilesPerCta key tiles; a second kernel (the
 // same merge the CUDA-core decode path uses) combines the per-CTA (max, sum, partial O) triples.
+// Two CTAs share an SM (three 32 KiB ring slots each): one CTA's softmax and barrier latencies are
+// covered by the other's loads, which measured 1.6x the bandwidth of one CTA with a five-slot ring.
+// The page ids of a CTA's 1024 keys are fetched once into shared memory.
 // Semantics as the reference (lib/Compiler/SequenceGraph.cpp:1839-1889, 1988-2341): a key is
 // valid iff it lies inside the sequence's [lo, hi) window; a page id outside [0, pages) reads as
 // zeros (its keys score 0 and add nothing to O) and is never dereferenced.

@@ -250,15 +250,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // ---- persistent variant for the bandwidth-bound convolutions ------------------------------
 //
 // One CTA per SM walks a static list of output tiles. These convolutions have tiny K loops and
-// almost no math per byte, so what matters is bytes in flight per SM:
+// almost no math per byte, so what matters is bytes in flight per SM and cycles per handshake:
 //   * the whole filter (all taps, all output-channel tiles) is loaded into shared memory ONCE per
-//     CTA and stays there; the ring then carries only 16 KiB activation tiles, as many stages as
-//     the remaining shared memory allows (8-10), filled by the TMA producer across tile borders;
-//   * the MMA lane alternates between two TMEM accumulators, so tile i+1 is multiplied while the
-//     four epilogue warps drain tile i: tcgen05.ld -> bias / ReLU / residual -> bf16 -> swizzled
-//     shared-memory tile -> one TMA store per 64 output channels;
-//   * a residual operand is prefetched by TMA into one of three epilogue buffers and the result
-//     is written over it in place, so the same buffer is the source of the TMA store.
+//     CTA and stays there; the ring then carries only activation tiles, as many slots as the
+//     remaining shared memory allows, filled by the TMA loader warp across tile borders;
+//   * filters wider than one tap use the halo form (see PersistentArgs): one slot per filter row,
+//     the taps of that row read it from shifted start rows;
+//   * the issuing warp (two of them for many-tap tiles, alternating tiles) rotates over four TMEM
+//     accumulators, so the next tiles are multiplied while the two epilogue warpgroups drain
+//     finished ones: tcgen05.ld -> bias / ReLU / residual -> bf16 -> swizzled shared-memory tile
+//     -> one TMA store per 64 output channels;
+//   * a residual operand is prefetched by TMA into one of four epilogue buffers (two per epilogue
+//     group) and the result is written over it in place, so the same buffer is the source of the
+//     TMA store; it goes back to the loader as soon as that store has read it.
 // Every global access is a full-line TMA transfer; nothing is read from HBM twice.
 
 constexpr int kMaxRingStages = 12;
