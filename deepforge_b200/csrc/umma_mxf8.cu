@@ -41,6 +41,8 @@ struct MxArgs {
     int64_t out_ld;
     int32_t out_dtype;
     int32_t m_tiles, n_tiles, k_blocks;
+    int32_t whole_items;   // work items that are whole 128 x BN tiles; the items after them are 128-column halves of the
+    int32_t total_items;   // remaining tiles, so that the last round over the SMs takes half a tile's time instead of a whole one
     int32_t b_mn_major;
     int32_t step_count;
     int32_t step_kind[kMaxSteps];
@@ -107,7 +109,23 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
     const bool leader = elect_one();
-    const int total_tiles = args.m_tiles * args.n_tiles;
+    const int total_tiles = args.total_items;
+    // work item -> (row tile, first column, width in columns)
+    auto decode_item = [&](int item, int& m_tile, int& n0, int& width) {
+        int tile = item, half = -1;
+        if (item >= args.whole_items) {
+            const int h = item - args.whole_items;
+            tile = args.whole_items + (h >> 1);
+            half = h & 1;
+        }
+        m_tile = tile % args.m_tiles;
+        n0 = (tile / args.m_tiles) * BN;
+        width = BN;
+        if (half >= 0) {
+            width = BN / 2;
+            n0 += half * (BN / 2);
+        }
+    };
     chain_release();
 
     if (warp == 0) {
@@ -137,21 +155,20 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         uint32_t phase = 1;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
+            int m_tile, n0, width;
+            decode_item(tile, m_tile, n0, width);
             for (int kb = 0; kb < args.k_blocks; ++kb) {
                 ok = mbar_wait_warp(empty_bar(stage), phase, 401);
                 if (!ok) break;
                 const uint32_t a_dst = smem_base + stage * L::kStageBytes;
                 const uint32_t b_dst = a_dst + kABytes;
                 if (leader) {
-                    mbar_expect_tx(full_bar(stage), kABytes + L::kBBytes);
+                    mbar_expect_tx(full_bar(stage), kABytes + width * kBlockK);
                     tma_load_2d(a_dst, &map_a, kb * kBlockK, m_tile * kTileM, full_bar(stage));
-                    if (args.b_mn_major) {
-#pragma unroll
-                        for (int j = 0; j < BN / 128; ++j)
-                            tma_load_2d(b_dst + j * (kBlockK * 128), &map_b, n_tile * BN + 128 * j, kb * kBlockK, full_bar(stage));
-                    } else {
-                        tma_load_2d(b_dst, &map_b, kb * kBlockK, n_tile * BN, full_bar(stage));
+                    // B arrives as boxes of 128 columns: 128 x 128 bytes each, consecutive in the slot in either layout
+                    for (int j = 0; j < width / 128; ++j) {
+                        if (args.b_mn_major) tma_load_2d(b_dst + j * (kBlockK * 128), &map_b, n0 + 128 * j, kb * kBlockK, full_bar(stage));
+                        else tma_load_2d(b_dst + j * (128 * kBlockK), &map_b, kb * kBlockK, n0 + 128 * j, full_bar(stage));
                     }
                 }
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -161,14 +178,16 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // ---- issuing warp ----
         // instruction descriptor: E4M3 x E4M3, E8M0 scales, A K-major, B per flag, N = BN, M = 128; the two
         // scale-id fields (bits 4-5 for B, 29-30 for A) pick the K block's byte inside the scale columns
-        const uint32_t idesc_base = (static_cast<uint32_t>(args.b_mn_major) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) | (1u << 23) |
-                                    (static_cast<uint32_t>(kTileM >> 4) << 24);
+        const uint32_t idesc_fixed = (static_cast<uint32_t>(args.b_mn_major) << 16) | (1u << 23) | (static_cast<uint32_t>(kTileM >> 4) << 24);
         const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
         int local = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+            int m_tile, n0, width;
+            decode_item(tile, m_tile, n0, width);
+            const uint32_t idesc_base = idesc_fixed | (static_cast<uint32_t>(width >> 3) << 17);
             if (ok) ok = mbar_wait_warp(acc_empty_bar, (local & 1) ^ 1, 402);
             tc_fence_after();
             for (int kb = 0; kb < args.k_blocks && ok; ++kb) {
@@ -180,8 +199,7 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 const uint32_t sf_tmem = tmem_u + 256 + (stage & 1) * 16;  // SFA at +0..3, SFB at +4..
                 if (leader) {
                     tmem_copy_scales(sf_tmem, scale_desc(a_src + L::kSfaOffset));
-#pragma unroll
-                    for (int c = 0; c < BN / 128; ++c) tmem_copy_scales(sf_tmem + 4 + 4 * c, scale_desc(a_src + L::kSfbOffset + 512 * c));
+                    for (int c = 0; c < width / 128; ++c) tmem_copy_scales(sf_tmem + 4 + 4 * c, scale_desc(a_src + L::kSfbOffset + 512 * c));
                 }
                 const uint32_t a_lo = smem_desc_lo(a_src, 16);
                 const uint32_t b_lo = args.b_mn_major ? smem_desc_lo(b_src, kBlockK * 128) : smem_desc_lo(b_src, 16);
@@ -206,20 +224,21 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         bool ok = true;
         int local = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
-            const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
+            int m_tile, n0, width;
+            decode_item(tile, m_tile, n0, width);
             if (ok) ok = mbar_wait(acc_full_bar, local & 1, 404);
             tc_fence_after();
             const bool healthy = ok && g_device_status == 0;
             const int64_t out_row = static_cast<int64_t>(m_tile) * kTileM + row;
 #pragma unroll 1
-            for (int chunk = 0; chunk < BN / 32; ++chunk) {
+            for (int chunk = 0; chunk < width / 32; ++chunk) {
                 uint32_t raw[32];
                 tmem_load_32(tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) + chunk * 32, raw);
                 tmem_load_wait();
                 float v[32];
 #pragma unroll
                 for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[e]);
-                const int64_t col0 = static_cast<int64_t>(n_tile) * BN + chunk * 32;
+                const int64_t col0 = static_cast<int64_t>(n0) + chunk * 32;
                 for (int s = 0; s < args.step_count; ++s) {
                     const int kind = args.step_kind[s];
                     if (kind == kStepRelu) {
@@ -265,7 +284,8 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         bool ok = true;
         int it = 0;  // ring events of this CTA, in the loader's order
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
+            int m_tile, n0, width;
+            decode_item(tile, m_tile, n0, width);
             for (int kb = 0; kb < args.k_blocks; ++kb, ++it) {
                 if ((it & (kStages - 1)) != slot) continue;
                 // issue the global loads first: they do not depend on the slot being free
@@ -278,7 +298,11 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 for (int c = 0; c < BN / 128; ++c)
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
-                        const uint8_t* p = args.sfb + static_cast<int64_t>(kb) * 4 * args.sfb_ld + static_cast<int64_t>(n_tile) * BN + c * 128 + g * 32 + lane;
+                        if (c * 128 >= width) {  // a half-width work item has one chunk of column scales
+                            b_words[c][g] = 0;
+                            continue;
+                        }
+                        const uint8_t* p = args.sfb + static_cast<int64_t>(kb) * 4 * args.sfb_ld + static_cast<int64_t>(n0) + c * 128 + g * 32 + lane;
                         const uint32_t b0 = __ldg(p), b1 = __ldg(p + args.sfb_ld), b2 = __ldg(p + 2 * args.sfb_ld), b3 = __ldg(p + 3 * args.sfb_ld);
                         b_words[c][g] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
                     }
@@ -398,7 +422,7 @@ int launch_matmul_mxf8(const dfgpu_matmul_params& p, void* const* tensors, cudaS
     if (b_k_major) {
         uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
         uint64_t strides[1] = {static_cast<uint64_t>(p.b.stride[rank - 1])};
-        uint32_t box[2] = {kBlockK, static_cast<uint32_t>(bn)};
+        uint32_t box[2] = {kBlockK, 128};
         int status = make_map_u8(&map_b, tensors[1], dims, strides, box, "MATMUL B (E4M3)");
         if (status) return status;
     } else {
@@ -423,6 +447,15 @@ int launch_matmul_mxf8(const dfgpu_matmul_params& p, void* const* tensors, cudaS
     if (!translate_steps(p, tensors, &args)) return fail(kUnsupported, "MATMUL: the fused epilogue is not one the MXFP8 kernel applies");
     const int64_t tiles = static_cast<int64_t>(args.m_tiles) * args.n_tiles;
     const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
+    // The tiles left over after the last full round over the SMs are cut into halves when the halves still fit one
+    // round: 4096^3 is 512 tiles on 148 SMs, i.e. three full rounds and 68 tiles, which become 136 half tiles.
+    const int remainder = static_cast<int>(tiles % grid);
+    args.whole_items = static_cast<int>(tiles);
+    args.total_items = static_cast<int>(tiles);
+    if (bn == 256 && remainder > 0 && 2 * remainder <= grid) {
+        args.whole_items = static_cast<int>(tiles - remainder);
+        args.total_items = args.whole_items + 2 * remainder;
+    }
     auto run = [&](auto kernel, int dynamic) -> int {
         cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dynamic);
         if (error != cudaSuccess) return fail(kExecutionFailed, "MATMUL: cannot reserve %d bytes of shared memory: %s", dynamic, cudaGetErrorString(error));

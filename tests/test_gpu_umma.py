@@ -97,6 +97,28 @@ def test_conv_umma_matches_oracle(n, c, h, w, k, r, pad, one_tile_per_cta):
     check_bf16(out, ref)
 
 
+@pytest.mark.parametrize("n,c,h,w,k,r,pad", [
+    (2, 128, 28, 28, 64, 3, 1),   # two channel blocks per filter row, 4 rows of pitch 30 per tile
+    (1, 64, 28, 28, 128, 3, 1),   # 128 output channels in one N tile
+    (3, 64, 56, 56, 256, 3, 1),   # two N tiles share each activation tile
+])
+def test_conv_umma_halo_form(n, c, h, w, k, r, pad):
+    """Filters wider than one tap on the persistent kernel: each filter row's input rows are loaded once with
+    their padded columns and the three taps read that slot from shifted start rows; GEMM rows that fall on the
+    padding columns are computed and dropped."""
+    info, out, ref = conv_case(n, c, h, w, k, r, pad, epilogue=[step(dfgpu.EPI_RELU)], seed=12)
+    assert info.kernel == dfgpu.CONV_UMMA_BF16
+    check_bf16(out, ref)
+
+
+def test_conv_umma_halo_form_one_by_three_filter():
+    n, c, h, w, k = 2, 64, 16, 28, 64
+    x_dims, w_dims, y_dims = [n, c, h, w], [k, c, 1, 3], [n, k, h, w]
+    info, out, ref = run_conv(BF16, x_dims, w_dims, [0, 1], [0, 1], [1, 1], [1, 1], dfgpu.CONV_UMMA_BF16,
+                              nhwc_strides(x_dims), nhwc_strides(w_dims), nhwc_strides(y_dims), seed=13)
+    check_bf16(out, ref)
+
+
 @pytest.mark.parametrize("one_tile_per_cta", [False, True])
 @pytest.mark.parametrize("n,c,h,w,k,r,pad", [(2, 64, 12, 12, 256, 1, 0), (3, 64, 16, 16, 64, 3, 1), (40, 64, 28, 28, 128, 1, 0)])
 def test_conv_umma_fused_bias_relu_and_residual(n, c, h, w, k, r, pad, one_tile_per_cta):
