@@ -58,6 +58,13 @@ __device__ __forceinline__ void tmem_store_32(uint32_t taddr, const uint32_t (&r
           "r"(r[30]), "r"(r[31])
         : "memory");
 }
+__device__ __forceinline__ void tmem_store_16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
 __device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __global__ void __launch_bounds__(kSdpaThreads, 1)
@@ -303,10 +310,12 @@ sdpa_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 // ---- two query tiles per CTA ------------------------------------------------------
 // The softmax of one tile costs about as many cycles as its two products, so a CTA that owns two
 // 128-row query tiles (A and B) lets the tensor pipe work on one while the other is in its softmax:
-//   warp 0      TMA: Q_A, Q_B once, then K_0, V_0, K_1, ... into a ring of 32 KiB slots
-//   warp 1      one lane issues, per key tile j:  O_A += P_A(j) V_j ; S_A(j+1) = Q_A K_{j+1}^T ;
+//   warp 16     TMA: Q_A, Q_B once, then K_0, V_0, K_1, ... into a ring of 32 KiB slots
+//   warp 17     one lane issues, per key tile j:  O_A += P_A(j) V_j ; S_A(j+1) = Q_A K_{j+1}^T ;
 //                                                 O_B += P_B(j) V_j ; S_B(j+1) = Q_B K_{j+1}^T
-//   warps 2-5   softmax of tile A, warps 6-9 softmax of tile B, one query row per thread
+//   warps 0-7   softmax of tile A, warps 8-15 softmax of tile B (four whole warpgroups, which take the registers the
+//               loader and issuing warps give up): two threads per query row, each with 64 of the
+//               tile's 128 keys (the two warps that share a lane quarter trade row maxima through shared memory)
 // TMEM: S_A at +0, S_B at +128, O_A at +256, O_B at +384. P never goes through shared memory: each
 // thread overwrites the front of its own score row with the bf16 probabilities (two per 32-bit
 // column) and the second product takes its A operand from tensor memory. The tensor pipe runs the
@@ -321,13 +330,18 @@ __device__ long long g_sdpa_trace[3][64][10];
 #define SDPA_TRACE(role, j, k) do {} while (0)
 #endif
 
-constexpr int kPairSlots = 5;
-constexpr int kPairThreads = 320;
+constexpr int kPairSlots = 4;
+#ifndef DFGPU_SDPA_POLY_EVERY
+#define DFGPU_SDPA_POLY_EVERY 2
+#endif
+constexpr int kPolyEvery = DFGPU_SDPA_POLY_EVERY;  // of each 2 * kPolyEvery exponentials one is computed on the FMA pipe
+constexpr int kPairThreads = 576;  // loader warp, issuing warp, 2 x 8 softmax warps (two threads per query row)
 
 struct PairSmem {
     static constexpr int kQ = 0;                       // Q_A, Q_B; later the output staging tiles
     static constexpr int kRing = 2 * kTileBytes;
-    static constexpr int kBarriers = kRing + kPairSlots * kTileBytes;
+    static constexpr int kExchange = kRing + kPairSlots * kTileBytes;  // row maxima [tile][parity][quadrant][half][lane] + row sums [tile][quadrant][half][lane]
+    static constexpr int kBarriers = kExchange + (2 * 2 * 4 * 2 * 32 + 2 * 4 * 2 * 32) * 4;
     // q_full, kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2]
     static constexpr int kBarrierCount = 1 + 2 * kPairSlots + 6;
     static constexpr int kTotal = kBarriers + kBarrierCount * 8 + 16;
@@ -367,6 +381,19 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
     return d;
 }
 
+// 2^x on the FMA and integer pipes: round x to the nearest integer n with the 1.5 * 2^23 trick, evaluate a
+// cubic for 2^(x - n) on [-0.5, 0.5] (relative error 7.5e-5, far below the bf16 rounding of P) and add n
+// to the exponent field. The special-function unit runs 16 ex2 per clock per SM: 1024 cycles for a 128 x 128
+// score tile, as long as its two tensor-core products take, so part of the exponentials go this way.
+__device__ __forceinline__ float exp2_poly(float x) {
+    x = fmaxf(x, -125.0f);  // masked scores (-inf) end as 2^-125: nothing in a sum that holds a term >= 2^-8
+    const float magic = 12582912.0f;
+    const float t = x + magic;
+    const float f = x - (t - magic);
+    const float p = fmaf(fmaf(fmaf(0.0551716685f, f, 0.2426111251f), f, 0.6932609677f), f, 0.9999280572f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
 __global__ void __launch_bounds__(kPairThreads, 1)
 sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o, SdpaUmmaArgs args) {
@@ -404,12 +431,12 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
         for (int x = 0; x < 2; ++x) {
             mbar_init(s_full(x), 1);
-            mbar_init(p_full(x), 4);
+            mbar_init(p_full(x), 8);
             mbar_init(o_full(x), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {
+    if (warp == 17) {
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
         tc_fence_before();
@@ -418,7 +445,7 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
 
-    if (warp == 0) {
+    if (warp == 16) {
         const bool leader = elect_one();
         if (leader) {
             mbar_expect_tx(q_full, 2 * kTileBytes);
@@ -441,7 +468,7 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             }
             if (++slot == kPairSlots) { slot = 0; phase ^= 1; }
         }
-    } else if (warp == 1) {
+    } else if (warp == 17) {
         // All 32 lanes walk the schedule; the elected lane issues the products and their commits.
         const bool leader = elect_one();
         const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kKeys >> 3) << 17) | (static_cast<uint32_t>(kRows >> 4) << 24);
@@ -525,45 +552,60 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
         commit(o_full(1));
     } else {
-        const int x = (warp - 2) >> 2;  // 0: tile A, 1: tile B
-        const int quadrant = warp & 3;
+        const int sw = warp;
+        const int x = sw >> 3;           // 0: tile A, 1: tile B
+        const int half = (sw >> 2) & 1;  // which 64 of the tile's 128 keys (and of the 128 output columns) this thread owns
+        const int quadrant = warp & 3;   // tensor-memory lane quarter of this warp; warps w and w + 4 share it
         const int row = quadrant * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
         const uint32_t tmem_s = tmem_base + lane_base + x * 128;
-        const uint32_t tmem_o = tmem_base + lane_base + 256 + x * 128;
+        const uint32_t tmem_o = tmem_base + lane_base + 256 + x * 128 + half * 64;
         const int q_tile = q_tile_a + x;
         const int q_index = q_tile * kRows + row;
         const int my_tiles = x ? tiles_b : tiles_a;
         const float scale = args.scale_log2;
-        float m_ref = -INFINITY;  // reference maximum, scaled, log2 domain
-        float l_sum = 0.0f;
+        const int pair_barrier = 1 + x * 4 + quadrant;  // the 64 threads that share these 32 rows
+        float* exchange = reinterpret_cast<float*>(generic_base + PairSmem::kExchange);
+        float* sum_exchange = exchange + 2 * 2 * 4 * 2 * 32;
+        const bool stamp = threadIdx.x == x * 256;
+        float m_ref = -INFINITY;  // reference maximum, scaled, log2 domain (identical in both threads of a row)
+        float l_sum = 0.0f;       // this thread's half of the row sum
         bool ok = true;
         for (int j = 0; j < my_tiles; ++j) {
-            if (threadIdx.x == 64 + x * 128) SDPA_TRACE(x, j, 0);
+            if (stamp) SDPA_TRACE(x, j, 0);
             if (ok) ok = mbar_wait(s_full(x), j & 1, 228 + x);
             tc_fence_after();
-            if (threadIdx.x == 64 + x * 128) SDPA_TRACE(x, j, 1);
-            uint32_t raw[4][32];
+            if (stamp) SDPA_TRACE(x, j, 1);
+            // Two passes over this thread's 64 scores, 32 at a time (with 576 threads a thread has ~88 registers): the
+            // first finds the half-row maximum, the second reloads the scores and forms the probabilities.
+            const bool diagonal = args.causal && j == q_tile;
+            const int limit = q_index - j * kKeys - half * 64;  // diagonal tile: keys 0..limit of this thread's 64 are visible
+            float mine = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_load_32(tmem_s + c * 32, raw[c]);
-            tmem_load_wait();
-            if (threadIdx.x == 64 + x * 128) SDPA_TRACE(x, j, 2);
-            if (args.causal && j == q_tile) {
-                const int limit = q_index - j * kKeys;  // keys 0..limit of this tile are visible
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < 2; ++c) {
+                uint32_t raw[32];
+                tmem_load_32(tmem_s + half * 64 + c * 32, raw);
+                tmem_load_wait();
+                if (diagonal) {
 #pragma unroll
                     for (int e = 0; e < 32; ++e)
-                        if (c * 32 + e > limit) raw[c][e] = 0xff800000u;  // -inf
-            }
-            float lane_max[4];
+                        if (c * 32 + e > limit) raw[e] = 0xff800000u;  // -inf
+                }
+                float part[4];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                lane_max[c] = __uint_as_float(raw[c][0]);
+                for (int g = 0; g < 4; ++g) {
+                    part[g] = __uint_as_float(raw[g * 8]);
 #pragma unroll
-                for (int e = 1; e < 32; ++e) lane_max[c] = fmaxf(lane_max[c], __uint_as_float(raw[c][e]));
+                    for (int e = 1; e < 8; ++e) part[g] = fmaxf(part[g], __uint_as_float(raw[g * 8 + e]));
+                }
+                mine = fmaxf(mine, fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])));
             }
-            const float tile_max = fmaxf(fmaxf(lane_max[0], lane_max[1]), fmaxf(lane_max[2], lane_max[3])) * scale;
+            if (stamp) SDPA_TRACE(x, j, 2);
+            // trade the half-row maxima with the warp that owns the other 64 keys of these rows
+            float* slot = exchange + (((x * 2 + (j & 1)) * 4 + quadrant) * 2) * 32;
+            slot[half * 32 + lane] = mine;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
+            const float tile_max = fmaxf(mine, slot[(half ^ 1) * 32 + lane]) * scale;
             // raise the reference only when it would grow by more than the threshold (or on the first tile)
             const bool raise = tile_max > m_ref + kRescaleThreshold;
             if (__any_sync(0xffffffffu, raise)) {
@@ -572,9 +614,10 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 l_sum *= alpha;
                 m_ref = m_new;
                 if (j > 0) {
-                    // O_x holds P V up to tile j-1; that product was issued ahead of S_x(j), which has completed
+                    // O_x holds P V up to tile j-1; that product was issued ahead of S_x(j), which has completed.
+                    // This thread rescales its 64 columns of the row.
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < 2; ++c) {
                         uint32_t acc[32];
                         tmem_load_32(tmem_o + c * 32, acc);
                         tmem_load_wait();
@@ -584,44 +627,58 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     }
                 }
             }
-            if (threadIdx.x == 64 + x * 128) SDPA_TRACE(x, j, 3);
+            if (stamp) SDPA_TRACE(x, j, 3);
             const uint64_t scale2 = pack2(scale, scale), bias2 = pack2(-m_ref, -m_ref);
             uint64_t sums[4] = {0, 0, 0, 0};  // four independent chains of packed partial sums
+            uint32_t packed[32];              // this thread's 64 probabilities as bf16 pairs
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t packed[32];  // 64 keys as bf16 pairs
+            for (int c = 0; c < 2; ++c) {
+                uint32_t raw[32];
+                tmem_load_32(tmem_s + half * 64 + c * 32, raw);
+                tmem_load_wait();
+                if (diagonal) {
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const int key = half * 64 + 2 * e;
-                    const uint64_t x = fma2(pack2(__uint_as_float(raw[key >> 5][key & 31]), __uint_as_float(raw[(key + 1) >> 5][(key + 1) & 31])), scale2, bias2);
+                    for (int e = 0; e < 32; ++e)
+                        if (c * 32 + e > limit) raw[e] = 0xff800000u;
+                }
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const uint64_t v = fma2(pack2(__uint_as_float(raw[2 * e]), __uint_as_float(raw[2 * e + 1])), scale2, bias2);
                     float x0, x1;
-                    unpack2(x, x0, x1);
-                    const float p0 = ex2_fast(x0), p1 = ex2_fast(x1);
+                    unpack2(v, x0, x1);
+                    const float p0 = ex2_fast(x0), p1 = (e % kPolyEvery == 0) ? exp2_poly(x1) : ex2_fast(x1);
                     sums[e & 3] = add2(sums[e & 3], pack2(p0, p1));
                     __nv_bfloat162 two = __floats2bfloat162_rn(p0, p1);
-                    packed[e] = *reinterpret_cast<uint32_t*>(&two);
+                    packed[c * 16 + e] = *reinterpret_cast<uint32_t*>(&two);
                 }
-                tmem_store_32(tmem_s + half * 32, packed);
             }
+            // The probabilities of keys 64..127 land on columns that hold scores of keys 32..63: both threads of a
+            // row must have finished re-reading their scores before either stores.
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
+            tmem_store_32(tmem_s + half * 32, packed);
             {
                 float lo, hi;
                 unpack2(add2(add2(sums[0], sums[1]), add2(sums[2], sums[3])), lo, hi);
                 l_sum += lo + hi;
             }
-            if (threadIdx.x == 64 + x * 128) SDPA_TRACE(x, j, 4);
+            if (stamp) SDPA_TRACE(x, j, 4);
             tmem_store_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full(x));
-            if (threadIdx.x == 64 + x * 128) SDPA_TRACE(x, j, 5);
+            if (stamp) SDPA_TRACE(x, j, 5);
         }
         // last product done -> normalise, stage O in this tile's Q buffer (no product reads it any more), TMA store
         if (ok) ok = mbar_wait(o_full(x), 0, 230 + x);
         tc_fence_after();
-        const float inverse = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
-        uint8_t* o_row = generic_base + PairSmem::kQ + x * kTileBytes + row * 128;
+        float* sum_slot = sum_exchange + ((x * 4 + quadrant) * 2) * 32;
+        sum_slot[half * 32 + lane] = l_sum;
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
+        const float total = l_sum + sum_slot[(half ^ 1) * 32 + lane];
+        const float inverse = total > 0.0f ? 1.0f / total : 0.0f;
+        uint8_t* o_row = generic_base + PairSmem::kQ + x * kTileBytes + half * kHalfBytes + row * 128;  // this thread's 64 output columns
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
             uint32_t acc[32];
             tmem_load_32(tmem_o + c * 32, acc);
             tmem_load_wait();
@@ -633,19 +690,18 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     __nv_bfloat162 two = __floats2bfloat162_rn(__uint_as_float(acc[u * 8 + 2 * t]) * inverse, __uint_as_float(acc[u * 8 + 2 * t + 1]) * inverse);
                     w[t] = *reinterpret_cast<uint32_t*>(&two);
                 }
-                const int unit16 = c * 4 + u;  // 16-byte unit inside the 256-byte output row
-                const int half = unit16 >> 3, unit = unit16 & 7;
-                *reinterpret_cast<uint4*>(o_row + half * kHalfBytes + ((unit ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                const int unit = c * 4 + u;  // 16-byte unit inside this thread's 128 bytes of the output row
+                *reinterpret_cast<uint4*>(o_row + ((unit ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
-        if (args.stats != nullptr && ok)
+        if (args.stats != nullptr && ok && half == 0)
             args.stats[batch * args.stats_batch_stride + head * args.stats_head_stride + static_cast<int64_t>(q_index) * args.stats_row_stride] =
-                l_sum > 0.0f ? 0.6931471805599453f * (m_ref + log2f(l_sum)) : -INFINITY;
+                total > 0.0f ? 0.6931471805599453f * (m_ref + log2f(total)) : -INFINITY;
         tc_fence_before();
         fence_async_shared();
-        if (x == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
-        else asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (quadrant == 0 && lane == 0) {
+        if (x == 0) asm volatile("bar.sync 9, 256;" ::: "memory");
+        else asm volatile("bar.sync 10, 256;" ::: "memory");
+        if ((sw & 7) == 0 && lane == 0) {
             if (ok && g_device_status == 0) {
                 tma_store_2d(&map_o, smem_base + PairSmem::kQ + x * kTileBytes, 0, q_row_a + x * kRows);
                 tma_store_2d(&map_o, smem_base + PairSmem::kQ + x * kTileBytes + kHalfBytes, 64, q_row_a + x * kRows);
@@ -657,7 +713,7 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == 17) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
