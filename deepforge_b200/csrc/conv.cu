@@ -186,6 +186,125 @@ conv_igemm_ffma_kernel(const void* __restrict__ x, const void* __restrict__ w, v
     }
 }
 
+// Fast form of the implicit GEMM for the common f32 case: channels-last X with C % 16 == 0, a packed KRSC filter,
+// one group, no filter reversal. A 16-deep K slice then lies inside one filter tap, so the tap is decoded once
+// per slice for the whole CTA (no per-element divisions), X and W come in as 16-byte loads, and the loads of
+// slice k+1 are in flight (in registers) while slice k is multiplied out of shared memory.
+template <int BM>
+__global__ void __launch_bounds__(256)
+conv_nhwc_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, void* __restrict__ y, ConvArgs a, int m_total) {
+    constexpr int BN = 64, BK = 16, TM = BM / 16, TN = 4;
+    __shared__ float as[2][BK][BM + 4];
+    __shared__ float bs[2][BK][BN + 4];
+    const int tid = threadIdx.x;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    const int P = static_cast<int>(a.y.dim[2]), Q = static_cast<int>(a.y.dim[3]);
+    const int C = static_cast<int>(a.x.dim[1]), S = static_cast<int>(a.w.dim[3]);
+    const int H = static_cast<int>(a.x.dim[2]), W = static_cast<int>(a.x.dim[3]);
+    const int K = static_cast<int>(a.y.dim[1]);
+    const int slices_per_tap = C / BK;
+    const int slices = static_cast<int>(a.w.dim[2]) * S * slices_per_tap;
+
+    // A: BM pixels x 16 channels = BM * 4 float4, one per thread for the first BM * 4 threads
+    const bool a_loader = tid < BM * 4;
+    const int a_m = tid >> 2, a_quad = tid & 3;
+    int a_ih0 = 0, a_iw0 = 0;
+    const float* a_base = x;
+    bool a_valid = false;
+    if (a_loader) {
+        const int m = m0 + a_m;
+        a_valid = m < m_total;
+        const int mm = a_valid ? m : 0;
+        const int q = mm % Q, p = (mm / Q) % P, n = mm / (P * Q);
+        a_ih0 = p * a.stride_h - a.pad_h;
+        a_iw0 = q * a.stride_w - a.pad_w;
+        a_base = x + static_cast<int64_t>(n) * a.x.stride[0] + a_quad * 4;
+    }
+    // B: 64 output channels x 16 = 256 float4, one per thread
+    const int b_n = tid >> 2, b_quad = tid & 3;
+    const bool b_valid = n0 + b_n < K;
+    const float* b_base = w + static_cast<int64_t>(b_valid ? n0 + b_n : 0) * a.w.stride[0] + b_quad * 4;
+
+    auto fetch = [&](int slice, float4& av, float4& bv) {
+        const int tap = slice / slices_per_tap, c0 = (slice - tap * slices_per_tap) * BK;
+        const int r = tap / S, sx = tap - r * S;
+        av = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (a_loader && a_valid) {
+            const int ih = a_ih0 + r * a.dilation_h, iw = a_iw0 + sx * a.dilation_w;
+            if (ih >= 0 && ih < H && iw >= 0 && iw < W)
+                av = __ldg(reinterpret_cast<const float4*>(a_base + static_cast<int64_t>(ih) * a.x.stride[2] + static_cast<int64_t>(iw) * a.x.stride[3] + c0));
+        }
+        bv = b_valid ? __ldg(reinterpret_cast<const float4*>(b_base + static_cast<int64_t>(tap) * C + c0)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    };
+    auto stash = [&](int buffer, const float4& av, const float4& bv) {
+        if (a_loader) {
+            as[buffer][a_quad * 4 + 0][a_m] = av.x;
+            as[buffer][a_quad * 4 + 1][a_m] = av.y;
+            as[buffer][a_quad * 4 + 2][a_m] = av.z;
+            as[buffer][a_quad * 4 + 3][a_m] = av.w;
+        }
+        bs[buffer][b_quad * 4 + 0][b_n] = bv.x;
+        bs[buffer][b_quad * 4 + 1][b_n] = bv.y;
+        bs[buffer][b_quad * 4 + 2][b_n] = bv.z;
+        bs[buffer][b_quad * 4 + 3][b_n] = bv.w;
+    };
+
+    const int ty = tid / 16, tx = tid % 16;
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+
+    float4 av, bv;
+    fetch(0, av, bv);
+    stash(0, av, bv);
+    __syncthreads();
+    for (int slice = 0; slice < slices; ++slice) {
+        const int buffer = slice & 1;
+        if (slice + 1 < slices) fetch(slice + 1, av, bv);
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a_reg[TM], b_reg[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a_reg[i] = as[buffer][kk][ty * TM + i];
+            const float4 b4 = *reinterpret_cast<const float4*>(&bs[buffer][kk][tx * TN]);
+            b_reg[0] = b4.x; b_reg[1] = b4.y; b_reg[2] = b4.z; b_reg[3] = b4.w;
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a_reg[i], b_reg[j], acc[i][j]);
+        }
+        if (slice + 1 < slices) stash(buffer ^ 1, av, bv);  // the other buffer was last read before the previous barrier
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int m = m0 + ty * TM + i;
+        if (m >= m_total) continue;
+        const int q = m % Q, p = (m / Q) % P, n = m / (P * Q);
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int k = n0 + tx * TN + j;
+            if (k >= K) continue;
+            const float value = apply_epilogue(acc[i][j], a, n, k, p, q);
+            store_from_f32(y, a.y.dtype, n * a.y.stride[0] + k * a.y.stride[1] + p * a.y.stride[2] + q * a.y.stride[3], value);
+        }
+    }
+}
+
+bool nhwc_f32_fast_form(const dfgpu_conv_params& p, void* const* tensors) {
+    if (p.x.dtype != DFGPU_F32 || p.w.dtype != DFGPU_F32 || p.reverse_filter) return false;
+    const int64_t C = p.x.dim[1], R = p.w.dim[2], S = p.w.dim[3];
+    if (p.w.dim[1] != C || C % 16 != 0) return false;  // one group, whole 16-channel slices
+    if (p.x.stride[1] != 1 || p.x.stride[3] % 4 != 0 || p.x.stride[2] % 4 != 0 || p.x.stride[0] % 4 != 0) return false;
+    if (p.w.stride[1] != 1 || p.w.stride[3] != C || p.w.stride[2] != S * C || p.w.stride[0] != R * S * C) return false;
+    if (element_count(p.x) >= (1ll << 31) || element_count(p.y) >= (1ll << 31) || element_count(p.w) >= (1ll << 31)) return false;
+    if ((reinterpret_cast<uintptr_t>(tensors[0]) & 15u) != 0 || (reinterpret_cast<uintptr_t>(tensors[1]) & 15u) != 0) return false;
+    return true;
+}
+
 int build_args(const dfgpu_conv_params& p, void* const* tensors, ConvArgs& a) {
     if (!valid_tensor(p.x) || !valid_tensor(p.w) || !valid_tensor(p.y))
         return fail(kInvalidShape, "CONV_FPROP: tensor rank or extent out of range");
@@ -289,7 +408,17 @@ extern "C" int dfgpu_conv_fprop(const dfgpu_conv_params* p, void* const* tensors
         unsigned grid_n = static_cast<unsigned>((p->y.dim[1] + 63) / 64);
         int64_t tiles64 = (m_total + 63) / 64 * grid_n;
         bool small = tiles64 < 2 * sm_count();
-        if (small) {
+        if (nhwc_f32_fast_form(*p, tensors)) {
+            const float* xf = static_cast<const float*>(tensors[0]);
+            const float* wf = static_cast<const float*>(tensors[1]);
+            if (small) {
+                dim3 grid(static_cast<unsigned>((m_total + 31) / 32), grid_n);
+                conv_nhwc_f32_kernel<32><<<grid, 256, 0, stream>>>(xf, wf, tensors[2], a, static_cast<int>(m_total));
+            } else {
+                dim3 grid(static_cast<unsigned>((m_total + 63) / 64), grid_n);
+                conv_nhwc_f32_kernel<64><<<grid, 256, 0, stream>>>(xf, wf, tensors[2], a, static_cast<int>(m_total));
+            }
+        } else if (small) {
             dim3 grid(static_cast<unsigned>((m_total + 31) / 32), grid_n);
             if (channels_last) conv_igemm_ffma_kernel<32, true><<<grid, 256, 0, stream>>>(tensors[0], tensors[1], tensors[2], a, m_total, k_total);
             else conv_igemm_ffma_kernel<32, false><<<grid, 256, 0, stream>>>(tensors[0], tensors[1], tensors[2], a, m_total, k_total);
