@@ -139,7 +139,7 @@ def test_conv_umma_many_tiles_per_cta():
     check_bf16(out, ref)
 
 
-def run_matmul_mxf8(m, n, k, out_dtype=F32, b_k_major=False, bias_relu=False, seed=9):
+def run_matmul_mxf8(m, n, k, out_dtype=F32, b_k_major=False, bias_relu=False, seed=9, kernel=None):
     """A [m, k] with blocks along K, B [k, n] with blocks along K, quantized by the oracle; the reference is the
     oracle's dequantize + f32 matmul of the same codes and scales."""
     rng = np.random.default_rng(seed)
@@ -161,7 +161,7 @@ def run_matmul_mxf8(m, n, k, out_dtype=F32, b_k_major=False, bias_relu=False, se
     p.a, p.b, p.c = tensor(E4M3, [m, k]), tensor(E4M3, [k, n], b_strides), tensor(out_dtype, [m, n])
     p.a_scale, p.b_scale = tensor(E8M0, [m, k // 32]), tensor(E8M0, [k // 32, n])
     p.a_block[0], p.a_block[1], p.b_block[0], p.b_block[1] = 1, 32, 32, 1
-    p.kernel = dfgpu.MATMUL_UMMA_MXF8
+    p.kernel = dfgpu.MATMUL_UMMA_MXF8 if kernel is None else kernel
     extra = None
     if bias_relu:
         bv = synthetic.round_to_bf16(synthetic.uniform(seed, 3, n, -1.0, 1.0))
@@ -174,7 +174,7 @@ def run_matmul_mxf8(m, n, k, out_dtype=F32, b_k_major=False, bias_relu=False, se
         oracle.pointwise(dfgpu.PW_ADD, cd, ref, tensor(F32, [n]), bv, cd, tmp)
         ref = np.zeros_like(tmp)
         oracle.pointwise(dfgpu.PW_RELU_FWD, cd, tmp, None, None, cd, ref)
-    assert dfgpu.query("matmul", p).kernel == dfgpu.MATMUL_UMMA_MXF8
+    assert dfgpu.query("matmul", p).kernel == p.kernel
     b_codes = np.ascontiguousarray(bq.reshape(k, n).T).reshape(-1) if b_k_major else bq
     d = [g.to_device(v) for v in (aq, b_codes, sa, sb)]
     dc = g.device_zeros(m * n * dfgpu.DTYPE_BYTES[out_dtype], 0x7f)
@@ -185,7 +185,7 @@ def run_matmul_mxf8(m, n, k, out_dtype=F32, b_k_major=False, bias_relu=False, se
 
 
 @pytest.mark.parametrize("b_k_major", [False, True])
-@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (128, 256, 256), (256, 384, 512), (384, 512, 1024)])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (128, 256, 256), (256, 384, 512), (384, 512, 1024), (256, 256, 128), (512, 256, 384)])
 def test_matmul_mxf8_f32_out(m, n, k, b_k_major):
     """Block-scaled tensor-core matmul on E4M3 codes and E8M0 scales: products and scales are exact, so
     with an f32 output only the order of the f32 additions differs from the oracle. The inputs span 2^-6..2^6
@@ -199,4 +199,18 @@ def test_matmul_mxf8_f32_out(m, n, k, b_k_major):
 def test_matmul_mxf8_bf16_out_bias_relu_many_tiles_per_cta():
     """160 tiles of 128 x 256 on 148 SMs: some CTAs run two tiles through the same accumulator."""
     out, ref = run_matmul_mxf8(2560, 2048, 256, BF16, False, bias_relu=True)
+    check_bf16(out, ref)
+
+
+@pytest.mark.parametrize("b_k_major", [False, True])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (512, 256, 384)])
+def test_matmul_mxf8_two_sm_tiles(m, n, k, b_k_major):
+    """The same matmul on 256 x 256 tiles owned by clusters of two CTAs (tcgen05.mma.cta_group::2), chosen by kernel id."""
+    out, ref = run_matmul_mxf8(m, n, k, F32, b_k_major, kernel=dfgpu.MATMUL_UMMA_MXF8_2SM)
+    assert float(np.max(np.abs(out - ref))) <= 1e-4 * float(np.max(np.abs(ref)))
+
+
+def test_matmul_mxf8_two_sm_tiles_many_tiles_per_cluster():
+    """80 tiles of 256 x 256 on 74 clusters: some clusters run two tiles through the same accumulators."""
+    out, ref = run_matmul_mxf8(2560, 2048, 256, BF16, False, bias_relu=True, kernel=dfgpu.MATMUL_UMMA_MXF8_2SM)
     check_bf16(out, ref)
