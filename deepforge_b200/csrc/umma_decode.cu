@@ -131,6 +131,11 @@ sdpa_decode_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + DecodeSmem::kBarriers + 8 * DecodeSmem::kBarrierCount);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_q);
+        prefetch_tensormap(&map_k);
+        prefetch_tensormap(&map_v);
+    }
     const int chunk = blockIdx.x;
     const int kv_head = blockIdx.y;
     const int64_t batch = blockIdx.z;

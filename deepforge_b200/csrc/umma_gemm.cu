@@ -334,6 +334,12 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
     chain_release();  // the next kernel of the plan may start taking SMs as this one's CTAs leave
     CONV_SPAN_AT(0, 0);
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        prefetch_tensormap(&map_out);
+        if (HAS_RES) prefetch_tensormap(&map_res);
+    }
 
     auto tile_geometry = [&](int tile, int& m_tile, int& n_tile, int& image, int& h0, int64_t& out_row0) {
         m_tile = tile / pargs.n_tiles;

@@ -157,6 +157,10 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
     const bool leader = elect_one();
     const int total_tiles = args.total_items;
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+    }
     // work item -> (row tile, first column, width in columns)
     auto decode_item = [&](int item, int& m_tile, int& n0, int& width) {
         int tile = item, half = -1;

@@ -411,6 +411,12 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + PairSmem::kBarriers + 8 * PairSmem::kBarrierCount);
 
     const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_q);
+        prefetch_tensormap(&map_k);
+        prefetch_tensormap(&map_v);
+        prefetch_tensormap(&map_o);
+    }
     const int pairs = args.q_tiles >> 1;
     const int pair = pairs - 1 - static_cast<int>(blockIdx.x);  // heavy (late) causal pairs first
     const int bh = blockIdx.y;
