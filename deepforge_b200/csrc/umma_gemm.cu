@@ -288,6 +288,7 @@ struct PersistentArgs {
     int32_t halo;          // 0 = one slot per tap (or plain GEMM rows)
     int32_t pitch;         // Q + S - 1
     int32_t slot_bytes;    // bytes between ring slots
+    int32_t early_static;  // filter and bias may be fetched before the wait on the previous kernel
     int32_t issuers;       // 1, or 2: warp 10 issues the odd tiles of this CTA (a lone lane issues ~60 cycles per product,
                            // twice what a 128 x 64 x 16 product takes to run, so many-tap tiles are issue-bound with one)
 };
@@ -455,12 +456,15 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             mbar_expect_tx(w_full_bar, static_cast<uint32_t>(pargs.filter_bytes));
         }
         __syncwarp();
-        chain_wait();  // everything before this line is private to the CTA; the loads below read the previous kernel's output
+        // Everything up to chain_wait() is private to the CTA or reads operands no running kernel writes; the loads
+        // after it read the previous kernel's output.
+        if (!pargs.early_static) chain_wait();
         // Start streaming right away: the filter and the first ring-full of activations are in flight
         // while the other warps allocate tensor memory and stage the bias vectors.
         for (int nt = 0; nt < pargs.n_tiles; ++nt)
             for (int kb = 0; kb < args.k_blocks; ++kb)
                 if (leader) tma_load_2d(w_base + (nt * args.k_blocks + kb) * kBTileBytes, &map_b, kb * kBlockK, nt * BN, w_full_bar);
+        if (pargs.early_static) chain_wait();
         ld.tile = blockIdx.x;
         ld.phase = 1;
         ld.ok = true;
@@ -473,7 +477,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         tc_fence_before();
         CONV_SPAN_AT(32, 4);
     }
-    if (warp != 0) chain_wait();  // warp 0 waited before its first load
+    if (warp != 0 && !pargs.early_static) chain_wait();  // warp 0 waited before its first load
     {
         // per-channel ADD operands -> f32 in shared memory, once per CTA
         float* bias_stage = reinterpret_cast<float*>(generic_base + pargs.bias_offset);
@@ -486,6 +490,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         }
     }
     CONV_SPAN_AT(64, 5);
+    if (warp != 0 && pargs.early_static) chain_wait();  // the bias vectors above are static operands
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
@@ -915,9 +920,10 @@ int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStrea
     for (int e = 0; e < args.epi_count; ++e) bias_steps += args.epi_kind[e] == kEpiBias;
     const bool filter_fits = bias_steps * K <= kMaxBiasFloats &&
                              filter_bytes + epilogue_bytes + 3 * kTileM * kBlockK * 2 + bias_steps * K * 4 + 6144 <= kSmemBudget;
-    if (p.reserved != 1 && p.y.dtype == DFGPU_BF16 && whole_tiles && residual_ok && filter_fits && N * P * Q < (1ll << 31) && bn <= 128) {
+    if ((p.reserved & 1) == 0 && p.y.dtype == DFGPU_BF16 && whole_tiles && residual_ok && filter_fits && N * P * Q < (1ll << 31) && bn <= 128) {
         PersistentArgs pargs{};
         pargs.gemm = args;
+        pargs.early_static = (p.reserved & 2) ? 1 : 0;
         // filters wider than one tap: load each filter row's input rows once, padded columns included
         const int64_t pitch = Q + S - 1;
         if (!pointwise && S > 1 && S <= 8 && pitch <= kTileM) {

@@ -272,6 +272,11 @@ Status lower_conv(Lowering& low, std::size_t index) {
     if (low.options.disable_tensor_cores) params.kernel = low.tensor(*x).dim[1] == low.tensor(*w).dim[1] ? DFGPU_CONV_IGEMM_FFMA : DFGPU_CONV_DIRECT;
     step.tensors = {low.bind(*x), low.bind(*w), low.bind(final_uid), TensorBinding{}, TensorBinding{}};
     for (std::size_t i = 0; i < extras.size(); ++i) step.tensors[3 + i] = low.bind(extras[i]);
+    // Filter and ADD operands that no node of the graph writes, behind another convolution of the same plan: the
+    // kernel may fetch them while the previous kernel is still draining (see dfgpu_conv_params::reserved).
+    bool static_operands = !low.plan.steps.empty() && low.plan.steps.back().op == KernelOp::kConvFprop && low.producer.find(*w) == low.producer.end();
+    for (auto uid : extras) static_operands = static_operands && low.producer.find(uid) == low.producer.end();
+    if (static_operands) params.reserved |= 2;
     step.params = params;
     low.plan.steps.push_back(std::move(step));
     return Status::ok();

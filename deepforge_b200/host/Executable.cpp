@@ -158,7 +158,14 @@ Status Executable::execute_steps(std::int64_t first, std::int64_t last, VariantP
             case KernelOp::kBlockScaleQuantize: code = dfgpu_block_scale_quantize(&std::get<dfgpu_bsq_params>(step.params), pointers.data(), scratch, impl.stream); break;
             case KernelOp::kBlockScaleDequantize: code = dfgpu_block_scale_dequantize(&std::get<dfgpu_bsd_params>(step.params), pointers.data(), scratch, impl.stream); break;
             case KernelOp::kPointwise: code = dfgpu_pointwise(&std::get<dfgpu_pointwise_params>(step.params), pointers.data(), scratch, impl.stream); break;
-            case KernelOp::kConvFprop: code = dfgpu_conv_fprop(&std::get<dfgpu_conv_params>(step.params), pointers.data(), scratch, impl.stream); break;
+            case KernelOp::kConvFprop: {
+                // bit 1 of `reserved` (set by the lowering) promises that the kernel launched just before this one is the
+                // plan's previous step; that does not hold for the first launch of a call
+                dfgpu_conv_params params = std::get<dfgpu_conv_params>(step.params);
+                if (index == first) params.reserved &= ~2;
+                code = dfgpu_conv_fprop(&params, pointers.data(), scratch, impl.stream);
+                break;
+            }
             case KernelOp::kMatmul: code = dfgpu_matmul(&std::get<dfgpu_matmul_params>(step.params), pointers.data(), scratch, impl.stream); break;
             case KernelOp::kSdpaForward: code = dfgpu_sdpa_forward(&std::get<dfgpu_sdpa_params>(step.params), pointers.data(), scratch, impl.stream); break;
         }

@@ -143,7 +143,11 @@ typedef struct dfgpu_conv_params {
     int32_t epilogue_count;
     dfgpu_epilogue_step epilogue[DFGPU_MAX_EPILOGUE];
     int32_t kernel;
-    int32_t reserved; /* 0; 1 selects the one-tile-per-CTA form of the tcgen05 kernel (cross-check) */
+    int32_t reserved; /* bit 0: select the one-tile-per-CTA form of the tcgen05 kernel (cross-check).
+                         bit 1: W and the per-channel ADD operands are written by no kernel that may still be
+                         running when this one starts (the launch just before it in the stream is a dfgpu
+                         convolution that does not write them): the persistent kernel then loads them before
+                         it waits for that launch to finish. Leave clear when in doubt. */
 } dfgpu_conv_params;
 int dfgpu_query_conv_fprop(const dfgpu_conv_params*, dfgpu_plan_info*);
 int dfgpu_conv_fprop(const dfgpu_conv_params*, void* const* tensors, void* scratch, void* stream);
