@@ -592,7 +592,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const int n0 = n_tile * BN;
             const int i = group + 2 * j;  // position of this tile in the CTA's tile list
             const int acc = i % kAccumulators;
-            const int buf = HAS_RES ? group * 2 + (j & 1) : group;
+            const int buf = group * 2 + (j & 1);  // two staging buffers per epilogue group, used alternately
             if (HAS_RES && store_thread && j >= 1) {
                 // The store of this group's previous tile has had a whole wait to read its buffer: hand the
                 // buffer back now, so that its next residual tile streams in while this tile is worked on.
@@ -605,8 +605,9 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             if (HAS_RES) {
                 if (ok) ok = mbar_wait(res_full_bar(buf), (j >> 1) & 1, 116);
             } else {
-                // this group's staging buffer was last read by the TMA store of its previous tile
-                if (store_thread) tma_store_wait_read<0>();
+                // this staging buffer was last read by the TMA store of this group's tile before last: at most the
+                // previous tile's store may still be reading (the other buffer)
+                if (store_thread) tma_store_wait_read<1>();
                 epilogue_barrier(1 + group);
             }
             tc_fence_after();
@@ -733,7 +734,7 @@ template <int BN, bool HAS_RES>
 int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_out, const CUtensorMap& map_res,
                       PersistentArgs args, cudaStream_t stream) {
     constexpr int kEpiBytes = (BN / 64) * kTileM * 128;
-    constexpr int kEpiBuffers = HAS_RES ? 4 : 2;
+    constexpr int kEpiBuffers = 4;  // two per epilogue group: a tile is staged while the previous tile's TMA store still reads
     constexpr int kBarrierBytes = (2 * kMaxRingStages + 18) * 8;
     int bias_vectors = 0;
     for (int e = 0; e < args.gemm.epi_count; ++e) bias_vectors += args.gemm.epi_kind[e] == kEpiBias;
@@ -764,7 +765,7 @@ int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const 
     args.barrier_offset = args.bias_offset + bias_bytes;
     const int dynamic = args.barrier_offset + kBarrierBytes + 1024;
     // two issuing warps when a tile is many products (filters wider than one tap) and the ring holds two tiles
-    args.issuers = (args.halo && 2 * (args.gemm.k_blocks / args.gemm.filter_s) <= stages) ? 2 : 1;
+    args.issuers = (args.halo && args.gemm.k_blocks / args.gemm.filter_s + 2 <= stages) ? 2 : 1;
     static int configured = 0;
     if (configured < dynamic) {
         cudaError_t error = cudaFuncSetAttribute(umma_conv_persistent_kernel<BN, HAS_RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
@@ -915,7 +916,7 @@ int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStrea
     const bool whole_tiles = pointwise || P % args.rows_per_tile == 0;
     const bool residual_ok = full_steps == 0 || (full_steps == 1 && args.epi_dtype[residual_step] == DFGPU_BF16);
     const int64_t filter_bytes = K * R * S * C * 2;
-    const int epilogue_bytes = (full_steps ? 4 : 2) * (bn / 64) * kTileM * 128;
+    const int epilogue_bytes = 4 * (bn / 64) * kTileM * 128;
     int bias_steps = 0;
     for (int e = 0; e < args.epi_count; ++e) bias_steps += args.epi_kind[e] == kEpiBias;
     const bool filter_fits = bias_steps * K <= kMaxBiasFloats &&
