@@ -330,18 +330,20 @@ __device__ long long g_sdpa_trace[3][64][10];
 #define SDPA_TRACE(role, j, k) do {} while (0)
 #endif
 
-constexpr int kPairSlots = 4;
+constexpr int kPairSlots = 5;
 #ifndef DFGPU_SDPA_POLY_EVERY
-#define DFGPU_SDPA_POLY_EVERY 2
+#define DFGPU_SDPA_POLY_EVERY 4
 #endif
-constexpr int kPolyEvery = DFGPU_SDPA_POLY_EVERY;  // of each 2 * kPolyEvery exponentials one is computed on the FMA pipe
+constexpr int kPolyEvery = DFGPU_SDPA_POLY_EVERY;  // one pair of exponentials in kPolyEvery goes to the FMA pipe
 constexpr int kPairThreads = 576;  // loader warp, issuing warp, 2 x 8 softmax warps (two threads per query row)
 
 struct PairSmem {
     static constexpr int kQ = 0;                       // Q_A, Q_B; later the output staging tiles
     static constexpr int kRing = 2 * kTileBytes;
-    static constexpr int kExchange = kRing + kPairSlots * kTileBytes;  // row maxima [tile][parity][quadrant][half][lane] + row sums [tile][quadrant][half][lane]
-    static constexpr int kBarriers = kExchange + (2 * 2 * 4 * 2 * 32 + 2 * 4 * 2 * 32) * 4;
+    // 128 bytes per (tile, lane quarter): during the key loop the half-row maxima [half][lane] as bf16, after it the row sum
+    // [lane] as f32. 1 KiB in all: with two Q tiles and five 32 KiB ring slots this is what the 227 KiB leave.
+    static constexpr int kExchange = kRing + kPairSlots * kTileBytes;
+    static constexpr int kBarriers = kExchange + 1024;
     // q_full, kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2]
     static constexpr int kBarrierCount = 1 + 2 * kPairSlots + 6;
     static constexpr int kTotal = kBarriers + kBarrierCount * 8 + 16;
@@ -392,6 +394,26 @@ __device__ __forceinline__ float exp2_poly(float x) {
     const float f = x - (t - magic);
     const float p = fmaf(fmaf(fmaf(0.0551716685f, f, 0.2426111251f), f, 0.6932609677f), f, 0.9999280572f);
     return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
+// The same on a packed pair: the range reduction and the cubic run as f32x2 instructions (6 per pair), only the clamp
+// and the exponent insertion are per element.
+__device__ __forceinline__ void exp2_poly_pair(uint64_t x2, float& p0, float& p1) {
+    float x0, x1;
+    unpack2(x2, x0, x1);
+    x2 = pack2(fmaxf(x0, -125.0f), fmaxf(x1, -125.0f));
+    const uint64_t magic2 = pack2(12582912.0f, 12582912.0f);
+    const uint64_t t2 = add2(x2, magic2);
+    const uint64_t n2 = add2(t2, pack2(-12582912.0f, -12582912.0f));
+    const uint64_t f2 = fma2(n2, pack2(-1.0f, -1.0f), x2);
+    uint64_t q2 = fma2(pack2(0.0551716685f, 0.0551716685f), f2, pack2(0.2426111251f, 0.2426111251f));
+    q2 = fma2(q2, f2, pack2(0.6932609677f, 0.6932609677f));
+    q2 = fma2(q2, f2, pack2(0.9999280572f, 0.9999280572f));
+    float q0, q1, t0, t1;
+    unpack2(q2, q0, q1);
+    unpack2(t2, t0, t1);
+    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
 }
 
 __global__ void __launch_bounds__(kPairThreads, 1)
@@ -571,8 +593,8 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const int my_tiles = x ? tiles_b : tiles_a;
         const float scale = args.scale_log2;
         const int pair_barrier = 1 + x * 4 + quadrant;  // the 64 threads that share these 32 rows
-        float* exchange = reinterpret_cast<float*>(generic_base + PairSmem::kExchange);
-        float* sum_exchange = exchange + 2 * 2 * 4 * 2 * 32;
+        uint16_t* exchange = reinterpret_cast<uint16_t*>(generic_base + PairSmem::kExchange) + ((x * 4 + quadrant) * 2) * 32;  // [half][lane]
+        float* sum_exchange = reinterpret_cast<float*>(generic_base + PairSmem::kExchange) + (x * 4 + quadrant) * 32;
         const bool stamp = threadIdx.x == x * 256;
         float m_ref = -INFINITY;  // reference maximum, scaled, log2 domain (identical in both threads of a row)
         float l_sum = 0.0f;       // this thread's half of the row sum
@@ -607,11 +629,16 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 mine = fmaxf(mine, fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])));
             }
             if (stamp) SDPA_TRACE(x, j, 2);
-            // trade the half-row maxima with the warp that owns the other 64 keys of these rows
-            float* slot = exchange + (((x * 2 + (j & 1)) * 4 + quadrant) * 2) * 32;
-            slot[half * 32 + lane] = mine;
+            // Trade the half-row maxima with the warp that owns the other 64 keys of these rows, as bf16 rounded towards
+            // +inf: any reference not below the true maximum by more than the threshold serves, and both threads must
+            // arrive at the same value, so each uses the rounded form of its own half too. (One buffer suffices: the second
+            // barrier of this iteration orders these reads before the next iteration's writes.)
+            const uint32_t mine_bits = __float_as_uint(mine);
+            const uint32_t mine_up = (mine_bits & 0x80000000u) ? (mine_bits & 0xffff0000u) : ((mine_bits + 0xffffu) & 0xffff0000u);
+            exchange[half * 32 + lane] = static_cast<uint16_t>(mine_up >> 16);
             asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
-            const float tile_max = fmaxf(mine, slot[(half ^ 1) * 32 + lane]) * scale;
+            const float other = __uint_as_float(static_cast<uint32_t>(exchange[(half ^ 1) * 32 + lane]) << 16);
+            const float tile_max = fmaxf(__uint_as_float(mine_up), other) * scale;
             // raise the reference only when it would grow by more than the threshold (or on the first tile)
             const bool raise = tile_max > m_ref + kRescaleThreshold;
             if (__any_sync(0xffffffffu, raise)) {
@@ -650,9 +677,15 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
                     const uint64_t v = fma2(pack2(__uint_as_float(raw[2 * e]), __uint_as_float(raw[2 * e + 1])), scale2, bias2);
-                    float x0, x1;
-                    unpack2(v, x0, x1);
-                    const float p0 = ex2_fast(x0), p1 = (e % kPolyEvery == 0) ? exp2_poly(x1) : ex2_fast(x1);
+                    float p0, p1;
+                    if (e % kPolyEvery == 0) {
+                        exp2_poly_pair(v, p0, p1);  // this pair on the FMA pipe
+                    } else {
+                        float x0, x1;
+                        unpack2(v, x0, x1);
+                        p0 = ex2_fast(x0);
+                        p1 = ex2_fast(x1);
+                    }
                     sums[e & 3] = add2(sums[e & 3], pack2(p0, p1));
                     __nv_bfloat162 two = __floats2bfloat162_rn(p0, p1);
                     packed[c * 16 + e] = *reinterpret_cast<uint32_t*>(&two);
@@ -677,10 +710,16 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         // last product done -> normalise, stage O in this tile's Q buffer (no product reads it any more), TMA store
         if (ok) ok = mbar_wait(o_full(x), 0, 230 + x);
         tc_fence_after();
-        float* sum_slot = sum_exchange + ((x * 4 + quadrant) * 2) * 32;
-        sum_slot[half * 32 + lane] = l_sum;
+        // row sum = this thread's half + the other thread's: two hand-overs through one f32 word per row
+        if (half == 1) sum_exchange[lane] = l_sum;
         asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
-        const float total = l_sum + sum_slot[(half ^ 1) * 32 + lane];
+        float total = l_sum;
+        if (half == 0) {
+            total += sum_exchange[lane];
+            sum_exchange[lane] = total;
+        }
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
+        if (half == 1) total = sum_exchange[lane];
         const float inverse = total > 0.0f ? 1.0f / total : 0.0f;
         uint8_t* o_row = generic_base + PairSmem::kQ + x * kTileBytes + half * kHalfBytes + row * 128;  // this thread's 64 output columns
 #pragma unroll 1
