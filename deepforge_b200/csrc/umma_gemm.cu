@@ -524,8 +524,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             for (int kb0 = 0; kb0 < args.k_blocks && ok; kb0 += (pargs.halo ? args.filter_s : G), ++it) {
                 if (leader && me == 0) CONV_TRACE(1, it, 0);
                 ok = mbar_wait_warp(full_bar(stage), phase, 114);
-                if (!ok) break;
-                tc_fence_after();
+                if (!ok) break;  // (the slot was filled by TMA: no tcgen05 fence needed before the products read it)
                 if (leader && me == 0) CONV_TRACE(1, it, 1);
                 const uint32_t a_lo = smem_desc_lo(ring_base + stage * pargs.slot_bytes, 16);
                 if (pargs.halo) {

@@ -243,8 +243,7 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             tc_fence_after();
             for (int kb = 0; kb < args.k_blocks && ok; ++kb) {
                 ok = mbar_wait_warp(full_bar(stage), phase, 403);
-                if (!ok) break;
-                tc_fence_after();
+                if (!ok) break;  // (operands by TMA, scales by generic stores + fence.proxy.async: no tcgen05 fence needed)
                 const uint32_t a_src = smem_base + stage * L::kStageBytes;
                 const uint32_t b_src = a_src + kABytes;
                 const uint32_t sf_tmem = tmem_u + 256 + (stage & 1) * 16;  // SFA at +0..3, SFB at +4..

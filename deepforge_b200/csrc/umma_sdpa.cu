@@ -505,9 +505,9 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         bool ok = mbar_wait_warp(q_full, 0, 222);
         int slot = 0;         // ring slot of the next K or V tile to consume
         uint32_t phase = 0;
+        // (no tcgen05 fence here: the slot was filled by TMA, not by tensor-memory traffic of other threads)
         auto wait_slot = [&](int code) {
             if (ok) ok = mbar_wait_warp(kv_full(slot), phase, code);
-            tc_fence_after();
         };
         auto next_slot = [&]() { if (++slot == kPairSlots) { slot = 0; phase ^= 1; } };
         auto commit = [&](uint32_t bar) { if (leader) umma_commit(bar); };
