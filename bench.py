@@ -14,7 +14,8 @@ host read of every output inside the timed region (upload, kernels and download 
 consecutive steps overlap on three streams); `roofline` is measured per kernel with CUDA
 events in a separate pass over the same plan; `cpu_baseline` times the CPU oracle (a port
 of the reference's algorithm: the reference binary needs LLVM/MLIR 22.1.8, absent here)
-on a bounded sample of the same workload, single-threaded like the reference.
+on a bounded sample of the same workload, single-threaded like the reference; the
+`--impl reference` arm runs one such sample per host thread side by side.
 
 Multi-GPU (torchrun, one rank per GPU): every rank runs the full per-GPU configuration on
 its own data (the path has no exchange step), so scaling is "weak"; --gather adds the NCCL
@@ -178,25 +179,40 @@ def time_cpu(name: str, budget_s: float = 12.0, max_runs: int = 5):
 
 
 def reference_arm(args) -> None:
-    """The reference's CPU implementation of the path (its restatement: the binary cannot be built here)."""
+    """The reference's CPU implementation of the path (its restatement: the binary cannot be built here), on all
+    the host cores this process may use. The reference itself is single-threaded; the sample is one independent
+    piece of the workload (an image strip, a block of rows, a few (batch, head) pairs), so T threads run T such
+    pieces side by side (the C library is called with the GIL released) and a step is one piece per thread."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    from concurrent.futures import ThreadPoolExecutor
     from deepforge_b200 import workloads
     wl = workloads.BUILDERS[args.workload]()
     description, run, units = cpu_sample(args.workload)
+    try:
+        threads = len(os.sched_getaffinity(0))
+    except AttributeError:
+        threads = os.cpu_count() or 1
+    threads = max(1, min(threads, args.ref_threads if args.ref_threads > 0 else threads))
+    pool = ThreadPoolExecutor(max_workers=threads)
+
+    def step():
+        for future in [pool.submit(run) for _ in range(threads)]:
+            future.result()
+
     for _ in range(max(args.warmup, 1)):
-        run()
+        step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        run()
+        step()
     elapsed = time.perf_counter() - t0
-    value = units * args.steps / elapsed
+    value = units * threads * args.steps / elapsed
     line = {
         "impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {**wl.description, "sample_per_step": description},
-        "cpu_baseline": {"value": value, "unit": wl.unit, "cores": 1, "kind": "port", "sample": description,
+        "config": {**wl.description, "sample_per_step": f"{threads} x ({description}), one per host thread"},
+        "cpu_baseline": {"value": value, "unit": wl.unit, "cores": threads, "kind": "port", "sample": f"{threads} x ({description})",
                          "note": "restatement of the reference algorithm; the reference is single-threaded and its binary needs LLVM/MLIR 22.1.8"},
         "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -339,6 +355,7 @@ def main() -> None:
     parser.add_argument("--gather", action="store_true", help="all-gather the outputs over NCCL inside the timed region")
     parser.add_argument("--no-also", action="store_true", help="skip the short runs of the other configurations")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    parser.add_argument("--ref-threads", type=int, default=0, help="host threads of the reference arm (0 = all this process may use)")
     args = parser.parse_args()
     if args.impl == "reference":
         reference_arm(args)
