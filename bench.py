@@ -128,13 +128,15 @@ class ClockSampler:
 
 # ---- CPU baseline: the oracle on a bounded sample of the workload ----------------------------
 
-def cpu_sample(name: str):
-    """Returns (sample description, callable running one pass, units of the metric it covers)."""
+def cpu_sample(name: str, fraction: float = 1.0):
+    """Returns (sample description, callable running one pass, units of the metric it covers). `fraction` < 1
+    shrinks the sample (fewer strip rows / matrix rows / query rows / tokens) for runs with many steps."""
     sys.path.insert(0, str(ROOT / "oracle"))
     import df_oracle_binding as oracle
     import graph_oracle
     from deepforge_b200 import workloads
     oracle.use_native()  # -O3 -march=native build, compiled on this host
+    fraction = min(1.0, max(fraction, 1e-3))
     if name in ("c1", "c1_nchw"):
         wl = workloads.BUILDERS[name]()
         x, w = wl.inputs[1](), wl.inputs[2]()
@@ -144,24 +146,32 @@ def cpu_sample(name: str):
         ins = {1: x, 2: w}
         return "full workload, generic strided path", (lambda: graph_oracle.run(wl.document, ins)), wl.flops / 1e12
     if name == "c2":
-        wl = workloads.c2(n=1, h=14, w=56)
+        rows = max(1, int(round(14 * fraction)))
+        wl = workloads.c2(n=1, h=rows, w=56)
         ins = {uid: graph_oracle.widen(make(), wl.tensor(uid)["data_type"]) for uid, make in wl.inputs.items()}
-        return "a 14x56 strip of one image, 1/128 of the batch (all three convolutions and the pointwise nodes), f32 twin of the DAG", (lambda: graph_oracle.run(wl.document, ins)), wl.flops / 1e12
+        return (f"a {rows}x56 strip of one image, 1/{32 * 56 // rows} of the batch (all three convolutions and the pointwise nodes), f32 twin of the DAG",
+                (lambda: graph_oracle.run(wl.document, ins)), wl.flops / 1e12)
     if name == "c3":
-        wl = workloads.c3(m=256, k=4096, n=256)
+        rows = max(32, int(round(256 * fraction)) // 32 * 32)
+        wl = workloads.c3(m=rows, k=4096, n=rows)
         ins = {uid: graph_oracle.widen(make(), "BFLOAT16") for uid, make in wl.inputs.items()}
         storage = {uid: make() for uid, make in wl.inputs.items()}
-        return "256 rows of A x 256 columns of B over the full K=4096 (quantize, dequantize, matmul)", (lambda: graph_oracle.run(wl.document, ins, storage_inputs=storage)), wl.flops / 1e12
+        return (f"{rows} rows of A x {rows} columns of B over the full K=4096 (quantize, dequantize, matmul)",
+                (lambda: graph_oracle.run(wl.document, ins, storage_inputs=storage)), wl.flops / 1e12)
     if name == "c4":
         wl = workloads.c4(b=1, h=1, s=2048)
         ins = {uid: graph_oracle.widen(make(), "BFLOAT16") for uid, make in wl.inputs.items()}
-        rows = 2048 // 32
-        flops = sum(4.0 * 128 * (q + 1) for q in range(0, 2048, 32))
-        return f"{rows} query rows (every 32nd) of one (batch, head) pair at S=2048", (lambda: graph_oracle.run(wl.document, ins, sdpa_q_step=32)), flops / 1e12
+        step = min(2048, max(32, int(round(32 / fraction))))
+        rows = len(range(0, 2048, step))
+        flops = sum(4.0 * 128 * (q + 1) for q in range(0, 2048, step))
+        return (f"{rows} query rows (every {step}th) of one (batch, head) pair at S=2048",
+                (lambda: graph_oracle.run(wl.document, ins, sdpa_q_step=step)), flops / 1e12)
     if name == "c5":
-        wl = workloads.c5(batch=2, hq=4, hkv=1, pages=256, max_len=8192, min_len=4096)
+        longest = max(512, int(round(8192 * fraction)) // 64 * 64)
+        wl = workloads.c5(batch=2, hq=4, hkv=1, pages=256, max_len=longest, min_len=max(256, longest // 2))
         ins = {uid: graph_oracle.widen(make(), wl.tensor(uid)["data_type"]) for uid, make in wl.inputs.items()}
-        return "2 sequences x 1 KV head (4 query heads) with lengths in [4096, 8192]", (lambda: graph_oracle.run(wl.document, ins)), wl.bytes / 1e9
+        return (f"2 sequences x 1 KV head (4 query heads) with lengths in [{max(256, longest // 2)}, {longest}]",
+                (lambda: graph_oracle.run(wl.document, ins)), wl.bytes / 1e9)
     raise KeyError(name)
 
 
@@ -190,6 +200,14 @@ def reference_arm(args) -> None:
     from deepforge_b200 import workloads
     wl = workloads.BUILDERS[args.workload]()
     description, run, units = cpu_sample(args.workload)
+    # keep the whole run (warm-up + steps) within about two and a half minutes: shrink the per-step sample when the
+    # caller asks for many steps (throughput, the reported value, does not depend on the sample size)
+    t0 = time.perf_counter()
+    run()
+    one = time.perf_counter() - t0
+    wanted = 150.0 / (max(args.warmup, 1) + args.steps)
+    if one * 1.5 > wanted:
+        description, run, units = cpu_sample(args.workload, fraction=wanted / (one * 1.5))
     try:
         threads = len(os.sched_getaffinity(0))
     except AttributeError:
