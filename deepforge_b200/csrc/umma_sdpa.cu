@@ -34,6 +34,11 @@ struct SdpaUmmaArgs {
     float scale_log2;  // attn_scale * log2(e)
     float* stats;      // [B, Hq, Sq] or null
     int64_t stats_batch_stride, stats_head_stride, stats_row_stride;
+    // Max and Sum_exp rows (two-tile kernel only), or null; element strides like Stats
+    float* row_max;
+    float* row_sum;
+    int64_t max_stride[3], sum_stride[3];
+    float attn_scale;  // natural-log units: Max = attn_scale * largest dot product
 };
 
 struct Smem {
@@ -598,6 +603,7 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const bool stamp = threadIdx.x == x * 256;
         float m_ref = -INFINITY;  // reference maximum, scaled, log2 domain (identical in both threads of a row)
         float l_sum = 0.0f;       // this thread's half of the row sum
+        float raw_max = -INFINITY;  // exact largest dot product among this thread's keys (for the Max / Sum_exp outputs)
         bool ok = true;
         for (int j = 0; j < my_tiles; ++j) {
             if (stamp) SDPA_TRACE(x, j, 0);
@@ -628,6 +634,7 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 }
                 mine = fmaxf(mine, fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])));
             }
+            raw_max = fmaxf(raw_max, mine);
             if (stamp) SDPA_TRACE(x, j, 2);
             // Trade the half-row maxima with the warp that owns the other 64 keys of these rows, as bf16 rounded towards
             // +inf: any reference not below the true maximum by more than the threshold serves, and both threads must
@@ -720,6 +727,22 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
         asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
         if (half == 1) total = sum_exchange[lane];
+        float row_raw_max = raw_max;
+        if (args.row_max != nullptr || args.row_sum != nullptr) {
+            // exact row maximum: the same two hand-overs with the f32 half-row maxima
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
+            if (half == 1) sum_exchange[lane] = raw_max;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
+            if (half == 0) {
+                row_raw_max = fmaxf(raw_max, sum_exchange[lane]);
+                const int64_t b64 = batch, h64 = head, q64 = q_index;
+                const bool any = total > 0.0f;
+                if (ok && args.row_max != nullptr)
+                    args.row_max[b64 * args.max_stride[0] + h64 * args.max_stride[1] + q64 * args.max_stride[2]] = any ? row_raw_max * args.attn_scale : -INFINITY;
+                if (ok && args.row_sum != nullptr)  // the sum was accumulated against m_ref; re-express it against the true maximum
+                    args.row_sum[b64 * args.sum_stride[0] + h64 * args.sum_stride[1] + q64 * args.sum_stride[2]] = any ? total * exp2f(m_ref - row_raw_max * scale) : 0.0f;
+            }
+        }
         const float inverse = total > 0.0f ? 1.0f / total : 0.0f;
         uint8_t* o_row = generic_base + PairSmem::kQ + x * kTileBytes + half * kHalfBytes + row * 128;  // this thread's 64 output columns
 #pragma unroll 1
@@ -776,7 +799,8 @@ bool sdpa_umma_supported(const dfgpu_sdpa_params& p) {
     if (p.q.rank != 4 || p.k.rank != 4 || p.v.rank != 4 || p.o.rank != 4) return false;
     if (p.q.dim[3] != kHeadDim || p.v.dim[3] != kHeadDim || p.k.dim[3] != kHeadDim) return false;
     if (p.page_table_k.rank || p.page_table_v.rank || p.padding_mask || p.has_left_bound || p.bottom_right) return false;
-    if (p.max.rank || p.sum_exp.rank) return false;
+    if ((p.max.rank || p.sum_exp.rank) && (p.q.dim[2] % (2 * kRows) != 0 || !(p.attn_scale > 0.0f) || !(p.attn_scale < INFINITY))) return false;  // only the two-tile kernel writes them
+    if ((p.max.rank && p.max.dtype != DFGPU_F32) || (p.sum_exp.rank && p.sum_exp.dtype != DFGPU_F32)) return false;
     if (!packed_bhsd(p.q) || !packed_bhsd(p.k) || !packed_bhsd(p.v) || !packed_bhsd(p.o)) return false;
     const int64_t sq = p.q.dim[2], skv = p.k.dim[2];
     if (p.s_kv != skv || p.v.dim[2] != skv || p.k.dim[1] != p.v.dim[1]) return false;
@@ -816,6 +840,13 @@ int launch_sdpa_umma(const dfgpu_sdpa_params& p, void* const* tensors, void* scr
         args.stats_batch_stride = p.stats.stride[0];
         args.stats_head_stride = p.stats.stride[1];
         args.stats_row_stride = p.stats.stride[2];
+    }
+    args.attn_scale = p.attn_scale;
+    args.row_max = p.max.rank ? static_cast<float*>(tensors[5]) : nullptr;
+    args.row_sum = p.sum_exp.rank ? static_cast<float*>(tensors[6]) : nullptr;
+    for (int i = 0; i < 3; ++i) {
+        args.max_stride[i] = p.max.rank ? p.max.stride[i] : 0;
+        args.sum_stride[i] = p.sum_exp.rank ? p.sum_exp.stride[i] : 0;
     }
     const bool pair_form = sq % (2 * kRows) == 0 && p.attn_scale > 0.0f && p.attn_scale < INFINITY;
     static bool configured = false;

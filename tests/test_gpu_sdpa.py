@@ -199,6 +199,21 @@ def test_umma_sdpa_matches_oracle(causal, batch, hq, hkv, seq):
     close_bf16(o, o_ref)
 
 
+@pytest.mark.parametrize("causal", [True, False])
+def test_umma_sdpa_max_and_sum_exp_rows(causal):
+    """Stats, Max and Sum_exp from the two-tile tcgen05 kernel: the kernel's running reference maximum is raised
+    lazily and exchanged in rounded form, so Max must come from the exact per-thread maxima and Sum_exp must be
+    re-expressed against it."""
+    flags = dict(has_right_bound=1, right_bound=0) if causal else {}
+    info, o, o_ref, rows, rows_ref = both(BF16, [1, 4, 512, 128], [1, 2, 512, 128], [1, 2, 512, 128], 512, 2.5 * 128 ** -0.5,
+                                          dfgpu.SDPA_UMMA, stats=True, seed=31, **flags)
+    assert info.kernel == dfgpu.SDPA_UMMA
+    close_bf16(o, o_ref)
+    close_f32(rows[0], rows_ref[0], 2e-3)  # Stats
+    close_f32(rows[1], rows_ref[1], 1e-5)  # Max: exact dot-product maximum times the scale
+    close_f32(rows[2], rows_ref[2], 2e-3)  # Sum_exp
+
+
 def test_umma_sdpa_stats_and_large_scores():
     """Stats = max + ln(sum) in natural log; a 4x larger scale makes the running maximum jump between
     tiles, which exercises the in-TMEM rescale of the output accumulator."""
