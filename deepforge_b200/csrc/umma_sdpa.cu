@@ -39,6 +39,9 @@ struct SdpaUmmaArgs {
     float* row_sum;
     int64_t max_stride[3], sum_stride[3];
     float attn_scale;  // natural-log units: Max = attn_scale * largest dot product
+    // two-tile kernel: batch * query heads, and O as a packed [B * Hq * Sq, 128] bf16 matrix (it stores rows directly)
+    int32_t batch_heads;
+    __nv_bfloat16* o;
 };
 
 struct Smem {
@@ -330,7 +333,7 @@ sdpa_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 // Cycle stamps of the first CTA's three roles (softmax A, softmax B, issuing lane), for tuning builds only.
 #ifdef DFGPU_SDPA_TRACE
 __device__ long long g_sdpa_trace[3][64][10];
-#define SDPA_TRACE(role, j, k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (j) < 64) g_sdpa_trace[role][j][k] = clock64(); } while (0)
+#define SDPA_TRACE(role, j, k) do { if (blockIdx.x == 0 && (j) < 64) g_sdpa_trace[role][j][k] = clock64(); } while (0)
 #else
 #define SDPA_TRACE(role, j, k) do {} while (0)
 #endif
@@ -349,8 +352,8 @@ struct PairSmem {
     // [lane] as f32. 1 KiB in all: with two Q tiles and five 32 KiB ring slots this is what the 227 KiB leave.
     static constexpr int kExchange = kRing + kPairSlots * kTileBytes;
     static constexpr int kBarriers = kExchange + 1024;
-    // q_full, kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2]
-    static constexpr int kBarrierCount = 1 + 2 * kPairSlots + 6;
+    // q_full, q_empty, kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2], o_empty[2]
+    static constexpr int kBarrierCount = 2 + 2 * kPairSlots + 8;
     static constexpr int kTotal = kBarriers + kBarrierCount * 8 + 16;
     static constexpr int kDynamic = kTotal + 1024;
 };
@@ -421,19 +424,121 @@ __device__ __forceinline__ void exp2_poly_pair(uint64_t x2, float& p0, float& p1
     p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
 }
 
+__device__ __forceinline__ void tmem_load_16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+// Wait for the tensor-memory loads in flight. The registers of the load that is about to be used pass through the
+// statement, so that nothing that reads them can be scheduled above the wait while a later load is already in flight.
+__device__ __forceinline__ void tmem_load_wait_for(uint32_t (&r)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :: "memory");
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// Largest of 16 scores folded into `running`: eight three-input maxima.
+__device__ __forceinline__ float max_of_16(const uint32_t (&raw)[16], float running) {
+    float part[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+        part[g] = max3(__uint_as_float(raw[4 * g]), __uint_as_float(raw[4 * g + 1]), max3(__uint_as_float(raw[4 * g + 2]), __uint_as_float(raw[4 * g + 3]), running));
+    return fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
+}
+// Sixteen scores -> probabilities 2^(s * scale + bias) as eight bf16 pairs, their sum added to two packed partial sums.
+__device__ __forceinline__ void probabilities_of_16(const uint32_t (&raw)[16], uint64_t scale2, uint64_t bias2, uint64_t (&sums)[2], uint32_t* packed) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const uint64_t v = fma2(pack2(__uint_as_float(raw[2 * e]), __uint_as_float(raw[2 * e + 1])), scale2, bias2);
+        float p0, p1;
+        if (e % kPolyEvery == 0) {
+            exp2_poly_pair(v, p0, p1);  // this pair on the FMA pipe
+        } else {
+            float x0, x1;
+            unpack2(v, x0, x1);
+            p0 = ex2_fast(x0);
+            p1 = ex2_fast(x1);
+        }
+        sums[e & 1] = add2(sums[e & 1], pack2(p0, p1));
+        __nv_bfloat162 two = __floats2bfloat162_rn(p0, p1);
+        packed[e] = *reinterpret_cast<uint32_t*>(&two);
+    }
+}
+
+// One (batch, head, query pair) of the two-tile kernel's work list.
+struct PairItem {
+    int batch, head;
+    int q_tile_a;        // index of the first of the two 128-row query tiles
+    int q_row_a;         // its first row in the [B * Hq * Sq, D] view of Q and O
+    int kv_row0;         // first row of this head in the [B * Hkv * Skv, D] view of K and V
+    int tiles_a, tiles_b;  // key tiles the two query tiles walk (causal: up to their diagonals)
+};
+
+__device__ __forceinline__ PairItem pair_item(const SdpaUmmaArgs& args, int bh, int pair) {
+    PairItem item;
+    item.batch = bh / args.heads_q;
+    item.head = bh - item.batch * args.heads_q;
+    const int kv_head = item.head / (args.heads_q / args.heads_kv);
+    item.q_tile_a = 2 * pair;
+    item.q_row_a = bh * args.seq_q + item.q_tile_a * kRows;
+    item.kv_row0 = (item.batch * args.heads_kv + kv_head) * args.seq_kv;
+    const int total_kv_tiles = args.seq_kv / kKeys;
+    item.tiles_a = args.causal ? min(total_kv_tiles, item.q_tile_a + 1) : total_kv_tiles;
+    item.tiles_b = args.causal ? min(total_kv_tiles, item.q_tile_a + 2) : total_kv_tiles;
+    return item;
+}
+
+// The work list of one CTA, the same in every warp role. A head's P query pairs form units: under a causal mask unit i
+// is the heavy pair P-1-i followed by the light pair i, so that every unit walks 2P+2 key tiles and equal numbers of
+// units are equal work; otherwise each pair is a unit. CTA c takes units c, c + gridDim.x, ...; neighbouring CTAs
+// thus work on the same head at the same time and share its K and V in L2. `body(bh, pair)` returns false to stop.
+template <class Body>
+__device__ __forceinline__ void for_each_pair_item(const SdpaUmmaArgs& args, Body&& body) {
+    const int pairs = args.q_tiles >> 1;
+    const int units_per_head = args.causal ? (pairs + 1) >> 1 : pairs;
+    const int units = units_per_head * args.batch_heads;
+    for (int k = 0;; ++k) {  // one call site of the body: it is a whole warp role
+        const int unit = static_cast<int>(blockIdx.x) + (k >> 1) * static_cast<int>(gridDim.x);
+        if (unit >= units) return;
+        const int bh = unit / units_per_head, i = unit - bh * units_per_head;
+        int pair = i;
+        if (args.causal) {
+            pair = (k & 1) ? i : pairs - 1 - i;
+            if ((k & 1) && 2 * i == pairs - 1) continue;  // the middle pair of an odd count stands alone
+        } else if (k & 1) {
+            continue;
+        }
+        if (!body(bh, pair)) return;
+    }
+}
+
+// Persistent form: one CTA per SM walks its work list, and the prologue of an item (Q and the first K/V tiles, the
+// first score products) runs under the tail of the previous one. 18 warps:
+//   warps 0-15  softmax, two threads per query row (8 warps per query tile); they also normalise O and store it
+//   warp 16     TMA producer: Q_A and Q_B of an item as soon as the previous item's last score product has read the
+//               old ones, then K_0, V_0, K_1, ... through a ring of 32 KiB slots that runs on across items
+//   warp 17     issues the products; one elected lane issues, all lanes walk the schedule
 __global__ void __launch_bounds__(kPairThreads, 1)
 sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o, SdpaUmmaArgs args) {
+                      const __grid_constant__ CUtensorMap map_v, SdpaUmmaArgs args) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar_base = smem_base + PairSmem::kBarriers;
-    const uint32_t q_full = bar_base;
-    auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
-    auto kv_empty = [&](int s) { return bar_base + 8u * (1 + kPairSlots + s); };
-    auto s_full = [&](int x) { return bar_base + 8u * (1 + 2 * kPairSlots + x); };
-    auto p_full = [&](int x) { return bar_base + 8u * (3 + 2 * kPairSlots + x); };
-    auto o_full = [&](int x) { return bar_base + 8u * (5 + 2 * kPairSlots + x); };
+    const uint32_t q_full = bar_base, q_empty = bar_base + 8u;
+    auto kv_full = [&](int s) { return bar_base + 8u * (2 + s); };
+    auto kv_empty = [&](int s) { return bar_base + 8u * (2 + kPairSlots + s); };
+    auto s_full = [&](int x) { return bar_base + 8u * (2 + 2 * kPairSlots + x); };
+    auto p_full = [&](int x) { return bar_base + 8u * (4 + 2 * kPairSlots + x); };
+    auto o_full = [&](int x) { return bar_base + 8u * (6 + 2 * kPairSlots + x); };
+    auto o_empty = [&](int x) { return bar_base + 8u * (8 + 2 * kPairSlots + x); };
     const uint32_t tmem_slot = bar_base + 8u * PairSmem::kBarrierCount;
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + PairSmem::kBarriers + 8 * PairSmem::kBarrierCount);
 
@@ -442,22 +547,8 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         prefetch_tensormap(&map_q);
         prefetch_tensormap(&map_k);
         prefetch_tensormap(&map_v);
-        prefetch_tensormap(&map_o);
-    }
-    const int pairs = args.q_tiles >> 1;
-    const int pair = pairs - 1 - static_cast<int>(blockIdx.x);  // heavy (late) causal pairs first
-    const int bh = blockIdx.y;
-    const int batch = bh / args.heads_q, head = bh - batch * args.heads_q;
-    const int kv_head = head / (args.heads_q / args.heads_kv);
-    const int q_tile_a = 2 * pair;
-    const int q_row_a = (batch * args.heads_q + head) * args.seq_q + q_tile_a * kRows;
-    const int kv_row0 = (batch * args.heads_kv + kv_head) * args.seq_kv;
-    const int total_kv_tiles = args.seq_kv / kKeys;
-    const int tiles_a = args.causal ? min(total_kv_tiles, q_tile_a + 1) : total_kv_tiles;
-    const int tiles_b = args.causal ? min(total_kv_tiles, q_tile_a + 2) : total_kv_tiles;
-
-    if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
+        mbar_init(q_empty, 1);
         for (int s = 0; s < kPairSlots; ++s) {
             mbar_init(kv_full(s), 1);
             mbar_init(kv_empty(s), 1);
@@ -466,6 +557,7 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             mbar_init(s_full(x), 1);
             mbar_init(p_full(x), 8);
             mbar_init(o_full(x), 1);
+            mbar_init(o_empty(x), 8);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -480,37 +572,49 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
     if (warp == 16) {
         const bool leader = elect_one();
-        if (leader) {
-            mbar_expect_tx(q_full, 2 * kTileBytes);
-            for (int x = 0; x < 2; ++x) {
-                tma_load_2d(smem_base + PairSmem::kQ + x * kTileBytes, &map_q, 0, q_row_a + x * kRows, q_full);
-                tma_load_2d(smem_base + PairSmem::kQ + x * kTileBytes + kHalfBytes, &map_q, 64, q_row_a + x * kRows, q_full);
-            }
-        }
         int slot = 0;
         uint32_t phase = 1;  // parity of the "slot is free" wait
-        for (int t = 0; t < 2 * tiles_b; ++t) {
-            if (!mbar_wait_warp(kv_empty(slot), phase, 221)) break;
-            const int row = kv_row0 + (t >> 1) * kKeys;
-            const uint32_t dst = smem_base + PairSmem::kRing + slot * kTileBytes;
+        uint32_t n = 0;      // items started
+        for_each_pair_item(args, [&](int bh, int pair) {
+            const PairItem item = pair_item(args, bh, pair);
+            // the Q buffers are free once the previous item's last score product has completed
+            if (!mbar_wait_warp(q_empty, (n & 1) ^ 1, 220)) return false;
             if (leader) {
-                const CUtensorMap* map = (t & 1) ? &map_v : &map_k;
-                mbar_expect_tx(kv_full(slot), kTileBytes);
-                tma_load_2d(dst, map, 0, row, kv_full(slot));
-                tma_load_2d(dst + kHalfBytes, map, 64, row, kv_full(slot));
+                mbar_expect_tx(q_full, 2 * kTileBytes);
+                for (int x = 0; x < 2; ++x) {
+                    tma_load_2d(smem_base + PairSmem::kQ + x * kTileBytes, &map_q, 0, item.q_row_a + x * kRows, q_full);
+                    tma_load_2d(smem_base + PairSmem::kQ + x * kTileBytes + kHalfBytes, &map_q, 64, item.q_row_a + x * kRows, q_full);
+                }
             }
-            if (++slot == kPairSlots) { slot = 0; phase ^= 1; }
-        }
+            for (int t = 0; t < 2 * item.tiles_b; ++t) {
+                if (!mbar_wait_warp(kv_empty(slot), phase, 221)) return false;
+                const int row = item.kv_row0 + (t >> 1) * kKeys;
+                const uint32_t dst = smem_base + PairSmem::kRing + slot * kTileBytes;
+                if (leader) {
+                    const CUtensorMap* map = (t & 1) ? &map_v : &map_k;
+                    mbar_expect_tx(kv_full(slot), kTileBytes);
+                    tma_load_2d(dst, map, 0, row, kv_full(slot));
+                    tma_load_2d(dst + kHalfBytes, map, 64, row, kv_full(slot));
+                }
+                if (++slot == kPairSlots) { slot = 0; phase ^= 1; }
+            }
+            ++n;
+            return true;
+        });
     } else if (warp == 17) {
         // All 32 lanes walk the schedule; the elected lane issues the products and their commits.
         const bool leader = elect_one();
         const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kKeys >> 3) << 17) | (static_cast<uint32_t>(kRows >> 4) << 24);
         const uint32_t idesc_pv = idesc_qk | (1u << 16);  // B = V read MN-major
         const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
-        bool ok = mbar_wait_warp(q_full, 0, 222);
+        bool ok = true;
         int slot = 0;         // ring slot of the next K or V tile to consume
         uint32_t phase = 0;
-        // (no tcgen05 fence here: the slot was filled by TMA, not by tensor-memory traffic of other threads)
+        uint32_t n = 0;       // items started
+        uint32_t p_count[2] = {0, 0};  // probability tiles consumed per query tile (parity of p_full)
+        uint32_t stamp_j = 0;
+        (void)stamp_j;
+        // (no tcgen05 fence after a slot wait: the slot was filled by TMA, not by tensor-memory traffic of other threads)
         auto wait_slot = [&](int code) {
             if (ok) ok = mbar_wait_warp(kv_full(slot), phase, code);
         };
@@ -530,8 +634,13 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 }
             }
         };
-        auto product = [&](int x, int j, int v_slot) {  // O_x += P_x V_j, P_x as bf16 pairs in the front 64 columns of S_x
-            if (ok) ok = mbar_wait_warp(p_full(x), j & 1, 223 + x);
+        // O_x += P_x V_j. P_x lies as bf16 pairs over the scores: keys 0..63 in columns 0..31 of S_x, keys 64..127 in columns
+        // 64..95 (each softmax thread overwrites columns that held its own scores only). The first product of an item
+        // overwrites O_x, which the softmax warps must have read out for the previous item.
+        auto product = [&](int x, int j, int v_slot) {
+            if (ok && j == 0) ok = mbar_wait_warp(o_empty(x), (n & 1) ^ 1, 218 + x);
+            if (ok) ok = mbar_wait_warp(p_full(x), p_count[x] & 1, 223 + x);
+            ++p_count[x];
             tc_fence_after();
             if (!ok) return;
             const uint32_t v_lo = smem_desc_lo(smem_base + PairSmem::kRing + v_slot * kTileBytes, kHalfBytes);
@@ -539,51 +648,60 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             if (leader) {
 #pragma unroll
                 for (int k = 0; k < kKeys / 16; ++k)
-                    umma_bf16_a_tmem(d_tmem, p_tmem + k * 8, desc_words(v_lo + ((k * 2048) >> 4), kDescHi), idesc_pv, (j | k) != 0 ? 1u : 0u);
+                    umma_bf16_a_tmem(d_tmem, p_tmem + (k >> 2) * 64 + (k & 3) * 8, desc_words(v_lo + ((k * 2048) >> 4), kDescHi), idesc_pv, (j | k) != 0 ? 1u : 0u);
             }
         };
-        wait_slot(225);
-        scores(0, slot);
-        commit(s_full(0));
-        scores(1, slot);
-        commit(s_full(1));
-        commit(kv_empty(slot));
-        next_slot();
-        for (int j = 0; j < tiles_b; ++j) {
-            if (leader) SDPA_TRACE(2, j, 0);
-            wait_slot(226);
-            const int v_slot = slot;
+        for_each_pair_item(args, [&](int bh, int pair) {
+            const PairItem item = pair_item(args, bh, pair);
+            const int tiles_a = item.tiles_a, tiles_b = item.tiles_b;
+            if (ok) ok = mbar_wait_warp(q_full, n & 1, 222);
+            wait_slot(225);
+            scores(0, slot);
+            commit(s_full(0));
+            scores(1, slot);
+            commit(s_full(1));
+            commit(kv_empty(slot));
+            if (tiles_b == 1) commit(q_empty);
             next_slot();
-            if (leader) SDPA_TRACE(2, j, 1);
-            if (j < tiles_a) {
-                product(0, j, v_slot);
-                if (j == tiles_a - 1) commit(o_full(0));
-            }
-            if (leader) SDPA_TRACE(2, j, 2);
-            const bool more = j + 1 < tiles_b;
-            int k_slot = 0;
-            if (more) {
-                wait_slot(227);
-                k_slot = slot;
+            for (int j = 0; j < tiles_b; ++j, ++stamp_j) {
+                if (leader) SDPA_TRACE(2, stamp_j, 0);
+                wait_slot(226);
+                const int v_slot = slot;
                 next_slot();
+                if (leader) SDPA_TRACE(2, stamp_j, 1);
+                if (j < tiles_a) {
+                    product(0, j, v_slot);
+                    if (j == tiles_a - 1) commit(o_full(0));
+                }
+                if (leader) SDPA_TRACE(2, stamp_j, 2);
+                const bool more = j + 1 < tiles_b;
+                int k_slot = 0;
+                if (more) {
+                    wait_slot(227);
+                    k_slot = slot;
+                    next_slot();
+                }
+                if (leader) SDPA_TRACE(2, stamp_j, 3);
+                if (j + 1 < tiles_a) {
+                    scores(0, k_slot);
+                    commit(s_full(0));
+                }
+                if (leader) SDPA_TRACE(2, stamp_j, 4);
+                product(1, j, v_slot);
+                if (leader) SDPA_TRACE(2, stamp_j, 5);
+                commit(kv_empty(v_slot));
+                if (more) {
+                    scores(1, k_slot);
+                    commit(s_full(1));
+                    commit(kv_empty(k_slot));
+                    if (j + 2 == tiles_b) commit(q_empty);  // the item's last read of Q_A and Q_B
+                }
+                if (leader) SDPA_TRACE(2, stamp_j, 6);
             }
-            if (leader) SDPA_TRACE(2, j, 3);
-            if (j + 1 < tiles_a) {
-                scores(0, k_slot);
-                commit(s_full(0));
-            }
-            if (leader) SDPA_TRACE(2, j, 4);
-            product(1, j, v_slot);
-            if (leader) SDPA_TRACE(2, j, 5);
-            commit(kv_empty(v_slot));
-            if (more) {
-                scores(1, k_slot);
-                commit(s_full(1));
-                commit(kv_empty(k_slot));
-            }
-            if (leader) SDPA_TRACE(2, j, 6);
-        }
-        commit(o_full(1));
+            commit(o_full(1));
+            ++n;
+            return ok;
+        });
     } else {
         const int sw = warp;
         const int x = sw >> 3;           // 0: tile A, 1: tile B
@@ -593,62 +711,74 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
         const uint32_t tmem_s = tmem_base + lane_base + x * 128;
         const uint32_t tmem_o = tmem_base + lane_base + 256 + x * 128 + half * 64;
-        const int q_tile = q_tile_a + x;
-        const int q_index = q_tile * kRows + row;
-        const int my_tiles = x ? tiles_b : tiles_a;
         const float scale = args.scale_log2;
         const int pair_barrier = 1 + x * 4 + quadrant;  // the 64 threads that share these 32 rows
         uint16_t* exchange = reinterpret_cast<uint16_t*>(generic_base + PairSmem::kExchange) + ((x * 4 + quadrant) * 2) * 32;  // [half][lane]
         float* sum_exchange = reinterpret_cast<float*>(generic_base + PairSmem::kExchange) + (x * 4 + quadrant) * 32;
-        const bool stamp = threadIdx.x == x * 256;
+        const bool stamp = blockIdx.x == 0 && (threadIdx.x & 255) == 0;
+        (void)stamp;
+        uint32_t n = 0;        // items started
+        uint32_t s_count = 0;  // score tiles consumed (parity of s_full)
+        bool ok = true;
+        for_each_pair_item(args, [&](int bh, int pair) {
+        const PairItem item = pair_item(args, bh, pair);
+        const int q_tile = item.q_tile_a + x;
+        const int q_index = q_tile * kRows + row;
+        const int my_tiles = x ? item.tiles_b : item.tiles_a;
         float m_ref = -INFINITY;  // reference maximum, scaled, log2 domain (identical in both threads of a row)
         float l_sum = 0.0f;       // this thread's half of the row sum
         float raw_max = -INFINITY;  // exact largest dot product among this thread's keys (for the Max / Sum_exp outputs)
-        bool ok = true;
-        for (int j = 0; j < my_tiles; ++j) {
-            if (stamp) SDPA_TRACE(x, j, 0);
-            if (ok) ok = mbar_wait(s_full(x), j & 1, 228 + x);
+        for (int j = 0; j < my_tiles; ++j, ++s_count) {
+            if (stamp) SDPA_TRACE(x, s_count, 0);
+            if (ok) ok = mbar_wait(s_full(x), s_count & 1, 228 + x);
             tc_fence_after();
-            if (stamp) SDPA_TRACE(x, j, 1);
-            // Two passes over this thread's 64 scores, 32 at a time (with 576 threads a thread has ~88 registers): the
-            // first finds the half-row maximum, the second reloads the scores and forms the probabilities.
+            if (stamp) SDPA_TRACE(x, s_count, 1);
+            // One pass over this thread's 64 scores, 16 at a time with the next load in flight: each chunk gives its part
+            // of the half-row maximum and, from the second key tile on, its probabilities against the reference maximum
+            // of the earlier tiles. Only a tile that raises the reference (rare after the first) is read a second time.
             const bool diagonal = args.causal && j == q_tile;
             const int limit = q_index - j * kKeys - half * 64;  // diagonal tile: keys 0..limit of this thread's 64 are visible
+            const bool speculative = j > 0;
+            const uint64_t scale2 = pack2(scale, scale);
+            uint64_t bias2 = pack2(-m_ref, -m_ref);
+            uint64_t sums[2] = {0, 0};  // two independent chains of packed partial sums
+            uint32_t packed[32];        // this thread's 64 probabilities as bf16 pairs
             float mine = -INFINITY;
+            {
+                uint32_t raw[4][16];
+                tmem_load_16(tmem_s + half * 64, raw[0]);
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t raw[32];
-                tmem_load_32(tmem_s + half * 64 + c * 32, raw);
-                tmem_load_wait();
-                if (diagonal) {
+                for (int c = 0; c < 4; ++c) {
+                    tmem_load_wait_for(raw[c]);
+                    if (c < 3) tmem_load_16(tmem_s + half * 64 + (c + 1) * 16, raw[c + 1]);
+                    if (diagonal) {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e)
-                        if (c * 32 + e > limit) raw[e] = 0xff800000u;  // -inf
+                        for (int e = 0; e < 16; ++e)
+                            if (c * 16 + e > limit) raw[c][e] = 0xff800000u;  // -inf
+                    }
+                    mine = max_of_16(raw[c], mine);
+                    if (speculative) probabilities_of_16(raw[c], scale2, bias2, sums, packed + c * 8);
                 }
-                float part[4];
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    part[g] = __uint_as_float(raw[g * 8]);
-#pragma unroll
-                    for (int e = 1; e < 8; ++e) part[g] = fmaxf(part[g], __uint_as_float(raw[g * 8 + e]));
-                }
-                mine = fmaxf(mine, fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])));
             }
             raw_max = fmaxf(raw_max, mine);
-            if (stamp) SDPA_TRACE(x, j, 2);
+            if (stamp) SDPA_TRACE(x, s_count, 2);
             // Trade the half-row maxima with the warp that owns the other 64 keys of these rows, as bf16 rounded towards
             // +inf: any reference not below the true maximum by more than the threshold serves, and both threads must
-            // arrive at the same value, so each uses the rounded form of its own half too. (One buffer suffices: the second
-            // barrier of this iteration orders these reads before the next iteration's writes.)
+            // arrive at the same value, so each uses the rounded form of its own half too. (One buffer suffices: the next
+            // scores of this tile, which precede the next write, need the probabilities of all eight warps, and a warp
+            // hands those over after this read.)
             const uint32_t mine_bits = __float_as_uint(mine);
             const uint32_t mine_up = (mine_bits & 0x80000000u) ? (mine_bits & 0xffff0000u) : ((mine_bits + 0xffffu) & 0xffff0000u);
             exchange[half * 32 + lane] = static_cast<uint16_t>(mine_up >> 16);
             asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
             const float other = __uint_as_float(static_cast<uint32_t>(exchange[(half ^ 1) * 32 + lane]) << 16);
             const float tile_max = fmaxf(__uint_as_float(mine_up), other) * scale;
-            // raise the reference only when it would grow by more than the threshold (or on the first tile)
+            // raise the reference only when it would grow by more than the threshold (or on the first tile); the two
+            // warps of these rows see the same maxima, so they take the same branches
             const bool raise = tile_max > m_ref + kRescaleThreshold;
+            bool again = !speculative;
             if (__any_sync(0xffffffffu, raise)) {
+                again = true;
                 const float m_new = fmaxf(m_ref, tile_max);
                 const float alpha = m_ref == -INFINITY ? 0.0f : ex2_fast(m_ref - m_new);
                 l_sum *= alpha;
@@ -667,55 +797,40 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     }
                 }
             }
-            if (stamp) SDPA_TRACE(x, j, 3);
-            const uint64_t scale2 = pack2(scale, scale), bias2 = pack2(-m_ref, -m_ref);
-            uint64_t sums[4] = {0, 0, 0, 0};  // four independent chains of packed partial sums
-            uint32_t packed[32];              // this thread's 64 probabilities as bf16 pairs
+            if (stamp) SDPA_TRACE(x, s_count, 3);
+            if (again) {
+                // the scores are still in place (no probabilities stored yet): form them against the new reference
+                bias2 = pack2(-m_ref, -m_ref);
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t raw[32];
-                tmem_load_32(tmem_s + half * 64 + c * 32, raw);
-                tmem_load_wait();
-                if (diagonal) {
+                for (int g = 0; g < 2; ++g) sums[g] = 0;
 #pragma unroll
-                    for (int e = 0; e < 32; ++e)
-                        if (c * 32 + e > limit) raw[e] = 0xff800000u;
-                }
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t raw[16];
+                    tmem_load_16(tmem_s + half * 64 + c * 16, raw);
+                    tmem_load_wait_for(raw);
+                    if (diagonal) {
 #pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    const uint64_t v = fma2(pack2(__uint_as_float(raw[2 * e]), __uint_as_float(raw[2 * e + 1])), scale2, bias2);
-                    float p0, p1;
-                    if (e % kPolyEvery == 0) {
-                        exp2_poly_pair(v, p0, p1);  // this pair on the FMA pipe
-                    } else {
-                        float x0, x1;
-                        unpack2(v, x0, x1);
-                        p0 = ex2_fast(x0);
-                        p1 = ex2_fast(x1);
+                        for (int e = 0; e < 16; ++e)
+                            if (c * 16 + e > limit) raw[e] = 0xff800000u;
                     }
-                    sums[e & 3] = add2(sums[e & 3], pack2(p0, p1));
-                    __nv_bfloat162 two = __floats2bfloat162_rn(p0, p1);
-                    packed[c * 16 + e] = *reinterpret_cast<uint32_t*>(&two);
+                    probabilities_of_16(raw, scale2, bias2, sums, packed + c * 8);
                 }
             }
-            // The probabilities of keys 64..127 land on columns that hold scores of keys 32..63: both threads of a
-            // row must have finished re-reading their scores before either stores.
-            asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
-            tmem_store_32(tmem_s + half * 32, packed);
+            tmem_store_32(tmem_s + half * 64, packed);
             {
                 float lo, hi;
-                unpack2(add2(add2(sums[0], sums[1]), add2(sums[2], sums[3])), lo, hi);
+                unpack2(add2(sums[0], sums[1]), lo, hi);
                 l_sum += lo + hi;
             }
-            if (stamp) SDPA_TRACE(x, j, 4);
+            if (stamp) SDPA_TRACE(x, s_count, 4);
             tmem_store_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full(x));
-            if (stamp) SDPA_TRACE(x, j, 5);
+            if (stamp) SDPA_TRACE(x, s_count, 5);
         }
-        // last product done -> normalise, stage O in this tile's Q buffer (no product reads it any more), TMA store
-        if (ok) ok = mbar_wait(o_full(x), 0, 230 + x);
+        // last product done -> read O out of tensor memory (which frees it for the next item), normalise, store
+        if (ok) ok = mbar_wait(o_full(x), n & 1, 230 + x);
         tc_fence_after();
         // row sum = this thread's half + the other thread's: two hand-overs through one f32 word per row
         if (half == 1) sum_exchange[lane] = l_sum;
@@ -727,15 +842,14 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
         asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
         if (half == 1) total = sum_exchange[lane];
-        float row_raw_max = raw_max;
         if (args.row_max != nullptr || args.row_sum != nullptr) {
             // exact row maximum: the same two hand-overs with the f32 half-row maxima
             asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
             if (half == 1) sum_exchange[lane] = raw_max;
             asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
             if (half == 0) {
-                row_raw_max = fmaxf(raw_max, sum_exchange[lane]);
-                const int64_t b64 = batch, h64 = head, q64 = q_index;
+                const float row_raw_max = fmaxf(raw_max, sum_exchange[lane]);
+                const int64_t b64 = item.batch, h64 = item.head, q64 = q_index;
                 const bool any = total > 0.0f;
                 if (ok && args.row_max != nullptr)
                     args.row_max[b64 * args.max_stride[0] + h64 * args.max_stride[1] + q64 * args.max_stride[2]] = any ? row_raw_max * args.attn_scale : -INFINITY;
@@ -743,13 +857,22 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     args.row_sum[b64 * args.sum_stride[0] + h64 * args.sum_stride[1] + q64 * args.sum_stride[2]] = any ? total * exp2f(m_ref - row_raw_max * scale) : 0.0f;
             }
         }
+        // the hand-over words double as the next item's maxima: every read above must precede those writes
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
         const float inverse = total > 0.0f ? 1.0f / total : 0.0f;
-        uint8_t* o_row = generic_base + PairSmem::kQ + x * kTileBytes + half * kHalfBytes + row * 128;  // this thread's 64 output columns
+        // this thread's 64 output columns: 128 contiguous bytes of the row
+        uint4* o_row = reinterpret_cast<uint4*>(args.o + (static_cast<int64_t>(item.q_row_a + x * kRows + row) * kHeadDim + half * 64));
+        const bool store = ok && g_device_status == 0;
 #pragma unroll 1
         for (int c = 0; c < 2; ++c) {
             uint32_t acc[32];
             tmem_load_32(tmem_o + c * 32, acc);
             tmem_load_wait();
+            if (c == 1) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(o_empty(x));
+            }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 uint32_t w[4];
@@ -758,25 +881,15 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     __nv_bfloat162 two = __floats2bfloat162_rn(__uint_as_float(acc[u * 8 + 2 * t]) * inverse, __uint_as_float(acc[u * 8 + 2 * t + 1]) * inverse);
                     w[t] = *reinterpret_cast<uint32_t*>(&two);
                 }
-                const int unit = c * 4 + u;  // 16-byte unit inside this thread's 128 bytes of the output row
-                *reinterpret_cast<uint4*>(o_row + ((unit ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                if (store) o_row[c * 4 + u] = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
         if (args.stats != nullptr && ok && half == 0)
-            args.stats[batch * args.stats_batch_stride + head * args.stats_head_stride + static_cast<int64_t>(q_index) * args.stats_row_stride] =
+            args.stats[item.batch * args.stats_batch_stride + item.head * args.stats_head_stride + static_cast<int64_t>(q_index) * args.stats_row_stride] =
                 total > 0.0f ? 0.6931471805599453f * (m_ref + log2f(total)) : -INFINITY;
-        tc_fence_before();
-        fence_async_shared();
-        if (x == 0) asm volatile("bar.sync 9, 256;" ::: "memory");
-        else asm volatile("bar.sync 10, 256;" ::: "memory");
-        if ((sw & 7) == 0 && lane == 0) {
-            if (ok && g_device_status == 0) {
-                tma_store_2d(&map_o, smem_base + PairSmem::kQ + x * kTileBytes, 0, q_row_a + x * kRows);
-                tma_store_2d(&map_o, smem_base + PairSmem::kQ + x * kTileBytes + kHalfBytes, 64, q_row_a + x * kRows);
-            }
-            tma_store_commit();
-            tma_store_wait_all();
-        }
+        ++n;
+        return true;  // also after a wait gave up: the two warps of a row pair must meet at the same barriers to the end
+        });
     }
 
     tc_fence_before();
@@ -857,8 +970,21 @@ int launch_sdpa_umma(const dfgpu_sdpa_params& p, void* const* tensors, void* scr
         configured = true;
     }
     if (pair_form) {
-        dim3 grid(static_cast<unsigned>(args.q_tiles / 2), static_cast<unsigned>(batch * hq));
-        sdpa_umma_pair_kernel<<<grid, kPairThreads, PairSmem::kDynamic, stream>>>(map_q, map_k, map_v, map_o, args);
+        // persistent: one CTA per SM over the work list (see for_each_pair_item)
+        static int sm_count = 0;
+        if (sm_count == 0) {
+            int device = 0;
+            if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0) {
+                sm_count = 0;
+                return fail(kExecutionFailed, "SDPA: cannot read the number of multiprocessors");
+            }
+        }
+        const int pairs = args.q_tiles / 2;
+        const int64_t units = static_cast<int64_t>(args.causal ? (pairs + 1) / 2 : pairs) * batch * hq;
+        args.batch_heads = static_cast<int>(batch * hq);
+        args.o = static_cast<__nv_bfloat16*>(tensors[3]);
+        const unsigned grid = static_cast<unsigned>(units < sm_count ? units : sm_count);
+        sdpa_umma_pair_kernel<<<grid, kPairThreads, PairSmem::kDynamic, stream>>>(map_q, map_k, map_v, args);
         return check_launch("SDPA (tcgen05, two query tiles per CTA)");
     }
     dim3 grid(static_cast<unsigned>(args.q_tiles), static_cast<unsigned>(batch * hq));

@@ -188,7 +188,7 @@ def _device_healthy():
 
 
 @pytest.mark.parametrize("causal", [True, False])
-@pytest.mark.parametrize("batch,hq,hkv,seq", [(1, 2, 2, 128), (2, 4, 2, 384), (1, 8, 1, 640), (1, 4, 2, 256), (2, 2, 1, 768)])
+@pytest.mark.parametrize("batch,hq,hkv,seq", [(1, 2, 2, 128), (2, 4, 2, 384), (1, 8, 1, 640), (1, 4, 2, 256), (2, 2, 1, 768), (2, 80, 20, 512)])
 def test_umma_sdpa_matches_oracle(causal, batch, hq, hkv, seq):
     """Sequence lengths that are a multiple of 256 take the form with two query tiles per CTA
     (probabilities kept in tensor memory), the others one tile per CTA."""
