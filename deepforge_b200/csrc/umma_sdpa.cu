@@ -39,9 +39,7 @@ struct SdpaUmmaArgs {
     float* row_sum;
     int64_t max_stride[3], sum_stride[3];
     float attn_scale;  // natural-log units: Max = attn_scale * largest dot product
-    // two-tile kernel: batch * query heads, and O as a packed [B * Hq * Sq, 128] bf16 matrix (it stores rows directly)
-    int32_t batch_heads;
-    __nv_bfloat16* o;
+    int32_t batch_heads;  // two-tile kernel: batch * query heads
 };
 
 struct Smem {
@@ -338,22 +336,23 @@ __device__ long long g_sdpa_trace[3][64][10];
 #define SDPA_TRACE(role, j, k) do {} while (0)
 #endif
 
-constexpr int kPairSlots = 5;
+constexpr int kPairSlots = 4;
 #ifndef DFGPU_SDPA_POLY_EVERY
 #define DFGPU_SDPA_POLY_EVERY 4
 #endif
 constexpr int kPolyEvery = DFGPU_SDPA_POLY_EVERY;  // one pair of exponentials in kPolyEvery goes to the FMA pipe
-constexpr int kPairThreads = 576;  // loader warp, issuing warp, 2 x 8 softmax warps (two threads per query row)
+constexpr int kPairThreads = 608;  // 2 x 8 softmax warps (two threads per query row), loader, issuer and output-store warps
 
 struct PairSmem {
-    static constexpr int kQ = 0;                       // Q_A, Q_B; later the output staging tiles
+    static constexpr int kQ = 0;                       // Q_A, Q_B
     static constexpr int kRing = 2 * kTileBytes;
+    static constexpr int kStage = kRing + kPairSlots * kTileBytes;  // one output tile on its way to global memory
     // 128 bytes per (tile, lane quarter): during the key loop the half-row maxima [half][lane] as bf16, after it the row sum
-    // [lane] as f32. 1 KiB in all: with two Q tiles and five 32 KiB ring slots this is what the 227 KiB leave.
-    static constexpr int kExchange = kRing + kPairSlots * kTileBytes;
+    // [lane] as f32. 1 KiB in all: with two Q tiles, four 32 KiB ring slots and the output tile this is what the 227 KiB leave.
+    static constexpr int kExchange = kStage + kTileBytes;
     static constexpr int kBarriers = kExchange + 1024;
-    // q_full, q_empty, kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2], o_empty[2]
-    static constexpr int kBarrierCount = 2 + 2 * kPairSlots + 8;
+    // q_full, q_empty, stage_free, kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2], o_empty[2], staged[2]
+    static constexpr int kBarrierCount = 3 + 2 * kPairSlots + 10;
     static constexpr int kTotal = kBarriers + kBarrierCount * 8 + 16;
     static constexpr int kDynamic = kTotal + 1024;
 };
@@ -520,25 +519,28 @@ __device__ __forceinline__ void for_each_pair_item(const SdpaUmmaArgs& args, Bod
 }
 
 // Persistent form: one CTA per SM walks its work list, and the prologue of an item (Q and the first K/V tiles, the
-// first score products) runs under the tail of the previous one. 18 warps:
-//   warps 0-15  softmax, two threads per query row (8 warps per query tile); they also normalise O and store it
+// first score products) runs under the tail of the previous one. 19 warps:
+//   warps 0-15  softmax, two threads per query row (8 warps per query tile); they also normalise O into a staging tile
 //   warp 16     TMA producer: Q_A and Q_B of an item as soon as the previous item's last score product has read the
 //               old ones, then K_0, V_0, K_1, ... through a ring of 32 KiB slots that runs on across items
 //   warp 17     issues the products; one elected lane issues, all lanes walk the schedule
+//   warp 18     sends staged output tiles to global memory by TMA (row-per-thread global stores of 16 bytes at a
+//               256-byte stride kept the load/store unit busy for ~5000 cycles per tile)
 __global__ void __launch_bounds__(kPairThreads, 1)
 sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                      const __grid_constant__ CUtensorMap map_v, SdpaUmmaArgs args) {
+                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o, SdpaUmmaArgs args) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar_base = smem_base + PairSmem::kBarriers;
-    const uint32_t q_full = bar_base, q_empty = bar_base + 8u;
-    auto kv_full = [&](int s) { return bar_base + 8u * (2 + s); };
-    auto kv_empty = [&](int s) { return bar_base + 8u * (2 + kPairSlots + s); };
-    auto s_full = [&](int x) { return bar_base + 8u * (2 + 2 * kPairSlots + x); };
-    auto p_full = [&](int x) { return bar_base + 8u * (4 + 2 * kPairSlots + x); };
-    auto o_full = [&](int x) { return bar_base + 8u * (6 + 2 * kPairSlots + x); };
-    auto o_empty = [&](int x) { return bar_base + 8u * (8 + 2 * kPairSlots + x); };
+    const uint32_t q_full = bar_base, q_empty = bar_base + 8u, stage_free = bar_base + 16u;
+    auto kv_full = [&](int s) { return bar_base + 8u * (3 + s); };
+    auto kv_empty = [&](int s) { return bar_base + 8u * (3 + kPairSlots + s); };
+    auto s_full = [&](int x) { return bar_base + 8u * (3 + 2 * kPairSlots + x); };
+    auto p_full = [&](int x) { return bar_base + 8u * (5 + 2 * kPairSlots + x); };
+    auto o_full = [&](int x) { return bar_base + 8u * (7 + 2 * kPairSlots + x); };
+    auto o_empty = [&](int x) { return bar_base + 8u * (9 + 2 * kPairSlots + x); };
+    auto staged = [&](int x) { return bar_base + 8u * (11 + 2 * kPairSlots + x); };
     const uint32_t tmem_slot = bar_base + 8u * PairSmem::kBarrierCount;
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + PairSmem::kBarriers + 8 * PairSmem::kBarrierCount);
 
@@ -547,8 +549,10 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         prefetch_tensormap(&map_q);
         prefetch_tensormap(&map_k);
         prefetch_tensormap(&map_v);
+        prefetch_tensormap(&map_o);
         mbar_init(q_full, 1);
         mbar_init(q_empty, 1);
+        mbar_init(stage_free, 1);
         for (int s = 0; s < kPairSlots; ++s) {
             mbar_init(kv_full(s), 1);
             mbar_init(kv_empty(s), 1);
@@ -558,6 +562,7 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             mbar_init(p_full(x), 8);
             mbar_init(o_full(x), 1);
             mbar_init(o_empty(x), 8);
+            mbar_init(staged(x), 8);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -702,6 +707,31 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             ++n;
             return ok;
         });
+    } else if (warp == 18) {
+        // Output stores: a query tile's softmax warps leave the normalised tile in the staging buffer; this warp sends it
+        // off and hands the buffer to the next tile once the copy engine has read it.
+        const bool leader = elect_one();
+        uint32_t n = 0;
+        bool ok = true;
+        for_each_pair_item(args, [&](int bh, int pair) {
+            const PairItem item = pair_item(args, bh, pair);
+            for (int x = 0; x < 2; ++x) {
+                if (ok) ok = mbar_wait_warp(staged(x), n & 1, 216 + x);
+                if (leader) {
+                    if (ok && g_device_status == 0) {
+                        tma_store_2d(&map_o, smem_base + PairSmem::kStage, 0, item.q_row_a + x * kRows);
+                        tma_store_2d(&map_o, smem_base + PairSmem::kStage + kHalfBytes, 64, item.q_row_a + x * kRows);
+                    }
+                    tma_store_commit();
+                    tma_store_wait_read<0>();
+                    mbar_arrive(stage_free);
+                }
+                __syncwarp();
+            }
+            ++n;
+            return true;
+        });
+        if (leader) tma_store_wait_all();
     } else {
         const int sw = warp;
         const int x = sw >> 3;           // 0: tile A, 1: tile B
@@ -832,6 +862,7 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         // last product done -> read O out of tensor memory (which frees it for the next item), normalise, store
         if (ok) ok = mbar_wait(o_full(x), n & 1, 230 + x);
         tc_fence_after();
+        if (stamp) SDPA_TRACE(x, s_count - 1, 6);
         // row sum = this thread's half + the other thread's: two hand-overs through one f32 word per row
         if (half == 1) sum_exchange[lane] = l_sum;
         asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
@@ -859,10 +890,14 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
         // the hand-over words double as the next item's maxima: every read above must precede those writes
         asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
+        if (stamp) SDPA_TRACE(x, s_count - 1, 7);
         const float inverse = total > 0.0f ? 1.0f / total : 0.0f;
-        // this thread's 64 output columns: 128 contiguous bytes of the row
-        uint4* o_row = reinterpret_cast<uint4*>(args.o + (static_cast<int64_t>(item.q_row_a + x * kRows + row) * kHeadDim + half * 64));
-        const bool store = ok && g_device_status == 0;
+        // the staging tile serves the query tiles in turn: A, B, the next item's A, ...
+        {
+            const uint32_t turn = 2 * n + x;
+            if (ok) ok = mbar_wait(stage_free, (turn & 1) ^ 1, 232 + x);
+        }
+        uint8_t* o_row = generic_base + PairSmem::kStage + half * kHalfBytes + row * 128;  // this thread's 64 output columns
 #pragma unroll 1
         for (int c = 0; c < 2; ++c) {
             uint32_t acc[32];
@@ -881,9 +916,14 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     __nv_bfloat162 two = __floats2bfloat162_rn(__uint_as_float(acc[u * 8 + 2 * t]) * inverse, __uint_as_float(acc[u * 8 + 2 * t + 1]) * inverse);
                     w[t] = *reinterpret_cast<uint32_t*>(&two);
                 }
-                if (store) o_row[c * 4 + u] = make_uint4(w[0], w[1], w[2], w[3]);
+                const int unit = c * 4 + u;  // 16-byte unit inside this thread's 128 bytes of the output row
+                *reinterpret_cast<uint4*>(o_row + ((unit ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
+        fence_async_shared();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(staged(x));
+        if (stamp) SDPA_TRACE(x, s_count - 1, 8);
         if (args.stats != nullptr && ok && half == 0)
             args.stats[item.batch * args.stats_batch_stride + item.head * args.stats_head_stride + static_cast<int64_t>(q_index) * args.stats_row_stride] =
                 total > 0.0f ? 0.6931471805599453f * (m_ref + log2f(total)) : -INFINITY;
@@ -982,9 +1022,8 @@ int launch_sdpa_umma(const dfgpu_sdpa_params& p, void* const* tensors, void* scr
         const int pairs = args.q_tiles / 2;
         const int64_t units = static_cast<int64_t>(args.causal ? (pairs + 1) / 2 : pairs) * batch * hq;
         args.batch_heads = static_cast<int>(batch * hq);
-        args.o = static_cast<__nv_bfloat16*>(tensors[3]);
         const unsigned grid = static_cast<unsigned>(units < sm_count ? units : sm_count);
-        sdpa_umma_pair_kernel<<<grid, kPairThreads, PairSmem::kDynamic, stream>>>(map_q, map_k, map_v, args);
+        sdpa_umma_pair_kernel<<<grid, kPairThreads, PairSmem::kDynamic, stream>>>(map_q, map_k, map_v, map_o, args);
         return check_launch("SDPA (tcgen05, two query tiles per CTA)");
     }
     dim3 grid(static_cast<unsigned>(args.q_tiles), static_cast<unsigned>(batch * hq));
