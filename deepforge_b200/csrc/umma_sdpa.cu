@@ -351,8 +351,8 @@ struct PairSmem {
     // [lane] as f32. 1 KiB in all: with two Q tiles, four 32 KiB ring slots and the output tile this is what the 227 KiB leave.
     static constexpr int kExchange = kStage + kTileBytes;
     static constexpr int kBarriers = kExchange + 1024;
-    // q_full, q_empty, stage_free, kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2], o_empty[2], staged[2]
-    static constexpr int kBarrierCount = 3 + 2 * kPairSlots + 10;
+    // stage_free, q_full[2], q_empty[2], kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2], o_empty[2], staged[2]
+    static constexpr int kBarrierCount = 5 + 2 * kPairSlots + 10;
     static constexpr int kTotal = kBarriers + kBarrierCount * 8 + 16;
     static constexpr int kDynamic = kTotal + 1024;
 };
@@ -498,24 +498,35 @@ __device__ __forceinline__ PairItem pair_item(const SdpaUmmaArgs& args, int bh, 
 // is the heavy pair P-1-i followed by the light pair i, so that every unit walks 2P+2 key tiles and equal numbers of
 // units are equal work; otherwise each pair is a unit. CTA c takes units c, c + gridDim.x, ...; neighbouring CTAs
 // thus work on the same head at the same time and share its K and V in L2. `body(bh, pair)` returns false to stop.
+struct PairWalker {
+    int k = 0;
+    __device__ __forceinline__ bool next(const SdpaUmmaArgs& args, int& bh, int& pair) {
+        const int pairs = args.q_tiles >> 1;
+        const int units_per_head = args.causal ? (pairs + 1) >> 1 : pairs;
+        const int units = units_per_head * args.batch_heads;
+        for (;; ++k) {
+            const int unit = static_cast<int>(blockIdx.x) + (k >> 1) * static_cast<int>(gridDim.x);
+            if (unit >= units) return false;
+            bh = unit / units_per_head;
+            const int i = unit - bh * units_per_head;
+            pair = i;
+            if (args.causal) {
+                pair = (k & 1) ? i : pairs - 1 - i;
+                if ((k & 1) && 2 * i == pairs - 1) continue;  // the middle pair of an odd count stands alone
+            } else if (k & 1) {
+                continue;
+            }
+            ++k;
+            return true;
+        }
+    }
+};
 template <class Body>
 __device__ __forceinline__ void for_each_pair_item(const SdpaUmmaArgs& args, Body&& body) {
-    const int pairs = args.q_tiles >> 1;
-    const int units_per_head = args.causal ? (pairs + 1) >> 1 : pairs;
-    const int units = units_per_head * args.batch_heads;
-    for (int k = 0;; ++k) {  // one call site of the body: it is a whole warp role
-        const int unit = static_cast<int>(blockIdx.x) + (k >> 1) * static_cast<int>(gridDim.x);
-        if (unit >= units) return;
-        const int bh = unit / units_per_head, i = unit - bh * units_per_head;
-        int pair = i;
-        if (args.causal) {
-            pair = (k & 1) ? i : pairs - 1 - i;
-            if ((k & 1) && 2 * i == pairs - 1) continue;  // the middle pair of an odd count stands alone
-        } else if (k & 1) {
-            continue;
-        }
+    PairWalker walker;
+    int bh, pair;
+    while (walker.next(args, bh, pair))  // one call site of the body: it is a whole warp role
         if (!body(bh, pair)) return;
-    }
 }
 
 // Persistent form: one CTA per SM walks its work list, and the prologue of an item (Q and the first K/V tiles, the
@@ -533,14 +544,16 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar_base = smem_base + PairSmem::kBarriers;
-    const uint32_t q_full = bar_base, q_empty = bar_base + 8u, stage_free = bar_base + 16u;
-    auto kv_full = [&](int s) { return bar_base + 8u * (3 + s); };
-    auto kv_empty = [&](int s) { return bar_base + 8u * (3 + kPairSlots + s); };
-    auto s_full = [&](int x) { return bar_base + 8u * (3 + 2 * kPairSlots + x); };
-    auto p_full = [&](int x) { return bar_base + 8u * (5 + 2 * kPairSlots + x); };
-    auto o_full = [&](int x) { return bar_base + 8u * (7 + 2 * kPairSlots + x); };
-    auto o_empty = [&](int x) { return bar_base + 8u * (9 + 2 * kPairSlots + x); };
-    auto staged = [&](int x) { return bar_base + 8u * (11 + 2 * kPairSlots + x); };
+    const uint32_t stage_free = bar_base;
+    auto q_full = [&](int x) { return bar_base + 8u * (1 + x); };
+    auto q_empty = [&](int x) { return bar_base + 8u * (3 + x); };
+    auto kv_full = [&](int s) { return bar_base + 8u * (5 + s); };
+    auto kv_empty = [&](int s) { return bar_base + 8u * (5 + kPairSlots + s); };
+    auto s_full = [&](int x) { return bar_base + 8u * (5 + 2 * kPairSlots + x); };
+    auto p_full = [&](int x) { return bar_base + 8u * (7 + 2 * kPairSlots + x); };
+    auto o_full = [&](int x) { return bar_base + 8u * (9 + 2 * kPairSlots + x); };
+    auto o_empty = [&](int x) { return bar_base + 8u * (11 + 2 * kPairSlots + x); };
+    auto staged = [&](int x) { return bar_base + 8u * (13 + 2 * kPairSlots + x); };
     const uint32_t tmem_slot = bar_base + 8u * PairSmem::kBarrierCount;
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + PairSmem::kBarriers + 8 * PairSmem::kBarrierCount);
 
@@ -550,8 +563,6 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         prefetch_tensormap(&map_k);
         prefetch_tensormap(&map_v);
         prefetch_tensormap(&map_o);
-        mbar_init(q_full, 1);
-        mbar_init(q_empty, 1);
         mbar_init(stage_free, 1);
         for (int s = 0; s < kPairSlots; ++s) {
             mbar_init(kv_full(s), 1);
@@ -561,6 +572,8 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             mbar_init(s_full(x), 1);
             mbar_init(p_full(x), 8);
             mbar_init(o_full(x), 1);
+            mbar_init(q_full(x), 1);
+            mbar_init(q_empty(x), 1);
             mbar_init(o_empty(x), 8);
             mbar_init(staged(x), 8);
         }
@@ -582,17 +595,22 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         uint32_t n = 0;      // items started
         for_each_pair_item(args, [&](int bh, int pair) {
             const PairItem item = pair_item(args, bh, pair);
-            // the Q buffers are free once the previous item's last score product has completed
-            if (!mbar_wait_warp(q_empty, (n & 1) ^ 1, 220)) return false;
-            if (leader) {
-                mbar_expect_tx(q_full, 2 * kTileBytes);
-                for (int x = 0; x < 2; ++x) {
-                    tma_load_2d(smem_base + PairSmem::kQ + x * kTileBytes, &map_q, 0, item.q_row_a + x * kRows, q_full);
-                    tma_load_2d(smem_base + PairSmem::kQ + x * kTileBytes + kHalfBytes, &map_q, 64, item.q_row_a + x * kRows, q_full);
+            // a Q buffer is free once the previous item's last score product of that query tile has completed; tile A's
+            // (which under a causal mask ends a key tile earlier) and the first K tile go first, so that the issuing warp
+            // can start this item's tile A under the previous item's last round
+            auto load_q = [&](int x) {
+                if (!mbar_wait_warp(q_empty(x), (n & 1) ^ 1, 220 + x)) return false;
+                if (leader) {
+                    mbar_expect_tx(q_full(x), kTileBytes);
+                    tma_load_2d(smem_base + PairSmem::kQ + x * kTileBytes, &map_q, 0, item.q_row_a + x * kRows, q_full(x));
+                    tma_load_2d(smem_base + PairSmem::kQ + x * kTileBytes + kHalfBytes, &map_q, 64, item.q_row_a + x * kRows, q_full(x));
                 }
-            }
+                return true;
+            };
+            if (!load_q(0)) return false;
             for (int t = 0; t < 2 * item.tiles_b; ++t) {
-                if (!mbar_wait_warp(kv_empty(slot), phase, 221)) return false;
+                if (t == 1 && !load_q(1)) return false;
+                if (!mbar_wait_warp(kv_empty(slot), phase, 215)) return false;
                 const int row = item.kv_row0 + (t >> 1) * kKeys;
                 const uint32_t dst = smem_base + PairSmem::kRing + slot * kTileBytes;
                 if (leader) {
@@ -656,18 +674,32 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     umma_bf16_a_tmem(d_tmem, p_tmem + (k >> 2) * 64 + (k & 3) * 8, desc_words(v_lo + ((k * 2048) >> 4), kDescHi), idesc_pv, (j | k) != 0 ? 1u : 0u);
             }
         };
-        for_each_pair_item(args, [&](int bh, int pair) {
+        PairWalker walker;
+        int bh = 0, pair = 0, next_bh = 0, next_pair = 0;
+        bool have = walker.next(args, bh, pair);
+        bool early = false;  // S_A of the current item was issued in the previous item's last round
+        int early_slot = 0;  // the ring slot of its K tile
+        while (have && ok) {
             const PairItem item = pair_item(args, bh, pair);
             const int tiles_a = item.tiles_a, tiles_b = item.tiles_b;
-            if (ok) ok = mbar_wait_warp(q_full, n & 1, 222);
-            wait_slot(225);
-            scores(0, slot);
-            commit(s_full(0));
-            scores(1, slot);
+            const bool have_next = walker.next(args, next_bh, next_pair);
+            const int next_tiles_a = have_next ? pair_item(args, next_bh, next_pair).tiles_a : 0;
+            int k0_slot = early_slot;
+            if (!early) {
+                if (ok) ok = mbar_wait_warp(q_full(0), n & 1, 222);
+                wait_slot(225);
+                k0_slot = slot;
+                next_slot();
+                scores(0, k0_slot);
+                commit(s_full(0));
+                if (tiles_a == 1) commit(q_empty(0));
+            }
+            early = false;
+            if (ok) ok = mbar_wait_warp(q_full(1), n & 1, 214);
+            scores(1, k0_slot);
             commit(s_full(1));
-            commit(kv_empty(slot));
-            if (tiles_b == 1) commit(q_empty);
-            next_slot();
+            commit(kv_empty(k0_slot));
+            if (tiles_b == 1) commit(q_empty(1));
             for (int j = 0; j < tiles_b; ++j, ++stamp_j) {
                 if (leader) SDPA_TRACE(2, stamp_j, 0);
                 wait_slot(226);
@@ -677,6 +709,18 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 if (j < tiles_a) {
                     product(0, j, v_slot);
                     if (j == tiles_a - 1) commit(o_full(0));
+                } else if (have_next && ok && j == tiles_b - 1) {
+                    // Tile A has no key tile in this item's last round (causal mask): if the next item's Q_A and first K
+                    // tile have landed, its first scores go out now and its softmax runs under tile B's last round.
+                    const bool landed = __all_sync(0xffffffffu, mbar_test_wait(q_full(0), (n + 1) & 1)) && __all_sync(0xffffffffu, mbar_test_wait(kv_full(slot), phase));
+                    if (landed) {
+                        early = true;
+                        early_slot = slot;
+                        next_slot();
+                        scores(0, early_slot);
+                        commit(s_full(0));
+                        if (next_tiles_a == 1) commit(q_empty(0));
+                    }
                 }
                 if (leader) SDPA_TRACE(2, stamp_j, 2);
                 const bool more = j + 1 < tiles_b;
@@ -690,6 +734,7 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 if (j + 1 < tiles_a) {
                     scores(0, k_slot);
                     commit(s_full(0));
+                    if (j + 2 == tiles_a) commit(q_empty(0));  // the item's last read of Q_A
                 }
                 if (leader) SDPA_TRACE(2, stamp_j, 4);
                 product(1, j, v_slot);
@@ -699,14 +744,16 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     scores(1, k_slot);
                     commit(s_full(1));
                     commit(kv_empty(k_slot));
-                    if (j + 2 == tiles_b) commit(q_empty);  // the item's last read of Q_A and Q_B
+                    if (j + 2 == tiles_b) commit(q_empty(1));  // the item's last read of Q_B
                 }
                 if (leader) SDPA_TRACE(2, stamp_j, 6);
             }
             commit(o_full(1));
             ++n;
-            return ok;
-        });
+            bh = next_bh;
+            pair = next_pair;
+            have = have_next;
+        }
     } else if (warp == 18) {
         // Output stores: a query tile's softmax warps leave the normalised tile in the staging buffer; this warp sends it
         // off and hands the buffer to the next tile once the copy engine has read it.
