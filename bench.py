@@ -335,7 +335,7 @@ def measure(name: str, steps: int, warmup: int, torch, device, distributed: bool
 NCU_TRAFFIC_BYTES = {
     (2, "conv3+residual"): 73.0e6,     # profiles/umma_conv_persistent_kernel_c2_bottleneck.md
     (3, "dequantize_b+dequantize_a+matmul"): 34.8e6,  # profiles/umma_mxf8_and_bsq_kernels_c3_quantize_matmul.md
-    (4, "sdpa"): 516.1e6,              # profiles/sdpa_umma_pair_kernel_c4_sdpa.md
+    (4, "sdpa"): 511.2e6,              # profiles/sdpa_umma_pair_kernel_c4_sdpa.md
     (5, "paged_decode"): 1313.1e6,     # profiles/sdpa_decode_umma_kernel_c5_paged_decode.md
 }
 
