@@ -38,27 +38,6 @@ __device__ __forceinline__ uint32_t scale_code_from_amax_bits(uint32_t amax_bits
     return static_cast<uint32_t>(code < 0 ? 0 : (code > 254 ? 254 : code));
 }
 
-// Two f32 -> two E4M3 codes (first value in the low byte).
-__device__ __forceinline__ uint32_t cvt_e4m3_pair(float first, float second) {
-    uint16_t packed;
-    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(packed) : "f"(second), "f"(first));
-    return packed;
-}
-
-// A negative in [-2^-10, -0) rounds to zero: the reference gives +0 for it.
-__device__ __forceinline__ float flush_negative_underflow(float v) {
-    uint32_t bits = __float_as_uint(v);
-    return (bits - 0x80000001u) <= (0xBA800000u - 0x80000001u) ? 0.0f : v;
-}
-
-__device__ __forceinline__ uint32_t encode_e4m3_pair(float a, float b) {
-    return cvt_e4m3_pair(flush_negative_underflow(a), flush_negative_underflow(b));
-}
-
-__device__ __forceinline__ uint32_t encode_e4m3_scalar(float v) {
-    if (v != v) return 0x7fu;
-    return encode_e4m3_pair(v, 0.0f) & 0xffu;
-}
 
 // The reference's search, literally (used only by the self-check kernel).
 __device__ uint32_t encode_e4m3_search(float value) {

@@ -128,6 +128,31 @@ __device__ __forceinline__ float reciprocal_e8m0(uint32_t code) {
     return __uint_as_float((254u - code) << 23);
 }
 
+// ---- f32 -> E4M3 with the reference's search semantics (lib/Compiler/Numeric.cpp:504-632): the hardware
+// convert (round to nearest even, saturate to 448) plus two fix-ups, NaN -> 0x7f and a negative that rounds
+// to zero -> +0.
+// Two f32 -> two E4M3 codes (first value in the low byte).
+__device__ __forceinline__ uint32_t cvt_e4m3_pair(float first, float second) {
+    uint16_t packed;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(packed) : "f"(second), "f"(first));
+    return packed;
+}
+
+// A negative in [-2^-10, -0) rounds to zero: the reference gives +0 for it.
+__device__ __forceinline__ float flush_negative_underflow(float v) {
+    uint32_t bits = __float_as_uint(v);
+    return (bits - 0x80000001u) <= (0xBA800000u - 0x80000001u) ? 0.0f : v;
+}
+
+__device__ __forceinline__ uint32_t encode_e4m3_pair(float a, float b) {
+    return cvt_e4m3_pair(flush_negative_underflow(a), flush_negative_underflow(b));
+}
+
+__device__ __forceinline__ uint32_t encode_e4m3_scalar(float v) {
+    if (v != v) return 0x7fu;
+    return encode_e4m3_pair(v, 0.0f) & 0xffu;
+}
+
 __device__ __forceinline__ float load_as_f32(const void* data, int dtype, int64_t offset) {
     switch (dtype) {
         case DFGPU_F32: return static_cast<const float*>(data)[offset];
@@ -145,6 +170,7 @@ __device__ __forceinline__ void store_from_f32(void* data, int dtype, int64_t of
         case DFGPU_F32: static_cast<float*>(data)[offset] = value; break;
         case DFGPU_F16: static_cast<__half*>(data)[offset] = __float2half_rn(value); break;
         case DFGPU_BF16: static_cast<uint16_t*>(data)[offset] = f32_to_bf16_bits(value); break;
+        case DFGPU_E4M3: static_cast<uint8_t*>(data)[offset] = static_cast<uint8_t>(encode_e4m3_scalar(value)); break;
         default: break;
     }
 }

@@ -44,6 +44,12 @@ struct MxArgs {
     int32_t whole_items;   // work items that are whole 128 x BN tiles; the items after them are 128-column halves of the
     int32_t total_items;   // remaining tiles, so that the last round over the SMs takes half a tile's time instead of a whole one
     int32_t b_mn_major;
+    // MATMUL_FP8 form: sfa == nullptr (every block scale is 1), and after the fused steps value = acc * *descale_a * *descale_b,
+    // *amax_bits = max over all elements of |value| (bits of the non-negative f32, NaN canonical), C = value * *scale_c
+    const float* descale_a;
+    const float* descale_b;
+    const float* scale_c;
+    unsigned int* amax_bits;
     int32_t step_count;
     int32_t step_kind[kMaxSteps];
     float relu_lower[kMaxSteps], relu_upper[kMaxSteps], relu_slope[kMaxSteps];
@@ -93,7 +99,12 @@ __device__ __forceinline__ float load_step_f32(const void* base, int dtype, int6
 }
 
 // One thread's row of a finished tile: tensor memory -> fused steps -> bf16 / f32 -> global, 32 columns at a time.
-__device__ __forceinline__ void mx_store_row(const MxArgs& args, uint32_t tmem_row_base, int64_t out_row, int64_t n0, int width, bool healthy) {
+struct MxScalars {
+    bool on;
+    float descale_a, descale_b, scale_c;
+    float magnitude;  // running max |value| of this thread (NaN sticks)
+};
+__device__ __forceinline__ void mx_store_row(const MxArgs& args, uint32_t tmem_row_base, int64_t out_row, int64_t n0, int width, bool healthy, MxScalars& scalars) {
 #pragma unroll 1
     for (int chunk = 0; chunk < width / 32; ++chunk) {
         uint32_t raw[32];
@@ -117,8 +128,37 @@ __device__ __forceinline__ void mx_store_row(const MxArgs& args, uint32_t tmem_r
                 for (int e = 0; e < 32; ++e) v[e] = __fadd_rn(v[e], load_step_f32(args.step_data[s], args.step_dtype[s], out_row * args.step_ld[s] + col0 + e));
             }
         }
+        if (scalars.on) {
+            float top = scalars.magnitude;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                // (+0.0 first: the reference's sum starts from +0.0 and so is never -0.0, the tensor core's can be)
+                const float value = __fmul_rn(__fmul_rn(__fadd_rn(v[e], 0.0f), scalars.descale_a), scalars.descale_b);
+                top = maximum_nan(top, fabsf(value));
+                v[e] = __fmul_rn(value, scalars.scale_c);
+            }
+            scalars.magnitude = top;
+        }
         if (healthy) {
-            if (args.out_dtype == DFGPU_BF16) {
+            if (args.out_dtype == DFGPU_E4M3) {
+                uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(args.out) + out_row * args.out_ld + col0);
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        const float* f = v + 16 * q + 4 * t;
+                        uint32_t lo = encode_e4m3_pair(f[0], f[1]), hi = encode_e4m3_pair(f[2], f[3]);
+                        // NaN -> 0x7f whatever its sign (the hardware convert keeps the sign bit)
+                        if (f[0] != f[0]) lo = (lo & 0xff00u) | 0x7fu;
+                        if (f[1] != f[1]) lo = (lo & 0x00ffu) | 0x7f00u;
+                        if (f[2] != f[2]) hi = (hi & 0xff00u) | 0x7fu;
+                        if (f[3] != f[3]) hi = (hi & 0x00ffu) | 0x7f00u;
+                        w[t] = lo | (hi << 16);
+                    }
+                    dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            } else if (args.out_dtype == DFGPU_BF16) {
                 uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(args.out) + out_row * args.out_ld + col0);
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
@@ -273,6 +313,13 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int row = quadrant * 32 + lane;
         bool ok = true;
         int local = 0;
+        MxScalars scalars{};
+        if (args.descale_a != nullptr) {
+            scalars.on = true;
+            scalars.descale_a = *args.descale_a;
+            scalars.descale_b = *args.descale_b;
+            scalars.scale_c = *args.scale_c;
+        }
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
             int m_tile, n0, width;
             decode_item(tile, m_tile, n0, width);
@@ -280,10 +327,15 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             tc_fence_after();
             const bool healthy = ok && g_device_status == 0;
             const int64_t out_row = static_cast<int64_t>(m_tile) * kTileM + row;
-            mx_store_row(args, tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16), out_row, n0, width, healthy);
+            mx_store_row(args, tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16), out_row, n0, width, healthy, scalars);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty_bar);
+        }
+        if (scalars.on && args.amax_bits != nullptr) {
+            unsigned int bits = scalars.magnitude != scalars.magnitude ? 0x7fc00000u : __float_as_uint(scalars.magnitude);
+            bits = __reduce_max_sync(0xffffffffu, bits);
+            if (lane == 0 && bits != 0u && ok) atomicMax(args.amax_bits, bits);
         }
     } else {
         // ---- scale loaders: warp 6 + q owns ring slot q ----
@@ -297,10 +349,11 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int kb = 0; kb < args.k_blocks; ++kb, ++it) {
                 if ((it & (kStages - 1)) != slot) continue;
                 // issue the global loads first: they do not depend on the slot being free
+                const bool unit = args.sfa == nullptr;  // MATMUL_FP8: every block scale is 2^0
                 uint32_t a_words[4];
 #pragma unroll
                 for (int g = 0; g < 4; ++g)
-                    a_words[g] = __ldg(reinterpret_cast<const uint32_t*>(args.sfa + (static_cast<int64_t>(m_tile) * kTileM + g * 32 + lane) * args.sfa_ld + kb * 4));
+                    a_words[g] = unit ? 0x7f7f7f7fu : __ldg(reinterpret_cast<const uint32_t*>(args.sfa + (static_cast<int64_t>(m_tile) * kTileM + g * 32 + lane) * args.sfa_ld + kb * 4));
                 uint32_t b_words[BN / 128][4];
 #pragma unroll
                 for (int c = 0; c < BN / 128; ++c)
@@ -308,6 +361,10 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     for (int g = 0; g < 4; ++g) {
                         if (c * 128 >= width) {  // a half-width work item has one chunk of column scales
                             b_words[c][g] = 0;
+                            continue;
+                        }
+                        if (unit) {
+                            b_words[c][g] = 0x7f7f7f7fu;
                             continue;
                         }
                         const uint8_t* p = args.sfb + static_cast<int64_t>(kb) * 4 * args.sfb_ld + static_cast<int64_t>(n0) + c * 128 + g * 32 + lane;
@@ -568,7 +625,8 @@ umma_mxf8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             tc_fence_after();
             const bool healthy = ok && g_device_status == 0;
             const int64_t out_row = static_cast<int64_t>(m_tile) * 256 + rank * 128 + row;
-            mx_store_row(args, tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16), out_row, static_cast<int64_t>(n_tile) * 256, 256, healthy);
+            MxScalars none{};
+            mx_store_row(args, tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16), out_row, static_cast<int64_t>(n_tile) * 256, 256, healthy, none);
             if (warp == 2) MX_ADD(6, MX_CLOCK() - t_store);
             tc_fence_before();
             __syncwarp();
@@ -638,6 +696,34 @@ inline int make_map_u8(CUtensorMap* map, const void* base, const uint64_t* dims,
 
 bool aligned(const void* p, uintptr_t to) { return (reinterpret_cast<uintptr_t>(p) & (to - 1)) == 0; }
 
+bool b_is_k_major(const dfgpu_tensor& b, int64_t K) {
+    const int rank = b.rank;
+    return b.stride[rank - 2] == 1 && b.stride[rank - 1] % 16 == 0 && b.stride[rank - 1] >= K;
+}
+
+// Tensor maps of the E4M3 operands: A as [M rows, K bytes], B as [N rows, K bytes] (K-major) or [K rows, N bytes].
+int make_operand_maps(const dfgpu_tensor& a, const dfgpu_tensor& b, const void* a_data, const void* b_data, int64_t M, int64_t N, int64_t K,
+                      CUtensorMap* map_a, CUtensorMap* map_b) {
+    const int rank = a.rank;
+    {
+        uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+        uint64_t strides[1] = {static_cast<uint64_t>(a.stride[rank - 2])};
+        uint32_t box[2] = {kBlockK, kTileM};
+        int status = make_map_u8(map_a, a_data, dims, strides, box, "MATMUL A (E4M3)");
+        if (status) return status;
+    }
+    if (b_is_k_major(b, K)) {
+        uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+        uint64_t strides[1] = {static_cast<uint64_t>(b.stride[rank - 1])};
+        uint32_t box[2] = {kBlockK, 128};
+        return make_map_u8(map_b, b_data, dims, strides, box, "MATMUL B (E4M3)");
+    }
+    uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
+    uint64_t strides[1] = {static_cast<uint64_t>(b.stride[rank - 2])};
+    uint32_t box[2] = {128, kBlockK};
+    return make_map_u8(map_b, b_data, dims, strides, box, "MATMUL B (E4M3)");
+}
+
 // The fused steps this kernel applies: ReLU, a per-column ADD operand, a full [M, N] ADD operand.
 bool translate_steps(const dfgpu_matmul_params& p, void* const* tensors, MxArgs* args) {
     if (p.epilogue_count < 0 || p.epilogue_count > kMaxSteps) return false;
@@ -673,6 +759,30 @@ bool translate_steps(const dfgpu_matmul_params& p, void* const* tensors, MxArgs*
     return true;
 }
 
+// One-SM form: grid, tail split and launch.
+int launch_one_sm(const CUtensorMap& map_a, const CUtensorMap& map_b, MxArgs args, int bn, cudaStream_t stream) {
+    const int64_t tiles = static_cast<int64_t>(args.m_tiles) * args.n_tiles;
+    const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
+    // The tiles left over after the last full round over the SMs are cut into halves when the halves still fit one
+    // round: 4096^3 is 512 tiles on 148 SMs, i.e. three full rounds and 68 tiles, which become 136 half tiles.
+    const int remainder = static_cast<int>(tiles % grid);
+    args.whole_items = static_cast<int>(tiles);
+    args.total_items = static_cast<int>(tiles);
+    if (bn == 256 && remainder > 0 && 2 * remainder <= grid) {
+        args.whole_items = static_cast<int>(tiles - remainder);
+        args.total_items = args.whole_items + 2 * remainder;
+    }
+    auto run = [&](auto kernel, int dynamic) -> int {
+        cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dynamic);
+        if (error != cudaSuccess) return fail(kExecutionFailed, "MATMUL: cannot reserve %d bytes of shared memory: %s", dynamic, cudaGetErrorString(error));
+        error = launch_chained(kernel, dim3(grid), dim3(kMxThreads), dynamic, stream, map_a, map_b, args);
+        if (error != cudaSuccess) return fail(kExecutionFailed, "MATMUL (tcgen05, MXFP8 block scaled): launch failed: %s", cudaGetErrorString(error));
+        return check_launch("MATMUL (tcgen05, MXFP8 block scaled)");
+    };
+    if (bn == 256) return run(umma_mxf8_kernel<256>, MxSmem<256>::kDynamic);
+    return run(umma_mxf8_kernel<128>, MxSmem<128>::kDynamic);
+}
+
 }  // namespace
 
 bool matmul_mxf8_supported(const dfgpu_matmul_params& p) {
@@ -704,27 +814,11 @@ int launch_matmul_mxf8(const dfgpu_matmul_params& p, void* const* tensors, bool 
     const int64_t M = p.c.dim[rank - 2], N = p.c.dim[rank - 1], K = p.a.dim[rank - 1];
     if (!aligned(tensors[0], 16) || !aligned(tensors[1], 16) || !aligned(tensors[2], 16) || !aligned(tensors[3], 4))
         return fail(kInvalidArgument, "MATMUL: the MXFP8 kernel needs 16-byte aligned A, B and C and a 4-byte aligned A scale");
-    const bool b_k_major = p.b.stride[rank - 2] == 1 && p.b.stride[rank - 1] % 16 == 0 && p.b.stride[rank - 1] >= K;
+    const bool b_k_major = b_is_k_major(p.b, K);
     const int bn = N % 256 == 0 ? 256 : 128;
     CUtensorMap map_a, map_b;
     {
-        uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
-        uint64_t strides[1] = {static_cast<uint64_t>(p.a.stride[rank - 2])};
-        uint32_t box[2] = {kBlockK, kTileM};
-        int status = make_map_u8(&map_a, tensors[0], dims, strides, box, "MATMUL A (E4M3)");
-        if (status) return status;
-    }
-    if (b_k_major) {
-        uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
-        uint64_t strides[1] = {static_cast<uint64_t>(p.b.stride[rank - 1])};
-        uint32_t box[2] = {kBlockK, 128};
-        int status = make_map_u8(&map_b, tensors[1], dims, strides, box, "MATMUL B (E4M3)");
-        if (status) return status;
-    } else {
-        uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
-        uint64_t strides[1] = {static_cast<uint64_t>(p.b.stride[rank - 2])};
-        uint32_t box[2] = {128, kBlockK};
-        int status = make_map_u8(&map_b, tensors[1], dims, strides, box, "MATMUL B (E4M3)");
+        int status = make_operand_maps(p.a, p.b, tensors[0], tensors[1], M, N, K, &map_a, &map_b);
         if (status) return status;
     }
     MxArgs args{};
@@ -740,25 +834,8 @@ int launch_matmul_mxf8(const dfgpu_matmul_params& p, void* const* tensors, bool 
     args.k_blocks = static_cast<int>(K / kBlockK);
     args.b_mn_major = b_k_major ? 0 : 1;
     if (!translate_steps(p, tensors, &args)) return fail(kUnsupported, "MATMUL: the fused epilogue is not one the MXFP8 kernel applies");
-    const int64_t tiles = static_cast<int64_t>(args.m_tiles) * args.n_tiles;
-    const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
-    // The tiles left over after the last full round over the SMs are cut into halves when the halves still fit one
-    // round: 4096^3 is 512 tiles on 148 SMs, i.e. three full rounds and 68 tiles, which become 136 half tiles.
-    const int remainder = static_cast<int>(tiles % grid);
-    args.whole_items = static_cast<int>(tiles);
-    args.total_items = static_cast<int>(tiles);
-    if (bn == 256 && remainder > 0 && 2 * remainder <= grid) {
-        args.whole_items = static_cast<int>(tiles - remainder);
-        args.total_items = args.whole_items + 2 * remainder;
-    }
-    auto run = [&](auto kernel, int dynamic) -> int {
-        cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dynamic);
-        if (error != cudaSuccess) return fail(kExecutionFailed, "MATMUL: cannot reserve %d bytes of shared memory: %s", dynamic, cudaGetErrorString(error));
-        error = launch_chained(kernel, dim3(grid), dim3(kMxThreads), dynamic, stream, map_a, map_b, args);
-        if (error != cudaSuccess) return fail(kExecutionFailed, "MATMUL (tcgen05, MXFP8 block scaled): launch failed: %s", cudaGetErrorString(error));
-        return check_launch("MATMUL (tcgen05, MXFP8 block scaled)");
-    };
-    if (two_sm_tiles) {
+    if (!two_sm_tiles) return launch_one_sm(map_a, map_b, args, bn, stream);
+    {
         // two-SM form: 256 x 256 tiles, one cluster of two CTAs each
         MxArgs pair_args = args;
         pair_args.m_tiles = static_cast<int>(M / 256);
@@ -771,8 +848,53 @@ int launch_matmul_mxf8(const dfgpu_matmul_params& p, void* const* tensors, bool 
         if (error != cudaSuccess) return fail(kExecutionFailed, "MATMUL (tcgen05, MXFP8, two-SM tiles): launch failed: %s", cudaGetErrorString(error));
         return check_launch("MATMUL (tcgen05, MXFP8, two-SM tiles)");
     }
-    if (bn == 256) return run(umma_mxf8_kernel<256>, MxSmem<256>::kDynamic);
-    return run(umma_mxf8_kernel<128>, MxSmem<128>::kDynamic);
+    return fail(kInvalidArgument, "MATMUL: unreachable");
+}
+
+bool matmul_fp8_umma_supported(const dfgpu_matmul_fp8_params& p) {
+    if (p.a.dtype != DFGPU_E4M3 || p.b.dtype != DFGPU_E4M3) return false;
+    if (p.c.dtype != DFGPU_BF16 && p.c.dtype != DFGPU_F32 && p.c.dtype != DFGPU_E4M3) return false;
+    const int rank = p.c.rank;
+    if (rank < 2 || p.a.rank != rank || p.b.rank != rank) return false;
+    for (int i = 0; i < rank - 2; ++i)
+        if (p.c.dim[i] != 1 || p.a.dim[i] != 1 || p.b.dim[i] != 1) return false;
+    const int64_t M = p.c.dim[rank - 2], N = p.c.dim[rank - 1], K = p.a.dim[rank - 1];
+    if (M % kTileM != 0 || N % 128 != 0 || K % kBlockK != 0 || M < kTileM || N < 128 || K < kBlockK) return false;
+    if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30)) return false;
+    if (p.b.dim[rank - 2] != K || p.b.dim[rank - 1] != N || p.a.dim[rank - 2] != M) return false;
+    if (p.a.stride[rank - 1] != 1 || p.a.stride[rank - 2] % 16 != 0 || p.a.stride[rank - 2] < K) return false;
+    const bool b_n_major = p.b.stride[rank - 1] == 1 && p.b.stride[rank - 2] % 16 == 0 && p.b.stride[rank - 2] >= N;
+    if (!b_is_k_major(p.b, K) && !b_n_major) return false;
+    // 32 output columns leave a thread as 16-byte vectors
+    const int64_t row_multiple = p.c.dtype == DFGPU_E4M3 ? 16 : (p.c.dtype == DFGPU_BF16 ? 8 : 4);
+    if (p.c.stride[rank - 1] != 1 || p.c.stride[rank - 2] % row_multiple != 0 || p.c.stride[rank - 2] < N) return false;
+    return true;
+}
+
+int launch_matmul_fp8_umma(const dfgpu_matmul_fp8_params& p, void* const* tensors, cudaStream_t stream) {
+    const int rank = p.c.rank;
+    const int64_t M = p.c.dim[rank - 2], N = p.c.dim[rank - 1], K = p.a.dim[rank - 1];
+    if (!aligned(tensors[0], 16) || !aligned(tensors[1], 16) || !aligned(tensors[2], 16))
+        return fail(kInvalidArgument, "MATMUL_FP8: the tcgen05 kernel needs 16-byte aligned A, B and C");
+    const int bn = N % 256 == 0 ? 256 : 128;
+    CUtensorMap map_a, map_b;
+    int status = make_operand_maps(p.a, p.b, tensors[0], tensors[1], M, N, K, &map_a, &map_b);
+    if (status) return status;
+    MxArgs args{};
+    args.sfa = nullptr;  // unit block scales
+    args.sfb = nullptr;
+    args.out = tensors[2];
+    args.out_ld = p.c.stride[rank - 2];
+    args.out_dtype = p.c.dtype;
+    args.m_tiles = static_cast<int>(M / kTileM);
+    args.n_tiles = static_cast<int>(N / bn);
+    args.k_blocks = static_cast<int>(K / kBlockK);
+    args.b_mn_major = b_is_k_major(p.b, K) ? 0 : 1;
+    args.amax_bits = static_cast<unsigned int*>(tensors[3]);
+    args.descale_a = static_cast<const float*>(tensors[4]);
+    args.descale_b = static_cast<const float*>(tensors[5]);
+    args.scale_c = static_cast<const float*>(tensors[6]);
+    return launch_one_sm(map_a, map_b, args, bn, stream);
 }
 
 int mxf8_device_status(int* status) { return read_and_clear_device_status(status); }

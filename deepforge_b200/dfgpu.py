@@ -23,6 +23,7 @@ BSQ_AUTO, BSQ_GENERIC, BSQ_ROW32, BSQ_COL32 = range(4)
 BSD_AUTO, BSD_GENERIC, BSD_PACKED = range(3)
 CONV_AUTO, CONV_DIRECT, CONV_IGEMM_FFMA, CONV_UMMA_BF16 = range(4)
 MATMUL_AUTO, MATMUL_FFMA, MATMUL_UMMA_BF16, MATMUL_UMMA_MXF8, MATMUL_UMMA_MXF8_2SM = range(5)
+MATMUL_FP8_AUTO, MATMUL_FP8_SCALAR, MATMUL_FP8_UMMA = range(3)
 SDPA_AUTO, SDPA_ROWWISE, SDPA_PAGED_DECODE, SDPA_UMMA, SDPA_PAGED_DECODE_UMMA = range(5)
 
 
@@ -87,6 +88,10 @@ class MatmulParams(C.Structure):
                 ("epilogue_count", C.c_int32), ("kernel", C.c_int32), ("epilogue", EpilogueStep * MAX_EPILOGUE)]
 
 
+class MatmulFp8Params(C.Structure):
+    _fields_ = [("a", Tensor), ("b", Tensor), ("c", Tensor), ("kernel", C.c_int32), ("reserved", C.c_int32)]
+
+
 class SdpaParams(C.Structure):
     _fields_ = [("q", Tensor), ("k", Tensor), ("v", Tensor), ("o", Tensor), ("stats", Tensor), ("max", Tensor),
                 ("sum_exp", Tensor), ("seq_q", Tensor), ("seq_kv", Tensor), ("page_table_k", Tensor),
@@ -103,6 +108,7 @@ EXPORTS = [
     "dfgpu_query_pointwise", "dfgpu_pointwise",
     "dfgpu_query_conv_fprop", "dfgpu_conv_fprop",
     "dfgpu_query_matmul", "dfgpu_matmul",
+    "dfgpu_query_matmul_fp8", "dfgpu_matmul_fp8",
     "dfgpu_query_sdpa_forward", "dfgpu_sdpa_forward", "dfgpu_sdpa_paged_decode_static",
     "dfgpu_selfcheck_e4m3", "dfgpu_debug_scale_codes", "dfgpu_debug_encode_e4m3", "dfgpu_device_status",
 ]
@@ -178,6 +184,10 @@ def conv_fprop(params, x, w, y, extra0=None, extra1=None, scratch=None, stream=N
 
 def matmul(params, a, b, c, a_scale=None, b_scale=None, extra0=None, extra1=None, scratch=None, stream=None):
     _call("dfgpu_matmul", params, [a, b, c, a_scale, b_scale, extra0, extra1], scratch, stream)
+
+
+def matmul_fp8(params, a, b, c, amax, descale_a, descale_b, scale_c, scratch=None, stream=None):
+    _call("dfgpu_matmul_fp8", params, [a, b, c, amax, descale_a, descale_b, scale_c], scratch, stream)
 
 
 def sdpa_forward(params, pointers: Sequence[Optional[int]], scratch=None, stream=None):

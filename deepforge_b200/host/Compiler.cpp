@@ -407,6 +407,67 @@ Status lower_matmul(Lowering& low, std::size_t index) {
     return Status::ok();
 }
 
+// MATMUL_FP8 (reference checks: lib/Compiler/SpecializedGraph.cpp:409-496): A, B, two descales, Scale_C in; C and
+// Amax_C out; the scales and Amax_C hold one FLOAT element each.
+Status lower_matmul_fp8(Lowering& low, std::size_t index) {
+    auto const& node = low.graph.nodes[index];
+    auto const where = node_path(index, node);
+    auto status = require_float_compute(node, where);
+    if (status.is_bad()) return status;
+    for (auto name : {"M_override", "N_override", "K_override"})
+        if (port(node.inputs, name)) return fail(ErrorCode::kUnsupportedOperation, where, "extent override tensors are not executable on this backend");
+    if (node.inputs.size() != 5 || node.outputs.size() != 2)
+        return fail(ErrorCode::kInvalidValue, where, "MATMUL_FP8 requires A, B, two descales, Scale_C, C, and Amax_C");
+    auto a = port(node.inputs, "A"), b = port(node.inputs, "B"), c = port(node.outputs, "C"), amax = port(node.outputs, "Amax_C");
+    auto descale_a = port(node.inputs, "Descale_A"), descale_b = port(node.inputs, "Descale_B"), scale_c = port(node.inputs, "Scale_C");
+    if (!a || !b || !c || !amax || !descale_a || !descale_b || !scale_c)
+        return fail(ErrorCode::kInvalidValue, where, "MATMUL_FP8 requires A, B, two descales, Scale_C, C, and Amax_C");
+    auto one_float = [&](std::int64_t uid, char const* name, char const* message) -> Status {
+        auto const& t = low.tensor(uid);
+        if (t.data_type != DataType::kFloat32) return fail(ErrorCode::kUnsupportedDataType, where + "." + name, "expected FLOAT");
+        std::int64_t count = 1;
+        for (auto extent : t.dim) count *= extent;
+        if (count != 1) return fail(ErrorCode::kInvalidShape, where + "." + name, message);
+        return Status::ok();
+    };
+    if ((status = one_float(*amax, "Amax_C", "Amax_C must contain one FLOAT element")).is_bad()) return status;
+    for (auto [uid, name] : {std::pair{*descale_a, "Descale_A"}, std::pair{*descale_b, "Descale_B"}, std::pair{*scale_c, "Scale_C"}})
+        if ((status = one_float(uid, name, "scale tensors must contain one FLOAT element")).is_bad()) return status;
+    auto typed = [&](std::int64_t uid, char const* name, std::initializer_list<DataType> allowed) -> Status {
+        auto const type = low.tensor(uid).data_type;
+        if (std::find(allowed.begin(), allowed.end(), type) != allowed.end()) return Status::ok();
+        return fail(ErrorCode::kUnsupportedDataType, where + "." + name, std::string(import::data_type_name(type)) + " is not supported on this port");
+    };
+    // the reference also takes FP8_E5M2 here; this backend executes the E4M3 codec only
+    if ((status = typed(*a, "A", {DataType::kFp8E4M3})).is_bad()) return status;
+    if ((status = typed(*b, "B", {DataType::kFp8E4M3})).is_bad()) return status;
+    if ((status = typed(*c, "C", {DataType::kFp8E4M3, DataType::kFloat32, DataType::kFloat16, DataType::kBFloat16})).is_bad()) return status;
+    dfgpu_matmul_fp8_params params{};
+    if ((status = low.describe(*a, params.a, where)).is_bad()) return status;
+    if ((status = low.describe(*b, params.b, where)).is_bad()) return status;
+    if ((status = low.describe(*c, params.c, where)).is_bad()) return status;
+    auto const& ta = low.tensor(*a);
+    auto const& tb = low.tensor(*b);
+    auto const& tc = low.tensor(*c);
+    if (ta.dim.size() < 2 || ta.dim.size() != tb.dim.size() || tc.dim.size() != ta.dim.size())
+        return fail(ErrorCode::kInvalidShape, where, "A, B, and C must have equal rank of at least two");
+    auto const rank = ta.dim.size();
+    if (ta.dim[rank - 1] != tb.dim[rank - 2] || tc.dim[rank - 2] != ta.dim[rank - 2] || tc.dim[rank - 1] != tb.dim[rank - 1])
+        return fail(ErrorCode::kInvalidShape, where, "matrix M, N, and K dimensions are inconsistent");
+    for (std::size_t axis = 0; axis + 2 < rank; ++axis)
+        if ((ta.dim[axis] != 1 && ta.dim[axis] != tc.dim[axis]) || (tb.dim[axis] != 1 && tb.dim[axis] != tc.dim[axis]))
+            return fail(ErrorCode::kInvalidShape, where, "batch dimensions are not broadcast-compatible");
+    if (low.options.disable_tensor_cores) params.kernel = DFGPU_MATMUL_FP8_SCALAR;
+    KernelStep step;
+    step.op = KernelOp::kMatmulFp8;
+    step.label = node.name;
+    step.nodes = {index};
+    step.tensors = {low.bind(*a), low.bind(*b), low.bind(*c), low.bind(*amax), low.bind(*descale_a), low.bind(*descale_b), low.bind(*scale_c)};
+    step.params = params;
+    low.plan.steps.push_back(std::move(step));
+    return Status::ok();
+}
+
 Status lower_pointwise(Lowering& low, std::size_t index) {
     auto const& node = low.graph.nodes[index];
     auto const where = node_path(index, node);
@@ -644,6 +705,7 @@ Status query_step(KernelStep& step, std::int64_t& scratch_bytes) {
         case KernelOp::kConvFprop: code = dfgpu_query_conv_fprop(&std::get<dfgpu_conv_params>(step.params), &info); break;
         case KernelOp::kMatmul: code = dfgpu_query_matmul(&std::get<dfgpu_matmul_params>(step.params), &info); break;
         case KernelOp::kSdpaForward: code = dfgpu_query_sdpa_forward(&std::get<dfgpu_sdpa_params>(step.params), &info); break;
+        case KernelOp::kMatmulFp8: code = dfgpu_query_matmul_fp8(&std::get<dfgpu_matmul_fp8_params>(step.params), &info); break;
     }
     if (code != 0) return Status::failure(static_cast<ErrorCode>(code), step.label, dfgpu_last_error());
     step.kernel = info.kernel;
@@ -662,6 +724,7 @@ char const* kernel_op_name(KernelOp op) {
         case KernelOp::kConvFprop: return "conv_fprop";
         case KernelOp::kMatmul: return "matmul";
         case KernelOp::kSdpaForward: return "sdpa_forward";
+        case KernelOp::kMatmulFp8: return "matmul_fp8";
     }
     return "?";
 }
@@ -729,6 +792,7 @@ Status compile_graph(SerializedGraph const& graph, CompileOptions const& options
             case OperationTag::kBlockScaleQuantize: status = lower_quantize(low, index); break;
             case OperationTag::kBlockScaleDequantize: status = lower_dequantize(low, index); break;
             case OperationTag::kSdpa: status = lower_sdpa(low, index); break;
+            case OperationTag::kMatmulFp8: status = lower_matmul_fp8(low, index); break;
         }
         if (status.is_bad()) return status;
     }

@@ -58,6 +58,8 @@ std::vector<TagSchema> const& schemas() {
         {OperationTag::kBlockScaleQuantize, "BLOCK_SCALE_QUANTIZE", {"compute_data_type", "block_size", "axis"}, {}, {"X"}, {"Y", "scale"}},
         {OperationTag::kConvFprop, "CONV_FPROP", {"compute_data_type", "pre_padding", "post_padding", "stride", "dilation", "math_mode"}, {}, {"X", "W"}, {"Y"}},
         {OperationTag::kMatmul, "MATMUL", {"compute_data_type", "padding_value"}, {}, {"A", "B", "M_override", "N_override", "K_override"}, {"C"}},
+        {OperationTag::kMatmulFp8, "MATMUL_FP8", {"compute_data_type"}, {},
+         {"A", "B", "Descale_A", "Descale_B", "M_override", "N_override", "K_override", "Scale_C"}, {"C", "Amax_C"}},
         {OperationTag::kPointwise, "POINTWISE",
          {"compute_data_type", "mode", "axis", "relu_lower_clip", "relu_upper_clip", "relu_lower_clip_slope", "swish_beta", "elu_alpha", "softplus_beta"},
          {}, {"IN_0", "IN_1", "IN_2"}, {"OUT_0"}},
@@ -73,9 +75,9 @@ std::vector<TagSchema> const& schemas() {
 }
 
 // Tags the Frontend can serialize but this backend does not execute.
-constexpr std::array<std::string_view, 33> kOtherTags{{
+constexpr std::array<std::string_view, 32> kOtherTags{{
     "ADA_LAYER_NORM", "ADA_LAYER_NORM_BPROP", "BATCHNORM", "BATCHNORM_INFERENCE", "BN_FINALIZE", "CONCATENATE", "CONV_DGRAD", "CONV_WGRAD",
-    "DBN", "DBN_WEIGHT", "DIAGONAL_BAND_MASK", "DLN", "DIN", "DRMS_NORM", "GEN_STATS", "INSTANCE_NORM", "LAYER_NORM", "MATMUL_FP8",
+    "DBN", "DBN_WEIGHT", "DIAGONAL_BAND_MASK", "DLN", "DIN", "DRMS_NORM", "GEN_STATS", "INSTANCE_NORM", "LAYER_NORM",
     "MOE_GROUPED_MATMUL", "MOE_GROUPED_MATMUL_BWD", "PAGED_CACHE_LOAD", "REDUCTION", "RESAMPLE", "RESHAPE", "RMS_NORM", "RNG", "ROPE",
     "ROPE_BWD", "SDPA_BWD", "SDPA_FP8", "SDPA_FP8_BWD", "SLICE", "TRANSPOSE",
 }};

@@ -147,6 +147,43 @@ def c3(m=4096, k=4096, n=4096, io="BFLOAT16", c_type="BFLOAT16", first_row=0) ->
         inputs={1: operand(1, m * k, first_row * k), 2: operand(2, k * n)}, outputs=[3, 4, 5, 6, 9])
 
 
+def matmul_fp8(m=4096, k=4096, n=4096, c_type="BFLOAT16", batch=(1,), b_k_major=False, a_batch=None, b_batch=None,
+               scalars=(0.5, 0.25, 0.125), exact=True) -> Workload:
+    """One MATMUL_FP8 node (the first row of the "next" list after the five configurations). Operands are E4M3 codes
+    with exponent fields 6..8 (|value| in [0.5, 3.75], one in sixteen a zero): with `exact` every partial sum of up to
+    2^10 products is exactly representable in f32, so the result does not depend on the order of the additions and
+    the tensor-core kernel can be compared bit for bit; without it the exponent fields span 1..9."""
+    doc = graphs.matmul_fp8(m, k, n, c_type, batch, b_k_major, a_batch, b_batch)
+    seed = BASE_SEED + 8
+
+    def codes(uid: int, count: int):
+        def make():
+            r = synthetic.raw_u64(seed, uid, count, 0)
+            mantissa = (r & np.uint64(7)).astype(np.uint8)
+            span = 3 if exact else 9
+            exponent = ((r >> np.uint64(3)) % np.uint64(span)).astype(np.uint8) + np.uint8(6 if exact else 1)
+            sign = ((r >> np.uint64(16)) & np.uint64(1)).astype(np.uint8)
+            out = (sign << 7) | (exponent << 3) | mantissa
+            out[((r >> np.uint64(20)) & np.uint64(15)) == 0] = 0
+            return out.astype(np.uint8)
+        return make
+
+    def scalar(value: float):
+        return lambda: np.array([value], dtype=np.float32)
+
+    def count(uid: int) -> int:
+        return int(np.prod(doc["tensors"][str(uid)]["dim"]))
+
+    batches = int(np.prod(batch))
+    return Workload(
+        name="matmul_fp8", config=8, document=doc,
+        description={"workload": f"MATMUL_FP8 E4M3 x E4M3 -> {c_type}, M={m} K={k} N={n} batch={list(batch)}, scalar descales, Amax_C"},
+        metric="matmul_fp8_throughput", unit="TFLOP/s", flops=2.0 * batches * m * n * k,
+        bytes=float(count(21) + count(22) + batches * m * n * DTYPE_BYTES[c_type]), bound="tensor",
+        inputs={21: codes(21, count(21)), 22: codes(22, count(22)), 23: scalar(scalars[0]), 24: scalar(scalars[1]), 25: scalar(scalars[2])},
+        outputs=[26, 27])
+
+
 def c4(b=8, h=32, s=2048, d=128, io="BFLOAT16", causal=True, first_batch=0) -> Workload:
     doc = graphs.c4_sdpa(b, h, s, d, io, causal)
     seed = BASE_SEED + 4

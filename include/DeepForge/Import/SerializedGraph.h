@@ -42,6 +42,7 @@ enum class OperationTag : std::uint8_t {
     kSdpa,
     kBlockScaleQuantize,
     kBlockScaleDequantize,
+    kMatmulFp8,
 };
 [[nodiscard]] std::string_view operation_tag_name(OperationTag tag) noexcept;
 

@@ -174,6 +174,28 @@ typedef struct dfgpu_matmul_params {
 int dfgpu_query_matmul(const dfgpu_matmul_params*, dfgpu_plan_info*);
 int dfgpu_matmul(const dfgpu_matmul_params*, void* const* tensors, void* scratch, void* stream);
 
+/* ---- MATMUL_FP8 -------------------------------------------------------------
+   Replaces emit_matmul_fp8 (lib/Compiler/SpecializedGraph.cpp:982-1090; checks
+   :409-496): per element value = (sum_k a*b in f32) * Descale_A * Descale_B,
+   Amax_C = max |value| over all elements (NaN stays NaN), C = store(value * Scale_C).
+   A and B are FP8_E4M3 codes, C is FLOAT, HALF, BFLOAT16 or FP8_E4M3 (encoded with the
+   reference's rounding: ties to even, saturation at 448, a negative that rounds to zero
+   gives +0, NaN gives 0x7f). The three scales and Amax_C are one-element FLOAT tensors in
+   device memory. tensors: {A, B, C, Amax_C, Descale_A, Descale_B, Scale_C}.
+   The extent-override inputs (M_override, N_override, K_override) are not executable.
+   Two launches: Amax_C is cleared, then one kernel computes C and folds Amax_C with an
+   atomic maximum. DFGPU_MATMUL_FP8_UMMA runs the products on tcgen05
+   (kind::mxf8f6f4 with unit block scales) and needs M, N, K multiples of 128, no batch
+   axes, A rows and B rows or columns contiguous; AUTO picks it when it fits. */
+enum { DFGPU_MATMUL_FP8_AUTO = 0, DFGPU_MATMUL_FP8_SCALAR = 1, DFGPU_MATMUL_FP8_UMMA = 2 };
+typedef struct dfgpu_matmul_fp8_params {
+    dfgpu_tensor a, b, c;
+    int32_t kernel;
+    int32_t reserved;
+} dfgpu_matmul_fp8_params;
+int dfgpu_query_matmul_fp8(const dfgpu_matmul_fp8_params*, dfgpu_plan_info*);
+int dfgpu_matmul_fp8(const dfgpu_matmul_fp8_params*, void* const* tensors, void* scratch, void* stream);
+
 /* ---- SDPA forward -----------------------------------------------------------
    Replaces emit_sdpa_forward with its helpers (lib/Compiler/SequenceGraph.cpp
    :1839-1889 paged loads, :1988-2091 validity, :2135-2341 scores and softmax

@@ -591,6 +591,53 @@ int dfo_matmul(const dfo_tensor* a, const void* a_data,
 }
 
 /* ------------------------------------------------------------------------ */
+/* MATMUL_FP8 (reference: lib/Compiler/SpecializedGraph.cpp:409-496 checks,   */
+/* :982-1090 arithmetic)                                                      */
+/* ------------------------------------------------------------------------ */
+/* Per output element: f32 sum over k of a * b in k order from 0.0, then        */
+/* * descale_a, * descale_b (two separate multiplications). Amax_C is the        */
+/* maximumf fold from 0.0 of |that value| over all elements (NaN stays NaN);     */
+/* C stores value * scale_c through store_from_f32.                              */
+int dfo_matmul_fp8(const dfo_tensor* a, const void* a_data,
+                   const dfo_tensor* b, const void* b_data,
+                   const dfo_tensor* c, void* c_data,
+                   float descale_a, float descale_b, float scale_c, float* amax_out) {
+    int rank = c->rank;
+    if (rank < 2 || a->rank != rank || b->rank != rank) return 15;
+    int64_t m = c->dim[rank - 2], n = c->dim[rank - 1], kk = a->dim[rank - 1];
+    int64_t batches = 1;
+    for (int i = 0; i < rank - 2; ++i) batches *= c->dim[i];
+    int64_t bi[DFO_MAX_RANK];
+    float amax = 0.0f;
+    for (int64_t batch = 0; batch < batches; ++batch) {
+        int64_t rest = batch;
+        for (int i = rank - 3; i >= 0; --i) { bi[i] = rest % c->dim[i]; rest /= c->dim[i]; }
+        int64_t a_base = 0, b_base = 0, c_base = 0;
+        for (int i = 0; i < rank - 2; ++i) {
+            a_base += (a->dim[i] == 1 ? 0 : bi[i]) * a->stride[i];
+            b_base += (b->dim[i] == 1 ? 0 : bi[i]) * b->stride[i];
+            c_base += bi[i] * c->stride[i];
+        }
+        for (int64_t im = 0; im < m; ++im)
+            for (int64_t in = 0; in < n; ++in) {
+                float sum = 0.0f;
+                for (int64_t ik = 0; ik < kk; ++ik) {
+                    float av = load_f32(a, a_data, a_base + im * a->stride[rank - 2] + ik * a->stride[rank - 1]);
+                    float bv = load_f32(b, b_data, b_base + ik * b->stride[rank - 2] + in * b->stride[rank - 1]);
+                    float product = av * bv;
+                    sum = sum + product;
+                }
+                float value = sum * descale_a;
+                value = value * descale_b;
+                amax = maximumf_nan(amax, fabsf(value));
+                store_f32(c, c_data, c_base + im * c->stride[rank - 2] + in * c->stride[rank - 1], value * scale_c);
+            }
+    }
+    if (amax_out) *amax_out = amax;
+    return 0;
+}
+
+/* ------------------------------------------------------------------------ */
 /* SDPA forward (reference: lib/Compiler/SequenceGraph.cpp)                  */
 /* ------------------------------------------------------------------------ */
 

@@ -113,6 +113,12 @@ int dfo_matmul(const dfo_tensor* a, const void* a_data,
                const dfo_tensor* c, void* c_data,
                int64_t row_begin, int64_t row_end);
 
+/* MATMUL_FP8: C = encode((sum_k a*b) * descale_a * descale_b * scale_c), *amax = max |value before scale_c| */
+int dfo_matmul_fp8(const dfo_tensor* a, const void* a_data,
+                   const dfo_tensor* b, const void* b_data,
+                   const dfo_tensor* c, void* c_data,
+                   float descale_a, float descale_b, float scale_c, float* amax_out);
+
 /* SDPA forward */
 typedef struct dfo_sdpa_params {
     dfo_tensor q, k, v, o;

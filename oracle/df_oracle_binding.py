@@ -149,6 +149,15 @@ def matmul(ad, a, bd, b, cd, c, row_begin=0, row_end=-1) -> None:
     assert code == 0, code
 
 
+def matmul_fp8(ad, a, bd, b, cd, c, descale_a: float, descale_b: float, scale_c: float) -> float:
+    """C in place; returns Amax_C."""
+    amax = C.c_float(0.0)
+    code = lib().dfo_matmul_fp8(C.byref(ad), ptr(a), C.byref(bd), ptr(b), C.byref(cd), ptr(c), C.c_float(descale_a), C.c_float(descale_b),
+                                C.c_float(scale_c), C.byref(amax))
+    assert code == 0, code
+    return amax.value
+
+
 def sdpa_forward(params: SdpaParams, arrays, bh_begin=0, bh_end=1 << 62, q_step=1) -> None:
     assert len(arrays) == 11
     pointers = (C.c_void_p * 11)(*[C.c_void_p(a.ctypes.data) if a is not None else C.c_void_p(None) for a in arrays])

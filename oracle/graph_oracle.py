@@ -89,6 +89,12 @@ def run(document: dict, inputs: Dict[int, np.ndarray], matmul_rows: Optional[Tup
             values[c] = _alloc(tensors[c])
             lo, hi = matmul_rows if matmul_rows else (0, -1)
             oracle.matmul(_desc(tensors[a]), values[a], _desc(tensors[b]), values[b], _desc(tensors[c]), values[c], lo, hi)
+        elif tag == "MATMUL_FP8":
+            a, b, c, amax = ins["A"], ins["B"], outs["C"], outs["Amax_C"]
+            values[c] = _alloc(tensors[c])
+            scalars = [float(np.asarray(values[ins[name]], dtype=np.float32).reshape(-1)[0]) for name in ("Descale_A", "Descale_B", "Scale_C")]
+            result = oracle.matmul_fp8(_desc(tensors[a]), values[a], _desc(tensors[b]), values[b], _desc(tensors[c]), values[c], *scalars)
+            values[amax] = np.full(_span(tensors[amax]), result, dtype=np.float32)
         elif tag == "BLOCK_SCALE_QUANTIZE":
             x, y, scale = ins["X"], outs["Y"], outs["scale"]
             values[y], values[scale] = _alloc(tensors[y]), _alloc(tensors[scale])

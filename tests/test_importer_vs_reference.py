@@ -47,6 +47,7 @@ DOCS = {
     "c3": graphs.c3_quantize_matmul(128, 128, 128),
     "c4": graphs.c4_sdpa(1, 2, 16, 8),
     "c5": graphs.c5_paged_decode(2, 4, 2, 16, 8, 4, 16),
+    "matmul_fp8": graphs.matmul_fp8(2, 2, 2),
 }
 
 
