@@ -158,6 +158,11 @@ def cpu_sample(name: str, fraction: float = 1.0):
         storage = {uid: make() for uid, make in wl.inputs.items()}
         return (f"{rows} rows of A x {rows} columns of B over the full K=4096 (quantize, dequantize, matmul)",
                 (lambda: graph_oracle.run(wl.document, ins, storage_inputs=storage)), wl.flops / 1e12)
+    if name == "fp8":
+        rows = max(32, int(round(256 * fraction)) // 32 * 32)
+        wl = workloads.matmul_fp8(m=rows, k=4096, n=rows)
+        ins = {uid: graph_oracle.widen(make(), wl.tensor(uid)["data_type"]) for uid, make in wl.inputs.items()}
+        return (f"{rows} rows of A x {rows} columns of B over the full K=4096", (lambda: graph_oracle.run(wl.document, ins)), wl.flops / 1e12)
     if name == "c4":
         wl = workloads.c4(b=1, h=1, s=2048)
         ins = {uid: graph_oracle.widen(make(), "BFLOAT16") for uid, make in wl.inputs.items()}
@@ -349,10 +354,10 @@ def roofline_for(result: dict, peaks: dict) -> dict:
     # touches only the valid tokens of the pool, so it uses the workload's figure
     nbytes = wl.bytes if info["op"] == 5 and wl.config == 5 else float(info["bound_bytes"])
     kernels = [{"label": p["label"], "kernel": p["kernel"], "ms": round(t, 5)} for p, t in zip(plan, per_step)]
-    if wl.bound == "tensor" and info["op"] in (4, 5):
+    if wl.bound == "tensor" and info["op"] in (4, 5, 6):
         tflops = wl.flops / 1e12 / duration_s
         peak, note = peaks["bf16_tflops"], " (bf16 burst)"
-        if info["op"] == 4 and info["kernel"] == 3:
+        if (info["op"] == 4 and info["kernel"] == 3) or (info["op"] == 6 and info["kernel"] == 2):
             # The block-scaled MXFP8 tensor-core kind issues twice the bf16 rate (dense nominal 4.5 vs 2.25 PFLOP/s);
             # the measured peaks hold no fp8 figure, so the denominator is twice the measured bf16 burst.
             peak, note = 2.0 * peak, " (2 x bf16 burst: MXFP8 kind, no measured fp8 peak)"
@@ -368,7 +373,7 @@ def main() -> None:
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=500)
     parser.add_argument("--warmup", type=int, default=5)
-    parser.add_argument("--workload", default="c2", choices=["c1", "c1_nchw", "c2", "c3", "c4", "c5"])
+    parser.add_argument("--workload", default="c2", choices=["c1", "c1_nchw", "c2", "c3", "c4", "c5", "fp8"])
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--gather", action="store_true", help="all-gather the outputs over NCCL inside the timed region")
     parser.add_argument("--no-also", action="store_true", help="skip the short runs of the other configurations")
@@ -427,7 +432,7 @@ def main() -> None:
         torch.cuda.empty_cache()
         if world == 1 and not args.no_also:
             also = {}
-            for other in ("c1", "c2", "c3", "c4", "c5"):
+            for other in ("c1", "c2", "c3", "c4", "c5", "fp8"):
                 if other == args.workload:
                     continue
                 try:

@@ -349,28 +349,33 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int kb = 0; kb < args.k_blocks; ++kb, ++it) {
                 if ((it & (kStages - 1)) != slot) continue;
                 // issue the global loads first: they do not depend on the slot being free
-                const bool unit = args.sfa == nullptr;  // MATMUL_FP8: every block scale is 2^0
                 uint32_t a_words[4];
-#pragma unroll
-                for (int g = 0; g < 4; ++g)
-                    a_words[g] = unit ? 0x7f7f7f7fu : __ldg(reinterpret_cast<const uint32_t*>(args.sfa + (static_cast<int64_t>(m_tile) * kTileM + g * 32 + lane) * args.sfa_ld + kb * 4));
                 uint32_t b_words[BN / 128][4];
+                if (args.sfa == nullptr) {
+                    // MATMUL_FP8: every block scale is 2^0
 #pragma unroll
-                for (int c = 0; c < BN / 128; ++c)
+                    for (int g = 0; g < 4; ++g) a_words[g] = 0x7f7f7f7fu;
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        if (c * 128 >= width) {  // a half-width work item has one chunk of column scales
-                            b_words[c][g] = 0;
-                            continue;
+                    for (int c = 0; c < BN / 128; ++c)
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) b_words[c][g] = c * 128 >= width ? 0u : 0x7f7f7f7fu;
+                } else {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g)
+                        a_words[g] = __ldg(reinterpret_cast<const uint32_t*>(args.sfa + (static_cast<int64_t>(m_tile) * kTileM + g * 32 + lane) * args.sfa_ld + kb * 4));
+#pragma unroll
+                    for (int c = 0; c < BN / 128; ++c)
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            if (c * 128 >= width) {  // a half-width work item has one chunk of column scales
+                                b_words[c][g] = 0;
+                                continue;
+                            }
+                            const uint8_t* p = args.sfb + static_cast<int64_t>(kb) * 4 * args.sfb_ld + static_cast<int64_t>(n0) + c * 128 + g * 32 + lane;
+                            const uint32_t b0 = __ldg(p), b1 = __ldg(p + args.sfb_ld), b2 = __ldg(p + 2 * args.sfb_ld), b3 = __ldg(p + 3 * args.sfb_ld);
+                            b_words[c][g] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
                         }
-                        if (unit) {
-                            b_words[c][g] = 0x7f7f7f7fu;
-                            continue;
-                        }
-                        const uint8_t* p = args.sfb + static_cast<int64_t>(kb) * 4 * args.sfb_ld + static_cast<int64_t>(n0) + c * 128 + g * 32 + lane;
-                        const uint32_t b0 = __ldg(p), b1 = __ldg(p + args.sfb_ld), b2 = __ldg(p + 2 * args.sfb_ld), b3 = __ldg(p + 3 * args.sfb_ld);
-                        b_words[c][g] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
-                    }
+                }
                 ok = mbar_wait_warp(empty_bar(slot), phase, 405);
                 phase ^= 1;
                 if (!ok) break;

@@ -234,7 +234,7 @@ def c5(batch=64, hq=32, hkv=8, d=128, pages=16384, block=64, max_len=8192, min_l
     return workload
 
 
-BUILDERS = {"c1": c1, "c1_nchw": lambda **kw: c1("nchw", **kw), "c2": c2, "c3": c3, "c4": c4, "c5": c5}
+BUILDERS = {"c1": c1, "c1_nchw": lambda **kw: c1("nchw", **kw), "c2": c2, "c3": c3, "c4": c4, "c5": c5, "fp8": matmul_fp8}
 
 
 # which axis of which output tensor the shards concatenate along when gathered
@@ -265,4 +265,6 @@ def shard(name: str, rank: int, world: int, **size) -> Workload:
         batch = size.pop("batch", 64)
         assert batch % world == 0
         return c5(batch=batch // world, first_sequence=rank * (batch // world), **size)
+    if name == "fp8":  # every rank runs the full matrix product on its own stream of codes (Amax_C is a whole-matrix result)
+        return matmul_fp8(**size)
     raise KeyError(name)
