@@ -1,0 +1,499 @@
+// Artifact container: writer, bounds-checked reader and loader (see include/DeepForge/Compiler/Artifact.h).
+// Field order of the common part follows the reference's format 12 (docs/artifact-format.en.md:55-123).
+#include "DeepForge/Compiler/Artifact.h"
+
+#include "Internal.h"
+
+#include <atomic>
+#include <bit>
+#include <cstring>
+#include <fstream>
+#include <set>
+#include <system_error>
+#include <unistd.h>
+
+namespace deepforge::compiler {
+namespace {
+
+using import::ErrorCode;
+using import::Status;
+
+constexpr std::uint8_t kMagic[8] = {'D', 'F', 'O', 'B', 'J', '\r', '\n', 0x1a};
+constexpr std::uint32_t kEndianMarker = 0x01020304u;
+constexpr char kBackendVersion[] = "deepforge_b200 1";
+constexpr char kFrontendVersion[] = "1.24.0";
+constexpr char kTarget[] = "sm_100a";
+constexpr std::uint64_t kMaxBytes = 1ull << 30;
+
+Status bad(std::string_view detail) { return Status::failure(ErrorCode::kParseError, "artifact", detail); }
+Status invalid(std::string_view subject, std::string_view detail) { return Status::failure(ErrorCode::kInvalidValue, subject, detail); }
+
+std::uint64_t fnv1a(std::uint8_t const* data, std::size_t size) {
+    std::uint64_t hash = 0xcbf29ce484222325ull;
+    for (std::size_t i = 0; i < size; ++i) {
+        hash ^= data[i];
+        hash *= 0x100000001b3ull;
+    }
+    return hash;
+}
+
+struct Writer {
+    std::vector<std::uint8_t> bytes;
+    void raw(void const* data, std::size_t size) {
+        auto const* p = static_cast<std::uint8_t const*>(data);
+        bytes.insert(bytes.end(), p, p + size);
+    }
+    void u32(std::uint32_t v) {
+        for (int i = 0; i < 4; ++i) bytes.push_back(static_cast<std::uint8_t>(v >> (8 * i)));
+    }
+    void u64(std::uint64_t v) {
+        for (int i = 0; i < 8; ++i) bytes.push_back(static_cast<std::uint8_t>(v >> (8 * i)));
+    }
+    void i64(std::int64_t v) { u64(static_cast<std::uint64_t>(v)); }
+    void f64(double v) { u64(std::bit_cast<std::uint64_t>(v)); }
+    void string(std::string_view v) {
+        u32(static_cast<std::uint32_t>(v.size()));
+        raw(v.data(), v.size());
+    }
+};
+
+// Every read checks the remaining length; after a failed read all further reads fail too.
+struct Reader {
+    std::uint8_t const* data;
+    std::size_t size;
+    std::size_t at = 0;
+    bool ok = true;
+    bool need(std::size_t count) {
+        if (!ok || count > size - at) ok = false;
+        return ok;
+    }
+    std::uint32_t u32() {
+        if (!need(4)) return 0;
+        std::uint32_t v = 0;
+        for (int i = 0; i < 4; ++i) v |= static_cast<std::uint32_t>(data[at + i]) << (8 * i);
+        at += 4;
+        return v;
+    }
+    std::uint64_t u64() {
+        if (!need(8)) return 0;
+        std::uint64_t v = 0;
+        for (int i = 0; i < 8; ++i) v |= static_cast<std::uint64_t>(data[at + i]) << (8 * i);
+        at += 8;
+        return v;
+    }
+    std::int64_t i64() { return static_cast<std::int64_t>(u64()); }
+    double f64() { return std::bit_cast<double>(u64()); }
+    std::string string() {
+        std::uint32_t count = u32();
+        if (!need(count)) return {};
+        std::string v(reinterpret_cast<char const*>(data + at), count);
+        at += count;
+        return v;
+    }
+    void raw(void* out, std::size_t count) {
+        if (!need(count)) return;
+        std::memcpy(out, data + at, count);
+        at += count;
+    }
+};
+
+template <class T>
+constexpr std::uint32_t params_size() { return static_cast<std::uint32_t>(sizeof(T)); }
+
+std::uint32_t params_size_of(KernelOp op) {
+    switch (op) {
+        case KernelOp::kBlockScaleQuantize: return params_size<dfgpu_bsq_params>();
+        case KernelOp::kBlockScaleDequantize: return params_size<dfgpu_bsd_params>();
+        case KernelOp::kPointwise: return params_size<dfgpu_pointwise_params>();
+        case KernelOp::kConvFprop: return params_size<dfgpu_conv_params>();
+        case KernelOp::kMatmul: return params_size<dfgpu_matmul_params>();
+        case KernelOp::kSdpaForward: return params_size<dfgpu_sdpa_params>();
+        case KernelOp::kMatmulFp8: return params_size<dfgpu_matmul_fp8_params>();
+    }
+    return 0;
+}
+
+// Number of tensor slots of each dfgpu entry point.
+std::size_t tensor_slots(KernelOp op) {
+    switch (op) {
+        case KernelOp::kBlockScaleQuantize: return 3;
+        case KernelOp::kBlockScaleDequantize: return 3;
+        case KernelOp::kPointwise: return 3;
+        case KernelOp::kConvFprop: return 5;
+        case KernelOp::kMatmul: return 7;
+        case KernelOp::kSdpaForward: return 11;
+        case KernelOp::kMatmulFp8: return 7;
+    }
+    return 0;
+}
+
+constexpr std::uint32_t kLastOp = static_cast<std::uint32_t>(KernelOp::kMatmulFp8);
+
+void write_binding(Writer& w, TensorBinding const& binding) {
+    w.u32(static_cast<std::uint32_t>(binding.kind));
+    w.i64(binding.uid);
+    w.u64(binding.offset);
+}
+
+void write_plan(Writer& w, KernelPlan const& plan) {
+    w.u32(static_cast<std::uint32_t>(dfgpu_abi_version()));
+    w.u32(static_cast<std::uint32_t>(plan.steps.size()));
+    for (auto const& step : plan.steps) {
+        w.u32(static_cast<std::uint32_t>(step.op));
+        w.string(step.label);
+        w.u32(static_cast<std::uint32_t>(step.nodes.size()));
+        for (auto node : step.nodes) w.u64(node);
+        w.u32(static_cast<std::uint32_t>(step.kernel));
+        w.u32(static_cast<std::uint32_t>(step.launches));
+        std::visit([&](auto const& params) {
+            w.u32(static_cast<std::uint32_t>(sizeof(params)));
+            w.raw(&params, sizeof(params));  // POD with explicit reserved fields: no implicit padding
+        }, step.params);
+        w.u32(static_cast<std::uint32_t>(step.tensors.size()));
+        for (auto const& binding : step.tensors) write_binding(w, binding);
+        write_binding(w, step.scratch);
+    }
+}
+
+bool power_of_two(std::uint64_t v) { return v != 0 && (v & (v - 1)) == 0; }
+
+Status check_workspace(WorkspacePlan const& workspace) {
+    if (!power_of_two(workspace.alignment) || workspace.alignment > 4096) return invalid("workspace", "alignment must be a power of two up to 4096");
+    std::uint64_t top = 0;
+    for (auto const& allocation : workspace.allocations) {
+        if (!power_of_two(allocation.alignment) || allocation.offset % allocation.alignment != 0) return invalid("workspace", "allocation '" + allocation.name + "' is misaligned");
+        if (allocation.size_bytes > kMaxBytes * 256 || allocation.offset > kMaxBytes * 256) return invalid("workspace", "allocation '" + allocation.name + "' is out of range");
+        if (allocation.live_start > allocation.live_end) return invalid("workspace", "allocation '" + allocation.name + "' ends before it starts");
+        top = std::max(top, allocation.offset + allocation.size_bytes);
+    }
+    // exactly the 64-byte aligned high-water mark of the plan, as the reference's artifact validator requires
+    if (workspace.size_bytes != (top + 63) / 64 * 64) return invalid("workspace", "size is not the aligned high-water mark of its allocations");
+    return Status::ok();
+}
+
+bool tensor_in_range(dfgpu_tensor const& t) { return t.rank >= 0 && t.rank <= DFGPU_MAX_RANK && t.dtype >= 0 && t.dtype <= DFGPU_I32; }
+
+bool params_in_range(KernelParams const& params) {
+    return std::visit([](auto const& p) {
+        using T = std::decay_t<decltype(p)>;
+        if constexpr (std::is_same_v<T, dfgpu_bsq_params>) return tensor_in_range(p.x) && tensor_in_range(p.y) && tensor_in_range(p.scale);
+        else if constexpr (std::is_same_v<T, dfgpu_bsd_params>) return tensor_in_range(p.x) && tensor_in_range(p.y) && tensor_in_range(p.scale);
+        else if constexpr (std::is_same_v<T, dfgpu_pointwise_params>) return tensor_in_range(p.in0) && tensor_in_range(p.in1) && tensor_in_range(p.out);
+        else if constexpr (std::is_same_v<T, dfgpu_conv_params>)
+            return tensor_in_range(p.x) && tensor_in_range(p.w) && tensor_in_range(p.y) && tensor_in_range(p.extra[0]) && tensor_in_range(p.extra[1]) &&
+                   p.epilogue_count >= 0 && p.epilogue_count <= DFGPU_MAX_EPILOGUE;
+        else if constexpr (std::is_same_v<T, dfgpu_matmul_params>)
+            return tensor_in_range(p.a) && tensor_in_range(p.b) && tensor_in_range(p.c) && tensor_in_range(p.a_scale) && tensor_in_range(p.b_scale) &&
+                   tensor_in_range(p.extra[0]) && tensor_in_range(p.extra[1]) && p.epilogue_count >= 0 && p.epilogue_count <= DFGPU_MAX_EPILOGUE;
+        else if constexpr (std::is_same_v<T, dfgpu_sdpa_params>)
+            return tensor_in_range(p.q) && tensor_in_range(p.k) && tensor_in_range(p.v) && tensor_in_range(p.o) && tensor_in_range(p.stats) &&
+                   tensor_in_range(p.max) && tensor_in_range(p.sum_exp) && tensor_in_range(p.seq_q) && tensor_in_range(p.seq_kv) &&
+                   tensor_in_range(p.page_table_k) && tensor_in_range(p.page_table_v);
+        else return tensor_in_range(p.a) && tensor_in_range(p.b) && tensor_in_range(p.c);
+    }, params);
+}
+
+template <class T>
+KernelParams read_params(Reader& r) {
+    T params{};
+    r.raw(&params, sizeof(T));
+    return params;
+}
+
+bool read_binding(Reader& r, TensorBinding& binding) {
+    std::uint32_t kind = r.u32();
+    binding.uid = r.i64();
+    binding.offset = r.u64();
+    if (!r.ok || kind > static_cast<std::uint32_t>(TensorBinding::Kind::kWorkspace)) return false;
+    binding.kind = static_cast<TensorBinding::Kind>(kind);
+    return true;
+}
+
+Status read_plan(Reader& r, ArtifactInfo& info) {
+    info.kernel_abi_version = static_cast<std::int32_t>(r.u32());
+    std::uint32_t count = r.u32();
+    if (!r.ok || count == 0 || count > 65536) return bad("kernel plan: launch count out of range");
+    for (std::uint32_t s = 0; s < count; ++s) {
+        KernelStep step;
+        std::uint32_t op = r.u32();
+        if (!r.ok || op > kLastOp) return bad("kernel plan: unknown entry point");
+        step.op = static_cast<KernelOp>(op);
+        step.label = r.string();
+        std::uint32_t nodes = r.u32();
+        if (!r.ok || nodes > 4096 || !r.need(static_cast<std::size_t>(nodes) * 8)) return bad("kernel plan: node list out of range");
+        for (std::uint32_t n = 0; n < nodes; ++n) step.nodes.push_back(static_cast<std::size_t>(r.u64()));
+        step.kernel = static_cast<std::int32_t>(r.u32());
+        step.launches = static_cast<std::int32_t>(r.u32());
+        std::uint32_t size = r.u32();
+        if (!r.ok || size != params_size_of(step.op)) return bad("kernel plan: params block has the wrong size for its entry point");
+        switch (step.op) {
+            case KernelOp::kBlockScaleQuantize: step.params = read_params<dfgpu_bsq_params>(r); break;
+            case KernelOp::kBlockScaleDequantize: step.params = read_params<dfgpu_bsd_params>(r); break;
+            case KernelOp::kPointwise: step.params = read_params<dfgpu_pointwise_params>(r); break;
+            case KernelOp::kConvFprop: step.params = read_params<dfgpu_conv_params>(r); break;
+            case KernelOp::kMatmul: step.params = read_params<dfgpu_matmul_params>(r); break;
+            case KernelOp::kSdpaForward: step.params = read_params<dfgpu_sdpa_params>(r); break;
+            case KernelOp::kMatmulFp8: step.params = read_params<dfgpu_matmul_fp8_params>(r); break;
+        }
+        if (!r.ok || !params_in_range(step.params)) return bad("kernel plan: tensor descriptor out of range");
+        if (step.kernel < 0 || step.launches < 1 || step.launches > 16) return bad("kernel plan: kernel id or launch count out of range");
+        std::uint32_t tensors = r.u32();
+        if (!r.ok || tensors != tensor_slots(step.op)) return bad("kernel plan: wrong number of tensor bindings for the entry point");
+        step.tensors.resize(tensors);
+        for (auto& binding : step.tensors)
+            if (!read_binding(r, binding)) return bad("kernel plan: tensor binding out of range");
+        if (!read_binding(r, step.scratch) || step.scratch.kind == TensorBinding::Kind::kArgument) return bad("kernel plan: scratch binding out of range");
+        info.plan.steps.push_back(std::move(step));
+    }
+    return Status::ok();
+}
+
+// Bindings must name an argument of the table or lie inside the workspace.
+Status check_bindings(ArtifactInfo const& info) {
+    std::set<std::int64_t> uids;
+    for (auto const& argument : info.metadata.arguments) uids.insert(argument.uid);
+    auto check = [&](TensorBinding const& binding) {
+        if (binding.kind == TensorBinding::Kind::kArgument) return uids.count(binding.uid) != 0;
+        if (binding.kind == TensorBinding::Kind::kWorkspace) return binding.offset < info.workspace.size_bytes && binding.offset % 16 == 0;
+        return true;
+    };
+    for (auto const& step : info.plan.steps) {
+        for (auto const& binding : step.tensors)
+            if (!check(binding)) return bad("kernel plan: '" + step.label + "' binds a tensor that is neither an argument nor inside the workspace");
+        if (!check(step.scratch)) return bad("kernel plan: '" + step.label + "' has its scratch outside the workspace");
+    }
+    return Status::ok();
+}
+
+std::atomic<std::uint64_t> g_publish_sequence{0};
+
+Status read_file(std::filesystem::path const& path, std::vector<std::uint8_t>& bytes) {
+    std::ifstream file(path, std::ios::binary | std::ios::ate);
+    if (!file) return Status::failure(ErrorCode::kIoError, path.string(), "cannot open the artifact");
+    auto const size = file.tellg();
+    if (size < 0 || static_cast<std::uint64_t>(size) > kMaxBytes) return Status::failure(ErrorCode::kIoError, path.string(), "artifact size out of range");
+    bytes.resize(static_cast<std::size_t>(size));
+    file.seekg(0);
+    if (!bytes.empty() && !file.read(reinterpret_cast<char*>(bytes.data()), size)) return Status::failure(ErrorCode::kIoError, path.string(), "short read");
+    return Status::ok();
+}
+
+}  // namespace
+
+Status serialize_artifact(CompilationResult const& compilation, std::vector<std::uint8_t>& output) {
+    if (compilation.metadata.arguments.empty()) return invalid("arguments", "an artifact needs a non-empty argument table");
+    auto status = validate_graph_compile_metadata(compilation.metadata);
+    if (status.is_bad()) return Status::failure(ErrorCode::kInvalidValue, "arguments", status.message());
+    if ((status = check_workspace(compilation.workspace)).is_bad()) return status;
+    if (compilation.plan.steps.empty()) return invalid("plan", "an artifact needs at least one launch");
+    for (auto const& step : compilation.plan.steps)
+        if (step.tensors.size() != tensor_slots(step.op)) return invalid("plan", "launch '" + step.label + "' has the wrong number of tensor bindings");
+
+    Writer w;
+    w.raw(kMagic, sizeof(kMagic));
+    w.u32(kArtifactFormatVersion);
+    w.u32(kEndianMarker);
+    w.string(kBackendVersion);
+    w.string("");  // llvm_version: none
+    w.string(kFrontendVersion);
+    w.string(compilation.target);
+    w.string(compilation.metadata.function_name);
+    w.u32(0);  // dynamic_shape_enabled
+    w.u32(0);  // override_shape_enabled
+    w.u32(0);  // shape_override_policy: none
+    w.u32(0);  // override_role_count
+    w.u32(0);  // override_axis_count
+    w.u32(static_cast<std::uint32_t>(compilation.metadata.arguments.size()));
+    for (auto const& argument : compilation.metadata.arguments) {
+        w.i64(argument.uid);
+        w.string(argument.name);
+        w.u32(static_cast<std::uint32_t>(argument.data_type));
+        w.u32(static_cast<std::uint32_t>(argument.access));
+        w.u32(0);  // storage_policy: strided
+        w.i64(0);  // ragged_offset_uid
+        w.i64(0);  // ragged_sequence_uid
+        w.i64(1);  // ragged_sequence_divisor
+        w.u64(argument.alignment);
+        w.u64(argument.size_bytes);
+        w.u32(static_cast<std::uint32_t>(argument.dimensions.size()));
+        for (auto extent : argument.dimensions) w.i64(extent);
+        for (auto stride : argument.strides) w.i64(stride);
+    }
+    w.u32(static_cast<std::uint32_t>(ArtifactAdapterKind::kGpuKernelPlan));
+    Writer plan;
+    write_plan(plan, compilation.plan);
+    w.u64(plan.bytes.size());
+    w.raw(plan.bytes.data(), plan.bytes.size());
+    w.u64(compilation.workspace.size_bytes);
+    w.u64(compilation.workspace.alignment);
+    w.u32(static_cast<std::uint32_t>(compilation.workspace.allocations.size()));
+    for (auto const& allocation : compilation.workspace.allocations) {
+        w.string(allocation.name);
+        w.u64(allocation.offset);
+        w.u64(allocation.size_bytes);
+        w.u64(allocation.alignment);
+        w.u64(allocation.live_start);
+        w.u64(allocation.live_end);
+    }
+    w.f64(kDefaultAbsoluteTolerance);
+    w.f64(kDefaultRelativeTolerance);
+    w.u32(0);  // variant_count: the code is in the kernel library
+    w.u64(fnv1a(w.bytes.data(), w.bytes.size()));
+    output = std::move(w.bytes);
+    return Status::ok();
+}
+
+Status parse_artifact(std::span<std::uint8_t const> input, ArtifactInfo& output) {
+    if (input.size() < sizeof(kMagic) + 8 + 8) return bad("shorter than the fixed header and checksum");
+    if (input.size() > kMaxBytes) return bad("larger than 1 GiB");
+    if (std::memcmp(input.data(), kMagic, sizeof(kMagic)) != 0) return bad("magic bytes do not match");
+    Reader r{input.data(), input.size() - 8};  // everything before the checksum
+    r.at = sizeof(kMagic);
+    ArtifactInfo info;
+    info.format_version = r.u32();
+    if (r.u32() != kEndianMarker) return bad("endian marker does not match");
+    if (info.format_version >= 1 && info.format_version <= kReferenceArtifactFormatVersion)
+        return bad("format " + std::to_string(info.format_version) + " holds x86 objects; this backend loads format " + std::to_string(kArtifactFormatVersion));
+    if (info.format_version != kArtifactFormatVersion) return bad("unknown format version " + std::to_string(info.format_version));
+    {
+        Reader tail{input.data(), input.size()};
+        tail.at = input.size() - 8;
+        if (tail.u64() != fnv1a(input.data(), input.size() - 8)) return bad("checksum does not match");
+    }
+    info.deepforge_version = r.string();
+    info.llvm_version = r.string();
+    info.frontend_version = r.string();
+    info.target_triple = r.string();
+    info.metadata.function_name = r.string();
+    std::uint32_t dynamic_shape = r.u32(), override_shape = r.u32(), policy = r.u32(), roles = r.u32(), axes = r.u32();
+    if (!r.ok) return bad("truncated header");
+    if (dynamic_shape > 1 || override_shape > 1) return bad("a boolean flag holds neither 0 nor 1");
+    if (dynamic_shape || override_shape || policy != 0 || roles != 0 || axes != 0) return bad("shape-override metadata is not executable on this backend");
+    std::uint32_t arguments = r.u32();
+    if (!r.ok || arguments == 0 || arguments > 4096) return bad("argument count out of range");
+    for (std::uint32_t i = 0; i < arguments; ++i) {
+        TensorArgumentMetadata argument;
+        argument.uid = r.i64();
+        argument.name = r.string();
+        std::uint32_t data_type = r.u32(), access = r.u32(), storage_policy = r.u32();
+        std::int64_t ragged_offset = r.i64(), ragged_sequence = r.i64(), divisor = r.i64();
+        argument.alignment = r.u64();
+        argument.size_bytes = r.u64();
+        std::uint32_t rank = r.u32();
+        if (!r.ok) return bad("truncated argument table");
+        if (data_type > static_cast<std::uint32_t>(import::DataType::kInt4)) return bad("argument '" + argument.name + "': unknown data type");
+        if (access > static_cast<std::uint32_t>(TensorAccess::kReadWrite)) return bad("argument '" + argument.name + "': unknown access");
+        if (storage_policy != 0 || ragged_offset != 0 || ragged_sequence != 0 || divisor != 1) return bad("argument '" + argument.name + "': only strided storage is executable on this backend");
+        if (rank < 1 || rank > 64 || !r.need(static_cast<std::size_t>(rank) * 16)) return bad("argument '" + argument.name + "': rank out of range");
+        argument.data_type = static_cast<import::DataType>(data_type);
+        argument.access = static_cast<TensorAccess>(access);
+        for (std::uint32_t axis = 0; axis < rank; ++axis) argument.dimensions.push_back(r.i64());
+        for (std::uint32_t axis = 0; axis < rank; ++axis) argument.strides.push_back(r.i64());
+        info.metadata.arguments.push_back(std::move(argument));
+    }
+    if (auto status = validate_graph_compile_metadata(info.metadata); status.is_bad()) return bad("argument table: " + status.message());
+    std::uint32_t adapter = r.u32();
+    std::uint64_t adapter_size = r.u64();
+    if (!r.ok) return bad("truncated adapter header");
+    if (adapter != static_cast<std::uint32_t>(ArtifactAdapterKind::kGpuKernelPlan)) return bad("adapter kind " + std::to_string(adapter) + " is a CPU invocation adapter");
+    if (!r.need(adapter_size)) return bad("adapter section runs past the end");
+    {
+        Reader plan{input.data() + r.at, static_cast<std::size_t>(adapter_size)};
+        if (auto status = read_plan(plan, info); status.is_bad()) return status;
+        if (!plan.ok || plan.at != plan.size) return bad("kernel plan does not fill its section");
+        r.at += static_cast<std::size_t>(adapter_size);
+    }
+    info.adapter_kind = ArtifactAdapterKind::kGpuKernelPlan;
+    info.workspace.size_bytes = r.u64();
+    info.workspace.alignment = r.u64();
+    std::uint32_t allocations = r.u32();
+    if (!r.ok || allocations > 65536) return bad("workspace allocation count out of range");
+    for (std::uint32_t i = 0; i < allocations; ++i) {
+        WorkspaceAllocation allocation;
+        allocation.name = r.string();
+        allocation.offset = r.u64();
+        allocation.size_bytes = r.u64();
+        allocation.alignment = r.u64();
+        allocation.live_start = r.u64();
+        allocation.live_end = r.u64();
+        if (!r.ok) return bad("truncated workspace plan");
+        info.workspace.allocations.push_back(std::move(allocation));
+    }
+    if (auto status = check_workspace(info.workspace); status.is_bad()) return bad("workspace plan: " + status.message());
+    info.absolute_tolerance = r.f64();
+    info.relative_tolerance = r.f64();
+    std::uint32_t variants = r.u32();
+    if (!r.ok) return bad("truncated tail");
+    if (variants != 0) return bad("a kernel-plan artifact carries no code variants");
+    if (r.at != r.size) return bad("bytes between the last field and the checksum");
+    if (auto status = check_bindings(info); status.is_bad()) return status;
+    output = std::move(info);
+    return Status::ok();
+}
+
+Status write_artifact(std::filesystem::path const& path, CompilationResult const& compilation) {
+    std::vector<std::uint8_t> bytes;
+    auto status = serialize_artifact(compilation, bytes);
+    if (status.is_bad()) return status;
+    auto temporary = path;
+    temporary += ".tmp." + std::to_string(static_cast<long long>(::getpid())) + "." + std::to_string(g_publish_sequence.fetch_add(1));
+    {
+        std::ofstream file(temporary, std::ios::binary | std::ios::trunc);
+        if (!file) return Status::failure(ErrorCode::kIoError, temporary.string(), "cannot create the temporary file");
+        file.write(reinterpret_cast<char const*>(bytes.data()), static_cast<std::streamsize>(bytes.size()));
+        file.flush();
+        if (!file) {
+            std::error_code ignored;
+            std::filesystem::remove(temporary, ignored);
+            return Status::failure(ErrorCode::kIoError, temporary.string(), "short write");
+        }
+    }
+    std::error_code error;
+    std::filesystem::rename(temporary, path, error);
+    if (error) {
+        std::error_code ignored;
+        std::filesystem::remove(temporary, ignored);
+        return Status::failure(ErrorCode::kIoError, path.string(), "cannot publish the artifact: " + error.message());
+    }
+    return Status::ok();
+}
+
+Status read_artifact(std::filesystem::path const& path, ArtifactInfo& output) {
+    std::vector<std::uint8_t> bytes;
+    auto status = read_file(path, bytes);
+    if (status.is_bad()) return status;
+    return parse_artifact(bytes, output);
+}
+
+Status load_artifact_executable(std::span<std::uint8_t const> input, std::unique_ptr<runtime::Executable>& output, ArtifactInfo* info) {
+    ArtifactInfo parsed;
+    auto status = parse_artifact(input, parsed);
+    if (status.is_bad()) return status;
+    if (parsed.kernel_abi_version != dfgpu_abi_version())
+        return Status::failure(ErrorCode::kInvalidValue, "artifact", "built against kernel ABI " + std::to_string(parsed.kernel_abi_version) + ", this library is ABI " +
+                                                                         std::to_string(dfgpu_abi_version()) + ": recompile the graph");
+    for (auto const& step : parsed.plan.steps) {
+        KernelStep probe = step;
+        std::int64_t scratch = 0;
+        if ((status = query_kernel_step(probe, scratch)).is_bad())
+            return Status::failure(ErrorCode::kInvalidValue, "artifact", "the kernel library rejects launch '" + step.label + "': " + status.message());
+        if (probe.kernel != step.kernel || probe.launches != step.launches)
+            return Status::failure(ErrorCode::kInvalidValue, "artifact", "launch '" + step.label + "' resolves to another kernel in this library: recompile the graph");
+        if (scratch > 0) {
+            if (step.scratch.kind != TensorBinding::Kind::kWorkspace || step.scratch.offset + static_cast<std::uint64_t>(scratch) > parsed.workspace.size_bytes)
+                return Status::failure(ErrorCode::kInvalidValue, "artifact", "launch '" + step.label + "' needs " + std::to_string(scratch) + " bytes of scratch that the workspace plan does not hold");
+        }
+    }
+    output = runtime::ExecutableFactory::create(parsed.metadata, parsed.workspace, parsed.plan);
+    if (info) *info = std::move(parsed);
+    return Status::ok();
+}
+
+Status load_artifact_executable(std::filesystem::path const& path, std::unique_ptr<runtime::Executable>& output, ArtifactInfo* info) {
+    std::vector<std::uint8_t> bytes;
+    auto status = read_file(path, bytes);
+    if (status.is_bad()) return status;
+    return load_artifact_executable(bytes, output, info);
+}
+
+}  // namespace deepforge::compiler

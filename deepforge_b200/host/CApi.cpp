@@ -1,6 +1,7 @@
 // Flat C API (include/deepforge_b200.h) over the C++ host side.
 #include "deepforge_b200.h"
 
+#include "DeepForge/Compiler/Artifact.h"
 #include "DeepForge/Compiler/Codegen.h"
 
 #include <algorithm>
@@ -139,6 +140,50 @@ extern "C" int df_execute_steps(const df_executable* executable, int64_t first, 
     pack.reserve(count);
     for (size_t i = 0; i < count; ++i) pack[uids[i]] = pointers[i];
     return report(executable->result.executable->execute_steps(first, last, pack, workspace));
+}
+
+extern "C" int df_serialize_artifact(const df_executable* executable, uint8_t* buffer, size_t capacity, size_t* size) {
+    std::vector<std::uint8_t> bytes;
+    auto status = compiler::serialize_artifact(executable->result, bytes);
+    if (status.is_bad()) return report(status);
+    if (size) *size = bytes.size();
+    if (buffer && capacity) std::memcpy(buffer, bytes.data(), std::min(capacity, bytes.size()));
+    return 0;
+}
+
+extern "C" int df_write_artifact(const df_executable* executable, const char* path) {
+    if (!path) return report(import::Status::failure(import::ErrorCode::kInvalidArgument, "path", "null path"));
+    return report(compiler::write_artifact(path, executable->result));
+}
+
+namespace {
+int adopt(import::Status status, std::unique_ptr<df_executable> holder, compiler::ArtifactInfo& info, df_executable** out) {
+    if (status.is_bad()) return report(status);
+    holder->result.metadata = std::move(info.metadata);
+    holder->result.workspace = std::move(info.workspace);
+    holder->result.plan = std::move(info.plan);
+    holder->result.target = info.target_triple;
+    *out = holder.release();
+    return 0;
+}
+}  // namespace
+
+extern "C" int df_load_artifact(const uint8_t* bytes, size_t size, df_executable** out) {
+    if (!out || !bytes) return report(import::Status::failure(import::ErrorCode::kInvalidArgument, "out", "null pointer"));
+    *out = nullptr;
+    auto holder = std::make_unique<df_executable>();
+    compiler::ArtifactInfo info;
+    auto status = compiler::load_artifact_executable(std::span<const uint8_t>(bytes, size), holder->result.executable, &info);
+    return adopt(status, std::move(holder), info, out);
+}
+
+extern "C" int df_load_artifact_file(const char* path, df_executable** out) {
+    if (!out || !path) return report(import::Status::failure(import::ErrorCode::kInvalidArgument, "out", "null pointer"));
+    *out = nullptr;
+    auto holder = std::make_unique<df_executable>();
+    compiler::ArtifactInfo info;
+    auto status = compiler::load_artifact_executable(std::filesystem::path(path), holder->result.executable, &info);
+    return adopt(status, std::move(holder), info, out);
 }
 
 extern "C" int df_plan_workspace(size_t count, const char* const* names, const uint64_t* sizes, const uint64_t* alignments, const uint64_t* live_starts,

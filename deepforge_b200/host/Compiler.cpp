@@ -695,7 +695,9 @@ void narrow_virtual_tensors(Lowering& low) {
     }
 }
 
-Status query_step(KernelStep& step, std::int64_t& scratch_bytes) {
+}  // namespace
+
+Status query_kernel_step(KernelStep& step, std::int64_t& scratch_bytes) {
     dfgpu_plan_info info{};
     int code = 0;
     switch (step.op) {
@@ -714,7 +716,6 @@ Status query_step(KernelStep& step, std::int64_t& scratch_bytes) {
     return Status::ok();
 }
 
-}  // namespace
 
 char const* kernel_op_name(KernelOp op) {
     switch (op) {
@@ -825,7 +826,7 @@ Status compile_graph(SerializedGraph const& graph, CompileOptions const& options
     for (std::size_t s = 0; s < low.plan.steps.size(); ++s) {
         auto& step = low.plan.steps[s];
         std::int64_t scratch = 0;
-        if ((status = query_step(step, scratch)).is_bad()) return status;
+        if ((status = query_kernel_step(step, scratch)).is_bad()) return status;
         for (auto const& binding : step.tensors) {
             if (binding.kind != TensorBinding::Kind::kWorkspace) continue;
             auto it = lifetime.find(binding.uid);
@@ -881,6 +882,18 @@ Status validate_graph_compile_metadata(GraphCompileMetadata const& metadata) {
             return fail(ErrorCode::kInvalidShape, argument.name, "rank must be between 1 and 64 with matching strides");
         if (argument.alignment == 0 || (argument.alignment & (argument.alignment - 1)) != 0 || argument.alignment > 4096)
             return fail(ErrorCode::kInvalidValue, argument.name, "alignment must be a power of two no greater than 4096");
+        // size_bytes is the storage span of the strided view, or the full extent product for a reordered (F8_128x4) tensor
+        import::TensorDesc view;
+        view.data_type = argument.data_type;
+        view.dim = argument.dimensions;
+        view.stride = argument.strides;
+        view.reordering_type = "NONE";
+        std::uint64_t strided = 0, reordered = 0;
+        if (!import::tensor_storage_bytes(view, strided)) return fail(ErrorCode::kInvalidShape, argument.name, "extents, strides or data type do not give a storage span");
+        view.reordering_type = "F8_128x4";
+        (void)import::tensor_storage_bytes(view, reordered);
+        if (argument.size_bytes != strided && argument.size_bytes != reordered)
+            return fail(ErrorCode::kInvalidValue, argument.name, "size_bytes is not the storage span of the tensor");
     }
     return Status::ok();
 }

@@ -10,6 +10,8 @@
 
 namespace deepforge::compiler {
 char const* kernel_op_name(KernelOp op);
+// Asks the kernel library about one launch: fills step.kernel / step.launches and reports its scratch need.
+import::Status query_kernel_step(KernelStep& step, std::int64_t& scratch_bytes);
 }
 
 namespace deepforge::runtime {

@@ -18,6 +18,7 @@ EXPORTS = [
     "df_last_error", "df_parse", "df_compile", "df_destroy", "df_workspace_size", "df_launch_count", "df_plan_text",
     "df_argument_count", "df_argument_info", "df_set_stream", "df_execute", "df_plan_workspace",
     "df_step_count", "df_step_info", "df_execute_steps",
+    "df_serialize_artifact", "df_write_artifact", "df_load_artifact", "df_load_artifact_file",
 ]
 
 _LIB: Optional[C.CDLL] = None
@@ -113,6 +114,18 @@ class Executable:
             out.append({"uid": uid.value, "size_bytes": size.value, "alignment": alignment.value, "access": ("read", "write", "readwrite")[access.value]})
         return out
 
+    def serialize(self) -> bytes:
+        """The artifact bytes of this executable (compiler::serialize_artifact)."""
+        size = C.c_size_t(0)
+        _check(load().df_serialize_artifact(self._handle, None, C.c_size_t(0), C.byref(size)))
+        buffer = (C.c_uint8 * size.value)()
+        _check(load().df_serialize_artifact(self._handle, buffer, C.c_size_t(size.value), C.byref(size)))
+        return bytes(buffer)
+
+    def write_artifact(self, path: Union[str, Path]) -> None:
+        """Publishes the artifact at `path` by writing a temporary file beside it and renaming it."""
+        _check(load().df_write_artifact(self._handle, str(path).encode()))
+
     def set_stream(self, stream: Optional[int]) -> None:
         load().df_set_stream(self._handle, C.c_void_p(stream or None))
 
@@ -144,6 +157,17 @@ def compile_graph(document: Union[str, bytes, dict], fmt: int = FORMAT_AUTO, opt
     data = _bytes(document)
     handle = C.c_void_p()
     _check(load().df_compile(data, C.c_size_t(len(data)), C.c_int(fmt), C.c_uint32(options), C.byref(handle)))
+    return Executable(handle.value)
+
+
+def load_artifact(source: Union[bytes, str, Path]) -> Executable:
+    """An Executable from artifact bytes or from an artifact file, without recompiling (compiler::load_artifact_executable)."""
+    handle = C.c_void_p()
+    if isinstance(source, (bytes, bytearray)):
+        data = bytes(source)
+        _check(load().df_load_artifact(data, C.c_size_t(len(data)), C.byref(handle)))
+    else:
+        _check(load().df_load_artifact_file(str(source).encode(), C.byref(handle)))
     return Executable(handle.value)
 
 

@@ -58,6 +58,15 @@ int df_step_info(const df_executable* executable, int64_t step, char* label, siz
 int df_execute_steps(const df_executable* executable, int64_t first, int64_t last, const int64_t* uids, void* const* pointers,
                      size_t count, void* workspace);
 
+/* Artifacts (compiler::serialize_artifact / write_artifact / load_artifact_executable,
+   include/DeepForge/Compiler/Artifact.h:45-69 of the reference): a compiled executable as bytes or as a file
+   published by rename, and back without recompiling. df_serialize_artifact copies up to `capacity` bytes and
+   always reports the full size. */
+int df_serialize_artifact(const df_executable* executable, uint8_t* buffer, size_t capacity, size_t* size);
+int df_write_artifact(const df_executable* executable, const char* path);
+int df_load_artifact(const uint8_t* bytes, size_t size, df_executable** out);
+int df_load_artifact_file(const char* path, df_executable** out);
+
 /* Workspace planner on its own: sizes/alignments/live ranges in, offsets + total out. */
 int df_plan_workspace(size_t count, const char* const* names, const uint64_t* sizes, const uint64_t* alignments,
                       const uint64_t* live_starts, const uint64_t* live_ends, uint64_t* offsets, int64_t* placement_order,

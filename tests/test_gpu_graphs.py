@@ -207,3 +207,21 @@ def test_c5_paged_decode_full_size_sampled_sequences():
     s.run()
     doubled = s.output(4).reshape(64, 32, 128)
     assert np.array_equal(doubled, out * 2)
+
+
+@pytest.mark.parametrize("name,size", [("c2", dict(n=2, h=14, w=14)), ("c3", dict(m=128, k=128, n=128)), ("c4", dict(b=1, h=2, s=256)),
+                                       ("c5", dict(batch=3, hq=8, hkv=2, pages=32, max_len=512, min_len=100)), ("fp8", dict(m=128, k=128, n=128))])
+def test_executable_loaded_from_an_artifact_gives_the_same_bits(name, size):
+    """compile -> serialize -> load_artifact_executable: the loaded plan runs the same launches on the same buffers."""
+    wl = workloads.BUILDERS[name](**size)
+    s = harness.Session(wl)
+    s.run()
+    compiled = {uid: s.raw(uid).copy() for uid in wl.outputs}
+    loaded = runtime.load_artifact(s.exe.serialize())
+    assert loaded.plan_text() == s.exe.plan_text()
+    for uid in wl.outputs:
+        s.dev[uid].zero_()
+    s.exe = loaded
+    s.run()
+    for uid in wl.outputs:
+        assert np.array_equal(s.raw(uid), compiled[uid]), f"tensor {uid}"
