@@ -109,9 +109,27 @@ def build_host(force: bool = False) -> Path:
     return target
 
 
+def build_cli(force: bool = False) -> Path:
+    """deepforge-compile (host/cli/deepforge_compile.cpp), linked against the host library beside it."""
+    library = build_host()
+    source = PKG / "host" / "cli" / "deepforge_compile.cpp"
+    headers = sorted((ROOT / "include").rglob("*.h"))
+    target = OUT / "deepforge-compile"
+    flags = ["-std=c++20", "-O2", "-Wall", "-Wextra"]
+    stamp = _stamp([source] + headers, " ".join(flags))
+    if not force and _up_to_date(target, stamp):
+        return target
+    _run(["g++", *flags, "-I", str(ROOT / "include"), str(source), "-o", str(target), f"-L{OUT}", "-ldeepforge_b200", "-ldfgpu",
+          "-Wl,-rpath,$ORIGIN", "-lpthread"])
+    target.with_suffix(target.suffix + ".stamp").write_text(stamp)
+    assert library.exists()
+    return target
+
+
 def build_all(force: bool = False) -> None:
     build_kernels(force)
     build_host(force)
+    build_cli(force)
 
 
 if __name__ == "__main__":
