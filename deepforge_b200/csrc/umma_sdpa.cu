@@ -340,7 +340,7 @@ constexpr int kPairSlots = 4;
 #ifndef DFGPU_SDPA_POLY_EVERY
 #define DFGPU_SDPA_POLY_EVERY 4
 #endif
-constexpr int kPolyEvery = DFGPU_SDPA_POLY_EVERY;  // one pair of exponentials in kPolyEvery goes to the FMA pipe
+constexpr int kPolyEvery = DFGPU_SDPA_POLY_EVERY;  // one pair of exponentials in kPolyEvery goes to the FMA pipe (0: none)
 constexpr int kPairThreads = 608;  // 2 x 8 softmax warps (two threads per query row), loader, issuer and output-store warps
 
 struct PairSmem {
@@ -457,7 +457,7 @@ __device__ __forceinline__ void probabilities_of_16(const uint32_t (&raw)[16], u
     for (int e = 0; e < 8; ++e) {
         const uint64_t v = fma2(pack2(__uint_as_float(raw[2 * e]), __uint_as_float(raw[2 * e + 1])), scale2, bias2);
         float p0, p1;
-        if (e % kPolyEvery == 0) {
+        if (kPolyEvery > 0 && e % (kPolyEvery > 0 ? kPolyEvery : 1) == 0) {
             exp2_poly_pair(v, p0, p1);  // this pair on the FMA pipe
         } else {
             float x0, x1;
