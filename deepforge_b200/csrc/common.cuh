@@ -44,6 +44,7 @@ inline bool is_packed_row_major(const dfgpu_tensor& t) {
 inline int dtype_bytes(int dtype) {
     switch (dtype) {
         case DFGPU_F32: case DFGPU_I32: return 4;
+        case DFGPU_E5M2: return 1;
         case DFGPU_F16: case DFGPU_BF16: return 2;
         default: return 1;
     }
@@ -153,6 +154,21 @@ __device__ __forceinline__ uint32_t encode_e4m3_scalar(float v) {
     return encode_e4m3_pair(v, 0.0f) & 0xffu;
 }
 
+// E5M2 is the upper byte of binary16: decode through the half type (subnormals, infinity and NaN included).
+__device__ __forceinline__ float decode_e5m2(uint32_t code) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(code << 8)));
+}
+// f32 -> E5M2 with the reference's search semantics (lib/Compiler/Numeric.cpp:396-425, 504-632): round to nearest
+// even, |v| > 57344 (infinity included) -> 0x7b | sign, NaN -> 0x7f, a negative that rounds to zero -> +0.
+__device__ __forceinline__ uint32_t encode_e5m2_scalar(float v) {
+    if (v != v) return 0x7fu;
+    const uint32_t bits = __float_as_uint(v);
+    if ((bits - 0x80000001u) <= (0xB7000000u - 0x80000001u)) v = 0.0f;  // [-2^-17, -0): rounds to zero, the reference gives +0
+    uint16_t packed;
+    asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(packed) : "f"(0.0f), "f"(v));
+    return packed & 0xffu;
+}
+
 __device__ __forceinline__ float load_as_f32(const void* data, int dtype, int64_t offset) {
     switch (dtype) {
         case DFGPU_F32: return static_cast<const float*>(data)[offset];
@@ -160,6 +176,7 @@ __device__ __forceinline__ float load_as_f32(const void* data, int dtype, int64_
         case DFGPU_BF16: return bf16_bits_to_f32(static_cast<const uint16_t*>(data)[offset]);
         case DFGPU_E4M3: return decode_e4m3(static_cast<const uint8_t*>(data)[offset]);
         case DFGPU_E8M0: return decode_e8m0(static_cast<const uint8_t*>(data)[offset]);
+        case DFGPU_E5M2: return decode_e5m2(static_cast<const uint8_t*>(data)[offset]);
         case DFGPU_I32: return static_cast<float>(static_cast<const int32_t*>(data)[offset]);
         default: return 0.0f;
     }
@@ -171,6 +188,7 @@ __device__ __forceinline__ void store_from_f32(void* data, int dtype, int64_t of
         case DFGPU_F16: static_cast<__half*>(data)[offset] = __float2half_rn(value); break;
         case DFGPU_BF16: static_cast<uint16_t*>(data)[offset] = f32_to_bf16_bits(value); break;
         case DFGPU_E4M3: static_cast<uint8_t*>(data)[offset] = static_cast<uint8_t>(encode_e4m3_scalar(value)); break;
+        case DFGPU_E5M2: static_cast<uint8_t*>(data)[offset] = static_cast<uint8_t>(encode_e5m2_scalar(value)); break;
         default: break;
     }
 }

@@ -62,9 +62,10 @@ int build_args(const dfgpu_matmul_fp8_params& p, void* const* tensors, Fp8Args& 
     const int rank = p.c.rank;
     if (rank < 2 || rank > DFGPU_MAX_RANK || p.a.rank != rank || p.b.rank != rank)
         return fail(kInvalidShape, "MATMUL_FP8: A, B, and C must have equal rank of at least two");
-    if (p.a.dtype != DFGPU_E4M3 || p.b.dtype != DFGPU_E4M3) return fail(kUnsupported, "MATMUL_FP8: only FP8_E4M3 operands are executable");
-    if (p.c.dtype != DFGPU_F32 && p.c.dtype != DFGPU_F16 && p.c.dtype != DFGPU_BF16 && p.c.dtype != DFGPU_E4M3)
-        return fail(kUnsupported, "MATMUL_FP8: C must be FLOAT, HALF, BFLOAT16 or FP8_E4M3");
+    if ((p.a.dtype != DFGPU_E4M3 && p.a.dtype != DFGPU_E5M2) || (p.b.dtype != DFGPU_E4M3 && p.b.dtype != DFGPU_E5M2))
+        return fail(kUnsupported, "MATMUL_FP8: A and B must be FP8_E4M3 or FP8_E5M2");
+    if (p.c.dtype != DFGPU_F32 && p.c.dtype != DFGPU_F16 && p.c.dtype != DFGPU_BF16 && p.c.dtype != DFGPU_E4M3 && p.c.dtype != DFGPU_E5M2)
+        return fail(kUnsupported, "MATMUL_FP8: C must be FLOAT, HALF, BFLOAT16, FP8_E4M3 or FP8_E5M2");
     const int64_t m = p.c.dim[rank - 2], n = p.c.dim[rank - 1], k = p.a.dim[rank - 1];
     if (p.b.dim[rank - 2] != k || p.a.dim[rank - 2] != m || p.b.dim[rank - 1] != n)
         return fail(kInvalidShape, "MATMUL_FP8: matrix M, N, and K dimensions are inconsistent");

@@ -44,6 +44,7 @@ struct MxArgs {
     int32_t whole_items;   // work items that are whole 128 x BN tiles; the items after them are 128-column halves of the
     int32_t total_items;   // remaining tiles, so that the last round over the SMs takes half a tile's time instead of a whole one
     int32_t b_mn_major;
+    int32_t a_format, b_format;  // operand formats of the instruction descriptor: 0 E4M3, 1 E5M2
     // MATMUL_FP8 form: sfa == nullptr (every block scale is 1), and after the fused steps value = acc * *descale_a * *descale_b,
     // *amax_bits = max over all elements of |value| (bits of the non-negative f32, NaN canonical), C = value * *scale_c
     const float* descale_a;
@@ -269,7 +270,8 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // ---- issuing warp ----
         // instruction descriptor: E4M3 x E4M3, E8M0 scales, A K-major, B per flag, N = BN, M = 128; the two
         // scale-id fields (bits 4-5 for B, 29-30 for A) pick the K block's byte inside the scale columns
-        const uint32_t idesc_fixed = (static_cast<uint32_t>(args.b_mn_major) << 16) | (1u << 23) | (static_cast<uint32_t>(kTileM >> 4) << 24);
+        const uint32_t idesc_fixed = (static_cast<uint32_t>(args.a_format) << 7) | (static_cast<uint32_t>(args.b_format) << 10) |
+                                     (static_cast<uint32_t>(args.b_mn_major) << 16) | (1u << 23) | (static_cast<uint32_t>(kTileM >> 4) << 24);
         const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
         int stage = 0;
         uint32_t phase = 0;
@@ -857,7 +859,7 @@ int launch_matmul_mxf8(const dfgpu_matmul_params& p, void* const* tensors, bool 
 }
 
 bool matmul_fp8_umma_supported(const dfgpu_matmul_fp8_params& p) {
-    if (p.a.dtype != DFGPU_E4M3 || p.b.dtype != DFGPU_E4M3) return false;
+    if ((p.a.dtype != DFGPU_E4M3 && p.a.dtype != DFGPU_E5M2) || (p.b.dtype != DFGPU_E4M3 && p.b.dtype != DFGPU_E5M2)) return false;
     if (p.c.dtype != DFGPU_BF16 && p.c.dtype != DFGPU_F32 && p.c.dtype != DFGPU_E4M3) return false;
     const int rank = p.c.rank;
     if (rank < 2 || p.a.rank != rank || p.b.rank != rank) return false;
@@ -895,6 +897,8 @@ int launch_matmul_fp8_umma(const dfgpu_matmul_fp8_params& p, void* const* tensor
     args.n_tiles = static_cast<int>(N / bn);
     args.k_blocks = static_cast<int>(K / kBlockK);
     args.b_mn_major = b_is_k_major(p.b, K) ? 0 : 1;
+    args.a_format = p.a.dtype == DFGPU_E5M2 ? 1 : 0;
+    args.b_format = p.b.dtype == DFGPU_E5M2 ? 1 : 0;
     args.amax_bits = static_cast<unsigned int*>(tensors[3]);
     args.descale_a = static_cast<const float*>(tensors[4]);
     args.descale_b = static_cast<const float*>(tensors[5]);

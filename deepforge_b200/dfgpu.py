@@ -13,7 +13,7 @@ from typing import Iterable, Optional, Sequence
 MAX_RANK = 8
 MAX_EPILOGUE = 4
 
-F32, F16, BF16, E4M3, E8M0, I32 = range(6)
+F32, F16, BF16, E4M3, E8M0, I32, E5M2 = range(7)
 REORDER_NONE, REORDER_F8_128x4 = 0, 1
 DTYPE_BYTES = {F32: 4, F16: 2, BF16: 2, E4M3: 1, E8M0: 1, I32: 4}
 

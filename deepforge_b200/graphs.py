@@ -62,7 +62,8 @@ def matmul_fp8_node(name: str, a: int, b: int, descale_a: int, descale_b: int, s
 
 
 def matmul_fp8(m: int, k: int, n: int, c_type: str = "FLOAT", batch: Sequence[int] = (1,), b_k_major: bool = False,
-               a_batch: Optional[Sequence[int]] = None, b_batch: Optional[Sequence[int]] = None) -> dict:
+               a_batch: Optional[Sequence[int]] = None, b_batch: Optional[Sequence[int]] = None, a_type: str = "FP8_E4M3",
+               b_type: str = "FP8_E4M3") -> dict:
     """One MATMUL_FP8 node in the shape of the reference's own test graph (test/Compiler/SpecializedOpsTest.cpp:370-390):
     UIDs 21 A, 22 B, 23 Descale_A, 24 Descale_B, 25 Scale_C, 26 C, 27 Amax_C. `b_k_major` stores B as [N, K]."""
     batch = list(batch)
@@ -72,7 +73,7 @@ def matmul_fp8(m: int, k: int, n: int, c_type: str = "FLOAT", batch: Sequence[in
     if b_k_major:
         b_strides = contiguous(b_dims[:-2] + [n, k])
         b_strides[-2], b_strides[-1] = b_strides[-1], b_strides[-2]
-    tensors = [tensor(21, "A", a_dims, "FP8_E4M3"), tensor(22, "B", b_dims, "FP8_E4M3", strides=b_strides),
+    tensors = [tensor(21, "A", a_dims, a_type), tensor(22, "B", b_dims, b_type, strides=b_strides),
                tensor(23, "Descale_A", [1]), tensor(24, "Descale_B", [1]), tensor(25, "Scale_C", [1]),
                tensor(26, "C", batch + [m, n], c_type), tensor(27, "Amax_C", [1])]
     return document("matmul-fp8", [matmul_fp8_node("matmul_fp8", 21, 22, 23, 24, 25, 26, 27)], tensors, io=c_type, graph_uid=5003)

@@ -171,7 +171,7 @@ Status check_workspace(WorkspacePlan const& workspace) {
     return Status::ok();
 }
 
-bool tensor_in_range(dfgpu_tensor const& t) { return t.rank >= 0 && t.rank <= DFGPU_MAX_RANK && t.dtype >= 0 && t.dtype <= DFGPU_I32; }
+bool tensor_in_range(dfgpu_tensor const& t) { return t.rank >= 0 && t.rank <= DFGPU_MAX_RANK && t.dtype >= 0 && t.dtype <= DFGPU_E5M2; }
 
 bool params_in_range(KernelParams const& params) {
     return std::visit([](auto const& p) {

@@ -87,6 +87,7 @@ std::optional<int> to_dfgpu_dtype(DataType type) {
         case DataType::kFp8E4M3: return DFGPU_E4M3;
         case DataType::kFp8E8M0: return DFGPU_E8M0;
         case DataType::kInt32: return DFGPU_I32;
+        case DataType::kFp8E5M2: return DFGPU_E5M2;
         default: return std::nullopt;
     }
 }
@@ -104,9 +105,11 @@ struct Lowering {
 
     TensorDesc const& tensor(std::int64_t uid) const { return graph.tensors.at(uid); }
 
-    Status describe(std::int64_t uid, dfgpu_tensor& out, std::string const& where) const {
+    // FP8_E5M2 is executable as a MATMUL_FP8 operand or output only (`allow_e5m2`).
+    Status describe(std::int64_t uid, dfgpu_tensor& out, std::string const& where, bool allow_e5m2 = false) const {
         auto const& t = tensor(uid);
         auto dtype = to_dfgpu_dtype(t.data_type);
+        if (dtype && *dtype == DFGPU_E5M2 && !allow_e5m2) dtype.reset();
         if (!dtype) return fail(ErrorCode::kUnsupportedDataType, where, "tensor '" + t.name + "' has data type " + std::string(import::data_type_name(t.data_type)) + ", which this backend does not execute");
         if (t.dim.size() > DFGPU_MAX_RANK) return fail(ErrorCode::kInvalidShape, where, "tensor rank above 8");
         out = dfgpu_tensor{};
@@ -438,14 +441,13 @@ Status lower_matmul_fp8(Lowering& low, std::size_t index) {
         if (std::find(allowed.begin(), allowed.end(), type) != allowed.end()) return Status::ok();
         return fail(ErrorCode::kUnsupportedDataType, where + "." + name, std::string(import::data_type_name(type)) + " is not supported on this port");
     };
-    // the reference also takes FP8_E5M2 here; this backend executes the E4M3 codec only
-    if ((status = typed(*a, "A", {DataType::kFp8E4M3})).is_bad()) return status;
-    if ((status = typed(*b, "B", {DataType::kFp8E4M3})).is_bad()) return status;
-    if ((status = typed(*c, "C", {DataType::kFp8E4M3, DataType::kFloat32, DataType::kFloat16, DataType::kBFloat16})).is_bad()) return status;
+    if ((status = typed(*a, "A", {DataType::kFp8E4M3, DataType::kFp8E5M2})).is_bad()) return status;
+    if ((status = typed(*b, "B", {DataType::kFp8E4M3, DataType::kFp8E5M2})).is_bad()) return status;
+    if ((status = typed(*c, "C", {DataType::kFp8E4M3, DataType::kFp8E5M2, DataType::kFloat32, DataType::kFloat16, DataType::kBFloat16})).is_bad()) return status;
     dfgpu_matmul_fp8_params params{};
-    if ((status = low.describe(*a, params.a, where)).is_bad()) return status;
-    if ((status = low.describe(*b, params.b, where)).is_bad()) return status;
-    if ((status = low.describe(*c, params.c, where)).is_bad()) return status;
+    if ((status = low.describe(*a, params.a, where, true)).is_bad()) return status;
+    if ((status = low.describe(*b, params.b, where, true)).is_bad()) return status;
+    if ((status = low.describe(*c, params.c, where, true)).is_bad()) return status;
     auto const& ta = low.tensor(*a);
     auto const& tb = low.tensor(*b);
     auto const& tc = low.tensor(*c);

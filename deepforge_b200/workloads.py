@@ -18,8 +18,8 @@ import numpy as np
 from . import graphs, synthetic
 
 BASE_SEED = 20261125
-NP_DTYPE = {"FLOAT": np.float32, "BFLOAT16": np.uint16, "HALF": np.float16, "FP8_E4M3": np.uint8, "FP8_E8M0": np.uint8, "INT32": np.int32}
-DTYPE_BYTES = {"FLOAT": 4, "BFLOAT16": 2, "HALF": 2, "FP8_E4M3": 1, "FP8_E8M0": 1, "INT32": 4}
+NP_DTYPE = {"FLOAT": np.float32, "BFLOAT16": np.uint16, "HALF": np.float16, "FP8_E4M3": np.uint8, "FP8_E5M2": np.uint8, "FP8_E8M0": np.uint8, "INT32": np.int32}
+DTYPE_BYTES = {"FLOAT": 4, "BFLOAT16": 2, "HALF": 2, "FP8_E4M3": 1, "FP8_E5M2": 1, "FP8_E8M0": 1, "INT32": 4}
 
 
 @dataclasses.dataclass
@@ -148,22 +148,28 @@ def c3(m=4096, k=4096, n=4096, io="BFLOAT16", c_type="BFLOAT16", first_row=0) ->
 
 
 def matmul_fp8(m=4096, k=4096, n=4096, c_type="BFLOAT16", batch=(1,), b_k_major=False, a_batch=None, b_batch=None,
-               scalars=(0.5, 0.25, 0.125), exact=True) -> Workload:
+               scalars=(0.5, 0.25, 0.125), exact=True, a_type="FP8_E4M3", b_type="FP8_E4M3") -> Workload:
     """One MATMUL_FP8 node (the first row of the "next" list after the five configurations). Operands are E4M3 codes
     with exponent fields 6..8 (|value| in [0.5, 3.75], one in sixteen a zero): with `exact` every partial sum of up to
     2^10 products is exactly representable in f32, so the result does not depend on the order of the additions and
     the tensor-core kernel can be compared bit for bit; without it the exponent fields span 1..9."""
-    doc = graphs.matmul_fp8(m, k, n, c_type, batch, b_k_major, a_batch, b_batch)
+    doc = graphs.matmul_fp8(m, k, n, c_type, batch, b_k_major, a_batch, b_batch, a_type, b_type)
     seed = BASE_SEED + 8
 
-    def codes(uid: int, count: int):
+    def codes(uid: int, count: int, data_type: str):
         def make():
             r = synthetic.raw_u64(seed, uid, count, 0)
-            mantissa = (r & np.uint64(7)).astype(np.uint8)
-            span = 3 if exact else 9
-            exponent = ((r >> np.uint64(3)) % np.uint64(span)).astype(np.uint8) + np.uint8(6 if exact else 1)
             sign = ((r >> np.uint64(16)) & np.uint64(1)).astype(np.uint8)
-            out = (sign << 7) | (exponent << 3) | mantissa
+            if data_type == "FP8_E5M2":  # two mantissa bits, bias 15: the same [0.5, 3.5] (or wider) value range
+                mantissa = (r & np.uint64(3)).astype(np.uint8)
+                span = 3 if exact else 9
+                exponent = ((r >> np.uint64(3)) % np.uint64(span)).astype(np.uint8) + np.uint8(14 if exact else 9)
+                out = (sign << 7) | (exponent << 2) | mantissa
+            else:
+                mantissa = (r & np.uint64(7)).astype(np.uint8)
+                span = 3 if exact else 9
+                exponent = ((r >> np.uint64(3)) % np.uint64(span)).astype(np.uint8) + np.uint8(6 if exact else 1)
+                out = (sign << 7) | (exponent << 3) | mantissa
             out[((r >> np.uint64(20)) & np.uint64(15)) == 0] = 0
             return out.astype(np.uint8)
         return make
@@ -177,10 +183,10 @@ def matmul_fp8(m=4096, k=4096, n=4096, c_type="BFLOAT16", batch=(1,), b_k_major=
     batches = int(np.prod(batch))
     return Workload(
         name="matmul_fp8", config=8, document=doc,
-        description={"workload": f"MATMUL_FP8 E4M3 x E4M3 -> {c_type}, M={m} K={k} N={n} batch={list(batch)}, scalar descales, Amax_C"},
+        description={"workload": f"MATMUL_FP8 {a_type[4:]} x {b_type[4:]} -> {c_type}, M={m} K={k} N={n} batch={list(batch)}, scalar descales, Amax_C"},
         metric="matmul_fp8_throughput", unit="TFLOP/s", flops=2.0 * batches * m * n * k,
         bytes=float(count(21) + count(22) + batches * m * n * DTYPE_BYTES[c_type]), bound="tensor",
-        inputs={21: codes(21, count(21)), 22: codes(22, count(22)), 23: scalar(scalars[0]), 24: scalar(scalars[1]), 25: scalar(scalars[2])},
+        inputs={21: codes(21, count(21), a_type), 22: codes(22, count(22), b_type), 23: scalar(scalars[0]), 24: scalar(scalars[1]), 25: scalar(scalars[2])},
         outputs=[26, 27])
 
 

@@ -41,7 +41,8 @@ enum {
     DFGPU_BF16 = 2,
     DFGPU_E4M3 = 3,
     DFGPU_E8M0 = 4,
-    DFGPU_I32 = 5
+    DFGPU_I32 = 5,
+    DFGPU_E5M2 = 6 /* FP8_E5M2: MATMUL_FP8 operands and output only */
 };
 
 enum { DFGPU_REORDER_NONE = 0, DFGPU_REORDER_F8_128x4 = 1 };
@@ -178,9 +179,9 @@ int dfgpu_matmul(const dfgpu_matmul_params*, void* const* tensors, void* scratch
    Replaces emit_matmul_fp8 (lib/Compiler/SpecializedGraph.cpp:982-1090; checks
    :409-496): per element value = (sum_k a*b in f32) * Descale_A * Descale_B,
    Amax_C = max |value| over all elements (NaN stays NaN), C = store(value * Scale_C).
-   A and B are FP8_E4M3 codes, C is FLOAT, HALF, BFLOAT16 or FP8_E4M3 (encoded with the
-   reference's rounding: ties to even, saturation at 448, a negative that rounds to zero
-   gives +0, NaN gives 0x7f). The three scales and Amax_C are one-element FLOAT tensors in
+   A and B are FP8_E4M3 or FP8_E5M2 codes, C is FLOAT, HALF, BFLOAT16, FP8_E4M3 or FP8_E5M2 (encoded with the
+   reference's rounding: ties to even, saturation at 448 / 57344, a negative that rounds to
+   zero gives +0, NaN gives 0x7f). The three scales and Amax_C are one-element FLOAT tensors in
    device memory. tensors: {A, B, C, Amax_C, Descale_A, Descale_B, Scale_C}.
    The extent-override inputs (M_override, N_override, K_override) are not executable.
    Two launches: Amax_C is cleared, then one kernel computes C and folds Amax_C with an

@@ -32,6 +32,53 @@ float dfo_decode_e4m3(uint8_t code) {
     return sign ? -value : value;
 }
 
+/* Numeric.cpp:127-146 */
+float dfo_decode_e5m2(uint8_t code) {
+    int sign = (code & 0x80u) != 0;
+    unsigned exponent = (code >> 2) & 0x1fu;
+    unsigned mantissa = code & 0x03u;
+    float value;
+    if (exponent == 0) {
+        value = ldexpf((float)mantissa, -16);
+    } else if (exponent == 31) {
+        if (mantissa != 0) return NAN;
+        value = INFINITY;
+    } else {
+        value = ldexpf(1.0f + (float)mantissa / 4.0f, (int)exponent - 15);
+    }
+    return sign ? -value : value;
+}
+
+/* Numeric.cpp:396-425, 504-632, E5M2 branch: the same search; candidates whose
+   low 7 bits are >= 124 (infinity and the NaNs) are skipped, |v| > 57344
+   saturates to 0x7b|sign, NaN is 0x7f. */
+uint8_t dfo_encode_e5m2(float value) {
+    uint8_t best = 0;
+    float best_difference = fabsf(value - dfo_decode_e5m2(0));
+    for (unsigned candidate = 0; candidate < 256; ++candidate) {
+        int valid = (candidate % 128u) < 124u;
+        if (!valid) continue;
+        float difference = fabsf(value - dfo_decode_e5m2((uint8_t)candidate));
+        int better = difference < best_difference;
+        int equal = difference == best_difference;
+        int candidate_even = (candidate & 1u) == 0;
+        int best_odd = (best & 1u) != 0;
+        if (better || (equal && candidate_even && best_odd)) {
+            best = (uint8_t)candidate;
+            best_difference = difference;
+        }
+    }
+    uint32_t bits;
+    memcpy(&bits, &value, 4);
+    int negative = (bits & 0x80000000u) != 0;
+    float absolute = fabsf(value);
+    uint8_t result = best;
+    if (absolute == 0.0f) result = negative ? 0x80 : 0x00;
+    if (absolute > 57344.0f) result = (uint8_t)(0x7b | (negative ? 0x80 : 0x00));
+    if (value != value) result = 0x7f;
+    return result;
+}
+
 /* Numeric.cpp:148-153 */
 float dfo_decode_e8m0(uint8_t code) {
     if (code == 0xffu) return NAN;
@@ -236,6 +283,7 @@ static float load_f32(const dfo_tensor* t, const void* data, int64_t offset) {
         case DFO_BF16: return dfo_bf16_to_f32(((const uint16_t*)data)[offset]);
         case DFO_E4M3: return dfo_decode_e4m3(((const uint8_t*)data)[offset]);
         case DFO_E8M0: return dfo_decode_e8m0(((const uint8_t*)data)[offset]);
+        case DFO_E5M2: return dfo_decode_e5m2(((const uint8_t*)data)[offset]);
         case DFO_I32: return (float)((const int32_t*)data)[offset];
         default: return NAN;
     }
@@ -248,6 +296,7 @@ static void store_f32(const dfo_tensor* t, void* data, int64_t offset, float val
         case DFO_F16: ((uint16_t*)data)[offset] = dfo_f32_to_f16(value); break;
         case DFO_BF16: ((uint16_t*)data)[offset] = dfo_f32_to_bf16(value); break;
         case DFO_E4M3: ((uint8_t*)data)[offset] = dfo_encode_e4m3(value); break;
+        case DFO_E5M2: ((uint8_t*)data)[offset] = dfo_encode_e5m2(value); break;
         case DFO_E8M0: ((uint8_t*)data)[offset] = dfo_encode_e8m0(value); break;
         default: break;
     }

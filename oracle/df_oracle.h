@@ -31,7 +31,8 @@ enum {
     DFO_BF16 = 2,
     DFO_E4M3 = 3,
     DFO_E8M0 = 4,
-    DFO_I32 = 5
+    DFO_I32 = 5,
+    DFO_E5M2 = 6
 };
 
 enum { DFO_REORDER_NONE = 0, DFO_REORDER_F8_128x4 = 1 };
@@ -49,8 +50,10 @@ typedef struct dfo_tensor {
 /* codecs */
 float dfo_decode_e4m3(uint8_t code);
 float dfo_decode_e8m0(uint8_t code);
+float dfo_decode_e5m2(uint8_t code);
 uint8_t dfo_encode_e4m3(float value);
 uint8_t dfo_encode_e8m0(float value);
+uint8_t dfo_encode_e5m2(float value);
 uint16_t dfo_f32_to_bf16(float value);
 float dfo_bf16_to_f32(uint16_t bits);
 uint16_t dfo_f32_to_f16(float value);

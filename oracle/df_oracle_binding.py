@@ -45,6 +45,10 @@ def _declare(l: C.CDLL) -> C.CDLL:
     l.dfo_encode_e4m3.argtypes = [C.c_float]
     l.dfo_encode_e8m0.restype = C.c_uint8
     l.dfo_encode_e8m0.argtypes = [C.c_float]
+    l.dfo_decode_e5m2.restype = C.c_float
+    l.dfo_decode_e5m2.argtypes = [C.c_uint8]
+    l.dfo_encode_e5m2.restype = C.c_uint8
+    l.dfo_encode_e5m2.argtypes = [C.c_float]
     l.dfo_block_scale_code.restype = C.c_uint8
     l.dfo_block_scale_code.argtypes = [C.c_float]
     l.dfo_f32_to_bf16.restype = C.c_uint16

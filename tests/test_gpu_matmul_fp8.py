@@ -44,7 +44,7 @@ def as_stored(reference_f32, data_type):
 
 def check(session, reference, c_type):
     actual = session.output(26)
-    expected = reference[26] if c_type == "FP8_E4M3" else as_stored(reference[26], c_type)
+    expected = reference[26] if c_type.startswith("FP8") else as_stored(reference[26], c_type)
     assert np.array_equal(actual, expected), f"{int(np.sum(actual != expected))} of {actual.size} elements differ"
     assert session.output(27).tobytes() == reference[27].astype(np.float32).tobytes()
 
@@ -78,6 +78,30 @@ def test_tcgen05_kernel_matches_oracle(c_type, shape):
     if shape["m"] <= 384:
         session, _ = run_both(wl, options=runtime.NO_TENSOR_CORES)
         check(session, reference, c_type)
+
+
+@pytest.mark.parametrize("a_type,b_type", [("FP8_E5M2", "FP8_E5M2"), ("FP8_E5M2", "FP8_E4M3"), ("FP8_E4M3", "FP8_E5M2")])
+@pytest.mark.parametrize("shape,c_type", [(dict(m=9, k=33, n=5), "FLOAT"), (dict(m=9, k=33, n=5), "FP8_E5M2"), (dict(m=256, k=512, n=384), "BFLOAT16"),
+                                          (dict(m=128, k=256, n=128, b_k_major=True), "FP8_E4M3"), (dict(m=128, k=128, n=256), "FP8_E5M2")])
+def test_e5m2_operands_and_output(a_type, b_type, shape, c_type):
+    wl = workloads.matmul_fp8(c_type=c_type, a_type=a_type, b_type=b_type, **shape)
+    session, reference = run_both(wl)
+    tensor_core = shape["m"] >= 128 and c_type != "FP8_E5M2"
+    assert f"kernel={dfgpu.MATMUL_FP8_UMMA if tensor_core else dfgpu.MATMUL_FP8_SCALAR}" in session.exe.plan_text()
+    check(session, reference, c_type)
+
+
+def test_e5m2_output_saturates_and_keeps_nan():
+    wl = workloads.matmul_fp8(8, 16, 8, c_type="FP8_E5M2", scalars=(1.0, 1.0, 65536.0))
+    codes = wl.inputs[21]()
+    codes[5] = 0x7f
+    session, reference = run_both(wl, overrides={21: codes})
+    actual = session.output(26)
+    assert np.array_equal(actual, reference[26])
+    assert np.all(actual[:8] == 0x7f) and np.any((actual[8:] & 0x7f) == 0x7b) and np.all((actual[8:] & 0x7f) <= 0x7b)
+    wl = workloads.matmul_fp8(8, 16, 8, c_type="FP8_E5M2", scalars=(1.0, 1.0, 2.0 ** -22))
+    session, reference = run_both(wl)
+    assert np.array_equal(session.output(26), reference[26]) and not np.any(session.output(26) == 0x80)
 
 
 @pytest.mark.parametrize("shape", [dict(m=4, k=8, n=4), dict(m=128, k=128, n=128)])

@@ -45,6 +45,21 @@ def test_oracle_amax_keeps_nan_and_c_encodes_like_the_reference():
     assert graph_oracle.run(doc, values)[26].tolist() == [0x00, 0x00]  # 2^-11 ties to even (zero); -2^-13 rounds to +0
 
 
+def test_e5m2_codec_matches_the_reference_known_answers():
+    """test/Compiler/SpecializedOpsTest.cpp:642-659 (decode 0x3c, 0x40, 0xc0, 0x38) and :716-735 (1, 2, -4, 8 divided by
+    their block scales 2^-14, 2^-12 encode to 0x74, 0x78, 0xf4, 0x78); encoding rules of lib/Compiler/Numeric.cpp:396-425."""
+    lib = oracle.lib()
+    assert [lib.dfo_decode_e5m2(code) for code in (0x3c, 0x40, 0xc0, 0x38)] == [1.0, 2.0, -2.0, 0.5]
+    assert [lib.dfo_encode_e5m2(value) for value in (16384.0, 32768.0, -16384.0, 32768.0)] == [0x74, 0x78, 0xf4, 0x78]
+    assert lib.dfo_decode_e5m2(0x7c) == float("inf") and np.isnan(lib.dfo_decode_e5m2(0x7e)) and lib.dfo_decode_e5m2(0x01) == 2.0 ** -16
+    assert lib.dfo_encode_e5m2(float("inf")) == 0x7b and lib.dfo_encode_e5m2(-1e9) == 0xfb and lib.dfo_encode_e5m2(57344.0) == 0x7b
+    assert lib.dfo_encode_e5m2(float("nan")) == 0x7f and lib.dfo_encode_e5m2(-0.0) == 0x80 and lib.dfo_encode_e5m2(-2.0 ** -18) == 0x00
+    assert lib.dfo_encode_e5m2(1.125) == 0x3c and lib.dfo_encode_e5m2(1.375) == 0x3e  # ties go to the even code
+    for code in range(256):  # every finite code survives a round trip
+        if (code & 0x7f) < 0x7c:
+            assert lib.dfo_encode_e5m2(lib.dfo_decode_e5m2(code)) == code
+
+
 def test_plans_and_argument_table():
     small = runtime.compile_graph(graphs.matmul_fp8(2, 2, 2))
     assert small.launch_count == 1 and small.workspace_size == 0
@@ -59,6 +74,10 @@ def test_plans_and_argument_table():
     # what the tcgen05 kernel does not take goes to the general one: HALF output, K not a multiple of 128, batches
     for doc in (graphs.matmul_fp8(256, 256, 256, c_type="HALF"), graphs.matmul_fp8(256, 192, 256), graphs.matmul_fp8(128, 128, 128, batch=(2,))):
         assert f"matmul_fp8 kernel={dfgpu.MATMUL_FP8_SCALAR}" in runtime.compile_graph(doc).plan_text()
+    # E5M2 operands run on the same tensor-core kernel; an E5M2 output goes to the general one
+    mixed = runtime.compile_graph(graphs.matmul_fp8(256, 256, 256, a_type="FP8_E5M2", b_type="FP8_E4M3", c_type="BFLOAT16"))
+    assert f"matmul_fp8 kernel={dfgpu.MATMUL_FP8_UMMA}" in mixed.plan_text()
+    assert f"matmul_fp8 kernel={dfgpu.MATMUL_FP8_SCALAR}" in runtime.compile_graph(graphs.matmul_fp8(256, 256, 256, c_type="FP8_E5M2")).plan_text()
     off = runtime.compile_graph(graphs.matmul_fp8(256, 256, 256), options=runtime.NO_TENSOR_CORES)
     assert f"matmul_fp8 kernel={dfgpu.MATMUL_FP8_SCALAR}" in off.plan_text()
 
