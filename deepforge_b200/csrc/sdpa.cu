@@ -21,7 +21,11 @@ namespace dfgpu {
 namespace {
 
 struct SdpaArgs {
-    View q, k, v, o, stats, max, sum_exp, seq_q, seq_kv, table_k, table_v;
+    View q, k, v, o, stats, max, sum_exp, seq_q, seq_kv, table_k, table_v, bias;
+    const void* bias_data;
+    int32_t alibi;
+    float alibi_slope_scale;  // -8 / n, n the largest power of two not above the head count
+    int32_t alibi_n;
     const void* q_data;
     const void* k_data;
     const void* v_data;
@@ -128,6 +132,17 @@ sdpa_rowwise_kernel(SdpaArgs a, int64_t rows) {
                 }
             }
             score = __fmul_rn(a.scale, dot);
+            if (a.bias.rank) {
+                const int64_t offset = (a.bias.dim[0] == 1 ? 0 : ib) * a.bias.stride[0] + (a.bias.dim[1] == 1 ? 0 : ih) * a.bias.stride[1] +
+                                       (a.bias.dim[2] == 1 ? 0 : iq) * a.bias.stride[2] + (a.bias.dim[3] == 1 ? 0 : ikv) * a.bias.stride[3];
+                score = __fadd_rn(score, load_as_f32(a.bias_data, a.bias.dtype, offset));
+            }
+            if (a.alibi) {
+                // slope of head h: 2^(-8 (h+1) / n) for h < n, else 2^(-8 (2 (h-n) + 1) / 2 / n)
+                const float position = ih < a.alibi_n ? static_cast<float>(ih + 1) : (static_cast<float>(2 * (ih - a.alibi_n) + 1) * 0.5f);
+                const float slope = exp2f(__fmul_rn(a.alibi_slope_scale, position));
+                score = __fadd_rn(score, __fmul_rn(static_cast<float>(ikv - iq), slope));
+            }
         }
         float chunk_max = score;
 #pragma unroll
@@ -453,6 +468,19 @@ int build_args(const dfgpu_sdpa_params& p, void* const* tensors, SdpaArgs& a) {
         if (p.padding_mask && (!a.seq_q_data || !a.seq_kv_data)) return fail(kInvalidArgument, "SDPA: null sequence length pointer");
         if ((paged_k && !a.table_k_data) || (paged_v && !a.table_v_data)) return fail(kInvalidArgument, "SDPA: null page table pointer");
     }
+    a.bias = make_view(p.bias);
+    a.bias_data = (tensors && p.bias.rank) ? tensors[11] : nullptr;  // callers without a bias may pass 11 pointers
+    if (p.bias.rank) {
+        if (!valid_tensor(p.bias) || p.bias.rank != 4 || !float_type(p.bias.dtype)) return fail(kInvalidShape, "SDPA: bias must be a rank-4 FLOAT, HALF or BFLOAT16 tensor");
+        const int64_t extent[4] = {p.q.dim[0], hq, p.q.dim[2], p.s_kv};
+        for (int i = 0; i < 4; ++i)
+            if (p.bias.dim[i] != 1 && p.bias.dim[i] != extent[i]) return fail(kInvalidShape, "SDPA: bias is not broadcast-compatible with attention scores");
+        if (tensors && !a.bias_data) return fail(kInvalidArgument, "SDPA: null bias pointer");
+    }
+    a.alibi = p.alibi_mask;
+    a.alibi_n = 1;
+    while (2 * static_cast<int64_t>(a.alibi_n) <= hq) a.alibi_n *= 2;
+    a.alibi_slope_scale = -8.0f / static_cast<float>(a.alibi_n);
     a.scale = p.attn_scale;
     a.padding = p.padding_mask;
     a.has_left = p.has_left_bound;
@@ -484,10 +512,13 @@ int decode_chunks(const dfgpu_sdpa_params& p) { return static_cast<int>((p.s_kv 
 
 int choose_kernel(const dfgpu_sdpa_params& p, int& kernel) {
     int automatic = DFGPU_SDPA_ROWWISE;
-    if (decode_umma_supported(p)) automatic = DFGPU_SDPA_PAGED_DECODE_UMMA;
+    const bool plain_scores = p.bias.rank == 0 && !p.alibi_mask;  // only the general kernel adds bias or ALiBi
+    if (!plain_scores) automatic = DFGPU_SDPA_ROWWISE;
+    else if (decode_umma_supported(p)) automatic = DFGPU_SDPA_PAGED_DECODE_UMMA;
     else if (decode_supported(p)) automatic = DFGPU_SDPA_PAGED_DECODE;
     else if (sdpa_umma_supported(p)) automatic = DFGPU_SDPA_UMMA;
     kernel = p.kernel == DFGPU_SDPA_AUTO ? automatic : p.kernel;
+    if (!plain_scores && kernel != DFGPU_SDPA_ROWWISE) return fail(kUnsupported, "SDPA: bias and ALiBi run on the general kernel only");
     if (kernel == DFGPU_SDPA_ROWWISE) {
         if (p.q.dim[3] > kRowwiseMaxD || p.v.dim[3] > kRowwiseMaxD) return fail(kUnsupported, "SDPA: head dimension above %d", kRowwiseMaxD);
         return kOk;
@@ -626,8 +657,8 @@ extern "C" int dfgpu_sdpa_paged_decode_static(const dfgpu_sdpa_params* p, void* 
     SdpaArgs a;
     int status = build_args(*p, tensors, a);
     if (status) return status;
-    if (!decode_supported(*p))
-        return fail(kUnsupported, "SDPA static decode: needs Sq=1, bf16, D=128, paged K and V, group size 1/2/4/8");
+    if (!decode_supported(*p) || p->bias.rank != 0 || p->alibi_mask)
+        return fail(kUnsupported, "SDPA static decode: needs Sq=1, bf16, D=128, paged K and V, group size 1/2/4/8, no bias or ALiBi");
     if (!aligned16(a.q_data) || !aligned16(a.k_data) || !aligned16(a.v_data))
         return fail(kInvalidArgument, "SDPA static decode: needs 16-byte aligned Q, K and V");
     const int chunks = decode_chunks(*p);

@@ -97,7 +97,8 @@ class SdpaParams(C.Structure):
                 ("sum_exp", Tensor), ("seq_q", Tensor), ("seq_kv", Tensor), ("page_table_k", Tensor),
                 ("page_table_v", Tensor), ("attn_scale", C.c_float), ("padding_mask", C.c_int32),
                 ("has_left_bound", C.c_int32), ("has_right_bound", C.c_int32), ("left_bound", C.c_int64),
-                ("right_bound", C.c_int64), ("bottom_right", C.c_int32), ("kernel", C.c_int32), ("s_kv", C.c_int64)]
+                ("right_bound", C.c_int64), ("bottom_right", C.c_int32), ("kernel", C.c_int32), ("s_kv", C.c_int64),
+                ("bias", Tensor), ("alibi_mask", C.c_int32), ("reserved", C.c_int32)]
 
 
 # every symbol include/dfgpu.h declares
@@ -191,7 +192,9 @@ def matmul_fp8(params, a, b, c, amax, descale_a, descale_b, scale_c, scratch=Non
 
 
 def sdpa_forward(params, pointers: Sequence[Optional[int]], scratch=None, stream=None):
-    assert len(pointers) == 11
+    """pointers: Q, K, V, O, Stats, Max, Sum_exp, SEQ_LEN_Q, SEQ_LEN_KV, Page_table_K, Page_table_V[, Bias]."""
+    assert len(pointers) in (11, 12)
+    pointers = list(pointers) + [None] * (12 - len(pointers))
     _call("dfgpu_sdpa_forward", params, pointers, scratch, stream)
 
 

@@ -90,8 +90,8 @@ def dequantize_node(name: str, x: int, scale: int, y: int, blocks: Sequence[int]
 
 
 def sdpa_node(name: str, inputs: Dict[str, int], outputs: Dict[str, int], scale: float, padding: bool, stats: bool, max_seq_len_kv=None,
-              left_bound=None, right_bound=None, alignment="TOP_LEFT") -> dict:
-    return {"tag": "SDPA", "name": name, "inputs": inputs, "outputs": outputs, "generate_stats": stats, "alibi_mask": False,
+              left_bound=None, right_bound=None, alignment="TOP_LEFT", alibi: bool = False) -> dict:
+    return {"tag": "SDPA", "name": name, "inputs": inputs, "outputs": outputs, "generate_stats": stats, "alibi_mask": alibi,
             "padding_mask": padding, "dropout_probability": None, "attn_scale_value": scale, "max_seq_len_kv": max_seq_len_kv,
             "mma_core_mode": None, "left_bound": left_bound, "right_bound": right_bound, "diagonal_alignment": alignment,
             "implementation": "AUTO", "is_mxfp8": False, "unfuse_fma": False}

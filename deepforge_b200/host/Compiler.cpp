@@ -551,14 +551,16 @@ Status lower_dequantize(Lowering& low, std::size_t index) {
 Status lower_sdpa(Lowering& low, std::size_t index) {
     auto const& node = low.graph.nodes[index];
     auto const where = node_path(index, node);
-    for (auto name : {"Attn_scale", "Bias", "Seed", "Offset", "Dropout_mask", "Dropout_scale", "Block_mask", "Descale_Q", "Descale_K", "Descale_V",
+    for (auto name : {"Attn_scale", "Seed", "Offset", "Dropout_mask", "Dropout_scale", "Block_mask", "Descale_Q", "Descale_K", "Descale_V",
                       "Descale_S", "Scale_S", "Scale_O", "SINK_TOKEN"})
         if (port(node.inputs, name)) return fail(ErrorCode::kUnsupportedOperation, where, std::string("input port ") + name + " is outside the GPU hot path");
     for (auto name : {"RNG_DUMP", "Amax_S", "Amax_O"})
         if (port(node.outputs, name)) return fail(ErrorCode::kUnsupportedOperation, where, std::string("output port ") + name + " is outside the GPU hot path");
     auto q = port(node.inputs, "Q"), k = port(node.inputs, "K"), v = port(node.inputs, "V"), o = port(node.outputs, "O");
     if (!q || !k || !v || !o) return fail(ErrorCode::kInvalidValue, where, "SDPA ports are incomplete");
-    if (get_bool(node, "alibi_mask").value_or(true)) return fail(ErrorCode::kUnsupportedOperation, where, "alibi_mask is outside the GPU hot path");
+    auto alibi = get_bool(node, "alibi_mask");
+    if (!alibi) return fail(ErrorCode::kInvalidValue, where, "alibi_mask must be a boolean");
+    auto bias = port(node.inputs, "Bias");
     if (!is_null(node, "dropout_probability")) return fail(ErrorCode::kUnsupportedOperation, where, "dropout is outside the GPU hot path");
     if (get_bool(node, "is_mxfp8").value_or(true)) return fail(ErrorCode::kUnsupportedOperation, where, "is_mxfp8 must be false");
     auto padding = get_bool(node, "padding_mask"), stats_flag = get_bool(node, "generate_stats");
@@ -607,15 +609,32 @@ Status lower_sdpa(Lowering& low, std::size_t index) {
     std::int64_t capacity_k = table_k ? params.page_table_k.dim[2] * params.k.dim[2] : params.k.dim[2];
     std::int64_t capacity_v = table_v ? params.page_table_v.dim[2] * params.v.dim[2] : params.v.dim[2];
     params.s_kv = max_len ? *max_len : std::min(capacity_k, capacity_v);
+    if (bias) {
+        // reference checks: lib/Compiler/SequenceGraph.cpp:692-697 (rank 4; the key length of a both-paged graph without
+        // max_seq_len_kv comes from the bias), :879-883 (broadcast onto [B, Hq, Sq, Skv])
+        if ((status = low.describe(*bias, params.bias, where)).is_bad()) return status;
+        if (params.bias.rank != 4) return fail(ErrorCode::kInvalidShape, where + ".Bias", "Bias must have rank 4");
+        if (!max_len && table_k && table_v) params.s_kv = params.bias.dim[3];
+    }
     if (params.s_kv <= 0 || params.s_kv > capacity_k || params.s_kv > capacity_v)
         return fail(ErrorCode::kInvalidShape, where, "key/value capacity is below the logical sequence length");
+    if (bias) {
+        const std::int64_t scores[4] = {params.q.dim[0], params.q.dim[1], params.q.dim[2], params.s_kv};
+        for (int axis = 0; axis < 4; ++axis)
+            if (params.bias.dim[axis] != 1 && params.bias.dim[axis] != scores[axis])
+                return fail(ErrorCode::kInvalidShape, where + ".Bias", "bias is not broadcast-compatible with attention scores");
+    }
+    params.alibi_mask = *alibi;
+    // lib/Compiler/SequenceGraph.cpp:951-955
+    if (params.bottom_right && params.has_right_bound && (bias || *alibi))
+        return fail(ErrorCode::kUnsupportedOperation, where, "cuDNN bottom-right causal masking does not combine with bias, ALiBi, or dropout");
     KernelStep step;
     step.op = KernelOp::kSdpaForward;
     step.label = node.name;
     step.nodes = {index};
     auto optional_binding = [&](std::optional<std::int64_t> uid) { return uid ? low.bind(*uid) : TensorBinding{}; };
     step.tensors = {low.bind(*q), low.bind(*k), low.bind(*v), low.bind(*o), optional_binding(stats), optional_binding(max), optional_binding(sum_exp),
-                    optional_binding(seq_q), optional_binding(seq_kv), optional_binding(table_k), optional_binding(table_v)};
+                    optional_binding(seq_q), optional_binding(seq_kv), optional_binding(table_k), optional_binding(table_v), optional_binding(bias)};
     step.params = params;
     low.plan.steps.push_back(std::move(step));
     return Status::ok();

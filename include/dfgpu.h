@@ -201,7 +201,9 @@ int dfgpu_matmul_fp8(const dfgpu_matmul_fp8_params*, void* const* tensors, void*
    Replaces emit_sdpa_forward with its helpers (lib/Compiler/SequenceGraph.cpp
    :1839-1889 paged loads, :1988-2091 validity, :2135-2341 scores and softmax
    row, :2416-2582 outputs). tensors: {Q, K, V, O, Stats, Max, Sum_exp,
-   SEQ_LEN_Q, SEQ_LEN_KV, Page_table_K, Page_table_V} (null when absent). */
+   SEQ_LEN_Q, SEQ_LEN_KV, Page_table_K, Page_table_V, Bias} (null when absent).
+   Bias and ALiBi (score = attn_scale * dot + bias + (kv - q) * slope, :2169-2193) run on the
+   general kernel only. */
 enum {
     DFGPU_SDPA_AUTO = 0,
     DFGPU_SDPA_ROWWISE = 1,           /* general kernel on CUDA cores */
@@ -223,6 +225,9 @@ typedef struct dfgpu_sdpa_params {
     int32_t bottom_right;
     int32_t kernel;
     int64_t s_kv; /* logical key/value length */
+    dfgpu_tensor bias;  /* rank 0: absent. Rank 4, extent-1 axes broadcast onto [B, Hq, Sq, Skv]; added to the scaled score */
+    int32_t alibi_mask; /* adds (kv - q) * slope(head), slopes as in lib/Compiler/SequenceGraph.cpp:1748-1778 */
+    int32_t reserved;
 } dfgpu_sdpa_params;
 int dfgpu_query_sdpa_forward(const dfgpu_sdpa_params*, dfgpu_plan_info*);
 int dfgpu_sdpa_forward(const dfgpu_sdpa_params*, void* const* tensors, void* scratch, void* stream);

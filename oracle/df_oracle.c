@@ -706,6 +706,17 @@ static float load_kv(const dfo_tensor* t, const void* data, const dfo_tensor* ta
     return load_f32(t, data, offset4(t, page, head, within, d));
 }
 
+/* SequenceGraph.cpp:1748-1778: slope of head h among H heads. With n the largest power of
+   two <= H, heads 0..n-1 take 2^(-8 (h+1) / n) and the rest 2^(-8 ((2 (h-n) + 1) / 2) / n),
+   each computed as a float power. */
+static float alibi_slope(int64_t head, int64_t heads) {
+    int power = (int)floor(log2((double)heads));
+    int64_t n = (int64_t)1 << power;
+    if (head < n) return powf(2.0f, -8.0f * (float)(head + 1) / (float)n);
+    int64_t index = 2 * (head - n);
+    return powf(2.0f, -8.0f * ((float)(index + 1) * 0.5f) / (float)n);
+}
+
 /* SequenceGraph.cpp:1988-2091 (validity), :2135-2195 (score = scale * dot),
    :2248-2314 (row max and sum of exp over valid scores), :2316-2341
    (probability), :2416-2582 (outputs; Stats = max + ln(sum)). */
@@ -754,6 +765,16 @@ int dfo_sdpa_forward(const dfo_sdpa_params* p, void* const* data,
                     dot = dot + product;
                 }
                 scores[ikv] = p->attn_scale * dot;
+                if (p->bias.rank == 4) { /* :2171-2178: + bias, extent-1 axes broadcast */
+                    const dfo_tensor* bt = &p->bias;
+                    float bias_value = load_f32(bt, data[11], offset4(bt, bt->dim[0] == 1 ? 0 : ib, bt->dim[1] == 1 ? 0 : ih,
+                                                                      bt->dim[2] == 1 ? 0 : iq, bt->dim[3] == 1 ? 0 : ikv));
+                    scores[ikv] = scores[ikv] + bias_value;
+                }
+                if (p->alibi_mask) { /* :2179-2193: + (kv - q) * slope(head) */
+                    float distance = (float)(ikv - iq);
+                    scores[ikv] = scores[ikv] + distance * alibi_slope(ih, hq);
+                }
                 if (scores[ikv] > maximum) maximum = scores[ikv];
                 if (scores[ikv] != scores[ikv]) maximum = scores[ikv];
             }

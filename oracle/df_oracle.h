@@ -137,8 +137,11 @@ typedef struct dfo_sdpa_params {
     int32_t bottom_right;
     int32_t reserved;
     int64_t s_kv; /* logical kv length */
+    dfo_tensor bias;      /* rank 0 => absent; rank 4, broadcast over extent-1 axes onto [B, Hq, Sq, Skv] */
+    int32_t alibi_mask;
+    int32_t reserved2;
 } dfo_sdpa_params;
-/* pointer order: Q,K,V,O,Stats,Max,Sum_exp,SEQ_LEN_Q,SEQ_LEN_KV,Page_table_K,Page_table_V.
+/* pointer order: Q,K,V,O,Stats,Max,Sum_exp,SEQ_LEN_Q,SEQ_LEN_KV,Page_table_K,Page_table_V,Bias.
    Only (b,h) pairs with flat index bh_begin <= b*Hq+h < bh_end and rows with
    q % q_step == 0 are computed; others are left untouched. */
 int dfo_sdpa_forward(const dfo_sdpa_params* p, void* const* data,

@@ -135,6 +135,12 @@ def run(document: dict, inputs: Dict[int, np.ndarray], matmul_rows: Optional[Tup
                     arrays.append(values[ins[name]])
                 else:
                     arrays.append(None)
+            if "Bias" in ins:
+                p.bias = _desc(tensors[ins["Bias"]])
+                arrays.append(values[ins["Bias"]])
+            else:
+                arrays.append(None)
+            p.alibi_mask = int(bool(node.get("alibi_mask")))
             p.attn_scale = node["attn_scale_value"] if node["attn_scale_value"] is not None else 1.0
             p.padding_mask = int(node["padding_mask"])
             if node["left_bound"] is not None:

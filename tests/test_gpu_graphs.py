@@ -225,3 +225,22 @@ def test_executable_loaded_from_an_artifact_gives_the_same_bits(name, size):
     s.run()
     for uid in wl.outputs:
         assert np.array_equal(s.raw(uid), compiled[uid]), f"tensor {uid}"
+
+
+def test_sdpa_graph_with_bias_and_alibi():
+    """The Bias port and alibi_mask through the importer, the lowering and Executable.execute (general kernel)."""
+    from deepforge_b200 import graphs, synthetic
+    wl = workloads.c4(b=2, h=4, s=48, d=32, io="FLOAT")
+    wl.document["tensors"]["9"] = graphs.tensor(9, "Bias", [1, 4, 48, 48])
+    wl.document["nodes"][0]["inputs"]["Bias"] = 9
+    wl.document["nodes"][0]["alibi_mask"] = True
+    wl.inputs[9] = lambda: synthetic.normal(77, 9, 4 * 48 * 48).astype(np.float32)
+    s = harness.Session(wl)
+    assert "kernel=1" in s.exe.plan_text()
+    s.run()
+    ins, _ = oracle_inputs(wl, s)
+    ref = graph_oracle.run(wl.document, ins)
+    check_f32(s.output(4), ref[4])
+    check_f32(s.output(5), ref[5])
+    loaded = runtime.load_artifact(s.exe.serialize())
+    assert loaded.plan_text() == s.exe.plan_text()

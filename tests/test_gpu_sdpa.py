@@ -21,7 +21,8 @@ def close_bf16(actual, expected):
     assert np.all(np.abs(actual - expected) <= 1e-2 + 2e-2 * np.abs(expected))
 
 
-def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=None, stats=True, seed=5, q_step=1, bh_range=None, **flags):
+def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=None, stats=True, seed=5, q_step=1, bh_range=None,
+         bias_dims=None, **flags):
     """Run oracle (f32 restatement on dtype-rounded inputs) and the GPU kernel on the same data."""
     b, hq, sq, _ = q_dims
     o_dims = [b, hq, sq, v_dims[3]]
@@ -41,9 +42,12 @@ def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=No
         if tables is not None:
             params.page_table_k = tensor(I32, [b, 1, tables[0].shape[1], 1])
             params.page_table_v = tensor(I32, [b, 1, tables[1].shape[1], 1])
+        if bias_dims is not None:
+            params.bias = tensor(F32, bias_dims)
         for key, value in flags.items():
             setattr(params, key, value)
 
+    bias = synthetic.normal(seed, 9, int(np.prod(bias_dims))) if bias_dims is not None else None
     op = oracle.SdpaParams()
     fill(op, F32)
     o_ref = np.full(int(np.prod(o_dims)), -99.0, dtype=np.float32)
@@ -51,7 +55,7 @@ def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=No
     seq_arrays = [None, None] if seq is None else [np.asarray(s, dtype=np.int32) for s in seq]
     table_arrays = [None, None] if tables is None else [np.ascontiguousarray(t, dtype=np.int32) for t in tables]
     lo, hi = bh_range if bh_range else (0, b * hq)
-    oracle.sdpa_forward(op, rounded + [o_ref] + (rows_ref if stats else [None] * 3) + seq_arrays + table_arrays, lo, hi, q_step)
+    oracle.sdpa_forward(op, rounded + [o_ref] + (rows_ref if stats else [None] * 3) + seq_arrays + table_arrays + [bias], lo, hi, q_step)
 
     gp = dfgpu.SdpaParams()
     fill(gp, dtype)
@@ -63,7 +67,8 @@ def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=No
     dseq = [g.to_device(a) if a is not None else None for a in seq_arrays]
     dtab = [g.to_device(a) if a is not None else None for a in table_arrays]
     scratch = g.device_zeros(info.scratch_bytes) if info.scratch_bytes else None
-    dfgpu.sdpa_forward(gp, [g.ptr(t) for t in dev + [do] + drows + dseq + dtab], scratch=g.ptr(scratch))
+    dbias = g.to_device(bias) if bias is not None else None
+    dfgpu.sdpa_forward(gp, [g.ptr(t) for t in dev + [do] + drows + dseq + dtab + [dbias]], scratch=g.ptr(scratch))
     if dtype == BF16:
         o = synthetic.bf16_bits_to_f32(g.to_host(do, np.uint16))
     else:
@@ -81,6 +86,34 @@ def test_rowwise_gqa_padding_windows_stats_f32():
         for a, r in zip(rows, rows_ref):
             close_f32(a, r)
         assert np.all(o[1, :, 3:] == 0.0) and np.all(rows[0].reshape(2, 4, 5)[1, :, 3:] == -INF)
+
+
+@pytest.mark.parametrize("bias_dims", [None, [2, 6, 5, 7], [1, 1, 5, 7], [1, 6, 1, 7], [2, 1, 5, 1]])
+@pytest.mark.parametrize("alibi", [0, 1])
+def test_rowwise_bias_and_alibi(bias_dims, alibi):
+    """score = attn_scale * dot + bias (extent-1 axes broadcast) + (kv - q) * slope(head); six heads, so the slopes of
+    heads 4 and 5 come from the second formula (lib/Compiler/SequenceGraph.cpp:1748-1778)."""
+    if bias_dims is None and not alibi:
+        pytest.skip("covered by the other tests")
+    info, o, o_ref, rows, rows_ref = both(F32, [2, 6, 5, 8], [2, 3, 7, 8], [2, 3, 7, 6], 7, 0.4, dfgpu.SDPA_AUTO, seq=([5, 4], [7, 6]),
+                                          bias_dims=bias_dims, alibi_mask=alibi, has_right_bound=1, right_bound=2)
+    assert info.kernel == dfgpu.SDPA_ROWWISE
+    close_f32(o, o_ref)
+    for a, r in zip(rows, rows_ref):
+        close_f32(a, r)
+
+
+def test_bias_keeps_the_tensor_core_kernels_out():
+    params = dfgpu.SdpaParams()
+    params.q = params.k = params.v = params.o = tensor(BF16, [1, 2, 256, 128])
+    params.attn_scale, params.s_kv = 0.1, 256
+    assert dfgpu.query("sdpa_forward", params).kernel == dfgpu.SDPA_UMMA
+    params.bias = tensor(F32, [1, 1, 256, 256])
+    assert dfgpu.query("sdpa_forward", params).kernel == dfgpu.SDPA_ROWWISE
+    params.kernel = dfgpu.SDPA_UMMA
+    with pytest.raises(dfgpu.DfgpuError) as error:
+        dfgpu.query("sdpa_forward", params)
+    assert error.value.code == 20
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])

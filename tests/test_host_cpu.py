@@ -174,7 +174,8 @@ def test_argument_table_is_sorted_with_clamped_alignment():
 
 @pytest.mark.parametrize("doc_fn,expected", [
     (lambda: graphs.c4_sdpa(1, 2, 16, 8, io="HALF"), 0),
-    (lambda: _with(graphs.c4_sdpa(1, 2, 16, 8), lambda d: d["nodes"][0].update(alibi_mask=True)), 20),
+    (lambda: _with(graphs.c4_sdpa(1, 2, 16, 8), lambda d: d["nodes"][0].update(alibi_mask=True)), 0),
+    (lambda: _with(graphs.c4_sdpa(1, 2, 16, 8), lambda d: d["nodes"][0].update(alibi_mask=True, diagonal_alignment="BOTTOM_RIGHT")), 20),
     (lambda: _with(graphs.c4_sdpa(1, 2, 16, 8), lambda d: d["nodes"][0].update(dropout_probability=0.1)), 20),
     (lambda: _with(graphs.c4_sdpa(1, 2, 16, 8), lambda d: d["nodes"][0].update(generate_stats=False)), 8),
     (lambda: _with(graphs.c2_bottleneck(n=1, h=8, w=8), lambda d: d["nodes"][2].update(mode="GELU_FWD")), 20),
