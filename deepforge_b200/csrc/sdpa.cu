@@ -23,6 +23,8 @@ namespace {
 struct SdpaArgs {
     View q, k, v, o, stats, max, sum_exp, seq_q, seq_kv, table_k, table_v, bias;
     const void* bias_data;
+    View sink;
+    const float* sink_data;
     int32_t alibi;
     float alibi_slope_scale;  // -8 / n, n the largest power of two not above the head count
     int32_t alibi_n;
@@ -104,6 +106,10 @@ sdpa_rowwise_kernel(SdpaArgs a, int64_t rows) {
     int64_t lo, hi;
     valid_range(a, ib, iq, lo, hi);
     float running_max = -INFINITY, running_sum = 0.0f;
+    if (a.sink.rank) {  // the sink logit takes part in the maximum and the sum, not in O
+        running_max = a.sink_data[ih * a.sink.stride[1]];
+        running_sum = 1.0f;
+    }
     float acc[kRowwiseMaxD / 32];
 #pragma unroll
     for (int i = 0; i < kRowwiseMaxD / 32; ++i) acc[i] = 0.0f;
@@ -477,6 +483,13 @@ int build_args(const dfgpu_sdpa_params& p, void* const* tensors, SdpaArgs& a) {
             if (p.bias.dim[i] != 1 && p.bias.dim[i] != extent[i]) return fail(kInvalidShape, "SDPA: bias is not broadcast-compatible with attention scores");
         if (tensors && !a.bias_data) return fail(kInvalidArgument, "SDPA: null bias pointer");
     }
+    a.sink = make_view(p.sink);
+    a.sink_data = (tensors && p.sink.rank) ? static_cast<const float*>(tensors[12]) : nullptr;
+    if (p.sink.rank) {
+        if (p.sink.rank != 4 || p.sink.dtype != DFGPU_F32 || p.sink.dim[0] != 1 || p.sink.dim[1] != hq || p.sink.dim[2] != 1 || p.sink.dim[3] != 1)
+            return fail(kInvalidShape, "SDPA: sink token must have dimensions [1,Hq,1,1] and type FLOAT");
+        if (tensors && !a.sink_data) return fail(kInvalidArgument, "SDPA: null sink token pointer");
+    }
     a.alibi = p.alibi_mask;
     a.alibi_n = 1;
     while (2 * static_cast<int64_t>(a.alibi_n) <= hq) a.alibi_n *= 2;
@@ -512,13 +525,13 @@ int decode_chunks(const dfgpu_sdpa_params& p) { return static_cast<int>((p.s_kv 
 
 int choose_kernel(const dfgpu_sdpa_params& p, int& kernel) {
     int automatic = DFGPU_SDPA_ROWWISE;
-    const bool plain_scores = p.bias.rank == 0 && !p.alibi_mask;  // only the general kernel adds bias or ALiBi
+    const bool plain_scores = p.bias.rank == 0 && !p.alibi_mask && p.sink.rank == 0;  // only the general kernel takes bias, ALiBi or a sink token
     if (!plain_scores) automatic = DFGPU_SDPA_ROWWISE;
     else if (decode_umma_supported(p)) automatic = DFGPU_SDPA_PAGED_DECODE_UMMA;
     else if (decode_supported(p)) automatic = DFGPU_SDPA_PAGED_DECODE;
     else if (sdpa_umma_supported(p)) automatic = DFGPU_SDPA_UMMA;
     kernel = p.kernel == DFGPU_SDPA_AUTO ? automatic : p.kernel;
-    if (!plain_scores && kernel != DFGPU_SDPA_ROWWISE) return fail(kUnsupported, "SDPA: bias and ALiBi run on the general kernel only");
+    if (!plain_scores && kernel != DFGPU_SDPA_ROWWISE) return fail(kUnsupported, "SDPA: bias, ALiBi and the sink token run on the general kernel only");
     if (kernel == DFGPU_SDPA_ROWWISE) {
         if (p.q.dim[3] > kRowwiseMaxD || p.v.dim[3] > kRowwiseMaxD) return fail(kUnsupported, "SDPA: head dimension above %d", kRowwiseMaxD);
         return kOk;
@@ -657,7 +670,7 @@ extern "C" int dfgpu_sdpa_paged_decode_static(const dfgpu_sdpa_params* p, void* 
     SdpaArgs a;
     int status = build_args(*p, tensors, a);
     if (status) return status;
-    if (!decode_supported(*p) || p->bias.rank != 0 || p->alibi_mask)
+    if (!decode_supported(*p) || p->bias.rank != 0 || p->alibi_mask || p->sink.rank != 0)
         return fail(kUnsupported, "SDPA static decode: needs Sq=1, bf16, D=128, paged K and V, group size 1/2/4/8, no bias or ALiBi");
     if (!aligned16(a.q_data) || !aligned16(a.k_data) || !aligned16(a.v_data))
         return fail(kInvalidArgument, "SDPA static decode: needs 16-byte aligned Q, K and V");

@@ -98,7 +98,7 @@ class SdpaParams(C.Structure):
                 ("page_table_v", Tensor), ("attn_scale", C.c_float), ("padding_mask", C.c_int32),
                 ("has_left_bound", C.c_int32), ("has_right_bound", C.c_int32), ("left_bound", C.c_int64),
                 ("right_bound", C.c_int64), ("bottom_right", C.c_int32), ("kernel", C.c_int32), ("s_kv", C.c_int64),
-                ("bias", Tensor), ("alibi_mask", C.c_int32), ("reserved", C.c_int32)]
+                ("bias", Tensor), ("alibi_mask", C.c_int32), ("reserved", C.c_int32), ("sink", Tensor)]
 
 
 # every symbol include/dfgpu.h declares
@@ -192,9 +192,9 @@ def matmul_fp8(params, a, b, c, amax, descale_a, descale_b, scale_c, scratch=Non
 
 
 def sdpa_forward(params, pointers: Sequence[Optional[int]], scratch=None, stream=None):
-    """pointers: Q, K, V, O, Stats, Max, Sum_exp, SEQ_LEN_Q, SEQ_LEN_KV, Page_table_K, Page_table_V[, Bias]."""
-    assert len(pointers) in (11, 12)
-    pointers = list(pointers) + [None] * (12 - len(pointers))
+    """pointers: Q, K, V, O, Stats, Max, Sum_exp, SEQ_LEN_Q, SEQ_LEN_KV, Page_table_K, Page_table_V[, Bias[, SINK_TOKEN]]."""
+    assert 11 <= len(pointers) <= 13
+    pointers = list(pointers) + [None] * (13 - len(pointers))
     _call("dfgpu_sdpa_forward", params, pointers, scratch, stream)
 
 

@@ -552,7 +552,7 @@ Status lower_sdpa(Lowering& low, std::size_t index) {
     auto const& node = low.graph.nodes[index];
     auto const where = node_path(index, node);
     for (auto name : {"Attn_scale", "Seed", "Offset", "Dropout_mask", "Dropout_scale", "Block_mask", "Descale_Q", "Descale_K", "Descale_V",
-                      "Descale_S", "Scale_S", "Scale_O", "SINK_TOKEN"})
+                      "Descale_S", "Scale_S", "Scale_O"})
         if (port(node.inputs, name)) return fail(ErrorCode::kUnsupportedOperation, where, std::string("input port ") + name + " is outside the GPU hot path");
     for (auto name : {"RNG_DUMP", "Amax_S", "Amax_O"})
         if (port(node.outputs, name)) return fail(ErrorCode::kUnsupportedOperation, where, std::string("output port ") + name + " is outside the GPU hot path");
@@ -625,6 +625,15 @@ Status lower_sdpa(Lowering& low, std::size_t index) {
                 return fail(ErrorCode::kInvalidShape, where + ".Bias", "bias is not broadcast-compatible with attention scores");
     }
     params.alibi_mask = *alibi;
+    auto sink = port(node.inputs, "SINK_TOKEN");
+    if (sink) {
+        // lib/Compiler/SequenceGraph.cpp:561-577: an external plain FLOAT tensor [1, Hq, 1, 1]
+        if ((status = low.describe(*sink, params.sink, where)).is_bad()) return status;
+        auto const& t = low.tensor(*sink);
+        if (t.dim != std::vector<std::int64_t>{1, params.q.dim[1], 1, 1}) return fail(ErrorCode::kInvalidShape, where + ".SINK_TOKEN", "sink token must have dimensions [1,Hq,1,1]");
+        if (t.is_virtual || t.reordering_type != "NONE" || t.data_type != DataType::kFloat32)
+            return fail(ErrorCode::kUnsupportedOperation, where + ".SINK_TOKEN", "sink token must be an external plain FLOAT tensor");
+    }
     // lib/Compiler/SequenceGraph.cpp:951-955
     if (params.bottom_right && params.has_right_bound && (bias || *alibi))
         return fail(ErrorCode::kUnsupportedOperation, where, "cuDNN bottom-right causal masking does not combine with bias, ALiBi, or dropout");
@@ -634,7 +643,7 @@ Status lower_sdpa(Lowering& low, std::size_t index) {
     step.nodes = {index};
     auto optional_binding = [&](std::optional<std::int64_t> uid) { return uid ? low.bind(*uid) : TensorBinding{}; };
     step.tensors = {low.bind(*q), low.bind(*k), low.bind(*v), low.bind(*o), optional_binding(stats), optional_binding(max), optional_binding(sum_exp),
-                    optional_binding(seq_q), optional_binding(seq_kv), optional_binding(table_k), optional_binding(table_v), optional_binding(bias)};
+                    optional_binding(seq_q), optional_binding(seq_kv), optional_binding(table_k), optional_binding(table_v), optional_binding(bias), optional_binding(sink)};
     step.params = params;
     low.plan.steps.push_back(std::move(step));
     return Status::ok();

@@ -201,9 +201,10 @@ int dfgpu_matmul_fp8(const dfgpu_matmul_fp8_params*, void* const* tensors, void*
    Replaces emit_sdpa_forward with its helpers (lib/Compiler/SequenceGraph.cpp
    :1839-1889 paged loads, :1988-2091 validity, :2135-2341 scores and softmax
    row, :2416-2582 outputs). tensors: {Q, K, V, O, Stats, Max, Sum_exp,
-   SEQ_LEN_Q, SEQ_LEN_KV, Page_table_K, Page_table_V, Bias} (null when absent).
-   Bias and ALiBi (score = attn_scale * dot + bias + (kv - q) * slope, :2169-2193) run on the
-   general kernel only. */
+   SEQ_LEN_Q, SEQ_LEN_KV, Page_table_K, Page_table_V, Bias, SINK_TOKEN} (null when absent;
+   a caller without Bias and SINK_TOKEN may pass the first eleven only).
+   Bias, ALiBi (score = attn_scale * dot + bias + (kv - q) * slope, :2169-2193) and the sink token
+   run on the general kernel only. */
 enum {
     DFGPU_SDPA_AUTO = 0,
     DFGPU_SDPA_ROWWISE = 1,           /* general kernel on CUDA cores */
@@ -228,6 +229,8 @@ typedef struct dfgpu_sdpa_params {
     dfgpu_tensor bias;  /* rank 0: absent. Rank 4, extent-1 axes broadcast onto [B, Hq, Sq, Skv]; added to the scaled score */
     int32_t alibi_mask; /* adds (kv - q) * slope(head), slopes as in lib/Compiler/SequenceGraph.cpp:1748-1778 */
     int32_t reserved;
+    dfgpu_tensor sink;  /* rank 0: absent. [1, Hq, 1, 1] FLOAT: the row maximum starts from the head's sink logit and the
+                           row sum from exp(sink - max) (lib/Compiler/SequenceGraph.cpp:2256-2288) */
 } dfgpu_sdpa_params;
 int dfgpu_query_sdpa_forward(const dfgpu_sdpa_params*, dfgpu_plan_info*);
 int dfgpu_sdpa_forward(const dfgpu_sdpa_params*, void* const* tensors, void* scratch, void* stream);

@@ -748,7 +748,10 @@ int dfo_sdpa_forward(const dfo_sdpa_params* p, void* const* data,
         int64_t shift = 0;
         if (p->bottom_right) shift = p->padding_mask ? len_kv - len_q : skv - sq;
         for (int64_t iq = 0; iq < sq; iq += q_step) {
-            float maximum = -INFINITY;
+            /* SequenceGraph.cpp:2256-2267: with a sink token the row maximum starts from the head's sink logit */
+            float sink = 0.0f;
+            if (p->sink.rank == 4) sink = load_f32(&p->sink, data[12], offset4(&p->sink, 0, ih, 0, 0));
+            float maximum = p->sink.rank == 4 ? sink : -INFINITY;
             for (int64_t ikv = 0; ikv < skv; ++ikv) {
                 int ok = 1;
                 if (p->padding_mask && !(iq < len_q && ikv < len_kv && iq >= 0 && ikv >= 0)) ok = 0;
@@ -779,6 +782,7 @@ int dfo_sdpa_forward(const dfo_sdpa_params* p, void* const* data,
                 if (scores[ikv] != scores[ikv]) maximum = scores[ikv];
             }
             float sum = 0.0f;
+            if (p->sink.rank == 4) sum = expf(sink - maximum); /* :2284-2288: and the sum from exp(sink - max) */
             for (int64_t ikv = 0; ikv < skv; ++ikv)
                 if (valid[ikv]) sum = sum + expf(scores[ikv] - maximum);
             for (int64_t d = 0; d < dv; ++d) out_row[d] = 0.0f;

@@ -140,8 +140,9 @@ typedef struct dfo_sdpa_params {
     dfo_tensor bias;      /* rank 0 => absent; rank 4, broadcast over extent-1 axes onto [B, Hq, Sq, Skv] */
     int32_t alibi_mask;
     int32_t reserved2;
+    dfo_tensor sink;      /* rank 0 => absent; [1, Hq, 1, 1]: one extra logit per head in the softmax */
 } dfo_sdpa_params;
-/* pointer order: Q,K,V,O,Stats,Max,Sum_exp,SEQ_LEN_Q,SEQ_LEN_KV,Page_table_K,Page_table_V,Bias.
+/* pointer order: Q,K,V,O,Stats,Max,Sum_exp,SEQ_LEN_Q,SEQ_LEN_KV,Page_table_K,Page_table_V,Bias,SINK_TOKEN.
    Only (b,h) pairs with flat index bh_begin <= b*Hq+h < bh_end and rows with
    q % q_step == 0 are computed; others are left untouched. */
 int dfo_sdpa_forward(const dfo_sdpa_params* p, void* const* data,

@@ -140,6 +140,11 @@ def run(document: dict, inputs: Dict[int, np.ndarray], matmul_rows: Optional[Tup
                 arrays.append(values[ins["Bias"]])
             else:
                 arrays.append(None)
+            if "SINK_TOKEN" in ins:
+                p.sink = _desc(tensors[ins["SINK_TOKEN"]])
+                arrays.append(values[ins["SINK_TOKEN"]])
+            else:
+                arrays.append(None)
             p.alibi_mask = int(bool(node.get("alibi_mask")))
             p.attn_scale = node["attn_scale_value"] if node["attn_scale_value"] is not None else 1.0
             p.padding_mask = int(node["padding_mask"])

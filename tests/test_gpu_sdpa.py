@@ -22,7 +22,7 @@ def close_bf16(actual, expected):
 
 
 def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=None, stats=True, seed=5, q_step=1, bh_range=None,
-         bias_dims=None, **flags):
+         bias_dims=None, sink=False, **flags):
     """Run oracle (f32 restatement on dtype-rounded inputs) and the GPU kernel on the same data."""
     b, hq, sq, _ = q_dims
     o_dims = [b, hq, sq, v_dims[3]]
@@ -44,10 +44,13 @@ def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=No
             params.page_table_v = tensor(I32, [b, 1, tables[1].shape[1], 1])
         if bias_dims is not None:
             params.bias = tensor(F32, bias_dims)
+        if sink:
+            params.sink = tensor(F32, [1, hq, 1, 1])
         for key, value in flags.items():
             setattr(params, key, value)
 
     bias = synthetic.normal(seed, 9, int(np.prod(bias_dims))) if bias_dims is not None else None
+    sink_values = (2.0 * synthetic.normal(seed, 10, hq)).astype(np.float32) if sink else None
     op = oracle.SdpaParams()
     fill(op, F32)
     o_ref = np.full(int(np.prod(o_dims)), -99.0, dtype=np.float32)
@@ -55,7 +58,7 @@ def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=No
     seq_arrays = [None, None] if seq is None else [np.asarray(s, dtype=np.int32) for s in seq]
     table_arrays = [None, None] if tables is None else [np.ascontiguousarray(t, dtype=np.int32) for t in tables]
     lo, hi = bh_range if bh_range else (0, b * hq)
-    oracle.sdpa_forward(op, rounded + [o_ref] + (rows_ref if stats else [None] * 3) + seq_arrays + table_arrays + [bias], lo, hi, q_step)
+    oracle.sdpa_forward(op, rounded + [o_ref] + (rows_ref if stats else [None] * 3) + seq_arrays + table_arrays + [bias, sink_values], lo, hi, q_step)
 
     gp = dfgpu.SdpaParams()
     fill(gp, dtype)
@@ -68,7 +71,8 @@ def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=No
     dtab = [g.to_device(a) if a is not None else None for a in table_arrays]
     scratch = g.device_zeros(info.scratch_bytes) if info.scratch_bytes else None
     dbias = g.to_device(bias) if bias is not None else None
-    dfgpu.sdpa_forward(gp, [g.ptr(t) for t in dev + [do] + drows + dseq + dtab + [dbias]], scratch=g.ptr(scratch))
+    dsink = g.to_device(sink_values) if sink else None
+    dfgpu.sdpa_forward(gp, [g.ptr(t) for t in dev + [do] + drows + dseq + dtab + [dbias, dsink]], scratch=g.ptr(scratch))
     if dtype == BF16:
         o = synthetic.bf16_bits_to_f32(g.to_host(do, np.uint16))
     else:
@@ -101,6 +105,21 @@ def test_rowwise_bias_and_alibi(bias_dims, alibi):
     close_f32(o, o_ref)
     for a, r in zip(rows, rows_ref):
         close_f32(a, r)
+
+
+@pytest.mark.parametrize("padded", [False, True])
+def test_rowwise_sink_token(padded):
+    """One extra logit per head: the row maximum starts from it and the row sum from exp(sink - max); it adds nothing to O
+    (lib/Compiler/SequenceGraph.cpp:2256-2288). With padding, the rows past SEQ_LEN_Q keep Max = sink, Sum_exp = 1, O = 0."""
+    seq = ([5, 3], [7, 4]) if padded else None
+    info, o, o_ref, rows, rows_ref = both(F32, [2, 4, 5, 8], [2, 2, 7, 8], [2, 2, 7, 6], 7, 0.5, dfgpu.SDPA_AUTO, seq=seq, sink=True,
+                                          has_right_bound=1, right_bound=1, bias_dims=[1, 4, 5, 7])
+    assert info.kernel == dfgpu.SDPA_ROWWISE
+    close_f32(o, o_ref)
+    for a, r in zip(rows, rows_ref):
+        close_f32(a, r)
+    if padded:
+        assert np.all(o[1, :, 3:] == 0.0) and np.all(rows[2].reshape(2, 4, 5)[1, :, 3:] == 1.0)
 
 
 def test_bias_keeps_the_tensor_core_kernels_out():
