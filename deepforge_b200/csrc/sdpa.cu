@@ -25,6 +25,8 @@ struct SdpaArgs {
     const void* bias_data;
     View sink;
     const float* sink_data;
+    View block_mask;
+    const uint8_t* block_mask_data;
     int32_t alibi;
     float alibi_slope_scale;  // -8 / n, n the largest power of two not above the head count
     int32_t alibi_n;
@@ -117,7 +119,13 @@ sdpa_rowwise_kernel(SdpaArgs a, int64_t rows) {
     for (int64_t base = lo; base < hi; base += 32) {
         int64_t ikv = base + lane;
         float score = -INFINITY;
-        if (ikv < hi) {
+        bool enabled = ikv < hi;
+        if (enabled && a.block_mask.rank) {
+            const int64_t key_tile = ikv >> 7;
+            const uint32_t byte = a.block_mask_data[off4(a.block_mask, ib, ih, iq >> 7, key_tile >> 3)];
+            enabled = ((byte >> (key_tile & 7)) & 1u) != 0u;
+        }
+        if (enabled) {
             int64_t offset = kv_row_offset(a.k, a.table_k, a.table_k_data, ib, kh, ikv);
             float dot = 0.0f;
             if (offset >= 0) {
@@ -155,7 +163,7 @@ sdpa_rowwise_kernel(SdpaArgs a, int64_t rows) {
         for (int s = 16; s > 0; s >>= 1) chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, s));
         float new_max = fmaxf(running_max, chunk_max);
         float correction = running_max == -INFINITY ? 0.0f : expf(running_max - new_max);
-        float probability = (ikv < hi && new_max != -INFINITY) ? expf(score - new_max) : 0.0f;
+        float probability = (enabled && new_max != -INFINITY) ? expf(score - new_max) : 0.0f;
         float chunk_sum = probability;
 #pragma unroll
         for (int s = 16; s > 0; s >>= 1) chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, s);
@@ -490,6 +498,15 @@ int build_args(const dfgpu_sdpa_params& p, void* const* tensors, SdpaArgs& a) {
             return fail(kInvalidShape, "SDPA: sink token must have dimensions [1,Hq,1,1] and type FLOAT");
         if (tensors && !a.sink_data) return fail(kInvalidArgument, "SDPA: null sink token pointer");
     }
+    a.block_mask = make_view(p.block_mask);
+    a.block_mask_data = (tensors && p.block_mask.rank) ? static_cast<const uint8_t*>(tensors[13]) : nullptr;
+    if (p.block_mask.rank) {
+        const int64_t query_tiles = (p.q.dim[2] - 1) / 128 + 1, key_tiles = (p.s_kv - 1) / 128 + 1;
+        if (p.block_mask.rank != 4 || p.block_mask.dtype != DFGPU_U8 || p.block_mask.dim[0] != p.q.dim[0] || p.block_mask.dim[1] != hq ||
+            p.block_mask.dim[2] != query_tiles || p.block_mask.dim[3] != (key_tiles + 7) / 8)
+            return fail(kInvalidShape, "SDPA: block mask must be UINT8 with dimensions [B,Hq,ceil(Sq/128),ceil(ceil(Skv/128)/8)]");
+        if (tensors && !a.block_mask_data) return fail(kInvalidArgument, "SDPA: null block mask pointer");
+    }
     a.alibi = p.alibi_mask;
     a.alibi_n = 1;
     while (2 * static_cast<int64_t>(a.alibi_n) <= hq) a.alibi_n *= 2;
@@ -525,13 +542,13 @@ int decode_chunks(const dfgpu_sdpa_params& p) { return static_cast<int>((p.s_kv 
 
 int choose_kernel(const dfgpu_sdpa_params& p, int& kernel) {
     int automatic = DFGPU_SDPA_ROWWISE;
-    const bool plain_scores = p.bias.rank == 0 && !p.alibi_mask && p.sink.rank == 0;  // only the general kernel takes bias, ALiBi or a sink token
+    const bool plain_scores = p.bias.rank == 0 && !p.alibi_mask && p.sink.rank == 0 && p.block_mask.rank == 0;  // bias, ALiBi, sink token, block mask: general kernel only
     if (!plain_scores) automatic = DFGPU_SDPA_ROWWISE;
     else if (decode_umma_supported(p)) automatic = DFGPU_SDPA_PAGED_DECODE_UMMA;
     else if (decode_supported(p)) automatic = DFGPU_SDPA_PAGED_DECODE;
     else if (sdpa_umma_supported(p)) automatic = DFGPU_SDPA_UMMA;
     kernel = p.kernel == DFGPU_SDPA_AUTO ? automatic : p.kernel;
-    if (!plain_scores && kernel != DFGPU_SDPA_ROWWISE) return fail(kUnsupported, "SDPA: bias, ALiBi and the sink token run on the general kernel only");
+    if (!plain_scores && kernel != DFGPU_SDPA_ROWWISE) return fail(kUnsupported, "SDPA: bias, ALiBi, the sink token and the block mask run on the general kernel only");
     if (kernel == DFGPU_SDPA_ROWWISE) {
         if (p.q.dim[3] > kRowwiseMaxD || p.v.dim[3] > kRowwiseMaxD) return fail(kUnsupported, "SDPA: head dimension above %d", kRowwiseMaxD);
         return kOk;
@@ -670,7 +687,7 @@ extern "C" int dfgpu_sdpa_paged_decode_static(const dfgpu_sdpa_params* p, void* 
     SdpaArgs a;
     int status = build_args(*p, tensors, a);
     if (status) return status;
-    if (!decode_supported(*p) || p->bias.rank != 0 || p->alibi_mask || p->sink.rank != 0)
+    if (!decode_supported(*p) || p->bias.rank != 0 || p->alibi_mask || p->sink.rank != 0 || p->block_mask.rank != 0)
         return fail(kUnsupported, "SDPA static decode: needs Sq=1, bf16, D=128, paged K and V, group size 1/2/4/8, no bias or ALiBi");
     if (!aligned16(a.q_data) || !aligned16(a.k_data) || !aligned16(a.v_data))
         return fail(kInvalidArgument, "SDPA static decode: needs 16-byte aligned Q, K and V");

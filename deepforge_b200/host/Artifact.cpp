@@ -121,7 +121,7 @@ std::size_t tensor_slots(KernelOp op) {
         case KernelOp::kPointwise: return 3;
         case KernelOp::kConvFprop: return 5;
         case KernelOp::kMatmul: return 7;
-        case KernelOp::kSdpaForward: return 13;
+        case KernelOp::kSdpaForward: return 14;
         case KernelOp::kMatmulFp8: return 7;
     }
     return 0;
@@ -171,7 +171,7 @@ Status check_workspace(WorkspacePlan const& workspace) {
     return Status::ok();
 }
 
-bool tensor_in_range(dfgpu_tensor const& t) { return t.rank >= 0 && t.rank <= DFGPU_MAX_RANK && t.dtype >= 0 && t.dtype <= DFGPU_E5M2; }
+bool tensor_in_range(dfgpu_tensor const& t) { return t.rank >= 0 && t.rank <= DFGPU_MAX_RANK && t.dtype >= 0 && t.dtype <= DFGPU_U8; }
 
 bool params_in_range(KernelParams const& params) {
     return std::visit([](auto const& p) {
@@ -188,7 +188,7 @@ bool params_in_range(KernelParams const& params) {
         else if constexpr (std::is_same_v<T, dfgpu_sdpa_params>)
             return tensor_in_range(p.q) && tensor_in_range(p.k) && tensor_in_range(p.v) && tensor_in_range(p.o) && tensor_in_range(p.stats) &&
                    tensor_in_range(p.max) && tensor_in_range(p.sum_exp) && tensor_in_range(p.seq_q) && tensor_in_range(p.seq_kv) &&
-                   tensor_in_range(p.page_table_k) && tensor_in_range(p.page_table_v) && tensor_in_range(p.bias) && tensor_in_range(p.sink);
+                   tensor_in_range(p.page_table_k) && tensor_in_range(p.page_table_v) && tensor_in_range(p.bias) && tensor_in_range(p.sink) && tensor_in_range(p.block_mask);
         else return tensor_in_range(p.a) && tensor_in_range(p.b) && tensor_in_range(p.c);
     }, params);
 }

@@ -88,6 +88,7 @@ std::optional<int> to_dfgpu_dtype(DataType type) {
         case DataType::kFp8E8M0: return DFGPU_E8M0;
         case DataType::kInt32: return DFGPU_I32;
         case DataType::kFp8E5M2: return DFGPU_E5M2;
+        case DataType::kUint8: return DFGPU_U8;
         default: return std::nullopt;
     }
 }
@@ -105,11 +106,12 @@ struct Lowering {
 
     TensorDesc const& tensor(std::int64_t uid) const { return graph.tensors.at(uid); }
 
-    // FP8_E5M2 is executable as a MATMUL_FP8 operand or output only (`allow_e5m2`).
+    // FP8_E5M2 is executable as a MATMUL_FP8 operand or output only, UINT8 as the SDPA block mask only (`allow_e5m2`
+    // admits either).
     Status describe(std::int64_t uid, dfgpu_tensor& out, std::string const& where, bool allow_e5m2 = false) const {
         auto const& t = tensor(uid);
         auto dtype = to_dfgpu_dtype(t.data_type);
-        if (dtype && *dtype == DFGPU_E5M2 && !allow_e5m2) dtype.reset();
+        if (dtype && (*dtype == DFGPU_E5M2 || *dtype == DFGPU_U8) && !allow_e5m2) dtype.reset();
         if (!dtype) return fail(ErrorCode::kUnsupportedDataType, where, "tensor '" + t.name + "' has data type " + std::string(import::data_type_name(t.data_type)) + ", which this backend does not execute");
         if (t.dim.size() > DFGPU_MAX_RANK) return fail(ErrorCode::kInvalidShape, where, "tensor rank above 8");
         out = dfgpu_tensor{};
@@ -551,7 +553,7 @@ Status lower_dequantize(Lowering& low, std::size_t index) {
 Status lower_sdpa(Lowering& low, std::size_t index) {
     auto const& node = low.graph.nodes[index];
     auto const where = node_path(index, node);
-    for (auto name : {"Attn_scale", "Seed", "Offset", "Dropout_mask", "Dropout_scale", "Block_mask", "Descale_Q", "Descale_K", "Descale_V",
+    for (auto name : {"Attn_scale", "Seed", "Offset", "Dropout_mask", "Dropout_scale", "Descale_Q", "Descale_K", "Descale_V",
                       "Descale_S", "Scale_S", "Scale_O"})
         if (port(node.inputs, name)) return fail(ErrorCode::kUnsupportedOperation, where, std::string("input port ") + name + " is outside the GPU hot path");
     for (auto name : {"RNG_DUMP", "Amax_S", "Amax_O"})
@@ -625,6 +627,17 @@ Status lower_sdpa(Lowering& low, std::size_t index) {
                 return fail(ErrorCode::kInvalidShape, where + ".Bias", "bias is not broadcast-compatible with attention scores");
     }
     params.alibi_mask = *alibi;
+    auto block_mask = port(node.inputs, "Block_mask");
+    if (block_mask) {
+        // lib/Compiler/SequenceGraph.cpp:854-877: an external plain UINT8 tensor, one bit per 128 x 128 score tile
+        if ((status = low.describe(*block_mask, params.block_mask, where, true)).is_bad()) return status;
+        auto const& t = low.tensor(*block_mask);
+        if (t.data_type != DataType::kUint8) return fail(ErrorCode::kUnsupportedDataType, where + ".Block_mask", std::string(import::data_type_name(t.data_type)) + " is not supported on this port");
+        const std::int64_t query_tiles = (params.q.dim[2] - 1) / 128 + 1, key_tiles = (params.s_kv - 1) / 128 + 1;
+        if (t.dim != std::vector<std::int64_t>{params.q.dim[0], params.q.dim[1], query_tiles, (key_tiles + 7) / 8})
+            return fail(ErrorCode::kInvalidShape, where + ".Block_mask", "block mask must have dimensions [B,Hq,ceil(Sq/128),ceil(ceil(Skv/128)/8)]");
+        if (t.is_virtual || t.reordering_type != "NONE") return fail(ErrorCode::kUnsupportedOperation, where + ".Block_mask", "block mask must be an external plain UINT8 tensor");
+    }
     auto sink = port(node.inputs, "SINK_TOKEN");
     if (sink) {
         // lib/Compiler/SequenceGraph.cpp:561-577: an external plain FLOAT tensor [1, Hq, 1, 1]
@@ -643,7 +656,7 @@ Status lower_sdpa(Lowering& low, std::size_t index) {
     step.nodes = {index};
     auto optional_binding = [&](std::optional<std::int64_t> uid) { return uid ? low.bind(*uid) : TensorBinding{}; };
     step.tensors = {low.bind(*q), low.bind(*k), low.bind(*v), low.bind(*o), optional_binding(stats), optional_binding(max), optional_binding(sum_exp),
-                    optional_binding(seq_q), optional_binding(seq_kv), optional_binding(table_k), optional_binding(table_v), optional_binding(bias), optional_binding(sink)};
+                    optional_binding(seq_q), optional_binding(seq_kv), optional_binding(table_k), optional_binding(table_v), optional_binding(bias), optional_binding(sink), optional_binding(block_mask)};
     step.params = params;
     low.plan.steps.push_back(std::move(step));
     return Status::ok();

@@ -18,8 +18,8 @@ import numpy as np
 from . import graphs, synthetic
 
 BASE_SEED = 20261125
-NP_DTYPE = {"FLOAT": np.float32, "BFLOAT16": np.uint16, "HALF": np.float16, "FP8_E4M3": np.uint8, "FP8_E5M2": np.uint8, "FP8_E8M0": np.uint8, "INT32": np.int32}
-DTYPE_BYTES = {"FLOAT": 4, "BFLOAT16": 2, "HALF": 2, "FP8_E4M3": 1, "FP8_E5M2": 1, "FP8_E8M0": 1, "INT32": 4}
+NP_DTYPE = {"FLOAT": np.float32, "BFLOAT16": np.uint16, "HALF": np.float16, "FP8_E4M3": np.uint8, "FP8_E5M2": np.uint8, "FP8_E8M0": np.uint8, "INT32": np.int32, "UINT8": np.uint8}
+DTYPE_BYTES = {"FLOAT": 4, "BFLOAT16": 2, "HALF": 2, "FP8_E4M3": 1, "FP8_E5M2": 1, "FP8_E8M0": 1, "INT32": 4, "UINT8": 1}
 
 
 @dataclasses.dataclass

@@ -42,7 +42,8 @@ enum {
     DFGPU_E4M3 = 3,
     DFGPU_E8M0 = 4,
     DFGPU_I32 = 5,
-    DFGPU_E5M2 = 6 /* FP8_E5M2: MATMUL_FP8 operands and output only */
+    DFGPU_E5M2 = 6, /* FP8_E5M2: MATMUL_FP8 operands and output only */
+    DFGPU_U8 = 7    /* UINT8: the SDPA block mask only */
 };
 
 enum { DFGPU_REORDER_NONE = 0, DFGPU_REORDER_F8_128x4 = 1 };
@@ -201,10 +202,10 @@ int dfgpu_matmul_fp8(const dfgpu_matmul_fp8_params*, void* const* tensors, void*
    Replaces emit_sdpa_forward with its helpers (lib/Compiler/SequenceGraph.cpp
    :1839-1889 paged loads, :1988-2091 validity, :2135-2341 scores and softmax
    row, :2416-2582 outputs). tensors: {Q, K, V, O, Stats, Max, Sum_exp,
-   SEQ_LEN_Q, SEQ_LEN_KV, Page_table_K, Page_table_V, Bias, SINK_TOKEN} (null when absent;
-   a caller without Bias and SINK_TOKEN may pass the first eleven only).
-   Bias, ALiBi (score = attn_scale * dot + bias + (kv - q) * slope, :2169-2193) and the sink token
-   run on the general kernel only. */
+   SEQ_LEN_Q, SEQ_LEN_KV, Page_table_K, Page_table_V, Bias, SINK_TOKEN, Block_mask} (null when absent;
+   a caller without the last three may pass the first eleven only).
+   Bias, ALiBi (score = attn_scale * dot + bias + (kv - q) * slope, :2169-2193), the sink token and the
+   block mask run on the general kernel only. */
 enum {
     DFGPU_SDPA_AUTO = 0,
     DFGPU_SDPA_ROWWISE = 1,           /* general kernel on CUDA cores */
@@ -231,6 +232,8 @@ typedef struct dfgpu_sdpa_params {
     int32_t reserved;
     dfgpu_tensor sink;  /* rank 0: absent. [1, Hq, 1, 1] FLOAT: the row maximum starts from the head's sink logit and the
                            row sum from exp(sink - max) (lib/Compiler/SequenceGraph.cpp:2256-2288) */
+    dfgpu_tensor block_mask; /* rank 0: absent. UINT8 [B, Hq, ceil(Sq/128), ceil(ceil(Skv/128)/8)]: bit (kv/128) % 8 of byte
+                                [b, h, q/128, (kv/128)/8] enables the 128 x 128 score tile (lib/Compiler/SequenceGraph.cpp:2059-2088) */
 } dfgpu_sdpa_params;
 int dfgpu_query_sdpa_forward(const dfgpu_sdpa_params*, dfgpu_plan_info*);
 int dfgpu_sdpa_forward(const dfgpu_sdpa_params*, void* const* tensors, void* scratch, void* stream);

@@ -758,6 +758,11 @@ int dfo_sdpa_forward(const dfo_sdpa_params* p, void* const* data,
                 int64_t difference = ikv - iq;
                 if (p->has_right_bound && !(difference <= shift + p->right_bound)) ok = 0;
                 if (p->has_left_bound && !(difference > shift - p->left_bound)) ok = 0;
+                if (p->block_mask.rank == 4) { /* SequenceGraph.cpp:2059-2088: bit (kv/128) % 8 of byte [b, h, q/128, (kv/128)/8] */
+                    int64_t key_tile = ikv / 128;
+                    unsigned byte = ((const uint8_t*)data[13])[offset4(&p->block_mask, ib, ih, iq / 128, key_tile / 8)];
+                    if (((byte >> (key_tile % 8)) & 1u) == 0) ok = 0;
+                }
                 valid[ikv] = (unsigned char)ok;
                 if (!ok) { scores[ikv] = -INFINITY; continue; }
                 float dot = 0.0f;

@@ -32,7 +32,8 @@ enum {
     DFO_E4M3 = 3,
     DFO_E8M0 = 4,
     DFO_I32 = 5,
-    DFO_E5M2 = 6
+    DFO_E5M2 = 6,
+    DFO_U8 = 7
 };
 
 enum { DFO_REORDER_NONE = 0, DFO_REORDER_F8_128x4 = 1 };
@@ -141,8 +142,9 @@ typedef struct dfo_sdpa_params {
     int32_t alibi_mask;
     int32_t reserved2;
     dfo_tensor sink;      /* rank 0 => absent; [1, Hq, 1, 1]: one extra logit per head in the softmax */
+    dfo_tensor block_mask; /* rank 0 => absent; UINT8 [B, Hq, ceil(Sq/128), ceil(ceil(Skv/128)/8)], one bit per 128 x 128 tile */
 } dfo_sdpa_params;
-/* pointer order: Q,K,V,O,Stats,Max,Sum_exp,SEQ_LEN_Q,SEQ_LEN_KV,Page_table_K,Page_table_V,Bias,SINK_TOKEN.
+/* pointer order: Q,K,V,O,Stats,Max,Sum_exp,SEQ_LEN_Q,SEQ_LEN_KV,Page_table_K,Page_table_V,Bias,SINK_TOKEN,Block_mask.
    Only (b,h) pairs with flat index bh_begin <= b*Hq+h < bh_end and rows with
    q % q_step == 0 are computed; others are left untouched. */
 int dfo_sdpa_forward(const dfo_sdpa_params* p, void* const* data,

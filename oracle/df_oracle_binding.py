@@ -34,7 +34,7 @@ class SdpaParams(C.Structure):
                 ("page_table_v", Tensor), ("attn_scale", C.c_float), ("padding_mask", C.c_int32),
                 ("has_left_bound", C.c_int32), ("has_right_bound", C.c_int32), ("left_bound", C.c_int64),
                 ("right_bound", C.c_int64), ("bottom_right", C.c_int32), ("reserved", C.c_int32), ("s_kv", C.c_int64),
-                ("bias", Tensor), ("alibi_mask", C.c_int32), ("reserved2", C.c_int32), ("sink", Tensor)]
+                ("bias", Tensor), ("alibi_mask", C.c_int32), ("reserved2", C.c_int32), ("sink", Tensor), ("block_mask", Tensor)]
 
 
 def _declare(l: C.CDLL) -> C.CDLL:
@@ -164,8 +164,8 @@ def matmul_fp8(ad, a, bd, b, cd, c, descale_a: float, descale_b: float, scale_c:
 
 
 def sdpa_forward(params: SdpaParams, arrays, bh_begin=0, bh_end=1 << 62, q_step=1) -> None:
-    assert 11 <= len(arrays) <= 13  # the twelfth is the bias, the thirteenth the sink token
-    arrays = list(arrays) + [None] * (13 - len(arrays))
-    pointers = (C.c_void_p * 13)(*[C.c_void_p(a.ctypes.data) if a is not None else C.c_void_p(None) for a in arrays])
+    assert 11 <= len(arrays) <= 14  # the twelfth is the bias, then the sink token, then the block mask
+    arrays = list(arrays) + [None] * (14 - len(arrays))
+    pointers = (C.c_void_p * 14)(*[C.c_void_p(a.ctypes.data) if a is not None else C.c_void_p(None) for a in arrays])
     code = lib().dfo_sdpa_forward(C.byref(params), pointers, C.c_int64(bh_begin), C.c_int64(bh_end), C.c_int64(q_step))
     assert code == 0, code

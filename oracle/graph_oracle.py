@@ -17,7 +17,7 @@ from deepforge_b200 import dfgpu, synthetic
 
 FLT_MAX = 3.4028234663852886e38
 _FLOATING = {"FLOAT", "BFLOAT16", "HALF"}
-_CODE = {"FP8_E4M3": dfgpu.E4M3, "FP8_E5M2": dfgpu.E5M2, "FP8_E8M0": dfgpu.E8M0, "INT32": dfgpu.I32}
+_CODE = {"FP8_E4M3": dfgpu.E4M3, "FP8_E5M2": dfgpu.E5M2, "FP8_E8M0": dfgpu.E8M0, "INT32": dfgpu.I32, "UINT8": dfgpu.U8}
 _STORAGE = {"FLOAT": dfgpu.F32, "BFLOAT16": dfgpu.BF16, "HALF": dfgpu.F16}
 
 
@@ -143,6 +143,11 @@ def run(document: dict, inputs: Dict[int, np.ndarray], matmul_rows: Optional[Tup
             if "SINK_TOKEN" in ins:
                 p.sink = _desc(tensors[ins["SINK_TOKEN"]])
                 arrays.append(values[ins["SINK_TOKEN"]])
+            else:
+                arrays.append(None)
+            if "Block_mask" in ins:
+                p.block_mask = _desc(tensors[ins["Block_mask"]])
+                arrays.append(values[ins["Block_mask"]])
             else:
                 arrays.append(None)
             p.alibi_mask = int(bool(node.get("alibi_mask")))

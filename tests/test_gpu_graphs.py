@@ -244,3 +244,24 @@ def test_sdpa_graph_with_bias_and_alibi():
     check_f32(s.output(5), ref[5])
     loaded = runtime.load_artifact(s.exe.serialize())
     assert loaded.plan_text() == s.exe.plan_text()
+
+
+def test_sdpa_graph_with_sink_token_and_block_mask():
+    """SINK_TOKEN ([1, Hq, 1, 1] FLOAT) and Block_mask (UINT8, one bit per 128 x 128 tile) through Executable.execute."""
+    from deepforge_b200 import graphs, synthetic
+    wl = workloads.c4(b=1, h=2, s=256, d=32, io="FLOAT", causal=False)
+    wl.document["tensors"]["9"] = graphs.tensor(9, "SINK_TOKEN", [1, 2, 1, 1])
+    wl.document["tensors"]["10"] = graphs.tensor(10, "Block_mask", [1, 2, 2, 1], "UINT8")
+    wl.document["nodes"][0]["inputs"]["SINK_TOKEN"] = 9
+    wl.document["nodes"][0]["inputs"]["Block_mask"] = 10
+    wl.inputs[9] = lambda: np.array([0.5, -1.0], dtype=np.float32)
+    wl.inputs[10] = lambda: np.array([0b01, 0b11, 0b10, 0b00], dtype=np.uint8)
+    s = harness.Session(wl)
+    assert "kernel=1" in s.exe.plan_text()  # the general kernel, although the shape fits the tcgen05 one
+    s.run()
+    ins, _ = oracle_inputs(wl, s)
+    ref = graph_oracle.run(wl.document, ins)
+    check_f32(s.output(4), ref[4])
+    check_f32(s.output(5), ref[5])
+    stats = s.output(5).reshape(1, 2, 256)
+    assert np.allclose(stats[0, 1, 128:], -1.0)  # fully masked rows keep the sink logit: Stats = sink + ln(1)

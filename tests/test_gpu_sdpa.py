@@ -22,7 +22,7 @@ def close_bf16(actual, expected):
 
 
 def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=None, stats=True, seed=5, q_step=1, bh_range=None,
-         bias_dims=None, sink=False, **flags):
+         bias_dims=None, sink=False, block_mask=None, **flags):
     """Run oracle (f32 restatement on dtype-rounded inputs) and the GPU kernel on the same data."""
     b, hq, sq, _ = q_dims
     o_dims = [b, hq, sq, v_dims[3]]
@@ -46,6 +46,8 @@ def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=No
             params.bias = tensor(F32, bias_dims)
         if sink:
             params.sink = tensor(F32, [1, hq, 1, 1])
+        if block_mask is not None:
+            params.block_mask = tensor(dfgpu.U8, list(block_mask.shape))
         for key, value in flags.items():
             setattr(params, key, value)
 
@@ -58,7 +60,7 @@ def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=No
     seq_arrays = [None, None] if seq is None else [np.asarray(s, dtype=np.int32) for s in seq]
     table_arrays = [None, None] if tables is None else [np.ascontiguousarray(t, dtype=np.int32) for t in tables]
     lo, hi = bh_range if bh_range else (0, b * hq)
-    oracle.sdpa_forward(op, rounded + [o_ref] + (rows_ref if stats else [None] * 3) + seq_arrays + table_arrays + [bias, sink_values], lo, hi, q_step)
+    oracle.sdpa_forward(op, rounded + [o_ref] + (rows_ref if stats else [None] * 3) + seq_arrays + table_arrays + [bias, sink_values, block_mask], lo, hi, q_step)
 
     gp = dfgpu.SdpaParams()
     fill(gp, dtype)
@@ -72,7 +74,8 @@ def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=No
     scratch = g.device_zeros(info.scratch_bytes) if info.scratch_bytes else None
     dbias = g.to_device(bias) if bias is not None else None
     dsink = g.to_device(sink_values) if sink else None
-    dfgpu.sdpa_forward(gp, [g.ptr(t) for t in dev + [do] + drows + dseq + dtab + [dbias, dsink]], scratch=g.ptr(scratch))
+    dmask = g.to_device(block_mask) if block_mask is not None else None
+    dfgpu.sdpa_forward(gp, [g.ptr(t) for t in dev + [do] + drows + dseq + dtab + [dbias, dsink, dmask]], scratch=g.ptr(scratch))
     if dtype == BF16:
         o = synthetic.bf16_bits_to_f32(g.to_host(do, np.uint16))
     else:
@@ -120,6 +123,20 @@ def test_rowwise_sink_token(padded):
         close_f32(a, r)
     if padded:
         assert np.all(o[1, :, 3:] == 0.0) and np.all(rows[2].reshape(2, 4, 5)[1, :, 3:] == 1.0)
+
+
+def test_rowwise_block_mask():
+    """One bit per 128 x 128 score tile (lib/Compiler/SequenceGraph.cpp:2059-2088): 2 x 3 tiles per head here; head 1 of batch 0
+    has its second query tile switched off entirely, so those rows are fully masked (O = 0, Stats = -inf, Sum_exp = 0)."""
+    mask = np.array([[[[0b101], [0b011]], [[0b110], [0b000]]]], dtype=np.uint8)  # [B=1, H=2, 2 query tiles, 1 byte]
+    info, o, o_ref, rows, rows_ref = both(F32, [1, 2, 200, 8], [1, 1, 300, 8], [1, 1, 300, 8], 300, 0.4, dfgpu.SDPA_AUTO, block_mask=mask,
+                                          has_right_bound=1, right_bound=150)
+    assert info.kernel == dfgpu.SDPA_ROWWISE
+    close_f32(o, o_ref)
+    for a, r in zip(rows, rows_ref):
+        close_f32(a, r)
+    assert np.all(o[0, 1, 128:] == 0.0) and np.all(rows[0].reshape(1, 2, 200)[0, 1, 128:] == -INF) and np.all(rows[2].reshape(1, 2, 200)[0, 1, 128:] == 0.0)
+    assert np.any(o[0, 0, 128:] != 0.0)
 
 
 def test_bias_keeps_the_tensor_core_kernels_out():
