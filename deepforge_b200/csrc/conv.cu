@@ -311,7 +311,8 @@ int build_args(const dfgpu_conv_params& p, void* const* tensors, ConvArgs& a) {
     if (p.x.rank != 4 || p.w.rank != 4 || p.y.rank != 4)
         return fail(kUnsupported, "CONV_FPROP: only rank-4 (2-D spatial) convolutions are executable on this backend");
     auto float_type = [](int t) { return t == DFGPU_F32 || t == DFGPU_F16 || t == DFGPU_BF16; };
-    if (!float_type(p.x.dtype) || !float_type(p.w.dtype) || !float_type(p.y.dtype))
+    // split (hi, lo) activations exist for the tcgen05 kernel only: choose_kernel() refuses them for every other one
+    if (!(float_type(p.x.dtype) || p.x.dtype == DFGPU_BF16X2) || !float_type(p.w.dtype) || !(float_type(p.y.dtype) || p.y.dtype == DFGPU_BF16X2))
         return fail(kUnsupported, "CONV_FPROP: tensors must be FLOAT, HALF or BFLOAT16");
     if (p.x.dim[0] != p.y.dim[0] || p.w.dim[0] != p.y.dim[1] || p.w.dim[1] <= 0 || p.x.dim[1] % p.w.dim[1] != 0)
         return fail(kInvalidShape, "CONV_FPROP: convolution N/K/C dimensions are inconsistent");
@@ -354,6 +355,8 @@ int choose_kernel(const dfgpu_conv_params& p, const ConvArgs& a, int& kernel) {
     int automatic = a.groups == 1 ? DFGPU_CONV_IGEMM_FFMA : DFGPU_CONV_DIRECT;
     if (conv_umma_supported(p)) automatic = DFGPU_CONV_UMMA_BF16;
     kernel = p.kernel == DFGPU_CONV_AUTO ? automatic : p.kernel;
+    if (kernel != DFGPU_CONV_UMMA_BF16 && (p.x.dtype == DFGPU_BF16X2 || p.y.dtype == DFGPU_BF16X2))
+        return fail(kUnsupported, "CONV_FPROP: split bf16 pair tensors are read and written by the tcgen05 kernel only");
     if (kernel == DFGPU_CONV_IGEMM_FFMA && a.groups != 1)
         return fail(kUnsupported, "CONV_FPROP: the implicit-GEMM kernel needs groups == 1");
     if (kernel == DFGPU_CONV_UMMA_BF16 && !conv_umma_supported(p))

@@ -291,6 +291,15 @@ struct PersistentArgs {
     int32_t early_static;  // filter and bias may be fetched before the wait on the previous kernel
     int32_t issuers;       // 1, or 2: warp 10 issues the odd tiles of this CTA (a lone lane issues ~60 cycles per product,
                            // twice what a 128 x 64 x 16 product takes to run, so many-tap tiles are issue-bound with one)
+    // Split storage (DFGPU_BF16X2): an f32 value kept as hi = bf16(x) and lo = bf16(x - hi), per pixel C hi values
+    // followed by C lo values. A split INPUT is a 2C-channel bf16 activation tensor whose two halves meet the same
+    // filter (gemm.k_blocks / k_blocks_per_tap count activation slices, w_k_blocks / w_blocks_per_tap filter slices);
+    // a split OUTPUT stages and stores the hi boxes at channel n0 and the lo boxes at channel K + n0.
+    int32_t split_in, split_out;
+    int32_t w_k_blocks;        // 64-deep K slices of the resident filter (per N tile)
+    int32_t w_blocks_per_tap;  // C / 64
+    int32_t epi_bytes;         // bytes of one epilogue staging buffer
+    int32_t epi_per_group;     // staging buffers per epilogue group: 2, or 1 when a buffer holds hi and lo boxes
 };
 
 // Cycle stamps of the first CTA's roles (loader, issuing lane, two epilogue groups), for tuning builds only.
@@ -303,6 +312,12 @@ __device__ unsigned long long g_conv_span[160][8];  // per CTA wall-clock ns: en
 #define CONV_TRACE(role, n, k) do {} while (0)
 #define CONV_SPAN_AT(thread, k) do {} while (0)
 #endif
+
+// x - hi for the lo half of a split (hi, lo) pair; 0 when hi is not finite (an infinite or NaN value lives in hi alone,
+// so that hi + lo reproduces it instead of inf - inf). x - hi is exact: hi holds the leading 8 significant bits of x.
+__device__ __forceinline__ float split_remainder(float x, uint32_t hi_bits) {
+    return (hi_bits & 0x7f800000u) == 0x7f800000u ? 0.0f : x - __uint_as_float(hi_bits);
+}
 
 template <int BN, bool HAS_RES>
 __global__ void __launch_bounds__(kPersistentThreads, 1)
@@ -391,7 +406,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                         mbar_expect_tx(res_full_bar(b), res_bytes);
 #pragma unroll
                         for (int j = 0; j < BN / 64; ++j)
-                            tma_load_2d(epi_base + b * kEpiBytes + j * (kTileM * 128), &map_res, ld.n_tile * BN + 64 * j, static_cast<int>(ld.out_row0), res_full_bar(b));
+                            tma_load_2d(epi_base + b * pargs.epi_bytes + j * (kTileM * 128), &map_res, ld.n_tile * BN + 64 * j, static_cast<int>(ld.out_row0), res_full_bar(b));
                     }
                 }
                 ld.open = true;
@@ -462,8 +477,8 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         // Start streaming right away: the filter and the first ring-full of activations are in flight
         // while the other warps allocate tensor memory and stage the bias vectors.
         for (int nt = 0; nt < pargs.n_tiles; ++nt)
-            for (int kb = 0; kb < args.k_blocks; ++kb)
-                if (leader) tma_load_2d(w_base + (nt * args.k_blocks + kb) * kBTileBytes, &map_b, kb * kBlockK, nt * BN, w_full_bar);
+            for (int kb = 0; kb < pargs.w_k_blocks; ++kb)
+                if (leader) tma_load_2d(w_base + (nt * pargs.w_k_blocks + kb) * kBTileBytes, &map_b, kb * kBlockK, nt * BN, w_full_bar);
         if (pargs.early_static) chain_wait();
         ld.tile = blockIdx.x;
         ld.phase = 1;
@@ -531,8 +546,9 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     // tap s of this filter row reads the slot from row s on: only the start address moves, by s * 128 bytes.
                     // The 128-byte swizzle is a function of the absolute shared-memory address (TMA wrote the slot that
                     // way), so a start in the middle of an 8-row swizzle atom needs no base offset in the descriptor.
-                    const uint32_t b_first = smem_desc_lo(w_base + ((n_tile * args.k_blocks + halo_r * args.filter_s * args.k_blocks_per_tap + halo_c) * kBTileBytes), 16);
-                    const uint32_t b_tap_step = static_cast<uint32_t>(args.k_blocks_per_tap * kBTileBytes) >> 4;
+                    const int w_c = halo_c >= pargs.w_blocks_per_tap ? halo_c - pargs.w_blocks_per_tap : halo_c;  // the lo half meets the same filter slices
+                    const uint32_t b_first = smem_desc_lo(w_base + ((n_tile * pargs.w_k_blocks + halo_r * args.filter_s * pargs.w_blocks_per_tap + w_c) * kBTileBytes), 16);
+                    const uint32_t b_tap_step = static_cast<uint32_t>(pargs.w_blocks_per_tap * kBTileBytes) >> 4;
                     if (leader) {
                         const uint32_t first = kb0 != 0 ? 1u : 0u;
                         if (args.filter_s == 3) {
@@ -554,7 +570,11 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     }
                     if (++halo_c == args.k_blocks_per_tap) { halo_c = 0; ++halo_r; }
                 } else if (leader) {
-                    const uint32_t b_lo = smem_desc_lo(w_base + (n_tile * args.k_blocks + kb0) * kBTileBytes, 16);
+                    // filter slice of activation slice kb0 (they differ for a split input: both halves of a tap's channels
+                    // meet that tap's filter slices; a group of G slices never straddles a half)
+                    const int tap = kb0 / args.k_blocks_per_tap, c = kb0 - tap * args.k_blocks_per_tap;
+                    const int w_kb0 = tap * pargs.w_blocks_per_tap + (c >= pargs.w_blocks_per_tap ? c - pargs.w_blocks_per_tap : c);
+                    const uint32_t b_lo = smem_desc_lo(w_base + (n_tile * pargs.w_k_blocks + w_kb0) * kBTileBytes, 16);
                     for (int g = 0; g < G; ++g) {
 #pragma unroll
                         for (int k = 0; k < kBlockK / 16; ++k)
@@ -591,7 +611,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const int n0 = n_tile * BN;
             const int i = group + 2 * j;  // position of this tile in the CTA's tile list
             const int acc = i % kAccumulators;
-            const int buf = group * 2 + (j & 1);  // two staging buffers per epilogue group, used alternately
+            const int buf = pargs.epi_per_group == 2 ? group * 2 + (j & 1) : group;  // two staging buffers per epilogue group, used alternately (or one)
             if (HAS_RES && store_thread && j >= 1) {
                 // The store of this group's previous tile has had a whole wait to read its buffer: hand the
                 // buffer back now, so that its next residual tile streams in while this tile is worked on.
@@ -606,12 +626,15 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             } else {
                 // this staging buffer was last read by the TMA store of this group's tile before last: at most the
                 // previous tile's store may still be reading (the other buffer)
-                if (store_thread) tma_store_wait_read<1>();
+                if (store_thread) {
+                    if (pargs.epi_per_group == 2) tma_store_wait_read<1>();
+                    else tma_store_wait_read<0>();
+                }
                 epilogue_barrier(1 + group);
             }
             tc_fence_after();
             const bool healthy = ok && g_device_status == 0;
-            uint8_t* tile_smem = generic_base + pargs.epi_offset + buf * kEpiBytes;
+            uint8_t* tile_smem = generic_base + pargs.epi_offset + buf * pargs.epi_bytes;
 #pragma unroll 1
             for (int chunk = 0; chunk < BN / 32; ++chunk) {
                 uint32_t raw[32];
@@ -664,6 +687,22 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     }
                     if (row_is_output) *reinterpret_cast<uint4*>(row_smem + (((chunk16 + q4) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
+                if (!HAS_RES && pargs.split_out) {
+                    uint8_t* lo_smem = row_smem + (BN / 64) * (kTileM * 128);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            const float a = v[8 * q4 + 2 * t], b = v[8 * q4 + 2 * t + 1];
+                            __nv_bfloat162 hi = __floats2bfloat162_rn(a, b);
+                            const uint32_t hi_bits = *reinterpret_cast<uint32_t*>(&hi);
+                            __nv_bfloat162 pair = __floats2bfloat162_rn(split_remainder(a, hi_bits << 16), split_remainder(b, hi_bits & 0xffff0000u));
+                            w[t] = *reinterpret_cast<uint32_t*>(&pair);
+                        }
+                        if (row_is_output) *reinterpret_cast<uint4*>(lo_smem + (((chunk16 + q4) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
             }
             // release the accumulator, then publish the finished tile
             if (store_thread) CONV_TRACE(2 + group, j, 2);
@@ -676,7 +715,12 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 if (healthy) {
 #pragma unroll
                     for (int q = 0; q < BN / 64; ++q)
-                        tma_store_2d(&map_out, epi_base + buf * kEpiBytes + q * (kTileM * 128), n0 + 64 * q, static_cast<int>(out_row0));
+                        tma_store_2d(&map_out, epi_base + buf * pargs.epi_bytes + q * (kTileM * 128), n0 + 64 * q, static_cast<int>(out_row0));
+                    if (!HAS_RES && pargs.split_out) {
+#pragma unroll
+                        for (int q = 0; q < BN / 64; ++q)
+                            tma_store_2d(&map_out, epi_base + buf * pargs.epi_bytes + (BN / 64 + q) * (kTileM * 128), static_cast<int>(args.n_total) + n0 + 64 * q, static_cast<int>(out_row0));
+                    }
                 }
                 tma_store_commit();
                 CONV_TRACE(2 + group, j, 3);
@@ -732,15 +776,17 @@ constexpr int kSmemBudget = 227 * 1024;
 template <int BN, bool HAS_RES>
 int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_out, const CUtensorMap& map_res,
                       PersistentArgs args, cudaStream_t stream) {
-    constexpr int kEpiBytes = (BN / 64) * kTileM * 128;
-    constexpr int kEpiBuffers = 4;  // two per epilogue group: a tile is staged while the previous tile's TMA store still reads
     constexpr int kBarrierBytes = (2 * kMaxRingStages + 18) * 8;
     int bias_vectors = 0;
     for (int e = 0; e < args.gemm.epi_count; ++e) bias_vectors += args.gemm.epi_kind[e] == kEpiBias;
     const int bias_bytes = (bias_vectors * args.bias_stride * 4 + 1023) & ~1023;
+    // staging: two buffers per epilogue group (a tile is staged while the previous tile's TMA store still reads), or one
+    // per group when a buffer holds the hi and the lo boxes of a split output
+    args.epi_per_group = args.split_out ? 1 : 2;
+    args.epi_bytes = (BN / 64) * kTileM * 128 * (args.split_out ? 2 : 1);
     args.w_offset = 0;
     args.epi_offset = (args.filter_bytes + 1023) & ~1023;
-    args.ring_offset = args.epi_offset + kEpiBuffers * kEpiBytes;
+    args.ring_offset = args.epi_offset + 2 * args.epi_per_group * args.epi_bytes;
     int room = kSmemBudget - 1024 - kBarrierBytes - bias_bytes - args.ring_offset;
     // K slices per handshake: the largest divisor of the K loop (<= 4) that still leaves >= 2 ring slots
     int group = 1;
@@ -749,7 +795,7 @@ int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const 
         args.slot_bytes = ((kTileM + args.gemm.filter_s - 1) * 128 + 1023) & ~1023;
     } else {
         for (int candidate = 4; candidate >= 2; --candidate)
-            if (args.gemm.k_blocks % candidate == 0 && room / (candidate * kTileM * kBlockK * 2) >= 2) {
+            if (args.gemm.k_blocks % candidate == 0 && (!args.split_in || args.w_blocks_per_tap % candidate == 0) && room / (candidate * kTileM * kBlockK * 2) >= 2) {
                 group = candidate;
                 break;
             }
@@ -771,7 +817,14 @@ int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const 
         if (error != cudaSuccess) return fail(kExecutionFailed, "tcgen05 conv: cannot reserve %d bytes of shared memory: %s", kSmemBudget, cudaGetErrorString(error));
         configured = kSmemBudget;
     }
-    const int grid = args.total_tiles < sm_count() ? args.total_tiles : sm_count();
+    // Even shares: every CTA walks ceil(tiles / SMs) tiles or one fewer. These launches are bandwidth-bound and a
+    // handful of tiles per CTA long, so a last round that only a few CTAs run costs more than the SMs left idle.
+    const int sms = sm_count();
+    int grid = args.total_tiles < sms ? args.total_tiles : sms;
+    if (args.total_tiles > sms) {
+        const int rounds = (args.total_tiles + sms - 1) / sms;
+        grid = (args.total_tiles + rounds - 1) / rounds;
+    }
     cudaError_t launched = launch_chained(umma_conv_persistent_kernel<BN, HAS_RES>, dim3(grid), dim3(kPersistentThreads), dynamic, stream, map_a, map_b, map_out, map_res, args);
     if (launched != cudaSuccess) return fail(kExecutionFailed, "tcgen05 conv (persistent): launch failed: %s", cudaGetErrorString(launched));
     return check_launch("tcgen05 conv (persistent)");
@@ -838,33 +891,105 @@ int pick_bn(int64_t n, int64_t k_blocks) {
 
 }  // namespace
 
-bool conv_umma_supported(const dfgpu_conv_params& p) {
-    if (p.x.dtype != DFGPU_BF16 || p.w.dtype != DFGPU_BF16 || (p.y.dtype != DFGPU_BF16 && p.y.dtype != DFGPU_F32)) return false;
+namespace {
+
+// What launch_conv_umma() does with a convolution, worked out from the descriptors alone (the query has no pointers).
+struct ConvForm {
+    int64_t N, C, H, W, K, P, Q, R, S;
+    bool split_in, split_out;   // DFGPU_BF16X2 activations / output
+    bool pointwise;             // 1 x 1, no padding: plain GEMM rows
+    int bn;
+    int rows_per_tile;          // output rows of one image per tile (non-pointwise, one slot per tap)
+    bool persistent;            // the persistent kernel (TMA-store epilogue) takes it
+    bool halo;                  // ... in the halo form
+    int halo_rows;
+};
+
+bool conv_form(const dfgpu_conv_params& p, ConvForm& f) {
+    const bool x_ok = p.x.dtype == DFGPU_BF16 || p.x.dtype == DFGPU_BF16X2;
+    const bool y_ok = p.y.dtype == DFGPU_BF16 || p.y.dtype == DFGPU_F32 || p.y.dtype == DFGPU_BF16X2;
+    if (!x_ok || p.w.dtype != DFGPU_BF16 || !y_ok) return false;
     if (!nhwc_packed(p.x) || !nhwc_packed(p.w) || !nhwc_packed(p.y)) return false;
     if (p.x.dim[1] != p.w.dim[1]) return false;  // groups == 1
-    const int64_t C = p.x.dim[1], K = p.y.dim[1], Q = p.y.dim[3];
-    if (C % 64 != 0 || K % 64 != 0 || Q > 128 || Q < 1) return false;
+    f.N = p.x.dim[0]; f.C = p.x.dim[1]; f.H = p.x.dim[2]; f.W = p.x.dim[3];
+    f.K = p.y.dim[1]; f.P = p.y.dim[2]; f.Q = p.y.dim[3]; f.R = p.w.dim[2]; f.S = p.w.dim[3];
+    f.split_in = p.x.dtype == DFGPU_BF16X2;
+    f.split_out = p.y.dtype == DFGPU_BF16X2;
+    if (f.C % 64 != 0 || f.K % 64 != 0 || f.Q > 128 || f.Q < 1) return false;
     if (p.stride[0] != 1 || p.stride[1] != 1 || p.dilation[0] != 1 || p.dilation[1] != 1 || p.reverse_filter) return false;
-    if (p.w.dim[2] * p.w.dim[3] > 49 || p.x.dim[0] * p.y.dim[2] > (1 << 22)) return false;
-    if (p.x.dim[2] > 65535 || p.x.dim[3] > 65535 || p.pre_pad[0] > 64 || p.pre_pad[1] > 64) return false;
-    return translate_epilogue(p.epilogue_count, p.epilogue, p.extra, p.y, 1, true, K, nullptr, nullptr);
+    if (f.R * f.S > 49 || f.N * f.P > (1 << 22)) return false;
+    if (f.H > 65535 || f.W > 65535 || p.pre_pad[0] > 64 || p.pre_pad[1] > 64) return false;
+    if (!translate_epilogue(p.epilogue_count, p.epilogue, p.extra, p.y, 1, true, f.K, nullptr, nullptr)) return false;
+    f.pointwise = f.R == 1 && f.S == 1 && p.pre_pad[0] == 0 && p.pre_pad[1] == 0 && p.post_pad[0] == 0 && p.post_pad[1] == 0;
+    f.bn = pick_bn(f.K, f.R * f.S * (f.C / kBlockK));
+    f.rows_per_tile = static_cast<int>(kTileM / f.Q);
+    // persistent form
+    int full_steps = 0, bias_steps = 0;
+    bool residual_bf16 = true;
+    for (int e = 0; e < p.epilogue_count; ++e) {
+        if (p.epilogue[e].op != DFGPU_EPI_ADD) continue;
+        const dfgpu_tensor& t = p.extra[p.epilogue[e].operand];
+        bool per_channel = true;  // same classification as translate_epilogue: anything that is not one value per channel is a full tensor
+        const int shift = p.y.rank - t.rank;
+        for (int axis = 0; axis < t.rank; ++axis) {
+            if (axis + shift == 1) per_channel = per_channel && t.dim[axis] == p.y.dim[1] && t.stride[axis] == 1;
+            else per_channel = per_channel && t.dim[axis] == 1;
+        }
+        if (shift > 1) per_channel = false;
+        if (per_channel) ++bias_steps;
+        else {
+            ++full_steps;
+            residual_bf16 = residual_bf16 && t.dtype == DFGPU_BF16;
+        }
+    }
+    // halo form: a tile is `halo_rows` output rows with their padded columns, halo_rows the largest divisor of P that fits
+    f.halo = false;
+    f.halo_rows = 0;
+    const int64_t pitch = f.Q + f.S - 1;
+    if (!f.pointwise && f.S > 1 && f.S <= 8 && pitch <= kTileM) {
+        int halo_rows = static_cast<int>(kTileM / pitch);
+        while (halo_rows > 1 && f.P % halo_rows != 0) --halo_rows;
+        f.halo = true;
+        f.halo_rows = halo_rows;
+    }
+    const bool whole_tiles = f.pointwise || f.halo || f.P % f.rows_per_tile == 0;
+    const bool residual_ok = full_steps == 0 || (full_steps == 1 && residual_bf16 && !f.split_out);
+    const int64_t filter_bytes = f.K * f.R * f.S * f.C * 2;
+    const int epilogue_bytes = (f.split_out ? 2 * 2 : 4) * (f.bn / 64) * kTileM * 128;
+    const bool filter_fits = bias_steps * f.K <= kMaxBiasFloats &&
+                             filter_bytes + epilogue_bytes + 3 * kTileM * kBlockK * 2 + bias_steps * f.K * 4 + 6144 <= kSmemBudget;
+    f.persistent = (p.reserved & 1) == 0 && p.y.dtype != DFGPU_F32 && whole_tiles && residual_ok && filter_fits && f.N * f.P * f.Q < (1ll << 31) && f.bn <= 128;
+    if (!f.persistent) f.halo = false;
+    // split tensors exist only in the persistent kernel
+    if ((f.split_in || f.split_out) && !f.persistent) return false;
+    return true;
+}
+
+}  // namespace
+
+bool conv_umma_supported(const dfgpu_conv_params& p) {
+    ConvForm form;
+    return conv_form(p, form);
 }
 
 int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStream_t stream) {
-    const int64_t N = p.x.dim[0], C = p.x.dim[1], H = p.x.dim[2], W = p.x.dim[3];
-    const int64_t K = p.y.dim[1], P = p.y.dim[2], Q = p.y.dim[3], R = p.w.dim[2], S = p.w.dim[3];
+    ConvForm f;
+    if (!conv_form(p, f)) return fail(kUnsupported, "CONV_FPROP: the tcgen05 kernel does not take this convolution");
+    const int64_t N = f.N, C = f.C, H = f.H, W = f.W, K = f.K, P = f.P, Q = f.Q, R = f.R, S = f.S;
+    const int64_t Ca = f.split_in ? 2 * C : C;    // bf16 channels per activation pixel in storage
+    const int64_t Kout = f.split_out ? 2 * K : K;  // bf16 channels per output pixel in storage
     if (!aligned16(tensors[0]) || !aligned16(tensors[1]) || !aligned16(tensors[2]))
         return fail(kInvalidArgument, "CONV_FPROP: the tcgen05 kernel needs 16-byte aligned X, W and Y");
     GemmArgs args{};
-    const bool pointwise = R == 1 && S == 1 && p.pre_pad[0] == 0 && p.pre_pad[1] == 0 && p.post_pad[0] == 0 && p.post_pad[1] == 0;
-    const int bn = pick_bn(K, R * S * (C / kBlockK));
+    const bool pointwise = f.pointwise;
+    const int bn = f.bn;
     CUtensorMap map_a, map_b;
     int status;
     int64_t m_tiles;
     if (pointwise) {
         const int64_t M = N * H * W;
-        uint64_t dims[2] = {static_cast<uint64_t>(C), static_cast<uint64_t>(M)};
-        uint64_t strides[1] = {static_cast<uint64_t>(C) * 2};
+        uint64_t dims[2] = {static_cast<uint64_t>(Ca), static_cast<uint64_t>(M)};
+        uint64_t strides[1] = {static_cast<uint64_t>(Ca) * 2};
         uint32_t box[2] = {kBlockK, kTileM};
         status = make_map(&map_a, tensors[0], 2, dims, strides, box, "CONV_FPROP X");
         if (status) return status;
@@ -872,9 +997,9 @@ int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStrea
         args.m_total = M;
         m_tiles = (M + kTileM - 1) / kTileM;
     } else {
-        const int rows = static_cast<int>(kTileM / Q);
-        uint64_t dims[4] = {static_cast<uint64_t>(C), static_cast<uint64_t>(W), static_cast<uint64_t>(H), static_cast<uint64_t>(N)};
-        uint64_t strides[3] = {static_cast<uint64_t>(C) * 2, static_cast<uint64_t>(W * C) * 2, static_cast<uint64_t>(H * W * C) * 2};
+        const int rows = f.rows_per_tile;
+        uint64_t dims[4] = {static_cast<uint64_t>(Ca), static_cast<uint64_t>(W), static_cast<uint64_t>(H), static_cast<uint64_t>(N)};
+        uint64_t strides[3] = {static_cast<uint64_t>(Ca) * 2, static_cast<uint64_t>(W * Ca) * 2, static_cast<uint64_t>(H * W * Ca) * 2};
         uint32_t box[4] = {kBlockK, static_cast<uint32_t>(Q), static_cast<uint32_t>(rows), 1};
         status = make_map(&map_a, tensors[0], 4, dims, strides, box, "CONV_FPROP X");
         if (status) return status;
@@ -890,7 +1015,7 @@ int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStrea
         status = make_map(&map_b, tensors[1], 2, dims, strides, box, "CONV_FPROP W");
         if (status) return status;
     }
-    args.k_blocks_per_tap = static_cast<int>(C / kBlockK);
+    args.k_blocks_per_tap = static_cast<int>(Ca / kBlockK);
     args.k_blocks = static_cast<int>(R * S) * args.k_blocks_per_tap;
     args.filter_s = static_cast<int>(S);
     args.pad_h = static_cast<int>(p.pre_pad[0]);
@@ -911,45 +1036,38 @@ int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStrea
             residual_step = e;
             ++full_steps;
         }
-    const int box_rows = pointwise ? kTileM : args.rows_per_tile * static_cast<int>(Q);
-    const bool whole_tiles = pointwise || P % args.rows_per_tile == 0;
-    const bool residual_ok = full_steps == 0 || (full_steps == 1 && args.epi_dtype[residual_step] == DFGPU_BF16);
-    const int64_t filter_bytes = K * R * S * C * 2;
-    const int epilogue_bytes = 4 * (bn / 64) * kTileM * 128;
-    int bias_steps = 0;
-    for (int e = 0; e < args.epi_count; ++e) bias_steps += args.epi_kind[e] == kEpiBias;
-    const bool filter_fits = bias_steps * K <= kMaxBiasFloats &&
-                             filter_bytes + epilogue_bytes + 3 * kTileM * kBlockK * 2 + bias_steps * K * 4 + 6144 <= kSmemBudget;
-    if ((p.reserved & 1) == 0 && p.y.dtype == DFGPU_BF16 && whole_tiles && residual_ok && filter_fits && N * P * Q < (1ll << 31) && bn <= 128) {
+    if (f.persistent) {
         PersistentArgs pargs{};
         pargs.gemm = args;
         pargs.early_static = (p.reserved & 2) ? 1 : 0;
+        pargs.split_in = f.split_in;
+        pargs.split_out = f.split_out;
+        pargs.w_blocks_per_tap = static_cast<int>(C / kBlockK);
+        pargs.w_k_blocks = static_cast<int>(R * S * (C / kBlockK));
+        int out_box_rows = pointwise ? kTileM : args.rows_per_tile * static_cast<int>(Q);
         // filters wider than one tap: load each filter row's input rows once, padded columns included
-        const int64_t pitch = Q + S - 1;
-        if (!pointwise && S > 1 && S <= 8 && pitch <= kTileM) {
-            const int halo_rows = static_cast<int>(kTileM / pitch);
-            if (halo_rows >= 1 && P % halo_rows == 0) {
-                pargs.halo = 1;
-                pargs.pitch = static_cast<int>(pitch);
-                pargs.gemm.rows_per_tile = halo_rows;
-                pargs.gemm.tiles_per_image = static_cast<int>(P / halo_rows);
-                m_tiles = N * pargs.gemm.tiles_per_image;
-                uint64_t dims4[4] = {static_cast<uint64_t>(C), static_cast<uint64_t>(W), static_cast<uint64_t>(H), static_cast<uint64_t>(N)};
-                uint64_t strides3[3] = {static_cast<uint64_t>(C) * 2, static_cast<uint64_t>(W * C) * 2, static_cast<uint64_t>(H * W * C) * 2};
-                uint32_t box4[4] = {kBlockK, static_cast<uint32_t>(pitch), static_cast<uint32_t>(halo_rows), 1};
-                status = make_map(&map_a, tensors[0], 4, dims4, strides3, box4, "CONV_FPROP X (halo)");
-                if (status) return status;
-            }
+        if (f.halo) {
+            const int64_t pitch = Q + S - 1;
+            pargs.halo = 1;
+            pargs.pitch = static_cast<int>(pitch);
+            pargs.gemm.rows_per_tile = f.halo_rows;
+            pargs.gemm.tiles_per_image = static_cast<int>(P / f.halo_rows);
+            m_tiles = N * pargs.gemm.tiles_per_image;
+            uint64_t dims4[4] = {static_cast<uint64_t>(Ca), static_cast<uint64_t>(W), static_cast<uint64_t>(H), static_cast<uint64_t>(N)};
+            uint64_t strides3[3] = {static_cast<uint64_t>(Ca) * 2, static_cast<uint64_t>(W * Ca) * 2, static_cast<uint64_t>(H * W * Ca) * 2};
+            uint32_t box4[4] = {kBlockK, static_cast<uint32_t>(pitch), static_cast<uint32_t>(f.halo_rows), 1};
+            status = make_map(&map_a, tensors[0], 4, dims4, strides3, box4, "CONV_FPROP X (halo)");
+            if (status) return status;
+            out_box_rows = f.halo_rows * static_cast<int>(Q);
         }
-        const int out_box_rows = pargs.halo ? pargs.gemm.rows_per_tile * static_cast<int>(Q) : box_rows;
         pargs.n_tiles = static_cast<int>(K / bn);
         pargs.total_tiles = static_cast<int>(m_tiles) * pargs.n_tiles;
         pargs.box_rows = out_box_rows;
-        pargs.filter_bytes = static_cast<int>(filter_bytes);
+        pargs.filter_bytes = static_cast<int>(K * R * S * C * 2);
         pargs.bias_stride = static_cast<int>(K);
         CUtensorMap map_out, map_res;
-        uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N * P * Q)};
-        uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
+        uint64_t dims[2] = {static_cast<uint64_t>(Kout), static_cast<uint64_t>(N * P * Q)};
+        uint64_t strides[1] = {static_cast<uint64_t>(Kout) * 2};
         uint32_t box[2] = {64, static_cast<uint32_t>(out_box_rows)};
         status = make_map(&map_out, tensors[2], 2, dims, strides, box, "CONV_FPROP Y");
         if (status) return status;

@@ -8,7 +8,9 @@
 #include <bit>
 #include <cstring>
 #include <fstream>
+#include <map>
 #include <set>
+#include <variant>
 #include <system_error>
 #include <unistd.h>
 
@@ -171,7 +173,7 @@ Status check_workspace(WorkspacePlan const& workspace) {
     return Status::ok();
 }
 
-bool tensor_in_range(dfgpu_tensor const& t) { return t.rank >= 0 && t.rank <= DFGPU_MAX_RANK && t.dtype >= 0 && t.dtype <= DFGPU_U8; }
+bool tensor_in_range(dfgpu_tensor const& t) { return t.rank >= 0 && t.rank <= DFGPU_MAX_RANK && t.dtype >= 0 && t.dtype <= DFGPU_BF16X2; }
 
 bool params_in_range(KernelParams const& params) {
     return std::visit([](auto const& p) {
@@ -248,19 +250,75 @@ Status read_plan(Reader& r, ArtifactInfo& info) {
     return Status::ok();
 }
 
-// Bindings must name an argument of the table or lie inside the workspace.
+std::uint64_t element_bytes(int dtype) {
+    switch (dtype) {
+        case DFGPU_F32: case DFGPU_I32: case DFGPU_BF16X2: return 4;
+        case DFGPU_F16: case DFGPU_BF16: return 2;
+        default: return 1;
+    }
+}
+
+// Bytes from the tensor's base to the end of its last element, the import::tensor_storage_bytes rule applied to a
+// kernel descriptor. False on a negative extent or stride, or when the span does not fit.
+bool descriptor_span(dfgpu_tensor const& t, std::uint64_t& bytes) {
+    constexpr std::uint64_t limit = std::uint64_t{1} << 56;
+    std::uint64_t last = 0, count = 1;
+    for (int axis = 0; axis < t.rank; ++axis) {
+        if (t.dim[axis] <= 0 || t.stride[axis] < 0) return false;
+        auto const extent = static_cast<std::uint64_t>(t.dim[axis]), stride = static_cast<std::uint64_t>(t.stride[axis]);
+        if (extent > limit || stride > limit || (extent > 1 && stride > limit / (extent - 1))) return false;
+        last += (extent - 1) * stride;
+        if (last > limit || count > limit / extent) return false;
+        count *= extent;
+    }
+    bytes = (t.reorder == DFGPU_REORDER_F8_128x4 ? count : last + 1) * element_bytes(t.dtype);
+    return true;
+}
+
+// The descriptor the launch applies to tensor slot `slot`, or null for a slot that carries one FLOAT value
+// (MATMUL_FP8's Amax_C and scales).
+dfgpu_tensor const* slot_descriptor(KernelStep const& step, std::size_t slot) {
+    return std::visit([slot](auto const& p) -> dfgpu_tensor const* {
+        using T = std::decay_t<decltype(p)>;
+        if constexpr (std::is_same_v<T, dfgpu_bsq_params>) { dfgpu_tensor const* t[] = {&p.x, &p.y, &p.scale}; return slot < 3 ? t[slot] : nullptr; }
+        else if constexpr (std::is_same_v<T, dfgpu_bsd_params>) { dfgpu_tensor const* t[] = {&p.x, &p.scale, &p.y}; return slot < 3 ? t[slot] : nullptr; }
+        else if constexpr (std::is_same_v<T, dfgpu_pointwise_params>) { dfgpu_tensor const* t[] = {&p.in0, &p.in1, &p.out}; return slot < 3 ? t[slot] : nullptr; }
+        else if constexpr (std::is_same_v<T, dfgpu_conv_params>) { dfgpu_tensor const* t[] = {&p.x, &p.w, &p.y, &p.extra[0], &p.extra[1]}; return slot < 5 ? t[slot] : nullptr; }
+        else if constexpr (std::is_same_v<T, dfgpu_matmul_params>) { dfgpu_tensor const* t[] = {&p.a, &p.b, &p.c, &p.a_scale, &p.b_scale, &p.extra[0], &p.extra[1]}; return slot < 7 ? t[slot] : nullptr; }
+        else if constexpr (std::is_same_v<T, dfgpu_sdpa_params>) {
+            dfgpu_tensor const* t[] = {&p.q, &p.k, &p.v, &p.o, &p.stats, &p.max, &p.sum_exp, &p.seq_q, &p.seq_kv, &p.page_table_k, &p.page_table_v, &p.bias, &p.sink, &p.block_mask};
+            return slot < 14 ? t[slot] : nullptr;
+        } else { dfgpu_tensor const* t[] = {&p.a, &p.b, &p.c}; return slot < 3 ? t[slot] : nullptr; }
+    }, step.params);
+}
+
+// Bindings must name an argument of the table or lie inside the workspace, and what the launch will read or write
+// through a binding (the storage span of the descriptor in its params block) must fit the argument's size_bytes or
+// the rest of the workspace: a stale or edited artifact must fail here, not write past the caller's buffers.
 Status check_bindings(ArtifactInfo const& info) {
-    std::set<std::int64_t> uids;
-    for (auto const& argument : info.metadata.arguments) uids.insert(argument.uid);
-    auto check = [&](TensorBinding const& binding) {
-        if (binding.kind == TensorBinding::Kind::kArgument) return uids.count(binding.uid) != 0;
-        if (binding.kind == TensorBinding::Kind::kWorkspace) return binding.offset < info.workspace.size_bytes && binding.offset % 16 == 0;
-        return true;
-    };
+    std::map<std::int64_t, std::uint64_t> argument_bytes;
+    for (auto const& argument : info.metadata.arguments) argument_bytes[argument.uid] = argument.size_bytes;
     for (auto const& step : info.plan.steps) {
-        for (auto const& binding : step.tensors)
-            if (!check(binding)) return bad("kernel plan: '" + step.label + "' binds a tensor that is neither an argument nor inside the workspace");
-        if (!check(step.scratch)) return bad("kernel plan: '" + step.label + "' has its scratch outside the workspace");
+        for (std::size_t slot = 0; slot < step.tensors.size(); ++slot) {
+            auto const& binding = step.tensors[slot];
+            if (binding.kind == TensorBinding::Kind::kAbsent) continue;
+            std::uint64_t span = 4;
+            if (auto const* descriptor = slot_descriptor(step, slot)) {
+                if (descriptor->rank == 0) return bad("kernel plan: '" + step.label + "' binds a tensor its params block marks absent");
+                if (!descriptor_span(*descriptor, span)) return bad("kernel plan: '" + step.label + "' has a tensor descriptor without a storage span");
+            }
+            if (binding.kind == TensorBinding::Kind::kArgument) {
+                auto it = argument_bytes.find(binding.uid);
+                if (it == argument_bytes.end()) return bad("kernel plan: '" + step.label + "' binds a tensor that is neither an argument nor inside the workspace");
+                if (span > it->second) return bad("kernel plan: '" + step.label + "' reads or writes past the end of argument " + std::to_string(binding.uid));
+            } else {
+                if (binding.offset >= info.workspace.size_bytes || binding.offset % 16 != 0)
+                    return bad("kernel plan: '" + step.label + "' binds a tensor that is neither an argument nor inside the workspace");
+                if (span > info.workspace.size_bytes - binding.offset) return bad("kernel plan: '" + step.label + "' reads or writes past the end of the workspace");
+            }
+        }
+        if (step.scratch.kind == TensorBinding::Kind::kWorkspace && (step.scratch.offset >= info.workspace.size_bytes || step.scratch.offset % 16 != 0))
+            return bad("kernel plan: '" + step.label + "' has its scratch outside the workspace");
     }
     return Status::ok();
 }

@@ -711,6 +711,7 @@ void narrow_virtual_tensors(Lowering& low) {
             if (!wanted) continue;
             dequantize->y.dtype = DFGPU_BF16;
         } else {
+            if (!low.options.bf16_virtual_tensors) continue;  // lossy: only on request
             if (!is_contraction(step.op)) continue;
             bool bf16_inputs = false;
             if (auto* conv = std::get_if<dfgpu_conv_params>(&step.params)) bf16_inputs = conv->x.dtype == DFGPU_BF16 && conv->w.dtype == DFGPU_BF16;
@@ -735,6 +736,71 @@ void narrow_virtual_tensors(Lowering& low) {
                 }
             }
         }
+    }
+}
+
+// FLOAT virtual tensors between bf16 tcgen05 convolutions -> DFGPU_BF16X2 (hi, lo) pairs. A tensor qualifies when
+// a convolution writes it and only convolutions read it, as their X; the set is then trimmed until the kernel
+// library resolves every touched launch to the tcgen05 kernel with those types (a launch that cannot take a
+// split tensor drops the tensors around it back to FLOAT).
+void split_virtual_tensors(Lowering& low) {
+    if (!low.options.narrow_virtual_tensors || low.options.disable_tensor_cores || low.options.bf16_virtual_tensors) return;
+    std::map<std::int64_t, std::size_t> writer;
+    std::map<std::int64_t, std::vector<std::size_t>> readers;
+    std::set<std::int64_t> disqualified;
+    for (std::size_t s = 0; s < low.plan.steps.size(); ++s) {
+        auto const& step = low.plan.steps[s];
+        for (std::size_t slot = 0; slot < step.tensors.size(); ++slot) {
+            auto const& binding = step.tensors[slot];
+            if (binding.kind != TensorBinding::Kind::kWorkspace) continue;
+            if (step.op != KernelOp::kConvFprop || (slot != 0 && slot != 2)) disqualified.insert(binding.uid);
+            else if (slot == 2) writer[binding.uid] = s;
+            else readers[binding.uid].push_back(s);
+        }
+    }
+    std::set<std::int64_t> chosen;
+    for (auto const& [uid, s] : writer)
+        if (!disqualified.count(uid) && !readers[uid].empty() && low.tensor(uid).data_type == DataType::kFloat32 && !low.storage_override.count(uid)) chosen.insert(uid);
+    auto resolves = [&](std::size_t s) {
+        auto const& step = low.plan.steps[s];
+        dfgpu_conv_params trial = std::get<dfgpu_conv_params>(step.params);
+        if (step.tensors[0].kind == TensorBinding::Kind::kWorkspace && chosen.count(step.tensors[0].uid)) trial.x.dtype = DFGPU_BF16X2;
+        if (step.tensors[2].kind == TensorBinding::Kind::kWorkspace && chosen.count(step.tensors[2].uid)) trial.y.dtype = DFGPU_BF16X2;
+        dfgpu_plan_info info{};
+        return dfgpu_query_conv_fprop(&trial, &info) == 0 && info.kernel == DFGPU_CONV_UMMA_BF16;
+    };
+    for (bool changed = true; changed && !chosen.empty();) {
+        changed = false;
+        for (auto uid : std::vector<std::int64_t>(chosen.begin(), chosen.end())) {
+            bool ok = resolves(writer[uid]);
+            for (auto reader : readers[uid]) ok = ok && resolves(reader);
+            if (!ok) {
+                chosen.erase(uid);
+                changed = true;
+            }
+        }
+    }
+    for (auto uid : chosen) {
+        low.storage_override[uid] = DFGPU_BF16X2;
+        std::get<dfgpu_conv_params>(low.plan.steps[writer[uid]].params).y.dtype = DFGPU_BF16X2;
+        for (auto reader : readers[uid]) std::get<dfgpu_conv_params>(low.plan.steps[reader].params).x.dtype = DFGPU_BF16X2;
+    }
+}
+
+// Alignment the resolved kernel's launcher demands of the pointer in tensor slot `slot` (0: no demand of its own).
+// The TMA-fed kernels read and write 16-byte units and have no narrower fallback (the block-scale launchers do).
+std::uint64_t kernel_alignment(KernelStep const& step, std::size_t slot) {
+    switch (step.op) {
+        case KernelOp::kConvFprop: return step.kernel == DFGPU_CONV_UMMA_BF16 ? 16 : 0;
+        case KernelOp::kMatmul:
+            if (step.kernel != DFGPU_MATMUL_UMMA_BF16 && step.kernel != DFGPU_MATMUL_UMMA_MXF8 && step.kernel != DFGPU_MATMUL_UMMA_MXF8_2SM) return 0;
+            return slot == 3 || slot == 4 ? 4 : 16;  // the scale tensors are gathered with 4-byte loads
+        case KernelOp::kSdpaForward:
+            if (step.kernel == DFGPU_SDPA_UMMA) return slot <= 3 ? 16 : 0;
+            if (step.kernel == DFGPU_SDPA_PAGED_DECODE_UMMA || step.kernel == DFGPU_SDPA_PAGED_DECODE) return slot <= 2 ? 16 : 0;
+            return 0;
+        case KernelOp::kMatmulFp8: return step.kernel == DFGPU_MATMUL_FP8_UMMA && slot <= 2 ? 16 : 0;
+        default: return 0;
     }
 }
 
@@ -841,6 +907,7 @@ Status compile_graph(SerializedGraph const& graph, CompileOptions const& options
         if (status.is_bad()) return status;
     }
     narrow_virtual_tensors(low);
+    split_virtual_tensors(low);
 
     // argument table: ascending UID, non-virtual tensors only
     GraphCompileMetadata metadata;
@@ -860,8 +927,7 @@ Status compile_graph(SerializedGraph const& graph, CompileOptions const& options
         argument.access = read && written ? TensorAccess::kReadWrite : (written ? TensorAccess::kWrite : TensorAccess::kRead);
         metadata.arguments.push_back(std::move(argument));
     }
-    auto status = validate_graph_compile_metadata(metadata);
-    if (status.is_bad()) return status;
+    Status status = Status::ok();
 
     // kernel queries + workspace requests (lifetimes in plan-step indices)
     std::vector<WorkspaceRequest> requests;
@@ -880,11 +946,19 @@ Status compile_graph(SerializedGraph const& graph, CompileOptions const& options
             requests.push_back({"scratch." + std::to_string(s), static_cast<std::uint64_t>(scratch), kWorkspaceAlignment, s, s});
             step.scratch.kind = TensorBinding::Kind::kWorkspace;
         }
+        // The reference's rule is alignment = clamp(element bytes, 1, 8); the TMA-fed kernels need 16, and saying so in
+        // the argument table makes execute() refuse a misaligned pack up front (DFE_INVALID_VARIANT_PACK) instead of
+        // part-way through the plan.
+        for (std::size_t slot = 0; slot < step.tensors.size(); ++slot)
+            if (step.tensors[slot].kind == TensorBinding::Kind::kArgument)
+                for (auto& argument : metadata.arguments)
+                    if (argument.uid == step.tensors[slot].uid) argument.alignment = std::max(argument.alignment, kernel_alignment(step, slot));
     }
+    if ((status = validate_graph_compile_metadata(metadata)).is_bad()) return status;
     for (auto const& [uid, range] : lifetime) {
         auto tensor = graph.tensors.at(uid);
         auto narrowed = low.storage_override.find(uid);
-        if (narrowed != low.storage_override.end()) tensor.data_type = DataType::kBFloat16;
+        if (narrowed != low.storage_override.end() && narrowed->second == DFGPU_BF16) tensor.data_type = DataType::kBFloat16;  // a (hi, lo) pair keeps FLOAT's 4 bytes
         std::uint64_t bytes = 0;
         if (!import::tensor_storage_bytes(tensor, bytes)) return fail(ErrorCode::kDimensionOverflow, tensor.name, "storage span overflows int64");
         requests.push_back({tensor.name, bytes, kWorkspaceAlignment, range.first, range.second});

@@ -52,6 +52,39 @@ def normal(seed: int, stream: int, count: int, mean: float = 0.0, std: float = 1
     return (mean + std * out[:count]).astype(np.float32)
 
 
+def normal_on_device(device, seed: int, stream: int, count: int, bf16: bool = True, chunk: int = 1 << 24):
+    """The N(0, 1) stream of normal() / the workloads' generators evaluated with torch on `device`, for tensors too
+    large to draw on the host in reasonable time (the paged KV pools): the same splitmix64 words (two's-complement
+    int64 arithmetic wraps like uint64), the same Box-Muller pairs in f64, cast to f32 and rounded to bf16. The
+    device's f64 log / cos / sin may differ from the host's in the last place, which survives the rounding to bf16
+    with probability ~2^-40 per element. `count` must be even. Returns a torch tensor (bf16 or f32)."""
+    import torch
+    assert count % 2 == 0
+    base = (seed * 0x9E3779B97F4A7C15 + stream * 0xD1B54A32D192ED03) & 0xFFFFFFFFFFFFFFFF
+
+    def signed(value: int) -> int:
+        value &= 0xFFFFFFFFFFFFFFFF
+        return value - (1 << 64) if value >= (1 << 63) else value
+
+    def shift_right(z, bits: int):
+        return (z >> bits) & ((1 << (64 - bits)) - 1)  # logical shift of the uint64 the int64 stands for
+
+    out = torch.empty(count, dtype=torch.bfloat16 if bf16 else torch.float32, device=device)
+    for start in range(0, count, chunk):
+        n = min(chunk, count - start)
+        z = torch.arange(n, dtype=torch.int64, device=device) + signed(base + start + 0x9E3779B97F4A7C15)
+        z = (z ^ shift_right(z, 30)) * signed(0xBF58476D1CE4E5B9)
+        z = (z ^ shift_right(z, 27)) * signed(0x94D049BB133111EB)
+        z = z ^ shift_right(z, 31)
+        u = shift_right(z, 11).to(torch.float64) * (2.0 ** -53)
+        u1 = torch.clamp(u[0::2], min=2.0 ** -53)
+        radius = torch.sqrt(-2.0 * torch.log(u1))
+        angle = 2.0 * np.pi * u[1::2]
+        values = torch.stack((radius * torch.cos(angle), radius * torch.sin(angle)), dim=1).reshape(-1)
+        out[start:start + n] = values.to(torch.float32).to(out.dtype)
+    return out
+
+
 def integers(seed: int, stream: int, count: int, low: int, high_inclusive: int) -> np.ndarray:
     span = np.uint64(high_inclusive - low + 1)
     return (raw_u64(seed, stream, count) % span).astype(np.int64) + low

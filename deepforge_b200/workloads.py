@@ -4,8 +4,8 @@ the algorithmic FLOPs / bytes the roofline is computed from.
 
 Inputs are synthetic stand-ins (there is no dataset in this benchmark): element i of the
 tensor with UID u in configuration c is a pure function of (20261125 + c, u, i), see
-synthetic.py. Tensors above 2^27 elements (the paged KV pool) are drawn on the device
-from torch's seeded generator instead, because the host generator would take minutes.
+synthetic.py. Tensors above 2^27 elements (the paged KV pool) are the same streams evaluated
+on the device (synthetic.normal_on_device), because the host generator would take minutes.
 """
 from __future__ import annotations
 
@@ -223,12 +223,8 @@ def c5(batch=64, hq=32, hkv=8, d=128, pages=16384, block=64, max_len=8192, min_l
         inputs[3] = _normal(seed, 3, pool, io)
     else:
         def device_pool(uid: int):
-            def make(device):
-                import torch
-                generator = torch.Generator(device=device)
-                generator.manual_seed(seed * 1000 + uid)
-                return torch.randn(pool, generator=generator, device=device, dtype=torch.float32 if io == "FLOAT" else torch.bfloat16)
-            return make
+            # the tensor's documented stream (synthetic.py), evaluated on the device
+            return lambda device: synthetic.normal_on_device(device, seed, uid, pool, bf16=io != "FLOAT")
         device_inputs = {2: device_pool(2), 3: device_pool(3)}
     width = DTYPE_BYTES[io]
     nbytes = total * hkv * d * width * 2.0 + 2.0 * batch * hq * d * width + 2.0 * batch * table * 4

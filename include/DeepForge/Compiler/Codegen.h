@@ -22,8 +22,15 @@ struct CompileOptions {
     // Fuse POINTWISE consumers into contraction epilogues and BLOCK_SCALE_DEQUANTIZE
     // producers into MATMUL operand loads.
     bool fuse = true;
-    // Store virtual tensors that only feed bf16 tensor-core contractions as bf16.
+    // Re-type FLOAT virtual tensors that only tensor-core contractions read, without giving up the FLOAT
+    // semantics of the graph: a dequantize output becomes bf16 (exact: an E4M3 code times a power of two),
+    // a tensor between two bf16 tcgen05 convolutions becomes a (hi, lo) bf16 pair per element (DFGPU_BF16X2:
+    // 4 bytes like FLOAT, the value kept to 2^-17 relative, both halves multiplied by the bf16 filter).
     bool narrow_virtual_tensors = true;
+    // Lossy and off by default: store such tensors as one bf16 instead (half the intermediate traffic; every
+    // narrowed tensor adds a rounding of up to 2^-9 relative to what its readers see, so a chain of
+    // contractions can leave the bf16 gate against the all-FLOAT evaluation of the graph).
+    bool bf16_virtual_tensors = false;
     // Force the CUDA-core kernels (used by tests to cross-check the tcgen05 paths).
     bool disable_tensor_cores = false;
 };

@@ -43,7 +43,14 @@ enum {
     DFGPU_E8M0 = 4,
     DFGPU_I32 = 5,
     DFGPU_E5M2 = 6, /* FP8_E5M2: MATMUL_FP8 operands and output only */
-    DFGPU_U8 = 7    /* UINT8: the SDPA block mask only */
+    DFGPU_U8 = 7,   /* UINT8: the SDPA block mask only */
+    /* An f32 value stored as two bf16, hi = bf16(x) and lo = bf16(x - hi) (x up to 2^-17 relative; an infinity or NaN
+       lives in hi with lo = 0). 4 bytes per element and strides counted in 4-byte elements, like FLOAT, but the
+       channel axis (stride 1, extent C) holds C hi values followed by C lo values. Only for workspace tensors that
+       one tcgen05 convolution writes and others read (CONV_FPROP X and Y with DFGPU_CONV_UMMA_BF16): the readers
+       multiply both halves by the same bf16 filter, so an intermediate keeps f32-grade precision through bf16
+       tensor-core products. */
+    DFGPU_BF16X2 = 8
 };
 
 enum { DFGPU_REORDER_NONE = 0, DFGPU_REORDER_F8_128x4 = 1 };

@@ -544,6 +544,61 @@ int dfo_conv_mvp_vector(const float* x, const float* w, float* y,
     return 0;
 }
 
+/* The same convolution as dfo_conv_generic below for the case a compiler turns into a static loop nest: rank 4,
+   one group, FLOAT data, channels with stride 1 in X, W and Y. Every output element is the same chain of f32
+   operations in the same order (c outermost, then the filter taps; a padded tap adds +0.0), so the results are
+   bit-identical to the flat loop; the chains of the K output channels of one pixel advance together, which is what
+   lets the compiler vectorise them. Output pixels [pixel_begin, pixel_end) of the N*P*Q (end < 0: all), so that
+   callers can run slabs on several threads. Returns 20 when the case does not apply. */
+int dfo_conv_generic_nhwc(const dfo_tensor* x, const float* x_data, const dfo_tensor* w, const float* w_data,
+                          const dfo_tensor* y, float* y_data, const dfo_conv_attrs* attrs,
+                          int64_t pixel_begin, int64_t pixel_end) {
+    if (x->rank != 4 || w->rank != 4 || y->rank != 4 || attrs->spatial_rank != 2) return 20;
+    if (x->dtype != DFO_F32 || w->dtype != DFO_F32 || y->dtype != DFO_F32) return 20;
+    if (x->dim[1] != w->dim[1] || x->stride[1] != 1 || w->stride[1] != 1 || y->stride[1] != 1) return 20;
+    const int64_t C = x->dim[1], H = x->dim[2], W = x->dim[3], K = y->dim[1], P = y->dim[2], Q = y->dim[3];
+    const int64_t R = w->dim[2], S = w->dim[3];
+    const int64_t pixels = y->dim[0] * P * Q;
+    if (pixel_begin < 0) pixel_begin = 0;
+    if (pixel_end < 0 || pixel_end > pixels) pixel_end = pixels;
+    float* filter = (float*)malloc((size_t)(C * R * S * K) * sizeof(float));  /* [c][r][s][k] */
+    float* sums = (float*)malloc((size_t)K * sizeof(float));
+    if (!filter || !sums) { free(filter); free(sums); return 19; }
+    for (int64_t c = 0; c < C; ++c)
+        for (int64_t r = 0; r < R; ++r)
+            for (int64_t s = 0; s < S; ++s) {
+                const int64_t wr = attrs->reverse_filter ? R - 1 - r : r, ws = attrs->reverse_filter ? S - 1 - s : s;
+                for (int64_t k = 0; k < K; ++k)
+                    filter[((c * R + r) * S + s) * K + k] = w_data[k * w->stride[0] + c + wr * w->stride[2] + ws * w->stride[3]];
+            }
+    for (int64_t pixel = pixel_begin; pixel < pixel_end; ++pixel) {
+        const int64_t q = pixel % Q, p = (pixel / Q) % P, n = pixel / (P * Q);
+        for (int64_t k = 0; k < K; ++k) sums[k] = 0.0f;
+        for (int64_t c = 0; c < C; ++c)
+            for (int64_t r = 0; r < R; ++r) {
+                const int64_t ih = p * attrs->stride[0] + r * attrs->dilation[0] - attrs->pre_pad[0];
+                for (int64_t s = 0; s < S; ++s) {
+                    const int64_t iw = q * attrs->stride[1] + s * attrs->dilation[1] - attrs->pre_pad[1];
+                    if (ih < 0 || ih >= H || iw < 0 || iw >= W) {
+                        for (int64_t k = 0; k < K; ++k) sums[k] = sums[k] + 0.0f;
+                        continue;
+                    }
+                    const float value = x_data[n * x->stride[0] + c + ih * x->stride[2] + iw * x->stride[3]];
+                    const float* row = filter + ((c * R + r) * S + s) * K;
+                    for (int64_t k = 0; k < K; ++k) {
+                        float product = value * row[k];
+                        sums[k] = sums[k] + product;
+                    }
+                }
+            }
+        float* out = y_data + n * y->stride[0] + p * y->stride[2] + q * y->stride[3];
+        for (int64_t k = 0; k < K; ++k) out[k] = sums[k];
+    }
+    free(filter);
+    free(sums);
+    return 0;
+}
+
 /* lib/Compiler/TrainingGraph.cpp:165-296 (decode) and :380-542 (emit_fprop):
    flat loop over logical Y; reduction over c (within the group), then filter
    axes; a tap whose input coordinate falls in the padding contributes +0.0
@@ -623,6 +678,29 @@ int dfo_matmul(const dfo_tensor* a, const void* a_data,
             a_base += (a->dim[i] == 1 ? 0 : bi[i]) * a->stride[i];
             b_base += (b->dim[i] == 1 ? 0 : bi[i]) * b->stride[i];
             c_base += bi[i] * c->stride[i];
+        }
+        if (a->dtype == DFO_F32 && b->dtype == DFO_F32 && c->dtype == DFO_F32 && b->stride[rank - 1] == 1 && c->stride[rank - 1] == 1) {
+            /* static loop nest: the n chains of one row advance together (each still sums k in order, one multiply
+               and one add per step), so the compiler can vectorise across n; results are bit-identical */
+            const float* af = (const float*)a_data + a_base;
+            const float* bf = (const float*)b_data + b_base;
+            float* cf = (float*)c_data + c_base;
+            float* sums = (float*)malloc((size_t)n * sizeof(float));
+            if (!sums) return 19;
+            for (int64_t im = row_begin; im < row_end; ++im) {
+                for (int64_t in = 0; in < n; ++in) sums[in] = 0.0f;
+                for (int64_t ik = 0; ik < kk; ++ik) {
+                    const float av = af[im * a->stride[rank - 2] + ik * a->stride[rank - 1]];
+                    const float* brow = bf + ik * b->stride[rank - 2];
+                    for (int64_t in = 0; in < n; ++in) {
+                        float product = av * brow[in];
+                        sums[in] = sums[in] + product;
+                    }
+                }
+                for (int64_t in = 0; in < n; ++in) cf[im * c->stride[rank - 2] + in] = sums[in];
+            }
+            free(sums);
+            continue;
         }
         for (int64_t im = row_begin; im < row_end; ++im)
             for (int64_t in = 0; in < n; ++in) {

@@ -106,6 +106,12 @@ int dfo_conv_mvp_vector(const float* x, const float* w, float* y,
                         int64_t pad_bottom, int64_t pad_right, int32_t vf);
 /* generic DAG path: logical NC[D]HW dims with arbitrary strides, groups,
    stride, dilation; padded taps are skipped; order c then filter axes. */
+/* dfo_conv_generic for rank-4, one-group FLOAT tensors with stride-1 channels, written as a static loop nest
+   (bit-identical results, see the definition); output pixels [pixel_begin, pixel_end), end < 0 = all. 20 when
+   the case does not apply. */
+int dfo_conv_generic_nhwc(const dfo_tensor* x, const float* x_data, const dfo_tensor* w, const float* w_data,
+                          const dfo_tensor* y, float* y_data, const dfo_conv_attrs* attrs,
+                          int64_t pixel_begin, int64_t pixel_end);
 int dfo_conv_generic(const dfo_tensor* x, const void* x_data,
                      const dfo_tensor* w, const void* w_data,
                      const dfo_tensor* y, void* y_data,

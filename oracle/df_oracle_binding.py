@@ -6,8 +6,10 @@ is built on the machine that runs it)."""
 from __future__ import annotations
 
 import ctypes as C
+import os
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 import numpy as np
@@ -130,9 +132,45 @@ def conv_attrs(pre, post, stride, dilation, reverse=False) -> ConvAttrs:
     return a
 
 
-def conv_generic(xd, x, wd, w, yd, y, attrs) -> None:
+def host_threads() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def _slabs(total: int, threads: int):
+    threads = max(1, min(threads, total))
+    edges = [total * i // threads for i in range(threads + 1)]
+    return [(lo, hi) for lo, hi in zip(edges[:-1], edges[1:]) if hi > lo]
+
+
+def _run_slabs(call, total: int, threads: int) -> None:
+    """call(lo, hi) -> status code, over slabs of [0, total) on `threads` host threads (ctypes drops the GIL)."""
+    slabs = _slabs(total, threads)
+    if len(slabs) == 1:
+        codes = [call(*slabs[0])]
+    else:
+        with ThreadPoolExecutor(max_workers=len(slabs)) as pool:
+            codes = list(pool.map(lambda slab: call(*slab), slabs))
+    assert all(code == 0 for code in codes), codes
+
+
+def conv_generic_flat(xd, x, wd, w, yd, y, attrs) -> None:
+    """The literal flat loop over the logical output (any rank, groups, strides, storage types)."""
     code = lib().dfo_conv_generic(C.byref(xd), ptr(x), C.byref(wd), ptr(w), C.byref(yd), ptr(y), C.byref(attrs))
     assert code == 0, code
+
+
+def conv_generic(xd, x, wd, w, yd, y, attrs, threads: int = 1) -> None:
+    """Static-loop-nest form when the tensors allow it (bit-identical to the flat loop, see df_oracle.c), in pixel
+    slabs on `threads` host threads; the flat loop otherwise."""
+    pixels = int(yd.dim[0] * yd.dim[2] * yd.dim[3]) if yd.rank == 4 else 0
+    fn = lib().dfo_conv_generic_nhwc
+    probe = fn(C.byref(xd), ptr(x), C.byref(wd), ptr(w), C.byref(yd), ptr(y), C.byref(attrs), C.c_int64(0), C.c_int64(0)) if pixels else 20
+    if probe != 0:
+        return conv_generic_flat(xd, x, wd, w, yd, y, attrs)
+    _run_slabs(lambda lo, hi: fn(C.byref(xd), ptr(x), C.byref(wd), ptr(w), C.byref(yd), ptr(y), C.byref(attrs), C.c_int64(lo), C.c_int64(hi)), pixels, threads)
 
 
 def conv_mvp(x, w, n, h, wd, c, k, r, s, pads, vector_width=0) -> np.ndarray:
@@ -148,10 +186,13 @@ def conv_mvp(x, w, n, h, wd, c, k, r, s, pads, vector_width=0) -> np.ndarray:
     return y
 
 
-def matmul(ad, a, bd, b, cd, c, row_begin=0, row_end=-1) -> None:
-    code = lib().dfo_matmul(C.byref(ad), ptr(a), C.byref(bd), ptr(b), C.byref(cd), ptr(c), C.c_int64(row_begin),
-                            C.c_int64(row_end))
-    assert code == 0, code
+def matmul(ad, a, bd, b, cd, c, row_begin=0, row_end=-1, threads: int = 1) -> None:
+    rows = int(cd.dim[cd.rank - 2])
+    row_end = rows if row_end < 0 else min(row_end, rows)
+    if row_end <= row_begin:
+        return
+    _run_slabs(lambda lo, hi: lib().dfo_matmul(C.byref(ad), ptr(a), C.byref(bd), ptr(b), C.byref(cd), ptr(c), C.c_int64(row_begin + lo), C.c_int64(row_begin + hi)),
+               row_end - row_begin, threads)
 
 
 def matmul_fp8(ad, a, bd, b, cd, c, descale_a: float, descale_b: float, scale_c: float) -> float:
@@ -163,9 +204,13 @@ def matmul_fp8(ad, a, bd, b, cd, c, descale_a: float, descale_b: float, scale_c:
     return amax.value
 
 
-def sdpa_forward(params: SdpaParams, arrays, bh_begin=0, bh_end=1 << 62, q_step=1) -> None:
+def sdpa_forward(params: SdpaParams, arrays, bh_begin=0, bh_end=1 << 62, q_step=1, threads: int = 1) -> None:
     assert 11 <= len(arrays) <= 14  # the twelfth is the bias, then the sink token, then the block mask
     arrays = list(arrays) + [None] * (14 - len(arrays))
     pointers = (C.c_void_p * 14)(*[C.c_void_p(a.ctypes.data) if a is not None else C.c_void_p(None) for a in arrays])
-    code = lib().dfo_sdpa_forward(C.byref(params), pointers, C.c_int64(bh_begin), C.c_int64(bh_end), C.c_int64(q_step))
-    assert code == 0, code
+    bh_end = min(bh_end, int(params.q.dim[0] * params.q.dim[1]))
+    if bh_end <= bh_begin:
+        return
+    # (batch, head) pairs write disjoint outputs: slabs of them run side by side
+    _run_slabs(lambda lo, hi: lib().dfo_sdpa_forward(C.byref(params), pointers, C.c_int64(bh_begin + lo), C.c_int64(bh_begin + hi), C.c_int64(q_step)),
+               bh_end - bh_begin, threads)

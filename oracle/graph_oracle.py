@@ -57,11 +57,13 @@ def _alloc(t: dict) -> np.ndarray:
 
 def run(document: dict, inputs: Dict[int, np.ndarray], matmul_rows: Optional[Tuple[int, int]] = None,
         sdpa_bh: Optional[Tuple[int, int]] = None, sdpa_q_step: int = 1, storage_inputs: Optional[Dict[int, np.ndarray]] = None,
-        round_to_bf16: Tuple[int, ...] = ()) -> Dict[int, np.ndarray]:
+        round_to_bf16: Tuple[int, ...] = (), threads: int = 1) -> Dict[int, np.ndarray]:
     """inputs: uid -> widened arrays (see widen()). storage_inputs: uid -> raw storage-dtype arrays
     for tensors a BLOCK_SCALE_QUANTIZE reads (so bf16/f16 inputs are decoded by the oracle itself).
     round_to_bf16: UIDs of intermediate tensors to round to bf16 once produced -- the "staged"
-    oracle for a chain of bf16 tensor-core contractions, each of which reads bf16 operands."""
+    oracle for a chain of bf16 tensor-core contractions, each of which reads bf16 operands.
+    threads: host threads for the convolutions, matmuls and SDPA (batch, head) pairs; each output element is
+    computed by one thread with the same arithmetic, so the results do not depend on it."""
     tensors = {int(k): v for k, v in document["tensors"].items()}
     values: Dict[int, np.ndarray] = dict(inputs)
     for node in document["nodes"]:
@@ -71,7 +73,7 @@ def run(document: dict, inputs: Dict[int, np.ndarray], matmul_rows: Optional[Tup
             x, w, y = ins["X"], ins["W"], outs["Y"]
             values[y] = _alloc(tensors[y])
             attrs = oracle.conv_attrs(node["pre_padding"], node["post_padding"], node["stride"], node["dilation"], node["math_mode"] == "CONVOLUTION")
-            oracle.conv_generic(_desc(tensors[x]), values[x], _desc(tensors[w]), values[w], _desc(tensors[y]), values[y], attrs)
+            oracle.conv_generic(_desc(tensors[x]), values[x], _desc(tensors[w]), values[w], _desc(tensors[y]), values[y], attrs, threads=threads)
         elif tag == "POINTWISE":
             out = outs["OUT_0"]
             values[out] = _alloc(tensors[out])
@@ -88,7 +90,7 @@ def run(document: dict, inputs: Dict[int, np.ndarray], matmul_rows: Optional[Tup
             a, b, c = ins["A"], ins["B"], outs["C"]
             values[c] = _alloc(tensors[c])
             lo, hi = matmul_rows if matmul_rows else (0, -1)
-            oracle.matmul(_desc(tensors[a]), values[a], _desc(tensors[b]), values[b], _desc(tensors[c]), values[c], lo, hi)
+            oracle.matmul(_desc(tensors[a]), values[a], _desc(tensors[b]), values[b], _desc(tensors[c]), values[c], lo, hi, threads=threads)
         elif tag == "MATMUL_FP8":
             a, b, c, amax = ins["A"], ins["B"], outs["C"], outs["Amax_C"]
             values[c] = _alloc(tensors[c])
@@ -165,8 +167,9 @@ def run(document: dict, inputs: Dict[int, np.ndarray], matmul_rows: Optional[Tup
                 p.s_kv = tensors[ins["Page_table_K"]]["dim"][2] * k_t["dim"][2]
             else:
                 p.s_kv = k_t["dim"][2]
-            lo, hi = sdpa_bh if sdpa_bh else (0, 1 << 62)
-            oracle.sdpa_forward(p, arrays, lo, hi, sdpa_q_step)
+            q_t = tensors[ins["Q"]]
+            lo, hi = sdpa_bh if sdpa_bh else (0, q_t["dim"][0] * q_t["dim"][1])
+            oracle.sdpa_forward(p, arrays, lo, hi, sdpa_q_step, threads=threads)
         else:
             raise NotImplementedError(tag)
         for uid in outs.values():

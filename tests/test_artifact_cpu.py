@@ -178,9 +178,27 @@ def test_bindings_must_stay_inside_arguments_and_workspace():
     at = data.index(needle, layout.plan)
     assert code_of(_patched(data, at + 12, "<Q", exe.workspace_size)) == PARSE_ERROR
     assert code_of(_patched(data, at + 12, "<Q", 8)) == PARSE_ERROR  # inside, but not 16-byte aligned
+    assert code_of(_patched(data, at + 12, "<Q", exe.workspace_size - 64)) == PARSE_ERROR  # starts inside, its span runs past the end
     needle = struct.pack("<Iq", 1, 1)   # kArgument, uid 1 (X)
     at = data.index(needle, layout.plan)
     assert code_of(_patched(data, at + 4, "<q", 4242)) == PARSE_ERROR
+
+
+def test_descriptors_must_fit_the_buffers_they_are_bound_to():
+    """A params block whose tensor descriptor spans more bytes than the argument (or workspace range) its slot is
+    bound to would make the kernel read or write past the caller's buffer: refused at load, checksum or not."""
+    data = runtime.compile_graph(DOCS["c3"]).serialize()
+    layout = Layout(data)
+    at = layout.plan + 8 + 4
+    at += 4 + struct.unpack_from("<I", data, at)[0]
+    nodes = struct.unpack_from("<I", data, at)[0]
+    params_at = at + 4 + 8 * nodes + 12
+    # first launch = quantize A: x is the first descriptor (16 bytes of header, then dim[8], stride[8] as int64)
+    assert struct.unpack_from("<q", data, params_at + 16)[0] == 128
+    assert code_of(_patched(data, params_at + 16, "<q", 256)) == PARSE_ERROR       # twice the rows of the bound argument
+    assert code_of(_patched(data, params_at + 16 + 64, "<q", 1 << 40)) == PARSE_ERROR  # a row stride far beyond it
+    assert code_of(_patched(data, params_at + 16, "<q", -1)) == PARSE_ERROR        # no storage span at all
+    assert code_of(_patched(data, params_at + 16, "<q", 64)) in (0, INVALID_VALUE)  # a smaller view fits (the kernel re-resolution may still refuse it)
 
 
 def test_files_are_published_by_rename(tmp_path: Path):

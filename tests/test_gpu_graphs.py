@@ -10,8 +10,11 @@ import numpy as np
 import pytest
 
 sys.path.insert(0, str(Path(__file__).resolve().parent.parent / "oracle"))
+import df_oracle_binding as oracle_binding  # noqa: E402
 import graph_oracle  # noqa: E402
 from deepforge_b200 import dfgpu, harness, runtime, workloads  # noqa: E402
+
+THREADS = oracle_binding.host_threads()  # the oracle's per-element arithmetic does not depend on the thread count
 
 pytestmark = pytest.mark.gpu
 
@@ -54,16 +57,8 @@ def test_c1_single_conv(layout, shape):
     assert np.all(np.abs(s.output(3) - ref[3]) <= 1e-4 + 1e-3 * np.abs(ref[3]))  # the reference's own acceptance rule
 
 
-def check_chain(actual, staged, pure):
-    """A chain of three bf16 contractions: each contraction is held to the bf16 gate against the
-    oracle that feeds it the same bf16-rounded operands (the tensor core reads bf16); against
-    the all-f32 twin the rounding of the two intermediates compounds, so that comparison gets
-    twice the gate."""
-    check_bf16(actual, staged)
-    assert np.all(np.abs(actual - pure) <= 2e-2 + 4e-2 * np.abs(pure))
-
-
-@pytest.mark.parametrize("io,options", [("FLOAT", 0), ("BFLOAT16", 0), ("BFLOAT16", runtime.NO_TENSOR_CORES), ("BFLOAT16", runtime.NO_FUSION)])
+@pytest.mark.parametrize("io,options", [("FLOAT", 0), ("BFLOAT16", 0), ("BFLOAT16", runtime.NO_TENSOR_CORES), ("BFLOAT16", runtime.NO_FUSION),
+                                        ("BFLOAT16", runtime.NO_NARROWING), ("BFLOAT16", runtime.BF16_INTERMEDIATES)])
 def test_c2_bottleneck_small(io, options):
     wl = workloads.c2(n=2, h=14, w=14, io=io)
     s = harness.Session(wl, options=options)
@@ -72,11 +67,67 @@ def test_c2_bottleneck_small(io, options):
     ref = graph_oracle.run(wl.document, ins)
     if io == "FLOAT":
         check_f32(s.output(7), ref[7])
-    elif options == 0:
-        # intermediates 13 and 16 live in the workspace as bf16 (they only feed tensor-core convolutions)
-        check_chain(s.output(7), graph_oracle.run(wl.document, ins, round_to_bf16=(13, 16))[7], ref[7])
+    elif options == runtime.BF16_INTERMEDIATES:
+        # the lossy option, off by default: intermediates 13 and 16 are rounded to bf16 in the workspace, so the
+        # gate is held against the oracle that rounds at the same two points, not against the all-FLOAT twin
+        assert s.exe.plan_text().count("kernel=3") == 3
+        check_bf16(s.output(7), graph_oracle.run(wl.document, ins, round_to_bf16=(13, 16))[7])
     else:
-        check_bf16(s.output(7), ref[7])  # f32 intermediates: the plain gate holds end to end
+        # every other plan, the default one included (intermediates as (hi, lo) bf16 pairs between tcgen05
+        # convolutions), holds the plain gate against the all-FLOAT evaluation of the DAG
+        if options == 0:
+            assert s.exe.plan_text().count("kernel=3") == 3
+        check_bf16(s.output(7), ref[7])
+
+
+@pytest.mark.parametrize("shape", [dict(n=1, h=7, w=7), dict(n=3, h=28, w=28), dict(n=2, h=9, w=11), dict(n=1, h=8, w=120)])
+def test_c2_bottleneck_other_geometries(shape):
+    """Image sizes that give other tile shapes: the 3 x 3 convolution takes 7, 4, 9 or 1 output rows per tile."""
+    wl = workloads.c2(**shape)
+    s = harness.Session(wl)
+    assert s.exe.plan_text().count("kernel=3") == 3
+    s.run()
+    ins, _ = oracle_inputs(wl, s)
+    check_bf16(s.output(7), graph_oracle.run(wl.document, ins, threads=THREADS)[7])
+
+
+def test_split_intermediates_carry_f32_grade_values():
+    """The (hi, lo) pair storage on its own: with the intermediates made visible through a FLOAT-intermediate run of
+    the same graph, hi + lo of what conv1 wrote equals the f32 value to 2^-16 relative, far inside what a single
+    bf16 (2^-9) keeps. Read back from the workspace of the default plan."""
+    wl = workloads.c2(n=1, h=14, w=14)
+    s = harness.Session(wl)
+    s.run()
+    import torch
+    torch.cuda.synchronize()
+    plan = s.exe.plan_text()
+    assert "ws+0(uid13)" in plan
+    pixels, channels = 14 * 14, 64
+    raw = s.workspace[: pixels * channels * 4].cpu().numpy().view(np.uint16).reshape(pixels, 2, channels)
+    from deepforge_b200 import synthetic
+    hi, lo = synthetic.bf16_bits_to_f32(raw[:, 0, :]), synthetic.bf16_bits_to_f32(raw[:, 1, :])
+    ins, _ = oracle_inputs(wl, s)
+    t1 = graph_oracle.run({**wl.document, "nodes": wl.document["nodes"][:3]}, ins)[13].reshape(pixels, channels)
+    assert np.all(np.abs((hi.astype(np.float64) + lo) - t1) <= 2.0 ** -15 * np.abs(t1) + 1e-6)
+    assert np.all(np.abs(lo) <= 2.0 ** -8 * np.abs(hi) + 1e-30)  # lo is the rounding remainder of hi
+
+
+def test_misaligned_argument_is_refused_before_any_launch():
+    """Arguments bound to a TMA-fed launch advertise 16-byte alignment: a pointer the reference's rule would accept
+    (8-byte aligned bf16) is DFE_INVALID_VARIANT_PACK up front, not a failure part-way through the plan."""
+    import torch
+    wl = workloads.c2(n=1, h=14, w=14)
+    s = harness.Session(wl)
+    shifted = torch.zeros(s.dev[1].numel() + 16, dtype=torch.uint8, device=s.device)
+    shifted[8:8 + s.dev[1].numel()].copy_(s.dev[1])
+    pack = dict(s.pack)
+    pack[1] = shifted.data_ptr() + 8
+    s.dev[7].zero_()
+    with pytest.raises(runtime.DeepForgeError) as error:
+        s.exe.execute(pack, s.workspace_ptr)
+    assert error.value.code == 17 and "aligned" in str(error.value)
+    torch.cuda.synchronize()
+    assert not s.dev[7].any()  # nothing ran
 
 
 def test_c2_each_contraction_within_the_gate_given_its_own_inputs():
@@ -100,10 +151,20 @@ def test_c2_each_contraction_within_the_gate_given_its_own_inputs():
 def test_c2_bottleneck_full_geometry_two_images():
     wl = workloads.c2(n=2)  # 56x56, 256->64->64->256, the benchmark's per-image geometry
     s = harness.Session(wl)
-    assert s.exe.launch_count == 3 and s.exe.plan_text().count("kernel=3") == 3
+    assert s.exe.plan_text().count("kernel=3") == s.exe.launch_count
     s.run()
     ins, _ = oracle_inputs(wl, s)
-    check_chain(s.output(7), graph_oracle.run(wl.document, ins, round_to_bf16=(13, 16))[7], graph_oracle.run(wl.document, ins)[7])
+    check_bf16(s.output(7), graph_oracle.run(wl.document, ins, threads=THREADS)[7])
+
+
+def test_c2_bottleneck_full_size():
+    """The benchmark configuration itself (N = 32): every one of the 25.7 M outputs against the all-FLOAT twin."""
+    wl = workloads.c2()
+    s = harness.Session(wl)
+    assert s.exe.plan_text().count("kernel=3") == s.exe.launch_count
+    s.run()
+    ins, _ = oracle_inputs(wl, s)
+    check_bf16(s.output(7), graph_oracle.run(wl.document, ins, threads=THREADS)[7])
 
 
 @pytest.mark.parametrize("io,c_type,options", [("FLOAT", "FLOAT", 0), ("BFLOAT16", "BFLOAT16", 0), ("BFLOAT16", "FLOAT", runtime.NO_FUSION)])
@@ -118,33 +179,55 @@ def test_c3_quantize_matmul_small(io, c_type, options):
     (check_f32 if c_type == "FLOAT" else check_bf16)(s.output(9), ref[9])
 
 
-def test_c3_full_size_codes_exact_and_matmul_rows():
+def _quantize_slabs(document, node_index, uid, storage, slabs):
+    """The oracle's block-scale quantize over independent slabs of one operand (whole 32-element blocks each), on
+    host threads; returns (codes, scales) joined in slab order."""
+    from concurrent.futures import ThreadPoolExecutor
+    node = document["nodes"][node_index]
+    y, scale = node["outputs"]["Y"], node["outputs"]["scale"]
+
+    def one(slab):
+        sub_document, sub_storage = slab
+        out = graph_oracle.run({**sub_document, "nodes": [sub_document["nodes"][node_index]]}, {}, storage_inputs={uid: sub_storage})
+        return out[y], out[scale]
+
+    with ThreadPoolExecutor(max_workers=THREADS) as pool:
+        parts = list(pool.map(one, slabs))
+    return np.concatenate([p[0] for p in parts]), np.concatenate([p[1] for p in parts])
+
+
+def test_c3_full_size_every_code_and_scale_exact_and_matmul_rows():
+    """The benchmark configuration: all 2 x 16.8 M codes and 2 x 524,288 scales byte for byte against the oracle's
+    candidate search, and C on 256 rows spread over the matrix (every 16th)."""
     wl = workloads.c3()
     s = harness.Session(wl)
     s.run()
-    ins, storage = oracle_inputs(wl, s)
-    # oracle on a slab: 32 rows of A (all of K), and B through its first 64 K-rows
-    rows = 32
-    sub = workloads.c3(m=rows, k=4096, n=4096)
-    a_sub = {1: ins[1][: rows * 4096], 2: ins[2]}
-    st_sub = {1: storage[1][: rows * 4096]}
-    ref = graph_oracle.run({**sub.document, "nodes": [sub.document["nodes"][0]]}, a_sub, storage_inputs=st_sub)
-    assert np.array_equal(s.output(3)[: rows * 4096], ref[3])
-    assert np.array_equal(s.output(4)[: rows * 128], ref[4])
-    kb = workloads.c3(m=4096, k=64, n=4096)
-    ref_b = graph_oracle.run({**kb.document, "nodes": [kb.document["nodes"][1]]}, {2: ins[2][: 64 * 4096]}, storage_inputs={2: storage[2][: 64 * 4096]})
-    assert np.array_equal(s.output(5)[: 64 * 4096], ref_b[5])
-    assert np.array_equal(s.output(6)[: 2 * 4096], ref_b[6])
-    # matmul rows 0..7 from the GPU's own (verified) codes: dequantize + f32 matmul in the oracle
+    _, storage = oracle_inputs(wl, s)
+    m = k = n = 4096
+    # A is quantized along K inside each row: slabs of rows. B along K down each column: slabs of 32 K-rows.
+    rows = 128
+    a_doc = workloads.c3(m=rows, k=k, n=n).document
+    aq, sfa = _quantize_slabs(a_doc, 0, 1, storage[1], [(a_doc, storage[1][r * k:(r + rows) * k]) for r in range(0, m, rows)])
+    assert np.array_equal(s.output(3), aq), "Aq"
+    assert np.array_equal(s.output(4), sfa), "SFA"
+    depth = 128
+    b_doc = workloads.c3(m=m, k=depth, n=n).document
+    bq, sfb = _quantize_slabs(b_doc, 1, 2, storage[2], [(b_doc, storage[2][r * n:(r + depth) * n]) for r in range(0, k, depth)])
+    assert np.array_equal(s.output(5), bq), "Bq"
+    assert np.array_equal(s.output(6), sfb), "SFB"
+    # C rows 0, 16, 32, ...: dequantize (exact) and multiply in the oracle, f32 with k in order
+    picked = np.arange(0, m, 16)
     from oracle import tensor as T
     import oracle
-    aq, sa, bq, sb = s.output(3), s.output(4), s.output(5), s.output(6)
-    af = np.zeros(8 * 4096, dtype=np.float32)
-    oracle.block_scale_dequantize(T(dfgpu.E4M3, [8, 4096]), aq[: 8 * 4096], T(dfgpu.E8M0, [8, 128]), sa[: 8 * 128], T(dfgpu.F32, [8, 4096]), af, [1, 32])
-    bf = np.zeros(4096 * 4096, dtype=np.float32)
-    oracle.block_scale_dequantize(T(dfgpu.E4M3, [4096, 4096]), bq, T(dfgpu.E8M0, [128, 4096]), sb, T(dfgpu.F32, [4096, 4096]), bf, [32, 1])
-    c_ref = (af.reshape(8, 4096).astype(np.float64) @ bf.reshape(4096, 4096).astype(np.float64)).astype(np.float32)
-    check_bf16(s.output(9)[: 8 * 4096].reshape(8, 4096), c_ref)
+    a_rows = np.ascontiguousarray(aq.reshape(m, k)[picked]).reshape(-1)
+    s_rows = np.ascontiguousarray(sfa.reshape(m, k // 32)[picked]).reshape(-1)
+    af = np.zeros(picked.size * k, dtype=np.float32)
+    oracle.block_scale_dequantize(T(dfgpu.E4M3, [picked.size, k]), a_rows, T(dfgpu.E8M0, [picked.size, k // 32]), s_rows, T(dfgpu.F32, [picked.size, k]), af, [1, 32])
+    bf = np.zeros(k * n, dtype=np.float32)
+    oracle.block_scale_dequantize(T(dfgpu.E4M3, [k, n]), bq, T(dfgpu.E8M0, [k // 32, n]), sfb, T(dfgpu.F32, [k, n]), bf, [32, 1])
+    c_ref = np.zeros(picked.size * n, dtype=np.float32)
+    oracle.matmul(T(dfgpu.F32, [picked.size, k]), af, T(dfgpu.F32, [k, n]), bf, T(dfgpu.F32, [picked.size, n]), c_ref, threads=THREADS)
+    check_bf16(s.output(9).reshape(m, n)[picked], c_ref.reshape(picked.size, n))
 
 
 @pytest.mark.parametrize("io", ["FLOAT", "BFLOAT16"])
@@ -162,20 +245,23 @@ def test_c4_sdpa_small(io):
         assert np.all(np.abs(s.output(5) - ref[5]) <= 2e-3 * (1 + np.abs(ref[5])))
 
 
-def test_c4_sdpa_full_size_sampled_rows():
+def test_c4_sdpa_full_size_whole_heads():
+    """The benchmark configuration: every query row of eight (batch, head) pairs, the first and the last among them."""
     wl = workloads.c4()
     s = harness.Session(wl)
     s.run()
     ins, _ = oracle_inputs(wl, s)
-    # oracle on (batch 3, head 17) and (batch 7, head 31), every 64th query row
     out = s.output(4).reshape(8, 32, 2048, 128)
     stats = s.output(5).reshape(8, 32, 2048)
-    for bh in (3 * 32 + 17, 7 * 32 + 31):
-        ref = graph_oracle.run(wl.document, ins, sdpa_bh=(bh, bh + 1), sdpa_q_step=64)
+    pairs = [0, 1, 3 * 32 + 17, 4 * 32, 5 * 32 + 9, 6 * 32 + 30, 7 * 32 + 30, 7 * 32 + 31]
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(max_workers=THREADS) as pool:
+        references = list(pool.map(lambda bh: graph_oracle.run(wl.document, ins, sdpa_bh=(bh, bh + 1)), pairs))
+    for bh, ref in zip(pairs, references):
         b, h = divmod(bh, 32)
-        check_bf16(out[b, h, ::64], ref[4].reshape(8, 32, 2048, 128)[b, h, ::64])
-        r = ref[5].reshape(8, 32, 2048)[b, h, ::64]
-        assert np.all(np.abs(stats[b, h, ::64] - r) <= 2e-3 * (1 + np.abs(r)))
+        check_bf16(out[b, h], ref[4].reshape(8, 32, 2048, 128)[b, h])
+        r = ref[5].reshape(8, 32, 2048)[b, h]
+        assert np.all(np.abs(stats[b, h] - r) <= 2e-3 * (1 + np.abs(r)))
     # size-independent property: causal row 0 attends to key 0 only, so O[.., 0, :] == V[.., 0, :]
     v = ins[3].reshape(8, 32, 2048, 128)
     assert np.array_equal(out[:, :, 0], v[:, :, 0])
@@ -192,15 +278,21 @@ def test_c5_paged_decode_small_and_generic_agree():
         check_bf16(s.output(4), ref[4])
 
 
-def test_c5_paged_decode_full_size_sampled_sequences():
+def test_c5_paged_decode_full_size_ten_sequences():
+    """The benchmark configuration: all 32 heads of ten sequences, the shortest and the longest of the batch among them."""
     wl = workloads.c5()
     s = harness.Session(wl)
     s.run()
     out = s.output(4).reshape(64, 32, 128)
     ins, storage = oracle_inputs(wl, s, keep_in_storage=(2, 3))  # the 2 x 2.1 GB pools stay bf16 on the host
-    for b in (0, 41):
-        ref = graph_oracle.run(wl.document, ins, sdpa_bh=(b * 32, b * 32 + 8), storage_inputs=storage)
-        check_bf16(out[b, :8], ref[4].reshape(64, 32, 128)[b, :8])
+    lengths = ins[6]
+    chosen = sorted({int(np.argmin(lengths)), int(np.argmax(lengths)), 0, 7, 19, 28, 41, 50, 57, 63})
+    assert len(chosen) >= 8
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(max_workers=THREADS) as pool:
+        references = list(pool.map(lambda b: graph_oracle.run(wl.document, ins, sdpa_bh=(b * 32, b * 32 + 32), storage_inputs=storage), chosen))
+    for b, ref in zip(chosen, references):
+        check_bf16(out[b], ref[4].reshape(64, 32, 128)[b])
     # linearity in V: doubling the V pool doubles the output (bf16 doubling is exact)
     import torch
     s.dev[3].view(torch.bfloat16).mul_(2)

@@ -133,8 +133,14 @@ def test_bottleneck_plan_fuses_to_three_launches_and_shares_workspace():
     assert exe.launch_count == 3
     assert "[conv1+bias1+relu1]" in text and "[conv2+bias2+relu2]" in text and "[conv3+residual]" in text
     assert text.count("kernel=3") == 3  # tcgen05 implicit GEMM for all three
-    # two bf16 intermediates of 2*8*8*64 elements, alive at the same time
-    assert exe.workspace_size == 2 * (2 * 8 * 8 * 64 * 2)
+    # two intermediates of 2*8*8*64 elements, alive at the same time, each stored as (hi, lo) bf16 pairs: FLOAT's 4 bytes per element
+    assert exe.workspace_size == 2 * (2 * 8 * 8 * 64 * 4)
+    # the lossy option stores them as single bf16 values
+    lossy = runtime.compile_graph(graphs.c2_bottleneck(n=2, h=8, w=8), options=runtime.BF16_INTERMEDIATES)
+    assert lossy.plan_text().count("kernel=3") == 3 and lossy.workspace_size == 2 * (2 * 8 * 8 * 64 * 2)
+    # without narrowing the intermediates stay FLOAT: the first convolution still runs on tcgen05, its readers on CUDA cores
+    plain = runtime.compile_graph(graphs.c2_bottleneck(n=2, h=8, w=8), options=runtime.NO_NARROWING)
+    assert plain.plan_text().count("kernel=3") == 1 and plain.workspace_size == 2 * (2 * 8 * 8 * 64 * 4)
     unfused = runtime.compile_graph(graphs.c2_bottleneck(n=2, h=8, w=8), options=runtime.NO_FUSION)
     assert unfused.launch_count == 8
     f32 = runtime.compile_graph(graphs.c2_bottleneck(n=2, h=8, w=8, io="FLOAT"))
@@ -161,11 +167,18 @@ def test_quantize_matmul_plans():
 
 
 def test_argument_table_is_sorted_with_clamped_alignment():
-    exe = runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 128))
+    # the reference's rule, clamp(element bytes, 1, 8), wherever no TMA-fed kernel reads the argument
+    exe = runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 128), options=runtime.NO_TENSOR_CORES)
     arguments = exe.arguments()
     assert [a["uid"] for a in arguments] == [1, 2, 3, 4, 5, 6, 9]
     by_uid = {a["uid"]: a for a in arguments}
     assert by_uid[1]["alignment"] == 2 and by_uid[3]["alignment"] == 1 and by_uid[9]["alignment"] == 2
+    # arguments bound to a tcgen05 / TMA launch advertise the 16 bytes (scales: 4) that launch needs, so that
+    # execute() refuses a misaligned variant pack before anything is launched
+    exe = runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 128))
+    by_uid = {a["uid"]: a for a in exe.arguments()}
+    assert by_uid[1]["alignment"] == 2 and by_uid[3]["alignment"] == 16 and by_uid[5]["alignment"] == 16 and by_uid[9]["alignment"] == 16
+    assert by_uid[4]["alignment"] == 4 and by_uid[6]["alignment"] == 4
     assert by_uid[1]["access"] == "read" and by_uid[3]["access"] == "readwrite" and by_uid[9]["access"] == "write"
     assert by_uid[4]["size_bytes"] == 128 * 4
     decode = runtime.compile_graph(graphs.c5_paged_decode(2, 4, 2, 128, 8, 64, 256))

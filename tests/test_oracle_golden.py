@@ -416,3 +416,46 @@ def test_paged_sdpa_equals_contiguous_and_guards_invalid_pages():
     o[:] = -99.0
     oracle.sdpa_forward(p, [q, kc, vc, o, None, None, None, seq_q, seq_kv, page_k, page_v])
     assert o[0, 0, 0, 0] == 0.0 and o[0, 0, 0, 1] == 0.0
+
+
+def test_static_loop_nest_forms_are_bit_identical_to_the_flat_loops():
+    """dfo_conv_generic_nhwc and the vectorisable branch of dfo_matmul run the same chain of f32 operations per output
+    element as the literal restatements (c, then taps; k in order; one multiply and one add per step), so their
+    results must agree bit for bit, whatever the thread count."""
+    from deepforge_b200 import dfgpu
+    T = dfgpu.tensor
+    rng = np.random.default_rng(5)
+
+    def nhwc(n, c, h, w):
+        return T(dfgpu.F32, [n, c, h, w], [h * w * c, 1, w * c, c])
+
+    for n, c, h, w, k, r, pad, stride, dilation, reverse in [(2, 5, 7, 6, 9, 3, 1, 1, 1, False), (1, 4, 9, 9, 3, 3, 2, 2, 1, True), (1, 16, 6, 5, 8, 1, 0, 1, 1, False),
+                                                             (1, 3, 11, 8, 4, 3, 2, 1, 2, False)]:
+        x = rng.standard_normal(n * c * h * w).astype(np.float32)
+        x[::7] *= 1e4
+        weights = rng.standard_normal(k * c * r * r).astype(np.float32)
+        p = (h + 2 * pad - (dilation * (r - 1) + 1)) // stride + 1
+        q = (w + 2 * pad - (dilation * (r - 1) + 1)) // stride + 1
+        flat, fast = np.zeros(n * k * p * q, np.float32), np.zeros(n * k * p * q, np.float32)
+        attrs = oracle.conv_attrs([pad, pad], [pad, pad], [stride, stride], [dilation, dilation], reverse)
+        xd, wd, yd = nhwc(n, c, h, w), T(dfgpu.F32, [k, c, r, r], [r * r * c, 1, r * c, c]), nhwc(n, k, p, q)
+        oracle.conv_generic_flat(xd, x, wd, weights, yd, flat, attrs)
+        oracle.conv_generic(xd, x, wd, weights, yd, fast, attrs, threads=3)
+        assert np.array_equal(flat.view(np.uint32), fast.view(np.uint32))
+    m, kk, nn = 37, 200, 130
+    a, b = rng.standard_normal(m * kk).astype(np.float32), rng.standard_normal(kk * nn).astype(np.float32)
+    fast, flat = np.zeros(m * nn, np.float32), np.zeros(m * nn, np.float32)
+    oracle.matmul(T(dfgpu.F32, [m, kk]), a, T(dfgpu.F32, [kk, nn]), b, T(dfgpu.F32, [m, nn]), fast, threads=4)
+    transposed = np.ascontiguousarray(b.reshape(kk, nn).T).reshape(-1)  # column-major B takes the flat loop
+    oracle.matmul(T(dfgpu.F32, [m, kk]), a, T(dfgpu.F32, [kk, nn], [1, kk]), transposed, T(dfgpu.F32, [m, nn]), flat)
+    assert np.array_equal(flat.view(np.uint32), fast.view(np.uint32))
+
+
+def test_device_side_generator_reproduces_the_host_stream():
+    import torch
+    from deepforge_b200 import synthetic, workloads
+    seed, uid, count = 20261130, 2, 1 << 15
+    host = workloads._normal(seed, uid, count, "BFLOAT16")()
+    device = synthetic.normal_on_device(torch.device("cpu"), seed, uid, count, chunk=1 << 12).view(torch.uint16).numpy()
+    assert np.array_equal(host, device)
+    assert np.array_equal(synthetic.normal_on_device(torch.device("cpu"), seed, uid, 1000, bf16=False).numpy(), synthetic.normal(seed, uid, 1000))
