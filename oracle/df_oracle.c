@@ -408,53 +408,69 @@ int dfo_block_scale_dequantize(const dfo_tensor* x, const void* x_data,
 /* trailing-axis broadcast, :2599 ADD, :2731-2758 RELU_FWD)                  */
 /* ------------------------------------------------------------------------ */
 
-static int64_t broadcast_offset(const dfo_tensor* t, const dfo_tensor* out, const int64_t* index) {
-    int64_t offset = 0;
-    int shift = out->rank - t->rank;
-    for (int i = 0; i < t->rank; ++i) {
-        int64_t position = t->dim[i] == 1 ? 0 : index[i + shift];
-        offset += position * t->stride[i];
+/* One element of emit_pointwise; *unknown is set for a mode outside the executable set. */
+static float pointwise_value(int32_t mode, float x, float y, float relu_lower, float relu_upper, float relu_slope, int* unknown) {
+    switch (mode) {
+        case DFO_PW_ADD: return x + y;
+        case DFO_PW_MUL: return x * y;
+        case DFO_PW_SUB: return x - y;
+        case DFO_PW_RELU_FWD: {
+            float clipped = minimumf_nan(maximumf_nan(x, relu_lower), relu_upper);
+            float lower_branch = relu_lower + relu_slope * (x - relu_lower);
+            return x < relu_lower ? lower_branch : clipped;
+        }
+        case DFO_PW_IDENTITY: return x;
+        default: *unknown = 1; return 0.0f;
     }
-    return offset;
+}
+
+/* Elements [flat_begin, flat_end) of the logical output (row-major over its dims; end < 0 = all), so that callers can
+   run slabs on several threads. The index and the three storage offsets advance like an odometer instead of being
+   re-derived by division for every element; the arithmetic per element is the same. */
+int dfo_pointwise_range(int32_t mode, const dfo_tensor* a, const void* a_data,
+                        const dfo_tensor* b, const void* b_data,
+                        const dfo_tensor* out, void* out_data,
+                        float relu_lower, float relu_upper, float relu_slope,
+                        int64_t flat_begin, int64_t flat_end) {
+    int64_t index[DFO_MAX_RANK];
+    int64_t a_step[DFO_MAX_RANK], b_step[DFO_MAX_RANK];
+    int64_t count = element_count(out);
+    if (flat_begin < 0) flat_begin = 0;
+    if (flat_end < 0 || flat_end > count) flat_end = count;
+    if (flat_begin >= flat_end) return 0;
+    const int binary = mode == DFO_PW_ADD || mode == DFO_PW_MUL || mode == DFO_PW_SUB;
+    if (binary && (!b || !b_data)) return 1;
+    const int rank = out->rank;
+    for (int i = 0; i < rank; ++i) {  /* stride of each operand along output axis i (0 where it broadcasts) */
+        int ia = i - (rank - a->rank), ib = b ? i - (rank - b->rank) : -1;
+        a_step[i] = ia >= 0 && a->dim[ia] != 1 ? a->stride[ia] : 0;
+        b_step[i] = binary && ib >= 0 && b->dim[ib] != 1 ? b->stride[ib] : 0;
+    }
+    unflatten(out, flat_begin, index);
+    int64_t ao = 0, bo = 0, oo = 0;
+    for (int i = 0; i < rank; ++i) { ao += index[i] * a_step[i]; bo += index[i] * b_step[i]; oo += index[i] * out->stride[i]; }
+    int unknown = 0;
+    for (int64_t flat = flat_begin; flat < flat_end; ++flat) {
+        float x = load_f32(a, a_data, ao);
+        float y = binary ? load_f32(b, b_data, bo) : 0.0f;
+        store_f32(out, out_data, oo, pointwise_value(mode, x, y, relu_lower, relu_upper, relu_slope, &unknown));
+        if (unknown) return 20;
+        for (int i = rank - 1; i >= 0; --i) {  /* next index */
+            ++index[i];
+            ao += a_step[i]; bo += b_step[i]; oo += out->stride[i];
+            if (index[i] < out->dim[i]) break;
+            ao -= index[i] * a_step[i]; bo -= index[i] * b_step[i]; oo -= index[i] * out->stride[i];
+            index[i] = 0;
+        }
+    }
+    return 0;
 }
 
 int dfo_pointwise(int32_t mode, const dfo_tensor* a, const void* a_data,
                   const dfo_tensor* b, const void* b_data,
                   const dfo_tensor* out, void* out_data,
                   float relu_lower, float relu_upper, float relu_slope) {
-    int64_t index[DFO_MAX_RANK];
-    int64_t count = element_count(out);
-    for (int64_t flat = 0; flat < count; ++flat) {
-        unflatten(out, flat, index);
-        float x = load_f32(a, a_data, broadcast_offset(a, out, index));
-        float result;
-        switch (mode) {
-            case DFO_PW_ADD:
-                result = x + load_f32(b, b_data, broadcast_offset(b, out, index));
-                break;
-            case DFO_PW_MUL:
-                result = x * load_f32(b, b_data, broadcast_offset(b, out, index));
-                break;
-            case DFO_PW_SUB:
-                result = x - load_f32(b, b_data, broadcast_offset(b, out, index));
-                break;
-            case DFO_PW_RELU_FWD: {
-                float clipped = minimumf_nan(maximumf_nan(x, relu_lower), relu_upper);
-                float lower_branch = relu_lower + relu_slope * (x - relu_lower);
-                result = x < relu_lower ? lower_branch : clipped;
-                break;
-            }
-            case DFO_PW_IDENTITY:
-                result = x;
-                break;
-            default:
-                return 20;
-        }
-        int64_t offset = 0;
-        for (int i = 0; i < out->rank; ++i) offset += index[i] * out->stride[i];
-        store_f32(out, out_data, offset, result);
-    }
-    return 0;
+    return dfo_pointwise_range(mode, a, a_data, b, b_data, out, out_data, relu_lower, relu_upper, relu_slope, 0, -1);
 }
 
 /* ------------------------------------------------------------------------ */

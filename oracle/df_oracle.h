@@ -78,6 +78,12 @@ int dfo_block_scale_dequantize(const dfo_tensor* x, const void* x_data,
 
 /* pointwise */
 enum { DFO_PW_ADD = 0, DFO_PW_RELU_FWD = 1, DFO_PW_IDENTITY = 2, DFO_PW_MUL = 3, DFO_PW_SUB = 4 };
+/* dfo_pointwise over elements [flat_begin, flat_end) of the logical output (end < 0: all). */
+int dfo_pointwise_range(int32_t mode, const dfo_tensor* a, const void* a_data,
+                        const dfo_tensor* b, const void* b_data,
+                        const dfo_tensor* out, void* out_data,
+                        float relu_lower, float relu_upper, float relu_slope,
+                        int64_t flat_begin, int64_t flat_end);
 int dfo_pointwise(int32_t mode, const dfo_tensor* a, const void* a_data,
                   const dfo_tensor* b, const void* b_data,
                   const dfo_tensor* out, void* out_data,

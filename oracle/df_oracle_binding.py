@@ -116,11 +116,14 @@ def block_scale_dequantize(xd, x, sd, scale, yd, y, blocks) -> None:
     assert code == 0, code
 
 
-def pointwise(mode, ad, a, bd, b, od, out, lower=0.0, upper=3.4028234663852886e38, slope=0.0) -> None:
-    code = lib().dfo_pointwise(C.c_int32(mode), C.byref(ad), ptr(a), C.byref(bd) if bd is not None else None,
-                               ptr(b) if b is not None else None, C.byref(od), ptr(out), C.c_float(lower),
-                               C.c_float(upper), C.c_float(slope))
-    assert code == 0, code
+def pointwise(mode, ad, a, bd, b, od, out, lower=0.0, upper=3.4028234663852886e38, slope=0.0, threads: int = 1) -> None:
+    count = 1
+    for i in range(od.rank):
+        count *= int(od.dim[i])
+    fn = lib().dfo_pointwise_range
+    _run_slabs(lambda lo, hi: fn(C.c_int32(mode), C.byref(ad), ptr(a), C.byref(bd) if bd is not None else None, ptr(b) if b is not None else None,
+                                 C.byref(od), ptr(out), C.c_float(lower), C.c_float(upper), C.c_float(slope), C.c_int64(lo), C.c_int64(hi)),
+               count, threads if count >= (1 << 16) else 1)
 
 
 def conv_attrs(pre, post, stride, dilation, reverse=False) -> ConvAttrs:

@@ -85,7 +85,7 @@ def run(document: dict, inputs: Dict[int, np.ndarray], matmul_rows: Optional[Tup
             slope = node.get("relu_lower_clip_slope")
             oracle.pointwise(mode, _desc(tensors[a]), values[a], _desc(tensors[b]) if b is not None else None, values[b] if b is not None else None,
                              _desc(tensors[out]), values[out], 0.0 if lower is None else lower, FLT_MAX if upper is None else upper,
-                             0.0 if slope is None else slope)
+                             0.0 if slope is None else slope, threads=threads)
         elif tag == "MATMUL":
             a, b, c = ins["A"], ins["B"], outs["C"]
             values[c] = _alloc(tensors[c])
