@@ -14,6 +14,7 @@
 // iff padding/bounds allow it; max and sum run over valid scores only; a row with
 // no valid score gives O = 0, Stats = Max = -inf, Sum_exp = 0; an out-of-range page
 // id reads as zeros without touching memory.
+#include <atomic>
 #include "common.cuh"
 #include "umma.cuh"
 
@@ -661,23 +662,33 @@ static __device__ __align__(256) unsigned char g_static_decode_scratch[kStaticDe
 
 namespace {
 constexpr int kMaxDevices = 64;
-void* g_static_decode_scratch_address[kMaxDevices] = {};
+// One address per device, written once; atomic because two host threads may make their first call at the same time
+// (both resolve the same value).
+std::atomic<void*> g_static_decode_scratch_address[kMaxDevices];
 
-int static_decode_scratch(void** address) {
+int static_decode_scratch(void** address, cudaStream_t stream) {
     int device = 0;
     cudaError_t error = cudaGetDevice(&device);
     if (error != cudaSuccess) return dfgpu::fail(dfgpu::kExecutionFailed, "SDPA static decode: cudaGetDevice failed: %s", cudaGetErrorString(error));
     if (device < 0 || device >= kMaxDevices) return dfgpu::fail(dfgpu::kUnsupported, "SDPA static decode: device ordinal %d is above %d", device, kMaxDevices - 1);
-    if (g_static_decode_scratch_address[device] == nullptr) {
+    // The array belongs to the CURRENT device: a stream of another device would run the kernels there with this
+    // device's array. The legacy default stream (null) and the per-thread default stream follow the current device.
+    if (stream != nullptr && stream != cudaStreamLegacy && stream != cudaStreamPerThread) {
+        int stream_device = device;
+        if (cudaStreamGetDevice(stream, &stream_device) == cudaSuccess && stream_device != device)
+            return dfgpu::fail(dfgpu::kInvalidArgument, "SDPA static decode: the stream belongs to device %d but device %d is current", stream_device, device);
+        (void)cudaGetLastError();
+    }
+    if (g_static_decode_scratch_address[device].load(std::memory_order_acquire) == nullptr) {
         // In host code the array's name is only a handle for the runtime, not a device pointer:
         // the address a kernel can use has to come from the runtime, for the current device.
         void* resolved = nullptr;
         error = cudaGetSymbolAddress(&resolved, g_static_decode_scratch);
         if (error != cudaSuccess || resolved == nullptr)
             return dfgpu::fail(dfgpu::kExecutionFailed, "SDPA static decode: cudaGetSymbolAddress failed: %s", cudaGetErrorString(error));
-        g_static_decode_scratch_address[device] = resolved;
+        g_static_decode_scratch_address[device].store(resolved, std::memory_order_release);
     }
-    *address = g_static_decode_scratch_address[device];
+    *address = g_static_decode_scratch_address[device].load(std::memory_order_acquire);
     return dfgpu::kOk;
 }
 }  // namespace
@@ -697,9 +708,9 @@ extern "C" int dfgpu_sdpa_paged_decode_static(const dfgpu_sdpa_params* p, void* 
         return fail(kInvalidShape, "SDPA static decode: this call needs %zu bytes of split-KV partials, the built-in scratch holds %zu (batch * query heads * ceil(s_kv/256) * 520 must not exceed it)",
                     needed, kStaticDecodeScratchBytes);
     void* scratch = nullptr;
-    status = static_decode_scratch(&scratch);
-    if (status) return status;
     cudaStream_t stream = as_stream(stream_handle);
+    status = static_decode_scratch(&scratch, stream);
+    if (status) return status;
     const int group = static_cast<int>(p->q.dim[1] / p->k.dim[1]);
     dim3 grid(static_cast<unsigned>(chunks), static_cast<unsigned>(p->k.dim[1]), static_cast<unsigned>(p->q.dim[0]));
     float* partial = static_cast<float*>(scratch);

@@ -323,6 +323,34 @@ Status check_bindings(ArtifactInfo const& info) {
     return Status::ok();
 }
 
+// The single-node convolution form is recognisable from the table (exactly X, W, Y, rank-4 FLOAT, one CONV_FPROP
+// launch): rebuild the fields compile_graph derived, so that a loaded artifact describes itself like a compiled one.
+void restore_conv_metadata(ArtifactInfo& info) {
+    auto const& arguments = info.metadata.arguments;
+    if (arguments.size() != 3 || info.plan.steps.size() != 1 || info.plan.steps[0].op != KernelOp::kConvFprop) return;
+    if (arguments[0].name != "X" || arguments[1].name != "W" || arguments[2].name != "Y") return;
+    for (auto const& argument : arguments)
+        if (argument.data_type != import::DataType::kFloat32 || argument.dimensions.size() != 4) return;
+    auto const& params = std::get<dfgpu_conv_params>(info.plan.steps[0].params);
+    auto& m = info.metadata;
+    m.x_uid = arguments[0].uid;
+    m.w_uid = arguments[1].uid;
+    m.y_uid = arguments[2].uid;
+    std::copy(arguments[0].dimensions.begin(), arguments[0].dimensions.end(), m.x_shape.begin());
+    std::copy(arguments[1].dimensions.begin(), arguments[1].dimensions.end(), m.w_shape.begin());
+    std::copy(arguments[2].dimensions.begin(), arguments[2].dimensions.end(), m.y_shape.begin());
+    m.padded_x_shape = m.x_shape;
+    m.padded_x_shape[1] += params.pre_pad[0] + params.post_pad[0];
+    m.padded_x_shape[2] += params.pre_pad[1] + params.post_pad[1];
+    for (int i = 0; i < 2; ++i) {
+        m.pre_padding[i] = params.pre_pad[i];
+        m.post_padding[i] = params.post_pad[i];
+        m.stride[i] = params.stride[i];
+        m.dilation[i] = params.dilation[i];
+    }
+    if (validate_conv2d_adapter_metadata(m).is_good()) info.invocation = InvocationAdapterKind::kConv2DRankedMemref;
+}
+
 std::atomic<std::uint64_t> g_publish_sequence{0};
 
 Status read_file(std::filesystem::path const& path, std::vector<std::uint8_t>& bytes) {
@@ -354,7 +382,7 @@ Status serialize_artifact(CompilationResult const& compilation, std::vector<std:
     w.string(kBackendVersion);
     w.string("");  // llvm_version: none
     w.string(kFrontendVersion);
-    w.string(compilation.target);
+    w.string(compilation.target_triple);
     w.string(compilation.metadata.function_name);
     w.u32(0);  // dynamic_shape_enabled
     w.u32(0);  // override_shape_enabled
@@ -485,6 +513,7 @@ Status parse_artifact(std::span<std::uint8_t const> input, ArtifactInfo& output)
     if (variants != 0) return bad("a kernel-plan artifact carries no code variants");
     if (r.at != r.size) return bad("bytes between the last field and the checksum");
     if (auto status = check_bindings(info); status.is_bad()) return status;
+    restore_conv_metadata(info);
     output = std::move(info);
     return Status::ok();
 }

@@ -88,6 +88,32 @@ extern "C" int df_argument_info(const df_executable* executable, int64_t index, 
     return 0;
 }
 
+extern "C" size_t df_argument_name(const df_executable* executable, int64_t index, char* buffer, size_t capacity) {
+    auto const& arguments = executable->result.metadata.arguments;
+    if (index < 0 || index >= static_cast<int64_t>(arguments.size())) return 0;
+    auto const& name = arguments[static_cast<size_t>(index)].name;
+    if (buffer && capacity) {
+        size_t n = std::min(capacity - 1, name.size());
+        std::memcpy(buffer, name.data(), n);
+        buffer[n] = '\0';
+    }
+    return name.size();
+}
+
+extern "C" int df_conv2d_metadata(const df_executable* executable, int32_t* adapter_kind, int64_t* values) {
+    auto const& m = executable->result.metadata;
+    if (adapter_kind) *adapter_kind = static_cast<int32_t>(executable->result.adapter_kind);
+    if (values) {
+        int64_t* out = values;
+        *out++ = m.x_uid;
+        *out++ = m.w_uid;
+        *out++ = m.y_uid;
+        for (auto const* shape : {&m.x_shape, &m.w_shape, &m.y_shape, &m.padded_x_shape}) out = std::copy(shape->begin(), shape->end(), out);
+        for (auto const* pair : {&m.pre_padding, &m.post_padding, &m.stride, &m.dilation}) out = std::copy(pair->begin(), pair->end(), out);
+    }
+    return 0;
+}
+
 extern "C" void df_set_stream(df_executable* executable, void* stream) { executable->result.executable->set_stream(stream); }
 
 extern "C" int df_execute(const df_executable* executable, void* handle, const int64_t* uids, void* const* pointers, size_t count, void* workspace) {
@@ -161,9 +187,10 @@ namespace {
 int adopt(import::Status status, std::unique_ptr<df_executable> holder, compiler::ArtifactInfo& info, df_executable** out) {
     if (status.is_bad()) return report(status);
     holder->result.metadata = std::move(info.metadata);
+    holder->result.adapter_kind = info.invocation;
     holder->result.workspace = std::move(info.workspace);
     holder->result.plan = std::move(info.plan);
-    holder->result.target = info.target_triple;
+    holder->result.target_triple = info.target_triple;
     *out = holder.release();
     return 0;
 }

@@ -12,6 +12,7 @@
 #include "Internal.h"
 
 #include <algorithm>
+#include <array>
 #include <cfloat>
 #include <cmath>
 #include <map>
@@ -787,6 +788,57 @@ void split_virtual_tensors(Lowering& low) {
     }
 }
 
+// Fills the conv-adapter metadata when the graph is the reference's single-node case; false otherwise (the generic
+// table stands).
+bool single_conv_metadata(SerializedGraph const& graph, CompileOptions const& options, Conv2DCompileMetadata& metadata) {
+    auto const* node = graph.single_conv_fprop();
+    if (!node || graph.tensors.size() != 3) return false;
+    auto x = port(node->inputs, "X"), w = port(node->inputs, "W"), y = port(node->outputs, "Y");
+    auto pre = get_int_array(*node, "pre_padding"), post = get_int_array(*node, "post_padding"), stride = get_int_array(*node, "stride"),
+         dilation = get_int_array(*node, "dilation");
+    if (!x || !w || !y || !pre || !post || !stride || !dilation || pre->size() != 2 || post->size() != 2 || stride->size() != 2 || dilation->size() != 2) return false;
+    auto packed_channels_last = [](TensorDesc const& t) {
+        return t.dim.size() == 4 && !t.is_virtual && t.stride[1] == 1 && t.stride[3] == t.dim[1] && t.stride[2] == t.dim[3] * t.dim[1] &&
+               t.stride[0] == t.dim[2] * t.dim[3] * t.dim[1];
+    };
+    auto const &tx = graph.tensors.at(*x), &tw = graph.tensors.at(*w), &ty = graph.tensors.at(*y);
+    if (!packed_channels_last(tx) || !packed_channels_last(tw) || !packed_channels_last(ty)) return false;  // e.g. the NCHW-strided extension
+    auto physical = [](TensorDesc const& t) { return std::array<std::int64_t, 4>{t.dim[0], t.dim[2], t.dim[3], t.dim[1]}; };
+    metadata.function_name = options.importer.function_name;
+    metadata.x_uid = *x;
+    metadata.w_uid = *w;
+    metadata.y_uid = *y;
+    metadata.x_shape = physical(tx);
+    metadata.w_shape = physical(tw);
+    metadata.y_shape = physical(ty);
+    metadata.padded_x_shape = metadata.x_shape;
+    metadata.padded_x_shape[1] += (*pre)[0] + (*post)[0];
+    metadata.padded_x_shape[2] += (*pre)[1] + (*post)[1];
+    for (int i = 0; i < 2; ++i) {
+        metadata.pre_padding[i] = (*pre)[i];
+        metadata.post_padding[i] = (*post)[i];
+        metadata.stride[i] = (*stride)[i];
+        metadata.dilation[i] = (*dilation)[i];
+    }
+    metadata.arguments.clear();
+    auto append = [&](std::int64_t uid, char const* name, std::array<std::int64_t, 4> const& shape, TensorAccess access) {
+        TensorArgumentMetadata argument;
+        argument.uid = uid;
+        argument.name = name;
+        argument.data_type = DataType::kFloat32;
+        argument.dimensions.assign(shape.begin(), shape.end());
+        argument.strides = {shape[1] * shape[2] * shape[3], shape[2] * shape[3], shape[3], 1};
+        argument.size_bytes = static_cast<std::uint64_t>(shape[0] * shape[1] * shape[2] * shape[3]) * 4;
+        argument.alignment = alignof(float);
+        argument.access = access;
+        metadata.arguments.push_back(std::move(argument));
+    };
+    append(*x, "X", metadata.x_shape, TensorAccess::kRead);
+    append(*w, "W", metadata.w_shape, TensorAccess::kRead);
+    append(*y, "Y", metadata.y_shape, TensorAccess::kWrite);
+    return true;
+}
+
 // Alignment the resolved kernel's launcher demands of the pointer in tensor slot `slot` (0: no demand of its own).
 // The TMA-fed kernels read and write 16-byte units and have no narrower fallback (the block-scale launchers do).
 std::uint64_t kernel_alignment(KernelStep const& step, std::size_t slot) {
@@ -910,7 +962,7 @@ Status compile_graph(SerializedGraph const& graph, CompileOptions const& options
     split_virtual_tensors(low);
 
     // argument table: ascending UID, non-virtual tensors only
-    GraphCompileMetadata metadata;
+    Conv2DCompileMetadata metadata;
     metadata.function_name = options.foundational_function_name;
     for (auto const& [uid, tensor] : graph.tensors) {
         if (tensor.is_virtual) continue;
@@ -928,6 +980,9 @@ Status compile_graph(SerializedGraph const& graph, CompileOptions const& options
         metadata.arguments.push_back(std::move(argument));
     }
     Status status = Status::ok();
+    // The reference's single-node path (one f32 CONV_FPROP on packed NHWC / KRSC tensors) carries its own metadata
+    // and argument convention (lib/MLIR/Conv2DImporter.cpp:332-370): X, W, Y by those names, physical shapes.
+    bool const conv_adapter = single_conv_metadata(graph, options, metadata);
 
     // kernel queries + workspace requests (lifetimes in plan-step indices)
     std::vector<WorkspaceRequest> requests;
@@ -974,9 +1029,19 @@ Status compile_graph(SerializedGraph const& graph, CompileOptions const& options
         if (step.scratch.kind == TensorBinding::Kind::kWorkspace) step.scratch.offset = offsets.at("scratch." + std::to_string(s));
     }
 
+    if (conv_adapter && (status = validate_conv2d_adapter_metadata(metadata)).is_bad()) return status;
+    output.adapter_kind = conv_adapter ? InvocationAdapterKind::kConv2DRankedMemref : InvocationAdapterKind::kGenericRankedMemrefPointerTable;
     output.metadata = metadata;
     output.workspace = workspace;
     output.plan = low.plan;
+    output.target_triple = "sm_100a";
+    output.variants = {};
+    output.variants[0].variant = runtime::CpuVariant::kScalar;
+    output.variants[0].symbol = metadata.function_name;
+    output.variants[0].required_features = "sm_100a";
+    output.variants[0].schedule = "kernel-plan";
+    output.variants[1].variant = runtime::CpuVariant::kAvx2;
+    output.variants[2].variant = runtime::CpuVariant::kAvx512;
     output.executable = runtime::ExecutableFactory::create(metadata, workspace, low.plan);
     return Status::ok();
 }
@@ -989,8 +1054,33 @@ Status compile_file(std::filesystem::path const& path, CompileOptions const& opt
     return compile_graph(graph, options, output);
 }
 
+Status validate_conv2d_adapter_metadata(Conv2DCompileMetadata const& metadata) {
+    if (metadata.arguments.size() != 3) return fail(ErrorCode::kInvalidValue, "metadata.arguments", "Conv adapter requires a function name and three arguments");
+    if (metadata.dynamic_shape_enabled || metadata.override_shape_enabled || metadata.override_policy != ShapeOverridePolicy::kNone)
+        return fail(ErrorCode::kInvalidValue, "metadata.override", "Conv adapter does not support dynamic or override metadata");
+    for (auto const& argument : metadata.arguments)
+        if (argument.data_type != DataType::kFloat32 || argument.dimensions.size() != 4)
+            return fail(ErrorCode::kInvalidValue, "metadata.arguments", "Conv adapter requires rank-4 FLOAT arguments");
+    auto const &x = metadata.arguments[0], &w = metadata.arguments[1], &y = metadata.arguments[2];
+    auto same = [](TensorArgumentMetadata const& argument, std::array<std::int64_t, 4> const& shape) {
+        return std::equal(argument.dimensions.begin(), argument.dimensions.end(), shape.begin());
+    };
+    bool const matches = x.uid == metadata.x_uid && w.uid == metadata.w_uid && y.uid == metadata.y_uid && x.name == "X" && w.name == "W" && y.name == "Y" &&
+                         x.access == TensorAccess::kRead && w.access == TensorAccess::kRead && y.access == TensorAccess::kWrite &&
+                         same(x, metadata.x_shape) && same(w, metadata.w_shape) && same(y, metadata.y_shape);
+    if (!matches) return fail(ErrorCode::kInvalidValue, "metadata.arguments", "argument table does not match the Conv adapter");
+    return Status::ok();
+}
+
 Status validate_graph_compile_metadata(GraphCompileMetadata const& metadata) {
     if (metadata.arguments.empty() || metadata.arguments.size() > 4096) return fail(ErrorCode::kInvalidValue, "metadata", "argument count must be between 1 and 4096");
+    // no override or dynamic-shape metadata on this backend (override_shape_enabled == (policy != none) in the reference)
+    if (metadata.dynamic_shape_enabled || metadata.override_shape_enabled || metadata.override_policy != ShapeOverridePolicy::kNone ||
+        !metadata.override_role_uids.empty() || !metadata.override_axis_map.empty())
+        return fail(ErrorCode::kInvalidValue, "metadata.override", "shape-override metadata is not executable on this backend");
+    for (auto const& argument : metadata.arguments)
+        if (argument.storage_policy != TensorStoragePolicy::kStrided || argument.ragged_offset_uid != 0 || argument.ragged_sequence_uid != 0 || argument.ragged_sequence_divisor != 1)
+            return fail(ErrorCode::kInvalidValue, argument.name, "a strided argument carries no ragged references and divisor 1");
     std::set<std::int64_t> uids;
     for (auto const& argument : metadata.arguments) {
         if (!uids.insert(argument.uid).second) return fail(ErrorCode::kDuplicateUid, argument.name, "argument UID is used twice");

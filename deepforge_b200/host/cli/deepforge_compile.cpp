@@ -281,7 +281,7 @@ int run(int argc, char** argv) {
         return 1;
     }
     std::cout << "output: " << options.output << '\n'
-              << "target: " << compilation.target << '\n'
+              << "target: " << compilation.target_triple << '\n'
               << "workspace: " << compilation.workspace.size_bytes << " bytes\n";
     return 0;
 }

@@ -19,6 +19,7 @@ EXPORTS = [
     "df_argument_count", "df_argument_info", "df_set_stream", "df_execute", "df_plan_workspace",
     "df_step_count", "df_step_info", "df_execute_steps",
     "df_serialize_artifact", "df_write_artifact", "df_load_artifact", "df_load_artifact_file",
+    "df_argument_name", "df_conv2d_metadata",
 ]
 
 _LIB: Optional[C.CDLL] = None
@@ -55,6 +56,8 @@ def load() -> C.CDLL:
         for name in ("df_workspace_size", "df_launch_count", "df_argument_count", "df_destroy"):
             getattr(lib, name).argtypes = [C.c_void_p]
         lib.df_plan_text.argtypes = [C.c_void_p, C.c_char_p, C.c_size_t]
+        lib.df_argument_name.restype = C.c_size_t
+        lib.df_argument_name.argtypes = [C.c_void_p, C.c_int64, C.c_char_p, C.c_size_t]
         lib.df_set_stream.argtypes = [C.c_void_p, C.c_void_p]
         _LIB = lib
     return _LIB
@@ -111,8 +114,22 @@ class Executable:
         for index in range(lib.df_argument_count(self._handle)):
             uid, size, alignment, access = C.c_int64(), C.c_uint64(), C.c_uint64(), C.c_int32()
             _check(lib.df_argument_info(self._handle, C.c_int64(index), C.byref(uid), C.byref(size), C.byref(alignment), C.byref(access)))
-            out.append({"uid": uid.value, "size_bytes": size.value, "alignment": alignment.value, "access": ("read", "write", "readwrite")[access.value]})
+            name = C.create_string_buffer(lib.df_argument_name(self._handle, C.c_int64(index), None, 0) + 1)
+            lib.df_argument_name(self._handle, C.c_int64(index), name, len(name))
+            out.append({"uid": uid.value, "name": name.value.decode(), "size_bytes": size.value, "alignment": alignment.value,
+                        "access": ("read", "write", "readwrite")[access.value]})
         return out
+
+    def conv2d_metadata(self) -> Optional[dict]:
+        """The single-node CONV_FPROP metadata (physical N, H, W, C shapes), or None under the generic argument table."""
+        kind = C.c_int32(1)
+        values = (C.c_int64 * 27)()
+        _check(load().df_conv2d_metadata(self._handle, C.byref(kind), values))
+        if kind.value != 0:
+            return None
+        v = list(values)
+        return {"x_uid": v[0], "w_uid": v[1], "y_uid": v[2], "x_shape": v[3:7], "w_shape": v[7:11], "y_shape": v[11:15], "padded_x_shape": v[15:19],
+                "pre_padding": v[19:21], "post_padding": v[21:23], "stride": v[23:25], "dilation": v[25:27]}
 
     def serialize(self) -> bytes:
         """The artifact bytes of this executable (compiler::serialize_artifact)."""

@@ -35,7 +35,10 @@ struct ArtifactInfo {
     std::string frontend_version;
     std::string target_triple;     // "sm_100a"
     std::int32_t kernel_abi_version = 0;
-    GraphCompileMetadata metadata;
+    // The convolution fields are filled when the artifact holds the single-node CONV_FPROP form (arguments X, W, Y):
+    // UIDs and shapes from the argument table, padding / stride / dilation from the launch's params block.
+    InvocationAdapterKind invocation = InvocationAdapterKind::kGenericRankedMemrefPointerTable;
+    Conv2DCompileMetadata metadata;
     WorkspacePlan workspace;
     KernelPlan plan;
     double absolute_tolerance = kDefaultAbsoluteTolerance;

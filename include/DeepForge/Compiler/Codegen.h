@@ -5,20 +5,33 @@
 #pragma once
 
 #include "DeepForge/Compiler/Bufferization.h"
+#include "DeepForge/Compiler/Conv2DImporter.h"
 #include "DeepForge/Compiler/GraphMetadata.h"
 #include "DeepForge/Compiler/KernelPlan.h"
+#include "DeepForge/Compiler/Schedule.h"
 #include "DeepForge/Import/SerializedGraphImporter.h"
 #include "DeepForge/Runtime/Executable.h"
 
+#include <array>
 #include <filesystem>
 #include <memory>
 #include <string>
+#include <vector>
 
 namespace deepforge::compiler {
 
 struct CompileOptions {
+    // The reference's fields (include/DeepForge/Compiler/Codegen.h:17-26). The x86 emission switches are accepted
+    // and have no effect: there is no object code, LLVM IR or MLIR to emit, capture or schedule here.
+    Conv2DImportOptions importer;
     std::string foundational_function_name = "deepforge_graph";
     import::InputFormat input_format = import::InputFormat::kAuto;
+    bool build_avx_variants = true;
+    bool emit_object = true;
+    bool emit_llvm_ir = true;
+    bool capture_mlir = false;
+    Conv2DSchedulePolicy schedule_policy = Conv2DSchedulePolicy::kAuto;
+    // ---- this backend's own switches ----
     // Fuse POINTWISE consumers into contraction epilogues and BLOCK_SCALE_DEQUANTIZE
     // producers into MATMUL operand loads.
     bool fuse = true;
@@ -35,12 +48,24 @@ struct CompileOptions {
     bool disable_tensor_cores = false;
 };
 
+// One entry per variant name of the reference (scalar, AVX2, AVX-512). There is one compiled form, the kernel plan:
+// the scalar entry names it ("kernel-plan" as schedule, "sm_100a" as required features), the other two stay empty, and
+// no entry carries code (mlir, llvm_ir and object are always empty).
+struct VariantCode {
+    runtime::CpuVariant variant = runtime::CpuVariant::kScalar;
+    std::string symbol, required_features, schedule, mlir, llvm_ir;
+    std::vector<std::uint8_t> object;
+};
+
 struct CompilationResult {
     std::unique_ptr<runtime::Executable> executable;
-    GraphCompileMetadata metadata;
+    InvocationAdapterKind adapter_kind = InvocationAdapterKind::kGenericRankedMemrefPointerTable;
+    Conv2DCompileMetadata metadata;
     WorkspacePlan workspace;
-    KernelPlan plan;
-    std::string target = "sm_100a";
+    std::string target_triple = "sm_100a";
+    std::string imported_mlir, bufferized_mlir;  // always empty
+    std::array<VariantCode, 3> variants;
+    KernelPlan plan;                             // what this backend compiles to
 };
 
 [[nodiscard]] import::Status compile_graph(import::SerializedGraph const& graph, CompileOptions const& options, CompilationResult& output);

@@ -44,6 +44,15 @@ int64_t df_argument_count(const df_executable* executable);
 int df_argument_info(const df_executable* executable, int64_t index, int64_t* uid, uint64_t* size_bytes,
                      uint64_t* alignment, int32_t* access);
 
+/* Name of argument `index` ("X", "W", "Y" for the single-node convolution form, the tensor's name otherwise);
+   returns the full length. */
+size_t df_argument_name(const df_executable* executable, int64_t index, char* buffer, size_t capacity);
+/* Metadata of the single-node CONV_FPROP form (Conv2DCompileMetadata, include/DeepForge/Compiler/Conv2DImporter.h
+   :24-37 of the reference). *adapter_kind: 0 = that form (arguments X, W, Y), 1 = the generic table. values[27] =
+   x_uid, w_uid, y_uid, x_shape[4], w_shape[4], y_shape[4], padded_x_shape[4] (physical N, H, W, C order),
+   pre_padding[2], post_padding[2], stride[2], dilation[2]; all zero under the generic table. */
+int df_conv2d_metadata(const df_executable* executable, int32_t* adapter_kind, int64_t* values);
+
 /* stream: a cudaStream_t (NULL = legacy default stream). */
 void df_set_stream(df_executable* executable, void* stream);
 

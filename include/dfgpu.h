@@ -256,7 +256,9 @@ int dfgpu_sdpa_forward(const dfgpu_sdpa_params*, void* const* tensors, void* scr
    call rewrites all it reads, so nothing needs clearing), so calls that overlap on the GPU
    race and must be serialised by the caller; each GPU that loads the library holds the
    8 MiB until exit. The first call on a device resolves the array's address (with that
-   device current): make it before any stream capture. Makes no allocation of any kind. */
+   device current): make it before any stream capture. `stream` must belong to the device
+   that is current at the call (checked: a stream of another device is refused with 1), since
+   the array used is the current device's. Makes no allocation of any kind. */
 int dfgpu_sdpa_paged_decode_static(const dfgpu_sdpa_params*, void* const* tensors, void* stream);
 
 /* ---- self-check of the E4M3 encoder ------------------------------------------

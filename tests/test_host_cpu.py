@@ -37,7 +37,7 @@ def test_exports_of_the_host_library():
     import re
     from pathlib import Path
     header = (Path(__file__).resolve().parent.parent / "include" / "deepforge_b200.h").read_text()
-    declared = sorted(set(re.findall(r"\b(df_[a-z_]+)\s*\(", header)))
+    declared = sorted(set(re.findall(r"\b(df_[a-z0-9_]+)\s*\(", header)))
     assert declared == sorted(runtime.EXPORTS)
     for name in declared:
         assert hasattr(lib, name)
@@ -239,3 +239,30 @@ def test_runtime_rejects_bad_variant_packs_before_any_launch():
     assert code(good, 0) == 17                                       # workspace required but null
     assert code(good, workspace + 8) == 17                           # workspace misaligned
     assert code(good, good[7]) == 17                                 # workspace overlaps an argument
+
+
+def test_single_convolution_carries_the_conv_adapter_metadata():
+    """The reference's single-node path (lib/MLIR/Conv2DImporter.cpp:332-370, checks of lib/Runtime/Executable.cpp:735-768):
+    arguments X, W, Y by those names and in that order whatever their UIDs, FLOAT, physical NHWC / KRSC shapes with packed
+    strides, alignment 4, read / read / write; UIDs, shapes, the padded input shape and the attributes in the metadata."""
+    doc = graphs.c1_conv("nhwc", n=2, c=16, h=9, w=7, k=8)
+    # UIDs out of order on purpose: Y has the smallest
+    renumber = {"1": 30, "2": 20, "3": 10}
+    doc["tensors"] = {str(renumber[k]): {**t, "uid": renumber[k]} for k, t in doc["tensors"].items()}
+    node = doc["nodes"][0]
+    node["inputs"] = {"X": 30, "W": 20}
+    node["outputs"] = {"Y": 10}
+    exe = runtime.compile_graph(doc)
+    arguments = exe.arguments()
+    assert [(a["name"], a["uid"], a["access"], a["alignment"]) for a in arguments] == [("X", 30, "read", 4), ("W", 20, "read", 4), ("Y", 10, "write", 4)]
+    assert [a["size_bytes"] for a in arguments] == [2 * 9 * 7 * 16 * 4, 8 * 3 * 3 * 16 * 4, 2 * 9 * 7 * 8 * 4]
+    meta = exe.conv2d_metadata()
+    assert meta == {"x_uid": 30, "w_uid": 20, "y_uid": 10, "x_shape": [2, 9, 7, 16], "w_shape": [8, 3, 3, 16], "y_shape": [2, 9, 7, 8],
+                    "padded_x_shape": [2, 11, 9, 16], "pre_padding": [1, 1], "post_padding": [1, 1], "stride": [1, 1], "dilation": [1, 1]}
+    # the artifact describes itself the same way after a round trip
+    loaded = runtime.load_artifact(exe.serialize())
+    assert loaded.arguments() == arguments and loaded.conv2d_metadata() == meta
+    # everything else keeps the generic table: the NCHW-strided extension, a convolution inside a DAG
+    assert runtime.compile_graph(graphs.c1_conv("nchw", n=1, c=4, h=5, w=5, k=4)).conv2d_metadata() is None
+    generic = runtime.compile_graph(graphs.c2_bottleneck(n=1, h=8, w=8))
+    assert generic.conv2d_metadata() is None and [a["uid"] for a in generic.arguments()] == sorted(a["uid"] for a in generic.arguments())

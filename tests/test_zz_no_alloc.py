@@ -4,7 +4,9 @@ A host that may not allocate device memory around the call -- allocation frozen 
 start-up, an allocator lock held above it, a real-time thread -- uses
 dfgpu_sdpa_paged_decode_static, which keeps its split-KV partials in an 8 MiB array built
 into the library. Its result must equal the regular entry point's (same kernels, different
-scratch), on two calls in a row: the array is shared and keeps the first call's contents."""
+scratch), on two calls in a row: the array is shared and keeps the first call's contents.
+Both are also held to the CPU oracle's answer for the same inputs, so that the pair cannot
+agree on something wrong."""
 import numpy as np
 import pytest
 
@@ -31,7 +33,27 @@ def _case(batch, hq, hkv, pages, block, max_len, seed):
     host = [synthetic.to_bf16_bits(synthetic.normal(seed, i + 1, n)) for i, n in enumerate((batch * hq * 128, pages * hkv * block * 128, pages * hkv * block * 128))]
     dev = [g.to_device(a) for a in host]
     extra = [g.to_device(np.ones(batch, dtype=np.int32)), g.to_device(lengths), g.to_device(tk), g.to_device(tv)]
-    return p, dev, extra
+    return p, dev, extra, (host, lengths, tk, tv)
+
+
+def _oracle(p, host, lengths, tk, tv):
+    """The CPU oracle on the same (bf16-rounded) inputs: O and Stats in f32."""
+    import oracle
+    batch, hq = int(p.q.dim[0]), int(p.q.dim[1])
+    op = oracle.SdpaParams()
+    for name in ("q", "k", "v", "o"):
+        t = getattr(p, name)
+        setattr(op, name, tensor(F32, [int(t.dim[i]) for i in range(4)]))
+    op.stats = tensor(F32, [batch, hq, 1, 1])
+    op.seq_q = op.seq_kv = tensor(I32, [batch, 1, 1, 1])
+    op.page_table_k = op.page_table_v = tensor(I32, [batch, 1, tk.shape[1], 1])
+    op.attn_scale, op.padding_mask, op.s_kv = p.attn_scale, 1, p.s_kv
+    o_ref = np.zeros(batch * hq * 128, dtype=np.float32)
+    stats_ref = np.zeros(batch * hq, dtype=np.float32)
+    widened = [synthetic.bf16_bits_to_f32(a) for a in host]
+    oracle.sdpa_forward(op, widened + [o_ref, stats_ref, None, None, np.ones(batch, dtype=np.int32), lengths,
+                                       np.ascontiguousarray(tk), np.ascontiguousarray(tv)])
+    return o_ref, stats_ref
 
 
 def _run(p, dev, extra, static):
@@ -52,17 +74,22 @@ def _run(p, dev, extra, static):
 def test_static_scratch_decode_matches_the_regular_entry_point_twice_in_a_row():
     # two different problems back to back: the second starts with the first one's partials in the array
     for batch, hq, hkv, pages, block, max_len, seed in ((4, 8, 2, 48, 64, 1024, 3), (3, 32, 8, 40, 64, 768, 4)):
-        p, dev, extra = _case(batch, hq, hkv, pages, block, max_len, seed)
+        p, dev, extra, host_side = _case(batch, hq, hkv, pages, block, max_len, seed)
         want_o, want_stats = _run(p, dev, extra, static=False)
         got_o, got_stats = _run(p, dev, extra, static=True)
         # same kernels on the same data: bit-identical, which is inside every tolerance the suite uses
         assert np.array_equal(got_o, want_o)
         assert np.array_equal(got_stats, want_stats)
+        # and the answer itself, against the CPU oracle (the suite's bf16 gate; Stats as in the other decode tests)
+        o_ref, stats_ref = _oracle(p, *host_side)
+        got = synthetic.bf16_bits_to_f32(got_o)
+        assert np.all(np.abs(got - o_ref) <= 1e-2 + 2e-2 * np.abs(o_ref))
+        assert np.all(np.abs(got_stats - stats_ref) <= 1e-3 * (1 + np.abs(stats_ref)))
     assert dfgpu.device_status() == 0
 
 
 def test_static_scratch_decode_refuses_requests_beyond_its_limit():
-    p, dev, extra = _case(2, 8, 2, 16, 64, 512, 5)
+    p, dev, extra, _ = _case(2, 8, 2, 16, 64, 512, 5)
     p.q = p.o = tensor(BF16, [64, 32, 1, 128])  # 64 * 32 * 32 chunks * 520 B = 34 MB > 8 MiB
     p.k = p.v = tensor(BF16, [16, 8, 64, 128])
     p.s_kv = 8192
