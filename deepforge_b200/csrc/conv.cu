@@ -433,3 +433,43 @@ extern "C" int dfgpu_conv_fprop(const dfgpu_conv_params* p, void* const* tensors
     }
     return check_launch("CONV_FPROP");
 }
+
+// ---- two convolutions in one launch -------------------------------------------------------------
+
+namespace {
+int check_pair(const dfgpu_conv_pair_params& p, void* const* tensors) {
+    dfgpu::ConvArgs a;
+    void* first_tensors[5] = {tensors ? tensors[0] : nullptr, tensors ? tensors[1] : nullptr, nullptr, tensors ? tensors[4] : nullptr, tensors ? tensors[5] : nullptr};
+    void* second_tensors[5] = {nullptr, tensors ? tensors[2] : nullptr, tensors ? tensors[3] : nullptr, tensors ? tensors[6] : nullptr, tensors ? tensors[7] : nullptr};
+    dfgpu_conv_params first = p.first, second = p.second;
+    if (!tensors) first.epilogue_count = second.epilogue_count = 0;  // operand pointers are not available at query time
+    int status = dfgpu::build_args(first, tensors ? first_tensors : nullptr, a);
+    if (status) return status;
+    status = dfgpu::build_args(second, tensors ? second_tensors : nullptr, a);
+    if (status) return status;
+    if (p.first.kernel != DFGPU_CONV_PAIR_AUTO && p.first.kernel != DFGPU_CONV_PAIR_UMMA) return fail(kInvalidArgument, "CONV_FPROP pair: unknown kernel id %d", p.first.kernel);
+    if (!dfgpu::conv_pair_umma_supported(p.first, p.second))
+        return fail(kUnsupported, "CONV_FPROP pair: needs a wide bf16 filter with 64 output channels and per-channel steps, then a 1 x 1 filter with 128 or 256 output channels");
+    return kOk;
+}
+}  // namespace
+
+extern "C" int dfgpu_query_conv_fprop_pair(const dfgpu_conv_pair_params* p, dfgpu_plan_info* info) {
+    if (!p || !info) return fail(kInvalidArgument, "CONV_FPROP pair: null params");
+    int status = check_pair(*p, nullptr);
+    if (status) return status;
+    info->kernel = DFGPU_CONV_PAIR_UMMA;
+    info->launches = 1;
+    info->scratch_bytes = 0;
+    return kOk;
+}
+
+extern "C" int dfgpu_conv_fprop_pair(const dfgpu_conv_pair_params* p, void* const* tensors, void* scratch, void* stream_handle) {
+    (void)scratch;
+    if (!p || !tensors) return fail(kInvalidArgument, "CONV_FPROP pair: null params");
+    for (int i = 0; i < 4; ++i)
+        if (!tensors[i]) return fail(kInvalidArgument, "CONV_FPROP pair: null tensor pointer");
+    int status = check_pair(*p, tensors);
+    if (status) return status;
+    return dfgpu::launch_conv_pair_umma(p->first, p->second, tensors, as_stream(stream_handle));
+}

@@ -5,9 +5,28 @@
 
 namespace dfgpu {
 
+// What launch_conv_umma() does with a convolution, worked out from the descriptors alone (a query has no pointers).
+struct ConvForm {
+    int64_t N, C, H, W, K, P, Q, R, S;
+    bool split_in, split_out;   // DFGPU_BF16X2 activations / output
+    bool pointwise;             // 1 x 1, no padding: plain GEMM rows
+    int bn;
+    int rows_per_tile;          // output rows of one image per tile (non-pointwise, one slot per tap)
+    bool persistent;            // the persistent kernel (TMA-store epilogue) takes it
+    bool halo;                  // ... in the halo form
+    int halo_rows;
+};
+bool conv_umma_form(const dfgpu_conv_params& p, ConvForm& form);
+
 // bf16 NHWC/KRSC convolution as an implicit GEMM on tcgen05 (1x1 and 3x3, stride 1).
 bool conv_umma_supported(const dfgpu_conv_params& p);
 int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStream_t stream);
+
+// A wide-filter convolution and the 1 x 1 convolution that consumes it, in one persistent kernel (the intermediate
+// stays on the SM). tensors: {X, W first, W second, Y, first.extra0, first.extra1, second.extra0, second.extra1}.
+bool conv_pair_umma_supported(const dfgpu_conv_params& first, const dfgpu_conv_params& second);
+int launch_conv_pair_umma(const dfgpu_conv_params& first, const dfgpu_conv_params& second, void* const* tensors, cudaStream_t stream);
+int conv_pair_device_status(int* status);
 
 // MATMUL on tcgen05: kernel is DFGPU_MATMUL_UMMA_BF16 or DFGPU_MATMUL_UMMA_MXF8.
 bool matmul_umma_supported(const dfgpu_matmul_params& p, int kernel);

@@ -891,21 +891,7 @@ int pick_bn(int64_t n, int64_t k_blocks) {
 
 }  // namespace
 
-namespace {
-
-// What launch_conv_umma() does with a convolution, worked out from the descriptors alone (the query has no pointers).
-struct ConvForm {
-    int64_t N, C, H, W, K, P, Q, R, S;
-    bool split_in, split_out;   // DFGPU_BF16X2 activations / output
-    bool pointwise;             // 1 x 1, no padding: plain GEMM rows
-    int bn;
-    int rows_per_tile;          // output rows of one image per tile (non-pointwise, one slot per tap)
-    bool persistent;            // the persistent kernel (TMA-store epilogue) takes it
-    bool halo;                  // ... in the halo form
-    int halo_rows;
-};
-
-bool conv_form(const dfgpu_conv_params& p, ConvForm& f) {
+bool conv_umma_form(const dfgpu_conv_params& p, ConvForm& f) {
     const bool x_ok = p.x.dtype == DFGPU_BF16 || p.x.dtype == DFGPU_BF16X2;
     const bool y_ok = p.y.dtype == DFGPU_BF16 || p.y.dtype == DFGPU_F32 || p.y.dtype == DFGPU_BF16X2;
     if (!x_ok || p.w.dtype != DFGPU_BF16 || !y_ok) return false;
@@ -965,16 +951,14 @@ bool conv_form(const dfgpu_conv_params& p, ConvForm& f) {
     return true;
 }
 
-}  // namespace
-
 bool conv_umma_supported(const dfgpu_conv_params& p) {
     ConvForm form;
-    return conv_form(p, form);
+    return conv_umma_form(p, form);
 }
 
 int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStream_t stream) {
     ConvForm f;
-    if (!conv_form(p, f)) return fail(kUnsupported, "CONV_FPROP: the tcgen05 kernel does not take this convolution");
+    if (!conv_umma_form(p, f)) return fail(kUnsupported, "CONV_FPROP: the tcgen05 kernel does not take this convolution");
     const int64_t N = f.N, C = f.C, H = f.H, W = f.W, K = f.K, P = f.P, Q = f.Q, R = f.R, S = f.S;
     const int64_t Ca = f.split_in ? 2 * C : C;    // bf16 channels per activation pixel in storage
     const int64_t Kout = f.split_out ? 2 * K : K;  // bf16 channels per output pixel in storage
@@ -1160,9 +1144,12 @@ int launch_matmul_umma(const dfgpu_matmul_params& p, void* const* tensors, int k
 extern "C" int dfgpu_device_status(int* status) {
     using namespace dfgpu;
     if (!status) return fail(kInvalidArgument, "device_status: null pointer");
-    int gemm = 0, sdpa = 0, decode = 0, mxf8 = 0;
+    int gemm = 0, sdpa = 0, decode = 0, mxf8 = 0, pair = 0;
     int code = read_and_clear_device_status(&gemm);
     if (code) return code;
+    code = conv_pair_device_status(&pair);
+    if (code) return code;
+    if (!gemm) gemm = pair;
     code = mxf8_device_status(&mxf8);
     if (code) return code;
     if (!gemm) gemm = mxf8;

@@ -82,6 +82,10 @@ class ConvParams(C.Structure):
                 ("epilogue", EpilogueStep * MAX_EPILOGUE), ("kernel", C.c_int32), ("reserved", C.c_int32)]
 
 
+class ConvPairParams(C.Structure):
+    _fields_ = [("first", ConvParams), ("second", ConvParams)]
+
+
 class MatmulParams(C.Structure):
     _fields_ = [("a", Tensor), ("b", Tensor), ("c", Tensor), ("a_scale", Tensor), ("b_scale", Tensor),
                 ("a_block", C.c_int64 * 2), ("b_block", C.c_int64 * 2), ("extra", Tensor * 2),
@@ -108,6 +112,7 @@ EXPORTS = [
     "dfgpu_query_block_scale_dequantize", "dfgpu_block_scale_dequantize",
     "dfgpu_query_pointwise", "dfgpu_pointwise",
     "dfgpu_query_conv_fprop", "dfgpu_conv_fprop",
+    "dfgpu_query_conv_fprop_pair", "dfgpu_conv_fprop_pair",
     "dfgpu_query_matmul", "dfgpu_matmul",
     "dfgpu_query_matmul_fp8", "dfgpu_matmul_fp8",
     "dfgpu_query_sdpa_forward", "dfgpu_sdpa_forward", "dfgpu_sdpa_paged_decode_static",
@@ -181,6 +186,10 @@ def pointwise(params, in0, in1, out, scratch=None, stream=None):
 
 def conv_fprop(params, x, w, y, extra0=None, extra1=None, scratch=None, stream=None):
     _call("dfgpu_conv_fprop", params, [x, w, y, extra0, extra1], scratch, stream)
+
+
+def conv_fprop_pair(params, x, w_first, w_second, y, first_extra=(None, None), second_extra=(None, None), stream=None):
+    _call("dfgpu_conv_fprop_pair", params, [x, w_first, w_second, y, *first_extra, *second_extra], None, stream)
 
 
 def matmul(params, a, b, c, a_scale=None, b_scale=None, extra0=None, extra1=None, scratch=None, stream=None):

@@ -111,6 +111,7 @@ std::uint32_t params_size_of(KernelOp op) {
         case KernelOp::kMatmul: return params_size<dfgpu_matmul_params>();
         case KernelOp::kSdpaForward: return params_size<dfgpu_sdpa_params>();
         case KernelOp::kMatmulFp8: return params_size<dfgpu_matmul_fp8_params>();
+        case KernelOp::kConvFpropPair: return params_size<dfgpu_conv_pair_params>();
     }
     return 0;
 }
@@ -125,11 +126,12 @@ std::size_t tensor_slots(KernelOp op) {
         case KernelOp::kMatmul: return 7;
         case KernelOp::kSdpaForward: return 14;
         case KernelOp::kMatmulFp8: return 7;
+        case KernelOp::kConvFpropPair: return 8;
     }
     return 0;
 }
 
-constexpr std::uint32_t kLastOp = static_cast<std::uint32_t>(KernelOp::kMatmulFp8);
+constexpr std::uint32_t kLastOp = static_cast<std::uint32_t>(KernelOp::kConvFpropPair);
 
 void write_binding(Writer& w, TensorBinding const& binding) {
     w.u32(static_cast<std::uint32_t>(binding.kind));
@@ -184,6 +186,12 @@ bool params_in_range(KernelParams const& params) {
         else if constexpr (std::is_same_v<T, dfgpu_conv_params>)
             return tensor_in_range(p.x) && tensor_in_range(p.w) && tensor_in_range(p.y) && tensor_in_range(p.extra[0]) && tensor_in_range(p.extra[1]) &&
                    p.epilogue_count >= 0 && p.epilogue_count <= DFGPU_MAX_EPILOGUE;
+        else if constexpr (std::is_same_v<T, dfgpu_conv_pair_params>) {
+            for (auto const* c : {&p.first, &p.second})
+                if (!(tensor_in_range(c->x) && tensor_in_range(c->w) && tensor_in_range(c->y) && tensor_in_range(c->extra[0]) && tensor_in_range(c->extra[1]) &&
+                      c->epilogue_count >= 0 && c->epilogue_count <= DFGPU_MAX_EPILOGUE)) return false;
+            return true;
+        }
         else if constexpr (std::is_same_v<T, dfgpu_matmul_params>)
             return tensor_in_range(p.a) && tensor_in_range(p.b) && tensor_in_range(p.c) && tensor_in_range(p.a_scale) && tensor_in_range(p.b_scale) &&
                    tensor_in_range(p.extra[0]) && tensor_in_range(p.extra[1]) && p.epilogue_count >= 0 && p.epilogue_count <= DFGPU_MAX_EPILOGUE;
@@ -236,6 +244,7 @@ Status read_plan(Reader& r, ArtifactInfo& info) {
             case KernelOp::kMatmul: step.params = read_params<dfgpu_matmul_params>(r); break;
             case KernelOp::kSdpaForward: step.params = read_params<dfgpu_sdpa_params>(r); break;
             case KernelOp::kMatmulFp8: step.params = read_params<dfgpu_matmul_fp8_params>(r); break;
+            case KernelOp::kConvFpropPair: step.params = read_params<dfgpu_conv_pair_params>(r); break;
         }
         if (!r.ok || !params_in_range(step.params)) return bad("kernel plan: tensor descriptor out of range");
         if (step.kernel < 0 || step.launches < 1 || step.launches > 16) return bad("kernel plan: kernel id or launch count out of range");
@@ -285,6 +294,10 @@ dfgpu_tensor const* slot_descriptor(KernelStep const& step, std::size_t slot) {
         else if constexpr (std::is_same_v<T, dfgpu_pointwise_params>) { dfgpu_tensor const* t[] = {&p.in0, &p.in1, &p.out}; return slot < 3 ? t[slot] : nullptr; }
         else if constexpr (std::is_same_v<T, dfgpu_conv_params>) { dfgpu_tensor const* t[] = {&p.x, &p.w, &p.y, &p.extra[0], &p.extra[1]}; return slot < 5 ? t[slot] : nullptr; }
         else if constexpr (std::is_same_v<T, dfgpu_matmul_params>) { dfgpu_tensor const* t[] = {&p.a, &p.b, &p.c, &p.a_scale, &p.b_scale, &p.extra[0], &p.extra[1]}; return slot < 7 ? t[slot] : nullptr; }
+        else if constexpr (std::is_same_v<T, dfgpu_conv_pair_params>) {
+            dfgpu_tensor const* t[] = {&p.first.x, &p.first.w, &p.second.w, &p.second.y, &p.first.extra[0], &p.first.extra[1], &p.second.extra[0], &p.second.extra[1]};
+            return slot < 8 ? t[slot] : nullptr;
+        }
         else if constexpr (std::is_same_v<T, dfgpu_sdpa_params>) {
             dfgpu_tensor const* t[] = {&p.q, &p.k, &p.v, &p.o, &p.stats, &p.max, &p.sum_exp, &p.seq_q, &p.seq_kv, &p.page_table_k, &p.page_table_v, &p.bias, &p.sink, &p.block_mask};
             return slot < 14 ? t[slot] : nullptr;

@@ -52,6 +52,7 @@ extern "C" int df_compile(const uint8_t* document, size_t size, int format, uint
     compile_options.narrow_virtual_tensors = !(options & DF_OPTION_NO_NARROWING);
     compile_options.disable_tensor_cores = (options & DF_OPTION_NO_TENSOR_CORES) != 0;
     compile_options.bf16_virtual_tensors = (options & DF_OPTION_BF16_INTERMEDIATES) != 0;
+    compile_options.fuse_convolution_pairs = !(options & DF_OPTION_NO_CONV_PAIRS);
     auto holder = std::make_unique<df_executable>();
     status = compiler::compile_graph(graph, compile_options, holder->result);
     if (status.is_bad()) return report(status);

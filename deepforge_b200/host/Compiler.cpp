@@ -788,6 +788,42 @@ void split_virtual_tensors(Lowering& low) {
     }
 }
 
+// A convolution whose only reader is the 1 x 1 convolution launched right after it becomes one launch with it when
+// the kernel library has a fused kernel for the pair: the tensor between them then needs no workspace at all (it is
+// handed over inside the SM). Runs after the storage types are settled, so the pair is offered to the library with
+// the types the two launches would have used.
+void fuse_convolution_pairs(Lowering& low) {
+    if (!low.options.fuse || !low.options.fuse_convolution_pairs || low.options.disable_tensor_cores) return;
+    auto uses = [&](std::int64_t uid) {
+        int count = 0;
+        for (auto const& step : low.plan.steps)
+            for (auto const& binding : step.tensors) count += binding.kind == TensorBinding::Kind::kWorkspace && binding.uid == uid;
+        return count;
+    };
+    for (std::size_t s = 0; s + 1 < low.plan.steps.size(); ++s) {
+        auto& first = low.plan.steps[s];
+        auto& second = low.plan.steps[s + 1];
+        if (first.op != KernelOp::kConvFprop || second.op != KernelOp::kConvFprop) continue;
+        auto const& between = first.tensors[2];
+        if (between.kind != TensorBinding::Kind::kWorkspace || second.tensors[0].kind != TensorBinding::Kind::kWorkspace || second.tensors[0].uid != between.uid) continue;
+        if (uses(between.uid) != 2) continue;  // written here, read there, nowhere else
+        dfgpu_conv_pair_params pair{};
+        pair.first = std::get<dfgpu_conv_params>(first.params);
+        pair.second = std::get<dfgpu_conv_params>(second.params);
+        dfgpu_plan_info info{};
+        if (dfgpu_query_conv_fprop_pair(&pair, &info) != 0) continue;
+        KernelStep fused;
+        fused.op = KernelOp::kConvFpropPair;
+        fused.label = first.label + ">" + second.label;
+        fused.nodes = first.nodes;
+        fused.nodes.insert(fused.nodes.end(), second.nodes.begin(), second.nodes.end());
+        fused.tensors = {first.tensors[0], first.tensors[1], second.tensors[1], second.tensors[2], first.tensors[3], first.tensors[4], second.tensors[3], second.tensors[4]};
+        fused.params = pair;
+        low.plan.steps[s] = std::move(fused);
+        low.plan.steps.erase(low.plan.steps.begin() + static_cast<std::ptrdiff_t>(s) + 1);
+    }
+}
+
 // Fills the conv-adapter metadata when the graph is the reference's single-node case; false otherwise (the generic
 // table stands).
 bool single_conv_metadata(SerializedGraph const& graph, CompileOptions const& options, Conv2DCompileMetadata& metadata) {
@@ -852,6 +888,7 @@ std::uint64_t kernel_alignment(KernelStep const& step, std::size_t slot) {
             if (step.kernel == DFGPU_SDPA_PAGED_DECODE_UMMA || step.kernel == DFGPU_SDPA_PAGED_DECODE) return slot <= 2 ? 16 : 0;
             return 0;
         case KernelOp::kMatmulFp8: return step.kernel == DFGPU_MATMUL_FP8_UMMA && slot <= 2 ? 16 : 0;
+        case KernelOp::kConvFpropPair: return 16;
         default: return 0;
     }
 }
@@ -869,6 +906,7 @@ Status query_kernel_step(KernelStep& step, std::int64_t& scratch_bytes) {
         case KernelOp::kMatmul: code = dfgpu_query_matmul(&std::get<dfgpu_matmul_params>(step.params), &info); break;
         case KernelOp::kSdpaForward: code = dfgpu_query_sdpa_forward(&std::get<dfgpu_sdpa_params>(step.params), &info); break;
         case KernelOp::kMatmulFp8: code = dfgpu_query_matmul_fp8(&std::get<dfgpu_matmul_fp8_params>(step.params), &info); break;
+        case KernelOp::kConvFpropPair: code = dfgpu_query_conv_fprop_pair(&std::get<dfgpu_conv_pair_params>(step.params), &info); break;
     }
     if (code != 0) return Status::failure(static_cast<ErrorCode>(code), step.label, dfgpu_last_error());
     step.kernel = info.kernel;
@@ -887,6 +925,7 @@ char const* kernel_op_name(KernelOp op) {
         case KernelOp::kMatmul: return "matmul";
         case KernelOp::kSdpaForward: return "sdpa_forward";
         case KernelOp::kMatmulFp8: return "matmul_fp8";
+        case KernelOp::kConvFpropPair: return "conv_fprop_pair";
     }
     return "?";
 }
@@ -960,6 +999,7 @@ Status compile_graph(SerializedGraph const& graph, CompileOptions const& options
     }
     narrow_virtual_tensors(low);
     split_virtual_tensors(low);
+    fuse_convolution_pairs(low);
 
     // argument table: ascending UID, non-virtual tensors only
     Conv2DCompileMetadata metadata;

@@ -169,6 +169,12 @@ Status Executable::execute_steps(std::int64_t first, std::int64_t last, VariantP
             case KernelOp::kMatmul: code = dfgpu_matmul(&std::get<dfgpu_matmul_params>(step.params), pointers.data(), scratch, impl.stream); break;
             case KernelOp::kSdpaForward: code = dfgpu_sdpa_forward(&std::get<dfgpu_sdpa_params>(step.params), pointers.data(), scratch, impl.stream); break;
             case KernelOp::kMatmulFp8: code = dfgpu_matmul_fp8(&std::get<dfgpu_matmul_fp8_params>(step.params), pointers.data(), scratch, impl.stream); break;
+            case KernelOp::kConvFpropPair: {
+                dfgpu_conv_pair_params params = std::get<dfgpu_conv_pair_params>(step.params);
+                if (index == first) params.first.reserved &= ~2;  // see kConvFprop above
+                code = dfgpu_conv_fprop_pair(&params, pointers.data(), scratch, impl.stream);
+                break;
+            }
         }
         if (code != 0) {
             auto mapped = code == 19 ? ErrorCode::kGraphExecutionFailed : static_cast<ErrorCode>(code);

@@ -12,7 +12,7 @@ from pathlib import Path
 from typing import Dict, Mapping, Optional, Union
 
 FORMAT_AUTO, FORMAT_JSON, FORMAT_UBJSON = 0, 1, 2
-NO_FUSION, NO_NARROWING, NO_TENSOR_CORES, BF16_INTERMEDIATES = 1, 2, 4, 8
+NO_FUSION, NO_NARROWING, NO_TENSOR_CORES, BF16_INTERMEDIATES, NO_CONV_PAIRS = 1, 2, 4, 8, 16
 
 EXPORTS = [
     "df_last_error", "df_parse", "df_compile", "df_destroy", "df_workspace_size", "df_launch_count", "df_plan_text",

@@ -44,6 +44,9 @@ struct CompileOptions {
     // narrowed tensor adds a rounding of up to 2^-9 relative to what its readers see, so a chain of
     // contractions can leave the bf16 gate against the all-FLOAT evaluation of the graph).
     bool bf16_virtual_tensors = false;
+    // Hand a convolution and the 1 x 1 convolution that alone reads it to the fused two-convolution kernel when the
+    // kernel library has one for the pair (needs `fuse`).
+    bool fuse_convolution_pairs = true;
     // Force the CUDA-core kernels (used by tests to cross-check the tcgen05 paths).
     bool disable_tensor_cores = false;
 };

@@ -23,8 +23,9 @@ extern "C" {
 typedef struct df_executable df_executable;
 
 enum { DF_FORMAT_AUTO = 0, DF_FORMAT_JSON = 1, DF_FORMAT_UBJSON = 2 };
-/* DF_OPTION_BF16_INTERMEDIATES: lossy, see CompileOptions::bf16_virtual_tensors. */
-enum { DF_OPTION_NO_FUSION = 1, DF_OPTION_NO_NARROWING = 2, DF_OPTION_NO_TENSOR_CORES = 4, DF_OPTION_BF16_INTERMEDIATES = 8 };
+/* DF_OPTION_BF16_INTERMEDIATES: lossy, see CompileOptions::bf16_virtual_tensors. DF_OPTION_NO_CONV_PAIRS: every
+   convolution is its own launch (CompileOptions::fuse_convolution_pairs = false). */
+enum { DF_OPTION_NO_FUSION = 1, DF_OPTION_NO_NARROWING = 2, DF_OPTION_NO_TENSOR_CORES = 4, DF_OPTION_BF16_INTERMEDIATES = 8, DF_OPTION_NO_CONV_PAIRS = 16 };
 
 const char* df_last_error(void);
 

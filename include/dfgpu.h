@@ -161,6 +161,22 @@ typedef struct dfgpu_conv_params {
 int dfgpu_query_conv_fprop(const dfgpu_conv_params*, dfgpu_plan_info*);
 int dfgpu_conv_fprop(const dfgpu_conv_params*, void* const* tensors, void* scratch, void* stream);
 
+/* ---- CONV_FPROP followed by a 1 x 1 CONV_FPROP, in one launch ------------------
+   Stands for two emit_fprop calls (lib/Compiler/TrainingGraph.cpp:436-542) with the POINTWISE nodes between and
+   after them: `first` (a filter wider than one tap, 64 output channels, per-channel ADD / RELU steps) writes a
+   virtual tensor that only `second` (1 x 1, no padding, 128 or 256 output channels, bf16 output, at most one
+   full-tensor bf16 ADD operand) reads. The intermediate is first.y == second.x, declared FLOAT or DFGPU_BF16X2; it
+   is never stored: the kernel hands it from one product to the next inside the SM as (hi, lo) bf16 pairs.
+   tensors: {X, W of first, W of second, Y, first.extra0, first.extra1, second.extra0, second.extra1}.
+   The query fails with 20 when the pair is not one the fused kernel takes (the caller then launches the two
+   convolutions separately). */
+enum { DFGPU_CONV_PAIR_AUTO = 0, DFGPU_CONV_PAIR_UMMA = 1 };
+typedef struct dfgpu_conv_pair_params {
+    dfgpu_conv_params first, second;
+} dfgpu_conv_pair_params;
+int dfgpu_query_conv_fprop_pair(const dfgpu_conv_pair_params*, dfgpu_plan_info*);
+int dfgpu_conv_fprop_pair(const dfgpu_conv_pair_params*, void* const* tensors, void* scratch, void* stream);
+
 /* ---- MATMUL -----------------------------------------------------------------
    Replaces emit_matmul (lib/Compiler/FoundationalGraph.cpp:3167-3295); with
    a_scale/b_scale present it also absorbs the BLOCK_SCALE_DEQUANTIZE nodes

@@ -98,7 +98,7 @@ def test_options_reach_the_artifact():
     plain = runtime.compile_graph(DOCS["c2"]).serialize()
     unfused = runtime.compile_graph(DOCS["c2"], options=runtime.NO_FUSION).serialize()
     assert plain != unfused
-    assert runtime.load_artifact(unfused).launch_count == 8 and runtime.load_artifact(plain).launch_count == 3
+    assert runtime.load_artifact(unfused).launch_count == 8 and runtime.load_artifact(plain).launch_count == 2
 
 
 def test_every_truncation_and_sampled_corruption_is_a_parse_error():

@@ -34,7 +34,7 @@ def test_compile_inspect_and_plan(tool, tmp_path: Path):
     lines = inspected.stdout.splitlines()
     assert lines[:8] == ["format: DFOBJ/13", "deepforge: deepforge_b200 1", "llvm: ", "frontend: 1.24.0", "target: sm_100a",
                          "function: deepforge_graph", "uids: 1,2,3,4,5,6,7", f"workspace: {exe.workspace_size} bytes"]
-    assert [line.split("]")[0] for line in lines[8:]] == ["launch: [conv1+bias1+relu1", "launch: [conv2+bias2+relu2", "launch: [conv3+residual"]
+    assert [line.split("]")[0] for line in lines[8:]] == ["launch: [conv1+bias1+relu1", "launch: [conv2+bias2+relu2>conv3+residual"]
     plan = run(tool, "bottleneck.json", "--emit=plan", "-o", "out.plan", "--no-fusion", cwd=tmp_path)
     assert plan.returncode == 0 and plan.stdout.splitlines()[0] == 'output: "out.plan"'
     assert (tmp_path / "out.plan").read_text() == runtime.compile_graph(document, options=runtime.NO_FUSION).plan_text()

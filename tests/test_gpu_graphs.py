@@ -57,7 +57,7 @@ def test_c1_single_conv(layout, shape):
     assert np.all(np.abs(s.output(3) - ref[3]) <= 1e-4 + 1e-3 * np.abs(ref[3]))  # the reference's own acceptance rule
 
 
-@pytest.mark.parametrize("io,options", [("FLOAT", 0), ("BFLOAT16", 0), ("BFLOAT16", runtime.NO_TENSOR_CORES), ("BFLOAT16", runtime.NO_FUSION),
+@pytest.mark.parametrize("io,options", [("FLOAT", 0), ("BFLOAT16", 0), ("BFLOAT16", runtime.NO_CONV_PAIRS), ("BFLOAT16", runtime.NO_TENSOR_CORES), ("BFLOAT16", runtime.NO_FUSION),
                                         ("BFLOAT16", runtime.NO_NARROWING), ("BFLOAT16", runtime.BF16_INTERMEDIATES)])
 def test_c2_bottleneck_small(io, options):
     wl = workloads.c2(n=2, h=14, w=14, io=io)
@@ -73,19 +73,27 @@ def test_c2_bottleneck_small(io, options):
         assert s.exe.plan_text().count("kernel=3") == 3
         check_bf16(s.output(7), graph_oracle.run(wl.document, ins, round_to_bf16=(13, 16))[7])
     else:
-        # every other plan, the default one included (intermediates as (hi, lo) bf16 pairs between tcgen05
-        # convolutions), holds the plain gate against the all-FLOAT evaluation of the DAG
+        # every other plan holds the plain gate against the all-FLOAT evaluation of the DAG: the default one (conv1, then
+        # conv2 > conv3 in the two-convolution kernel, intermediates as (hi, lo) bf16 pairs) and the one with three
+        # tcgen05 launches included
         if options == 0:
-            assert s.exe.plan_text().count("kernel=3") == 3
+            assert s.exe.launch_count == 2 and "conv_fprop_pair kernel=1" in s.exe.plan_text()
+        if options == runtime.NO_CONV_PAIRS:
+            assert s.exe.plan_text().count("conv_fprop kernel=3") == 3
         check_bf16(s.output(7), ref[7])
 
 
-@pytest.mark.parametrize("shape", [dict(n=1, h=7, w=7), dict(n=3, h=28, w=28), dict(n=2, h=9, w=11), dict(n=1, h=8, w=120)])
-def test_c2_bottleneck_other_geometries(shape):
-    """Image sizes that give other tile shapes: the 3 x 3 convolution takes 7, 4, 9 or 1 output rows per tile."""
+@pytest.mark.parametrize("options", [0, runtime.NO_CONV_PAIRS])
+@pytest.mark.parametrize("shape", [dict(n=1, h=7, w=7), dict(n=3, h=28, w=28), dict(n=2, h=9, w=11), dict(n=1, h=8, w=120), dict(n=5, h=56, w=56, c_in=128)])
+def test_c2_bottleneck_other_geometries(shape, options):
+    """Image sizes that give other tile shapes (the 3 x 3 convolution takes 7, 4, 9, 1 or 2 output rows per tile) and a
+    128-channel block, through the two-convolution kernel and as three launches."""
     wl = workloads.c2(**shape)
-    s = harness.Session(wl)
-    assert s.exe.plan_text().count("kernel=3") == 3
+    s = harness.Session(wl, options=options)
+    if options == 0:
+        assert s.exe.launch_count == 2 and "conv_fprop_pair kernel=1" in s.exe.plan_text()
+    else:
+        assert s.exe.plan_text().count("conv_fprop kernel=3") == 3
     s.run()
     ins, _ = oracle_inputs(wl, s)
     check_bf16(s.output(7), graph_oracle.run(wl.document, ins, threads=THREADS)[7])
@@ -151,7 +159,7 @@ def test_c2_each_contraction_within_the_gate_given_its_own_inputs():
 def test_c2_bottleneck_full_geometry_two_images():
     wl = workloads.c2(n=2)  # 56x56, 256->64->64->256, the benchmark's per-image geometry
     s = harness.Session(wl)
-    assert s.exe.plan_text().count("kernel=3") == s.exe.launch_count
+    assert s.exe.launch_count == 2 and "conv_fprop_pair kernel=1" in s.exe.plan_text()
     s.run()
     ins, _ = oracle_inputs(wl, s)
     check_bf16(s.output(7), graph_oracle.run(wl.document, ins, threads=THREADS)[7])
@@ -160,11 +168,16 @@ def test_c2_bottleneck_full_geometry_two_images():
 def test_c2_bottleneck_full_size():
     """The benchmark configuration itself (N = 32): every one of the 25.7 M outputs against the all-FLOAT twin."""
     wl = workloads.c2()
-    s = harness.Session(wl)
-    assert s.exe.plan_text().count("kernel=3") == s.exe.launch_count
-    s.run()
-    ins, _ = oracle_inputs(wl, s)
-    check_bf16(s.output(7), graph_oracle.run(wl.document, ins, threads=THREADS)[7])
+    ins = reference = None
+    for options in (0, runtime.NO_CONV_PAIRS):  # the benchmarked plan, and the same graph as three tcgen05 launches
+        s = harness.Session(wl, options=options)
+        assert ("conv_fprop_pair kernel=1" in s.exe.plan_text()) == (options == 0)
+        s.run()
+        if reference is None:
+            ins, _ = oracle_inputs(wl, s)
+            reference = graph_oracle.run(wl.document, ins, threads=THREADS)[7]
+        check_bf16(s.output(7), reference)
+        del s
 
 
 @pytest.mark.parametrize("io,c_type,options", [("FLOAT", "FLOAT", 0), ("BFLOAT16", "BFLOAT16", 0), ("BFLOAT16", "FLOAT", runtime.NO_FUSION)])

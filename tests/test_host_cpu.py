@@ -128,12 +128,19 @@ def test_workspace_planner_rejections(requests, expected):
 
 
 def test_bottleneck_plan_fuses_to_three_launches_and_shares_workspace():
-    exe = runtime.compile_graph(graphs.c2_bottleneck(n=2, h=8, w=8))
+    # default plan: conv1 with its bias and ReLU, then conv2 and conv3 with everything around them in one launch of the
+    # two-convolution kernel; the tensor between those two never exists in memory, so the workspace holds one intermediate
+    # of 2*8*8*64 elements, stored as (hi, lo) bf16 pairs: FLOAT's 4 bytes per element
+    fused = runtime.compile_graph(graphs.c2_bottleneck(n=2, h=8, w=8))
+    assert fused.launch_count == 2 and fused.workspace_size == 2 * 8 * 8 * 64 * 4
+    assert "conv_fprop kernel=3 launches=1 [conv1+bias1+relu1]" in fused.plan_text()
+    assert "conv_fprop_pair kernel=1 launches=1 [conv2+bias2+relu2>conv3+residual]" in fused.plan_text()
+    exe = runtime.compile_graph(graphs.c2_bottleneck(n=2, h=8, w=8), options=runtime.NO_CONV_PAIRS)
     text = exe.plan_text()
     assert exe.launch_count == 3
     assert "[conv1+bias1+relu1]" in text and "[conv2+bias2+relu2]" in text and "[conv3+residual]" in text
     assert text.count("kernel=3") == 3  # tcgen05 implicit GEMM for all three
-    # two intermediates of 2*8*8*64 elements, alive at the same time, each stored as (hi, lo) bf16 pairs: FLOAT's 4 bytes per element
+    # two intermediates, alive at the same time
     assert exe.workspace_size == 2 * (2 * 8 * 8 * 64 * 4)
     # the lossy option stores them as single bf16 values
     lossy = runtime.compile_graph(graphs.c2_bottleneck(n=2, h=8, w=8), options=runtime.BF16_INTERMEDIATES)
