@@ -1,5 +1,5 @@
-// Two convolutions in one persistent kernel: a filter wider than one tap (halo form) whose output, after its
-// per-channel ADD / RELU steps, feeds a 1 x 1 convolution without leaving the SM.
+// Two convolutions in one persistent kernel: a filter wider than one tap whose output, after its per-channel
+// ADD / RELU steps, feeds a 1 x 1 convolution without leaving the SM.
 //
 //   T = relu(conv_a(X, Wa) + bias_a)          K1 = 64 channels, f32 in tensor memory
 //   Y = conv_b(T, Wb) [+ bias_b] [relu] [+ R]  1 x 1, K2 = 128 or 256 channels, bf16 out
@@ -7,18 +7,26 @@
 // The intermediate T never reaches global memory: the first epilogue group splits every f32 value into a (hi, lo)
 // bf16 pair and writes both halves into shared memory in the K-major 128-byte-swizzled layout the second product
 // reads as its A operand; the second product multiplies both halves by the same filter, so T keeps f32-grade
-// precision (2^-17 relative) through the bf16 tensor-core product. One tile = `rows_per_tile` output rows of one image
-// with their padded columns (GEMM row m = padded position (m / pitch, m % pitch); positions with m % pitch >= Q are
-// computed and never stored).
+// precision (2^-17 relative) through the bf16 tensor-core product.
+//
+// One tile = `rows_per_tile` output rows of one image with their padded columns: GEMM row m is the padded position
+// (m / pitch, m % pitch), pitch = Q + S - 1, and positions with m % pitch >= Q are computed and never stored. The
+// input WINDOW of a tile (rows_per_tile + R - 1 input rows, padded columns included) is loaded once per 64-channel
+// block as one TMA box; filter tap (r, s) reads it from row r * pitch + s on, so every tap is a start address into
+// the same slot and an input element crosses L2 -> shared memory once per tile (the 128-byte swizzle is a function
+// of the absolute shared-memory address, as TMA wrote it, so a start at any 128-byte row needs no descriptor offset).
+// The last taps read up to (R - 1) * pitch + S - 1 rows past the 128th row of the window: whatever lies there only
+// reaches GEMM rows that are never stored.
 //
 // Roles (15 warps, one CTA per SM):
-//   warp 0       ring loader: both filters once, then one TMA box per (filter row, 64-channel block) of every tile
-//   warp 1       issues the products: conv_a of tile j + 1 first, then conv_b of tile j, so the tensor pipe works on the
-//                next tile while the epilogue groups drain this one
-//   warps 2-5    epilogue A: accumulator -> bias / ReLU -> (hi, lo) -> shared-memory T tile
-//   warps 6-13   epilogue B, two groups, each half of the K2 output channels in chunks of 64: accumulator -> steps ->
-//                bf16 -> staging box -> TMA store; the residual operand is prefetched by TMA into the same box
-//   warp 14      residual loader
+//   warp 0       loader: both filters once, then one window box per 64-channel block of every tile (ring of slots)
+//   warp 1       issues the products of the hi blocks of conv_a (tile j + 1 first), then conv_b of tile j
+//   warp 14      issues the products of the lo blocks of a split input into a second accumulator (a lone lane issues a
+//                128 x 64 x 16 product in about twice the time the tensor pipe needs to run it)
+//   warps 2-5    epilogue A: accumulator(s) -> bias / ReLU -> (hi, lo) -> shared-memory T tile
+//   warps 6-13   epilogue B, two groups, each half of the K2 output channels in chunks of 64: residual box copied in by
+//                the group itself (coalesced loads, one chunk ahead in registers), accumulator -> steps -> bf16 -> the
+//                same box -> TMA store
 // Every wait is bounded (~2 s): on expiry the waiter records a code in g_device_status, every role falls through to
 // the common exit and tensor memory is freed.
 #include "umma_ptx.cuh"
@@ -31,9 +39,10 @@ constexpr int kBlockK = 64;
 constexpr int kK1 = 64;                  // channels of the intermediate
 constexpr int kPairThreads = 15 * 32;
 constexpr int kMaxStages = 6;
-constexpr int kAccAColumns = 64;         // per conv_a accumulator (two of them)
-constexpr int kAccBColumn0 = 2 * kAccAColumns;
+constexpr int kAccAColumns = 64;         // per conv_a accumulator: [buffer 0 hi, buffer 0 lo, buffer 1 hi, buffer 1 lo]
+constexpr int kAccBColumn0 = 4 * kAccAColumns;
 constexpr int kTmemColumns = 512;
+constexpr int kMaxBoxPieces = 8;         // 16-byte pieces of a residual box per thread: 128 rows x 8 pieces / 128 threads
 
 enum { kStepBias = 1, kStepFull = 2, kStepRelu = 3 };
 
@@ -46,17 +55,20 @@ struct StepList {
 };
 
 struct PairArgs {
-    // first convolution, halo form
-    int32_t a_blocks_per_row;   // 64-channel activation blocks per filter row (2 * C / 64 for a split input)
+    // first convolution
+    int32_t a_blocks;           // 64-channel activation blocks (2 * C / 64 for a split input: hi blocks, then lo blocks)
     int32_t w_blocks_per_tap;   // C / 64
+    int32_t split_in;
     int32_t filter_r, filter_s, pad_h, pad_w;
-    int32_t rows_per_tile, tiles_per_image, out_p, out_q, pitch;
+    int32_t rows_per_tile, window_rows, tiles_per_image, out_p, out_q, pitch;
     int32_t total_tiles;
-    int32_t stages, slot_bytes;
+    int32_t stages, slot_bytes, window_bytes;
     int32_t k2;                 // output channels of the second convolution: 128 or 256
     int32_t box_rows;           // rows_per_tile * Q: rows of the output / residual boxes
+    int32_t box_bytes;          // bytes between the two staging boxes
     int32_t has_residual;
-    int32_t early_static;       // filters and per-channel operands are written by no kernel that may still be running
+    const void* residual;       // bf16 [N * P * Q, K2], when has_residual
+    int32_t early_static;       // filters are written by no kernel that may still be running
     StepList steps_a, steps_b;
     // shared-memory layout (bytes from the 1024-aligned base)
     int32_t wa_offset, wb_offset, t_offset, stage_offset, ring_offset, bias_offset, barrier_offset;
@@ -69,14 +81,14 @@ __device__ __forceinline__ float split_remainder(float x, uint32_t hi_bits) {
 
 __global__ void __launch_bounds__(kPairThreads, 1)
 umma_conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wa, const __grid_constant__ CUtensorMap map_wb,
-                      const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_res, PairArgs args) {
+                      const __grid_constant__ CUtensorMap map_out, PairArgs args) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t wa_base = smem_base + args.wa_offset;
     const uint32_t wb_base = smem_base + args.wb_offset;
-    const uint32_t t_base = smem_base + args.t_offset;        // hi tile, then lo tile (16 KiB each)
-    const uint32_t stage_base = smem_base + args.stage_offset;  // one 16 KiB box per epilogue B group
+    const uint32_t t_base = smem_base + args.t_offset;          // hi tile, then lo tile (16 KiB each)
+    const uint32_t stage_base = smem_base + args.stage_offset;  // one box per epilogue B group
     const uint32_t ring_base = smem_base + args.ring_offset;
     const uint32_t bar_base = smem_base + args.barrier_offset;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -88,22 +100,19 @@ umma_conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     const uint32_t t_empty_bar = bar_base + 8u * (2 * kMaxStages + 6);
     const uint32_t acc_b_full = bar_base + 8u * (2 * kMaxStages + 7);
     const uint32_t acc_b_empty = bar_base + 8u * (2 * kMaxStages + 8);
-    auto res_full = [&](int g) { return bar_base + 8u * (2 * kMaxStages + 9 + g); };
-    auto res_empty = [&](int g) { return bar_base + 8u * (2 * kMaxStages + 11 + g); };
-    const uint32_t tmem_slot = bar_base + 8u * (2 * kMaxStages + 13);
-    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + args.barrier_offset + 8 * (2 * kMaxStages + 13));
+    const uint32_t tmem_slot = bar_base + 8u * (2 * kMaxStages + 9);
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + args.barrier_offset + 8 * (2 * kMaxStages + 9));
 
     const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
     const bool leader = elect_one();
+    const int issuers = args.split_in ? 2 : 1;
     chain_release();
     if (threadIdx.x == 0) {
         prefetch_tensormap(&map_x);
         prefetch_tensormap(&map_wa);
         prefetch_tensormap(&map_wb);
         prefetch_tensormap(&map_out);
-        if (args.has_residual) prefetch_tensormap(&map_res);
     }
-    const int slots_per_tile = args.filter_r * args.a_blocks_per_row;
     const int chunks = args.k2 / 128;  // 64-channel chunks per epilogue B group and tile
     int my_tiles = 0;
     for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x) ++my_tiles;
@@ -122,17 +131,13 @@ umma_conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             }
             mbar_init(w_full_bar, 1);
             for (int a = 0; a < 2; ++a) {
-                mbar_init(acc_a_full(a), 1);
+                mbar_init(acc_a_full(a), issuers);
                 mbar_init(acc_a_empty(a), 4);
             }
             mbar_init(t_full_bar, 4);
             mbar_init(t_empty_bar, 1);
             mbar_init(acc_b_full, 1);
             mbar_init(acc_b_empty, 8);
-            for (int g = 0; g < 2; ++g) {
-                mbar_init(res_full(g), 1);
-                mbar_init(res_empty(g), 1);
-            }
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             mbar_expect_tx(w_full_bar, static_cast<uint32_t>(args.wa_bytes + args.wb_bytes));
         }
@@ -172,68 +177,79 @@ umma_conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     const uint32_t tmem_base = *tmem_slot_ptr;
 
     if (warp == 0) {
-        // ---- ring loader ----
+        // ---- loader: one window box per activation block of every tile ----
         int stage = 0;
         uint32_t phase = 1;
         bool ok = true;
         for (int tile = blockIdx.x; tile < args.total_tiles && ok; tile += gridDim.x) {
             int image, h0, out_row0;
             tile_origin(tile, image, h0, out_row0);
-            for (int r = 0; r < args.filter_r && ok; ++r)
-                for (int cb = 0; cb < args.a_blocks_per_row; ++cb) {
-                    ok = mbar_wait_warp(empty_bar(stage), phase, 201);
-                    if (!ok) break;
-                    if (leader) {
-                        mbar_expect_tx(full_bar(stage), static_cast<uint32_t>(args.rows_per_tile * args.pitch * kBlockK * 2));
-                        tma_load_4d(ring_base + stage * args.slot_bytes, &map_x, cb * kBlockK, -args.pad_w, h0 + r - args.pad_h, image, full_bar(stage));
-                    }
-                    if (++stage == args.stages) { stage = 0; phase ^= 1; }
+            for (int cb = 0; cb < args.a_blocks; ++cb) {
+                ok = mbar_wait_warp(empty_bar(stage), phase, 201);
+                if (!ok) break;
+                if (leader) {
+                    mbar_expect_tx(full_bar(stage), static_cast<uint32_t>(args.window_bytes));
+                    tma_load_4d(ring_base + stage * args.slot_bytes, &map_x, cb * kBlockK, -args.pad_w, h0 - args.pad_h, image, full_bar(stage));
                 }
+                if (++stage == args.stages) { stage = 0; phase ^= 1; }
+            }
         }
-    } else if (warp == 1) {
-        // ---- product issuer ----
+    } else if (warp == 1 || warp == 14) {
+        // ---- product issuers ----
+        const int me = warp == 1 ? 0 : 1;
         const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
         const uint32_t idesc_a = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kK1 >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
         const uint32_t idesc_b = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(args.k2 >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
+        const uint32_t row_step = static_cast<uint32_t>(args.pitch * 128) >> 4;  // descriptor units per filter row
+        const uint32_t w_tap_step = static_cast<uint32_t>(args.w_blocks_per_tap * (kK1 * 128)) >> 4;
         int stage = 0;
         uint32_t phase = 0;
-        bool ok = mbar_wait_warp(w_full_bar, 0, 202);
+        bool ok = me < issuers && mbar_wait_warp(w_full_bar, 0, 202);
         auto issue_a = [&](int j) {
-            const int acc = j & 1;
-            if (ok) ok = mbar_wait_warp(acc_a_empty(acc), ((j >> 1) & 1) ^ 1, 203);
+            const int buffer = j & 1;
+            if (ok) ok = mbar_wait_warp(acc_a_empty(buffer), ((j >> 1) & 1) ^ 1, 203);
             tc_fence_after();
-            const uint32_t tmem_acc = tmem_u + static_cast<uint32_t>(acc * kAccAColumns);
-            int slot = 0;
-            for (int r = 0; r < args.filter_r && ok; ++r)
-                for (int cb = 0; cb < args.a_blocks_per_row; ++cb, ++slot) {
+            const uint32_t tmem_acc = tmem_u + static_cast<uint32_t>((2 * buffer + me) * kAccAColumns);
+            uint32_t accumulate = 0;
+            for (int cb = 0; cb < args.a_blocks; ++cb) {
+                const bool lo_block = cb >= args.w_blocks_per_tap;
+                const bool mine = args.split_in ? (lo_block == (me == 1)) : true;
+                if (mine && ok) {
                     ok = mbar_wait_warp(full_bar(stage), phase, 204);
-                    if (!ok) break;
-                    const uint32_t a_lo = smem_desc_lo(ring_base + stage * args.slot_bytes, 16);
-                    const int wc = cb >= args.w_blocks_per_tap ? cb - args.w_blocks_per_tap : cb;  // the lo half meets the same filter slices
-                    const uint32_t b_first = smem_desc_lo(wa_base + ((r * args.filter_s * args.w_blocks_per_tap + wc) * (kK1 * 128)), 16);
-                    const uint32_t b_tap_step = static_cast<uint32_t>(args.w_blocks_per_tap * (kK1 * 128)) >> 4;
-                    if (leader) {
-                        const uint32_t first = slot != 0 ? 1u : 0u;
-                        if (args.filter_s == 3) {
+                    if (ok) {
+                        const uint32_t a_lo = smem_desc_lo(ring_base + stage * args.slot_bytes, 16);
+                        const int wc = lo_block ? cb - args.w_blocks_per_tap : cb;  // the lo half meets the same filter slices
+                        const uint32_t b_block = smem_desc_lo(wa_base + wc * (kK1 * 128), 16);
+                        if (leader) {
+                            for (int r = 0; r < args.filter_r; ++r) {
+                                const uint32_t a_row = a_lo + r * row_step;
+                                const uint32_t b_row = b_block + r * args.filter_s * w_tap_step;
+                                if (args.filter_s == 3) {
 #pragma unroll
-                            for (int tap = 0; tap < 3; ++tap)
+                                    for (int tap = 0; tap < 3; ++tap)
 #pragma unroll
-                                for (int k = 0; k < kBlockK / 16; ++k)
-                                    umma_bf16(tmem_acc, desc_words(a_lo + ((tap * 128 + k * 32) >> 4), smem_desc_hi(1024)),
-                                              desc_words(b_first + tap * b_tap_step + ((k * 32) >> 4), smem_desc_hi(1024)), idesc_a, (tap | k) != 0 ? 1u : first);
-                        } else {
-                            for (int tap = 0; tap < args.filter_s; ++tap) {
+                                        for (int k = 0; k < kBlockK / 16; ++k) {
+                                            umma_bf16(tmem_acc, desc_words(a_row + ((tap * 128 + k * 32) >> 4), smem_desc_hi(1024)),
+                                                      desc_words(b_row + tap * w_tap_step + ((k * 32) >> 4), smem_desc_hi(1024)), idesc_a, accumulate);
+                                            accumulate = 1;
+                                        }
+                                } else {
+                                    for (int tap = 0; tap < args.filter_s; ++tap)
 #pragma unroll
-                                for (int k = 0; k < kBlockK / 16; ++k)
-                                    umma_bf16(tmem_acc, desc_words(a_lo + ((tap * 128 + k * 32) >> 4), smem_desc_hi(1024)),
-                                              desc_words(b_first + tap * b_tap_step + ((k * 32) >> 4), smem_desc_hi(1024)), idesc_a, (tap | k) != 0 ? 1u : first);
+                                        for (int k = 0; k < kBlockK / 16; ++k) {
+                                            umma_bf16(tmem_acc, desc_words(a_row + ((tap * 128 + k * 32) >> 4), smem_desc_hi(1024)),
+                                                      desc_words(b_row + tap * w_tap_step + ((k * 32) >> 4), smem_desc_hi(1024)), idesc_a, accumulate);
+                                            accumulate = 1;
+                                        }
+                                }
                             }
+                            umma_commit(empty_bar(stage));
                         }
-                        umma_commit(empty_bar(stage));
                     }
-                    if (++stage == args.stages) { stage = 0; phase ^= 1; }
                 }
-            if (leader) umma_commit(acc_a_full(acc));  // arrives even after a failed wait, so the epilogue never hangs on it
+                if (++stage == args.stages) { stage = 0; phase ^= 1; }
+            }
+            if (leader) umma_commit(acc_a_full(buffer));  // arrives even after a failed wait, so the epilogue never hangs on it
         };
         auto issue_b = [&](int j) {
             if (ok) ok = mbar_wait_warp(t_full_bar, j & 1, 205);
@@ -256,13 +272,15 @@ umma_conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 umma_commit(acc_b_full);
             }
         };
-        if (my_tiles > 0) issue_a(0);
-        for (int j = 0; j < my_tiles; ++j) {
-            if (j + 1 < my_tiles) issue_a(j + 1);
-            issue_b(j);
+        if (me < issuers) {
+            issue_a(0);
+            for (int j = 0; j < my_tiles; ++j) {
+                if (j + 1 < my_tiles) issue_a(j + 1);
+                if (me == 0) issue_b(j);
+            }
         }
     } else if (warp >= 2 && warp <= 5) {
-        // ---- epilogue A: conv_a accumulator -> steps -> (hi, lo) bf16 -> the T tile ----
+        // ---- epilogue A: conv_a accumulator(s) -> steps -> (hi, lo) bf16 -> the T tile ----
         const int quadrant = warp & 3;
         const int row = quadrant * 32 + lane;  // GEMM row = TMEM lane; the T tile keeps GEMM row order
         const float* bias_smem = reinterpret_cast<const float*>(generic_base + args.bias_offset);
@@ -270,22 +288,33 @@ umma_conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         uint8_t* t_lo = t_hi + kTileM * 128;
         bool ok = true;
         for (int j = 0; j < my_tiles; ++j) {
-            const int acc = j & 1;
-            if (ok) ok = mbar_wait(acc_a_full(acc), (j >> 1) & 1, 207);
+            const int buffer = j & 1;
+            if (ok) ok = mbar_wait(acc_a_full(buffer), (j >> 1) & 1, 207);
             tc_fence_after();
             float v[kK1];
+            const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) + 2 * buffer * kAccAColumns;
 #pragma unroll
             for (int chunk = 0; chunk < kK1 / 32; ++chunk) {
                 uint32_t raw[32];
-                tmem_load_32(tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) + acc * kAccAColumns + chunk * 32, raw);
+                tmem_load_32(lane_base + chunk * 32, raw);
                 tmem_load_wait();
 #pragma unroll
                 for (int e = 0; e < 32; ++e) v[chunk * 32 + e] = __uint_as_float(raw[e]);
             }
-            // the accumulator is in registers: hand it back before the arithmetic
+            if (args.split_in) {  // the lo blocks' share of the sum, from the second issuing warp's accumulator
+#pragma unroll
+                for (int chunk = 0; chunk < kK1 / 32; ++chunk) {
+                    uint32_t raw[32];
+                    tmem_load_32(lane_base + kAccAColumns + chunk * 32, raw);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) v[chunk * 32 + e] = __fadd_rn(v[chunk * 32 + e], __uint_as_float(raw[e]));
+                }
+            }
+            // the accumulators are in registers: hand them back before the arithmetic
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_a_empty(acc));
+            if (lane == 0) mbar_arrive(acc_a_empty(buffer));
             int bias_at = 0;
             for (int e = 0; e < args.steps_a.count; ++e) {
                 if (args.steps_a.kind[e] == kStepRelu) {
@@ -329,120 +358,122 @@ umma_conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     } else if (warp >= 6 && warp <= 13) {
         // ---- epilogue B: conv_b accumulator -> steps -> bf16 -> staging box -> TMA store ----
         const int group = (warp - 6) >> 2;
+        const int member = threadIdx.x - (6 + 4 * group) * 32;  // 0..127 inside the group
         const int quadrant = warp & 3;
         const int gemm_row = quadrant * 32 + lane;
         const int line = gemm_row / args.pitch, column = gemm_row - line * args.pitch;
         const bool row_is_output = column < args.out_q && line < args.rows_per_tile;
         const int row = row_is_output ? line * args.out_q + column : 0;  // rows compacted for the store
-        const bool store_thread = ((warp - 6) & 3) == 0 && lane == 0;
+        const bool store_thread = member == 0;
         const float* bias_smem = reinterpret_cast<const float*>(generic_base + args.bias_offset);
         int bias_a_floats = 0;
         for (int e = 0; e < args.steps_a.count; ++e) bias_a_floats += args.steps_a.kind[e] == kStepBias ? kK1 : 0;
-        uint8_t* box = generic_base + args.stage_offset + group * (kTileM * 128);
+        uint8_t* box = generic_base + args.stage_offset + group * args.box_bytes;
         uint8_t* row_smem = box + row * 128;
+        const int pieces = args.box_rows * 8;  // 16-byte pieces of one residual box
+        // Residual pieces of the chunk after the one being worked on, fetched with coalesced loads (eight consecutive
+        // threads read one 128-byte row) and parked in registers until the box is free to take them.
+        uint4 parked[kMaxBoxPieces];
+        auto fetch_residual = [&](int tile, int c) {
+            int image, h0, out_row0;
+            tile_origin(tile, image, h0, out_row0);
+            const uint8_t* source = static_cast<const uint8_t*>(args.residual) + (static_cast<int64_t>(out_row0) * args.k2 + group * (args.k2 / 2) + c * 64) * 2;
+#pragma unroll
+            for (int q = 0; q < kMaxBoxPieces; ++q) {
+                const int piece = q * 128 + member;
+                if (piece < pieces) parked[q] = __ldg(reinterpret_cast<const uint4*>(source + static_cast<int64_t>(piece >> 3) * args.k2 * 2 + (piece & 7) * 16));
+            }
+        };
+        if (args.has_residual && my_tiles > 0) fetch_residual(blockIdx.x, 0);
         bool ok = true;
-        int n = 0;  // chunks this group has handled
         for (int j = 0, tile = blockIdx.x; j < my_tiles; ++j, tile += gridDim.x) {
             int image, h0, out_row0;
             tile_origin(tile, image, h0, out_row0);
-            if (ok) ok = mbar_wait(acc_b_full, j & 1, 209);
-            tc_fence_after();
-            for (int c = 0; c < chunks; ++c, ++n) {
+            for (int c = 0; c < chunks; ++c) {
                 const int col0 = group * (args.k2 / 2) + c * 64;
-                float v[64];
+                // the previous chunk's store has read the box: it can take this chunk's residual, then its result
+                if (store_thread) tma_store_wait_read<0>();
+                epilogue_barrier(1 + group);
+                if (args.has_residual) {
 #pragma unroll
+                    for (int q = 0; q < kMaxBoxPieces; ++q) {
+                        const int piece = q * 128 + member;
+                        if (piece < pieces) *reinterpret_cast<uint4*>(box + (piece >> 3) * 128 + (((piece & 7) ^ ((piece >> 3) & 7)) << 4)) = parked[q];
+                    }
+                    // next chunk's residual on its way while this one is worked on
+                    if (c + 1 < chunks) fetch_residual(tile, c + 1);
+                    else if (j + 1 < my_tiles) fetch_residual(tile + gridDim.x, 0);
+                    epilogue_barrier(1 + group);
+                }
+                if (c == 0) {
+                    if (ok) ok = mbar_wait(acc_b_full, j & 1, 209);
+                    tc_fence_after();
+                }
+                const bool healthy = ok && g_device_status == 0;
+#pragma unroll 1
                 for (int half = 0; half < 2; ++half) {
                     uint32_t raw[32];
                     tmem_load_32(tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) + kAccBColumn0 + col0 + half * 32, raw);
                     tmem_load_wait();
+                    if (c == chunks - 1 && half == 1) {  // this group's columns have all left tensor memory
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acc_b_empty);
+                    }
+                    float v[32];
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) v[half * 32 + e] = __uint_as_float(raw[e]);
-                }
-                if (c == chunks - 1) {  // this group's columns are all in registers now
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(acc_b_empty);
-                }
-                if (args.has_residual) {
-                    if (ok) ok = mbar_wait(res_full(group), n & 1, 210);
-                } else {
-                    if (store_thread) tma_store_wait_read<0>();  // the previous chunk's store has read the box
-                    epilogue_barrier(1 + group);
-                }
-                const bool healthy = ok && g_device_status == 0;
-                int bias_at = bias_a_floats;
-                for (int e = 0; e < args.steps_b.count; ++e) {
-                    const int kind = args.steps_b.kind[e];
-                    if (kind == kStepRelu) {
-                        const float lower = args.steps_b.lower[e], upper = args.steps_b.upper[e], slope = args.steps_b.slope[e];
+                    for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[e]);
+                    int bias_at = bias_a_floats;
+                    for (int e = 0; e < args.steps_b.count; ++e) {
+                        const int kind = args.steps_b.kind[e];
+                        if (kind == kStepRelu) {
+                            const float lower = args.steps_b.lower[e], upper = args.steps_b.upper[e], slope = args.steps_b.slope[e];
 #pragma unroll
-                        for (int t = 0; t < 64; ++t) v[t] = relu_fast(v[t], lower, upper, slope);
-                    } else if (kind == kStepBias) {
-                        const float4* p = reinterpret_cast<const float4*>(bias_smem + bias_at + col0);
-                        bias_at += args.k2;
+                            for (int t = 0; t < 32; ++t) v[t] = relu_fast(v[t], lower, upper, slope);
+                        } else if (kind == kStepBias) {
+                            const float4* p = reinterpret_cast<const float4*>(bias_smem + bias_at + col0 + half * 32);
+                            bias_at += args.k2;
 #pragma unroll
-                        for (int q4 = 0; q4 < 16; ++q4) {
-                            const float4 q = p[q4];
-                            v[4 * q4] = __fadd_rn(v[4 * q4], q.x);
-                            v[4 * q4 + 1] = __fadd_rn(v[4 * q4 + 1], q.y);
-                            v[4 * q4 + 2] = __fadd_rn(v[4 * q4 + 2], q.z);
-                            v[4 * q4 + 3] = __fadd_rn(v[4 * q4 + 3], q.w);
-                        }
-                    } else {  // the residual box the loader staged here
+                            for (int q4 = 0; q4 < 8; ++q4) {
+                                const float4 q = p[q4];
+                                v[4 * q4] = __fadd_rn(v[4 * q4], q.x);
+                                v[4 * q4 + 1] = __fadd_rn(v[4 * q4 + 1], q.y);
+                                v[4 * q4 + 2] = __fadd_rn(v[4 * q4 + 2], q.z);
+                                v[4 * q4 + 3] = __fadd_rn(v[4 * q4 + 3], q.w);
+                            }
+                        } else {  // the residual box staged above
 #pragma unroll
-                        for (int c16 = 0; c16 < 8; ++c16) {
-                            const uint4 q = *reinterpret_cast<const uint4*>(row_smem + ((c16 ^ (row & 7)) << 4));
-                            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+                            for (int c16 = 0; c16 < 4; ++c16) {
+                                const uint4 q = *reinterpret_cast<const uint4*>(row_smem + (((half * 4 + c16) ^ (row & 7)) << 4));
+                                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-                            for (int t = 0; t < 4; ++t) {
-                                v[8 * c16 + 2 * t] = __fadd_rn(v[8 * c16 + 2 * t], __uint_as_float(w[t] << 16));
-                                v[8 * c16 + 2 * t + 1] = __fadd_rn(v[8 * c16 + 2 * t + 1], __uint_as_float(w[t] & 0xffff0000u));
+                                for (int t = 0; t < 4; ++t) {
+                                    v[8 * c16 + 2 * t] = __fadd_rn(v[8 * c16 + 2 * t], __uint_as_float(w[t] << 16));
+                                    v[8 * c16 + 2 * t + 1] = __fadd_rn(v[8 * c16 + 2 * t + 1], __uint_as_float(w[t] & 0xffff0000u));
+                                }
                             }
                         }
                     }
-                }
 #pragma unroll
-                for (int c16 = 0; c16 < 8; ++c16) {
-                    uint32_t w[4];
+                    for (int c16 = 0; c16 < 4; ++c16) {
+                        uint32_t w[4];
 #pragma unroll
-                    for (int t = 0; t < 4; ++t) {
-                        __nv_bfloat162 pair = __floats2bfloat162_rn(v[8 * c16 + 2 * t], v[8 * c16 + 2 * t + 1]);
-                        w[t] = *reinterpret_cast<uint32_t*>(&pair);
+                        for (int t = 0; t < 4; ++t) {
+                            __nv_bfloat162 pair = __floats2bfloat162_rn(v[8 * c16 + 2 * t], v[8 * c16 + 2 * t + 1]);
+                            w[t] = *reinterpret_cast<uint32_t*>(&pair);
+                        }
+                        if (row_is_output) *reinterpret_cast<uint4*>(row_smem + (((half * 4 + c16) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                    if (row_is_output) *reinterpret_cast<uint4*>(row_smem + ((c16 ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
                 fence_async_shared();
                 epilogue_barrier(1 + group);
                 if (store_thread) {
-                    if (healthy) tma_store_2d(&map_out, stage_base + group * (kTileM * 128), col0, out_row0);
+                    if (healthy) tma_store_2d(&map_out, stage_base + group * args.box_bytes, col0, out_row0);
                     tma_store_commit();
-                    if (args.has_residual) {
-                        tma_store_wait_read<0>();  // the box goes back to the residual loader once the store has read it
-                        mbar_arrive(res_empty(group));
-                    }
                 }
             }
         }
         if (store_thread) tma_store_wait_all();
-    } else if (warp == 14) {
-        // ---- residual loader ----
-        if (args.has_residual) {
-            bool ok = true;
-            int n = 0;
-            for (int tile = blockIdx.x; tile < args.total_tiles && ok; tile += gridDim.x) {
-                int image, h0, out_row0;
-                tile_origin(tile, image, h0, out_row0);
-                for (int c = 0; c < chunks && ok; ++c, ++n)
-                    for (int g = 0; g < 2; ++g) {
-                        ok = mbar_wait_warp(res_empty(g), (n & 1) ^ 1, 211);
-                        if (!ok) break;
-                        if (leader) {
-                            mbar_expect_tx(res_full(g), static_cast<uint32_t>(args.box_rows) * 128u);
-                            tma_load_2d(stage_base + g * (kTileM * 128), &map_res, g * (args.k2 / 2) + c * 64, out_row0, res_full(g));
-                        }
-                    }
-            }
-        }
     }
 
     tc_fence_before();
@@ -511,9 +542,11 @@ struct PairForm {
     ConvForm a;
     int64_t k2;
     int bias_a, bias_b, full_b, residual_operand;
-    int stages, slot_bytes;
+    int window_rows, window_bytes, stages, slot_bytes, box_rows, box_bytes;
     int wa_bytes, wb_bytes, bias_bytes;
 };
+
+int round_up_1k(int64_t bytes) { return static_cast<int>((bytes + 1023) & ~int64_t{1023}); }
 
 bool pair_form(const dfgpu_conv_params& first, const dfgpu_conv_params& second, PairForm& f) {
     // the intermediate must keep f32-grade values: FLOAT as the graph declares it, or the (hi, lo) pair type
@@ -534,17 +567,27 @@ bool pair_form(const dfgpu_conv_params& first, const dfgpu_conv_params& second, 
     if (second.y.rank != 4 || second.y.dim[0] != f.a.N || second.y.dim[2] != f.a.P || second.y.dim[3] != f.a.Q) return false;
     // packed NHWC output
     if (second.y.stride[1] != 1 || second.y.stride[3] != f.k2 || second.y.stride[2] != f.a.Q * f.k2 || second.y.stride[0] != f.a.P * f.a.Q * f.k2) return false;
-    if (f.a.N * f.a.P * f.a.Q >= (1ll << 31)) return false;
+    if (f.a.N * f.a.P * f.a.Q >= (1ll << 31) / 256) return false;  // byte offsets of the output stay inside 32 bits times the row pitch
     int full_a = 0, unused = -1;
     if (!classify_steps(first, nullptr, nullptr, &f.bias_a, &full_a, &unused) || full_a != 0) return false;
     if (!classify_steps(second, nullptr, nullptr, &f.bias_b, &f.full_b, &f.residual_operand) || f.full_b > 1) return false;
+    const int64_t pitch = f.a.Q + f.a.S - 1;
+    f.window_rows = f.a.halo_rows + static_cast<int>(f.a.R) - 1;
+    if (f.window_rows > 256 || pitch > 256) return false;  // TMA box extents
+    f.window_bytes = static_cast<int>(f.window_rows * pitch * 128);
+    f.slot_bytes = round_up_1k(f.window_bytes);
+    f.box_rows = f.a.halo_rows * static_cast<int>(f.a.Q);
+    f.box_bytes = round_up_1k(f.box_rows * 128);
     f.wa_bytes = static_cast<int>(kK1 * f.a.R * f.a.S * f.a.C * 2);
     f.wb_bytes = static_cast<int>(f.k2 * kK1 * 2);
-    f.bias_bytes = static_cast<int>(((f.bias_a * kK1 + f.bias_b * f.k2) * 4 + 1023) & ~1023);
-    f.slot_bytes = static_cast<int>(((kTileM + f.a.S - 1) * 128 + 1023) & ~1023);
-    const int fixed = ((f.wa_bytes + 1023) & ~1023) + ((f.wb_bytes + 1023) & ~1023) + 2 * kTileM * 128 + 2 * kTileM * 128 + f.bias_bytes + 256 + 1024;
+    f.bias_bytes = round_up_1k((f.bias_a * kK1 + f.bias_b * f.k2) * 4 + 256);  // staged bias vectors, then the barriers
+    const int fixed = round_up_1k(f.wa_bytes) + round_up_1k(f.wb_bytes) + 2 * kTileM * 128 + 2 * f.box_bytes + f.bias_bytes + 1024;
     f.stages = (kPairSmemBudget - fixed) / f.slot_bytes;
     if (f.stages > kMaxStages) f.stages = kMaxStages;
+    // the last taps read past the window's rows (into rows no stored GEMM row uses): that must stay inside the allocation,
+    // i.e. inside what follows the last slot
+    const int64_t rows_read = kTileM + (f.a.R - 1) * pitch + f.a.S - 1;
+    if (rows_read * 128 - f.slot_bytes > 2 * f.box_bytes + f.bias_bytes) return false;
     return f.stages >= 2;
 }
 
@@ -564,13 +607,15 @@ int launch_conv_pair_umma(const dfgpu_conv_params& first, const dfgpu_conv_param
     const ConvForm& a = f.a;
     const int64_t Ca = a.split_in ? 2 * a.C : a.C;
     PairArgs args{};
-    args.a_blocks_per_row = static_cast<int>(Ca / kBlockK);
+    args.a_blocks = static_cast<int>(Ca / kBlockK);
     args.w_blocks_per_tap = static_cast<int>(a.C / kBlockK);
+    args.split_in = a.split_in ? 1 : 0;
     args.filter_r = static_cast<int>(a.R);
     args.filter_s = static_cast<int>(a.S);
     args.pad_h = static_cast<int>(first.pre_pad[0]);
     args.pad_w = static_cast<int>(first.pre_pad[1]);
     args.rows_per_tile = a.halo_rows;
+    args.window_rows = f.window_rows;
     args.tiles_per_image = static_cast<int>(a.P / a.halo_rows);
     args.out_p = static_cast<int>(a.P);
     args.out_q = static_cast<int>(a.Q);
@@ -578,8 +623,10 @@ int launch_conv_pair_umma(const dfgpu_conv_params& first, const dfgpu_conv_param
     args.total_tiles = static_cast<int>(a.N) * args.tiles_per_image;
     args.stages = f.stages;
     args.slot_bytes = f.slot_bytes;
+    args.window_bytes = f.window_bytes;
     args.k2 = static_cast<int>(f.k2);
-    args.box_rows = a.halo_rows * static_cast<int>(a.Q);
+    args.box_rows = f.box_rows;
+    args.box_bytes = f.box_bytes;
     args.has_residual = f.full_b;
     args.early_static = ((first.reserved & 2) && (second.reserved & 2)) ? 1 : 0;  // both filters are static operands
     int bias = 0, full = 0, operand = -1;
@@ -589,24 +636,26 @@ int launch_conv_pair_umma(const dfgpu_conv_params& first, const dfgpu_conv_param
         for (int e = 0; e < list->count; ++e)
             if (list->kind[e] != kStepRelu && (!list->data[e] || !aligned16(list->data[e])))
                 return fail(kInvalidArgument, "CONV_FPROP pair: ADD operands must be non-null and 16-byte aligned");
+    for (int e = 0; e < args.steps_b.count; ++e)
+        if (args.steps_b.kind[e] == kStepFull) args.residual = args.steps_b.data[e];
     args.wa_bytes = f.wa_bytes;
     args.wb_bytes = f.wb_bytes;
     args.wa_offset = 0;
-    args.wb_offset = (f.wa_bytes + 1023) & ~1023;
-    args.t_offset = args.wb_offset + ((f.wb_bytes + 1023) & ~1023);
-    args.stage_offset = args.t_offset + 2 * kTileM * 128;
-    args.ring_offset = args.stage_offset + 2 * kTileM * 128;
-    args.bias_offset = args.ring_offset + f.stages * f.slot_bytes;
-    args.barrier_offset = args.bias_offset + f.bias_bytes;
-    const int dynamic = args.barrier_offset + 256 + 1024;
+    args.wb_offset = round_up_1k(f.wa_bytes);
+    args.t_offset = args.wb_offset + round_up_1k(f.wb_bytes);
+    args.ring_offset = args.t_offset + 2 * kTileM * 128;
+    args.stage_offset = args.ring_offset + f.stages * f.slot_bytes;  // right behind the ring: the taps' reads past the last slot land here
+    args.bias_offset = args.stage_offset + 2 * f.box_bytes;
+    args.barrier_offset = args.bias_offset + f.bias_bytes - 256;
+    const int dynamic = args.bias_offset + f.bias_bytes + 1024;
     if (dynamic > kPairSmemBudget) return fail(kUnsupported, "CONV_FPROP pair: shared-memory layout does not fit");
 
-    CUtensorMap map_x, map_wa, map_wb, map_out, map_res;
+    CUtensorMap map_x, map_wa, map_wb, map_out;
     int status;
     {
         uint64_t dims[4] = {static_cast<uint64_t>(Ca), static_cast<uint64_t>(a.W), static_cast<uint64_t>(a.H), static_cast<uint64_t>(a.N)};
         uint64_t strides[3] = {static_cast<uint64_t>(Ca) * 2, static_cast<uint64_t>(a.W * Ca) * 2, static_cast<uint64_t>(a.H * a.W * Ca) * 2};
-        uint32_t box[4] = {kBlockK, static_cast<uint32_t>(args.pitch), static_cast<uint32_t>(a.halo_rows), 1};
+        uint32_t box[4] = {kBlockK, static_cast<uint32_t>(args.pitch), static_cast<uint32_t>(f.window_rows), 1};
         if ((status = make_map(&map_x, tensors[0], 4, dims, strides, box, "CONV_FPROP pair X"))) return status;
     }
     {
@@ -624,12 +673,8 @@ int launch_conv_pair_umma(const dfgpu_conv_params& first, const dfgpu_conv_param
     {
         uint64_t dims[2] = {static_cast<uint64_t>(f.k2), static_cast<uint64_t>(a.N * a.P * a.Q)};
         uint64_t strides[1] = {static_cast<uint64_t>(f.k2) * 2};
-        uint32_t box[2] = {64, static_cast<uint32_t>(args.box_rows)};
+        uint32_t box[2] = {64, static_cast<uint32_t>(f.box_rows)};
         if ((status = make_map(&map_out, tensors[3], 2, dims, strides, box, "CONV_FPROP pair Y"))) return status;
-        const void* residual = tensors[3];
-        for (int e = 0; e < args.steps_b.count; ++e)
-            if (args.steps_b.kind[e] == kStepFull) residual = args.steps_b.data[e];
-        if ((status = make_map(&map_res, residual, 2, dims, strides, box, "CONV_FPROP pair residual"))) return status;
     }
     static bool configured = false;
     if (!configured) {
@@ -644,7 +689,7 @@ int launch_conv_pair_umma(const dfgpu_conv_params& first, const dfgpu_conv_param
         const int rounds = (args.total_tiles + sms - 1) / sms;
         grid = (args.total_tiles + rounds - 1) / rounds;
     }
-    cudaError_t launched = launch_chained(umma_conv_pair_kernel, dim3(grid), dim3(kPairThreads), dynamic, stream, map_x, map_wa, map_wb, map_out, map_res, args);
+    cudaError_t launched = launch_chained(umma_conv_pair_kernel, dim3(grid), dim3(kPairThreads), dynamic, stream, map_x, map_wa, map_wb, map_out, args);
     if (launched != cudaSuccess) return fail(kExecutionFailed, "CONV_FPROP pair: launch failed: %s", cudaGetErrorString(launched));
     return check_launch("CONV_FPROP pair");
 }

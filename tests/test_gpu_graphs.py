@@ -90,7 +90,7 @@ def test_c2_bottleneck_other_geometries(shape, options):
     128-channel block, through the two-convolution kernel and as three launches."""
     wl = workloads.c2(**shape)
     s = harness.Session(wl, options=options)
-    if options == 0:
+    if options == 0 and shape["w"] != 120:  # (two windows of a 122-pixel pitch do not fit beside the filters: three launches there)
         assert s.exe.launch_count == 2 and "conv_fprop_pair kernel=1" in s.exe.plan_text()
     else:
         assert s.exe.plan_text().count("conv_fprop kernel=3") == 3
