@@ -4,10 +4,10 @@
 //   T = relu(conv_a(X, Wa) + bias_a)          K1 = 64 channels, f32 in tensor memory
 //   Y = conv_b(T, Wb) [+ bias_b] [relu] [+ R]  1 x 1, K2 = 128 or 256 channels, bf16 out
 //
-// The intermediate T never reaches global memory: the first epilogue group splits every f32 value into a (hi, lo)
-// bf16 pair and writes both halves into shared memory in the K-major 128-byte-swizzled layout the second product
-// reads as its A operand; the second product multiplies both halves by the same filter, so T keeps f32-grade
-// precision (2^-17 relative) through the bf16 tensor-core product.
+// The intermediate T never reaches global memory, nor shared memory: the first epilogue group splits every f32 value
+// into a (hi, lo) bf16 pair and stores both halves back into TENSOR memory, over accumulator columns it has just read;
+// the second product takes its A operand from there and multiplies both halves by the same filter, so T keeps
+// f32-grade precision (2^-17 relative) through the bf16 tensor-core product.
 //
 // One tile = `rows_per_tile` output rows of one image with their padded columns: GEMM row m is the padded position
 // (m / pitch, m % pitch), pitch = Q + S - 1, and positions with m % pitch >= Q are computed and never stored. The
@@ -18,15 +18,20 @@
 // The last taps read up to (R - 1) * pitch + S - 1 rows past the 128th row of the window: whatever lies there only
 // reaches GEMM rows that are never stored.
 //
-// Roles (15 warps, one CTA per SM):
+// Roles (23 warps, one CTA per SM; the epilogues are chains of dependent tensor-memory loads, conversions and
+// shared-memory stores, so they get most of the warps):
 //   warp 0       loader: both filters once, then one window box per 64-channel block of every tile (ring of slots)
 //   warp 1       issues the products of the hi blocks of conv_a (tile j + 1 first), then conv_b of tile j
-//   warp 14      issues the products of the lo blocks of a split input into a second accumulator (a lone lane issues a
+//   warp 2       issues the products of the lo blocks of a split input into a second accumulator (a lone lane issues a
 //                128 x 64 x 16 product in about twice the time the tensor pipe needs to run it)
-//   warps 2-5    epilogue A: accumulator(s) -> bias / ReLU -> (hi, lo) -> shared-memory T tile
-//   warps 6-13   epilogue B, two groups, each half of the K2 output channels in chunks of 64: residual box copied in by
-//                the group itself (coalesced loads, one chunk ahead in registers), accumulator -> steps -> bf16 -> the
-//                same box -> TMA store
+//   warps 3-6    epilogue A: accumulator(s) -> bias / ReLU -> (hi, lo) -> tensor memory (the T operand of conv_b)
+//   warps 7-22   epilogue B, two groups of eight warps, each half of the K2 output channels in chunks of 64 (a thread
+//                owns 32 columns of one row), two staging boxes per group used alternately: accumulator -> steps (the
+//                residual operand waits in the box) -> bf16 -> the same box -> TMA store
+//   warp 23      residual loader: the residual box of a chunk by TMA, as soon as the box's last store has been read
+// Tensor memory (512 columns): conv_a accumulators [buffer b: hi products at 128 b, lo products at 128 b + 64], conv_b
+// accumulator at 256. T of a tile overwrites the lo-product columns of its buffer as packed bf16 pairs, per 32 channels
+// [16 columns of hi words | 16 columns of lo words].
 // Every wait is bounded (~2 s): on expiry the waiter records a code in g_device_status, every role falls through to
 // the common exit and tensor memory is freed.
 #include "umma_ptx.cuh"
@@ -37,12 +42,11 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kBlockK = 64;
 constexpr int kK1 = 64;                  // channels of the intermediate
-constexpr int kPairThreads = 15 * 32;
+constexpr int kPairThreads = 24 * 32;    // 3 control warps, 4 for epilogue A, 2 x 8 for epilogue B, the residual loader
 constexpr int kMaxStages = 6;
 constexpr int kAccAColumns = 64;         // per conv_a accumulator: [buffer 0 hi, buffer 0 lo, buffer 1 hi, buffer 1 lo]
 constexpr int kAccBColumn0 = 4 * kAccAColumns;
 constexpr int kTmemColumns = 512;
-constexpr int kMaxBoxPieces = 8;         // 16-byte pieces of a residual box per thread: 128 rows x 8 pieces / 128 threads
 
 enum { kStepBias = 1, kStepFull = 2, kStepRelu = 3 };
 
@@ -65,30 +69,57 @@ struct PairArgs {
     int32_t stages, slot_bytes, window_bytes;
     int32_t k2;                 // output channels of the second convolution: 128 or 256
     int32_t box_rows;           // rows_per_tile * Q: rows of the output / residual boxes
-    int32_t box_bytes;          // bytes between the two staging boxes
+    int32_t box_bytes;          // bytes between staging boxes (two per epilogue B group)
     int32_t has_residual;
-    const void* residual;       // bf16 [N * P * Q, K2], when has_residual
     int32_t early_static;       // filters are written by no kernel that may still be running
     StepList steps_a, steps_b;
     // shared-memory layout (bytes from the 1024-aligned base)
-    int32_t wa_offset, wb_offset, t_offset, stage_offset, ring_offset, bias_offset, barrier_offset;
+    int32_t wa_offset, wb_offset, stage_offset, ring_offset, bias_offset, barrier_offset;
     int32_t wa_bytes, wb_bytes;
 };
+
+__device__ __forceinline__ void tmem_store_32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]),
+          "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (bf16 pairs, one row per lane, 8 columns per 16-deep K step) is read
+// from tensor memory.
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
 
 __device__ __forceinline__ float split_remainder(float x, uint32_t hi_bits) {
     return (hi_bits & 0x7f800000u) == 0x7f800000u ? 0.0f : x - __uint_as_float(hi_bits);
 }
 
+// RELU_FWD, same results as relu_forward(): below `lower` the sloped branch (NaN for -inf with slope 0, as the separate
+// multiply and add give), otherwise min(x, upper) -- max(x, lower) is x there -- with NaN passed through by min.NaN.
+__device__ __forceinline__ float relu_step(float x, float lower, float upper, float slope) {
+    float clipped;
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(clipped) : "f"(x), "f"(upper));
+    return x < lower ? fmaf(slope, x - lower, lower) : clipped;
+}
+
 __global__ void __launch_bounds__(kPairThreads, 1)
 umma_conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wa, const __grid_constant__ CUtensorMap map_wb,
-                      const __grid_constant__ CUtensorMap map_out, PairArgs args) {
+                      const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_res, PairArgs args) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t wa_base = smem_base + args.wa_offset;
     const uint32_t wb_base = smem_base + args.wb_offset;
-    const uint32_t t_base = smem_base + args.t_offset;          // hi tile, then lo tile (16 KiB each)
-    const uint32_t stage_base = smem_base + args.stage_offset;  // one box per epilogue B group
+    const uint32_t stage_base = smem_base + args.stage_offset;  // two boxes per epilogue B group
     const uint32_t ring_base = smem_base + args.ring_offset;
     const uint32_t bar_base = smem_base + args.barrier_offset;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -97,11 +128,13 @@ umma_conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     auto acc_a_full = [&](int a) { return bar_base + 8u * (2 * kMaxStages + 1 + a); };
     auto acc_a_empty = [&](int a) { return bar_base + 8u * (2 * kMaxStages + 3 + a); };
     const uint32_t t_full_bar = bar_base + 8u * (2 * kMaxStages + 5);
-    const uint32_t t_empty_bar = bar_base + 8u * (2 * kMaxStages + 6);
+    auto t_done_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + 10 + b); };  // conv_b has read the T of buffer b
     const uint32_t acc_b_full = bar_base + 8u * (2 * kMaxStages + 7);
     const uint32_t acc_b_empty = bar_base + 8u * (2 * kMaxStages + 8);
     const uint32_t tmem_slot = bar_base + 8u * (2 * kMaxStages + 9);
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + args.barrier_offset + 8 * (2 * kMaxStages + 9));
+    auto res_full = [&](int box) { return bar_base + 8u * (2 * kMaxStages + 12 + box); };   // four staging boxes
+    auto res_free = [&](int box) { return bar_base + 8u * (2 * kMaxStages + 16 + box); };
 
     const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
     const bool leader = elect_one();
@@ -112,6 +145,7 @@ umma_conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         prefetch_tensormap(&map_wa);
         prefetch_tensormap(&map_wb);
         prefetch_tensormap(&map_out);
+        if (args.has_residual) prefetch_tensormap(&map_res);
     }
     const int chunks = args.k2 / 128;  // 64-channel chunks per epilogue B group and tile
     int my_tiles = 0;
@@ -135,9 +169,14 @@ umma_conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 mbar_init(acc_a_empty(a), 4);
             }
             mbar_init(t_full_bar, 4);
-            mbar_init(t_empty_bar, 1);
+            mbar_init(t_done_bar(0), 1);
+            mbar_init(t_done_bar(1), 1);
+            for (int box = 0; box < 4; ++box) {
+                mbar_init(res_full(box), 1);
+                mbar_init(res_free(box), 1);
+            }
             mbar_init(acc_b_full, 1);
-            mbar_init(acc_b_empty, 8);
+            mbar_init(acc_b_empty, 16);
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             mbar_expect_tx(w_full_bar, static_cast<uint32_t>(args.wa_bytes + args.wb_bytes));
         }
@@ -194,7 +233,7 @@ umma_conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 if (++stage == args.stages) { stage = 0; phase ^= 1; }
             }
         }
-    } else if (warp == 1 || warp == 14) {
+    } else if (warp == 1 || warp == 2) {
         // ---- product issuers ----
         const int me = warp == 1 ? 0 : 1;
         const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
@@ -208,6 +247,8 @@ umma_conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         auto issue_a = [&](int j) {
             const int buffer = j & 1;
             if (ok) ok = mbar_wait_warp(acc_a_empty(buffer), ((j >> 1) & 1) ^ 1, 203);
+            // the lo products land in the columns where the T of tile j - 2 lives until conv_b of that tile has run
+            if (ok && me == 1 && j >= 2) ok = mbar_wait_warp(t_done_bar(buffer), ((j >> 1) & 1) ^ 1, 212);
             tc_fence_after();
             const uint32_t tmem_acc = tmem_u + static_cast<uint32_t>((2 * buffer + me) * kAccAColumns);
             uint32_t accumulate = 0;
@@ -258,17 +299,19 @@ umma_conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             if (leader) {
                 if (ok) {
                     const uint32_t tmem_acc = tmem_u + kAccBColumn0;
+                    const uint32_t t_tmem = tmem_u + static_cast<uint32_t>((2 * (j & 1) + 1) * kAccAColumns);
                     const uint32_t b_lo = smem_desc_lo(wb_base, 16);
+                    // per 32 channels: hi words (2 K steps of 8 columns), then lo words; both against the same filter slices
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        const uint32_t a_lo = smem_desc_lo(t_base + half * (kTileM * 128), 16);
+                    for (int chunk = 0; chunk < kK1 / 32; ++chunk)
 #pragma unroll
-                        for (int k = 0; k < kBlockK / 16; ++k)
-                            umma_bf16(tmem_acc, desc_words(a_lo + ((k * 32) >> 4), smem_desc_hi(1024)), desc_words(b_lo + ((k * 32) >> 4), smem_desc_hi(1024)), idesc_b,
-                                      (half | k) != 0 ? 1u : 0u);
-                    }
+                        for (int part = 0; part < 2; ++part)
+#pragma unroll
+                            for (int kk = 0; kk < 2; ++kk)
+                                umma_bf16_a_tmem(tmem_acc, t_tmem + chunk * 32 + part * 16 + kk * 8, desc_words(b_lo + (((chunk * 2 + kk) * 32) >> 4), smem_desc_hi(1024)), idesc_b,
+                                                 (chunk | part | kk) != 0 ? 1u : 0u);
                 }
-                umma_commit(t_empty_bar);
+                umma_commit(t_done_bar(j & 1));
                 umma_commit(acc_b_full);
             }
         };
@@ -279,201 +322,211 @@ umma_conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 if (me == 0) issue_b(j);
             }
         }
-    } else if (warp >= 2 && warp <= 5) {
-        // ---- epilogue A: conv_a accumulator(s) -> steps -> (hi, lo) bf16 -> the T tile ----
+    } else if (warp >= 3 && warp <= 6) {
+        // ---- epilogue A: conv_a accumulator(s) -> steps -> (hi, lo) bf16 -> the T tile, 32 channels at a time ----
         const int quadrant = warp & 3;
-        const int row = quadrant * 32 + lane;  // GEMM row = TMEM lane; the T tile keeps GEMM row order
         const float* bias_smem = reinterpret_cast<const float*>(generic_base + args.bias_offset);
-        uint8_t* t_hi = generic_base + args.t_offset + row * 128;
-        uint8_t* t_lo = t_hi + kTileM * 128;
         bool ok = true;
         for (int j = 0; j < my_tiles; ++j) {
             const int buffer = j & 1;
             if (ok) ok = mbar_wait(acc_a_full(buffer), (j >> 1) & 1, 207);
             tc_fence_after();
-            float v[kK1];
             const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) + 2 * buffer * kAccAColumns;
-#pragma unroll
+#pragma unroll 1
             for (int chunk = 0; chunk < kK1 / 32; ++chunk) {
-                uint32_t raw[32];
-                tmem_load_32(lane_base + chunk * 32, raw);
-                tmem_load_wait();
-#pragma unroll
-                for (int e = 0; e < 32; ++e) v[chunk * 32 + e] = __uint_as_float(raw[e]);
-            }
-            if (args.split_in) {  // the lo blocks' share of the sum, from the second issuing warp's accumulator
-#pragma unroll
-                for (int chunk = 0; chunk < kK1 / 32; ++chunk) {
+                float v[32];
+                {
                     uint32_t raw[32];
-                    tmem_load_32(lane_base + kAccAColumns + chunk * 32, raw);
-                    tmem_load_wait();
+                    tmem_load_32(lane_base + chunk * 32, raw);
+                    if (args.split_in) {  // the lo blocks' share of the sum, from the second issuing warp's accumulator
+                        uint32_t more[32];
+                        tmem_load_32(lane_base + kAccAColumns + chunk * 32, more);
+                        tmem_load_wait();
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) v[chunk * 32 + e] = __fadd_rn(v[chunk * 32 + e], __uint_as_float(raw[e]));
-                }
-            }
-            // the accumulators are in registers: hand them back before the arithmetic
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_a_empty(buffer));
-            int bias_at = 0;
-            for (int e = 0; e < args.steps_a.count; ++e) {
-                if (args.steps_a.kind[e] == kStepRelu) {
-                    const float lower = args.steps_a.lower[e], upper = args.steps_a.upper[e], slope = args.steps_a.slope[e];
+                        for (int e = 0; e < 32; ++e) v[e] = __fadd_rn(__uint_as_float(raw[e]), __uint_as_float(more[e]));
+                    } else {
+                        tmem_load_wait();
 #pragma unroll
-                    for (int t = 0; t < kK1; ++t) v[t] = relu_fast(v[t], lower, upper, slope);
-                } else {
-                    const float4* p = reinterpret_cast<const float4*>(bias_smem + bias_at);
-                    bias_at += kK1;
-#pragma unroll
-                    for (int q4 = 0; q4 < kK1 / 4; ++q4) {
-                        const float4 q = p[q4];
-                        v[4 * q4] = __fadd_rn(v[4 * q4], q.x);
-                        v[4 * q4 + 1] = __fadd_rn(v[4 * q4 + 1], q.y);
-                        v[4 * q4 + 2] = __fadd_rn(v[4 * q4 + 2], q.z);
-                        v[4 * q4 + 3] = __fadd_rn(v[4 * q4 + 3], q.w);
+                        for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[e]);
                     }
                 }
-            }
-            // the second product of the previous tile must have read the T tile before it is overwritten
-            if (ok) ok = mbar_wait(t_empty_bar, (j & 1) ^ 1, 208);
-#pragma unroll
-            for (int c16 = 0; c16 < 8; ++c16) {
-                uint32_t hi[4], lo[4];
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    const float a = v[8 * c16 + 2 * t], b = v[8 * c16 + 2 * t + 1];
-                    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-                    hi[t] = *reinterpret_cast<uint32_t*>(&h);
-                    __nv_bfloat162 l = __floats2bfloat162_rn(split_remainder(a, hi[t] << 16), split_remainder(b, hi[t] & 0xffff0000u));
-                    lo[t] = *reinterpret_cast<uint32_t*>(&l);
+                if (chunk == kK1 / 32 - 1) {  // the accumulators are in registers: hand them back before the arithmetic
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_a_empty(buffer));
                 }
-                const int at = (c16 ^ (row & 7)) << 4;
-                *reinterpret_cast<uint4*>(t_hi + at) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                *reinterpret_cast<uint4*>(t_lo + at) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                int bias_at = 0;
+                for (int e = 0; e < args.steps_a.count; ++e) {
+                    if (args.steps_a.kind[e] == kStepRelu) {
+                        const float lower = args.steps_a.lower[e], upper = args.steps_a.upper[e], slope = args.steps_a.slope[e];
+#pragma unroll
+                        for (int t = 0; t < 32; ++t) v[t] = relu_step(v[t], lower, upper, slope);
+                    } else {
+                        const float4* p = reinterpret_cast<const float4*>(bias_smem + bias_at + chunk * 32);
+                        bias_at += kK1;
+#pragma unroll
+                        for (int q4 = 0; q4 < 8; ++q4) {
+                            const float4 q = p[q4];
+                            v[4 * q4] = __fadd_rn(v[4 * q4], q.x);
+                            v[4 * q4 + 1] = __fadd_rn(v[4 * q4 + 1], q.y);
+                            v[4 * q4 + 2] = __fadd_rn(v[4 * q4 + 2], q.z);
+                            v[4 * q4 + 3] = __fadd_rn(v[4 * q4 + 3], q.w);
+                        }
+                    }
+                }
+                // (hi, lo) words of these 32 channels over the lo-product columns just read: 16 hi words, then 16 lo words
+                uint32_t words[32];
+                uint32_t not_finite = 0;  // bit 15 / 31 set when a hi half has an all-ones exponent (infinity or NaN)
+#pragma unroll
+                for (int t = 0; t < 16; ++t) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * t], v[2 * t + 1]);
+                    words[t] = *reinterpret_cast<uint32_t*>(&h);
+                    not_finite |= (words[t] & 0x7f807f80u) + 0x00800080u;
+                }
+                if (__any_sync(0xffffffffu, (not_finite & 0x80008000u) != 0)) {
+#pragma unroll
+                    for (int t = 0; t < 16; ++t) {
+                        __nv_bfloat162 l = __floats2bfloat162_rn(split_remainder(v[2 * t], words[t] << 16), split_remainder(v[2 * t + 1], words[t] & 0xffff0000u));
+                        words[16 + t] = *reinterpret_cast<uint32_t*>(&l);
+                    }
+                } else {  // every hi half is finite: the remainders need no guard
+#pragma unroll
+                    for (int t = 0; t < 16; ++t) {
+                        __nv_bfloat162 l = __floats2bfloat162_rn(v[2 * t] - __uint_as_float(words[t] << 16), v[2 * t + 1] - __uint_as_float(words[t] & 0xffff0000u));
+                        words[16 + t] = *reinterpret_cast<uint32_t*>(&l);
+                    }
+                }
+                tmem_store_32(lane_base + kAccAColumns + chunk * 32, words);
             }
-            fence_async_shared();  // generic-proxy stores -> visible to the tensor core's reads
+            tmem_store_wait();
+            tc_fence_before();  // tensor-memory stores -> ordered before the product that the arrival below releases
             __syncwarp();
             if (lane == 0) mbar_arrive(t_full_bar);
         }
-    } else if (warp >= 6 && warp <= 13) {
+    } else if (warp >= 7 && warp <= 22) {
         // ---- epilogue B: conv_b accumulator -> steps -> bf16 -> staging box -> TMA store ----
-        const int group = (warp - 6) >> 2;
-        const int member = threadIdx.x - (6 + 4 * group) * 32;  // 0..127 inside the group
+        const int group = (warp - 7) >> 3;
+        const int member = threadIdx.x - (7 + 8 * group) * 32;  // 0..255 inside the group
+        const int half = ((warp - 7) >> 2) & 1;                 // which 32 of a chunk's 64 columns this warp owns
         const int quadrant = warp & 3;
         const int gemm_row = quadrant * 32 + lane;
         const int line = gemm_row / args.pitch, column = gemm_row - line * args.pitch;
         const bool row_is_output = column < args.out_q && line < args.rows_per_tile;
         const int row = row_is_output ? line * args.out_q + column : 0;  // rows compacted for the store
         const bool store_thread = member == 0;
+        const int barrier_id = 1 + group;
+        auto group_barrier = [&] { asm volatile("bar.sync %0, 256;" ::"r"(barrier_id) : "memory"); };
         const float* bias_smem = reinterpret_cast<const float*>(generic_base + args.bias_offset);
         int bias_a_floats = 0;
         for (int e = 0; e < args.steps_a.count; ++e) bias_a_floats += args.steps_a.kind[e] == kStepBias ? kK1 : 0;
-        uint8_t* box = generic_base + args.stage_offset + group * args.box_bytes;
-        uint8_t* row_smem = box + row * 128;
-        const int pieces = args.box_rows * 8;  // 16-byte pieces of one residual box
-        // Residual pieces of the chunk after the one being worked on, fetched with coalesced loads (eight consecutive
-        // threads read one 128-byte row) and parked in registers until the box is free to take them.
-        uint4 parked[kMaxBoxPieces];
-        auto fetch_residual = [&](int tile, int c) {
-            int image, h0, out_row0;
-            tile_origin(tile, image, h0, out_row0);
-            const uint8_t* source = static_cast<const uint8_t*>(args.residual) + (static_cast<int64_t>(out_row0) * args.k2 + group * (args.k2 / 2) + c * 64) * 2;
-#pragma unroll
-            for (int q = 0; q < kMaxBoxPieces; ++q) {
-                const int piece = q * 128 + member;
-                if (piece < pieces) parked[q] = __ldg(reinterpret_cast<const uint4*>(source + static_cast<int64_t>(piece >> 3) * args.k2 * 2 + (piece & 7) * 16));
-            }
-        };
-        if (args.has_residual && my_tiles > 0) fetch_residual(blockIdx.x, 0);
+        int image, h0, out_row0, next_row0 = 0;
+        if (my_tiles > 0) tile_origin(blockIdx.x, image, h0, next_row0);
         bool ok = true;
+        int n = 0;  // chunks handled: chunk n uses box n & 1 of the group
         for (int j = 0, tile = blockIdx.x; j < my_tiles; ++j, tile += gridDim.x) {
-            int image, h0, out_row0;
-            tile_origin(tile, image, h0, out_row0);
-            for (int c = 0; c < chunks; ++c) {
+            out_row0 = next_row0;
+            if (j + 1 < my_tiles) tile_origin(tile + gridDim.x, image, h0, next_row0);
+            for (int c = 0; c < chunks; ++c, ++n) {
                 const int col0 = group * (args.k2 / 2) + c * 64;
-                // the previous chunk's store has read the box: it can take this chunk's residual, then its result
-                if (store_thread) tma_store_wait_read<0>();
-                epilogue_barrier(1 + group);
-                if (args.has_residual) {
-#pragma unroll
-                    for (int q = 0; q < kMaxBoxPieces; ++q) {
-                        const int piece = q * 128 + member;
-                        if (piece < pieces) *reinterpret_cast<uint4*>(box + (piece >> 3) * 128 + (((piece & 7) ^ ((piece >> 3) & 7)) << 4)) = parked[q];
-                    }
-                    // next chunk's residual on its way while this one is worked on
-                    if (c + 1 < chunks) fetch_residual(tile, c + 1);
-                    else if (j + 1 < my_tiles) fetch_residual(tile + gridDim.x, 0);
-                    epilogue_barrier(1 + group);
-                }
+                const int box_index = 2 * group + (n & 1);
+                uint8_t* box = generic_base + args.stage_offset + box_index * args.box_bytes;
+                uint8_t* row_smem = box + row * 128;
+                // (this box's previous store, two chunks back, has been read: see the end of the previous chunk; with a
+                // residual operand the loader refilled it after that and the wait below sees its bytes arrive)
                 if (c == 0) {
                     if (ok) ok = mbar_wait(acc_b_full, j & 1, 209);
                     tc_fence_after();
                 }
-                const bool healthy = ok && g_device_status == 0;
-#pragma unroll 1
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t raw[32];
-                    tmem_load_32(tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) + kAccBColumn0 + col0 + half * 32, raw);
-                    tmem_load_wait();
-                    if (c == chunks - 1 && half == 1) {  // this group's columns have all left tensor memory
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(acc_b_empty);
-                    }
-                    float v[32];
+                if (args.has_residual && ok) ok = mbar_wait(res_full(box_index), (n >> 1) & 1, 210);
+                const bool healthy = ok;
+                uint32_t raw[32];
+                tmem_load_32(tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) + kAccBColumn0 + col0 + half * 32, raw);
+                tmem_load_wait();
+                if (c == chunks - 1) {  // this warp's columns have all left tensor memory
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_b_empty);
+                }
+                float v[32];
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[e]);
-                    int bias_at = bias_a_floats;
-                    for (int e = 0; e < args.steps_b.count; ++e) {
-                        const int kind = args.steps_b.kind[e];
-                        if (kind == kStepRelu) {
-                            const float lower = args.steps_b.lower[e], upper = args.steps_b.upper[e], slope = args.steps_b.slope[e];
+                for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[e]);
+                int bias_at = bias_a_floats;
+                for (int e = 0; e < args.steps_b.count; ++e) {
+                    const int kind = args.steps_b.kind[e];
+                    if (kind == kStepRelu) {
+                        const float lower = args.steps_b.lower[e], upper = args.steps_b.upper[e], slope = args.steps_b.slope[e];
 #pragma unroll
-                            for (int t = 0; t < 32; ++t) v[t] = relu_fast(v[t], lower, upper, slope);
-                        } else if (kind == kStepBias) {
-                            const float4* p = reinterpret_cast<const float4*>(bias_smem + bias_at + col0 + half * 32);
-                            bias_at += args.k2;
+                        for (int t = 0; t < 32; ++t) v[t] = relu_step(v[t], lower, upper, slope);
+                    } else if (kind == kStepBias) {
+                        const float4* p = reinterpret_cast<const float4*>(bias_smem + bias_at + col0 + half * 32);
+                        bias_at += args.k2;
 #pragma unroll
-                            for (int q4 = 0; q4 < 8; ++q4) {
-                                const float4 q = p[q4];
-                                v[4 * q4] = __fadd_rn(v[4 * q4], q.x);
-                                v[4 * q4 + 1] = __fadd_rn(v[4 * q4 + 1], q.y);
-                                v[4 * q4 + 2] = __fadd_rn(v[4 * q4 + 2], q.z);
-                                v[4 * q4 + 3] = __fadd_rn(v[4 * q4 + 3], q.w);
-                            }
-                        } else {  // the residual box staged above
+                        for (int q4 = 0; q4 < 8; ++q4) {
+                            const float4 q = p[q4];
+                            v[4 * q4] = __fadd_rn(v[4 * q4], q.x);
+                            v[4 * q4 + 1] = __fadd_rn(v[4 * q4 + 1], q.y);
+                            v[4 * q4 + 2] = __fadd_rn(v[4 * q4 + 2], q.z);
+                            v[4 * q4 + 3] = __fadd_rn(v[4 * q4 + 3], q.w);
+                        }
+                    } else {  // the residual box staged above
 #pragma unroll
-                            for (int c16 = 0; c16 < 4; ++c16) {
-                                const uint4 q = *reinterpret_cast<const uint4*>(row_smem + (((half * 4 + c16) ^ (row & 7)) << 4));
-                                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+                        for (int c16 = 0; c16 < 4; ++c16) {
+                            const uint4 q = *reinterpret_cast<const uint4*>(row_smem + (((half * 4 + c16) ^ (row & 7)) << 4));
+                            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-                                for (int t = 0; t < 4; ++t) {
-                                    v[8 * c16 + 2 * t] = __fadd_rn(v[8 * c16 + 2 * t], __uint_as_float(w[t] << 16));
-                                    v[8 * c16 + 2 * t + 1] = __fadd_rn(v[8 * c16 + 2 * t + 1], __uint_as_float(w[t] & 0xffff0000u));
-                                }
+                            for (int t = 0; t < 4; ++t) {
+                                v[8 * c16 + 2 * t] = __fadd_rn(v[8 * c16 + 2 * t], __uint_as_float(w[t] << 16));
+                                v[8 * c16 + 2 * t + 1] = __fadd_rn(v[8 * c16 + 2 * t + 1], __uint_as_float(w[t] & 0xffff0000u));
                             }
                         }
-                    }
-#pragma unroll
-                    for (int c16 = 0; c16 < 4; ++c16) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int t = 0; t < 4; ++t) {
-                            __nv_bfloat162 pair = __floats2bfloat162_rn(v[8 * c16 + 2 * t], v[8 * c16 + 2 * t + 1]);
-                            w[t] = *reinterpret_cast<uint32_t*>(&pair);
-                        }
-                        if (row_is_output) *reinterpret_cast<uint4*>(row_smem + (((half * 4 + c16) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
+#pragma unroll
+                for (int c16 = 0; c16 < 4; ++c16) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        __nv_bfloat162 pair = __floats2bfloat162_rn(v[8 * c16 + 2 * t], v[8 * c16 + 2 * t + 1]);
+                        w[t] = *reinterpret_cast<uint32_t*>(&pair);
+                    }
+                    if (row_is_output) *reinterpret_cast<uint4*>(row_smem + (((half * 4 + c16) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
                 fence_async_shared();
-                epilogue_barrier(1 + group);
+                // The other box of the group is written next (by the residual loader, or by this group's next chunk): its
+                // last store (the previous chunk's) must have read it first.
                 if (store_thread) {
-                    if (healthy) tma_store_2d(&map_out, stage_base + group * args.box_bytes, col0, out_row0);
+                    tma_store_wait_read<0>();
+                    if (args.has_residual && n >= 1) mbar_arrive(res_free(box_index ^ 1));
+                }
+                group_barrier();
+                if (store_thread) {
+                    if (healthy) tma_store_2d(&map_out, stage_base + box_index * args.box_bytes, col0, out_row0);
                     tma_store_commit();
                 }
             }
         }
         if (store_thread) tma_store_wait_all();
+    }
+
+    if (warp == 23 && args.has_residual) {
+        // ---- residual loader: chunk n of group g goes to box 2 g + (n & 1), once the store of chunk n - 2 has been read ----
+        bool ok = true;
+        int n = 0;
+        for (int tile = blockIdx.x; tile < args.total_tiles && ok; tile += gridDim.x) {
+            int image, h0, out_row0;
+            tile_origin(tile, image, h0, out_row0);
+            for (int c = 0; c < chunks && ok; ++c, ++n)
+                for (int g = 0; g < 2; ++g) {
+                    const int box = 2 * g + (n & 1);
+                    // the box's (n >> 1)-th use: free once its previous use, chunk n - 2, has been stored and read
+                    ok = mbar_wait_warp(res_free(box), ((n >> 1) & 1) ^ 1, 211);
+                    if (!ok) break;
+                    if (leader) {
+                        mbar_expect_tx(res_full(box), static_cast<uint32_t>(args.box_rows) * 128u);
+                        tma_load_2d(stage_base + box * args.box_bytes, &map_res, g * (args.k2 / 2) + c * 64, out_row0, res_full(box));
+                    }
+                }
+        }
     }
 
     tc_fence_before();
@@ -581,13 +634,13 @@ bool pair_form(const dfgpu_conv_params& first, const dfgpu_conv_params& second, 
     f.wa_bytes = static_cast<int>(kK1 * f.a.R * f.a.S * f.a.C * 2);
     f.wb_bytes = static_cast<int>(f.k2 * kK1 * 2);
     f.bias_bytes = round_up_1k((f.bias_a * kK1 + f.bias_b * f.k2) * 4 + 256);  // staged bias vectors, then the barriers
-    const int fixed = round_up_1k(f.wa_bytes) + round_up_1k(f.wb_bytes) + 2 * kTileM * 128 + 2 * f.box_bytes + f.bias_bytes + 1024;
+    const int fixed = round_up_1k(f.wa_bytes) + round_up_1k(f.wb_bytes) + 4 * f.box_bytes + f.bias_bytes + 1024;
     f.stages = (kPairSmemBudget - fixed) / f.slot_bytes;
     if (f.stages > kMaxStages) f.stages = kMaxStages;
     // the last taps read past the window's rows (into rows no stored GEMM row uses): that must stay inside the allocation,
     // i.e. inside what follows the last slot
     const int64_t rows_read = kTileM + (f.a.R - 1) * pitch + f.a.S - 1;
-    if (rows_read * 128 - f.slot_bytes > 2 * f.box_bytes + f.bias_bytes) return false;
+    if (rows_read * 128 - f.slot_bytes > 4 * f.box_bytes + f.bias_bytes) return false;
     return f.stages >= 2;
 }
 
@@ -636,21 +689,18 @@ int launch_conv_pair_umma(const dfgpu_conv_params& first, const dfgpu_conv_param
         for (int e = 0; e < list->count; ++e)
             if (list->kind[e] != kStepRelu && (!list->data[e] || !aligned16(list->data[e])))
                 return fail(kInvalidArgument, "CONV_FPROP pair: ADD operands must be non-null and 16-byte aligned");
-    for (int e = 0; e < args.steps_b.count; ++e)
-        if (args.steps_b.kind[e] == kStepFull) args.residual = args.steps_b.data[e];
     args.wa_bytes = f.wa_bytes;
     args.wb_bytes = f.wb_bytes;
     args.wa_offset = 0;
     args.wb_offset = round_up_1k(f.wa_bytes);
-    args.t_offset = args.wb_offset + round_up_1k(f.wb_bytes);
-    args.ring_offset = args.t_offset + 2 * kTileM * 128;
+    args.ring_offset = args.wb_offset + round_up_1k(f.wb_bytes);
     args.stage_offset = args.ring_offset + f.stages * f.slot_bytes;  // right behind the ring: the taps' reads past the last slot land here
-    args.bias_offset = args.stage_offset + 2 * f.box_bytes;
+    args.bias_offset = args.stage_offset + 4 * f.box_bytes;
     args.barrier_offset = args.bias_offset + f.bias_bytes - 256;
     const int dynamic = args.bias_offset + f.bias_bytes + 1024;
     if (dynamic > kPairSmemBudget) return fail(kUnsupported, "CONV_FPROP pair: shared-memory layout does not fit");
 
-    CUtensorMap map_x, map_wa, map_wb, map_out;
+    CUtensorMap map_x, map_wa, map_wb, map_out, map_res;
     int status;
     {
         uint64_t dims[4] = {static_cast<uint64_t>(Ca), static_cast<uint64_t>(a.W), static_cast<uint64_t>(a.H), static_cast<uint64_t>(a.N)};
@@ -675,6 +725,10 @@ int launch_conv_pair_umma(const dfgpu_conv_params& first, const dfgpu_conv_param
         uint64_t strides[1] = {static_cast<uint64_t>(f.k2) * 2};
         uint32_t box[2] = {64, static_cast<uint32_t>(f.box_rows)};
         if ((status = make_map(&map_out, tensors[3], 2, dims, strides, box, "CONV_FPROP pair Y"))) return status;
+        const void* residual = tensors[3];
+        for (int e = 0; e < args.steps_b.count; ++e)
+            if (args.steps_b.kind[e] == kStepFull) residual = args.steps_b.data[e];
+        if ((status = make_map(&map_res, residual, 2, dims, strides, box, "CONV_FPROP pair residual"))) return status;
     }
     static bool configured = false;
     if (!configured) {
@@ -689,7 +743,7 @@ int launch_conv_pair_umma(const dfgpu_conv_params& first, const dfgpu_conv_param
         const int rounds = (args.total_tiles + sms - 1) / sms;
         grid = (args.total_tiles + rounds - 1) / rounds;
     }
-    cudaError_t launched = launch_chained(umma_conv_pair_kernel, dim3(grid), dim3(kPairThreads), dynamic, stream, map_x, map_wa, map_wb, map_out, args);
+    cudaError_t launched = launch_chained(umma_conv_pair_kernel, dim3(grid), dim3(kPairThreads), dynamic, stream, map_x, map_wa, map_wb, map_out, map_res, args);
     if (launched != cudaSuccess) return fail(kExecutionFailed, "CONV_FPROP pair: launch failed: %s", cudaGetErrorString(launched));
     return check_launch("CONV_FPROP pair");
 }
