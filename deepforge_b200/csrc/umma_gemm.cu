@@ -302,17 +302,6 @@ struct PersistentArgs {
     int32_t epi_per_group;     // staging buffers per epilogue group: 2, or 1 when a buffer holds hi and lo boxes
 };
 
-// Cycle stamps of the first CTA's roles (loader, issuing lane, two epilogue groups), for tuning builds only.
-#ifdef DFGPU_CONV_TRACE
-__device__ long long g_conv_trace[4][128][4];
-__device__ unsigned long long g_conv_span[160][8];  // per CTA wall-clock ns: entry, after the prologue barrier, exit, loader prefetch done, tensor memory allocated, bias staged
-#define CONV_TRACE(role, n, k) do { if (blockIdx.x == 0 && (n) < 128) g_conv_trace[role][n][k] = clock64(); } while (0)
-#define CONV_SPAN_AT(thread, k) do { if (threadIdx.x == (thread) && blockIdx.x < 160) g_conv_span[blockIdx.x][k] = global_timer_ns(); } while (0)
-#else
-#define CONV_TRACE(role, n, k) do {} while (0)
-#define CONV_SPAN_AT(thread, k) do {} while (0)
-#endif
-
 // x - hi for the lo half of a split (hi, lo) pair; 0 when hi is not finite (an infinite or NaN value lives in hi alone,
 // so that hi + lo reproduces it instead of inf - inf). x - hi is exact: hi holds the leading 8 significant bits of x.
 __device__ __forceinline__ float split_remainder(float x, uint32_t hi_bits) {
@@ -349,7 +338,6 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 
     const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
     chain_release();  // the next kernel of the plan may start taking SMs as this one's CTAs leave
-    CONV_SPAN_AT(0, 0);
     if (threadIdx.x == 0) {
         prefetch_tensormap(&map_a);
         prefetch_tensormap(&map_b);
@@ -412,10 +400,8 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 ld.open = true;
             }
             if (bounded && ld.filled >= static_cast<uint32_t>(STAGES)) return;
-            if (leader) CONV_TRACE(0, ld.filled, 0);
             ld.ok = mbar_wait_warp(empty_bar(ld.stage), ld.phase, 112);
             if (!ld.ok) return;
-            if (leader) CONV_TRACE(0, ld.filled, 1);
             if (pargs.halo) {
                 // one slot = the rows of filter row tap_r for channel block cblk: box (64 ch, pitch, rows, 1)
                 if (leader) {
@@ -438,7 +424,6 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 }
             }
             }
-            if (leader) CONV_TRACE(0, ld.filled, 2);
             ++ld.filled;
             if (++ld.stage == STAGES) { ld.stage = 0; ld.phase ^= 1; }
             ld.kb0 += pargs.halo ? args.filter_s : G;  // K slices this slot covers
@@ -484,13 +469,11 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         ld.phase = 1;
         ld.ok = true;
         run_loader(true);
-        CONV_SPAN_AT(0, 3);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, kAccumulators * BN);
         tmem_relinquish();
         tc_fence_before();
-        CONV_SPAN_AT(32, 4);
     }
     if (warp != 0 && !pargs.early_static) chain_wait();  // warp 0 waited before its first load
     {
@@ -504,12 +487,10 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             ++slot;
         }
     }
-    CONV_SPAN_AT(64, 5);
     if (warp != 0 && pargs.early_static) chain_wait();  // the bias vectors above are static operands
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
-    CONV_SPAN_AT(0, 1);
 
     if (warp == 0) {
         run_loader(false);
@@ -537,10 +518,8 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const uint32_t tmem_acc = tmem_u + static_cast<uint32_t>(acc * BN);
             int halo_r = 0, halo_c = 0;  // filter row and channel block of the next slot (halo form)
             for (int kb0 = 0; kb0 < args.k_blocks && ok; kb0 += (pargs.halo ? args.filter_s : G), ++it) {
-                if (leader && me == 0) CONV_TRACE(1, it, 0);
                 ok = mbar_wait_warp(full_bar(stage), phase, 114);
                 if (!ok) break;  // (the slot was filled by TMA: no tcgen05 fence needed before the products read it)
-                if (leader && me == 0) CONV_TRACE(1, it, 1);
                 const uint32_t a_lo = smem_desc_lo(ring_base + stage * pargs.slot_bytes, 16);
                 if (pargs.halo) {
                     // tap s of this filter row reads the slot from row s on: only the start address moves, by s * 128 bytes.
@@ -583,7 +562,6 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     }
                 }
                 if (leader) umma_commit(empty_bar(stage));
-                if (leader && me == 0) CONV_TRACE(1, it, 2);
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
             if (leader) umma_commit(acc_full_bar(acc));  // arrives even after a failed wait so the epilogue never hangs
@@ -618,9 +596,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 tma_store_wait_read<0>();
                 mbar_arrive(res_empty_bar(group * 2 + ((j - 1) & 1)));
             }
-            if (store_thread) CONV_TRACE(2 + group, j, 0);
             if (ok) ok = mbar_wait(acc_full_bar(acc), (i / kAccumulators) & 1, 115);
-            if (store_thread) CONV_TRACE(2 + group, j, 1);
             if (HAS_RES) {
                 if (ok) ok = mbar_wait(res_full_bar(buf), (j >> 1) & 1, 116);
             } else {
@@ -705,7 +681,6 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 }
             }
             // release the accumulator, then publish the finished tile
-            if (store_thread) CONV_TRACE(2 + group, j, 2);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty_bar(acc));
@@ -723,7 +698,6 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     }
                 }
                 tma_store_commit();
-                CONV_TRACE(2 + group, j, 3);
             }
         }
         if (store_thread) tma_store_wait_all();
@@ -731,7 +705,6 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 
     tc_fence_before();
     __syncthreads();
-    CONV_SPAN_AT(0, 2);
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kAccumulators * BN);

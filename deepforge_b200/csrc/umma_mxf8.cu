@@ -413,16 +413,6 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // back in a microbenchmark and ~300 here), so MATMUL AUTO keeps the one-SM form and this one is chosen by kernel id only.
 constexpr int kPairStages = 6;
 
-// Cycle totals of the first cluster's roles, for tuning builds only.
-#ifdef DFGPU_MX_TRACE
-__device__ long long g_mx_trace[2][8];
-#define MX_ADD(slot, value) do { if (blockIdx.x < 2 && leader) g_mx_trace[blockIdx.x][slot] += (value); } while (0)
-#define MX_CLOCK() clock64()
-#else
-#define MX_ADD(slot, value) do {} while (0)
-#define MX_CLOCK() 0ll
-#endif
-
 struct MxPairSmem {
     static constexpr int kBBytes = 128 * kBlockK;                 // this CTA's 128 columns of B
     static constexpr int kSfaOffset = kABytes + kBBytes;          // 512 B: own 128 rows
@@ -547,9 +537,7 @@ umma_mxf8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
             const int row0 = m_tile * 256 + static_cast<int>(rank) * 128, col0 = n_tile * 256 + static_cast<int>(rank) * 128;
             for (int kb = 0; kb < args.k_blocks; ++kb) {
-                const long long t_wait = MX_CLOCK();
                 ok = mbar_wait_warp(empty_bar(stage), phase, 411);
-                MX_ADD(0, MX_CLOCK() - t_wait);
                 if (!ok) break;
                 const uint32_t a_dst = smem_base + stage * L::kStageBytes;
                 const uint32_t b_dst = a_dst + kABytes;
@@ -574,16 +562,11 @@ umma_mxf8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             bool ok = true;
             int local = 0;
             for (int tile = pair; tile < total_tiles; tile += pairs, ++local) {
-                const long long t_acc = MX_CLOCK();
                 if (ok) ok = mbar_wait_warp_cluster(acc_empty_bar, (local & 1) ^ 1, 412);
-                MX_ADD(1, MX_CLOCK() - t_acc);
                 tc_fence_after();
                 for (int kb = 0; kb < args.k_blocks && ok; ++kb) {
-                    const long long t_full = MX_CLOCK();
                     ok = mbar_wait_warp_cluster(full_bar(stage), phase, 413);
-                    MX_ADD(2, MX_CLOCK() - t_full);
                     if (!ok) break;
-                    const long long t_issue = MX_CLOCK();
                     tc_fence_after();
                     const uint32_t a_src = smem_base + stage * L::kStageBytes;
                     const uint32_t b_src = a_src + kABytes;
@@ -592,11 +575,9 @@ umma_mxf8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     const uint32_t b_lo = args.b_mn_major ? smem_desc_lo(b_src, kBlockK * 128) : smem_desc_lo(b_src, 16);
                     const uint32_t b_step = args.b_mn_major ? (4096u >> 4) : (32u >> 4);
                     if (leader) {
-#ifndef DFGPU_MX_SKIP_SCALE_COPY
                         tmem_copy_scales_pair(sf_tmem, scale_desc(a_src + L::kSfaOffset));
                         tmem_copy_scales_pair(sf_tmem + 4, scale_desc(a_src + L::kSfbOffset));
                         tmem_copy_scales_pair(sf_tmem + 8, scale_desc(a_src + L::kSfbOffset + 512));
-#endif
 #pragma unroll
                         for (int j = 0; j < kBlockK / 32; ++j) {
                             const uint32_t idesc = idesc_base | (static_cast<uint32_t>(j) << 29) | (static_cast<uint32_t>(j) << 4);
@@ -607,7 +588,6 @@ umma_mxf8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                         umma_commit_pair(empty_bar(stage));
                         umma_commit_pair(peer_address(empty_bar(stage), 1));
                     }
-                    MX_ADD(3, MX_CLOCK() - t_issue);
                     if (++stage == kPairStages) { stage = 0; phase ^= 1; }
                 }
                 if (leader) {  // arrives even after a failed wait so that neither epilogue hangs
@@ -625,16 +605,12 @@ umma_mxf8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         int local = 0;
         for (int tile = pair; tile < total_tiles; tile += pairs, ++local) {
             const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
-            const long long t_epi = MX_CLOCK();
             if (ok) ok = mbar_wait(acc_full_bar, local & 1, 414);
-            if (warp == 2) MX_ADD(5, MX_CLOCK() - t_epi);
-            const long long t_store = MX_CLOCK();
             tc_fence_after();
             const bool healthy = ok && g_device_status == 0;
             const int64_t out_row = static_cast<int64_t>(m_tile) * 256 + rank * 128 + row;
             MxScalars none{};
             mx_store_row(args, tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16), out_row, static_cast<int64_t>(n_tile) * 256, 256, healthy, none);
-            if (warp == 2) MX_ADD(6, MX_CLOCK() - t_store);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
@@ -664,9 +640,7 @@ umma_mxf8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                         const uint32_t b0 = __ldg(p), b1 = __ldg(p + args.sfb_ld), b2 = __ldg(p + 2 * args.sfb_ld), b3 = __ldg(p + 3 * args.sfb_ld);
                         b_words[c][g] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
                     }
-                const long long t_sf = MX_CLOCK();
                 ok = mbar_wait_warp(empty_bar(slot), phase, 415);
-                if (q == 0) MX_ADD(4, MX_CLOCK() - t_sf);
                 if (!ok) break;
                 uint8_t* stage_base = generic_base + slot * L::kStageBytes;
                 *reinterpret_cast<uint4*>(stage_base + L::kSfaOffset + lane * 16) = make_uint4(a_words[0], a_words[1], a_words[2], a_words[3]);

@@ -328,19 +328,8 @@ sdpa_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 // products of one CTA in issue order, so S_X(j+1) may be issued right behind the product that reads P_X(j).
 // Under a causal mask tile A (the earlier rows) has one key tile fewer than tile B.
 
-// Cycle stamps of the first CTA's three roles (softmax A, softmax B, issuing lane), for tuning builds only.
-#ifdef DFGPU_SDPA_TRACE
-__device__ long long g_sdpa_trace[3][64][10];
-#define SDPA_TRACE(role, j, k) do { if (blockIdx.x == 0 && (j) < 64) g_sdpa_trace[role][j][k] = clock64(); } while (0)
-#else
-#define SDPA_TRACE(role, j, k) do {} while (0)
-#endif
-
 constexpr int kPairSlots = 4;
-#ifndef DFGPU_SDPA_POLY_EVERY
-#define DFGPU_SDPA_POLY_EVERY 4
-#endif
-constexpr int kPolyEvery = DFGPU_SDPA_POLY_EVERY;  // one pair of exponentials in kPolyEvery goes to the FMA pipe (0: none)
+constexpr int kPolyEvery = 4;  // one pair of exponentials in kPolyEvery goes to the FMA pipe (0: none)
 constexpr int kPairThreads = 608;  // 2 x 8 softmax warps (two threads per query row), loader, issuer and output-store warps
 
 struct PairSmem {
@@ -635,8 +624,6 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         uint32_t phase = 0;
         uint32_t n = 0;       // items started
         uint32_t p_count[2] = {0, 0};  // probability tiles consumed per query tile (parity of p_full)
-        uint32_t stamp_j = 0;
-        (void)stamp_j;
         // (no tcgen05 fence after a slot wait: the slot was filled by TMA, not by tensor-memory traffic of other threads)
         auto wait_slot = [&](int code) {
             if (ok) ok = mbar_wait_warp(kv_full(slot), phase, code);
@@ -700,12 +687,10 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             commit(s_full(1));
             commit(kv_empty(k0_slot));
             if (tiles_b == 1) commit(q_empty(1));
-            for (int j = 0; j < tiles_b; ++j, ++stamp_j) {
-                if (leader) SDPA_TRACE(2, stamp_j, 0);
+            for (int j = 0; j < tiles_b; ++j) {
                 wait_slot(226);
                 const int v_slot = slot;
                 next_slot();
-                if (leader) SDPA_TRACE(2, stamp_j, 1);
                 if (j < tiles_a) {
                     product(0, j, v_slot);
                     if (j == tiles_a - 1) commit(o_full(0));
@@ -722,7 +707,6 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         if (next_tiles_a == 1) commit(q_empty(0));
                     }
                 }
-                if (leader) SDPA_TRACE(2, stamp_j, 2);
                 const bool more = j + 1 < tiles_b;
                 int k_slot = 0;
                 if (more) {
@@ -730,15 +714,12 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     k_slot = slot;
                     next_slot();
                 }
-                if (leader) SDPA_TRACE(2, stamp_j, 3);
                 if (j + 1 < tiles_a) {
                     scores(0, k_slot);
                     commit(s_full(0));
                     if (j + 2 == tiles_a) commit(q_empty(0));  // the item's last read of Q_A
                 }
-                if (leader) SDPA_TRACE(2, stamp_j, 4);
                 product(1, j, v_slot);
-                if (leader) SDPA_TRACE(2, stamp_j, 5);
                 commit(kv_empty(v_slot));
                 if (more) {
                     scores(1, k_slot);
@@ -746,7 +727,6 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     commit(kv_empty(k_slot));
                     if (j + 2 == tiles_b) commit(q_empty(1));  // the item's last read of Q_B
                 }
-                if (leader) SDPA_TRACE(2, stamp_j, 6);
             }
             commit(o_full(1));
             ++n;
@@ -806,10 +786,8 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         float l_sum = 0.0f;       // this thread's half of the row sum
         float raw_max = -INFINITY;  // exact largest dot product among this thread's keys (for the Max / Sum_exp outputs)
         for (int j = 0; j < my_tiles; ++j, ++s_count) {
-            if (stamp) SDPA_TRACE(x, s_count, 0);
             if (ok) ok = mbar_wait(s_full(x), s_count & 1, 228 + x);
             tc_fence_after();
-            if (stamp) SDPA_TRACE(x, s_count, 1);
             // One pass over this thread's 64 scores, 16 at a time with the next load in flight: each chunk gives its part
             // of the half-row maximum and, from the second key tile on, its probabilities against the reference maximum
             // of the earlier tiles. Only a tile that raises the reference (rare after the first) is read a second time.
@@ -838,7 +816,6 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 }
             }
             raw_max = fmaxf(raw_max, mine);
-            if (stamp) SDPA_TRACE(x, s_count, 2);
             // Trade the half-row maxima with the warp that owns the other 64 keys of these rows, as bf16 rounded towards
             // +inf: any reference not below the true maximum by more than the threshold serves, and both threads must
             // arrive at the same value, so each uses the rounded form of its own half too. (One buffer suffices: the next
@@ -874,7 +851,6 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     }
                 }
             }
-            if (stamp) SDPA_TRACE(x, s_count, 3);
             if (again) {
                 // the scores are still in place (no probabilities stored yet): form them against the new reference
                 bias2 = pack2(-m_ref, -m_ref);
@@ -899,17 +875,14 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 unpack2(add2(sums[0], sums[1]), lo, hi);
                 l_sum += lo + hi;
             }
-            if (stamp) SDPA_TRACE(x, s_count, 4);
             tmem_store_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full(x));
-            if (stamp) SDPA_TRACE(x, s_count, 5);
         }
         // last product done -> read O out of tensor memory (which frees it for the next item), normalise, store
         if (ok) ok = mbar_wait(o_full(x), n & 1, 230 + x);
         tc_fence_after();
-        if (stamp) SDPA_TRACE(x, s_count - 1, 6);
         // row sum = this thread's half + the other thread's: two hand-overs through one f32 word per row
         if (half == 1) sum_exchange[lane] = l_sum;
         asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
@@ -937,7 +910,6 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
         // the hand-over words double as the next item's maxima: every read above must precede those writes
         asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
-        if (stamp) SDPA_TRACE(x, s_count - 1, 7);
         const float inverse = total > 0.0f ? 1.0f / total : 0.0f;
         // the staging tile serves the query tiles in turn: A, B, the next item's A, ...
         {
@@ -970,7 +942,6 @@ sdpa_umma_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         fence_async_shared();
         __syncwarp();
         if (lane == 0) mbar_arrive(staged(x));
-        if (stamp) SDPA_TRACE(x, s_count - 1, 8);
         if (args.stats != nullptr && ok && half == 0)
             args.stats[item.batch * args.stats_batch_stride + item.head * args.stats_head_stride + static_cast<int64_t>(q_index) * args.stats_row_stride] =
                 total > 0.0f ? 0.6931471805599453f * (m_ref + log2f(total)) : -INFINITY;

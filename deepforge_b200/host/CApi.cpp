@@ -40,6 +40,101 @@ extern "C" int df_parse(const uint8_t* document, size_t size, int format, int64_
     return report(status);
 }
 
+namespace {
+// Canonical text of a parsed graph. A convolution node the reference's importer turns into its ConvFpropDesc
+// (lib/Import/SerializedGraphImporter.cpp:1437-1461: FLOAT compute, ports X, W, Y by UID, two-element integer
+// padding / stride / dilation, cross-correlation) is written through the fields that description keeps; every other
+// node with all its ports and attributes.
+std::string real_text(double value) {
+    char text[40];
+    std::snprintf(text, sizeof(text), "%.17g", value);
+    return text;
+}
+std::string attribute_text(import::AttributeValue const& value) {
+    return std::visit([](auto const& v) -> std::string {
+        using T = std::decay_t<decltype(v)>;
+        if constexpr (std::is_same_v<T, std::monostate>) return "null";
+        else if constexpr (std::is_same_v<T, bool>) return v ? "true" : "false";
+        else if constexpr (std::is_same_v<T, std::int64_t>) return std::to_string(v);
+        else if constexpr (std::is_same_v<T, double>) return real_text(v);
+        else if constexpr (std::is_same_v<T, std::string>) return "\"" + v + "\"";
+        else {
+            std::string out = "[";
+            for (std::size_t i = 0; i < v.size(); ++i) {
+                if (i) out += ",";
+                if constexpr (std::is_same_v<T, std::vector<std::int64_t>>) out += std::to_string(v[i]);
+                else out += real_text(v[i]);
+            }
+            return out + "]";
+        }
+    }, value);
+}
+std::string list_text(std::vector<std::int64_t> const& values) {
+    std::string out = "[";
+    for (std::size_t i = 0; i < values.size(); ++i) out += (i ? "," : "") + std::to_string(values[i]);
+    return out + "]";
+}
+std::string dump_graph(import::SerializedGraph const& graph) {
+    std::string out;
+    auto type_or_null = [](std::optional<import::DataType> const& t) { return t ? std::string(import::data_type_name(*t)) : std::string("null"); };
+    auto flag_or_null = [](std::optional<bool> const& f) { return f ? std::string(*f ? "true" : "false") : std::string("null"); };
+    out += "context name=" + (graph.context.name ? "\"" + *graph.context.name + "\"" : std::string("null")) + " compute=" + type_or_null(graph.context.compute_data_type) +
+           " intermediate=" + type_or_null(graph.context.intermediate_data_type) + " io=" + type_or_null(graph.context.io_data_type) +
+           " sm_count=" + std::to_string(graph.context.sm_count) + " dynamic=" + flag_or_null(graph.context.is_dynamic_shape_enabled) +
+           " override=" + flag_or_null(graph.context.is_override_shape_enabled) + "\n";
+    out += "graph uid=" + std::to_string(graph.graph_uid) + " backend=\"" + graph.cudnn_backend_version + "\"\n";
+    for (auto const& [uid, t] : graph.tensors)
+        out += "tensor " + std::to_string(uid) + " name=\"" + t.name + "\" type=" + std::string(import::data_type_name(t.data_type)) + " dim=" + list_text(t.dim) +
+               " stride=" + list_text(t.stride) + " virtual=" + (t.is_virtual ? "1" : "0") + " by_value=" + (t.is_pass_by_value ? "1" : "0") + " reorder=" + t.reordering_type + "\n";
+    auto described_as_conv = [](import::OperationDesc const& node) {
+        if (node.tag != import::OperationTag::kConvFprop || node.inputs.size() != 2 || node.outputs.size() != 1) return false;
+        if (!node.inputs.count("X") || !node.inputs.count("W") || !node.outputs.count("Y")) return false;
+        auto find = [&](char const* key) -> import::AttributeValue const* {
+            auto it = node.attributes.find(key);
+            return it == node.attributes.end() ? nullptr : &it->second;
+        };
+        auto const* compute = find("compute_data_type");
+        auto const* mode = find("math_mode");
+        if (!compute || !std::holds_alternative<std::string>(*compute) || std::get<std::string>(*compute) != "FLOAT") return false;
+        if (!mode || !std::holds_alternative<std::string>(*mode) || std::get<std::string>(*mode) != "CROSS_CORRELATION") return false;
+        for (auto key : {"pre_padding", "post_padding", "stride", "dilation"}) {
+            auto const* value = find(key);
+            if (!value || !std::holds_alternative<std::vector<std::int64_t>>(*value) || std::get<std::vector<std::int64_t>>(*value).size() != 2) return false;
+        }
+        return true;
+    };
+    for (std::size_t i = 0; i < graph.nodes.size(); ++i) {
+        auto const& node = graph.nodes[i];
+        out += "node " + std::to_string(i) + " tag=" + std::string(import::operation_tag_name(node.tag)) + " name=\"" + node.name + "\"\n";
+        if (described_as_conv(node)) {
+            auto text = [&](char const* key) {
+                auto it = node.attributes.find(key);
+                return it == node.attributes.end() ? std::string("?") : attribute_text(it->second);
+            };
+            out += "  conv compute=" + text("compute_data_type") + " x=" + std::to_string(node.inputs.at("X")) + " w=" + std::to_string(node.inputs.at("W")) +
+                   " y=" + std::to_string(node.outputs.at("Y")) + " pre=" + text("pre_padding") + " post=" + text("post_padding") + " stride=" + text("stride") +
+                   " dilation=" + text("dilation") + "\n";
+            continue;
+        }
+        for (auto const& [port, uid] : node.inputs) out += "  in " + port + "=" + std::to_string(uid) + "\n";
+        for (auto const& [port, uid] : node.outputs) out += "  out " + port + "=" + std::to_string(uid) + "\n";
+        for (auto const& [key, value] : node.attributes) out += "  attr " + key + "=" + attribute_text(value) + "\n";
+    }
+    return out;
+}
+}  // namespace
+
+extern "C" int df_dump_graph(const uint8_t* document, size_t size, int format, char* buffer, size_t capacity, size_t* length) {
+    import::SerializedGraph graph;
+    import::SerializedGraphImporter importer;
+    auto status = importer.parse(std::span<const uint8_t>(document, size), to_format(format), graph);
+    if (status.is_bad()) return report(status);
+    auto const text = dump_graph(graph);
+    if (length) *length = text.size();
+    if (buffer && capacity) std::memcpy(buffer, text.data(), std::min(capacity, text.size()));
+    return 0;
+}
+
 extern "C" int df_compile(const uint8_t* document, size_t size, int format, uint32_t options, df_executable** out) {
     if (!out) return report(import::Status::failure(import::ErrorCode::kInvalidArgument, "out", "null output pointer"));
     *out = nullptr;

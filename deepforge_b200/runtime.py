@@ -19,7 +19,7 @@ EXPORTS = [
     "df_argument_count", "df_argument_info", "df_set_stream", "df_execute", "df_plan_workspace",
     "df_step_count", "df_step_info", "df_execute_steps",
     "df_serialize_artifact", "df_write_artifact", "df_load_artifact", "df_load_artifact_file",
-    "df_argument_name", "df_conv2d_metadata",
+    "df_argument_name", "df_conv2d_metadata", "df_dump_graph",
 ]
 
 _LIB: Optional[C.CDLL] = None
@@ -82,6 +82,16 @@ def parse(document: Union[str, bytes, dict], fmt: int = FORMAT_AUTO) -> tuple[in
     tensors, nodes = C.c_int64(0), C.c_int64(0)
     _check(load().df_parse(data, C.c_size_t(len(data)), C.c_int(fmt), C.byref(tensors), C.byref(nodes)))
     return tensors.value, nodes.value
+
+
+def dump_graph(document: Union[str, bytes, dict], fmt: int = FORMAT_AUTO) -> str:
+    """The parsed model as canonical text (df_dump_graph): context, tensors, nodes with ports and attributes."""
+    data = _bytes(document)
+    length = C.c_size_t(0)
+    _check(load().df_dump_graph(data, C.c_size_t(len(data)), C.c_int(fmt), None, C.c_size_t(0), C.byref(length)))
+    buffer = C.create_string_buffer(length.value + 1)
+    _check(load().df_dump_graph(data, C.c_size_t(len(data)), C.c_int(fmt), buffer, C.c_size_t(length.value), C.byref(length)))
+    return buffer.raw[: length.value].decode()
 
 
 class Executable:

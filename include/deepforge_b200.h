@@ -32,6 +32,11 @@ const char* df_last_error(void);
 /* Parse only: validates a serialized graph and reports the tensor and node counts. */
 int df_parse(const uint8_t* document, size_t size, int format, int64_t* tensor_count, int64_t* node_count);
 
+/* Parse, then write the canonical model as text (one line per context field, tensor, node, port and attribute, in a
+   fixed order): what SerializedGraph::operator== compares, in a form two importers can be diffed by. Copies up to
+   `capacity` bytes and always reports the full length in *length. */
+int df_dump_graph(const uint8_t* document, size_t size, int format, char* buffer, size_t capacity, size_t* length);
+
 int df_compile(const uint8_t* document, size_t size, int format, uint32_t options, df_executable** out);
 void df_destroy(df_executable* executable);
 

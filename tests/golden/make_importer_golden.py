@@ -5,7 +5,7 @@ malformed variants of them and for broken encodings. Run on a machine that has t
     python tests/golden/make_importer_golden.py
 
 The fixture lets tests/test_importer_golden.py hold the importer of this repository to the reference's status
-codes and tensor / node counts on machines that do not have the reference."""
+codes, tensor / node counts and parsed models on machines that do not have the reference."""
 import copy
 import json
 import sys
@@ -21,9 +21,15 @@ import test_importer_vs_reference as live  # noqa: E402  (the document set and t
 def main() -> None:
     reference = live._reference.__wrapped__() if hasattr(live._reference, "__wrapped__") else live._reference()
     cases = []
-    for name in sorted(live.DOCS):
-        code, tensors, nodes, message = reference(live.DOCS[name])
-        cases.append({"case": f"accept:{name}", "format": 0, "text": json.dumps(live.DOCS[name]), "code": code, "tensors": tensors, "nodes": nodes})
+    for name in sorted(live.MODEL_DOCS):
+        code, tensors, nodes, message = reference(live.MODEL_DOCS[name])
+        # "model": the reference's parsed model as canonical text (ref_dump of oracle/ref_importer_shim.cpp)
+        cases.append({"case": f"accept:{name}", "format": 0, "text": json.dumps(live.MODEL_DOCS[name]), "code": code, "tensors": tensors, "nodes": nodes,
+                      "model": live._reference_dump(live.MODEL_DOCS[name])})
+        encoded = live._to_ubjson(live.MODEL_DOCS[name])
+        code, tensors, nodes, message = reference(encoded, 2)
+        cases.append({"case": f"accept_ubjson:{name}", "format": 2, "hex": encoded.hex(), "code": code, "tensors": tensors, "nodes": nodes,
+                      "model": live._reference_dump(encoded, 2)})
     for name in ("c1", "c2_f32"):
         for index, mutate in enumerate(live.MUTATIONS):
             document = copy.deepcopy(live.DOCS[name])

@@ -4,6 +4,7 @@ present (the machine that has the reference tree); the GPU box does not need it.
 import copy
 import ctypes as C
 import json
+import os
 import subprocess
 from pathlib import Path
 
@@ -14,14 +15,42 @@ from deepforge_b200 import graphs, runtime
 ROOT = Path(__file__).resolve().parent.parent
 REF = ROOT / "oracle" / "_ref" / "libdf_ref_import.so"
 
+def _reference_tree() -> Path:
+    """Where the reference's source tree lies when this machine has it: oracle/Makefile knows (DEEPFORGE_REFERENCE)."""
+    found = subprocess.run(["make", "-s", "-C", str(ROOT / "oracle"), "print-reference"], capture_output=True, text=True)
+    return Path(found.stdout.strip() or "/nonexistent")
 
-def _reference():
-    if not REF.exists() and Path("/root/reference/lib/Import").exists():
+
+
+def _library():
+    shim = ROOT / "oracle" / "ref_importer_shim.cpp"
+    stale = REF.exists() and REF.stat().st_mtime < shim.stat().st_mtime
+    if (not REF.exists() or stale) and (_reference_tree() / "lib" / "Import").exists():
         subprocess.run(["make", "-C", str(ROOT / "oracle"), "ref"], capture_output=True)
     if not REF.exists():
         pytest.skip("reference importer not built on this machine")
     lib = C.CDLL(str(REF))
     lib.ref_parse.restype = C.c_int
+    return lib
+
+
+def _reference_dump(document, fmt=0):
+    """The REFERENCE importer's parsed model as canonical text (ref_dump of the shim), or its error code."""
+    lib = _library()
+    if not hasattr(lib, "ref_dump"):
+        pytest.skip("the reference importer library on this machine predates ref_dump")
+    data = document if isinstance(document, bytes) else json.dumps(document).encode()
+    length = C.c_size_t(0)
+    code = lib.ref_dump(data, C.c_size_t(len(data)), C.c_int(fmt), None, C.c_size_t(0), C.byref(length))
+    if code != 0:
+        return code
+    buffer = C.create_string_buffer(length.value + 1)
+    lib.ref_dump(data, C.c_size_t(len(data)), C.c_int(fmt), buffer, C.c_size_t(length.value), C.byref(length))
+    return buffer.raw[: length.value].decode()
+
+
+def _reference():
+    lib = _library()
 
     def parse(document, fmt=0):
         data = document if isinstance(document, bytes) else json.dumps(document).encode()
@@ -57,6 +86,71 @@ def test_both_importers_accept_the_benchmark_graphs(name):
     code, tensors, nodes, message = reference(DOCS[name])
     assert code == 0, message
     assert _ours(DOCS[name]) == (0, tensors, nodes)
+
+
+# graphs beyond the benchmark set, for the model comparison: strides, reordering, virtual flags, every attribute type
+MODEL_DOCS = {
+    **DOCS,
+    "c1_wide": graphs.c1_conv("nhwc", n=2, c=4, h=6, w=5, k=3),
+    "c3_f32_unaligned": graphs.c3_quantize_matmul(64, 96, 32, io="FLOAT", c_type="FLOAT"),
+    "c4_noncausal_f32": graphs.c4_sdpa(2, 3, 40, 16, io="FLOAT", causal=False),
+    "fp8_batched": graphs.matmul_fp8(4, 8, 4, c_type="FP8_E4M3", batch=(2, 3), b_k_major=True),
+}
+
+
+@pytest.mark.parametrize("name", sorted(MODEL_DOCS))
+def test_parsed_models_are_identical(name):
+    """Not only accept / reject: the canonical model itself -- context, every tensor (uid, name, type, dims, strides,
+    virtual, by-value, reordering) and every node (tag, name, ports, attributes with their value types) -- is the
+    same text from both importers (what SerializedGraph::operator== compares, lib/Import/SerializedGraphImporter.cpp
+    :1951-2090)."""
+    expected = _reference_dump(MODEL_DOCS[name])
+    assert isinstance(expected, str), f"the reference rejects this graph with code {expected}"
+    assert runtime.dump_graph(MODEL_DOCS[name]) == expected
+    # and through the canonical UBJSON encoding of the same document
+    ubjson = _to_ubjson(MODEL_DOCS[name])
+    if ubjson is not None:
+        again = _reference_dump(ubjson, 2)
+        if isinstance(again, str):
+            assert runtime.dump_graph(ubjson, 2) == again
+
+
+def _to_ubjson(value) -> bytes:
+    """The canonical UBJSON both importers demand (what nlohmann::json::to_ubjson writes without size or type
+    optimisation): smallest integer type, 'D' for reals, object keys in sorted order."""
+    import struct
+
+    def integer(n: int) -> bytes:
+        if 0 <= n <= 127 or -128 <= n < 0:
+            return b"i" + struct.pack(">b", n)
+        if 0 <= n <= 255:
+            return b"U" + struct.pack(">B", n)
+        if -32768 <= n <= 32767:
+            return b"I" + struct.pack(">h", n)
+        if -(2 ** 31) <= n <= 2 ** 31 - 1:
+            return b"l" + struct.pack(">i", n)
+        return b"L" + struct.pack(">q", n)
+
+    if value is None:
+        return b"Z"
+    if value is True:
+        return b"T"
+    if value is False:
+        return b"F"
+    if isinstance(value, int):
+        return integer(value)
+    if isinstance(value, float):
+        return b"D" + struct.pack(">d", value)
+    if isinstance(value, str):
+        raw = value.encode()
+        return b"S" + integer(len(raw)) + raw
+    if isinstance(value, (list, tuple)):
+        return b"[" + b"".join(_to_ubjson(item) for item in value) + b"]"
+    out = b"{"
+    for key in sorted(value):
+        raw = key.encode()
+        out += integer(len(raw)) + raw + _to_ubjson(value[key])
+    return out + b"}"
 
 
 MUTATIONS = [
