@@ -409,13 +409,34 @@ def measure(name: str, steps: int, warmup: int, torch, device, distributed: bool
         gathered = {uid: torch.empty(world * session.dev[uid].numel(), dtype=torch.uint8, device=device) for uid in wl.outputs}
         gather_bytes = sum(t.numel() for t in gathered.values())
 
+    # The all-gather of step i runs on a side stream while the kernels of step i + 1 run on the launching stream (the
+    # steps rotate over the buffer replicas; a replica's outputs are not overwritten before their gather has finished).
+    side = torch.cuda.Stream(device) if gathered is not None else None
+    computed = [torch.cuda.Event() for _ in range(replicas)]
+    gather_done = [torch.cuda.Event() for _ in range(replicas)]
+    pending = [False] * replicas
+
     def step(i):
-        graphs[i % replicas].replay()
+        r = i % replicas
+        if pending[r]:
+            stream.wait_event(gather_done[r])
+        graphs[r].replay()
         if gathered is not None:
             import torch.distributed as dist
-            tensors = session.replica_tensors(i % replicas)
-            for uid in wl.outputs:
-                dist.all_gather_into_tensor(gathered[uid], tensors[uid])
+            tensors = session.replica_tensors(r)
+            computed[r].record(stream)
+            with torch.cuda.stream(side):
+                side.wait_event(computed[r])
+                for uid in wl.outputs:
+                    dist.all_gather_into_tensor(gathered[uid], tensors[uid])
+                gather_done[r].record(side)
+            pending[r] = True
+
+    def join_gathers():
+        """The launching stream waits for every gather in flight (so that an event recorded on it covers them)."""
+        for r in range(replicas):
+            if pending[r]:
+                stream.wait_event(gather_done[r])
 
     def barrier():
         if distributed:
@@ -425,9 +446,10 @@ def measure(name: str, steps: int, warmup: int, torch, device, distributed: bool
 
     for i in range(max(warmup, 3)):
         step(i)
-    barrier()
+    join_gathers()
     if sampler is not None:
-        sampler.start()
+        sampler.start()  # before the barrier: what one rank does between the barrier and its first event, the others wait for inside their timed region
+    barrier()
     # exactly `steps` steps between the first and the last event; the events in between cut them into blocks
     blocks = max(1, min(TIMED_BLOCKS, steps))
     edges = [steps * j // blocks for j in range(blocks + 1)]
@@ -436,6 +458,8 @@ def measure(name: str, steps: int, warmup: int, torch, device, distributed: bool
     for j in range(blocks):
         for i in range(edges[j], edges[j + 1]):
             step(i)
+        if j + 1 == blocks:
+            join_gathers()  # the timed region ends when the last gather has
         events[j + 1].record(stream)
     barrier()
     device_ms = events[0].elapsed_time(events[-1])
@@ -654,7 +678,7 @@ def main() -> None:
         }
         if gather:
             line["all_gather"] = {"bytes_received_per_rank_and_step": result["gather_bytes"], "ms_alone": result["gather_ms"],
-                                  "collective": "ncclAllGather of every output tensor (torch.distributed.all_gather_into_tensor), after the kernels of the step, inside the timed region"}
+                                  "collective": "ncclAllGather of every output tensor (torch.distributed.all_gather_into_tensor) after the kernels of each step, inside the timed region, on a side stream: the gather of step i overlaps the kernels of step i + 1, and the region ends when the last gather has"}
         if here is not None:
             line["peaks_measured_here"] = here
         del result

@@ -126,10 +126,36 @@ def build_cli(force: bool = False) -> Path:
     return target
 
 
+def cuda_home() -> Path:
+    for candidate in (os.environ.get("CUDA_HOME"), os.environ.get("CUDA_PATH"), "/usr/local/cuda"):
+        if candidate and (Path(candidate) / "include" / "cuda_runtime_api.h").exists():
+            return Path(candidate)
+    raise RuntimeError("CUDA toolkit headers not found")
+
+
+def build_benchmark_tool(force: bool = False) -> Path:
+    """deepforge-benchmark (host/cli/deepforge_benchmark.cpp): device buffers and CUDA events through the CUDA runtime."""
+    library = build_host()
+    source = PKG / "host" / "cli" / "deepforge_benchmark.cpp"
+    headers = sorted((ROOT / "include").rglob("*.h"))
+    target = OUT / "deepforge-benchmark"
+    flags = ["-std=c++20", "-O2", "-Wall", "-Wextra"]
+    stamp = _stamp([source] + headers, " ".join(flags))
+    if not force and _up_to_date(target, stamp):
+        return target
+    cuda = cuda_home()
+    _run(["g++", *flags, "-I", str(ROOT / "include"), "-isystem", str(cuda / "include"), str(source), "-o", str(target), f"-L{OUT}", "-ldeepforge_b200", "-ldfgpu",
+          f"-L{cuda / 'lib64'}", "-lcudart", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{cuda / 'lib64'}", "-lpthread"])
+    target.with_suffix(target.suffix + ".stamp").write_text(stamp)
+    assert library.exists()
+    return target
+
+
 def build_all(force: bool = False) -> None:
     build_kernels(force)
     build_host(force)
     build_cli(force)
+    build_benchmark_tool(force)
 
 
 if __name__ == "__main__":

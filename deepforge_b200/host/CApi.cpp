@@ -219,6 +219,13 @@ extern "C" int df_execute(const df_executable* executable, void* handle, const i
     return report(executable->result.executable->execute(handle, pack, workspace));
 }
 
+extern "C" int df_execute_on(const df_executable* executable, void* stream, const int64_t* uids, void* const* pointers, size_t count, void* workspace) {
+    runtime::VariantPack pack;
+    pack.reserve(count);
+    for (size_t i = 0; i < count; ++i) pack[uids[i]] = pointers[i];
+    return report(executable->result.executable->execute_on(stream, pack, workspace));
+}
+
 extern "C" int64_t df_step_count(const df_executable* executable) { return static_cast<int64_t>(executable->result.plan.steps.size()); }
 
 extern "C" int df_step_info(const df_executable* executable, int64_t step, char* label, size_t label_capacity, int32_t* op, int32_t* kernel,

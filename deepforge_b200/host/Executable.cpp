@@ -79,7 +79,14 @@ std::int64_t Executable::get_workspace_size(FrontendHandle, OverrideUids const& 
 
 bool Executable::supports_variant(CpuVariant variant) const noexcept { return variant == CpuVariant::kScalar; }
 CpuVariant Executable::selected_variant() const noexcept { return CpuVariant::kScalar; }
-void Executable::set_stream(void* stream) noexcept { impl_->stream = stream; }
+void Executable::set_stream(void* stream) noexcept {
+    std::lock_guard<std::mutex> lock(impl_->mutex);
+    impl_->stream = stream;
+}
+
+Status Executable::execute_on(void* stream, VariantPack& pack, void* workspace) const {
+    return run_steps(0, static_cast<std::int64_t>(impl_->plan.steps.size()), pack, workspace, stream, true);
+}
 std::int64_t Executable::launch_count() const noexcept { return impl_->launches; }
 std::string Executable::plan_text() const { return impl_->plan.to_text(); }
 
@@ -106,6 +113,10 @@ Status Executable::execute_variant(CpuVariant variant, FrontendHandle, VariantPa
 }
 
 Status Executable::execute_steps(std::int64_t first, std::int64_t last, VariantPack& pack, void* workspace) const {
+    return run_steps(first, last, pack, workspace, nullptr, false);
+}
+
+Status Executable::run_steps(std::int64_t first, std::int64_t last, VariantPack& pack, void* workspace, void* call_stream, bool own_stream) const {
     auto const& impl = *impl_;
     if (first < 0 || last > static_cast<std::int64_t>(impl.plan.steps.size()) || first > last)
         return Status::failure(ErrorCode::kInvalidArgument, "steps", "step range is outside the kernel plan");
@@ -139,7 +150,14 @@ Status Executable::execute_steps(std::int64_t first, std::int64_t last, VariantP
                 return Status::failure(ErrorCode::kInvalidVariantPack, "workspace", "storage overlaps '" + *range.name + "'");
     }
 
-    std::lock_guard<std::mutex> lock(impl.mutex);
+    // The plan is immutable and the launchers keep no state between calls, so a call with its own stream needs no
+    // lock; calls on the shared stream take it, so that the launches of one plan stay together on that stream.
+    std::unique_lock<std::mutex> lock(impl.mutex, std::defer_lock);
+    void* stream = call_stream;
+    if (!own_stream) {
+        lock.lock();
+        stream = impl.stream;
+    }
     auto resolve = [&](TensorBinding const& binding) -> void* {
         switch (binding.kind) {
             case TensorBinding::Kind::kArgument: return pack.at(binding.uid);
@@ -155,24 +173,24 @@ Status Executable::execute_steps(std::int64_t first, std::int64_t last, VariantP
         void* scratch = resolve(step.scratch);
         int code = 0;
         switch (step.op) {
-            case KernelOp::kBlockScaleQuantize: code = dfgpu_block_scale_quantize(&std::get<dfgpu_bsq_params>(step.params), pointers.data(), scratch, impl.stream); break;
-            case KernelOp::kBlockScaleDequantize: code = dfgpu_block_scale_dequantize(&std::get<dfgpu_bsd_params>(step.params), pointers.data(), scratch, impl.stream); break;
-            case KernelOp::kPointwise: code = dfgpu_pointwise(&std::get<dfgpu_pointwise_params>(step.params), pointers.data(), scratch, impl.stream); break;
+            case KernelOp::kBlockScaleQuantize: code = dfgpu_block_scale_quantize(&std::get<dfgpu_bsq_params>(step.params), pointers.data(), scratch, stream); break;
+            case KernelOp::kBlockScaleDequantize: code = dfgpu_block_scale_dequantize(&std::get<dfgpu_bsd_params>(step.params), pointers.data(), scratch, stream); break;
+            case KernelOp::kPointwise: code = dfgpu_pointwise(&std::get<dfgpu_pointwise_params>(step.params), pointers.data(), scratch, stream); break;
             case KernelOp::kConvFprop: {
                 // bit 1 of `reserved` (set by the lowering) promises that the kernel launched just before this one is the
                 // plan's previous step; that does not hold for the first launch of a call
                 dfgpu_conv_params params = std::get<dfgpu_conv_params>(step.params);
                 if (index == first) params.reserved &= ~2;
-                code = dfgpu_conv_fprop(&params, pointers.data(), scratch, impl.stream);
+                code = dfgpu_conv_fprop(&params, pointers.data(), scratch, stream);
                 break;
             }
-            case KernelOp::kMatmul: code = dfgpu_matmul(&std::get<dfgpu_matmul_params>(step.params), pointers.data(), scratch, impl.stream); break;
-            case KernelOp::kSdpaForward: code = dfgpu_sdpa_forward(&std::get<dfgpu_sdpa_params>(step.params), pointers.data(), scratch, impl.stream); break;
-            case KernelOp::kMatmulFp8: code = dfgpu_matmul_fp8(&std::get<dfgpu_matmul_fp8_params>(step.params), pointers.data(), scratch, impl.stream); break;
+            case KernelOp::kMatmul: code = dfgpu_matmul(&std::get<dfgpu_matmul_params>(step.params), pointers.data(), scratch, stream); break;
+            case KernelOp::kSdpaForward: code = dfgpu_sdpa_forward(&std::get<dfgpu_sdpa_params>(step.params), pointers.data(), scratch, stream); break;
+            case KernelOp::kMatmulFp8: code = dfgpu_matmul_fp8(&std::get<dfgpu_matmul_fp8_params>(step.params), pointers.data(), scratch, stream); break;
             case KernelOp::kConvFpropPair: {
                 dfgpu_conv_pair_params params = std::get<dfgpu_conv_pair_params>(step.params);
                 if (index == first) params.first.reserved &= ~2;  // see kConvFprop above
-                code = dfgpu_conv_fprop_pair(&params, pointers.data(), scratch, impl.stream);
+                code = dfgpu_conv_fprop_pair(&params, pointers.data(), scratch, stream);
                 break;
             }
         }

@@ -19,7 +19,7 @@ EXPORTS = [
     "df_argument_count", "df_argument_info", "df_set_stream", "df_execute", "df_plan_workspace",
     "df_step_count", "df_step_info", "df_execute_steps",
     "df_serialize_artifact", "df_write_artifact", "df_load_artifact", "df_load_artifact_file",
-    "df_argument_name", "df_conv2d_metadata", "df_dump_graph",
+    "df_argument_name", "df_conv2d_metadata", "df_dump_graph", "df_execute_on",
 ]
 
 _LIB: Optional[C.CDLL] = None
@@ -178,6 +178,14 @@ class Executable:
         uids = (C.c_int64 * count)(*pack.keys())
         pointers = (C.c_void_p * count)(*[C.c_void_p(p or None) for p in pack.values()])
         _check(load().df_execute(self._handle, C.c_void_p(handle or None), uids, pointers, C.c_size_t(count), C.c_void_p(workspace or None)))
+
+    def execute_on(self, stream: int, pack: Mapping[int, int], workspace: Optional[int] = None) -> None:
+        """execute() with the launches on `stream` (a cudaStream_t) for this call only; safe to call from several
+        threads at once with different streams, workspaces and outputs (ctypes releases the GIL during the call)."""
+        count = len(pack)
+        uids = (C.c_int64 * count)(*pack.keys())
+        pointers = (C.c_void_p * count)(*[C.c_void_p(p or None) for p in pack.values()])
+        _check(load().df_execute_on(self._handle, C.c_void_p(stream or None), uids, pointers, C.c_size_t(count), C.c_void_p(workspace or None)))
 
 
 def compile_graph(document: Union[str, bytes, dict], fmt: int = FORMAT_AUTO, options: int = 0) -> Executable:

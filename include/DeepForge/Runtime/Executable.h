@@ -67,11 +67,23 @@ public:
     // GPU-side additions (not in the reference): the CUDA stream launches go to (a
     // cudaStream_t, null = legacy default stream), the number of kernel launches one
     // execute() makes, and a text dump of the kernel plan.
+    // Threading: concurrent execute() calls on one Executable are legal with distinct
+    // workspaces and outputs, as in the reference (which serialises them with a mutex,
+    // lib/Runtime/Executable.cpp:1154). Calls that share the stream of set_stream() are
+    // enqueued one whole plan after the other (a lock is held while a call enqueues);
+    // execute_on() takes the stream per call and holds no lock, so calls on different
+    // streams also overlap on the device. set_stream() takes the same lock.
     void set_stream(void* stream) noexcept;
+    [[nodiscard]] import::Status execute_on(void* stream, VariantPack& uid_to_device_ptr, void* workspace) const;
     [[nodiscard]] std::int64_t launch_count() const noexcept;
     [[nodiscard]] std::string plan_text() const;
     // Runs plan steps [first, last) only, after the same validation as execute().
     [[nodiscard]] import::Status execute_steps(std::int64_t first, std::int64_t last, VariantPack& uid_to_device_ptr, void* workspace) const;
+
+private:
+    import::Status run_steps(std::int64_t first, std::int64_t last, VariantPack& pack, void* workspace, void* stream, bool own_stream) const;
+
+public:
 
 private:
     struct Impl;

@@ -66,6 +66,11 @@ void df_set_stream(df_executable* executable, void* stream);
 int df_execute(const df_executable* executable, void* handle, const int64_t* uids, void* const* pointers, size_t count,
                void* workspace);
 
+/* df_execute with the launches on `stream` (a cudaStream_t) for this call only: calls on different streams with
+   different workspaces and outputs may run concurrently from different threads (Executable::execute_on). */
+int df_execute_on(const df_executable* executable, void* stream, const int64_t* uids, void* const* pointers, size_t count,
+                  void* workspace);
+
 /* Kernel plan introspection and partial execution (used for per-kernel timing): the plan has
    df_step_count() launches groups; df_execute_steps runs steps [first, last) only. */
 int64_t df_step_count(const df_executable* executable);

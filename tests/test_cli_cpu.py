@@ -62,3 +62,24 @@ def test_exit_codes(tool, tmp_path: Path):
     (tmp_path / "ok.json").write_text(json.dumps(graphs.matmul_fp8(2, 2, 2)))
     nowhere = run(tool, "ok.json", "-o", "no_such_directory/x.dfo", cwd=tmp_path)
     assert nowhere.returncode == 1 and nowhere.stderr.startswith("DFE_IO_ERROR")
+
+
+def test_benchmark_tool_command_line():
+    """deepforge-benchmark keeps the reference tool's command line and exit codes (tools/deepforge-benchmark.cpp:58-103,
+    :315-345): --help prints the usage and exits 0, a bad option prints it on stderr and exits 2; without a CUDA device
+    the run itself fails with exit code 1 (there is no CPU path to fall back to)."""
+    from deepforge_b200 import build
+    tool = build.build_benchmark_tool()
+    result = subprocess.run([str(tool), "--help"], capture_output=True, text=True)
+    assert result.returncode == 0 and result.stdout.startswith("usage: deepforge-benchmark [--profile=small|medium|large|all]")
+    for bad in (["--profile=huge"], ["--schedule=fast"], ["--iterations=0"], ["--iterations=1001"], ["--iterations=3x"], ["--surprise"]):
+        result = subprocess.run([str(tool), *bad], capture_output=True, text=True)
+        assert result.returncode == 2 and "usage:" in result.stderr, bad
+    try:
+        import torch
+        has_gpu = torch.cuda.is_available()
+    except ImportError:
+        has_gpu = False
+    if not has_gpu:
+        result = subprocess.run([str(tool), "--profile=small"], capture_output=True, text=True)
+        assert result.returncode == 1 and "no CUDA device" in result.stderr

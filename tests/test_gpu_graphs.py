@@ -370,3 +370,47 @@ def test_sdpa_graph_with_sink_token_and_block_mask():
     check_f32(s.output(5), ref[5])
     stats = s.output(5).reshape(1, 2, 256)
     assert np.allclose(stats[0, 1, 128:], -1.0)  # fully masked rows keep the sink logit: Stats = sink + ln(1)
+
+
+def test_two_threads_execute_one_executable_concurrently():
+    """The reference's concurrency case (test/Compiler/CompilerTest.cpp:405-432): two threads call execute on ONE
+    executable with the same inputs, separate outputs and separate workspaces; both succeed and agree bit for bit.
+    Here once through execute() (shared stream: whole plans are enqueued one after the other) and once through
+    execute_on() with a stream per thread (no lock: the plans also overlap on the device), repeated to give the two
+    threads many chances to interleave."""
+    import threading
+    import torch
+    wl = workloads.c2(n=2, h=28, w=28)
+    s = harness.Session(wl)
+    s.run()
+    expected = s.raw(7).copy()
+    size = s.exe.workspace_size
+    outputs = [torch.full_like(s.dev[7], 0x7f) for _ in range(2)]
+    spaces = [torch.empty(max(size, 1), dtype=torch.uint8, device=s.device) for _ in range(2)]
+    streams = [torch.cuda.Stream(s.device) for _ in range(2)]
+    packs = [{**s.pack, 7: out.data_ptr()} for out in outputs]
+    for own_stream in (False, True):
+        for out in outputs:
+            out.fill_(0x7f)
+        torch.cuda.synchronize()
+        errors = []
+
+        def work(i):
+            try:
+                for _ in range(50):
+                    if own_stream:
+                        s.exe.execute_on(streams[i].cuda_stream, packs[i], spaces[i].data_ptr())
+                    else:
+                        s.exe.execute(packs[i], spaces[i].data_ptr())
+            except Exception as error:  # noqa: BLE001 - reported below, in the main thread
+                errors.append(error)
+
+        threads = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        torch.cuda.synchronize()
+        assert not errors, errors
+        for out in outputs:
+            assert np.array_equal(out.cpu().numpy(), expected)
