@@ -406,7 +406,8 @@ def measure(name: str, steps: int, warmup: int, torch, device, distributed: bool
     gathered = None
     gather_bytes = 0
     if gather and distributed:
-        gathered = {uid: torch.empty(world * session.dev[uid].numel(), dtype=torch.uint8, device=device) for uid in wl.outputs}
+        # only what the shards split: an output every rank computes in full (the quantized B operand) is not exchanged
+        gathered = {uid: torch.empty(world * session.dev[uid].numel(), dtype=torch.uint8, device=device) for uid in wl.outputs if uid in workloads.GATHER_AXIS.get(name, {})}
         gather_bytes = sum(t.numel() for t in gathered.values())
 
     # The all-gather of step i runs on a side stream while the kernels of step i + 1 run on the launching stream (the
@@ -427,7 +428,7 @@ def measure(name: str, steps: int, warmup: int, torch, device, distributed: bool
             computed[r].record(stream)
             with torch.cuda.stream(side):
                 side.wait_event(computed[r])
-                for uid in wl.outputs:
+                for uid in gathered:
                     dist.all_gather_into_tensor(gathered[uid], tensors[uid])
                 gather_done[r].record(side)
             pending[r] = True
@@ -474,7 +475,7 @@ def measure(name: str, steps: int, warmup: int, torch, device, distributed: bool
         barrier()
         begin.record(stream)
         for i in range(20):
-            for uid in wl.outputs:
+            for uid in gathered:
                 dist.all_gather_into_tensor(gathered[uid], session.replica_tensors(i % replicas)[uid])
         end.record(stream)
         barrier()

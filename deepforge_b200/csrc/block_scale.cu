@@ -314,14 +314,12 @@ __device__ __forceinline__ bool has_byte_0x80(uint32_t word) {
     return ((t - 0x01010101u) & ~t & 0x80808080u) != 0u;
 }
 
-__global__ void __launch_bounds__(256)
-bsq_row32_bf16_kernel(const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* __restrict__ scale,
-                      int64_t rows, int64_t cols, int reordered, int64_t scale_k_extent) {
+// One tile of 256 threads x 4 chunks x 8 elements; `tile` is the tile's index along the flattened tensor.
+__device__ __forceinline__ void bsq_row32_bf16_tile(int64_t tile, const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* __restrict__ scale,
+                                                    int64_t rows, int64_t cols, int reordered, int64_t scale_k_extent) {
     constexpr int kChunks = 4;
-    chain_release();
-    chain_wait();
     const int64_t total = rows * cols;
-    const int64_t tile0 = static_cast<int64_t>(blockIdx.x) * (256 * 8 * kChunks);
+    const int64_t tile0 = tile * (256 * 8 * kChunks);
     const int lane = threadIdx.x & 31;
     uint4 raw[kChunks];
     bool live[kChunks];
@@ -381,6 +379,14 @@ bsq_row32_bf16_kernel(const void* __restrict__ x, uint8_t* __restrict__ y, uint8
             }
         }
     }
+}
+
+__global__ void __launch_bounds__(256)
+bsq_row32_bf16_kernel(const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* __restrict__ scale,
+                      int64_t rows, int64_t cols, int reordered, int64_t scale_k_extent) {
+    chain_release();
+    chain_wait();
+    bsq_row32_bf16_tile(blockIdx.x, x, y, scale, rows, cols, reordered, scale_k_extent);
 }
 
 // ---- column kernel: block of 32 along the second-to-last axis -------------------
@@ -528,19 +534,24 @@ bsq_col32_kernel(const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* _
 // bf16 input, same economies as the bf16 row kernel: packed maxima, each of the CTA's four warps derives the
 // scale codes of two of the eight column groups and the warps trade them through shared memory, and the exact
 // negative-underflow rule only runs for rows whose codes contain a 0x80 byte.
-__global__ void __launch_bounds__(128)
-bsq_col32_bf16_kernel(const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* __restrict__ scale,
-                      int64_t k_extent, int64_t n_extent, int reordered, int64_t scale_k_extent) {
+// Shared memory of one 128-thread column tile.
+struct BsqColumnShared {
+    uint32_t partial[4][4][32];  // [row group][column pair][lane]: packed |x| maxima of two columns
+    uint32_t codes[8][32];       // [column][lane]
+};
+
+// One tile of 128 threads: 32 rows x 256 columns. `thread` is 0..127, (tile_x, kb, batch) the tile's coordinates and
+// `sync` the barrier over exactly those 128 threads.
+template <typename Sync>
+__device__ __forceinline__ void bsq_col32_bf16_tile(int thread, int64_t tile_x, int64_t kb, int64_t batch, BsqColumnShared& shared, Sync sync,
+                                                    const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* __restrict__ scale,
+                                                    int64_t k_extent, int64_t n_extent, int reordered, int64_t scale_k_extent) {
     constexpr int kRows = 8;
-    __shared__ uint32_t partial[4][4][32];  // [row group][column pair][lane]: packed |x| maxima of two columns
-    __shared__ uint32_t codes[8][32];       // [column][lane]
-    chain_release();
-    chain_wait();
-    const int lane = threadIdx.x & 31, group = threadIdx.x >> 5;
-    const int64_t column = (static_cast<int64_t>(blockIdx.x) * 32 + lane) * 8;
+    auto& partial = shared.partial;
+    auto& codes = shared.codes;
+    const int lane = thread & 31, group = thread >> 5;
+    const int64_t column = (tile_x * 32 + lane) * 8;
     const bool live = column < n_extent;
-    const int64_t kb = blockIdx.y;
-    const int64_t batch = blockIdx.z;
     const int64_t base = (batch * k_extent + kb * 32 + group * kRows) * n_extent + (live ? column : 0);
     const uint16_t* xp = static_cast<const uint16_t*>(x) + base;
     uint4 raw[kRows];
@@ -556,14 +567,14 @@ bsq_col32_bf16_kernel(const void* __restrict__ x, uint8_t* __restrict__ y, uint8
     }
 #pragma unroll
     for (int c = 0; c < 4; ++c) partial[group][c][lane] = best[c];
-    __syncthreads();
+    sync();
     {
         // warp `group` owns column pair `group` of every lane's eight columns
         const uint32_t m = __vmaxu2(__vmaxu2(partial[0][group][lane], partial[1][group][lane]), __vmaxu2(partial[2][group][lane], partial[3][group][lane]));
         codes[2 * group][lane] = scale_code_from_amax_bits((m & 0xffffu) << 16);
         codes[2 * group + 1][lane] = scale_code_from_amax_bits(m & 0xffff0000u);
     }
-    __syncthreads();
+    sync();
     if (!live) return;
     uint32_t code[8];
     float reciprocal[8];
@@ -605,6 +616,58 @@ bsq_col32_bf16_kernel(const void* __restrict__ x, uint8_t* __restrict__ y, uint8
         }
         *reinterpret_cast<uint2*>(y + base + r * n_extent) = packed;
     }
+}
+
+__global__ void __launch_bounds__(128)
+bsq_col32_bf16_kernel(const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* __restrict__ scale,
+                      int64_t k_extent, int64_t n_extent, int reordered, int64_t scale_k_extent) {
+    __shared__ BsqColumnShared shared;
+    chain_release();
+    chain_wait();
+    bsq_col32_bf16_tile(threadIdx.x, blockIdx.x, blockIdx.y, blockIdx.z, shared, [] { __syncthreads(); }, x, y, scale, k_extent, n_extent, reordered, scale_k_extent);
+}
+
+// ---- two quantizations in one launch ------------------------------------------------------------------
+// Independent BLOCK_SCALE_QUANTIZE nodes of one graph (the two operands of a block-scaled matmul) as ONE grid: the
+// CTAs of the first tensor, then the CTAs of the second. Each launch of these kernels is only ~10 us long, a third
+// of which is ramp and tail; one grid pays them once. A CTA has 256 threads: one row tile, or two column tiles
+// (threads 0-127 and 128-255, each pair with its own shared memory and its own named barrier).
+struct BsqTask {
+    const void* x;
+    uint8_t* y;
+    uint8_t* scale;
+    int64_t rows, cols;        // row form: flattened rows x cols; column form: K x N of one batch entry
+    int64_t scale_k_extent;
+    int32_t reordered;
+    int32_t column_form;
+    int32_t tiles_x, tiles_y;  // column form: tiles along N and K (the batch axis is the slowest)
+    int64_t tiles;             // row tiles, or column tiles (two per CTA)
+    int64_t ctas;
+};
+
+__device__ __forceinline__ void bsq_pair_run(const BsqTask& task, int64_t cta, BsqColumnShared (&shared)[2]) {
+    if (!task.column_form) {
+        if (cta < task.tiles) bsq_row32_bf16_tile(cta, task.x, task.y, task.scale, task.rows, task.cols, task.reordered, task.scale_k_extent);
+        return;
+    }
+    const int side = threadIdx.x >> 7;
+    const int64_t tile = 2 * cta + side;
+    if (tile >= task.tiles) return;  // (all 128 threads of the side together: nobody is left at its barrier)
+    const int64_t tile_x = tile % task.tiles_x, rest = tile / task.tiles_x;
+    const int64_t kb = rest % task.tiles_y, batch = rest / task.tiles_y;
+    const int barrier = 1 + side;
+    bsq_col32_bf16_tile(threadIdx.x & 127, tile_x, kb, batch, shared[side], [barrier] { asm volatile("bar.sync %0, 128;" ::"r"(barrier) : "memory"); },
+                        task.x, task.y, task.scale, task.rows, task.cols, task.reordered, task.scale_k_extent);
+}
+
+__global__ void __launch_bounds__(256)
+bsq_pair_bf16_kernel(BsqTask first, BsqTask second) {
+    __shared__ BsqColumnShared shared[2];
+    chain_release();
+    chain_wait();
+    const int64_t cta = blockIdx.x;
+    if (cta < first.ctas) bsq_pair_run(first, cta, shared);
+    else bsq_pair_run(second, cta - first.ctas, shared);
 }
 
 // ---- dequantize -------------------------------------------------------------------
@@ -877,6 +940,68 @@ int plan_bsd(const dfgpu_bsd_params& p, BsdPlan& plan) {
 }
 
 }  // namespace
+
+// ---- two BLOCK_SCALE_QUANTIZE nodes in one launch ---------------------------------------------------
+
+namespace {
+// The task of one tensor inside the pair grid, when its plan is one of the two bf16 fast forms with nothing to
+// pre-fill; false otherwise (the caller then launches the nodes separately).
+bool pair_task(const dfgpu_bsq_params& p, void* const* tensors, dfgpu::BsqTask& task) {
+    using namespace dfgpu;
+    BsqPlan plan;
+    if (plan_bsq(p, plan) != kOk || plan.needs_fill || p.x.dtype != DFGPU_BF16) return false;
+    if (plan.kernel != DFGPU_BSQ_ROW32 && plan.kernel != DFGPU_BSQ_COL32) return false;
+    task = BsqTask{};
+    task.rows = plan.rows;
+    task.cols = plan.cols;
+    task.scale_k_extent = plan.scale_k_extent;
+    task.reordered = plan.layout.reordered;
+    if (plan.kernel == DFGPU_BSQ_ROW32) {
+        task.column_form = 0;
+        task.tiles = (plan.rows * plan.cols + 8191) / 8192;  // 256 threads x 4 chunks x 8 elements
+        task.ctas = task.tiles;
+    } else {
+        task.column_form = 1;
+        task.tiles_x = static_cast<int32_t>((plan.cols / 8 + 31) / 32);
+        task.tiles_y = static_cast<int32_t>(plan.rows / 32);
+        task.tiles = static_cast<int64_t>(task.tiles_x) * task.tiles_y * plan.batch;
+        task.ctas = (task.tiles + 1) / 2;
+    }
+    if (task.ctas <= 0 || task.ctas > (1ll << 30)) return false;
+    if (tensors) {
+        task.x = tensors[0];
+        task.y = static_cast<uint8_t*>(tensors[1]);
+        task.scale = static_cast<uint8_t*>(tensors[2]);
+    }
+    return true;
+}
+}  // namespace
+
+extern "C" int dfgpu_query_block_scale_quantize_pair(const dfgpu_bsq_pair_params* p, dfgpu_plan_info* info) {
+    if (!p || !info) return fail(kInvalidArgument, "BLOCK_SCALE_QUANTIZE pair: null params");
+    BsqTask first, second;
+    if (!pair_task(p->first, nullptr, first) || !pair_task(p->second, nullptr, second))
+        return fail(kUnsupported, "BLOCK_SCALE_QUANTIZE pair: both tensors must take a bf16 32-element fast form with an unpadded scale tensor");
+    info->kernel = DFGPU_BSQ_PAIR_BF16;
+    info->launches = 1;
+    info->scratch_bytes = 0;
+    return kOk;
+}
+
+extern "C" int dfgpu_block_scale_quantize_pair(const dfgpu_bsq_pair_params* p, void* const* tensors, void* scratch, void* stream_handle) {
+    (void)scratch;
+    if (!p || !tensors) return fail(kInvalidArgument, "BLOCK_SCALE_QUANTIZE pair: null params");
+    for (int i = 0; i < 6; ++i)
+        if (!tensors[i]) return fail(kInvalidArgument, "BLOCK_SCALE_QUANTIZE pair: null tensor pointer");
+    BsqTask first, second;
+    if (!pair_task(p->first, tensors, first) || !pair_task(p->second, tensors + 3, second))
+        return fail(kUnsupported, "BLOCK_SCALE_QUANTIZE pair: both tensors must take a bf16 32-element fast form with an unpadded scale tensor");
+    for (int i = 0; i < 6; ++i)
+        if (!aligned(tensors[i], i % 3 == 0 ? 16 : 8)) return fail(kInvalidArgument, "BLOCK_SCALE_QUANTIZE pair: X must be 16-byte aligned, Y and scale 8-byte aligned");
+    cudaError_t launched = launch_chained(bsq_pair_bf16_kernel, dim3(static_cast<unsigned>(first.ctas + second.ctas)), dim3(256), 0, as_stream(stream_handle), first, second);
+    if (launched != cudaSuccess) return fail(kExecutionFailed, "BLOCK_SCALE_QUANTIZE pair: launch failed: %s", cudaGetErrorString(launched));
+    return check_launch("BLOCK_SCALE_QUANTIZE pair");
+}
 
 extern "C" int dfgpu_query_block_scale_dequantize(const dfgpu_bsd_params* p, dfgpu_plan_info* info) {
     if (!p || !info) return fail(kInvalidArgument, "BLOCK_SCALE_DEQUANTIZE: null params");

@@ -66,5 +66,5 @@ int validate_epilogue(int count, const dfgpu_epilogue_step* steps, const dfgpu_t
 extern "C" const char* dfgpu_last_error(void) { return dfgpu::g_error; }
 // Bumped whenever a params struct, a pointer list or an enumeration changes.
 // 2: dfgpu_sdpa_params gained bias and alibi_mask. 3: it gained sink and block_mask (14 pointers); DFGPU_BF16X2.
-// 4: dfgpu_conv_fprop_pair.
+// 4: dfgpu_conv_fprop_pair, dfgpu_block_scale_quantize_pair.
 extern "C" int dfgpu_abi_version(void) { return 4; }

@@ -65,6 +65,10 @@ class BsqParams(C.Structure):
                 ("kernel", C.c_int32)]
 
 
+class BsqPairParams(C.Structure):
+    _fields_ = [("first", BsqParams), ("second", BsqParams)]
+
+
 class BsdParams(C.Structure):
     _fields_ = [("x", Tensor), ("scale", Tensor), ("y", Tensor), ("block", C.c_int64 * MAX_RANK),
                 ("block_count", C.c_int32), ("kernel", C.c_int32)]
@@ -109,6 +113,7 @@ class SdpaParams(C.Structure):
 EXPORTS = [
     "dfgpu_last_error", "dfgpu_abi_version",
     "dfgpu_query_block_scale_quantize", "dfgpu_block_scale_quantize",
+    "dfgpu_query_block_scale_quantize_pair", "dfgpu_block_scale_quantize_pair",
     "dfgpu_query_block_scale_dequantize", "dfgpu_block_scale_dequantize",
     "dfgpu_query_pointwise", "dfgpu_pointwise",
     "dfgpu_query_conv_fprop", "dfgpu_conv_fprop",
@@ -174,6 +179,11 @@ def query(name: str, params) -> PlanInfo:
 
 def block_scale_quantize(params, x, y, scale, scratch=None, stream=None):
     _call("dfgpu_block_scale_quantize", params, [x, y, scale], scratch, stream)
+
+
+def block_scale_quantize_pair(params, first, second, stream=None):
+    """first, second: (x, y, scale) device pointers of the two tensors."""
+    _call("dfgpu_block_scale_quantize_pair", params, [*first, *second], None, stream)
 
 
 def block_scale_dequantize(params, x, scale, y, scratch=None, stream=None):

@@ -112,6 +112,7 @@ std::uint32_t params_size_of(KernelOp op) {
         case KernelOp::kSdpaForward: return params_size<dfgpu_sdpa_params>();
         case KernelOp::kMatmulFp8: return params_size<dfgpu_matmul_fp8_params>();
         case KernelOp::kConvFpropPair: return params_size<dfgpu_conv_pair_params>();
+        case KernelOp::kBlockScaleQuantizePair: return params_size<dfgpu_bsq_pair_params>();
     }
     return 0;
 }
@@ -127,11 +128,12 @@ std::size_t tensor_slots(KernelOp op) {
         case KernelOp::kSdpaForward: return 14;
         case KernelOp::kMatmulFp8: return 7;
         case KernelOp::kConvFpropPair: return 8;
+        case KernelOp::kBlockScaleQuantizePair: return 6;
     }
     return 0;
 }
 
-constexpr std::uint32_t kLastOp = static_cast<std::uint32_t>(KernelOp::kConvFpropPair);
+constexpr std::uint32_t kLastOp = static_cast<std::uint32_t>(KernelOp::kBlockScaleQuantizePair);
 
 void write_binding(Writer& w, TensorBinding const& binding) {
     w.u32(static_cast<std::uint32_t>(binding.kind));
@@ -186,6 +188,9 @@ bool params_in_range(KernelParams const& params) {
         else if constexpr (std::is_same_v<T, dfgpu_conv_params>)
             return tensor_in_range(p.x) && tensor_in_range(p.w) && tensor_in_range(p.y) && tensor_in_range(p.extra[0]) && tensor_in_range(p.extra[1]) &&
                    p.epilogue_count >= 0 && p.epilogue_count <= DFGPU_MAX_EPILOGUE;
+        else if constexpr (std::is_same_v<T, dfgpu_bsq_pair_params>)
+            return tensor_in_range(p.first.x) && tensor_in_range(p.first.y) && tensor_in_range(p.first.scale) && tensor_in_range(p.second.x) && tensor_in_range(p.second.y) &&
+                   tensor_in_range(p.second.scale);
         else if constexpr (std::is_same_v<T, dfgpu_conv_pair_params>) {
             for (auto const* c : {&p.first, &p.second})
                 if (!(tensor_in_range(c->x) && tensor_in_range(c->w) && tensor_in_range(c->y) && tensor_in_range(c->extra[0]) && tensor_in_range(c->extra[1]) &&
@@ -245,6 +250,7 @@ Status read_plan(Reader& r, ArtifactInfo& info) {
             case KernelOp::kSdpaForward: step.params = read_params<dfgpu_sdpa_params>(r); break;
             case KernelOp::kMatmulFp8: step.params = read_params<dfgpu_matmul_fp8_params>(r); break;
             case KernelOp::kConvFpropPair: step.params = read_params<dfgpu_conv_pair_params>(r); break;
+            case KernelOp::kBlockScaleQuantizePair: step.params = read_params<dfgpu_bsq_pair_params>(r); break;
         }
         if (!r.ok || !params_in_range(step.params)) return bad("kernel plan: tensor descriptor out of range");
         if (step.kernel < 0 || step.launches < 1 || step.launches > 16) return bad("kernel plan: kernel id or launch count out of range");
@@ -294,6 +300,10 @@ dfgpu_tensor const* slot_descriptor(KernelStep const& step, std::size_t slot) {
         else if constexpr (std::is_same_v<T, dfgpu_pointwise_params>) { dfgpu_tensor const* t[] = {&p.in0, &p.in1, &p.out}; return slot < 3 ? t[slot] : nullptr; }
         else if constexpr (std::is_same_v<T, dfgpu_conv_params>) { dfgpu_tensor const* t[] = {&p.x, &p.w, &p.y, &p.extra[0], &p.extra[1]}; return slot < 5 ? t[slot] : nullptr; }
         else if constexpr (std::is_same_v<T, dfgpu_matmul_params>) { dfgpu_tensor const* t[] = {&p.a, &p.b, &p.c, &p.a_scale, &p.b_scale, &p.extra[0], &p.extra[1]}; return slot < 7 ? t[slot] : nullptr; }
+        else if constexpr (std::is_same_v<T, dfgpu_bsq_pair_params>) {
+            dfgpu_tensor const* t[] = {&p.first.x, &p.first.y, &p.first.scale, &p.second.x, &p.second.y, &p.second.scale};
+            return slot < 6 ? t[slot] : nullptr;
+        }
         else if constexpr (std::is_same_v<T, dfgpu_conv_pair_params>) {
             dfgpu_tensor const* t[] = {&p.first.x, &p.first.w, &p.second.w, &p.second.y, &p.first.extra[0], &p.first.extra[1], &p.second.extra[0], &p.second.extra[1]};
             return slot < 8 ? t[slot] : nullptr;

@@ -824,6 +824,37 @@ void fuse_convolution_pairs(Lowering& low) {
     }
 }
 
+// Two BLOCK_SCALE_QUANTIZE launches next to each other that do not touch each other's tensors become one launch
+// when the kernel library takes the pair (both in a bf16 fast form): these launches are ~10 us each, a third of it
+// ramp and tail, which one grid pays once.
+void fuse_quantize_pairs(Lowering& low) {
+    if (!low.options.fuse) return;
+    for (std::size_t s = 0; s + 1 < low.plan.steps.size(); ++s) {
+        auto& first = low.plan.steps[s];
+        auto& second = low.plan.steps[s + 1];
+        if (first.op != KernelOp::kBlockScaleQuantize || second.op != KernelOp::kBlockScaleQuantize) continue;
+        bool independent = true;
+        for (auto const& a : first.tensors)
+            for (auto const& b : second.tensors)
+                independent = independent && !(a.kind == b.kind && a.kind != TensorBinding::Kind::kAbsent && a.uid == b.uid);
+        if (!independent) continue;
+        dfgpu_bsq_pair_params pair{};
+        pair.first = std::get<dfgpu_bsq_params>(first.params);
+        pair.second = std::get<dfgpu_bsq_params>(second.params);
+        dfgpu_plan_info info{};
+        if (dfgpu_query_block_scale_quantize_pair(&pair, &info) != 0) continue;
+        KernelStep fused;
+        fused.op = KernelOp::kBlockScaleQuantizePair;
+        fused.label = first.label + "|" + second.label;
+        fused.nodes = first.nodes;
+        fused.nodes.insert(fused.nodes.end(), second.nodes.begin(), second.nodes.end());
+        fused.tensors = {first.tensors[0], first.tensors[1], first.tensors[2], second.tensors[0], second.tensors[1], second.tensors[2]};
+        fused.params = pair;
+        low.plan.steps[s] = std::move(fused);
+        low.plan.steps.erase(low.plan.steps.begin() + static_cast<std::ptrdiff_t>(s) + 1);
+    }
+}
+
 // Fills the conv-adapter metadata when the graph is the reference's single-node case; false otherwise (the generic
 // table stands).
 bool single_conv_metadata(SerializedGraph const& graph, CompileOptions const& options, Conv2DCompileMetadata& metadata) {
@@ -889,6 +920,7 @@ std::uint64_t kernel_alignment(KernelStep const& step, std::size_t slot) {
             return 0;
         case KernelOp::kMatmulFp8: return step.kernel == DFGPU_MATMUL_FP8_UMMA && slot <= 2 ? 16 : 0;
         case KernelOp::kConvFpropPair: return 16;
+        case KernelOp::kBlockScaleQuantizePair: return slot % 3 == 0 ? 16 : 8;
         default: return 0;
     }
 }
@@ -907,6 +939,7 @@ Status query_kernel_step(KernelStep& step, std::int64_t& scratch_bytes) {
         case KernelOp::kSdpaForward: code = dfgpu_query_sdpa_forward(&std::get<dfgpu_sdpa_params>(step.params), &info); break;
         case KernelOp::kMatmulFp8: code = dfgpu_query_matmul_fp8(&std::get<dfgpu_matmul_fp8_params>(step.params), &info); break;
         case KernelOp::kConvFpropPair: code = dfgpu_query_conv_fprop_pair(&std::get<dfgpu_conv_pair_params>(step.params), &info); break;
+        case KernelOp::kBlockScaleQuantizePair: code = dfgpu_query_block_scale_quantize_pair(&std::get<dfgpu_bsq_pair_params>(step.params), &info); break;
     }
     if (code != 0) return Status::failure(static_cast<ErrorCode>(code), step.label, dfgpu_last_error());
     step.kernel = info.kernel;
@@ -926,6 +959,7 @@ char const* kernel_op_name(KernelOp op) {
         case KernelOp::kSdpaForward: return "sdpa_forward";
         case KernelOp::kMatmulFp8: return "matmul_fp8";
         case KernelOp::kConvFpropPair: return "conv_fprop_pair";
+        case KernelOp::kBlockScaleQuantizePair: return "block_scale_quantize_pair";
     }
     return "?";
 }
@@ -1000,6 +1034,7 @@ Status compile_graph(SerializedGraph const& graph, CompileOptions const& options
     narrow_virtual_tensors(low);
     split_virtual_tensors(low);
     fuse_convolution_pairs(low);
+    fuse_quantize_pairs(low);
 
     // argument table: ascending UID, non-virtual tensors only
     Conv2DCompileMetadata metadata;

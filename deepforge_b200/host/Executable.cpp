@@ -187,6 +187,7 @@ Status Executable::run_steps(std::int64_t first, std::int64_t last, VariantPack&
             case KernelOp::kMatmul: code = dfgpu_matmul(&std::get<dfgpu_matmul_params>(step.params), pointers.data(), scratch, stream); break;
             case KernelOp::kSdpaForward: code = dfgpu_sdpa_forward(&std::get<dfgpu_sdpa_params>(step.params), pointers.data(), scratch, stream); break;
             case KernelOp::kMatmulFp8: code = dfgpu_matmul_fp8(&std::get<dfgpu_matmul_fp8_params>(step.params), pointers.data(), scratch, stream); break;
+            case KernelOp::kBlockScaleQuantizePair: code = dfgpu_block_scale_quantize_pair(&std::get<dfgpu_bsq_pair_params>(step.params), pointers.data(), scratch, stream); break;
             case KernelOp::kConvFpropPair: {
                 dfgpu_conv_pair_params params = std::get<dfgpu_conv_pair_params>(step.params);
                 if (index == first) params.first.reserved &= ~2;  // see kConvFprop above

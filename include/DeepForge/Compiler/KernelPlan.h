@@ -13,7 +13,7 @@
 
 namespace deepforge::compiler {
 
-enum class KernelOp : std::uint8_t { kBlockScaleQuantize, kBlockScaleDequantize, kPointwise, kConvFprop, kMatmul, kSdpaForward, kMatmulFp8, kConvFpropPair };
+enum class KernelOp : std::uint8_t { kBlockScaleQuantize, kBlockScaleDequantize, kPointwise, kConvFprop, kMatmul, kSdpaForward, kMatmulFp8, kConvFpropPair, kBlockScaleQuantizePair };
 
 struct TensorBinding {
     enum class Kind : std::uint8_t { kAbsent, kArgument, kWorkspace } kind = Kind::kAbsent;
@@ -22,7 +22,7 @@ struct TensorBinding {
 };
 
 using KernelParams = std::variant<dfgpu_bsq_params, dfgpu_bsd_params, dfgpu_pointwise_params, dfgpu_conv_params,
-                                  dfgpu_matmul_params, dfgpu_sdpa_params, dfgpu_matmul_fp8_params, dfgpu_conv_pair_params>;
+                                  dfgpu_matmul_params, dfgpu_sdpa_params, dfgpu_matmul_fp8_params, dfgpu_conv_pair_params, dfgpu_bsq_pair_params>;
 
 struct KernelStep {
     KernelOp op = KernelOp::kPointwise;

@@ -107,6 +107,18 @@ typedef struct dfgpu_bsq_params {
 int dfgpu_query_block_scale_quantize(const dfgpu_bsq_params*, dfgpu_plan_info*);
 int dfgpu_block_scale_quantize(const dfgpu_bsq_params*, void* const* tensors, void* scratch, void* stream);
 
+/* Two independent BLOCK_SCALE_QUANTIZE nodes (the operands of a block-scaled matmul) in one launch: the CTAs of
+   the first tensor, then those of the second, so that ramp and tail of these ~10 us kernels are paid once.
+   tensors: {X, Y, scale of first; X, Y, scale of second}. Both must be bf16 with 32-element blocks along one of
+   the two trailing axes and an unpadded scale tensor; X 16-byte aligned, Y and scale 8-byte aligned. The query
+   fails with 20 otherwise (the caller then launches the nodes one by one). Codes and scales are the same bits. */
+enum { DFGPU_BSQ_PAIR_AUTO = 0, DFGPU_BSQ_PAIR_BF16 = 1 };
+typedef struct dfgpu_bsq_pair_params {
+    dfgpu_bsq_params first, second;
+} dfgpu_bsq_pair_params;
+int dfgpu_query_block_scale_quantize_pair(const dfgpu_bsq_pair_params*, dfgpu_plan_info*);
+int dfgpu_block_scale_quantize_pair(const dfgpu_bsq_pair_params*, void* const* tensors, void* scratch, void* stream);
+
 /* ---- BLOCK_SCALE_DEQUANTIZE -----------------------------------------------
    Replaces emit_block_dequantize (lib/Compiler/SpecializedGraph.cpp:752-795).
    tensors: {X, scale, Y}. X E4M3, scale E8M0, Y f32/f16/bf16. block[] covers

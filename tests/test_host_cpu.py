@@ -156,26 +156,30 @@ def test_bottleneck_plan_fuses_to_three_launches_and_shares_workspace():
 
 def test_quantize_matmul_plans():
     # MXFP8 shape: the block-scaled tensor-core matmul reads codes and scales itself, no dequantize launch, no workspace
+    # and the two quantize nodes (bf16, independent of each other) share one launch
     exe = runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 128))
-    assert exe.launch_count == 3 and exe.workspace_size == 0
+    assert exe.launch_count == 2 and exe.workspace_size == 0
+    assert "block_scale_quantize_pair kernel=1 launches=1 [quantize_a|quantize_b]" in exe.plan_text()
     assert "matmul kernel=3" in exe.plan_text() and "[dequantize_b+dequantize_a+matmul]" in exe.plan_text()
     # only the bf16 tensor-core kernel fits (N is not a multiple of 128): dequantize stays a launch whose
     # output is stored as bf16 (exact), matmul on tcgen05
     exe = runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 64))
-    assert exe.launch_count == 5 and exe.workspace_size == 128 * 128 * 2 + 128 * 64 * 2
+    assert exe.launch_count == 4 and exe.workspace_size == 128 * 128 * 2 + 128 * 64 * 2
     assert "matmul kernel=2" in exe.plan_text()
     # shapes the tcgen05 kernel does not cover: the dequantize nodes are absorbed into the CUDA-core matmul
     for doc, options in ((graphs.c3_quantize_matmul(128, 128, 96), 0), (graphs.c3_quantize_matmul(128, 128, 128), runtime.NO_TENSOR_CORES)):
         absorbed = runtime.compile_graph(doc, options=options)
-        assert absorbed.launch_count == 3 and absorbed.workspace_size == 0
+        assert absorbed.launch_count == 2 and absorbed.workspace_size == 0
         assert "[dequantize_b+dequantize_a+matmul]" in absorbed.plan_text()
+    # FLOAT inputs keep one launch per quantize node (the shared launch is the bf16 form)
+    assert runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 128, io="FLOAT")).launch_count == 3
     unfused = runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 96), options=runtime.NO_FUSION)
     assert unfused.launch_count == 5 and unfused.workspace_size == 128 * 128 * 4 + 128 * 96 * 4
 
 
 def test_argument_table_is_sorted_with_clamped_alignment():
     # the reference's rule, clamp(element bytes, 1, 8), wherever no TMA-fed kernel reads the argument
-    exe = runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 128), options=runtime.NO_TENSOR_CORES)
+    exe = runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 128), options=runtime.NO_TENSOR_CORES | runtime.NO_FUSION)
     arguments = exe.arguments()
     assert [a["uid"] for a in arguments] == [1, 2, 3, 4, 5, 6, 9]
     by_uid = {a["uid"]: a for a in arguments}
@@ -184,8 +188,8 @@ def test_argument_table_is_sorted_with_clamped_alignment():
     # execute() refuses a misaligned variant pack before anything is launched
     exe = runtime.compile_graph(graphs.c3_quantize_matmul(128, 128, 128))
     by_uid = {a["uid"]: a for a in exe.arguments()}
-    assert by_uid[1]["alignment"] == 2 and by_uid[3]["alignment"] == 16 and by_uid[5]["alignment"] == 16 and by_uid[9]["alignment"] == 16
-    assert by_uid[4]["alignment"] == 4 and by_uid[6]["alignment"] == 4
+    assert by_uid[1]["alignment"] == 16 and by_uid[3]["alignment"] == 16 and by_uid[5]["alignment"] == 16 and by_uid[9]["alignment"] == 16
+    assert by_uid[4]["alignment"] == 8 and by_uid[6]["alignment"] == 8  # 4 for the matmul's scale loads, 8 for the shared quantize launch's stores
     assert by_uid[1]["access"] == "read" and by_uid[3]["access"] == "readwrite" and by_uid[9]["access"] == "write"
     assert by_uid[4]["size_bytes"] == 128 * 4
     decode = runtime.compile_graph(graphs.c5_paged_decode(2, 4, 2, 128, 8, 64, 256))
