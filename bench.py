@@ -499,22 +499,24 @@ def measure(name: str, steps: int, warmup: int, torch, device, distributed: bool
     barrier()
     e2e_ms = begin.elapsed_time(end)
 
-    # per-kernel pass: each launch group of the plan as its own graph, replayed back to back over the replicas
+    # per-kernel pass: each launch group of the plan over all replicas in turn as ONE graph (a stream of launches of
+    # that kernel, each on buffers the one before did not touch), replayed back to back
     plan = session.exe.steps()
     per_step = []
-    repeats = max(10, min(steps, 50))
+    count = len(session.replicas)
+    repeats = max(3, -(-max(10, min(steps, 50)) // count))
     for index in range(len(plan)):
-        step_graphs = session.capture(index, index + 1)
-        for i in range(3):
-            step_graphs[i % replicas].replay()
+        round_graph = session.capture_round(index, index + 1)
+        for i in range(2):
+            round_graph.replay()
         torch.cuda.synchronize(device)
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         begin.record(stream)
         for i in range(repeats):
-            step_graphs[i % replicas].replay()
+            round_graph.replay()
         end.record(stream)
         torch.cuda.synchronize(device)
-        per_step.append(begin.elapsed_time(end) / repeats)
+        per_step.append(begin.elapsed_time(end) / (repeats * count))
     from deepforge_b200 import dfgpu
     status = dfgpu.device_status()
     return {"workload": wl, "session": session, "device_ms": device_ms, "e2e_ms": e2e_ms, "h2d": h2d, "d2h": d2h, "clocks": clocks,

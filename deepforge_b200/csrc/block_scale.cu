@@ -304,91 +304,6 @@ bsq_row32_kernel(const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* _
     }
 }
 
-// bf16 input, fewer instructions per element (the generic row kernel above spends ~13 per element and is bound
-// by that, not by HBM): the amax runs on packed bf16 pairs, each lane of a block computes the scale of ONE of the
-// thread group's four chunks and the lanes trade results by shuffle, and the tiny-negative fix-up of the E4M3
-// encode (cvt rounds -1e-9 to -0 = 0x80, the reference's search to +0 = 0x00) is applied only to chunks whose
-// packed codes contain a 0x80 byte, which random data almost never does.
-__device__ __forceinline__ bool has_byte_0x80(uint32_t word) {
-    const uint32_t t = word ^ 0x80808080u;  // a byte is zero exactly where the code was 0x80
-    return ((t - 0x01010101u) & ~t & 0x80808080u) != 0u;
-}
-
-// One tile of 256 threads x 4 chunks x 8 elements; `tile` is the tile's index along the flattened tensor.
-__device__ __forceinline__ void bsq_row32_bf16_tile(int64_t tile, const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* __restrict__ scale,
-                                                    int64_t rows, int64_t cols, int reordered, int64_t scale_k_extent) {
-    constexpr int kChunks = 4;
-    const int64_t total = rows * cols;
-    const int64_t tile0 = tile * (256 * 8 * kChunks);
-    const int lane = threadIdx.x & 31;
-    uint4 raw[kChunks];
-    bool live[kChunks];
-#pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
-        const int64_t element = tile0 + (static_cast<int64_t>(c) * 256 + threadIdx.x) * 8;
-        live[c] = element < total;
-        raw[c] = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + (live[c] ? element : 0)));
-    }
-    // |x| maxima as bf16 bit patterns (integer order = magnitude order, NaN patterns are the largest)
-    uint32_t amax16[kChunks];
-#pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
-        const uint32_t a = raw[c].x & 0x7fff7fffu, b = raw[c].y & 0x7fff7fffu, d = raw[c].z & 0x7fff7fffu, e = raw[c].w & 0x7fff7fffu;
-        const uint32_t m = __vmaxu2(__vmaxu2(a, b), __vmaxu2(d, e));
-        uint32_t best = max(m & 0xffffu, m >> 16);
-        best = max(best, __shfl_xor_sync(0xffffffffu, best, 1));
-        best = max(best, __shfl_xor_sync(0xffffffffu, best, 2));
-        amax16[c] = best;
-    }
-    // lane q of a block (q = lane & 3) turns chunk q's maximum into its scale code; the four lanes then exchange
-    const int q = lane & 3;
-    const uint32_t mine = q == 0 ? amax16[0] : (q == 1 ? amax16[1] : (q == 2 ? amax16[2] : amax16[3]));
-    const uint32_t my_code = scale_code_from_amax_bits(mine << 16);
-    const int64_t k_blocks = cols >> 5;
-#pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
-        const int64_t element = tile0 + (static_cast<int64_t>(c) * 256 + threadIdx.x) * 8;
-        const uint32_t code = __shfl_sync(0xffffffffu, my_code, (lane & ~3) + c);
-        uint2 packed;
-        if (code == 0xffu) {
-            packed = make_uint2(0x7f7f7f7fu, 0x7f7f7f7fu);
-        } else {
-            const float reciprocal = reciprocal_e8m0(code);
-            const uint32_t w[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
-            uint32_t pair[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-                pair[i] = cvt_e4m3_pair(__fmul_rn(__uint_as_float(w[i] << 16), reciprocal), __fmul_rn(__uint_as_float(w[i] & 0xffff0000u), reciprocal));
-            packed = make_uint2(pair[0] | (pair[1] << 16), pair[2] | (pair[3] << 16));
-            if (has_byte_0x80(packed.x) || has_byte_0x80(packed.y)) {
-                // a product rounded to -0: redo the chunk with the exact rule (tiny negatives -> +0, -0.0 stays -0)
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    pair[i] = encode_e4m3_pair(__fmul_rn(__uint_as_float(w[i] << 16), reciprocal), __fmul_rn(__uint_as_float(w[i] & 0xffff0000u), reciprocal));
-                packed = make_uint2(pair[0] | (pair[1] << 16), pair[2] | (pair[3] << 16));
-            }
-        }
-        if (live[c]) *reinterpret_cast<uint2*>(y + element) = packed;
-        if (live[c] && q == 0) {
-            const int64_t block_index = element >> 5;
-            if (reordered) {
-                const int64_t row = block_index / k_blocks, kb = block_index - row * k_blocks;
-                scale[f8_128x4_offset(0, row, kb, rows, scale_k_extent)] = static_cast<uint8_t>(code);
-            } else {
-                scale[block_index] = static_cast<uint8_t>(code);
-            }
-        }
-    }
-}
-
-__global__ void __launch_bounds__(256)
-bsq_row32_bf16_kernel(const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* __restrict__ scale,
-                      int64_t rows, int64_t cols, int reordered, int64_t scale_k_extent) {
-    chain_release();
-    chain_wait();
-    bsq_row32_bf16_tile(blockIdx.x, x, y, scale, rows, cols, reordered, scale_k_extent);
-}
-
 // ---- column kernel: block of 32 along the second-to-last axis -------------------
 // X is [batch, K, N] packed; a thread owns 8 rows x VEC columns and keeps the raw
 // 16-byte loads in registers (VEC = 8 for 16-bit inputs, 4 for f32), so X is read
@@ -531,107 +446,43 @@ bsq_col32_kernel(const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* _
     }
 }
 
-// bf16 input, same economies as the bf16 row kernel: packed maxima, each of the CTA's four warps derives the
-// scale codes of two of the eight column groups and the warps trade them through shared memory, and the exact
-// negative-underflow rule only runs for rows whose codes contain a 0x80 byte.
-// Shared memory of one 128-thread column tile.
-struct BsqColumnShared {
-    uint32_t partial[4][4][32];  // [row group][column pair][lane]: packed |x| maxima of two columns
-    uint32_t codes[8][32];       // [column][lane]
+// ---- bf16 input: the row form, the column form and pairs of either in one kernel ---------------------------
+// A CTA of 256 threads encodes one tile of 16 KB of input: 8192 consecutive elements (row form), or 32 rows x 256
+// columns (column form). A grid is the tiles of one tensor, or the tiles of two independent tensors back to back
+// (the two operands of a block-scaled matmul): one launch, one ramp and one tail for both.
+//
+// Instruction issue, not HBM, bounds these kernels (the generic kernels above spend ~13 instructions per element),
+// so the encode is kept short and free of barriers and shared memory:
+//   * the amax runs on packed bf16 bit patterns (max.u16x2), and the scale code comes from those bits by integer
+//     arithmetic: amax = (1 + f/128) * 2^E with a 7-bit fraction f gives amax/448 = ((128 + f)/224) * 2^(E-8), whose
+//     ceil(log2) is E-8 for f <= 96 and E-7 above (128+f is never close enough to 224 for the f32 rounding of the
+//     quotient to matter), so code = max(0, ((bits + 31) >> 7) - 8); zero, infinity and NaN are set apart;
+//   * elements are scaled as packed bf16 pairs (a product with a power of two is exact in bf16 wherever the E4M3
+//     code is not zero anyway) and widened only for the hardware e4m3x2 convert;
+//   * the lanes that share a block meet by shuffle, one lane derives each block's scale and the others get it by
+//     shuffle again;
+//   * the tiny-negative fix-up of the E4M3 encode (cvt rounds -1e-9 to -0 = 0x80, the reference's search to
+//     +0 = 0x00) and the plain f32 path for blocks with an infinite or NaN amax run behind ONE warp-uniform branch per
+//     tile, taken only where some packed code is 0x80 or some scale code is 0xfe/0xff, which random data almost never has.
+constexpr int kTileThreads = 256;
+
+// n / d for 0 <= n < 2^31 as a multiply and a shift (d >= 1): m = ceil(2^(31+L) / d) with L = ceil(log2 d).
+struct FastDivisor {
+    uint32_t divisor, multiplier, shift;
 };
 
-// One tile of 128 threads: 32 rows x 256 columns. `thread` is 0..127, (tile_x, kb, batch) the tile's coordinates and
-// `sync` the barrier over exactly those 128 threads.
-template <typename Sync>
-__device__ __forceinline__ void bsq_col32_bf16_tile(int thread, int64_t tile_x, int64_t kb, int64_t batch, BsqColumnShared& shared, Sync sync,
-                                                    const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* __restrict__ scale,
-                                                    int64_t k_extent, int64_t n_extent, int reordered, int64_t scale_k_extent) {
-    constexpr int kRows = 8;
-    auto& partial = shared.partial;
-    auto& codes = shared.codes;
-    const int lane = thread & 31, group = thread >> 5;
-    const int64_t column = (tile_x * 32 + lane) * 8;
-    const bool live = column < n_extent;
-    const int64_t base = (batch * k_extent + kb * 32 + group * kRows) * n_extent + (live ? column : 0);
-    const uint16_t* xp = static_cast<const uint16_t*>(x) + base;
-    uint4 raw[kRows];
-#pragma unroll
-    for (int r = 0; r < kRows; ++r) raw[r] = __ldg(reinterpret_cast<const uint4*>(xp + r * n_extent));
-    uint32_t best[4] = {0, 0, 0, 0};
-#pragma unroll
-    for (int r = 0; r < kRows; ++r) {
-        best[0] = __vmaxu2(best[0], raw[r].x & 0x7fff7fffu);
-        best[1] = __vmaxu2(best[1], raw[r].y & 0x7fff7fffu);
-        best[2] = __vmaxu2(best[2], raw[r].z & 0x7fff7fffu);
-        best[3] = __vmaxu2(best[3], raw[r].w & 0x7fff7fffu);
-    }
-#pragma unroll
-    for (int c = 0; c < 4; ++c) partial[group][c][lane] = best[c];
-    sync();
-    {
-        // warp `group` owns column pair `group` of every lane's eight columns
-        const uint32_t m = __vmaxu2(__vmaxu2(partial[0][group][lane], partial[1][group][lane]), __vmaxu2(partial[2][group][lane], partial[3][group][lane]));
-        codes[2 * group][lane] = scale_code_from_amax_bits((m & 0xffffu) << 16);
-        codes[2 * group + 1][lane] = scale_code_from_amax_bits(m & 0xffff0000u);
-    }
-    sync();
-    if (!live) return;
-    uint32_t code[8];
-    float reciprocal[8];
-    bool any_nan = false;
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        code[c] = codes[c][lane];
-        reciprocal[c] = reciprocal_e8m0(code[c]);
-        any_nan = any_nan || code[c] == 0xffu;
-    }
-    const int64_t k_blocks = k_extent >> 5;
-    if (group == 0) {
-        if (reordered) {
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                scale[f8_128x4_offset(batch, column + c, kb, n_extent, scale_k_extent)] = static_cast<uint8_t>(code[c]);
-        } else {
-            *reinterpret_cast<uint2*>(scale + (batch * k_blocks + kb) * n_extent + column) =
-                make_uint2(code[0] | (code[1] << 8) | (code[2] << 16) | (code[3] << 24), code[4] | (code[5] << 8) | (code[6] << 16) | (code[7] << 24));
-        }
-    }
-#pragma unroll
-    for (int r = 0; r < kRows; ++r) {
-        const uint32_t w[4] = {raw[r].x, raw[r].y, raw[r].z, raw[r].w};
-        uint32_t pair[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-            pair[i] = cvt_e4m3_pair(__fmul_rn(__uint_as_float(w[i] << 16), reciprocal[2 * i]), __fmul_rn(__uint_as_float(w[i] & 0xffff0000u), reciprocal[2 * i + 1]));
-        uint2 packed = make_uint2(pair[0] | (pair[1] << 16), pair[2] | (pair[3] << 16));
-        if (any_nan || has_byte_0x80(packed.x) || has_byte_0x80(packed.y)) {
-            // exact rule for this row: NaN-scaled columns are all 0x7f, tiny negatives go to +0, -0.0 stays -0
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t both = encode_e4m3_pair(__fmul_rn(__uint_as_float(w[i] << 16), reciprocal[2 * i]), __fmul_rn(__uint_as_float(w[i] & 0xffff0000u), reciprocal[2 * i + 1]));
-                const uint32_t lo = code[2 * i] == 0xffu ? 0x7fu : (both & 0xffu), hi = code[2 * i + 1] == 0xffu ? 0x7fu : (both >> 8);
-                pair[i] = lo | (hi << 8);
-            }
-            packed = make_uint2(pair[0] | (pair[1] << 16), pair[2] | (pair[3] << 16));
-        }
-        *reinterpret_cast<uint2*>(y + base + r * n_extent) = packed;
-    }
+FastDivisor make_fast_divisor(uint32_t d) {
+    if (d <= 1) return FastDivisor{1, 0, 0};
+    uint32_t log = 0;
+    while ((1ull << log) < d) ++log;
+    const uint64_t power = 1ull << (31 + log);
+    return FastDivisor{d, static_cast<uint32_t>((power + d - 1) / d), log - 1};
 }
 
-__global__ void __launch_bounds__(128)
-bsq_col32_bf16_kernel(const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* __restrict__ scale,
-                      int64_t k_extent, int64_t n_extent, int reordered, int64_t scale_k_extent) {
-    __shared__ BsqColumnShared shared;
-    chain_release();
-    chain_wait();
-    bsq_col32_bf16_tile(threadIdx.x, blockIdx.x, blockIdx.y, blockIdx.z, shared, [] { __syncthreads(); }, x, y, scale, k_extent, n_extent, reordered, scale_k_extent);
+__device__ __forceinline__ uint32_t fast_divide(uint32_t n, const FastDivisor& d) {
+    return d.divisor == 1 ? n : __umulhi(n, d.multiplier) >> d.shift;
 }
 
-// ---- two quantizations in one launch ------------------------------------------------------------------
-// Independent BLOCK_SCALE_QUANTIZE nodes of one graph (the two operands of a block-scaled matmul) as ONE grid: the
-// CTAs of the first tensor, then the CTAs of the second. Each launch of these kernels is only ~10 us long, a third
-// of which is ramp and tail; one grid pays them once. A CTA has 256 threads: one row tile, or two column tiles
-// (threads 0-127 and 128-255, each pair with its own shared memory and its own named barrier).
 struct BsqTask {
     const void* x;
     uint8_t* y;
@@ -640,34 +491,223 @@ struct BsqTask {
     int64_t scale_k_extent;
     int32_t reordered;
     int32_t column_form;
-    int32_t tiles_x, tiles_y;  // column form: tiles along N and K (the batch axis is the slowest)
-    int64_t tiles;             // row tiles, or column tiles (two per CTA)
-    int64_t ctas;
+    uint32_t tiles_x, tiles_y;  // column form: tiles along N and K (the batch axis is the slowest)
+    uint32_t tiles;
+    FastDivisor k_blocks;       // row form with a reordered scale: blocks per row, when every block index is < 2^29
+    int32_t narrow_blocks;
+    int32_t narrow_scale;       // a scale tensor of less than 2^30 bytes: 32-bit offsets into a reordered layout
 };
 
-__device__ __forceinline__ void bsq_pair_run(const BsqTask& task, int64_t cta, BsqColumnShared (&shared)[2]) {
-    if (!task.column_form) {
-        if (cta < task.tiles) bsq_row32_bf16_tile(cta, task.x, task.y, task.scale, task.rows, task.cols, task.reordered, task.scale_k_extent);
-        return;
-    }
-    const int side = threadIdx.x >> 7;
-    const int64_t tile = 2 * cta + side;
-    if (tile >= task.tiles) return;  // (all 128 threads of the side together: nobody is left at its barrier)
-    const int64_t tile_x = tile % task.tiles_x, rest = tile / task.tiles_x;
-    const int64_t kb = rest % task.tiles_y, batch = rest / task.tiles_y;
-    const int barrier = 1 + side;
-    bsq_col32_bf16_tile(threadIdx.x & 127, tile_x, kb, batch, shared[side], [barrier] { asm volatile("bar.sync %0, 128;" ::"r"(barrier) : "memory"); },
-                        task.x, task.y, task.scale, task.rows, task.cols, task.reordered, task.scale_k_extent);
+// f8_128x4_offset() in 32-bit arithmetic, for scale tensors below 2^30 bytes.
+__device__ __forceinline__ uint32_t f8_128x4_offset32(uint32_t leading, uint32_t m, uint32_t k, uint32_t m_extent, uint32_t k_extent) {
+    const uint32_t m_blocks = m_extent >> 7, k_blocks = k_extent >> 2;
+    return (((leading * m_blocks + (m >> 7)) * k_blocks + (k >> 2)) << 9) + ((m & 31u) << 4) + (((m >> 5) & 3u) << 2) + (k & 3u);
 }
 
-__global__ void __launch_bounds__(256)
-bsq_pair_bf16_kernel(BsqTask first, BsqTask second) {
-    __shared__ BsqColumnShared shared[2];
+// Bit 7 of some byte of the result is set iff a byte of `codes` is 0x80 (callers OR several of these and mask once).
+__device__ __forceinline__ uint32_t marks_of_0x80(uint32_t codes) {
+    const uint32_t t = codes ^ 0x80808080u;  // a byte is zero exactly where the code was 0x80
+    return (t - 0x01010101u) & ~t;
+}
+
+// Scale code of a block from the bf16 bit pattern of its |x| maximum (see above); equal to
+// scale_code_from_amax_bits(bits << 16) for all 32768 patterns.
+__device__ __forceinline__ uint32_t scale_code_from_bf16_amax(uint32_t bits) {
+    const int code = static_cast<int>((bits + 31u) >> 7) - 8;
+    uint32_t result = static_cast<uint32_t>(code < 0 ? 0 : code);
+    if (bits == 0u) result = 127u;
+    if (bits >= 0x7f80u) result = bits > 0x7f80u ? 0xffu : 0xfeu;
+    return result;
+}
+
+// Unsigned maximum of the two 16-bit halves (one instruction; the __vmaxu2 intrinsic is a software sequence here).
+__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+// Two bf16 values (one word) times their two power-of-two reciprocals (bf16 pair) -> two E4M3 codes, low element in
+// the low byte. Only meaningful for finite scales below 2^127 (codes 0..253).
+__device__ __forceinline__ uint32_t scale_and_cvt_pair(uint32_t word, uint32_t reciprocals) {
+    const uint32_t product = mul_bf16x2(word, reciprocals);
+    return cvt_e4m3_pair(__uint_as_float(product << 16), __uint_as_float(product & 0xffff0000u));
+}
+
+// The exact rule for one word, whatever the codes: NaN-scaled elements are 0x7f, tiny negatives go to +0, -0.0 stays -0.
+__device__ __forceinline__ uint32_t encode_pair_exact(uint32_t word, uint32_t code_lo, uint32_t code_hi) {
+    const uint32_t both = encode_e4m3_pair(__fmul_rn(__uint_as_float(word << 16), reciprocal_e8m0(code_lo)),
+                                           __fmul_rn(__uint_as_float(word & 0xffff0000u), reciprocal_e8m0(code_hi)));
+    const uint32_t lo = code_lo == 0xffu ? 0x7fu : (both & 0xffu), hi = code_hi == 0xffu ? 0x7fu : (both >> 8);
+    return lo | (hi << 8);
+}
+
+// Row form: thread t holds chunks (c * 256 + t) of 8 elements, c = 0..3; four lanes make one block of 32.
+__device__ __forceinline__ void encode_row_tile(const BsqTask& task, uint32_t tile) {
+    const int lane = threadIdx.x & 31;
+    const int64_t tile0 = static_cast<int64_t>(tile) * 8192, left = task.rows * task.cols - tile0;
+    const uint32_t count = static_cast<uint32_t>(left < 8192 ? left : 8192);  // elements of this tile
+    const uint4* const x_tile = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(task.x) + tile0);
+    uint4 raw[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const uint32_t chunk = static_cast<uint32_t>(c) * 256u + threadIdx.x;
+        raw[c] = chunk * 8u < count ? __ldg(x_tile + chunk) : make_uint4(0, 0, 0, 0);
+    }
+    // |x| maxima as bf16 bit patterns (integer order = magnitude order, NaN patterns are the largest)
+    uint32_t amax16[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const uint32_t a = raw[c].x & 0x7fff7fffu, b = raw[c].y & 0x7fff7fffu, d = raw[c].z & 0x7fff7fffu, e = raw[c].w & 0x7fff7fffu;
+        uint32_t m = max_u16x2(max_u16x2(a, b), max_u16x2(d, e));
+        m = max_u16x2(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        m = max_u16x2(m, __shfl_xor_sync(0xffffffffu, m, 2));
+        amax16[c] = max(m & 0xffffu, m >> 16);
+    }
+    // lane q of a block (q = lane & 3) turns chunk q's maximum into its scale code; the four lanes then exchange
+    const int q = lane & 3;
+    const uint32_t mine = q == 0 ? amax16[0] : (q == 1 ? amax16[1] : (q == 2 ? amax16[2] : amax16[3]));
+    const uint32_t my_code = scale_code_from_bf16_amax(mine);
+    uint32_t code[4], worst = 0, marks = 0;
+    uint2 packed[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        code[c] = __shfl_sync(0xffffffffu, my_code, (lane & ~3) + c);
+        worst = max(worst, code[c]);
+        const uint32_t reciprocals = ((254u - code[c]) << 7) * 0x00010001u;  // 2^(127 - code) twice, as bf16
+        const uint32_t p0 = scale_and_cvt_pair(raw[c].x, reciprocals), p1 = scale_and_cvt_pair(raw[c].y, reciprocals);
+        const uint32_t p2 = scale_and_cvt_pair(raw[c].z, reciprocals), p3 = scale_and_cvt_pair(raw[c].w, reciprocals);
+        packed[c] = make_uint2(p0 | (p1 << 16), p2 | (p3 << 16));
+        marks |= marks_of_0x80(packed[c].x) | marks_of_0x80(packed[c].y);
+    }
+    const bool redo = (marks & 0x80808080u) != 0u || worst >= 0xfeu;
+    if (__any_sync(0xffffffffu, redo)) {
+        if (redo) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                packed[c] = make_uint2(encode_pair_exact(raw[c].x, code[c], code[c]) | (encode_pair_exact(raw[c].y, code[c], code[c]) << 16),
+                                       encode_pair_exact(raw[c].z, code[c], code[c]) | (encode_pair_exact(raw[c].w, code[c], code[c]) << 16));
+        }
+    }
+    uint8_t* const y_tile = task.y + tile0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const uint32_t offset = (static_cast<uint32_t>(c) * 256u + threadIdx.x) * 8u;
+        if (offset < count) *reinterpret_cast<uint2*>(y_tile + offset) = packed[c];
+    }
+    if (q == 0) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const uint32_t offset = (static_cast<uint32_t>(c) * 256u + threadIdx.x) * 8u;
+            if (offset >= count) continue;
+            if (!task.reordered) {
+                task.scale[(tile0 + offset) >> 5] = static_cast<uint8_t>(code[c]);
+            } else if (task.narrow_blocks && task.narrow_scale) {
+                const uint32_t block_index = tile * 256u + (offset >> 5);
+                const uint32_t row = fast_divide(block_index, task.k_blocks), kb = block_index - row * task.k_blocks.divisor;
+                task.scale[f8_128x4_offset32(0, row, kb, static_cast<uint32_t>(task.rows), static_cast<uint32_t>(task.scale_k_extent))] = static_cast<uint8_t>(code[c]);
+            } else {
+                const int64_t block_index = (tile0 + offset) >> 5, k_blocks = task.cols >> 5;
+                const int64_t row = block_index / k_blocks, kb = block_index - row * k_blocks;
+                task.scale[f8_128x4_offset(0, row, kb, task.rows, task.scale_k_extent)] = static_cast<uint8_t>(code[c]);
+            }
+        }
+    }
+}
+
+// Column form: warp w holds columns 32w..32w+31 of the tile's 256, lane l rows (l >> 2) + 8j (j = 0..3) and the 8
+// columns 8(l & 3).. of them. The eight row groups of a warp meet by shuffle, lane l derives the scale code of column
+// (l >> 2) of its lane group's eight, and the lanes of equal (l & 3) trade the eight codes by shuffle again.
+__device__ __forceinline__ void encode_column_tile(const BsqTask& task, uint32_t tile) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int group = lane >> 2, part = lane & 3;
+    const uint32_t tile_x = tile % task.tiles_x, rest = tile / task.tiles_x;
+    const uint32_t kb = rest % task.tiles_y, batch = rest / task.tiles_y;
+    const int64_t column = static_cast<int64_t>(tile_x) * 256 + warp * 32 + part * 8;
+    const bool live = column < task.cols;
+    const int64_t row0 = static_cast<int64_t>(batch) * task.rows + static_cast<int64_t>(kb) * 32 + group;  // counted over all batch entries
+    const int64_t first = row0 * task.cols + (live ? column : 0), row_step = 8 * task.cols;
+    const uint16_t* const x = static_cast<const uint16_t*>(task.x) + first;
+    uint4 raw[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) raw[r] = __ldg(reinterpret_cast<const uint4*>(x + r * row_step));
+    uint32_t best[4];
+    best[0] = raw[0].x & 0x7fff7fffu;
+    best[1] = raw[0].y & 0x7fff7fffu;
+    best[2] = raw[0].z & 0x7fff7fffu;
+    best[3] = raw[0].w & 0x7fff7fffu;
+#pragma unroll
+    for (int r = 1; r < 4; ++r) {
+        best[0] = max_u16x2(best[0], raw[r].x & 0x7fff7fffu);
+        best[1] = max_u16x2(best[1], raw[r].y & 0x7fff7fffu);
+        best[2] = max_u16x2(best[2], raw[r].z & 0x7fff7fffu);
+        best[3] = max_u16x2(best[3], raw[r].w & 0x7fff7fffu);
+    }
+#pragma unroll
+    for (int offset = 4; offset < 32; offset <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) best[i] = max_u16x2(best[i], __shfl_xor_sync(0xffffffffu, best[i], offset));
+    }
+    // column `group` of this lane's eight: word group >> 1, low or high half
+    const uint32_t word = (group >> 1) == 0 ? best[0] : ((group >> 1) == 1 ? best[1] : ((group >> 1) == 2 ? best[2] : best[3]));
+    const uint32_t my_code = scale_code_from_bf16_amax((group & 1) ? (word >> 16) : (word & 0xffffu));
+    uint32_t code[8], worst = 0;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        code[c] = __shfl_sync(0xffffffffu, my_code, c * 4 + part);
+        worst = max(worst, code[c]);
+    }
+    uint32_t reciprocals[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) reciprocals[i] = ((254u - code[2 * i]) << 7) | ((254u - code[2 * i + 1]) << 23);
+    uint2 packed[4];
+    uint32_t marks = 0;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const uint32_t p0 = scale_and_cvt_pair(raw[r].x, reciprocals[0]), p1 = scale_and_cvt_pair(raw[r].y, reciprocals[1]);
+        const uint32_t p2 = scale_and_cvt_pair(raw[r].z, reciprocals[2]), p3 = scale_and_cvt_pair(raw[r].w, reciprocals[3]);
+        packed[r] = make_uint2(p0 | (p1 << 16), p2 | (p3 << 16));
+        marks |= marks_of_0x80(packed[r].x) | marks_of_0x80(packed[r].y);
+    }
+    const bool redo = (marks & 0x80808080u) != 0u || worst >= 0xfeu;
+    if (__any_sync(0xffffffffu, redo)) {
+        if (redo) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+                packed[r] = make_uint2(encode_pair_exact(raw[r].x, code[0], code[1]) | (encode_pair_exact(raw[r].y, code[2], code[3]) << 16),
+                                       encode_pair_exact(raw[r].z, code[4], code[5]) | (encode_pair_exact(raw[r].w, code[6], code[7]) << 16));
+        }
+    }
+    if (!live) return;
+    uint8_t* const out = task.y + first;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) *reinterpret_cast<uint2*>(out + r * row_step) = packed[r];
+    // (lane `group` == column index: every lane stores the one code it derived)
+    if (task.reordered && task.narrow_scale) {
+        task.scale[f8_128x4_offset32(batch, static_cast<uint32_t>(column) + group, kb, static_cast<uint32_t>(task.cols), static_cast<uint32_t>(task.scale_k_extent))] = static_cast<uint8_t>(my_code);
+    } else if (task.reordered) {
+        task.scale[f8_128x4_offset(batch, column + group, kb, task.cols, task.scale_k_extent)] = static_cast<uint8_t>(my_code);
+    } else {
+        task.scale[(static_cast<int64_t>(batch) * (task.rows >> 5) + kb) * task.cols + column + group] = static_cast<uint8_t>(my_code);
+    }
+}
+
+// (five CTAs per SM: 48 registers; more warps hide the load latency better than the few spilled bytes cost)
+__global__ void __launch_bounds__(kTileThreads, 5)
+bsq_tile_bf16_kernel(const BsqTask first, const BsqTask second) {
     chain_release();
     chain_wait();
-    const int64_t cta = blockIdx.x;
-    if (cta < first.ctas) bsq_pair_run(first, cta, shared);
-    else bsq_pair_run(second, cta - first.ctas, shared);
+    const bool in_first = blockIdx.x < first.tiles;
+    const BsqTask task = in_first ? first : second;
+    const uint32_t tile = in_first ? blockIdx.x : blockIdx.x - first.tiles;
+    if (task.column_form) encode_column_tile(task, tile);
+    else encode_row_tile(task, tile);
 }
 
 // ---- dequantize -------------------------------------------------------------------
@@ -760,6 +800,7 @@ struct BsqPlan {
     bool needs_fill = false;
     ScaleLayout layout{};
     int64_t rows = 0, cols = 0, batch = 0, scale_k_extent = 0;
+    int64_t scale_bytes = 0;  // (E8M0: one byte per slot, padding slots included)
 };
 
 int plan_bsq(const dfgpu_bsq_params& p, BsqPlan& plan) {
@@ -786,6 +827,7 @@ int plan_bsq(const dfgpu_bsq_params& p, BsqPlan& plan) {
         return fail(kInvalidLayout, "BLOCK_SCALE_QUANTIZE: scale is not a valid F8_128x4 layout");
     plan.axis = axis;
     plan.needs_fill = !scale_matches;
+    plan.scale_bytes = element_count(p.scale);
 
     bool packed = is_packed_row_major(p.x) && is_packed_row_major(p.y);
     for (int i = 0; i + 2 < rank; ++i)
@@ -821,6 +863,45 @@ int plan_bsq(const dfgpu_bsq_params& p, BsqPlan& plan) {
     }
     plan.kernel = kernel;
     return kOk;
+}
+
+// The bf16 tile kernel's view of one tensor whose plan is the row or the column form.
+BsqTask tile_task(const BsqPlan& plan, const void* x, uint8_t* y, uint8_t* scale) {
+    BsqTask task{};
+    task.x = x;
+    task.y = y;
+    task.scale = scale;
+    task.rows = plan.rows;
+    task.cols = plan.cols;
+    task.scale_k_extent = plan.scale_k_extent;
+    task.reordered = plan.layout.reordered;
+    task.k_blocks = make_fast_divisor(1);
+    task.narrow_scale = plan.scale_bytes > 0 && plan.scale_bytes < (1ll << 30) ? 1 : 0;
+    if (plan.kernel == DFGPU_BSQ_ROW32) {
+        task.column_form = 0;
+        task.tiles = static_cast<uint32_t>((plan.rows * plan.cols + 8191) / 8192);
+        const int64_t k_blocks = plan.cols / 32, blocks = plan.rows * k_blocks;
+        task.narrow_blocks = blocks < (1ll << 29) ? 1 : 0;
+        if (task.narrow_blocks) task.k_blocks = make_fast_divisor(static_cast<uint32_t>(k_blocks));
+    } else {
+        task.column_form = 1;
+        task.tiles_x = static_cast<uint32_t>((plan.cols + 255) / 256);
+        task.tiles_y = static_cast<uint32_t>(plan.rows / 32);
+        task.tiles = task.tiles_x * task.tiles_y * static_cast<uint32_t>(plan.batch);
+    }
+    return task;
+}
+
+// One CTA per tile: the tiles of one launch must fit a grid.
+bool tile_task_fits(const BsqPlan& plan) {
+    const int64_t tiles = plan.kernel == DFGPU_BSQ_ROW32 ? (plan.rows * plan.cols + 8191) / 8192 : ((plan.cols + 255) / 256) * (plan.rows / 32) * plan.batch;
+    return tiles > 0 && tiles <= (1ll << 30);
+}
+
+int launch_tiles(const BsqTask& first, const BsqTask& second, cudaStream_t stream, const char* what) {
+    cudaError_t status = launch_chained(bsq_tile_bf16_kernel, dim3(first.tiles + second.tiles), dim3(kTileThreads), 0, stream, first, second);
+    if (status != cudaSuccess) return fail(kExecutionFailed, "%s: launch failed: %s", what, cudaGetErrorString(status));
+    return check_launch(what);
 }
 
 }  // namespace
@@ -867,13 +948,14 @@ extern "C" int dfgpu_block_scale_quantize(const dfgpu_bsq_params* p, void* const
     int kernel = plan.kernel;
     if (kernel == DFGPU_BSQ_ROW32 && !(aligned(x, 16) && aligned(y, 8))) kernel = DFGPU_BSQ_GENERIC;
     if (kernel == DFGPU_BSQ_COL32 && !(aligned(x, 16) && aligned(y, 8) && aligned(scale, 8))) kernel = DFGPU_BSQ_GENERIC;
+    if (p->x.dtype == DFGPU_BF16 && kernel != DFGPU_BSQ_GENERIC && !tile_task_fits(plan)) kernel = DFGPU_BSQ_GENERIC;
 
     if (kernel == DFGPU_BSQ_ROW32) {
         int64_t threads = (plan.rows * plan.cols / 8 + 3) / 4;  // 4 chunks of 8 elements per thread
         unsigned grid = static_cast<unsigned>((threads + 255) / 256);
         int reordered = plan.layout.reordered;
         if (p->x.dtype == DFGPU_F32) launch_chained(bsq_row32_kernel<float>, dim3(grid), dim3(256), 0, stream, x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
-        else if (p->x.dtype == DFGPU_BF16) launch_chained(bsq_row32_bf16_kernel, dim3(grid), dim3(256), 0, stream, x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
+        else if (p->x.dtype == DFGPU_BF16) return launch_tiles(tile_task(plan, x, y, scale), BsqTask{}, stream, "BLOCK_SCALE_QUANTIZE");
         else launch_chained(bsq_row32_kernel<__half>, dim3(grid), dim3(256), 0, stream, x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
     } else if (kernel == DFGPU_BSQ_COL32) {
         int vec = p->x.dtype == DFGPU_F32 ? 4 : 8;
@@ -882,7 +964,7 @@ extern "C" int dfgpu_block_scale_quantize(const dfgpu_bsq_params* p, void* const
                   static_cast<unsigned>(plan.batch));
         int reordered = plan.layout.reordered;
         if (p->x.dtype == DFGPU_F32) launch_chained(bsq_col32_kernel<float>, grid, dim3(128), 0, stream, x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
-        else if (p->x.dtype == DFGPU_BF16) launch_chained(bsq_col32_bf16_kernel, grid, dim3(128), 0, stream, x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
+        else if (p->x.dtype == DFGPU_BF16) return launch_tiles(tile_task(plan, x, y, scale), BsqTask{}, stream, "BLOCK_SCALE_QUANTIZE");
         else launch_chained(bsq_col32_kernel<__half>, grid, dim3(128), 0, stream, x, y, scale, plan.rows, plan.cols, reordered, plan.scale_k_extent);
     } else {
         int64_t block_total = element_count(p->x) / p->block_size;
@@ -944,35 +1026,15 @@ int plan_bsd(const dfgpu_bsd_params& p, BsdPlan& plan) {
 // ---- two BLOCK_SCALE_QUANTIZE nodes in one launch ---------------------------------------------------
 
 namespace {
-// The task of one tensor inside the pair grid, when its plan is one of the two bf16 fast forms with nothing to
+// The task of one tensor inside the shared grid, when its plan is one of the two bf16 fast forms with nothing to
 // pre-fill; false otherwise (the caller then launches the nodes separately).
 bool pair_task(const dfgpu_bsq_params& p, void* const* tensors, dfgpu::BsqTask& task) {
     using namespace dfgpu;
     BsqPlan plan;
     if (plan_bsq(p, plan) != kOk || plan.needs_fill || p.x.dtype != DFGPU_BF16) return false;
     if (plan.kernel != DFGPU_BSQ_ROW32 && plan.kernel != DFGPU_BSQ_COL32) return false;
-    task = BsqTask{};
-    task.rows = plan.rows;
-    task.cols = plan.cols;
-    task.scale_k_extent = plan.scale_k_extent;
-    task.reordered = plan.layout.reordered;
-    if (plan.kernel == DFGPU_BSQ_ROW32) {
-        task.column_form = 0;
-        task.tiles = (plan.rows * plan.cols + 8191) / 8192;  // 256 threads x 4 chunks x 8 elements
-        task.ctas = task.tiles;
-    } else {
-        task.column_form = 1;
-        task.tiles_x = static_cast<int32_t>((plan.cols / 8 + 31) / 32);
-        task.tiles_y = static_cast<int32_t>(plan.rows / 32);
-        task.tiles = static_cast<int64_t>(task.tiles_x) * task.tiles_y * plan.batch;
-        task.ctas = (task.tiles + 1) / 2;
-    }
-    if (task.ctas <= 0 || task.ctas > (1ll << 30)) return false;
-    if (tensors) {
-        task.x = tensors[0];
-        task.y = static_cast<uint8_t*>(tensors[1]);
-        task.scale = static_cast<uint8_t*>(tensors[2]);
-    }
+    if (!tile_task_fits(plan)) return false;
+    task = tile_task(plan, tensors ? tensors[0] : nullptr, tensors ? static_cast<uint8_t*>(tensors[1]) : nullptr, tensors ? static_cast<uint8_t*>(tensors[2]) : nullptr);
     return true;
 }
 }  // namespace
@@ -998,9 +1060,7 @@ extern "C" int dfgpu_block_scale_quantize_pair(const dfgpu_bsq_pair_params* p, v
         return fail(kUnsupported, "BLOCK_SCALE_QUANTIZE pair: both tensors must take a bf16 32-element fast form with an unpadded scale tensor");
     for (int i = 0; i < 6; ++i)
         if (!aligned(tensors[i], i % 3 == 0 ? 16 : 8)) return fail(kInvalidArgument, "BLOCK_SCALE_QUANTIZE pair: X must be 16-byte aligned, Y and scale 8-byte aligned");
-    cudaError_t launched = launch_chained(bsq_pair_bf16_kernel, dim3(static_cast<unsigned>(first.ctas + second.ctas)), dim3(256), 0, as_stream(stream_handle), first, second);
-    if (launched != cudaSuccess) return fail(kExecutionFailed, "BLOCK_SCALE_QUANTIZE pair: launch failed: %s", cudaGetErrorString(launched));
-    return check_launch("BLOCK_SCALE_QUANTIZE pair");
+    return launch_tiles(first, second, as_stream(stream_handle), "BLOCK_SCALE_QUANTIZE pair");
 }
 
 extern "C" int dfgpu_query_block_scale_dequantize(const dfgpu_bsd_params* p, dfgpu_plan_info* info) {

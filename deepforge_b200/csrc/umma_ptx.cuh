@@ -199,7 +199,19 @@ using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, 
                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// The encoder is a DRIVER entry point and needs a current context. A host thread that has made no runtime call yet
+// (a worker thread of the caller's pool running its first launch) has none: bind the primary context of the thread's
+// current device once per thread, the way the first runtime call would.
+inline void bind_primary_context() {
+    thread_local const bool bound = [] {
+        int device = 0;
+        return cudaGetDevice(&device) == cudaSuccess && cudaSetDevice(device) == cudaSuccess;  // (binds; allocates nothing)
+    }();
+    (void)bound;
+}
+
 inline EncodeTiled encode_tiled() {
+    bind_primary_context();
     static EncodeTiled fn = [] {
         void* entry = nullptr;
         cudaDriverEntryPointQueryResult result;

@@ -86,6 +86,23 @@ class Session:
         torch.cuda.synchronize(self.device)
         return graphs
 
+    def capture_round(self, first: int, last: int):
+        """ONE CUDA graph holding plan steps [first, last) of every replica in turn: the launches follow one another
+        the way they do inside a step (chained, each on buffers the one before did not touch), so a replay measures
+        what a launch costs in a stream of launches rather than alone behind a graph launch."""
+        if not hasattr(self, "replicas"):
+            self.make_replicas(1)
+        stream = torch.cuda.Stream(self.device)
+        with torch.cuda.stream(stream):
+            self.exe.set_stream(stream.cuda_stream)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for pack, workspace in self.replicas:
+                    self.exe.execute_steps(first, last, pack, workspace)
+        self.exe.set_stream(None)
+        torch.cuda.synchronize(self.device)
+        return graph
+
     def replica_tensors(self, index: int) -> Dict[int, torch.Tensor]:
         return self.dev if index == 0 else self._replica_buffers[index - 1][0]
 

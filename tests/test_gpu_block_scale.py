@@ -102,6 +102,73 @@ def test_column_blocks_match_oracle(dtype, kernel):
     assert np.array_equal(y, y_ref)
 
 
+@pytest.mark.parametrize("shape,axis", [([1000, 1056], 1), ([2, 96, 1000], 1), ([7, 32], 1), ([64, 8], 0), ([9, 3200, 264], 1)])
+def test_ragged_bf16_tiles_match_oracle(shape, axis):
+    """Sizes that leave the streaming kernel a partial last tile (row form: elements % 8192 != 0; column form: N % 256
+    != 0) and more tiles than one pass of the grid (the last case walks its ring of stages around)."""
+    info, x, y, s, y_ref, s_ref = _quantize_both(BF16, shape, 32, axis, dfgpu.BSQ_AUTO, special=True, seed=31)
+    assert info.kernel == (dfgpu.BSQ_ROW32 if axis == len(shape) - 1 else dfgpu.BSQ_COL32)
+    assert np.array_equal(s, s_ref)
+    assert np.array_equal(y, y_ref)
+
+
+@pytest.mark.parametrize("axis", [1, 0])
+def test_every_bf16_amax_pattern(axis):
+    """One block per bf16 magnitude pattern (0 .. 0x7fff: zero, subnormals, every exponent and fraction, infinity and
+    the NaNs) as that block's largest |x|, the other elements anywhere below it with random signs: the bf16 kernels
+    derive the scale code from the pattern's bits and multiply in bf16, and must still equal the oracle bit for bit."""
+    import gpu_util as g
+    rng = np.random.default_rng(77)
+    top = np.arange(0x8000, dtype=np.uint32)
+    magnitude = (rng.random((0x8000, 32)) * (top[:, None] + 1)).astype(np.uint32)
+    magnitude = np.minimum(magnitude, top[:, None])
+    magnitude[np.arange(0x8000), rng.integers(0, 32, 0x8000)] = top
+    bits = (magnitude | (rng.integers(0, 2, magnitude.shape).astype(np.uint32) << 15)).astype(np.uint16)
+    if axis == 1:
+        x = bits.reshape(1024, 1024)          # block b = elements 32b .. 32b+31 of the flattened tensor
+        sdims = [1024, 32]
+    else:
+        x = np.ascontiguousarray(bits.reshape(32, 1024, 32).transpose(0, 2, 1)).reshape(1024, 1024)  # block (kb, n) down the rows
+        sdims = [32, 1024]
+    xd, yd, sd = tensor(BF16, [1024, 1024]), tensor(E4M3, [1024, 1024]), tensor(E8M0, sdims)
+    y_ref = np.zeros(1024 * 1024, dtype=np.uint8)
+    s_ref = np.zeros(32768, dtype=np.uint8)
+    oracle.block_scale_quantize(xd, x, yd, y_ref, sd, s_ref, 32, axis)
+    p = dfgpu.BsqParams()
+    p.x, p.y, p.scale, p.block_size, p.axis = xd, yd, sd, 32, axis
+    dx, dy, ds = g.to_device(x), g.device_zeros(y_ref.size, 0x55), g.device_zeros(32768, 0xAA)
+    dfgpu.block_scale_quantize(p, g.ptr(dx), g.ptr(dy), g.ptr(ds))
+    assert np.array_equal(g.to_host(ds, np.uint8), s_ref)
+    assert np.array_equal(g.to_host(dy, np.uint8), y_ref)
+
+
+@pytest.mark.parametrize("shapes", [(([300, 1056], 1), ([96, 1000], 0)), (([64, 264], 0), ([2, 64, 72], 1)), (([33, 64], 1), ([9, 32], 1))])
+def test_quantize_pair_matches_oracle(shapes):
+    """Two tensors through dfgpu_block_scale_quantize_pair (one grid): each result equals the oracle's for that tensor
+    alone, for row+column, column+column and row+row pairs with ragged last tiles."""
+    import gpu_util as g
+    pair = dfgpu.BsqPairParams()
+    device, expected = [], []
+    for index, (shape, axis) in enumerate(shapes):
+        x = _make_x(BF16, shape, 40 + index, special=True)
+        logical = list(shape)
+        logical[axis] //= 32
+        xd, yd, sd = tensor(BF16, shape), tensor(E4M3, shape), tensor(E8M0, logical)
+        y_ref = np.zeros(int(np.prod(shape)), dtype=np.uint8)
+        s_ref = np.zeros(int(np.prod(logical)), dtype=np.uint8)
+        oracle.block_scale_quantize(xd, x, yd, y_ref, sd, s_ref, 32, axis)
+        p = pair.first if index == 0 else pair.second
+        p.x, p.y, p.scale, p.block_size, p.axis = xd, yd, sd, 32, axis
+        device.append((g.to_device(x), g.device_zeros(y_ref.size, 0x55), g.device_zeros(s_ref.size, 0xAA)))
+        expected.append((y_ref, s_ref))
+    assert dfgpu.query("block_scale_quantize_pair", pair).launches == 1
+    dfgpu.block_scale_quantize_pair(pair, [g.ptr(t) for t in device[0]], [g.ptr(t) for t in device[1]])
+    for (dx, dy, ds), (y_ref, s_ref) in zip(device, expected):
+        assert np.array_equal(g.to_host(ds, np.uint8), s_ref)
+        assert np.array_equal(g.to_host(dy, np.uint8), y_ref)
+    assert dfgpu.device_status() == 0
+
+
 @pytest.mark.parametrize("block,axis,shape", [(2, 1, [5, 6]), (16, 0, [32, 7]), (64, 2, [2, 3, 128]), (8, 1, [4, 24, 5])])
 def test_generic_blocks_match_oracle(block, axis, shape):
     info, x, y, s, y_ref, s_ref = _quantize_both(F32, shape, block, axis, dfgpu.BSQ_AUTO, special=True, seed=21)
