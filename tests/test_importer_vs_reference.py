@@ -194,3 +194,15 @@ def test_encodings_match_the_reference():
     text = json.dumps(DOCS["c1"]).encode()
     for payload, fmt in ((b"{not json", 1), (text + b" trailing", 1), (b"\x00" * 16, 2), (b"\xff\xfegarbage", 0), (text, 2)):
         assert _ours(payload, fmt)[0] == reference(payload, fmt)[0]
+
+
+@pytest.mark.parametrize("source", ["test/Compiler/RuntimeHeaderTest.cpp"])
+def test_reference_header_checks_compile_against_our_headers(source):
+    """The reference's own compile-time check of the runtime interface (member signatures of Executable::execute and
+    get_workspace_size, as static_asserts) compiled UNMODIFIED against this repository's include/ tree: a host that
+    builds against the reference's headers builds against these."""
+    path = _reference_tree() / source
+    if not path.exists():
+        pytest.skip("reference tree not on this machine")
+    built = subprocess.run(["g++", "-std=c++20", "-fsyntax-only", "-I", str(ROOT / "include"), str(path)], capture_output=True, text=True)
+    assert built.returncode == 0, built.stderr[-2000:]
