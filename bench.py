@@ -527,7 +527,8 @@ def measure(name: str, steps: int, warmup: int, torch, device, distributed: bool
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each configuration's dominant kernel, from the ncu
 # captures summarised under profiles/ (keyed by configuration number and launch label).
 NCU_TRAFFIC_BYTES = {
-    (3, "dequantize_b+dequantize_a+matmul"): 34.8e6,  # profiles/umma_mxf8_and_bsq_kernels_c3_quantize_matmul.md
+    (2, "conv2+bias2+relu2>conv3+residual"): 91.3e6,  # profiles/umma_conv_pair_kernel_c2_bottleneck.md
+    (3, "dequantize_b+dequantize_a+matmul"): 35.6e6,  # profiles/umma_mxf8_and_bsq_kernels_c3_quantize_matmul.md
     (4, "sdpa"): 511.2e6,              # profiles/sdpa_umma_pair_kernel_c4_sdpa.md
     (5, "paged_decode"): 1313.1e6,     # profiles/sdpa_decode_umma_kernel_c5_paged_decode.md
 }

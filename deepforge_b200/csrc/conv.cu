@@ -192,11 +192,51 @@ conv_igemm_ffma_kernel(const void* __restrict__ x, const void* __restrict__ w, v
 // slice k+1 are in flight (in registers) while slice k is multiplied out of shared memory.
 template <int BM>
 __global__ void __launch_bounds__(256)
-conv_nhwc_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, void* __restrict__ y, ConvArgs a, int m_total) {
+conv_nhwc_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, void* __restrict__ y, ConvArgs a, int m_total,
+                     const int* __restrict__ run_if_any, int flag_count, const float* __restrict__ partial, int partial_count) {
     constexpr int BN = 64, BK = 16, TM = BM / 16, TN = 4;
     __shared__ float as[2][BK][BM + 4];
     __shared__ float bs[2][BK][BN + 4];
     const int tid = threadIdx.x;
+    if (run_if_any) {
+        // Second pass behind the split-operand tensor-core form: it only convolves when one of the flags is set. With
+        // the flags clear it is done at once, or, where the tensor-core launch split K over several CTAs per tile, it
+        // adds their partial sums (in order) for its own outputs and applies the epilogue.
+        int any = 0;
+        for (int i = tid; i < flag_count; i += 256) any |= run_if_any[i];
+        if (!__syncthreads_or(any)) {
+            if (partial_count < 2) return;
+            const int P = static_cast<int>(a.y.dim[2]), Q = static_cast<int>(a.y.dim[3]), K = static_cast<int>(a.y.dim[1]);
+            const int64_t stride = static_cast<int64_t>(m_total) * K;
+            const int ty = tid / 16, tx = tid % 16;
+            for (int i = 0; i < TM; ++i) {
+                const int m = blockIdx.x * BM + ty * TM + i;
+                const int k0 = blockIdx.y * BN + tx * TN;
+                if (m >= m_total || k0 >= K) continue;  // (K is a multiple of 64 in this form: whole float4s)
+                const float* source = partial + static_cast<int64_t>(m) * K + k0;
+                float4 part[kMaxKSplits];
+#pragma unroll
+                for (int z = 0; z < kMaxKSplits; ++z)  // every load in flight before the first sum
+                    part[z] = z < partial_count ? __ldg(reinterpret_cast<const float4*>(source + z * stride)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                float4 sum = part[0];
+#pragma unroll
+                for (int z = 1; z < kMaxKSplits; ++z) {
+                    if (z >= partial_count) break;
+                    sum.x = __fadd_rn(sum.x, part[z].x);
+                    sum.y = __fadd_rn(sum.y, part[z].y);
+                    sum.z = __fadd_rn(sum.z, part[z].z);
+                    sum.w = __fadd_rn(sum.w, part[z].w);
+                }
+                const int q = m % Q, p = (m / Q) % P, n = m / (P * Q);
+                const float values[4] = {sum.x, sum.y, sum.z, sum.w};
+                for (int j = 0; j < TN; ++j) {
+                    const float value = apply_epilogue(values[j], a, n, k0 + j, p, q);
+                    store_from_f32(y, a.y.dtype, n * a.y.stride[0] + (k0 + j) * a.y.stride[1] + p * a.y.stride[2] + q * a.y.stride[3], value);
+                }
+            }
+            return;
+        }
+    }
     const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
     const int P = static_cast<int>(a.y.dim[2]), Q = static_cast<int>(a.y.dim[3]);
     const int C = static_cast<int>(a.x.dim[1]), S = static_cast<int>(a.w.dim[3]);
@@ -305,6 +345,115 @@ bool nhwc_f32_fast_form(const dfgpu_conv_params& p, void* const* tensors) {
     return true;
 }
 
+// ---- f32 convolution on the bf16 tensor cores ------------------------------------------------------------
+// x = xh + xm + xl and w = wh + wm + wl with bf16 pieces (the leading 8 significant bits, the next 8, the last 8; every
+// subtraction that forms them is exact), so x * w = xh*wh + xh*wm + xm*wh + xh*wl + xl*wh + xm*wm up to 2^-24 relative:
+// the bf16 convolution of [xh | xh | xm | xh | xl | xm] (6C channels) with [wh | wm | wh | wl | wh | wm], accumulated
+// in f32 by the tensor cores. (Two pieces and three products stop at 2^-16, which fails the reference's own
+// acceptance rule 1e-4 + 1e-3 |ref| where |ref| is small.) The split kernel writes both 6C-channel copies into scratch.
+// A product with an infinite or NaN factor does not survive the split (inf * 0 where the other factor's lower pieces
+// are zero), so every CTA of the split kernel also records whether it saw such a value, and the CUDA-core kernel is
+// launched behind the tensor-core one to redo the convolution when any did (it returns at once otherwise).
+constexpr int kSplitQuadsPerCta = 1024;  // 256 threads x 4 float4
+constexpr int kSplitPieces = 6;           // bf16 channels per f32 channel
+
+// The three bf16 pieces of v; false (and everything in the first piece) when v is infinite or NaN.
+__device__ __forceinline__ bool split_f32(float v, uint32_t (&piece)[3]) {
+    const uint32_t bits = __float_as_uint(v);
+    if ((bits & 0x7f800000u) == 0x7f800000u) {
+        piece[0] = bits >> 16 | ((bits & 0xffffu) != 0u ? 0x40u : 0u);  // (a NaN stays a NaN whatever its low bits were)
+        piece[1] = piece[2] = 0u;
+        return false;
+    }
+    uint32_t hi = f32_to_bf16_bits(v);
+    if ((hi & 0x7f80u) == 0x7f80u) hi = (hi & 0x8000u) | 0x7f7fu;  // rounded past the largest bf16: keep it finite
+    const float rest = v - __uint_as_float(hi << 16);
+    const uint32_t mid = f32_to_bf16_bits(rest);
+    piece[0] = hi;
+    piece[1] = mid;
+    piece[2] = f32_to_bf16_bits(rest - __uint_as_float(mid << 16));
+    return true;
+}
+
+// rows of C floats -> rows of 6C bf16, piece order per operand as above
+__global__ void __launch_bounds__(256)
+split6_f32_kernel(const float* __restrict__ x, uint16_t* __restrict__ xs, int64_t x_quads, const float* __restrict__ w, uint16_t* __restrict__ ws,
+                  int64_t w_quads, int c_quads, int* __restrict__ flags) {
+    bool finite = true;
+    float4 v[4];
+    bool live[4], filter[4];
+    int64_t quad[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {  // all four loads in flight before the first is used
+        quad[i] = static_cast<int64_t>(blockIdx.x) * kSplitQuadsPerCta + i * 256 + threadIdx.x;
+        filter[i] = quad[i] >= x_quads;
+        if (filter[i]) quad[i] -= x_quads;
+        live[i] = !filter[i] || quad[i] < w_quads;
+        v[i] = live[i] ? __ldg(reinterpret_cast<const float4*>(filter[i] ? w : x) + quad[i]) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (!live[i]) continue;
+        uint32_t p0[3], p1[3], p2[3], p3[3];
+        finite = split_f32(v[i].x, p0) && finite;
+        finite = split_f32(v[i].y, p1) && finite;
+        finite = split_f32(v[i].z, p2) && finite;
+        finite = split_f32(v[i].w, p3) && finite;
+        uint2 piece[3];
+#pragma unroll
+        for (int j = 0; j < 3; ++j) piece[j] = make_uint2(p0[j] | (p1[j] << 16), p2[j] | (p3[j] << 16));
+        const int64_t row = quad[i] / c_quads, column = (quad[i] - row * c_quads) * 4, c = static_cast<int64_t>(c_quads) * 4;
+        uint16_t* out = (filter[i] ? ws : xs) + row * kSplitPieces * c + column;
+        // activations: h h m h l m; filter: h m h l h m
+        const int order_x[kSplitPieces] = {0, 0, 1, 0, 2, 1}, order_w[kSplitPieces] = {0, 1, 0, 2, 0, 1};
+#pragma unroll
+        for (int j = 0; j < kSplitPieces; ++j) *reinterpret_cast<uint2*>(out + j * c) = filter[i] ? piece[order_w[j]] : piece[order_x[j]];
+    }
+    const int any = __syncthreads_or(finite ? 0 : 1);
+    if (threadIdx.x == 0) flags[blockIdx.x] = any;
+}
+
+struct SplitForm {
+    dfgpu_conv_params bf16;   // the 6C-channel bf16 convolution
+    int64_t x_quads, w_quads;
+    int64_t xs_offset, ws_offset, flags_offset, partial_offset, scratch_bytes;
+    int flag_count;
+    ConvKSplit k_split;       // few tiles: several CTAs per tile, partial sums in scratch, added by the CUDA-core launch
+};
+
+// The split-operand form takes packed channels-last f32 X, a packed KRSC f32 filter and a packed channels-last Y, with
+// the shape limits of the tcgen05 convolution (C and K multiples of 64, stride 1, dilation 1).
+bool f32_split_form(const dfgpu_conv_params& p, SplitForm& form) {
+    if (p.x.dtype != DFGPU_F32 || p.w.dtype != DFGPU_F32 || p.y.dtype != DFGPU_F32 || p.reverse_filter) return false;
+    if (p.x.rank != 4 || p.w.rank != 4 || p.y.rank != 4) return false;
+    auto packed = [](const dfgpu_tensor& t) {
+        return t.stride[1] == 1 && t.stride[3] == t.dim[1] && t.stride[2] == t.dim[3] * t.dim[1] && t.stride[0] == t.dim[2] * t.dim[3] * t.dim[1];
+    };
+    if (!packed(p.x) || !packed(p.w) || !packed(p.y) || p.x.dim[1] != p.w.dim[1] || p.x.dim[1] % 64 != 0) return false;
+    if (element_count(p.x) >= (1ll << 29) || element_count(p.w) >= (1ll << 29) || element_count(p.y) >= (1ll << 31)) return false;
+    form.bf16 = p;
+    form.bf16.kernel = DFGPU_CONV_UMMA_BF16;
+    for (dfgpu_tensor* t : {&form.bf16.x, &form.bf16.w}) {
+        t->dtype = DFGPU_BF16;
+        t->dim[1] *= kSplitPieces;
+        t->stride[3] = t->dim[1];
+        t->stride[2] = t->dim[3] * t->dim[1];
+        t->stride[0] = t->dim[2] * t->dim[3] * t->dim[1];
+    }
+    if (!conv_umma_supported(form.bf16)) return false;
+    form.x_quads = element_count(p.x) / 4;
+    form.w_quads = element_count(p.w) / 4;
+    auto round_up = [](int64_t v) { return (v + 255) / 256 * 256; };
+    form.flag_count = static_cast<int>((form.x_quads + form.w_quads + kSplitQuadsPerCta - 1) / kSplitQuadsPerCta);
+    form.xs_offset = 0;
+    form.ws_offset = round_up(element_count(p.x) * kSplitPieces * 2);
+    form.flags_offset = form.ws_offset + round_up(element_count(p.w) * kSplitPieces * 2);
+    form.partial_offset = form.flags_offset + round_up(static_cast<int64_t>(form.flag_count) * 4);
+    form.k_split = conv_umma_k_split(form.bf16);
+    form.scratch_bytes = form.partial_offset + (form.k_split.splits > 1 ? round_up(form.k_split.splits * element_count(p.y) * 4) : 0);
+    return true;
+}
+
 int build_args(const dfgpu_conv_params& p, void* const* tensors, ConvArgs& a) {
     if (!valid_tensor(p.x) || !valid_tensor(p.w) || !valid_tensor(p.y))
         return fail(kInvalidShape, "CONV_FPROP: tensor rank or extent out of range");
@@ -354,14 +503,19 @@ int build_args(const dfgpu_conv_params& p, void* const* tensors, ConvArgs& a) {
 int choose_kernel(const dfgpu_conv_params& p, const ConvArgs& a, int& kernel) {
     int automatic = a.groups == 1 ? DFGPU_CONV_IGEMM_FFMA : DFGPU_CONV_DIRECT;
     if (conv_umma_supported(p)) automatic = DFGPU_CONV_UMMA_BF16;
+    SplitForm split;
+    const bool split_ok = f32_split_form(p, split);
+    if (split_ok) automatic = DFGPU_CONV_UMMA_F32X3;
     kernel = p.kernel == DFGPU_CONV_AUTO ? automatic : p.kernel;
+    if (kernel == DFGPU_CONV_UMMA_F32X3 && !split_ok)
+        return fail(kUnsupported, "CONV_FPROP: the split-operand tcgen05 form needs packed channels-last f32 X, W and Y, C and K multiples of 64, stride 1, dilation 1");
     if (kernel != DFGPU_CONV_UMMA_BF16 && (p.x.dtype == DFGPU_BF16X2 || p.y.dtype == DFGPU_BF16X2))
         return fail(kUnsupported, "CONV_FPROP: split bf16 pair tensors are read and written by the tcgen05 kernel only");
     if (kernel == DFGPU_CONV_IGEMM_FFMA && a.groups != 1)
         return fail(kUnsupported, "CONV_FPROP: the implicit-GEMM kernel needs groups == 1");
     if (kernel == DFGPU_CONV_UMMA_BF16 && !conv_umma_supported(p))
         return fail(kUnsupported, "CONV_FPROP: the tcgen05 kernel needs bf16 NHWC/KRSC, C and K multiples of 64, stride 1, dilation 1");
-    if (kernel < DFGPU_CONV_DIRECT || kernel > DFGPU_CONV_UMMA_BF16)
+    if (kernel < DFGPU_CONV_DIRECT || kernel > DFGPU_CONV_UMMA_F32X3)
         return fail(kInvalidArgument, "CONV_FPROP: unknown kernel id %d", kernel);
     return kOk;
 }
@@ -386,11 +540,16 @@ extern "C" int dfgpu_query_conv_fprop(const dfgpu_conv_params* p, dfgpu_plan_inf
     info->kernel = kernel;
     info->launches = 1;
     info->scratch_bytes = 0;
+    if (kernel == DFGPU_CONV_UMMA_F32X3) {
+        SplitForm split;
+        f32_split_form(copy, split);
+        info->launches = 3;
+        info->scratch_bytes = split.scratch_bytes;
+    }
     return kOk;
 }
 
 extern "C" int dfgpu_conv_fprop(const dfgpu_conv_params* p, void* const* tensors, void* scratch, void* stream_handle) {
-    (void)scratch;
     if (!p || !tensors) return fail(kInvalidArgument, "CONV_FPROP: null params");
     if (!tensors[0] || !tensors[1] || !tensors[2]) return fail(kInvalidArgument, "CONV_FPROP: null tensor pointer");
     ConvArgs a;
@@ -402,6 +561,35 @@ extern "C" int dfgpu_conv_fprop(const dfgpu_conv_params* p, void* const* tensors
     cudaStream_t stream = as_stream(stream_handle);
     if (kernel == DFGPU_CONV_UMMA_BF16) return launch_conv_umma(*p, tensors, stream);
     int64_t m_total = p->y.dim[0] * p->y.dim[2] * p->y.dim[3];
+    if (kernel == DFGPU_CONV_UMMA_F32X3) {
+        SplitForm split;
+        if (!f32_split_form(*p, split) || !nhwc_f32_fast_form(*p, tensors))
+            return fail(kInvalidArgument, "CONV_FPROP: the split-operand tcgen05 form needs 16-byte aligned X and W");
+        if (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 15u) != 0)
+            return fail(kInvalidArgument, "CONV_FPROP: the split-operand tcgen05 form needs its 16-byte aligned scratch (dfgpu_query_conv_fprop gives the size)");
+        uint8_t* base = static_cast<uint8_t*>(scratch);
+        uint16_t* xs = reinterpret_cast<uint16_t*>(base + split.xs_offset);
+        uint16_t* ws = reinterpret_cast<uint16_t*>(base + split.ws_offset);
+        int* flags = reinterpret_cast<int*>(base + split.flags_offset);
+        const float* xf = static_cast<const float*>(tensors[0]);
+        const float* wf = static_cast<const float*>(tensors[1]);
+        split6_f32_kernel<<<split.flag_count, 256, 0, stream>>>(xf, xs, split.x_quads, wf, ws, split.w_quads, static_cast<int>(p->x.dim[1] / 4), flags);
+        void* bf16_tensors[5] = {xs, ws, tensors[2], tensors[3], tensors[4]};
+        ConvKSplit k_split = split.k_split;
+        k_split.partial = reinterpret_cast<float*>(base + split.partial_offset);
+        status = launch_conv_umma(split.bf16, bf16_tensors, stream, &k_split);
+        if (status) return status;
+        const float* partial = k_split.splits > 1 ? k_split.partial : nullptr;
+        unsigned grid_n = static_cast<unsigned>((p->y.dim[1] + 63) / 64);
+        if ((m_total + 63) / 64 * grid_n < 2 * sm_count()) {
+            dim3 grid(static_cast<unsigned>((m_total + 31) / 32), grid_n);
+            conv_nhwc_f32_kernel<32><<<grid, 256, 0, stream>>>(xf, wf, tensors[2], a, static_cast<int>(m_total), flags, split.flag_count, partial, k_split.splits);
+        } else {
+            dim3 grid(static_cast<unsigned>((m_total + 63) / 64), grid_n);
+            conv_nhwc_f32_kernel<64><<<grid, 256, 0, stream>>>(xf, wf, tensors[2], a, static_cast<int>(m_total), flags, split.flag_count, partial, k_split.splits);
+        }
+        return check_launch("CONV_FPROP");
+    }
     if (kernel == DFGPU_CONV_DIRECT) {
         int64_t total = element_count(p->y);
         conv_direct_kernel<<<static_cast<unsigned>((total + 127) / 128), 128, 0, stream>>>(tensors[0], tensors[1], tensors[2], a, total);
@@ -416,10 +604,10 @@ extern "C" int dfgpu_conv_fprop(const dfgpu_conv_params* p, void* const* tensors
             const float* wf = static_cast<const float*>(tensors[1]);
             if (small) {
                 dim3 grid(static_cast<unsigned>((m_total + 31) / 32), grid_n);
-                conv_nhwc_f32_kernel<32><<<grid, 256, 0, stream>>>(xf, wf, tensors[2], a, static_cast<int>(m_total));
+                conv_nhwc_f32_kernel<32><<<grid, 256, 0, stream>>>(xf, wf, tensors[2], a, static_cast<int>(m_total), nullptr, 0, nullptr, 0);
             } else {
                 dim3 grid(static_cast<unsigned>((m_total + 63) / 64), grid_n);
-                conv_nhwc_f32_kernel<64><<<grid, 256, 0, stream>>>(xf, wf, tensors[2], a, static_cast<int>(m_total));
+                conv_nhwc_f32_kernel<64><<<grid, 256, 0, stream>>>(xf, wf, tensors[2], a, static_cast<int>(m_total), nullptr, 0, nullptr, 0);
             }
         } else if (small) {
             dim3 grid(static_cast<unsigned>((m_total + 31) / 32), grid_n);

@@ -20,7 +20,17 @@ bool conv_umma_form(const dfgpu_conv_params& p, ConvForm& form);
 
 // bf16 NHWC/KRSC convolution as an implicit GEMM on tcgen05 (1x1 and 3x3, stride 1).
 bool conv_umma_supported(const dfgpu_conv_params& p);
-int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStream_t stream);
+// K split of the one-tile-per-CTA form, for convolutions with fewer tiles than SMs: `splits` CTAs per tile each take
+// k_blocks_per_split 64-deep K slices and store raw f32 partial sums (no epilogue) at partial + z * N*P*Q*K floats; the
+// caller adds them in order and applies the epilogue. conv_umma_k_split() proposes a split (splits == 1: none).
+constexpr int kMaxKSplits = 8;
+struct ConvKSplit {
+    int splits;
+    int k_blocks_per_split;
+    float* partial;
+};
+ConvKSplit conv_umma_k_split(const dfgpu_conv_params& p);
+int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStream_t stream, const ConvKSplit* k_split = nullptr);
 
 // A wide-filter convolution and the 1 x 1 convolution that consumes it, in one persistent kernel (the intermediate
 // stays on the SM). tensors: {X, W first, W second, Y, first.extra0, first.extra1, second.extra0, second.extra1}.

@@ -55,6 +55,12 @@ struct GemmArgs {
     int32_t epi_dtype[DFGPU_MAX_EPILOGUE];
     int64_t epi_ld[DFGPU_MAX_EPILOGUE];
     float epi_lower[DFGPU_MAX_EPILOGUE], epi_upper[DFGPU_MAX_EPILOGUE], epi_slope[DFGPU_MAX_EPILOGUE];
+    // K split (one-tile kernel only): blockIdx.z takes K slices [z * k_per_split, ...) and stores its raw f32 sums at
+    // partial + z * partial_stride (same row/column indexing as `out`, leading dimension n_total); no epilogue runs,
+    // whoever adds the partial sums applies it. k_split <= 1: the whole K loop in one CTA, the result goes to `out`.
+    int32_t k_split, k_per_split;
+    float* partial;
+    int64_t partial_stride;
 };
 
 template <int BN, int STAGES>
@@ -84,6 +90,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tile = blockIdx.x, n_tile = blockIdx.y;
     const int n0 = n_tile * BN;
+    const bool split_k = args.k_split > 1;
+    const int kb_begin = split_k ? static_cast<int>(blockIdx.z) * args.k_per_split : 0;
+    const int kb_count = split_k ? min(args.k_per_split, args.k_blocks - kb_begin) : args.k_blocks;
 
     // tile geometry
     int64_t out_row0;
@@ -117,13 +126,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
-
     if (warp == 0) {
         if (lane == 0) {
             const uint32_t a_bytes = args.is_conv ? static_cast<uint32_t>(args.rows_per_tile * args.out_q * kBlockK * 2) : L::kABytes;
-            for (int kb = 0; kb < args.k_blocks; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t parity = ((kb / STAGES) & 1) ^ 1;
+            for (int i = 0; i < kb_count; ++i) {
+                const int kb = kb_begin + i;
+                const int s = i % STAGES;
+                const uint32_t parity = ((i / STAGES) & 1) ^ 1;
                 if (!mbar_wait(empty_bar(s), parity, 101)) break;
                 const uint32_t a_dst = smem_base + s * L::kStageBytes;
                 const uint32_t b_dst = a_dst + L::kABytes;
@@ -151,9 +160,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(args.b_mn_major) << 16) |
                                    (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
             bool ok = true;
-            for (int kb = 0; kb < args.k_blocks && ok; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t parity = (kb / STAGES) & 1;
+            for (int i = 0; i < kb_count && ok; ++i) {
+                const int s = i % STAGES;
+                const uint32_t parity = (i / STAGES) & 1;
                 ok = mbar_wait(full_bar(s), parity, 102);
                 if (!ok) break;
                 tc_fence_after();
@@ -164,7 +173,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 const uint32_t b_step = args.b_mn_major ? (2048u >> 4) : (32u >> 4);
 #pragma unroll
                 for (int k = 0; k < kBlockK / 16; ++k)
-                    umma_bf16(tmem_base, desc_words(a_lo + ((k * 32) >> 4), smem_desc_hi(1024)), desc_words(b_lo + k * b_step, smem_desc_hi(1024)), idesc, (kb | k) != 0 ? 1u : 0u);
+                    umma_bf16(tmem_base, desc_words(a_lo + ((k * 32) >> 4), smem_desc_hi(1024)), desc_words(b_lo + k * b_step, smem_desc_hi(1024)), idesc, (i | k) != 0 ? 1u : 0u);
                 umma_commit(empty_bar(s));
             }
             // always arrive, so the epilogue's wait ends even after a failed wait above
@@ -188,6 +197,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 float v[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
+                if (split_k) {
+                    float4* dst = reinterpret_cast<float4*>(args.partial + static_cast<int64_t>(blockIdx.z) * args.partial_stride + out_row * args.n_total + col0);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    continue;
+                }
                 for (int e = 0; e < args.epi_count; ++e) {
                     const int kind = args.epi_kind[e];
                     if (kind == kEpiRelu) {
@@ -714,7 +729,7 @@ umma_conv_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 // ---- host side ----------------------------------------------------------------------------
 
 template <int BN, int STAGES>
-int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& args, dim3 grid, cudaStream_t stream) {
+int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& args, dim3 grid, cudaStream_t stream, bool chained) {
     using L = SmemLayout<BN, STAGES>;
     static bool configured = false;
     if (!configured) {
@@ -722,26 +737,31 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& a
         if (error != cudaSuccess) return fail(kExecutionFailed, "tcgen05 GEMM: cannot reserve %d bytes of shared memory: %s", L::kDynamic, cudaGetErrorString(error));
         configured = true;
     }
-    umma_gemm_kernel<BN, STAGES><<<grid, kThreads, L::kDynamic, stream>>>(map_a, map_b, args);
+    if (chained) {
+        cudaError_t error = launch_chained(umma_gemm_kernel<BN, STAGES>, grid, dim3(kThreads), L::kDynamic, stream, map_a, map_b, args);
+        if (error != cudaSuccess) return fail(kExecutionFailed, "tcgen05 GEMM: launch failed: %s", cudaGetErrorString(error));
+    } else {
+        umma_gemm_kernel<BN, STAGES><<<grid, kThreads, L::kDynamic, stream>>>(map_a, map_b, args);
+    }
     return check_launch("tcgen05 GEMM");
 }
 
 // Ring depth: shallow K loops (the 1x1 convolutions) get short rings so that several CTAs fit on
 // one SM and overlap each other's load / MMA / epilogue phases; deep K loops (matmul) get 4 stages.
-int dispatch(int bn, int k_blocks, const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& args, dim3 grid, cudaStream_t stream) {
+int dispatch(int bn, int k_blocks, const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& args, dim3 grid, cudaStream_t stream, bool chained = false) {
     const int stages = k_blocks <= 1 ? 1 : (k_blocks <= 12 ? 2 : 4);
     if (bn == 64) {
-        if (stages == 1) return launch<64, 1>(map_a, map_b, args, grid, stream);
-        if (stages == 2) return launch<64, 2>(map_a, map_b, args, grid, stream);
-        return launch<64, 4>(map_a, map_b, args, grid, stream);
+        if (stages == 1) return launch<64, 1>(map_a, map_b, args, grid, stream, chained);
+        if (stages == 2) return launch<64, 2>(map_a, map_b, args, grid, stream, chained);
+        return launch<64, 4>(map_a, map_b, args, grid, stream, chained);
     }
     if (bn == 128) {
-        if (stages == 1) return launch<128, 1>(map_a, map_b, args, grid, stream);
-        if (stages == 2) return launch<128, 2>(map_a, map_b, args, grid, stream);
-        return launch<128, 4>(map_a, map_b, args, grid, stream);
+        if (stages == 1) return launch<128, 1>(map_a, map_b, args, grid, stream, chained);
+        if (stages == 2) return launch<128, 2>(map_a, map_b, args, grid, stream, chained);
+        return launch<128, 4>(map_a, map_b, args, grid, stream, chained);
     }
-    if (stages <= 2) return launch<256, 2>(map_a, map_b, args, grid, stream);
-    return launch<256, 4>(map_a, map_b, args, grid, stream);
+    if (stages <= 2) return launch<256, 2>(map_a, map_b, args, grid, stream, chained);
+    return launch<256, 4>(map_a, map_b, args, grid, stream, chained);
 }
 
 constexpr int kSmemBudget = 227 * 1024;
@@ -929,7 +949,7 @@ bool conv_umma_supported(const dfgpu_conv_params& p) {
     return conv_umma_form(p, form);
 }
 
-int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStream_t stream) {
+int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStream_t stream, const ConvKSplit* k_split) {
     ConvForm f;
     if (!conv_umma_form(p, f)) return fail(kUnsupported, "CONV_FPROP: the tcgen05 kernel does not take this convolution");
     const int64_t N = f.N, C = f.C, H = f.H, W = f.W, K = f.K, P = f.P, Q = f.Q, R = f.R, S = f.S;
@@ -1039,7 +1059,32 @@ int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStrea
         return launch_persistent<128, false>(map_a, map_b, map_out, map_res, pargs, stream);
     }
     dim3 grid(static_cast<unsigned>(m_tiles), static_cast<unsigned>(K / bn));
+    if (k_split && k_split->splits > 1) {
+        args.k_split = k_split->splits;
+        args.k_per_split = k_split->k_blocks_per_split;
+        args.partial = k_split->partial;
+        args.partial_stride = N * P * Q * K;
+        grid.z = static_cast<unsigned>(k_split->splits);
+        return dispatch(bn, args.k_blocks, map_a, map_b, args, grid, stream);  // (ring depth as for the whole K loop: the loads are the launch)
+    }
     return dispatch(bn, args.k_blocks, map_a, map_b, args, grid, stream);
+}
+
+ConvKSplit conv_umma_k_split(const dfgpu_conv_params& p) {
+    ConvKSplit split{1, 0, nullptr};
+    ConvForm f;
+    if (!conv_umma_form(p, f) || f.persistent) return split;
+    const int64_t m_tiles = f.pointwise ? (f.N * f.H * f.W + kTileM - 1) / kTileM : f.N * ((f.P + f.rows_per_tile - 1) / f.rows_per_tile);
+    const int64_t tiles = m_tiles * (f.K / f.bn);
+    const int k_blocks = static_cast<int>(f.R * f.S * (f.C / kBlockK));
+    // (a function of the shape alone, so that a plan made on one machine sizes the scratch for every other: 148 SMs)
+    const int wanted = static_cast<int>(148 / tiles);  // CTAs per tile that the tiles alone leave idle SMs for
+    if (wanted < 2 || k_blocks < 4) return split;
+    split.k_blocks_per_split = (k_blocks + wanted - 1) / wanted;
+    if (split.k_blocks_per_split < 2) split.k_blocks_per_split = 2;
+    if (split.k_blocks_per_split * kMaxKSplits < k_blocks) split.k_blocks_per_split = (k_blocks + kMaxKSplits - 1) / kMaxKSplits;
+    split.splits = (k_blocks + split.k_blocks_per_split - 1) / split.k_blocks_per_split;
+    return split;
 }
 
 bool matmul_umma_supported(const dfgpu_matmul_params& p, int kernel) {

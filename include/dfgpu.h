@@ -154,7 +154,12 @@ enum {
     DFGPU_CONV_AUTO = 0,
     DFGPU_CONV_DIRECT = 1,      /* any rank-4 conv, one thread per output */
     DFGPU_CONV_IGEMM_FFMA = 2,  /* f32-accumulate implicit GEMM on CUDA cores */
-    DFGPU_CONV_UMMA_BF16 = 3    /* bf16 NHWC implicit GEMM on tcgen05 */
+    DFGPU_CONV_UMMA_BF16 = 3,   /* bf16 NHWC implicit GEMM on tcgen05 */
+    DFGPU_CONV_UMMA_F32X3 = 4   /* f32 NHWC on tcgen05: X and W split into three bf16 pieces each, six bf16 products (2^-24
+                                   relative); needs scratch, three launches: split X and W, the bf16 convolution over 6C
+                                   channels (K split over several CTAs per tile when the tiles are few), and the CUDA-core
+                                   kernel again, which adds the partial sums, or redoes the convolution when X or W held
+                                   an infinity or a NaN */
 };
 typedef struct dfgpu_conv_params {
     dfgpu_tensor x, w, y;

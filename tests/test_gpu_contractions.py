@@ -123,7 +123,8 @@ def run_conv(dtype, x_dims, w_dims, pre, post, stride, dilation, kernel, x_strid
     dx, dw = g.to_device(hx), g.to_device(hw)
     dy = g.device_zeros(ref.size * dfgpu.DTYPE_BYTES[dtype])
     info = dfgpu.query("conv_fprop", p)
-    dfgpu.conv_fprop(p, g.ptr(dx), g.ptr(dw), g.ptr(dy), g.ptr(extra_dev[0]), g.ptr(extra_dev[1]))
+    scratch = g.device_zeros(info.scratch_bytes, 0xA5) if info.scratch_bytes else None
+    dfgpu.conv_fprop(p, g.ptr(dx), g.ptr(dw), g.ptr(dy), g.ptr(extra_dev[0]), g.ptr(extra_dev[1]), scratch=g.ptr(scratch))
     out = read_back(dy, dtype, -1)
     return info, out, ref
 
@@ -171,6 +172,66 @@ def test_conv_benchmark_shape_c1_both_layouts():
     check_f32(out, ref)
     info, out, ref = run_conv(F32, x_dims, w_dims, [1, 1], [1, 1], [1, 1], [1, 1], dfgpu.CONV_AUTO, seed=20261126)
     check_f32(out, ref)
+
+
+def test_conv_benchmark_shape_c1_runs_on_tensor_cores():
+    """The same convolution resolves to the split-operand tcgen05 form (three bf16 products, f32 accumulation) and holds
+    the f32 gates against the oracle; so does a 1x1 filter, a deeper one with bias and ReLU, and a batch of images."""
+    x_dims, w_dims, y_dims = [1, 64, 56, 56], [64, 64, 3, 3], [1, 64, 56, 56]
+    info, out, ref = run_conv(F32, x_dims, w_dims, [1, 1], [1, 1], [1, 1], [1, 1], dfgpu.CONV_AUTO,
+                              nhwc_strides(x_dims), nhwc_strides(w_dims), nhwc_strides(y_dims), seed=20261126)
+    assert info.kernel == dfgpu.CONV_UMMA_F32X3 and info.launches == 3 and info.scratch_bytes > 0
+    check_f32(out, ref)
+    # the CUDA-core kernel on the same inputs: the two agree far inside the gate
+    info2, out2, _ = run_conv(F32, x_dims, w_dims, [1, 1], [1, 1], [1, 1], [1, 1], dfgpu.CONV_IGEMM_FFMA,
+                              nhwc_strides(x_dims), nhwc_strides(w_dims), nhwc_strides(y_dims), seed=20261126)
+    assert info2.kernel == dfgpu.CONV_IGEMM_FFMA
+    assert float(np.max(np.abs(out - out2))) <= 3e-5 * float(np.max(np.abs(ref)))
+    for x_dims, w_dims, pad in (([3, 128, 14, 14], [64, 128, 1, 1], 0), ([2, 64, 28, 28], [128, 64, 3, 3], 1), ([1, 64, 9, 20], [64, 64, 5, 5], 2)):
+        n, c, h, w = x_dims
+        y_dims = [n, w_dims[0], h, w]
+        bias = synthetic.uniform(3, 5, w_dims[0], -0.1, 0.1)
+        info, out, ref = run_conv(F32, x_dims, w_dims, [pad, pad], [pad, pad], [1, 1], [1, 1], dfgpu.CONV_AUTO,
+                                  nhwc_strides(x_dims), nhwc_strides(w_dims), nhwc_strides(y_dims), seed=5,
+                                  epilogue=[step(dfgpu.EPI_ADD, 0), step(dfgpu.EPI_RELU)], extras=[([1, w_dims[0], 1, 1], [w_dims[0], 1, w_dims[0], w_dims[0]], bias)])
+        assert info.kernel == dfgpu.CONV_UMMA_F32X3
+        check_f32(out, ref)
+
+
+@pytest.mark.parametrize("where", ["x_inf", "x_nan", "w_inf", "x_huge", "clean"])
+def test_conv_split_form_with_non_finite_operands(where):
+    """An infinity or a NaN in X or W does not survive the hi/lo split (inf * 0), so the CUDA-core kernel behind the
+    tensor-core one redoes the convolution: the result is then bit for bit the CUDA-core kernel's own (NaNs in the same
+    places). Finite values past the largest bf16 stay on the tensor cores."""
+    x_dims, w_dims, y_dims = [1, 64, 12, 12], [64, 64, 3, 3], [1, 64, 12, 12]
+    x = synthetic.normal(9, 1, int(np.prod(x_dims)))
+    w = synthetic.normal(9, 2, int(np.prod(w_dims)), std=0.05)
+    w[::7] = np.float32(0.5)          # low halves of exactly zero
+    if where == "x_inf": x[5 * 64 + 3] = np.inf
+    if where == "x_nan": x[77 * 64 + 9] = np.nan
+    if where == "w_inf": w[1000] = -np.inf
+    if where == "x_huge": x[40 * 64 + 1], w[:] = np.float32(3.395e38), np.float32(2.0 ** -20)
+    p = dfgpu.ConvParams()
+    p.x, p.w, p.y = tensor(F32, x_dims, nhwc_strides(x_dims)), tensor(F32, w_dims, nhwc_strides(w_dims)), tensor(F32, y_dims, nhwc_strides(y_dims))
+    for i in range(2):
+        p.pre_pad[i], p.post_pad[i], p.stride[i], p.dilation[i] = 1, 1, 1, 1
+    dx, dw = g.to_device(x.astype(np.float32)), g.to_device(w.astype(np.float32))
+    results = {}
+    for kernel in (dfgpu.CONV_IGEMM_FFMA, dfgpu.CONV_UMMA_F32X3):
+        p.kernel = kernel
+        info = dfgpu.query("conv_fprop", p)
+        dy = g.device_zeros(int(np.prod(y_dims)) * 4, 0x5A)
+        scratch = g.device_zeros(info.scratch_bytes, 0xA5) if info.scratch_bytes else None
+        dfgpu.conv_fprop(p, g.ptr(dx), g.ptr(dw), g.ptr(dy), scratch=g.ptr(scratch))
+        results[kernel] = g.to_host(dy, np.uint32).copy()
+    cores, split = results[dfgpu.CONV_IGEMM_FFMA], results[dfgpu.CONV_UMMA_F32X3]
+    if where in ("x_inf", "x_nan", "w_inf"):
+        assert np.array_equal(cores, split)
+        assert not np.all(np.isfinite(cores.view(np.float32)))
+    else:
+        a, b = split.view(np.float32), cores.view(np.float32)
+        assert np.all(np.isfinite(a)) and not np.array_equal(cores, split)  # (the tensor-core result stands)
+        assert float(np.max(np.abs(a - b))) <= 3e-5 * float(np.max(np.abs(b)))
 
 
 def test_conv_special_values_single_node_rule():
