@@ -568,18 +568,42 @@ def roofline_for(result: dict, peaks: dict, here: dict | None = None) -> dict:
             "kernel": info["label"], "algorithmic_bytes": nbytes, "peak_source": peaks["source"], "kernels": kernels, "step": step}
 
 
+def cores_near_gpu(index: int) -> list[int]:
+    """Host cores NVML reports as local to GPU `index` of this process (its NUMA node); empty when that cannot be read."""
+    try:
+        import pynvml
+        import torch
+        pynvml.nvmlInit()
+        uuid = torch.cuda.get_device_properties(index).uuid
+        handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        return [64 * w + bit for w, word in enumerate(words) for bit in range(64) if (int(word) >> bit) & 1]
+    except Exception:
+        return []
+
+
 def spread_over_cores(local_rank: int, local_world: int) -> str:
-    """Gives each rank of a multi-GPU run its own share of the host cores this process may use (the copy threads and
-    the Python driver of eight ranks otherwise all crowd onto the same cores). Returns what was done."""
+    """Gives each rank of a multi-GPU run its own share of the host cores this process may use, taken from the cores
+    local to its GPU's NUMA node where NVML tells (the copy threads, pinned buffers and the Python driver of eight
+    ranks otherwise crowd onto the same cores, or sit across the socket from their GPU). Returns what was done."""
     try:
         allowed = sorted(os.sched_getaffinity(0))
         if local_world <= 1 or len(allowed) < 2 * local_world:
             return "unchanged"
+        near = [sorted(set(cores_near_gpu(r)) & set(allowed)) for r in range(local_world)]
+        mine = near[local_rank]
+        sharing = [r for r in range(local_world) if near[r] == mine]  # ranks whose GPUs hang off the same node
+        if len(mine) >= 2 * len(sharing):
+            share = len(mine) // len(sharing)
+            position = sharing.index(local_rank)
+            chosen = mine[position * share:(position + 1) * share]
+            os.sched_setaffinity(0, chosen)
+            return f"cores {chosen[0]}-{chosen[-1]}: this GPU's NUMA node ({len(mine)} cores, {len(sharing)} ranks on it)"
         share = len(allowed) // local_world
-        mine = allowed[local_rank * share:(local_rank + 1) * share]
-        os.sched_setaffinity(0, mine)
-        return f"cores {mine[0]}-{mine[-1]} of {len(allowed)} allowed"
-    except (AttributeError, OSError):
+        chosen = allowed[local_rank * share:(local_rank + 1) * share]
+        os.sched_setaffinity(0, chosen)
+        return f"cores {chosen[0]}-{chosen[-1]} of {len(allowed)} allowed (GPU locality unknown)"
+    except (AttributeError, OSError, ValueError):
         return "unchanged"
 
 

@@ -198,7 +198,7 @@ int choose_kernel(const dfgpu_matmul_params& p, int& kernel) {
     if (matmul_umma_supported(p, DFGPU_MATMUL_UMMA_MXF8)) automatic = DFGPU_MATMUL_UMMA_MXF8;
     else if (matmul_umma_supported(p, DFGPU_MATMUL_UMMA_BF16)) automatic = DFGPU_MATMUL_UMMA_BF16;
     kernel = p.kernel == DFGPU_MATMUL_AUTO ? automatic : p.kernel;
-    if (kernel < DFGPU_MATMUL_FFMA || kernel > DFGPU_MATMUL_UMMA_MXF8_2SM) return fail(kInvalidArgument, "MATMUL: unknown kernel id %d", kernel);
+    if (kernel < DFGPU_MATMUL_FFMA || kernel > DFGPU_MATMUL_UMMA_MXF8) return fail(kInvalidArgument, "MATMUL: unknown kernel id %d", kernel);
     if (kernel != DFGPU_MATMUL_FFMA && !matmul_umma_supported(p, kernel))
         return fail(kUnsupported, "MATMUL: the requested tcgen05 kernel does not cover this shape, layout or type");
     return kOk;

@@ -44,7 +44,7 @@ int launch_matmul_umma(const dfgpu_matmul_params& p, void* const* tensors, int k
 
 // MATMUL on MXFP8 codes + E8M0 block scales (tcgen05 block-scaled kind), no dequantize pass.
 bool matmul_mxf8_supported(const dfgpu_matmul_params& p);
-int launch_matmul_mxf8(const dfgpu_matmul_params& p, void* const* tensors, bool two_sm_tiles, cudaStream_t stream);
+int launch_matmul_mxf8(const dfgpu_matmul_params& p, void* const* tensors, cudaStream_t stream);
 // MATMUL_FP8 on the same kernel: unit block scales, the three scalars and Amax_C applied in the epilogue.
 bool matmul_fp8_umma_supported(const dfgpu_matmul_fp8_params& p);
 int launch_matmul_fp8_umma(const dfgpu_matmul_fp8_params& p, void* const* tensors, cudaStream_t stream);

@@ -1089,8 +1089,6 @@ ConvKSplit conv_umma_k_split(const dfgpu_conv_params& p) {
 
 bool matmul_umma_supported(const dfgpu_matmul_params& p, int kernel) {
     if (kernel == DFGPU_MATMUL_UMMA_MXF8) return matmul_mxf8_supported(p);
-    if (kernel == DFGPU_MATMUL_UMMA_MXF8_2SM)
-        return matmul_mxf8_supported(p) && p.c.dim[p.c.rank - 2] % 256 == 0 && p.c.dim[p.c.rank - 1] % 256 == 0;
     if (kernel != DFGPU_MATMUL_UMMA_BF16) return false;
     if (p.a_scale.rank || p.b_scale.rank) return false;
     if (p.a.dtype != DFGPU_BF16 || p.b.dtype != DFGPU_BF16 || (p.c.dtype != DFGPU_BF16 && p.c.dtype != DFGPU_F32)) return false;
@@ -1109,7 +1107,7 @@ bool matmul_umma_supported(const dfgpu_matmul_params& p, int kernel) {
 }
 
 int launch_matmul_umma(const dfgpu_matmul_params& p, void* const* tensors, int kernel, cudaStream_t stream) {
-    if (kernel == DFGPU_MATMUL_UMMA_MXF8 || kernel == DFGPU_MATMUL_UMMA_MXF8_2SM) return launch_matmul_mxf8(p, tensors, kernel == DFGPU_MATMUL_UMMA_MXF8_2SM, stream);
+    if (kernel == DFGPU_MATMUL_UMMA_MXF8) return launch_matmul_mxf8(p, tensors, stream);
     const int rank = p.c.rank;
     const int64_t M = p.c.dim[rank - 2], N = p.c.dim[rank - 1], K = p.a.dim[rank - 1];
     if (!aligned16(tensors[0]) || !aligned16(tensors[1]) || !aligned16(tensors[2]))

@@ -401,268 +401,6 @@ umma_mxf8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
 }
 
-// ---- two-SM form --------------------------------------------------------------------------
-// A cluster of two CTAs (SMs) owns a 256 x 256 output tile: CTA r holds rows r*128..r*128+127 of A and columns
-// r*128..r*128+127 of B in its shared memory and the 128 x 256 accumulator of its rows in its tensor memory. One lane
-// of CTA 0 issues tcgen05.mma.cta_group::2 (M = 256), which reads both CTAs' shared memory. Per SM and 128-deep K
-// step that is 16 + 16 KiB of operands instead of 16 + 32, and the one-SM form is bound by exactly that L2 ->
-// shared-memory traffic. Hand-shakes that cross the pair: the ring's "full" barrier lives in CTA 0 (both CTAs' TMA
-// loads complete their bytes there, both CTAs' scale loaders arrive there); "slot free" and "accumulator ready" are
-// committed to both CTAs' barriers; the epilogue warps of both CTAs arrive on CTA 0's "accumulator drained".
-// Measured on 4096^3: 81 us against 63 us for the one-SM form (a 256 x 256 x 32 two-SM product takes ~170 cycles back to
-// back in a microbenchmark and ~300 here), so MATMUL AUTO keeps the one-SM form and this one is chosen by kernel id only.
-constexpr int kPairStages = 6;
-
-struct MxPairSmem {
-    static constexpr int kBBytes = 128 * kBlockK;                 // this CTA's 128 columns of B
-    static constexpr int kSfaOffset = kABytes + kBBytes;          // 512 B: own 128 rows
-    static constexpr int kSfbOffset = kSfaOffset + kSfaBytes;     // 1024 B: all 256 columns
-    static constexpr int kStageBytes = kSfbOffset + 1024 + 512;   // 34 KiB, keeps every slot 1024-byte aligned
-    static constexpr int kBarriers = kPairStages * kStageBytes;
-    static constexpr int kBarrierCount = 2 * kPairStages + 2;     // full[S], empty[S], acc_full, acc_empty
-    static constexpr int kTotal = kBarriers + kBarrierCount * 8 + 16;
-    static constexpr int kDynamic = kTotal + 1024;
-};
-
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t peer_address(uint32_t own_address, uint32_t peer_rank) {
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(own_address), "r"(peer_rank));
-    return remote;
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_address) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_address) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    return done != 0;
-}
-// Bounded wait with cluster-scope acquire (the other CTA's shared-memory writes must be visible afterwards).
-__device__ __noinline__ bool mbar_wait_cluster_slow(uint32_t bar, uint32_t parity, int code) {
-    const uint64_t start = global_timer_ns();
-    for (;;) {
-        for (int spin = 0; spin < 128; ++spin)
-            if (mbar_try_wait_cluster(bar, parity)) return true;
-        if (global_timer_ns() - start > 2000000000ull) {
-            atomicCAS(&g_device_status, 0, code);
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ bool mbar_wait_warp_cluster(uint32_t bar, uint32_t parity, int code) {
-#pragma unroll 1
-    for (int spin = 0; spin < 64; ++spin)
-        if (__all_sync(0xffffffffu, mbar_try_wait_cluster(bar, parity))) return true;
-    return __all_sync(0xffffffffu, mbar_wait_cluster_slow(bar, parity, code)) != 0;
-}
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t leader_bar) {
-    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(leader_bar) : "memory");
-}
-__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
-}
-__device__ __forceinline__ void tmem_copy_scales_pair(uint32_t tmem_dst, uint64_t smem_descriptor) {
-    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(smem_descriptor) : "memory");
-}
-__device__ __forceinline__ void umma_mxf8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate,
-                                               uint32_t tmem_sfa, uint32_t tmem_sfb) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
-}
-
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMxThreads, 1)
-umma_mxf8_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, MxArgs args) {
-    using L = MxPairSmem;
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t bar_base = smem_base + L::kBarriers;
-    auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (kPairStages + s); };
-    const uint32_t acc_full_bar = bar_base + 8u * (2 * kPairStages);
-    const uint32_t acc_empty_bar = bar_base + 8u * (2 * kPairStages + 1);
-    const uint32_t tmem_slot = bar_base + 8u * L::kBarrierCount;
-    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_base + L::kBarriers + 8 * L::kBarrierCount);
-
-    const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
-    const bool leader = elect_one();
-    const uint32_t rank = cluster_rank();          // 0: the CTA whose lane issues the products
-    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
-    const int total_tiles = args.m_tiles * args.n_tiles;  // 256 x 256 tiles here
-    const uint32_t leader_bars = peer_address(bar_base, 0);  // CTA 0's barrier block as seen from this CTA
-    chain_release();
-
-    if (warp == 0 && leader) {
-        for (int s = 0; s < kPairStages; ++s) {
-            mbar_init(full_bar(s), 3);   // CTA 0's loader (with the byte count of both CTAs) + one scale warp of each CTA
-            mbar_init(empty_bar(s), 1);  // tcgen05.commit
-        }
-        mbar_init(acc_full_bar, 1);
-        mbar_init(acc_empty_bar, 8);     // four epilogue warps of each CTA
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-        tc_fence_before();
-    }
-    __syncthreads();
-    cluster_sync_all();  // both CTAs' barriers exist before either touches the other's
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot_ptr;
-    chain_wait();
-
-    if (warp == 0) {
-        // ---- TMA loader: own 128 rows of A and own 128 columns of B; bytes are counted on CTA 0's barrier ----
-        int stage = 0;
-        uint32_t phase = 1;
-        bool ok = true;
-        for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
-            const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
-            const int row0 = m_tile * 256 + static_cast<int>(rank) * 128, col0 = n_tile * 256 + static_cast<int>(rank) * 128;
-            for (int kb = 0; kb < args.k_blocks; ++kb) {
-                ok = mbar_wait_warp(empty_bar(stage), phase, 411);
-                if (!ok) break;
-                const uint32_t a_dst = smem_base + stage * L::kStageBytes;
-                const uint32_t b_dst = a_dst + kABytes;
-                const uint32_t leader_full = leader_bars + 8u * stage;
-                if (leader) {
-                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * (kABytes + L::kBBytes));
-                    tma_load_2d_pair(a_dst, &map_a, kb * kBlockK, row0, leader_full);
-                    if (args.b_mn_major) tma_load_2d_pair(b_dst, &map_b, col0, kb * kBlockK, leader_full);
-                    else tma_load_2d_pair(b_dst, &map_b, kb * kBlockK, col0, leader_full);
-                }
-                if (++stage == kPairStages) { stage = 0; phase ^= 1; }
-            }
-        }
-    } else if (warp == 1) {
-        // ---- issuing warp (CTA 0 only) ----
-        if (rank == 0) {
-            const uint32_t idesc_base = (static_cast<uint32_t>(args.b_mn_major) << 16) | (static_cast<uint32_t>(256 >> 3) << 17) | (1u << 23) |
-                                        (static_cast<uint32_t>(256 >> 4) << 24);
-            const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            int local = 0;
-            for (int tile = pair; tile < total_tiles; tile += pairs, ++local) {
-                if (ok) ok = mbar_wait_warp_cluster(acc_empty_bar, (local & 1) ^ 1, 412);
-                tc_fence_after();
-                for (int kb = 0; kb < args.k_blocks && ok; ++kb) {
-                    ok = mbar_wait_warp_cluster(full_bar(stage), phase, 413);
-                    if (!ok) break;
-                    tc_fence_after();
-                    const uint32_t a_src = smem_base + stage * L::kStageBytes;
-                    const uint32_t b_src = a_src + kABytes;
-                    const uint32_t sf_tmem = tmem_u + 256 + (stage & 1) * 16;  // SFA at +0..3, SFB at +4..11
-                    const uint32_t a_lo = smem_desc_lo(a_src, 16);
-                    const uint32_t b_lo = args.b_mn_major ? smem_desc_lo(b_src, kBlockK * 128) : smem_desc_lo(b_src, 16);
-                    const uint32_t b_step = args.b_mn_major ? (4096u >> 4) : (32u >> 4);
-                    if (leader) {
-                        tmem_copy_scales_pair(sf_tmem, scale_desc(a_src + L::kSfaOffset));
-                        tmem_copy_scales_pair(sf_tmem + 4, scale_desc(a_src + L::kSfbOffset));
-                        tmem_copy_scales_pair(sf_tmem + 8, scale_desc(a_src + L::kSfbOffset + 512));
-#pragma unroll
-                        for (int j = 0; j < kBlockK / 32; ++j) {
-                            const uint32_t idesc = idesc_base | (static_cast<uint32_t>(j) << 29) | (static_cast<uint32_t>(j) << 4);
-                            umma_mxf8_pair(tmem_u, desc_words(a_lo + ((j * 32) >> 4), smem_desc_hi(1024)), desc_words(b_lo + j * b_step, smem_desc_hi(1024)), idesc,
-                                           (kb | j) != 0 ? 1u : 0u, sf_tmem, sf_tmem + 4);
-                        }
-                        // the slot is free again in both CTAs
-                        umma_commit_pair(empty_bar(stage));
-                        umma_commit_pair(peer_address(empty_bar(stage), 1));
-                    }
-                    if (++stage == kPairStages) { stage = 0; phase ^= 1; }
-                }
-                if (leader) {  // arrives even after a failed wait so that neither epilogue hangs
-                    umma_commit_pair(acc_full_bar);
-                    umma_commit_pair(peer_address(acc_full_bar, 1));
-                }
-            }
-        }
-    } else if (warp < 6) {
-        // ---- epilogue: this CTA's 128 rows x 256 columns ----
-        const int quadrant = warp & 3;
-        const int row = quadrant * 32 + lane;
-        const uint32_t leader_acc_empty = leader_bars + 8u * (2 * kPairStages + 1);
-        bool ok = true;
-        int local = 0;
-        for (int tile = pair; tile < total_tiles; tile += pairs, ++local) {
-            const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
-            if (ok) ok = mbar_wait(acc_full_bar, local & 1, 414);
-            tc_fence_after();
-            const bool healthy = ok && g_device_status == 0;
-            const int64_t out_row = static_cast<int64_t>(m_tile) * 256 + rank * 128 + row;
-            MxScalars none{};
-            mx_store_row(args, tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16), out_row, static_cast<int64_t>(n_tile) * 256, 256, healthy, none);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
-        }
-    } else {
-        // ---- scale loaders: own rows' A scales, all 256 columns' B scales; warp 6 + q takes the ring events q mod 4 ----
-        const int q = warp - 6;
-        bool ok = true;
-        int it = 0;
-        for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
-            const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
-            const int64_t row0 = static_cast<int64_t>(m_tile) * 256 + rank * 128, col0 = static_cast<int64_t>(n_tile) * 256;
-            for (int kb = 0; kb < args.k_blocks; ++kb, ++it) {
-                if ((it & 3) != q) continue;
-                const int slot = it % kPairStages;
-                const uint32_t phase = ((it / kPairStages) & 1) ^ 1;
-                uint32_t a_words[4];
-#pragma unroll
-                for (int g = 0; g < 4; ++g)
-                    a_words[g] = __ldg(reinterpret_cast<const uint32_t*>(args.sfa + (row0 + g * 32 + lane) * args.sfa_ld + kb * 4));
-                uint32_t b_words[2][4];
-#pragma unroll
-                for (int c = 0; c < 2; ++c)
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        const uint8_t* p = args.sfb + static_cast<int64_t>(kb) * 4 * args.sfb_ld + col0 + c * 128 + g * 32 + lane;
-                        const uint32_t b0 = __ldg(p), b1 = __ldg(p + args.sfb_ld), b2 = __ldg(p + 2 * args.sfb_ld), b3 = __ldg(p + 3 * args.sfb_ld);
-                        b_words[c][g] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
-                    }
-                ok = mbar_wait_warp(empty_bar(slot), phase, 415);
-                if (!ok) break;
-                uint8_t* stage_base = generic_base + slot * L::kStageBytes;
-                *reinterpret_cast<uint4*>(stage_base + L::kSfaOffset + lane * 16) = make_uint4(a_words[0], a_words[1], a_words[2], a_words[3]);
-#pragma unroll
-                for (int c = 0; c < 2; ++c)
-                    *reinterpret_cast<uint4*>(stage_base + L::kSfbOffset + c * 512 + lane * 16) = make_uint4(b_words[c][0], b_words[c][1], b_words[c][2], b_words[c][3]);
-                fence_async_shared();
-                __syncwarp();
-                if (leader) mbar_arrive_cluster(leader_bars + 8u * slot);
-            }
-        }
-    }
-
-    tc_fence_before();
-    __syncthreads();
-    cluster_sync_all();  // no CTA leaves while the other may still signal its barriers or read its memory
-    if (warp == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
-    }
-}
-
 inline int make_map_u8(CUtensorMap* map, const void* base, const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box, const char* what) {
     EncodeTiled encode = encode_tiled();
     if (!encode) return fail(kExecutionFailed, "%s: cuTensorMapEncodeTiled is unavailable", what);
@@ -790,7 +528,7 @@ bool matmul_mxf8_supported(const dfgpu_matmul_params& p) {
     return translate_steps(p, nullptr, nullptr);
 }
 
-int launch_matmul_mxf8(const dfgpu_matmul_params& p, void* const* tensors, bool two_sm_tiles, cudaStream_t stream) {
+int launch_matmul_mxf8(const dfgpu_matmul_params& p, void* const* tensors, cudaStream_t stream) {
     const int rank = p.c.rank;
     const int64_t M = p.c.dim[rank - 2], N = p.c.dim[rank - 1], K = p.a.dim[rank - 1];
     if (!aligned(tensors[0], 16) || !aligned(tensors[1], 16) || !aligned(tensors[2], 16) || !aligned(tensors[3], 4))
@@ -815,21 +553,7 @@ int launch_matmul_mxf8(const dfgpu_matmul_params& p, void* const* tensors, bool 
     args.k_blocks = static_cast<int>(K / kBlockK);
     args.b_mn_major = b_k_major ? 0 : 1;
     if (!translate_steps(p, tensors, &args)) return fail(kUnsupported, "MATMUL: the fused epilogue is not one the MXFP8 kernel applies");
-    if (!two_sm_tiles) return launch_one_sm(map_a, map_b, args, bn, stream);
-    {
-        // two-SM form: 256 x 256 tiles, one cluster of two CTAs each
-        MxArgs pair_args = args;
-        pair_args.m_tiles = static_cast<int>(M / 256);
-        pair_args.n_tiles = static_cast<int>(N / 256);
-        const int64_t pair_tiles = static_cast<int64_t>(pair_args.m_tiles) * pair_args.n_tiles;
-        const int pairs = static_cast<int>(pair_tiles < sm_count() / 2 ? pair_tiles : sm_count() / 2);
-        cudaError_t error = cudaFuncSetAttribute(umma_mxf8_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MxPairSmem::kDynamic);
-        if (error != cudaSuccess) return fail(kExecutionFailed, "MATMUL: cannot reserve %d bytes of shared memory: %s", MxPairSmem::kDynamic, cudaGetErrorString(error));
-        error = launch_chained(umma_mxf8_pair_kernel, dim3(2 * pairs), dim3(kMxThreads), MxPairSmem::kDynamic, stream, map_a, map_b, pair_args);
-        if (error != cudaSuccess) return fail(kExecutionFailed, "MATMUL (tcgen05, MXFP8, two-SM tiles): launch failed: %s", cudaGetErrorString(error));
-        return check_launch("MATMUL (tcgen05, MXFP8, two-SM tiles)");
-    }
-    return fail(kInvalidArgument, "MATMUL: unreachable");
+    return launch_one_sm(map_a, map_b, args, bn, stream);
 }
 
 bool matmul_fp8_umma_supported(const dfgpu_matmul_fp8_params& p) {

@@ -200,10 +200,7 @@ int dfgpu_conv_fprop_pair(const dfgpu_conv_pair_params*, void* const* tensors, v
    that feed A and B (SpecializedGraph.cpp:752-795), reading E4M3 codes and
    E8M0 scales directly. tensors: {A, B, C, A_scale or null, B_scale or null,
    extra0 or null, extra1 or null}. */
-/* UMMA_MXF8_2SM: the same block-scaled matmul on 256 x 256 tiles owned by clusters of two CTAs
-   (tcgen05.mma.cta_group::2); needs M and N multiples of 256. Never chosen by AUTO: it is
-   measured slower than the one-SM form on this part and kept as a selectable, tested variant. */
-enum { DFGPU_MATMUL_AUTO = 0, DFGPU_MATMUL_FFMA = 1, DFGPU_MATMUL_UMMA_BF16 = 2, DFGPU_MATMUL_UMMA_MXF8 = 3, DFGPU_MATMUL_UMMA_MXF8_2SM = 4 };
+enum { DFGPU_MATMUL_AUTO = 0, DFGPU_MATMUL_FFMA = 1, DFGPU_MATMUL_UMMA_BF16 = 2, DFGPU_MATMUL_UMMA_MXF8 = 3 };
 typedef struct dfgpu_matmul_params {
     dfgpu_tensor a, b, c;
     dfgpu_tensor a_scale, b_scale;

@@ -200,17 +200,3 @@ def test_matmul_mxf8_bf16_out_bias_relu_many_tiles_per_cta():
     """160 tiles of 128 x 256 on 148 SMs: some CTAs run two tiles through the same accumulator."""
     out, ref = run_matmul_mxf8(2560, 2048, 256, BF16, False, bias_relu=True)
     check_bf16(out, ref)
-
-
-@pytest.mark.parametrize("b_k_major", [False, True])
-@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (512, 256, 384)])
-def test_matmul_mxf8_two_sm_tiles(m, n, k, b_k_major):
-    """The same matmul on 256 x 256 tiles owned by clusters of two CTAs (tcgen05.mma.cta_group::2), chosen by kernel id."""
-    out, ref = run_matmul_mxf8(m, n, k, F32, b_k_major, kernel=dfgpu.MATMUL_UMMA_MXF8_2SM)
-    assert float(np.max(np.abs(out - ref))) <= 1e-4 * float(np.max(np.abs(ref)))
-
-
-def test_matmul_mxf8_two_sm_tiles_many_tiles_per_cluster():
-    """80 tiles of 256 x 256 on 74 clusters: some clusters run two tiles through the same accumulators."""
-    out, ref = run_matmul_mxf8(2560, 2048, 256, BF16, False, bias_relu=True, kernel=dfgpu.MATMUL_UMMA_MXF8_2SM)
-    check_bf16(out, ref)
