@@ -346,72 +346,9 @@ bool nhwc_f32_fast_form(const dfgpu_conv_params& p, void* const* tensors) {
 }
 
 // ---- f32 convolution on the bf16 tensor cores ------------------------------------------------------------
-// x = xh + xm + xl and w = wh + wm + wl with bf16 pieces (the leading 8 significant bits, the next 8, the last 8; every
-// subtraction that forms them is exact), so x * w = xh*wh + xh*wm + xm*wh + xh*wl + xl*wh + xm*wm up to 2^-24 relative:
-// the bf16 convolution of [xh | xh | xm | xh | xl | xm] (6C channels) with [wh | wm | wh | wl | wh | wm], accumulated
-// in f32 by the tensor cores. (Two pieces and three products stop at 2^-16, which fails the reference's own
-// acceptance rule 1e-4 + 1e-3 |ref| where |ref| is small.) The split kernel writes both 6C-channel copies into scratch.
-// A product with an infinite or NaN factor does not survive the split (inf * 0 where the other factor's lower pieces
-// are zero), so every CTA of the split kernel also records whether it saw such a value, and the CUDA-core kernel is
-// launched behind the tensor-core one to redo the convolution when any did (it returns at once otherwise).
-constexpr int kSplitQuadsPerCta = 1024;  // 256 threads x 4 float4
-constexpr int kSplitPieces = 6;           // bf16 channels per f32 channel
-
-// The three bf16 pieces of v; false (and everything in the first piece) when v is infinite or NaN.
-__device__ __forceinline__ bool split_f32(float v, uint32_t (&piece)[3]) {
-    const uint32_t bits = __float_as_uint(v);
-    if ((bits & 0x7f800000u) == 0x7f800000u) {
-        piece[0] = bits >> 16 | ((bits & 0xffffu) != 0u ? 0x40u : 0u);  // (a NaN stays a NaN whatever its low bits were)
-        piece[1] = piece[2] = 0u;
-        return false;
-    }
-    uint32_t hi = f32_to_bf16_bits(v);
-    if ((hi & 0x7f80u) == 0x7f80u) hi = (hi & 0x8000u) | 0x7f7fu;  // rounded past the largest bf16: keep it finite
-    const float rest = v - __uint_as_float(hi << 16);
-    const uint32_t mid = f32_to_bf16_bits(rest);
-    piece[0] = hi;
-    piece[1] = mid;
-    piece[2] = f32_to_bf16_bits(rest - __uint_as_float(mid << 16));
-    return true;
-}
-
-// rows of C floats -> rows of 6C bf16, piece order per operand as above
-__global__ void __launch_bounds__(256)
-split6_f32_kernel(const float* __restrict__ x, uint16_t* __restrict__ xs, int64_t x_quads, const float* __restrict__ w, uint16_t* __restrict__ ws,
-                  int64_t w_quads, int c_quads, int* __restrict__ flags) {
-    bool finite = true;
-    float4 v[4];
-    bool live[4], filter[4];
-    int64_t quad[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {  // all four loads in flight before the first is used
-        quad[i] = static_cast<int64_t>(blockIdx.x) * kSplitQuadsPerCta + i * 256 + threadIdx.x;
-        filter[i] = quad[i] >= x_quads;
-        if (filter[i]) quad[i] -= x_quads;
-        live[i] = !filter[i] || quad[i] < w_quads;
-        v[i] = live[i] ? __ldg(reinterpret_cast<const float4*>(filter[i] ? w : x) + quad[i]) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        if (!live[i]) continue;
-        uint32_t p0[3], p1[3], p2[3], p3[3];
-        finite = split_f32(v[i].x, p0) && finite;
-        finite = split_f32(v[i].y, p1) && finite;
-        finite = split_f32(v[i].z, p2) && finite;
-        finite = split_f32(v[i].w, p3) && finite;
-        uint2 piece[3];
-#pragma unroll
-        for (int j = 0; j < 3; ++j) piece[j] = make_uint2(p0[j] | (p1[j] << 16), p2[j] | (p3[j] << 16));
-        const int64_t row = quad[i] / c_quads, column = (quad[i] - row * c_quads) * 4, c = static_cast<int64_t>(c_quads) * 4;
-        uint16_t* out = (filter[i] ? ws : xs) + row * kSplitPieces * c + column;
-        // activations: h h m h l m; filter: h m h l h m
-        const int order_x[kSplitPieces] = {0, 0, 1, 0, 2, 1}, order_w[kSplitPieces] = {0, 1, 0, 2, 0, 1};
-#pragma unroll
-        for (int j = 0; j < kSplitPieces; ++j) *reinterpret_cast<uint2*>(out + j * c) = filter[i] ? piece[order_w[j]] : piece[order_x[j]];
-    }
-    const int any = __syncthreads_or(finite ? 0 : 1);
-    if (threadIdx.x == 0) flags[blockIdx.x] = any;
-}
+// X and W as six-piece bf16 copies (split_f32.cu), the bf16 convolution over 6C channels on tcgen05, and the CUDA-core
+// kernel behind it: it adds the partial sums when the tensor-core launch split K over several CTAs per tile, or redoes
+// the convolution when the split kernel flagged an infinity or a NaN in X or W (it returns at once otherwise).
 
 struct SplitForm {
     dfgpu_conv_params bf16;   // the 6C-channel bf16 convolution
@@ -444,7 +381,7 @@ bool f32_split_form(const dfgpu_conv_params& p, SplitForm& form) {
     form.x_quads = element_count(p.x) / 4;
     form.w_quads = element_count(p.w) / 4;
     auto round_up = [](int64_t v) { return (v + 255) / 256 * 256; };
-    form.flag_count = static_cast<int>((form.x_quads + form.w_quads + kSplitQuadsPerCta - 1) / kSplitQuadsPerCta);
+    form.flag_count = split_flag_count(SplitOperand{nullptr, nullptr, form.x_quads, 1, 0, 0, 0}, SplitOperand{nullptr, nullptr, form.w_quads, 1, 0, 0, 0});
     form.xs_offset = 0;
     form.ws_offset = round_up(element_count(p.x) * kSplitPieces * 2);
     form.flags_offset = form.ws_offset + round_up(element_count(p.w) * kSplitPieces * 2);
@@ -573,7 +510,10 @@ extern "C" int dfgpu_conv_fprop(const dfgpu_conv_params* p, void* const* tensors
         int* flags = reinterpret_cast<int*>(base + split.flags_offset);
         const float* xf = static_cast<const float*>(tensors[0]);
         const float* wf = static_cast<const float*>(tensors[1]);
-        split6_f32_kernel<<<split.flag_count, 256, 0, stream>>>(xf, xs, split.x_quads, wf, ws, split.w_quads, static_cast<int>(p->x.dim[1] / 4), flags);
+        const int64_t C = p->x.dim[1];
+        const SplitOperand x_pieces{xf, xs, split.x_quads, C / 4, C, kSplitPieces * C, C}, w_pieces{wf, ws, split.w_quads, C / 4, C, kSplitPieces * C, C};
+        status = launch_split6(x_pieces, w_pieces, flags, stream);
+        if (status) return status;
         void* bf16_tensors[5] = {xs, ws, tensors[2], tensors[3], tensors[4]};
         ConvKSplit k_split = split.k_split;
         k_split.partial = reinterpret_cast<float*>(base + split.partial_offset);

@@ -38,11 +38,18 @@ __device__ __forceinline__ void batch_offsets(const MatmulArgs& g, int64_t batch
 }
 
 __global__ void __launch_bounds__(256)
-matmul_ffma_kernel(const void* __restrict__ a, const void* __restrict__ b, void* __restrict__ c, MatmulArgs g) {
+matmul_ffma_kernel(const void* __restrict__ a, const void* __restrict__ b, void* __restrict__ c, MatmulArgs g, const int* __restrict__ run_if_any,
+                   int flag_count) {
     constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
     __shared__ float as[BK][BM + 4];
     __shared__ float bs[BK][BN + 4];
     const int tid = threadIdx.x;
+    if (run_if_any) {
+        // second pass behind the split-operand tensor-core form: it only has work when one of the flags is set
+        int any = 0;
+        for (int i = tid; i < flag_count; i += 256) any |= run_if_any[i];
+        if (!__syncthreads_or(any)) return;
+    }
     const int64_t m0 = static_cast<int64_t>(blockIdx.x) * BM;
     const int64_t n0 = static_cast<int64_t>(blockIdx.y) * BN;
     int64_t batch_index[DFGPU_MAX_RANK];
@@ -193,12 +200,69 @@ int build_args(const dfgpu_matmul_params& p, void* const* tensors, MatmulArgs& g
     return kOk;
 }
 
+// ---- f32 matmul on the bf16 tensor cores (split_f32.cu) ----------------------------------------------------
+struct SplitMatmul {
+    dfgpu_matmul_params bf16;  // the bf16 matmul over 6K
+    SplitOperand a, b;         // (pointers filled in at launch)
+    int64_t as_offset, bs_offset, flags_offset, scratch_bytes;
+    int flag_count;
+};
+
+// Takes unbatched f32 A [M, K] with K contiguous, f32 B with N or K contiguous and f32 C, K a multiple of 32 and the
+// shape limits of the bf16 tcgen05 matmul on the 6K-deep copies.
+bool f32_split_matmul(const dfgpu_matmul_params& p, SplitMatmul& form) {
+    if (p.a.dtype != DFGPU_F32 || p.b.dtype != DFGPU_F32 || p.c.dtype != DFGPU_F32 || p.a_scale.rank || p.b_scale.rank) return false;
+    const int rank = p.c.rank;
+    if (rank < 2 || p.a.rank != rank || p.b.rank != rank) return false;
+    for (int i = 0; i < rank - 2; ++i)
+        if (p.c.dim[i] != 1 || p.a.dim[i] != 1 || p.b.dim[i] != 1) return false;
+    const int64_t M = p.c.dim[rank - 2], N = p.c.dim[rank - 1], K = p.a.dim[rank - 1];
+    if (K % 32 != 0 || N % 4 != 0 || M * K >= (1ll << 29) || K * N >= (1ll << 29)) return false;
+    if (p.a.stride[rank - 1] != 1 || p.a.stride[rank - 2] % 4 != 0 || p.a.stride[rank - 2] < K) return false;
+    const bool b_n_major = p.b.stride[rank - 1] == 1 && p.b.stride[rank - 2] % 4 == 0 && p.b.stride[rank - 2] >= N;
+    const bool b_k_major = !b_n_major && p.b.stride[rank - 2] == 1 && p.b.stride[rank - 1] % 4 == 0 && p.b.stride[rank - 1] >= K;
+    if (!b_n_major && !b_k_major) return false;
+    form.bf16 = p;
+    form.bf16.kernel = DFGPU_MATMUL_UMMA_BF16;
+    dfgpu_tensor& a = form.bf16.a;
+    dfgpu_tensor& b = form.bf16.b;
+    a.dtype = b.dtype = DFGPU_BF16;
+    a.dim[rank - 1] = kSplitPieces * K;
+    a.stride[rank - 2] = kSplitPieces * K;
+    b.dim[rank - 2] = kSplitPieces * K;
+    if (b_n_major) {
+        b.stride[rank - 2] = N;  // [6K, N], N contiguous
+        b.stride[rank - 1] = 1;
+    } else {
+        b.stride[rank - 2] = 1;  // [N, 6K] seen as [6K, N] with K contiguous
+        b.stride[rank - 1] = kSplitPieces * K;
+    }
+    if (!matmul_umma_supported(form.bf16, DFGPU_MATMUL_UMMA_BF16)) return false;
+    form.a = SplitOperand{nullptr, nullptr, M * K / 4, K / 4, p.a.stride[rank - 2], kSplitPieces * K, K};
+    form.b = b_n_major ? SplitOperand{nullptr, nullptr, K * N / 4, N / 4, p.b.stride[rank - 2], N, K * N}
+                       : SplitOperand{nullptr, nullptr, N * K / 4, K / 4, p.b.stride[rank - 1], kSplitPieces * K, K};
+    auto round_up = [](int64_t v) { return (v + 255) / 256 * 256; };
+    form.flag_count = split_flag_count(form.a, form.b);
+    form.as_offset = 0;
+    form.bs_offset = round_up(M * K * kSplitPieces * 2);
+    form.flags_offset = form.bs_offset + round_up(K * N * kSplitPieces * 2);
+    form.scratch_bytes = form.flags_offset + round_up(static_cast<int64_t>(form.flag_count) * 4);
+    return true;
+}
+
 int choose_kernel(const dfgpu_matmul_params& p, int& kernel) {
     int automatic = DFGPU_MATMUL_FFMA;
+    SplitMatmul split;
+    const bool split_ok = f32_split_matmul(p, split);
     if (matmul_umma_supported(p, DFGPU_MATMUL_UMMA_MXF8)) automatic = DFGPU_MATMUL_UMMA_MXF8;
     else if (matmul_umma_supported(p, DFGPU_MATMUL_UMMA_BF16)) automatic = DFGPU_MATMUL_UMMA_BF16;
+    else if (split_ok) automatic = DFGPU_MATMUL_UMMA_F32X3;
     kernel = p.kernel == DFGPU_MATMUL_AUTO ? automatic : p.kernel;
-    if (kernel < DFGPU_MATMUL_FFMA || kernel > DFGPU_MATMUL_UMMA_MXF8) return fail(kInvalidArgument, "MATMUL: unknown kernel id %d", kernel);
+    if (kernel < DFGPU_MATMUL_FFMA || kernel > DFGPU_MATMUL_UMMA_F32X3) return fail(kInvalidArgument, "MATMUL: unknown kernel id %d", kernel);
+    if (kernel == DFGPU_MATMUL_UMMA_F32X3) {
+        if (!split_ok) return fail(kUnsupported, "MATMUL: the split-operand tcgen05 form needs unbatched f32 A (K contiguous), B and C, K a multiple of 32, N of 64");
+        return kOk;
+    }
     if (kernel != DFGPU_MATMUL_FFMA && !matmul_umma_supported(p, kernel))
         return fail(kUnsupported, "MATMUL: the requested tcgen05 kernel does not cover this shape, layout or type");
     return kOk;
@@ -222,11 +286,16 @@ extern "C" int dfgpu_query_matmul(const dfgpu_matmul_params* p, dfgpu_plan_info*
     info->kernel = kernel;
     info->launches = 1;
     info->scratch_bytes = 0;
+    if (kernel == DFGPU_MATMUL_UMMA_F32X3) {
+        SplitMatmul split;
+        f32_split_matmul(*p, split);
+        info->launches = 3;
+        info->scratch_bytes = split.scratch_bytes;
+    }
     return kOk;
 }
 
 extern "C" int dfgpu_matmul(const dfgpu_matmul_params* p, void* const* tensors, void* scratch, void* stream_handle) {
-    (void)scratch;
     if (!p || !tensors) return fail(kInvalidArgument, "MATMUL: null params");
     if (!tensors[0] || !tensors[1] || !tensors[2]) return fail(kInvalidArgument, "MATMUL: null tensor pointer");
     if ((p->a_scale.rank && !tensors[3]) || (p->b_scale.rank && !tensors[4])) return fail(kInvalidArgument, "MATMUL: null block scale pointer");
@@ -237,11 +306,32 @@ extern "C" int dfgpu_matmul(const dfgpu_matmul_params* p, void* const* tensors, 
     status = choose_kernel(*p, kernel);
     if (status) return status;
     cudaStream_t stream = as_stream(stream_handle);
+    if (kernel == DFGPU_MATMUL_UMMA_F32X3) {
+        SplitMatmul split;
+        if (!f32_split_matmul(*p, split)) return fail(kUnsupported, "MATMUL: the split-operand tcgen05 form does not take this matmul");
+        if (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 15u) != 0 || (reinterpret_cast<uintptr_t>(tensors[0]) & 15u) != 0 ||
+            (reinterpret_cast<uintptr_t>(tensors[1]) & 15u) != 0)
+            return fail(kInvalidArgument, "MATMUL: the split-operand tcgen05 form needs 16-byte aligned A and B and its 16-byte aligned scratch (dfgpu_query_matmul gives the size)");
+        uint8_t* base = static_cast<uint8_t*>(scratch);
+        split.a.source = static_cast<const float*>(tensors[0]);
+        split.a.pieces = reinterpret_cast<uint16_t*>(base + split.as_offset);
+        split.b.source = static_cast<const float*>(tensors[1]);
+        split.b.pieces = reinterpret_cast<uint16_t*>(base + split.bs_offset);
+        int* flags = reinterpret_cast<int*>(base + split.flags_offset);
+        status = launch_split6(split.a, split.b, flags, stream);
+        if (status) return status;
+        void* bf16_tensors[7] = {split.a.pieces, split.b.pieces, tensors[2], nullptr, nullptr, tensors[5], tensors[6]};
+        status = launch_matmul_umma(split.bf16, bf16_tensors, DFGPU_MATMUL_UMMA_BF16, stream);
+        if (status) return status;
+        dim3 grid(static_cast<unsigned>((g.m + 63) / 64), static_cast<unsigned>((g.n + 63) / 64), 1);
+        matmul_ffma_kernel<<<grid, 256, 0, stream>>>(tensors[0], tensors[1], tensors[2], g, flags, split.flag_count);
+        return check_launch("MATMUL");
+    }
     if (kernel != DFGPU_MATMUL_FFMA) return launch_matmul_umma(*p, tensors, kernel, stream);
     int64_t batches = 1;
     for (int i = 0; i < g.rank - 2; ++i) batches *= p->c.dim[i];
     if (batches > 65535) return fail(kUnsupported, "MATMUL: more than 65535 batch matrices");
     dim3 grid(static_cast<unsigned>((g.m + 63) / 64), static_cast<unsigned>((g.n + 63) / 64), static_cast<unsigned>(batches));
-    matmul_ffma_kernel<<<grid, 256, 0, stream>>>(tensors[0], tensors[1], tensors[2], g);
+    matmul_ffma_kernel<<<grid, 256, 0, stream>>>(tensors[0], tensors[1], tensors[2], g, nullptr, 0);
     return check_launch("MATMUL");
 }

@@ -38,6 +38,22 @@ bool conv_pair_umma_supported(const dfgpu_conv_params& first, const dfgpu_conv_p
 int launch_conv_pair_umma(const dfgpu_conv_params& first, const dfgpu_conv_params& second, void* const* tensors, cudaStream_t stream);
 int conv_pair_device_status(int* status);
 
+// ---- f32 operands as six-piece bf16 copies (split_f32.cu) -------------------------------------------------
+// `quads` float4 groups of `source` (rows of row_quads float4, source_ld floats apart) become bf16 pieces at
+// pieces + row * row_stride + j * piece_stride + column, j = 0..5 in the operand's piece order. A K-contiguous operand
+// [rows, K] becomes [rows, 6K] with row_stride = 6K and piece_stride = K; an N-contiguous operand [K, N] becomes
+// [6K, N] with row_stride = N and piece_stride = K * N. One flag per CTA (split_flag_count of them): 1 when the CTA saw
+// an infinity or a NaN.
+constexpr int kSplitQuadsPerCta = 1024;  // 256 threads x 4 float4
+constexpr int kSplitPieces = 6;           // bf16 values per f32 value
+struct SplitOperand {
+    const float* source;
+    uint16_t* pieces;
+    int64_t quads, row_quads, source_ld, row_stride, piece_stride;
+};
+int split_flag_count(const SplitOperand& first, const SplitOperand& second);
+int launch_split6(const SplitOperand& first, const SplitOperand& second, int* flags, cudaStream_t stream);
+
 // MATMUL on tcgen05: kernel is DFGPU_MATMUL_UMMA_BF16 or DFGPU_MATMUL_UMMA_MXF8.
 bool matmul_umma_supported(const dfgpu_matmul_params& p, int kernel);
 int launch_matmul_umma(const dfgpu_matmul_params& p, void* const* tensors, int kernel, cudaStream_t stream);

@@ -200,7 +200,10 @@ int dfgpu_conv_fprop_pair(const dfgpu_conv_pair_params*, void* const* tensors, v
    that feed A and B (SpecializedGraph.cpp:752-795), reading E4M3 codes and
    E8M0 scales directly. tensors: {A, B, C, A_scale or null, B_scale or null,
    extra0 or null, extra1 or null}. */
-enum { DFGPU_MATMUL_AUTO = 0, DFGPU_MATMUL_FFMA = 1, DFGPU_MATMUL_UMMA_BF16 = 2, DFGPU_MATMUL_UMMA_MXF8 = 3 };
+/* UMMA_F32X3: f32 A, B and C on tcgen05: A and B split into three bf16 pieces each, six bf16 products (2^-24 relative);
+   needs scratch, three launches (split, the bf16 matmul over 6K, and the CUDA-core kernel again, which returns at once
+   unless A or B held an infinity or a NaN). */
+enum { DFGPU_MATMUL_AUTO = 0, DFGPU_MATMUL_FFMA = 1, DFGPU_MATMUL_UMMA_BF16 = 2, DFGPU_MATMUL_UMMA_MXF8 = 3, DFGPU_MATMUL_UMMA_F32X3 = 4 };
 typedef struct dfgpu_matmul_params {
     dfgpu_tensor a, b, c;
     dfgpu_tensor a_scale, b_scale;

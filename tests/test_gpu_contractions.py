@@ -265,8 +265,47 @@ def run_matmul(dtype, a_dims, b_dims, kernel=dfgpu.MATMUL_FFMA, a_strides=None, 
     p.a, p.b, p.c, p.kernel = tensor(dtype, a_dims, a_strides), tensor(dtype, b_dims, b_strides), tensor(dtype, c_dims), kernel
     da, db = g.to_device(host_array(a, dtype)), g.to_device(host_array(b, dtype))
     dc = g.device_zeros(ref.size * dfgpu.DTYPE_BYTES[dtype])
-    dfgpu.matmul(p, g.ptr(da), g.ptr(db), g.ptr(dc))
+    info = dfgpu.query("matmul", p)
+    scratch = g.device_zeros(info.scratch_bytes, 0xA5) if info.scratch_bytes else None
+    dfgpu.matmul(p, g.ptr(da), g.ptr(db), g.ptr(dc), scratch=g.ptr(scratch))
     return read_back(dc, dtype, -1), ref
+
+
+@pytest.mark.parametrize("a_dims,b_dims,b_strides", [([256, 128], [128, 192], None), ([130, 96], [96, 64], None), ([200, 64], [64, 128], [1, 64]),
+                                                    ([1024, 1024], [1024, 1024], None)])
+def test_matmul_f32_on_tensor_cores(a_dims, b_dims, b_strides):
+    """f32 A, B, C resolve to the split-operand tcgen05 form (six bf16 products, f32 accumulation) and hold the f32 gates
+    against the oracle, for N-contiguous and K-contiguous B and a last row tile that is not full."""
+    p = dfgpu.MatmulParams()
+    p.a, p.b, p.c = tensor(F32, a_dims), tensor(F32, b_dims, b_strides), tensor(F32, [a_dims[0], b_dims[1]])
+    info = dfgpu.query("matmul", p)
+    assert info.kernel == dfgpu.MATMUL_UMMA_F32X3 and info.launches == 3 and info.scratch_bytes > 0
+    out, ref = run_matmul(F32, a_dims, b_dims, kernel=dfgpu.MATMUL_AUTO, b_strides=b_strides)
+    check_f32(out, ref)
+    cores, _ = run_matmul(F32, a_dims, b_dims, kernel=dfgpu.MATMUL_FFMA, b_strides=b_strides)
+    assert float(np.max(np.abs(out - cores))) <= 3e-6 * float(np.max(np.abs(ref)))
+    assert not np.array_equal(out, cores)  # (the tensor-core result stands: no operand was infinite or NaN)
+
+
+def test_matmul_f32_split_form_with_non_finite_operand():
+    """An infinity in A: the CUDA-core kernel behind the tensor-core one redoes the product, bit for bit its own result."""
+    a_dims, b_dims = [128, 64], [64, 64]
+    a = synthetic.normal(4, 1, 128 * 64).astype(np.float32)
+    b = np.full(64 * 64, 0.5, dtype=np.float32)  # (lower pieces of exactly zero: inf * 0 in the split products)
+    a[77] = np.inf
+    p = dfgpu.MatmulParams()
+    p.a, p.b, p.c = tensor(F32, a_dims), tensor(F32, b_dims), tensor(F32, [128, 64])
+    da, db = g.to_device(a), g.to_device(b)
+    results = {}
+    for kernel in (dfgpu.MATMUL_FFMA, dfgpu.MATMUL_UMMA_F32X3):
+        p.kernel = kernel
+        info = dfgpu.query("matmul", p)
+        dc = g.device_zeros(128 * 64 * 4, 0x5A)
+        scratch = g.device_zeros(info.scratch_bytes, 0xA5) if info.scratch_bytes else None
+        dfgpu.matmul(p, g.ptr(da), g.ptr(db), g.ptr(dc), scratch=g.ptr(scratch))
+        results[kernel] = g.to_host(dc, np.uint32).copy()
+    assert np.array_equal(results[dfgpu.MATMUL_FFMA], results[dfgpu.MATMUL_UMMA_F32X3])
+    assert np.isinf(results[dfgpu.MATMUL_FFMA].view(np.float32)).any()
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
