@@ -283,7 +283,7 @@ def test_matmul_f32_on_tensor_cores(a_dims, b_dims, b_strides):
     out, ref = run_matmul(F32, a_dims, b_dims, kernel=dfgpu.MATMUL_AUTO, b_strides=b_strides)
     check_f32(out, ref)
     cores, _ = run_matmul(F32, a_dims, b_dims, kernel=dfgpu.MATMUL_FFMA, b_strides=b_strides)
-    assert float(np.max(np.abs(out - cores))) <= 3e-6 * float(np.max(np.abs(ref)))
+    assert float(np.max(np.abs(out - cores))) <= 2e-5 * float(np.max(np.abs(ref)))  # (each carries its own f32 accumulation error)
     assert not np.array_equal(out, cores)  # (the tensor-core result stands: no operand was infinite or NaN)
 
 
