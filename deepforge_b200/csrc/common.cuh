@@ -44,6 +44,7 @@ inline bool is_packed_row_major(const dfgpu_tensor& t) {
 inline int dtype_bytes(int dtype) {
     switch (dtype) {
         case DFGPU_F32: case DFGPU_I32: case DFGPU_BF16X2: return 4;
+        case DFGPU_I64: return 8;
         case DFGPU_E5M2: case DFGPU_U8: return 1;
         case DFGPU_F16: case DFGPU_BF16: return 2;
         default: return 1;

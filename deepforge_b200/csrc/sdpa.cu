@@ -42,6 +42,12 @@ struct SdpaArgs {
     const int32_t* seq_kv_data;
     const int32_t* table_k_data;
     const int32_t* table_v_data;
+    // compact page tables: per-batch element offsets into the table's storage (null: the table is strided [B,1,P,1])
+    const void* offsets_k_data;
+    const void* offsets_v_data;
+    int32_t offsets_k_wide, offsets_v_wide;      // INT64 offsets
+    int64_t offsets_k_stride, offsets_v_stride;  // elements between consecutive batch entries
+    const int* prefix_ok;                        // [2] written by the validation kernel: K table, V table
     float scale;
     int32_t padding, has_left, has_right, bottom_right;
     int64_t left, right, s_kv;
@@ -75,18 +81,75 @@ __device__ __forceinline__ void valid_range(const SdpaArgs& a, int64_t ib, int64
     if (hi < 0) hi = 0;
 }
 
-// Base offset of the row (token ikv, head) of a K/V container, or -1 for an invalid page.
-__device__ __forceinline__ int64_t kv_row_offset(const View& t, const View& table, const int32_t* table_data,
-                                                 int64_t ib, int64_t head, int64_t ikv) {
+__device__ __forceinline__ int64_t load_offset(const void* data, int wide, int64_t index) {
+    return wide ? static_cast<const int64_t*>(data)[index] : static_cast<int64_t>(static_cast<const int32_t*>(data)[index]);
+}
+
+// Page id of (batch ib, table slot), or -1 where the table holds none: a strided table has dim[2] slots per batch; a
+// compact one (which = 0 K, 1 V) has the slots its batch's sequence length needs, at offsets[ib] + slot * stride[2],
+// and none at all when its prefix failed validation.
+__device__ __forceinline__ int64_t page_of_slot(const SdpaArgs& a, int which, int64_t ib, int64_t slot) {
+    const View& table = which ? a.table_v : a.table_k;
+    const int32_t* data = which ? a.table_v_data : a.table_k_data;
+    const void* offsets = which ? a.offsets_v_data : a.offsets_k_data;
+    if (!offsets) return slot < table.dim[2] ? static_cast<int64_t>(data[off4(table, ib, 0, slot, 0)]) : -1;
+    if (!a.prefix_ok[which]) return -1;
+    const int64_t block = which ? a.v.dim[2] : a.k.dim[2];
+    const int64_t length = a.seq_kv_data[ib * a.seq_kv.stride[0]];
+    if (slot >= (length + block - 1) / block) return -1;
+    const int64_t base = load_offset(offsets, which ? a.offsets_v_wide : a.offsets_k_wide, ib * (which ? a.offsets_v_stride : a.offsets_k_stride));
+    return data[base + slot * table.stride[2]];
+}
+
+// Base offset of the row (token ikv, head) of a K/V container (which = 0 K, 1 V), or -1 for an invalid page.
+__device__ __forceinline__ int64_t kv_row_offset(const SdpaArgs& a, int which, int64_t ib, int64_t head, int64_t ikv) {
+    const View& t = which ? a.v : a.k;
+    const View& table = which ? a.table_v : a.table_k;
     if (table.rank == 0) return off4(t, ib, head, ikv, 0);
     int64_t block = t.dim[2];
     int64_t slot = ikv / block, within = ikv - slot * block;
-    int64_t page = table_data[off4(table, ib, 0, slot, 0)];
+    int64_t page = page_of_slot(a, which, ib, slot);
     if (page < 0 || page >= t.dim[0]) return -1;
     return off4(t, page, head, within, 0);
 }
 
+// Validation of a compact page table's batch prefix, one CTA per table (blockIdx.x = 0 K, 1 V): the rules of the
+// reference's host-side check (lib/Runtime/Executable.cpp:619-716), applied where the offsets live. Writes
+// prefix_ok[table] and, on failure, a status code the host reads through dfgpu_device_status().
+__device__ int g_sdpa_status = 0;
+
+__global__ void __launch_bounds__(256)
+validate_page_prefix_kernel(SdpaArgs a, int* prefix_ok) {
+    const int which = blockIdx.x;
+    const void* offsets = which ? a.offsets_v_data : a.offsets_k_data;
+    if (!offsets) {
+        if (threadIdx.x == 0) prefix_ok[which] = 1;
+        return;
+    }
+    const View& table = which ? a.table_v : a.table_k;
+    const int wide = which ? a.offsets_v_wide : a.offsets_k_wide;
+    const int64_t stride = which ? a.offsets_v_stride : a.offsets_k_stride;
+    const int64_t batches = table.dim[0], block = which ? a.v.dim[2] : a.k.dim[2];
+    const int64_t bound = batches * ((table.dim[2] - 1) * table.stride[2] + 1);  // the compiled storage bound, in entries
+    bool bad = load_offset(offsets, wide, 0) != 0;
+    for (int64_t b = threadIdx.x; b < batches; b += blockDim.x) {
+        const int64_t start = load_offset(offsets, wide, b * stride), end = load_offset(offsets, wide, (b + 1) * stride);
+        const int64_t length = a.seq_kv_data[b * a.seq_kv.stride[0]];
+        if (start < 0 || end < start || end > bound) bad = true;
+        if (length < 0 || length > table.dim[2] * block) bad = true;
+        const int64_t slots = (length + block - 1) / block;
+        const int64_t needed = slots > 0 ? 1 + (slots - 1) * table.stride[2] : 0;
+        if (end - start < needed) bad = true;
+    }
+    const int any_bad = __syncthreads_or(bad ? 1 : 0);
+    if (threadIdx.x == 0) {
+        prefix_ok[which] = any_bad ? 0 : 1;
+        if (any_bad) atomicCAS(&g_sdpa_status, 0, 601 + which);
+    }
+}
+
 constexpr int kRowwiseMaxD = 256;
+constexpr int kPrefixScratchBytes = 256;  // the two validation results of compact page tables, ahead of a kernel's own scratch
 
 __global__ void __launch_bounds__(128)
 sdpa_rowwise_kernel(SdpaArgs a, int64_t rows) {
@@ -127,7 +190,7 @@ sdpa_rowwise_kernel(SdpaArgs a, int64_t rows) {
             enabled = ((byte >> (key_tile & 7)) & 1u) != 0u;
         }
         if (enabled) {
-            int64_t offset = kv_row_offset(a.k, a.table_k, a.table_k_data, ib, kh, ikv);
+            int64_t offset = kv_row_offset(a, 0, ib, kh, ikv);
             float dot = 0.0f;
             if (offset >= 0) {
                 if (a.k.dtype == DFGPU_BF16 && (dqk & 7) == 0 && (offset & 7) == 0 &&
@@ -175,7 +238,7 @@ sdpa_rowwise_kernel(SdpaArgs a, int64_t rows) {
         int count = static_cast<int>(hi - base < 32 ? hi - base : 32);
         for (int j = 0; j < count; ++j) {
             float pj = __shfl_sync(0xffffffffu, probability, j);
-            int64_t offset = kv_row_offset(a.v, a.table_v, a.table_v_data, ib, vh, base + j);
+            int64_t offset = kv_row_offset(a, 1, ib, vh, base + j);
             if (offset < 0) continue;
 #pragma unroll
             for (int i = 0; i < kRowwiseMaxD / 32; ++i) {
@@ -248,12 +311,12 @@ sdpa_paged_decode_kernel(SdpaArgs a, float* __restrict__ partial, int max_chunks
     if (tid < pages_in_chunk) {
         int64_t slot = chunk_begin / block + tid;
         int64_t kb = -1, vb = -1;
-        if (slot < a.table_k.dim[2]) {
-            int64_t page = a.table_k_data[off4(a.table_k, ib, 0, slot, 0)];
+        {
+            int64_t page = page_of_slot(a, 0, ib, slot);
             if (page >= 0 && page < a.k.dim[0]) kb = page * a.k.stride[0] + hkv * a.k.stride[1];
         }
-        if (slot < a.table_v.dim[2]) {
-            int64_t page = a.table_v_data[off4(a.table_v, ib, 0, slot, 0)];
+        {
+            int64_t page = page_of_slot(a, 1, ib, slot);
             if (page >= 0 && page < a.v.dim[0]) vb = page * a.v.stride[0] + hkv * a.v.stride[1];
         }
         page_base_k[tid] = kb;
@@ -452,7 +515,15 @@ int build_args(const dfgpu_sdpa_params& p, void* const* tensors, SdpaArgs& a) {
         if (table.rank != 4 || table.dtype != DFGPU_I32 || table.dim[0] != p.q.dim[0] || table.dim[1] != 1 || table.dim[3] != 1)
             return fail(kInvalidShape, "SDPA: page table must be INT32 [B,1,P,1]");
         if (table.dim[2] * containers[i]->dim[2] < p.s_kv) return fail(kInvalidShape, "SDPA: page table capacity is below the key/value length");
+        const dfgpu_tensor& offsets = i == 0 ? p.page_offsets_k : p.page_offsets_v;
+        if (offsets.rank != 0) {
+            if (offsets.rank != 4 || (offsets.dtype != DFGPU_I32 && offsets.dtype != DFGPU_I64) || offsets.dim[0] != p.q.dim[0] + 1 || offsets.dim[1] != 1 ||
+                offsets.dim[2] != 1 || offsets.dim[3] != 1)
+                return fail(kInvalidShape, "SDPA: page table offsets must be INT32 or INT64 [B+1,1,1,1]");
+            if (table.stride[2] <= 0) return fail(kInvalidLayout, "SDPA: a compact page table needs a positive slot stride");
+        }
     }
+    if ((p.page_offsets_k.rank && !paged_k) || (p.page_offsets_v.rank && !paged_v)) return fail(kInvalidArgument, "SDPA: page table offsets without a page table");
     if ((paged_k || paged_v) && !p.padding_mask) return fail(kInvalidArgument, "SDPA: paged K/V requires the padding mask and sequence lengths");
     if (p.padding_mask) {
         if (p.seq_q.rank == 0 || p.seq_kv.rank == 0 || p.seq_q.dtype != DFGPU_I32 || p.seq_kv.dtype != DFGPU_I32)
@@ -483,6 +554,15 @@ int build_args(const dfgpu_sdpa_params& p, void* const* tensors, SdpaArgs& a) {
         if (p.padding_mask && (!a.seq_q_data || !a.seq_kv_data)) return fail(kInvalidArgument, "SDPA: null sequence length pointer");
         if ((paged_k && !a.table_k_data) || (paged_v && !a.table_v_data)) return fail(kInvalidArgument, "SDPA: null page table pointer");
     }
+    a.offsets_k_data = (tensors && p.page_offsets_k.rank) ? tensors[14] : nullptr;  // (read only when declared: shorter pointer lists stay valid)
+    a.offsets_v_data = (tensors && p.page_offsets_v.rank) ? tensors[15] : nullptr;
+    if (tensors && ((p.page_offsets_k.rank && !a.offsets_k_data) || (p.page_offsets_v.rank && !a.offsets_v_data)))
+        return fail(kInvalidArgument, "SDPA: null page table offsets pointer");
+    a.offsets_k_wide = p.page_offsets_k.dtype == DFGPU_I64;
+    a.offsets_v_wide = p.page_offsets_v.dtype == DFGPU_I64;
+    a.offsets_k_stride = p.page_offsets_k.rank ? p.page_offsets_k.stride[0] : 0;
+    a.offsets_v_stride = p.page_offsets_v.rank ? p.page_offsets_v.stride[0] : 0;
+    a.prefix_ok = nullptr;
     a.bias = make_view(p.bias);
     a.bias_data = (tensors && p.bias.rank) ? tensors[11] : nullptr;  // callers without a bias may pass 11 pointers
     if (p.bias.rank) {
@@ -593,6 +673,10 @@ extern "C" int dfgpu_query_sdpa_forward(const dfgpu_sdpa_params* p, dfgpu_plan_i
         info->launches = 2;
         info->scratch_bytes = decode_umma_scratch_bytes(*p);
     }
+    if (p->page_offsets_k.rank || p->page_offsets_v.rank) {  // compact page tables: the validation launch and its two result words
+        info->launches += 1;
+        info->scratch_bytes += kPrefixScratchBytes;
+    }
     return kOk;
 }
 
@@ -605,10 +689,20 @@ extern "C" int dfgpu_sdpa_forward(const dfgpu_sdpa_params* p, void* const* tenso
     status = choose_kernel(*p, kernel);
     if (status) return status;
     cudaStream_t stream = as_stream(stream_handle);
+    if (p->page_offsets_k.rank || p->page_offsets_v.rank) {
+        // compact page tables: validate the prefixes on the device first; the attention kernels read the verdict
+        if (!scratch || !aligned16(scratch)) return fail(kInvalidArgument, "SDPA: compact page tables need the 16-byte aligned scratch dfgpu_query_sdpa_forward reports");
+        int* prefix_ok = static_cast<int*>(scratch);
+        scratch = static_cast<uint8_t*>(scratch) + kPrefixScratchBytes;
+        validate_page_prefix_kernel<<<2, 256, 0, stream>>>(a, prefix_ok);
+        status = check_launch("SDPA page table prefix validation");
+        if (status) return status;
+        a.prefix_ok = prefix_ok;
+    }
     if (kernel == DFGPU_SDPA_UMMA) return launch_sdpa_umma(*p, tensors, scratch, stream);
     if (kernel == DFGPU_SDPA_PAGED_DECODE_UMMA) {
         if (!scratch || !aligned16(scratch)) return fail(kInvalidArgument, "SDPA: the paged decode kernel needs its 16-byte aligned scratch buffer");
-        status = launch_decode_umma(*p, tensors, scratch, stream);
+        status = launch_decode_umma(*p, tensors, scratch, a.prefix_ok, stream);
         if (status) return status;
         const int chunks = decode_umma_chunks(*p);
         sdpa_decode_merge_kernel<<<static_cast<unsigned>(p->q.dim[0] * p->q.dim[1]), kDecodeD, 0, stream>>>(a, static_cast<const float*>(scratch), chunks, 1024);
@@ -637,6 +731,16 @@ extern "C" int dfgpu_sdpa_forward(const dfgpu_sdpa_params* p, void* const* tenso
     sdpa_rowwise_kernel<<<static_cast<unsigned>((rows + 3) / 4), 128, 0, stream>>>(a, rows);
     return check_launch("SDPA");
 }
+
+namespace dfgpu {
+int sdpa_device_status(int* status) {
+    int zero = 0;
+    cudaError_t error = cudaMemcpyFromSymbol(status, g_sdpa_status, sizeof(int));
+    if (error == cudaSuccess) error = cudaMemcpyToSymbol(g_sdpa_status, &zero, sizeof(int));
+    if (error != cudaSuccess) return fail(kExecutionFailed, "device_status: %s", cudaGetErrorString(error));
+    return kOk;
+}
+}  // namespace dfgpu
 
 // ---- paged decode for callers that cannot allocate ---------------------------------------
 //
@@ -698,8 +802,9 @@ extern "C" int dfgpu_sdpa_paged_decode_static(const dfgpu_sdpa_params* p, void* 
     SdpaArgs a;
     int status = build_args(*p, tensors, a);
     if (status) return status;
-    if (!decode_supported(*p) || p->bias.rank != 0 || p->alibi_mask || p->sink.rank != 0 || p->block_mask.rank != 0)
-        return fail(kUnsupported, "SDPA static decode: needs Sq=1, bf16, D=128, paged K and V, group size 1/2/4/8, no bias or ALiBi");
+    if (!decode_supported(*p) || p->bias.rank != 0 || p->alibi_mask || p->sink.rank != 0 || p->block_mask.rank != 0 || p->page_offsets_k.rank != 0 ||
+        p->page_offsets_v.rank != 0)
+        return fail(kUnsupported, "SDPA static decode: needs Sq=1, bf16, D=128, strided page tables for K and V, group size 1/2/4/8, no bias or ALiBi");
     if (!aligned16(a.q_data) || !aligned16(a.k_data) || !aligned16(a.v_data))
         return fail(kInvalidArgument, "SDPA static decode: needs 16-byte aligned Q, K and V");
     const int chunks = decode_chunks(*p);

@@ -76,7 +76,8 @@ int sdpa_umma_device_status(int* status);  // reads and clears that unit's statu
 bool decode_umma_supported(const dfgpu_sdpa_params& p);
 int decode_umma_chunks(const dfgpu_sdpa_params& p);
 int64_t decode_umma_scratch_bytes(const dfgpu_sdpa_params& p);
-int launch_decode_umma(const dfgpu_sdpa_params& p, void* const* tensors, void* scratch, cudaStream_t stream);
+int launch_decode_umma(const dfgpu_sdpa_params& p, void* const* tensors, void* scratch, const int* prefix_ok, cudaStream_t stream);  // prefix_ok: the validation result of compact page tables (null without them)
+int sdpa_device_status(int* status);  // (sdpa.cu: compact page table validation)
 int decode_umma_device_status(int* status);
 
 }  // namespace dfgpu

@@ -45,6 +45,13 @@ struct DecodeArgs {
     const int32_t* table_v;
     int64_t seq_q_stride, seq_kv_stride, table_k_stride, table_v_stride, table_k_slot_stride, table_v_slot_stride;
     float* partial;
+    // compact page tables (null offsets: strided [B,1,P,1]): entry (b, slot) at offsets[b] + slot * slot stride, only
+    // the slots the batch's sequence length needs, and none when the prefix failed validation (prefix_ok[0 K | 1 V])
+    const void* offsets_k;
+    const void* offsets_v;
+    int32_t offsets_k_wide, offsets_v_wide;
+    int64_t offsets_k_stride, offsets_v_stride;
+    const int* prefix_ok;
 };
 
 template <int kRingSlots>
@@ -181,9 +188,20 @@ sdpa_decode_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const int entry = threadIdx.x & 63;
         const int64_t table_slot = chunk_begin / args.block + entry;
         int64_t page = -1;
+        const void* offsets = is_v ? args.offsets_v : args.offsets_k;
         if (entry < kTilesPerCta * args.pages_per_tile && table_slot < (is_v ? args.table_len_v : args.table_len_k)) {
-            page = is_v ? args.table_v[batch * args.table_v_stride + table_slot * args.table_v_slot_stride]
-                        : args.table_k[batch * args.table_k_stride + table_slot * args.table_k_slot_stride];
+            if (!offsets) {
+                page = is_v ? args.table_v[batch * args.table_v_stride + table_slot * args.table_v_slot_stride]
+                            : args.table_k[batch * args.table_k_stride + table_slot * args.table_k_slot_stride];
+            } else if (args.prefix_ok[is_v ? 1 : 0]) {
+                const int64_t length = args.seq_kv[batch * args.seq_kv_stride];
+                if (table_slot < (length + args.block - 1) / args.block) {
+                    const int64_t at = batch * (is_v ? args.offsets_v_stride : args.offsets_k_stride);
+                    const int64_t base = (is_v ? args.offsets_v_wide : args.offsets_k_wide) ? static_cast<const int64_t*>(offsets)[at]
+                                                                                          : static_cast<int64_t>(static_cast<const int32_t*>(offsets)[at]);
+                    page = is_v ? args.table_v[base + table_slot * args.table_v_slot_stride] : args.table_k[base + table_slot * args.table_k_slot_stride];
+                }
+            }
         }
         page_ids[threadIdx.x] = (page >= 0 && page < args.num_pages) ? static_cast<int32_t>(page) : -1;
     }
@@ -455,7 +473,7 @@ int64_t decode_umma_scratch_bytes(const dfgpu_sdpa_params& p) {
     return p.q.dim[0] * p.q.dim[1] * decode_umma_chunks(p) * kPartialStride * static_cast<int64_t>(sizeof(float));
 }
 
-int launch_decode_umma(const dfgpu_sdpa_params& p, void* const* tensors, void* scratch, cudaStream_t stream) {
+int launch_decode_umma(const dfgpu_sdpa_params& p, void* const* tensors, void* scratch, const int* prefix_ok, cudaStream_t stream) {
     for (int i = 0; i < 3; ++i)
         if ((reinterpret_cast<uintptr_t>(tensors[i]) & 15u) != 0) return fail(kInvalidArgument, "SDPA: the paged decode kernel needs 16-byte aligned Q, K and V");
     const int64_t batch = p.q.dim[0], hq = p.q.dim[1], hkv = p.k.dim[1], block = p.k.dim[2], pages = p.k.dim[0];
@@ -498,6 +516,13 @@ int launch_decode_umma(const dfgpu_sdpa_params& p, void* const* tensors, void* s
     args.table_k_slot_stride = p.page_table_k.stride[2];
     args.table_v_slot_stride = p.page_table_v.stride[2];
     args.partial = static_cast<float*>(scratch);
+    args.offsets_k = p.page_offsets_k.rank ? tensors[14] : nullptr;
+    args.offsets_v = p.page_offsets_v.rank ? tensors[15] : nullptr;
+    args.offsets_k_wide = p.page_offsets_k.dtype == DFGPU_I64;
+    args.offsets_v_wide = p.page_offsets_v.dtype == DFGPU_I64;
+    args.offsets_k_stride = p.page_offsets_k.rank ? p.page_offsets_k.stride[0] : 0;
+    args.offsets_v_stride = p.page_offsets_v.rank ? p.page_offsets_v.stride[0] : 0;
+    args.prefix_ok = prefix_ok;
     dim3 grid(static_cast<unsigned>(args.max_chunks), static_cast<unsigned>(hkv), static_cast<unsigned>(batch));
     auto run = [&](auto kernel, int dynamic) -> int {
         cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dynamic);

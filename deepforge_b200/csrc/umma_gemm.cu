@@ -1173,6 +1173,10 @@ extern "C" int dfgpu_device_status(int* status) {
     if (code) return code;
     code = decode_umma_device_status(&decode);
     if (code) return code;
+    int prefix = 0;
+    code = sdpa_device_status(&prefix);
+    if (code) return code;
+    if (!decode) decode = prefix;
     *status = gemm ? gemm : (sdpa ? sdpa : decode);
     return kOk;
 }

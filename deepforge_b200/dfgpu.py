@@ -13,9 +13,9 @@ from typing import Iterable, Optional, Sequence
 MAX_RANK = 8
 MAX_EPILOGUE = 4
 
-F32, F16, BF16, E4M3, E8M0, I32, E5M2, U8, BF16X2 = range(9)
+F32, F16, BF16, E4M3, E8M0, I32, E5M2, U8, BF16X2, I64 = range(10)
 REORDER_NONE, REORDER_F8_128x4 = 0, 1
-DTYPE_BYTES = {F32: 4, F16: 2, BF16: 2, E4M3: 1, E8M0: 1, I32: 4, E5M2: 1, U8: 1, BF16X2: 4}
+DTYPE_BYTES = {F32: 4, F16: 2, BF16: 2, E4M3: 1, E8M0: 1, I32: 4, E5M2: 1, U8: 1, BF16X2: 4, I64: 8}
 
 EPI_ADD, EPI_RELU = 1, 2
 PW_ADD, PW_RELU_FWD, PW_IDENTITY, PW_MUL, PW_SUB = range(5)
@@ -106,7 +106,8 @@ class SdpaParams(C.Structure):
                 ("page_table_v", Tensor), ("attn_scale", C.c_float), ("padding_mask", C.c_int32),
                 ("has_left_bound", C.c_int32), ("has_right_bound", C.c_int32), ("left_bound", C.c_int64),
                 ("right_bound", C.c_int64), ("bottom_right", C.c_int32), ("kernel", C.c_int32), ("s_kv", C.c_int64),
-                ("bias", Tensor), ("alibi_mask", C.c_int32), ("reserved", C.c_int32), ("sink", Tensor), ("block_mask", Tensor)]
+                ("bias", Tensor), ("alibi_mask", C.c_int32), ("reserved", C.c_int32), ("sink", Tensor), ("block_mask", Tensor),
+                ("page_offsets_k", Tensor), ("page_offsets_v", Tensor)]
 
 
 # every symbol include/dfgpu.h declares
@@ -211,9 +212,10 @@ def matmul_fp8(params, a, b, c, amax, descale_a, descale_b, scale_c, scratch=Non
 
 
 def sdpa_forward(params, pointers: Sequence[Optional[int]], scratch=None, stream=None):
-    """pointers: Q, K, V, O, Stats, Max, Sum_exp, SEQ_LEN_Q, SEQ_LEN_KV, Page_table_K, Page_table_V[, Bias[, SINK_TOKEN[, Block_mask]]]."""
-    assert 11 <= len(pointers) <= 14
-    pointers = list(pointers) + [None] * (14 - len(pointers))
+    """pointers: Q, K, V, O, Stats, Max, Sum_exp, SEQ_LEN_Q, SEQ_LEN_KV, Page_table_K, Page_table_V[, Bias[, SINK_TOKEN[, Block_mask[,
+    Page_table_K offsets, Page_table_V offsets]]]]."""
+    assert 11 <= len(pointers) <= 16
+    pointers = list(pointers) + [None] * (16 - len(pointers))
     _call("dfgpu_sdpa_forward", params, pointers, scratch, stream)
 
 

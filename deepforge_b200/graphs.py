@@ -162,13 +162,19 @@ def c4_sdpa(b=8, h=32, s=2048, d=128, io: str = "BFLOAT16", causal: bool = True,
     return document("c4_sdpa", [node], t, io=io)
 
 
-def c5_paged_decode(batch=64, hq=32, hkv=8, d=128, pages=16384, block=64, max_len=8192, io: str = "BFLOAT16") -> dict:
+def c5_paged_decode(batch=64, hq=32, hkv=8, d=128, pages=16384, block=64, max_len=8192, io: str = "BFLOAT16", compact: bool = False) -> dict:
+    """compact: the page tables are stored back to back with only the slots each sequence needs (ragged batch prefix):
+    tensors 9 (INT64) and 10 (INT32) hold the per-sequence offsets into them, [batch + 1, 1, 1, 1]."""
     table = max_len // block
     t = [
         tensor(1, "Q", [batch, hq, 1, d], io), tensor(2, "K", [pages, hkv, block, d], io), tensor(3, "V", [pages, hkv, block, d], io),
         tensor(4, "O", [batch, hq, 1, d], io), tensor(5, "SEQ_LEN_Q", [batch, 1, 1, 1], "INT32"), tensor(6, "SEQ_LEN_KV", [batch, 1, 1, 1], "INT32"),
         tensor(7, "Page_table_K", [batch, 1, table, 1], "INT32"), tensor(8, "Page_table_V", [batch, 1, table, 1], "INT32"),
     ]
+    if compact:
+        t[6].update(ragged_offset_uid=9, ragged_offset_name="Page_table_K_offsets")
+        t[7].update(ragged_offset_uid=10, ragged_offset_name="Page_table_V_offsets")
+        t += [tensor(9, "Page_table_K_offsets", [batch + 1, 1, 1, 1], "INT64"), tensor(10, "Page_table_V_offsets", [batch + 1, 1, 1, 1], "INT32")]
     node = sdpa_node("paged_decode", {"Q": 1, "K": 2, "V": 3, "SEQ_LEN_Q": 5, "SEQ_LEN_KV": 6, "Page_table_K": 7, "Page_table_V": 8},
                      {"O": 4}, d ** -0.5, True, False, max_seq_len_kv=max_len)
     return document("c5_paged_decode", [node], t, io=io)

@@ -125,7 +125,7 @@ std::size_t tensor_slots(KernelOp op) {
         case KernelOp::kPointwise: return 3;
         case KernelOp::kConvFprop: return 5;
         case KernelOp::kMatmul: return 7;
-        case KernelOp::kSdpaForward: return 14;
+        case KernelOp::kSdpaForward: return 16;
         case KernelOp::kMatmulFp8: return 7;
         case KernelOp::kConvFpropPair: return 8;
         case KernelOp::kBlockScaleQuantizePair: return 6;
@@ -268,6 +268,7 @@ Status read_plan(Reader& r, ArtifactInfo& info) {
 std::uint64_t element_bytes(int dtype) {
     switch (dtype) {
         case DFGPU_F32: case DFGPU_I32: case DFGPU_BF16X2: return 4;
+        case DFGPU_I64: return 8;
         case DFGPU_F16: case DFGPU_BF16: return 2;
         default: return 1;
     }
@@ -309,8 +310,9 @@ dfgpu_tensor const* slot_descriptor(KernelStep const& step, std::size_t slot) {
             return slot < 8 ? t[slot] : nullptr;
         }
         else if constexpr (std::is_same_v<T, dfgpu_sdpa_params>) {
-            dfgpu_tensor const* t[] = {&p.q, &p.k, &p.v, &p.o, &p.stats, &p.max, &p.sum_exp, &p.seq_q, &p.seq_kv, &p.page_table_k, &p.page_table_v, &p.bias, &p.sink, &p.block_mask};
-            return slot < 14 ? t[slot] : nullptr;
+            dfgpu_tensor const* t[] = {&p.q, &p.k, &p.v, &p.o, &p.stats, &p.max, &p.sum_exp, &p.seq_q, &p.seq_kv, &p.page_table_k, &p.page_table_v, &p.bias, &p.sink, &p.block_mask,
+                                       &p.page_offsets_k, &p.page_offsets_v};
+            return slot < 16 ? t[slot] : nullptr;
         } else { dfgpu_tensor const* t[] = {&p.a, &p.b, &p.c}; return slot < 3 ? t[slot] : nullptr; }
     }, step.params);
 }
@@ -418,10 +420,10 @@ Status serialize_artifact(CompilationResult const& compilation, std::vector<std:
         w.string(argument.name);
         w.u32(static_cast<std::uint32_t>(argument.data_type));
         w.u32(static_cast<std::uint32_t>(argument.access));
-        w.u32(0);  // storage_policy: strided
-        w.i64(0);  // ragged_offset_uid
-        w.i64(0);  // ragged_sequence_uid
-        w.i64(1);  // ragged_sequence_divisor
+        w.u32(static_cast<std::uint32_t>(argument.storage_policy));  // strided, or the ragged batch prefix of a compact page table
+        w.i64(argument.ragged_offset_uid);
+        w.i64(argument.ragged_sequence_uid);
+        w.i64(argument.ragged_sequence_divisor);
         w.u64(argument.alignment);
         w.u64(argument.size_bytes);
         w.u32(static_cast<std::uint32_t>(argument.dimensions.size()));
@@ -492,7 +494,13 @@ Status parse_artifact(std::span<std::uint8_t const> input, ArtifactInfo& output)
         if (!r.ok) return bad("truncated argument table");
         if (data_type > static_cast<std::uint32_t>(import::DataType::kInt4)) return bad("argument '" + argument.name + "': unknown data type");
         if (access > static_cast<std::uint32_t>(TensorAccess::kReadWrite)) return bad("argument '" + argument.name + "': unknown access");
-        if (storage_policy != 0 || ragged_offset != 0 || ragged_sequence != 0 || divisor != 1) return bad("argument '" + argument.name + "': only strided storage is executable on this backend");
+        if (storage_policy > static_cast<std::uint32_t>(TensorStoragePolicy::kRaggedBatchPrefix)) return bad("argument '" + argument.name + "': unknown storage policy");
+        if (storage_policy == 0 && (ragged_offset != 0 || ragged_sequence != 0 || divisor != 1)) return bad("argument '" + argument.name + "': a strided argument carries no ragged references");
+        if (storage_policy != 0 && divisor < 1) return bad("argument '" + argument.name + "': ragged sequence divisor must be positive");
+        argument.storage_policy = static_cast<TensorStoragePolicy>(storage_policy);
+        argument.ragged_offset_uid = ragged_offset;
+        argument.ragged_sequence_uid = ragged_sequence;
+        argument.ragged_sequence_divisor = divisor;
         if (rank < 1 || rank > 64 || !r.need(static_cast<std::size_t>(rank) * 16)) return bad("argument '" + argument.name + "': rank out of range");
         argument.data_type = static_cast<import::DataType>(data_type);
         argument.access = static_cast<TensorAccess>(access);

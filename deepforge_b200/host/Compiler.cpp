@@ -90,6 +90,7 @@ std::optional<int> to_dfgpu_dtype(DataType type) {
         case DataType::kInt32: return DFGPU_I32;
         case DataType::kFp8E5M2: return DFGPU_E5M2;
         case DataType::kUint8: return DFGPU_U8;
+        case DataType::kInt64: return DFGPU_I64;
         default: return std::nullopt;
     }
 }
@@ -109,10 +110,13 @@ struct Lowering {
 
     // FP8_E5M2 is executable as a MATMUL_FP8 operand or output only, UINT8 as the SDPA block mask only (`allow_e5m2`
     // admits either).
-    Status describe(std::int64_t uid, dfgpu_tensor& out, std::string const& where, bool allow_e5m2 = false) const {
+    // allow_special: the port takes the types only some ports execute (FP8_E5M2, UINT8, INT64) and ragged storage
+    Status describe(std::int64_t uid, dfgpu_tensor& out, std::string const& where, bool allow_special = false) const {
         auto const& t = tensor(uid);
         auto dtype = to_dfgpu_dtype(t.data_type);
-        if (dtype && (*dtype == DFGPU_E5M2 || *dtype == DFGPU_U8) && !allow_e5m2) dtype.reset();
+        if (dtype && (*dtype == DFGPU_E5M2 || *dtype == DFGPU_U8 || *dtype == DFGPU_I64) && !allow_special) dtype.reset();
+        if (t.ragged_offset_uid && !allow_special)
+            return fail(ErrorCode::kUnsupportedOperation, where, "tensor '" + t.name + "' uses ragged storage, which this backend executes for SDPA page tables only");
         if (!dtype) return fail(ErrorCode::kUnsupportedDataType, where, "tensor '" + t.name + "' has data type " + std::string(import::data_type_name(t.data_type)) + ", which this backend does not execute");
         if (t.dim.size() > DFGPU_MAX_RANK) return fail(ErrorCode::kInvalidShape, where, "tensor rank above 8");
         out = dfgpu_tensor{};
@@ -589,8 +593,28 @@ Status lower_sdpa(Lowering& low, std::size_t index) {
     if ((table_k || table_v) && !*padding) return fail(ErrorCode::kInvalidValue, where, "paged K/V requires padding_mask with sequence lengths");
     if (seq_q && (status = low.describe(*seq_q, params.seq_q, where)).is_bad()) return status;
     if (seq_kv && (status = low.describe(*seq_kv, params.seq_kv, where)).is_bad()) return status;
-    if (table_k && (status = low.describe(*table_k, params.page_table_k, where)).is_bad()) return status;
-    if (table_v && (status = low.describe(*table_v, params.page_table_v, where)).is_bad()) return status;
+    if (table_k && (status = low.describe(*table_k, params.page_table_k, where, true)).is_bad()) return status;
+    if (table_v && (status = low.describe(*table_v, params.page_table_v, where, true)).is_bad()) return status;
+    // compact page tables (lib/Compiler/SequenceGraph.cpp:741-773, :1811-1864): the table's entry names the INT32 / INT64
+    // tensor [B+1,1,1,1] of per-batch element offsets into its storage
+    std::optional<std::int64_t> offsets_k, offsets_v;
+    for (int which = 0; which < 2; ++which) {
+        auto const& table = which ? table_v : table_k;
+        if (!table) continue;
+        auto const& t = low.tensor(*table);
+        if (t.data_type != DataType::kInt32) return fail(ErrorCode::kUnsupportedDataType, where, "page tables are INT32");
+        if (!t.ragged_offset_uid) continue;
+        auto const port_name = where + (which ? ".Page_table_V" : ".Page_table_K");
+        if (t.is_virtual) return fail(ErrorCode::kInvalidValue, port_name, "ragged attention data must be an external tensor");
+        auto found = low.graph.tensors.find(*t.ragged_offset_uid);
+        if (found == low.graph.tensors.end()) return fail(ErrorCode::kMissingUid, port_name, "ragged offset tensor is unresolved");
+        auto const& offsets = found->second;
+        if (offsets.dim != std::vector<std::int64_t>{t.dim[0] + 1, 1, 1, 1}) return fail(ErrorCode::kInvalidShape, port_name, "ragged offset must have dimensions [B+1,1,1,1]");
+        if ((offsets.data_type != DataType::kInt32 && offsets.data_type != DataType::kInt64) || offsets.is_virtual || offsets.reordering_type != "NONE" || offsets.ragged_offset_uid)
+            return fail(ErrorCode::kUnsupportedOperation, port_name, "ragged offsets must be an external plain INT32 or INT64 tensor");
+        if ((status = low.describe(*t.ragged_offset_uid, which ? params.page_offsets_v : params.page_offsets_k, where, true)).is_bad()) return status;
+        (which ? offsets_v : offsets_k) = *t.ragged_offset_uid;
+    }
     if (params.q.rank != 4 || params.k.rank != 4 || params.v.rank != 4) return fail(ErrorCode::kInvalidShape, where, "Q, K and V must have rank 4");
     params.attn_scale = static_cast<float>(get_number(node, "attn_scale_value").value_or(1.0));
     params.padding_mask = *padding;
@@ -657,7 +681,8 @@ Status lower_sdpa(Lowering& low, std::size_t index) {
     step.nodes = {index};
     auto optional_binding = [&](std::optional<std::int64_t> uid) { return uid ? low.bind(*uid) : TensorBinding{}; };
     step.tensors = {low.bind(*q), low.bind(*k), low.bind(*v), low.bind(*o), optional_binding(stats), optional_binding(max), optional_binding(sum_exp),
-                    optional_binding(seq_q), optional_binding(seq_kv), optional_binding(table_k), optional_binding(table_v), optional_binding(bias), optional_binding(sink), optional_binding(block_mask)};
+                    optional_binding(seq_q), optional_binding(seq_kv), optional_binding(table_k), optional_binding(table_v), optional_binding(bias), optional_binding(sink), optional_binding(block_mask),
+                    optional_binding(offsets_k), optional_binding(offsets_v)};
     step.params = params;
     low.plan.steps.push_back(std::move(step));
     return Status::ok();
@@ -1054,6 +1079,26 @@ Status compile_graph(SerializedGraph const& graph, CompileOptions const& options
         argument.access = read && written ? TensorAccess::kReadWrite : (written ? TensorAccess::kWrite : TensorAccess::kRead);
         metadata.arguments.push_back(std::move(argument));
     }
+    // compact page tables: ragged batch-prefix storage, bounded by B * inner span (lib/Compiler/FoundationalGraph.cpp:2070-2095)
+    for (auto const& step : low.plan.steps) {
+        if (step.op != KernelOp::kSdpaForward) continue;
+        auto const& params = std::get<dfgpu_sdpa_params>(step.params);
+        for (int which = 0; which < 2; ++which) {
+            auto const& offsets = step.tensors[14 + which];
+            if (offsets.kind == TensorBinding::Kind::kAbsent) continue;
+            auto const table_uid = step.tensors[9 + which].uid;
+            for (auto& argument : metadata.arguments) {
+                if (argument.uid != table_uid) continue;
+                argument.storage_policy = TensorStoragePolicy::kRaggedBatchPrefix;
+                argument.ragged_offset_uid = offsets.uid;
+                argument.ragged_sequence_uid = step.tensors[8].uid;
+                argument.ragged_sequence_divisor = which ? params.v.dim[2] : params.k.dim[2];
+                std::uint64_t inner = 1;
+                for (std::size_t axis = 1; axis < argument.dimensions.size(); ++axis) inner += static_cast<std::uint64_t>(argument.dimensions[axis] - 1) * static_cast<std::uint64_t>(argument.strides[axis]);
+                argument.size_bytes = static_cast<std::uint64_t>(argument.dimensions[0]) * inner * 4;
+            }
+        }
+    }
     Status status = Status::ok();
     // The reference's single-node path (one f32 CONV_FPROP on packed NHWC / KRSC tensors) carries its own metadata
     // and argument convention (lib/MLIR/Conv2DImporter.cpp:332-370): X, W, Y by those names, physical shapes.
@@ -1153,9 +1198,18 @@ Status validate_graph_compile_metadata(GraphCompileMetadata const& metadata) {
     if (metadata.dynamic_shape_enabled || metadata.override_shape_enabled || metadata.override_policy != ShapeOverridePolicy::kNone ||
         !metadata.override_role_uids.empty() || !metadata.override_axis_map.empty())
         return fail(ErrorCode::kInvalidValue, "metadata.override", "shape-override metadata is not executable on this backend");
-    for (auto const& argument : metadata.arguments)
-        if (argument.storage_policy != TensorStoragePolicy::kStrided || argument.ragged_offset_uid != 0 || argument.ragged_sequence_uid != 0 || argument.ragged_sequence_divisor != 1)
-            return fail(ErrorCode::kInvalidValue, argument.name, "a strided argument carries no ragged references and divisor 1");
+    for (auto const& argument : metadata.arguments) {
+        if (argument.storage_policy == TensorStoragePolicy::kStrided) {
+            if (argument.ragged_offset_uid != 0 || argument.ragged_sequence_uid != 0 || argument.ragged_sequence_divisor != 1)
+                return fail(ErrorCode::kInvalidValue, argument.name, "a strided argument carries no ragged references and divisor 1");
+            continue;
+        }
+        // ragged batch prefix (compact page tables): an INT32 [B,1,P,1] table whose offsets and sequence lengths are arguments too
+        auto is_argument = [&](std::int64_t uid) { return std::any_of(metadata.arguments.begin(), metadata.arguments.end(), [&](auto const& other) { return other.uid == uid && other.uid != argument.uid; }); };
+        if (argument.storage_policy != TensorStoragePolicy::kRaggedBatchPrefix || argument.data_type != import::DataType::kInt32 || argument.dimensions.size() != 4 ||
+            !is_argument(argument.ragged_offset_uid) || !is_argument(argument.ragged_sequence_uid) || argument.ragged_sequence_divisor < 1)
+            return fail(ErrorCode::kInvalidValue, argument.name, "ragged metadata references are unresolved");
+    }
     std::set<std::int64_t> uids;
     for (auto const& argument : metadata.arguments) {
         if (!uids.insert(argument.uid).second) return fail(ErrorCode::kDuplicateUid, argument.name, "argument UID is used twice");
@@ -1174,6 +1228,14 @@ Status validate_graph_compile_metadata(GraphCompileMetadata const& metadata) {
         if (!import::tensor_storage_bytes(view, strided)) return fail(ErrorCode::kInvalidShape, argument.name, "extents, strides or data type do not give a storage span");
         view.reordering_type = "F8_128x4";
         (void)import::tensor_storage_bytes(view, reordered);
+        std::uint64_t ragged = 0;
+        if (argument.storage_policy == TensorStoragePolicy::kRaggedBatchPrefix) {
+            std::uint64_t inner = 1;
+            for (std::size_t axis = 1; axis < argument.dimensions.size(); ++axis) inner += static_cast<std::uint64_t>(argument.dimensions[axis] - 1) * static_cast<std::uint64_t>(argument.strides[axis]);
+            ragged = static_cast<std::uint64_t>(argument.dimensions[0]) * inner * std::max<std::uint64_t>(1, import::data_type_storage_bits(argument.data_type) / 8);
+            if (argument.size_bytes != ragged) return fail(ErrorCode::kInvalidValue, argument.name, "size_bytes is not the ragged storage bound of the tensor");
+            continue;
+        }
         if (argument.size_bytes != strided && argument.size_bytes != reordered)
             return fail(ErrorCode::kInvalidValue, argument.name, "size_bytes is not the storage span of the tensor");
     }

@@ -211,11 +211,18 @@ Status parse_tensor(Json const& value, std::string const& path, TensorDesc& tens
     if (!read_int(value["uid"], tensor.uid)) return fail(ErrorCode::kInvalidFieldType, join(path, "uid"), "expected integer");
     if (!value["uid_assigned"].is_boolean()) return fail(ErrorCode::kInvalidFieldType, join(path, "uid_assigned"), "expected boolean");
     if (!value["uid_assigned"].get<bool>()) return fail(ErrorCode::kMissingUid, join(path, "uid_assigned"), "tensor has no assigned UID");
-    for (auto field : {"ragged_offset_uid", "ragged_offset_name"}) {
-        auto it = value.find(field);
-        if (it != value.end() && !it->is_null())
-            return fail(ErrorCode::kUnsupportedExecutionMetadata, join(path, field), "ragged storage is not executable on this backend");
+    // lib/Import/SerializedGraphImporter.cpp:687-711: both or neither
+    if (auto it = value.find("ragged_offset_uid"); it != value.end() && !it->is_null()) {
+        std::int64_t offsets = 0;
+        if (!read_int(*it, offsets)) return fail(ErrorCode::kInvalidFieldType, join(path, "ragged_offset_uid"), "expected integer");
+        tensor.ragged_offset_uid = offsets;
     }
+    if (auto it = value.find("ragged_offset_name"); it != value.end() && !it->is_null()) {
+        if (!it->is_string()) return fail(ErrorCode::kInvalidFieldType, join(path, "ragged_offset_name"), "expected string");
+        tensor.ragged_offset_name = it->get<std::string>();
+    }
+    if (tensor.ragged_offset_uid.has_value() != tensor.ragged_offset_name.has_value())
+        return fail(ErrorCode::kInvalidValue, path, "ragged offset UID and name must appear together");
     return Status::ok();
 }
 
@@ -374,6 +381,9 @@ Status validate_document(Json const& root, SerializedGraph& graph) {
         }
         graph.nodes.push_back(std::move(operation));
     }
+    // a ragged tensor's offsets are reached through the tensor that names them, not through a port
+    for (auto const& [uid, tensor] : graph.tensors)
+        if (tensor.ragged_offset_uid && used.count(uid)) used.insert(*tensor.ragged_offset_uid);
     for (auto const& [uid, tensor] : graph.tensors)
         if (!used.count(uid)) return fail(ErrorCode::kInvalidValue, "tensors." + std::to_string(uid), "tensor is not referenced by any node");
 

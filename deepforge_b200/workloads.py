@@ -204,9 +204,10 @@ def c4(b=8, h=32, s=2048, d=128, io="BFLOAT16", causal=True, first_batch=0) -> W
         outputs=[4, 5])
 
 
-def c5(batch=64, hq=32, hkv=8, d=128, pages=16384, block=64, max_len=8192, min_len=512, io="BFLOAT16", first_sequence=0) -> Workload:
-    """first_sequence: index of this shard's first sequence inside the full batch (the KV pool is replicated)."""
-    doc = graphs.c5_paged_decode(batch, hq, hkv, d, pages, block, max_len, io)
+def c5(batch=64, hq=32, hkv=8, d=128, pages=16384, block=64, max_len=8192, min_len=512, io="BFLOAT16", first_sequence=0, compact=False) -> Workload:
+    """first_sequence: index of this shard's first sequence inside the full batch (the KV pool is replicated).
+    compact: page tables stored back to back with exactly the slots each sequence needs, plus their offsets."""
+    doc = graphs.c5_paged_decode(batch, hq, hkv, d, pages, block, max_len, io, compact=compact)
     seed = BASE_SEED + 5
     table = max_len // block
     lengths = synthetic.integers(seed, 6, first_sequence + batch, min_len, max_len).astype(np.int32)[first_sequence:]
@@ -217,6 +218,17 @@ def c5(batch=64, hq=32, hkv=8, d=128, pages=16384, block=64, max_len=8192, min_l
         return lambda: np.stack([synthetic.permutation_prefix(seed, stream * 1000 + first_sequence + i, pages, table) for i in range(batch)]).astype(np.int32).reshape(-1)
 
     inputs = {1: _normal(seed, 1, batch * hq * d, io, first=first_sequence * hq * d), 5: lambda: np.ones(batch, dtype=np.int32), 6: lambda: lengths.copy(), 7: tables(7), 8: tables(8)}
+    if compact:
+        slots = (lengths.astype(np.int64) + block - 1) // block
+        offsets = np.concatenate([[0], np.cumsum(slots)])
+
+        def packed(stream: int):
+            full = tables(stream)
+            return lambda: np.concatenate([full().reshape(batch, table)[i, :slots[i]] for i in range(batch)]).astype(np.int32)
+
+        inputs[7], inputs[8] = packed(7), packed(8)
+        inputs[9] = lambda: offsets.astype(np.int64)
+        inputs[10] = lambda: offsets.astype(np.int32)
     device_inputs = {}
     if pool <= (1 << 27):
         inputs[2] = _normal(seed, 2, pool, io)

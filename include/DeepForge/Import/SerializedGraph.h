@@ -56,6 +56,10 @@ struct TensorDesc {
     bool is_pass_by_value = false;
     std::optional<double> pass_by_value;
     std::string reordering_type = "NONE";
+    // Ragged batch-prefix storage (reference: include/DeepForge/Import/SerializedGraph.h:136-137): entry (b, ...) of the
+    // tensor lies at offsets[b] + the inner strides. Executable here for SDPA page tables only (compact page tables).
+    std::optional<std::int64_t> ragged_offset_uid;
+    std::optional<std::string> ragged_offset_name;
 
     bool operator==(TensorDesc const&) const = default;
 };

@@ -50,7 +50,8 @@ enum {
        one tcgen05 convolution writes and others read (CONV_FPROP X and Y with DFGPU_CONV_UMMA_BF16): the readers
        multiply both halves by the same bf16 filter, so an intermediate keeps f32-grade precision through bf16
        tensor-core products. */
-    DFGPU_BF16X2 = 8
+    DFGPU_BF16X2 = 8,
+    DFGPU_I64 = 9   /* INT64: the offsets of a compact page table only */
 };
 
 enum { DFGPU_REORDER_NONE = 0, DFGPU_REORDER_F8_128x4 = 1 };
@@ -242,8 +243,9 @@ int dfgpu_matmul_fp8(const dfgpu_matmul_fp8_params*, void* const* tensors, void*
    Replaces emit_sdpa_forward with its helpers (lib/Compiler/SequenceGraph.cpp
    :1839-1889 paged loads, :1988-2091 validity, :2135-2341 scores and softmax
    row, :2416-2582 outputs). tensors: {Q, K, V, O, Stats, Max, Sum_exp,
-   SEQ_LEN_Q, SEQ_LEN_KV, Page_table_K, Page_table_V, Bias, SINK_TOKEN, Block_mask} (null when absent;
-   a caller without the last three may pass the first eleven only).
+   SEQ_LEN_Q, SEQ_LEN_KV, Page_table_K, Page_table_V, Bias, SINK_TOKEN, Block_mask, Page_table_K offsets,
+   Page_table_V offsets} (null when absent; the list is read only as far as the last port the params declare, so a caller
+   without the last five may pass the first eleven only).
    Bias, ALiBi (score = attn_scale * dot + bias + (kv - q) * slope, :2169-2193), the sink token and the
    block mask run on the general kernel only. */
 enum {
@@ -274,6 +276,13 @@ typedef struct dfgpu_sdpa_params {
                            row sum from exp(sink - max) (lib/Compiler/SequenceGraph.cpp:2256-2288) */
     dfgpu_tensor block_mask; /* rank 0: absent. UINT8 [B, Hq, ceil(Sq/128), ceil(ceil(Skv/128)/8)]: bit (kv/128) % 8 of byte
                                 [b, h, q/128, (kv/128)/8] enables the 128 x 128 score tile (lib/Compiler/SequenceGraph.cpp:2059-2088) */
+    dfgpu_tensor page_offsets_k, page_offsets_v; /* rank 0: absent. INT32 or INT64 [B+1,1,1,1]: a COMPACT page table (the table's
+                                ragged batch prefix, lib/Compiler/SequenceGraph.cpp:1811-1838): the entry of (batch b, slot s) lies
+                                at element offsets[b] + s * stride[2] of the table's storage, which holds offsets[B] entries.
+                                The prefix is validated on the device before the attention kernel runs (offsets start at 0, are
+                                monotonic and within B * P, every batch's segment covers ceil(SEQ_LEN_KV / block) slots:
+                                lib/Runtime/Executable.cpp:619-716); a table that fails reads as all-invalid pages (zeros) and
+                                leaves 601 (K) or 602 (V) in dfgpu_device_status(). Needs 256 bytes of scratch more. */
 } dfgpu_sdpa_params;
 int dfgpu_query_sdpa_forward(const dfgpu_sdpa_params*, dfgpu_plan_info*);
 int dfgpu_sdpa_forward(const dfgpu_sdpa_params*, void* const* tensors, void* scratch, void* stream);

@@ -790,14 +790,45 @@ static int64_t offset4(const dfo_tensor* t, int64_t i0, int64_t i1, int64_t i2, 
 
 /* SequenceGraph.cpp:1839-1889: slot = kv / block, page = table[b,0,slot,0];
    an id outside [0, num_blocks) reads as 0.0 and never touches memory. */
+static int64_t load_prefix(const dfo_tensor* offsets, const void* data, int64_t b) {
+    if (offsets->dtype == DFO_I64) return ((const int64_t*)data)[b * offsets->stride[0]];
+    return ((const int32_t*)data)[b * offsets->stride[0]];
+}
+
+/* A compact table (SequenceGraph.cpp:1811-1838, :1859-1864): the entry of (b, slot) lies at
+   offsets[b] + slot * stride[2] of the table's storage. */
 static float load_kv(const dfo_tensor* t, const void* data, const dfo_tensor* table,
-                     const int32_t* table_data, int64_t b, int64_t head, int64_t kv, int64_t d) {
+                     const int32_t* table_data, const dfo_tensor* offsets, const void* offsets_data,
+                     int64_t b, int64_t head, int64_t kv, int64_t d) {
     if (table->rank == 0) return load_f32(t, data, offset4(t, b, head, kv, d));
     int64_t block = t->dim[2];
     int64_t slot = kv / block, within = kv % block;
-    int64_t page = table_data[offset4(table, b, 0, slot, 0)];
+    int64_t at = offsets->rank ? load_prefix(offsets, offsets_data, b) + slot * table->stride[2] : offset4(table, b, 0, slot, 0);
+    int64_t page = table_data[at];
     if (page < 0 || page >= t->dim[0]) return 0.0f;
     return load_f32(t, data, offset4(t, page, head, within, d));
+}
+
+int dfo_validate_page_prefix(const dfo_sdpa_params* p, void* const* data, int which) {
+    const dfo_tensor* table = which ? &p->page_table_v : &p->page_table_k;
+    const dfo_tensor* offsets = which ? &p->page_offsets_v : &p->page_offsets_k;
+    const dfo_tensor* container = which ? &p->v : &p->k;
+    if (offsets->rank == 0) return 0;
+    const void* prefix = data[14 + which];
+    const int32_t* lengths = (const int32_t*)data[8];
+    int64_t batches = table->dim[0], block = container->dim[2];
+    int64_t bound = batches * ((table->dim[2] - 1) * table->stride[2] + 1);
+    if (load_prefix(offsets, prefix, 0) != 0) return 17;
+    for (int64_t b = 0; b < batches; ++b) {
+        int64_t start = load_prefix(offsets, prefix, b), end = load_prefix(offsets, prefix, b + 1);
+        int64_t length = lengths[b * p->seq_kv.stride[0]];
+        if (start < 0 || end < start || end > bound) return 17;
+        if (length < 0 || length > table->dim[2] * block) return 17;
+        int64_t slots = length / block + (length % block != 0 ? 1 : 0);
+        int64_t needed = slots > 0 ? 1 + (slots - 1) * table->stride[2] : 0;
+        if (end - start < needed) return 17;
+    }
+    return 0;
 }
 
 /* SequenceGraph.cpp:1748-1778: slope of head h among H heads. With n the largest power of
@@ -862,7 +893,7 @@ int dfo_sdpa_forward(const dfo_sdpa_params* p, void* const* data,
                 float dot = 0.0f;
                 for (int64_t d = 0; d < dqk; ++d) {
                     float qv = load_f32(q, data[0], offset4(q, ib, ih, iq, d));
-                    float kv = load_kv(k, data[1], &p->page_table_k, table_k, ib, kh, ikv, d);
+                    float kv = load_kv(k, data[1], &p->page_table_k, table_k, &p->page_offsets_k, p->page_offsets_k.rank ? data[14] : NULL, ib, kh, ikv, d);
                     float product = qv * kv;
                     dot = dot + product;
                 }
@@ -889,7 +920,7 @@ int dfo_sdpa_forward(const dfo_sdpa_params* p, void* const* data,
                 if (!valid[ikv] || !(sum > 0.0f)) continue;
                 float probability = expf(scores[ikv] - maximum) / sum;
                 for (int64_t d = 0; d < dv; ++d) {
-                    float vv = load_kv(v, data[2], &p->page_table_v, table_v, ib, vh, ikv, d);
+                    float vv = load_kv(v, data[2], &p->page_table_v, table_v, &p->page_offsets_v, p->page_offsets_v.rank ? data[15] : NULL, ib, vh, ikv, d);
                     float product = probability * vv;
                     out_row[d] = out_row[d] + product;
                 }

@@ -33,7 +33,8 @@ enum {
     DFO_E8M0 = 4,
     DFO_I32 = 5,
     DFO_E5M2 = 6,
-    DFO_U8 = 7
+    DFO_U8 = 7,
+    DFO_I64 = 9 /* (same number as the kernel library's: the offsets of a compact page table) */
 };
 
 enum { DFO_REORDER_NONE = 0, DFO_REORDER_F8_128x4 = 1 };
@@ -155,12 +156,18 @@ typedef struct dfo_sdpa_params {
     int32_t reserved2;
     dfo_tensor sink;      /* rank 0 => absent; [1, Hq, 1, 1]: one extra logit per head in the softmax */
     dfo_tensor block_mask; /* rank 0 => absent; UINT8 [B, Hq, ceil(Sq/128), ceil(ceil(Skv/128)/8)], one bit per 128 x 128 tile */
+    dfo_tensor page_offsets_k, page_offsets_v; /* rank 0 => absent; INT32 / INT64 [B+1,1,1,1]: compact page table, entry (b, slot) at
+                                                  offsets[b] + slot * stride[2] of the table's storage */
 } dfo_sdpa_params;
-/* pointer order: Q,K,V,O,Stats,Max,Sum_exp,SEQ_LEN_Q,SEQ_LEN_KV,Page_table_K,Page_table_V,Bias,SINK_TOKEN,Block_mask.
+/* pointer order: Q,K,V,O,Stats,Max,Sum_exp,SEQ_LEN_Q,SEQ_LEN_KV,Page_table_K,Page_table_V,Bias,SINK_TOKEN,Block_mask,
+   Page_table_K offsets,Page_table_V offsets.
    Only (b,h) pairs with flat index bh_begin <= b*Hq+h < bh_end and rows with
    q % q_step == 0 are computed; others are left untouched. */
 int dfo_sdpa_forward(const dfo_sdpa_params* p, void* const* data,
                      int64_t bh_begin, int64_t bh_end, int64_t q_step);
+/* The reference's runtime check of a compact page table's batch prefix (lib/Runtime/Executable.cpp:619-716):
+   0 when the prefix of table `which` (0 K, 1 V) is valid, 17 (DFE_INVALID_VARIANT_PACK) otherwise. */
+int dfo_validate_page_prefix(const dfo_sdpa_params* p, void* const* data, int which);
 
 #ifdef __cplusplus
 }

@@ -36,7 +36,8 @@ class SdpaParams(C.Structure):
                 ("page_table_v", Tensor), ("attn_scale", C.c_float), ("padding_mask", C.c_int32),
                 ("has_left_bound", C.c_int32), ("has_right_bound", C.c_int32), ("left_bound", C.c_int64),
                 ("right_bound", C.c_int64), ("bottom_right", C.c_int32), ("reserved", C.c_int32), ("s_kv", C.c_int64),
-                ("bias", Tensor), ("alibi_mask", C.c_int32), ("reserved2", C.c_int32), ("sink", Tensor), ("block_mask", Tensor)]
+                ("bias", Tensor), ("alibi_mask", C.c_int32), ("reserved2", C.c_int32), ("sink", Tensor), ("block_mask", Tensor),
+                ("page_offsets_k", Tensor), ("page_offsets_v", Tensor)]
 
 
 def _declare(l: C.CDLL) -> C.CDLL:
@@ -207,10 +208,17 @@ def matmul_fp8(ad, a, bd, b, cd, c, descale_a: float, descale_b: float, scale_c:
     return amax.value
 
 
+def validate_page_prefix(params: SdpaParams, arrays, which: int) -> int:
+    """The reference's runtime rule for a compact page table's batch prefix: 0 valid, 17 invalid."""
+    arrays = list(arrays) + [None] * (16 - len(arrays))
+    pointers = (C.c_void_p * 16)(*[C.c_void_p(a.ctypes.data) if a is not None else C.c_void_p(None) for a in arrays])
+    return int(lib().dfo_validate_page_prefix(C.byref(params), pointers, C.c_int(which)))
+
+
 def sdpa_forward(params: SdpaParams, arrays, bh_begin=0, bh_end=1 << 62, q_step=1, threads: int = 1) -> None:
-    assert 11 <= len(arrays) <= 14  # the twelfth is the bias, then the sink token, then the block mask
-    arrays = list(arrays) + [None] * (14 - len(arrays))
-    pointers = (C.c_void_p * 14)(*[C.c_void_p(a.ctypes.data) if a is not None else C.c_void_p(None) for a in arrays])
+    assert 11 <= len(arrays) <= 16  # the twelfth is the bias, then the sink token, the block mask, the offsets of compact K and V page tables
+    arrays = list(arrays) + [None] * (16 - len(arrays))
+    pointers = (C.c_void_p * 16)(*[C.c_void_p(a.ctypes.data) if a is not None else C.c_void_p(None) for a in arrays])
     bh_end = min(bh_end, int(params.q.dim[0] * params.q.dim[1]))
     if bh_end <= bh_begin:
         return

@@ -17,7 +17,7 @@ from deepforge_b200 import dfgpu, synthetic
 
 FLT_MAX = 3.4028234663852886e38
 _FLOATING = {"FLOAT", "BFLOAT16", "HALF"}
-_CODE = {"FP8_E4M3": dfgpu.E4M3, "FP8_E5M2": dfgpu.E5M2, "FP8_E8M0": dfgpu.E8M0, "INT32": dfgpu.I32, "UINT8": dfgpu.U8}
+_CODE = {"FP8_E4M3": dfgpu.E4M3, "FP8_E5M2": dfgpu.E5M2, "FP8_E8M0": dfgpu.E8M0, "INT32": dfgpu.I32, "UINT8": dfgpu.U8, "INT64": dfgpu.I64}
 _STORAGE = {"FLOAT": dfgpu.F32, "BFLOAT16": dfgpu.BF16, "HALF": dfgpu.F16}
 
 
@@ -31,6 +31,8 @@ def widen(array: np.ndarray, data_type: str) -> np.ndarray:
         return np.ascontiguousarray(array).view(np.float32).reshape(-1).copy()
     if data_type == "INT32":
         return np.ascontiguousarray(array).view(np.int32).reshape(-1).copy()
+    if data_type == "INT64":
+        return np.ascontiguousarray(array).view(np.int64).reshape(-1).copy()
     return np.ascontiguousarray(array).view(np.uint8).reshape(-1).copy()
 
 
@@ -152,6 +154,14 @@ def run(document: dict, inputs: Dict[int, np.ndarray], matmul_rows: Optional[Tup
                 arrays.append(values[ins["Block_mask"]])
             else:
                 arrays.append(None)
+            for name, field in (("Page_table_K", "page_offsets_k"), ("Page_table_V", "page_offsets_v")):
+                # a compact page table names its batch prefix in the table's own tensor entry
+                offsets_uid = tensors[ins[name]].get("ragged_offset_uid") if name in ins else None
+                if offsets_uid is not None:
+                    setattr(p, field, _desc(tensors[offsets_uid], True))
+                    arrays.append(storage_inputs[offsets_uid] if storage_inputs and offsets_uid in storage_inputs else values[offsets_uid])
+                else:
+                    arrays.append(None)
             p.alibi_mask = int(bool(node.get("alibi_mask")))
             p.attn_scale = node["attn_scale_value"] if node["attn_scale_value"] is not None else 1.0
             p.padding_mask = int(node["padding_mask"])

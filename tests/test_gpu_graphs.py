@@ -32,7 +32,7 @@ def oracle_inputs(wl, session, keep_in_storage=()):
         data_type = wl.tensor(uid)["data_type"]
         if uid not in keep_in_storage:
             widened[uid] = graph_oracle.widen(raw, data_type)
-        storage[uid] = raw.view({"BFLOAT16": np.uint16, "HALF": np.float16, "FLOAT": np.float32, "INT32": np.int32}.get(data_type, np.uint8))
+        storage[uid] = raw.view({"BFLOAT16": np.uint16, "HALF": np.float16, "FLOAT": np.float32, "INT32": np.int32, "INT64": np.int64}.get(data_type, np.uint8))
     return widened, storage
 
 
@@ -289,6 +289,23 @@ def test_c5_paged_decode_small_and_generic_agree():
         ins, _ = oracle_inputs(wl, s)
         ref = graph_oracle.run(wl.document, ins)
         check_bf16(s.output(4), ref[4])
+
+
+def test_c5_paged_decode_with_compact_page_tables():
+    """The same decode with compact page tables (the graph names the offsets in the tables' tensor entries): same plan
+    kernel, one launch more, results equal to the oracle's and bit for bit to the strided-table run of the same pages."""
+    sizes = dict(batch=6, hq=8, hkv=2, pages=64, block=64, max_len=1024, min_len=1)
+    wl = workloads.c5(compact=True, **sizes)
+    s = harness.Session(wl)
+    assert "kernel=4 launches=3" in s.exe.plan_text() and "uid9 uid10" in s.exe.plan_text()
+    s.run()
+    ins, _ = oracle_inputs(wl, s)
+    ref = graph_oracle.run(wl.document, ins)
+    check_bf16(s.output(4), ref[4])
+    strided = harness.Session(workloads.c5(**sizes))
+    strided.run()
+    assert np.array_equal(s.output(4), strided.output(4))
+    assert dfgpu.device_status() == 0
 
 
 def test_c5_paged_decode_full_size_ten_sequences():

@@ -22,8 +22,9 @@ def close_bf16(actual, expected):
 
 
 def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=None, stats=True, seed=5, q_step=1, bh_range=None,
-         bias_dims=None, sink=False, block_mask=None, **flags):
-    """Run oracle (f32 restatement on dtype-rounded inputs) and the GPU kernel on the same data."""
+         bias_dims=None, sink=False, block_mask=None, compact=None, **flags):
+    """Run oracle (f32 restatement on dtype-rounded inputs) and the GPU kernel on the same data.
+    compact: (slots per batch entry, K offsets as int64, V offsets as int32) when `tables` are compact 1-D page tables."""
     b, hq, sq, _ = q_dims
     o_dims = [b, hq, sq, v_dims[3]]
     row_dims = [b, hq, sq, 1]
@@ -39,9 +40,12 @@ def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=No
         if seq is not None:
             params.padding_mask = 1
             params.seq_q = params.seq_kv = tensor(I32, [b, 1, 1, 1])
-        if tables is not None:
+        if tables is not None and compact is None:
             params.page_table_k = tensor(I32, [b, 1, tables[0].shape[1], 1])
             params.page_table_v = tensor(I32, [b, 1, tables[1].shape[1], 1])
+        if compact is not None:
+            params.page_table_k = params.page_table_v = tensor(I32, [b, 1, compact[0], 1])
+            params.page_offsets_k, params.page_offsets_v = tensor(dfgpu.I64, [b + 1, 1, 1, 1]), tensor(I32, [b + 1, 1, 1, 1])
         if bias_dims is not None:
             params.bias = tensor(F32, bias_dims)
         if sink:
@@ -60,7 +64,8 @@ def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=No
     seq_arrays = [None, None] if seq is None else [np.asarray(s, dtype=np.int32) for s in seq]
     table_arrays = [None, None] if tables is None else [np.ascontiguousarray(t, dtype=np.int32) for t in tables]
     lo, hi = bh_range if bh_range else (0, b * hq)
-    oracle.sdpa_forward(op, rounded + [o_ref] + (rows_ref if stats else [None] * 3) + seq_arrays + table_arrays + [bias, sink_values, block_mask], lo, hi, q_step)
+    offset_arrays = [None, None] if compact is None else [np.ascontiguousarray(compact[1], dtype=np.int64), np.ascontiguousarray(compact[2], dtype=np.int32)]
+    oracle.sdpa_forward(op, rounded + [o_ref] + (rows_ref if stats else [None] * 3) + seq_arrays + table_arrays + [bias, sink_values, block_mask] + offset_arrays, lo, hi, q_step)
 
     gp = dfgpu.SdpaParams()
     fill(gp, dtype)
@@ -75,7 +80,8 @@ def both(dtype, q_dims, k_dims, v_dims, s_kv, scale, kernel, seq=None, tables=No
     dbias = g.to_device(bias) if bias is not None else None
     dsink = g.to_device(sink_values) if sink else None
     dmask = g.to_device(block_mask) if block_mask is not None else None
-    dfgpu.sdpa_forward(gp, [g.ptr(t) for t in dev + [do] + drows + dseq + dtab + [dbias, dsink, dmask]], scratch=g.ptr(scratch))
+    doff = [g.to_device(a) if a is not None else None for a in offset_arrays]
+    dfgpu.sdpa_forward(gp, [g.ptr(t) for t in dev + [do] + drows + dseq + dtab + [dbias, dsink, dmask] + doff], scratch=g.ptr(scratch))
     if dtype == BF16:
         o = synthetic.bf16_bits_to_f32(g.to_host(do, np.uint16))
     else:
@@ -238,6 +244,74 @@ def test_paged_decode_matches_oracle(group, block, kernel):
     info2, o2, _, _, _ = both(BF16, [batch, hq, 1, 128], [pages, hkv, block, 128], [pages, hkv, block, 128], max_len,
                               128 ** -0.5, dfgpu.SDPA_ROWWISE, seq=([1] * batch, lengths), tables=(tk, tv))
     close_bf16(o2, o_ref)
+
+
+def _compact(lengths, tk, tv, block):
+    """The same page assignments stored back to back: each entry keeps the slots its length needs."""
+    slots = (np.asarray(lengths, dtype=np.int64) + block - 1) // block
+    offsets = np.concatenate([[0], np.cumsum(slots)])
+    pack = lambda t: np.concatenate([t[i, :slots[i]] for i in range(len(slots))] + [np.zeros(0, np.int32)]).astype(np.int32)
+    return pack(tk), pack(tv), offsets
+
+
+@pytest.mark.parametrize("kernel", [dfgpu.SDPA_ROWWISE, dfgpu.SDPA_PAGED_DECODE, dfgpu.SDPA_PAGED_DECODE_UMMA])
+@pytest.mark.parametrize("group,block", [(4, 64), (1, 16), (8, 128)])
+def test_compact_page_tables_match_oracle_and_strided_tables(group, block, kernel):
+    """Compact (ragged batch-prefix) page tables, K offsets INT64 and V offsets INT32, exact allocation: every kernel gives
+    what it gives for the strided tables of the same pages, and what the oracle gives (lib/Compiler/SequenceGraph.cpp:1811-1864)."""
+    batch, hkv, pages, max_len = 5, 2, 64, 700
+    hq = hkv * group
+    lengths, tk, tv = _paged_inputs(batch, hq, hkv, pages, block, max_len, seed=61 + group)
+    lengths[0], lengths[1], lengths[3] = max_len, 1, 0
+    tk[2, 1] = -1          # invalid page ids still read as zeros
+    ck, cv, offsets = _compact(lengths, tk, tv, block)
+    dims = ([batch, hq, 1, 128], [pages, hkv, block, 128], [pages, hkv, block, 128])
+    info, o, o_ref, rows, rows_ref = both(BF16, *dims, max_len, 128 ** -0.5, kernel, seq=([1] * batch, lengths), tables=(ck, cv), compact=(tk.shape[1], offsets, offsets))
+    assert info.kernel == kernel and info.scratch_bytes >= 256 and info.launches == (2 if kernel == dfgpu.SDPA_ROWWISE else 3)
+    close_bf16(o, o_ref)
+    _, o_strided, _, rows_strided, _ = both(BF16, *dims, max_len, 128 ** -0.5, kernel, seq=([1] * batch, lengths), tables=(tk, tv))
+    assert np.array_equal(o, o_strided)
+    for a, r in zip(rows, rows_strided):
+        assert np.array_equal(a, r, equal_nan=True)
+
+
+@pytest.mark.parametrize("kernel", [dfgpu.SDPA_ROWWISE, dfgpu.SDPA_PAGED_DECODE, dfgpu.SDPA_PAGED_DECODE_UMMA])
+@pytest.mark.parametrize("which,offsets", [(0, [0, 2, 3, 20, 20, 21]), (1, [1, 11, 12, 23, 23, 34]), (0, [0, 11, 5, 23, 23, 34]), (1, [0, 11, 12, 23, 23, 1 << 20])])
+def test_compact_page_table_with_a_bad_prefix_reads_as_invalid_pages(kernel, which, offsets):
+    """A prefix that breaks the reference's runtime rule (lib/Runtime/Executable.cpp:619-716: segment shorter than the
+    sequence needs, non-zero start, decreasing, past the storage bound) is found on the device: the launch leaves 601 (K)
+    or 602 (V) in the device status, the table is never read (so nothing is fetched out of bounds) and its pages read
+    as invalid. The context stays usable."""
+    batch, hkv, pages, block, max_len = 5, 2, 64, 64, 700
+    lengths, tk, tv = _paged_inputs(batch, 8, hkv, pages, block, max_len, seed=71)
+    lengths[:] = [700, 1, 700, 0, 650]
+    ck, cv, good = _compact(lengths, tk, tv, block)
+    assert good.tolist() == [0, 11, 12, 23, 23, 34]
+    p = dfgpu.SdpaParams()
+    p.q = p.o = tensor(BF16, [batch, 8, 1, 128])
+    p.k = p.v = tensor(BF16, [pages, hkv, block, 128])
+    p.seq_q = p.seq_kv = tensor(I32, [batch, 1, 1, 1])
+    p.page_table_k = p.page_table_v = tensor(I32, [batch, 1, tk.shape[1], 1])
+    p.page_offsets_k, p.page_offsets_v = tensor(dfgpu.I64, [batch + 1, 1, 1, 1]), tensor(I32, [batch + 1, 1, 1, 1])
+    p.attn_scale, p.padding_mask, p.s_kv, p.kernel = 128 ** -0.5, 1, max_len, kernel
+    info = dfgpu.query("sdpa_forward", p)
+    host = [synthetic.to_bf16_bits(synthetic.normal(7, i + 1, n)) for i, n in enumerate((batch * 8 * 128, pages * hkv * block * 128, pages * hkv * block * 128))]
+    dev = [g.to_device(a) for a in host]
+    do = g.device_zeros(batch * 8 * 128 * 2, 0x55)
+    ok, ov = (np.array(offsets), good) if which == 0 else (good, np.array(offsets))
+    extra = [g.to_device(np.ones(batch, dtype=np.int32)), g.to_device(lengths), g.to_device(ck), g.to_device(cv)]
+    doff = [g.to_device(ok.astype(np.int64)), g.to_device(ov.astype(np.int32))]
+    scratch = g.device_zeros(info.scratch_bytes)
+    dfgpu.sdpa_forward(p, [g.ptr(t) for t in dev + [do]] + [0, 0, 0] + [g.ptr(t) for t in extra] + [0, 0, 0] + [g.ptr(t) for t in doff], scratch=g.ptr(scratch))
+    assert dfgpu.device_status() == 601 + which
+    o = synthetic.bf16_bits_to_f32(g.to_host(do, np.uint16)).reshape(batch, 8, 128)
+    if which == 1:
+        assert np.all(o == 0.0)  # every V page reads as zeros
+    assert np.all(np.isfinite(o))
+    # and the next launch with the good prefix is fine
+    doff = [g.to_device(good.astype(np.int64)), g.to_device(good.astype(np.int32))]
+    dfgpu.sdpa_forward(p, [g.ptr(t) for t in dev + [do]] + [0, 0, 0] + [g.ptr(t) for t in extra] + [0, 0, 0] + [g.ptr(t) for t in doff], scratch=g.ptr(scratch))
+    assert dfgpu.device_status() == 0
 
 
 def test_paged_decode_zero_length_sequence_gives_zero_output():

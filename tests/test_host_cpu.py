@@ -282,3 +282,30 @@ def test_single_convolution_carries_the_conv_adapter_metadata():
     assert runtime.compile_graph(graphs.c1_conv("nchw", n=1, c=4, h=5, w=5, k=4)).conv2d_metadata() is None
     generic = runtime.compile_graph(graphs.c2_bottleneck(n=1, h=8, w=8))
     assert generic.conv2d_metadata() is None and [a["uid"] for a in generic.arguments()] == sorted(a["uid"] for a in generic.arguments())
+
+
+def test_compact_page_tables_plan_metadata_and_rejections(tmp_path):
+    """Compact (ragged batch-prefix) page tables: the SDPA launch binds the two offset tensors, gains the validation
+    launch and its scratch, the artifact keeps all of it; ragged storage anywhere else is refused, and so are offsets of
+    the wrong shape or a dangling reference (lib/Compiler/SequenceGraph.cpp:741-773)."""
+    strided = runtime.compile_graph(graphs.c5_paged_decode(batch=4, pages=64, block=64, max_len=1024))
+    doc = graphs.c5_paged_decode(batch=4, pages=64, block=64, max_len=1024, compact=True)
+    exe = runtime.compile_graph(doc)
+    assert "sdpa_forward kernel=4 launches=2" in strided.plan_text() and "sdpa_forward kernel=4 launches=3" in exe.plan_text()
+    assert exe.plan_text().rstrip().endswith("uid9 uid10 scratch=ws+0") and exe.workspace_size == strided.workspace_size + 256
+    assert [a["uid"] for a in exe.arguments()] == list(range(1, 11))
+    target = tmp_path / "compact.dfo"
+    exe.write_artifact(target)
+    assert runtime.load_artifact(target).plan_text() == exe.plan_text()
+    for mutate, expected in (
+        (lambda d: d["tensors"]["1"].update(ragged_offset_uid=9, ragged_offset_name="Page_table_K_offsets"), 20),   # ragged Q: not executable here
+        (lambda d: d["tensors"]["9"].update(dim=[4, 1, 1, 1], stride=[1, 1, 1, 1]), 15),                             # offsets must be [B+1,1,1,1]
+        (lambda d: (d["tensors"]["7"].update(ragged_offset_uid=77), d["tensors"].pop("9")), 13),                       # unresolved offsets tensor
+        (lambda d: d["tensors"]["7"].pop("ragged_offset_name"), 8),                                                   # UID and name appear together
+        (lambda d: d["tensors"]["10"].update(data_type="FLOAT"), 20),                                                  # offsets are INT32 or INT64
+    ):
+        broken = copy.deepcopy(doc)
+        mutate(broken)
+        with pytest.raises(DeepForgeError) as error:
+            runtime.compile_graph(broken)
+        assert error.value.code == expected, error.value

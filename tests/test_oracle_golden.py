@@ -418,6 +418,43 @@ def test_paged_sdpa_equals_contiguous_and_guards_invalid_pages():
     assert o[0, 0, 0, 0] == 0.0 and o[0, 0, 0, 1] == 0.0
 
 
+def test_compact_page_tables_equal_contiguous_and_prefix_rule():
+    """test/Compiler/SequenceOpsTest.cpp:2031-2147: exact-allocation packed page tables (K offsets INT64 {0,2,3}, V offsets
+    INT32 {0,2,3}, sequence lengths {3,1}, two tokens per page) give the contiguous result, and a K segment shorter
+    than its sequence demands ({0,1,3}) is rejected with DFE_INVALID_VARIANT_PACK."""
+    from deepforge_b200.dfgpu import I64
+    q, k, v, _, _, _, _ = _paged_case()
+    seq_q = np.array([1, 1], dtype=np.int32)
+    seq_kv = np.array([3, 1], dtype=np.int32)
+    packed_k, packed_v = np.array([2, 0, 1], dtype=np.int32), np.array([1, 3, 2], dtype=np.int32)
+    offsets_k, offsets_v = np.array([0, 2, 3], dtype=np.int64), np.array([0, 2, 3], dtype=np.int32)
+
+    def container(logical, table, offsets):
+        c = np.full((4, 1, 2, 2), -17.0, dtype=np.float32)
+        for b in range(2):
+            for s in range(int(seq_kv[b])):
+                c[table[int(offsets[b]) + s // 2], 0, s % 2] = logical[b, 0, s]
+        return c
+
+    kc, vc = container(k, packed_k, offsets_k), container(v, packed_v, offsets_v)
+    o = np.full((2, 1, 1, 2), -99.0, dtype=np.float32)
+    p = _sdpa_params(q, kc, vc, o, 0.5, 3, padding_mask=1)
+    p.seq_q = p.seq_kv = tensor(I32, [2, 1, 1, 1])
+    p.page_table_k = p.page_table_v = tensor(I32, [2, 1, 2, 1])
+    p.page_offsets_k, p.page_offsets_v = tensor(I64, [3, 1, 1, 1]), tensor(I32, [3, 1, 1, 1])
+    arrays = [q, kc, vc, o, None, None, None, seq_q, seq_kv, packed_k, packed_v, None, None, None, offsets_k, offsets_v]
+    assert oracle.validate_page_prefix(p, arrays, 0) == 0 and oracle.validate_page_prefix(p, arrays, 1) == 0
+    oracle.sdpa_forward(p, arrays)
+    reference, _, _, _ = np_attention(q, k, v, 0.5, seq_q, seq_kv)
+    _close(o, reference)
+    for bad in ([0, 1, 3], [1, 2, 3], [0, 3, 2], [0, 2, 5], [0, -1, 3]):  # short segment, non-zero start, decreasing, past the bound (2 x 2), negative
+        arrays[14] = np.array(bad, dtype=np.int64)
+        assert oracle.validate_page_prefix(p, arrays, 0) == 17, bad
+    arrays[14] = offsets_k
+    arrays[8] = np.array([5, 1], dtype=np.int32)  # a sequence longer than the table's logical bound
+    assert oracle.validate_page_prefix(p, arrays, 0) == 17
+
+
 def test_static_loop_nest_forms_are_bit_identical_to_the_flat_loops():
     """dfo_conv_generic_nhwc and the vectorisable branch of dfo_matmul run the same chain of f32 operations per output
     element as the literal restatements (c, then taps; k in order; one multiply and one add per step), so their
