@@ -331,6 +331,26 @@ def test_c5_paged_decode_full_size_ten_sequences():
     assert np.array_equal(doubled, out * 2)
 
 
+@pytest.mark.parametrize("name,size", [("c2", dict(n=4, h=14, w=14)), ("c3", dict(m=256, k=128, n=128)), ("c4", dict(b=2, h=2, s=256)),
+                                       ("c5", dict(batch=4, hq=8, hkv=2, pages=32, max_len=512, min_len=100))])
+def test_shards_run_one_after_another_join_into_the_unsharded_result(name, size):
+    """What the multi-GPU benchmark runs, on one GPU: the shards workloads.shard cuts for two ranks (their own slices of the
+    input streams, kernel selection at the shard's size) executed in turn; their outputs, joined along the gather axis,
+    are the unsharded run's outputs bit for bit (which the tests above hold to the oracle)."""
+    whole = harness.Session(workloads.BUILDERS[name](**size))
+    whole.run()
+    parts = []
+    for rank in range(2):
+        shard = harness.Session(workloads.shard(name, rank, 2, **dict(size)))
+        shard.run()
+        parts.append({uid: shard.raw(uid).copy() for uid in workloads.GATHER_AXIS[name]})
+        del shard
+    for uid, axis in workloads.GATHER_AXIS[name].items():
+        assert axis == 0  # (every sharded output is split along its slowest axis: joining is concatenation)
+        joined = np.concatenate([part[uid].reshape(-1) for part in parts])
+        assert np.array_equal(joined.view(np.uint8), whole.raw(uid).reshape(-1).view(np.uint8)), (name, uid)
+
+
 @pytest.mark.parametrize("name,size", [("c2", dict(n=2, h=14, w=14)), ("c3", dict(m=128, k=128, n=128)), ("c4", dict(b=1, h=2, s=256)),
                                        ("c5", dict(batch=3, hq=8, hkv=2, pages=32, max_len=512, min_len=100)), ("fp8", dict(m=128, k=128, n=128))])
 def test_executable_loaded_from_an_artifact_gives_the_same_bits(name, size):
