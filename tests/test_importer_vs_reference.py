@@ -6,6 +6,7 @@ import ctypes as C
 import json
 import os
 import subprocess
+import sys
 from pathlib import Path
 
 import pytest
@@ -196,13 +197,95 @@ def test_encodings_match_the_reference():
         assert _ours(payload, fmt)[0] == reference(payload, fmt)[0]
 
 
-@pytest.mark.parametrize("source", ["test/Compiler/RuntimeHeaderTest.cpp"])
-def test_reference_header_checks_compile_against_our_headers(source):
-    """The reference's own compile-time check of the runtime interface (member signatures of Executable::execute and
-    get_workspace_size, as static_asserts) compiled UNMODIFIED against this repository's include/ tree: a host that
-    builds against the reference's headers builds against these."""
+@pytest.mark.parametrize("source", ["test/Compiler/RuntimeHeaderTest.cpp", "test/Compiler/SequenceOpsTest.cpp", "test/Compiler/SpecializedOpsTest.cpp",
+                                    "test/Compiler/TrainingNormOpsTest.cpp"])
+def test_reference_test_sources_compile_against_our_headers(source):
+    """The reference's own test sources compiled UNMODIFIED against this repository's include/ tree: the compile-time check
+    of the runtime interface (member signatures of Executable::execute and get_workspace_size as static_asserts), and the
+    SDPA, block-scale / FP8 and normalisation test programs with everything they use of CompileOptions, CompilationResult,
+    the argument metadata, the artifact calls and Executable. A host that builds against the reference's headers builds
+    against these. (The other test programs use the x86 schedule / CPU-variant API or the 39-tag schema API, which this
+    backend does not have.)"""
+    import sysconfig
     path = _reference_tree() / source
     if not path.exists():
         pytest.skip("reference tree not on this machine")
-    built = subprocess.run(["g++", "-std=c++20", "-fsyntax-only", "-I", str(ROOT / "include"), str(path)], capture_output=True, text=True)
+    json_include = sysconfig.get_paths()["purelib"] + "/include"
+    built = subprocess.run(["g++", "-std=c++20", "-fsyntax-only", "-I", str(ROOT / "include"), "-isystem", json_include, "-isystem",
+                            json_include + "/cudnn_frontend/thirdparty", str(path)], capture_output=True, text=True)
     assert built.returncode == 0, built.stderr[-2000:]
+
+
+def _reference_attention():
+    """The attention oracle of the reference's own SDPA tests, compiled from the test source (oracle/ref_sdpa_shim.cpp)."""
+    library = ROOT / "oracle" / "_ref" / "libdf_ref_sdpa.so"
+    shim = ROOT / "oracle" / "ref_sdpa_shim.cpp"
+    if (not library.exists() or library.stat().st_mtime < shim.stat().st_mtime) and (_reference_tree() / "test" / "Compiler" / "SequenceOpsTest.cpp").exists():
+        subprocess.run(["make", "-C", str(ROOT / "oracle"), "ref"], capture_output=True)
+    if not library.exists():
+        pytest.skip("reference attention oracle not built on this machine")
+    import os
+    lib = C.CDLL(str(library), mode=os.RTLD_LAZY)  # (the compiler entry points the test's other functions call are never bound)
+    lib.ref_attention_forward.restype = C.c_int
+    return lib
+
+
+@pytest.mark.parametrize("case", range(8))
+def test_sdpa_restatement_agrees_with_the_references_own_test_oracle(case):
+    """oracle/df_oracle.c's SDPA forward against attention_forward of test/Compiler/SequenceOpsTest.cpp:322-509 (the oracle the
+    reference's tests hold its compiler to, double-precision scores) on seeded cases: grouped heads, padding with short
+    and empty sequences, sliding windows, bottom-right alignment, ALiBi, a bias row, sink tokens, a block mask."""
+    import numpy as np
+    sys.path.insert(0, str(ROOT / "tests"))
+    import oracle
+    from deepforge_b200.dfgpu import F32, I32, U8, tensor
+    lib = _reference_attention()
+    rng = np.random.default_rng(100 + case)
+    b, hq, hk, hv = (2, 6, 3, 2) if case % 2 else (3, 4, 1, 4)
+    sq, skv, d, dv = (5, 9, 8, 6) if case < 6 else (130, 260, 16, 8)
+    q = rng.standard_normal((b, hq, sq, d)).astype(np.float32)
+    k = rng.standard_normal((b, hk, skv, d)).astype(np.float32)
+    v = rng.standard_normal((b, hv, skv, dv)).astype(np.float32)
+    padding = case in (1, 2, 3, 6)
+    seq_q = (rng.integers(0, sq + 1, b) if padding else np.full(b, sq)).astype(np.int32)
+    seq_kv = (rng.integers(0, skv + 1, b) if padding else np.full(b, skv)).astype(np.int32)
+    left, right = (3 if case in (2, 5) else None), (0 if case in (2, 3, 4, 7) else None)
+    bottom_right = case in (3, 4)
+    alibi = case == 5
+    bias = rng.standard_normal((1, hq, 1, skv)).astype(np.float32) if case == 1 else None
+    sink = rng.standard_normal(hq).astype(np.float32) if case in (0, 6) else None
+    mask = None
+    if case == 7:
+        mask = rng.integers(1, 256, (b, hq, 2, 1)).astype(np.uint8)  # 2 query tiles x 3 key tiles: one byte per row of tiles
+        mask[..., 0] |= 1  # (the first key tile stays on, so that causal rows keep a valid key)
+    scale = 0.37
+    p = oracle.SdpaParams()
+    p.q, p.k, p.v, p.o = tensor(F32, list(q.shape)), tensor(F32, list(k.shape)), tensor(F32, list(v.shape)), tensor(F32, [b, hq, sq, dv])
+    p.stats = p.max = p.sum_exp = tensor(F32, [b, hq, sq, 1])
+    p.attn_scale, p.s_kv, p.padding_mask, p.bottom_right, p.alibi_mask = scale, skv, int(padding), int(bottom_right), int(alibi)
+    if padding:
+        p.seq_q = p.seq_kv = tensor(I32, [b, 1, 1, 1])
+    if left is not None:
+        p.has_left_bound, p.left_bound = 1, left
+    if right is not None:
+        p.has_right_bound, p.right_bound = 1, right
+    if bias is not None:
+        p.bias = tensor(F32, list(bias.shape))
+    if sink is not None:
+        p.sink = tensor(F32, [1, hq, 1, 1])
+    if mask is not None:
+        p.block_mask = tensor(U8, list(mask.shape))
+    rows = b * hq * sq
+    o, stats, maximum, sum_exp = (np.zeros(rows * dv, np.float32), np.zeros(rows, np.float32), np.zeros(rows, np.float32), np.zeros(rows, np.float32))
+    oracle.sdpa_forward(p, [q, k, v, o, stats, maximum, sum_exp, seq_q if padding else None, seq_kv if padding else None, None, None, bias, sink, mask])
+    ro, rs, rm, re = (np.zeros_like(o), np.zeros_like(stats), np.zeros_like(maximum), np.zeros_like(sum_exp))
+    i64 = lambda a: (C.c_int64 * 4)(*[int(x) for x in a])
+    ptr = lambda a, t: a.ctypes.data_as(C.POINTER(t)) if a is not None else None
+    lib.ref_attention_forward(i64(q.shape), i64(k.shape), i64(v.shape), ptr(q, C.c_float), ptr(k, C.c_float), ptr(v, C.c_float), ptr(bias, C.c_float), ptr(sink, C.c_float),
+                              ptr(mask, C.c_uint8), C.c_int64(mask.size if mask is not None else 0), ptr(seq_q, C.c_int32), ptr(seq_kv, C.c_int32), C.c_float(scale),
+                              int(alibi), int(padding), int(bottom_right), int(left is not None), C.c_int64(left or 0), int(right is not None), C.c_int64(right or 0),
+                              ptr(ro, C.c_float), ptr(rs, C.c_float), ptr(rm, C.c_float), ptr(re, C.c_float))
+    assert np.allclose(o, ro, rtol=2e-5, atol=2e-6)
+    live = re > 0  # rows with at least one valid key (or a sink): the others have no defined statistics
+    assert live.any()
+    assert np.allclose(maximum[live], rm[live], rtol=1e-6, atol=1e-6) and np.allclose(sum_exp[live], re[live], rtol=2e-5) and np.allclose(stats[live], rs[live], rtol=2e-5, atol=2e-6)
