@@ -175,7 +175,7 @@ def test_conv_benchmark_shape_c1_both_layouts():
 
 
 def test_conv_benchmark_shape_c1_runs_on_tensor_cores():
-    """The same convolution resolves to the split-operand tcgen05 form (three bf16 products, f32 accumulation) and holds
+    """The same convolution resolves to the split-operand tcgen05 form (six bf16 products of three-piece operands, f32 accumulation) and holds
     the f32 gates against the oracle; so does a 1x1 filter, a deeper one with bias and ReLU, and a batch of images."""
     x_dims, w_dims, y_dims = [1, 64, 56, 56], [64, 64, 3, 3], [1, 64, 56, 56]
     info, out, ref = run_conv(F32, x_dims, w_dims, [1, 1], [1, 1], [1, 1], [1, 1], dfgpu.CONV_AUTO,
@@ -200,13 +200,13 @@ def test_conv_benchmark_shape_c1_runs_on_tensor_cores():
 
 @pytest.mark.parametrize("where", ["x_inf", "x_nan", "w_inf", "x_huge", "clean"])
 def test_conv_split_form_with_non_finite_operands(where):
-    """An infinity or a NaN in X or W does not survive the hi/lo split (inf * 0), so the CUDA-core kernel behind the
+    """An infinity or a NaN in X or W does not survive the split into bf16 pieces (inf * 0), so the CUDA-core kernel behind the
     tensor-core one redoes the convolution: the result is then bit for bit the CUDA-core kernel's own (NaNs in the same
     places). Finite values past the largest bf16 stay on the tensor cores."""
     x_dims, w_dims, y_dims = [1, 64, 12, 12], [64, 64, 3, 3], [1, 64, 12, 12]
     x = synthetic.normal(9, 1, int(np.prod(x_dims)))
     w = synthetic.normal(9, 2, int(np.prod(w_dims)), std=0.05)
-    w[::7] = np.float32(0.5)          # low halves of exactly zero
+    w[::7] = np.float32(0.5)          # lower pieces of exactly zero
     if where == "x_inf": x[5 * 64 + 3] = np.inf
     if where == "x_nan": x[77 * 64 + 9] = np.nan
     if where == "w_inf": w[1000] = -np.inf

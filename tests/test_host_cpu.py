@@ -151,7 +151,7 @@ def test_bottleneck_plan_fuses_to_three_launches_and_shares_workspace():
     unfused = runtime.compile_graph(graphs.c2_bottleneck(n=2, h=8, w=8), options=runtime.NO_FUSION)
     assert unfused.launch_count == 8
     f32 = runtime.compile_graph(graphs.c2_bottleneck(n=2, h=8, w=8, io="FLOAT"))
-    # an all-FLOAT graph runs on tcgen05 too, as three bf16 products of split operands: each convolution is three launches
+    # an all-FLOAT graph runs on tcgen05 too, as six bf16 products of three-piece operands: each convolution is three launches
     # (split, convolution, the guarded CUDA-core pass for non-finite inputs) and needs scratch for the split copies
     assert f32.plan_text().count("conv_fprop kernel=4 launches=3") == 3 and f32.launch_count == 9
     assert f32.plan_text().count("scratch=ws+") == 3 and f32.workspace_size > 2 * (2 * 8 * 8 * 64 * 4)
