@@ -621,6 +621,7 @@ def main() -> None:
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     parser.add_argument("--no-peaks", action="store_true", help="skip the FP8 / TF32 peak measurement")
     parser.add_argument("--no-check", action="store_true", help="skip the compared pass before timing")
+    parser.add_argument("--no-modes", action="store_true", help="multi-GPU default run: skip the short measurements of the two other modes (shards without the gather, replicas)")
     parser.add_argument("--ref-threads", type=int, default=0, help="host threads of the reference arm (0 = all this process may use)")
     args = parser.parse_args()
     if args.impl == "reference":
@@ -737,6 +738,30 @@ def main() -> None:
             line["cpu_baseline"] = {"value": cpu_value, "unit": wl.unit, "cores": 1, "kind": "port", "sample": description,
                                     "seconds_per_sample": seconds, "runs": runs, "whole_configuration": bool(whole),
                                     "note": "CPU restatement of the reference algorithm, single-threaded like the reference; its binary needs LLVM/MLIR 22.1.8 (absent)"}
+    # the same configuration in the other two multi-GPU modes, measured briefly by all ranks and carried in the same line:
+    # the shards without the exchange, and one full configuration per GPU (weak scaling, no exchange)
+    if distributed and shards and gather and not args.no_modes:
+        import torch.distributed as dist
+        if rank != 0:
+            del result
+        torch.cuda.empty_cache()
+        modes = {}
+        for mode, mode_sharded in (("sharded_without_gather", True), ("replicas", False)):
+            steps = min(args.steps, 100)
+            r = measure(args.workload, steps, args.warmup, torch, device, True, False, None, sharded=mode_sharded, check=False, options=options, pin=False)
+            times = torch.tensor([r["device_ms"]], device=device, dtype=torch.float64)
+            dist.all_reduce(times, op=dist.ReduceOp.MAX)
+            total = torch.tensor([r["workload"].units_per_second(1.0)], device=device, dtype=torch.float64)
+            dist.all_reduce(total, op=dist.ReduceOp.SUM)
+            ms = float(times.item()) / steps
+            modes[mode] = {"value": float(total.item()) / (ms / 1e3), "unit": r["workload"].unit, "ms_per_step": ms, "steps": steps,
+                           "scaling": "strong" if mode_sharded else "weak",
+                           "per_gpu": "its shard of the full configuration, outputs left where they are" if mode_sharded else "the full configuration (N configurations per step in all)"}
+            del r
+            torch.cuda.empty_cache()
+        if rank == 0:
+            line["other_modes"] = modes
+    if rank == 0:
         print(json.dumps(line))
     if distributed:
         import torch.distributed as dist
