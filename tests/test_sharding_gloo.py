@@ -69,3 +69,26 @@ def test_two_rank_shards_gather_to_the_unsharded_result(name):
         process.join(timeout=120)
         assert process.exitcode == 0, f"rank exited with {process.exitcode}"
     assert results.get(timeout=5) == (name, "ok")
+
+
+def test_ranks_take_disjoint_cores_near_their_gpus(monkeypatch):
+    """bench.py's host-side placement for multi-GPU runs: ranks whose GPUs hang off the same NUMA node split that
+    node's cores between them, ranks on different nodes each stay on their own, and without NVML's answer every rank
+    takes an equal share of the allowed cores. (os.sched_setaffinity is intercepted: the test process keeps its cores.)"""
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+    import bench
+    chosen = {}
+    monkeypatch.setattr(os, "sched_getaffinity", lambda pid: set(range(64)))
+    monkeypatch.setattr(os, "sched_setaffinity", lambda pid, cores: chosen.__setitem__("cores", sorted(cores)))
+    # GPUs 0-3 on node 0 (cores 0-31), GPUs 4-7 on node 1 (cores 32-63)
+    monkeypatch.setattr(bench, "cores_near_gpu", lambda index: list(range(0, 32)) if index < 4 else list(range(32, 64)))
+    seen = []
+    for rank in range(8):
+        text = bench.spread_over_cores(rank, 8)
+        assert "NUMA node" in text
+        seen.append(chosen["cores"])
+    assert seen[0] == list(range(0, 8)) and seen[3] == list(range(24, 32)) and seen[4] == list(range(32, 40)) and seen[7] == list(range(56, 64))
+    assert sorted(core for cores in seen for core in cores) == list(range(64))
+    monkeypatch.setattr(bench, "cores_near_gpu", lambda index: [])
+    assert "GPU locality unknown" in bench.spread_over_cores(5, 8) and chosen["cores"] == list(range(40, 48))
+    assert bench.spread_over_cores(0, 1) == "unchanged"
