@@ -442,7 +442,8 @@ int choose_kernel(const dfgpu_conv_params& p, const ConvArgs& a, int& kernel) {
     if (conv_umma_supported(p)) automatic = DFGPU_CONV_UMMA_BF16;
     SplitForm split;
     const bool split_ok = f32_split_form(p, split);
-    if (split_ok) automatic = DFGPU_CONV_UMMA_F32X3;
+    // (three launches instead of one: only where the convolution is big enough for the tensor cores to pay for them)
+    if (split_ok && p.y.dim[0] * p.y.dim[2] * p.y.dim[3] * p.y.dim[1] * p.w.dim[1] * p.w.dim[2] * p.w.dim[3] >= kSplitFormMinMacs) automatic = DFGPU_CONV_UMMA_F32X3;
     kernel = p.kernel == DFGPU_CONV_AUTO ? automatic : p.kernel;
     if (kernel == DFGPU_CONV_UMMA_F32X3 && !split_ok)
         return fail(kUnsupported, "CONV_FPROP: the split-operand tcgen05 form needs packed channels-last f32 X, W and Y, C and K multiples of 64, stride 1, dilation 1");

@@ -256,7 +256,7 @@ int choose_kernel(const dfgpu_matmul_params& p, int& kernel) {
     const bool split_ok = f32_split_matmul(p, split);
     if (matmul_umma_supported(p, DFGPU_MATMUL_UMMA_MXF8)) automatic = DFGPU_MATMUL_UMMA_MXF8;
     else if (matmul_umma_supported(p, DFGPU_MATMUL_UMMA_BF16)) automatic = DFGPU_MATMUL_UMMA_BF16;
-    else if (split_ok) automatic = DFGPU_MATMUL_UMMA_F32X3;
+    else if (split_ok && p.c.dim[p.c.rank - 2] * p.c.dim[p.c.rank - 1] * p.a.dim[p.a.rank - 1] >= kSplitFormMinMacs) automatic = DFGPU_MATMUL_UMMA_F32X3;  // (three launches: big products only)
     kernel = p.kernel == DFGPU_MATMUL_AUTO ? automatic : p.kernel;
     if (kernel < DFGPU_MATMUL_FFMA || kernel > DFGPU_MATMUL_UMMA_F32X3) return fail(kInvalidArgument, "MATMUL: unknown kernel id %d", kernel);
     if (kernel == DFGPU_MATMUL_UMMA_F32X3) {

@@ -46,6 +46,7 @@ int conv_pair_device_status(int* status);
 // an infinity or a NaN.
 constexpr int kSplitQuadsPerCta = 1024;  // 256 threads x 4 float4
 constexpr int kSplitPieces = 6;           // bf16 values per f32 value
+constexpr int64_t kSplitFormMinMacs = int64_t{1} << 24;  // AUTO takes the split-operand form from this many multiply-adds on; below, one CUDA-core launch is quicker than three
 struct SplitOperand {
     const float* source;
     uint16_t* pieces;

@@ -191,7 +191,8 @@ def test_conv_benchmark_shape_c1_runs_on_tensor_cores():
         n, c, h, w = x_dims
         y_dims = [n, w_dims[0], h, w]
         bias = synthetic.uniform(3, 5, w_dims[0], -0.1, 0.1)
-        info, out, ref = run_conv(F32, x_dims, w_dims, [pad, pad], [pad, pad], [1, 1], [1, 1], dfgpu.CONV_AUTO,
+        # (asked for by id: AUTO keeps convolutions below 2^24 multiply-adds on CUDA cores, where one launch beats three)
+        info, out, ref = run_conv(F32, x_dims, w_dims, [pad, pad], [pad, pad], [1, 1], [1, 1], dfgpu.CONV_UMMA_F32X3,
                                   nhwc_strides(x_dims), nhwc_strides(w_dims), nhwc_strides(y_dims), seed=5,
                                   epilogue=[step(dfgpu.EPI_ADD, 0), step(dfgpu.EPI_RELU)], extras=[([1, w_dims[0], 1, 1], [w_dims[0], 1, w_dims[0], w_dims[0]], bias)])
         assert info.kernel == dfgpu.CONV_UMMA_F32X3
@@ -278,9 +279,12 @@ def test_matmul_f32_on_tensor_cores(a_dims, b_dims, b_strides):
     against the oracle, for N-contiguous and K-contiguous B and a last row tile that is not full."""
     p = dfgpu.MatmulParams()
     p.a, p.b, p.c = tensor(F32, a_dims), tensor(F32, b_dims, b_strides), tensor(F32, [a_dims[0], b_dims[1]])
+    big = a_dims[0] * a_dims[1] * b_dims[1] >= 1 << 24  # AUTO takes the three-launch form for big products only
+    assert dfgpu.query("matmul", p).kernel == (dfgpu.MATMUL_UMMA_F32X3 if big else dfgpu.MATMUL_FFMA)
+    p.kernel = dfgpu.MATMUL_UMMA_F32X3
     info = dfgpu.query("matmul", p)
     assert info.kernel == dfgpu.MATMUL_UMMA_F32X3 and info.launches == 3 and info.scratch_bytes > 0
-    out, ref = run_matmul(F32, a_dims, b_dims, kernel=dfgpu.MATMUL_AUTO, b_strides=b_strides)
+    out, ref = run_matmul(F32, a_dims, b_dims, kernel=dfgpu.MATMUL_UMMA_F32X3, b_strides=b_strides)
     check_f32(out, ref)
     cores, _ = run_matmul(F32, a_dims, b_dims, kernel=dfgpu.MATMUL_FFMA, b_strides=b_strides)
     assert float(np.max(np.abs(out - cores))) <= 2e-5 * float(np.max(np.abs(ref)))  # (each carries its own f32 accumulation error)
