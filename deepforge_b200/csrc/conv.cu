@@ -8,37 +8,11 @@
 // reference's single-node path does with its materialised zero padding; for finite
 // data this equals the generic path's "skip the tap" rule.
 #include "common.cuh"
+#include "conv_args.cuh"
 #include "umma.cuh"
 
 namespace dfgpu {
 namespace {
-
-struct ConvArgs {
-    View x, w, y;
-    View extra[2];
-    const void* extra_data[2];
-    Epilogue epilogue;
-    int32_t pad_h, pad_w, stride_h, stride_w, dilation_h, dilation_w;
-    int32_t reverse;
-    int32_t groups;
-    int64_t c_per_group, k_per_group;
-};
-
-__device__ __forceinline__ float apply_epilogue(float value, const ConvArgs& a, int64_t n, int64_t k, int64_t p, int64_t q) {
-    for (int step = 0; step < a.epilogue.count; ++step) {
-        if (a.epilogue.op[step] == DFGPU_EPI_ADD) {
-            const View& t = a.extra[a.epilogue.operand[step]];
-            int64_t index[4] = {n, k, p, q};
-            int shift = 4 - t.rank;
-            int64_t offset = 0;
-            for (int i = 0; i < t.rank; ++i) offset += (t.dim[i] == 1 ? 0 : index[i + shift]) * t.stride[i];
-            value = __fadd_rn(value, load_as_f32(a.extra_data[a.epilogue.operand[step]], t.dtype, offset));
-        } else {
-            value = relu_forward(value, a.epilogue.lower[step], a.epilogue.upper[step], a.epilogue.slope[step]);
-        }
-    }
-    return value;
-}
 
 __global__ void conv_direct_kernel(const void* x, const void* w, void* y, ConvArgs a, int64_t total) {
     int64_t flat = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -443,17 +417,22 @@ int choose_kernel(const dfgpu_conv_params& p, const ConvArgs& a, int& kernel) {
     SplitForm split;
     const bool split_ok = f32_split_form(p, split);
     // (three launches instead of one: only where the convolution is big enough for the tensor cores to pay for them)
-    if (split_ok && p.y.dim[0] * p.y.dim[2] * p.y.dim[3] * p.y.dim[1] * p.w.dim[1] * p.w.dim[2] * p.w.dim[3] >= kSplitFormMinMacs) automatic = DFGPU_CONV_UMMA_F32X3;
+    const int64_t macs = p.y.dim[0] * p.y.dim[2] * p.y.dim[3] * p.y.dim[1] * p.w.dim[1] * p.w.dim[2] * p.w.dim[3];
+    if (split_ok && macs >= kSplitFormMinMacs) automatic = DFGPU_CONV_UMMA_F32X3;
+    const bool cluster_ok = conv_f32_cluster_supported(p);
+    if (cluster_ok && macs >= kClusterFormMinMacs) automatic = DFGPU_CONV_UMMA_F32X3_CLUSTER;   // (few tiles: one launch beats three)
     kernel = p.kernel == DFGPU_CONV_AUTO ? automatic : p.kernel;
     if (kernel == DFGPU_CONV_UMMA_F32X3 && !split_ok)
         return fail(kUnsupported, "CONV_FPROP: the split-operand tcgen05 form needs packed channels-last f32 X, W and Y, C and K multiples of 64, stride 1, dilation 1");
+    if (kernel == DFGPU_CONV_UMMA_F32X3_CLUSTER && !cluster_ok)
+        return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs packed channels-last f32 X, W and Y, C and K multiples of 64, stride 1, dilation 1 and at most 148 output tiles");
     if (kernel != DFGPU_CONV_UMMA_BF16 && (p.x.dtype == DFGPU_BF16X2 || p.y.dtype == DFGPU_BF16X2))
         return fail(kUnsupported, "CONV_FPROP: split bf16 pair tensors are read and written by the tcgen05 kernel only");
     if (kernel == DFGPU_CONV_IGEMM_FFMA && a.groups != 1)
         return fail(kUnsupported, "CONV_FPROP: the implicit-GEMM kernel needs groups == 1");
     if (kernel == DFGPU_CONV_UMMA_BF16 && !conv_umma_supported(p))
         return fail(kUnsupported, "CONV_FPROP: the tcgen05 kernel needs bf16 NHWC/KRSC, C and K multiples of 64, stride 1, dilation 1");
-    if (kernel < DFGPU_CONV_DIRECT || kernel > DFGPU_CONV_UMMA_F32X3)
+    if (kernel < DFGPU_CONV_DIRECT || kernel > DFGPU_CONV_UMMA_F32X3_CLUSTER)
         return fail(kInvalidArgument, "CONV_FPROP: unknown kernel id %d", kernel);
     return kOk;
 }
@@ -498,6 +477,7 @@ extern "C" int dfgpu_conv_fprop(const dfgpu_conv_params* p, void* const* tensors
     if (status) return status;
     cudaStream_t stream = as_stream(stream_handle);
     if (kernel == DFGPU_CONV_UMMA_BF16) return launch_conv_umma(*p, tensors, stream);
+    if (kernel == DFGPU_CONV_UMMA_F32X3_CLUSTER) return launch_conv_f32_cluster(*p, a, tensors, stream);
     int64_t m_total = p->y.dim[0] * p->y.dim[2] * p->y.dim[3];
     if (kernel == DFGPU_CONV_UMMA_F32X3) {
         SplitForm split;

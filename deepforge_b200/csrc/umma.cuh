@@ -32,6 +32,14 @@ struct ConvKSplit {
 ConvKSplit conv_umma_k_split(const dfgpu_conv_params& p);
 int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStream_t stream, const ConvKSplit* k_split = nullptr);
 
+// f32 NHWC/KRSC convolution with fewer output tiles than SMs on the bf16 tensor cores in one launch: a thread-block
+// cluster per output tile, the operands split into bf16 pieces on their way into shared memory (umma_conv_f32.cu).
+struct ConvArgs;
+bool conv_f32_cluster_supported(const dfgpu_conv_params& p);
+int launch_conv_f32_cluster(const dfgpu_conv_params& p, const ConvArgs& a, void* const* tensors, cudaStream_t stream);
+int conv_f32_device_status(int* status);
+constexpr int64_t kClusterFormMinMacs = int64_t{1} << 23;  // AUTO takes the one-launch form from this many multiply-adds on
+
 // A wide-filter convolution and the 1 x 1 convolution that consumes it, in one persistent kernel (the intermediate
 // stays on the SM). tensors: {X, W first, W second, Y, first.extra0, first.extra1, second.extra0, second.extra1}.
 bool conv_pair_umma_supported(const dfgpu_conv_params& first, const dfgpu_conv_params& second);

@@ -1,0 +1,404 @@
+// f32 CONV_FPROP on the bf16 tensor cores in ONE launch, for convolutions with fewer output tiles than SMs.
+//
+// x = xh + xm + xl and w = wh + wm + wl with bf16 pieces (the leading 8 significant bits, the next 8, the last 8, each
+// cut off rather than rounded, so every subtraction that forms them is exact and no piece can round past the largest
+// bf16), and x * w = xm*wm + xl*wh + xh*wl + xm*wh + xh*wm + xh*wh up to 2^-23 relative: six bf16 products per 16-deep K
+// step, accumulated in f32 in tensor memory.
+//
+// One thread-block cluster per 128-pixel x 64-channel output tile. The K loop runs over units (one filter tap x 64 input
+// channels); the cluster's CTAs share the units out between them. A CTA's 512 loader threads read the f32 X rows of a tap
+// (zero rows outside the image) and the f32 filter rows, split them in registers and write the three pieces of each
+// straight into the 128-byte-swizzled shared-memory tiles the tcgen05 descriptors expect, two units in flight; one more
+// warp issues the 24 products of a unit when its tiles are complete. At the end every CTA parks its f32 partial tile in
+// its own shared memory, the cluster synchronises, and each CTA adds one slice of rows over all ranks (in rank order,
+// through distributed shared memory), applies the epilogue and stores Y.
+//
+// A product with an infinite or NaN factor does not survive the split, so the loaders also record whether they saw
+// one; the ranks exchange that with the partial tiles, and a cluster that saw one computes its tile on the CUDA cores
+// instead (zero padding still multiplied, as the reference's single-node path does).
+#include <cooperative_groups.h>
+
+#include "conv_args.cuh"
+#include "umma_ptx.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace dfgpu {
+namespace {
+
+constexpr int kTileM = 128, kTileN = 64, kChunk = 64;
+constexpr int kLoaders = 512, kThreads = kLoaders + 32;
+constexpr int kPieceBytesA = kTileM * 128, kPieceBytesB = kTileN * 128;   // 64 bf16 = one 128-byte swizzled row per pixel
+constexpr int kUnitBytes = 3 * (kPieceBytesA + kPieceBytesB);
+constexpr int kBuffers = 2;
+constexpr int kControlOffset = kBuffers * kUnitBytes;
+constexpr int kSmemBytes = kControlOffset + 64 + 1024;                     // (+ the slack that aligns the tiles to 1024 bytes)
+constexpr int kAccumulatorColumns = 64;
+constexpr int kMaxRanks = 8;
+constexpr int kMaxUnitsPerRank = 6;
+static_assert(kTileM * kTileN * 4 <= kUnitBytes, "the partial tile is parked in the first operand buffer");
+
+struct ClusterConvArgs {
+    const float* x;
+    const float* w;
+    float* y;
+    int m_total, units, units_per_rank, chunks;   // chunks: 64-channel slices per filter tap
+};
+
+// Two consecutive f32 quads as three 16-byte groups of bf16 pieces (high, middle, low); false when a value is infinite or NaN.
+__device__ __forceinline__ bool split_eight(const float4& a, const float4& b, uint4 (&piece)[3]) {
+    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    uint32_t high[8], middle[8], low[8];
+    bool finite = true;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        high[i] = __float_as_uint(v[i]);
+        finite = finite && (high[i] & 0x7f800000u) != 0x7f800000u;
+        const float rest = v[i] - __uint_as_float(high[i] & 0xffff0000u);
+        middle[i] = __float_as_uint(rest);
+        low[i] = __float_as_uint(rest - __uint_as_float(middle[i] & 0xffff0000u));   // (at most 8 significant bits are left)
+    }
+    uint32_t h[4], m[4], l[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {   // the upper halves of two words side by side
+        h[i] = __byte_perm(high[2 * i], high[2 * i + 1], 0x7632);
+        m[i] = __byte_perm(middle[2 * i], middle[2 * i + 1], 0x7632);
+        l[i] = __byte_perm(low[2 * i], low[2 * i + 1], 0x7632);
+    }
+    piece[0] = make_uint4(h[0], h[1], h[2], h[3]);
+    piece[1] = make_uint4(m[0], m[1], m[2], m[3]);
+    piece[2] = make_uint4(l[0], l[1], l[2], l[3]);
+    return finite;
+}
+
+
+__global__ void __launch_bounds__(kThreads, 1)
+umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_constant__ ConvArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = static_cast<int>(cluster.block_rank()), ranks = static_cast<int>(cluster.num_blocks());
+    const int tid = threadIdx.x, warp = uniform_warp_index(), lane = tid & 31;
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t full_bar = smem_base + kControlOffset, empty_bar = full_bar + 8 * kBuffers;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kControlOffset + 16 * kBuffers);
+    int* flag_word = reinterpret_cast<int*>(smem + kControlOffset + 16 * kBuffers + 4);
+
+    const int m0 = blockIdx.y * kTileM, n0 = blockIdx.z * kTileN;
+    const int first_unit = rank * g.units_per_rank;
+    const int my_units = max(0, min(g.units - first_unit, g.units_per_rank));
+    const int P = static_cast<int>(a.y.dim[2]), Q = static_cast<int>(a.y.dim[3]), K = static_cast<int>(a.y.dim[1]);
+    const int H = static_cast<int>(a.x.dim[2]), W = static_cast<int>(a.x.dim[3]), C = static_cast<int>(a.x.dim[1]);
+    const int R = static_cast<int>(a.w.dim[2]), S = static_cast<int>(a.w.dim[3]);
+
+    if (tid == 0) {
+        for (int b = 0; b < kBuffers; ++b) {
+            mbar_init(full_bar + 8 * b, kLoaders);
+            mbar_init(empty_bar + 8 * b, 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kLoaders / 32) {
+        tmem_alloc(smem_u32(tmem_slot), kAccumulatorColumns);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    bool ok = true, finite = true;
+    if (tid < kLoaders) {
+        // ---- loaders: f32 rows -> three bf16 pieces in the swizzled operand tiles ----------------------------------
+        const int unit16 = tid & 7;                          // which 8 channels (16 bytes of bf16) of the 64
+        const int row[2] = {tid >> 3, 64 + (tid >> 3)};      // two of the tile's 128 pixels, and (row[0]) one filter row
+        int ih0[2], iw0[2];
+        const float* x_image[2];
+        bool live[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int m = m0 + row[i];
+            live[i] = m < g.m_total;
+            const int mm = live[i] ? m : 0;
+            const int q = mm % Q, p = (mm / Q) % P, n = mm / (P * Q);
+            ih0[i] = p - a.pad_h;
+            iw0[i] = q - a.pad_w;
+            x_image[i] = g.x + static_cast<int64_t>(n) * H * W * C + unit16 * 8;
+        }
+        const float* w_row = g.w + static_cast<int64_t>(n0 + row[0]) * R * S * C + unit16 * 8;
+        const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        auto fetch = [&](int u, float4 (&xv)[2][2], float4 (&wv)[2]) {
+            const int unit = first_unit + u;
+            const int tap = unit / g.chunks, c0 = (unit - tap * g.chunks) * kChunk;
+            const int r = tap / S, s = tap - r * S;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int ih = ih0[i] + r, iw = iw0[i] + s;
+                xv[i][0] = xv[i][1] = zero;
+                if (live[i] && ih >= 0 && ih < H && iw >= 0 && iw < W) {
+                    const float4* source = reinterpret_cast<const float4*>(x_image[i] + (static_cast<int64_t>(ih) * W + iw) * C + c0);
+                    xv[i][0] = __ldg(source);
+                    xv[i][1] = __ldg(source + 1);
+                }
+            }
+            const float4* source = reinterpret_cast<const float4*>(w_row + static_cast<int64_t>(tap) * C + c0);
+            wv[0] = __ldg(source);
+            wv[1] = __ldg(source + 1);
+        };
+        float4 xv[2][2], wv[2];
+        if (my_units > 0) fetch(0, xv, wv);
+#pragma unroll 1
+        for (int u = 0; u < my_units; ++u) {
+            const int buffer = u & 1;
+            float4 xn[2][2], wn[2];
+            if (u + 1 < my_units) fetch(u + 1, xn, wn);   // the next unit's loads are in flight while this one is split
+            if (u >= kBuffers) ok = mbar_wait(empty_bar + 8 * buffer, ((u >> 1) - 1) & 1, 131) && ok;
+            uint8_t* tiles = smem + buffer * kUnitBytes;
+            uint4 piece[3];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                finite = split_eight(xv[i][0], xv[i][1], piece) && finite;
+                uint8_t* target = tiles + row[i] * 128 + ((unit16 ^ (row[i] & 7)) << 4);
+#pragma unroll
+                for (int j = 0; j < 3; ++j) *reinterpret_cast<uint4*>(target + j * kPieceBytesA) = piece[j];
+            }
+            finite = split_eight(wv[0], wv[1], piece) && finite;
+            uint8_t* target = tiles + 3 * kPieceBytesA + row[0] * 128 + ((unit16 ^ (row[0] & 7)) << 4);
+#pragma unroll
+            for (int j = 0; j < 3; ++j) *reinterpret_cast<uint4*>(target + j * kPieceBytesB) = piece[j];
+            fence_async_shared();
+            mbar_arrive(full_bar + 8 * buffer);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                xv[i][0] = xn[i][0];
+                xv[i][1] = xn[i][1];
+                wv[i] = wn[i];
+            }
+        }
+    } else {
+        // ---- issuing warp: the 24 products of every unit --------------------------------------------------------------
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kTileN >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
+        const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+#pragma unroll 1
+        for (int u = 0; u < my_units; ++u) {
+            const int buffer = u & 1;
+            ok = mbar_wait_warp(full_bar + 8 * buffer, (u >> 1) & 1, 132) && ok;
+            tc_fence_after();
+            if (ok) {
+                const uint32_t a_lo = smem_desc_lo(smem_base + buffer * kUnitBytes, 16);
+                const uint32_t b_lo = smem_desc_lo(smem_base + buffer * kUnitBytes + 3 * kPieceBytesA, 16);
+                if (elect_one()) {
+                    // smallest products first: middle*middle, low*high, high*low, middle*high, high*middle, high*high
+                    constexpr int piece_a[6] = {1, 2, 0, 1, 0, 0}, piece_b[6] = {1, 0, 2, 0, 1, 0};
+#pragma unroll
+                    for (int product = 0; product < 6; ++product)
+#pragma unroll
+                        for (int k = 0; k < kChunk / 16; ++k)
+                            umma_bf16(tmem_u, desc_words(a_lo + ((piece_a[product] * kPieceBytesA + k * 32) >> 4), smem_desc_hi(1024)),
+                                      desc_words(b_lo + ((piece_b[product] * kPieceBytesB + k * 32) >> 4), smem_desc_hi(1024)), idesc, (u | product | k) != 0 ? 1u : 0u);
+                    umma_commit(empty_bar + 8 * buffer);
+                }
+                __syncwarp();
+            }
+        }
+    }
+
+    // ---- this CTA's partial tile: tensor memory -> its own shared memory (over the first operand buffer) ------------
+    if (warp < 8) {
+        const int quadrant = warp & 3, half = warp >> 2;   // lanes 32 * quadrant.. of tensor memory, 32 of the 64 columns
+        const int row = quadrant * 32 + lane;
+        uint32_t r[32];
+        if (my_units > 0) {
+            ok = mbar_wait(empty_bar + 8 * ((my_units - 1) & 1), ((my_units - 1) >> 1) & 1, 133) && ok;   // the last commit covers every product
+            tc_fence_after();
+            tmem_load_32(tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) + half * 32, r);
+            tmem_load_wait();
+            tc_fence_before();
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(smem + row * 256 + (((half * 8 + j) ^ (row & 7)) << 4)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+    }
+    const int unsplittable = __syncthreads_or(finite ? 0 : 1);
+    if (tid == 0) *flag_word = unsplittable;
+    cluster.sync();
+
+    // ---- one slice of rows per rank: the sum over all ranks' partial tiles, the epilogue, Y -------------------------
+    int any_unsplittable = 0;
+    for (int z = 0; z < ranks; ++z) any_unsplittable |= *cluster.map_shared_rank(flag_word, z);
+    const int rows_per_rank = (kTileM + ranks - 1) / ranks;
+    const int row_begin = rank * rows_per_rank, row_end = min(kTileM, row_begin + rows_per_rank);
+    if (!any_unsplittable) {
+        const uint8_t* parked[kMaxRanks];
+#pragma unroll
+        for (int z = 0; z < kMaxRanks; ++z) parked[z] = z < ranks ? cluster.map_shared_rank(smem, z) : smem;
+        for (int item = tid; item < (row_end - row_begin) * 16; item += kThreads) {
+            const int row = row_begin + (item >> 4), unit = item & 15;
+            const int m = m0 + row;
+            if (m >= g.m_total) continue;
+            const int offset = row * 256 + ((unit ^ (row & 7)) << 4);
+            float4 part[kMaxRanks];
+#pragma unroll
+            for (int z = 0; z < kMaxRanks; ++z)   // every load in flight before the first sum
+                part[z] = z < ranks ? *reinterpret_cast<const float4*>(parked[z] + offset) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            float4 sum = part[0];
+#pragma unroll
+            for (int z = 1; z < kMaxRanks; ++z) {
+                if (z >= ranks) break;
+                sum.x = __fadd_rn(sum.x, part[z].x);
+                sum.y = __fadd_rn(sum.y, part[z].y);
+                sum.z = __fadd_rn(sum.z, part[z].z);
+                sum.w = __fadd_rn(sum.w, part[z].w);
+            }
+            const int k = n0 + unit * 4;
+            if (a.epilogue.count > 0) {
+                const int q = m % Q, p = (m / Q) % P, n = m / (P * Q);
+                sum.x = apply_epilogue(sum.x, a, n, k, p, q);
+                sum.y = apply_epilogue(sum.y, a, n, k + 1, p, q);
+                sum.z = apply_epilogue(sum.z, a, n, k + 2, p, q);
+                sum.w = apply_epilogue(sum.w, a, n, k + 3, p, q);
+            }
+            *reinterpret_cast<float4*>(g.y + static_cast<int64_t>(m) * K + k) = sum;
+        }
+    } else {
+        // An infinity or a NaN among this tile's inputs: the same rows on the CUDA cores, every tap multiplied (zero
+        // padding included), channels innermost.
+        for (int item = tid; item < (row_end - row_begin) * kTileN; item += kThreads) {
+            const int row = row_begin + item / kTileN, k = n0 + item % kTileN;
+            const int m = m0 + row;
+            if (m >= g.m_total) continue;
+            const int q = m % Q, p = (m / Q) % P, n = m / (P * Q);
+            const float* filter = g.w + static_cast<int64_t>(k) * R * S * C;
+            float sum = 0.0f;
+            for (int r = 0; r < R; ++r)
+                for (int s = 0; s < S; ++s) {
+                    const int ih = p - a.pad_h + r, iw = q - a.pad_w + s;
+                    const bool inside = ih >= 0 && ih < H && iw >= 0 && iw < W;
+                    const float* pixel = g.x + ((static_cast<int64_t>(n) * H + (inside ? ih : 0)) * W + (inside ? iw : 0)) * C;
+                    const float* tap = filter + (r * S + s) * C;
+                    for (int c = 0; c < C; ++c) sum = fmaf(inside ? __ldg(pixel + c) : 0.0f, __ldg(tap + c), sum);
+                }
+            g.y[static_cast<int64_t>(m) * K + k] = apply_epilogue(sum, a, n, k, p, q);
+        }
+    }
+    cluster.sync();   // (no CTA leaves while another still reads its partial tile)
+    if (warp == kLoaders / 32) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kAccumulatorColumns);
+    }
+}
+
+}  // namespace
+
+namespace {
+
+struct ClusterForm {
+    int tiles_m, tiles_n, units, chunks, ranks, units_per_rank;
+};
+
+void share_units(ClusterForm& form, int ranks) {
+    form.units_per_rank = (form.units + ranks - 1) / ranks;
+    form.ranks = (form.units + form.units_per_rank - 1) / form.units_per_rank;   // (no rank without a unit)
+}
+
+bool cluster_form(const dfgpu_conv_params& p, ClusterForm& form) {
+    if (p.x.dtype != DFGPU_F32 || p.w.dtype != DFGPU_F32 || p.y.dtype != DFGPU_F32 || p.reverse_filter) return false;
+    if (p.x.rank != 4 || p.w.rank != 4 || p.y.rank != 4) return false;
+    auto packed = [](const dfgpu_tensor& t) {
+        return t.stride[1] == 1 && t.stride[3] == t.dim[1] && t.stride[2] == t.dim[3] * t.dim[1] && t.stride[0] == t.dim[2] * t.dim[3] * t.dim[1];
+    };
+    if (!packed(p.x) || !packed(p.w) || !packed(p.y)) return false;
+    if (p.x.dim[1] != p.w.dim[1] || p.x.dim[1] % kChunk != 0 || p.y.dim[1] % kTileN != 0 || p.w.dim[0] != p.y.dim[1]) return false;
+    for (int axis = 0; axis < 2; ++axis)
+        if (p.stride[axis] != 1 || p.dilation[axis] != 1) return false;
+    if (element_count(p.x) >= (1ll << 31) || element_count(p.w) >= (1ll << 31) || element_count(p.y) >= (1ll << 31)) return false;
+    const int64_t m_total = p.y.dim[0] * p.y.dim[2] * p.y.dim[3];
+    const int64_t tiles = (m_total + kTileM - 1) / kTileM * (p.y.dim[1] / kTileN);
+    const int64_t units = p.w.dim[2] * p.w.dim[3] * (p.x.dim[1] / kChunk);
+    constexpr int kSms = 148;   // (a query has no device: the count this library is built for)
+    if (tiles > kSms || units > kMaxRanks * kMaxUnitsPerRank) return false;
+    form.tiles_m = static_cast<int>((m_total + kTileM - 1) / kTileM);
+    form.tiles_n = static_cast<int>(p.y.dim[1] / kTileN);
+    form.units = static_cast<int>(units);
+    form.chunks = static_cast<int>(p.x.dim[1] / kChunk);
+    share_units(form, static_cast<int>(std::min<int64_t>(std::min<int64_t>(kMaxRanks, units), std::max<int64_t>(1, kSms / tiles))));
+    return form.units_per_rank <= kMaxUnitsPerRank;
+}
+
+// How many clusters of each size the device runs at once (index = cluster size).
+struct ClusterCapacity {
+    int clusters[kMaxRanks + 1];
+    cudaError_t error;
+};
+
+const ClusterCapacity& cluster_capacity() {
+    static const ClusterCapacity capacity = [] {
+        ClusterCapacity c{};
+        c.error = cudaFuncSetAttribute(umma_conv_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        for (int ranks = 1; ranks <= kMaxRanks && c.error == cudaSuccess; ++ranks) {
+            cudaLaunchConfig_t config{};
+            config.gridDim = dim3(ranks, 148, 1);
+            config.blockDim = dim3(kThreads);
+            config.dynamicSmemBytes = kSmemBytes;
+            cudaLaunchAttribute attribute{};
+            attribute.id = cudaLaunchAttributeClusterDimension;
+            attribute.val.clusterDim.x = ranks;
+            attribute.val.clusterDim.y = attribute.val.clusterDim.z = 1;
+            config.attrs = &attribute;
+            config.numAttrs = 1;
+            c.error = cudaOccupancyMaxActiveClusters(&c.clusters[ranks], umma_conv_f32_kernel, &config);
+        }
+        return c;
+    }();
+    return capacity;
+}
+
+}  // namespace
+
+bool conv_f32_cluster_supported(const dfgpu_conv_params& p) {
+    ClusterForm form;
+    return cluster_form(p, form);
+}
+
+int launch_conv_f32_cluster(const dfgpu_conv_params& p, const ConvArgs& a, void* const* tensors, cudaStream_t stream) {
+    ClusterForm form;
+    if (!cluster_form(p, form)) return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs packed channels-last f32 X, W and Y, C and K multiples of 64, stride 1, dilation 1 and at most 148 output tiles");
+    for (int i = 0; i < 3; ++i)
+        if ((reinterpret_cast<uintptr_t>(tensors[i]) & 15u) != 0) return fail(kInvalidArgument, "CONV_FPROP: the one-launch tcgen05 form needs 16-byte aligned X, W and Y");
+    const ClusterCapacity& capacity = cluster_capacity();
+    if (capacity.error != cudaSuccess) return fail(kExecutionFailed, "CONV_FPROP: cluster launch set-up failed: %s", cudaGetErrorString(capacity.error));
+    // All tiles' clusters at once: fewer ranks per tile when the device cannot co-schedule that many clusters of the first size.
+    const int tiles = form.tiles_m * form.tiles_n;
+    while (form.ranks > 1 && capacity.clusters[form.ranks] < tiles) share_units(form, form.ranks - 1);
+    if (capacity.clusters[form.ranks] < 1) return fail(kExecutionFailed, "CONV_FPROP: the device cannot run a cluster of %d CTAs with %d bytes of shared memory", form.ranks, kSmemBytes);
+
+    ClusterConvArgs g{};
+    g.x = static_cast<const float*>(tensors[0]);
+    g.w = static_cast<const float*>(tensors[1]);
+    g.y = static_cast<float*>(tensors[2]);
+    g.m_total = static_cast<int>(p.y.dim[0] * p.y.dim[2] * p.y.dim[3]);
+    g.units = form.units;
+    g.units_per_rank = form.units_per_rank;
+    g.chunks = form.chunks;
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(form.ranks, form.tiles_m, form.tiles_n);
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = kSmemBytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = form.ranks;
+    attribute.val.clusterDim.y = attribute.val.clusterDim.z = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    cudaError_t error = cudaLaunchKernelEx(&config, umma_conv_f32_kernel, g, a);
+    if (error != cudaSuccess) return fail(kExecutionFailed, "CONV_FPROP: cluster launch failed: %s", cudaGetErrorString(error));
+    return check_launch("CONV_FPROP");
+}
+
+int conv_f32_device_status(int* status) { return read_and_clear_device_status(status); }
+
+}  // namespace dfgpu

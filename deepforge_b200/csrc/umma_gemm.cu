@@ -1166,6 +1166,10 @@ extern "C" int dfgpu_device_status(int* status) {
     code = conv_pair_device_status(&pair);
     if (code) return code;
     if (!gemm) gemm = pair;
+    int cluster = 0;
+    code = conv_f32_device_status(&cluster);
+    if (code) return code;
+    if (!gemm) gemm = cluster;
     code = mxf8_device_status(&mxf8);
     if (code) return code;
     if (!gemm) gemm = mxf8;

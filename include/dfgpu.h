@@ -156,11 +156,16 @@ enum {
     DFGPU_CONV_DIRECT = 1,      /* any rank-4 conv, one thread per output */
     DFGPU_CONV_IGEMM_FFMA = 2,  /* f32-accumulate implicit GEMM on CUDA cores */
     DFGPU_CONV_UMMA_BF16 = 3,   /* bf16 NHWC implicit GEMM on tcgen05 */
-    DFGPU_CONV_UMMA_F32X3 = 4   /* f32 NHWC on tcgen05: X and W split into three bf16 pieces each, six bf16 products (2^-24
+    DFGPU_CONV_UMMA_F32X3 = 4,  /* f32 NHWC on tcgen05: X and W split into three bf16 pieces each, six bf16 products (2^-24
                                    relative); needs scratch, three launches: split X and W, the bf16 convolution over 6C
                                    channels (K split over several CTAs per tile when the tiles are few), and the CUDA-core
                                    kernel again, which adds the partial sums, or redoes the convolution when X or W held
                                    an infinity or a NaN */
+    DFGPU_CONV_UMMA_F32X3_CLUSTER = 5  /* the same six products in ONE launch, for convolutions of at most 148 output tiles
+                                   (128 pixels x 64 channels): a thread-block cluster per tile shares the filter taps out
+                                   between its CTAs, which split X and W on their way into shared memory and add their
+                                   partial tiles through distributed shared memory; a cluster whose inputs hold an
+                                   infinity or a NaN computes its tile on the CUDA cores. No scratch */
 };
 typedef struct dfgpu_conv_params {
     dfgpu_tensor x, w, y;

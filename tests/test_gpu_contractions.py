@@ -174,11 +174,97 @@ def test_conv_benchmark_shape_c1_both_layouts():
     check_f32(out, ref)
 
 
-def test_conv_benchmark_shape_c1_runs_on_tensor_cores():
-    """The same convolution resolves to the split-operand tcgen05 form (six bf16 products of three-piece operands, f32 accumulation) and holds
-    the f32 gates against the oracle; so does a 1x1 filter, a deeper one with bias and ReLU, and a batch of images."""
+def test_conv_benchmark_shape_c1_in_one_launch_on_tensor_cores():
+    """The benchmark convolution has 25 output tiles for 148 SMs: AUTO resolves it to the one-launch tcgen05 form (a thread-block cluster per
+    tile, the filter taps shared out between its CTAs, no scratch), which holds the f32 gates against the oracle and agrees with the CUDA-core
+    kernel far inside them. So do the shapes below, by id: one unit per CTA, several units per CTA (the operand buffers are reused), two
+    channel chunks per tap, two tiles along K, a ragged last tile, images that end inside a tile, no padding, and bias + ReLU."""
     x_dims, w_dims, y_dims = [1, 64, 56, 56], [64, 64, 3, 3], [1, 64, 56, 56]
     info, out, ref = run_conv(F32, x_dims, w_dims, [1, 1], [1, 1], [1, 1], [1, 1], dfgpu.CONV_AUTO,
+                              nhwc_strides(x_dims), nhwc_strides(w_dims), nhwc_strides(y_dims), seed=20261126)
+    assert info.kernel == dfgpu.CONV_UMMA_F32X3_CLUSTER and info.launches == 1 and info.scratch_bytes == 0
+    check_f32(out, ref)
+    info2, out2, _ = run_conv(F32, x_dims, w_dims, [1, 1], [1, 1], [1, 1], [1, 1], dfgpu.CONV_IGEMM_FFMA,
+                              nhwc_strides(x_dims), nhwc_strides(w_dims), nhwc_strides(y_dims), seed=20261126)
+    assert float(np.max(np.abs(out - out2))) <= 3e-5 * float(np.max(np.abs(ref)))
+    cases = (([3, 128, 14, 14], [64, 128, 1, 1], 0), ([2, 64, 28, 28], [128, 64, 3, 3], 1), ([1, 64, 9, 20], [64, 64, 5, 5], 2),
+             ([4, 64, 40, 40], [64, 64, 3, 3], 1), ([2, 192, 11, 13], [64, 192, 3, 3], 0), ([5, 64, 7, 7], [256, 64, 1, 1], 0))
+    for x_dims, w_dims, pad in cases:
+        n, c, h, w = x_dims
+        k, _, r, s_ = w_dims
+        y_dims = [n, k, h + 2 * pad - r + 1, w + 2 * pad - s_ + 1]
+        bias = synthetic.uniform(3, 5, k, -0.1, 0.1)
+        info, out, ref = run_conv(F32, x_dims, w_dims, [pad, pad], [pad, pad], [1, 1], [1, 1], dfgpu.CONV_UMMA_F32X3_CLUSTER,
+                                  nhwc_strides(x_dims), nhwc_strides(w_dims), nhwc_strides(y_dims), seed=5,
+                                  epilogue=[step(dfgpu.EPI_ADD, 0), step(dfgpu.EPI_RELU)], extras=[([1, k, 1, 1], [k, 1, k, k], bias)])
+        assert info.kernel == dfgpu.CONV_UMMA_F32X3_CLUSTER and info.launches == 1
+        check_f32(out, ref)
+    assert dfgpu.device_status() == 0
+
+
+def test_conv_one_launch_form_limits():
+    """More output tiles than SMs, a strided convolution or channels that are not a multiple of 64 are refused by id, and AUTO then takes
+    another kernel."""
+    for x_dims, w_dims, stride in (([8, 64, 56, 56], [64, 64, 3, 3], 1), ([1, 64, 56, 56], [64, 64, 3, 3], 2), ([1, 32, 56, 56], [64, 32, 3, 3], 1)):
+        p = dfgpu.ConvParams()
+        n, c, h, w = x_dims
+        y_dims = [n, w_dims[0], (h + 2 - 3) // stride + 1, (w + 2 - 3) // stride + 1]
+        p.x, p.w, p.y = tensor(F32, x_dims, nhwc_strides(x_dims)), tensor(F32, w_dims, nhwc_strides(w_dims)), tensor(F32, y_dims, nhwc_strides(y_dims))
+        for i in range(2):
+            p.pre_pad[i], p.post_pad[i], p.stride[i], p.dilation[i] = 1, 1, stride, 1
+        p.kernel = dfgpu.CONV_UMMA_F32X3_CLUSTER
+        with pytest.raises(dfgpu.DfgpuError) as error:
+            dfgpu.query("conv_fprop", p)
+        assert "one-launch tcgen05 form" in str(error.value)
+        p.kernel = dfgpu.CONV_AUTO
+        assert dfgpu.query("conv_fprop", p).kernel != dfgpu.CONV_UMMA_F32X3_CLUSTER
+
+
+@pytest.mark.parametrize("where", ["x_inf", "x_nan", "w_inf", "x_huge", "clean"])
+def test_conv_one_launch_form_with_non_finite_operands(where):
+    """A cluster whose inputs hold an infinity or a NaN computes its tile on the CUDA cores: those tiles are bit for bit the CUDA-core kernel's
+    own (NaNs in the same places, zero padding multiplied), the others stay on the tensor cores. Finite values up to the largest f32 stay on
+    the tensor cores everywhere (the pieces are cut off, not rounded, so none rounds past the largest bf16)."""
+    x_dims, w_dims, y_dims = [1, 64, 12, 12], [64, 64, 3, 3], [1, 64, 12, 12]
+    x = synthetic.normal(9, 1, int(np.prod(x_dims)))
+    w = synthetic.normal(9, 2, int(np.prod(w_dims)), std=0.05)
+    w[::7] = np.float32(0.5)          # lower pieces of exactly zero
+    if where == "x_inf": x[5 * 64 + 3] = np.inf        # pixel 5: inside the first tile's windows only
+    if where == "x_nan": x[140 * 64 + 9] = np.nan      # pixel 140: seen by both tiles (rows 10..11 of the image)
+    if where == "w_inf": w[1000] = -np.inf
+    if where == "x_huge": x[40 * 64 + 1], w[:] = np.float32(3.395e38), np.float32(2.0 ** -20)
+    p = dfgpu.ConvParams()
+    p.x, p.w, p.y = tensor(F32, x_dims, nhwc_strides(x_dims)), tensor(F32, w_dims, nhwc_strides(w_dims)), tensor(F32, y_dims, nhwc_strides(y_dims))
+    for i in range(2):
+        p.pre_pad[i], p.post_pad[i], p.stride[i], p.dilation[i] = 1, 1, 1, 1
+    dx, dw = g.to_device(x.astype(np.float32)), g.to_device(w.astype(np.float32))
+    results = {}
+    for kernel in (dfgpu.CONV_IGEMM_FFMA, dfgpu.CONV_UMMA_F32X3_CLUSTER):
+        p.kernel = kernel
+        dy = g.device_zeros(int(np.prod(y_dims)) * 4, 0x5A)
+        dfgpu.conv_fprop(p, g.ptr(dx), g.ptr(dw), g.ptr(dy))
+        results[kernel] = g.to_host(dy, np.uint32).copy().reshape(144, 64)
+    cores, cluster = results[dfgpu.CONV_IGEMM_FFMA], results[dfgpu.CONV_UMMA_F32X3_CLUSTER]
+    a, b = cluster.view(np.float32), cores.view(np.float32)
+    exact_tiles = {"x_inf": [0], "x_nan": [0, 1], "w_inf": [0, 1], "x_huge": [], "clean": []}[where]
+    for tile in range(2):
+        rows = slice(tile * 128, min(144, tile * 128 + 128))
+        if tile in exact_tiles:
+            assert np.array_equal(cores[rows], cluster[rows])
+        else:
+            assert np.all(np.isfinite(a[rows])) and not np.array_equal(cores[rows], cluster[rows])  # (the tensor-core result stands)
+            assert float(np.max(np.abs(a[rows] - b[rows]))) <= 3e-5 * float(np.max(np.abs(b[np.isfinite(b)])))
+    if exact_tiles:
+        assert not np.all(np.isfinite(b))
+    assert dfgpu.device_status() == 0
+
+
+def test_conv_split_form_runs_on_tensor_cores():
+    """The three-launch split-operand tcgen05 form (six bf16 products of three-piece operands, f32 accumulation), which AUTO takes for f32
+    convolutions of more tiles than SMs: it holds the f32 gates against the oracle on the benchmark convolution, a 1x1 filter, a deeper one
+    with bias and ReLU, and a batch of images."""
+    x_dims, w_dims, y_dims = [1, 64, 56, 56], [64, 64, 3, 3], [1, 64, 56, 56]
+    info, out, ref = run_conv(F32, x_dims, w_dims, [1, 1], [1, 1], [1, 1], [1, 1], dfgpu.CONV_UMMA_F32X3,
                               nhwc_strides(x_dims), nhwc_strides(w_dims), nhwc_strides(y_dims), seed=20261126)
     assert info.kernel == dfgpu.CONV_UMMA_F32X3 and info.launches == 3 and info.scratch_bytes > 0
     check_f32(out, ref)

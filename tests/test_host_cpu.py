@@ -153,11 +153,15 @@ def test_bottleneck_plan_fuses_to_three_launches_and_shares_workspace():
     f32 = runtime.compile_graph(graphs.c2_bottleneck(n=2, h=8, w=8, io="FLOAT"))
     # an all-FLOAT graph this small stays on CUDA cores (one launch per convolution beats three)
     assert f32.plan_text().count("kernel=2") == 3 and f32.workspace_size == 2 * (2 * 8 * 8 * 64 * 4)
-    # from 2^24 multiply-adds per convolution on it runs on tcgen05 too, as six bf16 products of three-piece operands: each
-    # convolution is three launches (split, convolution, the guarded CUDA-core pass) and needs scratch for the split copies
-    large = runtime.compile_graph(graphs.c2_bottleneck(n=8, h=28, w=28, io="FLOAT"))
+    # a bigger one runs on tcgen05 too, as six bf16 products of three-piece operands. With at most 148 output tiles (128 pixels x 64
+    # channels) a convolution is ONE launch without scratch (a thread-block cluster per tile); with more tiles, from 2^24 multiply-adds on,
+    # it is three launches (split, convolution, the guarded CUDA-core pass) and needs scratch for the split copies
+    medium = runtime.compile_graph(graphs.c2_bottleneck(n=8, h=28, w=28, io="FLOAT"))   # 49 pixel tiles: conv3 (256 channels) has 196
+    assert medium.plan_text().count("conv_fprop kernel=5 launches=1") == 2 and medium.plan_text().count("conv_fprop kernel=4 launches=3") == 1
+    assert medium.launch_count == 5 and medium.plan_text().count("scratch=ws+") == 1
+    large = runtime.compile_graph(graphs.c2_bottleneck(n=32, h=28, w=28, io="FLOAT"))
     assert large.plan_text().count("conv_fprop kernel=4 launches=3") == 3 and large.launch_count == 9
-    assert large.plan_text().count("scratch=ws+") == 3 and large.workspace_size > 2 * (8 * 28 * 28 * 64 * 4)
+    assert large.plan_text().count("scratch=ws+") == 3 and large.workspace_size > 2 * (32 * 28 * 28 * 64 * 4)
     cores = runtime.compile_graph(graphs.c2_bottleneck(n=8, h=28, w=28, io="FLOAT"), options=runtime.NO_TENSOR_CORES)
     assert cores.plan_text().count("kernel=2") == 3 and cores.workspace_size == 2 * (8 * 28 * 28 * 64 * 4)
 
