@@ -9,12 +9,13 @@
 // channels); the cluster's CTAs share the units out between them. A CTA's 512 loader threads read the f32 X rows of a tap
 // (zero rows outside the image) and the f32 filter rows, split them in registers and write the three pieces of each
 // straight into the 128-byte-swizzled shared-memory tiles the tcgen05 descriptors expect, two units in flight; one more
-// warp issues the 24 products of a unit when its tiles are complete. At the end every CTA parks its f32 partial tile in
-// its own shared memory, the cluster synchronises, and each CTA adds one slice of rows over all ranks (in rank order,
-// through distributed shared memory), applies the epilogue and stores Y.
+// warp issues the 24 products of a unit when its tiles are complete. Every rank owns one slice of the tile's rows: at the
+// end a CTA sends each row of its f32 partial tile to the row's owner (stores into the owner's shared memory, which
+// nobody waits for), the cluster synchronises once, and each CTA adds its rows over all ranks in rank order, applies the
+// epilogue and stores Y.
 //
 // A product with an infinite or NaN factor does not survive the split, so the loaders also record whether they saw
-// one; the ranks exchange that with the partial tiles, and a cluster that saw one computes its tile on the CUDA cores
+// one; the ranks exchange that beside the partial tiles, and a cluster that saw one computes its tile on the CUDA cores
 // instead (zero padding still multiplied, as the reference's single-node path does).
 #include <cooperative_groups.h>
 
@@ -31,12 +32,13 @@ constexpr int kLoaders = 512, kThreads = kLoaders + 32;
 constexpr int kPieceBytesA = kTileM * 128, kPieceBytesB = kTileN * 128;   // 64 bf16 = one 128-byte swizzled row per pixel
 constexpr int kUnitBytes = 3 * (kPieceBytesA + kPieceBytesB);
 constexpr int kBuffers = 2;
-constexpr int kControlOffset = kBuffers * kUnitBytes;
-constexpr int kSmemBytes = kControlOffset + 64 + 1024;                     // (+ the slack that aligns the tiles to 1024 bytes)
-constexpr int kAccumulatorColumns = 64;
 constexpr int kMaxRanks = 8;
 constexpr int kMaxUnitsPerRank = 6;
-static_assert(kTileM * kTileN * 4 <= kUnitBytes, "the partial tile is parked in the first operand buffer");
+constexpr int kInboxOffset = kBuffers * kUnitBytes;                        // the rows this rank owns, one copy per sending rank
+constexpr int kInboxBytes = (kTileM + kMaxRanks) * kTileN * 4;             // ranks * ceil(128 / ranks) rows at most
+constexpr int kControlOffset = kInboxOffset + kInboxBytes;
+constexpr int kSmemBytes = kControlOffset + 128 + 1024;                    // (+ the slack that aligns the tiles to 1024 bytes)
+constexpr int kAccumulatorColumns = 64;
 
 struct ClusterConvArgs {
     const float* x;
@@ -82,7 +84,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t full_bar = smem_base + kControlOffset, empty_bar = full_bar + 8 * kBuffers;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kControlOffset + 16 * kBuffers);
-    int* flag_word = reinterpret_cast<int*>(smem + kControlOffset + 16 * kBuffers + 4);
+    int* flags = reinterpret_cast<int*>(smem + kControlOffset + 64);   // one word per rank, written by that rank
 
     const int m0 = blockIdx.y * kTileM, n0 = blockIdx.z * kTileN;
     const int first_unit = rank * g.units_per_rank;
@@ -90,6 +92,45 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
     const int P = static_cast<int>(a.y.dim[2]), Q = static_cast<int>(a.y.dim[3]), K = static_cast<int>(a.y.dim[1]);
     const int H = static_cast<int>(a.x.dim[2]), W = static_cast<int>(a.x.dim[3]), C = static_cast<int>(a.x.dim[1]);
     const int R = static_cast<int>(a.w.dim[2]), S = static_cast<int>(a.w.dim[3]);
+
+    // Loader threads: which rows of the operand tiles this thread fills (the issuing warp computes them too, and loads nothing).
+    const int unit16 = tid & 7;                          // which 8 channels (16 bytes of bf16) of the 64
+    const int row[2] = {tid >> 3, 64 + (tid >> 3)};      // two of the tile's 128 pixels, and (row[0]) one filter row
+    int ih0[2], iw0[2];
+    const float* x_image[2];
+    bool live[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int m = m0 + row[i];
+        live[i] = m < g.m_total;
+        const int mm = live[i] ? m : 0;
+        const int q = mm % Q, p = (mm / Q) % P, n = mm / (P * Q);
+        ih0[i] = p - a.pad_h;
+        iw0[i] = q - a.pad_w;
+        x_image[i] = g.x + static_cast<int64_t>(n) * H * W * C + unit16 * 8;
+    }
+    const float* w_row = g.w + static_cast<int64_t>(n0 + row[0]) * R * S * C + unit16 * 8;
+    const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    auto fetch = [&](int u, float4 (&xv)[2][2], float4 (&wv)[2]) {
+        const int unit = first_unit + u;
+        const int tap = unit / g.chunks, c0 = (unit - tap * g.chunks) * kChunk;
+        const int r = tap / S, s = tap - r * S;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int ih = ih0[i] + r, iw = iw0[i] + s;
+            xv[i][0] = xv[i][1] = zero;
+            if (live[i] && ih >= 0 && ih < H && iw >= 0 && iw < W) {
+                const float4* source = reinterpret_cast<const float4*>(x_image[i] + (static_cast<int64_t>(ih) * W + iw) * C + c0);
+                xv[i][0] = __ldg(source);
+                xv[i][1] = __ldg(source + 1);
+            }
+        }
+        const float4* source = reinterpret_cast<const float4*>(w_row + static_cast<int64_t>(tap) * C + c0);
+        wv[0] = __ldg(source);
+        wv[1] = __ldg(source + 1);
+    };
+    float4 xv[2][2], wv[2];
+    if (tid < kLoaders && my_units > 0) fetch(0, xv, wv);   // in flight while the barriers and tensor memory are set up
 
     if (tid == 0) {
         for (int b = 0; b < kBuffers; ++b) {
@@ -102,6 +143,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         tmem_alloc(smem_u32(tmem_slot), kAccumulatorColumns);
         tmem_relinquish();
     }
+    cluster.barrier_arrive();   // (waited for before the first store into another CTA's shared memory: every CTA of the cluster runs by then)
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -110,43 +152,6 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
     bool ok = true, finite = true;
     if (tid < kLoaders) {
         // ---- loaders: f32 rows -> three bf16 pieces in the swizzled operand tiles ----------------------------------
-        const int unit16 = tid & 7;                          // which 8 channels (16 bytes of bf16) of the 64
-        const int row[2] = {tid >> 3, 64 + (tid >> 3)};      // two of the tile's 128 pixels, and (row[0]) one filter row
-        int ih0[2], iw0[2];
-        const float* x_image[2];
-        bool live[2];
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int m = m0 + row[i];
-            live[i] = m < g.m_total;
-            const int mm = live[i] ? m : 0;
-            const int q = mm % Q, p = (mm / Q) % P, n = mm / (P * Q);
-            ih0[i] = p - a.pad_h;
-            iw0[i] = q - a.pad_w;
-            x_image[i] = g.x + static_cast<int64_t>(n) * H * W * C + unit16 * 8;
-        }
-        const float* w_row = g.w + static_cast<int64_t>(n0 + row[0]) * R * S * C + unit16 * 8;
-        const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        auto fetch = [&](int u, float4 (&xv)[2][2], float4 (&wv)[2]) {
-            const int unit = first_unit + u;
-            const int tap = unit / g.chunks, c0 = (unit - tap * g.chunks) * kChunk;
-            const int r = tap / S, s = tap - r * S;
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int ih = ih0[i] + r, iw = iw0[i] + s;
-                xv[i][0] = xv[i][1] = zero;
-                if (live[i] && ih >= 0 && ih < H && iw >= 0 && iw < W) {
-                    const float4* source = reinterpret_cast<const float4*>(x_image[i] + (static_cast<int64_t>(ih) * W + iw) * C + c0);
-                    xv[i][0] = __ldg(source);
-                    xv[i][1] = __ldg(source + 1);
-                }
-            }
-            const float4* source = reinterpret_cast<const float4*>(w_row + static_cast<int64_t>(tap) * C + c0);
-            wv[0] = __ldg(source);
-            wv[1] = __ldg(source + 1);
-        };
-        float4 xv[2][2], wv[2];
-        if (my_units > 0) fetch(0, xv, wv);
 #pragma unroll 1
         for (int u = 0; u < my_units; ++u) {
             const int buffer = u & 1;
@@ -203,7 +208,9 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         }
     }
 
-    // ---- this CTA's partial tile: tensor memory -> its own shared memory (over the first operand buffer) ------------
+    // ---- this CTA's partial tile: tensor memory -> the inbox of each row's owner -------------------------------------
+    const int rows_per_rank = (kTileM + ranks - 1) / ranks;
+    cluster.barrier_wait();
     if (warp < 8) {
         const int quadrant = warp & 3, half = warp >> 2;   // lanes 32 * quadrant.. of tensor memory, 32 of the 64 columns
         const int row = quadrant * 32 + lane;
@@ -218,32 +225,33 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = 0u;
         }
+        const int owner = row / rows_per_rank;
+        uint8_t* inbox = cluster.map_shared_rank(smem + kInboxOffset, owner) + (rank * rows_per_rank + row - owner * rows_per_rank) * (kTileN * 4);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<uint4*>(smem + row * 256 + (((half * 8 + j) ^ (row & 7)) << 4)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            *reinterpret_cast<uint4*>(inbox + (((half * 8 + j) ^ (row & 7)) << 4)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
     }
     const int unsplittable = __syncthreads_or(finite ? 0 : 1);
-    if (tid == 0) *flag_word = unsplittable;
-    cluster.sync();
+    if (tid < ranks) *cluster.map_shared_rank(flags + rank, tid) = unsplittable;
+    cluster.sync();   // (the last access to another CTA's shared memory is behind this point: a CTA may leave when it is done)
 
-    // ---- one slice of rows per rank: the sum over all ranks' partial tiles, the epilogue, Y -------------------------
+    // ---- this rank's rows: the sum over all ranks' partial tiles, the epilogue, Y --------------------------------------
     int any_unsplittable = 0;
-    for (int z = 0; z < ranks; ++z) any_unsplittable |= *cluster.map_shared_rank(flag_word, z);
-    const int rows_per_rank = (kTileM + ranks - 1) / ranks;
+#pragma unroll
+    for (int z = 0; z < kMaxRanks; ++z) any_unsplittable |= z < ranks ? flags[z] : 0;
     const int row_begin = rank * rows_per_rank, row_end = min(kTileM, row_begin + rows_per_rank);
     if (!any_unsplittable) {
-        const uint8_t* parked[kMaxRanks];
-#pragma unroll
-        for (int z = 0; z < kMaxRanks; ++z) parked[z] = z < ranks ? cluster.map_shared_rank(smem, z) : smem;
+        const uint8_t* inbox = smem + kInboxOffset;
+        const int sender_stride = rows_per_rank * (kTileN * 4);
         for (int item = tid; item < (row_end - row_begin) * 16; item += kThreads) {
             const int row = row_begin + (item >> 4), unit = item & 15;
             const int m = m0 + row;
             if (m >= g.m_total) continue;
-            const int offset = row * 256 + ((unit ^ (row & 7)) << 4);
+            const int offset = (row - row_begin) * (kTileN * 4) + ((unit ^ (row & 7)) << 4);
             float4 part[kMaxRanks];
 #pragma unroll
             for (int z = 0; z < kMaxRanks; ++z)   // every load in flight before the first sum
-                part[z] = z < ranks ? *reinterpret_cast<const float4*>(parked[z] + offset) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                part[z] = z < ranks ? *reinterpret_cast<const float4*>(inbox + z * sender_stride + offset) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             float4 sum = part[0];
 #pragma unroll
             for (int z = 1; z < kMaxRanks; ++z) {
@@ -284,7 +292,6 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
             g.y[static_cast<int64_t>(m) * K + k] = apply_epilogue(sum, a, n, k, p, q);
         }
     }
-    cluster.sync();   // (no CTA leaves while another still reads its partial tile)
     if (warp == kLoaders / 32) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kAccumulatorColumns);
