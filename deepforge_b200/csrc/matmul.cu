@@ -256,9 +256,18 @@ int choose_kernel(const dfgpu_matmul_params& p, int& kernel) {
     const bool split_ok = f32_split_matmul(p, split);
     if (matmul_umma_supported(p, DFGPU_MATMUL_UMMA_MXF8)) automatic = DFGPU_MATMUL_UMMA_MXF8;
     else if (matmul_umma_supported(p, DFGPU_MATMUL_UMMA_BF16)) automatic = DFGPU_MATMUL_UMMA_BF16;
-    else if (split_ok && p.c.dim[p.c.rank - 2] * p.c.dim[p.c.rank - 1] * p.a.dim[p.a.rank - 1] >= kSplitFormMinMacs) automatic = DFGPU_MATMUL_UMMA_F32X3;  // (three launches: big products only)
+    else {
+        const int64_t macs = p.c.dim[p.c.rank - 2] * p.c.dim[p.c.rank - 1] * p.a.dim[p.a.rank - 1];
+        if (split_ok && macs >= kSplitFormMinMacs) automatic = DFGPU_MATMUL_UMMA_F32X3;  // (three launches: big products only)
+        if (macs >= kClusterFormMinMacs && matmul_f32_cluster_supported(p)) automatic = DFGPU_MATMUL_UMMA_F32X3_CLUSTER;  // (few tiles: one launch)
+    }
     kernel = p.kernel == DFGPU_MATMUL_AUTO ? automatic : p.kernel;
-    if (kernel < DFGPU_MATMUL_FFMA || kernel > DFGPU_MATMUL_UMMA_F32X3) return fail(kInvalidArgument, "MATMUL: unknown kernel id %d", kernel);
+    if (kernel < DFGPU_MATMUL_FFMA || kernel > DFGPU_MATMUL_UMMA_F32X3_CLUSTER) return fail(kInvalidArgument, "MATMUL: unknown kernel id %d", kernel);
+    if (kernel == DFGPU_MATMUL_UMMA_F32X3_CLUSTER) {
+        if (!matmul_f32_cluster_supported(p))
+            return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs unbatched f32 A (K contiguous), B and C (N contiguous), K and N multiples of 64 and at most 148 output tiles");
+        return kOk;
+    }
     if (kernel == DFGPU_MATMUL_UMMA_F32X3) {
         if (!split_ok) return fail(kUnsupported, "MATMUL: the split-operand tcgen05 form needs unbatched f32 A (K contiguous), B and C, K a multiple of 32, N of 64");
         return kOk;
@@ -306,6 +315,7 @@ extern "C" int dfgpu_matmul(const dfgpu_matmul_params* p, void* const* tensors, 
     status = choose_kernel(*p, kernel);
     if (status) return status;
     cudaStream_t stream = as_stream(stream_handle);
+    if (kernel == DFGPU_MATMUL_UMMA_F32X3_CLUSTER) return launch_matmul_f32_cluster(*p, tensors, stream);
     if (kernel == DFGPU_MATMUL_UMMA_F32X3) {
         SplitMatmul split;
         if (!f32_split_matmul(*p, split)) return fail(kUnsupported, "MATMUL: the split-operand tcgen05 form does not take this matmul");

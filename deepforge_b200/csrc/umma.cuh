@@ -38,6 +38,9 @@ struct ConvArgs;
 bool conv_f32_cluster_supported(const dfgpu_conv_params& p);
 int launch_conv_f32_cluster(const dfgpu_conv_params& p, const ConvArgs& a, void* const* tensors, cudaStream_t stream);
 int conv_f32_device_status(int* status);
+// The same kernel for an unbatched f32 MATMUL of at most 148 output tiles (the 1 x 1 convolution of M pixels; B with N or K contiguous).
+bool matmul_f32_cluster_supported(const dfgpu_matmul_params& p);
+int launch_matmul_f32_cluster(const dfgpu_matmul_params& p, void* const* tensors, cudaStream_t stream);
 constexpr int64_t kClusterFormMinMacs = int64_t{1} << 23;  // AUTO takes the one-launch form from this many multiply-adds on
 
 // A wide-filter convolution and the 1 x 1 convolution that consumes it, in one persistent kernel (the intermediate

@@ -45,6 +45,9 @@ struct ClusterConvArgs {
     const float* w;
     float* y;
     int m_total, units, units_per_rank, chunks;   // chunks: 64-channel slices per filter tap
+    int64_t x_pixel_stride, y_pixel_stride;       // floats between pixels (C and K when packed)
+    int64_t w_stride;                             // floats between output channels, or (w_n_major) between input channels
+    int w_n_major;                                // the filter is stored [C, K] with K contiguous (a MATMUL's row-major B; 1 x 1 only)
 };
 
 // Two consecutive f32 quads as three 16-byte groups of bf16 pieces (high, middle, low); false when a value is infinite or NaN.
@@ -95,7 +98,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
 
     // Loader threads: which rows of the operand tiles this thread fills (the issuing warp computes them too, and loads nothing).
     const int unit16 = tid & 7;                          // which 8 channels (16 bytes of bf16) of the 64
-    const int row[2] = {tid >> 3, 64 + (tid >> 3)};      // two of the tile's 128 pixels, and (row[0]) one filter row
+    const int row[2] = {tid >> 3, 64 + (tid >> 3)};      // two of the tile's 128 pixels
     int ih0[2], iw0[2];
     const float* x_image[2];
     bool live[2];
@@ -107,9 +110,14 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         const int q = mm % Q, p = (mm / Q) % P, n = mm / (P * Q);
         ih0[i] = p - a.pad_h;
         iw0[i] = q - a.pad_w;
-        x_image[i] = g.x + static_cast<int64_t>(n) * H * W * C + unit16 * 8;
+        x_image[i] = g.x + static_cast<int64_t>(n) * H * W * g.x_pixel_stride + unit16 * 8;
     }
-    const float* w_row = g.w + static_cast<int64_t>(n0 + row[0]) * R * S * C + unit16 * 8;
+    // The filter tile: 64 output channels x 8 groups of 8 input channels. Stored with input channels contiguous, a thread
+    // reads its group as two quads; stored with output channels contiguous, neighbouring threads take neighbouring output
+    // channels and each reads its 8 input channels one by one.
+    const int w_channel = g.w_n_major ? tid & 63 : tid >> 3, w_unit = g.w_n_major ? (tid >> 6) & 7 : unit16;
+    const float* w_row = g.w_n_major ? g.w + static_cast<int64_t>(w_unit) * 8 * g.w_stride + n0 + w_channel
+                                     : g.w + static_cast<int64_t>(n0 + w_channel) * g.w_stride + w_unit * 8;
     const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     auto fetch = [&](int u, float4 (&xv)[2][2], float4 (&wv)[2]) {
         const int unit = first_unit + u;
@@ -120,14 +128,20 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
             const int ih = ih0[i] + r, iw = iw0[i] + s;
             xv[i][0] = xv[i][1] = zero;
             if (live[i] && ih >= 0 && ih < H && iw >= 0 && iw < W) {
-                const float4* source = reinterpret_cast<const float4*>(x_image[i] + (static_cast<int64_t>(ih) * W + iw) * C + c0);
+                const float4* source = reinterpret_cast<const float4*>(x_image[i] + (static_cast<int64_t>(ih) * W + iw) * g.x_pixel_stride + c0);
                 xv[i][0] = __ldg(source);
                 xv[i][1] = __ldg(source + 1);
             }
         }
-        const float4* source = reinterpret_cast<const float4*>(w_row + static_cast<int64_t>(tap) * C + c0);
-        wv[0] = __ldg(source);
-        wv[1] = __ldg(source + 1);
+        if (g.w_n_major) {
+            const float* source = w_row + static_cast<int64_t>(c0) * g.w_stride;
+            wv[0] = make_float4(__ldg(source), __ldg(source + g.w_stride), __ldg(source + 2 * g.w_stride), __ldg(source + 3 * g.w_stride));
+            wv[1] = make_float4(__ldg(source + 4 * g.w_stride), __ldg(source + 5 * g.w_stride), __ldg(source + 6 * g.w_stride), __ldg(source + 7 * g.w_stride));
+        } else {
+            const float4* source = reinterpret_cast<const float4*>(w_row + static_cast<int64_t>(tap) * C + c0);
+            wv[0] = __ldg(source);
+            wv[1] = __ldg(source + 1);
+        }
     };
     float4 xv[2][2], wv[2];
     if (tid < kLoaders && my_units > 0) fetch(0, xv, wv);   // in flight while the barriers and tensor memory are set up
@@ -168,7 +182,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
                 for (int j = 0; j < 3; ++j) *reinterpret_cast<uint4*>(target + j * kPieceBytesA) = piece[j];
             }
             finite = split_eight(wv[0], wv[1], piece) && finite;
-            uint8_t* target = tiles + 3 * kPieceBytesA + row[0] * 128 + ((unit16 ^ (row[0] & 7)) << 4);
+            uint8_t* target = tiles + 3 * kPieceBytesA + w_channel * 128 + ((w_unit ^ (w_channel & 7)) << 4);
 #pragma unroll
             for (int j = 0; j < 3; ++j) *reinterpret_cast<uint4*>(target + j * kPieceBytesB) = piece[j];
             fence_async_shared();
@@ -269,7 +283,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
                 sum.z = apply_epilogue(sum.z, a, n, k + 2, p, q);
                 sum.w = apply_epilogue(sum.w, a, n, k + 3, p, q);
             }
-            *reinterpret_cast<float4*>(g.y + static_cast<int64_t>(m) * K + k) = sum;
+            *reinterpret_cast<float4*>(g.y + static_cast<int64_t>(m) * g.y_pixel_stride + k) = sum;
         }
     } else {
         // An infinity or a NaN among this tile's inputs: the same rows on the CUDA cores, every tap multiplied (zero
@@ -279,17 +293,18 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
             const int m = m0 + row;
             if (m >= g.m_total) continue;
             const int q = m % Q, p = (m / Q) % P, n = m / (P * Q);
-            const float* filter = g.w + static_cast<int64_t>(k) * R * S * C;
+            const float* filter = g.w_n_major ? g.w + k : g.w + static_cast<int64_t>(k) * g.w_stride;
+            const int64_t filter_step = g.w_n_major ? g.w_stride : 1;
             float sum = 0.0f;
             for (int r = 0; r < R; ++r)
                 for (int s = 0; s < S; ++s) {
                     const int ih = p - a.pad_h + r, iw = q - a.pad_w + s;
                     const bool inside = ih >= 0 && ih < H && iw >= 0 && iw < W;
-                    const float* pixel = g.x + ((static_cast<int64_t>(n) * H + (inside ? ih : 0)) * W + (inside ? iw : 0)) * C;
-                    const float* tap = filter + (r * S + s) * C;
-                    for (int c = 0; c < C; ++c) sum = fmaf(inside ? __ldg(pixel + c) : 0.0f, __ldg(tap + c), sum);
+                    const float* pixel = g.x + ((static_cast<int64_t>(n) * H + (inside ? ih : 0)) * W + (inside ? iw : 0)) * g.x_pixel_stride;
+                    const float* tap = filter + static_cast<int64_t>(r * S + s) * C * filter_step;
+                    for (int c = 0; c < C; ++c) sum = fmaf(inside ? __ldg(pixel + c) : 0.0f, __ldg(tap + c * filter_step), sum);
                 }
-            g.y[static_cast<int64_t>(m) * K + k] = apply_epilogue(sum, a, n, k, p, q);
+            g.y[static_cast<int64_t>(m) * g.y_pixel_stride + k] = apply_epilogue(sum, a, n, k, p, q);
         }
     }
     if (warp == kLoaders / 32) {
@@ -365,28 +380,14 @@ const ClusterCapacity& cluster_capacity() {
 
 }  // namespace
 
-bool conv_f32_cluster_supported(const dfgpu_conv_params& p) {
-    ClusterForm form;
-    return cluster_form(p, form);
-}
-
-int launch_conv_f32_cluster(const dfgpu_conv_params& p, const ConvArgs& a, void* const* tensors, cudaStream_t stream) {
-    ClusterForm form;
-    if (!cluster_form(p, form)) return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs packed channels-last f32 X, W and Y, C and K multiples of 64, stride 1, dilation 1 and at most 148 output tiles");
-    for (int i = 0; i < 3; ++i)
-        if ((reinterpret_cast<uintptr_t>(tensors[i]) & 15u) != 0) return fail(kInvalidArgument, "CONV_FPROP: the one-launch tcgen05 form needs 16-byte aligned X, W and Y");
+// The launch itself: all tiles' clusters at once, with fewer ranks per tile when the device cannot co-schedule that many
+// clusters of the first size.
+static int launch_clusters(ClusterForm form, ClusterConvArgs g, const ConvArgs& a, const char* what, cudaStream_t stream) {
     const ClusterCapacity& capacity = cluster_capacity();
-    if (capacity.error != cudaSuccess) return fail(kExecutionFailed, "CONV_FPROP: cluster launch set-up failed: %s", cudaGetErrorString(capacity.error));
-    // All tiles' clusters at once: fewer ranks per tile when the device cannot co-schedule that many clusters of the first size.
+    if (capacity.error != cudaSuccess) return fail(kExecutionFailed, "%s: cluster launch set-up failed: %s", what, cudaGetErrorString(capacity.error));
     const int tiles = form.tiles_m * form.tiles_n;
     while (form.ranks > 1 && capacity.clusters[form.ranks] < tiles) share_units(form, form.ranks - 1);
-    if (capacity.clusters[form.ranks] < 1) return fail(kExecutionFailed, "CONV_FPROP: the device cannot run a cluster of %d CTAs with %d bytes of shared memory", form.ranks, kSmemBytes);
-
-    ClusterConvArgs g{};
-    g.x = static_cast<const float*>(tensors[0]);
-    g.w = static_cast<const float*>(tensors[1]);
-    g.y = static_cast<float*>(tensors[2]);
-    g.m_total = static_cast<int>(p.y.dim[0] * p.y.dim[2] * p.y.dim[3]);
+    if (capacity.clusters[form.ranks] < 1) return fail(kExecutionFailed, "%s: the device cannot run a cluster of %d CTAs with %d bytes of shared memory", what, form.ranks, kSmemBytes);
     g.units = form.units;
     g.units_per_rank = form.units_per_rank;
     g.chunks = form.chunks;
@@ -402,8 +403,119 @@ int launch_conv_f32_cluster(const dfgpu_conv_params& p, const ConvArgs& a, void*
     config.attrs = &attribute;
     config.numAttrs = 1;
     cudaError_t error = cudaLaunchKernelEx(&config, umma_conv_f32_kernel, g, a);
-    if (error != cudaSuccess) return fail(kExecutionFailed, "CONV_FPROP: cluster launch failed: %s", cudaGetErrorString(error));
-    return check_launch("CONV_FPROP");
+    if (error != cudaSuccess) return fail(kExecutionFailed, "%s: cluster launch failed: %s", what, cudaGetErrorString(error));
+    return check_launch(what);
+}
+
+bool conv_f32_cluster_supported(const dfgpu_conv_params& p) {
+    ClusterForm form;
+    return cluster_form(p, form);
+}
+
+int launch_conv_f32_cluster(const dfgpu_conv_params& p, const ConvArgs& a, void* const* tensors, cudaStream_t stream) {
+    ClusterForm form;
+    if (!cluster_form(p, form)) return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs packed channels-last f32 X, W and Y, C and K multiples of 64, stride 1, dilation 1 and at most 148 output tiles");
+    for (int i = 0; i < 3; ++i)
+        if ((reinterpret_cast<uintptr_t>(tensors[i]) & 15u) != 0) return fail(kInvalidArgument, "CONV_FPROP: the one-launch tcgen05 form needs 16-byte aligned X, W and Y");
+    ClusterConvArgs g{};
+    g.x = static_cast<const float*>(tensors[0]);
+    g.w = static_cast<const float*>(tensors[1]);
+    g.y = static_cast<float*>(tensors[2]);
+    g.m_total = static_cast<int>(p.y.dim[0] * p.y.dim[2] * p.y.dim[3]);
+    g.x_pixel_stride = p.x.dim[1];
+    g.y_pixel_stride = p.y.dim[1];
+    g.w_stride = p.w.dim[1] * p.w.dim[2] * p.w.dim[3];
+    g.w_n_major = 0;
+    return launch_clusters(form, g, a, "CONV_FPROP", stream);
+}
+
+// ---- MATMUL through the same kernel: C[M, N] = A[M, K] B[K, N] is the 1 x 1 convolution of M pixels with K input and N
+// output channels, B its filter stored either way round ------------------------------------------------------------------
+namespace {
+struct MatmulAsConv {
+    ClusterForm form;
+    int64_t m, n, k, lda, ldb, ldc;
+    bool b_n_major;
+};
+
+bool matmul_cluster_form(const dfgpu_matmul_params& p, MatmulAsConv& f) {
+    if (p.a.dtype != DFGPU_F32 || p.b.dtype != DFGPU_F32 || p.c.dtype != DFGPU_F32 || p.a_scale.rank || p.b_scale.rank) return false;
+    const int rank = p.c.rank;
+    if (rank < 2 || p.a.rank != rank || p.b.rank != rank) return false;
+    for (int i = 0; i < rank - 2; ++i)
+        if (p.c.dim[i] != 1 || p.a.dim[i] != 1 || p.b.dim[i] != 1) return false;
+    f.m = p.c.dim[rank - 2], f.n = p.c.dim[rank - 1], f.k = p.a.dim[rank - 1];
+    f.lda = p.a.stride[rank - 2], f.ldc = p.c.stride[rank - 2];
+    if (f.k % kChunk != 0 || f.n % kTileN != 0 || f.m >= (1ll << 24) || f.m <= 0) return false;
+    if (p.a.stride[rank - 1] != 1 || f.lda % 4 != 0 || f.lda < f.k) return false;
+    if (p.c.stride[rank - 1] != 1 || f.ldc % 4 != 0 || f.ldc < f.n) return false;
+    f.b_n_major = p.b.stride[rank - 1] == 1 && p.b.stride[rank - 2] >= f.n;
+    const bool b_k_major = !f.b_n_major && p.b.stride[rank - 2] == 1 && p.b.stride[rank - 1] % 4 == 0 && p.b.stride[rank - 1] >= f.k;
+    if (!f.b_n_major && !b_k_major) return false;
+    f.ldb = f.b_n_major ? p.b.stride[rank - 2] : p.b.stride[rank - 1];
+    if (f.m * f.lda >= (1ll << 31) || f.k * f.n >= (1ll << 31) || f.ldb * std::max(f.k, f.n) >= (1ll << 31) || f.m * f.ldc >= (1ll << 31)) return false;
+    const int64_t tiles = (f.m + kTileM - 1) / kTileM * (f.n / kTileN), units = f.k / kChunk;
+    constexpr int kSms = 148;
+    if (tiles > kSms || units > kMaxRanks * kMaxUnitsPerRank) return false;
+    f.form.tiles_m = static_cast<int>((f.m + kTileM - 1) / kTileM);
+    f.form.tiles_n = static_cast<int>(f.n / kTileN);
+    f.form.units = f.form.chunks = static_cast<int>(units);
+    share_units(f.form, static_cast<int>(std::min<int64_t>(std::min<int64_t>(kMaxRanks, units), std::max<int64_t>(1, kSms / tiles))));
+    return f.form.units_per_rank <= kMaxUnitsPerRank;
+}
+}  // namespace
+
+bool matmul_f32_cluster_supported(const dfgpu_matmul_params& p) {
+    MatmulAsConv f;
+    return matmul_cluster_form(p, f);
+}
+
+int launch_matmul_f32_cluster(const dfgpu_matmul_params& p, void* const* tensors, cudaStream_t stream) {
+    MatmulAsConv f;
+    if (!matmul_cluster_form(p, f)) return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs unbatched f32 A (K contiguous), B and C (N contiguous), K and N multiples of 64 and at most 148 output tiles");
+    if ((reinterpret_cast<uintptr_t>(tensors[0]) & 15u) != 0 || (reinterpret_cast<uintptr_t>(tensors[2]) & 15u) != 0 ||
+        (!f.b_n_major && (reinterpret_cast<uintptr_t>(tensors[1]) & 15u) != 0))
+        return fail(kInvalidArgument, "MATMUL: the one-launch tcgen05 form needs 16-byte aligned A, B and C");
+    // The convolution's view of the problem: one image of 1 x M pixels; an epilogue operand [.., M, N] becomes [1, N, 1, M].
+    ConvArgs a{};
+    auto image = [](int64_t channels, int64_t pixels, int64_t pixel_stride) {
+        View v{};
+        v.dtype = DFGPU_F32;
+        v.rank = 4;
+        v.dim[0] = 1, v.dim[1] = channels, v.dim[2] = 1, v.dim[3] = pixels;
+        v.stride[0] = pixels * pixel_stride, v.stride[1] = 1, v.stride[2] = pixels * pixel_stride, v.stride[3] = pixel_stride;
+        return v;
+    };
+    a.x = image(f.k, f.m, f.lda);
+    a.y = image(f.n, f.m, f.ldc);
+    a.w = image(f.k, 1, f.k);
+    a.w.dim[0] = f.n;
+    a.epilogue = make_epilogue(p.epilogue_count, p.epilogue);
+    for (int i = 0; i < 2; ++i) {
+        const dfgpu_tensor& t = p.extra[i];
+        View v{};
+        v.dtype = t.dtype;
+        v.rank = 4;
+        for (int d = 0; d < 4; ++d) v.dim[d] = 1;
+        if (t.rank >= 1) v.dim[1] = t.dim[t.rank - 1], v.stride[1] = t.stride[t.rank - 1];
+        if (t.rank >= 2) v.dim[3] = t.dim[t.rank - 2], v.stride[3] = t.stride[t.rank - 2];
+        a.extra[i] = v;
+        a.extra_data[i] = tensors[5 + i];
+    }
+    a.stride_h = a.stride_w = a.dilation_h = a.dilation_w = 1;
+    a.groups = 1;
+    a.c_per_group = f.k;
+    a.k_per_group = f.n;
+    ClusterConvArgs g{};
+    g.x = static_cast<const float*>(tensors[0]);
+    g.w = static_cast<const float*>(tensors[1]);
+    g.y = static_cast<float*>(tensors[2]);
+    g.m_total = static_cast<int>(f.m);
+    g.x_pixel_stride = f.lda;
+    g.y_pixel_stride = f.ldc;
+    g.w_stride = f.ldb;
+    g.w_n_major = f.b_n_major ? 1 : 0;
+    return launch_clusters(f.form, g, a, "MATMUL", stream);
 }
 
 int conv_f32_device_status(int* status) { return read_and_clear_device_status(status); }

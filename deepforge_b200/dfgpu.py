@@ -22,7 +22,7 @@ PW_ADD, PW_RELU_FWD, PW_IDENTITY, PW_MUL, PW_SUB = range(5)
 BSQ_AUTO, BSQ_GENERIC, BSQ_ROW32, BSQ_COL32 = range(4)
 BSD_AUTO, BSD_GENERIC, BSD_PACKED = range(3)
 CONV_AUTO, CONV_DIRECT, CONV_IGEMM_FFMA, CONV_UMMA_BF16, CONV_UMMA_F32X3, CONV_UMMA_F32X3_CLUSTER = range(6)
-MATMUL_AUTO, MATMUL_FFMA, MATMUL_UMMA_BF16, MATMUL_UMMA_MXF8, MATMUL_UMMA_F32X3 = range(5)
+MATMUL_AUTO, MATMUL_FFMA, MATMUL_UMMA_BF16, MATMUL_UMMA_MXF8, MATMUL_UMMA_F32X3, MATMUL_UMMA_F32X3_CLUSTER = range(6)
 MATMUL_FP8_AUTO, MATMUL_FP8_SCALAR, MATMUL_FP8_UMMA = range(3)
 SDPA_AUTO, SDPA_ROWWISE, SDPA_PAGED_DECODE, SDPA_UMMA, SDPA_PAGED_DECODE_UMMA = range(5)
 

@@ -937,7 +937,7 @@ std::uint64_t kernel_alignment(KernelStep const& step, std::size_t slot) {
     switch (step.op) {
         case KernelOp::kConvFprop: return step.kernel == DFGPU_CONV_UMMA_BF16 || step.kernel == DFGPU_CONV_UMMA_F32X3 || step.kernel == DFGPU_CONV_UMMA_F32X3_CLUSTER ? 16 : 0;
         case KernelOp::kMatmul:
-            if (step.kernel != DFGPU_MATMUL_UMMA_BF16 && step.kernel != DFGPU_MATMUL_UMMA_MXF8 && step.kernel != DFGPU_MATMUL_UMMA_F32X3) return 0;
+            if (step.kernel != DFGPU_MATMUL_UMMA_BF16 && step.kernel != DFGPU_MATMUL_UMMA_MXF8 && step.kernel != DFGPU_MATMUL_UMMA_F32X3 && step.kernel != DFGPU_MATMUL_UMMA_F32X3_CLUSTER) return 0;
             return slot == 3 || slot == 4 ? 4 : 16;  // the scale tensors are gathered with 4-byte loads
         case KernelOp::kSdpaForward:
             if (step.kernel == DFGPU_SDPA_UMMA) return slot <= 3 ? 16 : 0;

@@ -208,8 +208,12 @@ int dfgpu_conv_fprop_pair(const dfgpu_conv_pair_params*, void* const* tensors, v
    extra0 or null, extra1 or null}. */
 /* UMMA_F32X3: f32 A, B and C on tcgen05: A and B split into three bf16 pieces each, six bf16 products (2^-24 relative);
    needs scratch, three launches (split, the bf16 matmul over 6K, and the CUDA-core kernel again, which returns at once
-   unless A or B held an infinity or a NaN). */
-enum { DFGPU_MATMUL_AUTO = 0, DFGPU_MATMUL_FFMA = 1, DFGPU_MATMUL_UMMA_BF16 = 2, DFGPU_MATMUL_UMMA_MXF8 = 3, DFGPU_MATMUL_UMMA_F32X3 = 4 };
+   unless A or B held an infinity or a NaN).
+   UMMA_F32X3_CLUSTER: the same six products in ONE launch without scratch, for unbatched products of at most 148 output
+   tiles (128 x 64): the kernel of DFGPU_CONV_UMMA_F32X3_CLUSTER run on the 1 x 1 convolution of M pixels (K and N
+   multiples of 64, B with N or K contiguous). */
+enum { DFGPU_MATMUL_AUTO = 0, DFGPU_MATMUL_FFMA = 1, DFGPU_MATMUL_UMMA_BF16 = 2, DFGPU_MATMUL_UMMA_MXF8 = 3, DFGPU_MATMUL_UMMA_F32X3 = 4,
+       DFGPU_MATMUL_UMMA_F32X3_CLUSTER = 5 };
 typedef struct dfgpu_matmul_params {
     dfgpu_tensor a, b, c;
     dfgpu_tensor a_scale, b_scale;

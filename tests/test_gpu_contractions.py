@@ -377,6 +377,73 @@ def test_matmul_f32_on_tensor_cores(a_dims, b_dims, b_strides):
     assert not np.array_equal(out, cores)  # (the tensor-core result stands: no operand was infinite or NaN)
 
 
+@pytest.mark.parametrize("a_dims,b_dims,b_strides", [([256, 128], [128, 192], None), ([130, 64], [64, 64], None), ([200, 64], [64, 128], [1, 64]),
+                                                    ([512, 512], [512, 256], None), ([1000, 1024], [1024, 64], [1, 1024])])
+def test_matmul_f32_in_one_launch_on_tensor_cores(a_dims, b_dims, b_strides):
+    """An unbatched f32 product of at most 148 output tiles runs on the one-launch tcgen05 kernel of the f32 convolution (as the 1 x 1
+    convolution of M pixels): no scratch, N-contiguous and K-contiguous B, a last row tile that is not full, one to eight CTAs per tile, and
+    a bias row + ReLU + full-size addend in the epilogue. AUTO takes it from 2^23 multiply-adds on."""
+    m, k, n = a_dims[0], a_dims[1], b_dims[1]
+    p = dfgpu.MatmulParams()
+    p.a, p.b, p.c = tensor(F32, a_dims), tensor(F32, b_dims, b_strides), tensor(F32, [m, n])
+    assert dfgpu.query("matmul", p).kernel == (dfgpu.MATMUL_UMMA_F32X3_CLUSTER if m * k * n >= 1 << 23 else dfgpu.MATMUL_FFMA)
+    p.kernel = dfgpu.MATMUL_UMMA_F32X3_CLUSTER
+    info = dfgpu.query("matmul", p)
+    assert info.kernel == dfgpu.MATMUL_UMMA_F32X3_CLUSTER and info.launches == 1 and info.scratch_bytes == 0
+    out, ref = run_matmul(F32, a_dims, b_dims, kernel=dfgpu.MATMUL_UMMA_F32X3_CLUSTER, b_strides=b_strides)
+    check_f32(out, ref)
+    cores, _ = run_matmul(F32, a_dims, b_dims, kernel=dfgpu.MATMUL_FFMA, b_strides=b_strides)
+    assert float(np.max(np.abs(out - cores))) <= 2e-5 * float(np.max(np.abs(ref)))
+    assert not np.array_equal(out, cores)
+    # the epilogue: C = relu(A B + bias[n]) + addend[m, n], against the CUDA-core kernel's
+    bias, addend = synthetic.uniform(8, 1, n, -1.0, 1.0).astype(np.float32), synthetic.normal(8, 2, m * n).astype(np.float32)
+    p.extra[0], p.extra[1] = tensor(F32, [1, n]), tensor(F32, [m, n])
+    p.epilogue_count = 3
+    p.epilogue[0], p.epilogue[1], p.epilogue[2] = step(dfgpu.EPI_ADD, 0), step(dfgpu.EPI_RELU), step(dfgpu.EPI_ADD, 1)
+    da = g.to_device(synthetic.normal(2, 1, m * k).astype(np.float32))
+    db = g.to_device(synthetic.normal(2, 2, k * n).astype(np.float32))
+    d0, d1 = g.to_device(bias), g.to_device(addend)
+    results = {}
+    for kernel in (dfgpu.MATMUL_FFMA, dfgpu.MATMUL_UMMA_F32X3_CLUSTER):
+        p.kernel = kernel
+        dc = g.device_zeros(m * n * 4, 0x5A)
+        dfgpu.matmul(p, g.ptr(da), g.ptr(db), g.ptr(dc), extra0=g.ptr(d0), extra1=g.ptr(d1))
+        results[kernel] = g.to_host(dc, np.float32).copy()
+    plain = np.maximum(ref.reshape(m, n) + bias[None, :], 0.0) + addend.reshape(m, n)
+    check_f32(results[dfgpu.MATMUL_UMMA_F32X3_CLUSTER].reshape(m, n), plain)
+    assert float(np.max(np.abs(results[dfgpu.MATMUL_UMMA_F32X3_CLUSTER] - results[dfgpu.MATMUL_FFMA]))) <= 2e-5 * float(np.max(np.abs(plain)))
+    assert dfgpu.device_status() == 0
+
+
+@pytest.mark.parametrize("b_strides", [None, [1, 128]])
+def test_matmul_f32_one_launch_form_with_non_finite_operand(b_strides):
+    """An infinity in A (rows 0..127 are the first tile) and a NaN in B: a cluster that sees one computes its tile on the CUDA cores, bit
+    for bit the CUDA-core kernel's result; the NaN in B is in every tile's filter."""
+    a_dims, b_dims = [256, 128], [128, 64]
+    for where in ("a", "b"):
+        a = synthetic.normal(4, 1, 256 * 128).astype(np.float32)
+        b = np.full(128 * 64, 0.5, dtype=np.float32)  # (lower pieces of exactly zero: inf * 0 in the split products)
+        if where == "a": a[77] = np.inf
+        else: b[5 * 64 + 9] = np.nan
+        p = dfgpu.MatmulParams()
+        p.a, p.b, p.c = tensor(F32, a_dims), tensor(F32, b_dims, b_strides), tensor(F32, [256, 64])
+        da, db = g.to_device(a), g.to_device(b)
+        results = {}
+        for kernel in (dfgpu.MATMUL_FFMA, dfgpu.MATMUL_UMMA_F32X3_CLUSTER):
+            p.kernel = kernel
+            dc = g.device_zeros(256 * 64 * 4, 0x5A)
+            dfgpu.matmul(p, g.ptr(da), g.ptr(db), g.ptr(dc))
+            results[kernel] = g.to_host(dc, np.uint32).copy().reshape(256, 64)
+        cores, cluster = results[dfgpu.MATMUL_FFMA], results[dfgpu.MATMUL_UMMA_F32X3_CLUSTER]
+        exact_rows = slice(0, 128) if where == "a" else slice(0, 256)
+        assert np.array_equal(cores[exact_rows], cluster[exact_rows])
+        assert not np.all(np.isfinite(cores.view(np.float32)))
+        if where == "a":
+            assert np.all(np.isfinite(cluster[128:].view(np.float32)))
+            assert float(np.max(np.abs(cluster[128:].view(np.float32) - cores[128:].view(np.float32)))) <= 2e-5 * float(np.max(np.abs(cores[128:].view(np.float32))))
+    assert dfgpu.device_status() == 0
+
+
 def test_matmul_f32_split_form_with_non_finite_operand():
     """An infinity in A: the CUDA-core kernel behind the tensor-core one redoes the product, bit for bit its own result."""
     a_dims, b_dims = [128, 64], [64, 64]
