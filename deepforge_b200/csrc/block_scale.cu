@@ -466,23 +466,6 @@ bsq_col32_kernel(const void* __restrict__ x, uint8_t* __restrict__ y, uint8_t* _
 //     tile, taken only where some packed code is 0x80 or some scale code is 0xfe/0xff, which random data almost never has.
 constexpr int kTileThreads = 256;
 
-// n / d for 0 <= n < 2^31 as a multiply and a shift (d >= 1): m = ceil(2^(31+L) / d) with L = ceil(log2 d).
-struct FastDivisor {
-    uint32_t divisor, multiplier, shift;
-};
-
-FastDivisor make_fast_divisor(uint32_t d) {
-    if (d <= 1) return FastDivisor{1, 0, 0};
-    uint32_t log = 0;
-    while ((1ull << log) < d) ++log;
-    const uint64_t power = 1ull << (31 + log);
-    return FastDivisor{d, static_cast<uint32_t>((power + d - 1) / d), log - 1};
-}
-
-__device__ __forceinline__ uint32_t fast_divide(uint32_t n, const FastDivisor& d) {
-    return d.divisor == 1 ? n : __umulhi(n, d.multiplier) >> d.shift;
-}
-
 struct BsqTask {
     const void* x;
     uint8_t* y;

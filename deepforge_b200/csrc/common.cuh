@@ -257,4 +257,21 @@ inline Epilogue make_epilogue(int count, const dfgpu_epilogue_step* steps) {
 int validate_epilogue(int count, const dfgpu_epilogue_step* steps, const dfgpu_tensor* extra,
                       void* const* extra_pointers, const dfgpu_tensor& out, const char* what);
 
+// n / d for 0 <= n < 2^31 as a multiply and a shift (d >= 1): m = ceil(2^(31+L) / d) with L = ceil(log2 d).
+struct FastDivisor {
+    uint32_t divisor, multiplier, shift;
+};
+
+inline FastDivisor make_fast_divisor(uint32_t d) {
+    if (d <= 1) return FastDivisor{1, 0, 0};
+    uint32_t log = 0;
+    while ((1ull << log) < d) ++log;
+    const uint64_t power = 1ull << (31 + log);
+    return FastDivisor{d, static_cast<uint32_t>((power + d - 1) / d), log - 1};
+}
+
+__device__ __forceinline__ uint32_t fast_divide(uint32_t n, const FastDivisor& d) {
+    return d.divisor == 1 ? n : __umulhi(n, d.multiplier) >> d.shift;
+}
+
 }  // namespace dfgpu

@@ -10,9 +10,9 @@
 // (zero rows outside the image) and the f32 filter rows, split them in registers and write the three pieces of each
 // straight into the 128-byte-swizzled shared-memory tiles the tcgen05 descriptors expect, two units in flight; one more
 // warp issues the 24 products of a unit when its tiles are complete. Every rank owns one slice of the tile's rows: at the
-// end a CTA sends each row of its f32 partial tile to the row's owner (stores into the owner's shared memory, which
-// nobody waits for), the cluster synchronises once, and each CTA adds its rows over all ranks in rank order, applies the
-// epilogue and stores Y.
+// end a CTA parks its f32 partial tile in its own shared memory and sends each owner its rows with one bulk copy into the
+// owner's inbox (shared memory to shared memory across the cluster, signalled on the owner's mbarrier); each CTA waits for
+// its inbox to fill, adds its rows over all ranks in rank order, applies the epilogue and stores Y.
 //
 // A product with an infinite or NaN factor does not survive the split, so the loaders also record whether they saw
 // one; the ranks exchange that beside the partial tiles, and a cluster that saw one computes its tile on the CUDA cores
@@ -34,8 +34,10 @@ constexpr int kUnitBytes = 3 * (kPieceBytesA + kPieceBytesB);
 constexpr int kBuffers = 2;
 constexpr int kMaxRanks = 8;
 constexpr int kMaxUnitsPerRank = 6;
-constexpr int kInboxOffset = kBuffers * kUnitBytes;                        // the rows this rank owns, one copy per sending rank
-constexpr int kInboxBytes = (kTileM + kMaxRanks) * kTileN * 4;             // ranks * ceil(128 / ranks) rows at most
+constexpr int kInboxOffset = kBuffers * kUnitBytes;                        // the rows this rank owns, one chunk per sending rank
+constexpr int kRowBytes = kTileN * 4;
+constexpr int kInboxBytes = (kTileM + kMaxRanks) * kRowBytes + kMaxRanks * 16;   // ranks * (ceil(128 / ranks) rows + a 16-byte trailer)
+static_assert(kInboxBytes <= kUnitBytes, "the outgoing chunks are parked in the first operand buffer");
 constexpr int kControlOffset = kInboxOffset + kInboxBytes;
 constexpr int kSmemBytes = kControlOffset + 128 + 1024;                    // (+ the slack that aligns the tiles to 1024 bytes)
 constexpr int kAccumulatorColumns = 64;
@@ -48,7 +50,19 @@ struct ClusterConvArgs {
     int64_t x_pixel_stride, y_pixel_stride;       // floats between pixels (C and K when packed)
     int64_t w_stride;                             // floats between output channels, or (w_n_major) between input channels
     int w_n_major;                                // the filter is stored [C, K] with K contiguous (a MATMUL's row-major B; 1 x 1 only)
+    FastDivisor by_q, by_p, by_chunks, by_s;      // output width and height, chunks, filter width
 };
+
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t cta_address, uint32_t rank) {
+    uint32_t cluster_address;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(cluster_address) : "r"(cta_address), "r"(rank));
+    return cluster_address;
+}
+// `bytes` (a multiple of 16) from this CTA's shared memory into another CTA's, counted on that CTA's mbarrier.
+__device__ __forceinline__ void bulk_copy_to_rank(uint32_t cluster_destination, uint32_t cta_source, uint32_t bytes, uint32_t cluster_barrier) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(cluster_destination), "r"(cta_source), "r"(bytes), "r"(cluster_barrier) : "memory");
+}
 
 // Two consecutive f32 quads as three 16-byte groups of bf16 pieces (high, middle, low); false when a value is infinite or NaN.
 __device__ __forceinline__ bool split_eight(const float4& a, const float4& b, uint4 (&piece)[3]) {
@@ -86,13 +100,13 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
     const int tid = threadIdx.x, warp = uniform_warp_index(), lane = tid & 31;
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t full_bar = smem_base + kControlOffset, empty_bar = full_bar + 8 * kBuffers;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kControlOffset + 16 * kBuffers);
-    int* flags = reinterpret_cast<int*>(smem + kControlOffset + 64);   // one word per rank, written by that rank
+    const uint32_t inbox_bar = empty_bar + 8 * kBuffers;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kControlOffset + 16 * kBuffers + 8);
 
     const int m0 = blockIdx.y * kTileM, n0 = blockIdx.z * kTileN;
     const int first_unit = rank * g.units_per_rank;
     const int my_units = max(0, min(g.units - first_unit, g.units_per_rank));
-    const int P = static_cast<int>(a.y.dim[2]), Q = static_cast<int>(a.y.dim[3]), K = static_cast<int>(a.y.dim[1]);
+    const int P = static_cast<int>(a.y.dim[2]), Q = static_cast<int>(a.y.dim[3]);
     const int H = static_cast<int>(a.x.dim[2]), W = static_cast<int>(a.x.dim[3]), C = static_cast<int>(a.x.dim[1]);
     const int R = static_cast<int>(a.w.dim[2]), S = static_cast<int>(a.w.dim[3]);
 
@@ -107,7 +121,8 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         const int m = m0 + row[i];
         live[i] = m < g.m_total;
         const int mm = live[i] ? m : 0;
-        const int q = mm % Q, p = (mm / Q) % P, n = mm / (P * Q);
+        const int line = static_cast<int>(fast_divide(mm, g.by_q)), q = mm - line * Q;
+        const int n = static_cast<int>(fast_divide(line, g.by_p)), p = line - n * P;
         ih0[i] = p - a.pad_h;
         iw0[i] = q - a.pad_w;
         x_image[i] = g.x + static_cast<int64_t>(n) * H * W * g.x_pixel_stride + unit16 * 8;
@@ -121,8 +136,8 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
     const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     auto fetch = [&](int u, float4 (&xv)[2][2], float4 (&wv)[2]) {
         const int unit = first_unit + u;
-        const int tap = unit / g.chunks, c0 = (unit - tap * g.chunks) * kChunk;
-        const int r = tap / S, s = tap - r * S;
+        const int tap = static_cast<int>(fast_divide(unit, g.by_chunks)), c0 = (unit - tap * g.chunks) * kChunk;
+        const int r = static_cast<int>(fast_divide(tap, g.by_s)), s = tap - r * S;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int ih = ih0[i] + r, iw = iw0[i] + s;
@@ -151,13 +166,15 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
             mbar_init(full_bar + 8 * b, kLoaders);
             mbar_init(empty_bar + 8 * b, 1);
         }
+        mbar_init(inbox_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_expect_tx(inbox_bar, static_cast<uint32_t>(ranks) * (((kTileM + ranks - 1) / ranks) * kRowBytes + 16));   // one chunk from every rank
     }
     if (warp == kLoaders / 32) {
         tmem_alloc(smem_u32(tmem_slot), kAccumulatorColumns);
         tmem_relinquish();
     }
-    cluster.barrier_arrive();   // (waited for before the first store into another CTA's shared memory: every CTA of the cluster runs by then)
+    cluster.barrier_arrive();   // (waited for before the first copy into another CTA's shared memory: its inbox barrier is armed by then)
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -222,9 +239,9 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         }
     }
 
-    // ---- this CTA's partial tile: tensor memory -> the inbox of each row's owner -------------------------------------
+    // ---- this CTA's partial tile: tensor memory -> its own shared memory, one chunk per owner -> the owners' inboxes ---
     const int rows_per_rank = (kTileM + ranks - 1) / ranks;
-    cluster.barrier_wait();
+    const int chunk_bytes = rows_per_rank * kRowBytes + 16;   // an owner's rows, then 16 bytes that say whether the sender met an infinity or a NaN
     if (warp < 8) {
         const int quadrant = warp & 3, half = warp >> 2;   // lanes 32 * quadrant.. of tensor memory, 32 of the 64 columns
         const int row = quadrant * 32 + lane;
@@ -240,32 +257,37 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
             for (int i = 0; i < 32; ++i) r[i] = 0u;
         }
         const int owner = row / rows_per_rank;
-        uint8_t* inbox = cluster.map_shared_rank(smem + kInboxOffset, owner) + (rank * rows_per_rank + row - owner * rows_per_rank) * (kTileN * 4);
+        uint8_t* parked = smem + owner * chunk_bytes + (row - owner * rows_per_rank) * kRowBytes;   // (over the first operand buffer: every product is done)
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<uint4*>(inbox + (((half * 8 + j) ^ (row & 7)) << 4)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            *reinterpret_cast<uint4*>(parked + (((half * 8 + j) ^ (row & 7)) << 4)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
     }
     const int unsplittable = __syncthreads_or(finite ? 0 : 1);
-    if (tid < ranks) *cluster.map_shared_rank(flags + rank, tid) = unsplittable;
-    cluster.sync();   // (the last access to another CTA's shared memory is behind this point: a CTA may leave when it is done)
+    if (tid < ranks) *reinterpret_cast<uint4*>(smem + tid * chunk_bytes + rows_per_rank * kRowBytes) = make_uint4(static_cast<uint32_t>(unsplittable), 0u, 0u, 0u);
+    fence_async_shared();
+    __syncthreads();
+    cluster.barrier_wait();
+    if (tid < ranks)
+        bulk_copy_to_rank(map_to_rank(smem_base + kInboxOffset + rank * chunk_bytes, tid), smem_base + tid * chunk_bytes, chunk_bytes, map_to_rank(inbox_bar, tid));
+    ok = mbar_wait(inbox_bar, 0, 134) && ok;
+    cluster.barrier_arrive();   // (waited for before leaving: a CTA whose inbox is full has been read by every copy aimed at it, so when all have arrived no copy still reads any CTA's shared memory)
 
     // ---- this rank's rows: the sum over all ranks' partial tiles, the epilogue, Y --------------------------------------
+    const uint8_t* inbox = smem + kInboxOffset;
     int any_unsplittable = 0;
 #pragma unroll
-    for (int z = 0; z < kMaxRanks; ++z) any_unsplittable |= z < ranks ? flags[z] : 0;
+    for (int z = 0; z < kMaxRanks; ++z) any_unsplittable |= z < ranks ? *reinterpret_cast<const int*>(inbox + z * chunk_bytes + rows_per_rank * kRowBytes) : 0;
     const int row_begin = rank * rows_per_rank, row_end = min(kTileM, row_begin + rows_per_rank);
     if (!any_unsplittable) {
-        const uint8_t* inbox = smem + kInboxOffset;
-        const int sender_stride = rows_per_rank * (kTileN * 4);
         for (int item = tid; item < (row_end - row_begin) * 16; item += kThreads) {
             const int row = row_begin + (item >> 4), unit = item & 15;
             const int m = m0 + row;
             if (m >= g.m_total) continue;
-            const int offset = (row - row_begin) * (kTileN * 4) + ((unit ^ (row & 7)) << 4);
+            const int offset = (row - row_begin) * kRowBytes + ((unit ^ (row & 7)) << 4);
             float4 part[kMaxRanks];
 #pragma unroll
             for (int z = 0; z < kMaxRanks; ++z)   // every load in flight before the first sum
-                part[z] = z < ranks ? *reinterpret_cast<const float4*>(inbox + z * sender_stride + offset) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                part[z] = z < ranks ? *reinterpret_cast<const float4*>(inbox + z * chunk_bytes + offset) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             float4 sum = part[0];
 #pragma unroll
             for (int z = 1; z < kMaxRanks; ++z) {
@@ -277,7 +299,8 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
             }
             const int k = n0 + unit * 4;
             if (a.epilogue.count > 0) {
-                const int q = m % Q, p = (m / Q) % P, n = m / (P * Q);
+                const int line = static_cast<int>(fast_divide(m, g.by_q)), q = m - line * Q;
+                const int n = static_cast<int>(fast_divide(line, g.by_p)), p = line - n * P;
                 sum.x = apply_epilogue(sum.x, a, n, k, p, q);
                 sum.y = apply_epilogue(sum.y, a, n, k + 1, p, q);
                 sum.z = apply_epilogue(sum.z, a, n, k + 2, p, q);
@@ -307,6 +330,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
             g.y[static_cast<int64_t>(m) * g.y_pixel_stride + k] = apply_epilogue(sum, a, n, k, p, q);
         }
     }
+    cluster.barrier_wait();
     if (warp == kLoaders / 32) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kAccumulatorColumns);
@@ -391,6 +415,10 @@ static int launch_clusters(ClusterForm form, ClusterConvArgs g, const ConvArgs& 
     g.units = form.units;
     g.units_per_rank = form.units_per_rank;
     g.chunks = form.chunks;
+    g.by_q = make_fast_divisor(static_cast<uint32_t>(a.y.dim[3]));
+    g.by_p = make_fast_divisor(static_cast<uint32_t>(a.y.dim[2]));
+    g.by_chunks = make_fast_divisor(static_cast<uint32_t>(form.chunks));
+    g.by_s = make_fast_divisor(static_cast<uint32_t>(a.w.dim[3]));
     cudaLaunchConfig_t config{};
     config.gridDim = dim3(form.ranks, form.tiles_m, form.tiles_n);
     config.blockDim = dim3(kThreads);
