@@ -64,32 +64,44 @@ __device__ __forceinline__ void bulk_copy_to_rank(uint32_t cluster_destination, 
                  ::"r"(cluster_destination), "r"(cta_source), "r"(bytes), "r"(cluster_barrier) : "memory");
 }
 
+__device__ __forceinline__ uint64_t pair_of(uint32_t first, uint32_t second) {
+    uint64_t pair;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(pair) : "r"(first), "r"(second));
+    return pair;
+}
+__device__ __forceinline__ uint64_t add_pairs(uint64_t a, uint64_t b) {   // two f32 additions in one instruction
+    uint64_t sum;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(sum) : "l"(a), "l"(b));
+    return sum;
+}
+__device__ __forceinline__ void halves_of(uint64_t pair, uint32_t& first, uint32_t& second) {
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(first), "=r"(second) : "l"(pair));
+}
+// The leading bf16 of an f32 bit pattern (cut off, not rounded), negated: what to add to take it away.
+__device__ __forceinline__ uint32_t minus_leading_bf16(uint32_t bits) { return (bits & 0xffff0000u) ^ 0x80000000u; }
+
 // Two consecutive f32 quads as three 16-byte groups of bf16 pieces (high, middle, low); false when a value is infinite or NaN.
 __device__ __forceinline__ bool split_eight(const float4& a, const float4& b, uint4 (&piece)[3]) {
     const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    uint32_t high[8], middle[8], low[8];
+    uint32_t h[4], m[4], l[4];
     bool finite = true;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        high[i] = __float_as_uint(v[i]);
-        finite = finite && (high[i] & 0x7f800000u) != 0x7f800000u;
-        const float rest = v[i] - __uint_as_float(high[i] & 0xffff0000u);
-        middle[i] = __float_as_uint(rest);
-        low[i] = __float_as_uint(rest - __uint_as_float(middle[i] & 0xffff0000u));   // (at most 8 significant bits are left)
-    }
-    uint32_t h[4], m[4], l[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {   // the upper halves of two words side by side
-        h[i] = __byte_perm(high[2 * i], high[2 * i + 1], 0x7632);
-        m[i] = __byte_perm(middle[2 * i], middle[2 * i + 1], 0x7632);
-        l[i] = __byte_perm(low[2 * i], low[2 * i + 1], 0x7632);
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t v0 = __float_as_uint(v[2 * i]), v1 = __float_as_uint(v[2 * i + 1]);
+        finite = finite && fabsf(v[2 * i]) <= 3.4028234663852886e38f && fabsf(v[2 * i + 1]) <= 3.4028234663852886e38f;
+        uint32_t r0, r1, l0, l1;
+        const uint64_t rest = add_pairs(pair_of(v0, v1), pair_of(minus_leading_bf16(v0), minus_leading_bf16(v1)));   // (exact)
+        halves_of(rest, r0, r1);
+        halves_of(add_pairs(rest, pair_of(minus_leading_bf16(r0), minus_leading_bf16(r1))), l0, l1);   // (at most 8 significant bits are left)
+        h[i] = __byte_perm(v0, v1, 0x7632);   // the upper halves of two words side by side
+        m[i] = __byte_perm(r0, r1, 0x7632);
+        l[i] = __byte_perm(l0, l1, 0x7632);
     }
     piece[0] = make_uint4(h[0], h[1], h[2], h[3]);
     piece[1] = make_uint4(m[0], m[1], m[2], m[3]);
     piece[2] = make_uint4(l[0], l[1], l[2], l[3]);
     return finite;
 }
-
 
 __global__ void __launch_bounds__(kThreads, 1)
 umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_constant__ ConvArgs a) {
@@ -175,10 +187,13 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         tmem_relinquish();
     }
     cluster.barrier_arrive();   // (waited for before the first copy into another CTA's shared memory: its inbox barrier is armed by then)
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
+    // The CTA meets once, for the barriers and the tensor memory address: the loaders after they have written their first
+    // unit (that needs neither), the issuing warp at once.
+    auto meet = [&] {
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+    };
 
     bool ok = true, finite = true;
     if (tid < kLoaders) {
@@ -203,6 +218,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
 #pragma unroll
             for (int j = 0; j < 3; ++j) *reinterpret_cast<uint4*>(target + j * kPieceBytesB) = piece[j];
             fence_async_shared();
+            if (u == 0) meet();
             mbar_arrive(full_bar + 8 * buffer);
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
@@ -211,10 +227,12 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
                 wv[i] = wn[i];
             }
         }
+        if (my_units == 0) meet();
     } else {
         // ---- issuing warp: the 24 products of every unit --------------------------------------------------------------
         const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kTileN >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
-        const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+        meet();
+        const uint32_t tmem_u = __shfl_sync(0xffffffffu, *tmem_slot, 0);
 #pragma unroll 1
         for (int u = 0; u < my_units; ++u) {
             const int buffer = u & 1;
@@ -249,7 +267,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         if (my_units > 0) {
             ok = mbar_wait(empty_bar + 8 * ((my_units - 1) & 1), ((my_units - 1) >> 1) & 1, 133) && ok;   // the last commit covers every product
             tc_fence_after();
-            tmem_load_32(tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) + half * 32, r);
+            tmem_load_32(*tmem_slot + (static_cast<uint32_t>(quadrant * 32) << 16) + half * 32, r);
             tmem_load_wait();
             tc_fence_before();
         } else {
@@ -270,7 +288,10 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
     if (tid < ranks)
         bulk_copy_to_rank(map_to_rank(smem_base + kInboxOffset + rank * chunk_bytes, tid), smem_base + tid * chunk_bytes, chunk_bytes, map_to_rank(inbox_bar, tid));
     ok = mbar_wait(inbox_bar, 0, 134) && ok;
-    cluster.barrier_arrive();   // (waited for before leaving: a CTA whose inbox is full has been read by every copy aimed at it, so when all have arrived no copy still reads any CTA's shared memory)
+    // Waited for before leaving: a CTA whose inbox is full has been read by every copy aimed at it, so when all have arrived
+    // no copy still reads any CTA's shared memory. (Relaxed: nothing is published with it, and the releasing form waits
+    // more than a thousand cycles here.)
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
     // ---- this rank's rows: the sum over all ranks' partial tiles, the epilogue, Y --------------------------------------
     const uint8_t* inbox = smem + kInboxOffset;
@@ -330,10 +351,10 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
             g.y[static_cast<int64_t>(m) * g.y_pixel_stride + k] = apply_epilogue(sum, a, n, k, p, q);
         }
     }
-    cluster.barrier_wait();
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
     if (warp == kLoaders / 32) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, kAccumulatorColumns);
+        tmem_dealloc(*tmem_slot, kAccumulatorColumns);
     }
 }
 
