@@ -527,6 +527,7 @@ def measure(name: str, steps: int, warmup: int, torch, device, distributed: bool
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each configuration's dominant kernel, from the ncu
 # captures summarised under profiles/ (keyed by configuration number and launch label).
 NCU_TRAFFIC_BYTES = {
+    (1, "conv_fprop"): 1.01e6,         # profiles/umma_conv_f32_kernel_c1_f32_conv.md (the output stays in L2 inside the capture)
     (2, "conv2+bias2+relu2>conv3+residual"): 91.3e6,  # profiles/umma_conv_pair_kernel_c2_bottleneck.md
     (3, "dequantize_b+dequantize_a+matmul"): 35.6e6,  # profiles/umma_mxf8_and_bsq_kernels_c3_quantize_matmul.md
     (4, "sdpa"): 511.2e6,              # profiles/sdpa_umma_pair_kernel_c4_sdpa.md
