@@ -83,6 +83,20 @@ def test_c2_bottleneck_small(io, options):
         check_bf16(s.output(7), ref[7])
 
 
+def test_c2_bottleneck_float_on_tensor_cores():
+    """An all-FLOAT bottleneck big enough for the tensor cores (N = 8, 28 x 28): conv1 and conv2 have 49 output tiles and run as one
+    cluster launch each (bias and ReLU in its epilogue), conv3 has 196 and runs as the three-launch split form (residual in the adder);
+    the f32 gates hold against the oracle."""
+    wl = workloads.c2(n=8, h=28, w=28, io="FLOAT")
+    s = harness.Session(wl)
+    plan = s.exe.plan_text()
+    assert plan.count("conv_fprop kernel=5 launches=1") == 2 and plan.count("conv_fprop kernel=4 launches=3") == 1 and s.exe.launch_count == 5
+    s.run()
+    ins, _ = oracle_inputs(wl, s)
+    check_f32(s.output(7), graph_oracle.run(wl.document, ins, threads=THREADS)[7])
+    assert dfgpu.device_status() == 0
+
+
 @pytest.mark.parametrize("options", [0, runtime.NO_CONV_PAIRS])
 @pytest.mark.parametrize("shape", [dict(n=1, h=7, w=7), dict(n=3, h=28, w=28), dict(n=2, h=9, w=11), dict(n=1, h=8, w=120), dict(n=5, h=56, w=56, c_in=128)])
 def test_c2_bottleneck_other_geometries(shape, options):
