@@ -420,7 +420,7 @@ int choose_kernel(const dfgpu_conv_params& p, const ConvArgs& a, int& kernel) {
     const int64_t macs = p.y.dim[0] * p.y.dim[2] * p.y.dim[3] * p.y.dim[1] * p.w.dim[1] * p.w.dim[2] * p.w.dim[3];
     if (split_ok && macs >= kSplitFormMinMacs) automatic = DFGPU_CONV_UMMA_F32X3;
     const bool cluster_ok = conv_f32_cluster_supported(p);
-    if (cluster_ok && macs >= kClusterFormMinMacs) automatic = DFGPU_CONV_UMMA_F32X3_CLUSTER;   // (few tiles: one launch beats three)
+    if (cluster_ok && p.w.dim[1] * p.w.dim[2] * p.w.dim[3] >= kClusterFormMinDepth) automatic = DFGPU_CONV_UMMA_F32X3_CLUSTER;   // (few tiles: one launch beats three)
     kernel = p.kernel == DFGPU_CONV_AUTO ? automatic : p.kernel;
     if (kernel == DFGPU_CONV_UMMA_F32X3 && !split_ok)
         return fail(kUnsupported, "CONV_FPROP: the split-operand tcgen05 form needs packed channels-last f32 X, W and Y, C and K multiples of 64, stride 1, dilation 1");

@@ -259,7 +259,7 @@ int choose_kernel(const dfgpu_matmul_params& p, int& kernel) {
     else {
         const int64_t macs = p.c.dim[p.c.rank - 2] * p.c.dim[p.c.rank - 1] * p.a.dim[p.a.rank - 1];
         if (split_ok && macs >= kSplitFormMinMacs) automatic = DFGPU_MATMUL_UMMA_F32X3;  // (three launches: big products only)
-        if (macs >= kClusterFormMinMacs && matmul_f32_cluster_supported(p)) automatic = DFGPU_MATMUL_UMMA_F32X3_CLUSTER;  // (few tiles: one launch)
+        if (p.a.dim[p.a.rank - 1] >= kClusterFormMinDepth && matmul_f32_cluster_supported(p)) automatic = DFGPU_MATMUL_UMMA_F32X3_CLUSTER;  // (few tiles: one launch)
     }
     kernel = p.kernel == DFGPU_MATMUL_AUTO ? automatic : p.kernel;
     if (kernel < DFGPU_MATMUL_FFMA || kernel > DFGPU_MATMUL_UMMA_F32X3_CLUSTER) return fail(kInvalidArgument, "MATMUL: unknown kernel id %d", kernel);

@@ -41,7 +41,7 @@ int conv_f32_device_status(int* status);
 // The same kernel for an unbatched f32 MATMUL of at most 148 output tiles (the 1 x 1 convolution of M pixels; B with N or K contiguous).
 bool matmul_f32_cluster_supported(const dfgpu_matmul_params& p);
 int launch_matmul_f32_cluster(const dfgpu_matmul_params& p, void* const* tensors, cudaStream_t stream);
-constexpr int64_t kClusterFormMinMacs = int64_t{1} << 23;  // AUTO takes the one-launch form from this many multiply-adds on
+constexpr int64_t kClusterFormMinDepth = 128;  // AUTO takes the one-launch form from this reduction depth (C R S, or K) on: the CUDA-core kernels walk the depth 16 at a time at ~0.8 us a step, the cluster launch costs 7-9 us whatever the depth
 
 // A wide-filter convolution and the 1 x 1 convolution that consumes it, in one persistent kernel (the intermediate
 // stays on the SM). tensors: {X, W first, W second, Y, first.extra0, first.extra1, second.extra0, second.extra1}.

@@ -19,6 +19,8 @@
 // instead (zero padding still multiplied, as the reference's single-node path does).
 #include <cooperative_groups.h>
 
+#include <mutex>
+
 #include "conv_args.cuh"
 #include "umma_ptx.cuh"
 
@@ -401,9 +403,19 @@ struct ClusterCapacity {
     cudaError_t error;
 };
 
+// Worked out once per device (the shared-memory attribute of the kernel is a per-device setting too).
+constexpr int kMaxDevices = 64;
 const ClusterCapacity& cluster_capacity() {
-    static const ClusterCapacity capacity = [] {
-        ClusterCapacity c{};
+    static ClusterCapacity table[kMaxDevices];
+    static std::once_flag once[kMaxDevices];
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {
+        static const ClusterCapacity unknown = [] { ClusterCapacity c{}; c.error = cudaErrorInvalidDevice; return c; }();
+        return unknown;
+    }
+    std::call_once(once[device], [device] {
+        ClusterCapacity& c = table[device];
+        c = ClusterCapacity{};
         c.error = cudaFuncSetAttribute(umma_conv_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         for (int ranks = 1; ranks <= kMaxRanks && c.error == cudaSuccess; ++ranks) {
             cudaLaunchConfig_t config{};
@@ -418,9 +430,8 @@ const ClusterCapacity& cluster_capacity() {
             config.numAttrs = 1;
             c.error = cudaOccupancyMaxActiveClusters(&c.clusters[ranks], umma_conv_f32_kernel, &config);
         }
-        return c;
-    }();
-    return capacity;
+    });
+    return table[device];
 }
 
 }  // namespace

@@ -365,8 +365,9 @@ def test_matmul_f32_on_tensor_cores(a_dims, b_dims, b_strides):
     against the oracle, for N-contiguous and K-contiguous B and a last row tile that is not full."""
     p = dfgpu.MatmulParams()
     p.a, p.b, p.c = tensor(F32, a_dims), tensor(F32, b_dims, b_strides), tensor(F32, [a_dims[0], b_dims[1]])
-    big = a_dims[0] * a_dims[1] * b_dims[1] >= 1 << 24  # AUTO takes the three-launch form for big products only
-    assert dfgpu.query("matmul", p).kernel == (dfgpu.MATMUL_UMMA_F32X3 if big else dfgpu.MATMUL_FFMA)
+    # AUTO: the one-launch form where it fits (K and N multiples of 64, K >= 128, few tiles), the three-launch form for big products, else CUDA cores
+    expected = {(256, 128): dfgpu.MATMUL_UMMA_F32X3_CLUSTER, (1024, 1024): dfgpu.MATMUL_UMMA_F32X3}.get((a_dims[0], a_dims[1]), dfgpu.MATMUL_FFMA)
+    assert dfgpu.query("matmul", p).kernel == expected
     p.kernel = dfgpu.MATMUL_UMMA_F32X3
     info = dfgpu.query("matmul", p)
     assert info.kernel == dfgpu.MATMUL_UMMA_F32X3 and info.launches == 3 and info.scratch_bytes > 0
@@ -382,11 +383,11 @@ def test_matmul_f32_on_tensor_cores(a_dims, b_dims, b_strides):
 def test_matmul_f32_in_one_launch_on_tensor_cores(a_dims, b_dims, b_strides):
     """An unbatched f32 product of at most 148 output tiles runs on the one-launch tcgen05 kernel of the f32 convolution (as the 1 x 1
     convolution of M pixels): no scratch, N-contiguous and K-contiguous B, a last row tile that is not full, one to eight CTAs per tile, and
-    a bias row + ReLU + full-size addend in the epilogue. AUTO takes it from 2^23 multiply-adds on."""
+    a bias row + ReLU + full-size addend in the epilogue. AUTO takes it from K = 128 on (the CUDA-core kernel walks K in steps of 16)."""
     m, k, n = a_dims[0], a_dims[1], b_dims[1]
     p = dfgpu.MatmulParams()
     p.a, p.b, p.c = tensor(F32, a_dims), tensor(F32, b_dims, b_strides), tensor(F32, [m, n])
-    assert dfgpu.query("matmul", p).kernel == (dfgpu.MATMUL_UMMA_F32X3_CLUSTER if m * k * n >= 1 << 23 else dfgpu.MATMUL_FFMA)
+    assert dfgpu.query("matmul", p).kernel == (dfgpu.MATMUL_UMMA_F32X3_CLUSTER if k >= 128 else dfgpu.MATMUL_FFMA)
     p.kernel = dfgpu.MATMUL_UMMA_F32X3_CLUSTER
     info = dfgpu.query("matmul", p)
     assert info.kernel == dfgpu.MATMUL_UMMA_F32X3_CLUSTER and info.launches == 1 and info.scratch_bytes == 0

@@ -151,11 +151,12 @@ def test_bottleneck_plan_fuses_to_three_launches_and_shares_workspace():
     unfused = runtime.compile_graph(graphs.c2_bottleneck(n=2, h=8, w=8), options=runtime.NO_FUSION)
     assert unfused.launch_count == 8
     f32 = runtime.compile_graph(graphs.c2_bottleneck(n=2, h=8, w=8, io="FLOAT"))
-    # an all-FLOAT graph this small stays on CUDA cores (one launch per convolution beats three)
-    assert f32.plan_text().count("kernel=2") == 3 and f32.workspace_size == 2 * (2 * 8 * 8 * 64 * 4)
-    # a bigger one runs on tcgen05 too, as six bf16 products of three-piece operands. With at most 148 output tiles (128 pixels x 64
-    # channels) a convolution is ONE launch without scratch (a thread-block cluster per tile); with more tiles, from 2^24 multiply-adds on,
-    # it is three launches (split, convolution, the guarded CUDA-core pass) and needs scratch for the split copies
+    # an all-FLOAT graph: convolutions of at most 148 output tiles with a reduction depth of 128 or more (conv1: 256, conv2: 576) run on
+    # tcgen05 in one cluster launch each, conv3 (depth 64) on CUDA cores; no scratch either way
+    assert f32.plan_text().count("conv_fprop kernel=5 launches=1") == 2 and f32.plan_text().count("kernel=2") == 1
+    assert f32.launch_count == 3 and f32.workspace_size == 2 * (2 * 8 * 8 * 64 * 4)
+    # with more than 148 output tiles (128 pixels x 64 channels), from 2^24 multiply-adds on, a convolution is three launches (split,
+    # convolution over six-piece operands, the guarded CUDA-core pass) and needs scratch for the split copies
     medium = runtime.compile_graph(graphs.c2_bottleneck(n=8, h=28, w=28, io="FLOAT"))   # 49 pixel tiles: conv3 (256 channels) has 196
     assert medium.plan_text().count("conv_fprop kernel=5 launches=1") == 2 and medium.plan_text().count("conv_fprop kernel=4 launches=3") == 1
     assert medium.launch_count == 5 and medium.plan_text().count("scratch=ws+") == 1
