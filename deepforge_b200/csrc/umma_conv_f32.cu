@@ -14,6 +14,9 @@
 // owner's inbox (shared memory to shared memory across the cluster, signalled on the owner's mbarrier); each CTA waits for
 // its inbox to fill, adds its rows over all ranks in rank order, applies the epilogue and stores Y.
 //
+// Input channels need only be a multiple of 8 and output channels of 4: a unit's missing channels and a tile's missing
+// filter rows are written as zeros.
+//
 // A product with an infinite or NaN factor does not survive the split, so the loaders also record whether they saw
 // one; the ranks exchange that beside the partial tiles, and a cluster that saw one computes its tile on the CUDA cores
 // instead (zero padding still multiplied, as the reference's single-node path does).
@@ -120,7 +123,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
     const int m0 = blockIdx.y * kTileM, n0 = blockIdx.z * kTileN;
     const int first_unit = rank * g.units_per_rank;
     const int my_units = max(0, min(g.units - first_unit, g.units_per_rank));
-    const int P = static_cast<int>(a.y.dim[2]), Q = static_cast<int>(a.y.dim[3]);
+    const int P = static_cast<int>(a.y.dim[2]), Q = static_cast<int>(a.y.dim[3]), K = static_cast<int>(a.y.dim[1]);
     const int H = static_cast<int>(a.x.dim[2]), W = static_cast<int>(a.x.dim[3]), C = static_cast<int>(a.x.dim[1]);
     const int R = static_cast<int>(a.w.dim[2]), S = static_cast<int>(a.w.dim[3]);
 
@@ -156,13 +159,16 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         for (int i = 0; i < 2; ++i) {
             const int ih = ih0[i] + r, iw = iw0[i] + s;
             xv[i][0] = xv[i][1] = zero;
-            if (live[i] && ih >= 0 && ih < H && iw >= 0 && iw < W) {
+            if (live[i] && ih >= 0 && ih < H && iw >= 0 && iw < W && c0 + unit16 * 8 < C) {   // (channels come in whole groups of 8)
                 const float4* source = reinterpret_cast<const float4*>(x_image[i] + (static_cast<int64_t>(ih) * W + iw) * g.x_pixel_stride + c0);
                 xv[i][0] = __ldg(source);
                 xv[i][1] = __ldg(source + 1);
             }
         }
-        if (g.w_n_major) {
+        wv[0] = wv[1] = zero;
+        if (n0 + w_channel >= K || c0 + w_unit * 8 >= C) {
+            // (a filter row or a channel group past the end: zeros, which add nothing)
+        } else if (g.w_n_major) {
             const float* source = w_row + static_cast<int64_t>(c0) * g.w_stride;
             wv[0] = make_float4(__ldg(source), __ldg(source + g.w_stride), __ldg(source + 2 * g.w_stride), __ldg(source + 3 * g.w_stride));
             wv[1] = make_float4(__ldg(source + 4 * g.w_stride), __ldg(source + 5 * g.w_stride), __ldg(source + 6 * g.w_stride), __ldg(source + 7 * g.w_stride));
@@ -321,6 +327,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
                 sum.w = __fadd_rn(sum.w, part[z].w);
             }
             const int k = n0 + unit * 4;
+            if (k >= K) continue;   // (output channels come in whole groups of 4)
             if (a.epilogue.count > 0) {
                 const int line = static_cast<int>(fast_divide(m, g.by_q)), q = m - line * Q;
                 const int n = static_cast<int>(fast_divide(line, g.by_p)), p = line - n * P;
@@ -337,7 +344,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         for (int item = tid; item < (row_end - row_begin) * kTileN; item += kThreads) {
             const int row = row_begin + item / kTileN, k = n0 + item % kTileN;
             const int m = m0 + row;
-            if (m >= g.m_total) continue;
+            if (m >= g.m_total || k >= K) continue;
             const int q = m % Q, p = (m / Q) % P, n = m / (P * Q);
             const float* filter = g.w_n_major ? g.w + k : g.w + static_cast<int64_t>(k) * g.w_stride;
             const int64_t filter_step = g.w_n_major ? g.w_stride : 1;
@@ -380,19 +387,20 @@ bool cluster_form(const dfgpu_conv_params& p, ClusterForm& form) {
         return t.stride[1] == 1 && t.stride[3] == t.dim[1] && t.stride[2] == t.dim[3] * t.dim[1] && t.stride[0] == t.dim[2] * t.dim[3] * t.dim[1];
     };
     if (!packed(p.x) || !packed(p.w) || !packed(p.y)) return false;
-    if (p.x.dim[1] != p.w.dim[1] || p.x.dim[1] % kChunk != 0 || p.y.dim[1] % kTileN != 0 || p.w.dim[0] != p.y.dim[1]) return false;
+    if (p.x.dim[1] != p.w.dim[1] || p.x.dim[1] % 8 != 0 || p.y.dim[1] % 4 != 0 || p.w.dim[0] != p.y.dim[1]) return false;
     for (int axis = 0; axis < 2; ++axis)
         if (p.stride[axis] != 1 || p.dilation[axis] != 1) return false;
     if (element_count(p.x) >= (1ll << 31) || element_count(p.w) >= (1ll << 31) || element_count(p.y) >= (1ll << 31)) return false;
     const int64_t m_total = p.y.dim[0] * p.y.dim[2] * p.y.dim[3];
-    const int64_t tiles = (m_total + kTileM - 1) / kTileM * (p.y.dim[1] / kTileN);
-    const int64_t units = p.w.dim[2] * p.w.dim[3] * (p.x.dim[1] / kChunk);
+    const int64_t chunks = (p.x.dim[1] + kChunk - 1) / kChunk, tiles_n = (p.y.dim[1] + kTileN - 1) / kTileN;
+    const int64_t tiles = (m_total + kTileM - 1) / kTileM * tiles_n;
+    const int64_t units = p.w.dim[2] * p.w.dim[3] * chunks;
     constexpr int kSms = 148;   // (a query has no device: the count this library is built for)
     if (tiles > kSms || units > kMaxRanks * kMaxUnitsPerRank) return false;
     form.tiles_m = static_cast<int>((m_total + kTileM - 1) / kTileM);
-    form.tiles_n = static_cast<int>(p.y.dim[1] / kTileN);
+    form.tiles_n = static_cast<int>(tiles_n);
     form.units = static_cast<int>(units);
-    form.chunks = static_cast<int>(p.x.dim[1] / kChunk);
+    form.chunks = static_cast<int>(chunks);
     share_units(form, static_cast<int>(std::min<int64_t>(std::min<int64_t>(kMaxRanks, units), std::max<int64_t>(1, kSms / tiles))));
     return form.units_per_rank <= kMaxUnitsPerRank;
 }
@@ -474,7 +482,7 @@ bool conv_f32_cluster_supported(const dfgpu_conv_params& p) {
 
 int launch_conv_f32_cluster(const dfgpu_conv_params& p, const ConvArgs& a, void* const* tensors, cudaStream_t stream) {
     ClusterForm form;
-    if (!cluster_form(p, form)) return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs packed channels-last f32 X, W and Y, C and K multiples of 64, stride 1, dilation 1 and at most 148 output tiles");
+    if (!cluster_form(p, form)) return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs packed channels-last f32 X, W and Y, C a multiple of 8 and K of 4, stride 1, dilation 1 and at most 148 output tiles");
     for (int i = 0; i < 3; ++i)
         if ((reinterpret_cast<uintptr_t>(tensors[i]) & 15u) != 0) return fail(kInvalidArgument, "CONV_FPROP: the one-launch tcgen05 form needs 16-byte aligned X, W and Y");
     ClusterConvArgs g{};
@@ -506,7 +514,7 @@ bool matmul_cluster_form(const dfgpu_matmul_params& p, MatmulAsConv& f) {
         if (p.c.dim[i] != 1 || p.a.dim[i] != 1 || p.b.dim[i] != 1) return false;
     f.m = p.c.dim[rank - 2], f.n = p.c.dim[rank - 1], f.k = p.a.dim[rank - 1];
     f.lda = p.a.stride[rank - 2], f.ldc = p.c.stride[rank - 2];
-    if (f.k % kChunk != 0 || f.n % kTileN != 0 || f.m >= (1ll << 24) || f.m <= 0) return false;
+    if (f.k % 8 != 0 || f.n % 4 != 0 || f.m >= (1ll << 24) || f.m <= 0) return false;
     if (p.a.stride[rank - 1] != 1 || f.lda % 4 != 0 || f.lda < f.k) return false;
     if (p.c.stride[rank - 1] != 1 || f.ldc % 4 != 0 || f.ldc < f.n) return false;
     f.b_n_major = p.b.stride[rank - 1] == 1 && p.b.stride[rank - 2] >= f.n;
@@ -514,11 +522,12 @@ bool matmul_cluster_form(const dfgpu_matmul_params& p, MatmulAsConv& f) {
     if (!f.b_n_major && !b_k_major) return false;
     f.ldb = f.b_n_major ? p.b.stride[rank - 2] : p.b.stride[rank - 1];
     if (f.m * f.lda >= (1ll << 31) || f.k * f.n >= (1ll << 31) || f.ldb * std::max(f.k, f.n) >= (1ll << 31) || f.m * f.ldc >= (1ll << 31)) return false;
-    const int64_t tiles = (f.m + kTileM - 1) / kTileM * (f.n / kTileN), units = f.k / kChunk;
+    const int64_t tiles_n = (f.n + kTileN - 1) / kTileN, units = (f.k + kChunk - 1) / kChunk;
+    const int64_t tiles = (f.m + kTileM - 1) / kTileM * tiles_n;
     constexpr int kSms = 148;
     if (tiles > kSms || units > kMaxRanks * kMaxUnitsPerRank) return false;
     f.form.tiles_m = static_cast<int>((f.m + kTileM - 1) / kTileM);
-    f.form.tiles_n = static_cast<int>(f.n / kTileN);
+    f.form.tiles_n = static_cast<int>(tiles_n);
     f.form.units = f.form.chunks = static_cast<int>(units);
     share_units(f.form, static_cast<int>(std::min<int64_t>(std::min<int64_t>(kMaxRanks, units), std::max<int64_t>(1, kSms / tiles))));
     return f.form.units_per_rank <= kMaxUnitsPerRank;
@@ -532,7 +541,7 @@ bool matmul_f32_cluster_supported(const dfgpu_matmul_params& p) {
 
 int launch_matmul_f32_cluster(const dfgpu_matmul_params& p, void* const* tensors, cudaStream_t stream) {
     MatmulAsConv f;
-    if (!matmul_cluster_form(p, f)) return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs unbatched f32 A (K contiguous), B and C (N contiguous), K and N multiples of 64 and at most 148 output tiles");
+    if (!matmul_cluster_form(p, f)) return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs unbatched f32 A (K contiguous), B and C (N contiguous), K a multiple of 8 and N of 4 and at most 148 output tiles");
     if ((reinterpret_cast<uintptr_t>(tensors[0]) & 15u) != 0 || (reinterpret_cast<uintptr_t>(tensors[2]) & 15u) != 0 ||
         (!f.b_n_major && (reinterpret_cast<uintptr_t>(tensors[1]) & 15u) != 0))
         return fail(kInvalidArgument, "MATMUL: the one-launch tcgen05 form needs 16-byte aligned A, B and C");

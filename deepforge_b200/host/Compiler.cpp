@@ -935,9 +935,9 @@ bool single_conv_metadata(SerializedGraph const& graph, CompileOptions const& op
 // The TMA-fed kernels read and write 16-byte units and have no narrower fallback (the block-scale launchers do).
 std::uint64_t kernel_alignment(KernelStep const& step, std::size_t slot) {
     switch (step.op) {
-        case KernelOp::kConvFprop: return step.kernel == DFGPU_CONV_UMMA_BF16 || step.kernel == DFGPU_CONV_UMMA_F32X3 || step.kernel == DFGPU_CONV_UMMA_F32X3_CLUSTER ? 16 : 0;
+        case KernelOp::kConvFprop: return step.kernel == DFGPU_CONV_UMMA_BF16 || step.kernel == DFGPU_CONV_UMMA_F32X3 ? 16 : 0;  // (the one-launch f32 form takes any pointer: see dfgpu_conv_fprop)
         case KernelOp::kMatmul:
-            if (step.kernel != DFGPU_MATMUL_UMMA_BF16 && step.kernel != DFGPU_MATMUL_UMMA_MXF8 && step.kernel != DFGPU_MATMUL_UMMA_F32X3 && step.kernel != DFGPU_MATMUL_UMMA_F32X3_CLUSTER) return 0;
+            if (step.kernel != DFGPU_MATMUL_UMMA_BF16 && step.kernel != DFGPU_MATMUL_UMMA_MXF8 && step.kernel != DFGPU_MATMUL_UMMA_F32X3) return 0;
             return slot == 3 || slot == 4 ? 4 : 16;  // the scale tensors are gathered with 4-byte loads
         case KernelOp::kSdpaForward:
             if (step.kernel == DFGPU_SDPA_UMMA) return slot <= 3 ? 16 : 0;

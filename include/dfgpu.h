@@ -165,7 +165,9 @@ enum {
                                    (128 pixels x 64 channels): a thread-block cluster per tile shares the filter taps out
                                    between its CTAs, which split X and W on their way into shared memory and add their
                                    partial tiles through distributed shared memory; a cluster whose inputs hold an
-                                   infinity or a NaN computes its tile on the CUDA cores. No scratch */
+                                   infinity or a NaN computes its tile on the CUDA cores. No scratch. C a multiple of 8, K of 4.
+                                   X, W or Y not 16-byte aligned: the launch runs DFGPU_CONV_IGEMM_FFMA instead (f32 arguments
+                                   keep the reference's 4-byte alignment) */
 };
 typedef struct dfgpu_conv_params {
     dfgpu_tensor x, w, y;
@@ -210,8 +212,8 @@ int dfgpu_conv_fprop_pair(const dfgpu_conv_pair_params*, void* const* tensors, v
    needs scratch, three launches (split, the bf16 matmul over 6K, and the CUDA-core kernel again, which returns at once
    unless A or B held an infinity or a NaN).
    UMMA_F32X3_CLUSTER: the same six products in ONE launch without scratch, for unbatched products of at most 148 output
-   tiles (128 x 64): the kernel of DFGPU_CONV_UMMA_F32X3_CLUSTER run on the 1 x 1 convolution of M pixels (K and N
-   multiples of 64, B with N or K contiguous). */
+   tiles (128 x 64): the kernel of DFGPU_CONV_UMMA_F32X3_CLUSTER run on the 1 x 1 convolution of M pixels (K a multiple
+   of 8, N of 4, B with N or K contiguous); A, B or C not 16-byte aligned: the launch runs DFGPU_MATMUL_FFMA instead. */
 enum { DFGPU_MATMUL_AUTO = 0, DFGPU_MATMUL_FFMA = 1, DFGPU_MATMUL_UMMA_BF16 = 2, DFGPU_MATMUL_UMMA_MXF8 = 3, DFGPU_MATMUL_UMMA_F32X3 = 4,
        DFGPU_MATMUL_UMMA_F32X3_CLUSTER = 5 };
 typedef struct dfgpu_matmul_params {

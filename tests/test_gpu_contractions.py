@@ -188,7 +188,9 @@ def test_conv_benchmark_shape_c1_in_one_launch_on_tensor_cores():
                               nhwc_strides(x_dims), nhwc_strides(w_dims), nhwc_strides(y_dims), seed=20261126)
     assert float(np.max(np.abs(out - out2))) <= 3e-5 * float(np.max(np.abs(ref)))
     cases = (([3, 128, 14, 14], [64, 128, 1, 1], 0), ([2, 64, 28, 28], [128, 64, 3, 3], 1), ([1, 64, 9, 20], [64, 64, 5, 5], 2),
-             ([4, 64, 40, 40], [64, 64, 3, 3], 1), ([2, 192, 11, 13], [64, 192, 3, 3], 0), ([5, 64, 7, 7], [256, 64, 1, 1], 0))
+             ([4, 64, 40, 40], [64, 64, 3, 3], 1), ([2, 192, 11, 13], [64, 192, 3, 3], 0), ([5, 64, 7, 7], [256, 64, 1, 1], 0),
+             # channel counts that do not fill a 64-channel unit or a 64-channel tile (C a multiple of 8, K of 4): zero-filled
+             ([1, 32, 32, 32], [32, 32, 3, 3], 1), ([2, 72, 9, 9], [20, 72, 3, 3], 1), ([1, 8, 10, 10], [4, 8, 5, 5], 2), ([3, 136, 6, 5], [132, 136, 1, 1], 0))
     for x_dims, w_dims, pad in cases:
         n, c, h, w = x_dims
         k, _, r, s_ = w_dims
@@ -202,10 +204,43 @@ def test_conv_benchmark_shape_c1_in_one_launch_on_tensor_cores():
     assert dfgpu.device_status() == 0
 
 
+def test_one_launch_forms_take_pointers_of_any_alignment():
+    """f32 arguments keep the reference's 4-byte alignment: with X (or A) 4 bytes off a 16-byte boundary the same call runs the CUDA-core
+    kernel and returns its result bit for bit."""
+    x_dims, w_dims, y_dims = [1, 64, 12, 12], [64, 64, 3, 3], [1, 64, 12, 12]
+    x = synthetic.normal(9, 1, int(np.prod(x_dims))).astype(np.float32)
+    w = synthetic.normal(9, 2, int(np.prod(w_dims)), std=0.05).astype(np.float32)
+    p = dfgpu.ConvParams()
+    p.x, p.w, p.y = tensor(F32, x_dims, nhwc_strides(x_dims)), tensor(F32, w_dims, nhwc_strides(w_dims)), tensor(F32, y_dims, nhwc_strides(y_dims))
+    for i in range(2):
+        p.pre_pad[i], p.post_pad[i], p.stride[i], p.dilation[i] = 1, 1, 1, 1
+    shifted = g.to_device(np.concatenate([np.zeros(1, np.float32), x]))
+    dw = g.to_device(w)
+    results = {}
+    for kernel in (dfgpu.CONV_IGEMM_FFMA, dfgpu.CONV_UMMA_F32X3_CLUSTER):
+        p.kernel = kernel
+        dy = g.device_zeros(int(np.prod(y_dims)) * 4, 0x5A)
+        dfgpu.conv_fprop(p, g.ptr(shifted) + 4, g.ptr(dw), g.ptr(dy))
+        results[kernel] = g.to_host(dy, np.uint32).copy()
+    assert np.array_equal(results[dfgpu.CONV_IGEMM_FFMA], results[dfgpu.CONV_UMMA_F32X3_CLUSTER])
+    a = synthetic.normal(4, 1, 128 * 128).astype(np.float32)
+    b = synthetic.normal(4, 2, 128 * 64).astype(np.float32)
+    q = dfgpu.MatmulParams()
+    q.a, q.b, q.c = tensor(F32, [128, 128]), tensor(F32, [128, 64]), tensor(F32, [128, 64])
+    da, db = g.to_device(np.concatenate([np.zeros(1, np.float32), a])), g.to_device(b)
+    for kernel in (dfgpu.MATMUL_FFMA, dfgpu.MATMUL_UMMA_F32X3_CLUSTER):
+        q.kernel = kernel
+        dc = g.device_zeros(128 * 64 * 4, 0x5A)
+        dfgpu.matmul(q, g.ptr(da) + 4, g.ptr(db), g.ptr(dc))
+        results[kernel] = g.to_host(dc, np.uint32).copy()
+    assert np.array_equal(results[dfgpu.MATMUL_FFMA], results[dfgpu.MATMUL_UMMA_F32X3_CLUSTER])
+    assert dfgpu.device_status() == 0
+
+
 def test_conv_one_launch_form_limits():
-    """More output tiles than SMs, a strided convolution or channels that are not a multiple of 64 are refused by id, and AUTO then takes
-    another kernel."""
-    for x_dims, w_dims, stride in (([8, 64, 56, 56], [64, 64, 3, 3], 1), ([1, 64, 56, 56], [64, 64, 3, 3], 2), ([1, 32, 56, 56], [64, 32, 3, 3], 1)):
+    """More output tiles than SMs, a strided convolution or input channels that are not a multiple of 8 are refused by id, and AUTO then
+    takes another kernel."""
+    for x_dims, w_dims, stride in (([8, 64, 56, 56], [64, 64, 3, 3], 1), ([1, 64, 56, 56], [64, 64, 3, 3], 2), ([1, 20, 56, 56], [64, 20, 3, 3], 1)):
         p = dfgpu.ConvParams()
         n, c, h, w = x_dims
         y_dims = [n, w_dims[0], (h + 2 - 3) // stride + 1, (w + 2 - 3) // stride + 1]
@@ -379,11 +414,13 @@ def test_matmul_f32_on_tensor_cores(a_dims, b_dims, b_strides):
 
 
 @pytest.mark.parametrize("a_dims,b_dims,b_strides", [([256, 128], [128, 192], None), ([130, 64], [64, 64], None), ([200, 64], [64, 128], [1, 64]),
-                                                    ([512, 512], [512, 256], None), ([1000, 1024], [1024, 64], [1, 1024])])
+                                                    ([512, 512], [512, 256], None), ([1000, 1024], [1024, 64], [1, 1024]),
+                                                    ([100, 40], [40, 12], None), ([130, 136], [136, 68], None), ([130, 136], [136, 68], [1, 136])])
 def test_matmul_f32_in_one_launch_on_tensor_cores(a_dims, b_dims, b_strides):
     """An unbatched f32 product of at most 148 output tiles runs on the one-launch tcgen05 kernel of the f32 convolution (as the 1 x 1
     convolution of M pixels): no scratch, N-contiguous and K-contiguous B, a last row tile that is not full, one to eight CTAs per tile, and
-    a bias row + ReLU + full-size addend in the epilogue. AUTO takes it from K = 128 on (the CUDA-core kernel walks K in steps of 16)."""
+    a bias row + ReLU + full-size addend in the epilogue; K need only be a multiple of 8 and N of 4. AUTO takes it from K = 128 on (the CUDA-core
+    kernel walks K in steps of 16)."""
     m, k, n = a_dims[0], a_dims[1], b_dims[1]
     p = dfgpu.MatmulParams()
     p.a, p.b, p.c = tensor(F32, a_dims), tensor(F32, b_dims, b_strides), tensor(F32, [m, n])
