@@ -15,7 +15,8 @@
 // its inbox to fill, adds its rows over all ranks in rank order, applies the epilogue and stores Y.
 //
 // Input channels need only be a multiple of 8 and output channels of 4: a unit's missing channels and a tile's missing
-// filter rows are written as zeros.
+// filter rows are written as zeros. Stride, dilation, asymmetric padding and filter reversal only change which input pixel
+// and which filter tap a loader thread reads.
 //
 // A product with an infinite or NaN factor does not survive the split, so the loaders also record whether they saw
 // one; the ranks exchange that beside the partial tiles, and a cluster that saw one computes its tile on the CUDA cores
@@ -140,8 +141,8 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         const int mm = live[i] ? m : 0;
         const int line = static_cast<int>(fast_divide(mm, g.by_q)), q = mm - line * Q;
         const int n = static_cast<int>(fast_divide(line, g.by_p)), p = line - n * P;
-        ih0[i] = p - a.pad_h;
-        iw0[i] = q - a.pad_w;
+        ih0[i] = p * a.stride_h - a.pad_h;
+        iw0[i] = q * a.stride_w - a.pad_w;
         x_image[i] = g.x + static_cast<int64_t>(n) * H * W * g.x_pixel_stride + unit16 * 8;
     }
     // The filter tile: 64 output channels x 8 groups of 8 input channels. Stored with input channels contiguous, a thread
@@ -157,7 +158,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         const int r = static_cast<int>(fast_divide(tap, g.by_s)), s = tap - r * S;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            const int ih = ih0[i] + r, iw = iw0[i] + s;
+            const int ih = ih0[i] + r * a.dilation_h, iw = iw0[i] + s * a.dilation_w;
             xv[i][0] = xv[i][1] = zero;
             if (live[i] && ih >= 0 && ih < H && iw >= 0 && iw < W && c0 + unit16 * 8 < C) {   // (channels come in whole groups of 8)
                 const float4* source = reinterpret_cast<const float4*>(x_image[i] + (static_cast<int64_t>(ih) * W + iw) * g.x_pixel_stride + c0);
@@ -173,7 +174,8 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
             wv[0] = make_float4(__ldg(source), __ldg(source + g.w_stride), __ldg(source + 2 * g.w_stride), __ldg(source + 3 * g.w_stride));
             wv[1] = make_float4(__ldg(source + 4 * g.w_stride), __ldg(source + 5 * g.w_stride), __ldg(source + 6 * g.w_stride), __ldg(source + 7 * g.w_stride));
         } else {
-            const float4* source = reinterpret_cast<const float4*>(w_row + static_cast<int64_t>(tap) * C + c0);
+            const int filter_tap = a.reverse ? R * S - 1 - tap : tap;   // (a reversed filter meets input tap (r, s) with its tap (R-1-r, S-1-s))
+            const float4* source = reinterpret_cast<const float4*>(w_row + static_cast<int64_t>(filter_tap) * C + c0);
             wv[0] = __ldg(source);
             wv[1] = __ldg(source + 1);
         }
@@ -351,10 +353,10 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
             float sum = 0.0f;
             for (int r = 0; r < R; ++r)
                 for (int s = 0; s < S; ++s) {
-                    const int ih = p - a.pad_h + r, iw = q - a.pad_w + s;
+                    const int ih = p * a.stride_h - a.pad_h + r * a.dilation_h, iw = q * a.stride_w - a.pad_w + s * a.dilation_w;
                     const bool inside = ih >= 0 && ih < H && iw >= 0 && iw < W;
                     const float* pixel = g.x + ((static_cast<int64_t>(n) * H + (inside ? ih : 0)) * W + (inside ? iw : 0)) * g.x_pixel_stride;
-                    const float* tap = filter + static_cast<int64_t>(r * S + s) * C * filter_step;
+                    const float* tap = filter + static_cast<int64_t>(a.reverse ? R * S - 1 - (r * S + s) : r * S + s) * C * filter_step;
                     for (int c = 0; c < C; ++c) sum = fmaf(inside ? __ldg(pixel + c) : 0.0f, __ldg(tap + c * filter_step), sum);
                 }
             g.y[static_cast<int64_t>(m) * g.y_pixel_stride + k] = apply_epilogue(sum, a, n, k, p, q);
@@ -381,15 +383,13 @@ void share_units(ClusterForm& form, int ranks) {
 }
 
 bool cluster_form(const dfgpu_conv_params& p, ClusterForm& form) {
-    if (p.x.dtype != DFGPU_F32 || p.w.dtype != DFGPU_F32 || p.y.dtype != DFGPU_F32 || p.reverse_filter) return false;
+    if (p.x.dtype != DFGPU_F32 || p.w.dtype != DFGPU_F32 || p.y.dtype != DFGPU_F32) return false;
     if (p.x.rank != 4 || p.w.rank != 4 || p.y.rank != 4) return false;
     auto packed = [](const dfgpu_tensor& t) {
         return t.stride[1] == 1 && t.stride[3] == t.dim[1] && t.stride[2] == t.dim[3] * t.dim[1] && t.stride[0] == t.dim[2] * t.dim[3] * t.dim[1];
     };
     if (!packed(p.x) || !packed(p.w) || !packed(p.y)) return false;
     if (p.x.dim[1] != p.w.dim[1] || p.x.dim[1] % 8 != 0 || p.y.dim[1] % 4 != 0 || p.w.dim[0] != p.y.dim[1]) return false;
-    for (int axis = 0; axis < 2; ++axis)
-        if (p.stride[axis] != 1 || p.dilation[axis] != 1) return false;
     if (element_count(p.x) >= (1ll << 31) || element_count(p.w) >= (1ll << 31) || element_count(p.y) >= (1ll << 31)) return false;
     const int64_t m_total = p.y.dim[0] * p.y.dim[2] * p.y.dim[3];
     const int64_t chunks = (p.x.dim[1] + kChunk - 1) / kChunk, tiles_n = (p.y.dim[1] + kTileN - 1) / kTileN;
@@ -482,7 +482,7 @@ bool conv_f32_cluster_supported(const dfgpu_conv_params& p) {
 
 int launch_conv_f32_cluster(const dfgpu_conv_params& p, const ConvArgs& a, void* const* tensors, cudaStream_t stream) {
     ClusterForm form;
-    if (!cluster_form(p, form)) return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs packed channels-last f32 X, W and Y, C a multiple of 8 and K of 4, stride 1, dilation 1 and at most 148 output tiles");
+    if (!cluster_form(p, form)) return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs packed channels-last f32 X, W and Y, one group, C a multiple of 8 and K of 4 and at most 148 output tiles");
     for (int i = 0; i < 3; ++i)
         if ((reinterpret_cast<uintptr_t>(tensors[i]) & 15u) != 0) return fail(kInvalidArgument, "CONV_FPROP: the one-launch tcgen05 form needs 16-byte aligned X, W and Y");
     ClusterConvArgs g{};

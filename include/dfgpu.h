@@ -165,7 +165,8 @@ enum {
                                    (128 pixels x 64 channels): a thread-block cluster per tile shares the filter taps out
                                    between its CTAs, which split X and W on their way into shared memory and add their
                                    partial tiles through distributed shared memory; a cluster whose inputs hold an
-                                   infinity or a NaN computes its tile on the CUDA cores. No scratch. C a multiple of 8, K of 4.
+                                   infinity or a NaN computes its tile on the CUDA cores. No scratch. One group, C a multiple of 8, K of 4;
+                                   any stride, dilation, padding, filter reversal.
                                    X, W or Y not 16-byte aligned: the launch runs DFGPU_CONV_IGEMM_FFMA instead (f32 arguments
                                    keep the reference's 4-byte alignment) */
 };

@@ -201,6 +201,20 @@ def test_conv_benchmark_shape_c1_in_one_launch_on_tensor_cores():
                                   epilogue=[step(dfgpu.EPI_ADD, 0), step(dfgpu.EPI_RELU)], extras=[([1, k, 1, 1], [k, 1, k, k], bias)])
         assert info.kernel == dfgpu.CONV_UMMA_F32X3_CLUSTER and info.launches == 1
         check_f32(out, ref)
+    # stride, dilation, asymmetric padding and a reversed filter only change which pixel and which tap a loader thread reads
+    for x_dims, w_dims, pre, post, stride, dilation, reverse in (([2, 64, 28, 28], [64, 64, 3, 3], [1, 1], [1, 1], [2, 2], [1, 1], False),
+                                                                   ([1, 64, 20, 17], [64, 64, 3, 3], [2, 2], [2, 2], [1, 1], [2, 2], False),
+                                                                   ([2, 32, 11, 9], [16, 32, 3, 2], [1, 0], [2, 1], [2, 1], [1, 2], True),
+                                                                   ([1, 64, 14, 14], [64, 64, 3, 3], [1, 1], [1, 1], [1, 1], [1, 1], True)):
+        kernels = {}
+        out_h = (x_dims[2] + pre[0] + post[0] - (dilation[0] * (w_dims[2] - 1) + 1)) // stride[0] + 1
+        out_w = (x_dims[3] + pre[1] + post[1] - (dilation[1] * (w_dims[3] - 1) + 1)) // stride[1] + 1
+        for kernel in (dfgpu.CONV_UMMA_F32X3_CLUSTER, dfgpu.CONV_AUTO):
+            info, out, ref = run_conv(F32, x_dims, w_dims, pre, post, stride, dilation, kernel, nhwc_strides(x_dims), nhwc_strides(w_dims),
+                                      nhwc_strides([x_dims[0], w_dims[0], out_h, out_w]), reverse=reverse, seed=11)
+            kernels[kernel] = info.kernel
+            check_f32(out, ref)
+        assert kernels[dfgpu.CONV_UMMA_F32X3_CLUSTER] == kernels[dfgpu.CONV_AUTO] == dfgpu.CONV_UMMA_F32X3_CLUSTER
     assert dfgpu.device_status() == 0
 
 
@@ -238,9 +252,9 @@ def test_one_launch_forms_take_pointers_of_any_alignment():
 
 
 def test_conv_one_launch_form_limits():
-    """More output tiles than SMs, a strided convolution or input channels that are not a multiple of 8 are refused by id, and AUTO then
+    """More output tiles than SMs, a grouped convolution or input channels that are not a multiple of 8 are refused by id, and AUTO then
     takes another kernel."""
-    for x_dims, w_dims, stride in (([8, 64, 56, 56], [64, 64, 3, 3], 1), ([1, 64, 56, 56], [64, 64, 3, 3], 2), ([1, 20, 56, 56], [64, 20, 3, 3], 1)):
+    for x_dims, w_dims, stride in (([8, 64, 56, 56], [64, 64, 3, 3], 1), ([1, 64, 56, 56], [64, 32, 3, 3], 1), ([1, 20, 56, 56], [64, 20, 3, 3], 1)):
         p = dfgpu.ConvParams()
         n, c, h, w = x_dims
         y_dims = [n, w_dims[0], (h + 2 - 3) // stride + 1, (w + 2 - 3) // stride + 1]
