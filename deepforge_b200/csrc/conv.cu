@@ -420,12 +420,16 @@ int choose_kernel(const dfgpu_conv_params& p, const ConvArgs& a, int& kernel) {
     const int64_t macs = p.y.dim[0] * p.y.dim[2] * p.y.dim[3] * p.y.dim[1] * p.w.dim[1] * p.w.dim[2] * p.w.dim[3];
     if (split_ok && macs >= kSplitFormMinMacs) automatic = DFGPU_CONV_UMMA_F32X3;
     const bool cluster_ok = conv_f32_cluster_supported(p);
-    if (cluster_ok && p.w.dim[1] * p.w.dim[2] * p.w.dim[3] >= kClusterFormMinDepth) automatic = DFGPU_CONV_UMMA_F32X3_CLUSTER;   // (few tiles: one launch beats three)
+    // One launch beats three where the output tiles fit one wave, or all output channels fit one tile (with several tiles
+    // along K every one of them splits the same X rows again: the three-launch form splits them once).
+    const int64_t pixel_tiles = (p.y.dim[0] * p.y.dim[2] * p.y.dim[3] + 127) / 128, channel_tiles = (p.y.dim[1] + 63) / 64;
+    const bool one_launch_pays = automatic != DFGPU_CONV_UMMA_F32X3 || pixel_tiles * channel_tiles <= 148 || channel_tiles == 1;
+    if (cluster_ok && one_launch_pays && p.w.dim[1] * p.w.dim[2] * p.w.dim[3] >= kClusterFormMinDepth) automatic = DFGPU_CONV_UMMA_F32X3_CLUSTER;
     kernel = p.kernel == DFGPU_CONV_AUTO ? automatic : p.kernel;
     if (kernel == DFGPU_CONV_UMMA_F32X3 && !split_ok)
         return fail(kUnsupported, "CONV_FPROP: the split-operand tcgen05 form needs packed channels-last f32 X, W and Y, C and K multiples of 64, stride 1, dilation 1");
     if (kernel == DFGPU_CONV_UMMA_F32X3_CLUSTER && !cluster_ok)
-        return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs packed channels-last f32 X, W and Y, one group, C a multiple of 8 and K of 4 and at most 148 output tiles");
+        return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs packed channels-last f32 X, W and Y, one group, C a multiple of 8 and K of 4 and a reduction depth of at most 4096");
     if (kernel != DFGPU_CONV_UMMA_BF16 && (p.x.dtype == DFGPU_BF16X2 || p.y.dtype == DFGPU_BF16X2))
         return fail(kUnsupported, "CONV_FPROP: split bf16 pair tensors are read and written by the tcgen05 kernel only");
     if (kernel == DFGPU_CONV_IGEMM_FFMA && a.groups != 1)

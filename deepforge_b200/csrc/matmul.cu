@@ -259,13 +259,16 @@ int choose_kernel(const dfgpu_matmul_params& p, int& kernel) {
     else {
         const int64_t macs = p.c.dim[p.c.rank - 2] * p.c.dim[p.c.rank - 1] * p.a.dim[p.a.rank - 1];
         if (split_ok && macs >= kSplitFormMinMacs) automatic = DFGPU_MATMUL_UMMA_F32X3;  // (three launches: big products only)
-        if (p.a.dim[p.a.rank - 1] >= kClusterFormMinDepth && matmul_f32_cluster_supported(p)) automatic = DFGPU_MATMUL_UMMA_F32X3_CLUSTER;  // (few tiles: one launch)
+        // (one launch beats three where the output tiles fit one wave or all columns fit one tile)
+        const int64_t row_tiles = (p.c.dim[p.c.rank - 2] + 127) / 128, column_tiles = (p.c.dim[p.c.rank - 1] + 63) / 64;
+        const bool one_launch_pays = automatic != DFGPU_MATMUL_UMMA_F32X3 || row_tiles * column_tiles <= 148 || column_tiles == 1;
+        if (one_launch_pays && p.a.dim[p.a.rank - 1] >= kClusterFormMinDepth && matmul_f32_cluster_supported(p)) automatic = DFGPU_MATMUL_UMMA_F32X3_CLUSTER;
     }
     kernel = p.kernel == DFGPU_MATMUL_AUTO ? automatic : p.kernel;
     if (kernel < DFGPU_MATMUL_FFMA || kernel > DFGPU_MATMUL_UMMA_F32X3_CLUSTER) return fail(kInvalidArgument, "MATMUL: unknown kernel id %d", kernel);
     if (kernel == DFGPU_MATMUL_UMMA_F32X3_CLUSTER) {
         if (!matmul_f32_cluster_supported(p))
-            return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs unbatched f32 A (K contiguous), B and C (N contiguous), K a multiple of 8 and N of 4 and at most 148 output tiles");
+            return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs unbatched f32 A (K contiguous), B and C (N contiguous), K a multiple of 8 (at most 4096) and N of 4");
         return kOk;
     }
     if (kernel == DFGPU_MATMUL_UMMA_F32X3) {

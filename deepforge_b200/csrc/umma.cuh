@@ -32,13 +32,13 @@ struct ConvKSplit {
 ConvKSplit conv_umma_k_split(const dfgpu_conv_params& p);
 int launch_conv_umma(const dfgpu_conv_params& p, void* const* tensors, cudaStream_t stream, const ConvKSplit* k_split = nullptr);
 
-// f32 NHWC/KRSC convolution with fewer output tiles than SMs on the bf16 tensor cores in one launch: a thread-block
+// f32 NHWC/KRSC convolution on the bf16 tensor cores in one launch (made for fewer output tiles than SMs): a thread-block
 // cluster per output tile, the operands split into bf16 pieces on their way into shared memory (umma_conv_f32.cu).
 struct ConvArgs;
 bool conv_f32_cluster_supported(const dfgpu_conv_params& p);
 int launch_conv_f32_cluster(const dfgpu_conv_params& p, const ConvArgs& a, void* const* tensors, cudaStream_t stream);
 int conv_f32_device_status(int* status);
-// The same kernel for an unbatched f32 MATMUL of at most 148 output tiles (the 1 x 1 convolution of M pixels; B with N or K contiguous).
+// The same kernel for an unbatched f32 MATMUL (the 1 x 1 convolution of M pixels; B with N or K contiguous).
 bool matmul_f32_cluster_supported(const dfgpu_matmul_params& p);
 int launch_matmul_f32_cluster(const dfgpu_matmul_params& p, void* const* tensors, cudaStream_t stream);
 constexpr int64_t kClusterFormMinDepth = 128;  // AUTO takes the one-launch form from this reduction depth (C R S, or K) on: the CUDA-core kernels walk the depth 16 at a time at ~0.8 us a step, the cluster launch costs 7-9 us whatever the depth

@@ -1,4 +1,5 @@
-// f32 CONV_FPROP on the bf16 tensor cores in ONE launch, for convolutions with fewer output tiles than SMs.
+// f32 CONV_FPROP on the bf16 tensor cores in ONE launch; made for convolutions with fewer output tiles than SMs, where
+// the clusters below spread one tile's reduction over several SMs, and correct for any number of tiles (one CTA per tile then).
 //
 // x = xh + xm + xl and w = wh + wm + wl with bf16 pieces (the leading 8 significant bits, the next 8, the last 8, each
 // cut off rather than rounded, so every subtraction that forms them is exact and no piece can round past the largest
@@ -39,7 +40,7 @@ constexpr int kPieceBytesA = kTileM * 128, kPieceBytesB = kTileN * 128;   // 64 
 constexpr int kUnitBytes = 3 * (kPieceBytesA + kPieceBytesB);
 constexpr int kBuffers = 2;
 constexpr int kMaxRanks = 8;
-constexpr int kMaxUnitsPerRank = 6;
+constexpr int kMaxUnitsPerRank = 64;
 constexpr int kInboxOffset = kBuffers * kUnitBytes;                        // the rows this rank owns, one chunk per sending rank
 constexpr int kRowBytes = kTileN * 4;
 constexpr int kInboxBytes = (kTileM + kMaxRanks) * kRowBytes + kMaxRanks * 16;   // ranks * (ceil(128 / ranks) rows + a 16-byte trailer)
@@ -396,7 +397,7 @@ bool cluster_form(const dfgpu_conv_params& p, ClusterForm& form) {
     const int64_t tiles = (m_total + kTileM - 1) / kTileM * tiles_n;
     const int64_t units = p.w.dim[2] * p.w.dim[3] * chunks;
     constexpr int kSms = 148;   // (a query has no device: the count this library is built for)
-    if (tiles > kSms || units > kMaxRanks * kMaxUnitsPerRank) return false;
+    if ((m_total + kTileM - 1) / kTileM > 65535 || tiles_n > 65535 || units > kMaxUnitsPerRank) return false;   // (grid extents; units one CTA walks)
     form.tiles_m = static_cast<int>((m_total + kTileM - 1) / kTileM);
     form.tiles_n = static_cast<int>(tiles_n);
     form.units = static_cast<int>(units);
@@ -482,7 +483,7 @@ bool conv_f32_cluster_supported(const dfgpu_conv_params& p) {
 
 int launch_conv_f32_cluster(const dfgpu_conv_params& p, const ConvArgs& a, void* const* tensors, cudaStream_t stream) {
     ClusterForm form;
-    if (!cluster_form(p, form)) return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs packed channels-last f32 X, W and Y, one group, C a multiple of 8 and K of 4 and at most 148 output tiles");
+    if (!cluster_form(p, form)) return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs packed channels-last f32 X, W and Y, one group, C a multiple of 8 and K of 4 and a reduction depth of at most 4096");
     for (int i = 0; i < 3; ++i)
         if ((reinterpret_cast<uintptr_t>(tensors[i]) & 15u) != 0) return fail(kInvalidArgument, "CONV_FPROP: the one-launch tcgen05 form needs 16-byte aligned X, W and Y");
     ClusterConvArgs g{};
@@ -525,7 +526,7 @@ bool matmul_cluster_form(const dfgpu_matmul_params& p, MatmulAsConv& f) {
     const int64_t tiles_n = (f.n + kTileN - 1) / kTileN, units = (f.k + kChunk - 1) / kChunk;
     const int64_t tiles = (f.m + kTileM - 1) / kTileM * tiles_n;
     constexpr int kSms = 148;
-    if (tiles > kSms || units > kMaxRanks * kMaxUnitsPerRank) return false;
+    if ((f.m + kTileM - 1) / kTileM > 65535 || tiles_n > 65535 || units > kMaxUnitsPerRank) return false;
     f.form.tiles_m = static_cast<int>((f.m + kTileM - 1) / kTileM);
     f.form.tiles_n = static_cast<int>(tiles_n);
     f.form.units = f.form.chunks = static_cast<int>(units);
@@ -541,7 +542,7 @@ bool matmul_f32_cluster_supported(const dfgpu_matmul_params& p) {
 
 int launch_matmul_f32_cluster(const dfgpu_matmul_params& p, void* const* tensors, cudaStream_t stream) {
     MatmulAsConv f;
-    if (!matmul_cluster_form(p, f)) return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs unbatched f32 A (K contiguous), B and C (N contiguous), K a multiple of 8 and N of 4 and at most 148 output tiles");
+    if (!matmul_cluster_form(p, f)) return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs unbatched f32 A (K contiguous), B and C (N contiguous), K a multiple of 8 (at most 4096) and N of 4");
     if ((reinterpret_cast<uintptr_t>(tensors[0]) & 15u) != 0 || (reinterpret_cast<uintptr_t>(tensors[2]) & 15u) != 0 ||
         (!f.b_n_major && (reinterpret_cast<uintptr_t>(tensors[1]) & 15u) != 0))
         return fail(kInvalidArgument, "MATMUL: the one-launch tcgen05 form needs 16-byte aligned A, B and C");

@@ -161,8 +161,9 @@ enum {
                                    channels (K split over several CTAs per tile when the tiles are few), and the CUDA-core
                                    kernel again, which adds the partial sums, or redoes the convolution when X or W held
                                    an infinity or a NaN */
-    DFGPU_CONV_UMMA_F32X3_CLUSTER = 5  /* the same six products in ONE launch, for convolutions of at most 148 output tiles
-                                   (128 pixels x 64 channels): a thread-block cluster per tile shares the filter taps out
+    DFGPU_CONV_UMMA_F32X3_CLUSTER = 5  /* the same six products in ONE launch, made for convolutions of at most 148 output tiles
+                                   (128 pixels x 64 channels; more tiles run one CTA each, reduction depth at most 4096):
+                                   a thread-block cluster per tile shares the filter taps out
                                    between its CTAs, which split X and W on their way into shared memory and add their
                                    partial tiles through distributed shared memory; a cluster whose inputs hold an
                                    infinity or a NaN computes its tile on the CUDA cores. No scratch. One group, C a multiple of 8, K of 4;
@@ -212,8 +213,8 @@ int dfgpu_conv_fprop_pair(const dfgpu_conv_pair_params*, void* const* tensors, v
 /* UMMA_F32X3: f32 A, B and C on tcgen05: A and B split into three bf16 pieces each, six bf16 products (2^-24 relative);
    needs scratch, three launches (split, the bf16 matmul over 6K, and the CUDA-core kernel again, which returns at once
    unless A or B held an infinity or a NaN).
-   UMMA_F32X3_CLUSTER: the same six products in ONE launch without scratch, for unbatched products of at most 148 output
-   tiles (128 x 64): the kernel of DFGPU_CONV_UMMA_F32X3_CLUSTER run on the 1 x 1 convolution of M pixels (K a multiple
+   UMMA_F32X3_CLUSTER: the same six products in ONE launch without scratch, made for unbatched products of at most 148 output
+   tiles (128 x 64; more tiles run one CTA each, K at most 4096): the kernel of DFGPU_CONV_UMMA_F32X3_CLUSTER run on the 1 x 1 convolution of M pixels (K a multiple
    of 8, N of 4, B with N or K contiguous); A, B or C not 16-byte aligned: the launch runs DFGPU_MATMUL_FFMA instead. */
 enum { DFGPU_MATMUL_AUTO = 0, DFGPU_MATMUL_FFMA = 1, DFGPU_MATMUL_UMMA_BF16 = 2, DFGPU_MATMUL_UMMA_MXF8 = 3, DFGPU_MATMUL_UMMA_F32X3 = 4,
        DFGPU_MATMUL_UMMA_F32X3_CLUSTER = 5 };

@@ -190,7 +190,9 @@ def test_conv_benchmark_shape_c1_in_one_launch_on_tensor_cores():
     cases = (([3, 128, 14, 14], [64, 128, 1, 1], 0), ([2, 64, 28, 28], [128, 64, 3, 3], 1), ([1, 64, 9, 20], [64, 64, 5, 5], 2),
              ([4, 64, 40, 40], [64, 64, 3, 3], 1), ([2, 192, 11, 13], [64, 192, 3, 3], 0), ([5, 64, 7, 7], [256, 64, 1, 1], 0),
              # channel counts that do not fill a 64-channel unit or a 64-channel tile (C a multiple of 8, K of 4): zero-filled
-             ([1, 32, 32, 32], [32, 32, 3, 3], 1), ([2, 72, 9, 9], [20, 72, 3, 3], 1), ([1, 8, 10, 10], [4, 8, 5, 5], 2), ([3, 136, 6, 5], [132, 136, 1, 1], 0))
+             ([1, 32, 32, 32], [32, 32, 3, 3], 1), ([2, 72, 9, 9], [20, 72, 3, 3], 1), ([1, 8, 10, 10], [4, 8, 5, 5], 2), ([3, 136, 6, 5], [132, 136, 1, 1], 0),
+             # more tiles than SMs: one CTA per tile walks all nine taps, the tiles run in waves
+             ([8, 64, 56, 56], [64, 64, 3, 3], 1))
     for x_dims, w_dims, pad in cases:
         n, c, h, w = x_dims
         k, _, r, s_ = w_dims
@@ -252,9 +254,9 @@ def test_one_launch_forms_take_pointers_of_any_alignment():
 
 
 def test_conv_one_launch_form_limits():
-    """More output tiles than SMs, a grouped convolution or input channels that are not a multiple of 8 are refused by id, and AUTO then
+    """A reduction deeper than 4096, a grouped convolution or input channels that are not a multiple of 8 are refused by id, and AUTO then
     takes another kernel."""
-    for x_dims, w_dims, stride in (([8, 64, 56, 56], [64, 64, 3, 3], 1), ([1, 64, 56, 56], [64, 32, 3, 3], 1), ([1, 20, 56, 56], [64, 20, 3, 3], 1)):
+    for x_dims, w_dims, stride in (([1, 512, 8, 8], [64, 512, 3, 3], 1), ([1, 64, 56, 56], [64, 32, 3, 3], 1), ([1, 20, 56, 56], [64, 20, 3, 3], 1)):
         p = dfgpu.ConvParams()
         n, c, h, w = x_dims
         y_dims = [n, w_dims[0], (h + 2 - 3) // stride + 1, (w + 2 - 3) // stride + 1]
@@ -408,14 +410,15 @@ def run_matmul(dtype, a_dims, b_dims, kernel=dfgpu.MATMUL_FFMA, a_strides=None, 
 
 
 @pytest.mark.parametrize("a_dims,b_dims,b_strides", [([256, 128], [128, 192], None), ([130, 96], [96, 64], None), ([200, 64], [64, 128], [1, 64]),
-                                                    ([1024, 1024], [1024, 1024], None)])
+                                                    ([1024, 1024], [1024, 1024], None), ([2048, 512], [512, 1024], None)])
 def test_matmul_f32_on_tensor_cores(a_dims, b_dims, b_strides):
     """f32 A, B, C resolve to the split-operand tcgen05 form (six bf16 products, f32 accumulation) and hold the f32 gates
     against the oracle, for N-contiguous and K-contiguous B and a last row tile that is not full."""
     p = dfgpu.MatmulParams()
     p.a, p.b, p.c = tensor(F32, a_dims), tensor(F32, b_dims, b_strides), tensor(F32, [a_dims[0], b_dims[1]])
-    # AUTO: the one-launch form where it fits (K and N multiples of 64, K >= 128, few tiles), the three-launch form for big products, else CUDA cores
-    expected = {(256, 128): dfgpu.MATMUL_UMMA_F32X3_CLUSTER, (1024, 1024): dfgpu.MATMUL_UMMA_F32X3}.get((a_dims[0], a_dims[1]), dfgpu.MATMUL_FFMA)
+    # AUTO: the one-launch form where it fits and pays (K >= 128; at most 148 tiles or one tile of columns), the three-launch form for other big products, else CUDA cores
+    expected = {(256, 128): dfgpu.MATMUL_UMMA_F32X3_CLUSTER, (1024, 1024): dfgpu.MATMUL_UMMA_F32X3_CLUSTER,
+                (2048, 512): dfgpu.MATMUL_UMMA_F32X3}.get((a_dims[0], a_dims[1]), dfgpu.MATMUL_FFMA)
     assert dfgpu.query("matmul", p).kernel == expected
     p.kernel = dfgpu.MATMUL_UMMA_F32X3
     info = dfgpu.query("matmul", p)
