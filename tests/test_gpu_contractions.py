@@ -191,8 +191,8 @@ def test_conv_benchmark_shape_c1_in_one_launch_on_tensor_cores():
              ([4, 64, 40, 40], [64, 64, 3, 3], 1), ([2, 192, 11, 13], [64, 192, 3, 3], 0), ([5, 64, 7, 7], [256, 64, 1, 1], 0),
              # channel counts that do not fill a 64-channel unit or a 64-channel tile (C a multiple of 8, K of 4): zero-filled
              ([1, 32, 32, 32], [32, 32, 3, 3], 1), ([2, 72, 9, 9], [20, 72, 3, 3], 1), ([1, 8, 10, 10], [4, 8, 5, 5], 2), ([3, 136, 6, 5], [132, 136, 1, 1], 0),
-             # more tiles than SMs: one CTA per tile walks all nine taps, the tiles run in waves
-             ([8, 64, 56, 56], [64, 64, 3, 3], 1))
+             # more tiles than SMs: one CTA per tile walks all nine taps, the tiles run in waves; and a single output pixel
+             ([8, 64, 56, 56], [64, 64, 3, 3], 1), ([1, 8, 1, 1], [4, 8, 1, 1], 0))
     for x_dims, w_dims, pad in cases:
         n, c, h, w = x_dims
         k, _, r, s_ = w_dims
