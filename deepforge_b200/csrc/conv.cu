@@ -429,7 +429,7 @@ int choose_kernel(const dfgpu_conv_params& p, const ConvArgs& a, int& kernel) {
     if (kernel == DFGPU_CONV_UMMA_F32X3 && !split_ok)
         return fail(kUnsupported, "CONV_FPROP: the split-operand tcgen05 form needs packed channels-last f32 X, W and Y, C and K multiples of 64, stride 1, dilation 1");
     if (kernel == DFGPU_CONV_UMMA_F32X3_CLUSTER && !cluster_ok)
-        return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs packed channels-last f32 X, W and Y, one group, C a multiple of 8 and K of 4 and a reduction depth of at most 4096");
+        return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs f32 X, W and Y, one group, C a multiple of 8 and K of 4 and a reduction depth of at most 4096");
     if (kernel != DFGPU_CONV_UMMA_BF16 && (p.x.dtype == DFGPU_BF16X2 || p.y.dtype == DFGPU_BF16X2))
         return fail(kUnsupported, "CONV_FPROP: split bf16 pair tensors are read and written by the tcgen05 kernel only");
     if (kernel == DFGPU_CONV_IGEMM_FFMA && a.groups != 1)
@@ -481,14 +481,7 @@ extern "C" int dfgpu_conv_fprop(const dfgpu_conv_params* p, void* const* tensors
     if (status) return status;
     cudaStream_t stream = as_stream(stream_handle);
     if (kernel == DFGPU_CONV_UMMA_BF16) return launch_conv_umma(*p, tensors, stream);
-    if (kernel == DFGPU_CONV_UMMA_F32X3_CLUSTER) {
-        // The reference's argument table promises f32 tensors 4-byte alignment only, and this form does not raise it: pointers
-        // that are not 16-byte aligned take the CUDA-core kernel (one launch and no scratch either).
-        bool aligned = true;
-        for (int i = 0; i < 3; ++i) aligned = aligned && (reinterpret_cast<uintptr_t>(tensors[i]) & 15u) == 0;
-        if (aligned) return launch_conv_f32_cluster(*p, a, tensors, stream);
-        kernel = DFGPU_CONV_IGEMM_FFMA;
-    }
+    if (kernel == DFGPU_CONV_UMMA_F32X3_CLUSTER) return launch_conv_f32_cluster(*p, a, tensors, stream);  // (any f32 pointer: 4-byte alignment is enough)
     int64_t m_total = p->y.dim[0] * p->y.dim[2] * p->y.dim[3];
     if (kernel == DFGPU_CONV_UMMA_F32X3) {
         SplitForm split;

@@ -268,7 +268,7 @@ int choose_kernel(const dfgpu_matmul_params& p, int& kernel) {
     if (kernel < DFGPU_MATMUL_FFMA || kernel > DFGPU_MATMUL_UMMA_F32X3_CLUSTER) return fail(kInvalidArgument, "MATMUL: unknown kernel id %d", kernel);
     if (kernel == DFGPU_MATMUL_UMMA_F32X3_CLUSTER) {
         if (!matmul_f32_cluster_supported(p))
-            return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs unbatched f32 A (K contiguous), B and C (N contiguous), K a multiple of 8 (at most 4096) and N of 4");
+            return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs unbatched f32 A, B and C, K a multiple of 8 (at most 4096) and N of 4");
         return kOk;
     }
     if (kernel == DFGPU_MATMUL_UMMA_F32X3) {
@@ -318,13 +318,7 @@ extern "C" int dfgpu_matmul(const dfgpu_matmul_params* p, void* const* tensors, 
     status = choose_kernel(*p, kernel);
     if (status) return status;
     cudaStream_t stream = as_stream(stream_handle);
-    if (kernel == DFGPU_MATMUL_UMMA_F32X3_CLUSTER) {
-        // (this form does not raise the 4-byte alignment of f32 arguments: other pointers take the CUDA-core kernel)
-        bool aligned = true;
-        for (int i = 0; i < 3; ++i) aligned = aligned && (reinterpret_cast<uintptr_t>(tensors[i]) & 15u) == 0;
-        if (aligned) return launch_matmul_f32_cluster(*p, tensors, stream);
-        kernel = DFGPU_MATMUL_FFMA;
-    }
+    if (kernel == DFGPU_MATMUL_UMMA_F32X3_CLUSTER) return launch_matmul_f32_cluster(*p, tensors, stream);  // (any f32 pointer: 4-byte alignment is enough)
     if (kernel == DFGPU_MATMUL_UMMA_F32X3) {
         SplitMatmul split;
         if (!f32_split_matmul(*p, split)) return fail(kUnsupported, "MATMUL: the split-operand tcgen05 form does not take this matmul");

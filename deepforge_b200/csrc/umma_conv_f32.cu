@@ -17,7 +17,10 @@
 //
 // Input channels need only be a multiple of 8 and output channels of 4: a unit's missing channels and a tile's missing
 // filter rows are written as zeros. Stride, dilation, asymmetric padding and filter reversal only change which input pixel
-// and which filter tap a loader thread reads.
+// and which filter tap a loader thread reads. The tensors may have any strides: with contiguous channels on 16-byte
+// boundaries (channels-last X and Y, KRSC filter) a group of 8 channels is two float4 loads; otherwise (NCHW, a
+// transposed MATMUL operand, a pointer that is only 4-byte aligned) neighbouring threads take neighbouring pixels (or
+// output channels) and read their channels value by value, so that a warp's loads still fall side by side.
 //
 // A product with an infinite or NaN factor does not survive the split, so the loaders also record whether they saw
 // one; the ranks exchange that beside the partial tiles, and a cluster that saw one computes its tile on the CUDA cores
@@ -54,9 +57,12 @@ struct ClusterConvArgs {
     const float* w;
     float* y;
     int m_total, units, units_per_rank, chunks;   // chunks: 64-channel slices per filter tap
-    int64_t x_pixel_stride, y_pixel_stride;       // floats between pixels (C and K when packed)
-    int64_t w_stride;                             // floats between output channels, or (w_n_major) between input channels
-    int w_n_major;                                // the filter is stored [C, K] with K contiguous (a MATMUL's row-major B; 1 x 1 only)
+    // strides in floats; 32 bits are enough, and cheaper in the loaders: every element lies within 2^31 floats of the first
+    int32_t x_n, x_c, x_h, x_w;                   // X by image, channel, row, column
+    int32_t w_k, w_c, w_r, w_s;                   // the filter by output channel, input channel, tap row, tap column
+    int32_t y_n, y_k, y_p, y_q;                   // Y by image, channel, row, column
+    int x_quads, w_quads, y_quads;                // channels are contiguous and every other stride and the pointer a multiple of 16 bytes: float4 accesses
+    int w_along_k;                                // output channels are contiguous in the filter (a MATMUL's row-major B): neighbouring threads take neighbouring output channels
     FastDivisor by_q, by_p, by_chunks, by_s;      // output width and height, chunks, filter width
 };
 
@@ -110,8 +116,12 @@ __device__ __forceinline__ bool split_eight(const float4& a, const float4& b, ui
     return finite;
 }
 
+// FAST: X, W and Y all take float4 accesses (the flags in the arguments are then not looked at).
+template <bool FAST>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_constant__ ConvArgs a) {
+    const bool x_quads = FAST || g.x_quads != 0, w_quads = FAST || g.w_quads != 0, y_quads = FAST || g.y_quads != 0;
+    const bool w_along_k = !FAST && g.w_along_k != 0;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     cg::cluster_group cluster = cg::this_cluster();
@@ -130,8 +140,11 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
     const int R = static_cast<int>(a.w.dim[2]), S = static_cast<int>(a.w.dim[3]);
 
     // Loader threads: which rows of the operand tiles this thread fills (the issuing warp computes them too, and loads nothing).
-    const int unit16 = tid & 7;                          // which 8 channels (16 bytes of bf16) of the 64
-    const int row[2] = {tid >> 3, 64 + (tid >> 3)};      // two of the tile's 128 pixels
+    // X with contiguous channels: a thread takes one group of 8 channels (16 bytes of bf16) of two pixels, as two float4 loads each.
+    // Any other X (channels strided, as in NCHW): neighbouring threads take neighbouring pixels, so that their loads of one
+    // channel fall side by side, and a thread reads two groups of 8 channels of one pixel value by value.
+    const int row[2] = {x_quads ? tid >> 3 : tid & 127, x_quads ? 64 + (tid >> 3) : tid & 127};
+    const int x_unit[2] = {x_quads ? tid & 7 : (tid >> 7) & 3, x_quads ? tid & 7 : 4 + ((tid >> 7) & 3)};
     int ih0[2], iw0[2];
     const float* x_image[2];
     bool live[2];
@@ -144,14 +157,17 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         const int n = static_cast<int>(fast_divide(line, g.by_p)), p = line - n * P;
         ih0[i] = p * a.stride_h - a.pad_h;
         iw0[i] = q * a.stride_w - a.pad_w;
-        x_image[i] = g.x + static_cast<int64_t>(n) * H * W * g.x_pixel_stride + unit16 * 8;
+        x_image[i] = g.x + (n * g.x_n + x_unit[i] * 8 * g.x_c);
     }
     // The filter tile: 64 output channels x 8 groups of 8 input channels. Stored with input channels contiguous, a thread
     // reads its group as two quads; stored with output channels contiguous, neighbouring threads take neighbouring output
     // channels and each reads its 8 input channels one by one.
-    const int w_channel = g.w_n_major ? tid & 63 : tid >> 3, w_unit = g.w_n_major ? (tid >> 6) & 7 : unit16;
-    const float* w_row = g.w_n_major ? g.w + static_cast<int64_t>(w_unit) * 8 * g.w_stride + n0 + w_channel
-                                     : g.w + static_cast<int64_t>(n0 + w_channel) * g.w_stride + w_unit * 8;
+    const int w_channel = w_along_k ? tid & 63 : tid >> 3, w_unit = w_along_k ? (tid >> 6) & 7 : tid & 7;
+    const float* w_row = g.w + (n0 + w_channel < K ? (n0 + w_channel) * g.w_k + w_unit * 8 * g.w_c : 0);   // (rows past the last filter are never read)
+    auto eight = [](const float* source, int stride, float4 (&v)[2]) {   // eight values `stride` floats apart
+        v[0] = make_float4(__ldg(source), __ldg(source + stride), __ldg(source + 2 * stride), __ldg(source + 3 * stride));
+        v[1] = make_float4(__ldg(source + 4 * stride), __ldg(source + 5 * stride), __ldg(source + 6 * stride), __ldg(source + 7 * stride));
+    };
     const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     auto fetch = [&](int u, float4 (&xv)[2][2], float4 (&wv)[2]) {
         const int unit = first_unit + u;
@@ -161,24 +177,28 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         for (int i = 0; i < 2; ++i) {
             const int ih = ih0[i] + r * a.dilation_h, iw = iw0[i] + s * a.dilation_w;
             xv[i][0] = xv[i][1] = zero;
-            if (live[i] && ih >= 0 && ih < H && iw >= 0 && iw < W && c0 + unit16 * 8 < C) {   // (channels come in whole groups of 8)
-                const float4* source = reinterpret_cast<const float4*>(x_image[i] + (static_cast<int64_t>(ih) * W + iw) * g.x_pixel_stride + c0);
-                xv[i][0] = __ldg(source);
-                xv[i][1] = __ldg(source + 1);
+            if (live[i] && ih >= 0 && ih < H && iw >= 0 && iw < W && c0 + x_unit[i] * 8 < C) {   // (channels come in whole groups of 8)
+                const float* source = x_image[i] + (ih * g.x_h + iw * g.x_w + c0 * g.x_c);
+                if (x_quads) {
+                    xv[i][0] = __ldg(reinterpret_cast<const float4*>(source));
+                    xv[i][1] = __ldg(reinterpret_cast<const float4*>(source) + 1);
+                } else {
+                    eight(source, g.x_c, xv[i]);
+                }
             }
         }
         wv[0] = wv[1] = zero;
         if (n0 + w_channel >= K || c0 + w_unit * 8 >= C) {
             // (a filter row or a channel group past the end: zeros, which add nothing)
-        } else if (g.w_n_major) {
-            const float* source = w_row + static_cast<int64_t>(c0) * g.w_stride;
-            wv[0] = make_float4(__ldg(source), __ldg(source + g.w_stride), __ldg(source + 2 * g.w_stride), __ldg(source + 3 * g.w_stride));
-            wv[1] = make_float4(__ldg(source + 4 * g.w_stride), __ldg(source + 5 * g.w_stride), __ldg(source + 6 * g.w_stride), __ldg(source + 7 * g.w_stride));
         } else {
-            const int filter_tap = a.reverse ? R * S - 1 - tap : tap;   // (a reversed filter meets input tap (r, s) with its tap (R-1-r, S-1-s))
-            const float4* source = reinterpret_cast<const float4*>(w_row + static_cast<int64_t>(filter_tap) * C + c0);
-            wv[0] = __ldg(source);
-            wv[1] = __ldg(source + 1);
+            // (a reversed filter meets input tap (r, s) with its tap (R-1-r, S-1-s))
+            const float* source = w_row + ((a.reverse ? R - 1 - r : r) * g.w_r + (a.reverse ? S - 1 - s : s) * g.w_s + c0 * g.w_c);
+            if (w_quads) {
+                wv[0] = __ldg(reinterpret_cast<const float4*>(source));
+                wv[1] = __ldg(reinterpret_cast<const float4*>(source) + 1);
+            } else {
+                eight(source, g.w_c, wv);
+            }
         }
     };
     float4 xv[2][2], wv[2];
@@ -220,7 +240,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 finite = split_eight(xv[i][0], xv[i][1], piece) && finite;
-                uint8_t* target = tiles + row[i] * 128 + ((unit16 ^ (row[i] & 7)) << 4);
+                uint8_t* target = tiles + row[i] * 128 + ((x_unit[i] ^ (row[i] & 7)) << 4);
 #pragma unroll
                 for (int j = 0; j < 3; ++j) *reinterpret_cast<uint4*>(target + j * kPieceBytesA) = piece[j];
             }
@@ -311,10 +331,13 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
     for (int z = 0; z < kMaxRanks; ++z) any_unsplittable |= z < ranks ? *reinterpret_cast<const int*>(inbox + z * chunk_bytes + rows_per_rank * kRowBytes) : 0;
     const int row_begin = rank * rows_per_rank, row_end = min(kTileM, row_begin + rows_per_rank);
     if (!any_unsplittable) {
-        for (int item = tid; item < (row_end - row_begin) * 16; item += kThreads) {
-            const int row = row_begin + (item >> 4), unit = item & 15;
-            const int m = m0 + row;
-            if (m >= g.m_total) continue;
+        // Y with contiguous channels: 16 neighbouring threads store one pixel's 64 channels as float4s. Any other Y (NCHW):
+        // neighbouring threads take neighbouring pixels and store their four channels one by one.
+        const int rows = row_end - row_begin;
+        for (int item = tid; item < rows * 16; item += kThreads) {
+            const int row = row_begin + (y_quads ? item >> 4 : item % rows), unit = y_quads ? item & 15 : item / rows;
+            const int m = m0 + row, k = n0 + unit * 4;
+            if (m >= g.m_total || k >= K) continue;   // (output channels come in whole groups of 4)
             const int offset = (row - row_begin) * kRowBytes + ((unit ^ (row & 7)) << 4);
             float4 part[kMaxRanks];
 #pragma unroll
@@ -329,17 +352,23 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
                 sum.z = __fadd_rn(sum.z, part[z].z);
                 sum.w = __fadd_rn(sum.w, part[z].w);
             }
-            const int k = n0 + unit * 4;
-            if (k >= K) continue;   // (output channels come in whole groups of 4)
+            const int line = static_cast<int>(fast_divide(m, g.by_q)), q = m - line * Q;
+            const int n = static_cast<int>(fast_divide(line, g.by_p)), p = line - n * P;
             if (a.epilogue.count > 0) {
-                const int line = static_cast<int>(fast_divide(m, g.by_q)), q = m - line * Q;
-                const int n = static_cast<int>(fast_divide(line, g.by_p)), p = line - n * P;
                 sum.x = apply_epilogue(sum.x, a, n, k, p, q);
                 sum.y = apply_epilogue(sum.y, a, n, k + 1, p, q);
                 sum.z = apply_epilogue(sum.z, a, n, k + 2, p, q);
                 sum.w = apply_epilogue(sum.w, a, n, k + 3, p, q);
             }
-            *reinterpret_cast<float4*>(g.y + static_cast<int64_t>(m) * g.y_pixel_stride + k) = sum;
+            float* target = g.y + (n * g.y_n + p * g.y_p + q * g.y_q + k * g.y_k);
+            if (y_quads) {
+                *reinterpret_cast<float4*>(target) = sum;
+            } else {
+                target[0] = sum.x;
+                target[g.y_k] = sum.y;
+                target[2 * g.y_k] = sum.z;
+                target[3 * g.y_k] = sum.w;
+            }
         }
     } else {
         // An infinity or a NaN among this tile's inputs: the same rows on the CUDA cores, every tap multiplied (zero
@@ -349,18 +378,17 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
             const int m = m0 + row;
             if (m >= g.m_total || k >= K) continue;
             const int q = m % Q, p = (m / Q) % P, n = m / (P * Q);
-            const float* filter = g.w_n_major ? g.w + k : g.w + static_cast<int64_t>(k) * g.w_stride;
-            const int64_t filter_step = g.w_n_major ? g.w_stride : 1;
+            const float* filter = g.w + k * g.w_k;
             float sum = 0.0f;
             for (int r = 0; r < R; ++r)
                 for (int s = 0; s < S; ++s) {
                     const int ih = p * a.stride_h - a.pad_h + r * a.dilation_h, iw = q * a.stride_w - a.pad_w + s * a.dilation_w;
                     const bool inside = ih >= 0 && ih < H && iw >= 0 && iw < W;
-                    const float* pixel = g.x + ((static_cast<int64_t>(n) * H + (inside ? ih : 0)) * W + (inside ? iw : 0)) * g.x_pixel_stride;
-                    const float* tap = filter + static_cast<int64_t>(a.reverse ? R * S - 1 - (r * S + s) : r * S + s) * C * filter_step;
-                    for (int c = 0; c < C; ++c) sum = fmaf(inside ? __ldg(pixel + c) : 0.0f, __ldg(tap + c * filter_step), sum);
+                    const float* pixel = g.x + (n * g.x_n + (inside ? ih : 0) * g.x_h + (inside ? iw : 0) * g.x_w);
+                    const float* tap = filter + ((a.reverse ? R - 1 - r : r) * g.w_r + (a.reverse ? S - 1 - s : s) * g.w_s);
+                    for (int c = 0; c < C; ++c) sum = fmaf(inside ? __ldg(pixel + c * g.x_c) : 0.0f, __ldg(tap + c * g.w_c), sum);
                 }
-            g.y[static_cast<int64_t>(m) * g.y_pixel_stride + k] = apply_epilogue(sum, a, n, k, p, q);
+            g.y[n * g.y_n + p * g.y_p + q * g.y_q + k * g.y_k] = apply_epilogue(sum, a, n, k, p, q);
         }
     }
     asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
@@ -386,12 +414,17 @@ void share_units(ClusterForm& form, int ranks) {
 bool cluster_form(const dfgpu_conv_params& p, ClusterForm& form) {
     if (p.x.dtype != DFGPU_F32 || p.w.dtype != DFGPU_F32 || p.y.dtype != DFGPU_F32) return false;
     if (p.x.rank != 4 || p.w.rank != 4 || p.y.rank != 4) return false;
-    auto packed = [](const dfgpu_tensor& t) {
-        return t.stride[1] == 1 && t.stride[3] == t.dim[1] && t.stride[2] == t.dim[3] * t.dim[1] && t.stride[0] == t.dim[2] * t.dim[3] * t.dim[1];
+    // any strides (channels-last, NCHW, padded rows ...), as long as every element lies within 2^31 floats of the first
+    auto reach = [](const dfgpu_tensor& t) {
+        int64_t last = 0;
+        for (int i = 0; i < t.rank; ++i) {
+            if (t.stride[i] < 0 || t.dim[i] <= 0) return int64_t{1} << 62;
+            last += (t.dim[i] - 1) * t.stride[i];
+        }
+        return last;
     };
-    if (!packed(p.x) || !packed(p.w) || !packed(p.y)) return false;
+    if (reach(p.x) >= (1ll << 31) || reach(p.w) >= (1ll << 31) || reach(p.y) >= (1ll << 31)) return false;
     if (p.x.dim[1] != p.w.dim[1] || p.x.dim[1] % 8 != 0 || p.y.dim[1] % 4 != 0 || p.w.dim[0] != p.y.dim[1]) return false;
-    if (element_count(p.x) >= (1ll << 31) || element_count(p.w) >= (1ll << 31) || element_count(p.y) >= (1ll << 31)) return false;
     const int64_t m_total = p.y.dim[0] * p.y.dim[2] * p.y.dim[3];
     const int64_t chunks = (p.x.dim[1] + kChunk - 1) / kChunk, tiles_n = (p.y.dim[1] + kTileN - 1) / kTileN;
     const int64_t tiles = (m_total + kTileM - 1) / kTileM * tiles_n;
@@ -425,7 +458,8 @@ const ClusterCapacity& cluster_capacity() {
     std::call_once(once[device], [device] {
         ClusterCapacity& c = table[device];
         c = ClusterCapacity{};
-        c.error = cudaFuncSetAttribute(umma_conv_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        c.error = cudaFuncSetAttribute(umma_conv_f32_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (c.error == cudaSuccess) c.error = cudaFuncSetAttribute(umma_conv_f32_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         for (int ranks = 1; ranks <= kMaxRanks && c.error == cudaSuccess; ++ranks) {
             cudaLaunchConfig_t config{};
             config.gridDim = dim3(ranks, 148, 1);
@@ -437,7 +471,7 @@ const ClusterCapacity& cluster_capacity() {
             attribute.val.clusterDim.y = attribute.val.clusterDim.z = 1;
             config.attrs = &attribute;
             config.numAttrs = 1;
-            c.error = cudaOccupancyMaxActiveClusters(&c.clusters[ranks], umma_conv_f32_kernel, &config);
+            c.error = cudaOccupancyMaxActiveClusters(&c.clusters[ranks], umma_conv_f32_kernel<false>, &config);   // (the same threads, registers bound and shared memory for both)
         }
     });
     return table[device];
@@ -453,6 +487,14 @@ static int launch_clusters(ClusterForm form, ClusterConvArgs g, const ConvArgs& 
     const int tiles = form.tiles_m * form.tiles_n;
     while (form.ranks > 1 && capacity.clusters[form.ranks] < tiles) share_units(form, form.ranks - 1);
     if (capacity.clusters[form.ranks] < 1) return fail(kExecutionFailed, "%s: the device cannot run a cluster of %d CTAs with %d bytes of shared memory", what, form.ranks, kSmemBytes);
+    // float4 accesses where the channels are contiguous and everything else falls on 16-byte boundaries
+    auto quads = [](const void* pointer, int32_t channel_stride, int32_t s0, int32_t s1, int32_t s2) {
+        return channel_stride == 1 && s0 % 4 == 0 && s1 % 4 == 0 && s2 % 4 == 0 && (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0;
+    };
+    g.x_quads = quads(g.x, g.x_c, g.x_n, g.x_h, g.x_w);
+    g.w_quads = quads(g.w, g.w_c, g.w_k, g.w_r, g.w_s);
+    g.y_quads = quads(g.y, g.y_k, g.y_n, g.y_p, g.y_q);
+    g.w_along_k = !g.w_quads && g.w_k == 1;
     g.units = form.units;
     g.units_per_rank = form.units_per_rank;
     g.chunks = form.chunks;
@@ -471,7 +513,8 @@ static int launch_clusters(ClusterForm form, ClusterConvArgs g, const ConvArgs& 
     attribute.val.clusterDim.y = attribute.val.clusterDim.z = 1;
     config.attrs = &attribute;
     config.numAttrs = 1;
-    cudaError_t error = cudaLaunchKernelEx(&config, umma_conv_f32_kernel, g, a);
+    const bool fast = g.x_quads && g.w_quads && g.y_quads;
+    cudaError_t error = fast ? cudaLaunchKernelEx(&config, umma_conv_f32_kernel<true>, g, a) : cudaLaunchKernelEx(&config, umma_conv_f32_kernel<false>, g, a);
     if (error != cudaSuccess) return fail(kExecutionFailed, "%s: cluster launch failed: %s", what, cudaGetErrorString(error));
     return check_launch(what);
 }
@@ -483,18 +526,16 @@ bool conv_f32_cluster_supported(const dfgpu_conv_params& p) {
 
 int launch_conv_f32_cluster(const dfgpu_conv_params& p, const ConvArgs& a, void* const* tensors, cudaStream_t stream) {
     ClusterForm form;
-    if (!cluster_form(p, form)) return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs packed channels-last f32 X, W and Y, one group, C a multiple of 8 and K of 4 and a reduction depth of at most 4096");
-    for (int i = 0; i < 3; ++i)
-        if ((reinterpret_cast<uintptr_t>(tensors[i]) & 15u) != 0) return fail(kInvalidArgument, "CONV_FPROP: the one-launch tcgen05 form needs 16-byte aligned X, W and Y");
+    if (!cluster_form(p, form)) return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs f32 X, W and Y, one group, C a multiple of 8 and K of 4 and a reduction depth of at most 4096");
     ClusterConvArgs g{};
     g.x = static_cast<const float*>(tensors[0]);
     g.w = static_cast<const float*>(tensors[1]);
     g.y = static_cast<float*>(tensors[2]);
     g.m_total = static_cast<int>(p.y.dim[0] * p.y.dim[2] * p.y.dim[3]);
-    g.x_pixel_stride = p.x.dim[1];
-    g.y_pixel_stride = p.y.dim[1];
-    g.w_stride = p.w.dim[1] * p.w.dim[2] * p.w.dim[3];
-    g.w_n_major = 0;
+    auto stride = [](const dfgpu_tensor& t, int axis) { return static_cast<int32_t>(t.dim[axis] == 1 ? 0 : t.stride[axis]); };   // (< 2^31: cluster_form)
+    g.x_n = stride(p.x, 0), g.x_c = stride(p.x, 1), g.x_h = stride(p.x, 2), g.x_w = stride(p.x, 3);
+    g.w_k = stride(p.w, 0), g.w_c = stride(p.w, 1), g.w_r = stride(p.w, 2), g.w_s = stride(p.w, 3);
+    g.y_n = stride(p.y, 0), g.y_k = stride(p.y, 1), g.y_p = stride(p.y, 2), g.y_q = stride(p.y, 3);
     return launch_clusters(form, g, a, "CONV_FPROP", stream);
 }
 
@@ -503,8 +544,8 @@ int launch_conv_f32_cluster(const dfgpu_conv_params& p, const ConvArgs& a, void*
 namespace {
 struct MatmulAsConv {
     ClusterForm form;
-    int64_t m, n, k, lda, ldb, ldc;
-    bool b_n_major;
+    int64_t m, n, k;
+    int64_t a_m, a_k, b_k, b_n, c_m, c_n;   // strides in floats
 };
 
 bool matmul_cluster_form(const dfgpu_matmul_params& p, MatmulAsConv& f) {
@@ -514,15 +555,16 @@ bool matmul_cluster_form(const dfgpu_matmul_params& p, MatmulAsConv& f) {
     for (int i = 0; i < rank - 2; ++i)
         if (p.c.dim[i] != 1 || p.a.dim[i] != 1 || p.b.dim[i] != 1) return false;
     f.m = p.c.dim[rank - 2], f.n = p.c.dim[rank - 1], f.k = p.a.dim[rank - 1];
-    f.lda = p.a.stride[rank - 2], f.ldc = p.c.stride[rank - 2];
     if (f.k % 8 != 0 || f.n % 4 != 0 || f.m >= (1ll << 24) || f.m <= 0) return false;
-    if (p.a.stride[rank - 1] != 1 || f.lda % 4 != 0 || f.lda < f.k) return false;
-    if (p.c.stride[rank - 1] != 1 || f.ldc % 4 != 0 || f.ldc < f.n) return false;
-    f.b_n_major = p.b.stride[rank - 1] == 1 && p.b.stride[rank - 2] >= f.n;
-    const bool b_k_major = !f.b_n_major && p.b.stride[rank - 2] == 1 && p.b.stride[rank - 1] % 4 == 0 && p.b.stride[rank - 1] >= f.k;
-    if (!f.b_n_major && !b_k_major) return false;
-    f.ldb = f.b_n_major ? p.b.stride[rank - 2] : p.b.stride[rank - 1];
-    if (f.m * f.lda >= (1ll << 31) || f.k * f.n >= (1ll << 31) || f.ldb * std::max(f.k, f.n) >= (1ll << 31) || f.m * f.ldc >= (1ll << 31)) return false;
+    f.a_m = p.a.stride[rank - 2], f.a_k = p.a.stride[rank - 1];
+    f.b_k = p.b.stride[rank - 2], f.b_n = p.b.stride[rank - 1];
+    f.c_m = p.c.stride[rank - 2], f.c_n = p.c.stride[rank - 1];
+    // any strides (either operand transposed, padded rows), every element within 2^31 floats of the first
+    for (int64_t stride : {f.a_m, f.a_k, f.b_k, f.b_n, f.c_m, f.c_n})
+        if (stride < 0) return false;
+    if ((f.m - 1) * f.a_m + (f.k - 1) * f.a_k >= (1ll << 31) || (f.k - 1) * f.b_k + (f.n - 1) * f.b_n >= (1ll << 31) ||
+        (f.m - 1) * f.c_m + (f.n - 1) * f.c_n >= (1ll << 31))
+        return false;
     const int64_t tiles_n = (f.n + kTileN - 1) / kTileN, units = (f.k + kChunk - 1) / kChunk;
     const int64_t tiles = (f.m + kTileM - 1) / kTileM * tiles_n;
     constexpr int kSms = 148;
@@ -542,23 +584,20 @@ bool matmul_f32_cluster_supported(const dfgpu_matmul_params& p) {
 
 int launch_matmul_f32_cluster(const dfgpu_matmul_params& p, void* const* tensors, cudaStream_t stream) {
     MatmulAsConv f;
-    if (!matmul_cluster_form(p, f)) return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs unbatched f32 A (K contiguous), B and C (N contiguous), K a multiple of 8 (at most 4096) and N of 4");
-    if ((reinterpret_cast<uintptr_t>(tensors[0]) & 15u) != 0 || (reinterpret_cast<uintptr_t>(tensors[2]) & 15u) != 0 ||
-        (!f.b_n_major && (reinterpret_cast<uintptr_t>(tensors[1]) & 15u) != 0))
-        return fail(kInvalidArgument, "MATMUL: the one-launch tcgen05 form needs 16-byte aligned A, B and C");
-    // The convolution's view of the problem: one image of 1 x M pixels; an epilogue operand [.., M, N] becomes [1, N, 1, M].
+    if (!matmul_cluster_form(p, f)) return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs unbatched f32 A, B and C, K a multiple of 8 (at most 4096) and N of 4");
+    // The convolution's view of the problem: one image of 1 x M pixels with K channels in and N out; an epilogue operand
+    // [.., M, N] becomes [1, N, 1, M].
     ConvArgs a{};
-    auto image = [](int64_t channels, int64_t pixels, int64_t pixel_stride) {
+    auto image = [](int64_t channels, int64_t pixels) {
         View v{};
         v.dtype = DFGPU_F32;
         v.rank = 4;
         v.dim[0] = 1, v.dim[1] = channels, v.dim[2] = 1, v.dim[3] = pixels;
-        v.stride[0] = pixels * pixel_stride, v.stride[1] = 1, v.stride[2] = pixels * pixel_stride, v.stride[3] = pixel_stride;
         return v;
     };
-    a.x = image(f.k, f.m, f.lda);
-    a.y = image(f.n, f.m, f.ldc);
-    a.w = image(f.k, 1, f.k);
+    a.x = image(f.k, f.m);
+    a.y = image(f.n, f.m);
+    a.w = image(f.k, 1);
     a.w.dim[0] = f.n;
     a.epilogue = make_epilogue(p.epilogue_count, p.epilogue);
     for (int i = 0; i < 2; ++i) {
@@ -581,10 +620,10 @@ int launch_matmul_f32_cluster(const dfgpu_matmul_params& p, void* const* tensors
     g.w = static_cast<const float*>(tensors[1]);
     g.y = static_cast<float*>(tensors[2]);
     g.m_total = static_cast<int>(f.m);
-    g.x_pixel_stride = f.lda;
-    g.y_pixel_stride = f.ldc;
-    g.w_stride = f.ldb;
-    g.w_n_major = f.b_n_major ? 1 : 0;
+    auto stride = [](int64_t extent, int64_t step) { return static_cast<int32_t>(extent == 1 ? 0 : step); };   // (< 2^31: matmul_cluster_form)
+    g.x_w = stride(f.m, f.a_m), g.x_c = stride(f.k, f.a_k);   // (one image, one row of pixels: the other strides are never multiplied by anything but 0)
+    g.w_k = stride(f.n, f.b_n), g.w_c = stride(f.k, f.b_k);
+    g.y_q = stride(f.m, f.c_m), g.y_k = stride(f.n, f.c_n);
     return launch_clusters(f.form, g, a, "MATMUL", stream);
 }
 

@@ -171,6 +171,11 @@ def test_conv_benchmark_shape_c1_both_layouts():
                               nhwc_strides(x_dims), nhwc_strides(w_dims), nhwc_strides(y_dims), seed=20261126)
     check_f32(out, ref)
     info, out, ref = run_conv(F32, x_dims, w_dims, [1, 1], [1, 1], [1, 1], [1, 1], dfgpu.CONV_AUTO, seed=20261126)
+    assert info.kernel == dfgpu.CONV_UMMA_F32X3_CLUSTER  # (the same one-launch tcgen05 kernel, reading and writing NCHW value by value)
+    check_f32(out, ref)
+    # mixed: channels-last X, NCHW filter and output
+    info, out, ref = run_conv(F32, x_dims, w_dims, [1, 1], [1, 1], [1, 1], [1, 1], dfgpu.CONV_AUTO, nhwc_strides(x_dims), seed=20261126)
+    assert info.kernel == dfgpu.CONV_UMMA_F32X3_CLUSTER
     check_f32(out, ref)
 
 
@@ -221,8 +226,8 @@ def test_conv_benchmark_shape_c1_in_one_launch_on_tensor_cores():
 
 
 def test_one_launch_forms_take_pointers_of_any_alignment():
-    """f32 arguments keep the reference's 4-byte alignment: with X (or A) 4 bytes off a 16-byte boundary the same call runs the CUDA-core
-    kernel and returns its result bit for bit."""
+    """f32 arguments keep the reference's 4-byte alignment: with X (or A) 4 bytes off a 16-byte boundary the one-launch kernel reads that
+    operand value by value instead of as float4s; the result agrees with the CUDA-core kernel's far inside the gate."""
     x_dims, w_dims, y_dims = [1, 64, 12, 12], [64, 64, 3, 3], [1, 64, 12, 12]
     x = synthetic.normal(9, 1, int(np.prod(x_dims))).astype(np.float32)
     w = synthetic.normal(9, 2, int(np.prod(w_dims)), std=0.05).astype(np.float32)
@@ -237,8 +242,9 @@ def test_one_launch_forms_take_pointers_of_any_alignment():
         p.kernel = kernel
         dy = g.device_zeros(int(np.prod(y_dims)) * 4, 0x5A)
         dfgpu.conv_fprop(p, g.ptr(shifted) + 4, g.ptr(dw), g.ptr(dy))
-        results[kernel] = g.to_host(dy, np.uint32).copy()
-    assert np.array_equal(results[dfgpu.CONV_IGEMM_FFMA], results[dfgpu.CONV_UMMA_F32X3_CLUSTER])
+        results[kernel] = g.to_host(dy, np.float32).copy()
+    assert float(np.max(np.abs(results[dfgpu.CONV_IGEMM_FFMA] - results[dfgpu.CONV_UMMA_F32X3_CLUSTER]))) <= 3e-5 * float(np.max(np.abs(results[dfgpu.CONV_IGEMM_FFMA])))
+    assert not np.array_equal(results[dfgpu.CONV_IGEMM_FFMA], results[dfgpu.CONV_UMMA_F32X3_CLUSTER])
     a = synthetic.normal(4, 1, 128 * 128).astype(np.float32)
     b = synthetic.normal(4, 2, 128 * 64).astype(np.float32)
     q = dfgpu.MatmulParams()
@@ -248,8 +254,9 @@ def test_one_launch_forms_take_pointers_of_any_alignment():
         q.kernel = kernel
         dc = g.device_zeros(128 * 64 * 4, 0x5A)
         dfgpu.matmul(q, g.ptr(da) + 4, g.ptr(db), g.ptr(dc))
-        results[kernel] = g.to_host(dc, np.uint32).copy()
-    assert np.array_equal(results[dfgpu.MATMUL_FFMA], results[dfgpu.MATMUL_UMMA_F32X3_CLUSTER])
+        results[kernel] = g.to_host(dc, np.float32).copy()
+    assert float(np.max(np.abs(results[dfgpu.MATMUL_FFMA] - results[dfgpu.MATMUL_UMMA_F32X3_CLUSTER]))) <= 2e-5 * float(np.max(np.abs(results[dfgpu.MATMUL_FFMA])))
+    assert not np.array_equal(results[dfgpu.MATMUL_FFMA], results[dfgpu.MATMUL_UMMA_F32X3_CLUSTER])
     assert dfgpu.device_status() == 0
 
 
@@ -467,6 +474,31 @@ def test_matmul_f32_in_one_launch_on_tensor_cores(a_dims, b_dims, b_strides):
     plain = np.maximum(ref.reshape(m, n) + bias[None, :], 0.0) + addend.reshape(m, n)
     check_f32(results[dfgpu.MATMUL_UMMA_F32X3_CLUSTER].reshape(m, n), plain)
     assert float(np.max(np.abs(results[dfgpu.MATMUL_UMMA_F32X3_CLUSTER] - results[dfgpu.MATMUL_FFMA]))) <= 2e-5 * float(np.max(np.abs(plain)))
+    assert dfgpu.device_status() == 0
+
+
+def test_matmul_f32_one_launch_form_with_other_strides():
+    """A stored transposed, rows of B padded to 130 floats (no 16-byte row pitch) and rows of C padded to 132: the one-launch kernel
+    reads A and B value by value and still stores C as float4s."""
+    m, k, n = 300, 256, 128
+    a_store = synthetic.normal(5, 1, k * m).astype(np.float32)            # [k, m]: A[i, j] = a_store[j * m + i]
+    b_store = synthetic.normal(5, 2, k * 130).astype(np.float32)          # [k, 130]
+    p = dfgpu.MatmulParams()
+    p.a, p.b, p.c = tensor(F32, [m, k], [1, m]), tensor(F32, [k, n], [130, 1]), tensor(F32, [m, n], [132, 1])
+    ref = (a_store.reshape(k, m).T.astype(np.float64) @ b_store.reshape(k, 130)[:, :n].astype(np.float64)).astype(np.float32)
+    da, db = g.to_device(a_store), g.to_device(b_store)
+    results = {}
+    for kernel in (dfgpu.MATMUL_AUTO, dfgpu.MATMUL_FFMA):
+        p.kernel = kernel
+        if kernel == dfgpu.MATMUL_AUTO:
+            assert dfgpu.query("matmul", p).kernel == dfgpu.MATMUL_UMMA_F32X3_CLUSTER
+        dc = g.device_zeros(m * 132 * 4, 0x5A)
+        dfgpu.matmul(p, g.ptr(da), g.ptr(db), g.ptr(dc))
+        stored = g.to_host(dc, np.float32).copy().reshape(m, 132)
+        assert np.all(stored[:, n:].view(np.uint32) == 0x5A5A5A5A)  # (the padding of C's rows is not touched)
+        results[kernel] = stored[:, :n]
+    check_f32(results[dfgpu.MATMUL_AUTO], ref)
+    assert float(np.max(np.abs(results[dfgpu.MATMUL_AUTO] - results[dfgpu.MATMUL_FFMA]))) <= 2e-5 * float(np.max(np.abs(ref)))
     assert dfgpu.device_status() == 0
 
 
