@@ -424,12 +424,13 @@ int choose_kernel(const dfgpu_conv_params& p, const ConvArgs& a, int& kernel) {
     // along K every one of them splits the same X rows again: the three-launch form splits them once).
     const int64_t pixel_tiles = (p.y.dim[0] * p.y.dim[2] * p.y.dim[3] + 127) / 128, channel_tiles = (p.y.dim[1] + 63) / 64;
     const bool one_launch_pays = automatic != DFGPU_CONV_UMMA_F32X3 || pixel_tiles * channel_tiles <= 148 || channel_tiles == 1;
-    if (cluster_ok && one_launch_pays && p.w.dim[1] * p.w.dim[2] * p.w.dim[3] >= kClusterFormMinDepth) automatic = DFGPU_CONV_UMMA_F32X3_CLUSTER;
+    if (automatic != DFGPU_CONV_UMMA_BF16 && cluster_ok && one_launch_pays && p.w.dim[1] * p.w.dim[2] * p.w.dim[3] >= kClusterFormMinDepth)
+        automatic = DFGPU_CONV_UMMA_F32X3_CLUSTER;   // (also what a bf16 or f16 convolution outside the bf16 tcgen05 kernel's shapes takes: stride, dilation, odd channel counts)
     kernel = p.kernel == DFGPU_CONV_AUTO ? automatic : p.kernel;
     if (kernel == DFGPU_CONV_UMMA_F32X3 && !split_ok)
         return fail(kUnsupported, "CONV_FPROP: the split-operand tcgen05 form needs packed channels-last f32 X, W and Y, C and K multiples of 64, stride 1, dilation 1");
     if (kernel == DFGPU_CONV_UMMA_F32X3_CLUSTER && !cluster_ok)
-        return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs f32 X, W and Y, one group, C a multiple of 8 and K of 4 and a reduction depth of at most 4096");
+        return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs FLOAT, HALF or BFLOAT16 X, W and Y, one group, C a multiple of 8 and K of 4 and a reduction depth of at most 4096");
     if (kernel != DFGPU_CONV_UMMA_BF16 && (p.x.dtype == DFGPU_BF16X2 || p.y.dtype == DFGPU_BF16X2))
         return fail(kUnsupported, "CONV_FPROP: split bf16 pair tensors are read and written by the tcgen05 kernel only");
     if (kernel == DFGPU_CONV_IGEMM_FFMA && a.groups != 1)

@@ -20,7 +20,9 @@
 // and which filter tap a loader thread reads. The tensors may have any strides: with contiguous channels on 16-byte
 // boundaries (channels-last X and Y, KRSC filter) a group of 8 channels is two float4 loads; otherwise (NCHW, a
 // transposed MATMUL operand, a pointer that is only 4-byte aligned) neighbouring threads take neighbouring pixels (or
-// output channels) and read their channels value by value, so that a warp's loads still fall side by side.
+// output channels) and read their channels value by value, so that a warp's loads still fall side by side. Read value by
+// value, the tensors may also be f16 or bf16 (widened to f32, whose lower pieces are then zero; Y narrowed on the store),
+// which gives strided, dilated and odd-sized convolutions of those types a tensor-core path too.
 //
 // A product with an infinite or NaN factor does not survive the split, so the loaders also record whether they saw
 // one; the ranks exchange that beside the partial tiles, and a cluster that saw one computes its tile on the CUDA cores
@@ -53,9 +55,10 @@ constexpr int kSmemBytes = kControlOffset + 128 + 1024;                    // (+
 constexpr int kAccumulatorColumns = 64;
 
 struct ClusterConvArgs {
-    const float* x;
-    const float* w;
-    float* y;
+    const void* x;
+    const void* w;
+    void* y;
+    int x_type, w_type, y_type;                   // DFGPU_F32, DFGPU_F16 or DFGPU_BF16 (the float4 accesses are for f32 only)
     int m_total, units, units_per_rank, chunks;   // chunks: 64-channel slices per filter tap
     // strides in floats; 32 bits are enough, and cheaper in the loaders: every element lies within 2^31 floats of the first
     int32_t x_n, x_c, x_h, x_w;                   // X by image, channel, row, column
@@ -92,6 +95,13 @@ __device__ __forceinline__ void halves_of(uint64_t pair, uint32_t& first, uint32
 }
 // The leading bf16 of an f32 bit pattern (cut off, not rounded), negated: what to add to take it away.
 __device__ __forceinline__ uint32_t minus_leading_bf16(uint32_t bits) { return (bits & 0xffff0000u) ^ 0x80000000u; }
+
+// One value of an f32, f16 or bf16 tensor.
+__device__ __forceinline__ float load_value(const void* data, int type, int offset) {
+    if (type == DFGPU_F32) return __ldg(static_cast<const float*>(data) + offset);
+    const uint16_t bits = __ldg(static_cast<const uint16_t*>(data) + offset);
+    return type == DFGPU_BF16 ? __uint_as_float(static_cast<uint32_t>(bits) << 16) : __half2float(__ushort_as_half(bits));
+}
 
 // Two consecutive f32 quads as three 16-byte groups of bf16 pieces (high, middle, low); false when a value is infinite or NaN.
 __device__ __forceinline__ bool split_eight(const float4& a, const float4& b, uint4 (&piece)[3]) {
@@ -146,7 +156,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
     const int row[2] = {x_quads ? tid >> 3 : tid & 127, x_quads ? 64 + (tid >> 3) : tid & 127};
     const int x_unit[2] = {x_quads ? tid & 7 : (tid >> 7) & 3, x_quads ? tid & 7 : 4 + ((tid >> 7) & 3)};
     int ih0[2], iw0[2];
-    const float* x_image[2];
+    int x_image[2];   // element offsets (everything lies within 2^31 elements of the first)
     bool live[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -157,16 +167,18 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         const int n = static_cast<int>(fast_divide(line, g.by_p)), p = line - n * P;
         ih0[i] = p * a.stride_h - a.pad_h;
         iw0[i] = q * a.stride_w - a.pad_w;
-        x_image[i] = g.x + (n * g.x_n + x_unit[i] * 8 * g.x_c);
+        x_image[i] = n * g.x_n + x_unit[i] * 8 * g.x_c;
     }
     // The filter tile: 64 output channels x 8 groups of 8 input channels. Stored with input channels contiguous, a thread
     // reads its group as two quads; stored with output channels contiguous, neighbouring threads take neighbouring output
     // channels and each reads its 8 input channels one by one.
     const int w_channel = w_along_k ? tid & 63 : tid >> 3, w_unit = w_along_k ? (tid >> 6) & 7 : tid & 7;
-    const float* w_row = g.w + (n0 + w_channel < K ? (n0 + w_channel) * g.w_k + w_unit * 8 * g.w_c : 0);   // (rows past the last filter are never read)
-    auto eight = [](const float* source, int stride, float4 (&v)[2]) {   // eight values `stride` floats apart
-        v[0] = make_float4(__ldg(source), __ldg(source + stride), __ldg(source + 2 * stride), __ldg(source + 3 * stride));
-        v[1] = make_float4(__ldg(source + 4 * stride), __ldg(source + 5 * stride), __ldg(source + 6 * stride), __ldg(source + 7 * stride));
+    const int w_row = n0 + w_channel < K ? (n0 + w_channel) * g.w_k + w_unit * 8 * g.w_c : 0;   // (rows past the last filter are never read)
+    auto eight = [](const void* data, int type, int first, int stride, float4 (&v)[2]) {   // eight values `stride` elements apart
+        v[0] = make_float4(load_value(data, type, first), load_value(data, type, first + stride), load_value(data, type, first + 2 * stride),
+                           load_value(data, type, first + 3 * stride));
+        v[1] = make_float4(load_value(data, type, first + 4 * stride), load_value(data, type, first + 5 * stride), load_value(data, type, first + 6 * stride),
+                           load_value(data, type, first + 7 * stride));
     };
     const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     auto fetch = [&](int u, float4 (&xv)[2][2], float4 (&wv)[2]) {
@@ -178,12 +190,12 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
             const int ih = ih0[i] + r * a.dilation_h, iw = iw0[i] + s * a.dilation_w;
             xv[i][0] = xv[i][1] = zero;
             if (live[i] && ih >= 0 && ih < H && iw >= 0 && iw < W && c0 + x_unit[i] * 8 < C) {   // (channels come in whole groups of 8)
-                const float* source = x_image[i] + (ih * g.x_h + iw * g.x_w + c0 * g.x_c);
+                const int source = x_image[i] + ih * g.x_h + iw * g.x_w + c0 * g.x_c;
                 if (x_quads) {
-                    xv[i][0] = __ldg(reinterpret_cast<const float4*>(source));
-                    xv[i][1] = __ldg(reinterpret_cast<const float4*>(source) + 1);
+                    xv[i][0] = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(g.x) + source));
+                    xv[i][1] = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(g.x) + source) + 1);
                 } else {
-                    eight(source, g.x_c, xv[i]);
+                    eight(g.x, g.x_type, source, g.x_c, xv[i]);
                 }
             }
         }
@@ -192,12 +204,12 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
             // (a filter row or a channel group past the end: zeros, which add nothing)
         } else {
             // (a reversed filter meets input tap (r, s) with its tap (R-1-r, S-1-s))
-            const float* source = w_row + ((a.reverse ? R - 1 - r : r) * g.w_r + (a.reverse ? S - 1 - s : s) * g.w_s + c0 * g.w_c);
+            const int source = w_row + (a.reverse ? R - 1 - r : r) * g.w_r + (a.reverse ? S - 1 - s : s) * g.w_s + c0 * g.w_c;
             if (w_quads) {
-                wv[0] = __ldg(reinterpret_cast<const float4*>(source));
-                wv[1] = __ldg(reinterpret_cast<const float4*>(source) + 1);
+                wv[0] = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(g.w) + source));
+                wv[1] = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(g.w) + source) + 1);
             } else {
-                eight(source, g.w_c, wv);
+                eight(g.w, g.w_type, source, g.w_c, wv);
             }
         }
     };
@@ -360,14 +372,14 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
                 sum.z = apply_epilogue(sum.z, a, n, k + 2, p, q);
                 sum.w = apply_epilogue(sum.w, a, n, k + 3, p, q);
             }
-            float* target = g.y + (n * g.y_n + p * g.y_p + q * g.y_q + k * g.y_k);
+            const int target = n * g.y_n + p * g.y_p + q * g.y_q + k * g.y_k;
             if (y_quads) {
-                *reinterpret_cast<float4*>(target) = sum;
+                *reinterpret_cast<float4*>(static_cast<float*>(g.y) + target) = sum;
             } else {
-                target[0] = sum.x;
-                target[g.y_k] = sum.y;
-                target[2 * g.y_k] = sum.z;
-                target[3 * g.y_k] = sum.w;
+                store_from_f32(g.y, g.y_type, target, sum.x);
+                store_from_f32(g.y, g.y_type, target + g.y_k, sum.y);
+                store_from_f32(g.y, g.y_type, target + 2 * g.y_k, sum.z);
+                store_from_f32(g.y, g.y_type, target + 3 * g.y_k, sum.w);
             }
         }
     } else {
@@ -378,17 +390,18 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
             const int m = m0 + row;
             if (m >= g.m_total || k >= K) continue;
             const int q = m % Q, p = (m / Q) % P, n = m / (P * Q);
-            const float* filter = g.w + k * g.w_k;
+            const int filter = k * g.w_k;
             float sum = 0.0f;
             for (int r = 0; r < R; ++r)
                 for (int s = 0; s < S; ++s) {
                     const int ih = p * a.stride_h - a.pad_h + r * a.dilation_h, iw = q * a.stride_w - a.pad_w + s * a.dilation_w;
                     const bool inside = ih >= 0 && ih < H && iw >= 0 && iw < W;
-                    const float* pixel = g.x + (n * g.x_n + (inside ? ih : 0) * g.x_h + (inside ? iw : 0) * g.x_w);
-                    const float* tap = filter + ((a.reverse ? R - 1 - r : r) * g.w_r + (a.reverse ? S - 1 - s : s) * g.w_s);
-                    for (int c = 0; c < C; ++c) sum = fmaf(inside ? __ldg(pixel + c * g.x_c) : 0.0f, __ldg(tap + c * g.w_c), sum);
+                    const int pixel = n * g.x_n + (inside ? ih : 0) * g.x_h + (inside ? iw : 0) * g.x_w;
+                    const int tap = filter + (a.reverse ? R - 1 - r : r) * g.w_r + (a.reverse ? S - 1 - s : s) * g.w_s;
+                    for (int c = 0; c < C; ++c)
+                        sum = fmaf(inside ? load_value(g.x, g.x_type, pixel + c * g.x_c) : 0.0f, load_value(g.w, g.w_type, tap + c * g.w_c), sum);
                 }
-            g.y[n * g.y_n + p * g.y_p + q * g.y_q + k * g.y_k] = apply_epilogue(sum, a, n, k, p, q);
+            store_from_f32(g.y, g.y_type, n * g.y_n + p * g.y_p + q * g.y_q + k * g.y_k, apply_epilogue(sum, a, n, k, p, q));
         }
     }
     asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
@@ -412,7 +425,8 @@ void share_units(ClusterForm& form, int ranks) {
 }
 
 bool cluster_form(const dfgpu_conv_params& p, ClusterForm& form) {
-    if (p.x.dtype != DFGPU_F32 || p.w.dtype != DFGPU_F32 || p.y.dtype != DFGPU_F32) return false;
+    auto plain_float = [](int type) { return type == DFGPU_F32 || type == DFGPU_F16 || type == DFGPU_BF16; };
+    if (!plain_float(p.x.dtype) || !plain_float(p.w.dtype) || !plain_float(p.y.dtype)) return false;
     if (p.x.rank != 4 || p.w.rank != 4 || p.y.rank != 4) return false;
     // any strides (channels-last, NCHW, padded rows ...), as long as every element lies within 2^31 floats of the first
     auto reach = [](const dfgpu_tensor& t) {
@@ -488,12 +502,12 @@ static int launch_clusters(ClusterForm form, ClusterConvArgs g, const ConvArgs& 
     while (form.ranks > 1 && capacity.clusters[form.ranks] < tiles) share_units(form, form.ranks - 1);
     if (capacity.clusters[form.ranks] < 1) return fail(kExecutionFailed, "%s: the device cannot run a cluster of %d CTAs with %d bytes of shared memory", what, form.ranks, kSmemBytes);
     // float4 accesses where the channels are contiguous and everything else falls on 16-byte boundaries
-    auto quads = [](const void* pointer, int32_t channel_stride, int32_t s0, int32_t s1, int32_t s2) {
-        return channel_stride == 1 && s0 % 4 == 0 && s1 % 4 == 0 && s2 % 4 == 0 && (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0;
+    auto quads = [](const void* pointer, int type, int32_t channel_stride, int32_t s0, int32_t s1, int32_t s2) {
+        return type == DFGPU_F32 && channel_stride == 1 && s0 % 4 == 0 && s1 % 4 == 0 && s2 % 4 == 0 && (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0;
     };
-    g.x_quads = quads(g.x, g.x_c, g.x_n, g.x_h, g.x_w);
-    g.w_quads = quads(g.w, g.w_c, g.w_k, g.w_r, g.w_s);
-    g.y_quads = quads(g.y, g.y_k, g.y_n, g.y_p, g.y_q);
+    g.x_quads = quads(g.x, g.x_type, g.x_c, g.x_n, g.x_h, g.x_w);
+    g.w_quads = quads(g.w, g.w_type, g.w_c, g.w_k, g.w_r, g.w_s);
+    g.y_quads = quads(g.y, g.y_type, g.y_k, g.y_n, g.y_p, g.y_q);
     g.w_along_k = !g.w_quads && g.w_k == 1;
     g.units = form.units;
     g.units_per_rank = form.units_per_rank;
@@ -526,11 +540,10 @@ bool conv_f32_cluster_supported(const dfgpu_conv_params& p) {
 
 int launch_conv_f32_cluster(const dfgpu_conv_params& p, const ConvArgs& a, void* const* tensors, cudaStream_t stream) {
     ClusterForm form;
-    if (!cluster_form(p, form)) return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs f32 X, W and Y, one group, C a multiple of 8 and K of 4 and a reduction depth of at most 4096");
+    if (!cluster_form(p, form)) return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs FLOAT, HALF or BFLOAT16 X, W and Y, one group, C a multiple of 8 and K of 4 and a reduction depth of at most 4096");
     ClusterConvArgs g{};
-    g.x = static_cast<const float*>(tensors[0]);
-    g.w = static_cast<const float*>(tensors[1]);
-    g.y = static_cast<float*>(tensors[2]);
+    g.x = tensors[0], g.w = tensors[1], g.y = tensors[2];
+    g.x_type = p.x.dtype, g.w_type = p.w.dtype, g.y_type = p.y.dtype;
     g.m_total = static_cast<int>(p.y.dim[0] * p.y.dim[2] * p.y.dim[3]);
     auto stride = [](const dfgpu_tensor& t, int axis) { return static_cast<int32_t>(t.dim[axis] == 1 ? 0 : t.stride[axis]); };   // (< 2^31: cluster_form)
     g.x_n = stride(p.x, 0), g.x_c = stride(p.x, 1), g.x_h = stride(p.x, 2), g.x_w = stride(p.x, 3);
@@ -549,7 +562,8 @@ struct MatmulAsConv {
 };
 
 bool matmul_cluster_form(const dfgpu_matmul_params& p, MatmulAsConv& f) {
-    if (p.a.dtype != DFGPU_F32 || p.b.dtype != DFGPU_F32 || p.c.dtype != DFGPU_F32 || p.a_scale.rank || p.b_scale.rank) return false;
+    auto plain_float = [](int type) { return type == DFGPU_F32 || type == DFGPU_F16 || type == DFGPU_BF16; };
+    if (!plain_float(p.a.dtype) || !plain_float(p.b.dtype) || !plain_float(p.c.dtype) || p.a_scale.rank || p.b_scale.rank) return false;
     const int rank = p.c.rank;
     if (rank < 2 || p.a.rank != rank || p.b.rank != rank) return false;
     for (int i = 0; i < rank - 2; ++i)
@@ -584,7 +598,7 @@ bool matmul_f32_cluster_supported(const dfgpu_matmul_params& p) {
 
 int launch_matmul_f32_cluster(const dfgpu_matmul_params& p, void* const* tensors, cudaStream_t stream) {
     MatmulAsConv f;
-    if (!matmul_cluster_form(p, f)) return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs unbatched f32 A, B and C, K a multiple of 8 (at most 4096) and N of 4");
+    if (!matmul_cluster_form(p, f)) return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs unbatched FLOAT, HALF or BFLOAT16 A, B and C, K a multiple of 8 (at most 4096) and N of 4");
     // The convolution's view of the problem: one image of 1 x M pixels with K channels in and N out; an epilogue operand
     // [.., M, N] becomes [1, N, 1, M].
     ConvArgs a{};
@@ -616,9 +630,8 @@ int launch_matmul_f32_cluster(const dfgpu_matmul_params& p, void* const* tensors
     a.c_per_group = f.k;
     a.k_per_group = f.n;
     ClusterConvArgs g{};
-    g.x = static_cast<const float*>(tensors[0]);
-    g.w = static_cast<const float*>(tensors[1]);
-    g.y = static_cast<float*>(tensors[2]);
+    g.x = tensors[0], g.w = tensors[1], g.y = tensors[2];
+    g.x_type = p.a.dtype, g.w_type = p.b.dtype, g.y_type = p.c.dtype;
     g.m_total = static_cast<int>(f.m);
     auto stride = [](int64_t extent, int64_t step) { return static_cast<int32_t>(extent == 1 ? 0 : step); };   // (< 2^31: matmul_cluster_form)
     g.x_w = stride(f.m, f.a_m), g.x_c = stride(f.k, f.a_k);   // (one image, one row of pixels: the other strides are never multiplied by anything but 0)

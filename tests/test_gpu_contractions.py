@@ -225,6 +225,42 @@ def test_conv_benchmark_shape_c1_in_one_launch_on_tensor_cores():
     assert dfgpu.device_status() == 0
 
 
+@pytest.mark.parametrize("dtype", [BF16, F32])
+def test_one_launch_form_for_convolutions_the_bf16_kernel_does_not_take(dtype):
+    """A stride-2 3 x 3 convolution, a dilated one and one with 24 -> 20 channels: AUTO resolves them to the one-launch tcgen05 kernel for
+    bf16 storage as for f32 (read value by value and widened), with bias + ReLU; a stride-1 64-channel bf16 convolution stays with the bf16
+    tcgen05 kernel."""
+    for x_dims, w_dims, pad, stride, dilation in (([2, 64, 28, 28], [64, 64, 3, 3], 1, 2, 1), ([1, 64, 20, 17], [128, 64, 3, 3], 2, 1, 2),
+                                                  ([3, 24, 12, 12], [20, 24, 3, 3], 1, 1, 1)):
+        n, c, h, w = x_dims
+        k = w_dims[0]
+        out_h = (h + 2 * pad - (dilation * 2 + 1)) // stride + 1
+        out_w = (w + 2 * pad - (dilation * 2 + 1)) // stride + 1
+        bias = synthetic.uniform(3, 5, k, -0.1, 0.1)
+        info, out, ref = run_conv(dtype, x_dims, w_dims, [pad, pad], [pad, pad], [stride, stride], [dilation, dilation], dfgpu.CONV_AUTO,
+                                  nhwc_strides(x_dims), nhwc_strides(w_dims), nhwc_strides([n, k, out_h, out_w]), seed=13,
+                                  epilogue=[step(dfgpu.EPI_ADD, 0), step(dfgpu.EPI_RELU)], extras=[([1, k, 1, 1], [k, 1, k, k], bias)])
+        assert info.kernel == dfgpu.CONV_UMMA_F32X3_CLUSTER and info.launches == 1 and info.scratch_bytes == 0
+        (check_f32 if dtype == F32 else check_bf16)(out, ref)
+    if dtype == BF16:
+        x_dims, w_dims = [2, 64, 14, 14], [64, 64, 3, 3]
+        info, out, ref = run_conv(BF16, x_dims, w_dims, [1, 1], [1, 1], [1, 1], [1, 1], dfgpu.CONV_AUTO,
+                                  nhwc_strides(x_dims), nhwc_strides(w_dims), nhwc_strides([2, 64, 14, 14]))
+        assert info.kernel == dfgpu.CONV_UMMA_BF16
+        check_bf16(out, ref)
+    assert dfgpu.device_status() == 0
+
+
+def test_matmul_bf16_odd_shape_in_one_launch_on_tensor_cores():
+    """A bf16 product the bf16 tcgen05 matmul does not take (M = 100, K = 136, N = 68) runs on the one-launch kernel."""
+    out, ref = run_matmul(BF16, [100, 136], [136, 68], kernel=dfgpu.MATMUL_AUTO)
+    check_bf16(out, ref)
+    p = dfgpu.MatmulParams()
+    p.a, p.b, p.c = tensor(BF16, [100, 136]), tensor(BF16, [136, 68]), tensor(BF16, [100, 68])
+    assert dfgpu.query("matmul", p).kernel == dfgpu.MATMUL_UMMA_F32X3_CLUSTER
+    assert dfgpu.device_status() == 0
+
+
 def test_one_launch_forms_take_pointers_of_any_alignment():
     """f32 arguments keep the reference's 4-byte alignment: with X (or A) 4 bytes off a 16-byte boundary the one-launch kernel reads that
     operand value by value instead of as float4s; the result agrees with the CUDA-core kernel's far inside the gate."""
