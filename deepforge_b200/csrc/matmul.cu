@@ -268,7 +268,7 @@ int choose_kernel(const dfgpu_matmul_params& p, int& kernel) {
     if (kernel < DFGPU_MATMUL_FFMA || kernel > DFGPU_MATMUL_UMMA_F32X3_CLUSTER) return fail(kInvalidArgument, "MATMUL: unknown kernel id %d", kernel);
     if (kernel == DFGPU_MATMUL_UMMA_F32X3_CLUSTER) {
         if (!matmul_f32_cluster_supported(p))
-            return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs unbatched FLOAT, HALF or BFLOAT16 A, B and C, K a multiple of 8 (at most 4096) and N of 4");
+            return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs FLOAT, HALF or BFLOAT16 A, B and C and at most one batch axis");
         return kOk;
     }
     if (kernel == DFGPU_MATMUL_UMMA_F32X3) {

@@ -60,6 +60,9 @@ struct ClusterConvArgs {
     void* y;
     int x_type, w_type, y_type;                   // DFGPU_F32, DFGPU_F16 or DFGPU_BF16 (the float4 accesses are for f32 only)
     int m_total, units, units_per_rank, chunks;   // chunks: 64-channel slices per filter tap
+    int tiles_per_image;                          // 0: tiles run over all pixels of all images; else over one image each, and the
+    int32_t w_n;                                  // filter of image n starts w_n elements further on (a batched MATMUL's B)
+    FastDivisor by_tiles;                         // tiles_per_image
     // strides in floats; 32 bits are enough, and cheaper in the loaders: every element lies within 2^31 floats of the first
     int32_t x_n, x_c, x_h, x_w;                   // X by image, channel, row, column
     int32_t w_k, w_c, w_r, w_s;                   // the filter by output channel, input channel, tap row, tap column
@@ -142,7 +145,16 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
     const uint32_t inbox_bar = empty_bar + 8 * kBuffers;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kControlOffset + 16 * kBuffers + 8);
 
-    const int m0 = blockIdx.y * kTileM, n0 = blockIdx.z * kTileN;
+    // The tile's first row as a pixel index over all images, and how many of its 128 rows exist.
+    const int n0 = blockIdx.z * kTileN;
+    int m0 = blockIdx.y * kTileM, rows_live = min(kTileM, g.m_total - m0), filter_first = 0;
+    if (g.tiles_per_image > 0) {
+        const int image = static_cast<int>(fast_divide(blockIdx.y, g.by_tiles)), first = (static_cast<int>(blockIdx.y) - image * g.tiles_per_image) * kTileM;
+        const int pixels = static_cast<int>(a.y.dim[2] * a.y.dim[3]);
+        m0 = image * pixels + first;
+        rows_live = min(kTileM, pixels - first);
+        filter_first = image * g.w_n;
+    }
     const int first_unit = rank * g.units_per_rank;
     const int my_units = max(0, min(g.units - first_unit, g.units_per_rank));
     const int P = static_cast<int>(a.y.dim[2]), Q = static_cast<int>(a.y.dim[3]), K = static_cast<int>(a.y.dim[1]);
@@ -161,7 +173,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int m = m0 + row[i];
-        live[i] = m < g.m_total;
+        live[i] = row[i] < rows_live;
         const int mm = live[i] ? m : 0;
         const int line = static_cast<int>(fast_divide(mm, g.by_q)), q = mm - line * Q;
         const int n = static_cast<int>(fast_divide(line, g.by_p)), p = line - n * P;
@@ -173,12 +185,13 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
     // reads its group as two quads; stored with output channels contiguous, neighbouring threads take neighbouring output
     // channels and each reads its 8 input channels one by one.
     const int w_channel = w_along_k ? tid & 63 : tid >> 3, w_unit = w_along_k ? (tid >> 6) & 7 : tid & 7;
-    const int w_row = n0 + w_channel < K ? (n0 + w_channel) * g.w_k + w_unit * 8 * g.w_c : 0;   // (rows past the last filter are never read)
-    auto eight = [](const void* data, int type, int first, int stride, float4 (&v)[2]) {   // eight values `stride` elements apart
-        v[0] = make_float4(load_value(data, type, first), load_value(data, type, first + stride), load_value(data, type, first + 2 * stride),
-                           load_value(data, type, first + 3 * stride));
-        v[1] = make_float4(load_value(data, type, first + 4 * stride), load_value(data, type, first + 5 * stride), load_value(data, type, first + 6 * stride),
-                           load_value(data, type, first + 7 * stride));
+    const int w_row = filter_first + (n0 + w_channel < K ? (n0 + w_channel) * g.w_k + w_unit * 8 * g.w_c : 0);   // (rows past the last filter are never read)
+    auto eight = [](const void* data, int type, int first, int stride, int count, float4 (&v)[2]) {   // `count` (of eight) values `stride` elements apart, zeros behind them
+        float value[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) value[j] = j < count ? load_value(data, type, first + j * stride) : 0.0f;
+        v[0] = make_float4(value[0], value[1], value[2], value[3]);
+        v[1] = make_float4(value[4], value[5], value[6], value[7]);
     };
     const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     auto fetch = [&](int u, float4 (&xv)[2][2], float4 (&wv)[2]) {
@@ -195,7 +208,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
                     xv[i][0] = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(g.x) + source));
                     xv[i][1] = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(g.x) + source) + 1);
                 } else {
-                    eight(g.x, g.x_type, source, g.x_c, xv[i]);
+                    eight(g.x, g.x_type, source, g.x_c, C - (c0 + x_unit[i] * 8), xv[i]);
                 }
             }
         }
@@ -209,7 +222,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
                 wv[0] = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(g.w) + source));
                 wv[1] = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(g.w) + source) + 1);
             } else {
-                eight(g.w, g.w_type, source, g.w_c, wv);
+                eight(g.w, g.w_type, source, g.w_c, C - (c0 + w_unit * 8), wv);
             }
         }
     };
@@ -349,7 +362,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         for (int item = tid; item < rows * 16; item += kThreads) {
             const int row = row_begin + (y_quads ? item >> 4 : item % rows), unit = y_quads ? item & 15 : item / rows;
             const int m = m0 + row, k = n0 + unit * 4;
-            if (m >= g.m_total || k >= K) continue;   // (output channels come in whole groups of 4)
+            if (row >= rows_live || k >= K) continue;
             const int offset = (row - row_begin) * kRowBytes + ((unit ^ (row & 7)) << 4);
             float4 part[kMaxRanks];
 #pragma unroll
@@ -377,9 +390,9 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
                 *reinterpret_cast<float4*>(static_cast<float*>(g.y) + target) = sum;
             } else {
                 store_from_f32(g.y, g.y_type, target, sum.x);
-                store_from_f32(g.y, g.y_type, target + g.y_k, sum.y);
-                store_from_f32(g.y, g.y_type, target + 2 * g.y_k, sum.z);
-                store_from_f32(g.y, g.y_type, target + 3 * g.y_k, sum.w);
+                if (k + 1 < K) store_from_f32(g.y, g.y_type, target + g.y_k, sum.y);
+                if (k + 2 < K) store_from_f32(g.y, g.y_type, target + 2 * g.y_k, sum.z);
+                if (k + 3 < K) store_from_f32(g.y, g.y_type, target + 3 * g.y_k, sum.w);
             }
         }
     } else {
@@ -388,9 +401,9 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         for (int item = tid; item < (row_end - row_begin) * kTileN; item += kThreads) {
             const int row = row_begin + item / kTileN, k = n0 + item % kTileN;
             const int m = m0 + row;
-            if (m >= g.m_total || k >= K) continue;
+            if (row >= rows_live || k >= K) continue;
             const int q = m % Q, p = (m / Q) % P, n = m / (P * Q);
-            const int filter = k * g.w_k;
+            const int filter = filter_first + k * g.w_k;
             float sum = 0.0f;
             for (int r = 0; r < R; ++r)
                 for (int s = 0; s < S; ++s) {
@@ -438,13 +451,13 @@ bool cluster_form(const dfgpu_conv_params& p, ClusterForm& form) {
         return last;
     };
     if (reach(p.x) >= (1ll << 31) || reach(p.w) >= (1ll << 31) || reach(p.y) >= (1ll << 31)) return false;
-    if (p.x.dim[1] != p.w.dim[1] || p.x.dim[1] % 8 != 0 || p.y.dim[1] % 4 != 0 || p.w.dim[0] != p.y.dim[1]) return false;
+    if (p.x.dim[1] != p.w.dim[1] || p.w.dim[0] != p.y.dim[1]) return false;   // (one group)
     const int64_t m_total = p.y.dim[0] * p.y.dim[2] * p.y.dim[3];
     const int64_t chunks = (p.x.dim[1] + kChunk - 1) / kChunk, tiles_n = (p.y.dim[1] + kTileN - 1) / kTileN;
     const int64_t tiles = (m_total + kTileM - 1) / kTileM * tiles_n;
     const int64_t units = p.w.dim[2] * p.w.dim[3] * chunks;
     constexpr int kSms = 148;   // (a query has no device: the count this library is built for)
-    if ((m_total + kTileM - 1) / kTileM > 65535 || tiles_n > 65535 || units > kMaxUnitsPerRank) return false;   // (grid extents; units one CTA walks)
+    if ((m_total + kTileM - 1) / kTileM > 65535 || tiles_n > 65535) return false;   // (grid extents)
     form.tiles_m = static_cast<int>((m_total + kTileM - 1) / kTileM);
     form.tiles_n = static_cast<int>(tiles_n);
     form.units = static_cast<int>(units);
@@ -502,12 +515,13 @@ static int launch_clusters(ClusterForm form, ClusterConvArgs g, const ConvArgs& 
     while (form.ranks > 1 && capacity.clusters[form.ranks] < tiles) share_units(form, form.ranks - 1);
     if (capacity.clusters[form.ranks] < 1) return fail(kExecutionFailed, "%s: the device cannot run a cluster of %d CTAs with %d bytes of shared memory", what, form.ranks, kSmemBytes);
     // float4 accesses where the channels are contiguous and everything else falls on 16-byte boundaries
-    auto quads = [](const void* pointer, int type, int32_t channel_stride, int32_t s0, int32_t s1, int32_t s2) {
-        return type == DFGPU_F32 && channel_stride == 1 && s0 % 4 == 0 && s1 % 4 == 0 && s2 % 4 == 0 && (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0;
+    auto quads = [](const void* pointer, int type, int64_t channels, int group, int32_t channel_stride, int32_t s0, int32_t s1, int32_t s2, int32_t s3) {
+        return type == DFGPU_F32 && channels % group == 0 && channel_stride == 1 && s0 % 4 == 0 && s1 % 4 == 0 && s2 % 4 == 0 && s3 % 4 == 0 &&
+               (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0;
     };
-    g.x_quads = quads(g.x, g.x_type, g.x_c, g.x_n, g.x_h, g.x_w);
-    g.w_quads = quads(g.w, g.w_type, g.w_c, g.w_k, g.w_r, g.w_s);
-    g.y_quads = quads(g.y, g.y_type, g.y_k, g.y_n, g.y_p, g.y_q);
+    g.x_quads = quads(g.x, g.x_type, a.x.dim[1], 8, g.x_c, g.x_n, g.x_h, g.x_w, 0);
+    g.w_quads = quads(g.w, g.w_type, a.x.dim[1], 8, g.w_c, g.w_k, g.w_r, g.w_s, g.w_n);
+    g.y_quads = quads(g.y, g.y_type, a.y.dim[1], 4, g.y_k, g.y_n, g.y_p, g.y_q, 0);
     g.w_along_k = !g.w_quads && g.w_k == 1;
     g.units = form.units;
     g.units_per_rank = form.units_per_rank;
@@ -516,6 +530,7 @@ static int launch_clusters(ClusterForm form, ClusterConvArgs g, const ConvArgs& 
     g.by_p = make_fast_divisor(static_cast<uint32_t>(a.y.dim[2]));
     g.by_chunks = make_fast_divisor(static_cast<uint32_t>(form.chunks));
     g.by_s = make_fast_divisor(static_cast<uint32_t>(a.w.dim[3]));
+    g.by_tiles = make_fast_divisor(static_cast<uint32_t>(std::max(1, g.tiles_per_image)));
     cudaLaunchConfig_t config{};
     config.gridDim = dim3(form.ranks, form.tiles_m, form.tiles_n);
     config.blockDim = dim3(kThreads);
@@ -540,7 +555,7 @@ bool conv_f32_cluster_supported(const dfgpu_conv_params& p) {
 
 int launch_conv_f32_cluster(const dfgpu_conv_params& p, const ConvArgs& a, void* const* tensors, cudaStream_t stream) {
     ClusterForm form;
-    if (!cluster_form(p, form)) return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs FLOAT, HALF or BFLOAT16 X, W and Y, one group, C a multiple of 8 and K of 4 and a reduction depth of at most 4096");
+    if (!cluster_form(p, form)) return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs FLOAT, HALF or BFLOAT16 X, W and Y and one group");
     ClusterConvArgs g{};
     g.x = tensors[0], g.w = tensors[1], g.y = tensors[2];
     g.x_type = p.x.dtype, g.w_type = p.w.dtype, g.y_type = p.y.dtype;
@@ -557,8 +572,10 @@ int launch_conv_f32_cluster(const dfgpu_conv_params& p, const ConvArgs& a, void*
 namespace {
 struct MatmulAsConv {
     ClusterForm form;
-    int64_t m, n, k;
-    int64_t a_m, a_k, b_k, b_n, c_m, c_n;   // strides in floats
+    int64_t m, n, k, batch;
+    int batch_axis;                          // the one batch axis of extent > 1 (-1: none)
+    int64_t a_m, a_k, b_k, b_n, c_m, c_n;   // strides in elements
+    int64_t a_b, b_b, c_b;                  // ... of the batch axis (0 where the operand is broadcast)
 };
 
 bool matmul_cluster_form(const dfgpu_matmul_params& p, MatmulAsConv& f) {
@@ -566,24 +583,32 @@ bool matmul_cluster_form(const dfgpu_matmul_params& p, MatmulAsConv& f) {
     if (!plain_float(p.a.dtype) || !plain_float(p.b.dtype) || !plain_float(p.c.dtype) || p.a_scale.rank || p.b_scale.rank) return false;
     const int rank = p.c.rank;
     if (rank < 2 || p.a.rank != rank || p.b.rank != rank) return false;
-    for (int i = 0; i < rank - 2; ++i)
-        if (p.c.dim[i] != 1 || p.a.dim[i] != 1 || p.b.dim[i] != 1) return false;
+    f.batch = 1, f.batch_axis = -1, f.a_b = f.b_b = f.c_b = 0;
+    for (int i = 0; i < rank - 2; ++i) {
+        if (p.c.dim[i] == 1) continue;
+        if (f.batch_axis >= 0) return false;   // (one batch axis: each image of the convolution is one matrix)
+        f.batch_axis = i;
+        f.batch = p.c.dim[i];
+        f.a_b = p.a.dim[i] == 1 ? 0 : p.a.stride[i];
+        f.b_b = p.b.dim[i] == 1 ? 0 : p.b.stride[i];
+        f.c_b = p.c.stride[i];
+    }
     f.m = p.c.dim[rank - 2], f.n = p.c.dim[rank - 1], f.k = p.a.dim[rank - 1];
-    if (f.k % 8 != 0 || f.n % 4 != 0 || f.m >= (1ll << 24) || f.m <= 0) return false;
+    if (f.m >= (1ll << 24) || f.m <= 0 || f.n <= 0 || f.k <= 0) return false;
     f.a_m = p.a.stride[rank - 2], f.a_k = p.a.stride[rank - 1];
     f.b_k = p.b.stride[rank - 2], f.b_n = p.b.stride[rank - 1];
     f.c_m = p.c.stride[rank - 2], f.c_n = p.c.stride[rank - 1];
-    // any strides (either operand transposed, padded rows), every element within 2^31 floats of the first
-    for (int64_t stride : {f.a_m, f.a_k, f.b_k, f.b_n, f.c_m, f.c_n})
+    // any strides (either operand transposed, padded rows), every element within 2^31 elements of the first
+    for (int64_t stride : {f.a_m, f.a_k, f.b_k, f.b_n, f.c_m, f.c_n, f.a_b, f.b_b, f.c_b})
         if (stride < 0) return false;
-    if ((f.m - 1) * f.a_m + (f.k - 1) * f.a_k >= (1ll << 31) || (f.k - 1) * f.b_k + (f.n - 1) * f.b_n >= (1ll << 31) ||
-        (f.m - 1) * f.c_m + (f.n - 1) * f.c_n >= (1ll << 31))
+    if ((f.batch - 1) * f.a_b + (f.m - 1) * f.a_m + (f.k - 1) * f.a_k >= (1ll << 31) || (f.batch - 1) * f.b_b + (f.k - 1) * f.b_k + (f.n - 1) * f.b_n >= (1ll << 31) ||
+        (f.batch - 1) * f.c_b + (f.m - 1) * f.c_m + (f.n - 1) * f.c_n >= (1ll << 31) || f.batch * f.m >= (1ll << 31))
         return false;
-    const int64_t tiles_n = (f.n + kTileN - 1) / kTileN, units = (f.k + kChunk - 1) / kChunk;
-    const int64_t tiles = (f.m + kTileM - 1) / kTileM * tiles_n;
+    const int64_t tiles_m = f.batch * ((f.m + kTileM - 1) / kTileM), tiles_n = (f.n + kTileN - 1) / kTileN, units = (f.k + kChunk - 1) / kChunk;
+    const int64_t tiles = tiles_m * tiles_n;
     constexpr int kSms = 148;
-    if ((f.m + kTileM - 1) / kTileM > 65535 || tiles_n > 65535 || units > kMaxUnitsPerRank) return false;
-    f.form.tiles_m = static_cast<int>((f.m + kTileM - 1) / kTileM);
+    if (tiles_m > 65535 || tiles_n > 65535) return false;
+    f.form.tiles_m = static_cast<int>(tiles_m);
     f.form.tiles_n = static_cast<int>(tiles_n);
     f.form.units = f.form.chunks = static_cast<int>(units);
     share_units(f.form, static_cast<int>(std::min<int64_t>(std::min<int64_t>(kMaxRanks, units), std::max<int64_t>(1, kSms / tiles))));
@@ -598,7 +623,7 @@ bool matmul_f32_cluster_supported(const dfgpu_matmul_params& p) {
 
 int launch_matmul_f32_cluster(const dfgpu_matmul_params& p, void* const* tensors, cudaStream_t stream) {
     MatmulAsConv f;
-    if (!matmul_cluster_form(p, f)) return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs unbatched FLOAT, HALF or BFLOAT16 A, B and C, K a multiple of 8 (at most 4096) and N of 4");
+    if (!matmul_cluster_form(p, f)) return fail(kUnsupported, "MATMUL: the one-launch tcgen05 form needs FLOAT, HALF or BFLOAT16 A, B and C and at most one batch axis");
     // The convolution's view of the problem: one image of 1 x M pixels with K channels in and N out; an epilogue operand
     // [.., M, N] becomes [1, N, 1, M].
     ConvArgs a{};
@@ -611,6 +636,7 @@ int launch_matmul_f32_cluster(const dfgpu_matmul_params& p, void* const* tensors
     };
     a.x = image(f.k, f.m);
     a.y = image(f.n, f.m);
+    a.x.dim[0] = a.y.dim[0] = f.batch;   // (one image per matrix of the batch)
     a.w = image(f.k, 1);
     a.w.dim[0] = f.n;
     a.epilogue = make_epilogue(p.epilogue_count, p.epilogue);
@@ -622,6 +648,8 @@ int launch_matmul_f32_cluster(const dfgpu_matmul_params& p, void* const* tensors
         for (int d = 0; d < 4; ++d) v.dim[d] = 1;
         if (t.rank >= 1) v.dim[1] = t.dim[t.rank - 1], v.stride[1] = t.stride[t.rank - 1];
         if (t.rank >= 2) v.dim[3] = t.dim[t.rank - 2], v.stride[3] = t.stride[t.rank - 2];
+        const int own_axis = f.batch_axis - (p.c.rank - t.rank);   // the operand's axis under C's batch axis
+        if (f.batch_axis >= 0 && own_axis >= 0) v.dim[0] = t.dim[own_axis], v.stride[0] = t.stride[own_axis];
         a.extra[i] = v;
         a.extra_data[i] = tensors[5 + i];
     }
@@ -632,7 +660,11 @@ int launch_matmul_f32_cluster(const dfgpu_matmul_params& p, void* const* tensors
     ClusterConvArgs g{};
     g.x = tensors[0], g.w = tensors[1], g.y = tensors[2];
     g.x_type = p.a.dtype, g.w_type = p.b.dtype, g.y_type = p.c.dtype;
-    g.m_total = static_cast<int>(f.m);
+    g.m_total = static_cast<int>(f.batch * f.m);
+    if (f.batch > 1) {
+        g.tiles_per_image = static_cast<int>((f.m + kTileM - 1) / kTileM);
+        g.x_n = static_cast<int32_t>(f.a_b), g.y_n = static_cast<int32_t>(f.c_b), g.w_n = static_cast<int32_t>(f.b_b);
+    }
     auto stride = [](int64_t extent, int64_t step) { return static_cast<int32_t>(extent == 1 ? 0 : step); };   // (< 2^31: matmul_cluster_form)
     g.x_w = stride(f.m, f.a_m), g.x_c = stride(f.k, f.a_k);   // (one image, one row of pixels: the other strides are never multiplied by anything but 0)
     g.w_k = stride(f.n, f.b_n), g.w_c = stride(f.k, f.b_k);

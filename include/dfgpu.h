@@ -166,7 +166,7 @@ enum {
                                    a thread-block cluster per tile shares the filter taps out
                                    between its CTAs, which split X and W on their way into shared memory and add their
                                    partial tiles through distributed shared memory; a cluster whose inputs hold an
-                                   infinity or a NaN computes its tile on the CUDA cores. No scratch. One group, C a multiple of 8, K of 4;
+                                   infinity or a NaN computes its tile on the CUDA cores. No scratch. One group, any channel counts;
                                    any stride, dilation, padding, filter reversal; any tensor strides (channels-last and 16-byte
                                    aligned is the fast case: float4 accesses; NCHW or a 4-byte aligned pointer works value by
                                    value), so f32 arguments keep the reference's 4-byte alignment. HALF and BFLOAT16 tensors are taken too
@@ -215,8 +215,8 @@ int dfgpu_conv_fprop_pair(const dfgpu_conv_pair_params*, void* const* tensors, v
    needs scratch, three launches (split, the bf16 matmul over 6K, and the CUDA-core kernel again, which returns at once
    unless A or B held an infinity or a NaN).
    UMMA_F32X3_CLUSTER: the same six products in ONE launch without scratch, made for unbatched products of at most 148 output
-   tiles (128 x 64; more tiles run one CTA each, K at most 4096): the kernel of DFGPU_CONV_UMMA_F32X3_CLUSTER run on the 1 x 1 convolution of M pixels (K a multiple
-   of 8, N of 4, any strides of A, B and C, 4-byte aligned pointers; HALF and BFLOAT16 matrices value by value). */
+   tiles (128 x 64; more tiles run one CTA each, K at most 4096 then), at most one batch axis: the kernel of DFGPU_CONV_UMMA_F32X3_CLUSTER run on the 1 x 1 convolution of M pixels (K a multiple
+   of 8, N of 4 for float4 accesses, any strides of A, B and C, 4-byte aligned pointers; HALF and BFLOAT16 matrices value by value). */
 enum { DFGPU_MATMUL_AUTO = 0, DFGPU_MATMUL_FFMA = 1, DFGPU_MATMUL_UMMA_BF16 = 2, DFGPU_MATMUL_UMMA_MXF8 = 3, DFGPU_MATMUL_UMMA_F32X3 = 4,
        DFGPU_MATMUL_UMMA_F32X3_CLUSTER = 5 };
 typedef struct dfgpu_matmul_params {

@@ -197,7 +197,9 @@ def test_conv_benchmark_shape_c1_in_one_launch_on_tensor_cores():
              # channel counts that do not fill a 64-channel unit or a 64-channel tile (C a multiple of 8, K of 4): zero-filled
              ([1, 32, 32, 32], [32, 32, 3, 3], 1), ([2, 72, 9, 9], [20, 72, 3, 3], 1), ([1, 8, 10, 10], [4, 8, 5, 5], 2), ([3, 136, 6, 5], [132, 136, 1, 1], 0),
              # more tiles than SMs: one CTA per tile walks all nine taps, the tiles run in waves; and a single output pixel
-             ([8, 64, 56, 56], [64, 64, 3, 3], 1), ([1, 8, 1, 1], [4, 8, 1, 1], 0))
+             ([8, 64, 56, 56], [64, 64, 3, 3], 1), ([1, 8, 1, 1], [4, 8, 1, 1], 0),
+             # channel counts that are no multiple of 8 or 4 (the last group of a unit is read value by value and zero-filled)
+             ([2, 17, 29, 30], [33, 17, 3, 3], 1), ([1, 31, 8, 8], [15, 31, 3, 3], 1), ([2, 7, 6, 9], [8, 7, 3, 3], 1))
     for x_dims, w_dims, pad in cases:
         n, c, h, w = x_dims
         k, _, r, s_ = w_dims
@@ -297,9 +299,9 @@ def test_one_launch_forms_take_pointers_of_any_alignment():
 
 
 def test_conv_one_launch_form_limits():
-    """A reduction deeper than 4096, a grouped convolution or input channels that are not a multiple of 8 are refused by id, and AUTO then
+    """A reduction of more than 64 units per CTA (here 144 with one CTA per tile) and a grouped convolution are refused by id, and AUTO then
     takes another kernel."""
-    for x_dims, w_dims, stride in (([1, 512, 8, 8], [64, 512, 3, 3], 1), ([1, 64, 56, 56], [64, 32, 3, 3], 1), ([1, 20, 56, 56], [64, 20, 3, 3], 1)):
+    for x_dims, w_dims, stride in (([32, 1024, 56, 56], [64, 1024, 3, 3], 1), ([1, 64, 56, 56], [64, 32, 3, 3], 1)):
         p = dfgpu.ConvParams()
         n, c, h, w = x_dims
         y_dims = [n, w_dims[0], (h + 2 - 3) // stride + 1, (w + 2 - 3) // stride + 1]
@@ -510,6 +512,27 @@ def test_matmul_f32_in_one_launch_on_tensor_cores(a_dims, b_dims, b_strides):
     plain = np.maximum(ref.reshape(m, n) + bias[None, :], 0.0) + addend.reshape(m, n)
     check_f32(results[dfgpu.MATMUL_UMMA_F32X3_CLUSTER].reshape(m, n), plain)
     assert float(np.max(np.abs(results[dfgpu.MATMUL_UMMA_F32X3_CLUSTER] - results[dfgpu.MATMUL_FFMA]))) <= 2e-5 * float(np.max(np.abs(plain)))
+    assert dfgpu.device_status() == 0
+
+
+@pytest.mark.parametrize("a_dims,b_dims", [([4, 130, 136], [4, 136, 68]), ([4, 130, 136], [1, 136, 68]), ([1, 200, 72], [5, 72, 31]), ([3, 1, 65, 129], [3, 1, 129, 64])])
+def test_matmul_batched_in_one_launch_on_tensor_cores(a_dims, b_dims):
+    """One batch axis (either operand may be broadcast along it): every matrix of the batch is one image of the 1 x 1 convolution, with its
+    own filter where B is batched; row, reduction and column counts that fill no tile."""
+    p = dfgpu.MatmulParams()
+    c_dims = [max(x, y) for x, y in zip(a_dims[:-2], b_dims[:-2])] + [a_dims[-2], b_dims[-1]]
+    p.a, p.b, p.c = tensor(F32, a_dims), tensor(F32, b_dims), tensor(F32, c_dims)
+    p.kernel = dfgpu.MATMUL_UMMA_F32X3_CLUSTER
+    info = dfgpu.query("matmul", p)
+    assert info.kernel == dfgpu.MATMUL_UMMA_F32X3_CLUSTER and info.launches == 1 and info.scratch_bytes == 0
+    out, ref = run_matmul(F32, a_dims, b_dims, kernel=dfgpu.MATMUL_UMMA_F32X3_CLUSTER)
+    check_f32(out, ref)
+    cores, _ = run_matmul(F32, a_dims, b_dims, kernel=dfgpu.MATMUL_FFMA)
+    assert float(np.max(np.abs(out - cores))) <= 2e-5 * float(np.max(np.abs(ref)))
+    # two batch axes of extent > 1 stay on CUDA cores
+    q = dfgpu.MatmulParams()
+    q.a, q.b, q.c = tensor(F32, [3, 1, 65, 136]), tensor(F32, [1, 2, 136, 64]), tensor(F32, [3, 2, 65, 64])
+    assert dfgpu.query("matmul", q).kernel == dfgpu.MATMUL_FFMA
     assert dfgpu.device_status() == 0
 
 
