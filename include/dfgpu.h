@@ -214,9 +214,11 @@ int dfgpu_conv_fprop_pair(const dfgpu_conv_pair_params*, void* const* tensors, v
 /* UMMA_F32X3: f32 A, B and C on tcgen05: A and B split into three bf16 pieces each, six bf16 products (2^-24 relative);
    needs scratch, three launches (split, the bf16 matmul over 6K, and the CUDA-core kernel again, which returns at once
    unless A or B held an infinity or a NaN).
-   UMMA_F32X3_CLUSTER: the same six products in ONE launch without scratch, made for unbatched products of at most 148 output
-   tiles (128 x 64; more tiles run one CTA each, K at most 4096 then), at most one batch axis: the kernel of DFGPU_CONV_UMMA_F32X3_CLUSTER run on the 1 x 1 convolution of M pixels (K a multiple
-   of 8, N of 4 for float4 accesses, any strides of A, B and C, 4-byte aligned pointers; HALF and BFLOAT16 matrices value by value). */
+   UMMA_F32X3_CLUSTER: the same six products in ONE launch without scratch: the kernel of DFGPU_CONV_UMMA_F32X3_CLUSTER run
+   on the 1 x 1 convolution of M pixels, one image per matrix of the (at most one) batch axis. Made for at most 148 output
+   tiles (128 x 64); more tiles run one CTA each (K at most 4096 then). Any strides of A, B and C and 4-byte aligned
+   pointers (float4 accesses where K is a multiple of 8, N of 4, the rows are contiguous and everything falls on 16-byte
+   boundaries); HALF and BFLOAT16 matrices value by value. */
 enum { DFGPU_MATMUL_AUTO = 0, DFGPU_MATMUL_FFMA = 1, DFGPU_MATMUL_UMMA_BF16 = 2, DFGPU_MATMUL_UMMA_MXF8 = 3, DFGPU_MATMUL_UMMA_F32X3 = 4,
        DFGPU_MATMUL_UMMA_F32X3_CLUSTER = 5 };
 typedef struct dfgpu_matmul_params {
