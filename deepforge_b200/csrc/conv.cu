@@ -430,7 +430,7 @@ int choose_kernel(const dfgpu_conv_params& p, const ConvArgs& a, int& kernel) {
     if (kernel == DFGPU_CONV_UMMA_F32X3 && !split_ok)
         return fail(kUnsupported, "CONV_FPROP: the split-operand tcgen05 form needs packed channels-last f32 X, W and Y, C and K multiples of 64, stride 1, dilation 1");
     if (kernel == DFGPU_CONV_UMMA_F32X3_CLUSTER && !cluster_ok)
-        return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs FLOAT, HALF or BFLOAT16 X, W and Y and one group");
+        return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs FLOAT, HALF or BFLOAT16 X, W and Y and at most 64 reduction units (64 channels x one tap) per CTA");
     if (kernel != DFGPU_CONV_UMMA_BF16 && (p.x.dtype == DFGPU_BF16X2 || p.y.dtype == DFGPU_BF16X2))
         return fail(kUnsupported, "CONV_FPROP: split bf16 pair tensors are read and written by the tcgen05 kernel only");
     if (kernel == DFGPU_CONV_IGEMM_FFMA && a.groups != 1)

@@ -22,7 +22,8 @@
 // transposed MATMUL operand, a pointer that is only 4-byte aligned) neighbouring threads take neighbouring pixels (or
 // output channels) and read their channels value by value, so that a warp's loads still fall side by side. Read value by
 // value, the tensors may also be f16 or bf16 (widened to f32, whose lower pieces are then zero; Y narrowed on the store),
-// which gives strided, dilated and odd-sized convolutions of those types a tensor-core path too.
+// which gives strided, dilated and odd-sized convolutions of those types a tensor-core path too. Groups: every 64-channel
+// output tile belongs to one group and reads that group's input channels.
 //
 // A product with an infinite or NaN factor does not survive the split, so the loaders also record whether they saw
 // one; the ranks exchange that beside the partial tiles, and a cluster that saw one computes its tile on the CUDA cores
@@ -146,9 +147,18 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kControlOffset + 16 * kBuffers + 8);
 
     // The tile's first row as a pixel index over all images, and how many of its 128 rows exist.
-    const int n0 = blockIdx.z * kTileN;
+    // Along z: the 64-channel tiles of the output, group by group (a group's output channels meet its own input channels only).
+    int n0 = blockIdx.z * kTileN, K = static_cast<int>(a.y.dim[1]), C = static_cast<int>(a.x.dim[1]), x_group = 0;
+    if (!FAST && a.groups > 1) {   // (the all-float4 instantiation is for one group)
+        const int per_group = static_cast<int>(a.k_per_group), tiles_per_group = (per_group + kTileN - 1) / kTileN;
+        const int group = static_cast<int>(blockIdx.z) / tiles_per_group;
+        n0 = group * per_group + (static_cast<int>(blockIdx.z) - group * tiles_per_group) * kTileN;
+        K = (group + 1) * per_group;                       // (the end of this group's output channels)
+        C = static_cast<int>(a.c_per_group);
+        x_group = group * C * g.x_c;                       // (where the group's input channels start in X; the filter holds C per output channel)
+    }
     int m0 = blockIdx.y * kTileM, rows_live = min(kTileM, g.m_total - m0), filter_first = 0;
-    if (g.tiles_per_image > 0) {
+    if (!FAST && g.tiles_per_image > 0) {   // (the all-float4 instantiation is for unbatched problems)
         const int image = static_cast<int>(fast_divide(blockIdx.y, g.by_tiles)), first = (static_cast<int>(blockIdx.y) - image * g.tiles_per_image) * kTileM;
         const int pixels = static_cast<int>(a.y.dim[2] * a.y.dim[3]);
         m0 = image * pixels + first;
@@ -157,8 +167,8 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
     }
     const int first_unit = rank * g.units_per_rank;
     const int my_units = max(0, min(g.units - first_unit, g.units_per_rank));
-    const int P = static_cast<int>(a.y.dim[2]), Q = static_cast<int>(a.y.dim[3]), K = static_cast<int>(a.y.dim[1]);
-    const int H = static_cast<int>(a.x.dim[2]), W = static_cast<int>(a.x.dim[3]), C = static_cast<int>(a.x.dim[1]);
+    const int P = static_cast<int>(a.y.dim[2]), Q = static_cast<int>(a.y.dim[3]);
+    const int H = static_cast<int>(a.x.dim[2]), W = static_cast<int>(a.x.dim[3]);
     const int R = static_cast<int>(a.w.dim[2]), S = static_cast<int>(a.w.dim[3]);
 
     // Loader threads: which rows of the operand tiles this thread fills (the issuing warp computes them too, and loads nothing).
@@ -179,7 +189,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         const int n = static_cast<int>(fast_divide(line, g.by_p)), p = line - n * P;
         ih0[i] = p * a.stride_h - a.pad_h;
         iw0[i] = q * a.stride_w - a.pad_w;
-        x_image[i] = n * g.x_n + x_unit[i] * 8 * g.x_c;
+        x_image[i] = n * g.x_n + x_group + x_unit[i] * 8 * g.x_c;
     }
     // The filter tile: 64 output channels x 8 groups of 8 input channels. Stored with input channels contiguous, a thread
     // reads its group as two quads; stored with output channels contiguous, neighbouring threads take neighbouring output
@@ -409,7 +419,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
                 for (int s = 0; s < S; ++s) {
                     const int ih = p * a.stride_h - a.pad_h + r * a.dilation_h, iw = q * a.stride_w - a.pad_w + s * a.dilation_w;
                     const bool inside = ih >= 0 && ih < H && iw >= 0 && iw < W;
-                    const int pixel = n * g.x_n + (inside ? ih : 0) * g.x_h + (inside ? iw : 0) * g.x_w;
+                    const int pixel = n * g.x_n + x_group + (inside ? ih : 0) * g.x_h + (inside ? iw : 0) * g.x_w;
                     const int tap = filter + (a.reverse ? R - 1 - r : r) * g.w_r + (a.reverse ? S - 1 - s : s) * g.w_s;
                     for (int c = 0; c < C; ++c)
                         sum = fmaf(inside ? load_value(g.x, g.x_type, pixel + c * g.x_c) : 0.0f, load_value(g.w, g.w_type, tap + c * g.w_c), sum);
@@ -451,9 +461,11 @@ bool cluster_form(const dfgpu_conv_params& p, ClusterForm& form) {
         return last;
     };
     if (reach(p.x) >= (1ll << 31) || reach(p.w) >= (1ll << 31) || reach(p.y) >= (1ll << 31)) return false;
-    if (p.x.dim[1] != p.w.dim[1] || p.w.dim[0] != p.y.dim[1]) return false;   // (one group)
+    if (p.w.dim[1] <= 0 || p.x.dim[1] % p.w.dim[1] != 0 || p.w.dim[0] != p.y.dim[1]) return false;
+    const int64_t groups = p.x.dim[1] / p.w.dim[1];
+    if (p.y.dim[1] % groups != 0) return false;
     const int64_t m_total = p.y.dim[0] * p.y.dim[2] * p.y.dim[3];
-    const int64_t chunks = (p.x.dim[1] + kChunk - 1) / kChunk, tiles_n = (p.y.dim[1] + kTileN - 1) / kTileN;
+    const int64_t chunks = (p.w.dim[1] + kChunk - 1) / kChunk, tiles_n = groups * ((p.y.dim[1] / groups + kTileN - 1) / kTileN);
     const int64_t tiles = (m_total + kTileM - 1) / kTileM * tiles_n;
     const int64_t units = p.w.dim[2] * p.w.dim[3] * chunks;
     constexpr int kSms = 148;   // (a query has no device: the count this library is built for)
@@ -519,9 +531,9 @@ static int launch_clusters(ClusterForm form, ClusterConvArgs g, const ConvArgs& 
         return type == DFGPU_F32 && channels % group == 0 && channel_stride == 1 && s0 % 4 == 0 && s1 % 4 == 0 && s2 % 4 == 0 && s3 % 4 == 0 &&
                (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0;
     };
-    g.x_quads = quads(g.x, g.x_type, a.x.dim[1], 8, g.x_c, g.x_n, g.x_h, g.x_w, 0);
-    g.w_quads = quads(g.w, g.w_type, a.x.dim[1], 8, g.w_c, g.w_k, g.w_r, g.w_s, g.w_n);
-    g.y_quads = quads(g.y, g.y_type, a.y.dim[1], 4, g.y_k, g.y_n, g.y_p, g.y_q, 0);
+    g.x_quads = quads(g.x, g.x_type, a.c_per_group, 8, g.x_c, g.x_n, g.x_h, g.x_w, 0);
+    g.w_quads = quads(g.w, g.w_type, a.c_per_group, 8, g.w_c, g.w_k, g.w_r, g.w_s, g.w_n);
+    g.y_quads = quads(g.y, g.y_type, a.k_per_group, 4, g.y_k, g.y_n, g.y_p, g.y_q, 0);
     g.w_along_k = !g.w_quads && g.w_k == 1;
     g.units = form.units;
     g.units_per_rank = form.units_per_rank;
@@ -542,7 +554,7 @@ static int launch_clusters(ClusterForm form, ClusterConvArgs g, const ConvArgs& 
     attribute.val.clusterDim.y = attribute.val.clusterDim.z = 1;
     config.attrs = &attribute;
     config.numAttrs = 1;
-    const bool fast = g.x_quads && g.w_quads && g.y_quads;
+    const bool fast = g.x_quads && g.w_quads && g.y_quads && a.groups == 1 && g.tiles_per_image == 0;
     cudaError_t error = fast ? cudaLaunchKernelEx(&config, umma_conv_f32_kernel<true>, g, a) : cudaLaunchKernelEx(&config, umma_conv_f32_kernel<false>, g, a);
     if (error != cudaSuccess) return fail(kExecutionFailed, "%s: cluster launch failed: %s", what, cudaGetErrorString(error));
     return check_launch(what);
@@ -555,7 +567,7 @@ bool conv_f32_cluster_supported(const dfgpu_conv_params& p) {
 
 int launch_conv_f32_cluster(const dfgpu_conv_params& p, const ConvArgs& a, void* const* tensors, cudaStream_t stream) {
     ClusterForm form;
-    if (!cluster_form(p, form)) return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs FLOAT, HALF or BFLOAT16 X, W and Y and one group");
+    if (!cluster_form(p, form)) return fail(kUnsupported, "CONV_FPROP: the one-launch tcgen05 form needs FLOAT, HALF or BFLOAT16 X, W and Y and at most 64 reduction units (64 channels x one tap) per CTA");
     ClusterConvArgs g{};
     g.x = tensors[0], g.w = tensors[1], g.y = tensors[2];
     g.x_type = p.x.dtype, g.w_type = p.w.dtype, g.y_type = p.y.dtype;

@@ -166,7 +166,7 @@ enum {
                                    a thread-block cluster per tile shares the filter taps out
                                    between its CTAs, which split X and W on their way into shared memory and add their
                                    partial tiles through distributed shared memory; a cluster whose inputs hold an
-                                   infinity or a NaN computes its tile on the CUDA cores. No scratch. One group, any channel counts;
+                                   infinity or a NaN computes its tile on the CUDA cores. No scratch. Any groups and channel counts;
                                    any stride, dilation, padding, filter reversal; any tensor strides (channels-last and 16-byte
                                    aligned is the fast case: float4 accesses; NCHW or a 4-byte aligned pointer works value by
                                    value), so f32 arguments keep the reference's 4-byte alignment. HALF and BFLOAT16 tensors are taken too

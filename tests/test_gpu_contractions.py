@@ -298,10 +298,24 @@ def test_one_launch_forms_take_pointers_of_any_alignment():
     assert dfgpu.device_status() == 0
 
 
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_grouped_convolutions_in_one_launch_on_tensor_cores(dtype):
+    """Groups: every 64-channel output tile belongs to one group and reads that group's input channels only (2 groups of 32 -> 32
+    channels; 4 groups of 16 -> 24, so a group's last tile and unit are partly empty; 2 groups of 80 -> 72 with stride 2)."""
+    for x_dims, w_dims, stride in (([2, 64, 12, 12], [64, 32, 3, 3], 1), ([1, 64, 9, 9], [96, 16, 3, 3], 1), ([2, 160, 15, 13], [144, 80, 3, 3], 2)):
+        n, c, h, w = x_dims
+        k = w_dims[0]
+        out_h, out_w = (h + 2 - 3) // stride + 1, (w + 2 - 3) // stride + 1
+        info, out, ref = run_conv(dtype, x_dims, w_dims, [1, 1], [1, 1], [stride, stride], [1, 1], dfgpu.CONV_AUTO,
+                                  nhwc_strides(x_dims), nhwc_strides(w_dims), nhwc_strides([n, k, out_h, out_w]), seed=17)
+        assert info.kernel == dfgpu.CONV_UMMA_F32X3_CLUSTER and info.launches == 1
+        (check_f32 if dtype == F32 else check_bf16)(out, ref)
+    assert dfgpu.device_status() == 0
+
+
 def test_conv_one_launch_form_limits():
-    """A reduction of more than 64 units per CTA (here 144 with one CTA per tile) and a grouped convolution are refused by id, and AUTO then
-    takes another kernel."""
-    for x_dims, w_dims, stride in (([32, 1024, 56, 56], [64, 1024, 3, 3], 1), ([1, 64, 56, 56], [64, 32, 3, 3], 1)):
+    """A reduction of more than 64 units per CTA (here 144 with one CTA per tile) is refused by id, and AUTO then takes another kernel."""
+    for x_dims, w_dims, stride in (([32, 1024, 56, 56], [64, 1024, 3, 3], 1),):
         p = dfgpu.ConvParams()
         n, c, h, w = x_dims
         y_dims = [n, w_dims[0], (h + 2 - 3) // stride + 1, (w + 2 - 3) // stride + 1]
