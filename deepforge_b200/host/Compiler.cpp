@@ -257,18 +257,30 @@ Status lower_conv(Lowering& low, std::size_t index) {
     if (rank < 3 || rank > 5 || low.tensor(*w).dim.size() != rank || low.tensor(*y).dim.size() != rank || pre->size() != rank - 2 ||
         post->size() != rank - 2 || stride->size() != rank - 2 || dilation->size() != rank - 2)
         return fail(ErrorCode::kInvalidShape, where, "convolution requires matching rank 3-5 tensors and spatial attributes");
-    if (rank != 4) return fail(ErrorCode::kUnsupportedOperation, where, "only 2-D (rank-4) convolutions are executable on this backend");
+    if (rank == 5) return fail(ErrorCode::kUnsupportedOperation, where, "3-D (rank-5) convolutions are not executable on this backend");
+    // A 1-D (rank-3) convolution runs as the 2-D one over images of a single row: a unit axis goes in before the last
+    // axis of every tensor, and the attributes of that axis are the neutral ones.
+    auto as_single_row = [](dfgpu_tensor& t) {
+        if (t.rank < 2 || t.rank >= DFGPU_MAX_RANK) return;
+        t.dim[t.rank] = t.dim[t.rank - 1];
+        t.stride[t.rank] = t.stride[t.rank - 1];
+        t.dim[t.rank - 1] = 1;
+        t.stride[t.rank - 1] = t.dim[t.rank] * t.stride[t.rank];   // (never multiplied by anything but 0)
+        ++t.rank;
+    };
 
     KernelStep step;
     step.op = KernelOp::kConvFprop;
     step.label = node.name;
     step.nodes = {index};
     dfgpu_conv_params params{};
-    for (int i = 0; i < 2; ++i) {
-        params.pre_pad[i] = (*pre)[i];
-        params.post_pad[i] = (*post)[i];
-        params.stride[i] = (*stride)[i];
-        params.dilation[i] = (*dilation)[i];
+    params.stride[0] = params.dilation[0] = 1;   // (rank 3: the single row)
+    for (std::size_t i = 0; i < rank - 2; ++i) {
+        std::size_t const axis = i + (4 - rank);
+        params.pre_pad[axis] = (*pre)[i];
+        params.post_pad[axis] = (*post)[i];
+        params.stride[axis] = (*stride)[i];
+        params.dilation[axis] = (*dilation)[i];
     }
     params.reverse_filter = *mode == "CONVOLUTION";
     std::vector<std::int64_t> extras;
@@ -279,6 +291,12 @@ Status lower_conv(Lowering& low, std::size_t index) {
     if ((status = low.describe(*w, params.w, where)).is_bad()) return status;
     if ((status = low.describe(final_uid, params.y, where)).is_bad()) return status;
     if (low.tensor(final_uid).dim != low.tensor(*y).dim) return fail(ErrorCode::kInvalidShape, where, "fused output shape differs from the convolution output");
+    if (rank == 3) {
+        as_single_row(params.x);
+        as_single_row(params.w);
+        as_single_row(params.y);
+        for (int i = 0; i < 2; ++i) as_single_row(params.extra[i]);   // (operands of fewer axes stay aligned with the last one)
+    }
     if (low.options.disable_tensor_cores) params.kernel = low.tensor(*x).dim[1] == low.tensor(*w).dim[1] ? DFGPU_CONV_IGEMM_FFMA : DFGPU_CONV_DIRECT;
     step.tensors = {low.bind(*x), low.bind(*w), low.bind(final_uid), TensorBinding{}, TensorBinding{}};
     for (std::size_t i = 0; i < extras.size(); ++i) step.tensors[3 + i] = low.bind(extras[i]);

@@ -83,6 +83,38 @@ def test_c2_bottleneck_small(io, options):
         check_bf16(s.output(7), ref[7])
 
 
+@pytest.mark.parametrize("layout", ["channels_last", "ncw"])
+def test_one_dimensional_convolution_with_bias_and_relu(layout):
+    """A rank-3 CONV_FPROP ([N, C, W], filter [K, C, R], stride 2, dilation 2, asymmetric padding) with bias and ReLU behind it: lowered as
+    the 2-D convolution over images of a single row, one launch on the tensor cores; a rank-5 one is refused."""
+    from deepforge_b200 import graphs
+    n, c, width, k, r = 3, 64, 50, 32, 5
+    pre, post, stride, dilation = 3, 1, 2, 2
+    q = (width + pre + post - (dilation * (r - 1) + 1)) // stride + 1
+    strides = (lambda d: [d[1] * d[2], 1, d[1]]) if layout == "channels_last" else (lambda d: [d[1] * d[2], d[2], 1])
+    tensors = [graphs.tensor(1, "X", [n, c, width], "FLOAT", strides([n, c, width])), graphs.tensor(2, "W", [k, c, r], "FLOAT", strides([k, c, r])),
+               graphs.tensor(3, "B", [1, k, 1], "FLOAT", [k, 1, 1]), graphs.tensor(4, "Y", [n, k, q], "FLOAT", strides([n, k, q])),
+               graphs.tensor(11, "conv_out", [n, k, q], "FLOAT", strides([n, k, q]), True), graphs.tensor(12, "bias_out", [n, k, q], "FLOAT", strides([n, k, q]), True)]
+    nodes = [graphs.conv_node("conv", 1, 2, 11, (pre,), (post,), (stride,), (dilation,)), graphs.pointwise_node("bias", "ADD", 11, 12, 3),
+             graphs.pointwise_node("relu", "RELU_FWD", 12, 4)]
+    doc = graphs.document("conv1d", nodes, tensors)
+    wl = workloads.Workload(name="conv1d", config=0, document=doc, description={}, metric="conv_fprop_throughput", unit="TFLOP/s", flops=1.0, bytes=1.0,
+                            bound="hbm", inputs={1: workloads._uniform(5, 1, n * c * width, "FLOAT", -1.0, 1.0), 2: workloads._uniform(5, 2, k * c * r, "FLOAT", -0.2, 0.2),
+                                                 3: workloads._uniform(5, 3, k, "FLOAT", -0.5, 0.5)}, outputs=[4])
+    s = harness.Session(wl)
+    assert s.exe.launch_count == 1 and "conv_fprop kernel=5 launches=1 [conv+bias+relu]" in s.exe.plan_text()
+    s.run()
+    ins, _ = oracle_inputs(wl, s)
+    ref = graph_oracle.run(wl.document, ins)
+    check_f32(s.output(4), ref[4])
+    assert np.all(np.abs(s.output(4) - ref[4]) <= 1e-4 + 1e-3 * np.abs(ref[4])) and float(np.min(s.output(4))) == 0.0
+    assert dfgpu.device_status() == 0
+    volume = [graphs.tensor(1, "X", [1, 8, 4, 4, 4]), graphs.tensor(2, "W", [8, 8, 1, 1, 1]), graphs.tensor(3, "Y", [1, 8, 4, 4, 4])]
+    with pytest.raises(runtime.DeepForgeError) as error:
+        runtime.compile_graph(graphs.document("conv3d", [graphs.conv_node("conv", 1, 2, 3, (0, 0, 0), None, (1, 1, 1), (1, 1, 1))], volume))
+    assert error.value.code == 20
+
+
 def test_c2_bottleneck_float_on_tensor_cores():
     """An all-FLOAT bottleneck big enough for the tensor cores (N = 8, 28 x 28): conv1 and conv2 have 49 output tiles and run as one
     cluster launch each (bias and ReLU in its epilogue), conv3 has 196 and runs as the three-launch split form (residual in the adder);
