@@ -18,9 +18,10 @@ namespace {
 // |x| bit patterns order like unsigned integers, and every NaN pattern is larger
 // than +Inf, so an unsigned max over (bits & 0x7fffffff) is arith.maximumf over
 // |x| with NaN propagation.
-__device__ __forceinline__ uint32_t scale_code_from_amax_bits(uint32_t amax_bits) {
+// `largest`: the largest finite value of the code type (448 for E4M3, 57344 for E5M2; SpecializedGraph.cpp:795-808).
+__device__ __forceinline__ uint32_t scale_code_from_amax_bits(uint32_t amax_bits, float largest = 448.0f) {
     if (amax_bits > 0x7f800000u) return 0xffu;  // NaN block
-    float desired = __fdiv_rn(__uint_as_float(amax_bits), 448.0f);
+    float desired = __fdiv_rn(__uint_as_float(amax_bits), largest);
     uint32_t bits = __float_as_uint(desired);
     if (bits == 0u) return 127u;            // desired > 0 is false -> scale 1.0
     if (bits == 0x7f800000u) return 0xfeu;  // +Inf saturates
@@ -192,12 +193,13 @@ __global__ void bsq_generic_kernel(const void* x, uint8_t* y, uint8_t* scale, Vi
         uint32_t bits = __float_as_uint(value) & 0x7fffffffu;
         amax_bits = bits > amax_bits ? bits : amax_bits;
     }
-    uint32_t code = scale_code_from_amax_bits(amax_bits);
+    const bool e5m2 = yv.dtype == DFGPU_E5M2;
+    uint32_t code = scale_code_from_amax_bits(amax_bits, e5m2 ? 57344.0f : 448.0f);
     scale[scale_offset(sv, layout, index)] = static_cast<uint8_t>(code);
     float reciprocal = reciprocal_e8m0(code);
     for (int64_t j = 0; j < block; ++j) {
-        float value = load_as_f32(x, xv.dtype, x_base + j * xv.stride[axis]);
-        y[y_base + j * yv.stride[axis]] = static_cast<uint8_t>(encode_e4m3_scalar(__fmul_rn(value, reciprocal)));
+        float value = __fmul_rn(load_as_f32(x, xv.dtype, x_base + j * xv.stride[axis]), reciprocal);
+        y[y_base + j * yv.stride[axis]] = static_cast<uint8_t>(e5m2 ? encode_e5m2_scalar(value) : encode_e4m3_scalar(value));
     }
 }
 
@@ -715,7 +717,8 @@ __global__ void bsd_generic_kernel(const uint8_t* x, const uint8_t* scale, void*
         xo += index[i] * xv.stride[i];
         yo += index[i] * yv.stride[i];
     }
-    float value = __fmul_rn(decode_e4m3(x[xo]), decode_e8m0(scale[scale_offset(sv, layout, scale_index)]));
+    float code_value = xv.dtype == DFGPU_E5M2 ? decode_e5m2(x[xo]) : decode_e4m3(x[xo]);
+    float value = __fmul_rn(code_value, decode_e8m0(scale[scale_offset(sv, layout, scale_index)]));
     store_from_f32(y, yv.dtype, yo, value);
 }
 
@@ -791,8 +794,8 @@ int plan_bsq(const dfgpu_bsq_params& p, BsqPlan& plan) {
         return fail(kInvalidShape, "BLOCK_SCALE_QUANTIZE: tensor rank or extent out of range");
     if (p.x.dtype != DFGPU_F32 && p.x.dtype != DFGPU_F16 && p.x.dtype != DFGPU_BF16)
         return fail(kUnsupported, "BLOCK_SCALE_QUANTIZE: X must be FLOAT, HALF or BFLOAT16");
-    if (p.y.dtype != DFGPU_E4M3 || p.scale.dtype != DFGPU_E8M0)
-        return fail(kUnsupported, "BLOCK_SCALE_QUANTIZE: only FP8_E4M3 codes with FP8_E8M0 scales are executable");
+    if ((p.y.dtype != DFGPU_E4M3 && p.y.dtype != DFGPU_E5M2) || p.scale.dtype != DFGPU_E8M0)
+        return fail(kUnsupported, "BLOCK_SCALE_QUANTIZE: only FP8_E4M3 or FP8_E5M2 codes with FP8_E8M0 scales are executable");
     int rank = p.x.rank;
     if (p.y.rank != rank || p.scale.rank != rank)
         return fail(kInvalidShape, "BLOCK_SCALE_QUANTIZE: X, Y and scale ranks differ");
@@ -840,6 +843,7 @@ int plan_bsq(const dfgpu_bsq_params& p, BsqPlan& plan) {
             }
         }
     }
+    if (p.y.dtype == DFGPU_E5M2) kernel = DFGPU_BSQ_GENERIC;   // (the fast kernels are built on the hardware e4m3x2 convert)
     if (p.kernel != DFGPU_BSQ_AUTO && p.kernel != kernel) {
         if (p.kernel == DFGPU_BSQ_GENERIC) kernel = DFGPU_BSQ_GENERIC;
         else return fail(kUnsupported, "BLOCK_SCALE_QUANTIZE: requested kernel %d does not cover this layout", p.kernel);
@@ -971,8 +975,8 @@ struct BsdPlan {
 int plan_bsd(const dfgpu_bsd_params& p, BsdPlan& plan) {
     if (!valid_tensor(p.x) || !valid_tensor(p.y) || !valid_tensor(p.scale))
         return fail(kInvalidShape, "BLOCK_SCALE_DEQUANTIZE: tensor rank or extent out of range");
-    if (p.x.dtype != DFGPU_E4M3 || p.scale.dtype != DFGPU_E8M0)
-        return fail(kUnsupported, "BLOCK_SCALE_DEQUANTIZE: only FP8_E4M3 codes with FP8_E8M0 scales are executable");
+    if ((p.x.dtype != DFGPU_E4M3 && p.x.dtype != DFGPU_E5M2) || p.scale.dtype != DFGPU_E8M0)
+        return fail(kUnsupported, "BLOCK_SCALE_DEQUANTIZE: only FP8_E4M3 or FP8_E5M2 codes with FP8_E8M0 scales are executable");
     if (p.y.dtype != DFGPU_F32 && p.y.dtype != DFGPU_F16 && p.y.dtype != DFGPU_BF16)
         return fail(kUnsupported, "BLOCK_SCALE_DEQUANTIZE: Y must be FLOAT, HALF or BFLOAT16");
     int rank = p.y.rank;
@@ -996,6 +1000,7 @@ int plan_bsd(const dfgpu_bsd_params& p, BsdPlan& plan) {
         p.y.dim[1] % plan.blocks[1] == 0 && p.scale.dim[0] == p.y.dim[0] / plan.blocks[0] &&
         p.scale.dim[1] == p.y.dim[1] / plan.blocks[1] && (plan.blocks[1] % 16 == 0 || plan.blocks[1] < 16))
         kernel = DFGPU_BSD_PACKED;
+    if (p.x.dtype == DFGPU_E5M2) kernel = DFGPU_BSD_GENERIC;
     if (p.kernel != DFGPU_BSD_AUTO && p.kernel != kernel) {
         if (p.kernel == DFGPU_BSD_GENERIC) kernel = DFGPU_BSD_GENERIC;
         else return fail(kUnsupported, "BLOCK_SCALE_DEQUANTIZE: requested kernel %d does not cover this layout", p.kernel);

@@ -108,8 +108,8 @@ struct Lowering {
 
     TensorDesc const& tensor(std::int64_t uid) const { return graph.tensors.at(uid); }
 
-    // FP8_E5M2 is executable as a MATMUL_FP8 operand or output only, UINT8 as the SDPA block mask only (`allow_e5m2`
-    // admits either).
+    // FP8_E5M2 is executable as a MATMUL_FP8 operand or output and as the codes of BLOCK_SCALE_QUANTIZE / DEQUANTIZE,
+    // UINT8 as the SDPA block mask only.
     // allow_special: the port takes the types only some ports execute (FP8_E5M2, UINT8, INT64) and ragged storage
     Status describe(std::int64_t uid, dfgpu_tensor& out, std::string const& where, bool allow_special = false) const {
         auto const& t = tensor(uid);
@@ -535,7 +535,7 @@ Status lower_quantize(Lowering& low, std::size_t index) {
     params.axis = axis ? static_cast<std::int32_t>(*axis) : -1;
     if (axis && (*axis < 0 || *axis >= static_cast<std::int64_t>(low.tensor(*x).dim.size()))) return fail(ErrorCode::kInvalidValue, where, "axis is out of range");
     if ((status = low.describe(*x, params.x, where)).is_bad()) return status;
-    if ((status = low.describe(*y, params.y, where)).is_bad()) return status;
+    if ((status = low.describe(*y, params.y, where, low.tensor(*y).data_type == DataType::kFp8E5M2)).is_bad()) return status;   // (E5M2 codes: the general kernel)
     if ((status = low.describe(*scale, params.scale, where)).is_bad()) return status;
     KernelStep step;
     step.op = KernelOp::kBlockScaleQuantize;
@@ -560,7 +560,7 @@ Status lower_dequantize(Lowering& low, std::size_t index) {
     dfgpu_bsd_params params{};
     params.block_count = static_cast<std::int32_t>(blocks->size());
     for (std::size_t i = 0; i < blocks->size(); ++i) params.block[i] = (*blocks)[i];
-    if ((status = low.describe(*x, params.x, where)).is_bad()) return status;
+    if ((status = low.describe(*x, params.x, where, low.tensor(*x).data_type == DataType::kFp8E5M2)).is_bad()) return status;
     if ((status = low.describe(*scale, params.scale, where)).is_bad()) return status;
     if ((status = low.describe(*y, params.y, where)).is_bad()) return status;
     KernelStep step;

@@ -338,7 +338,8 @@ int dfo_block_scale_quantize(const dfo_tensor* x, const void* x_data,
                              const dfo_tensor* y, void* y_data,
                              const dfo_tensor* scale, void* scale_data,
                              int64_t block, int32_t axis) {
-    if (y->dtype != DFO_E4M3 || scale->dtype != DFO_E8M0) return 20;
+    if ((y->dtype != DFO_E4M3 && y->dtype != DFO_E5M2) || scale->dtype != DFO_E8M0) return 20;
+    const float largest = y->dtype == DFO_E5M2 ? 57344.0f : 448.0f; /* quantized_maximum, SpecializedGraph.cpp:795-808 */
     if (axis < 0) axis = x->rank - 1;
     if (axis >= x->rank || block <= 0 || x->dim[axis] % block != 0) return 15;
     int64_t index[DFO_MAX_RANK];
@@ -362,7 +363,7 @@ int dfo_block_scale_quantize(const dfo_tensor* x, const void* x_data,
             float value = load_f32(x, x_data, element_offset(x, input_index));
             amax = maximumf_nan(amax, fabsf(value));
         }
-        float desired = amax / 448.0f;
+        float desired = amax / largest;
         float guarded = desired > 0.0f ? desired : 1.0f;
         if (desired != desired) guarded = desired;
         guarded = powf(2.0f, ceilf(log2f(guarded)));

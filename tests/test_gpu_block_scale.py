@@ -4,7 +4,7 @@ import pytest
 
 import oracle
 from deepforge_b200 import dfgpu, synthetic
-from deepforge_b200.dfgpu import BF16, E4M3, E8M0, F16, F32, REORDER_F8_128x4, tensor
+from deepforge_b200.dfgpu import BF16, E4M3, E5M2, E8M0, F16, F32, REORDER_F8_128x4, tensor
 
 pytestmark = pytest.mark.gpu
 
@@ -34,14 +34,14 @@ def _make_x(dtype, shape, seed, special=False):
 
 
 def _quantize_both(dtype, shape, block, axis, kernel, scale_dims=None, scale_strides=None, reorder=0, seed=3, special=False,
-                   x_strides=None):
+                   x_strides=None, code_type=E4M3):
     import gpu_util as g
     x = _make_x(dtype, shape, seed, special)
     logical = list(shape)
     logical[axis] //= block
     scale_dims = scale_dims or logical
     xd = tensor(dtype, shape, x_strides)
-    yd = tensor(E4M3, shape)
+    yd = tensor(code_type, shape)
     sd = tensor(E8M0, scale_dims, scale_strides, reorder)
     scale_bytes = int(np.prod(scale_dims))
     y_ref = np.zeros(int(np.prod(shape)), dtype=np.uint8)
@@ -58,6 +58,56 @@ def _quantize_both(dtype, shape, block, axis, kernel, scale_dims=None, scale_str
     y = g.to_host(dy, np.uint8)
     s = g.to_host(ds, np.uint8)
     return info, x, y, s, y_ref, s_ref
+
+
+@pytest.mark.parametrize("dtype", [F32, F16, BF16])
+def test_e5m2_codes_match_oracle_and_the_reference_known_answers(dtype):
+    """FP8_E5M2 codes run on the general kernels: the scale rule divides by 57344 (known answers of test/Compiler/SpecializedOpsTest.cpp:640-659
+    and :716-735), and codes and scales equal the oracle's bit for bit on ordinary and special values, blocks along either axis, plain and
+    F8_128x4 scale layouts; dequantize likewise."""
+    import gpu_util as g
+    if dtype == F32:
+        p = dfgpu.BsqParams()
+        p.x, p.y, p.scale, p.block_size, p.axis = tensor(F32, [1, 4]), tensor(E5M2, [1, 4]), tensor(E8M0, [1, 2]), 2, 1
+        assert dfgpu.query("block_scale_quantize", p).kernel == dfgpu.BSQ_GENERIC
+        dx, dy, ds = g.to_device(np.array([1.0, 2.0, -4.0, 8.0], dtype=np.float32)), g.device_zeros(4), g.device_zeros(2)
+        dfgpu.block_scale_quantize(p, g.ptr(dx), g.ptr(dy), g.ptr(ds))
+        assert g.to_host(ds, np.uint8).tolist() == [113, 115] and g.to_host(dy, np.uint8).tolist() == [0x74, 0x78, 0xf4, 0x78]
+        q = dfgpu.BsdParams()
+        q.x, q.scale, q.y, q.block_count = tensor(E5M2, [1, 4]), tensor(E8M0, [1, 2]), tensor(F32, [1, 4]), 1
+        q.block[0] = 2
+        dx, ds, dy = g.to_device(np.array([0x3c, 0x40, 0xc0, 0x38], dtype=np.uint8)), g.to_device(np.array([127, 128], dtype=np.uint8)), g.device_zeros(16)
+        dfgpu.block_scale_dequantize(q, g.ptr(dx), g.ptr(ds), g.ptr(dy))
+        assert g.to_host(dy, np.float32).tolist() == [1.0, 2.0, -4.0, 1.0]
+    for shape, block, axis, special, reorder, scale_dims in (([128, 256], 32, 1, False, 0, None), ([128, 256], 32, 1, True, 0, None), ([256, 64], 32, 0, True, 0, None),
+                                                              ([3, 40, 48], 8, 2, True, 0, None), ([128, 128], 32, 1, True, REORDER_F8_128x4, [128, 4])):
+        info, x, y, s, y_ref, s_ref = _quantize_both(dtype, shape, block, axis, dfgpu.BSQ_AUTO, scale_dims=scale_dims, reorder=reorder, special=special, code_type=E5M2)
+        assert info.kernel == dfgpu.BSQ_GENERIC
+        assert np.array_equal(s, s_ref) and np.array_equal(y, y_ref)
+        if reorder:
+            continue
+        # and back: the general dequantize kernel on the E5M2 codes against the oracle, bit for bit
+        blocks = [1] * len(shape)
+        blocks[axis] = block
+        out_type = dtype
+        width = dfgpu.DTYPE_BYTES[out_type]
+        ref = np.zeros(int(np.prod(shape)) * width, dtype=np.uint8)
+        logical = list(shape)
+        logical[axis] //= block
+        oracle.block_scale_dequantize(tensor(E5M2, shape), y_ref, tensor(E8M0, logical), s_ref, tensor(out_type, shape), ref, blocks)
+        q = dfgpu.BsdParams()
+        q.x, q.scale, q.y, q.block_count = tensor(E5M2, shape), tensor(E8M0, logical), tensor(out_type, shape), len(shape)
+        for i, b in enumerate(blocks):
+            q.block[i] = b
+        dx, ds, dy = g.to_device(y_ref), g.to_device(s_ref), g.device_zeros(ref.size, 0x11)
+        dfgpu.block_scale_dequantize(q, g.ptr(dx), g.ptr(ds), g.ptr(dy))
+        out = g.to_host(dy, np.uint8)
+        view = np.uint32 if width == 4 else np.uint16
+        a, b = out.view(view), ref.view(view)
+        as_float = (out.view(np.float32) if out_type == F32 else out.view(np.float16).astype(np.float32) if out_type == F16
+                    else synthetic.bf16_bits_to_f32(out.view(np.uint16)))
+        nan = np.isnan(as_float)
+        assert np.array_equal(a[~nan], b[~nan]) and nan.any() == special
 
 
 def test_known_answers_through_the_abi():

@@ -3,6 +3,7 @@ on device buffers, against the CPU oracle evaluating the same document.
 
 Gates: quantized codes and E8M0 scales bit-exact; f32 contractions max|d| <= 1e-4*max|ref|;
 bf16 contractions |d| <= 1e-2 + 2e-2*|ref| (f32 accumulation)."""
+import dataclasses
 import sys
 from pathlib import Path
 
@@ -236,6 +237,25 @@ def test_c3_quantize_matmul_small(io, c_type, options):
     for uid in (3, 4, 5, 6):
         assert np.array_equal(s.output(uid), ref[uid]), f"codes/scales of tensor {uid} must be bit-exact"
     (check_f32 if c_type == "FLOAT" else check_bf16)(s.output(9), ref[9])
+
+
+def test_c3_quantize_matmul_with_e5m2_codes():
+    """The same graph with FP8_E5M2 codes for A and B: the quantize nodes run the general kernel (two launches), the dequantize nodes stay
+    launches of their own (the block-scaled tensor-core matmul reads E4M3 codes), codes and scales are bit-exact, C holds the bf16 gate."""
+    import copy
+    wl = workloads.c3(m=128, k=256, n=192)
+    wl = dataclasses.replace(wl, document=copy.deepcopy(wl.document))
+    for uid in ("3", "5"):
+        wl.document["tensors"][uid]["data_type"] = "FP8_E5M2"
+    s = harness.Session(wl)
+    plan = s.exe.plan_text()
+    assert plan.count("block_scale_quantize kernel=1") == 2 and plan.count("block_scale_dequantize") == 2
+    s.run()
+    ins, storage = oracle_inputs(wl, s)
+    ref = graph_oracle.run(wl.document, ins, storage_inputs=storage)
+    for uid in (3, 4, 5, 6):
+        assert np.array_equal(s.output(uid), ref[uid]), f"codes/scales of tensor {uid} must be bit-exact"
+    check_bf16(s.output(9), ref[9])
 
 
 def _quantize_slabs(document, node_index, uid, storage, slabs):

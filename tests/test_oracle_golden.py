@@ -15,7 +15,7 @@ import pytest
 
 import oracle
 from deepforge_b200 import dfgpu
-from deepforge_b200.dfgpu import BF16, E4M3, E8M0, F16, F32, I32, REORDER_F8_128x4, tensor
+from deepforge_b200.dfgpu import BF16, E4M3, E5M2, E8M0, F16, F32, I32, REORDER_F8_128x4, tensor
 
 INF = float("inf")
 NAN = float("nan")
@@ -100,6 +100,21 @@ def test_block_quantize_exceptional_scales():
     oracle.block_scale_quantize(tensor(F32, [1, 4]), x, tensor(E4M3, [1, 4]), y, tensor(E8M0, [1, 2]), scale, 2, 1)
     assert scale.tolist() == [0xfe, 0xff]
     assert y.tolist() == [0x7e, 0x00, 0x7f, 0x7f]
+
+
+def test_e5m2_block_scale_known_answers():
+    """FP8_E5M2 codes (test/Compiler/SpecializedOpsTest.cpp:640-659 dequantize, :716-735 quantize): the scale rule divides by 57344."""
+    x = np.array([0x3c, 0x40, 0xc0, 0x38], dtype=np.uint8)
+    scale = np.array([127, 128], dtype=np.uint8)
+    y = np.full(4, -99.0, dtype=np.float32)
+    oracle.block_scale_dequantize(tensor(E5M2, [1, 4]), x, tensor(E8M0, [1, 2]), scale, tensor(F32, [1, 4]), y, [2])
+    assert y.tolist() == [1.0, 2.0, -4.0, 1.0]
+    x = np.array([1.0, 2.0, -4.0, 8.0], dtype=np.float32)
+    codes = np.zeros(4, dtype=np.uint8)
+    scale = np.zeros(2, dtype=np.uint8)
+    oracle.block_scale_quantize(tensor(F32, [1, 4]), x, tensor(E5M2, [1, 4]), codes, tensor(E8M0, [1, 2]), scale, 2, 1)
+    assert scale.tolist() == [113, 115]
+    assert codes.tolist() == [0x74, 0x78, 0xf4, 0x78]
 
 
 def test_bf16_fp8_f16_roundtrip_bits():
