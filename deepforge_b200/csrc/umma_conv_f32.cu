@@ -15,8 +15,8 @@
 // owner's inbox (shared memory to shared memory across the cluster, signalled on the owner's mbarrier); each CTA waits for
 // its inbox to fill, adds its rows over all ranks in rank order, applies the epilogue and stores Y.
 //
-// Input channels need only be a multiple of 8 and output channels of 4: a unit's missing channels and a tile's missing
-// filter rows are written as zeros. Stride, dilation, asymmetric padding and filter reversal only change which input pixel
+// Channel counts are free: a unit's missing channels and a tile's missing filter rows are written as zeros (a group of 8
+// input channels that is not whole is read value by value). Stride, dilation, asymmetric padding and filter reversal only change which input pixel
 // and which filter tap a loader thread reads. The tensors may have any strides: with contiguous channels on 16-byte
 // boundaries (channels-last X and Y, KRSC filter) a group of 8 channels is two float4 loads; otherwise (NCHW, a
 // transposed MATMUL operand, a pointer that is only 4-byte aligned) neighbouring threads take neighbouring pixels (or
