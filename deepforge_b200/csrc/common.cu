@@ -68,5 +68,5 @@ extern "C" const char* dfgpu_last_error(void) { return dfgpu::g_error; }
 // 2: dfgpu_sdpa_params gained bias and alibi_mask. 3: it gained sink and block_mask (14 pointers); DFGPU_BF16X2.
 // 4: dfgpu_conv_fprop_pair, dfgpu_block_scale_quantize_pair. 5: dfgpu_sdpa_params gained page_offsets_k / page_offsets_v
 // (16 pointers), DFGPU_I64, DFGPU_CONV_UMMA_F32X3, DFGPU_MATMUL_UMMA_F32X3 in place of the two-SM MXFP8 id.
-// 6: DFGPU_CONV_UMMA_F32X3_CLUSTER, DFGPU_MATMUL_UMMA_F32X3_CLUSTER.
-extern "C" int dfgpu_abi_version(void) { return 6; }
+// 6: DFGPU_CONV_UMMA_F32X3_CLUSTER, DFGPU_MATMUL_UMMA_F32X3_CLUSTER. 7: dfgpu_conv_params gained the depth attributes (rank 5).
+extern "C" int dfgpu_abi_version(void) { return 7; }

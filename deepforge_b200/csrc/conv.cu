@@ -368,8 +368,9 @@ bool f32_split_form(const dfgpu_conv_params& p, SplitForm& form) {
 int build_args(const dfgpu_conv_params& p, void* const* tensors, ConvArgs& a) {
     if (!valid_tensor(p.x) || !valid_tensor(p.w) || !valid_tensor(p.y))
         return fail(kInvalidShape, "CONV_FPROP: tensor rank or extent out of range");
-    if (p.x.rank != 4 || p.w.rank != 4 || p.y.rank != 4)
-        return fail(kUnsupported, "CONV_FPROP: only rank-4 (2-D spatial) convolutions are executable on this backend");
+    const int rank = p.x.rank;
+    if ((rank != 4 && rank != 5) || p.w.rank != rank || p.y.rank != rank)
+        return fail(kUnsupported, "CONV_FPROP: only rank-4 (2-D) and rank-5 (3-D) convolutions are executable on this backend");
     auto float_type = [](int t) { return t == DFGPU_F32 || t == DFGPU_F16 || t == DFGPU_BF16; };
     // split (hi, lo) activations exist for the tcgen05 kernel only: choose_kernel() refuses them for every other one
     if (!(float_type(p.x.dtype) || p.x.dtype == DFGPU_BF16X2) || !float_type(p.w.dtype) || !(float_type(p.y.dtype) || p.y.dtype == DFGPU_BF16X2))
@@ -379,13 +380,18 @@ int build_args(const dfgpu_conv_params& p, void* const* tensors, ConvArgs& a) {
     int64_t groups = p.x.dim[1] / p.w.dim[1];
     if (groups <= 0 || p.y.dim[1] % groups != 0)
         return fail(kInvalidShape, "CONV_FPROP: convolution output channels are not divisible by groups");
-    for (int axis = 0; axis < 2; ++axis) {
-        if (p.pre_pad[axis] < 0 || p.post_pad[axis] < 0 || p.stride[axis] <= 0 || p.dilation[axis] <= 0)
+    for (int axis = 2; axis < rank; ++axis) {
+        // rank 5: axis 2 is the depth with its own attributes, the last two axes use the arrays
+        const bool depth = rank == 5 && axis == 2;
+        const int slot = axis - (rank - 2);
+        const int64_t pre = depth ? p.depth_pre_pad : p.pre_pad[slot], post = depth ? p.depth_post_pad : p.post_pad[slot];
+        const int64_t step = depth ? p.depth_stride : p.stride[slot], spread = depth ? p.depth_dilation : p.dilation[slot];
+        if (pre < 0 || post < 0 || step <= 0 || spread <= 0)
             return fail(kInvalidArgument, "CONV_FPROP: padding must be non-negative and stride/dilation positive");
-        int64_t dilated = p.dilation[axis] * (p.w.dim[axis + 2] - 1) + 1;
-        int64_t padded = p.x.dim[axis + 2] + p.pre_pad[axis] + p.post_pad[axis];
+        int64_t dilated = spread * (p.w.dim[axis] - 1) + 1;
+        int64_t padded = p.x.dim[axis] + pre + post;
         if (padded < dilated) return fail(kInvalidShape, "CONV_FPROP: effective filter exceeds padded input");
-        if (p.y.dim[axis + 2] != 1 + (padded - dilated) / p.stride[axis])
+        if (p.y.dim[axis] != 1 + (padded - dilated) / step)
             return fail(kInvalidShape, "CONV_FPROP: output spatial dimensions do not match attributes");
     }
     int status = validate_epilogue(p.epilogue_count, p.epilogue, p.extra, tensors ? tensors + 3 : nullptr, p.y, "CONV_FPROP");
@@ -398,6 +404,9 @@ int build_args(const dfgpu_conv_params& p, void* const* tensors, ConvArgs& a) {
     a.extra_data[0] = tensors ? tensors[3] : nullptr;
     a.extra_data[1] = tensors ? tensors[4] : nullptr;
     a.epilogue = make_epilogue(p.epilogue_count, p.epilogue);
+    a.pad_d = rank == 5 ? static_cast<int32_t>(p.depth_pre_pad) : 0;
+    a.stride_d = rank == 5 ? static_cast<int32_t>(p.depth_stride) : 1;
+    a.dilation_d = rank == 5 ? static_cast<int32_t>(p.depth_dilation) : 1;
     a.pad_h = static_cast<int32_t>(p.pre_pad[0]);
     a.pad_w = static_cast<int32_t>(p.pre_pad[1]);
     a.stride_h = static_cast<int32_t>(p.stride[0]);
@@ -412,6 +421,14 @@ int build_args(const dfgpu_conv_params& p, void* const* tensors, ConvArgs& a) {
 }
 
 int choose_kernel(const dfgpu_conv_params& p, const ConvArgs& a, int& kernel) {
+    if (p.x.rank == 5) {   // 3-D: the one-launch tcgen05 kernel is the only one that walks a depth axis
+        if (!conv_f32_cluster_supported(p))
+            return fail(kUnsupported, "CONV_FPROP: a 3-D convolution needs FLOAT, HALF or BFLOAT16 tensors and at most 64 reduction units (64 channels x one tap) per CTA");
+        if (p.kernel != DFGPU_CONV_AUTO && p.kernel != DFGPU_CONV_UMMA_F32X3_CLUSTER)
+            return fail(kUnsupported, "CONV_FPROP: 3-D convolutions run on DFGPU_CONV_UMMA_F32X3_CLUSTER only");
+        kernel = DFGPU_CONV_UMMA_F32X3_CLUSTER;
+        return kOk;
+    }
     int automatic = a.groups == 1 ? DFGPU_CONV_IGEMM_FFMA : DFGPU_CONV_DIRECT;
     if (conv_umma_supported(p)) automatic = DFGPU_CONV_UMMA_BF16;
     SplitForm split;

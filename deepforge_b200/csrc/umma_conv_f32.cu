@@ -23,7 +23,8 @@
 // output channels) and read their channels value by value, so that a warp's loads still fall side by side. Read value by
 // value, the tensors may also be f16 or bf16 (widened to f32, whose lower pieces are then zero; Y narrowed on the store),
 // which gives strided, dilated and odd-sized convolutions of those types a tensor-core path too. Groups: every 64-channel
-// output tile belongs to one group and reads that group's input channels.
+// output tile belongs to one group and reads that group's input channels. Rank-5 convolutions: an output pixel is (image,
+// depth, row, column) and the units run over the depth taps as well.
 //
 // A product with an infinite or NaN factor does not survive the split, so the loaders also record whether they saw
 // one; the ranks exchange that beside the partial tiles, and a cluster that saw one computes its tile on the CUDA cores
@@ -68,6 +69,10 @@ struct ClusterConvArgs {
     int32_t x_n, x_c, x_h, x_w;                   // X by image, channel, row, column
     int32_t w_k, w_c, w_r, w_s;                   // the filter by output channel, input channel, tap row, tap column
     int32_t y_n, y_k, y_p, y_q;                   // Y by image, channel, row, column
+    int P, Q, H, W, R, S;                         // output and input rows and columns, filter rows and columns
+    int depth_out, depth_in, depth_taps;          // a rank-5 convolution's third spatial axis (1, 1, 1 otherwise): an output pixel is (image, depth, row, column)
+    int32_t x_d, w_t, y_d;                        // ... and its strides
+    FastDivisor by_depth, by_plane;               // depth_out; R * S
     int x_quads, w_quads, y_quads;                // channels are contiguous and every other stride and the pointer a multiple of 16 bytes: float4 accesses
     int w_along_k;                                // output channels are contiguous in the filter (a MATMUL's row-major B): neighbouring threads take neighbouring output channels
     FastDivisor by_q, by_p, by_chunks, by_s;      // output width and height, chunks, filter width
@@ -160,16 +165,15 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
     int m0 = blockIdx.y * kTileM, rows_live = min(kTileM, g.m_total - m0), filter_first = 0;
     if (!FAST && g.tiles_per_image > 0) {   // (the all-float4 instantiation is for unbatched problems)
         const int image = static_cast<int>(fast_divide(blockIdx.y, g.by_tiles)), first = (static_cast<int>(blockIdx.y) - image * g.tiles_per_image) * kTileM;
-        const int pixels = static_cast<int>(a.y.dim[2] * a.y.dim[3]);
+        const int pixels = g.P * g.Q;
         m0 = image * pixels + first;
         rows_live = min(kTileM, pixels - first);
         filter_first = image * g.w_n;
     }
     const int first_unit = rank * g.units_per_rank;
     const int my_units = max(0, min(g.units - first_unit, g.units_per_rank));
-    const int P = static_cast<int>(a.y.dim[2]), Q = static_cast<int>(a.y.dim[3]);
-    const int H = static_cast<int>(a.x.dim[2]), W = static_cast<int>(a.x.dim[3]);
-    const int R = static_cast<int>(a.w.dim[2]), S = static_cast<int>(a.w.dim[3]);
+    const int P = g.P, Q = g.Q, H = g.H, W = g.W, R = g.R, S = g.S;
+    const bool volume = !FAST && g.depth_taps * g.depth_in * g.depth_out > 1;   // (a depth axis: the general instantiation only)
 
     // Loader threads: which rows of the operand tiles this thread fills (the issuing warp computes them too, and loads nothing).
     // X with contiguous channels: a thread takes one group of 8 channels (16 bytes of bf16) of two pixels, as two float4 loads each.
@@ -177,7 +181,7 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
     // channel fall side by side, and a thread reads two groups of 8 channels of one pixel value by value.
     const int row[2] = {x_quads ? tid >> 3 : tid & 127, x_quads ? 64 + (tid >> 3) : tid & 127};
     const int x_unit[2] = {x_quads ? tid & 7 : (tid >> 7) & 3, x_quads ? tid & 7 : 4 + ((tid >> 7) & 3)};
-    int ih0[2], iw0[2];
+    int ih0[2], iw0[2], id0[2];
     int x_image[2];   // element offsets (everything lies within 2^31 elements of the first)
     bool live[2];
 #pragma unroll
@@ -186,9 +190,11 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
         live[i] = row[i] < rows_live;
         const int mm = live[i] ? m : 0;
         const int line = static_cast<int>(fast_divide(mm, g.by_q)), q = mm - line * Q;
-        const int n = static_cast<int>(fast_divide(line, g.by_p)), p = line - n * P;
+        const int plane = static_cast<int>(fast_divide(line, g.by_p)), p = line - plane * P;
+        const int n = volume ? static_cast<int>(fast_divide(plane, g.by_depth)) : plane;
         ih0[i] = p * a.stride_h - a.pad_h;
         iw0[i] = q * a.stride_w - a.pad_w;
+        id0[i] = volume ? (plane - n * g.depth_out) * a.stride_d - a.pad_d : 0;
         x_image[i] = n * g.x_n + x_group + x_unit[i] * 8 * g.x_c;
     }
     // The filter tile: 64 output channels x 8 groups of 8 input channels. Stored with input channels contiguous, a thread
@@ -207,13 +213,14 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
     auto fetch = [&](int u, float4 (&xv)[2][2], float4 (&wv)[2]) {
         const int unit = first_unit + u;
         const int tap = static_cast<int>(fast_divide(unit, g.by_chunks)), c0 = (unit - tap * g.chunks) * kChunk;
-        const int r = static_cast<int>(fast_divide(tap, g.by_s)), s = tap - r * S;
+        const int t = volume ? static_cast<int>(fast_divide(tap, g.by_plane)) : 0, in_plane = tap - t * R * S;
+        const int r = static_cast<int>(fast_divide(in_plane, g.by_s)), s = in_plane - r * S;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            const int ih = ih0[i] + r * a.dilation_h, iw = iw0[i] + s * a.dilation_w;
+            const int ih = ih0[i] + r * a.dilation_h, iw = iw0[i] + s * a.dilation_w, id = id0[i] + t * a.dilation_d;
             xv[i][0] = xv[i][1] = zero;
-            if (live[i] && ih >= 0 && ih < H && iw >= 0 && iw < W && c0 + x_unit[i] * 8 < C) {   // (channels come in whole groups of 8)
-                const int source = x_image[i] + ih * g.x_h + iw * g.x_w + c0 * g.x_c;
+            if (live[i] && ih >= 0 && ih < H && iw >= 0 && iw < W && (!volume || (id >= 0 && id < g.depth_in)) && c0 + x_unit[i] * 8 < C) {
+                const int source = x_image[i] + ih * g.x_h + iw * g.x_w + c0 * g.x_c + (volume ? id * g.x_d : 0);
                 if (x_quads) {
                     xv[i][0] = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(g.x) + source));
                     xv[i][1] = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(g.x) + source) + 1);
@@ -227,7 +234,8 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
             // (a filter row or a channel group past the end: zeros, which add nothing)
         } else {
             // (a reversed filter meets input tap (r, s) with its tap (R-1-r, S-1-s))
-            const int source = w_row + (a.reverse ? R - 1 - r : r) * g.w_r + (a.reverse ? S - 1 - s : s) * g.w_s + c0 * g.w_c;
+            const int source = w_row + (a.reverse ? R - 1 - r : r) * g.w_r + (a.reverse ? S - 1 - s : s) * g.w_s + c0 * g.w_c +
+                               (volume ? (a.reverse ? g.depth_taps - 1 - t : t) * g.w_t : 0);
             if (w_quads) {
                 wv[0] = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(g.w) + source));
                 wv[1] = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(g.w) + source) + 1);
@@ -388,14 +396,15 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
                 sum.w = __fadd_rn(sum.w, part[z].w);
             }
             const int line = static_cast<int>(fast_divide(m, g.by_q)), q = m - line * Q;
-            const int n = static_cast<int>(fast_divide(line, g.by_p)), p = line - n * P;
+            const int plane = static_cast<int>(fast_divide(line, g.by_p)), p = line - plane * P;
+            const int n = volume ? static_cast<int>(fast_divide(plane, g.by_depth)) : plane, d = volume ? plane - n * g.depth_out : 0;
             if (a.epilogue.count > 0) {
-                sum.x = apply_epilogue(sum.x, a, n, k, p, q);
-                sum.y = apply_epilogue(sum.y, a, n, k + 1, p, q);
-                sum.z = apply_epilogue(sum.z, a, n, k + 2, p, q);
-                sum.w = apply_epilogue(sum.w, a, n, k + 3, p, q);
+                sum.x = apply_epilogue(sum.x, a, n, k, p, q, d);
+                sum.y = apply_epilogue(sum.y, a, n, k + 1, p, q, d);
+                sum.z = apply_epilogue(sum.z, a, n, k + 2, p, q, d);
+                sum.w = apply_epilogue(sum.w, a, n, k + 3, p, q, d);
             }
-            const int target = n * g.y_n + p * g.y_p + q * g.y_q + k * g.y_k;
+            const int target = n * g.y_n + p * g.y_p + q * g.y_q + k * g.y_k + d * g.y_d;
             if (y_quads) {
                 *reinterpret_cast<float4*>(static_cast<float*>(g.y) + target) = sum;
             } else {
@@ -412,19 +421,22 @@ umma_conv_f32_kernel(const __grid_constant__ ClusterConvArgs g, const __grid_con
             const int row = row_begin + item / kTileN, k = n0 + item % kTileN;
             const int m = m0 + row;
             if (row >= rows_live || k >= K) continue;
-            const int q = m % Q, p = (m / Q) % P, n = m / (P * Q);
+            const int q = m % Q, p = (m / Q) % P, plane = m / (P * Q), n = plane / g.depth_out, d = plane % g.depth_out;
             const int filter = filter_first + k * g.w_k;
             float sum = 0.0f;
-            for (int r = 0; r < R; ++r)
-                for (int s = 0; s < S; ++s) {
-                    const int ih = p * a.stride_h - a.pad_h + r * a.dilation_h, iw = q * a.stride_w - a.pad_w + s * a.dilation_w;
-                    const bool inside = ih >= 0 && ih < H && iw >= 0 && iw < W;
-                    const int pixel = n * g.x_n + x_group + (inside ? ih : 0) * g.x_h + (inside ? iw : 0) * g.x_w;
-                    const int tap = filter + (a.reverse ? R - 1 - r : r) * g.w_r + (a.reverse ? S - 1 - s : s) * g.w_s;
-                    for (int c = 0; c < C; ++c)
-                        sum = fmaf(inside ? load_value(g.x, g.x_type, pixel + c * g.x_c) : 0.0f, load_value(g.w, g.w_type, tap + c * g.w_c), sum);
-                }
-            store_from_f32(g.y, g.y_type, n * g.y_n + p * g.y_p + q * g.y_q + k * g.y_k, apply_epilogue(sum, a, n, k, p, q));
+            for (int t = 0; t < g.depth_taps; ++t)
+                for (int r = 0; r < R; ++r)
+                    for (int s = 0; s < S; ++s) {
+                        const int ih = p * a.stride_h - a.pad_h + r * a.dilation_h, iw = q * a.stride_w - a.pad_w + s * a.dilation_w;
+                        const int id = d * a.stride_d - a.pad_d + t * a.dilation_d;
+                        const bool inside = ih >= 0 && ih < H && iw >= 0 && iw < W && id >= 0 && id < g.depth_in;
+                        const int pixel = n * g.x_n + x_group + (inside ? ih * g.x_h + iw * g.x_w + id * g.x_d : 0);
+                        const int tap = filter + (a.reverse ? R - 1 - r : r) * g.w_r + (a.reverse ? S - 1 - s : s) * g.w_s +
+                                        (a.reverse ? g.depth_taps - 1 - t : t) * g.w_t;
+                        for (int c = 0; c < C; ++c)
+                            sum = fmaf(inside ? load_value(g.x, g.x_type, pixel + c * g.x_c) : 0.0f, load_value(g.w, g.w_type, tap + c * g.w_c), sum);
+                    }
+            store_from_f32(g.y, g.y_type, n * g.y_n + p * g.y_p + q * g.y_q + k * g.y_k + d * g.y_d, apply_epilogue(sum, a, n, k, p, q, d));
         }
     }
     asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
@@ -450,7 +462,8 @@ void share_units(ClusterForm& form, int ranks) {
 bool cluster_form(const dfgpu_conv_params& p, ClusterForm& form) {
     auto plain_float = [](int type) { return type == DFGPU_F32 || type == DFGPU_F16 || type == DFGPU_BF16; };
     if (!plain_float(p.x.dtype) || !plain_float(p.w.dtype) || !plain_float(p.y.dtype)) return false;
-    if (p.x.rank != 4 || p.w.rank != 4 || p.y.rank != 4) return false;
+    const int rank = p.x.rank;   // 4, or 5 with a depth axis in front of the rows
+    if ((rank != 4 && rank != 5) || p.w.rank != rank || p.y.rank != rank) return false;
     // any strides (channels-last, NCHW, padded rows ...), as long as every element lies within 2^31 floats of the first
     auto reach = [](const dfgpu_tensor& t) {
         int64_t last = 0;
@@ -464,10 +477,12 @@ bool cluster_form(const dfgpu_conv_params& p, ClusterForm& form) {
     if (p.w.dim[1] <= 0 || p.x.dim[1] % p.w.dim[1] != 0 || p.w.dim[0] != p.y.dim[1]) return false;
     const int64_t groups = p.x.dim[1] / p.w.dim[1];
     if (p.y.dim[1] % groups != 0) return false;
-    const int64_t m_total = p.y.dim[0] * p.y.dim[2] * p.y.dim[3];
+    int64_t m_total = p.y.dim[0], taps = 1;
+    for (int axis = 2; axis < rank; ++axis) m_total *= p.y.dim[axis], taps *= p.w.dim[axis];
+    if (m_total >= (1ll << 31)) return false;
     const int64_t chunks = (p.w.dim[1] + kChunk - 1) / kChunk, tiles_n = groups * ((p.y.dim[1] / groups + kTileN - 1) / kTileN);
     const int64_t tiles = (m_total + kTileM - 1) / kTileM * tiles_n;
-    const int64_t units = p.w.dim[2] * p.w.dim[3] * chunks;
+    const int64_t units = taps * chunks;
     constexpr int kSms = 148;   // (a query has no device: the count this library is built for)
     if ((m_total + kTileM - 1) / kTileM > 65535 || tiles_n > 65535) return false;   // (grid extents)
     form.tiles_m = static_cast<int>((m_total + kTileM - 1) / kTileM);
@@ -538,10 +553,12 @@ static int launch_clusters(ClusterForm form, ClusterConvArgs g, const ConvArgs& 
     g.units = form.units;
     g.units_per_rank = form.units_per_rank;
     g.chunks = form.chunks;
-    g.by_q = make_fast_divisor(static_cast<uint32_t>(a.y.dim[3]));
-    g.by_p = make_fast_divisor(static_cast<uint32_t>(a.y.dim[2]));
+    g.by_q = make_fast_divisor(static_cast<uint32_t>(g.Q));
+    g.by_p = make_fast_divisor(static_cast<uint32_t>(g.P));
+    g.by_depth = make_fast_divisor(static_cast<uint32_t>(g.depth_out));
+    g.by_plane = make_fast_divisor(static_cast<uint32_t>(g.R * g.S));
     g.by_chunks = make_fast_divisor(static_cast<uint32_t>(form.chunks));
-    g.by_s = make_fast_divisor(static_cast<uint32_t>(a.w.dim[3]));
+    g.by_s = make_fast_divisor(static_cast<uint32_t>(g.S));
     g.by_tiles = make_fast_divisor(static_cast<uint32_t>(std::max(1, g.tiles_per_image)));
     cudaLaunchConfig_t config{};
     config.gridDim = dim3(form.ranks, form.tiles_m, form.tiles_n);
@@ -554,7 +571,7 @@ static int launch_clusters(ClusterForm form, ClusterConvArgs g, const ConvArgs& 
     attribute.val.clusterDim.y = attribute.val.clusterDim.z = 1;
     config.attrs = &attribute;
     config.numAttrs = 1;
-    const bool fast = g.x_quads && g.w_quads && g.y_quads && a.groups == 1 && g.tiles_per_image == 0;
+    const bool fast = g.x_quads && g.w_quads && g.y_quads && a.groups == 1 && g.tiles_per_image == 0 && g.depth_out * g.depth_in * g.depth_taps == 1;
     cudaError_t error = fast ? cudaLaunchKernelEx(&config, umma_conv_f32_kernel<true>, g, a) : cudaLaunchKernelEx(&config, umma_conv_f32_kernel<false>, g, a);
     if (error != cudaSuccess) return fail(kExecutionFailed, "%s: cluster launch failed: %s", what, cudaGetErrorString(error));
     return check_launch(what);
@@ -571,11 +588,20 @@ int launch_conv_f32_cluster(const dfgpu_conv_params& p, const ConvArgs& a, void*
     ClusterConvArgs g{};
     g.x = tensors[0], g.w = tensors[1], g.y = tensors[2];
     g.x_type = p.x.dtype, g.w_type = p.w.dtype, g.y_type = p.y.dtype;
-    g.m_total = static_cast<int>(p.y.dim[0] * p.y.dim[2] * p.y.dim[3]);
     auto stride = [](const dfgpu_tensor& t, int axis) { return static_cast<int32_t>(t.dim[axis] == 1 ? 0 : t.stride[axis]); };   // (< 2^31: cluster_form)
-    g.x_n = stride(p.x, 0), g.x_c = stride(p.x, 1), g.x_h = stride(p.x, 2), g.x_w = stride(p.x, 3);
-    g.w_k = stride(p.w, 0), g.w_c = stride(p.w, 1), g.w_r = stride(p.w, 2), g.w_s = stride(p.w, 3);
-    g.y_n = stride(p.y, 0), g.y_k = stride(p.y, 1), g.y_p = stride(p.y, 2), g.y_q = stride(p.y, 3);
+    const int rows = p.x.rank - 2, columns = p.x.rank - 1;   // the axes of the last two spatial extents
+    g.P = static_cast<int>(p.y.dim[rows]), g.Q = static_cast<int>(p.y.dim[columns]);
+    g.H = static_cast<int>(p.x.dim[rows]), g.W = static_cast<int>(p.x.dim[columns]);
+    g.R = static_cast<int>(p.w.dim[rows]), g.S = static_cast<int>(p.w.dim[columns]);
+    g.depth_out = g.depth_in = g.depth_taps = 1;
+    if (p.x.rank == 5) {
+        g.depth_out = static_cast<int>(p.y.dim[2]), g.depth_in = static_cast<int>(p.x.dim[2]), g.depth_taps = static_cast<int>(p.w.dim[2]);
+        g.x_d = stride(p.x, 2), g.w_t = stride(p.w, 2), g.y_d = stride(p.y, 2);
+    }
+    g.m_total = static_cast<int>(p.y.dim[0] * g.depth_out * g.P * g.Q);
+    g.x_n = stride(p.x, 0), g.x_c = stride(p.x, 1), g.x_h = stride(p.x, rows), g.x_w = stride(p.x, columns);
+    g.w_k = stride(p.w, 0), g.w_c = stride(p.w, 1), g.w_r = stride(p.w, rows), g.w_s = stride(p.w, columns);
+    g.y_n = stride(p.y, 0), g.y_k = stride(p.y, 1), g.y_p = stride(p.y, rows), g.y_q = stride(p.y, columns);
     return launch_clusters(form, g, a, "CONV_FPROP", stream);
 }
 
@@ -672,6 +698,9 @@ int launch_matmul_f32_cluster(const dfgpu_matmul_params& p, void* const* tensors
     ClusterConvArgs g{};
     g.x = tensors[0], g.w = tensors[1], g.y = tensors[2];
     g.x_type = p.a.dtype, g.w_type = p.b.dtype, g.y_type = p.c.dtype;
+    g.P = g.H = g.R = g.S = 1;
+    g.Q = g.W = static_cast<int>(f.m);
+    g.depth_out = g.depth_in = g.depth_taps = 1;
     g.m_total = static_cast<int>(f.batch * f.m);
     if (f.batch > 1) {
         g.tiles_per_image = static_cast<int>((f.m + kTileM - 1) / kTileM);

@@ -83,7 +83,8 @@ class ConvParams(C.Structure):
     _fields_ = [("x", Tensor), ("w", Tensor), ("y", Tensor), ("extra", Tensor * 2),
                 ("pre_pad", C.c_int64 * 2), ("post_pad", C.c_int64 * 2), ("stride", C.c_int64 * 2),
                 ("dilation", C.c_int64 * 2), ("reverse_filter", C.c_int32), ("epilogue_count", C.c_int32),
-                ("epilogue", EpilogueStep * MAX_EPILOGUE), ("kernel", C.c_int32), ("reserved", C.c_int32)]
+                ("epilogue", EpilogueStep * MAX_EPILOGUE), ("kernel", C.c_int32), ("reserved", C.c_int32),
+                ("depth_pre_pad", C.c_int64), ("depth_post_pad", C.c_int64), ("depth_stride", C.c_int64), ("depth_dilation", C.c_int64)]
 
 
 class ConvPairParams(C.Structure):

@@ -257,7 +257,6 @@ Status lower_conv(Lowering& low, std::size_t index) {
     if (rank < 3 || rank > 5 || low.tensor(*w).dim.size() != rank || low.tensor(*y).dim.size() != rank || pre->size() != rank - 2 ||
         post->size() != rank - 2 || stride->size() != rank - 2 || dilation->size() != rank - 2)
         return fail(ErrorCode::kInvalidShape, where, "convolution requires matching rank 3-5 tensors and spatial attributes");
-    if (rank == 5) return fail(ErrorCode::kUnsupportedOperation, where, "3-D (rank-5) convolutions are not executable on this backend");
     // A 1-D (rank-3) convolution runs as the 2-D one over images of a single row: a unit axis goes in before the last
     // axis of every tensor, and the attributes of that axis are the neutral ones.
     auto as_single_row = [](dfgpu_tensor& t) {
@@ -275,8 +274,16 @@ Status lower_conv(Lowering& low, std::size_t index) {
     step.nodes = {index};
     dfgpu_conv_params params{};
     params.stride[0] = params.dilation[0] = 1;   // (rank 3: the single row)
+    params.depth_stride = params.depth_dilation = 1;
     for (std::size_t i = 0; i < rank - 2; ++i) {
-        std::size_t const axis = i + (4 - rank);
+        if (rank == 5 && i == 0) {   // the depth axis of a 3-D convolution has attributes of its own
+            params.depth_pre_pad = (*pre)[0];
+            params.depth_post_pad = (*post)[0];
+            params.depth_stride = (*stride)[0];
+            params.depth_dilation = (*dilation)[0];
+            continue;
+        }
+        std::size_t const axis = rank == 3 ? 1 : i - (rank - 4);
         params.pre_pad[axis] = (*pre)[i];
         params.post_pad[axis] = (*post)[i];
         params.stride[axis] = (*stride)[i];
@@ -297,7 +304,7 @@ Status lower_conv(Lowering& low, std::size_t index) {
         as_single_row(params.y);
         for (int i = 0; i < 2; ++i) as_single_row(params.extra[i]);   // (operands of fewer axes stay aligned with the last one)
     }
-    if (low.options.disable_tensor_cores) params.kernel = low.tensor(*x).dim[1] == low.tensor(*w).dim[1] ? DFGPU_CONV_IGEMM_FFMA : DFGPU_CONV_DIRECT;
+    if (low.options.disable_tensor_cores && rank != 5) params.kernel = low.tensor(*x).dim[1] == low.tensor(*w).dim[1] ? DFGPU_CONV_IGEMM_FFMA : DFGPU_CONV_DIRECT;   // (3-D: one kernel only)
     step.tensors = {low.bind(*x), low.bind(*w), low.bind(final_uid), TensorBinding{}, TensorBinding{}};
     for (std::size_t i = 0; i < extras.size(); ++i) step.tensors[3 + i] = low.bind(extras[i]);
     // Filter and ADD operands that no node of the graph writes, behind another convolution of the same plan: the

@@ -185,6 +185,10 @@ typedef struct dfgpu_conv_params {
                          running when this one starts (the launch just before it in the stream is a dfgpu
                          convolution that does not write them): the persistent kernel then loads them before
                          it waits for that launch to finish. Leave clear when in doubt. */
+    /* 3-D (rank-5) convolutions, X [N, C, D, H, W], W [K, C, T, R, S], Y [N, K, D', P, Q]: the attributes of the depth
+       axis; pre_pad[0..1] etc. stay those of the last two axes. Ignored for rank 4 (zero is fine). Rank 5 runs on
+       DFGPU_CONV_UMMA_F32X3_CLUSTER only. */
+    int64_t depth_pre_pad, depth_post_pad, depth_stride, depth_dilation;
 } dfgpu_conv_params;
 int dfgpu_query_conv_fprop(const dfgpu_conv_params*, dfgpu_plan_info*);
 int dfgpu_conv_fprop(const dfgpu_conv_params*, void* const* tensors, void* scratch, void* stream);

@@ -21,7 +21,7 @@ def test_kernel_library_exports_every_declared_symbol():
     for name in names:
         assert hasattr(lib, name), name
     assert sorted(dfgpu.EXPORTS) == names
-    assert lib.dfgpu_abi_version() == 6
+    assert lib.dfgpu_abi_version() == 7
 
 
 def test_struct_layout_matches_header():
@@ -34,8 +34,8 @@ def test_struct_layout_matches_header():
     assert C.sizeof(dfgpu.BsdParams) == 504
     assert C.sizeof(dfgpu.BsqPairParams) == 896
     assert C.sizeof(dfgpu.PointwiseParams) == 448
-    assert C.sizeof(dfgpu.ConvParams) == 896
-    assert C.sizeof(dfgpu.ConvPairParams) == 1792
+    assert C.sizeof(dfgpu.ConvParams) == 928
+    assert C.sizeof(dfgpu.ConvPairParams) == 1856
     assert C.sizeof(dfgpu.MatmulParams) == 1144
     assert C.sizeof(dfgpu.MatmulFp8Params) == 440
     assert C.sizeof(dfgpu.SdpaParams) == 2360

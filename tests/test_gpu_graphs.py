@@ -110,10 +110,40 @@ def test_one_dimensional_convolution_with_bias_and_relu(layout):
     check_f32(s.output(4), ref[4])
     assert np.all(np.abs(s.output(4) - ref[4]) <= 1e-4 + 1e-3 * np.abs(ref[4])) and float(np.min(s.output(4))) == 0.0
     assert dfgpu.device_status() == 0
-    volume = [graphs.tensor(1, "X", [1, 8, 4, 4, 4]), graphs.tensor(2, "W", [8, 8, 1, 1, 1]), graphs.tensor(3, "Y", [1, 8, 4, 4, 4])]
-    with pytest.raises(runtime.DeepForgeError) as error:
-        runtime.compile_graph(graphs.document("conv3d", [graphs.conv_node("conv", 1, 2, 3, (0, 0, 0), None, (1, 1, 1), (1, 1, 1))], volume))
-    assert error.value.code == 20
+
+
+def test_three_dimensional_convolution_with_bias_and_residual():
+    """A rank-5 CONV_FPROP ([N, C, D, H, W], filter [K, C, T, R, S]; stride 2 in depth, dilation 2 in the rows, asymmetric padding) with a
+    per-channel bias, ReLU and a full-size addend: one launch of the one-launch tcgen05 kernel, which walks the depth axis too, for the
+    channels-last and the NCDHW layout, and for the reversed filter of math_mode CONVOLUTION."""
+    from deepforge_b200 import graphs
+    n, c, depth, h, w, k = 2, 24, 6, 9, 7, 20
+    taps, pre, post, stride, dilation = (3, 3, 2), (1, 2, 0), (1, 2, 1), (2, 1, 1), (1, 2, 1)
+    out = [(e + a + b - (d * (f - 1) + 1)) // s + 1 for e, a, b, d, f, s in zip((depth, h, w), pre, post, dilation, taps, stride)]
+    for layout in ("channels_last", "ncdhw"):
+        for mode in ("CROSS_CORRELATION", "CONVOLUTION"):
+            strides = (lambda d: [d[1] * d[2] * d[3] * d[4], 1, d[3] * d[4] * d[1], d[4] * d[1], d[1]]) if layout == "channels_last" else (lambda d: None)
+            xd, wd, yd = [n, c, depth, h, w], [k, c, *taps], [n, k, *out]
+            tensors = [graphs.tensor(1, "X", xd, "FLOAT", strides(xd)), graphs.tensor(2, "W", wd, "FLOAT", strides(wd)),
+                       graphs.tensor(3, "B", [1, k, 1, 1, 1], "FLOAT", [k, 1, 1, 1, 1]), graphs.tensor(4, "Z", yd, "FLOAT", strides(yd)),
+                       graphs.tensor(5, "Y", yd, "FLOAT", strides(yd)),
+                       graphs.tensor(11, "conv_out", yd, "FLOAT", strides(yd), True), graphs.tensor(12, "bias_out", yd, "FLOAT", strides(yd), True),
+                       graphs.tensor(13, "relu_out", yd, "FLOAT", strides(yd), True)]
+            nodes = [graphs.conv_node("conv", 1, 2, 11, pre, post, stride, dilation, mode), graphs.pointwise_node("bias", "ADD", 11, 12, 3),
+                     graphs.pointwise_node("relu", "RELU_FWD", 12, 13), graphs.pointwise_node("residual", "ADD", 13, 5, 4)]
+            doc = graphs.document("conv3d", nodes, tensors)
+            count = lambda d: int(np.prod(d))
+            wl = workloads.Workload(name="conv3d", config=0, document=doc, description={}, metric="conv_fprop_throughput", unit="TFLOP/s", flops=1.0, bytes=1.0,
+                                    bound="hbm", inputs={1: workloads._uniform(6, 1, count(xd), "FLOAT", -1.0, 1.0), 2: workloads._uniform(6, 2, count(wd), "FLOAT", -0.2, 0.2),
+                                                         3: workloads._uniform(6, 3, k, "FLOAT", -0.5, 0.5), 4: workloads._uniform(6, 4, count(yd), "FLOAT", -1.0, 1.0)}, outputs=[5])
+            s = harness.Session(wl)
+            assert s.exe.launch_count == 1 and "conv_fprop kernel=5 launches=1 [conv+bias+relu+residual]" in s.exe.plan_text()
+            s.run()
+            ins, _ = oracle_inputs(wl, s)
+            ref = graph_oracle.run(wl.document, ins)
+            check_f32(s.output(5), ref[5])
+            assert np.all(np.abs(s.output(5) - ref[5]) <= 1e-4 + 1e-3 * np.abs(ref[5]))
+    assert dfgpu.device_status() == 0
 
 
 def test_c2_bottleneck_float_on_tensor_cores():
