@@ -15,6 +15,7 @@
 // no valid score gives O = 0, Stats = Max = -inf, Sum_exp = 0; an out-of-range page
 // id reads as zeros without touching memory.
 #include <atomic>
+#include <cmath>
 #include "common.cuh"
 #include "umma.cuh"
 
@@ -51,7 +52,27 @@ struct SdpaArgs {
     float scale;
     int32_t padding, has_left, has_right, bottom_right;
     int64_t left, right, s_kv;
+    // dropout on the probabilities that weight V: 0 none, 1 the counter-based Bernoulli stream, 2 the caller's mask
+    int32_t dropout_kind;
+    uint32_t keep_threshold;       // floor((1 - probability) * 2^24): a 24-bit sample below it keeps the element
+    float dropout_scale;           // kind 1: 1 / (1 - probability)
+    View dropout_mask, rng_dump;
+    const float* dropout_mask_data;
+    const float* dropout_scale_data;
+    const int64_t* seed_data;
+    const int64_t* offset_data;
+    float* rng_dump_data;
 };
+
+// The reference's Bernoulli stream (lib/Compiler/SequenceGraph.cpp:1413-1456): a splitmix64 round over seed + offset + the flat index of
+// the score, whose top 24 bits are compared with the threshold.
+__device__ __forceinline__ float bernoulli_keep(int64_t seed, int64_t offset, int64_t linear, uint32_t threshold) {
+    uint64_t z = static_cast<uint64_t>(seed) + static_cast<uint64_t>(offset) + static_cast<uint64_t>(linear) + 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return (z >> 40) < threshold ? 1.0f : 0.0f;
+}
 
 __device__ __forceinline__ int64_t off4(const View& t, int64_t a, int64_t b, int64_t c, int64_t d) {
     return a * t.stride[0] + b * t.stride[1] + c * t.stride[2] + d * t.stride[3];
@@ -171,6 +192,19 @@ sdpa_rowwise_kernel(SdpaArgs a, int64_t rows) {
 
     int64_t lo, hi;
     valid_range(a, ib, iq, lo, hi);
+    float dropout_scale = 1.0f;
+    int64_t seed = 0, stream_offset = 0;
+    const int64_t linear_row = ((ib * hq + ih) * sq + iq) * a.s_kv;   // flat index of this row's first score in [B, Hq, Sq, Skv]
+    if (a.dropout_kind == 1) {
+        dropout_scale = a.dropout_scale;
+        seed = a.seed_data[0];
+        stream_offset = a.offset_data[0];
+        if (a.rng_dump.rank)   // the mask of every position of the row, masked ones too
+            for (int64_t ikv = lane; ikv < a.s_kv; ikv += 32)
+                a.rng_dump_data[off4(a.rng_dump, ib, ih, iq, ikv)] = bernoulli_keep(seed, stream_offset, linear_row + ikv, a.keep_threshold);
+    } else if (a.dropout_kind == 2) {
+        dropout_scale = a.dropout_scale_data[0];
+    }
     float running_max = -INFINITY, running_sum = 0.0f;
     if (a.sink.rank) {  // the sink logit takes part in the maximum and the sum, not in O
         running_max = a.sink_data[ih * a.sink.stride[1]];
@@ -235,9 +269,22 @@ sdpa_rowwise_kernel(SdpaArgs a, int64_t rows) {
         running_max = new_max;
 #pragma unroll
         for (int i = 0; i < kRowwiseMaxD / 32; ++i) acc[i] *= correction;
+        // what weights V: (p * mask) * scale; the maximum and the sum above are those without dropout
+        float weight = probability;
+        if (a.dropout_kind != 0 && enabled) {
+            float mask;
+            if (a.dropout_kind == 1) {
+                mask = bernoulli_keep(seed, stream_offset, linear_row + ikv, a.keep_threshold);
+            } else {
+                const View& t = a.dropout_mask;
+                mask = a.dropout_mask_data[(t.dim[0] == 1 ? 0 : ib) * t.stride[0] + (t.dim[1] == 1 ? 0 : ih) * t.stride[1] +
+                                           (t.dim[2] == 1 ? 0 : iq) * t.stride[2] + (t.dim[3] == 1 ? 0 : ikv) * t.stride[3]];
+            }
+            weight = __fmul_rn(__fmul_rn(probability, mask), dropout_scale);
+        }
         int count = static_cast<int>(hi - base < 32 ? hi - base : 32);
         for (int j = 0; j < count; ++j) {
-            float pj = __shfl_sync(0xffffffffu, probability, j);
+            float pj = __shfl_sync(0xffffffffu, weight, j);
             int64_t offset = kv_row_offset(a, 1, ib, vh, base + j);
             if (offset < 0) continue;
 #pragma unroll
@@ -588,6 +635,51 @@ int build_args(const dfgpu_sdpa_params& p, void* const* tensors, SdpaArgs& a) {
             return fail(kInvalidShape, "SDPA: block mask must be UINT8 with dimensions [B,Hq,ceil(Sq/128),ceil(ceil(Skv/128)/8)]");
         if (tensors && !a.block_mask_data) return fail(kInvalidArgument, "SDPA: null block mask pointer");
     }
+    a.dropout_kind = p.dropout_kind;
+    a.keep_threshold = 0;
+    a.dropout_scale = 1.0f;
+    a.dropout_mask = make_view(p.dropout_mask);
+    a.rng_dump = make_view(p.rng_dump);
+    a.dropout_mask_data = nullptr; a.dropout_scale_data = nullptr; a.seed_data = nullptr; a.offset_data = nullptr; a.rng_dump_data = nullptr;
+    if (p.dropout_kind < 0 || p.dropout_kind > 2) return fail(kInvalidArgument, "SDPA: unknown dropout kind %d", p.dropout_kind);
+    auto one_element = [](const dfgpu_tensor& t, int dtype) {
+        if (t.rank < 1 || t.dtype != dtype) return false;
+        for (int i = 0; i < t.rank; ++i)
+            if (t.dim[i] != 1) return false;
+        return true;
+    };
+    if (p.dropout_kind == 1) {
+        if (!(p.dropout_probability >= 0.0 && p.dropout_probability < 1.0)) return fail(kInvalidArgument, "SDPA: dropout probability must be in [0, 1)");
+        if (!one_element(p.seed, DFGPU_I64) || !one_element(p.offset, DFGPU_I64)) return fail(kInvalidShape, "SDPA: Seed and Offset must be one INT64 element each");
+        const double keep = 1.0 - p.dropout_probability;
+        a.keep_threshold = static_cast<uint32_t>(static_cast<int64_t>(std::floor(keep * static_cast<double>(1u << 24))));
+        a.dropout_scale = static_cast<float>(1.0 / keep);
+        if (p.rng_dump.rank) {
+            if (p.rng_dump.rank != 4 || p.rng_dump.dtype != DFGPU_F32 || p.rng_dump.dim[0] != p.q.dim[0] || p.rng_dump.dim[1] != hq || p.rng_dump.dim[2] != p.q.dim[2] ||
+                p.rng_dump.dim[3] != p.s_kv)
+                return fail(kInvalidShape, "SDPA: RNG_DUMP must be FLOAT [B, Hq, Sq, Skv]");
+        }
+        if (tensors) {
+            a.seed_data = static_cast<const int64_t*>(tensors[18]);
+            a.offset_data = static_cast<const int64_t*>(tensors[19]);
+            a.rng_dump_data = p.rng_dump.rank ? static_cast<float*>(tensors[20]) : nullptr;
+            if (!a.seed_data || !a.offset_data || (p.rng_dump.rank && !a.rng_dump_data)) return fail(kInvalidArgument, "SDPA: null Seed, Offset or RNG_DUMP pointer");
+        }
+    } else if (p.dropout_kind == 2) {
+        if (p.dropout_mask.rank != 4 || p.dropout_mask.dtype != DFGPU_F32 || !valid_tensor(p.dropout_mask)) return fail(kInvalidShape, "SDPA: Dropout_mask must be a rank-4 FLOAT tensor");
+        const int64_t extent[4] = {p.q.dim[0], hq, p.q.dim[2], p.s_kv};
+        for (int i = 0; i < 4; ++i)
+            if (p.dropout_mask.dim[i] != 1 && p.dropout_mask.dim[i] != extent[i]) return fail(kInvalidShape, "SDPA: Dropout_mask is not broadcast-compatible with attention scores");
+        if (!one_element(p.dropout_scale, DFGPU_F32)) return fail(kInvalidShape, "SDPA: Dropout_scale must be one FLOAT element");
+        if (p.rng_dump.rank) return fail(kInvalidArgument, "SDPA: RNG_DUMP requires probability dropout");
+        if (tensors) {
+            a.dropout_mask_data = static_cast<const float*>(tensors[16]);
+            a.dropout_scale_data = static_cast<const float*>(tensors[17]);
+            if (!a.dropout_mask_data || !a.dropout_scale_data) return fail(kInvalidArgument, "SDPA: null Dropout_mask or Dropout_scale pointer");
+        }
+    } else if (p.rng_dump.rank) {
+        return fail(kInvalidArgument, "SDPA: RNG_DUMP requires probability dropout");
+    }
     a.alibi = p.alibi_mask;
     a.alibi_n = 1;
     while (2 * static_cast<int64_t>(a.alibi_n) <= hq) a.alibi_n *= 2;
@@ -623,13 +715,13 @@ int decode_chunks(const dfgpu_sdpa_params& p) { return static_cast<int>((p.s_kv 
 
 int choose_kernel(const dfgpu_sdpa_params& p, int& kernel) {
     int automatic = DFGPU_SDPA_ROWWISE;
-    const bool plain_scores = p.bias.rank == 0 && !p.alibi_mask && p.sink.rank == 0 && p.block_mask.rank == 0;  // bias, ALiBi, sink token, block mask: general kernel only
+    const bool plain_scores = p.bias.rank == 0 && !p.alibi_mask && p.sink.rank == 0 && p.block_mask.rank == 0 && p.dropout_kind == 0;  // bias, ALiBi, sink token, block mask, dropout: general kernel only
     if (!plain_scores) automatic = DFGPU_SDPA_ROWWISE;
     else if (decode_umma_supported(p)) automatic = DFGPU_SDPA_PAGED_DECODE_UMMA;
     else if (decode_supported(p)) automatic = DFGPU_SDPA_PAGED_DECODE;
     else if (sdpa_umma_supported(p)) automatic = DFGPU_SDPA_UMMA;
     kernel = p.kernel == DFGPU_SDPA_AUTO ? automatic : p.kernel;
-    if (!plain_scores && kernel != DFGPU_SDPA_ROWWISE) return fail(kUnsupported, "SDPA: bias, ALiBi, the sink token and the block mask run on the general kernel only");
+    if (!plain_scores && kernel != DFGPU_SDPA_ROWWISE) return fail(kUnsupported, "SDPA: bias, ALiBi, the sink token, the block mask and dropout run on the general kernel only");
     if (kernel == DFGPU_SDPA_ROWWISE) {
         if (p.q.dim[3] > kRowwiseMaxD || p.v.dim[3] > kRowwiseMaxD) return fail(kUnsupported, "SDPA: head dimension above %d", kRowwiseMaxD);
         return kOk;
@@ -803,7 +895,7 @@ extern "C" int dfgpu_sdpa_paged_decode_static(const dfgpu_sdpa_params* p, void* 
     int status = build_args(*p, tensors, a);
     if (status) return status;
     if (!decode_supported(*p) || p->bias.rank != 0 || p->alibi_mask || p->sink.rank != 0 || p->block_mask.rank != 0 || p->page_offsets_k.rank != 0 ||
-        p->page_offsets_v.rank != 0)
+        p->page_offsets_v.rank != 0 || p->dropout_kind != 0)
         return fail(kUnsupported, "SDPA static decode: needs Sq=1, bf16, D=128, strided page tables for K and V, group size 1/2/4/8, no bias or ALiBi");
     if (!aligned16(a.q_data) || !aligned16(a.k_data) || !aligned16(a.v_data))
         return fail(kInvalidArgument, "SDPA static decode: needs 16-byte aligned Q, K and V");

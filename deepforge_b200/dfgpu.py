@@ -108,7 +108,9 @@ class SdpaParams(C.Structure):
                 ("has_left_bound", C.c_int32), ("has_right_bound", C.c_int32), ("left_bound", C.c_int64),
                 ("right_bound", C.c_int64), ("bottom_right", C.c_int32), ("kernel", C.c_int32), ("s_kv", C.c_int64),
                 ("bias", Tensor), ("alibi_mask", C.c_int32), ("reserved", C.c_int32), ("sink", Tensor), ("block_mask", Tensor),
-                ("page_offsets_k", Tensor), ("page_offsets_v", Tensor)]
+                ("page_offsets_k", Tensor), ("page_offsets_v", Tensor),
+                ("dropout_kind", C.c_int32), ("reserved2", C.c_int32), ("dropout_probability", C.c_double),
+                ("dropout_mask", Tensor), ("dropout_scale", Tensor), ("seed", Tensor), ("offset", Tensor), ("rng_dump", Tensor)]
 
 
 # every symbol include/dfgpu.h declares
@@ -214,9 +216,9 @@ def matmul_fp8(params, a, b, c, amax, descale_a, descale_b, scale_c, scratch=Non
 
 def sdpa_forward(params, pointers: Sequence[Optional[int]], scratch=None, stream=None):
     """pointers: Q, K, V, O, Stats, Max, Sum_exp, SEQ_LEN_Q, SEQ_LEN_KV, Page_table_K, Page_table_V[, Bias[, SINK_TOKEN[, Block_mask[,
-    Page_table_K offsets, Page_table_V offsets]]]]."""
-    assert 11 <= len(pointers) <= 16
-    pointers = list(pointers) + [None] * (16 - len(pointers))
+    Page_table_K offsets, Page_table_V offsets[, Dropout_mask, Dropout_scale, Seed, Offset, RNG_DUMP]]]]]."""
+    assert 11 <= len(pointers) <= 21
+    pointers = list(pointers) + [None] * (21 - len(pointers))
     _call("dfgpu_sdpa_forward", params, pointers, scratch, stream)
 
 

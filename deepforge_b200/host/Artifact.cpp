@@ -125,7 +125,7 @@ std::size_t tensor_slots(KernelOp op) {
         case KernelOp::kPointwise: return 3;
         case KernelOp::kConvFprop: return 5;
         case KernelOp::kMatmul: return 7;
-        case KernelOp::kSdpaForward: return 16;
+        case KernelOp::kSdpaForward: return 21;
         case KernelOp::kMatmulFp8: return 7;
         case KernelOp::kConvFpropPair: return 8;
         case KernelOp::kBlockScaleQuantizePair: return 6;
@@ -311,8 +311,8 @@ dfgpu_tensor const* slot_descriptor(KernelStep const& step, std::size_t slot) {
         }
         else if constexpr (std::is_same_v<T, dfgpu_sdpa_params>) {
             dfgpu_tensor const* t[] = {&p.q, &p.k, &p.v, &p.o, &p.stats, &p.max, &p.sum_exp, &p.seq_q, &p.seq_kv, &p.page_table_k, &p.page_table_v, &p.bias, &p.sink, &p.block_mask,
-                                       &p.page_offsets_k, &p.page_offsets_v};
-            return slot < 16 ? t[slot] : nullptr;
+                                       &p.page_offsets_k, &p.page_offsets_v, &p.dropout_mask, &p.dropout_scale, &p.seed, &p.offset, &p.rng_dump};
+            return slot < 21 ? t[slot] : nullptr;
         } else { dfgpu_tensor const* t[] = {&p.a, &p.b, &p.c}; return slot < 3 ? t[slot] : nullptr; }
     }, step.params);
 }

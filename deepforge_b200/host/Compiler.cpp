@@ -583,17 +583,33 @@ Status lower_dequantize(Lowering& low, std::size_t index) {
 Status lower_sdpa(Lowering& low, std::size_t index) {
     auto const& node = low.graph.nodes[index];
     auto const where = node_path(index, node);
-    for (auto name : {"Attn_scale", "Seed", "Offset", "Dropout_mask", "Dropout_scale", "Descale_Q", "Descale_K", "Descale_V",
-                      "Descale_S", "Scale_S", "Scale_O"})
+    for (auto name : {"Attn_scale", "Dropout_scale_inv", "Descale_Q", "Descale_K", "Descale_V", "Descale_S", "Scale_S", "Scale_O"})
         if (port(node.inputs, name)) return fail(ErrorCode::kUnsupportedOperation, where, std::string("input port ") + name + " is outside the GPU hot path");
-    for (auto name : {"RNG_DUMP", "Amax_S", "Amax_O"})
+    for (auto name : {"Amax_S", "Amax_O"})
         if (port(node.outputs, name)) return fail(ErrorCode::kUnsupportedOperation, where, std::string("output port ") + name + " is outside the GPU hot path");
     auto q = port(node.inputs, "Q"), k = port(node.inputs, "K"), v = port(node.inputs, "V"), o = port(node.outputs, "O");
     if (!q || !k || !v || !o) return fail(ErrorCode::kInvalidValue, where, "SDPA ports are incomplete");
     auto alibi = get_bool(node, "alibi_mask");
     if (!alibi) return fail(ErrorCode::kInvalidValue, where, "alibi_mask must be a boolean");
     auto bias = port(node.inputs, "Bias");
-    if (!is_null(node, "dropout_probability")) return fail(ErrorCode::kUnsupportedOperation, where, "dropout is outside the GPU hot path");
+    // Dropout (lib/Compiler/SequenceGraph.cpp:418-500): a probability with Seed and Offset, or the caller's mask and scale; never both.
+    auto probability = get_number(node, "dropout_probability");
+    if (!probability && !is_null(node, "dropout_probability")) return fail(ErrorCode::kInvalidValue, where + ".dropout_probability", "expected a number or null");
+    if (probability && (!std::isfinite(*probability) || *probability < 0.0 || *probability >= 1.0))
+        return fail(ErrorCode::kInvalidValue, where + ".dropout_probability", "probability must be finite and in [0, 1)");
+    auto dropout_mask = port(node.inputs, "Dropout_mask"), dropout_scale = port(node.inputs, "Dropout_scale");
+    auto seed = port(node.inputs, "Seed"), offset = port(node.inputs, "Offset"), rng_dump = port(node.outputs, "RNG_DUMP");
+    if (probability && dropout_mask) return fail(ErrorCode::kInvalidValue, where, "internal and custom dropout cannot be combined");
+    if (probability) {
+        if (!seed || !offset) return fail(ErrorCode::kInvalidValue, where, "probability dropout requires Seed and Offset");
+        if (dropout_scale) return fail(ErrorCode::kInvalidValue, where, "Dropout_scale is implicit for probability dropout");
+    } else if (dropout_mask) {
+        if (!dropout_scale) return fail(ErrorCode::kInvalidValue, where, "custom dropout requires Dropout_scale");
+        if (seed || offset) return fail(ErrorCode::kInvalidValue, where, "custom dropout does not accept Seed or Offset");
+        if (rng_dump) return fail(ErrorCode::kInvalidValue, where + ".RNG_DUMP", "RNG_DUMP requires probability dropout");
+    } else if (seed || offset || dropout_scale || rng_dump) {
+        return fail(ErrorCode::kInvalidValue, where, "Seed, Offset, Dropout_scale and RNG_DUMP require a configured dropout mode");
+    }
     if (get_bool(node, "is_mxfp8").value_or(true)) return fail(ErrorCode::kUnsupportedOperation, where, "is_mxfp8 must be false");
     auto padding = get_bool(node, "padding_mask"), stats_flag = get_bool(node, "generate_stats");
     if (!padding || !stats_flag) return fail(ErrorCode::kInvalidValue, where, "padding_mask and generate_stats must be booleans");
@@ -697,8 +713,32 @@ Status lower_sdpa(Lowering& low, std::size_t index) {
         if (t.is_virtual || t.reordering_type != "NONE" || t.data_type != DataType::kFloat32)
             return fail(ErrorCode::kUnsupportedOperation, where + ".SINK_TOKEN", "sink token must be an external plain FLOAT tensor");
     }
+    auto one_element = [](TensorDesc const& t) {
+        for (auto extent : t.dim)
+            if (extent != 1) return false;
+        return !t.dim.empty();
+    };
+    if (probability) {
+        params.dropout_kind = 1;
+        params.dropout_probability = *probability;
+        if ((status = low.describe(*seed, params.seed, where, true)).is_bad()) return status;
+        if ((status = low.describe(*offset, params.offset, where, true)).is_bad()) return status;
+        for (auto const* t : {&low.tensor(*seed), &low.tensor(*offset)})
+            if (t->data_type != DataType::kInt64 || !one_element(*t)) return fail(ErrorCode::kInvalidShape, where, "Seed and Offset must be INT64 scalars");
+        if (rng_dump) {
+            if ((status = low.describe(*rng_dump, params.rng_dump, where)).is_bad()) return status;
+            if (low.tensor(*rng_dump).data_type != DataType::kFloat32) return fail(ErrorCode::kUnsupportedDataType, where + ".RNG_DUMP", "RNG_DUMP must be FLOAT");
+        }
+    } else if (dropout_mask) {
+        params.dropout_kind = 2;
+        if ((status = low.describe(*dropout_mask, params.dropout_mask, where)).is_bad()) return status;
+        if ((status = low.describe(*dropout_scale, params.dropout_scale, where)).is_bad()) return status;
+        if (low.tensor(*dropout_mask).data_type != DataType::kFloat32 || low.tensor(*dropout_scale).data_type != DataType::kFloat32)
+            return fail(ErrorCode::kUnsupportedDataType, where, "Dropout_mask and Dropout_scale must be FLOAT");
+        if (!one_element(low.tensor(*dropout_scale))) return fail(ErrorCode::kInvalidShape, where + ".Dropout_scale", "Dropout_scale must be a scalar");
+    }
     // lib/Compiler/SequenceGraph.cpp:951-955
-    if (params.bottom_right && params.has_right_bound && (bias || *alibi))
+    if (params.bottom_right && params.has_right_bound && (bias || *alibi || params.dropout_kind != 0))
         return fail(ErrorCode::kUnsupportedOperation, where, "cuDNN bottom-right causal masking does not combine with bias, ALiBi, or dropout");
     KernelStep step;
     step.op = KernelOp::kSdpaForward;
@@ -707,7 +747,8 @@ Status lower_sdpa(Lowering& low, std::size_t index) {
     auto optional_binding = [&](std::optional<std::int64_t> uid) { return uid ? low.bind(*uid) : TensorBinding{}; };
     step.tensors = {low.bind(*q), low.bind(*k), low.bind(*v), low.bind(*o), optional_binding(stats), optional_binding(max), optional_binding(sum_exp),
                     optional_binding(seq_q), optional_binding(seq_kv), optional_binding(table_k), optional_binding(table_v), optional_binding(bias), optional_binding(sink), optional_binding(block_mask),
-                    optional_binding(offsets_k), optional_binding(offsets_v)};
+                    optional_binding(offsets_k), optional_binding(offsets_v), optional_binding(dropout_mask), optional_binding(dropout_scale), optional_binding(seed),
+                    optional_binding(offset), optional_binding(rng_dump)};
     step.params = params;
     low.plan.steps.push_back(std::move(step));
     return Status::ok();
@@ -737,7 +778,7 @@ void narrow_virtual_tensors(Lowering& low) {
             if (step.op == KernelOp::kPointwise) is_output = slot == 2;
             if (step.op == KernelOp::kBlockScaleQuantize) is_output = slot >= 1;
             if (step.op == KernelOp::kBlockScaleDequantize) is_output = slot == 2;
-            if (step.op == KernelOp::kSdpaForward) is_output = slot >= 3 && slot <= 6;
+            if (step.op == KernelOp::kSdpaForward) is_output = (slot >= 3 && slot <= 6) || slot == 20;
             if (is_output) writer[binding.uid] = s;
             else readers[binding.uid].push_back(s);
         }

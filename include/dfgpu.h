@@ -264,8 +264,8 @@ int dfgpu_matmul_fp8(const dfgpu_matmul_fp8_params*, void* const* tensors, void*
    :1839-1889 paged loads, :1988-2091 validity, :2135-2341 scores and softmax
    row, :2416-2582 outputs). tensors: {Q, K, V, O, Stats, Max, Sum_exp,
    SEQ_LEN_Q, SEQ_LEN_KV, Page_table_K, Page_table_V, Bias, SINK_TOKEN, Block_mask, Page_table_K offsets,
-   Page_table_V offsets} (null when absent; the list is read only as far as the last port the params declare, so a caller
-   without the last five may pass the first eleven only).
+   Page_table_V offsets, Dropout_mask, Dropout_scale, Seed, Offset, RNG_DUMP} (null when absent; the list is read only as far
+   as the last port the params declare, so a caller without the last ten may pass the first eleven only).
    Bias, ALiBi (score = attn_scale * dot + bias + (kv - q) * slope, :2169-2193), the sink token and the
    block mask run on the general kernel only. */
 enum {
@@ -303,6 +303,17 @@ typedef struct dfgpu_sdpa_params {
                                 monotonic and within B * P, every batch's segment covers ceil(SEQ_LEN_KV / block) slots:
                                 lib/Runtime/Executable.cpp:619-716); a table that fails reads as all-invalid pages (zeros) and
                                 leaves 601 (K) or 602 (V) in dfgpu_device_status(). Needs 256 bytes of scratch more. */
+    /* Dropout on the probabilities that weight V (lib/Compiler/SequenceGraph.cpp:2366-2391, :2545-2553): O = sum p * mask * scale * v;
+       the row maximum, the row sum and Stats are those without dropout. General kernel only. */
+    int32_t dropout_kind;        /* 0: none. 1: probability (Seed and Offset, mask = the reference's counter-based Bernoulli stream over the
+                                    flat index of [B, Hq, Sq, Skv], lib/Compiler/SequenceGraph.cpp:1413-1456; scale = 1 / (1 - probability)).
+                                    2: the caller's mask and scale (Dropout_mask, Dropout_scale) */
+    int32_t reserved2;
+    double dropout_probability;  /* kind 1: in [0, 1) */
+    dfgpu_tensor dropout_mask;   /* kind 2: FLOAT, rank 4, extent-1 axes broadcast onto [B, Hq, Sq, Skv] */
+    dfgpu_tensor dropout_scale;  /* kind 2: one FLOAT element */
+    dfgpu_tensor seed, offset;   /* kind 1: one INT64 element each */
+    dfgpu_tensor rng_dump;       /* kind 1, rank 0: absent. FLOAT [B, Hq, Sq, Skv]: receives the mask (every position, masked ones too) */
 } dfgpu_sdpa_params;
 int dfgpu_query_sdpa_forward(const dfgpu_sdpa_params*, dfgpu_plan_info*);
 int dfgpu_sdpa_forward(const dfgpu_sdpa_params*, void* const* tensors, void* scratch, void* stream);

@@ -846,6 +846,19 @@ static float alibi_slope(int64_t head, int64_t heads) {
 /* SequenceGraph.cpp:1988-2091 (validity), :2135-2195 (score = scale * dot),
    :2248-2314 (row max and sum of exp over valid scores), :2316-2341
    (probability), :2416-2582 (outputs; Stats = max + ln(sum)). */
+/* stable_bernoulli_condition, lib/Compiler/SequenceGraph.cpp:1413-1456: z = seed + offset + linear + 0x9E3779B97F4A7C15, two
+   xor-shift-multiply rounds and a final xor-shift (64-bit wrap-around), sample = z >> 40, kept when sample <
+   floor(keep_probability * 2^24). */
+float dfo_bernoulli(int64_t seed, int64_t offset, int64_t linear, double keep_probability) {
+    uint64_t z = (uint64_t)seed + (uint64_t)offset + (uint64_t)linear + 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z = z ^ (z >> 31);
+    uint64_t sample = z >> 40;
+    int64_t threshold = (int64_t)floor(keep_probability * (double)(1u << 24));
+    return (int64_t)sample < threshold ? 1.0f : 0.0f;
+}
+
 int dfo_sdpa_forward(const dfo_sdpa_params* p, void* const* data,
                      int64_t bh_begin, int64_t bh_end, int64_t q_step) {
     const dfo_tensor *q = &p->q, *k = &p->k, *v = &p->v, *o = &p->o;
@@ -859,6 +872,16 @@ int dfo_sdpa_forward(const dfo_sdpa_params* p, void* const* data,
     const int32_t* table_k = (const int32_t*)data[9];
     const int32_t* table_v = (const int32_t*)data[10];
     if (q_step <= 0) q_step = 1;
+    /* :1711-1724: probability dropout scales by float(1 / keep); a caller's mask comes with its own scale */
+    float dropout_scale = 1.0f;
+    int64_t seed = 0, stream_offset = 0;
+    if (p->dropout_kind == 1) {
+        dropout_scale = (float)(1.0 / (1.0 - p->dropout_probability));
+        seed = *(const int64_t*)data[18];
+        stream_offset = *(const int64_t*)data[19];
+    } else if (p->dropout_kind == 2) {
+        dropout_scale = *(const float*)data[17];
+    }
     float* scores = (float*)malloc((size_t)(skv > 0 ? skv : 1) * sizeof(float));
     unsigned char* valid = (unsigned char*)malloc((size_t)(skv > 0 ? skv : 1));
     float* out_row = (float*)malloc((size_t)dv * sizeof(float));
@@ -918,11 +941,22 @@ int dfo_sdpa_forward(const dfo_sdpa_params* p, void* const* data,
                 if (valid[ikv]) sum = sum + expf(scores[ikv] - maximum);
             for (int64_t d = 0; d < dv; ++d) out_row[d] = 0.0f;
             for (int64_t ikv = 0; ikv < skv; ++ikv) {
+                /* :2366-2391 the mask of this score (the flat index runs over [B, Hq, Sq, Skv]); :2393-2414 RNG_DUMP takes it at every position */
+                float mask = 1.0f;
+                if (p->dropout_kind == 1) {
+                    mask = dfo_bernoulli(seed, stream_offset, ((ib * hq + ih) * sq + iq) * skv + ikv, 1.0 - p->dropout_probability);
+                    if (p->rng_dump.rank == 4) store_f32(&p->rng_dump, data[20], offset4(&p->rng_dump, ib, ih, iq, ikv), mask);
+                } else if (p->dropout_kind == 2) {
+                    const dfo_tensor* mt = &p->dropout_mask;
+                    mask = load_f32(mt, data[16], offset4(mt, mt->dim[0] == 1 ? 0 : ib, mt->dim[1] == 1 ? 0 : ih, mt->dim[2] == 1 ? 0 : iq, mt->dim[3] == 1 ? 0 : ikv));
+                }
                 if (!valid[ikv] || !(sum > 0.0f)) continue;
                 float probability = expf(scores[ikv] - maximum) / sum;
+                float weighted = probability * mask; /* :2545-2553: (p * mask) * scale */
+                weighted = weighted * dropout_scale;
                 for (int64_t d = 0; d < dv; ++d) {
                     float vv = load_kv(v, data[2], &p->page_table_v, table_v, &p->page_offsets_v, p->page_offsets_v.rank ? data[15] : NULL, ib, vh, ikv, d);
-                    float product = probability * vv;
+                    float product = weighted * vv;
                     out_row[d] = out_row[d] + product;
                 }
             }

@@ -158,9 +158,17 @@ typedef struct dfo_sdpa_params {
     dfo_tensor block_mask; /* rank 0 => absent; UINT8 [B, Hq, ceil(Sq/128), ceil(ceil(Skv/128)/8)], one bit per 128 x 128 tile */
     dfo_tensor page_offsets_k, page_offsets_v; /* rank 0 => absent; INT32 / INT64 [B+1,1,1,1]: compact page table, entry (b, slot) at
                                                   offsets[b] + slot * stride[2] of the table's storage */
+    /* dropout on the probabilities that weight V (lib/Compiler/SequenceGraph.cpp:2366-2391, :2545-2553) */
+    int32_t dropout_kind;        /* 0 none; 1 probability with Seed and Offset (the stream of :1413-1456); 2 Dropout_mask and Dropout_scale */
+    int32_t reserved3;
+    double dropout_probability;
+    dfo_tensor dropout_mask;     /* kind 2: FLOAT rank 4, broadcast over extent-1 axes onto [B, Hq, Sq, Skv] */
+    dfo_tensor rng_dump;         /* kind 1, rank 0 => absent: FLOAT [B, Hq, Sq, Skv] receives the mask */
 } dfo_sdpa_params;
+/* The Bernoulli stream of lib/Compiler/SequenceGraph.cpp:1413-1456: 1.0 when element `linear` is kept. */
+float dfo_bernoulli(int64_t seed, int64_t offset, int64_t linear, double keep_probability);
 /* pointer order: Q,K,V,O,Stats,Max,Sum_exp,SEQ_LEN_Q,SEQ_LEN_KV,Page_table_K,Page_table_V,Bias,SINK_TOKEN,Block_mask,
-   Page_table_K offsets,Page_table_V offsets.
+   Page_table_K offsets,Page_table_V offsets,Dropout_mask,Dropout_scale (one FLOAT),Seed,Offset (one INT64 each),RNG_DUMP.
    Only (b,h) pairs with flat index bh_begin <= b*Hq+h < bh_end and rows with
    q % q_step == 0 are computed; others are left untouched. */
 int dfo_sdpa_forward(const dfo_sdpa_params* p, void* const* data,

@@ -37,7 +37,9 @@ class SdpaParams(C.Structure):
                 ("has_left_bound", C.c_int32), ("has_right_bound", C.c_int32), ("left_bound", C.c_int64),
                 ("right_bound", C.c_int64), ("bottom_right", C.c_int32), ("reserved", C.c_int32), ("s_kv", C.c_int64),
                 ("bias", Tensor), ("alibi_mask", C.c_int32), ("reserved2", C.c_int32), ("sink", Tensor), ("block_mask", Tensor),
-                ("page_offsets_k", Tensor), ("page_offsets_v", Tensor)]
+                ("page_offsets_k", Tensor), ("page_offsets_v", Tensor),
+                ("dropout_kind", C.c_int32), ("reserved3", C.c_int32), ("dropout_probability", C.c_double),
+                ("dropout_mask", Tensor), ("rng_dump", Tensor)]
 
 
 def _declare(l: C.CDLL) -> C.CDLL:
@@ -215,10 +217,18 @@ def validate_page_prefix(params: SdpaParams, arrays, which: int) -> int:
     return int(lib().dfo_validate_page_prefix(C.byref(params), pointers, C.c_int(which)))
 
 
+def bernoulli(seed: int, offset: int, linear: int, keep_probability: float) -> float:
+    fn = lib().dfo_bernoulli
+    fn.restype = C.c_float
+    return float(fn(C.c_int64(seed), C.c_int64(offset), C.c_int64(linear), C.c_double(keep_probability)))
+
+
 def sdpa_forward(params: SdpaParams, arrays, bh_begin=0, bh_end=1 << 62, q_step=1, threads: int = 1) -> None:
-    assert 11 <= len(arrays) <= 16  # the twelfth is the bias, then the sink token, the block mask, the offsets of compact K and V page tables
-    arrays = list(arrays) + [None] * (16 - len(arrays))
-    pointers = (C.c_void_p * 16)(*[C.c_void_p(a.ctypes.data) if a is not None else C.c_void_p(None) for a in arrays])
+    # the twelfth is the bias, then the sink token, the block mask, the offsets of compact K and V page tables, Dropout_mask, Dropout_scale,
+    # Seed, Offset, RNG_DUMP
+    assert 11 <= len(arrays) <= 21
+    arrays = list(arrays) + [None] * (21 - len(arrays))
+    pointers = (C.c_void_p * 21)(*[C.c_void_p(a.ctypes.data) if a is not None else C.c_void_p(None) for a in arrays])
     bh_end = min(bh_end, int(params.q.dim[0] * params.q.dim[1]))
     if bh_end <= bh_begin:
         return

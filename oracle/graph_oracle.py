@@ -162,6 +162,20 @@ def run(document: dict, inputs: Dict[int, np.ndarray], matmul_rows: Optional[Tup
                     arrays.append(storage_inputs[offsets_uid] if storage_inputs and offsets_uid in storage_inputs else values[offsets_uid])
                 else:
                     arrays.append(None)
+            # dropout: a probability with Seed and Offset (and optionally RNG_DUMP), or the caller's Dropout_mask and Dropout_scale
+            for name in ("Dropout_mask", "Dropout_scale", "Seed", "Offset"):
+                arrays.append((storage_inputs[ins[name]] if storage_inputs and ins[name] in storage_inputs else values[ins[name]]) if name in ins else None)
+            if node.get("dropout_probability") is not None:
+                p.dropout_kind, p.dropout_probability = 1, float(node["dropout_probability"])
+            elif "Dropout_mask" in ins:
+                p.dropout_kind = 2
+                p.dropout_mask = _desc(tensors[ins["Dropout_mask"]])
+            if "RNG_DUMP" in outs:
+                p.rng_dump = _desc(tensors[outs["RNG_DUMP"]])
+                values[outs["RNG_DUMP"]] = _alloc(tensors[outs["RNG_DUMP"]])
+                arrays.append(values[outs["RNG_DUMP"]])
+            else:
+                arrays.append(None)
             p.alibi_mask = int(bool(node.get("alibi_mask")))
             p.attn_scale = node["attn_scale_value"] if node["attn_scale_value"] is not None else 1.0
             p.padding_mask = int(node["padding_mask"])

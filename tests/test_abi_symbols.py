@@ -21,7 +21,7 @@ def test_kernel_library_exports_every_declared_symbol():
     for name in names:
         assert hasattr(lib, name), name
     assert sorted(dfgpu.EXPORTS) == names
-    assert lib.dfgpu_abi_version() == 7
+    assert lib.dfgpu_abi_version() == 8
 
 
 def test_struct_layout_matches_header():
@@ -38,7 +38,7 @@ def test_struct_layout_matches_header():
     assert C.sizeof(dfgpu.ConvPairParams) == 1856
     assert C.sizeof(dfgpu.MatmulParams) == 1144
     assert C.sizeof(dfgpu.MatmulFp8Params) == 440
-    assert C.sizeof(dfgpu.SdpaParams) == 2360
+    assert C.sizeof(dfgpu.SdpaParams) == 3096
 
 
 def test_struct_sizes_agree_with_the_c_compiler(tmp_path):

@@ -13,7 +13,7 @@ import pytest
 sys.path.insert(0, str(Path(__file__).resolve().parent.parent / "oracle"))
 import df_oracle_binding as oracle_binding  # noqa: E402
 import graph_oracle  # noqa: E402
-from deepforge_b200 import dfgpu, harness, runtime, workloads  # noqa: E402
+from deepforge_b200 import dfgpu, harness, runtime, synthetic, workloads  # noqa: E402
 
 THREADS = oracle_binding.host_threads()  # the oracle's per-element arithmetic does not depend on the thread count
 
@@ -143,6 +143,49 @@ def test_three_dimensional_convolution_with_bias_and_residual():
             ref = graph_oracle.run(wl.document, ins)
             check_f32(s.output(5), ref[5])
             assert np.all(np.abs(s.output(5) - ref[5]) <= 1e-4 + 1e-3 * np.abs(ref[5]))
+    assert dfgpu.device_status() == 0
+
+
+@pytest.mark.parametrize("kind", ["probability", "mask"])
+def test_sdpa_with_dropout_through_the_executable(kind):
+    """SDPA with dropout lowered from the serialized graph: probability dropout (Seed and Offset INT64 scalars, RNG_DUMP output) and custom dropout
+    (Dropout_mask broadcast over the batch, Dropout_scale), against the oracle; RNG_DUMP bit for bit."""
+    import copy
+    wl = workloads.c4(b=2, h=4, s=48, d=32, io="FLOAT")
+    doc = copy.deepcopy(wl.document)
+    node = doc["nodes"][0]
+    inputs = dict(wl.inputs)
+    outputs = list(wl.outputs)
+    from deepforge_b200 import graphs
+    if kind == "probability":
+        node["dropout_probability"] = 0.25
+        node["inputs"].update(Seed=20, Offset=21)
+        node["outputs"]["RNG_DUMP"] = 22
+        doc["tensors"]["20"] = graphs.tensor(20, "Seed", [1, 1, 1, 1], "INT64")
+        doc["tensors"]["21"] = graphs.tensor(21, "Offset", [1, 1, 1, 1], "INT64")
+        doc["tensors"]["22"] = graphs.tensor(22, "RNG_DUMP", [2, 4, 48, 48], "FLOAT")
+        inputs[20], inputs[21] = (lambda: np.array([4242], np.int64)), (lambda: np.array([-17], np.int64))
+        outputs.append(22)
+    else:
+        node["inputs"].update(Dropout_mask=20, Dropout_scale=21)
+        doc["tensors"]["20"] = graphs.tensor(20, "Dropout_mask", [1, 4, 48, 48], "FLOAT")
+        doc["tensors"]["21"] = graphs.tensor(21, "Dropout_scale", [1, 1, 1, 1], "FLOAT")
+        inputs[20] = lambda: (synthetic.uniform(3, 20, 4 * 48 * 48, 0.0, 1.0) < 0.8).astype(np.float32)
+        inputs[21] = lambda: np.array([1.25], np.float32)
+    wl = dataclasses.replace(wl, document=doc, inputs=inputs, outputs=outputs)
+    s = harness.Session(wl)
+    assert "sdpa_forward kernel=1" in s.exe.plan_text()
+    s.run()
+    ins, _ = oracle_inputs(wl, s)
+    ref = graph_oracle.run(wl.document, ins)
+    check_f32(s.output(4), ref[4])
+    assert np.allclose(s.output(5), ref[5], rtol=1e-4, atol=1e-5)
+    if kind == "probability":
+        dump = s.output(22)
+        assert np.array_equal(dump, ref[22]) and 0.65 < float(dump.mean()) < 0.85
+    plain = harness.Session(workloads.c4(b=2, h=4, s=48, d=32, io="FLOAT"))
+    plain.run()
+    assert not np.allclose(plain.output(4), s.output(4), atol=1e-3) and np.allclose(plain.output(5), s.output(5), rtol=1e-5, atol=1e-6)
     assert dfgpu.device_status() == 0
 
 

@@ -145,6 +145,79 @@ def test_rowwise_block_mask():
     assert np.any(o[0, 0, 128:] != 0.0)
 
 
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("kind", ["probability", "mask", "broadcast_mask"])
+def test_rowwise_dropout(kind, dtype):
+    """Dropout weights V with (p * mask) * scale and leaves Stats / Max / Sum_exp alone: probability dropout (the Bernoulli stream over the flat
+    score index, RNG_DUMP bit for bit the oracle's at every position, masked ones too) and a caller's mask with its scale (full size, and
+    broadcast over batch and query rows), with grouped heads, padding and a causal bound; the tensor-core kernels refuse dropout."""
+    b, hq, hk, sq, skv, d = 2, 6, 3, 37, 70, 16
+    q_dims, k_dims, v_dims, o_dims, row_dims = [b, hq, sq, d], [b, hk, skv, d], [b, hk, skv, d], [b, hq, sq, d], [b, hq, sq, 1]
+    raw = [synthetic.normal(21, i + 1, int(np.prod(dims))) for i, dims in enumerate((q_dims, k_dims, v_dims))]
+    rounded = [synthetic.round_to_bf16(a) if dtype == BF16 else a for a in raw]
+    host = [synthetic.to_bf16_bits(a) if dtype == BF16 else a for a in raw]
+    seq_q, seq_kv = np.array([sq, 20], np.int32), np.array([skv - 5, skv], np.int32)
+    mask_dims = [b, hq, sq, skv] if kind == "mask" else [1, hq, 1, skv]
+    mask = (synthetic.uniform(21, 7, int(np.prod(mask_dims)), 0.0, 1.0) < 0.75).astype(np.float32)
+    mask_scale = np.array([1.0 / 0.75], np.float32)
+    seed, offset = np.array([-977], np.int64), np.array([1 << 33], np.int64)
+
+    def fill(params, t):
+        params.q, params.k, params.v, params.o = (tensor(t, dims) for dims in (q_dims, k_dims, v_dims, o_dims))
+        params.stats = params.max = params.sum_exp = tensor(F32, row_dims)
+        params.attn_scale, params.s_kv, params.padding_mask, params.has_right_bound, params.right_bound = 0.25, skv, 1, 1, 3
+        params.seq_q = params.seq_kv = tensor(I32, [b, 1, 1, 1])
+        if kind == "probability":
+            params.dropout_kind, params.dropout_probability, params.rng_dump = 1, 0.3, tensor(F32, [b, hq, sq, skv])
+        else:
+            params.dropout_kind, params.dropout_mask = 2, tensor(F32, mask_dims)
+
+    op = oracle.SdpaParams()
+    fill(op, F32)
+    o_ref = np.full(int(np.prod(o_dims)), -99.0, np.float32)
+    rows_ref = [np.full(int(np.prod(row_dims)), -99.0, np.float32) for _ in range(3)]
+    dump_ref = np.full(b * hq * sq * skv, -1.0, np.float32)
+    tail = [None, None, seed, offset, dump_ref] if kind == "probability" else [mask, mask_scale, None, None, None]
+    oracle.sdpa_forward(op, rounded + [o_ref] + rows_ref + [seq_q, seq_kv] + [None] * 7 + tail)
+
+    gp = dfgpu.SdpaParams()
+    fill(gp, dtype)
+    if kind != "probability":
+        gp.dropout_scale = tensor(F32, [1, 1, 1, 1])
+    else:
+        gp.seed = gp.offset = tensor(dfgpu.I64, [1, 1, 1, 1])
+    gp.kernel = dfgpu.SDPA_AUTO
+    info = dfgpu.query("sdpa_forward", gp)
+    assert info.kernel == dfgpu.SDPA_ROWWISE
+    dev = [g.to_device(a) for a in host]
+    do = g.device_zeros(o_ref.size * dfgpu.DTYPE_BYTES[dtype])
+    drows = [g.device_zeros(rows_ref[0].size * 4) for _ in range(3)]
+    ddump = g.device_zeros(dump_ref.size * 4, 0x3C)
+    extra = [None, None, g.to_device(seed), g.to_device(offset), ddump] if kind == "probability" else [g.to_device(mask), g.to_device(mask_scale), None, None, None]
+    dfgpu.sdpa_forward(gp, [g.ptr(t) for t in dev + [do] + drows + [g.to_device(seq_q), g.to_device(seq_kv)] + [None] * 7 + extra])
+    o = synthetic.bf16_bits_to_f32(g.to_host(do, np.uint16)) if dtype == BF16 else g.to_host(do, np.float32)
+    (close_bf16 if dtype == BF16 else close_f32)(o, o_ref)
+    for got, want in zip(drows, rows_ref):
+        got = g.to_host(got, np.float32)
+        live = np.isfinite(want)
+        assert np.array_equal(np.isfinite(got), live) and np.allclose(got[live], want[live], rtol=1e-4, atol=1e-5)
+    if kind == "probability":
+        dump = g.to_host(ddump, np.float32)
+        assert np.array_equal(dump, dump_ref) and 0.6 < float(dump.mean()) < 0.8
+    # the same attention without dropout differs, and its statistics do not
+    gp.dropout_kind = 0
+    gp.rng_dump = dfgpu.Tensor()
+    do2, drows2 = g.device_zeros(o_ref.size * dfgpu.DTYPE_BYTES[dtype]), [g.device_zeros(rows_ref[0].size * 4) for _ in range(3)]
+    dfgpu.sdpa_forward(gp, [g.ptr(t) for t in dev + [do2] + drows2 + [g.to_device(seq_q), g.to_device(seq_kv)] + [None, None]])
+    assert not np.array_equal(g.to_host(do2, np.uint8), g.to_host(do, np.uint8))
+    assert np.array_equal(g.to_host(drows2[0], np.uint32), g.to_host(drows[0], np.uint32))
+    gp.dropout_kind = 1 if kind == "probability" else 2
+    for kernel in (dfgpu.SDPA_UMMA, dfgpu.SDPA_PAGED_DECODE):
+        gp.kernel = kernel
+        with pytest.raises(dfgpu.DfgpuError):
+            dfgpu.query("sdpa_forward", gp)
+
+
 def test_bias_keeps_the_tensor_core_kernels_out():
     params = dfgpu.SdpaParams()
     params.q = params.k = params.v = params.o = tensor(BF16, [1, 2, 256, 128])

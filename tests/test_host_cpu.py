@@ -214,7 +214,8 @@ def test_argument_table_is_sorted_with_clamped_alignment():
     (lambda: graphs.c4_sdpa(1, 2, 16, 8, io="HALF"), 0),
     (lambda: _with(graphs.c4_sdpa(1, 2, 16, 8), lambda d: d["nodes"][0].update(alibi_mask=True)), 0),
     (lambda: _with(graphs.c4_sdpa(1, 2, 16, 8), lambda d: d["nodes"][0].update(alibi_mask=True, diagonal_alignment="BOTTOM_RIGHT")), 20),
-    (lambda: _with(graphs.c4_sdpa(1, 2, 16, 8), lambda d: d["nodes"][0].update(dropout_probability=0.1)), 20),
+    (lambda: _with(graphs.c4_sdpa(1, 2, 16, 8), lambda d: d["nodes"][0].update(dropout_probability=0.1)), 8),   # (probability dropout without Seed and Offset)
+    (lambda: _with(graphs.c4_sdpa(1, 2, 16, 8), lambda d: d["nodes"][0].update(dropout_probability=1.0)), 8),
     (lambda: _with(graphs.c4_sdpa(1, 2, 16, 8), lambda d: d["nodes"][0].update(generate_stats=False)), 8),
     (lambda: _with(graphs.c2_bottleneck(n=1, h=8, w=8), lambda d: d["nodes"][2].update(mode="GELU_FWD")), 20),
     (lambda: _with(graphs.c1_conv(n=1, c=3, h=5, w=5, k=5), lambda d: d["tensors"]["3"].update(dim=[1, 5, 4, 5], stride=[100, 1, 25, 5])), 15),
@@ -301,7 +302,7 @@ def test_compact_page_tables_plan_metadata_and_rejections(tmp_path):
     doc = graphs.c5_paged_decode(batch=4, pages=64, block=64, max_len=1024, compact=True)
     exe = runtime.compile_graph(doc)
     assert "sdpa_forward kernel=4 launches=2" in strided.plan_text() and "sdpa_forward kernel=4 launches=3" in exe.plan_text()
-    assert exe.plan_text().rstrip().endswith("uid9 uid10 scratch=ws+0") and exe.workspace_size == strided.workspace_size + 256
+    assert exe.plan_text().rstrip().endswith("uid9 uid10 - - - - - scratch=ws+0") and exe.workspace_size == strided.workspace_size + 256
     assert [a["uid"] for a in exe.arguments()] == list(range(1, 11))
     target = tmp_path / "compact.dfo"
     exe.write_artifact(target)

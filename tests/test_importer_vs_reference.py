@@ -289,3 +289,78 @@ def test_sdpa_restatement_agrees_with_the_references_own_test_oracle(case):
     live = re > 0  # rows with at least one valid key (or a sink): the others have no defined statistics
     assert live.any()
     assert np.allclose(maximum[live], rm[live], rtol=1e-6, atol=1e-6) and np.allclose(sum_exp[live], re[live], rtol=2e-5) and np.allclose(stats[live], rs[live], rtol=2e-5, atol=2e-6)
+
+
+def test_bernoulli_stream_agrees_with_the_references_own():
+    """dfo_bernoulli against bernoulli() of test/Compiler/SequenceOpsTest.cpp:199-222 (the stream the reference's RNG and dropout tests hold its
+    compiler to): seeds and offsets of either sign, flat indices past 2^32, keep probabilities from 0 to 1."""
+    import numpy as np
+    sys.path.insert(0, str(ROOT / "tests"))
+    import oracle
+    lib = _reference_attention()
+    lib.ref_bernoulli.restype = C.c_float
+    rng = np.random.default_rng(7)
+    kept = 0
+    for _ in range(4000):
+        seed, offset = int(rng.integers(-2 ** 62, 2 ** 62)), int(rng.integers(-2 ** 40, 2 ** 40))
+        linear = int(rng.integers(0, 2 ** 40))
+        keep = float(rng.choice([0.0, 0.1, 0.375, 0.5, 0.6, 0.9, 0.999999, 1.0]))
+        ours = oracle.bernoulli(seed, offset, linear, keep)
+        theirs = float(lib.ref_bernoulli(C.c_int64(seed), C.c_int64(offset), C.c_uint64(linear), C.c_double(keep)))
+        assert ours == theirs
+        kept += int(ours)
+    assert 1000 < kept < 3000
+    # the cases the reference's tests use: seed -31, offset 19, keep 0.375 (:1149-1165) and seed 123, offset 9, keep 0.6 (:2351-2371)
+    for seed, offset, keep in ((-31, 19, 0.375), (123, 9, 0.6), (17, 0, 0.375)):
+        assert [oracle.bernoulli(seed, offset, i, keep) for i in range(6)] == [float(lib.ref_bernoulli(C.c_int64(seed), C.c_int64(offset), C.c_uint64(i), C.c_double(keep))) for i in range(6)]
+
+
+@pytest.mark.parametrize("kind", ["mask", "probability"])
+def test_sdpa_dropout_restatement_agrees_with_the_references_own_test_oracle(kind):
+    """Dropout in oracle/df_oracle.c's SDPA forward against attention_forward of test/Compiler/SequenceOpsTest.cpp (its dropout_mask and
+    dropout_scale, :493-498): a caller's mask with its scale, and probability dropout, whose mask the restatement draws from the Bernoulli stream
+    and writes to RNG_DUMP (compared with the reference's stream, then fed to the reference oracle as its mask, as :2351-2390 does)."""
+    import numpy as np
+    sys.path.insert(0, str(ROOT / "tests"))
+    import oracle
+    from deepforge_b200.dfgpu import F32, I32, I64, tensor
+    lib = _reference_attention()
+    lib.ref_bernoulli.restype = C.c_float
+    rng = np.random.default_rng(41)
+    b, hq, hk, hv, sq, skv, d, dv = 2, 4, 2, 4, 7, 11, 8, 5
+    q = rng.standard_normal((b, hq, sq, d)).astype(np.float32)
+    k = rng.standard_normal((b, hk, skv, d)).astype(np.float32)
+    v = rng.standard_normal((b, hv, skv, dv)).astype(np.float32)
+    seq_q, seq_kv = np.array([sq, 4], np.int32), np.array([skv - 2, skv], np.int32)
+    scale = 0.29
+    p = oracle.SdpaParams()
+    p.q, p.k, p.v, p.o = tensor(F32, list(q.shape)), tensor(F32, list(k.shape)), tensor(F32, list(v.shape)), tensor(F32, [b, hq, sq, dv])
+    p.stats = p.max = p.sum_exp = tensor(F32, [b, hq, sq, 1])
+    p.attn_scale, p.s_kv, p.padding_mask, p.has_right_bound, p.right_bound = scale, skv, 1, 1, 2
+    p.seq_q = p.seq_kv = tensor(I32, [b, 1, 1, 1])
+    rows = b * hq * sq
+    o, stats, maximum, sum_exp = (np.zeros(rows * dv, np.float32), np.zeros(rows, np.float32), np.zeros(rows, np.float32), np.zeros(rows, np.float32))
+    if kind == "mask":
+        mask = (rng.random((b, hq, sq, skv)) < 0.7).astype(np.float32)
+        mask[0, 1] = 0.5  # (the mask is a FLOAT tensor: any value multiplies)
+        dropout_scale = np.array([1.0 / 0.7], np.float32)
+        p.dropout_kind, p.dropout_mask = 2, tensor(F32, list(mask.shape))
+        oracle.sdpa_forward(p, [q, k, v, o, stats, maximum, sum_exp, seq_q, seq_kv, None, None, None, None, None, None, None, mask, dropout_scale])
+    else:
+        probability, seed, offset = 0.4, np.array([123], np.int64), np.array([9], np.int64)
+        dump = np.full(b * hq * sq * skv, -1.0, np.float32)
+        p.dropout_kind, p.dropout_probability, p.rng_dump = 1, probability, tensor(F32, [b, hq, sq, skv])
+        oracle.sdpa_forward(p, [q, k, v, o, stats, maximum, sum_exp, seq_q, seq_kv, None, None, None, None, None, None, None, None, None, seed, offset, dump])
+        expected = np.array([lib.ref_bernoulli(C.c_int64(123), C.c_int64(9), C.c_uint64(i), C.c_double(1.0 - probability)) for i in range(dump.size)], np.float32)
+        assert np.array_equal(dump, expected) and 0.5 < dump.mean() < 0.7
+        mask, dropout_scale = dump.reshape(b, hq, sq, skv), np.array([1.0 / (1.0 - probability)], np.float32)
+    ro, rs, rm, re = (np.zeros_like(o), np.zeros_like(stats), np.zeros_like(maximum), np.zeros_like(sum_exp))
+    i64 = lambda a: (C.c_int64 * 4)(*[int(x) for x in a])
+    ptr = lambda a, t: a.ctypes.data_as(C.POINTER(t)) if a is not None else None
+    lib.ref_attention_forward_dropout.restype = C.c_int
+    lib.ref_attention_forward_dropout(i64(q.shape), i64(k.shape), i64(v.shape), ptr(q, C.c_float), ptr(k, C.c_float), ptr(v, C.c_float), ptr(seq_q, C.c_int32),
+                                      ptr(seq_kv, C.c_int32), C.c_float(scale), 1, 1, C.c_int64(2), ptr(np.ascontiguousarray(mask), C.c_float),
+                                      C.c_float(float(dropout_scale[0])), ptr(ro, C.c_float), ptr(rs, C.c_float), ptr(rm, C.c_float), ptr(re, C.c_float))
+    assert np.allclose(o, ro, rtol=2e-5, atol=2e-6) and np.abs(ro).max() > 0.1
+    live = re > 0
+    assert live.any() and np.allclose(stats[live], rs[live], rtol=2e-5, atol=2e-6)   # (statistics are those without dropout)
