@@ -193,6 +193,21 @@ __global__ void bsq_generic_kernel(const void* x, uint8_t* y, uint8_t* scale, Vi
         uint32_t bits = __float_as_uint(value) & 0x7fffffffu;
         amax_bits = bits > amax_bits ? bits : amax_bits;
     }
+    if (yv.dtype == DFGPU_FP4) {
+        // FP4 codes take an E4M3 scale that is not made a power of two (lib/Compiler/SpecializedGraph.cpp:810-838): amax / 6, 1 when that
+        // is not positive, NaN kept; every value is divided by the STORED scale (:927-931) and packed two codes to a byte
+        const float desired = __fdiv_rn(__uint_as_float(amax_bits), 6.0f);
+        float guarded = desired > 0.0f ? desired : 1.0f;
+        if (desired != desired) guarded = desired;
+        const uint32_t scale_code = encode_e4m3_scalar(guarded);
+        scale[scale_offset(sv, layout, index)] = static_cast<uint8_t>(scale_code);
+        const float stored = decode_e4m3(scale_code);
+        for (int64_t j = 0; j < block; ++j) {
+            const float value = __fdiv_rn(load_as_f32(x, xv.dtype, x_base + j * xv.stride[axis]), stored);
+            store_nibble(y, y_base + j * yv.stride[axis], encode_e2m1_scalar(value));
+        }
+        return;
+    }
     const bool e5m2 = yv.dtype == DFGPU_E5M2;
     uint32_t code = scale_code_from_amax_bits(amax_bits, e5m2 ? 57344.0f : 448.0f);
     scale[scale_offset(sv, layout, index)] = static_cast<uint8_t>(code);
@@ -717,8 +732,9 @@ __global__ void bsd_generic_kernel(const uint8_t* x, const uint8_t* scale, void*
         xo += index[i] * xv.stride[i];
         yo += index[i] * yv.stride[i];
     }
-    float code_value = xv.dtype == DFGPU_E5M2 ? decode_e5m2(x[xo]) : decode_e4m3(x[xo]);
-    float value = __fmul_rn(code_value, decode_e8m0(scale[scale_offset(sv, layout, scale_index)]));
+    // codes: FP8 (a byte each) or FP4 / INT4 (two to a byte); scales: E8M0, E4M3 or a plain floating type
+    float code_value = load_as_f32(x, xv.dtype, xo);
+    float value = __fmul_rn(code_value, load_as_f32(scale, sv.dtype, scale_offset(sv, layout, scale_index)));
     store_from_f32(y, yv.dtype, yo, value);
 }
 
@@ -794,8 +810,11 @@ int plan_bsq(const dfgpu_bsq_params& p, BsqPlan& plan) {
         return fail(kInvalidShape, "BLOCK_SCALE_QUANTIZE: tensor rank or extent out of range");
     if (p.x.dtype != DFGPU_F32 && p.x.dtype != DFGPU_F16 && p.x.dtype != DFGPU_BF16)
         return fail(kUnsupported, "BLOCK_SCALE_QUANTIZE: X must be FLOAT, HALF or BFLOAT16");
-    if ((p.y.dtype != DFGPU_E4M3 && p.y.dtype != DFGPU_E5M2) || p.scale.dtype != DFGPU_E8M0)
-        return fail(kUnsupported, "BLOCK_SCALE_QUANTIZE: only FP8_E4M3 or FP8_E5M2 codes with FP8_E8M0 scales are executable");
+    // lib/Compiler/SpecializedGraph.cpp:368-380
+    const bool fp4 = p.y.dtype == DFGPU_FP4;
+    if (fp4 ? p.scale.dtype != DFGPU_E4M3 : ((p.y.dtype != DFGPU_E4M3 && p.y.dtype != DFGPU_E5M2) || p.scale.dtype != DFGPU_E8M0))
+        return fail(kUnsupported, "BLOCK_SCALE_QUANTIZE: FP8_E4M3 or FP8_E5M2 codes take FP8_E8M0 scales, FP4_E2M1 codes FP8_E4M3 scales");
+    if (fp4 && p.scale.reorder != DFGPU_REORDER_NONE) return fail(kUnsupported, "BLOCK_SCALE_QUANTIZE: FP4 codes take an unreordered scale tensor");
     int rank = p.x.rank;
     if (p.y.rank != rank || p.scale.rank != rank)
         return fail(kInvalidShape, "BLOCK_SCALE_QUANTIZE: X, Y and scale ranks differ");
@@ -843,7 +862,7 @@ int plan_bsq(const dfgpu_bsq_params& p, BsqPlan& plan) {
             }
         }
     }
-    if (p.y.dtype == DFGPU_E5M2) kernel = DFGPU_BSQ_GENERIC;   // (the fast kernels are built on the hardware e4m3x2 convert)
+    if (p.y.dtype != DFGPU_E4M3) kernel = DFGPU_BSQ_GENERIC;   // (the fast kernels are built on the hardware e4m3x2 convert)
     if (p.kernel != DFGPU_BSQ_AUTO && p.kernel != kernel) {
         if (p.kernel == DFGPU_BSQ_GENERIC) kernel = DFGPU_BSQ_GENERIC;
         else return fail(kUnsupported, "BLOCK_SCALE_QUANTIZE: requested kernel %d does not cover this layout", p.kernel);
@@ -923,12 +942,13 @@ extern "C" int dfgpu_block_scale_quantize(const dfgpu_bsq_params* p, void* const
     if (plan.needs_fill) {
         // step 1 of the reference: every scale slot, padding included, <- encode(1.0)
         int64_t count = element_count(p->scale);
+        const uint8_t one = p->scale.dtype == DFGPU_E4M3 ? 0x38 : 0x7f;   // 1.0 as E4M3 (FP4 codes) or E8M0
         if (plan.layout.reordered || is_packed_row_major(p->scale)) {
             int64_t threads = (count + 15) / 16;
-            fill_bytes_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(scale, count, 0x7f);
+            fill_bytes_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(scale, count, one);
         } else {
             fill_strided_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream>>>(
-                scale, make_view(p->scale), count, 0x7f);
+                scale, make_view(p->scale), count, one);
         }
     }
 
@@ -975,8 +995,12 @@ struct BsdPlan {
 int plan_bsd(const dfgpu_bsd_params& p, BsdPlan& plan) {
     if (!valid_tensor(p.x) || !valid_tensor(p.y) || !valid_tensor(p.scale))
         return fail(kInvalidShape, "BLOCK_SCALE_DEQUANTIZE: tensor rank or extent out of range");
-    if ((p.x.dtype != DFGPU_E4M3 && p.x.dtype != DFGPU_E5M2) || p.scale.dtype != DFGPU_E8M0)
-        return fail(kUnsupported, "BLOCK_SCALE_DEQUANTIZE: only FP8_E4M3 or FP8_E5M2 codes with FP8_E8M0 scales are executable");
+    // lib/Compiler/SpecializedGraph.cpp:291-302
+    const bool code_ok = p.x.dtype == DFGPU_E4M3 || p.x.dtype == DFGPU_E5M2 || p.x.dtype == DFGPU_FP4 || p.x.dtype == DFGPU_I4;
+    const bool scale_ok = p.scale.dtype == DFGPU_E8M0 || p.scale.dtype == DFGPU_E4M3 || p.scale.dtype == DFGPU_F32 || p.scale.dtype == DFGPU_F16 || p.scale.dtype == DFGPU_BF16;
+    if (!code_ok || !scale_ok)
+        return fail(kUnsupported, "BLOCK_SCALE_DEQUANTIZE: X must be FP8_E4M3, FP8_E5M2, FP4_E2M1 or INT4 and the scale FP8_E8M0, FP8_E4M3, FLOAT, HALF or BFLOAT16");
+    if (p.scale.dtype != DFGPU_E8M0 && p.scale.reorder != DFGPU_REORDER_NONE) return fail(kUnsupported, "BLOCK_SCALE_DEQUANTIZE: only FP8_E8M0 scales may be reordered");
     if (p.y.dtype != DFGPU_F32 && p.y.dtype != DFGPU_F16 && p.y.dtype != DFGPU_BF16)
         return fail(kUnsupported, "BLOCK_SCALE_DEQUANTIZE: Y must be FLOAT, HALF or BFLOAT16");
     int rank = p.y.rank;
@@ -1000,7 +1024,7 @@ int plan_bsd(const dfgpu_bsd_params& p, BsdPlan& plan) {
         p.y.dim[1] % plan.blocks[1] == 0 && p.scale.dim[0] == p.y.dim[0] / plan.blocks[0] &&
         p.scale.dim[1] == p.y.dim[1] / plan.blocks[1] && (plan.blocks[1] % 16 == 0 || plan.blocks[1] < 16))
         kernel = DFGPU_BSD_PACKED;
-    if (p.x.dtype == DFGPU_E5M2) kernel = DFGPU_BSD_GENERIC;
+    if (p.x.dtype != DFGPU_E4M3 || p.scale.dtype != DFGPU_E8M0) kernel = DFGPU_BSD_GENERIC;
     if (p.kernel != DFGPU_BSD_AUTO && p.kernel != kernel) {
         if (p.kernel == DFGPU_BSD_GENERIC) kernel = DFGPU_BSD_GENERIC;
         else return fail(kUnsupported, "BLOCK_SCALE_DEQUANTIZE: requested kernel %d does not cover this layout", p.kernel);

@@ -69,5 +69,5 @@ extern "C" const char* dfgpu_last_error(void) { return dfgpu::g_error; }
 // 4: dfgpu_conv_fprop_pair, dfgpu_block_scale_quantize_pair. 5: dfgpu_sdpa_params gained page_offsets_k / page_offsets_v
 // (16 pointers), DFGPU_I64, DFGPU_CONV_UMMA_F32X3, DFGPU_MATMUL_UMMA_F32X3 in place of the two-SM MXFP8 id.
 // 6: DFGPU_CONV_UMMA_F32X3_CLUSTER, DFGPU_MATMUL_UMMA_F32X3_CLUSTER. 7: dfgpu_conv_params gained the depth attributes (rank 5).
-// 8: dfgpu_sdpa_params gained dropout (21 pointers).
-extern "C" int dfgpu_abi_version(void) { return 8; }
+// 8: dfgpu_sdpa_params gained dropout (21 pointers). 9: DFGPU_FP4, DFGPU_I4.
+extern "C" int dfgpu_abi_version(void) { return 9; }

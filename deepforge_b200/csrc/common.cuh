@@ -170,6 +170,48 @@ __device__ __forceinline__ uint32_t encode_e5m2_scalar(float v) {
     return packed & 0xffu;
 }
 
+// FP4 E2M1 (lib/Compiler/Numeric.cpp:155-168): the low four bits of the code.
+__device__ __forceinline__ float decode_e2m1(uint32_t code) {
+    const uint32_t exponent = (code >> 1) & 3u, mantissa = code & 1u;
+    const float value = exponent == 0 ? 0.5f * static_cast<float>(mantissa) : ldexpf(1.0f + 0.5f * static_cast<float>(mantissa), static_cast<int>(exponent) - 1);
+    return (code & 8u) ? -value : value;
+}
+// f32 -> FP4 E2M1 as the reference's search gives it (lib/Compiler/Numeric.cpp:396-425, 504-632): the nearest of the 16 codes, an even code
+// taking a tie from an odd one, exact zero with its sign, |v| > 6 -> 0x7 | sign, NaN -> 0x7.
+__device__ __forceinline__ uint32_t encode_e2m1_scalar(float v) {
+    uint32_t best = 0;
+    float best_difference = fabsf(__fsub_rn(v, decode_e2m1(0)));
+    for (uint32_t candidate = 0; candidate < 16; ++candidate) {
+        const float difference = fabsf(__fsub_rn(v, decode_e2m1(candidate)));
+        if (difference < best_difference || (difference == best_difference && (candidate & 1u) == 0u && (best & 1u) != 0u)) {
+            best = candidate;
+            best_difference = difference;
+        }
+    }
+    const bool negative = (__float_as_uint(v) & 0x80000000u) != 0u;
+    const float absolute = fabsf(v);
+    uint32_t result = best;
+    if (absolute == 0.0f) result = negative ? 0x8u : 0x0u;
+    if (absolute > 6.0f) result = 0x7u | (negative ? 0x8u : 0x0u);
+    if (v != v) result = 0x7u;
+    return result;
+}
+// Packed four-bit tensors: element offset e is nibble e % 2 of byte e / 2. A store keeps the byte's other nibble; neighbouring
+// elements may belong to other threads, so it goes through a compare-and-swap on the aligned word that holds the byte.
+__device__ __forceinline__ uint32_t load_nibble(const void* data, int64_t offset) {
+    return (static_cast<const uint8_t*>(data)[offset >> 1] >> ((offset & 1) * 4)) & 0xfu;
+}
+__device__ __forceinline__ void store_nibble(void* data, int64_t offset, uint32_t code) {
+    uint8_t* byte = static_cast<uint8_t*>(data) + (offset >> 1);
+    uint32_t* word = reinterpret_cast<uint32_t*>(reinterpret_cast<uintptr_t>(byte) & ~static_cast<uintptr_t>(3));
+    const uint32_t shift = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(byte) & 3u) * 8u + static_cast<uint32_t>(offset & 1) * 4u;
+    uint32_t seen = *word, assumed;
+    do {
+        assumed = seen;
+        seen = atomicCAS(word, assumed, (assumed & ~(0xfu << shift)) | ((code & 0xfu) << shift));
+    } while (seen != assumed);
+}
+
 __device__ __forceinline__ float load_as_f32(const void* data, int dtype, int64_t offset) {
     switch (dtype) {
         case DFGPU_F32: return static_cast<const float*>(data)[offset];
@@ -179,6 +221,8 @@ __device__ __forceinline__ float load_as_f32(const void* data, int dtype, int64_
         case DFGPU_E8M0: return decode_e8m0(static_cast<const uint8_t*>(data)[offset]);
         case DFGPU_E5M2: return decode_e5m2(static_cast<const uint8_t*>(data)[offset]);
         case DFGPU_I32: return static_cast<float>(static_cast<const int32_t*>(data)[offset]);
+        case DFGPU_FP4: return decode_e2m1(load_nibble(data, offset));
+        case DFGPU_I4: { const int nibble = static_cast<int>(load_nibble(data, offset)); return static_cast<float>(nibble >= 8 ? nibble - 16 : nibble); }
         default: return 0.0f;
     }
 }
@@ -190,6 +234,7 @@ __device__ __forceinline__ void store_from_f32(void* data, int dtype, int64_t of
         case DFGPU_BF16: static_cast<uint16_t*>(data)[offset] = f32_to_bf16_bits(value); break;
         case DFGPU_E4M3: static_cast<uint8_t*>(data)[offset] = static_cast<uint8_t>(encode_e4m3_scalar(value)); break;
         case DFGPU_E5M2: static_cast<uint8_t*>(data)[offset] = static_cast<uint8_t>(encode_e5m2_scalar(value)); break;
+        case DFGPU_FP4: store_nibble(data, offset, encode_e2m1_scalar(value)); break;
         default: break;
     }
 }

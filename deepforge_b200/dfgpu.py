@@ -13,9 +13,9 @@ from typing import Iterable, Optional, Sequence
 MAX_RANK = 8
 MAX_EPILOGUE = 4
 
-F32, F16, BF16, E4M3, E8M0, I32, E5M2, U8, BF16X2, I64 = range(10)
+F32, F16, BF16, E4M3, E8M0, I32, E5M2, U8, BF16X2, I64, FP4, I4 = range(12)
 REORDER_NONE, REORDER_F8_128x4 = 0, 1
-DTYPE_BYTES = {F32: 4, F16: 2, BF16: 2, E4M3: 1, E8M0: 1, I32: 4, E5M2: 1, U8: 1, BF16X2: 4, I64: 8}
+DTYPE_BYTES = {F32: 4, F16: 2, BF16: 2, E4M3: 1, E8M0: 1, I32: 4, E5M2: 1, U8: 1, BF16X2: 4, I64: 8}  # (FP4 and I4: two elements per byte)
 
 EPI_ADD, EPI_RELU = 1, 2
 PW_ADD, PW_RELU_FWD, PW_IDENTITY, PW_MUL, PW_SUB = range(5)

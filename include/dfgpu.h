@@ -51,7 +51,10 @@ enum {
        multiply both halves by the same bf16 filter, so an intermediate keeps f32-grade precision through bf16
        tensor-core products. */
     DFGPU_BF16X2 = 8,
-    DFGPU_I64 = 9   /* INT64: the offsets of a compact page table only */
+    DFGPU_I64 = 9,  /* INT64: the offsets of a compact page table, Seed and Offset of SDPA dropout */
+    DFGPU_FP4 = 10, /* FP4_E2M1, two codes per byte: element offset e (by the strides) is the low nibble of byte e / 2 when e is even, the
+                       high one when it is odd (lib/Compiler/Numeric.cpp:326-393). BLOCK_SCALE_QUANTIZE output / DEQUANTIZE input only */
+    DFGPU_I4 = 11   /* INT4, packed the same way, two's-complement nibbles. BLOCK_SCALE_DEQUANTIZE input only */
 };
 
 enum { DFGPU_REORDER_NONE = 0, DFGPU_REORDER_F8_128x4 = 1 };

@@ -79,6 +79,48 @@ uint8_t dfo_encode_e5m2(float value) {
     return result;
 }
 
+/* Numeric.cpp:155-168: FP4 E2M1, the low four bits of the code */
+float dfo_decode_e2m1(uint8_t code) {
+    code &= 0x0fu;
+    int sign = (code & 0x08u) != 0;
+    unsigned exponent = (code >> 1) & 0x03u;
+    unsigned mantissa = code & 0x01u;
+    float value;
+    if (exponent == 0) {
+        value = (float)mantissa * 0.5f;
+    } else {
+        value = ldexpf(1.0f + (float)mantissa * 0.5f, (int)exponent - 1);
+    }
+    return sign ? -value : value;
+}
+
+/* Numeric.cpp:396-425, 504-632, FP4 branch: the search over all 16 codes (every one is a valid candidate), exact zero
+   keeps its sign (0x08), |v| > 6 saturates to 0x07|sign, NaN is 0x07. */
+uint8_t dfo_encode_e2m1(float value) {
+    uint8_t best = 0;
+    float best_difference = fabsf(value - dfo_decode_e2m1(0));
+    for (unsigned candidate = 0; candidate < 16; ++candidate) {
+        float difference = fabsf(value - dfo_decode_e2m1((uint8_t)candidate));
+        int better = difference < best_difference;
+        int equal = difference == best_difference;
+        int candidate_even = (candidate & 1u) == 0;
+        int best_odd = (best & 1u) != 0;
+        if (better || (equal && candidate_even && best_odd)) {
+            best = (uint8_t)candidate;
+            best_difference = difference;
+        }
+    }
+    uint32_t bits;
+    memcpy(&bits, &value, 4);
+    int negative = (bits & 0x80000000u) != 0;
+    float absolute = fabsf(value);
+    uint8_t result = best;
+    if (absolute == 0.0f) result = negative ? 0x08 : 0x00;
+    if (absolute > 6.0f) result = (uint8_t)(0x07 | (negative ? 0x08 : 0x00));
+    if (value != value) result = 0x07;
+    return result;
+}
+
 /* Numeric.cpp:148-153 */
 float dfo_decode_e8m0(uint8_t code) {
     if (code == 0xffu) return NAN;
@@ -285,6 +327,12 @@ static float load_f32(const dfo_tensor* t, const void* data, int64_t offset) {
         case DFO_E8M0: return dfo_decode_e8m0(((const uint8_t*)data)[offset]);
         case DFO_E5M2: return dfo_decode_e5m2(((const uint8_t*)data)[offset]);
         case DFO_I32: return (float)((const int32_t*)data)[offset];
+        /* Numeric.cpp:326-349: element offset e of a packed tensor is nibble e % 2 of byte e / 2 */
+        case DFO_FP4: return dfo_decode_e2m1((uint8_t)(((const uint8_t*)data)[offset / 2] >> ((offset % 2) * 4)));
+        case DFO_I4: { /* Numeric.cpp:664-676: a two's-complement nibble */
+            int nibble = (((const uint8_t*)data)[offset / 2] >> ((offset % 2) * 4)) & 0x0f;
+            return (float)(nibble >= 8 ? nibble - 16 : nibble);
+        }
         default: return NAN;
     }
 }
@@ -298,6 +346,12 @@ static void store_f32(const dfo_tensor* t, void* data, int64_t offset, float val
         case DFO_E4M3: ((uint8_t*)data)[offset] = dfo_encode_e4m3(value); break;
         case DFO_E5M2: ((uint8_t*)data)[offset] = dfo_encode_e5m2(value); break;
         case DFO_E8M0: ((uint8_t*)data)[offset] = dfo_encode_e8m0(value); break;
+        case DFO_FP4: { /* Numeric.cpp:351-393: the other nibble of the byte is kept */
+            uint8_t* byte = (uint8_t*)data + offset / 2;
+            uint8_t code = dfo_encode_e2m1(value) & 0x0f;
+            *byte = (offset % 2) ? (uint8_t)((*byte & 0x0f) | (code << 4)) : (uint8_t)((*byte & 0xf0) | code);
+            break;
+        }
         default: break;
     }
 }
@@ -338,8 +392,10 @@ int dfo_block_scale_quantize(const dfo_tensor* x, const void* x_data,
                              const dfo_tensor* y, void* y_data,
                              const dfo_tensor* scale, void* scale_data,
                              int64_t block, int32_t axis) {
-    if ((y->dtype != DFO_E4M3 && y->dtype != DFO_E5M2) || scale->dtype != DFO_E8M0) return 20;
-    const float largest = y->dtype == DFO_E5M2 ? 57344.0f : 448.0f; /* quantized_maximum, SpecializedGraph.cpp:795-808 */
+    /* SpecializedGraph.cpp:368-380: FP8 codes take an E8M0 scale, FP4 codes an E4M3 one */
+    const int fp4 = y->dtype == DFO_FP4;
+    if (fp4 ? scale->dtype != DFO_E4M3 : ((y->dtype != DFO_E4M3 && y->dtype != DFO_E5M2) || scale->dtype != DFO_E8M0)) return 20;
+    const float largest = fp4 ? 6.0f : (y->dtype == DFO_E5M2 ? 57344.0f : 448.0f); /* quantized_maximum, SpecializedGraph.cpp:795-808 */
     if (axis < 0) axis = x->rank - 1;
     if (axis >= x->rank || block <= 0 || x->dim[axis] % block != 0) return 15;
     int64_t index[DFO_MAX_RANK];
@@ -366,7 +422,7 @@ int dfo_block_scale_quantize(const dfo_tensor* x, const void* x_data,
         float desired = amax / largest;
         float guarded = desired > 0.0f ? desired : 1.0f;
         if (desired != desired) guarded = desired;
-        guarded = powf(2.0f, ceilf(log2f(guarded)));
+        if (scale->dtype == DFO_E8M0) guarded = powf(2.0f, ceilf(log2f(guarded))); /* :829-836: a power of two for E8M0 scales only */
         store_f32(scale, scale_data, element_offset(scale, index), guarded);
     }
 

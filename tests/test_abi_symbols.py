@@ -21,7 +21,7 @@ def test_kernel_library_exports_every_declared_symbol():
     for name in names:
         assert hasattr(lib, name), name
     assert sorted(dfgpu.EXPORTS) == names
-    assert lib.dfgpu_abi_version() == 8
+    assert lib.dfgpu_abi_version() == 9
 
 
 def test_struct_layout_matches_header():

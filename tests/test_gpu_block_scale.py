@@ -4,7 +4,7 @@ import pytest
 
 import oracle
 from deepforge_b200 import dfgpu, synthetic
-from deepforge_b200.dfgpu import BF16, E4M3, E5M2, E8M0, F16, F32, REORDER_F8_128x4, tensor
+from deepforge_b200.dfgpu import BF16, E4M3, E5M2, E8M0, F16, F32, FP4, I4, REORDER_F8_128x4, tensor
 
 pytestmark = pytest.mark.gpu
 
@@ -108,6 +108,62 @@ def test_e5m2_codes_match_oracle_and_the_reference_known_answers(dtype):
                     else synthetic.bf16_bits_to_f32(out.view(np.uint16)))
         nan = np.isnan(as_float)
         assert np.array_equal(a[~nan], b[~nan]) and nan.any() == special
+
+
+@pytest.mark.parametrize("dtype", [F32, F16, BF16])
+def test_packed_four_bit_codes_match_oracle_and_the_reference_known_answers(dtype):
+    """FP4_E2M1 codes (two to a byte) with FP8_E4M3 scales, and INT4 with floating scales, on the general kernels: the reference's known
+    answers (test/Compiler/SpecializedOpsTest.cpp:661-681, :736-754) and bit-exact parity with the oracle on ordinary and special values,
+    blocks along the contiguous axis and across it (neighbouring threads then share bytes)."""
+    import gpu_util as g
+    if dtype == F32:
+        p = dfgpu.BsqParams()
+        p.x, p.y, p.scale, p.block_size, p.axis = tensor(F32, [1, 4]), tensor(FP4, [1, 4]), tensor(E4M3, [1, 2]), 2, 1
+        assert dfgpu.query("block_scale_quantize", p).kernel == dfgpu.BSQ_GENERIC
+        dx, dy, ds = g.to_device(np.array([1.0, 2.0, -3.0, 6.0], dtype=np.float32)), g.device_zeros(4), g.device_zeros(4)
+        dfgpu.block_scale_quantize(p, g.ptr(dx), g.ptr(dy), g.ptr(ds))
+        q = dfgpu.BsdParams()
+        q.x, q.scale, q.y, q.block_count = tensor(FP4, [1, 4]), tensor(E4M3, [1, 2]), tensor(F32, [1, 4]), 1
+        q.block[0] = 2
+        dout = g.device_zeros(16)
+        dfgpu.block_scale_dequantize(q, g.ptr(dy), g.ptr(ds), g.ptr(dout))
+        assert g.to_host(dout, np.float32).tolist() == [1.03125, 2.0625, -3.0, 6.0]
+        q.x, q.scale, q.y = tensor(I4, [1, 4]), tensor(F16, [1, 2]), tensor(BF16, [1, 4])
+        dx, ds, dout = g.to_device(np.array([0xf8, 0x70, 0, 0], dtype=np.uint8)), g.to_device(np.array([0x3800, 0x4000], dtype=np.uint16)), g.device_zeros(8)
+        dfgpu.block_scale_dequantize(q, g.ptr(dx), g.ptr(ds), g.ptr(dout))
+        assert g.to_host(dout, np.uint16).tolist() == [0xc080, 0xbf00, 0x0000, 0x4160]
+    for shape, block, axis, special in (([64, 128], 16, 1, False), ([64, 128], 32, 1, True), ([96, 40], 32, 0, True), ([3, 20, 24], 4, 1, True)):
+        count = int(np.prod(shape))
+        x = _make_x(dtype, shape, 31, special)
+        logical = list(shape)
+        logical[axis] //= block
+        xd, yd, sd = tensor(dtype, shape), tensor(FP4, shape), tensor(E4M3, logical)
+        y_ref, s_ref = np.zeros(count // 2, dtype=np.uint8), np.zeros(int(np.prod(logical)), dtype=np.uint8)
+        oracle.block_scale_quantize(xd, x, yd, y_ref, sd, s_ref, block, axis)
+        p = dfgpu.BsqParams()
+        p.x, p.y, p.scale, p.block_size, p.axis = xd, yd, sd, block, axis
+        dx, dy, ds = g.to_device(x), g.device_zeros(count // 2, 0x55), g.device_zeros(s_ref.size, 0xAA)
+        dfgpu.block_scale_quantize(p, g.ptr(dx), g.ptr(dy), g.ptr(ds))
+        assert np.array_equal(g.to_host(ds, np.uint8), s_ref) and np.array_equal(g.to_host(dy, np.uint8), y_ref)
+        # back through the general dequantize kernel, and the same nibbles read as INT4 with bf16 scales
+        blocks = [1] * len(shape)
+        blocks[axis] = block
+        for code_type, scale_type, scales in ((FP4, E4M3, s_ref), (I4, BF16, synthetic.to_bf16_bits(synthetic.uniform(31, 3, s_ref.size, -2.0, 2.0)))):
+            width = dfgpu.DTYPE_BYTES[dtype]
+            ref = np.zeros(count * width, dtype=np.uint8)
+            oracle.block_scale_dequantize(tensor(code_type, shape), y_ref, tensor(scale_type, logical), scales, tensor(dtype, shape), ref, blocks)
+            q = dfgpu.BsdParams()
+            q.x, q.scale, q.y, q.block_count = tensor(code_type, shape), tensor(scale_type, logical), tensor(dtype, shape), len(shape)
+            for i, b in enumerate(blocks):
+                q.block[i] = b
+            dcodes, dscales, dout = g.to_device(y_ref), g.to_device(scales), g.device_zeros(ref.size, 0x11)
+            dfgpu.block_scale_dequantize(q, g.ptr(dcodes), g.ptr(dscales), g.ptr(dout))
+            out = g.to_host(dout, np.uint8)
+            view = np.uint32 if width == 4 else np.uint16
+            as_float = (out.view(np.float32) if dtype == F32 else out.view(np.float16).astype(np.float32) if dtype == F16
+                        else synthetic.bf16_bits_to_f32(out.view(np.uint16)))
+            nan = np.isnan(as_float)
+            assert np.array_equal(out.view(view)[~nan], ref.view(view)[~nan])
 
 
 def test_known_answers_through_the_abi():

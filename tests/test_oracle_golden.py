@@ -8,6 +8,7 @@ Sources (paths inside the reference project):
   test/Compiler/SequenceOpsTest.cpp:371-509      SDPA in-test oracle (f64), tolerance 8e-5*(1+|ref|)
   test/Compiler/SequenceOpsTest.cpp:1945-2009,2149-2158  paged K/V tables, invalid page ids
 """
+import ctypes as C
 import math
 
 import numpy as np
@@ -15,7 +16,7 @@ import pytest
 
 import oracle
 from deepforge_b200 import dfgpu
-from deepforge_b200.dfgpu import BF16, E4M3, E5M2, E8M0, F16, F32, I32, REORDER_F8_128x4, tensor
+from deepforge_b200.dfgpu import BF16, E4M3, E5M2, E8M0, F16, F32, FP4, I4, I32, REORDER_F8_128x4, tensor
 
 INF = float("inf")
 NAN = float("nan")
@@ -115,6 +116,29 @@ def test_e5m2_block_scale_known_answers():
     oracle.block_scale_quantize(tensor(F32, [1, 4]), x, tensor(E5M2, [1, 4]), codes, tensor(E8M0, [1, 2]), scale, 2, 1)
     assert scale.tolist() == [113, 115]
     assert codes.tolist() == [0x74, 0x78, 0xf4, 0x78]
+
+
+def test_packed_four_bit_known_answers():
+    """FP4_E2M1 codes with FP8_E4M3 scales through quantize and dequantize (test/Compiler/SpecializedOpsTest.cpp:736-754: 1, 2, -3, 6 come back
+    as 1.03125, 2.0625, -3, 6) and signed INT4 nibbles with HALF scales into BFLOAT16 (:661-681), two codes per byte, low nibble first."""
+    x = np.array([1.0, 2.0, -3.0, 6.0], dtype=np.float32)
+    codes = np.zeros(2, dtype=np.uint8)
+    scale = np.zeros(2, dtype=np.uint8)
+    oracle.block_scale_quantize(tensor(F32, [1, 4]), x, tensor(FP4, [1, 4]), codes, tensor(E4M3, [1, 2]), scale, 2, 1)
+    y = np.full(4, -99.0, dtype=np.float32)
+    oracle.block_scale_dequantize(tensor(FP4, [1, 4]), codes, tensor(E4M3, [1, 2]), scale, tensor(F32, [1, 4]), y, [2])
+    assert y.tolist() == [1.03125, 2.0625, -3.0, 6.0]
+    nibbles = np.array([0xf8, 0x70], dtype=np.uint8)
+    half_scales = np.array([0x3800, 0x4000], dtype=np.uint16)
+    out = np.full(4, 0xffff, dtype=np.uint16)
+    oracle.block_scale_dequantize(tensor(I4, [1, 4]), nibbles, tensor(F16, [1, 2]), half_scales, tensor(BF16, [1, 4]), out, [2])
+    assert out.tolist() == [0xc080, 0xbf00, 0x0000, 0x4160]
+    lib = oracle.lib()
+    lib.dfo_decode_e2m1.restype = C.c_float
+    assert [lib.dfo_decode_e2m1(code) for code in range(16)] == [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0]
+    encode = lambda v: lib.dfo_encode_e2m1(C.c_float(v))
+    assert [encode(v) for v in (0.0, -0.0, 0.25, 0.75, 1.25, 2.5, 5.0, 6.0, 7.0, -100.0, float("inf"), float("nan"), -0.2)] == \
+        [0x0, 0x8, 0x0, 0x2, 0x2, 0x4, 0x6, 0x7, 0x7, 0xf, 0x7, 0x7, 0x0]
 
 
 def test_bf16_fp8_f16_roundtrip_bits():
