@@ -287,7 +287,8 @@ bool descriptor_span(dfgpu_tensor const& t, std::uint64_t& bytes) {
         if (last > limit || count > limit / extent) return false;
         count *= extent;
     }
-    bytes = (t.reorder == DFGPU_REORDER_F8_128x4 ? count : last + 1) * element_bytes(t.dtype);
+    auto const elements = t.reorder == DFGPU_REORDER_F8_128x4 ? count : last + 1;
+    bytes = t.dtype == DFGPU_FP4 || t.dtype == DFGPU_I4 ? (elements + 1) / 2 : elements * element_bytes(t.dtype);   // (two four-bit codes per byte)
     return true;
 }
 

@@ -91,6 +91,8 @@ std::optional<int> to_dfgpu_dtype(DataType type) {
         case DataType::kFp8E5M2: return DFGPU_E5M2;
         case DataType::kUint8: return DFGPU_U8;
         case DataType::kInt64: return DFGPU_I64;
+        case DataType::kFp4E2M1: return DFGPU_FP4;
+        case DataType::kInt4: return DFGPU_I4;
         default: return std::nullopt;
     }
 }
@@ -114,7 +116,7 @@ struct Lowering {
     Status describe(std::int64_t uid, dfgpu_tensor& out, std::string const& where, bool allow_special = false) const {
         auto const& t = tensor(uid);
         auto dtype = to_dfgpu_dtype(t.data_type);
-        if (dtype && (*dtype == DFGPU_E5M2 || *dtype == DFGPU_U8 || *dtype == DFGPU_I64) && !allow_special) dtype.reset();
+        if (dtype && (*dtype == DFGPU_E5M2 || *dtype == DFGPU_U8 || *dtype == DFGPU_I64 || *dtype == DFGPU_FP4 || *dtype == DFGPU_I4) && !allow_special) dtype.reset();
         if (t.ragged_offset_uid && !allow_special)
             return fail(ErrorCode::kUnsupportedOperation, where, "tensor '" + t.name + "' uses ragged storage, which this backend executes for SDPA page tables only");
         if (!dtype) return fail(ErrorCode::kUnsupportedDataType, where, "tensor '" + t.name + "' has data type " + std::string(import::data_type_name(t.data_type)) + ", which this backend does not execute");
@@ -542,7 +544,8 @@ Status lower_quantize(Lowering& low, std::size_t index) {
     params.axis = axis ? static_cast<std::int32_t>(*axis) : -1;
     if (axis && (*axis < 0 || *axis >= static_cast<std::int64_t>(low.tensor(*x).dim.size()))) return fail(ErrorCode::kInvalidValue, where, "axis is out of range");
     if ((status = low.describe(*x, params.x, where)).is_bad()) return status;
-    if ((status = low.describe(*y, params.y, where, low.tensor(*y).data_type == DataType::kFp8E5M2)).is_bad()) return status;   // (E5M2 codes: the general kernel)
+    // (E5M2 and packed FP4 codes: the general kernel)
+    if ((status = low.describe(*y, params.y, where, low.tensor(*y).data_type == DataType::kFp8E5M2 || low.tensor(*y).data_type == DataType::kFp4E2M1)).is_bad()) return status;
     if ((status = low.describe(*scale, params.scale, where)).is_bad()) return status;
     KernelStep step;
     step.op = KernelOp::kBlockScaleQuantize;
@@ -567,7 +570,8 @@ Status lower_dequantize(Lowering& low, std::size_t index) {
     dfgpu_bsd_params params{};
     params.block_count = static_cast<std::int32_t>(blocks->size());
     for (std::size_t i = 0; i < blocks->size(); ++i) params.block[i] = (*blocks)[i];
-    if ((status = low.describe(*x, params.x, where, low.tensor(*x).data_type == DataType::kFp8E5M2)).is_bad()) return status;
+    auto const code_type = low.tensor(*x).data_type;
+    if ((status = low.describe(*x, params.x, where, code_type == DataType::kFp8E5M2 || code_type == DataType::kFp4E2M1 || code_type == DataType::kInt4)).is_bad()) return status;
     if ((status = low.describe(*scale, params.scale, where)).is_bad()) return status;
     if ((status = low.describe(*y, params.y, where)).is_bad()) return status;
     KernelStep step;
@@ -1012,6 +1016,8 @@ std::uint64_t kernel_alignment(KernelStep const& step, std::size_t slot) {
         case KernelOp::kMatmulFp8: return step.kernel == DFGPU_MATMUL_FP8_UMMA && slot <= 2 ? 16 : 0;
         case KernelOp::kConvFpropPair: return 16;
         case KernelOp::kBlockScaleQuantizePair: return slot % 3 == 0 ? 16 : 8;
+        case KernelOp::kBlockScaleQuantize:   // packed FP4 codes are written a nibble at a time through their aligned word
+            return slot == 1 && std::get<dfgpu_bsq_params>(step.params).y.dtype == DFGPU_FP4 ? 4 : 0;
         default: return 0;
     }
 }

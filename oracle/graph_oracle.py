@@ -17,7 +17,8 @@ from deepforge_b200 import dfgpu, synthetic
 
 FLT_MAX = 3.4028234663852886e38
 _FLOATING = {"FLOAT", "BFLOAT16", "HALF"}
-_CODE = {"FP8_E4M3": dfgpu.E4M3, "FP8_E5M2": dfgpu.E5M2, "FP8_E8M0": dfgpu.E8M0, "INT32": dfgpu.I32, "UINT8": dfgpu.U8, "INT64": dfgpu.I64}
+_CODE = {"FP8_E4M3": dfgpu.E4M3, "FP8_E5M2": dfgpu.E5M2, "FP8_E8M0": dfgpu.E8M0, "INT32": dfgpu.I32, "UINT8": dfgpu.U8, "INT64": dfgpu.I64,
+         "FP4_E2M1": dfgpu.FP4, "INT4": dfgpu.I4}
 _STORAGE = {"FLOAT": dfgpu.F32, "BFLOAT16": dfgpu.BF16, "HALF": dfgpu.F16}
 
 

@@ -331,6 +331,37 @@ def test_c3_quantize_matmul_with_e5m2_codes():
     check_bf16(s.output(9), ref[9])
 
 
+def test_packed_four_bit_graphs_reproduce_the_reference_known_answers():
+    """The reference's two four-bit cases through the Executable (test/Compiler/SpecializedOpsTest.cpp:736-754 and :661-681): FLOAT ->
+    FP4_E2M1 codes with FP8_E4M3 scales (both virtual, in the workspace) -> FLOAT gives 1.03125, 2.0625, -3, 6; INT4 nibbles with HALF
+    scales give the BFLOAT16 bits c080 bf00 0000 4160. And a larger FP4 round trip against the oracle, bit for bit."""
+    from deepforge_b200 import graphs
+
+    def roundtrip(rows, cols, block):
+        t = [graphs.tensor(14, "X", [rows, cols]), graphs.tensor(15, "Q", [rows, cols], "FP4_E2M1", None, True),
+             graphs.tensor(16, "S", [rows, cols // block], "FP8_E4M3", None, True), graphs.tensor(17, "Y", [rows, cols])]
+        return graphs.document("fp4_roundtrip", [graphs.quantize_node("q", 14, 15, 16, block, 1), graphs.dequantize_node("d", 15, 16, 17, [block])], t)
+
+    def session(doc, inputs, outputs):
+        wl = workloads.Workload(name="four_bit", config=0, document=doc, description={}, metric="", unit="GB/s", flops=1.0, bytes=1.0, bound="hbm",
+                                inputs=inputs, outputs=outputs)
+        s = harness.Session(wl)
+        s.run()
+        return wl, s
+
+    wl, s = session(roundtrip(1, 4, 2), {14: lambda: np.array([1.0, 2.0, -3.0, 6.0], np.float32)}, [17])
+    assert s.output(17).tolist() == [1.03125, 2.0625, -3.0, 6.0] and s.exe.workspace_size == 128
+    t = [graphs.tensor(1, "X", [1, 4], "INT4"), graphs.tensor(2, "S", [1, 2], "HALF"), graphs.tensor(3, "Y", [1, 4], "BFLOAT16")]
+    wl, s = session(graphs.document("int4", [graphs.dequantize_node("d", 1, 2, 3, [2])], t),
+                    {1: lambda: np.array([0xf8, 0x70], np.uint8), 2: lambda: np.array([0x3800, 0x4000], np.uint16)}, [3])
+    assert s.raw(3).view(np.uint16).tolist() == [0xc080, 0xbf00, 0x0000, 0x4160]
+    wl, s = session(roundtrip(96, 256, 16), {14: workloads._normal(9, 14, 96 * 256, "FLOAT", 3.0)}, [17])
+    ins, _ = oracle_inputs(wl, s)
+    ref = graph_oracle.run(wl.document, ins)
+    assert np.array_equal(s.output(17).view(np.uint32), ref[17].view(np.uint32))
+    assert dfgpu.device_status() == 0
+
+
 def _quantize_slabs(document, node_index, uid, storage, slabs):
     """The oracle's block-scale quantize over independent slabs of one operand (whole 32-element blocks each), on
     host threads; returns (codes, scales) joined in slab order."""

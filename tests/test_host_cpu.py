@@ -219,7 +219,7 @@ def test_argument_table_is_sorted_with_clamped_alignment():
     (lambda: _with(graphs.c4_sdpa(1, 2, 16, 8), lambda d: d["nodes"][0].update(generate_stats=False)), 8),
     (lambda: _with(graphs.c2_bottleneck(n=1, h=8, w=8), lambda d: d["nodes"][2].update(mode="GELU_FWD")), 20),
     (lambda: _with(graphs.c1_conv(n=1, c=3, h=5, w=5, k=5), lambda d: d["tensors"]["3"].update(dim=[1, 5, 4, 5], stride=[100, 1, 25, 5])), 15),
-    (lambda: _with(graphs.c3_quantize_matmul(128, 128, 128), lambda d: d["tensors"]["3"].update(data_type="FP4_E2M1")), 10),
+    (lambda: _with(graphs.c3_quantize_matmul(128, 128, 128), lambda d: d["tensors"]["3"].update(data_type="INT8")), 10),
     (lambda: _with(graphs.c3_quantize_matmul(128, 128, 128), lambda d: d["nodes"][0].update(block_size=24)), 15),
 ])
 def test_compile_time_rejections(doc_fn, expected):
