@@ -16,6 +16,7 @@ namespace dfgpu {
 // DeepForge Status codes the launchers return.
 constexpr int kOk = 0;
 constexpr int kInvalidArgument = 1;
+constexpr int kInvalidValue = 8;
 constexpr int kInvalidLayout = 14;
 constexpr int kInvalidShape = 15;
 constexpr int kExecutionFailed = 19;

@@ -1,5 +1,10 @@
 // POINTWISE nodes that could not be fused into a contraction's epilogue.
 // One thread per output element, trailing-axis NumPy broadcast, f32 math.
+//
+// Two families of kernels. ADD / MUL / SUB / RELU_FWD / IDENTITY (the modes the contractions' callers use on large
+// tensors) keep kernels of their own, with nothing else in them. Every other mode of the reference's pointwise_result
+// (lib/Compiler/FoundationalGraph.cpp:2581-2955) goes through pointwise_value below: the same expression, one
+// separately rounded f32 operation per step, with CUDA's full-precision math functions (no fast-math intrinsics).
 #include "common.cuh"
 
 namespace dfgpu {
@@ -10,6 +15,131 @@ __device__ __forceinline__ int64_t broadcast_offset(const View& t, int out_rank,
     int64_t offset = 0;
     for (int i = 0; i < t.rank; ++i) offset += (t.dim[i] == 1 ? 0 : index[i + shift]) * t.stride[i];
     return offset;
+}
+
+struct PointwiseScalars {
+    float relu_lower, relu_upper, relu_slope, elu_alpha, softplus_beta, swish_beta;
+    int axis;
+};
+
+__host__ __device__ __forceinline__ int input_count(int mode) {
+    if (mode < 0 || mode >= DFGPU_PW_MODE_COUNT) return 0;
+    if (mode == DFGPU_PW_BINARY_SELECT) return 3;
+    switch (mode) {
+        case DFGPU_PW_ADD: case DFGPU_PW_MUL: case DFGPU_PW_SUB: case DFGPU_PW_DIV: case DFGPU_PW_ADD_SQUARE:
+        case DFGPU_PW_MIN: case DFGPU_PW_MAX: case DFGPU_PW_MOD: case DFGPU_PW_POW:
+        case DFGPU_PW_LOGICAL_AND: case DFGPU_PW_LOGICAL_OR:
+        case DFGPU_PW_CMP_EQ: case DFGPU_PW_CMP_NEQ: case DFGPU_PW_CMP_GT: case DFGPU_PW_CMP_GE: case DFGPU_PW_CMP_LT: case DFGPU_PW_CMP_LE:
+        case DFGPU_PW_RELU_BWD: case DFGPU_PW_TANH_BWD: case DFGPU_PW_SIGMOID_BWD: case DFGPU_PW_ELU_BWD:
+        case DFGPU_PW_SOFTPLUS_BWD: case DFGPU_PW_SWISH_BWD: case DFGPU_PW_GELU_BWD: case DFGPU_PW_GELU_APPROX_TANH_BWD:
+            return 2;
+        default: return 1;
+    }
+}
+
+inline bool simple_mode(int mode) { return mode >= DFGPU_PW_ADD && mode <= DFGPU_PW_SUB; }
+
+// 1 / (1 + exp(-v)) (FoundationalGraph.cpp:2569-2579)
+__device__ __forceinline__ float sigmoid_value(float v) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-v))); }
+
+// x, y, z: IN_0, IN_1, IN_2 (0 where the mode has none). u: the activation's input (IN_1 of a _BWD mode, else IN_0).
+__device__ __forceinline__ float pointwise_value(int mode, float x, float y, float z, const PointwiseScalars& s, int64_t position) {
+    const float u = (mode >= DFGPU_PW_RELU_BWD && input_count(mode) == 2) ? y : x;
+    switch (mode) {
+        case DFGPU_PW_ADD: return __fadd_rn(x, y);
+        case DFGPU_PW_MUL: return __fmul_rn(x, y);
+        case DFGPU_PW_SUB: return __fsub_rn(x, y);
+        case DFGPU_PW_DIV: return __fdiv_rn(x, y);
+        case DFGPU_PW_ADD_SQUARE: return __fadd_rn(x, __fmul_rn(y, y));
+        // equal operands (the two zeros among them): -0 orders below +0, so the minimum ORs the sign bits and the maximum ANDs them
+        case DFGPU_PW_MIN: return x == y ? __uint_as_float(__float_as_uint(x) | __float_as_uint(y)) : minimum_nan(x, y);
+        case DFGPU_PW_MAX: return x == y ? __uint_as_float(__float_as_uint(x) & __float_as_uint(y)) : maximum_nan(x, y);
+        case DFGPU_PW_MOD: return fmodf(x, y);
+        case DFGPU_PW_POW: return powf(x, y);
+        case DFGPU_PW_SQRT: return __fsqrt_rn(x);
+        case DFGPU_PW_RSQRT: return __fdiv_rn(1.0f, __fsqrt_rn(x));
+        case DFGPU_PW_EXP: return expf(x);
+        case DFGPU_PW_LOG: return logf(x);
+        case DFGPU_PW_NEG: return -x;
+        case DFGPU_PW_ABS: return fabsf(x);
+        case DFGPU_PW_CEIL: return ceilf(x);
+        case DFGPU_PW_FLOOR: return floorf(x);
+        case DFGPU_PW_COS: return cosf(x);
+        case DFGPU_PW_SIN: return sinf(x);
+        case DFGPU_PW_TAN: return tanf(x);
+        case DFGPU_PW_ERF: return erff(x);
+        case DFGPU_PW_RECIPROCAL: return __fdiv_rn(1.0f, x);
+        case DFGPU_PW_IDENTITY: return x;
+        case DFGPU_PW_GEN_INDEX: return __ull2float_rn(static_cast<unsigned long long>(position));
+        case DFGPU_PW_LOGICAL_NOT: return x == 0.0f ? 1.0f : 0.0f;
+        case DFGPU_PW_LOGICAL_AND: return (x != 0.0f) && (y != 0.0f) ? 1.0f : 0.0f;
+        case DFGPU_PW_LOGICAL_OR: return (x != 0.0f) || (y != 0.0f) ? 1.0f : 0.0f;
+        case DFGPU_PW_BINARY_SELECT: return z != 0.0f ? y : x;
+        case DFGPU_PW_CMP_EQ: return x == y ? 1.0f : 0.0f;
+        case DFGPU_PW_CMP_NEQ: return x != y ? 1.0f : 0.0f;
+        case DFGPU_PW_CMP_GT: return x > y ? 1.0f : 0.0f;
+        case DFGPU_PW_CMP_GE: return x >= y ? 1.0f : 0.0f;
+        case DFGPU_PW_CMP_LT: return x < y ? 1.0f : 0.0f;
+        case DFGPU_PW_CMP_LE: return x <= y ? 1.0f : 0.0f;
+        case DFGPU_PW_RELU_FWD: return relu_forward(x, s.relu_lower, s.relu_upper, s.relu_slope);
+        case DFGPU_PW_RELU_BWD: return __fmul_rn(x, y < s.relu_lower ? s.relu_slope : (y > s.relu_upper ? 0.0f : 1.0f));
+        case DFGPU_PW_TANH_FWD: return tanhf(u);
+        case DFGPU_PW_TANH_BWD: { float t = tanhf(u); return __fmul_rn(x, __fsub_rn(1.0f, __fmul_rn(t, t))); }
+        case DFGPU_PW_SIGMOID_FWD: return sigmoid_value(u);
+        case DFGPU_PW_SIGMOID_BWD: { float v = sigmoid_value(u); return __fmul_rn(x, __fmul_rn(v, __fsub_rn(1.0f, v))); }
+        case DFGPU_PW_ELU_FWD: { float e = expf(u); return u >= 0.0f ? u : __fmul_rn(s.elu_alpha, __fsub_rn(e, 1.0f)); }
+        case DFGPU_PW_ELU_BWD: { float e = expf(u); return __fmul_rn(x, u >= 0.0f ? 1.0f : __fmul_rn(s.elu_alpha, e)); }
+        case DFGPU_PW_SOFTPLUS_FWD: {
+            float scaled = __fmul_rn(s.softplus_beta, u);
+            float logarithm = logf(__fadd_rn(1.0f, expf(-fabsf(scaled))));
+            return __fdiv_rn(__fadd_rn(maximum_nan(scaled, 0.0f), logarithm), s.softplus_beta);
+        }
+        case DFGPU_PW_SOFTPLUS_BWD: return __fmul_rn(x, sigmoid_value(__fmul_rn(s.softplus_beta, u)));
+        case DFGPU_PW_SWISH_FWD: return __fmul_rn(u, sigmoid_value(__fmul_rn(s.swish_beta, u)));
+        case DFGPU_PW_SWISH_BWD: {
+            float scaled = __fmul_rn(s.swish_beta, u);
+            float v = sigmoid_value(scaled);
+            return __fmul_rn(x, __fadd_rn(v, __fmul_rn(scaled, __fmul_rn(v, __fsub_rn(1.0f, v)))));
+        }
+        case DFGPU_PW_GELU_FWD: case DFGPU_PW_GELU_BWD: {
+            float cdf = __fmul_rn(0.5f, __fadd_rn(1.0f, erff(__fmul_rn(u, 0.7071067811865475f))));
+            if (mode == DFGPU_PW_GELU_FWD) return __fmul_rn(u, cdf);
+            float density = __fmul_rn(0.3989422804014327f, expf(__fmul_rn(-0.5f, __fmul_rn(u, u))));
+            return __fmul_rn(x, __fadd_rn(cdf, __fmul_rn(u, density)));
+        }
+        case DFGPU_PW_GELU_APPROX_TANH_FWD: case DFGPU_PW_GELU_APPROX_TANH_BWD: {
+            float square = __fmul_rn(u, u);
+            float cubic = __fmul_rn(square, u);
+            float inner = __fmul_rn(0.7978845608028654f, __fadd_rn(u, __fmul_rn(0.044715f, cubic)));
+            float t = tanhf(inner);
+            float cdf = __fmul_rn(0.5f, __fadd_rn(1.0f, t));
+            if (mode == DFGPU_PW_GELU_APPROX_TANH_FWD) return __fmul_rn(u, cdf);
+            float inner_derivative = __fmul_rn(0.7978845608028654f, __fadd_rn(1.0f, __fmul_rn(0.134145f, square)));
+            float tanh_derivative = __fsub_rn(1.0f, __fmul_rn(t, t));
+            return __fmul_rn(x, __fadd_rn(cdf, __fmul_rn(0.5f, __fmul_rn(u, __fmul_rn(tanh_derivative, inner_derivative)))));
+        }
+        default: return x;
+    }
+}
+
+// Any mode, any strides and storage types: one thread per output element.
+__global__ void pointwise_general_kernel(const void* a, const void* b, const void* c, void* out, View av, View bv, View cv, View ov,
+                                         int mode, PointwiseScalars s, int64_t total) {
+    int64_t flat = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (flat >= total) return;
+    int64_t index[DFGPU_MAX_RANK];
+    int64_t out_offset = 0;
+    for (int i = ov.rank - 1; i >= 0; --i) {
+        index[i] = flat % ov.dim[i];
+        flat /= ov.dim[i];
+        out_offset += index[i] * ov.stride[i];
+    }
+    const int inputs = input_count(mode);
+    float x = load_as_f32(a, av.dtype, broadcast_offset(av, ov.rank, index));
+    float y = inputs >= 2 ? load_as_f32(b, bv.dtype, broadcast_offset(bv, ov.rank, index)) : 0.0f;
+    float z = inputs >= 3 ? load_as_f32(c, cv.dtype, broadcast_offset(cv, ov.rank, index)) : 0.0f;
+    int64_t position = mode == DFGPU_PW_GEN_INDEX ? index[s.axis] : 0;
+    store_from_f32(out, ov.dtype, out_offset, pointwise_value(mode, x, y, z, s, position));
 }
 
 __global__ void pointwise_kernel(const void* a, const void* b, void* out, View av, View bv, View ov, int mode,
@@ -86,6 +216,19 @@ __global__ void pointwise_packed_kernel(const void* a, const void* b, void* out,
     store4<TO>(out, i, r);
 }
 
+// The same for the general modes with one or two inputs (not GEN_INDEX, which needs the element's index).
+template <typename T>
+__global__ void pointwise_general_packed_kernel(const void* a, const void* b, void* out, int mode, PointwiseScalars s, int64_t total) {
+    int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+    if (i >= total) return;
+    float x[4], y[4] = {0.f, 0.f, 0.f, 0.f}, r[4];
+    load4<T>(a, i, x);
+    if (input_count(mode) == 2) load4<T>(b, i, y);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) r[j] = pointwise_value(mode, x[j], y[j], 0.0f, s, 0);
+    store4<T>(out, i, r);
+}
+
 bool same_packed(const dfgpu_tensor& a, const dfgpu_tensor& b) {
     if (a.rank != b.rank) return false;
     for (int i = 0; i < a.rank; ++i)
@@ -93,14 +236,14 @@ bool same_packed(const dfgpu_tensor& a, const dfgpu_tensor& b) {
     return is_packed_row_major(a) && is_packed_row_major(b);
 }
 
-int validate(const dfgpu_pointwise_params& p, bool& binary) {
-    binary = p.mode == DFGPU_PW_ADD || p.mode == DFGPU_PW_MUL || p.mode == DFGPU_PW_SUB;
-    if (p.mode < DFGPU_PW_ADD || p.mode > DFGPU_PW_SUB) return fail(kUnsupported, "POINTWISE: mode %d is not executable on this backend", p.mode);
-    if (!valid_tensor(p.in0) || !valid_tensor(p.out) || (binary && !valid_tensor(p.in1)))
+int validate(const dfgpu_pointwise_params& p, int& inputs) {
+    inputs = input_count(p.mode);
+    if (inputs == 0) return fail(kUnsupported, "POINTWISE: mode %d is not executable on this backend", p.mode);
+    if (!valid_tensor(p.in0) || !valid_tensor(p.out) || (inputs >= 2 && !valid_tensor(p.in1)) || (inputs >= 3 && !valid_tensor(p.in2)))
         return fail(kInvalidShape, "POINTWISE: tensor rank or extent out of range");
-    const dfgpu_tensor* inputs[2] = {&p.in0, &p.in1};
-    for (int n = 0; n < (binary ? 2 : 1); ++n) {
-        const dfgpu_tensor& t = *inputs[n];
+    const dfgpu_tensor* operands[3] = {&p.in0, &p.in1, &p.in2};
+    for (int n = 0; n < inputs; ++n) {
+        const dfgpu_tensor& t = *operands[n];
         if (t.rank > p.out.rank) return fail(kInvalidShape, "POINTWISE: input rank exceeds output rank");
         int shift = p.out.rank - t.rank;
         for (int i = 0; i < t.rank; ++i)
@@ -111,6 +254,12 @@ int validate(const dfgpu_pointwise_params& p, bool& binary) {
     }
     if (p.out.dtype != DFGPU_F32 && p.out.dtype != DFGPU_BF16 && p.out.dtype != DFGPU_F16)
         return fail(kUnsupported, "POINTWISE: unsupported output type");
+    if (p.mode == DFGPU_PW_GEN_INDEX && (p.axis < 0 || p.axis >= p.out.rank))
+        return fail(kInvalidValue, "POINTWISE: GEN_INDEX needs an axis inside the output's rank");
+    if ((p.mode == DFGPU_PW_SOFTPLUS_FWD || p.mode == DFGPU_PW_SOFTPLUS_BWD) && !(p.softplus_beta > 0.0f))
+        return fail(kInvalidValue, "POINTWISE: softplus beta must be positive");
+    if ((p.mode == DFGPU_PW_RELU_FWD || p.mode == DFGPU_PW_RELU_BWD) && p.relu_lower > p.relu_upper)
+        return fail(kInvalidValue, "POINTWISE: ReLU lower clip exceeds upper clip");
     return kOk;
 }
 
@@ -119,10 +268,12 @@ int validate(const dfgpu_pointwise_params& p, bool& binary) {
 
 using namespace dfgpu;
 
+extern "C" int dfgpu_pointwise_input_count(int32_t mode) { return input_count(mode); }
+
 extern "C" int dfgpu_query_pointwise(const dfgpu_pointwise_params* p, dfgpu_plan_info* info) {
     if (!p || !info) return fail(kInvalidArgument, "POINTWISE: null params");
-    bool binary;
-    int status = validate(*p, binary);
+    int inputs;
+    int status = validate(*p, inputs);
     if (status) return status;
     info->kernel = 1;
     info->launches = 1;
@@ -133,10 +284,12 @@ extern "C" int dfgpu_query_pointwise(const dfgpu_pointwise_params* p, dfgpu_plan
 extern "C" int dfgpu_pointwise(const dfgpu_pointwise_params* p, void* const* tensors, void* scratch, void* stream_handle) {
     (void)scratch;
     if (!p || !tensors) return fail(kInvalidArgument, "POINTWISE: null params");
-    bool binary;
-    int status = validate(*p, binary);
+    int inputs;
+    int status = validate(*p, inputs);
     if (status) return status;
-    if (!tensors[0] || !tensors[2] || (binary && !tensors[1])) return fail(kInvalidArgument, "POINTWISE: null tensor pointer");
+    const bool binary = inputs == 2;
+    if (!tensors[0] || !tensors[2] || (inputs >= 2 && !tensors[1]) || (inputs >= 3 && !tensors[3]))
+        return fail(kInvalidArgument, "POINTWISE: null tensor pointer");
     cudaStream_t stream = as_stream(stream_handle);
     int64_t total = element_count(p->out);
     auto aligned16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
@@ -144,6 +297,21 @@ extern "C" int dfgpu_pointwise(const dfgpu_pointwise_params* p, void* const* ten
                   aligned16(tensors[0]) && aligned16(tensors[2]) && (!binary || aligned16(tensors[1]));
     bool f32_all = p->in0.dtype == DFGPU_F32 && p->out.dtype == DFGPU_F32 && (!binary || p->in1.dtype == DFGPU_F32);
     bool bf16_all = p->in0.dtype == DFGPU_BF16 && p->out.dtype == DFGPU_BF16 && (!binary || p->in1.dtype == DFGPU_BF16);
+    if (!simple_mode(p->mode)) {
+        PointwiseScalars s{p->relu_lower, p->relu_upper, p->relu_slope, p->elu_alpha, p->softplus_beta, p->swish_beta, p->axis};
+        if (packed && (f32_all || bf16_all) && inputs <= 2 && p->mode != DFGPU_PW_GEN_INDEX) {
+            unsigned grid = static_cast<unsigned>((total / 4 + 255) / 256);
+            if (f32_all) pointwise_general_packed_kernel<float><<<grid, 256, 0, stream>>>(tensors[0], tensors[1], tensors[2], p->mode, s, total);
+            else pointwise_general_packed_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(tensors[0], tensors[1], tensors[2], p->mode, s, total);
+        } else {
+            unsigned grid = static_cast<unsigned>((total + 255) / 256);
+            pointwise_general_kernel<<<grid, 256, 0, stream>>>(tensors[0], tensors[1], inputs >= 3 ? tensors[3] : nullptr, tensors[2],
+                                                               make_view(p->in0), inputs >= 2 ? make_view(p->in1) : make_view(p->in0),
+                                                               inputs >= 3 ? make_view(p->in2) : make_view(p->in0), make_view(p->out),
+                                                               p->mode, s, total);
+        }
+        return check_launch("POINTWISE");
+    }
     if (packed && (f32_all || bf16_all)) {
         unsigned grid = static_cast<unsigned>((total / 4 + 255) / 256);
         if (f32_all)

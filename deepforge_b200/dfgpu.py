@@ -19,6 +19,23 @@ DTYPE_BYTES = {F32: 4, F16: 2, BF16: 2, E4M3: 1, E8M0: 1, I32: 4, E5M2: 1, U8: 1
 
 EPI_ADD, EPI_RELU = 1, 2
 PW_ADD, PW_RELU_FWD, PW_IDENTITY, PW_MUL, PW_SUB = range(5)
+# Every POINTWISE mode by the reference's name (lib/Import/Schema.cpp:301-316), numbered as DFGPU_PW_* in dfgpu.h.
+PW_MODE_NAMES = (
+    "ADD", "RELU_FWD", "IDENTITY", "MUL", "SUB", "DIV", "ADD_SQUARE", "MIN", "MAX", "MOD", "POW", "SQRT", "RSQRT", "EXP",
+    "LOG", "NEG", "ABS", "CEIL", "FLOOR", "COS", "SIN", "TAN", "ERF", "RECIPROCAL", "GEN_INDEX", "LOGICAL_NOT",
+    "LOGICAL_AND", "LOGICAL_OR", "BINARY_SELECT", "CMP_EQ", "CMP_NEQ", "CMP_GT", "CMP_GE", "CMP_LT", "CMP_LE", "RELU_BWD",
+    "TANH_FWD", "TANH_BWD", "SIGMOID_FWD", "SIGMOID_BWD", "ELU_FWD", "ELU_BWD", "SOFTPLUS_FWD", "SOFTPLUS_BWD",
+    "SWISH_FWD", "SWISH_BWD", "GELU_FWD", "GELU_BWD", "GELU_APPROX_TANH_FWD", "GELU_APPROX_TANH_BWD")
+PW_MODES = {name: code for code, name in enumerate(PW_MODE_NAMES)}
+_PW_BINARY = {"ADD", "MUL", "SUB", "DIV", "ADD_SQUARE", "MIN", "MAX", "MOD", "POW", "LOGICAL_AND", "LOGICAL_OR", "CMP_EQ",
+              "CMP_NEQ", "CMP_GT", "CMP_GE", "CMP_LT", "CMP_LE"}
+
+
+def pointwise_input_count(name: str) -> int:
+    """Inputs the mode reads (lib/Import/Schema.cpp:353-377)."""
+    if name == "BINARY_SELECT":
+        return 3
+    return 2 if name in _PW_BINARY or name.endswith("_BWD") else 1
 BSQ_AUTO, BSQ_GENERIC, BSQ_ROW32, BSQ_COL32 = range(4)
 BSD_AUTO, BSD_GENERIC, BSD_PACKED = range(3)
 CONV_AUTO, CONV_DIRECT, CONV_IGEMM_FFMA, CONV_UMMA_BF16, CONV_UMMA_F32X3, CONV_UMMA_F32X3_CLUSTER = range(6)
@@ -76,7 +93,14 @@ class BsdParams(C.Structure):
 
 class PointwiseParams(C.Structure):
     _fields_ = [("in0", Tensor), ("in1", Tensor), ("out", Tensor), ("mode", C.c_int32), ("relu_lower", C.c_float),
-                ("relu_upper", C.c_float), ("relu_slope", C.c_float)]
+                ("relu_upper", C.c_float), ("relu_slope", C.c_float), ("in2", Tensor), ("elu_alpha", C.c_float),
+                ("softplus_beta", C.c_float), ("swish_beta", C.c_float), ("axis", C.c_int32)]
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        for name in ("elu_alpha", "softplus_beta", "swish_beta"):
+            if name not in kwargs:
+                setattr(self, name, 1.0)
 
 
 class ConvParams(C.Structure):
@@ -119,7 +143,7 @@ EXPORTS = [
     "dfgpu_query_block_scale_quantize", "dfgpu_block_scale_quantize",
     "dfgpu_query_block_scale_quantize_pair", "dfgpu_block_scale_quantize_pair",
     "dfgpu_query_block_scale_dequantize", "dfgpu_block_scale_dequantize",
-    "dfgpu_query_pointwise", "dfgpu_pointwise",
+    "dfgpu_query_pointwise", "dfgpu_pointwise", "dfgpu_pointwise_input_count",
     "dfgpu_query_conv_fprop", "dfgpu_conv_fprop",
     "dfgpu_query_conv_fprop_pair", "dfgpu_conv_fprop_pair",
     "dfgpu_query_matmul", "dfgpu_matmul",
@@ -194,8 +218,8 @@ def block_scale_dequantize(params, x, scale, y, scratch=None, stream=None):
     _call("dfgpu_block_scale_dequantize", params, [x, scale, y], scratch, stream)
 
 
-def pointwise(params, in0, in1, out, scratch=None, stream=None):
-    _call("dfgpu_pointwise", params, [in0, in1, out], scratch, stream)
+def pointwise(params, in0, in1, out, scratch=None, stream=None, in2=0):
+    _call("dfgpu_pointwise", params, [in0, in1, out, in2], scratch, stream)
 
 
 def conv_fprop(params, x, w, y, extra0=None, extra1=None, scratch=None, stream=None):

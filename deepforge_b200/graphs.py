@@ -43,13 +43,42 @@ def conv_node(name: str, x: int, w: int, y: int, pad=(1, 1), post_pad=None, stri
             "dilation": list(dilation), "math_mode": mode}
 
 
-def pointwise_node(name: str, mode: str, in0: int, out: int, in1: Optional[int] = None, lower=None, upper=None, slope=None) -> dict:
+def pointwise_node(name: str, mode: str, in0: int, out: int, in1: Optional[int] = None, lower=None, upper=None, slope=None,
+                   in2: Optional[int] = None, axis=None, swish_beta=None, elu_alpha=None, softplus_beta=None) -> dict:
     inputs = {"IN_0": in0}
     if in1 is not None:
         inputs["IN_1"] = in1
+    if in2 is not None:
+        inputs["IN_2"] = in2
     return {"tag": "POINTWISE", "name": name, "compute_data_type": "FLOAT", "inputs": inputs, "outputs": {"OUT_0": out}, "mode": mode,
-            "axis": None, "relu_lower_clip": lower, "relu_upper_clip": upper, "relu_lower_clip_slope": slope, "swish_beta": None,
-            "elu_alpha": None, "softplus_beta": None}
+            "axis": axis, "relu_lower_clip": lower, "relu_upper_clip": upper, "relu_lower_clip_slope": slope, "swish_beta": swish_beta,
+            "elu_alpha": elu_alpha, "softplus_beta": softplus_beta}
+
+
+def pointwise_all_modes(dims: Sequence[int] = (2, 3), data_type: str = "FLOAT") -> dict:
+    """One POINTWISE node per mode of the schema, in the shape of the reference's own test graph
+    (test/Compiler/FoundationalMathOpsTest.cpp:126-167): UID 101 A [rows, columns], 102 B [columns] (broadcast over rows),
+    103 T [rows, 1] (the selector of BINARY_SELECT), outputs 1000 + the mode's position in the schema's list; axis 1,
+    ReLU clips 0.25 / 1.0 with slope 0.2, swish beta 0.5, ELU alpha 2, softplus beta 2 on every node."""
+    from .dfgpu import pointwise_input_count
+    rows, columns = dims
+    tensors = [tensor(101, "A", [rows, columns], data_type), tensor(102, "B", [columns], data_type), tensor(103, "T", [rows, 1], data_type)]
+    nodes = []
+    for position, mode in enumerate(SCHEMA_POINTWISE_MODES):
+        count = pointwise_input_count(mode)
+        nodes.append(pointwise_node("pointwise_" + mode, mode, 101, 1000 + position, 102 if count >= 2 else None, 0.25, 1.0, 0.2,
+                                    103 if count >= 3 else None, 1, 0.5, 2.0, 2.0))
+        tensors.append(tensor(1000 + position, "O_" + mode, [rows, columns], data_type))
+    return document("pointwise_all_modes", nodes, tensors, io=data_type, graph_uid=2101)
+
+
+# lib/Import/Schema.cpp:301-316, in the schema's order
+SCHEMA_POINTWISE_MODES = (
+    "ADD", "MUL", "SQRT", "MAX", "MIN", "RELU_FWD", "TANH_FWD", "SIGMOID_FWD", "ELU_FWD", "GELU_FWD", "SOFTPLUS_FWD", "SWISH_FWD",
+    "RELU_BWD", "TANH_BWD", "SIGMOID_BWD", "ELU_BWD", "GELU_BWD", "SOFTPLUS_BWD", "SWISH_BWD", "ERF", "IDENTITY",
+    "GELU_APPROX_TANH_BWD", "GELU_APPROX_TANH_FWD", "GEN_INDEX", "BINARY_SELECT", "EXP", "LOG", "NEG", "MOD", "POW", "ABS", "CEIL",
+    "COS", "FLOOR", "RSQRT", "SIN", "LOGICAL_NOT", "TAN", "SUB", "ADD_SQUARE", "DIV", "CMP_EQ", "CMP_NEQ", "CMP_GT", "CMP_GE",
+    "CMP_LT", "CMP_LE", "LOGICAL_AND", "LOGICAL_OR", "RECIPROCAL")
 
 
 def matmul_node(name: str, a: int, b: int, c: int) -> dict:

@@ -184,7 +184,7 @@ bool params_in_range(KernelParams const& params) {
         using T = std::decay_t<decltype(p)>;
         if constexpr (std::is_same_v<T, dfgpu_bsq_params>) return tensor_in_range(p.x) && tensor_in_range(p.y) && tensor_in_range(p.scale);
         else if constexpr (std::is_same_v<T, dfgpu_bsd_params>) return tensor_in_range(p.x) && tensor_in_range(p.y) && tensor_in_range(p.scale);
-        else if constexpr (std::is_same_v<T, dfgpu_pointwise_params>) return tensor_in_range(p.in0) && tensor_in_range(p.in1) && tensor_in_range(p.out);
+        else if constexpr (std::is_same_v<T, dfgpu_pointwise_params>) return tensor_in_range(p.in0) && tensor_in_range(p.in1) && tensor_in_range(p.out) && tensor_in_range(p.in2);
         else if constexpr (std::is_same_v<T, dfgpu_conv_params>)
             return tensor_in_range(p.x) && tensor_in_range(p.w) && tensor_in_range(p.y) && tensor_in_range(p.extra[0]) && tensor_in_range(p.extra[1]) &&
                    p.epilogue_count >= 0 && p.epilogue_count <= DFGPU_MAX_EPILOGUE;
@@ -299,7 +299,7 @@ dfgpu_tensor const* slot_descriptor(KernelStep const& step, std::size_t slot) {
         using T = std::decay_t<decltype(p)>;
         if constexpr (std::is_same_v<T, dfgpu_bsq_params>) { dfgpu_tensor const* t[] = {&p.x, &p.y, &p.scale}; return slot < 3 ? t[slot] : nullptr; }
         else if constexpr (std::is_same_v<T, dfgpu_bsd_params>) { dfgpu_tensor const* t[] = {&p.x, &p.scale, &p.y}; return slot < 3 ? t[slot] : nullptr; }
-        else if constexpr (std::is_same_v<T, dfgpu_pointwise_params>) { dfgpu_tensor const* t[] = {&p.in0, &p.in1, &p.out}; return slot < 3 ? t[slot] : nullptr; }
+        else if constexpr (std::is_same_v<T, dfgpu_pointwise_params>) { dfgpu_tensor const* t[] = {&p.in0, &p.in1, &p.out, &p.in2}; return slot < 4 ? t[slot] : nullptr; }
         else if constexpr (std::is_same_v<T, dfgpu_conv_params>) { dfgpu_tensor const* t[] = {&p.x, &p.w, &p.y, &p.extra[0], &p.extra[1]}; return slot < 5 ? t[slot] : nullptr; }
         else if constexpr (std::is_same_v<T, dfgpu_matmul_params>) { dfgpu_tensor const* t[] = {&p.a, &p.b, &p.c, &p.a_scale, &p.b_scale, &p.extra[0], &p.extra[1]}; return slot < 7 ? t[slot] : nullptr; }
         else if constexpr (std::is_same_v<T, dfgpu_bsq_pair_params>) {

@@ -164,21 +164,40 @@ Status require_float_compute(OperationDesc const& node, std::string const& where
     return Status::ok();
 }
 
-// POINTWISE node -> (mode, relu parameters)
-Status pointwise_mode(OperationDesc const& node, std::string const& where, int& mode, float& lower, float& upper, float& slope) {
+// The reference's mode names (lib/Import/Schema.cpp:301-316) in the order of DFGPU_PW_*.
+constexpr std::array<std::string_view, DFGPU_PW_MODE_COUNT> kPointwiseModeNames{{
+    "ADD", "RELU_FWD", "IDENTITY", "MUL", "SUB", "DIV", "ADD_SQUARE", "MIN", "MAX", "MOD", "POW", "SQRT", "RSQRT", "EXP",
+    "LOG", "NEG", "ABS", "CEIL", "FLOOR", "COS", "SIN", "TAN", "ERF", "RECIPROCAL", "GEN_INDEX", "LOGICAL_NOT",
+    "LOGICAL_AND", "LOGICAL_OR", "BINARY_SELECT", "CMP_EQ", "CMP_NEQ", "CMP_GT", "CMP_GE", "CMP_LT", "CMP_LE", "RELU_BWD",
+    "TANH_FWD", "TANH_BWD", "SIGMOID_FWD", "SIGMOID_BWD", "ELU_FWD", "ELU_BWD", "SOFTPLUS_FWD", "SOFTPLUS_BWD",
+    "SWISH_FWD", "SWISH_BWD", "GELU_FWD", "GELU_BWD", "GELU_APPROX_TANH_FWD", "GELU_APPROX_TANH_BWD"}};
+
+// POINTWISE node -> mode and scalar attributes (validate_pointwise, lib/Compiler/FoundationalGraph.cpp:721-775: every
+// numeric attribute null or a finite f32, lower clip <= upper clip, softplus beta > 0, GEN_INDEX with an axis).
+Status pointwise_mode(OperationDesc const& node, std::string const& where, dfgpu_pointwise_params& params) {
     auto name = get_string(node, "mode");
     if (!name) return fail(ErrorCode::kInvalidValue, where, "mode must be a string");
-    if (*name == "ADD") mode = DFGPU_PW_ADD;
-    else if (*name == "MUL") mode = DFGPU_PW_MUL;
-    else if (*name == "SUB") mode = DFGPU_PW_SUB;
-    else if (*name == "RELU_FWD") mode = DFGPU_PW_RELU_FWD;
-    else if (*name == "IDENTITY") mode = DFGPU_PW_IDENTITY;
-    else return fail(ErrorCode::kUnsupportedOperation, where, "pointwise mode " + *name + " is outside the GPU hot path");
-    lower = static_cast<float>(get_number(node, "relu_lower_clip").value_or(0.0));
-    upper = static_cast<float>(get_number(node, "relu_upper_clip").value_or(static_cast<double>(FLT_MAX)));
-    slope = static_cast<float>(get_number(node, "relu_lower_clip_slope").value_or(0.0));
-    for (auto key : {"swish_beta", "elu_alpha", "softplus_beta"})
-        if (!is_null(node, key)) return fail(ErrorCode::kUnsupportedOperation, where, std::string(key) + " is not used by any executable mode");
+    auto found = std::find(kPointwiseModeNames.begin(), kPointwiseModeNames.end(), std::string_view(*name));
+    if (found == kPointwiseModeNames.end()) return fail(ErrorCode::kInvalidValue, where, "pointwise mode " + *name + " is not a mode of the schema");
+    params.mode = static_cast<std::int32_t>(found - kPointwiseModeNames.begin());
+    struct Attribute { char const* key; float* target; double fallback; };
+    Attribute const attributes[] = {{"relu_lower_clip", &params.relu_lower, 0.0}, {"relu_upper_clip", &params.relu_upper, static_cast<double>(FLT_MAX)},
+                                    {"relu_lower_clip_slope", &params.relu_slope, 0.0}, {"elu_alpha", &params.elu_alpha, 1.0},
+                                    {"softplus_beta", &params.softplus_beta, 1.0}, {"swish_beta", &params.swish_beta, 1.0}};
+    for (auto const& attribute : attributes) {
+        auto value = get_number(node, attribute.key);
+        if (!value && !is_null(node, attribute.key)) return fail(ErrorCode::kInvalidValue, where, std::string(attribute.key) + " must be a number or null");
+        if (value && (!std::isfinite(*value) || std::fabs(*value) > static_cast<double>(FLT_MAX)))
+            return fail(ErrorCode::kInvalidValue, where, std::string(attribute.key) + " must fit a finite f32");
+        *attribute.target = static_cast<float>(value.value_or(attribute.fallback));
+    }
+    if (get_number(node, "relu_lower_clip") && get_number(node, "relu_upper_clip") && *get_number(node, "relu_lower_clip") > *get_number(node, "relu_upper_clip"))
+        return fail(ErrorCode::kInvalidValue, where, "ReLU lower clip exceeds upper clip");
+    if (auto beta = get_number(node, "softplus_beta"); beta && *beta <= 0.0) return fail(ErrorCode::kInvalidValue, where, "softplus beta must be positive");
+    auto axis = get_int(node, "axis");
+    if (!axis && !is_null(node, "axis")) return fail(ErrorCode::kInvalidValue, where, "axis must be an integer or null");
+    params.axis = static_cast<std::int32_t>(axis.value_or(0));
+    if (params.mode == DFGPU_PW_GEN_INDEX && !axis) return fail(ErrorCode::kInvalidValue, where, "GEN_INDEX requires an axis in the output rank");
     return Status::ok();
 }
 
@@ -204,9 +223,10 @@ Status absorb_epilogue(Lowering& low, std::size_t anchor, std::int64_t value, df
         if (!current.is_virtual || !low.single_consumer(final_uid, next) || count >= DFGPU_MAX_EPILOGUE) break;
         auto const& node = low.graph.nodes[next];
         if (node.tag != OperationTag::kPointwise || low.absorbed_into[next] >= 0) break;
-        int mode = 0;
-        float lower = 0, upper = 0, slope = 0;
-        if (pointwise_mode(node, "", mode, lower, upper, slope).is_bad()) break;
+        dfgpu_pointwise_params described_mode{};
+        if (pointwise_mode(node, "", described_mode).is_bad()) break;
+        int const mode = described_mode.mode;
+        float const lower = described_mode.relu_lower, upper = described_mode.relu_upper, slope = described_mode.relu_slope;
         auto in0 = port(node.inputs, "IN_0"), in1 = port(node.inputs, "IN_1"), out = port(node.outputs, "OUT_0");
         if (!in0 || !out || port(node.inputs, "IN_2")) break;
         auto const& out_tensor = low.tensor(*out);
@@ -510,19 +530,23 @@ Status lower_pointwise(Lowering& low, std::size_t index) {
     auto status = require_float_compute(node, where);
     if (status.is_bad()) return status;
     dfgpu_pointwise_params params{};
-    if ((status = pointwise_mode(node, where, params.mode, params.relu_lower, params.relu_upper, params.relu_slope)).is_bad()) return status;
-    auto in0 = port(node.inputs, "IN_0"), in1 = port(node.inputs, "IN_1"), out = port(node.outputs, "OUT_0");
-    bool binary = params.mode == DFGPU_PW_ADD || params.mode == DFGPU_PW_MUL || params.mode == DFGPU_PW_SUB;
-    if (!in0 || !out || binary != in1.has_value() || port(node.inputs, "IN_2"))
+    if ((status = pointwise_mode(node, where, params)).is_bad()) return status;
+    auto in0 = port(node.inputs, "IN_0"), in1 = port(node.inputs, "IN_1"), in2 = port(node.inputs, "IN_2"), out = port(node.outputs, "OUT_0");
+    int const inputs = dfgpu_pointwise_input_count(params.mode);
+    if (!in0 || !out || (inputs >= 2) != in1.has_value() || (inputs >= 3) != in2.has_value() || static_cast<int>(node.inputs.size()) != inputs)
         return fail(ErrorCode::kInvalidValue, where, "pointwise input count does not match the mode");
     if ((status = low.describe(*in0, params.in0, where)).is_bad()) return status;
-    if (binary && (status = low.describe(*in1, params.in1, where)).is_bad()) return status;
+    if (in1 && (status = low.describe(*in1, params.in1, where)).is_bad()) return status;
+    if (in2 && (status = low.describe(*in2, params.in2, where)).is_bad()) return status;
     if ((status = low.describe(*out, params.out, where)).is_bad()) return status;
+    if (params.mode == DFGPU_PW_GEN_INDEX && (params.axis < 0 || params.axis >= params.out.rank))
+        return fail(ErrorCode::kInvalidValue, where, "GEN_INDEX requires an axis in the output rank");
     KernelStep step;
     step.op = KernelOp::kPointwise;
     step.label = node.name;
     step.nodes = {index};
-    step.tensors = {low.bind(*in0), binary ? low.bind(*in1) : TensorBinding{}, low.bind(*out)};
+    step.tensors = {low.bind(*in0), in1 ? low.bind(*in1) : TensorBinding{}, low.bind(*out)};
+    if (in2) step.tensors.push_back(low.bind(*in2));
     step.params = params;
     low.plan.steps.push_back(std::move(step));
     return Status::ok();

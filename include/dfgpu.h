@@ -138,14 +138,39 @@ int dfgpu_query_block_scale_dequantize(const dfgpu_bsd_params*, dfgpu_plan_info*
 int dfgpu_block_scale_dequantize(const dfgpu_bsd_params*, void* const* tensors, void* scratch, void* stream);
 
 /* ---- POINTWISE --------------------------------------------------------------
-   Replaces emit_pointwise (lib/Compiler/FoundationalGraph.cpp:2957-3004) for
-   the modes the path uses. tensors: {IN_0, IN_1 or null, OUT_0}. */
-enum { DFGPU_PW_ADD = 0, DFGPU_PW_RELU_FWD = 1, DFGPU_PW_IDENTITY = 2, DFGPU_PW_MUL = 3, DFGPU_PW_SUB = 4 };
+   Replaces emit_pointwise (lib/Compiler/FoundationalGraph.cpp:2957-3004) with
+   every mode of pointwise_result (:2581-2955; the mode list is
+   lib/Import/Schema.cpp:301-316, the input counts :353-377). The value is
+   computed in f32, one separately rounded operation per step of the reference's
+   expression. tensors: {IN_0, IN_1 or null, OUT_0, IN_2 or null}; inputs
+   broadcast onto OUT_0 over trailing axes. A _BWD mode reads the incoming
+   gradient from IN_0 and the activation's input from IN_1; BINARY_SELECT gives
+   IN_1 where IN_2 is non-zero, else IN_0; GEN_INDEX gives the output index
+   along `axis`. */
+enum {
+    DFGPU_PW_ADD = 0, DFGPU_PW_RELU_FWD = 1, DFGPU_PW_IDENTITY = 2, DFGPU_PW_MUL = 3, DFGPU_PW_SUB = 4,
+    DFGPU_PW_DIV = 5, DFGPU_PW_ADD_SQUARE = 6, DFGPU_PW_MIN = 7, DFGPU_PW_MAX = 8, DFGPU_PW_MOD = 9,
+    DFGPU_PW_POW = 10, DFGPU_PW_SQRT = 11, DFGPU_PW_RSQRT = 12, DFGPU_PW_EXP = 13, DFGPU_PW_LOG = 14,
+    DFGPU_PW_NEG = 15, DFGPU_PW_ABS = 16, DFGPU_PW_CEIL = 17, DFGPU_PW_FLOOR = 18, DFGPU_PW_COS = 19,
+    DFGPU_PW_SIN = 20, DFGPU_PW_TAN = 21, DFGPU_PW_ERF = 22, DFGPU_PW_RECIPROCAL = 23, DFGPU_PW_GEN_INDEX = 24,
+    DFGPU_PW_LOGICAL_NOT = 25, DFGPU_PW_LOGICAL_AND = 26, DFGPU_PW_LOGICAL_OR = 27, DFGPU_PW_BINARY_SELECT = 28,
+    DFGPU_PW_CMP_EQ = 29, DFGPU_PW_CMP_NEQ = 30, DFGPU_PW_CMP_GT = 31, DFGPU_PW_CMP_GE = 32, DFGPU_PW_CMP_LT = 33,
+    DFGPU_PW_CMP_LE = 34, DFGPU_PW_RELU_BWD = 35, DFGPU_PW_TANH_FWD = 36, DFGPU_PW_TANH_BWD = 37,
+    DFGPU_PW_SIGMOID_FWD = 38, DFGPU_PW_SIGMOID_BWD = 39, DFGPU_PW_ELU_FWD = 40, DFGPU_PW_ELU_BWD = 41,
+    DFGPU_PW_SOFTPLUS_FWD = 42, DFGPU_PW_SOFTPLUS_BWD = 43, DFGPU_PW_SWISH_FWD = 44, DFGPU_PW_SWISH_BWD = 45,
+    DFGPU_PW_GELU_FWD = 46, DFGPU_PW_GELU_BWD = 47, DFGPU_PW_GELU_APPROX_TANH_FWD = 48,
+    DFGPU_PW_GELU_APPROX_TANH_BWD = 49, DFGPU_PW_MODE_COUNT = 50
+};
 typedef struct dfgpu_pointwise_params {
     dfgpu_tensor in0, in1, out;
     int32_t mode;
-    float relu_lower, relu_upper, relu_slope;
+    float relu_lower, relu_upper, relu_slope;   /* relu_lower_clip (0), relu_upper_clip (FLT_MAX), relu_lower_clip_slope (0) */
+    dfgpu_tensor in2;                           /* BINARY_SELECT */
+    float elu_alpha, softplus_beta, swish_beta; /* the node's attributes; 1 where the node leaves them null */
+    int32_t axis;                               /* GEN_INDEX */
 } dfgpu_pointwise_params;
+/* Inputs the mode reads (1, 2 or 3); 0 for a number outside the table. */
+int dfgpu_pointwise_input_count(int32_t mode);
 int dfgpu_query_pointwise(const dfgpu_pointwise_params*, dfgpu_plan_info*);
 int dfgpu_pointwise(const dfgpu_pointwise_params*, void* const* tensors, void* scratch, void* stream);
 

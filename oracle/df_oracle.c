@@ -361,14 +361,17 @@ static void store_f32(const dfo_tensor* t, void* data, int64_t offset, float val
 /* ------------------------------------------------------------------------ */
 
 /* arith.maximumf: NaN if either operand is NaN. */
+/* arith.maximumf / arith.minimumf: a NaN operand gives NaN, and -0 orders below +0. */
 static float maximumf_nan(float a, float b) {
     if (a != a) return a;
     if (b != b) return b;
+    if (a == b) return signbit(a) ? b : a;
     return a > b ? a : b;
 }
 static float minimumf_nan(float a, float b) {
     if (a != a) return a;
     if (b != b) return b;
+    if (a == b) return signbit(a) ? a : b;
     return a < b ? a : b;
 }
 
@@ -462,65 +465,174 @@ int dfo_block_scale_dequantize(const dfo_tensor* x, const void* x_data,
 
 /* ------------------------------------------------------------------------ */
 /* pointwise (reference: lib/Compiler/FoundationalGraph.cpp:2552-2567 for   */
-/* trailing-axis broadcast, :2599 ADD, :2731-2758 RELU_FWD)                  */
+/* trailing-axis broadcast, :2581-2955 for the value of every mode)          */
 /* ------------------------------------------------------------------------ */
 
-/* One element of emit_pointwise; *unknown is set for a mode outside the executable set. */
-static float pointwise_value(int32_t mode, float x, float y, float relu_lower, float relu_upper, float relu_slope, int* unknown) {
+/* Inputs a mode reads (lib/Import/Schema.cpp:353-377); 0 for a mode outside the table. */
+int dfo_pointwise_input_count(int32_t mode) {
+    if (mode < 0 || mode >= DFO_PW_MODE_COUNT) return 0;
+    switch (mode) {
+        case DFO_PW_BINARY_SELECT: return 3;
+        case DFO_PW_ADD: case DFO_PW_MUL: case DFO_PW_SUB: case DFO_PW_DIV: case DFO_PW_ADD_SQUARE:
+        case DFO_PW_MIN: case DFO_PW_MAX: case DFO_PW_MOD: case DFO_PW_POW:
+        case DFO_PW_LOGICAL_AND: case DFO_PW_LOGICAL_OR:
+        case DFO_PW_CMP_EQ: case DFO_PW_CMP_NEQ: case DFO_PW_CMP_GT: case DFO_PW_CMP_GE: case DFO_PW_CMP_LT: case DFO_PW_CMP_LE:
+        case DFO_PW_RELU_BWD: case DFO_PW_TANH_BWD: case DFO_PW_SIGMOID_BWD: case DFO_PW_ELU_BWD: case DFO_PW_SOFTPLUS_BWD:
+        case DFO_PW_SWISH_BWD: case DFO_PW_GELU_BWD: case DFO_PW_GELU_APPROX_TANH_BWD:
+            return 2;
+        default: return 1;
+    }
+}
+
+/* FoundationalGraph.cpp:2569-2579 */
+static float sigmoid_f32(float v) { return 1.0f / (1.0f + expf(-v)); }
+
+/* One element of emit_pointwise, every step a separately rounded f32 operation as the reference emits it. x, y, z are
+   IN_0, IN_1, IN_2 (0 where the mode has no such input); for the _BWD modes IN_0 is the incoming gradient and IN_1 the
+   activation's input. `position` is the output index along the node's axis (GEN_INDEX). */
+static float pointwise_value(int32_t mode, float x, float y, float z, const dfo_pointwise_scalars* s, int64_t position, int* unknown) {
+    const float u = dfo_pointwise_input_count(mode) == 2 && mode >= DFO_PW_RELU_BWD ? y : x;  /* the activation's input */
     switch (mode) {
         case DFO_PW_ADD: return x + y;
         case DFO_PW_MUL: return x * y;
         case DFO_PW_SUB: return x - y;
-        case DFO_PW_RELU_FWD: {
-            float clipped = minimumf_nan(maximumf_nan(x, relu_lower), relu_upper);
-            float lower_branch = relu_lower + relu_slope * (x - relu_lower);
-            return x < relu_lower ? lower_branch : clipped;
-        }
+        case DFO_PW_DIV: return x / y;
+        case DFO_PW_ADD_SQUARE: { float square = y * y; return x + square; }
+        case DFO_PW_MIN: return minimumf_nan(x, y);
+        case DFO_PW_MAX: return maximumf_nan(x, y);
+        case DFO_PW_MOD: return fmodf(x, y);
+        case DFO_PW_POW: return powf(x, y);
+        case DFO_PW_SQRT: return sqrtf(x);
+        case DFO_PW_RSQRT: return 1.0f / sqrtf(x);
+        case DFO_PW_EXP: return expf(x);
+        case DFO_PW_LOG: return logf(x);
+        case DFO_PW_NEG: return -x;
+        case DFO_PW_ABS: return fabsf(x);
+        case DFO_PW_CEIL: return ceilf(x);
+        case DFO_PW_FLOOR: return floorf(x);
+        case DFO_PW_COS: return cosf(x);
+        case DFO_PW_SIN: return sinf(x);
+        case DFO_PW_TAN: return tanf(x);
+        case DFO_PW_ERF: return erff(x);
+        case DFO_PW_RECIPROCAL: return 1.0f / x;
         case DFO_PW_IDENTITY: return x;
+        case DFO_PW_GEN_INDEX: return (float)(uint64_t)position;
+        case DFO_PW_LOGICAL_NOT: return x == 0.0f ? 1.0f : 0.0f;
+        case DFO_PW_LOGICAL_AND: return (x != 0.0f) && (y != 0.0f) ? 1.0f : 0.0f;
+        case DFO_PW_LOGICAL_OR: return (x != 0.0f) || (y != 0.0f) ? 1.0f : 0.0f;
+        case DFO_PW_BINARY_SELECT: return z != 0.0f ? y : x;
+        case DFO_PW_CMP_EQ: return x == y ? 1.0f : 0.0f;
+        case DFO_PW_CMP_NEQ: return x != y ? 1.0f : 0.0f;
+        case DFO_PW_CMP_GT: return x > y ? 1.0f : 0.0f;
+        case DFO_PW_CMP_GE: return x >= y ? 1.0f : 0.0f;
+        case DFO_PW_CMP_LT: return x < y ? 1.0f : 0.0f;
+        case DFO_PW_CMP_LE: return x <= y ? 1.0f : 0.0f;
+        case DFO_PW_RELU_FWD: {
+            float clipped = minimumf_nan(maximumf_nan(x, s->relu_lower), s->relu_upper);
+            float lower_branch = s->relu_lower + s->relu_slope * (x - s->relu_lower);
+            return x < s->relu_lower ? lower_branch : clipped;
+        }
+        case DFO_PW_RELU_BWD: {
+            float derivative = y < s->relu_lower ? s->relu_slope : (y > s->relu_upper ? 0.0f : 1.0f);
+            return x * derivative;
+        }
+        case DFO_PW_TANH_FWD: return tanhf(u);
+        case DFO_PW_TANH_BWD: { float t = tanhf(u); float square = t * t; return x * (1.0f - square); }
+        case DFO_PW_SIGMOID_FWD: return sigmoid_f32(u);
+        case DFO_PW_SIGMOID_BWD: { float v = sigmoid_f32(u); return x * (v * (1.0f - v)); }
+        case DFO_PW_ELU_FWD: { float e = expf(u); return u >= 0.0f ? u : s->elu_alpha * (e - 1.0f); }
+        case DFO_PW_ELU_BWD: { float e = expf(u); return x * (u >= 0.0f ? 1.0f : s->elu_alpha * e); }
+        case DFO_PW_SOFTPLUS_FWD: {
+            float scaled = s->softplus_beta * u;
+            float logarithm = logf(1.0f + expf(-fabsf(scaled)));
+            float stable = maximumf_nan(scaled, 0.0f) + logarithm;
+            return stable / s->softplus_beta;
+        }
+        case DFO_PW_SOFTPLUS_BWD: return x * sigmoid_f32(s->softplus_beta * u);
+        case DFO_PW_SWISH_FWD: return u * sigmoid_f32(s->swish_beta * u);
+        case DFO_PW_SWISH_BWD: {
+            float scaled = s->swish_beta * u;
+            float v = sigmoid_f32(scaled);
+            return x * (v + scaled * (v * (1.0f - v)));
+        }
+        case DFO_PW_GELU_FWD: case DFO_PW_GELU_BWD: {
+            float cdf = 0.5f * (1.0f + erff(u * 0.7071067811865475f));
+            if (mode == DFO_PW_GELU_FWD) return u * cdf;
+            float square = u * u;
+            float density = 0.3989422804014327f * expf(-0.5f * square);
+            return x * (cdf + u * density);
+        }
+        case DFO_PW_GELU_APPROX_TANH_FWD: case DFO_PW_GELU_APPROX_TANH_BWD: {
+            float square = u * u;
+            float cubic = square * u;
+            float inner = 0.7978845608028654f * (u + 0.044715f * cubic);
+            float t = tanhf(inner);
+            float cdf = 0.5f * (1.0f + t);
+            if (mode == DFO_PW_GELU_APPROX_TANH_FWD) return u * cdf;
+            float inner_derivative = 0.7978845608028654f * (1.0f + 0.134145f * square);
+            float tanh_derivative = 1.0f - t * t;
+            return x * (cdf + 0.5f * (u * (tanh_derivative * inner_derivative)));
+        }
         default: *unknown = 1; return 0.0f;
     }
 }
 
 /* Elements [flat_begin, flat_end) of the logical output (row-major over its dims; end < 0 = all), so that callers can
-   run slabs on several threads. The index and the three storage offsets advance like an odometer instead of being
+   run slabs on several threads. The index and the storage offsets advance like an odometer instead of being
    re-derived by division for every element; the arithmetic per element is the same. */
+int dfo_pointwise_general_range(int32_t mode, const dfo_tensor* a, const void* a_data,
+                                const dfo_tensor* b, const void* b_data,
+                                const dfo_tensor* c, const void* c_data,
+                                const dfo_tensor* out, void* out_data,
+                                const dfo_pointwise_scalars* scalars,
+                                int64_t flat_begin, int64_t flat_end) {
+    int64_t index[DFO_MAX_RANK];
+    int64_t a_step[DFO_MAX_RANK], b_step[DFO_MAX_RANK], c_step[DFO_MAX_RANK];
+    int64_t count = element_count(out);
+    if (flat_begin < 0) flat_begin = 0;
+    if (flat_end < 0 || flat_end > count) flat_end = count;
+    if (flat_begin >= flat_end) return 0;
+    const int inputs = dfo_pointwise_input_count(mode);
+    if (inputs == 0) return 20;
+    if ((inputs >= 2 && (!b || !b_data)) || (inputs >= 3 && (!c || !c_data))) return 1;
+    const int rank = out->rank;
+    if (mode == DFO_PW_GEN_INDEX && (scalars->axis < 0 || scalars->axis >= rank)) return 8;
+    for (int i = 0; i < rank; ++i) {  /* stride of each operand along output axis i (0 where it broadcasts) */
+        int ia = i - (rank - a->rank), ib = inputs >= 2 ? i - (rank - b->rank) : -1, ic = inputs >= 3 ? i - (rank - c->rank) : -1;
+        a_step[i] = ia >= 0 && a->dim[ia] != 1 ? a->stride[ia] : 0;
+        b_step[i] = ib >= 0 && b->dim[ib] != 1 ? b->stride[ib] : 0;
+        c_step[i] = ic >= 0 && c->dim[ic] != 1 ? c->stride[ic] : 0;
+    }
+    unflatten(out, flat_begin, index);
+    int64_t ao = 0, bo = 0, co = 0, oo = 0;
+    for (int i = 0; i < rank; ++i) { ao += index[i] * a_step[i]; bo += index[i] * b_step[i]; co += index[i] * c_step[i]; oo += index[i] * out->stride[i]; }
+    int unknown = 0;
+    for (int64_t flat = flat_begin; flat < flat_end; ++flat) {
+        float x = load_f32(a, a_data, ao);
+        float y = inputs >= 2 ? load_f32(b, b_data, bo) : 0.0f;
+        float z = inputs >= 3 ? load_f32(c, c_data, co) : 0.0f;
+        int64_t position = mode == DFO_PW_GEN_INDEX ? index[scalars->axis] : 0;
+        store_f32(out, out_data, oo, pointwise_value(mode, x, y, z, scalars, position, &unknown));
+        if (unknown) return 20;
+        for (int i = rank - 1; i >= 0; --i) {  /* next index */
+            ++index[i];
+            ao += a_step[i]; bo += b_step[i]; co += c_step[i]; oo += out->stride[i];
+            if (index[i] < out->dim[i]) break;
+            ao -= index[i] * a_step[i]; bo -= index[i] * b_step[i]; co -= index[i] * c_step[i]; oo -= index[i] * out->stride[i];
+            index[i] = 0;
+        }
+    }
+    return 0;
+}
+
+/* The one- and two-input modes that take only the ReLU parameters. */
 int dfo_pointwise_range(int32_t mode, const dfo_tensor* a, const void* a_data,
                         const dfo_tensor* b, const void* b_data,
                         const dfo_tensor* out, void* out_data,
                         float relu_lower, float relu_upper, float relu_slope,
                         int64_t flat_begin, int64_t flat_end) {
-    int64_t index[DFO_MAX_RANK];
-    int64_t a_step[DFO_MAX_RANK], b_step[DFO_MAX_RANK];
-    int64_t count = element_count(out);
-    if (flat_begin < 0) flat_begin = 0;
-    if (flat_end < 0 || flat_end > count) flat_end = count;
-    if (flat_begin >= flat_end) return 0;
-    const int binary = mode == DFO_PW_ADD || mode == DFO_PW_MUL || mode == DFO_PW_SUB;
-    if (binary && (!b || !b_data)) return 1;
-    const int rank = out->rank;
-    for (int i = 0; i < rank; ++i) {  /* stride of each operand along output axis i (0 where it broadcasts) */
-        int ia = i - (rank - a->rank), ib = b ? i - (rank - b->rank) : -1;
-        a_step[i] = ia >= 0 && a->dim[ia] != 1 ? a->stride[ia] : 0;
-        b_step[i] = binary && ib >= 0 && b->dim[ib] != 1 ? b->stride[ib] : 0;
-    }
-    unflatten(out, flat_begin, index);
-    int64_t ao = 0, bo = 0, oo = 0;
-    for (int i = 0; i < rank; ++i) { ao += index[i] * a_step[i]; bo += index[i] * b_step[i]; oo += index[i] * out->stride[i]; }
-    int unknown = 0;
-    for (int64_t flat = flat_begin; flat < flat_end; ++flat) {
-        float x = load_f32(a, a_data, ao);
-        float y = binary ? load_f32(b, b_data, bo) : 0.0f;
-        store_f32(out, out_data, oo, pointwise_value(mode, x, y, relu_lower, relu_upper, relu_slope, &unknown));
-        if (unknown) return 20;
-        for (int i = rank - 1; i >= 0; --i) {  /* next index */
-            ++index[i];
-            ao += a_step[i]; bo += b_step[i]; oo += out->stride[i];
-            if (index[i] < out->dim[i]) break;
-            ao -= index[i] * a_step[i]; bo -= index[i] * b_step[i]; oo -= index[i] * out->stride[i];
-            index[i] = 0;
-        }
-    }
-    return 0;
+    dfo_pointwise_scalars scalars = {relu_lower, relu_upper, relu_slope, 1.0f, 1.0f, 1.0f, 0};
+    return dfo_pointwise_general_range(mode, a, a_data, b, b_data, NULL, NULL, out, out_data, &scalars, flat_begin, flat_end);
 }
 
 int dfo_pointwise(int32_t mode, const dfo_tensor* a, const void* a_data,

@@ -80,7 +80,34 @@ int dfo_block_scale_dequantize(const dfo_tensor* x, const void* x_data,
                                const int64_t* block, int32_t block_count);
 
 /* pointwise */
-enum { DFO_PW_ADD = 0, DFO_PW_RELU_FWD = 1, DFO_PW_IDENTITY = 2, DFO_PW_MUL = 3, DFO_PW_SUB = 4 };
+/* Every mode of lib/Import/Schema.cpp:301-316; the numbers are this oracle's own (and the CUDA library's). */
+enum {
+    DFO_PW_ADD = 0, DFO_PW_RELU_FWD = 1, DFO_PW_IDENTITY = 2, DFO_PW_MUL = 3, DFO_PW_SUB = 4,
+    DFO_PW_DIV = 5, DFO_PW_ADD_SQUARE = 6, DFO_PW_MIN = 7, DFO_PW_MAX = 8, DFO_PW_MOD = 9, DFO_PW_POW = 10,
+    DFO_PW_SQRT = 11, DFO_PW_RSQRT = 12, DFO_PW_EXP = 13, DFO_PW_LOG = 14, DFO_PW_NEG = 15, DFO_PW_ABS = 16,
+    DFO_PW_CEIL = 17, DFO_PW_FLOOR = 18, DFO_PW_COS = 19, DFO_PW_SIN = 20, DFO_PW_TAN = 21, DFO_PW_ERF = 22,
+    DFO_PW_RECIPROCAL = 23, DFO_PW_GEN_INDEX = 24, DFO_PW_LOGICAL_NOT = 25, DFO_PW_LOGICAL_AND = 26,
+    DFO_PW_LOGICAL_OR = 27, DFO_PW_BINARY_SELECT = 28, DFO_PW_CMP_EQ = 29, DFO_PW_CMP_NEQ = 30, DFO_PW_CMP_GT = 31,
+    DFO_PW_CMP_GE = 32, DFO_PW_CMP_LT = 33, DFO_PW_CMP_LE = 34,
+    /* from here on: activations; a _BWD mode reads the gradient from IN_0 and the activation's input from IN_1 */
+    DFO_PW_RELU_BWD = 35, DFO_PW_TANH_FWD = 36, DFO_PW_TANH_BWD = 37, DFO_PW_SIGMOID_FWD = 38, DFO_PW_SIGMOID_BWD = 39,
+    DFO_PW_ELU_FWD = 40, DFO_PW_ELU_BWD = 41, DFO_PW_SOFTPLUS_FWD = 42, DFO_PW_SOFTPLUS_BWD = 43, DFO_PW_SWISH_FWD = 44,
+    DFO_PW_SWISH_BWD = 45, DFO_PW_GELU_FWD = 46, DFO_PW_GELU_BWD = 47, DFO_PW_GELU_APPROX_TANH_FWD = 48,
+    DFO_PW_GELU_APPROX_TANH_BWD = 49, DFO_PW_MODE_COUNT = 50
+};
+typedef struct dfo_pointwise_scalars {
+    float relu_lower, relu_upper, relu_slope; /* defaults 0, FLT_MAX, 0 */
+    float elu_alpha, softplus_beta, swish_beta; /* defaults 1 */
+    int32_t axis;                               /* GEN_INDEX */
+} dfo_pointwise_scalars;
+int dfo_pointwise_input_count(int32_t mode);
+/* Any mode: c is IN_2 (BINARY_SELECT), NULL otherwise. Elements [flat_begin, flat_end) (end < 0: all). */
+int dfo_pointwise_general_range(int32_t mode, const dfo_tensor* a, const void* a_data,
+                                const dfo_tensor* b, const void* b_data,
+                                const dfo_tensor* c, const void* c_data,
+                                const dfo_tensor* out, void* out_data,
+                                const dfo_pointwise_scalars* scalars,
+                                int64_t flat_begin, int64_t flat_end);
 /* dfo_pointwise over elements [flat_begin, flat_end) of the logical output (end < 0: all). */
 int dfo_pointwise_range(int32_t mode, const dfo_tensor* a, const void* a_data,
                         const dfo_tensor* b, const void* b_data,

@@ -129,6 +129,28 @@ def pointwise(mode, ad, a, bd, b, od, out, lower=0.0, upper=3.4028234663852886e3
                count, threads if count >= (1 << 16) else 1)
 
 
+class PointwiseScalars(C.Structure):
+    _fields_ = [("relu_lower", C.c_float), ("relu_upper", C.c_float), ("relu_slope", C.c_float), ("elu_alpha", C.c_float),
+                ("softplus_beta", C.c_float), ("swish_beta", C.c_float), ("axis", C.c_int32)]
+
+
+def pointwise_general(mode, ad, a, bd, b, cd, c, od, out, lower=0.0, upper=3.4028234663852886e38, slope=0.0, elu_alpha=1.0,
+                      softplus_beta=1.0, swish_beta=1.0, axis=0, threads: int = 1) -> None:
+    """Any POINTWISE mode; (cd, c) is IN_2 of BINARY_SELECT, None otherwise."""
+    count = 1
+    for i in range(od.rank):
+        count *= int(od.dim[i])
+    scalars = PointwiseScalars(lower, upper, slope, elu_alpha, softplus_beta, swish_beta, axis)
+    fn = lib().dfo_pointwise_general_range
+    fn.restype = C.c_int
+
+    def slab(lo, hi):
+        return fn(C.c_int32(mode), C.byref(ad), ptr(a), C.byref(bd) if bd is not None else None, ptr(b) if b is not None else None,
+                  C.byref(cd) if cd is not None else None, ptr(c) if c is not None else None, C.byref(od), ptr(out),
+                  C.byref(scalars), C.c_int64(lo), C.c_int64(hi))
+    _run_slabs(slab, count, threads if count >= (1 << 16) else 1)
+
+
 def conv_attrs(pre, post, stride, dilation, reverse=False) -> ConvAttrs:
     a = ConvAttrs()
     a.spatial_rank = len(pre)

@@ -80,15 +80,18 @@ def run(document: dict, inputs: Dict[int, np.ndarray], matmul_rows: Optional[Tup
         elif tag == "POINTWISE":
             out = outs["OUT_0"]
             values[out] = _alloc(tensors[out])
-            mode = {"ADD": dfgpu.PW_ADD, "MUL": dfgpu.PW_MUL, "SUB": dfgpu.PW_SUB, "RELU_FWD": dfgpu.PW_RELU_FWD, "IDENTITY": dfgpu.PW_IDENTITY}[node["mode"]]
-            a = ins["IN_0"]
-            b = ins.get("IN_1")
-            lower = node.get("relu_lower_clip")
-            upper = node.get("relu_upper_clip")
-            slope = node.get("relu_lower_clip_slope")
-            oracle.pointwise(mode, _desc(tensors[a]), values[a], _desc(tensors[b]) if b is not None else None, values[b] if b is not None else None,
-                             _desc(tensors[out]), values[out], 0.0 if lower is None else lower, FLT_MAX if upper is None else upper,
-                             0.0 if slope is None else slope, threads=threads)
+            mode = dfgpu.PW_MODES[node["mode"]]
+            a, b, c = ins["IN_0"], ins.get("IN_1"), ins.get("IN_2")
+
+            def number(key, default):
+                value = node.get(key)
+                return default if value is None else value
+            oracle.pointwise_general(mode, _desc(tensors[a]), values[a], _desc(tensors[b]) if b is not None else None,
+                                     values[b] if b is not None else None, _desc(tensors[c]) if c is not None else None,
+                                     values[c] if c is not None else None, _desc(tensors[out]), values[out],
+                                     number("relu_lower_clip", 0.0), number("relu_upper_clip", FLT_MAX),
+                                     number("relu_lower_clip_slope", 0.0), number("elu_alpha", 1.0), number("softplus_beta", 1.0),
+                                     number("swish_beta", 1.0), number("axis", 0), threads=threads)
         elif tag == "MATMUL":
             a, b, c = ins["A"], ins["B"], outs["C"]
             values[c] = _alloc(tensors[c])

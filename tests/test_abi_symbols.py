@@ -4,6 +4,8 @@ import ctypes as C
 import re
 from pathlib import Path
 
+import pytest
+
 from deepforge_b200 import dfgpu
 
 ROOT = Path(__file__).resolve().parent.parent
@@ -21,7 +23,7 @@ def test_kernel_library_exports_every_declared_symbol():
     for name in names:
         assert hasattr(lib, name), name
     assert sorted(dfgpu.EXPORTS) == names
-    assert lib.dfgpu_abi_version() == 9
+    assert lib.dfgpu_abi_version() == 10
 
 
 def test_struct_layout_matches_header():
@@ -33,7 +35,7 @@ def test_struct_layout_matches_header():
     assert C.sizeof(dfgpu.BsqParams) == 448
     assert C.sizeof(dfgpu.BsdParams) == 504
     assert C.sizeof(dfgpu.BsqPairParams) == 896
-    assert C.sizeof(dfgpu.PointwiseParams) == 448
+    assert C.sizeof(dfgpu.PointwiseParams) == 608
     assert C.sizeof(dfgpu.ConvParams) == 928
     assert C.sizeof(dfgpu.ConvPairParams) == 1856
     assert C.sizeof(dfgpu.MatmulParams) == 1144
@@ -79,3 +81,23 @@ def test_query_rejects_bad_descriptors_without_a_gpu():
     p.scale = dfgpu.tensor(dfgpu.E8M0, [1, 64])
     p.block_size = 4
     assert dfgpu.query("block_scale_quantize", p).kernel == dfgpu.BSQ_GENERIC
+
+
+def test_pointwise_rejects_what_the_reference_rejects():
+    """validate_pointwise (lib/Compiler/FoundationalGraph.cpp:721-775): GEN_INDEX axis, softplus beta, clip order; no launch."""
+    d = dfgpu.tensor(dfgpu.F32, [4, 4])
+    for mode_name, change in (("GEN_INDEX", dict(axis=2)), ("GEN_INDEX", dict(axis=-1)), ("SOFTPLUS_FWD", dict(softplus_beta=0.0)),
+                              ("RELU_BWD", dict(relu_lower=2.0, relu_upper=1.0))):
+        p = dfgpu.PointwiseParams()
+        p.in0, p.in1, p.out, p.mode = d, d, d, dfgpu.PW_MODES[mode_name]
+        p.relu_upper = 3.4028234663852886e38
+        for key, value in change.items():
+            setattr(p, key, value)
+        with pytest.raises(dfgpu.DfgpuError) as error:
+            dfgpu.query("pointwise", p)
+        assert error.value.code == 8
+    p = dfgpu.PointwiseParams()
+    p.in0, p.out, p.mode = d, d, 50
+    with pytest.raises(dfgpu.DfgpuError) as error:
+        dfgpu.query("pointwise", p)
+    assert error.value.code == 20

@@ -70,6 +70,89 @@ def test_pointwise_broadcast(mode, dtype):
     assert np.array_equal(a_bits[~nan], r_bits[~nan])
 
 
+# modes whose value goes through exp, log, pow, erf, tanh or the trigonometric functions: CUDA's and the host's math
+# libraries round those differently (both within a few ulp), everything else is the same bits
+LIBM_MODES = {"POW", "EXP", "LOG", "COS", "SIN", "TAN", "ERF", "TANH_FWD", "TANH_BWD", "SIGMOID_FWD", "SIGMOID_BWD", "ELU_FWD",
+              "ELU_BWD", "SOFTPLUS_FWD", "SOFTPLUS_BWD", "SWISH_FWD", "SWISH_BWD", "GELU_FWD", "GELU_BWD", "GELU_APPROX_TANH_FWD",
+              "GELU_APPROX_TANH_BWD"}
+
+
+def pointwise_operands(rows, columns):
+    rng = np.random.default_rng(99)
+    a = (np.round(rng.uniform(-3.0, 3.0, (rows, columns)) * 8) / 8).astype(np.float32)   # multiples of 1/8: A == B happens
+    b = (np.round(rng.uniform(-3.0, 3.0, (rows, columns)) * 8) / 8).astype(np.float32)
+    t = (rng.integers(0, 2, (rows, columns)) * rng.uniform(-2.0, 2.0, (rows, columns))).astype(np.float32)
+    a[0, :8] = [0.0, -0.0, 0.0, -0.0, 2.5, -2.5, np.nan, np.inf]
+    b[0, :8] = [0.0, 0.0, -0.0, -0.0, 2.5, 0.0, 1.0, -1.0]
+    return a, b, t
+
+
+@pytest.mark.parametrize("layout", ["packed_f32", "packed_bf16", "broadcast_f32", "broadcast_f16_to_f32"])
+@pytest.mark.parametrize("mode_name", dfgpu.PW_MODE_NAMES)
+def test_pointwise_every_mode_against_the_oracle(mode_name, layout):
+    """lib/Compiler/FoundationalGraph.cpp:2581-2955: all 50 modes, through both general kernels (four packed values per
+    thread; one element per thread with broadcast, strides and mixed storage types) and the five dedicated ones."""
+    rows, columns = 24, 40
+    a, b, t = pointwise_operands(rows, columns)
+    count = dfgpu.pointwise_input_count(mode_name)
+    in_type = {"packed_f32": F32, "packed_bf16": BF16, "broadcast_f32": F32, "broadcast_f16_to_f32": dfgpu.F16}[layout]
+    out_type = BF16 if layout == "packed_bf16" else F32
+    if layout.startswith("packed"):
+        bd, td = tensor(in_type, [rows, columns]), tensor(in_type, [rows, columns])
+    else:   # B along the columns, T down the rows, A with padded rows
+        b, t = b[:1].copy(), t[:, :1].copy()
+        bd, td = tensor(in_type, [columns]), tensor(in_type, [rows, 1])
+    ad = tensor(in_type, [rows, columns]) if layout.startswith("packed") else tensor(in_type, [rows, columns], [columns + 3, 1])
+    od = tensor(out_type, [rows, columns])
+
+    def stored(values, descriptor):
+        if in_type == BF16:
+            bits = synthetic.to_bf16_bits(values)
+        elif in_type == dfgpu.F16:
+            bits = np.ascontiguousarray(values, dtype=np.float16).view(np.uint16)
+        else:
+            bits = np.ascontiguousarray(values, dtype=np.float32)
+        if descriptor.rank == 2 and int(descriptor.stride[0]) != int(descriptor.dim[1]):
+            padded = np.zeros((rows, int(descriptor.stride[0])), bits.dtype)
+            padded[:, :columns] = bits.reshape(rows, columns)
+            return np.ascontiguousarray(padded)
+        return np.ascontiguousarray(bits)
+    ha, hb, ht = stored(a, ad), stored(b, bd), stored(t, td)
+    width = dfgpu.DTYPE_BYTES[out_type]
+    ref = np.zeros(rows * columns * width, dtype=np.uint8)
+    scalars = dict(lower=-0.5, upper=1.25, slope=0.125, elu_alpha=1.5, softplus_beta=0.75, swish_beta=1.75, axis=1)
+    oracle.pointwise_general(dfgpu.PW_MODES[mode_name], ad, ha, bd if count >= 2 else None, hb if count >= 2 else None,
+                             td if count >= 3 else None, ht if count >= 3 else None, od, ref, **scalars)
+    p = dfgpu.PointwiseParams()
+    p.in0, p.out, p.mode = ad, od, dfgpu.PW_MODES[mode_name]
+    if count >= 2:
+        p.in1 = bd
+    if count >= 3:
+        p.in2 = td
+    p.relu_lower, p.relu_upper, p.relu_slope = scalars["lower"], scalars["upper"], scalars["slope"]
+    p.elu_alpha, p.softplus_beta, p.swish_beta, p.axis = scalars["elu_alpha"], scalars["softplus_beta"], scalars["swish_beta"], 1
+    da, db, dt, do = g.to_device(ha), g.to_device(hb), g.to_device(ht), g.device_zeros(ref.size)
+    dfgpu.pointwise(p, g.ptr(da), g.ptr(db) if count >= 2 else 0, g.ptr(do), in2=g.ptr(dt) if count >= 3 else 0)
+    out = g.to_host(do, np.uint8)
+    if out_type == F32:
+        got, want = out.view(np.float32), ref.view(np.float32)
+    else:
+        got, want = synthetic.bf16_bits_to_f32(out.view(np.uint16)), synthetic.bf16_bits_to_f32(ref.view(np.uint16))
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    finite = ~np.isnan(want)
+    if mode_name in LIBM_MODES:
+        infinite = np.isinf(want)
+        assert np.array_equal(got[infinite], want[infinite])
+        ok = finite & ~infinite
+        if out_type == F32:
+            assert np.all(np.abs(got[ok] - want[ok]) <= 2e-6 + 2e-6 * np.abs(want[ok])), float(np.max(np.abs(got[ok] - want[ok])))
+        else:   # one bf16 step where the f32 values straddle a rounding boundary
+            assert np.all(np.abs(got[ok] - want[ok]) <= 2.0 ** -7 * np.abs(want[ok]) + 1e-30)
+    else:
+        view = np.uint32 if out_type == F32 else np.uint16
+        assert np.array_equal(out.view(view)[finite], ref.view(view)[finite])
+
+
 def test_relu_default_clips_inf_to_flt_max_and_keeps_nan():
     x = np.array([-1.0, 0.5, np.inf, np.nan, -np.inf], dtype=np.float32)
     d = tensor(F32, [5])

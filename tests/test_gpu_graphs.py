@@ -362,6 +362,45 @@ def test_packed_four_bit_graphs_reproduce_the_reference_known_answers():
     assert dfgpu.device_status() == 0
 
 
+def test_every_pointwise_mode_through_the_executable():
+    """The reference's all-modes graph (test/Compiler/FoundationalMathOpsTest.cpp:126-167, inputs :617-619): 50 POINTWISE nodes
+    over A [2, 3], B [3], T [2, 1], each answer within the reference test's own 3e-4 + 3e-4 |expected| of its f64 formulas
+    (:440-556); then the same graph on 64 x 48 seeded values, and in BFLOAT16 against the oracle."""
+    import pointwise_reference as reference
+    from deepforge_b200 import graphs
+
+    def session(doc, inputs):
+        outputs = [1000 + i for i in range(len(graphs.SCHEMA_POINTWISE_MODES))]
+        wl = workloads.Workload(name="pointwise_all_modes", config=0, document=doc, description={}, metric="", unit="GB/s", flops=1.0, bytes=1.0,
+                                bound="hbm", inputs=inputs, outputs=outputs)
+        s = harness.Session(wl)
+        s.run()
+        return wl, s
+
+    wl, s = session(graphs.pointwise_all_modes(), {101: lambda: reference.A.copy(), 102: lambda: reference.B.copy(), 103: lambda: reference.T.copy()})
+    assert s.exe.launch_count == 50
+    for position, mode in enumerate(graphs.SCHEMA_POINTWISE_MODES):
+        reference.assert_close(mode, s.output(1000 + position), reference.expected(mode, reference.A.reshape(2, 3), reference.B, reference.T))
+
+    rng = np.random.default_rng(4321)
+    a = (np.round(rng.uniform(-3.0, 3.0, (64, 48)) * 8) / 8).astype(np.float32)
+    b = (np.round(rng.uniform(-3.0, 3.0, 48) * 8) / 8).astype(np.float32)
+    t = (rng.integers(0, 2, 64) * rng.uniform(-2.0, 2.0, 64)).astype(np.float32)
+    wl, s = session(graphs.pointwise_all_modes((64, 48)), {101: lambda: a.reshape(-1).copy(), 102: lambda: b.copy(), 103: lambda: t.copy()})
+    ins, _ = oracle_inputs(wl, s)
+    ref = graph_oracle.run(wl.document, ins)
+    for position, mode in enumerate(graphs.SCHEMA_POINTWISE_MODES):
+        reference.assert_close(mode, s.output(1000 + position), reference.expected(mode, a, b, t))
+        reference.assert_close(mode, s.output(1000 + position), ref[1000 + position], 2e-6, 2e-6)
+
+    wl, s = session(graphs.pointwise_all_modes((64, 48), "BFLOAT16"),
+                    {101: lambda: synthetic.to_bf16_bits(a.reshape(-1)), 102: lambda: synthetic.to_bf16_bits(b), 103: lambda: synthetic.to_bf16_bits(t)})
+    ins, _ = oracle_inputs(wl, s)
+    ref = graph_oracle.run(wl.document, ins)
+    for position, mode in enumerate(graphs.SCHEMA_POINTWISE_MODES):
+        reference.assert_close(mode, s.output(1000 + position), ref[1000 + position], 1e-30, 2.0 ** -7)   # one bf16 step
+
+
 def _quantize_slabs(document, node_index, uid, storage, slabs):
     """The oracle's block-scale quantize over independent slabs of one operand (whole 32-element blocks each), on
     host threads; returns (codes, scales) joined in slab order."""

@@ -535,3 +535,52 @@ def test_device_side_generator_reproduces_the_host_stream():
     device = synthetic.normal_on_device(torch.device("cpu"), seed, uid, count, chunk=1 << 12).view(torch.uint16).numpy()
     assert np.array_equal(host, device)
     assert np.array_equal(synthetic.normal_on_device(torch.device("cpu"), seed, uid, 1000, bf16=False).numpy(), synthetic.normal(seed, uid, 1000))
+
+
+# ---- POINTWISE: every mode of the schema -----------------------------------------------
+
+def _oracle_pointwise(mode_name, a, b, t, **scalars):
+    import pointwise_reference as reference
+    rows, columns = a.shape
+    out = np.full((rows, columns), -99.0, np.float32)
+    count = dfgpu.pointwise_input_count(mode_name)
+    oracle.pointwise_general(dfgpu.PW_MODES[mode_name], tensor(F32, [rows, columns]), a,
+                             tensor(F32, [columns]) if count >= 2 else None, b if count >= 2 else None,
+                             tensor(F32, [rows, 1]) if count >= 3 else None, t if count >= 3 else None,
+                             tensor(F32, [rows, columns]), out,
+                             lower=reference.RELU_LOWER, upper=reference.RELU_UPPER, slope=reference.RELU_SLOPE,
+                             elu_alpha=reference.ELU_ALPHA, softplus_beta=reference.SOFTPLUS_BETA, swish_beta=reference.SWISH_BETA,
+                             axis=1, **scalars)
+    return out
+
+
+@pytest.mark.parametrize("mode_name", dfgpu.PW_MODE_NAMES)
+def test_pointwise_modes_match_the_reference_test_oracle(mode_name):
+    """test/Compiler/FoundationalMathOpsTest.cpp:440-545,617-640: the reference's inputs, formulas and tolerance."""
+    import pointwise_reference as reference
+    a, b, t = reference.A.reshape(2, 3).copy(), reference.B.copy(), reference.T.copy()
+    out = _oracle_pointwise(mode_name, a, b, t)
+    reference.assert_close(mode_name, out, reference.expected(mode_name, a, b, t))
+
+
+@pytest.mark.parametrize("mode_name", dfgpu.PW_MODE_NAMES)
+def test_pointwise_modes_on_seeded_values(mode_name):
+    """The same formulas on 64 x 48 seeded values in [-3, 3] (both signs, fractions, exact ties and zeros)."""
+    import pointwise_reference as reference
+    rng = np.random.default_rng(1234)
+    a = np.round(rng.uniform(-3.0, 3.0, (64, 48)) * 8).astype(np.float32) / 8   # multiples of 1/8: ties between A and B exist
+    b = np.round(rng.uniform(-3.0, 3.0, 48) * 8).astype(np.float32) / 8
+    t = (rng.integers(0, 2, 64) * rng.uniform(-2.0, 2.0, 64)).astype(np.float32)
+    a[0, :4] = [0.0, -0.0, 2.5, -2.5]
+    b[:4] = [0.0, 1.0, 2.5, 0.0]
+    out = _oracle_pointwise(mode_name, a, b, t)
+    # f32 rounding of |values| up to e^3 and 3^3 stays far inside the reference's tolerance; POW's poles give infinities
+    reference.assert_close(mode_name, out, reference.expected(mode_name, a, b, t))
+
+
+def test_pointwise_softplus_is_stable_for_large_inputs():
+    """test/Compiler/FoundationalMathOpsTest.cpp:169-186 (single_softplus_graph): max(x, 0) + log1p-form, no overflow."""
+    x = np.array([1000.0, -1000.0], np.float32)
+    out = np.zeros(2, np.float32)
+    oracle.pointwise_general(dfgpu.PW_MODES["SOFTPLUS_FWD"], tensor(F32, [2]), x, None, None, None, None, tensor(F32, [2]), out)
+    assert out[0] == 1000.0 and out[1] == 0.0
