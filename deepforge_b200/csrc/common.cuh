@@ -240,14 +240,16 @@ __device__ __forceinline__ void store_from_f32(void* data, int dtype, int64_t of
     }
 }
 
-// arith.maximumf / minimumf: NaN if either side is NaN (CUDA's fmaxf drops NaN).
+// arith.maximumf / minimumf: NaN if either side is NaN (CUDA's fmaxf drops NaN), -0 below +0: one max.NaN / min.NaN.
 __device__ __forceinline__ float maximum_nan(float a, float b) {
-    float m = fmaxf(a, b);
-    return (a != a || b != b) ? __int_as_float(0x7fc00000) : m;
+    float m;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(m) : "f"(a), "f"(b));
+    return m;
 }
 __device__ __forceinline__ float minimum_nan(float a, float b) {
-    float m = fminf(a, b);
-    return (a != a || b != b) ? __int_as_float(0x7fc00000) : m;
+    float m;
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(m) : "f"(a), "f"(b));
+    return m;
 }
 
 // RELU_FWD with clips and lower slope:

@@ -1,10 +1,11 @@
 // POINTWISE nodes that could not be fused into a contraction's epilogue.
 // One thread per output element, trailing-axis NumPy broadcast, f32 math.
 //
-// Two families of kernels. ADD / MUL / SUB / RELU_FWD / IDENTITY (the modes the contractions' callers use on large
-// tensors) keep kernels of their own, with nothing else in them. Every other mode of the reference's pointwise_result
-// (lib/Compiler/FoundationalGraph.cpp:2581-2955) goes through pointwise_value below: the same expression, one
-// separately rounded f32 operation per step, with CUDA's full-precision math functions (no fast-math intrinsics).
+// Every mode of the reference's pointwise_result (lib/Compiler/FoundationalGraph.cpp:2581-2955) goes through
+// pointwise_value below: the same expression, one separately rounded f32 operation per step, with CUDA's full-precision
+// math functions (no fast-math intrinsics). Packed tensors of equal shape (f32 or bf16) take the kernel of four values per
+// load; anything else (broadcast, strides, mixed storage types, three inputs, GEN_INDEX) one element per thread, where
+// ADD / MUL / SUB / RELU_FWD / IDENTITY keep a kernel with nothing else in it.
 #include "common.cuh"
 
 namespace dfgpu {
@@ -22,7 +23,7 @@ struct PointwiseScalars {
     int axis;
 };
 
-__host__ __device__ __forceinline__ int input_count(int mode) {
+__host__ __device__ constexpr int input_count(int mode) {
     if (mode < 0 || mode >= DFGPU_PW_MODE_COUNT) return 0;
     if (mode == DFGPU_PW_BINARY_SELECT) return 3;
     switch (mode) {
@@ -51,9 +52,8 @@ __device__ __forceinline__ float pointwise_value(int mode, float x, float y, flo
         case DFGPU_PW_SUB: return __fsub_rn(x, y);
         case DFGPU_PW_DIV: return __fdiv_rn(x, y);
         case DFGPU_PW_ADD_SQUARE: return __fadd_rn(x, __fmul_rn(y, y));
-        // equal operands (the two zeros among them): -0 orders below +0, so the minimum ORs the sign bits and the maximum ANDs them
-        case DFGPU_PW_MIN: return x == y ? __uint_as_float(__float_as_uint(x) | __float_as_uint(y)) : minimum_nan(x, y);
-        case DFGPU_PW_MAX: return x == y ? __uint_as_float(__float_as_uint(x) & __float_as_uint(y)) : maximum_nan(x, y);
+        case DFGPU_PW_MIN: return minimum_nan(x, y);
+        case DFGPU_PW_MAX: return maximum_nan(x, y);
         case DFGPU_PW_MOD: return fmodf(x, y);
         case DFGPU_PW_POW: return powf(x, y);
         case DFGPU_PW_SQRT: return __fsqrt_rn(x);
@@ -190,43 +190,68 @@ __device__ __forceinline__ void store4<float>(void* p, int64_t i, const float (&
 }
 template <>
 __device__ __forceinline__ void store4<__nv_bfloat16>(void* p, int64_t i, const float (&v)[4]) {
-    uint32_t lo = f32_to_bf16_bits(v[0]) | (static_cast<uint32_t>(f32_to_bf16_bits(v[1])) << 16);
-    uint32_t hi = f32_to_bf16_bits(v[2]) | (static_cast<uint32_t>(f32_to_bf16_bits(v[3])) << 16);
-    *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p) + i) = make_uint2(lo, hi);
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);  // the same rounding, two values per cvt
+    *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p) + i) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
 }
 
-template <typename TA, typename TB, typename TO>
-__global__ void pointwise_packed_kernel(const void* a, const void* b, void* out, int mode, float lower, float upper,
-                                        float slope, int64_t total) {
-    int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
-    if (i >= total) return;
-    float x[4], y[4] = {0.f, 0.f, 0.f, 0.f}, r[4];
-    load4<TA>(a, i, x);
-    if (mode == DFGPU_PW_ADD || mode == DFGPU_PW_MUL || mode == DFGPU_PW_SUB) load4<TB>(b, i, y);
+// Quads of four values a thread keeps in flight: its U quads lie one block-width apart, so that each of a warp's loads
+// stays contiguous; every load is issued before the first value is used. 32 bytes per thread and operand: with 8 (bf16)
+// or 16 (f32) the loads in flight of a full SM do not cover the latency of HBM.
+template <typename T> struct QuadsInFlight;
+template <> struct QuadsInFlight<float> { static constexpr int value = 2; };
+template <> struct QuadsInFlight<__nv_bfloat16> { static constexpr int value = 4; };
+
+constexpr int kPackedThreads = 256;
+
+template <typename T>
+unsigned packed_grid(int64_t total) {
+    const int64_t per_block = static_cast<int64_t>(kPackedThreads) * 4 * QuadsInFlight<T>::value;
+    return static_cast<unsigned>((total + per_block - 1) / per_block);
+}
+
+// Every mode with one or two inputs (not GEN_INDEX, which needs the element's index). The mode is looked at once per
+// thread: the switch leads into a body compiled for that mode alone. A switch per value made every mode cost ~50 us on
+// 25.7 M values whatever its arithmetic, and even a five-way switch per value held bf16 RELU_FWD at 37 us (23 us here).
+template <typename T, int MODE>
+__device__ __forceinline__ void packed_body(const void* a, const void* b, void* out, const PointwiseScalars& s, int64_t total) {
+    constexpr int U = QuadsInFlight<T>::value;
+    constexpr bool binary = input_count(MODE) == 2;
+    const int64_t first = (static_cast<int64_t>(blockIdx.x) * U * kPackedThreads + threadIdx.x) * 4;
+    float x[U][4], y[U][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        switch (mode) {
-            case DFGPU_PW_ADD: r[j] = __fadd_rn(x[j], y[j]); break;
-            case DFGPU_PW_MUL: r[j] = __fmul_rn(x[j], y[j]); break;
-            case DFGPU_PW_SUB: r[j] = __fsub_rn(x[j], y[j]); break;
-            case DFGPU_PW_RELU_FWD: r[j] = relu_forward(x[j], lower, upper, slope); break;
-            default: r[j] = x[j]; break;
+    for (int u = 0; u < U; ++u) {
+        const int64_t i = first + static_cast<int64_t>(u) * kPackedThreads * 4;
+        if (i < total) {
+            load4<T>(a, i, x[u]);
+            if (binary) load4<T>(b, i, y[u]);
         }
     }
-    store4<TO>(out, i, r);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int64_t i = first + static_cast<int64_t>(u) * kPackedThreads * 4;
+        if (i >= total) break;
+        float r[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) r[j] = pointwise_value(MODE, x[u][j], binary ? y[u][j] : 0.0f, 0.0f, s, 0);
+        store4<T>(out, i, r);
+    }
 }
 
-// The same for the general modes with one or two inputs (not GEN_INDEX, which needs the element's index).
+#define DFGPU_PW_EVERY_MODE(X)                                                                                              \
+    X(0) X(1) X(2) X(3) X(4) X(5) X(6) X(7) X(8) X(9) X(10) X(11) X(12) X(13) X(14) X(15) X(16) X(17) X(18) X(19) X(20) X(21) \
+    X(22) X(23) X(24) X(25) X(26) X(27) X(28) X(29) X(30) X(31) X(32) X(33) X(34) X(35) X(36) X(37) X(38) X(39) X(40) X(41)  \
+    X(42) X(43) X(44) X(45) X(46) X(47) X(48) X(49)
+static_assert(DFGPU_PW_MODE_COUNT == 50, "DFGPU_PW_EVERY_MODE lists every mode");
+
 template <typename T>
-__global__ void pointwise_general_packed_kernel(const void* a, const void* b, void* out, int mode, PointwiseScalars s, int64_t total) {
-    int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
-    if (i >= total) return;
-    float x[4], y[4] = {0.f, 0.f, 0.f, 0.f}, r[4];
-    load4<T>(a, i, x);
-    if (input_count(mode) == 2) load4<T>(b, i, y);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) r[j] = pointwise_value(mode, x[j], y[j], 0.0f, s, 0);
-    store4<T>(out, i, r);
+__global__ void __launch_bounds__(kPackedThreads)
+pointwise_general_packed_kernel(const void* a, const void* b, void* out, int mode, PointwiseScalars s, int64_t total) {
+    switch (mode) {
+#define DFGPU_PW_CASE(M) case M: packed_body<T, M>(a, b, out, s, total); break;
+        DFGPU_PW_EVERY_MODE(DFGPU_PW_CASE)
+#undef DFGPU_PW_CASE
+        default: break;
+    }
 }
 
 bool same_packed(const dfgpu_tensor& a, const dfgpu_tensor& b) {
@@ -297,27 +322,16 @@ extern "C" int dfgpu_pointwise(const dfgpu_pointwise_params* p, void* const* ten
                   aligned16(tensors[0]) && aligned16(tensors[2]) && (!binary || aligned16(tensors[1]));
     bool f32_all = p->in0.dtype == DFGPU_F32 && p->out.dtype == DFGPU_F32 && (!binary || p->in1.dtype == DFGPU_F32);
     bool bf16_all = p->in0.dtype == DFGPU_BF16 && p->out.dtype == DFGPU_BF16 && (!binary || p->in1.dtype == DFGPU_BF16);
-    if (!simple_mode(p->mode)) {
-        PointwiseScalars s{p->relu_lower, p->relu_upper, p->relu_slope, p->elu_alpha, p->softplus_beta, p->swish_beta, p->axis};
-        if (packed && (f32_all || bf16_all) && inputs <= 2 && p->mode != DFGPU_PW_GEN_INDEX) {
-            unsigned grid = static_cast<unsigned>((total / 4 + 255) / 256);
-            if (f32_all) pointwise_general_packed_kernel<float><<<grid, 256, 0, stream>>>(tensors[0], tensors[1], tensors[2], p->mode, s, total);
-            else pointwise_general_packed_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(tensors[0], tensors[1], tensors[2], p->mode, s, total);
-        } else {
-            unsigned grid = static_cast<unsigned>((total + 255) / 256);
-            pointwise_general_kernel<<<grid, 256, 0, stream>>>(tensors[0], tensors[1], inputs >= 3 ? tensors[3] : nullptr, tensors[2],
-                                                               make_view(p->in0), inputs >= 2 ? make_view(p->in1) : make_view(p->in0),
-                                                               inputs >= 3 ? make_view(p->in2) : make_view(p->in0), make_view(p->out),
-                                                               p->mode, s, total);
-        }
-        return check_launch("POINTWISE");
-    }
-    if (packed && (f32_all || bf16_all)) {
-        unsigned grid = static_cast<unsigned>((total / 4 + 255) / 256);
-        if (f32_all)
-            pointwise_packed_kernel<float, float, float><<<grid, 256, 0, stream>>>(tensors[0], tensors[1], tensors[2], p->mode, p->relu_lower, p->relu_upper, p->relu_slope, total);
-        else
-            pointwise_packed_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>(tensors[0], tensors[1], tensors[2], p->mode, p->relu_lower, p->relu_upper, p->relu_slope, total);
+    PointwiseScalars s{p->relu_lower, p->relu_upper, p->relu_slope, p->elu_alpha, p->softplus_beta, p->swish_beta, p->axis};
+    if (packed && (f32_all || bf16_all) && inputs <= 2 && p->mode != DFGPU_PW_GEN_INDEX) {
+        if (f32_all) pointwise_general_packed_kernel<float><<<packed_grid<float>(total), kPackedThreads, 0, stream>>>(tensors[0], tensors[1], tensors[2], p->mode, s, total);
+        else pointwise_general_packed_kernel<__nv_bfloat16><<<packed_grid<__nv_bfloat16>(total), kPackedThreads, 0, stream>>>(tensors[0], tensors[1], tensors[2], p->mode, s, total);
+    } else if (!simple_mode(p->mode)) {
+        unsigned grid = static_cast<unsigned>((total + 255) / 256);
+        pointwise_general_kernel<<<grid, 256, 0, stream>>>(tensors[0], tensors[1], inputs >= 3 ? tensors[3] : nullptr, tensors[2],
+                                                           make_view(p->in0), inputs >= 2 ? make_view(p->in1) : make_view(p->in0),
+                                                           inputs >= 3 ? make_view(p->in2) : make_view(p->in0), make_view(p->out),
+                                                           p->mode, s, total);
     } else {
         unsigned grid = static_cast<unsigned>((total + 255) / 256);
         pointwise_kernel<<<grid, 256, 0, stream>>>(tensors[0], tensors[1], tensors[2], make_view(p->in0),
