@@ -71,4 +71,5 @@ extern "C" const char* dfgpu_last_error(void) { return dfgpu::g_error; }
 // 6: DFGPU_CONV_UMMA_F32X3_CLUSTER, DFGPU_MATMUL_UMMA_F32X3_CLUSTER. 7: dfgpu_conv_params gained the depth attributes (rank 5).
 // 8: dfgpu_sdpa_params gained dropout (21 pointers). 9: DFGPU_FP4, DFGPU_I4.
 // 10: dfgpu_pointwise_params gained in2, elu_alpha, softplus_beta, swish_beta, axis (every POINTWISE mode; 4 pointers).
-extern "C" int dfgpu_abi_version(void) { return 10; }
+// 11: dfgpu_constants (graph-owned pass-by-value scalars).
+extern "C" int dfgpu_abi_version(void) { return 11; }

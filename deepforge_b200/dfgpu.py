@@ -103,6 +103,13 @@ class PointwiseParams(C.Structure):
                 setattr(self, name, 1.0)
 
 
+MAX_CONSTANTS = 16
+
+
+class ConstantsParams(C.Structure):
+    _fields_ = [("count", C.c_int32), ("reserved", C.c_int32), ("bits", C.c_uint64 * MAX_CONSTANTS), ("bytes", C.c_int32 * MAX_CONSTANTS)]
+
+
 class ConvParams(C.Structure):
     _fields_ = [("x", Tensor), ("w", Tensor), ("y", Tensor), ("extra", Tensor * 2),
                 ("pre_pad", C.c_int64 * 2), ("post_pad", C.c_int64 * 2), ("stride", C.c_int64 * 2),
@@ -143,7 +150,7 @@ EXPORTS = [
     "dfgpu_query_block_scale_quantize", "dfgpu_block_scale_quantize",
     "dfgpu_query_block_scale_quantize_pair", "dfgpu_block_scale_quantize_pair",
     "dfgpu_query_block_scale_dequantize", "dfgpu_block_scale_dequantize",
-    "dfgpu_query_pointwise", "dfgpu_pointwise", "dfgpu_pointwise_input_count",
+    "dfgpu_query_pointwise", "dfgpu_pointwise", "dfgpu_pointwise_input_count", "dfgpu_query_constants", "dfgpu_constants",
     "dfgpu_query_conv_fprop", "dfgpu_conv_fprop",
     "dfgpu_query_conv_fprop_pair", "dfgpu_conv_fprop_pair",
     "dfgpu_query_matmul", "dfgpu_matmul",
@@ -216,6 +223,10 @@ def block_scale_quantize_pair(params, first, second, stream=None):
 
 def block_scale_dequantize(params, x, scale, y, scratch=None, stream=None):
     _call("dfgpu_block_scale_dequantize", params, [x, scale, y], scratch, stream)
+
+
+def constants(params, destinations, stream=None):
+    _call("dfgpu_constants", params, list(destinations), None, stream)
 
 
 def pointwise(params, in0, in1, out, scratch=None, stream=None, in2=0):

@@ -55,6 +55,20 @@ def pointwise_node(name: str, mode: str, in0: int, out: int, in1: Optional[int] 
             "elu_alpha": elu_alpha, "softplus_beta": softplus_beta}
 
 
+def scalar_pointwise(embedded: Optional[dict] = None, mode: str = "ADD", data_type: str = "FLOAT") -> dict:
+    """X [2, 3] (mode) ALPHA [1, 1] -> Y, ALPHA passed by value: the reference's runtime-scalar graph
+    (test/Compiler/FoundationalMathOpsTest.cpp:190-211) and, with `embedded` = the Frontend's scalar variant
+    {"index": ..., "value": ...}, its embedded-scalar graph (:213-221), where ALPHA is a constant the graph owns."""
+    tensors = [tensor(601, "X", [2, 3]), tensor(602, "ALPHA", [1, 1], data_type), tensor(603, "Y", [2, 3])]
+    tensors[1]["is_pass_by_value"] = True
+    doc = document("runtime-scalar-pointwise" if embedded is None else "embedded-scalar-pointwise",
+                   [pointwise_node("runtime_scalar_add", mode, 601, 603, 602)], tensors, graph_uid=2106 if embedded is None else 2107)
+    if embedded is not None:
+        doc["tensors"]["602"]["pass_by_value"] = dict(embedded)
+        doc["pass_by_values"] = {"602": dict(embedded)}
+    return doc
+
+
 def pointwise_all_modes(dims: Sequence[int] = (2, 3), data_type: str = "FLOAT") -> dict:
     """One POINTWISE node per mode of the schema, in the shape of the reference's own test graph
     (test/Compiler/FoundationalMathOpsTest.cpp:126-167): UID 101 A [rows, columns], 102 B [columns] (broadcast over rows),

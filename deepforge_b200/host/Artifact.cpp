@@ -113,16 +113,21 @@ std::uint32_t params_size_of(KernelOp op) {
         case KernelOp::kMatmulFp8: return params_size<dfgpu_matmul_fp8_params>();
         case KernelOp::kConvFpropPair: return params_size<dfgpu_conv_pair_params>();
         case KernelOp::kBlockScaleQuantizePair: return params_size<dfgpu_bsq_pair_params>();
+        case KernelOp::kConstants: return params_size<dfgpu_constants_params>();
     }
     return 0;
 }
 
-// Number of tensor slots of each dfgpu entry point.
-std::size_t tensor_slots(KernelOp op) {
-    switch (op) {
+// Number of tensor slots of each dfgpu entry point (the constants launch: one per constant).
+std::size_t tensor_slots(KernelStep const& step) {
+    switch (step.op) {
+        case KernelOp::kConstants: {
+            auto const count = std::get<dfgpu_constants_params>(step.params).count;
+            return count > 0 ? static_cast<std::size_t>(count) : 0;
+        }
         case KernelOp::kBlockScaleQuantize: return 3;
         case KernelOp::kBlockScaleDequantize: return 3;
-        case KernelOp::kPointwise: return 3;
+        case KernelOp::kPointwise: return 4;
         case KernelOp::kConvFprop: return 5;
         case KernelOp::kMatmul: return 7;
         case KernelOp::kSdpaForward: return 21;
@@ -133,7 +138,7 @@ std::size_t tensor_slots(KernelOp op) {
     return 0;
 }
 
-constexpr std::uint32_t kLastOp = static_cast<std::uint32_t>(KernelOp::kBlockScaleQuantizePair);
+constexpr std::uint32_t kLastOp = static_cast<std::uint32_t>(KernelOp::kConstants);
 
 void write_binding(Writer& w, TensorBinding const& binding) {
     w.u32(static_cast<std::uint32_t>(binding.kind));
@@ -184,6 +189,12 @@ bool params_in_range(KernelParams const& params) {
         using T = std::decay_t<decltype(p)>;
         if constexpr (std::is_same_v<T, dfgpu_bsq_params>) return tensor_in_range(p.x) && tensor_in_range(p.y) && tensor_in_range(p.scale);
         else if constexpr (std::is_same_v<T, dfgpu_bsd_params>) return tensor_in_range(p.x) && tensor_in_range(p.y) && tensor_in_range(p.scale);
+        else if constexpr (std::is_same_v<T, dfgpu_constants_params>) {
+            if (p.count < 1 || p.count > DFGPU_MAX_CONSTANTS) return false;
+            for (int i = 0; i < p.count; ++i)
+                if (p.bytes[i] != 2 && p.bytes[i] != 4 && p.bytes[i] != 8) return false;
+            return true;
+        }
         else if constexpr (std::is_same_v<T, dfgpu_pointwise_params>) return tensor_in_range(p.in0) && tensor_in_range(p.in1) && tensor_in_range(p.out) && tensor_in_range(p.in2);
         else if constexpr (std::is_same_v<T, dfgpu_conv_params>)
             return tensor_in_range(p.x) && tensor_in_range(p.w) && tensor_in_range(p.y) && tensor_in_range(p.extra[0]) && tensor_in_range(p.extra[1]) &&
@@ -251,11 +262,12 @@ Status read_plan(Reader& r, ArtifactInfo& info) {
             case KernelOp::kMatmulFp8: step.params = read_params<dfgpu_matmul_fp8_params>(r); break;
             case KernelOp::kConvFpropPair: step.params = read_params<dfgpu_conv_pair_params>(r); break;
             case KernelOp::kBlockScaleQuantizePair: step.params = read_params<dfgpu_bsq_pair_params>(r); break;
+            case KernelOp::kConstants: step.params = read_params<dfgpu_constants_params>(r); break;
         }
         if (!r.ok || !params_in_range(step.params)) return bad("kernel plan: tensor descriptor out of range");
         if (step.kernel < 0 || step.launches < 1 || step.launches > 16) return bad("kernel plan: kernel id or launch count out of range");
         std::uint32_t tensors = r.u32();
-        if (!r.ok || tensors != tensor_slots(step.op)) return bad("kernel plan: wrong number of tensor bindings for the entry point");
+        if (!r.ok || tensors != tensor_slots(step)) return bad("kernel plan: wrong number of tensor bindings for the entry point");
         step.tensors.resize(tensors);
         for (auto& binding : step.tensors)
             if (!read_binding(r, binding)) return bad("kernel plan: tensor binding out of range");
@@ -299,6 +311,7 @@ dfgpu_tensor const* slot_descriptor(KernelStep const& step, std::size_t slot) {
         using T = std::decay_t<decltype(p)>;
         if constexpr (std::is_same_v<T, dfgpu_bsq_params>) { dfgpu_tensor const* t[] = {&p.x, &p.y, &p.scale}; return slot < 3 ? t[slot] : nullptr; }
         else if constexpr (std::is_same_v<T, dfgpu_bsd_params>) { dfgpu_tensor const* t[] = {&p.x, &p.scale, &p.y}; return slot < 3 ? t[slot] : nullptr; }
+        else if constexpr (std::is_same_v<T, dfgpu_constants_params>) return nullptr;
         else if constexpr (std::is_same_v<T, dfgpu_pointwise_params>) { dfgpu_tensor const* t[] = {&p.in0, &p.in1, &p.out, &p.in2}; return slot < 4 ? t[slot] : nullptr; }
         else if constexpr (std::is_same_v<T, dfgpu_conv_params>) { dfgpu_tensor const* t[] = {&p.x, &p.w, &p.y, &p.extra[0], &p.extra[1]}; return slot < 5 ? t[slot] : nullptr; }
         else if constexpr (std::is_same_v<T, dfgpu_matmul_params>) { dfgpu_tensor const* t[] = {&p.a, &p.b, &p.c, &p.a_scale, &p.b_scale, &p.extra[0], &p.extra[1]}; return slot < 7 ? t[slot] : nullptr; }
@@ -328,7 +341,7 @@ Status check_bindings(ArtifactInfo const& info) {
         for (std::size_t slot = 0; slot < step.tensors.size(); ++slot) {
             auto const& binding = step.tensors[slot];
             if (binding.kind == TensorBinding::Kind::kAbsent) continue;
-            std::uint64_t span = 4;
+            std::uint64_t span = step.op == KernelOp::kConstants ? 8 : 4;
             if (auto const* descriptor = slot_descriptor(step, slot)) {
                 if (descriptor->rank == 0) return bad("kernel plan: '" + step.label + "' binds a tensor its params block marks absent");
                 if (!descriptor_span(*descriptor, span)) return bad("kernel plan: '" + step.label + "' has a tensor descriptor without a storage span");
@@ -399,7 +412,7 @@ Status serialize_artifact(CompilationResult const& compilation, std::vector<std:
     if ((status = check_workspace(compilation.workspace)).is_bad()) return status;
     if (compilation.plan.steps.empty()) return invalid("plan", "an artifact needs at least one launch");
     for (auto const& step : compilation.plan.steps)
-        if (step.tensors.size() != tensor_slots(step.op)) return invalid("plan", "launch '" + step.label + "' has the wrong number of tensor bindings");
+        if (step.tensors.size() != tensor_slots(step)) return invalid("plan", "launch '" + step.label + "' has the wrong number of tensor bindings");
 
     Writer w;
     w.raw(kMagic, sizeof(kMagic));

@@ -13,6 +13,7 @@
 
 #include <algorithm>
 #include <array>
+#include <bit>
 #include <cfloat>
 #include <cmath>
 #include <map>
@@ -135,7 +136,8 @@ struct Lowering {
 
     TensorBinding bind(std::int64_t uid) const {
         TensorBinding binding;
-        binding.kind = tensor(uid).is_virtual ? TensorBinding::Kind::kWorkspace : TensorBinding::Kind::kArgument;
+        // a virtual tensor and a graph-owned constant both live in the workspace; everything else is the caller's
+        binding.kind = tensor(uid).is_virtual || tensor(uid).pass_by_value ? TensorBinding::Kind::kWorkspace : TensorBinding::Kind::kArgument;
         binding.uid = uid;
         return binding;
     }
@@ -545,8 +547,7 @@ Status lower_pointwise(Lowering& low, std::size_t index) {
     step.op = KernelOp::kPointwise;
     step.label = node.name;
     step.nodes = {index};
-    step.tensors = {low.bind(*in0), in1 ? low.bind(*in1) : TensorBinding{}, low.bind(*out)};
-    if (in2) step.tensors.push_back(low.bind(*in2));
+    step.tensors = {low.bind(*in0), in1 ? low.bind(*in1) : TensorBinding{}, low.bind(*out), in2 ? low.bind(*in2) : TensorBinding{}};
     step.params = params;
     low.plan.steps.push_back(std::move(step));
     return Status::ok();
@@ -1025,6 +1026,75 @@ bool single_conv_metadata(SerializedGraph const& graph, CompileOptions const& op
     return true;
 }
 
+// A correctly rounded double -> binary16 / bfloat16 (round to nearest even), as the reference narrows an embedded
+// HALF / BFLOAT16 scalar from the JSON number (FloatAttr::get(type, double), lib/Compiler/FoundationalGraph.cpp:2193-2200).
+std::uint16_t narrow_double(double value, int exponent_bits, int mantissa_bits) {
+    auto const bits = std::bit_cast<std::uint64_t>(value);
+    auto const sign = static_cast<std::uint16_t>((bits >> 63) << (exponent_bits + mantissa_bits));
+    auto const exponent_mask = static_cast<std::uint16_t>(((1u << exponent_bits) - 1u) << mantissa_bits);
+    if (std::isnan(value)) return static_cast<std::uint16_t>(sign | exponent_mask | (1u << (mantissa_bits - 1)));
+    double const magnitude = std::fabs(value);
+    int const bias = (1 << (exponent_bits - 1)) - 1;
+    if (std::isinf(value)) return static_cast<std::uint16_t>(sign | exponent_mask);
+    if (magnitude == 0.0) return sign;
+    int exponent = 0;
+    (void)std::frexp(magnitude, &exponent);          // magnitude = f * 2^exponent, f in [0.5, 1)
+    int unbiased = std::max(exponent - 1, 1 - bias);  // subnormals share the smallest normal exponent
+    // magnitude / 2^(unbiased - mantissa_bits) is exact in double for every finite input; nearbyint rounds to even
+    double const scaled = std::nearbyint(std::ldexp(magnitude, mantissa_bits - unbiased));
+    auto mantissa = static_cast<std::uint64_t>(scaled);  // in [0, 2^(mantissa_bits + 1)]
+    std::uint64_t encoded = 0;
+    if (mantissa < (1ull << mantissa_bits)) encoded = mantissa;  // subnormal (or zero after rounding)
+    else encoded = (static_cast<std::uint64_t>(unbiased + bias - 1) << mantissa_bits) + mantissa;  // a carry into 2^(m+1) bumps the exponent by itself
+    if (encoded >= exponent_mask) encoded = exponent_mask;  // overflow rounds to infinity
+    return static_cast<std::uint16_t>(sign | encoded);
+}
+
+// The stored bits of an embedded scalar, as its tensor's data type holds the value (pass_by_value_initializer,
+// lib/Compiler/FoundationalGraph.cpp:2165-2214).
+void constant_bits(TensorDesc const& tensor, std::uint64_t& bits, std::int32_t& bytes) {
+    auto const& scalar = *tensor.pass_by_value;
+    switch (scalar.kind) {
+        case import::PassByValueKind::kInt64: bits = static_cast<std::uint64_t>(std::get<std::int64_t>(scalar.value)); bytes = 8; break;
+        case import::PassByValueKind::kInt32: bits = static_cast<std::uint32_t>(std::get<std::int32_t>(scalar.value)); bytes = 4; break;
+        case import::PassByValueKind::kFloat32: bits = std::get<std::uint32_t>(scalar.value); bytes = 4; break;
+        case import::PassByValueKind::kFloat64: bits = std::get<std::uint64_t>(scalar.value); bytes = 8; break;
+        case import::PassByValueKind::kFloat16: bits = narrow_double(std::bit_cast<double>(std::get<std::uint64_t>(scalar.value)), 5, 10); bytes = 2; break;
+        case import::PassByValueKind::kBFloat16: bits = narrow_double(std::bit_cast<double>(std::get<std::uint64_t>(scalar.value)), 8, 7); bytes = 2; break;
+    }
+}
+
+// Graph-owned constants that some launch reads are written into their workspace slots by launches at the head of the
+// plan (DFGPU_MAX_CONSTANTS each): their lifetime then runs from the first step to their last reader.
+void materialise_constants(Lowering& low) {
+    std::set<std::int64_t> wanted;
+    for (auto const& step : low.plan.steps)
+        for (auto const& binding : step.tensors)
+            if (binding.kind == TensorBinding::Kind::kWorkspace && low.tensor(binding.uid).pass_by_value) wanted.insert(binding.uid);
+    std::vector<KernelStep> head;
+    KernelStep fill;
+    auto flush = [&] {
+        if (fill.tensors.empty()) return;
+        fill.op = KernelOp::kConstants;
+        fill.label = "constants";
+        head.push_back(std::move(fill));
+        fill = KernelStep{};
+    };
+    dfgpu_constants_params params{};
+    for (auto uid : wanted) {
+        constant_bits(low.tensor(uid), params.bits[params.count], params.bytes[params.count]);
+        ++params.count;
+        fill.tensors.push_back(low.bind(uid));
+        fill.params = params;
+        if (params.count == DFGPU_MAX_CONSTANTS) {
+            flush();
+            params = dfgpu_constants_params{};
+        }
+    }
+    flush();
+    low.plan.steps.insert(low.plan.steps.begin(), std::make_move_iterator(head.begin()), std::make_move_iterator(head.end()));
+}
+
 // Alignment the resolved kernel's launcher demands of the pointer in tensor slot `slot` (0: no demand of its own).
 // The TMA-fed kernels read and write 16-byte units and have no narrower fallback (the block-scale launchers do).
 std::uint64_t kernel_alignment(KernelStep const& step, std::size_t slot) {
@@ -1061,6 +1131,7 @@ Status query_kernel_step(KernelStep& step, std::int64_t& scratch_bytes) {
         case KernelOp::kMatmulFp8: code = dfgpu_query_matmul_fp8(&std::get<dfgpu_matmul_fp8_params>(step.params), &info); break;
         case KernelOp::kConvFpropPair: code = dfgpu_query_conv_fprop_pair(&std::get<dfgpu_conv_pair_params>(step.params), &info); break;
         case KernelOp::kBlockScaleQuantizePair: code = dfgpu_query_block_scale_quantize_pair(&std::get<dfgpu_bsq_pair_params>(step.params), &info); break;
+        case KernelOp::kConstants: code = dfgpu_query_constants(&std::get<dfgpu_constants_params>(step.params), &info); break;
     }
     if (code != 0) return Status::failure(static_cast<ErrorCode>(code), step.label, dfgpu_last_error());
     step.kernel = info.kernel;
@@ -1081,6 +1152,7 @@ char const* kernel_op_name(KernelOp op) {
         case KernelOp::kMatmulFp8: return "matmul_fp8";
         case KernelOp::kConvFpropPair: return "conv_fprop_pair";
         case KernelOp::kBlockScaleQuantizePair: return "block_scale_quantize_pair";
+        case KernelOp::kConstants: return "constants";
     }
     return "?";
 }
@@ -1119,6 +1191,20 @@ Status compile_graph(SerializedGraph const& graph, CompileOptions const& options
     }
     for (auto const& [uid, tensor] : graph.tensors)
         if (tensor.is_virtual && !low.producer.count(uid)) return fail(ErrorCode::kInvalidValue, "tensors." + std::to_string(uid), "virtual tensor has no producer");
+    // pass-by-value scalars (validate_tensor, lib/Compiler/FoundationalGraph.cpp:411-490; input-only, :1870-1876)
+    for (auto const& [uid, tensor] : graph.tensors) {
+        if (!tensor.is_pass_by_value) continue;
+        auto const path = "tensors." + std::to_string(uid);
+        switch (tensor.data_type) {
+            case DataType::kInt64: case DataType::kInt32: case DataType::kFloat16: case DataType::kFloat32: case DataType::kFloat64: case DataType::kBFloat16: break;
+            default: return fail(ErrorCode::kUnsupportedDataType, path, "runtime pass-by-value scalar type is outside the cuDNN Frontend scalar set");
+        }
+        if (tensor.is_virtual || tensor.ragged_offset_uid || tensor.ragged_offset_name || tensor.reordering_type != "NONE")
+            return fail(ErrorCode::kUnsupportedOperation, path, "pass-by-value requires an external plain tensor");
+        if (!std::all_of(tensor.dim.begin(), tensor.dim.end(), [](std::int64_t extent) { return extent == 1; }))
+            return fail(ErrorCode::kUnsupportedOperation, path, "pass-by-value requires every dimension to equal one");
+        if (low.producer.count(uid)) return fail(ErrorCode::kUnsupportedOperation, path, "pass-by-value tensors are input-only");
+    }
 
     // dequantize nodes that a later MATMUL will absorb must not be emitted on their own:
     // decide that first, by lowering MATMULs' operand fusion lazily in node order.
@@ -1156,12 +1242,13 @@ Status compile_graph(SerializedGraph const& graph, CompileOptions const& options
     split_virtual_tensors(low);
     fuse_convolution_pairs(low);
     fuse_quantize_pairs(low);
+    materialise_constants(low);
 
     // argument table: ascending UID, non-virtual tensors only
     Conv2DCompileMetadata metadata;
     metadata.function_name = options.foundational_function_name;
     for (auto const& [uid, tensor] : graph.tensors) {
-        if (tensor.is_virtual) continue;
+        if (tensor.is_virtual || tensor.pass_by_value) continue;  // a graph-owned constant is no argument: a pointer passed for it is ignored
         TensorArgumentMetadata argument;
         argument.uid = uid;
         argument.name = tensor.name;

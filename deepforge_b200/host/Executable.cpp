@@ -175,6 +175,7 @@ Status Executable::run_steps(std::int64_t first, std::int64_t last, VariantPack&
         switch (step.op) {
             case KernelOp::kBlockScaleQuantize: code = dfgpu_block_scale_quantize(&std::get<dfgpu_bsq_params>(step.params), pointers.data(), scratch, stream); break;
             case KernelOp::kBlockScaleDequantize: code = dfgpu_block_scale_dequantize(&std::get<dfgpu_bsd_params>(step.params), pointers.data(), scratch, stream); break;
+            case KernelOp::kConstants: code = dfgpu_constants(&std::get<dfgpu_constants_params>(step.params), pointers.data(), scratch, stream); break;
             case KernelOp::kPointwise: code = dfgpu_pointwise(&std::get<dfgpu_pointwise_params>(step.params), pointers.data(), scratch, stream); break;
             case KernelOp::kConvFprop: {
                 // bit 1 of `reserved` (set by the lowering) promises that the kernel launched just before this one is the

@@ -11,6 +11,8 @@
 
 #include <algorithm>
 #include <array>
+#include <bit>
+#include <charconv>
 #include <fstream>
 #include <limits>
 #include <set>
@@ -162,6 +164,98 @@ Status read_int_array(Json const& value, std::string const& path, std::vector<st
     return Status::ok();
 }
 
+std::optional<PassByValueKind> pass_by_value_kind(DataType type) {
+    switch (type) {
+        case DataType::kInt64: return PassByValueKind::kInt64;
+        case DataType::kInt32: return PassByValueKind::kInt32;
+        case DataType::kFloat16: return PassByValueKind::kFloat16;
+        case DataType::kFloat32: return PassByValueKind::kFloat32;
+        case DataType::kFloat64: return PassByValueKind::kFloat64;
+        case DataType::kBFloat16: return PassByValueKind::kBFloat16;
+        default: return std::nullopt;
+    }
+}
+
+// {"index": variant index, "value": ...} (lib/Import/SerializedGraphImporter.cpp:190-268): the index must be the one of
+// the tensor's data type; INT64 / INT32 values are integers, FLOAT is its bit pattern as 8 hexadecimal digits, HALF /
+// DOUBLE / BFLOAT16 are JSON numbers.
+Status parse_pass_by_value(Json const& value, DataType tensor_type, std::string const& path, PassByValueScalar& out) {
+    if (!value.is_object()) return fail(ErrorCode::kInvalidFieldType, path, "expected Frontend scalar variant object");
+    if (value.size() != 2 || !value.contains("index") || !value.contains("value"))
+        return fail(ErrorCode::kInvalidValue, path, "Frontend scalar variant requires only index and value");
+    std::int64_t index = 0;
+    if (!read_int(value["index"], index)) return fail(ErrorCode::kInvalidFieldType, join(path, "index"), "expected integer");
+    if (index < 0 || index > 5) return fail(ErrorCode::kInvalidValue, join(path, "index"), "Frontend scalar variant index must be in [0, 5]");
+    auto const expected = pass_by_value_kind(tensor_type);
+    if (!expected || static_cast<std::int64_t>(*expected) != index)
+        return fail(ErrorCode::kInvalidValue, join(path, "index"), "Frontend scalar variant type does not match tensor data_type");
+    out.kind = *expected;
+    auto const& scalar = value["value"];
+    switch (*expected) {
+        case PassByValueKind::kInt64: {
+            std::int64_t integer = 0;
+            if (!read_int(scalar, integer)) return fail(ErrorCode::kInvalidFieldType, join(path, "value"), "expected integer");
+            out.value = integer;
+            return Status::ok();
+        }
+        case PassByValueKind::kInt32: {
+            std::int64_t integer = 0;
+            if (!read_int(scalar, integer)) return fail(ErrorCode::kInvalidFieldType, join(path, "value"), "expected integer");
+            if (integer < std::numeric_limits<std::int32_t>::min() || integer > std::numeric_limits<std::int32_t>::max())
+                return fail(ErrorCode::kInvalidValue, join(path, "value"), "Frontend INT32 scalar is out of range");
+            out.value = static_cast<std::int32_t>(integer);
+            return Status::ok();
+        }
+        case PassByValueKind::kFloat32: {
+            if (!scalar.is_string()) return fail(ErrorCode::kInvalidFieldType, join(path, "value"), "Frontend FLOAT scalar requires an 8-digit hexadecimal bit pattern");
+            auto const text = scalar.get<std::string>();
+            std::uint32_t bits = 0;
+            auto const parsed = std::from_chars(text.data(), text.data() + text.size(), bits, 16);
+            if (text.size() != 8 || parsed.ec != std::errc{} || parsed.ptr != text.data() + text.size())
+                return fail(ErrorCode::kInvalidValue, join(path, "value"), "Frontend FLOAT scalar requires exactly 8 hexadecimal digits");
+            out.value = bits;
+            return Status::ok();
+        }
+        default:
+            if (!scalar.is_number()) return fail(ErrorCode::kInvalidFieldType, join(path, "value"), "Frontend floating scalar requires a numeric value");
+            out.value = std::bit_cast<std::uint64_t>(scalar.get<double>());
+            return Status::ok();
+    }
+}
+
+// The root map "pass_by_values" repeats every embedded payload under its tensor's UID
+// (lib/Import/SerializedGraphImporter.cpp:860-925): both sides must hold the same scalars.
+Status validate_pass_by_values(Json const& root, SerializedGraph const& graph) {
+    auto const values = root.find("pass_by_values");
+    if (values == root.end()) {
+        for (auto const& [uid, tensor] : graph.tensors)
+            if (tensor.pass_by_value) return fail(ErrorCode::kMissingField, "pass_by_values", "embedded scalar payload requires the Frontend root map");
+        return Status::ok();
+    }
+    if (!values->is_object()) return fail(ErrorCode::kInvalidFieldType, "pass_by_values", "expected object keyed by tensor UID");
+    std::set<std::int64_t> seen;
+    for (auto it = values->begin(); it != values->end(); ++it) {
+        auto const path = join("pass_by_values", it.key());
+        std::int64_t uid = 0;
+        auto const& key = it.key();
+        auto const parsed = std::from_chars(key.data(), key.data() + key.size(), uid);
+        if (key.empty() || parsed.ec != std::errc{} || parsed.ptr != key.data() + key.size() || std::to_string(uid) != key)
+            return fail(ErrorCode::kInvalidValue, path, "root scalar key must be a canonical decimal int64 UID");
+        auto const tensor = graph.tensors.find(uid);
+        if (tensor == graph.tensors.end()) return fail(ErrorCode::kMissingUid, path, "root scalar UID has no tensor descriptor");
+        if (!tensor->second.pass_by_value) return fail(ErrorCode::kInvalidValue, path, "root scalar UID has no matching tensor payload");
+        PassByValueScalar scalar;
+        auto status = parse_pass_by_value(it.value(), tensor->second.data_type, path, scalar);
+        if (status.is_bad()) return status;
+        if (scalar != *tensor->second.pass_by_value) return fail(ErrorCode::kInvalidValue, path, "root and tensor scalar payloads differ");
+        seen.insert(uid);
+    }
+    for (auto const& [uid, tensor] : graph.tensors)
+        if (tensor.pass_by_value && !seen.count(uid))
+            return fail(ErrorCode::kMissingField, join("pass_by_values", std::to_string(uid)), "tensor scalar payload has no matching root entry");
+    return Status::ok();
+}
+
 Status parse_tensor(Json const& value, std::string const& path, TensorDesc& tensor) {
     if (!value.is_object()) return fail(ErrorCode::kInvalidFieldType, path, "expected tensor object");
     constexpr std::array<std::string_view, 12> fields{{"name", "data_type", "dim", "stride", "is_virtual", "pass_by_value", "is_pass_by_value",
@@ -199,11 +293,6 @@ Status parse_tensor(Json const& value, std::string const& path, TensorDesc& tens
         if (!value[field].is_boolean()) return fail(ErrorCode::kInvalidFieldType, join(path, field), "expected boolean");
         *target = value[field].get<bool>();
     }
-    if (value["pass_by_value"].is_number()) tensor.pass_by_value = value["pass_by_value"].get<double>();
-    else if (!value["pass_by_value"].is_null()) return fail(ErrorCode::kInvalidFieldType, join(path, "pass_by_value"), "expected number or null");
-    if (tensor.is_pass_by_value != tensor.pass_by_value.has_value())
-        return fail(ErrorCode::kInvalidValue, join(path, "pass_by_value"), "is_pass_by_value and pass_by_value disagree");
-    if (tensor.is_pass_by_value) return fail(ErrorCode::kUnsupportedExecutionMetadata, join(path, "pass_by_value"), "pass-by-value tensors are not executable on this backend");
     if (!value["reordering_type"].is_string()) return fail(ErrorCode::kInvalidFieldType, join(path, "reordering_type"), "expected string");
     tensor.reordering_type = value["reordering_type"].get<std::string>();
     if (tensor.reordering_type != "NONE" && tensor.reordering_type != "F8_128x4")
@@ -211,6 +300,14 @@ Status parse_tensor(Json const& value, std::string const& path, TensorDesc& tens
     if (!read_int(value["uid"], tensor.uid)) return fail(ErrorCode::kInvalidFieldType, join(path, "uid"), "expected integer");
     if (!value["uid_assigned"].is_boolean()) return fail(ErrorCode::kInvalidFieldType, join(path, "uid_assigned"), "expected boolean");
     if (!value["uid_assigned"].get<bool>()) return fail(ErrorCode::kMissingUid, join(path, "uid_assigned"), "tensor has no assigned UID");
+    if (!value["pass_by_value"].is_null()) {
+        PassByValueScalar payload;
+        auto payload_status = parse_pass_by_value(value["pass_by_value"], tensor.data_type, join(path, "pass_by_value"), payload);
+        if (payload_status.is_bad()) return payload_status;
+        tensor.pass_by_value = payload;
+    }
+    if (tensor.pass_by_value && !tensor.is_pass_by_value)
+        return fail(ErrorCode::kInvalidValue, join(path, "is_pass_by_value"), "scalar payload requires is_pass_by_value=true");
     // lib/Import/SerializedGraphImporter.cpp:687-711: both or neither
     if (auto it = value.find("ragged_offset_uid"); it != value.end() && !it->is_null()) {
         std::int64_t offsets = 0;
@@ -355,6 +452,8 @@ Status validate_document(Json const& root, SerializedGraph& graph) {
         if (!graph.tensors.emplace(tensor.uid, std::move(tensor)).second) return fail(ErrorCode::kDuplicateUid, path, "tensor UID is used twice");
     }
     if (graph.tensors.empty()) return fail(ErrorCode::kInvalidValue, "tensors", "graph has no tensors");
+    status = validate_pass_by_values(root, graph);
+    if (status.is_bad()) return status;
 
     auto const& nodes = root["nodes"];
     if (!nodes.is_array()) return fail(ErrorCode::kInvalidFieldType, "nodes", "expected array");
@@ -385,15 +484,20 @@ Status validate_document(Json const& root, SerializedGraph& graph) {
     for (auto const& [uid, tensor] : graph.tensors)
         if (tensor.ragged_offset_uid && used.count(uid)) used.insert(*tensor.ragged_offset_uid);
     for (auto const& [uid, tensor] : graph.tensors)
-        if (!used.count(uid)) return fail(ErrorCode::kInvalidValue, "tensors." + std::to_string(uid), "tensor is not referenced by any node");
+        if (!used.count(uid) && !tensor.pass_by_value)  // (a graph may carry embedded scalars that no node reads)
+            return fail(ErrorCode::kInvalidValue, "tensors." + std::to_string(uid), "tensor is not referenced by any node");
 
-    for (auto field : {"workspace_modifications", "variant_pack_replacements", "pass_by_values", "tensors_to_dump"}) {
+    for (auto field : {"workspace_modifications", "variant_pack_replacements", "tensors_to_dump"}) {
         status = expect_empty(root, field);
         if (status.is_bad()) return status;
     }
     // The single-node convolution graph is pinned harder than a DAG, as in the reference: no dynamic
     // shapes, no shape overrides, no Frontend-owned workspace.
     const bool single_conv = graph.nodes.size() == 1 && graph.nodes.front().tag == OperationTag::kConvFprop;
+    if (single_conv)  // lib/Import/SerializedGraphImporter.cpp:1667-1672
+        for (auto const& [uid, tensor] : graph.tensors)
+            if (tensor.is_pass_by_value)
+                return fail(ErrorCode::kUnsupportedExecutionMetadata, "tensors." + std::to_string(uid) + ".is_pass_by_value", "the single-node convolution graph does not accept pass-by-value tensors");
     if (single_conv && graph.context.is_dynamic_shape_enabled.value_or(false))
         return fail(ErrorCode::kUnsupportedExecutionMetadata, "context.is_dynamic_shape_enabled", "the single-node convolution graph has static shapes");
     if (single_conv && graph.context.is_override_shape_enabled.value_or(false))

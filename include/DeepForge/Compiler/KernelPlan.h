@@ -13,16 +13,17 @@
 
 namespace deepforge::compiler {
 
-enum class KernelOp : std::uint8_t { kBlockScaleQuantize, kBlockScaleDequantize, kPointwise, kConvFprop, kMatmul, kSdpaForward, kMatmulFp8, kConvFpropPair, kBlockScaleQuantizePair };
+enum class KernelOp : std::uint8_t { kBlockScaleQuantize, kBlockScaleDequantize, kPointwise, kConvFprop, kMatmul, kSdpaForward, kMatmulFp8, kConvFpropPair, kBlockScaleQuantizePair, kConstants };
 
 struct TensorBinding {
     enum class Kind : std::uint8_t { kAbsent, kArgument, kWorkspace } kind = Kind::kAbsent;
     std::int64_t uid = 0;            // kArgument: variant-pack UID; kWorkspace: the virtual tensor's UID
-    std::uint64_t offset = 0;        // kWorkspace: byte offset into the workspace
+    std::uint64_t offset = 0;        // kWorkspace: byte offset into the workspace (a virtual tensor, or a graph-owned constant)
 };
 
 using KernelParams = std::variant<dfgpu_bsq_params, dfgpu_bsd_params, dfgpu_pointwise_params, dfgpu_conv_params,
-                                  dfgpu_matmul_params, dfgpu_sdpa_params, dfgpu_matmul_fp8_params, dfgpu_conv_pair_params, dfgpu_bsq_pair_params>;
+                                  dfgpu_matmul_params, dfgpu_sdpa_params, dfgpu_matmul_fp8_params, dfgpu_conv_pair_params, dfgpu_bsq_pair_params,
+                                  dfgpu_constants_params>;
 
 struct KernelStep {
     KernelOp op = KernelOp::kPointwise;

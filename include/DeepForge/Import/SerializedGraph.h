@@ -46,6 +46,20 @@ enum class OperationTag : std::uint8_t {
 };
 [[nodiscard]] std::string_view operation_tag_name(OperationTag tag) noexcept;
 
+// The Frontend's scalar variant for a graph-owned constant (reference: include/DeepForge/Import/SerializedGraph.h:104-123).
+// The kind's number is the variant index the serializer writes.
+enum class PassByValueKind : std::uint8_t { kInt64 = 0, kInt32 = 1, kFloat16 = 2, kFloat32 = 3, kFloat64 = 4, kBFloat16 = 5 };
+
+struct PassByValueScalar {
+    // FLOAT: the f32 bit pattern (uint32). HALF / DOUBLE / BFLOAT16: the bits of the JSON number as a double (uint64),
+    // narrowed to the tensor's type where the constant is materialised.
+    using Storage = std::variant<std::int64_t, std::int32_t, std::uint32_t, std::uint64_t>;
+    PassByValueKind kind = PassByValueKind::kFloat32;
+    Storage value = std::uint32_t{0};
+
+    bool operator==(PassByValueScalar const&) const = default;
+};
+
 struct TensorDesc {
     std::int64_t uid = 0;
     std::string name;
@@ -53,8 +67,10 @@ struct TensorDesc {
     std::vector<std::int64_t> dim;
     std::vector<std::int64_t> stride;
     bool is_virtual = false;
+    // is_pass_by_value without a payload: a one-element argument the caller passes like any other tensor. With a
+    // payload: a constant the graph owns, absent from the argument table (a pointer the caller passes for it is ignored).
     bool is_pass_by_value = false;
-    std::optional<double> pass_by_value;
+    std::optional<PassByValueScalar> pass_by_value;
     std::string reordering_type = "NONE";
     // Ragged batch-prefix storage (reference: include/DeepForge/Import/SerializedGraph.h:136-137): entry (b, ...) of the
     // tensor lies at offsets[b] + the inner strides. Executable here for SDPA page tables only (compact page tables).

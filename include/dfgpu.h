@@ -137,6 +137,22 @@ typedef struct dfgpu_bsd_params {
 int dfgpu_query_block_scale_dequantize(const dfgpu_bsd_params*, dfgpu_plan_info*);
 int dfgpu_block_scale_dequantize(const dfgpu_bsd_params*, void* const* tensors, void* scratch, void* stream);
 
+/* ---- graph-owned constants --------------------------------------------------
+   Writes the embedded pass-by-value scalars of a graph (a tensor descriptor
+   with a `pass_by_value` payload, lib/Compiler/FoundationalGraph.cpp:2165-2250)
+   into their slots: bits[i], as the tensor's type stores the value, goes to
+   tensors[i] (bytes[i] = 2, 4 or 8; the pointer aligned to as many). One
+   launch of one warp. */
+#define DFGPU_MAX_CONSTANTS 16
+typedef struct dfgpu_constants_params {
+    int32_t count;
+    int32_t reserved;
+    uint64_t bits[DFGPU_MAX_CONSTANTS];
+    int32_t bytes[DFGPU_MAX_CONSTANTS];
+} dfgpu_constants_params;
+int dfgpu_query_constants(const dfgpu_constants_params*, dfgpu_plan_info*);
+int dfgpu_constants(const dfgpu_constants_params*, void* const* tensors, void* scratch, void* stream);
+
 /* ---- POINTWISE --------------------------------------------------------------
    Replaces emit_pointwise (lib/Compiler/FoundationalGraph.cpp:2957-3004) with
    every mode of pointwise_result (:2581-2955; the mode list is

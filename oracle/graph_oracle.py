@@ -58,6 +58,23 @@ def _alloc(t: dict) -> np.ndarray:
     return np.zeros(_span(t), dtype=np.int32 if t["data_type"] == "INT32" else np.uint8)
 
 
+def embedded_scalar(described: dict) -> np.ndarray:
+    """The value of an embedded pass-by-value payload as the tensor's type holds it, widened to f32 for the floating
+    types (lib/Compiler/FoundationalGraph.cpp:2165-2214: FLOAT is an f32 bit pattern, HALF / BFLOAT16 / DOUBLE a JSON
+    number narrowed to the type, INT32 / INT64 integers)."""
+    payload, data_type = described["pass_by_value"], described["data_type"]
+    if data_type == "FLOAT":
+        return np.array([int(payload["value"], 16)], np.uint32).view(np.float32)
+    if data_type == "HALF":
+        return np.array([payload["value"]], np.float64).astype(np.float16).astype(np.float32)
+    if data_type == "BFLOAT16":
+        from deepforge_b200 import synthetic
+        return synthetic.bf16_bits_to_f32(synthetic.to_bf16_bits(np.array([payload["value"]], np.float32)))
+    if data_type == "DOUBLE":
+        return np.array([payload["value"]], np.float64)
+    return np.array([payload["value"]], np.int32 if data_type == "INT32" else np.int64)
+
+
 def run(document: dict, inputs: Dict[int, np.ndarray], matmul_rows: Optional[Tuple[int, int]] = None,
         sdpa_bh: Optional[Tuple[int, int]] = None, sdpa_q_step: int = 1, storage_inputs: Optional[Dict[int, np.ndarray]] = None,
         round_to_bf16: Tuple[int, ...] = (), threads: int = 1) -> Dict[int, np.ndarray]:
@@ -69,6 +86,9 @@ def run(document: dict, inputs: Dict[int, np.ndarray], matmul_rows: Optional[Tup
     computed by one thread with the same arithmetic, so the results do not depend on it."""
     tensors = {int(k): v for k, v in document["tensors"].items()}
     values: Dict[int, np.ndarray] = dict(inputs)
+    for uid, described in tensors.items():   # graph-owned constants win over anything the caller passes for their UID
+        if described.get("pass_by_value") is not None:
+            values[uid] = embedded_scalar(described)
     for node in document["nodes"]:
         tag = node["tag"]
         ins, outs = node["inputs"], node["outputs"]

@@ -23,7 +23,7 @@ def test_kernel_library_exports_every_declared_symbol():
     for name in names:
         assert hasattr(lib, name), name
     assert sorted(dfgpu.EXPORTS) == names
-    assert lib.dfgpu_abi_version() == 10
+    assert lib.dfgpu_abi_version() == 11
 
 
 def test_struct_layout_matches_header():
@@ -36,6 +36,7 @@ def test_struct_layout_matches_header():
     assert C.sizeof(dfgpu.BsdParams) == 504
     assert C.sizeof(dfgpu.BsqPairParams) == 896
     assert C.sizeof(dfgpu.PointwiseParams) == 608
+    assert C.sizeof(dfgpu.ConstantsParams) == 200
     assert C.sizeof(dfgpu.ConvParams) == 928
     assert C.sizeof(dfgpu.ConvPairParams) == 1856
     assert C.sizeof(dfgpu.MatmulParams) == 1144
@@ -50,13 +51,13 @@ def test_struct_sizes_agree_with_the_c_compiler(tmp_path):
     if not shutil.which("gcc"):
         import pytest
         pytest.skip("no C compiler")
-    names = ["tensor", "plan_info", "epilogue_step", "bsq_params", "bsd_params", "pointwise_params", "conv_params", "matmul_params", "matmul_fp8_params", "sdpa_params", "conv_pair_params", "bsq_pair_params"]
+    names = ["tensor", "plan_info", "epilogue_step", "bsq_params", "bsd_params", "constants_params", "pointwise_params", "conv_params", "matmul_params", "matmul_fp8_params", "sdpa_params", "conv_pair_params", "bsq_pair_params"]
     source = tmp_path / "sizes.c"
     source.write_text('#include <stdio.h>\n#include "dfgpu.h"\nint main(void){' + "".join(f'printf("%zu\\n", sizeof(dfgpu_{n}));' for n in names) + "return 0;}\n")
     binary = tmp_path / "sizes"
     subprocess.run(["gcc", "-I", str(ROOT / "include"), str(source), "-o", str(binary)], check=True)
     sizes = [int(v) for v in subprocess.run([str(binary)], check=True, capture_output=True, text=True).stdout.split()]
-    mirrors = [dfgpu.Tensor, dfgpu.PlanInfo, dfgpu.EpilogueStep, dfgpu.BsqParams, dfgpu.BsdParams, dfgpu.PointwiseParams, dfgpu.ConvParams,
+    mirrors = [dfgpu.Tensor, dfgpu.PlanInfo, dfgpu.EpilogueStep, dfgpu.BsqParams, dfgpu.BsdParams, dfgpu.ConstantsParams, dfgpu.PointwiseParams, dfgpu.ConvParams,
                dfgpu.MatmulParams, dfgpu.MatmulFp8Params, dfgpu.SdpaParams, dfgpu.ConvPairParams, dfgpu.BsqPairParams]
     assert sizes == [C.sizeof(m) for m in mirrors]
 

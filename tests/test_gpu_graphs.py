@@ -401,6 +401,49 @@ def test_every_pointwise_mode_through_the_executable():
         reference.assert_close(mode, s.output(1000 + position), ref[1000 + position], 1e-30, 2.0 ** -7)   # one bf16 step
 
 
+def test_pass_by_value_scalars_reproduce_the_reference_known_answers():
+    """test/Compiler/FoundationalMathOpsTest.cpp:190-221,662-800. A runtime scalar stays an ordinary one-element read
+    argument (2.5 added to 1..6 gives 3.5..8.5); an embedded scalar (FLOAT bits 40200000 = 2.5) is owned by the graph:
+    absent from the argument table, written into the workspace by the plan's first launch, the same answers, a
+    pointer the caller passes for its UID is ignored, and an artifact carries it."""
+    from deepforge_b200 import graphs
+    x = np.array([1, 2, 3, 4, 5, 6], np.float32)
+    expected = [3.5, 4.5, 5.5, 6.5, 7.5, 8.5]
+
+    def session(doc, inputs):
+        wl = workloads.Workload(name="scalar", config=0, document=doc, description={}, metric="", unit="GB/s", flops=1.0, bytes=1.0, bound="hbm",
+                                inputs=inputs, outputs=[603])
+        s = harness.Session(wl)
+        s.run()
+        return wl, s
+
+    wl, s = session(graphs.scalar_pointwise(), {601: lambda: x.copy(), 602: lambda: np.array([2.5], np.float32)})
+    scalar = [a for a in s.exe.arguments() if a["uid"] == 602][0]
+    assert scalar["access"] == "read" and scalar["size_bytes"] == 4 and s.exe.workspace_size == 0
+    assert s.output(603).tolist() == expected
+
+    embedded = graphs.scalar_pointwise({"index": 3, "value": "40200000"})
+    wl, s = session(embedded, {601: lambda: x.copy()})
+    assert [a["uid"] for a in s.exe.arguments()] == [601, 603] and s.exe.workspace_size == 64 and s.exe.launch_count == 2
+    assert s.output(603).tolist() == expected
+    ins, _ = oracle_inputs(wl, s)
+    assert graph_oracle.run(wl.document, ins)[603].tolist() == expected
+    # the caller cannot override a graph-owned scalar
+    wl, s = session(embedded, {601: lambda: x.copy(), 602: lambda: np.array([100.0], np.float32)})
+    assert s.output(603).tolist() == expected
+    # and the artifact carries it
+    loaded = runtime.load_artifact(s.exe.serialize())
+    assert loaded.plan_text() == s.exe.plan_text() and [a["uid"] for a in loaded.arguments()] == [601, 603]
+    s.dev[603].zero_()
+    s.exe = loaded
+    s.run()
+    assert s.output(603).tolist() == expected
+    # HALF and BFLOAT16 payloads are JSON numbers, narrowed to the tensor's type: x * 1.5 and x * -2
+    for data_type, payload, factor in (("HALF", {"index": 2, "value": 1.5}, 1.5), ("BFLOAT16", {"index": 5, "value": -2.0}, -2.0)):
+        wl, s = session(graphs.scalar_pointwise(payload, mode="MUL", data_type=data_type), {601: lambda: x.copy()})
+        assert s.output(603).tolist() == (x * factor).tolist()
+
+
 def _quantize_slabs(document, node_index, uid, storage, slabs):
     """The oracle's block-scale quantize over independent slabs of one operand (whole 32-element blocks each), on
     host threads; returns (codes, scales) joined in slab order."""

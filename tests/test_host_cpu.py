@@ -65,7 +65,8 @@ def test_accepts_reference_fixture_shape_and_all_five_configs():
     (lambda d: d["tensors"]["1"].update(uid_assigned=False), 13),
     (lambda d: d["tensors"]["1"].update(dim=[1, 3, 0, 5]), 15),
     (lambda d: d["tensors"]["1"].update(dim=[2 ** 40, 2 ** 40, 5, 5]), 16),
-    (lambda d: d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value=1.0), 11),
+    (lambda d: d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value=1.0), 7),   # a payload is the Frontend's scalar variant object
+    (lambda d: d["tensors"]["1"].update(is_pass_by_value=True), 11),                      # the single-node convolution takes no scalars
     (lambda d: d["tensors"]["1"].update(reordering_type="F16x16"), 8),
     (lambda d: d["nodes"][0].update(tag="LAYER_NORM"), 9),
     (lambda d: d["nodes"][0].update(tag="NOT_A_TAG"), 9),
@@ -322,3 +323,53 @@ def test_compact_page_tables_plan_metadata_and_rejections(tmp_path):
         with pytest.raises(DeepForgeError) as error:
             runtime.compile_graph(broken)
         assert error.value.code == expected, error.value
+
+
+# ---- pass-by-value scalars (test/Compiler/FoundationalMathOpsTest.cpp:190-262,662-800) ---------------------
+
+def test_runtime_scalar_stays_an_ordinary_read_argument():
+    exe = runtime.compile_graph(graphs.scalar_pointwise())
+    scalar = [a for a in exe.arguments() if a["uid"] == 602][0]
+    assert scalar["access"] == "read" and scalar["size_bytes"] == 4
+    assert exe.workspace_size == 0 and exe.plan_text().splitlines() == ["0: pointwise kernel=1 launches=1 [runtime_scalar_add] uid601 uid602 uid603 -"]
+
+
+def test_embedded_scalar_is_graph_owned_and_survives_the_artifact():
+    exe = runtime.compile_graph(graphs.scalar_pointwise({"index": 3, "value": "40200000"}))
+    assert [a["uid"] for a in exe.arguments()] == [601, 603]          # absent from the public arguments
+    assert exe.workspace_size == 64
+    assert exe.plan_text().splitlines() == ["0: constants kernel=1 launches=1 [constants] ws+0(uid602)",
+                                            "1: pointwise kernel=1 launches=1 [runtime_scalar_add] uid601 ws+0(uid602) uid603 -"]
+    loaded = runtime.load_artifact(exe.serialize())
+    assert loaded.plan_text() == exe.plan_text() and loaded.arguments() == exe.arguments() and loaded.workspace_size == 64
+
+
+def test_every_embedded_scalar_type_is_accepted_and_unused_ones_cost_nothing():
+    """all_embedded_scalar_types_graph (:223-247): INT64, INT32, HALF, DOUBLE and BFLOAT16 payloads that no node reads."""
+    doc = graphs.scalar_pointwise({"index": 3, "value": "40200000"})
+    for uid, data_type, payload in ((604, "INT64", {"index": 0, "value": -7}), (605, "INT32", {"index": 1, "value": 7}),
+                                    (606, "HALF", {"index": 2, "value": 1.5}), (607, "DOUBLE", {"index": 4, "value": 1.25}),
+                                    (608, "BFLOAT16", {"index": 5, "value": -2.0})):
+        described = graphs.tensor(uid, "UNUSED_" + data_type, [1], data_type)
+        described.update(is_pass_by_value=True, pass_by_value=payload)
+        doc["tensors"][str(uid)] = described
+        doc["pass_by_values"][str(uid)] = payload
+    exe = runtime.compile_graph(doc)
+    assert [a["uid"] for a in exe.arguments()] == [601, 603] and exe.workspace_size == 64 and exe.launch_count == 2
+
+
+@pytest.mark.parametrize("change,expected", [
+    (lambda d: d["tensors"]["602"].update(dim=[1, 2], stride=[2, 1]), 20),            # every dimension must equal one
+    (lambda d: d["tensors"]["602"].update(data_type="FP8_E4M3"), 10),                 # outside the Frontend's scalar set
+    (lambda d: d["tensors"]["602"].update(is_virtual=True), 8),                        # virtual without a producer
+    (lambda d: d["tensors"]["603"].update(is_pass_by_value=True, dim=[1, 1], stride=[1, 1]), 20),   # input-only
+])
+def test_pass_by_value_rejections(change, expected):
+    doc = graphs.scalar_pointwise()
+    change(doc)
+    try:
+        runtime.compile_graph(doc)
+        code = 0
+    except DeepForgeError as error:
+        code = error.code
+    assert code == expected

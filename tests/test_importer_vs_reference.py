@@ -96,6 +96,10 @@ MODEL_DOCS = {
     "c3_f32_unaligned": graphs.c3_quantize_matmul(64, 96, 32, io="FLOAT", c_type="FLOAT"),
     "c4_noncausal_f32": graphs.c4_sdpa(2, 3, 40, 16, io="FLOAT", causal=False),
     "fp8_batched": graphs.matmul_fp8(4, 8, 4, c_type="FP8_E4M3", batch=(2, 3), b_k_major=True),
+    "scalar_runtime": graphs.scalar_pointwise(),
+    "scalar_embedded": graphs.scalar_pointwise({"index": 3, "value": "40200000"}),
+    "scalar_embedded_half": graphs.scalar_pointwise({"index": 2, "value": 1.5}, data_type="HALF"),
+    "pointwise_all_modes": graphs.pointwise_all_modes(),
 }
 
 
@@ -174,6 +178,26 @@ MUTATIONS = [
     lambda d: d.update(fe_workspace_size=64),
     lambda d: d.update(workspace_modifications={"1": [0, 1, 2]}),
     lambda d: d.update(variant_pack_replacements=[[1, 2]]),
+    # pass-by-value scalars (lib/Import/SerializedGraphImporter.cpp:190-268,670-686,860-925)
+    lambda d: d["tensors"]["1"].update(is_pass_by_value=True),
+    lambda d: d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value=1.0),
+    lambda d: d["tensors"]["1"].update(pass_by_value={"index": 3, "value": "40200000"}),
+    lambda d: d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value={"index": 3, "value": "40200000"}),
+    lambda d: (d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value={"index": 3, "value": "40200000"}),
+               d.update(pass_by_values={"1": {"index": 3, "value": "40200000"}})),
+    lambda d: (d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value={"index": 3, "value": "40200000"}),
+               d.update(pass_by_values={"1": {"index": 3, "value": "40200001"}})),
+    lambda d: (d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value={"index": 3, "value": "40200000"}),
+               d.update(pass_by_values={"01": {"index": 3, "value": "40200000"}})),
+    lambda d: d.update(pass_by_values={"77": {"index": 3, "value": "40200000"}}),
+    lambda d: d.update(pass_by_values={"1": {"index": 3, "value": "40200000"}}),
+    lambda d: d.update(pass_by_values=[1]),
+    lambda d: d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value={"index": 2, "value": 1.5}),
+    lambda d: d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value={"index": 3, "value": "4020000"}),
+    lambda d: d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value={"index": 3, "value": 2.5}),
+    lambda d: d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value={"index": 6, "value": 1}),
+    lambda d: d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value={"index": 3, "value": "40200000", "more": 1}),
+    lambda d: d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value=[3, "40200000"]),
 ]
 
 
