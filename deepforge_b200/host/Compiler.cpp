@@ -731,7 +731,7 @@ Status lower_sdpa(Lowering& low, std::size_t index) {
         const std::int64_t query_tiles = (params.q.dim[2] - 1) / 128 + 1, key_tiles = (params.s_kv - 1) / 128 + 1;
         if (t.dim != std::vector<std::int64_t>{params.q.dim[0], params.q.dim[1], query_tiles, (key_tiles + 7) / 8})
             return fail(ErrorCode::kInvalidShape, where + ".Block_mask", "block mask must have dimensions [B,Hq,ceil(Sq/128),ceil(ceil(Skv/128)/8)]");
-        if (t.is_virtual || t.reordering_type != "NONE") return fail(ErrorCode::kUnsupportedOperation, where + ".Block_mask", "block mask must be an external plain UINT8 tensor");
+        if (t.is_virtual || t.is_pass_by_value || t.reordering_type != "NONE") return fail(ErrorCode::kUnsupportedOperation, where + ".Block_mask", "block mask must be an external plain UINT8 tensor");
     }
     auto sink = port(node.inputs, "SINK_TOKEN");
     if (sink) {
@@ -739,7 +739,7 @@ Status lower_sdpa(Lowering& low, std::size_t index) {
         if ((status = low.describe(*sink, params.sink, where)).is_bad()) return status;
         auto const& t = low.tensor(*sink);
         if (t.dim != std::vector<std::int64_t>{1, params.q.dim[1], 1, 1}) return fail(ErrorCode::kInvalidShape, where + ".SINK_TOKEN", "sink token must have dimensions [1,Hq,1,1]");
-        if (t.is_virtual || t.reordering_type != "NONE" || t.data_type != DataType::kFloat32)
+        if (t.is_virtual || t.is_pass_by_value || t.reordering_type != "NONE" || t.data_type != DataType::kFloat32)  // lib/Compiler/SequenceGraph.cpp:570-576
             return fail(ErrorCode::kUnsupportedOperation, where + ".SINK_TOKEN", "sink token must be an external plain FLOAT tensor");
     }
     auto one_element = [](TensorDesc const& t) {
