@@ -372,6 +372,64 @@ Status parse_ports(Json const& node, std::string const& path, char const* field,
     return Status::ok();
 }
 
+constexpr std::array<std::string_view, 50> kPointwiseModes{{
+    "ADD", "MUL", "SQRT", "MAX", "MIN", "RELU_FWD", "TANH_FWD", "SIGMOID_FWD", "ELU_FWD", "GELU_FWD", "SOFTPLUS_FWD", "SWISH_FWD", "RELU_BWD",
+    "TANH_BWD", "SIGMOID_BWD", "ELU_BWD", "GELU_BWD", "SOFTPLUS_BWD", "SWISH_BWD", "ERF", "IDENTITY", "GELU_APPROX_TANH_BWD",
+    "GELU_APPROX_TANH_FWD", "GEN_INDEX", "BINARY_SELECT", "EXP", "LOG", "NEG", "MOD", "POW", "ABS", "CEIL", "COS", "FLOOR", "RSQRT", "SIN",
+    "LOGICAL_NOT", "TAN", "SUB", "ADD_SQUARE", "DIV", "CMP_EQ", "CMP_NEQ", "CMP_GT", "CMP_GE", "CMP_LT", "CMP_LE", "LOGICAL_AND", "LOGICAL_OR",
+    "RECIPROCAL"}};
+
+// Inputs a POINTWISE mode reads (lib/Import/Schema.cpp:353-377); 0 for a name outside the list.
+std::size_t pointwise_input_count(std::string_view mode) {
+    if (std::find(kPointwiseModes.begin(), kPointwiseModes.end(), mode) == kPointwiseModes.end()) return 0;
+    if (mode == "BINARY_SELECT") return 3;
+    constexpr std::array<std::string_view, 17> binary{{"ADD", "MUL", "DIV", "ADD_SQUARE", "SUB", "CMP_EQ", "CMP_NEQ", "CMP_GT", "CMP_GE", "CMP_LT", "CMP_LE",
+                                                       "LOGICAL_AND", "LOGICAL_OR", "MIN", "MAX", "MOD", "POW"}};
+    bool const backward = mode.size() > 4 && mode.substr(mode.size() - 4) == "_BWD";
+    return backward || std::find(binary.begin(), binary.end(), mode) != binary.end() ? 2 : 1;
+}
+
+bool fits_int32(Json const& value) {
+    std::int64_t integer = 0;
+    return read_int(value, integer) && integer >= std::numeric_limits<std::int32_t>::min() && integer <= std::numeric_limits<std::int32_t>::max();
+}
+
+// The value type every attribute of the executable tags must have (lib/Import/SerializedGraphImporter.cpp:1096-1192).
+bool attribute_value_is_valid(Json const& value, OperationTag tag, std::string_view name) {
+    auto one_of = [&](std::initializer_list<std::string_view> allowed, bool nullable) {
+        if (value.is_null()) return nullable;
+        if (!value.is_string()) return false;
+        auto const text = value.get<std::string>();
+        return std::find(allowed.begin(), allowed.end(), std::string_view(text)) != allowed.end();
+    };
+    auto integer = [](Json const& item) { return item.is_number_integer() || item.is_number_unsigned(); };
+    if (name == "compute_data_type" || name == "mma_core_mode") return value.is_null() || (value.is_string() && data_type_from_name(value.get<std::string>()).has_value());
+    if (name == "mode") {
+        if (tag != OperationTag::kPointwise) return one_of({"NONE", "GATHER", "SCATTER"}, false);
+        return value.is_string() && pointwise_input_count(value.get<std::string>()) != 0;
+    }
+    if (name == "math_mode") return one_of({"CONVOLUTION", "CROSS_CORRELATION"}, false);
+    if (name == "diagonal_alignment") return one_of({"TOP_LEFT", "BOTTOM_RIGHT"}, false);
+    if (name == "implementation") return one_of({"AUTO", "COMPOSITE", "UNIFIED"}, false);
+    if (name == "pre_padding" || name == "post_padding" || name == "stride" || name == "dilation")
+        return value.is_array() && std::all_of(value.begin(), value.end(), integer);
+    if (name == "block_size") {
+        if (tag == OperationTag::kBlockScaleDequantize) return value.is_array() && std::all_of(value.begin(), value.end(), fits_int32);
+        return value.is_null() || fits_int32(value);
+    }
+    if (name == "is_negative_scale" || name == "alibi_mask" || name == "padding_mask" || name == "is_deterministic_algorithm" || name == "is_mxfp8" ||
+        name == "unfuse_fma" || name == "is_deterministic")
+        return value.is_boolean();
+    if (name == "generate_stats" || name == "generate_index") return value.is_null() || value.is_boolean();
+    if (name == "max_seq_len_kv") return value.is_null() || fits_int32(value);
+    if (name == "axis" || name == "seed" || name == "left_bound" || name == "right_bound" || name == "max_total_seq_len_q" || name == "max_total_seq_len_kv")
+        return value.is_null() || integer(value);
+    if (name == "padding_value" || name == "relu_lower_clip" || name == "relu_upper_clip" || name == "relu_lower_clip_slope" || name == "swish_beta" ||
+        name == "elu_alpha" || name == "softplus_beta" || name == "dropout_probability" || name == "attn_scale_value" || name == "rescale_threshold")
+        return value.is_null() || value.is_number();
+    return true;  // an attribute the reference's table does not constrain
+}
+
 Status parse_node(Json const& node, std::string const& path, std::map<std::int64_t, TensorDesc> const& tensors, OperationDesc& operation) {
     if (!node.is_object()) return fail(ErrorCode::kInvalidFieldType, path, "expected node object");
     auto tag_it = node.find("tag");
@@ -403,10 +461,20 @@ Status parse_node(Json const& node, std::string const& path, std::map<std::int64
         bool known = std::find(schema->required.begin(), schema->required.end(), key) != schema->required.end() ||
                      std::find(schema->optional.begin(), schema->optional.end(), key) != schema->optional.end();
         if (!known) return fail(ErrorCode::kInvalidValue, join(path, key), "unknown attribute for this operation");
+        if (!attribute_value_is_valid(it.value(), schema->tag, key))
+            return fail(ErrorCode::kInvalidFieldType, join(path, key), "attribute has a value outside the pinned schema");
         AttributeValue attribute;
         status = to_attribute(it.value(), join(path, key), attribute);
         if (status.is_bad()) return status;
         operation.attributes[key] = std::move(attribute);
+    }
+    if (schema->tag == OperationTag::kPointwise) {  // lib/Import/SerializedGraphImporter.cpp:1325-1342
+        auto const expected = pointwise_input_count(node["mode"].get<std::string>());
+        if (operation.inputs.size() != expected || operation.outputs.size() != 1 || !operation.outputs.count("OUT_0"))
+            return fail(ErrorCode::kInvalidValue, path, "pointwise ports do not match mode arity");
+        for (std::size_t index = 0; index < expected; ++index)
+            if (!operation.inputs.count("IN_" + std::to_string(index)))
+                return fail(ErrorCode::kInvalidValue, join(path, "inputs"), "pointwise inputs must be contiguous from IN_0");
     }
     return Status::ok();
 }
@@ -484,8 +552,8 @@ Status validate_document(Json const& root, SerializedGraph& graph) {
     for (auto const& [uid, tensor] : graph.tensors)
         if (tensor.ragged_offset_uid && used.count(uid)) used.insert(*tensor.ragged_offset_uid);
     for (auto const& [uid, tensor] : graph.tensors)
-        if (!used.count(uid) && !tensor.pass_by_value)  // (a graph may carry embedded scalars that no node reads)
-            return fail(ErrorCode::kInvalidValue, "tensors." + std::to_string(uid), "tensor is not referenced by any node");
+        if (!used.count(uid) && tensor.is_virtual)  // (an external tensor, or an embedded scalar, that no node reads is legal)
+            return fail(ErrorCode::kInvalidValue, "tensors." + std::to_string(uid), "virtual tensor is not referenced by any node");
 
     for (auto field : {"workspace_modifications", "variant_pack_replacements", "tensors_to_dump"}) {
         status = expect_empty(root, field);
@@ -494,6 +562,7 @@ Status validate_document(Json const& root, SerializedGraph& graph) {
     // The single-node convolution graph is pinned harder than a DAG, as in the reference: no dynamic
     // shapes, no shape overrides, no Frontend-owned workspace.
     const bool single_conv = graph.nodes.size() == 1 && graph.nodes.front().tag == OperationTag::kConvFprop;
+    if (single_conv && graph.tensors.size() != 3) return fail(ErrorCode::kInvalidValue, "tensors", "the single-node convolution graph holds exactly its X, W and Y tensors");
     if (single_conv)  // lib/Import/SerializedGraphImporter.cpp:1667-1672
         for (auto const& [uid, tensor] : graph.tensors)
             if (tensor.is_pass_by_value)

@@ -198,7 +198,62 @@ MUTATIONS = [
     lambda d: d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value={"index": 6, "value": 1}),
     lambda d: d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value={"index": 3, "value": "40200000", "more": 1}),
     lambda d: d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value=[3, "40200000"]),
+    # tensors no node reads (legal in a DAG unless virtual) and the value types of node attributes (:1096-1192)
+    lambda d: d["tensors"].update({"99": graphs.tensor(99, "EXTRA", [4])}),
+    lambda d: d["tensors"].update({"99": graphs.tensor(99, "EXTRA", [4], virtual=True)}),
+    lambda d: d["nodes"][0].update(math_mode="CORRELATE"),
+    lambda d: d["nodes"][0].update(math_mode=None),
+    lambda d: d["nodes"][0].update(stride=[1, 1.5]),
+    lambda d: d["nodes"][0].update(pre_padding="x"),
+    lambda d: d["nodes"][0].update(compute_data_type="WIDE"),
+    lambda d: d["nodes"][0].update(compute_data_type=None),
+    lambda d: d["nodes"][1].update(mode="NOT_A_MODE"),
+    lambda d: d["nodes"][1].update(mode=None),
+    lambda d: d["nodes"][1].update(axis=1.5),
+    lambda d: d["nodes"][1].update(relu_lower_clip="x"),
+    lambda d: d["nodes"][1].update(softplus_beta=True),
+    lambda d: d["nodes"][1]["inputs"].update(IN_2=1),
+    lambda d: d["nodes"][1]["inputs"].pop("IN_1"),
+    lambda d: d["nodes"][1].update(mode="BINARY_SELECT"),
+    lambda d: d["nodes"][2].update(mode="TANH_BWD"),
 ]
+
+
+# the same for the attributes of the other executable tags
+ATTRIBUTE_MUTATIONS = [
+    ("c4", lambda d: d["nodes"][0].update(diagonal_alignment="CENTER")),
+    ("c4", lambda d: d["nodes"][0].update(diagonal_alignment=None)),
+    ("c4", lambda d: d["nodes"][0].update(padding_mask=None)),
+    ("c4", lambda d: d["nodes"][0].update(alibi_mask=1)),
+    ("c4", lambda d: d["nodes"][0].update(generate_stats=None)),
+    ("c4", lambda d: d["nodes"][0].update(generate_stats="yes")),
+    ("c4", lambda d: d["nodes"][0].update(attn_scale_value="1")),
+    ("c4", lambda d: d["nodes"][0].update(dropout_probability=True)),
+    ("c4", lambda d: d["nodes"][0].update(right_bound=0.5)),
+    ("c4", lambda d: d["nodes"][0].update(left_bound="0")),
+    ("c4", lambda d: d["nodes"][0].update(max_seq_len_kv=1 << 40)),
+    ("c4", lambda d: d["nodes"][0].update(mma_core_mode="FAST")),
+    ("c4", lambda d: d["nodes"][0].update(implementation="FUSED")),
+    ("c3", lambda d: d["nodes"][0].update(block_size=1 << 40)),
+    ("c3", lambda d: d["nodes"][0].update(block_size=[32])),
+    ("c3", lambda d: d["nodes"][0].update(axis="1")),
+    ("c3", lambda d: d["nodes"][2].update(block_size=32)),
+    ("c3", lambda d: d["nodes"][2].update(block_size=[1, 1 << 40])),
+    ("c3", lambda d: d["nodes"][2].update(is_negative_scale=None)),
+    ("c3", lambda d: d["nodes"][4].update(padding_value="0")),
+    ("c3", lambda d: d["nodes"][4].update(padding_value=None)),
+]
+
+
+@pytest.mark.parametrize("index", range(len(ATTRIBUTE_MUTATIONS)))
+def test_attribute_value_types_match_the_reference(index):
+    reference = _reference()
+    name, mutation = ATTRIBUTE_MUTATIONS[index]
+    doc = copy.deepcopy(DOCS[name])
+    mutation(doc)
+    expected = reference(doc)
+    assert _ours(doc)[0] == expected[0], expected[3]
+
 
 
 @pytest.mark.parametrize("index", range(len(MUTATIONS)))
@@ -208,7 +263,7 @@ def test_error_codes_match_the_reference(name, index):
     doc = copy.deepcopy(DOCS[name])
     try:
         MUTATIONS[index](doc)
-    except KeyError:
+    except (KeyError, IndexError):
         pytest.skip("mutation does not apply to this graph")
     expected = reference(doc)
     assert _ours(doc)[0] == expected[0], expected[3]
