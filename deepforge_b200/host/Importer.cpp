@@ -277,8 +277,9 @@ Status parse_tensor(Json const& value, std::string const& path, TensorDesc& tens
     if (status.is_bad()) return status;
     status = read_int_array(value["stride"], join(path, "stride"), tensor.stride);
     if (status.is_bad()) return status;
-    if (tensor.dim.empty() || tensor.dim.size() > 8 || tensor.dim.size() != tensor.stride.size())
-        return fail(ErrorCode::kInvalidShape, path, "dim and stride must have the same rank between 1 and 8");
+    // lib/Import/SerializedGraphImporter.cpp: ranks 1..64 parse (the kernels execute up to 8, which the lowering checks)
+    if (tensor.dim.empty() || tensor.dim.size() > 64) return fail(ErrorCode::kInvalidValue, join(path, "dim"), "tensor rank must be between 1 and 64");
+    if (tensor.dim.size() != tensor.stride.size()) return fail(ErrorCode::kInvalidValue, join(path, "stride"), "dimension and stride ranks must match");
     std::uint64_t count = 1;
     for (std::size_t axis = 0; axis < tensor.dim.size(); ++axis) {
         if (tensor.dim[axis] <= 0) return fail(ErrorCode::kInvalidShape, join(path, "dim"), "extents must be positive");
@@ -295,7 +296,7 @@ Status parse_tensor(Json const& value, std::string const& path, TensorDesc& tens
     }
     if (!value["reordering_type"].is_string()) return fail(ErrorCode::kInvalidFieldType, join(path, "reordering_type"), "expected string");
     tensor.reordering_type = value["reordering_type"].get<std::string>();
-    if (tensor.reordering_type != "NONE" && tensor.reordering_type != "F8_128x4")
+    if (tensor.reordering_type != "NONE" && tensor.reordering_type != "F8_128x4" && tensor.reordering_type != "INT8x32" && tensor.reordering_type != "F16x16")
         return fail(ErrorCode::kInvalidValue, join(path, "reordering_type"), "unknown reordering type");
     if (!read_int(value["uid"], tensor.uid)) return fail(ErrorCode::kInvalidFieldType, join(path, "uid"), "expected integer");
     if (!value["uid_assigned"].is_boolean()) return fail(ErrorCode::kInvalidFieldType, join(path, "uid_assigned"), "expected boolean");
@@ -365,6 +366,7 @@ Status parse_ports(Json const& node, std::string const& path, char const* field,
             return fail(ErrorCode::kInvalidValue, join(join(path, field), port.key()), "unknown port for this operation");
         if (port->is_null()) continue;
         std::int64_t uid = 0;
+        if (port->is_string()) return fail(ErrorCode::kMissingUid, join(join(path, field), port.key()), "name references are not accepted; use an integer UID");
         if (!read_int(port.value(), uid)) return fail(ErrorCode::kInvalidFieldType, join(join(path, field), port.key()), "tensor references must be integer UIDs");
         if (!tensors.count(uid)) return fail(ErrorCode::kMissingUid, join(join(path, field), port.key()), "tensor reference is unresolved");
         out[port.key()] = uid;
@@ -449,6 +451,7 @@ Status parse_node(Json const& node, std::string const& path, std::map<std::int64
     if (name_it == node.end()) return fail(ErrorCode::kMissingField, join(path, "name"), "required field is missing");
     if (!name_it->is_string()) return fail(ErrorCode::kInvalidFieldType, join(path, "name"), "expected string");
     operation.name = name_it->get<std::string>();
+    if (operation.name.empty() || operation.name.find('\0') != std::string::npos) return fail(ErrorCode::kInvalidValue, join(path, "name"), "node name is empty or contains NUL");
     auto status = parse_ports(node, path, "inputs", schema->inputs, tensors, operation.inputs);
     if (status.is_bad()) return status;
     status = parse_ports(node, path, "outputs", schema->outputs, tensors, operation.outputs);
@@ -468,6 +471,7 @@ Status parse_node(Json const& node, std::string const& path, std::map<std::int64
         if (status.is_bad()) return status;
         operation.attributes[key] = std::move(attribute);
     }
+    if (operation.outputs.empty()) return fail(ErrorCode::kInvalidValue, join(path, "outputs"), "operation must expose at least one serialized output");
     if (schema->tag == OperationTag::kPointwise) {  // lib/Import/SerializedGraphImporter.cpp:1325-1342
         auto const expected = pointwise_input_count(node["mode"].get<std::string>());
         if (operation.inputs.size() != expected || operation.outputs.size() != 1 || !operation.outputs.count("OUT_0"))
@@ -500,8 +504,8 @@ Status validate_document(Json const& root, SerializedGraph& graph) {
     std::int64_t frontend = 0;
     if (!read_int(root["cudnn_frontend_version"], frontend)) return fail(ErrorCode::kInvalidFieldType, "cudnn_frontend_version", "expected integer");
     if (frontend != kPinnedFrontendVersion) return fail(ErrorCode::kFrontendVersionMismatch, "cudnn_frontend_version", "cuDNN Frontend v1.24.0 (12400) is required");
-    if (!root["graph_uid"].is_number_unsigned() && !(root["graph_uid"].is_number_integer() && root["graph_uid"].get<std::int64_t>() >= 0))
-        return fail(ErrorCode::kInvalidFieldType, "graph_uid", "expected unsigned integer");
+    if (!root["graph_uid"].is_number_unsigned() && !root["graph_uid"].is_number_integer()) return fail(ErrorCode::kInvalidFieldType, "graph_uid", "expected unsigned integer");
+    if (!root["graph_uid"].is_number_unsigned() && root["graph_uid"].get<std::int64_t>() < 0) return fail(ErrorCode::kInvalidValue, "graph_uid", "expected a non-negative integer");
     graph.graph_uid = root["graph_uid"].get<std::uint64_t>();
     auto status = parse_context(root, graph.context);
     if (status.is_bad()) return status;
@@ -512,14 +516,15 @@ Status validate_document(Json const& root, SerializedGraph& graph) {
     for (auto it = tensors.begin(); it != tensors.end(); ++it) {
         TensorDesc tensor;
         auto const path = join("tensors", it.key());
+        // a tensor without an assigned UID is keyed by its name (and is then refused below: execution needs UIDs)
+        if (it.value().is_object() && it.value().contains("uid_assigned") && it.value()["uid_assigned"].is_boolean() && !it.value()["uid_assigned"].get<bool>() &&
+            it.value().contains("name") && it.value()["name"].is_string() && it.value()["name"].get<std::string>() != it.key())
+            return fail(ErrorCode::kInvalidValue, path, "name-keyed tensor requires a map key matching tensor.name");
         status = parse_tensor(it.value(), path, tensor);
         if (status.is_bad()) return status;
-        if (it.key() != std::to_string(tensor.uid) && it.key() != tensor.name)
-            return fail(ErrorCode::kInvalidValue, path, "tensor key matches neither its UID nor its name");
-        if (!names.insert(tensor.name).second) return fail(ErrorCode::kInvalidValue, join(path, "name"), "tensor names must be unique");
+        if (it.key() != std::to_string(tensor.uid)) return fail(ErrorCode::kInvalidValue, path, "UID-assigned tensor requires a matching decimal map key");
         if (!graph.tensors.emplace(tensor.uid, std::move(tensor)).second) return fail(ErrorCode::kDuplicateUid, path, "tensor UID is used twice");
     }
-    if (graph.tensors.empty()) return fail(ErrorCode::kInvalidValue, "tensors", "graph has no tensors");
     status = validate_pass_by_values(root, graph);
     if (status.is_bad()) return status;
 
@@ -540,8 +545,6 @@ Status validate_document(Json const& root, SerializedGraph& graph) {
             used.insert(uid);
         }
         for (auto const& [port, uid] : operation.outputs) {
-            if (operation.inputs.end() != std::find_if(operation.inputs.begin(), operation.inputs.end(), [&](auto const& in) { return in.second == uid; }))
-                return fail(ErrorCode::kInvalidValue, join(join(path, "outputs"), port), "a node may not write a tensor it reads");
             if (!producer.emplace(uid, index).second)
                 return fail(ErrorCode::kInvalidValue, join(join(path, "outputs"), port), "tensor is produced by more than one node");
             used.insert(uid);
@@ -555,7 +558,7 @@ Status validate_document(Json const& root, SerializedGraph& graph) {
         if (!used.count(uid) && tensor.is_virtual)  // (an external tensor, or an embedded scalar, that no node reads is legal)
             return fail(ErrorCode::kInvalidValue, "tensors." + std::to_string(uid), "virtual tensor is not referenced by any node");
 
-    for (auto field : {"workspace_modifications", "variant_pack_replacements", "tensors_to_dump"}) {
+    for (auto field : {"workspace_modifications", "variant_pack_replacements"}) {
         status = expect_empty(root, field);
         if (status.is_bad()) return status;
     }
@@ -571,22 +574,30 @@ Status validate_document(Json const& root, SerializedGraph& graph) {
         return fail(ErrorCode::kUnsupportedExecutionMetadata, "context.is_dynamic_shape_enabled", "the single-node convolution graph has static shapes");
     if (single_conv && graph.context.is_override_shape_enabled.value_or(false))
         return fail(ErrorCode::kUnsupportedExecutionMetadata, "context.is_override_shape_enabled", "the single-node convolution graph takes no shape overrides");
-    if (auto it = root.find("fe_workspace_size"); it != root.end()) {
-        std::int64_t size = 0;
-        if (!read_int(*it, size) || size < 0) return fail(ErrorCode::kInvalidFieldType, "fe_workspace_size", "expected non-negative integer");
-        if (single_conv && size != 0) return fail(ErrorCode::kUnsupportedExecutionMetadata, "fe_workspace_size", "a Frontend-owned workspace is not supported");
-    }
-    if (auto it = root.find("behavior_notes"); it != root.end() && !it->is_array())
-        return fail(ErrorCode::kInvalidFieldType, "behavior_notes", "expected array");
-    if (auto it = root.find("variant_pack_uids"); it != root.end()) {
-        std::vector<std::int64_t> listed;
-        status = read_int_array(*it, "variant_pack_uids", listed);
-        if (status.is_bad()) return status;
-        std::set<std::int64_t> expected;
-        for (auto const& [uid, tensor] : graph.tensors)
-            if (!tensor.is_virtual) expected.insert(uid);
-        if (std::set<std::int64_t>(listed.begin(), listed.end()) != expected || listed.size() != expected.size())
-            return fail(ErrorCode::kUnsupportedExecutionMetadata, "variant_pack_uids", "does not list exactly the non-virtual tensors");
+    if (single_conv) {  // the Frontend's execution metadata is pinned for the single-node graph only
+        for (auto const& [uid, tensor] : graph.tensors) {
+            if (tensor.data_type != DataType::kFloat32 && tensor.data_type != DataType::kFloat16 && tensor.data_type != DataType::kBFloat16)
+                return fail(ErrorCode::kUnsupportedDataType, "tensors." + std::to_string(uid) + ".data_type", "the single-node convolution graph takes FLOAT, HALF or BFLOAT16 tensors");
+            if (tensor.dim.size() < 3 || tensor.dim.size() > 5)  // (the reference's single-node path takes rank 4 only; ranks 3 and 5 run here as well)
+                return fail(ErrorCode::kInvalidShape, "tensors." + std::to_string(uid), "the single-node convolution graph requires rank-3 to rank-5 tensors");
+            if (tensor.reordering_type != "NONE")
+                return fail(ErrorCode::kInvalidLayout, "tensors." + std::to_string(uid) + ".reordering_type", "the single-node convolution graph requires NONE reordering");
+        }
+        if (auto it = root.find("fe_workspace_size"); it != root.end()) {
+            std::int64_t size = 0;
+            if (!read_int(*it, size)) return fail(ErrorCode::kInvalidFieldType, "fe_workspace_size", "expected integer");
+            if (size != 0) return fail(ErrorCode::kUnsupportedExecutionMetadata, "fe_workspace_size", "a Frontend-owned workspace is not supported");
+        }
+        if (auto it = root.find("variant_pack_uids"); it != root.end()) {
+            std::vector<std::int64_t> listed;
+            status = read_int_array(*it, "variant_pack_uids", listed);
+            if (status.is_bad()) return status;
+            std::set<std::int64_t> expected;
+            for (auto const& [uid, tensor] : graph.tensors)
+                if (!tensor.is_virtual) expected.insert(uid);
+            if (std::set<std::int64_t>(listed.begin(), listed.end()) != expected || listed.size() != expected.size())
+                return fail(ErrorCode::kUnsupportedExecutionMetadata, "variant_pack_uids", "does not list exactly the non-virtual tensors");
+        }
     }
     return Status::ok();
 }

@@ -62,20 +62,22 @@ def test_accepts_reference_fixture_shape_and_all_five_configs():
     (lambda d: d["tensors"]["1"].update(dim="x"), 7),
     (lambda d: d["tensors"]["1"].update(data_type="COMPLEX"), 10),
     (lambda d: d["tensors"]["1"].update(uid=9), 8),                      # key/UID mismatch
-    (lambda d: d["tensors"]["1"].update(uid_assigned=False), 13),
+    (lambda d: d["tensors"]["1"].update(uid_assigned=False), 8),         # a tensor without a UID is keyed by its name
+    (lambda d: (d["tensors"].update(X=d["tensors"].pop("1")), d["tensors"]["X"].update(uid_assigned=False)), 13),
     (lambda d: d["tensors"]["1"].update(dim=[1, 3, 0, 5]), 15),
     (lambda d: d["tensors"]["1"].update(dim=[2 ** 40, 2 ** 40, 5, 5]), 16),
     (lambda d: d["tensors"]["1"].update(is_pass_by_value=True, pass_by_value=1.0), 7),   # a payload is the Frontend's scalar variant object
     (lambda d: d["tensors"]["1"].update(is_pass_by_value=True), 11),                      # the single-node convolution takes no scalars
-    (lambda d: d["tensors"]["1"].update(reordering_type="F16x16"), 8),
+    (lambda d: d["tensors"]["1"].update(reordering_type="F16x16"), 14),  # a Frontend reordering, not NONE: the single-node graph's layout rule
+    (lambda d: d["tensors"]["1"].update(reordering_type="ZIGZAG"), 8),
     (lambda d: d["nodes"][0].update(tag="LAYER_NORM"), 9),
     (lambda d: d["nodes"][0].update(tag="NOT_A_TAG"), 9),
     (lambda d: d["nodes"][0].pop("math_mode"), 6),
     (lambda d: d["nodes"][0].update(surprise=True), 8),
     (lambda d: d["nodes"][0]["inputs"].update(Z=1), 8),
     (lambda d: d["nodes"][0]["inputs"].update(X=42), 13),
-    (lambda d: d["nodes"][0]["inputs"].update(X="X"), 7),
-    (lambda d: d["nodes"][0]["outputs"].update(Y=1), 8),                 # writes a tensor it reads
+    (lambda d: d["nodes"][0]["inputs"].update(X="X"), 13),               # name references are not accepted
+    (lambda d: d["nodes"][0]["outputs"].update(Y=1), 0),                 # writes a tensor it reads: parsed, refused by the lowering (20)
     (lambda d: d["context"].update(is_dynamic_shape_enabled=True), 11),
     (lambda d: d.update(fe_workspace_size=64), 11),
     (lambda d: d.update(workspace_modifications={"1": [0, 1, 2]}), 11),

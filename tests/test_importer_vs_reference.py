@@ -219,6 +219,69 @@ MUTATIONS = [
 ]
 
 
+def _first(d):
+    return d["tensors"][next(iter(d["tensors"]))]
+
+
+# document, tensor and node structure (every executable benchmark graph x every mutation)
+STRUCTURE_MUTATIONS = {
+    "tensor dim 0": lambda d: _first(d).update(dim=[0] + _first(d)["dim"][1:]),
+    "tensor stride 0": lambda d: _first(d).update(stride=[0] + _first(d)["stride"][1:]),
+    "tensor stride negative": lambda d: _first(d).update(stride=[-1] + _first(d)["stride"][1:]),
+    "tensor rank mismatch": lambda d: _first(d).update(stride=_first(d)["stride"][1:]),
+    "tensor name empty": lambda d: _first(d).update(name=""),
+    "tensor names repeat": lambda d: [v.update(name="SAME") for v in d["tensors"].values()],
+    "tensor without uid": lambda d: _first(d).update(uid_assigned=False),
+    "tensor uid string": lambda d: _first(d).update(uid="1"),
+    "tensor is_virtual null": lambda d: _first(d).update(is_virtual=None),
+    "tensor reordering unknown": lambda d: _first(d).update(reordering_type="WEIRD"),
+    "tensor reordering INT8x32": lambda d: _first(d).update(reordering_type="INT8x32"),
+    "tensor reordering F16x16": lambda d: _first(d).update(reordering_type="F16x16"),
+    "tensor ragged uid alone": lambda d: _first(d).update(ragged_offset_uid=5),
+    "tensor INT8": lambda d: _first(d).update(data_type="INT8"),
+    "tensor DOUBLE": lambda d: _first(d).update(data_type="DOUBLE"),
+    "tensor BOOLEAN": lambda d: _first(d).update(data_type="BOOLEAN"),
+    "tensor type null": lambda d: _first(d).update(data_type=None),
+    "tensor rank 9": lambda d: _first(d).update(dim=[1] * 9, stride=[1] * 9),
+    "tensor rank 65": lambda d: _first(d).update(dim=[1] * 65, stride=[1] * 65),
+    "tensor extents overflow": lambda d: _first(d).update(dim=[1 << 40, 1 << 40], stride=[1 << 40, 1]),
+    "node name missing": lambda d: d["nodes"][0].pop("name"),
+    "node name empty": lambda d: d["nodes"][0].update(name=""),
+    "node inputs list": lambda d: d["nodes"][0].update(inputs=[1]),
+    "node outputs empty": lambda d: d["nodes"][0].update(outputs={}),
+    "node input by name": lambda d: d["nodes"][0]["inputs"].update({next(iter(d["nodes"][0]["inputs"])): "X"}),
+    "node input real": lambda d: d["nodes"][0]["inputs"].update({next(iter(d["nodes"][0]["inputs"])): 1.0}),
+    "nodes empty": lambda d: d.update(nodes=[]),
+    "tensors empty": lambda d: d.update(tensors={}),
+    "graph_uid negative": lambda d: d.update(graph_uid=-1),
+    "graph_uid real": lambda d: d.update(graph_uid=1.5),
+    "backend version integer": lambda d: d.update(cudnn_backend_version=1),
+    "context name integer": lambda d: d["context"].update(name=1),
+    "context sm_count string": lambda d: d["context"].update(sm_count="x"),
+    "context io null": lambda d: d["context"].update(io_data_type=None),
+    "context io unknown": lambda d: d["context"].update(io_data_type="WIDE"),
+    "context override enabled": lambda d: d["context"].update(is_override_shape_enabled=True),
+    "context dynamic null": lambda d: d["context"].update(is_dynamic_shape_enabled=None),
+    "tensors_to_dump": lambda d: d.update(tensors_to_dump=[1]),
+    "behavior_notes object": lambda d: d.update(behavior_notes={}),
+    "variant_pack_uids strings": lambda d: d.update(variant_pack_uids=["a"]),
+    "fe_workspace_size negative": lambda d: d.update(fe_workspace_size=-1),
+    "tensor keyed by name": lambda d: d["tensors"].update({_first(d)["name"]: d["tensors"].pop(next(iter(d["tensors"])))}),
+    "output is also an input": lambda d: d["nodes"][0]["outputs"].update({next(iter(d["nodes"][0]["outputs"])): next(iter(d["nodes"][0]["inputs"].values()))}),
+}
+STRUCTURE_DOCS = {**DOCS, "pointwise_all_modes": graphs.pointwise_all_modes(), "scalar": graphs.scalar_pointwise()}
+
+
+@pytest.mark.parametrize("mutation", sorted(STRUCTURE_MUTATIONS))
+@pytest.mark.parametrize("name", sorted(STRUCTURE_DOCS))
+def test_structure_error_codes_match_the_reference(name, mutation):
+    reference = _reference()
+    doc = copy.deepcopy(STRUCTURE_DOCS[name])
+    STRUCTURE_MUTATIONS[mutation](doc)
+    expected = reference(doc)
+    assert _ours(doc)[0] == expected[0], expected[3]
+
+
 # the same for the attributes of the other executable tags
 ATTRIBUTE_MUTATIONS = [
     ("c4", lambda d: d["nodes"][0].update(diagonal_alignment="CENTER")),
