@@ -3,7 +3,7 @@
 //
 // Every mode of the reference's pointwise_result (lib/Compiler/FoundationalGraph.cpp:2581-2955) goes through
 // pointwise_value below: the same expression, one separately rounded f32 operation per step, with CUDA's full-precision
-// math functions (no fast-math intrinsics). Packed tensors of equal shape (f32 or bf16) take the kernel of four values per
+// math functions (no fast-math intrinsics). Packed tensors of equal shape (f32, f16 or bf16) take the kernel of four values per
 // load; anything else (broadcast, strides, mixed storage types, three inputs, GEN_INDEX) one element per thread, where
 // ADD / MUL / SUB / RELU_FWD / IDENTITY keep a kernel with nothing else in it.
 #include "common.cuh"
@@ -173,6 +173,7 @@ __global__ void pointwise_kernel(const void* a, const void* b, void* out, View a
 template <typename T> struct Quad;
 template <> struct Quad<float> { using type = float4; };
 template <> struct Quad<__nv_bfloat16> { using type = uint2; };
+template <> struct Quad<__half> { using type = ushort4; };  // (a type of its own, so that widen() tells HALF from BFLOAT16)
 
 template <typename T>
 __device__ __forceinline__ typename Quad<T>::type load_quad(const void* p, int64_t i) {
@@ -182,6 +183,10 @@ __device__ __forceinline__ void widen(const float4& r, float (&v)[4]) { v[0] = r
 __device__ __forceinline__ void widen(const uint2& r, float (&v)[4]) {
     v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xffff0000u);
     v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xffff0000u);
+}
+__device__ __forceinline__ void widen(const ushort4& r, float (&v)[4]) {
+    v[0] = __half2float(__ushort_as_half(r.x)); v[1] = __half2float(__ushort_as_half(r.y));
+    v[2] = __half2float(__ushort_as_half(r.z)); v[3] = __half2float(__ushort_as_half(r.w));
 }
 template <typename T>
 __device__ __forceinline__ void store4(void* p, int64_t i, const float (&v)[4]);
@@ -198,9 +203,16 @@ __device__ __forceinline__ void store4<__nv_bfloat16>(void* p, int64_t i, const 
 // Quads of four values a thread keeps in flight: its U quads lie one block-width apart, so that each of a warp's loads
 // stays contiguous; every load is issued before the first value is used. 32 bytes per thread and operand: with 8 (bf16)
 // or 16 (f32) the loads in flight of a full SM do not cover the latency of HBM.
+template <>
+__device__ __forceinline__ void store4<__half>(void* p, int64_t i, const float (&v)[4]) {
+    __half2 lo = __floats2half2_rn(v[0], v[1]), hi = __floats2half2_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p) + i) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+}
+
 template <typename T> struct QuadsInFlight;
 template <> struct QuadsInFlight<float> { static constexpr int value = 2; };
 template <> struct QuadsInFlight<__nv_bfloat16> { static constexpr int value = 4; };
+template <> struct QuadsInFlight<__half> { static constexpr int value = 4; };
 
 constexpr int kPackedThreads = 256;
 
@@ -334,9 +346,11 @@ extern "C" int dfgpu_pointwise(const dfgpu_pointwise_params* p, void* const* ten
                   aligned16(tensors[0]) && aligned16(tensors[2]) && (!binary || aligned16(tensors[1]));
     bool f32_all = p->in0.dtype == DFGPU_F32 && p->out.dtype == DFGPU_F32 && (!binary || p->in1.dtype == DFGPU_F32);
     bool bf16_all = p->in0.dtype == DFGPU_BF16 && p->out.dtype == DFGPU_BF16 && (!binary || p->in1.dtype == DFGPU_BF16);
+    bool f16_all = p->in0.dtype == DFGPU_F16 && p->out.dtype == DFGPU_F16 && (!binary || p->in1.dtype == DFGPU_F16);
     PointwiseScalars s{p->relu_lower, p->relu_upper, p->relu_slope, p->elu_alpha, p->softplus_beta, p->swish_beta, p->axis};
-    if (packed && (f32_all || bf16_all) && inputs <= 2 && p->mode != DFGPU_PW_GEN_INDEX) {
+    if (packed && (f32_all || bf16_all || f16_all) && inputs <= 2 && p->mode != DFGPU_PW_GEN_INDEX) {
         if (f32_all) launch_packed<float>(inputs, tensors[0], tensors[1], tensors[2], p->mode, s, total, stream);
+        else if (f16_all) launch_packed<__half>(inputs, tensors[0], tensors[1], tensors[2], p->mode, s, total, stream);
         else launch_packed<__nv_bfloat16>(inputs, tensors[0], tensors[1], tensors[2], p->mode, s, total, stream);
     } else if (!simple_mode(p->mode)) {
         unsigned grid = static_cast<unsigned>((total + 255) / 256);

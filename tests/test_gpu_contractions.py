@@ -87,7 +87,7 @@ def pointwise_operands(rows, columns):
     return a, b, t
 
 
-@pytest.mark.parametrize("layout", ["packed_f32", "packed_bf16", "broadcast_f32", "broadcast_f16_to_f32"])
+@pytest.mark.parametrize("layout", ["packed_f32", "packed_bf16", "packed_f16", "broadcast_f32", "broadcast_f16_to_f32"])
 @pytest.mark.parametrize("mode_name", dfgpu.PW_MODE_NAMES)
 def test_pointwise_every_mode_against_the_oracle(mode_name, layout):
     """lib/Compiler/FoundationalGraph.cpp:2581-2955: all 50 modes, through both general kernels (four packed values per
@@ -95,8 +95,8 @@ def test_pointwise_every_mode_against_the_oracle(mode_name, layout):
     rows, columns = 24, 40
     a, b, t = pointwise_operands(rows, columns)
     count = dfgpu.pointwise_input_count(mode_name)
-    in_type = {"packed_f32": F32, "packed_bf16": BF16, "broadcast_f32": F32, "broadcast_f16_to_f32": dfgpu.F16}[layout]
-    out_type = BF16 if layout == "packed_bf16" else F32
+    in_type = {"packed_f32": F32, "packed_bf16": BF16, "packed_f16": dfgpu.F16, "broadcast_f32": F32, "broadcast_f16_to_f32": dfgpu.F16}[layout]
+    out_type = {"packed_bf16": BF16, "packed_f16": dfgpu.F16}.get(layout, F32)
     if layout.startswith("packed"):
         bd, td = tensor(in_type, [rows, columns]), tensor(in_type, [rows, columns])
     else:   # B along the columns, T down the rows, A with padded rows
@@ -136,6 +136,8 @@ def test_pointwise_every_mode_against_the_oracle(mode_name, layout):
     out = g.to_host(do, np.uint8)
     if out_type == F32:
         got, want = out.view(np.float32), ref.view(np.float32)
+    elif out_type == dfgpu.F16:
+        got, want = out.view(np.float16).astype(np.float32), ref.view(np.float16).astype(np.float32)
     else:
         got, want = synthetic.bf16_bits_to_f32(out.view(np.uint16)), synthetic.bf16_bits_to_f32(ref.view(np.uint16))
     assert np.array_equal(np.isnan(got), np.isnan(want))
@@ -146,8 +148,9 @@ def test_pointwise_every_mode_against_the_oracle(mode_name, layout):
         ok = finite & ~infinite
         if out_type == F32:
             assert np.all(np.abs(got[ok] - want[ok]) <= 2e-6 + 2e-6 * np.abs(want[ok])), float(np.max(np.abs(got[ok] - want[ok])))
-        else:   # one bf16 step where the f32 values straddle a rounding boundary
-            assert np.all(np.abs(got[ok] - want[ok]) <= 2.0 ** -7 * np.abs(want[ok]) + 1e-30)
+        else:   # one bf16 (f16) step where the f32 values straddle a rounding boundary
+            step = 2.0 ** -7 if out_type == BF16 else 2.0 ** -10
+            assert np.all(np.abs(got[ok] - want[ok]) <= step * np.abs(want[ok]) + (1e-30 if out_type == BF16 else 2.0 ** -24))
     else:
         view = np.uint32 if out_type == F32 else np.uint16
         assert np.array_equal(out.view(view)[finite], ref.view(view)[finite])
